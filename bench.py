@@ -1,0 +1,213 @@
+#!/usr/bin/env python
+"""Headline benchmark: decode & prefill tokens/s of the Qwen3.5-4B-shaped bf16 hybrid model
+(prompt 2048 random ids, 256 greedy decode tokens, batch 1, CUDA-graph decode), on N GPUs of one
+node (N > 1 = tensor parallel, one rank per GPU under torchrun).
+
+A "step" is one whole request: prefill of the 2048-token prompt, then 256 decode steps.  Both
+phases are timed on the device with CUDA events (max over ranks); ``value`` is decode tokens/s,
+``prefill_tok_s`` and TTFT/TPOT are reported beside it.  The ``e2e`` figure runs the same request
+through the public engine API with the prompt copied from pinned host memory and every generated
+token read back to the host, as a serving process does.
+
+``--impl reference`` runs the unmodified reference engine (installed under ``baseline/_ref``) on
+the same shape through its own API instead.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+BASELINE_DECODE_TOK_S = 78.5     # Qwen3.5-4B int8 single-stream decode, Hygon DCU (docs/FACTS-RUNTIME.md:9-16)
+BASELINE_PREFILL_TOK_S = 1729.0
+
+MODEL = "qwen35-4b"
+PROMPT, NEW = 2048, 256
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks / throttle reasons every 200 ms while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int) -> None:
+        self.idx = gpu_index
+        self.proc = None
+        self.path = Path(tempfile.gettempdir()) / f"clocks_{os.getpid()}.csv"
+
+    def start(self) -> None:
+        try:
+            self.fh = open(self.path, "w")
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "200", "-i", str(self.idx)], stdout=self.fh, stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.25)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        self.fh.close()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.path.read_text().splitlines():
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for n, v in zip(names, f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        try:
+            self.path.unlink()
+        except OSError:
+            pass
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def reference_arm(args) -> None:
+    from baseline.reference_bench import run_reference
+    print(json.dumps(run_reference(args)), flush=True)
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=3)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--model", default=MODEL)
+    ap.add_argument("--prompt", type=int, default=PROMPT)
+    ap.add_argument("--new", type=int, default=NEW)
+    ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--no-pdl", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    args = ap.parse_args()
+    sys.path.insert(0, str(ROOT))
+    if args.impl == "reference":
+        reference_arm(args)
+        return
+
+    import torch
+    import torch.distributed as dist
+    from coffin_b200.config import preset
+    from coffin_b200.engine.llm import LLM
+    from coffin_b200.ops import kernels as K
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    W = max(3, args.warmup)
+    cfg = preset(args.model)
+    llm = LLM.from_random(cfg, seed=0, max_seq=args.prompt + args.new + 64, max_num_seqs=1,
+                          tp_world=world, tp_rank=rank, graph=not args.no_graph, pdl=not args.no_pdl,
+                          max_chunk=args.prompt)
+    model = llm.model
+    g = torch.Generator().manual_seed(1234)
+    prompts = [torch.randint(0, cfg.vocab_size, (args.prompt,), generator=g).pin_memory()
+               for _ in range(W + args.steps)]
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---------------- device-timed kernel path ------------------------------------------
+    ev = lambda: torch.cuda.Event(enable_timing=True)
+    pre_ms, dec_ms = [], []
+    launches = 0
+    sampler = ClockSampler(local)
+    for i, p in enumerate(prompts):
+        timed = i >= W
+        if i == W:
+            barrier()
+            if rank == 0:
+                sampler.start()
+            l0 = K.LAUNCHES
+            t_wall = time.perf_counter()
+        e0, e1, e2 = ev(), ev(), ev()
+        dev_prompt = p.cuda(non_blocking=True)
+        e0.record()
+        first = llm.device_prefill(dev_prompt)
+        e1.record()
+        llm.device_decode(first, args.new)
+        e2.record()
+        e2.synchronize()
+        if timed:
+            pre_ms.append(e0.elapsed_time(e1))
+            dec_ms.append(e1.elapsed_time(e2))
+    barrier()
+    wall_s = time.perf_counter() - t_wall
+    clocks = sampler.stop() if rank == 0 else {}
+    launches = (K.LAUNCHES - l0) + llm.graph_launches_replayed
+    K.check_status()
+    stats = torch.tensor([sum(pre_ms), sum(dec_ms)], dtype=torch.float64, device="cuda")
+    if world > 1:
+        dist.all_reduce(stats, op=dist.ReduceOp.MAX)
+    pre_total, dec_total = stats.tolist()
+    steps = args.steps
+    decode_tok_s = args.new * steps / (dec_total / 1e3)
+    prefill_tok_s = args.prompt * steps / (pre_total / 1e3)
+
+    # ---------------- end to end through the public API ---------------------------------
+    e2e = None
+    if not args.no_e2e:
+        e2e_dec, e2e_pre = [], []
+        for i, p in enumerate(prompts[: max(3, min(W, 3)) + steps]):
+            out = llm.generate(p, max_new_tokens=args.new, ignore_eos=True)
+            if i >= len(prompts[: max(3, min(W, 3)) + steps]) - steps:
+                e2e_dec.append(out.decode_ms)
+                e2e_pre.append(out.prefill_ms)
+        s2 = torch.tensor([sum(e2e_pre), sum(e2e_dec)], dtype=torch.float64, device="cuda")
+        if world > 1:
+            dist.all_reduce(s2, op=dist.ReduceOp.MAX)
+        e2e = {"value": args.new * steps / (s2[1].item() / 1e3), "unit": "decode tok/s",
+               "prefill_tok_s": args.prompt * steps / (s2[0].item() / 1e3),
+               "h2d_bytes_per_step": args.prompt * 8 + args.new * 8,
+               "d2h_bytes_per_step": (args.new + 1) * 8,
+               "timing": "host wall clock around LLM.generate phases, prompt from pinned memory, "
+                         "every token read back"}
+    if rank == 0:
+        line = {
+            "metric": "decode_tok_s", "value": decode_tok_s, "unit": "tok/s", "n_gpus": world,
+            "steps": steps, "warmup": W, "ms_per_step": (pre_total + dec_total) / steps,
+            "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": decode_tok_s / BASELINE_DECODE_TOK_S, "dtype": "bf16", "data": "synthetic",
+            "prefill_tok_s": prefill_tok_s, "prefill_vs_baseline": prefill_tok_s / BASELINE_PREFILL_TOK_S,
+            "ttft_ms_p50": statistics.median(pre_ms), "tpot_ms_p50": statistics.median(dec_ms) / args.new,
+            "config": {"model": args.model, "global_batch": 1, "seq_len": args.prompt, "decode_tokens": args.new,
+                       "parallelism": f"tp{world}" if world > 1 else "single", "cuda_graph": not args.no_graph,
+                       "cache": "weights (7.9 GB) far exceed the 126 MB L2, no flush needed",
+                       "weights": "random-init N(0,0.02)"},
+            "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "wall_s": wall_s, "impl": "ours",
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,514 @@
+// Gated GQA softmax attention over a paged bf16 KV pool.
+//
+//  * attn_prep:    per-head q/k RMSNorm + partial rotary + K/V append to the pool (prefill rows).
+//  * attn_prefill: causal flash attention, one CTA per (64-query tile, q head), tensor-core
+//                  QK^T and PV (bf16 mma, fp32 softmax state), sigmoid output gate in the epilogue.
+//                  Also serves speculative verification (a few queries per row, causal among them).
+//  * attn_decode:  one query per row, split over key tiles; the CTA that owns the tile holding
+//                  the current position also norms/rotates/appends this token's K/V, so a decode
+//                  layer needs no separate rope / kv-store launches.
+//  * attn_combine: merges the split partials and applies the gate.
+// The reference has decode kernels (backends/corex/kernels/attn.cu:370-566: slice + combine over
+// an int8 cache through pos2slot) but prefill attention is torch code
+// (models/qwen35/full_attn.py:658-789); rope, kv_quant and kv_pool_store are separate launches
+// there (attn.cu:132,249,1200).  The pool here is [slots, nkv, hd] per layer, addressed through
+// a per-row block table (block = 64 tokens).
+#include "common.cuh"
+
+namespace {
+
+constexpr int kBlock = 64;  // tokens per KV block == key tile
+
+// ------------------------------------------------------------------------------------------
+// q/k norm + rope (+ KV append) for prefill rows. One warp per (token, head).
+struct PrepArgs {
+  const bf16* proj; int64_t ldp;     // [T, ldp]: (q|gate) per head, then k heads, then v heads
+  const float* qg; const float* kg;  // [hd] gains (1 + w)
+  const float* cos; const float* sin;  // [rows, rot]
+  const int* rope_idx;               // [T] row of cos/sin per token (null: t)
+  const int* kv_slot;                // [T] flat pool slot per token
+  bf16* q_out;                       // [T, nh, hd]
+  bf16* kpool; bf16* vpool;          // [slots, nkv, hd]
+  int T, nh, nkv, rot;
+  float eps;
+};
+
+template <int HD>
+__device__ __forceinline__ void norm_rope_lane(float* x, const float* gain, const float* cs, const float* sn,
+                                               int rot, float eps, int lane) {
+  // x: this lane's HD/32 contiguous elements [lane*EPL, ...)
+  constexpr int EPL = HD / 32;
+  float ss = 0.f;
+#pragma unroll
+  for (int e = 0; e < EPL; ++e) ss += x[e] * x[e];
+  const float r = rsqrtf(warp_sum(ss) / (float)HD + eps);
+#pragma unroll
+  for (int e = 0; e < EPL; ++e) x[e] *= r * gain[lane * EPL + e];
+  const int half = rot >> 1, plane = half / EPL;  // lanes per half
+#pragma unroll
+  for (int e = 0; e < EPL; ++e) {
+    const float other = __shfl_xor_sync(0xffffffffu, x[e], plane);
+    const int i = lane * EPL + e;
+    if (i < rot) {
+      const float c = cs[i], s = sn[i];
+      x[e] = (i < half) ? x[e] * c - other * s : x[e] * c + other * s;
+    }
+  }
+}
+
+template <int HD>
+__global__ void __launch_bounds__(256) attn_prep_kernel(const PrepArgs a) {
+  constexpr int EPL = HD / 32;
+  griddep_wait();
+  griddep_launch();
+  const int lane = threadIdx.x & 31;
+  const int64_t task = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+  const int per = a.nh + 2 * a.nkv;
+  if (task >= (int64_t)a.T * per) return;
+  const int t = task / per, hh = task % per;
+  const bf16* prow = a.proj + (int64_t)t * a.ldp;
+  const int ridx = a.rope_idx ? a.rope_idx[t] : t;
+  const float* cs = a.cos + (int64_t)ridx * a.rot;
+  const float* sn = a.sin + (int64_t)ridx * a.rot;
+  float x[EPL];
+  if (hh < a.nh) {
+    const bf16* src = prow + (int64_t)hh * 2 * HD + lane * EPL;
+#pragma unroll
+    for (int e = 0; e < EPL; ++e) x[e] = __bfloat162float(src[e]);
+    norm_rope_lane<HD>(x, a.qg, cs, sn, a.rot, a.eps, lane);
+    bf16* dst = a.q_out + ((int64_t)t * a.nh + hh) * HD + lane * EPL;
+#pragma unroll
+    for (int e = 0; e < EPL; ++e) dst[e] = __float2bfloat16(x[e]);
+  } else if (hh < a.nh + a.nkv) {
+    const int kh = hh - a.nh;
+    const bf16* src = prow + (int64_t)a.nh * 2 * HD + (int64_t)kh * HD + lane * EPL;
+#pragma unroll
+    for (int e = 0; e < EPL; ++e) x[e] = __bfloat162float(src[e]);
+    norm_rope_lane<HD>(x, a.kg, cs, sn, a.rot, a.eps, lane);
+    bf16* dst = a.kpool + ((int64_t)a.kv_slot[t] * a.nkv + kh) * HD + lane * EPL;
+#pragma unroll
+    for (int e = 0; e < EPL; ++e) dst[e] = __float2bfloat16(x[e]);
+  } else {
+    const int vh = hh - a.nh - a.nkv;
+    const bf16* src = prow + (int64_t)a.nh * 2 * HD + (int64_t)(a.nkv + vh) * HD + lane * EPL;
+    bf16* dst = a.vpool + ((int64_t)a.kv_slot[t] * a.nkv + vh) * HD + lane * EPL;
+#pragma unroll
+    for (int e = 0; e < EPL; ++e) dst[e] = src[e];
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+// Prefill flash attention (bf16 mma.m16n8k16, 4 warps x 16 query rows, 64-key tiles).
+__device__ __forceinline__ void ldsm_x4(uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3, const void* p) {
+  const uint32_t addr = (uint32_t)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_t(uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3, const void* p) {
+  const uint32_t addr = (uint32_t)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
+  const uint32_t addr = (uint32_t)__cvta_generic_to_shared(smem);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(addr), "l"(gmem));
+}
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+
+struct PrefillArgs {
+  const bf16* q;            // [T, nh, hd]
+  const bf16* gate; int64_t ldg;  // gate of head h at gate[t*ldg + h*2*hd + hd + d]
+  const bf16* kpool; const bf16* vpool;  // [slots, nkv, hd]
+  const int* block_table;   // [nblocks] pool block ids of this sequence
+  bf16* out; int64_t ldo;   // [T, nh*hd]
+  int T, q_pos0, nh, nkv;
+  float scale_log2;         // hd^-0.5 * log2(e)
+};
+
+template <int HD>
+__global__ void __launch_bounds__(128) attn_prefill_kernel(const PrefillArgs a) {
+  constexpr int LD = HD + 8;  // padded row (bf16 elements): 16-byte odd multiple -> conflict-free ldmatrix
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  bf16* Qs = reinterpret_cast<bf16*>(smem_raw);  // [64][LD]
+  bf16* Ks = Qs + 64 * LD;
+  bf16* Vs = Ks + 64 * LD;
+  griddep_wait();
+  griddep_launch();
+  const int qt = blockIdx.x, h = blockIdx.y, kvh = h / (a.nh / a.nkv);
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, tq = lane & 3;
+  constexpr int CPR = HD / 8;  // 16-byte chunks per row
+  for (int idx = tid; idx < 64 * CPR; idx += 128) {
+    const int r = idx / CPR, c = idx % CPR;
+    const int t = qt * 64 + r;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (t < a.T) v = *reinterpret_cast<const uint4*>(a.q + ((int64_t)t * a.nh + h) * HD + c * 8);
+    *reinterpret_cast<uint4*>(Qs + r * LD + c * 8) = v;
+  }
+  float o[HD / 8][4];
+#pragma unroll
+  for (int n = 0; n < HD / 8; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+  float mrow[2] = {-INFINITY, -INFINITY}, lrow[2] = {0.f, 0.f};
+  const int qpos_lo = a.q_pos0 + qt * 64 + warp * 16 + g;  // position of row g (row g+8: +8)
+  const int last_q = min(a.T - 1, qt * 64 + 63);
+  const int kv_end = a.q_pos0 + last_q + 1;               // keys visible to this tile: [0, kv_end)
+  const int ntiles = (kv_end + kBlock - 1) / kBlock;
+
+  for (int kt = 0; kt < ntiles; ++kt) {
+    __syncthreads();  // previous tile fully consumed (also orders the Q store before first use)
+    const int64_t slot0 = (int64_t)a.block_table[kt] * kBlock;
+    for (int idx = tid; idx < 64 * CPR; idx += 128) {
+      const int r = idx / CPR, c = idx % CPR;
+      const int64_t off = ((slot0 + r) * a.nkv + kvh) * HD + c * 8;
+      cp_async16(Ks + r * LD + c * 8, a.kpool + off);
+      cp_async16(Vs + r * LD + c * 8, a.vpool + off);
+    }
+    cp_async_wait_all();
+    __syncthreads();
+    // ---- S = Q K^T (16 x 64 per warp) --------------------------------------------------
+    float s[8][4];
+#pragma unroll
+    for (int n = 0; n < 8; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
+#pragma unroll 4
+    for (int kk = 0; kk < HD / 16; ++kk) {
+      uint32_t af[4];
+      ldsm_x4(af[0], af[1], af[2], af[3], Qs + (warp * 16 + (lane & 15)) * LD + kk * 16 + (lane >> 4) * 8);
+#pragma unroll
+      for (int np = 0; np < 4; ++np) {
+        uint32_t b0, b1, b2, b3;
+        ldsm_x4(b0, b1, b2, b3, Ks + (np * 16 + (lane & 7) + ((lane >> 4) << 3)) * LD + kk * 16 + ((lane >> 3) & 1) * 8);
+        mma_bf16(s[2 * np], af, b0, b1);
+        mma_bf16(s[2 * np + 1], af, b2, b3);
+      }
+    }
+    // ---- mask + online softmax (base-2) --------------------------------------------------
+    float mnew[2] = {mrow[0], mrow[1]};
+#pragma unroll
+    for (int n = 0; n < 8; ++n)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int key = kt * kBlock + n * 8 + tq * 2 + (e & 1);
+        const int qp = qpos_lo + ((e >> 1) << 3);
+        const float v = (key <= qp) ? s[n][e] * a.scale_log2 : -INFINITY;
+        s[n][e] = v;
+        mnew[e >> 1] = fmaxf(mnew[e >> 1], v);
+      }
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      mnew[r] = fmaxf(mnew[r], __shfl_xor_sync(0xffffffffu, mnew[r], 1));
+      mnew[r] = fmaxf(mnew[r], __shfl_xor_sync(0xffffffffu, mnew[r], 2));
+    }
+    float corr[2], msafe[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      msafe[r] = (mnew[r] == -INFINITY) ? 0.f : mnew[r];
+      corr[r] = exp2f(mrow[r] - msafe[r]);  // mrow = -inf -> 0
+      mrow[r] = mnew[r];
+    }
+    float lsum[2] = {0.f, 0.f};
+    uint32_t pf[4][4];
+#pragma unroll
+    for (int n = 0; n < 8; ++n) {
+      const float p0 = exp2f(s[n][0] - msafe[0]), p1 = exp2f(s[n][1] - msafe[0]);
+      const float p2 = exp2f(s[n][2] - msafe[1]), p3 = exp2f(s[n][3] - msafe[1]);
+      lsum[0] += p0 + p1;
+      lsum[1] += p2 + p3;
+      pf[n >> 1][(n & 1) * 2] = pack_bf162(p0, p1);
+      pf[n >> 1][(n & 1) * 2 + 1] = pack_bf162(p2, p3);
+    }
+    lrow[0] = lrow[0] * corr[0] + lsum[0];
+    lrow[1] = lrow[1] * corr[1] + lsum[1];
+#pragma unroll
+    for (int n = 0; n < HD / 8; ++n) {
+      o[n][0] *= corr[0]; o[n][1] *= corr[0]; o[n][2] *= corr[1]; o[n][3] *= corr[1];
+    }
+    // ---- O += P V ----------------------------------------------------------------------------
+#pragma unroll
+    for (int kk = 0; kk < 4; ++kk) {
+#pragma unroll
+      for (int np = 0; np < HD / 16; ++np) {
+        uint32_t b0, b1, b2, b3;
+        ldsm_x4_t(b0, b1, b2, b3, Vs + (kk * 16 + (lane & 15)) * LD + np * 16 + (lane >> 4) * 8);
+        mma_bf16(o[2 * np], pf[kk], b0, b1);
+        mma_bf16(o[2 * np + 1], pf[kk], b2, b3);
+      }
+    }
+  }
+  // ---- epilogue: normalise, gate, store ---------------------------------------------------
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    lrow[r] += __shfl_xor_sync(0xffffffffu, lrow[r], 1);
+    lrow[r] += __shfl_xor_sync(0xffffffffu, lrow[r], 2);
+  }
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    const int t = qt * 64 + warp * 16 + g + r * 8;
+    if (t >= a.T) continue;
+    const float inv = lrow[r] > 0.f ? 1.f / lrow[r] : 0.f;
+    const bf16* gp = a.gate + (int64_t)t * a.ldg + (int64_t)h * 2 * HD + HD;
+    bf16* op = a.out + (int64_t)t * a.ldo + (int64_t)h * HD;
+#pragma unroll
+    for (int n = 0; n < HD / 8; ++n) {
+      const int d = n * 8 + tq * 2;
+      const float g0 = sigmoid_f(__bfloat162float(gp[d])), g1 = sigmoid_f(__bfloat162float(gp[d + 1]));
+      *reinterpret_cast<uint32_t*>(op + d) = pack_bf162(o[n][r * 2] * inv * g0, o[n][r * 2 + 1] * inv * g1);
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+// Decode: one query per row, split over strided key tiles.
+struct DecodeArgs {
+  const bf16* proj; int64_t ldp;      // [M, ldp] fused q|gate, k, v projection of this token
+  const float* qg; const float* kg;   // norm gains
+  const float* cos; const float* sin; // [max_pos, rot] tables
+  const int* positions;               // [M] token index (KV slot index / causal bound)
+  const int* rope_pos;                // [M] rotary position (token index + rope delta)
+  const int* block_table; int64_t ldbt;  // [M, ldbt]
+  bf16* kpool; bf16* vpool;
+  float* part_o;                      // [M, nh, nsplit, hd]
+  float* part_ml;                     // [M, nh, nsplit, 2]
+  int nh, nkv, rot, nsplit;
+  float scale_log2, eps;
+};
+
+template <int HD, int REP>
+__global__ void __launch_bounds__(128) attn_decode_kernel(const DecodeArgs a) {
+  constexpr int EPL = HD / 32;
+  __shared__ float q_s[REP][HD];
+  __shared__ float mo[4][REP][HD];
+  __shared__ float mml[4][REP][2];
+  const int kvh = blockIdx.x, split = blockIdx.y, m = blockIdx.z;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  griddep_wait();
+  griddep_launch();
+  const int pos = a.positions[m];
+  float* po = a.part_o + (((int64_t)m * a.nh + kvh * REP) * a.nsplit + split) * HD;
+  float* pml = a.part_ml + (((int64_t)m * a.nh + kvh * REP) * a.nsplit + split) * 2;
+  if (pos < 0) {  // padded row
+    for (int i = tid; i < REP * 2; i += 128) pml[(int64_t)(i >> 1) * a.nsplit * 2 + (i & 1)] = (i & 1) ? 0.f : -INFINITY;
+    return;
+  }
+  const bf16* prow = a.proj + (int64_t)m * a.ldp;
+  const int rp = a.rope_pos[m];
+  const float* cs = a.cos + (int64_t)rp * a.rot;
+  const float* sn = a.sin + (int64_t)rp * a.rot;
+  // q heads of this kv group: norm + rope -> shared (pre-scaled for base-2 softmax)
+  for (int r = warp; r < REP; r += 4) {
+    float x[EPL];
+    const bf16* src = prow + (int64_t)(kvh * REP + r) * 2 * HD + lane * EPL;
+#pragma unroll
+    for (int e = 0; e < EPL; ++e) x[e] = __bfloat162float(src[e]);
+    norm_rope_lane<HD>(x, a.qg, cs, sn, a.rot, a.eps, lane);
+#pragma unroll
+    for (int e = 0; e < EPL; ++e) q_s[r][lane * EPL + e] = x[e] * a.scale_log2;
+  }
+  const int ntiles = pos / kBlock + 1;
+  const int* bt = a.block_table + (int64_t)m * a.ldbt;
+  // the split that owns the tile holding `pos` appends this token's K/V first
+  if ((pos / kBlock) % a.nsplit == split) {
+    const int64_t slot = (int64_t)bt[pos / kBlock] * kBlock + pos % kBlock;
+    if (warp == 0) {
+      float x[EPL];
+      const bf16* src = prow + (int64_t)a.nh * 2 * HD + (int64_t)kvh * HD + lane * EPL;
+#pragma unroll
+      for (int e = 0; e < EPL; ++e) x[e] = __bfloat162float(src[e]);
+      norm_rope_lane<HD>(x, a.kg, cs, sn, a.rot, a.eps, lane);
+      bf16* dst = a.kpool + (slot * a.nkv + kvh) * HD + lane * EPL;
+#pragma unroll
+      for (int e = 0; e < EPL; ++e) dst[e] = __float2bfloat16(x[e]);
+    } else if (warp == 1) {
+      const bf16* src = prow + (int64_t)a.nh * 2 * HD + (int64_t)(a.nkv + kvh) * HD + lane * EPL;
+      bf16* dst = a.vpool + (slot * a.nkv + kvh) * HD + lane * EPL;
+#pragma unroll
+      for (int e = 0; e < EPL; ++e) dst[e] = src[e];
+    }
+    __threadfence_block();
+  }
+  __syncthreads();
+  float q[REP][EPL], o[REP][EPL], mx[REP], l[REP];
+#pragma unroll
+  for (int r = 0; r < REP; ++r) {
+    mx[r] = -INFINITY; l[r] = 0.f;
+#pragma unroll
+    for (int e = 0; e < EPL; ++e) { q[r][e] = q_s[r][lane * EPL + e]; o[r][e] = 0.f; }
+  }
+  for (int kt = split; kt < ntiles; kt += a.nsplit) {
+    const int64_t slot0 = (int64_t)bt[kt] * kBlock;
+    const int nkeys = min(kBlock, pos + 1 - kt * kBlock);
+    for (int i0 = warp; i0 < nkeys; i0 += 8) {
+      // two keys per iteration for memory-level parallelism
+      const int i1 = i0 + 4;
+      const bool has1 = i1 < nkeys;
+      float kf0[EPL], kf1[EPL], vf0[EPL], vf1[EPL];
+      const bf16* k0 = a.kpool + ((slot0 + i0) * a.nkv + kvh) * HD + lane * EPL;
+      const bf16* v0 = a.vpool + ((slot0 + i0) * a.nkv + kvh) * HD + lane * EPL;
+      const bf16* k1 = has1 ? a.kpool + ((slot0 + i1) * a.nkv + kvh) * HD + lane * EPL : k0;
+      const bf16* v1 = has1 ? a.vpool + ((slot0 + i1) * a.nkv + kvh) * HD + lane * EPL : v0;
+      if (EPL == 8) {
+        bf16x8_to_float(*reinterpret_cast<const uint4*>(k0), kf0);
+        bf16x8_to_float(*reinterpret_cast<const uint4*>(k1), kf1);
+        bf16x8_to_float(*reinterpret_cast<const uint4*>(v0), vf0);
+        bf16x8_to_float(*reinterpret_cast<const uint4*>(v1), vf1);
+      } else {
+#pragma unroll
+        for (int e = 0; e < EPL; ++e) {
+          kf0[e] = __bfloat162float(k0[e]); kf1[e] = __bfloat162float(k1[e]);
+          vf0[e] = __bfloat162float(v0[e]); vf1[e] = __bfloat162float(v1[e]);
+        }
+      }
+#pragma unroll
+      for (int r = 0; r < REP; ++r) {
+        float d0 = 0.f, d1 = 0.f;
+#pragma unroll
+        for (int e = 0; e < EPL; ++e) { d0 = fmaf(q[r][e], kf0[e], d0); d1 = fmaf(q[r][e], kf1[e], d1); }
+        d0 = warp_sum(d0);
+        d1 = has1 ? warp_sum(d1) : -INFINITY;
+        if (!has1) d1 = -INFINITY;
+        const float mn = fmaxf(mx[r], fmaxf(d0, d1));
+        const float c = exp2f(mx[r] - mn), p0 = exp2f(d0 - mn), p1 = exp2f(d1 - mn);
+        l[r] = l[r] * c + p0 + p1;
+        mx[r] = mn;
+#pragma unroll
+        for (int e = 0; e < EPL; ++e) o[r][e] = o[r][e] * c + p0 * vf0[e] + p1 * vf1[e];
+      }
+    }
+  }
+  // ---- merge the 4 warps ------------------------------------------------------------------
+#pragma unroll
+  for (int r = 0; r < REP; ++r) {
+#pragma unroll
+    for (int e = 0; e < EPL; ++e) mo[warp][r][lane * EPL + e] = o[r][e];
+    if (lane == 0) { mml[warp][r][0] = mx[r]; mml[warp][r][1] = l[r]; }
+  }
+  __syncthreads();
+  for (int idx = tid; idx < REP * HD; idx += 128) {
+    const int r = idx / HD, d = idx % HD;
+    float M4 = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) M4 = fmaxf(M4, mml[w][r][0]);
+    float acc = 0.f, L = 0.f;
+    if (M4 > -INFINITY) {
+#pragma unroll
+      for (int w = 0; w < 4; ++w) {
+        const float c = exp2f(mml[w][r][0] - M4);
+        acc += mo[w][r][d] * c;
+        L += mml[w][r][1] * c;
+      }
+    }
+    po[(int64_t)r * a.nsplit * HD + d] = acc;
+    if (d == 0) {
+      pml[(int64_t)r * a.nsplit * 2] = M4;
+      pml[(int64_t)r * a.nsplit * 2 + 1] = L;
+    }
+  }
+}
+
+template <int HD>
+__global__ void __launch_bounds__(HD) attn_combine_kernel(const float* part_o, const float* part_ml,
+                                                          const bf16* proj, int64_t ldp, bf16* out, int64_t ldo,
+                                                          int nh, int nsplit) {
+  griddep_wait();
+  griddep_launch();
+  const int h = blockIdx.x, m = blockIdx.y, d = threadIdx.x;
+  const float* po = part_o + ((int64_t)m * nh + h) * nsplit * HD;
+  const float* pml = part_ml + ((int64_t)m * nh + h) * nsplit * 2;
+  float M = -INFINITY;
+  for (int s = 0; s < nsplit; ++s) M = fmaxf(M, pml[s * 2]);
+  float acc = 0.f, L = 0.f;
+  if (M > -INFINITY)
+    for (int s = 0; s < nsplit; ++s) {
+      const float c = exp2f(pml[s * 2] - M);
+      acc += po[(int64_t)s * HD + d] * c;
+      L += pml[s * 2 + 1] * c;
+    }
+  const float g = sigmoid_f(__bfloat162float(proj[(int64_t)m * ldp + (int64_t)h * 2 * HD + HD + d]));
+  out[(int64_t)m * ldo + (int64_t)h * HD + d] = __float2bfloat16(L > 0.f ? acc / L * g : 0.f);
+}
+
+template <int HD, int REP>
+int launch_decode(const DecodeArgs& a, int M, cudaStream_t st) {
+  return (int)cb_launch(attn_decode_kernel<HD, REP>, dim3((unsigned)a.nkv, (unsigned)a.nsplit, (unsigned)M),
+                        dim3(128), 0, st, a);
+}
+
+}  // namespace
+
+CB_EXPORT int cb_attn_prep(const void* proj, int64_t ldp, const void* qg, const void* kg, const void* cos,
+                           const void* sin, const void* rope_idx, const void* kv_slot, void* q_out,
+                           void* kpool, void* vpool, int64_t T, int64_t nh, int64_t nkv, int64_t hd,
+                           int64_t rot, float eps, void* stream) {
+  if (T == 0) return 0;
+  PrepArgs a{(const bf16*)proj, ldp, (const float*)qg, (const float*)kg, (const float*)cos, (const float*)sin,
+             (const int*)rope_idx, (const int*)kv_slot, (bf16*)q_out, (bf16*)kpool, (bf16*)vpool,
+             (int)T, (int)nh, (int)nkv, (int)rot, eps};
+  const int64_t tasks = T * (nh + 2 * nkv);
+  dim3 grid((unsigned)((tasks + 7) / 8));
+  if (hd == 256 && (rot / 2) % 8 == 0) return (int)cb_launch(attn_prep_kernel<256>, grid, dim3(256), 0, (cudaStream_t)stream, a);
+  if (hd == 64 && (rot / 2) % 2 == 0) return (int)cb_launch(attn_prep_kernel<64>, grid, dim3(256), 0, (cudaStream_t)stream, a);
+  return CB_ERR_SHAPE;
+}
+
+CB_EXPORT int cb_attn_prefill(const void* q, const void* gate, int64_t ldg, const void* kpool, const void* vpool,
+                              const void* block_table, void* out, int64_t ldo, int64_t T, int64_t q_pos0,
+                              int64_t nh, int64_t nkv, int64_t hd, void* stream) {
+  if (T == 0) return 0;
+  PrefillArgs a{(const bf16*)q, (const bf16*)gate, ldg, (const bf16*)kpool, (const bf16*)vpool,
+                (const int*)block_table, (bf16*)out, ldo, (int)T, (int)q_pos0, (int)nh, (int)nkv,
+                1.4426950408889634f / sqrtf((float)hd)};
+  dim3 grid((unsigned)((T + 63) / 64), (unsigned)nh);
+  const size_t smem = (size_t)3 * 64 * (hd + 8) * sizeof(bf16);
+  cudaError_t e;
+  if (hd == 256) {
+    e = cudaFuncSetAttribute(attn_prefill_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    return (int)cb_launch(attn_prefill_kernel<256>, grid, dim3(128), smem, (cudaStream_t)stream, a);
+  }
+  if (hd == 64) return (int)cb_launch(attn_prefill_kernel<64>, grid, dim3(128), smem, (cudaStream_t)stream, a);
+  return CB_ERR_SHAPE;
+}
+
+CB_EXPORT int cb_attn_decode(const void* proj, int64_t ldp, const void* qg, const void* kg, const void* cos,
+                             const void* sin, const void* positions, const void* rope_pos,
+                             const void* block_table, int64_t ldbt, void* kpool, void* vpool, void* part_o,
+                             void* part_ml, void* out, int64_t ldo, int64_t M, int64_t nh, int64_t nkv,
+                             int64_t hd, int64_t rot, int64_t nsplit, float eps, void* stream) {
+  if (M == 0) return 0;
+  if (nh % nkv || nsplit < 1) return CB_ERR_SHAPE;
+  DecodeArgs a{(const bf16*)proj, ldp, (const float*)qg, (const float*)kg, (const float*)cos, (const float*)sin,
+               (const int*)positions, (const int*)rope_pos, (const int*)block_table, ldbt, (bf16*)kpool,
+               (bf16*)vpool, (float*)part_o, (float*)part_ml, (int)nh, (int)nkv, (int)rot, (int)nsplit,
+               1.4426950408889634f / sqrtf((float)hd), eps};
+  cudaStream_t st = (cudaStream_t)stream;
+  const int rep = (int)(nh / nkv);
+  int rc = CB_ERR_SHAPE;
+  if (hd == 256 && (rot / 2) % 8 == 0) {
+    switch (rep) {
+      case 1: rc = launch_decode<256, 1>(a, (int)M, st); break;
+      case 2: rc = launch_decode<256, 2>(a, (int)M, st); break;
+      case 3: rc = launch_decode<256, 3>(a, (int)M, st); break;
+      case 4: rc = launch_decode<256, 4>(a, (int)M, st); break;
+      case 6: rc = launch_decode<256, 6>(a, (int)M, st); break;
+      case 8: rc = launch_decode<256, 8>(a, (int)M, st); break;
+      default: return CB_ERR_SHAPE;
+    }
+  } else if (hd == 64 && (rot / 2) % 2 == 0) {
+    switch (rep) {
+      case 1: rc = launch_decode<64, 1>(a, (int)M, st); break;
+      case 2: rc = launch_decode<64, 2>(a, (int)M, st); break;
+      case 4: rc = launch_decode<64, 4>(a, (int)M, st); break;
+      default: return CB_ERR_SHAPE;
+    }
+  }
+  if (rc) return rc;
+  dim3 grid((unsigned)nh, (unsigned)M);
+  if (hd == 256)
+    return (int)cb_launch(attn_combine_kernel<256>, grid, dim3(256), 0, st, (const float*)part_o,
+                          (const float*)part_ml, (const bf16*)proj, ldp, (bf16*)out, ldo, (int)nh, (int)nsplit);
+  return (int)cb_launch(attn_combine_kernel<64>, grid, dim3(64), 0, st, (const float*)part_o,
+                        (const float*)part_ml, (const bf16*)proj, ldp, (bf16*)out, ldo, (int)nh, (int)nsplit);
+}

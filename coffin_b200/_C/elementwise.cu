@@ -1,0 +1,231 @@
+// Row-wise memory-bound kernels: embedding gather, (residual add +) RMSNorm, SwiGLU, argmax,
+// temperature sampling, block copies.  One CTA per row, 16-byte vector accesses, fp32 math.
+// Roles in the reference: TiedEmbedding.lookup (ops/embed.py:70-145), rms_norm / add_rms_norm
+// (backends/corex/kernels/norm.cu:132-206), silu_mul (attn.cu:201), the torch argmax /
+// multinomial of ModelRunner.sample (engine/model_runner.py:900-924), PagedKVCache.copy_block.
+#include "common.cuh"
+
+int g_cb_use_pdl = 0;
+CB_EXPORT int cb_set_pdl(int64_t on) { g_cb_use_pdl = on ? 1 : 0; return 0; }
+CB_EXPORT int cb_version() { return 1; }
+
+namespace {
+
+__global__ void embed_gather_kernel(const bf16* __restrict__ table, const int64_t* __restrict__ tokens,
+                                    bf16* __restrict__ out, int64_t H, int64_t V) {
+  griddep_wait();
+  griddep_launch();
+  int64_t tok = tokens[blockIdx.x];
+  if (tok < 0 || tok >= V) tok = 0;
+  const uint4* src = reinterpret_cast<const uint4*>(table + tok * H);
+  uint4* dst = reinterpret_cast<uint4*>(out + (int64_t)blockIdx.x * H);
+  for (int64_t c = threadIdx.x; c < (H >> 3); c += blockDim.x) dst[c] = src[c];
+}
+
+// out = rmsnorm(x [+ add]) * gain ; optionally writes the sum back (res_out may alias x here:
+// one CTA owns the whole row).
+__global__ void rmsnorm_kernel(const bf16* __restrict__ x, const bf16* __restrict__ add,
+                               const float* __restrict__ gain, bf16* __restrict__ res_out,
+                               bf16* __restrict__ out, int64_t N, int64_t ldx, int64_t ldo, float eps) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  float* row = reinterpret_cast<float*>(smem_raw);  // [N]
+  __shared__ float red[32];
+  griddep_wait();
+  griddep_launch();
+  const int64_t r = blockIdx.x;
+  float ss = 0.f;
+  for (int64_t c = threadIdx.x; c < (N >> 3); c += blockDim.x) {
+    float f[8], g[8];
+    bf16x8_to_float(*reinterpret_cast<const uint4*>(x + r * ldx + c * 8), f);
+    if (add) {
+      bf16x8_to_float(*reinterpret_cast<const uint4*>(add + r * ldx + c * 8), g);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) f[i] = __bfloat162float(__float2bfloat16(f[i] + g[i]));
+      if (res_out) *reinterpret_cast<uint4*>(res_out + r * ldx + c * 8) = float_to_bf16x8(f);
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) { row[c * 8 + i] = f[i]; ss += f[i] * f[i]; }
+  }
+  const float rstd = rsqrtf(block_sum(ss, red) / (float)N + eps);
+  for (int64_t c = threadIdx.x; c < (N >> 3); c += blockDim.x) {
+    float f[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) f[i] = row[c * 8 + i] * rstd * gain[c * 8 + i];
+    *reinterpret_cast<uint4*>(out + r * ldo + c * 8) = float_to_bf16x8(f);
+  }
+}
+
+// out[m, i] = silu(gu[m, i]) * gu[m, I + i]
+__global__ void swiglu_kernel(const bf16* __restrict__ gu, bf16* __restrict__ out, int64_t I,
+                              int64_t ldg, int64_t ldo, int64_t total_chunks) {
+  griddep_wait();
+  griddep_launch();
+  const int64_t cpr = I >> 3;
+  for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total_chunks;
+       idx += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t m = idx / cpr, c = idx % cpr;
+    float g[8], u[8];
+    bf16x8_to_float(*reinterpret_cast<const uint4*>(gu + m * ldg + c * 8), g);
+    bf16x8_to_float(*reinterpret_cast<const uint4*>(gu + m * ldg + I + c * 8), u);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) g[i] = silu_f(g[i]) * u[i];
+    *reinterpret_cast<uint4*>(out + m * ldo + c * 8) = float_to_bf16x8(g);
+  }
+}
+
+// argmax over a row of fp32 logits; ties resolve to the lowest index (torch.argmax order).
+__global__ void argmax_kernel(const float* __restrict__ logits, int64_t* __restrict__ out, int64_t V,
+                              int64_t ld) {
+  __shared__ float bv[32];
+  __shared__ int64_t bi[32];
+  griddep_wait();
+  griddep_launch();
+  const float* row = logits + (int64_t)blockIdx.x * ld;
+  float best = -INFINITY;
+  int64_t idx = 0x7fffffffffffffffLL;
+  for (int64_t i = threadIdx.x; i < V; i += blockDim.x) {
+    const float v = row[i];
+    if (v > best || (v == best && i < idx)) { best = v; idx = i; }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+    const int64_t oi = __shfl_xor_sync(0xffffffffu, idx, o);
+    if (ov > best || (ov == best && oi < idx)) { best = ov; idx = oi; }
+  }
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  if (lane == 0) { bv[w] = best; bi[w] = idx; }
+  __syncthreads();
+  if (w == 0) {
+    best = lane < nw ? bv[lane] : -INFINITY;
+    idx = lane < nw ? bi[lane] : 0x7fffffffffffffffLL;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+      const int64_t oi = __shfl_xor_sync(0xffffffffu, idx, o);
+      if (ov > best || (ov == best && oi < idx)) { best = ov; idx = oi; }
+    }
+    if (lane == 0) out[blockIdx.x] = idx;
+  }
+}
+
+// Temperature sampling by inverse CDF: p = softmax(logits / T); token = first i with cdf(i) > u.
+// One CTA per row; u[row] is a uniform random number supplied by the host (so that every
+// tensor-parallel rank draws the same token from the same logits).
+__global__ void sample_kernel(const float* __restrict__ logits, const float* __restrict__ temperature,
+                              const float* __restrict__ u, int64_t* __restrict__ out, int64_t V, int64_t ld) {
+  __shared__ float red[32];
+  __shared__ float chunk_sum[1024];
+  griddep_wait();
+  griddep_launch();
+  const float* row = logits + (int64_t)blockIdx.x * ld;
+  const float T = temperature[blockIdx.x];
+  const int tid = threadIdx.x, nt = blockDim.x;
+  float mx = -INFINITY;
+  for (int64_t i = tid; i < V; i += nt) mx = fmaxf(mx, row[i]);
+  mx = block_max(mx, red);
+  if (!(T > 0.f)) {  // greedy row inside a sampled batch
+    int64_t idx = 0x7fffffffffffffffLL;
+    for (int64_t i = tid; i < V; i += nt) if (row[i] == mx && i < idx) idx = i;
+    __shared__ unsigned long long best;
+    if (tid == 0) best = ~0ull;
+    __syncthreads();
+    atomicMin(&best, (unsigned long long)idx);
+    __syncthreads();
+    if (tid == 0) out[blockIdx.x] = (int64_t)best;
+    return;
+  }
+  // contiguous span per thread so the CDF order is the index order
+  const int64_t per = (V + nt - 1) / nt, b = (int64_t)tid * per, e = min(V, b + per);
+  const float inv = 1.f / T;
+  float s = 0.f;
+  for (int64_t i = b; i < e; ++i) s += __expf((row[i] - mx) * inv);
+  chunk_sum[tid] = s;
+  const float total = block_sum(s, red);
+  __syncthreads();
+  if (tid == 0) {
+    const float target = u[blockIdx.x] * total;
+    float cum = 0.f;
+    int t = 0;
+    for (; t < nt - 1; ++t) { if (cum + chunk_sum[t] > target) break; cum += chunk_sum[t]; }
+    int64_t bb = (int64_t)t * per, ee = min(V, bb + per), pick = min(V - 1, max(bb, ee - 1));
+    for (int64_t i = bb; i < ee; ++i) {
+      cum += __expf((row[i] - mx) * inv);
+      if (cum > target) { pick = i; break; }
+    }
+    out[blockIdx.x] = pick;
+  }
+}
+
+// dst[i] = src[i] for `n16` 16-byte words per (blockIdx.y) pair from index lists: copies
+// `count` blocks of `block_bytes` bytes: dst_base + dst_idx[j]*block_bytes <- src_base + src_idx[j]*block_bytes
+__global__ void block_copy_kernel(unsigned char* __restrict__ dst, const unsigned char* __restrict__ src,
+                                  const int64_t* __restrict__ dst_idx, const int64_t* __restrict__ src_idx,
+                                  int64_t block_bytes) {
+  griddep_wait();
+  griddep_launch();
+  const int64_t j = blockIdx.y;
+  const uint4* s = reinterpret_cast<const uint4*>(src + src_idx[j] * block_bytes);
+  uint4* d = reinterpret_cast<uint4*>(dst + dst_idx[j] * block_bytes);
+  for (int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; c < (block_bytes >> 4);
+       c += (int64_t)gridDim.x * blockDim.x)
+    d[c] = s[c];
+}
+
+}  // namespace
+
+CB_EXPORT int cb_embed_gather(const void* table, const void* tokens, void* out, int64_t T, int64_t H,
+                              int64_t V, void* stream) {
+  if (H % 8) return CB_ERR_SHAPE;
+  if (T == 0) return 0;
+  return (int)cb_launch(embed_gather_kernel, dim3((unsigned)T), dim3(256), 0, (cudaStream_t)stream,
+                        (const bf16*)table, (const int64_t*)tokens, (bf16*)out, H, V);
+}
+
+CB_EXPORT int cb_rmsnorm(const void* x, const void* add, const void* gain, void* res_out, void* out,
+                         int64_t M, int64_t N, int64_t ldx, int64_t ldo, float eps, void* stream) {
+  if (N % 8 || N * 4 > 200 * 1024) return CB_ERR_SHAPE;
+  if (M == 0) return 0;
+  const size_t smem = (size_t)N * 4;
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(rmsnorm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+  }
+  const int threads = N >= 2048 ? 256 : 128;
+  return (int)cb_launch(rmsnorm_kernel, dim3((unsigned)M), dim3(threads), smem, (cudaStream_t)stream,
+                        (const bf16*)x, (const bf16*)add, (const float*)gain, (bf16*)res_out, (bf16*)out,
+                        N, ldx, ldo, eps);
+}
+
+CB_EXPORT int cb_swiglu(const void* gu, void* out, int64_t M, int64_t I, int64_t ldg, int64_t ldo,
+                        void* stream) {
+  if (I % 8 || ldg % 8 || ldo % 8) return CB_ERR_SHAPE;
+  const int64_t total = M * (I >> 3);
+  if (total == 0) return 0;
+  const int64_t blocks = min((total + 255) / 256, (int64_t)148 * 8);
+  return (int)cb_launch(swiglu_kernel, dim3((unsigned)blocks), dim3(256), 0, (cudaStream_t)stream,
+                        (const bf16*)gu, (bf16*)out, I, ldg, ldo, total);
+}
+
+CB_EXPORT int cb_argmax(const void* logits, void* out, int64_t M, int64_t V, int64_t ld, void* stream) {
+  if (M == 0) return 0;
+  return (int)cb_launch(argmax_kernel, dim3((unsigned)M), dim3(1024), 0, (cudaStream_t)stream,
+                        (const float*)logits, (int64_t*)out, V, ld);
+}
+
+CB_EXPORT int cb_sample(const void* logits, const void* temperature, const void* u, void* out, int64_t M,
+                        int64_t V, int64_t ld, void* stream) {
+  if (M == 0) return 0;
+  return (int)cb_launch(sample_kernel, dim3((unsigned)M), dim3(1024), 0, (cudaStream_t)stream,
+                        (const float*)logits, (const float*)temperature, (const float*)u, (int64_t*)out, V, ld);
+}
+
+CB_EXPORT int cb_block_copy(void* dst, const void* src, const void* dst_idx, const void* src_idx,
+                            int64_t count, int64_t block_bytes, void* stream) {
+  if (block_bytes % 16) return CB_ERR_SHAPE;
+  if (count == 0) return 0;
+  const int64_t bx = min((int64_t)64, ((block_bytes >> 4) + 255) / 256);
+  return (int)cb_launch(block_copy_kernel, dim3((unsigned)bx, (unsigned)count), dim3(256), 0,
+                        (cudaStream_t)stream, (unsigned char*)dst, (const unsigned char*)src,
+                        (const int64_t*)dst_idx, (const int64_t*)src_idx, block_bytes);
+}

@@ -1,0 +1,660 @@
+// Gated DeltaNet (linear attention) kernels.
+//
+// Decode: ONE launch per layer does causal conv1d + SiLU, head prep (L2 norm, beta, log decay),
+// the gated delta-rule update of the fp32 recurrent state, and the gated RMSNorm of the output.
+// The reference runs these as 4-5 launches with fp32 scratch between them
+// (models/qwen35/linear_attn.py:358-396; kernels backends/corex/kernels/linear_attn.cu:172-744,
+// delta.cu:86-194).  Prefill: the chunked (UT-transform) form of ops/delta.py:57-178 as three
+// kernels: per-token prep, per-chunk triangular system, sequential inter-chunk scan.
+//
+// Conv memory is a ring of the last 16 raw projection rows per sequence slot, indexed by
+// position & 15: a step writes only slot pos&15 and reads the three before it, so the CTAs of
+// value heads that share a key head never race, and a speculative verify of up to 12 tokens
+// can be rolled back without restoring the window.
+#include "common.cuh"
+
+namespace {
+
+constexpr int kRing = 16;
+constexpr int kChunk = 64;
+
+struct GdnDecodeArgs {
+  const bf16* proj;       // [M*ntok, ldp]: q | k | v | z | b | a
+  int64_t ldp;
+  const float* conv_w;    // [conv_dim, 4], oldest tap first
+  const float* A_log;     // [nv]
+  const float* dt_bias;   // [nv]
+  const float* norm_w;    // [dv]
+  bf16* ring;             // [slots, 16, conv_dim]
+  float* state;           // [slots, nv, dk, dv]
+  const int* slots;       // [M] state slot per row, < 0 = padded row
+  const int* positions;   // [M] position of the row's first token
+  bf16* out;              // [M*ntok, ldo]
+  int64_t ldo;
+  float* record;          // optional [M, rec_w, nv, dk+dv+1]
+  int rec_w;
+  int ntok;               // tokens per row (1 = decode, c = verify chain)
+  int write_state;        // 0: leave the state untouched (verify; commit replays the record)
+  int nk, nv, rep;
+  float eps;
+};
+
+template <int DK, int DV>
+__global__ void __launch_bounds__(4 * DV) gdn_decode_kernel(const GdnDecodeArgs a) {
+  constexpr int G = 4, RPT = DK / G, NT = 4 * DV;
+  __shared__ float q_s[DK], k_s[DK], v_s[DV];
+  __shared__ float sk[G][DV], sq[G][DV];
+  __shared__ float scal[4];
+  __shared__ float red[32];
+  const int h = blockIdx.x, m = blockIdx.y, kh = h / a.rep;
+  const int tid = threadIdx.x, j = tid % DV, grp = tid / DV;
+  const int kdim = a.nk * DK, conv_dim = 2 * kdim + a.nv * DV;
+  const int slot = a.slots[m];
+  if (slot < 0) return;
+  const int pos0 = a.positions[m];
+
+  // The recurrent state was written by this layer's previous step, long complete: fetch it
+  // before waiting for the projection kernel.
+  float* sp = a.state + (((int64_t)slot * a.nv + h) * DK + grp * RPT) * DV + j;
+  float s[RPT];
+#pragma unroll
+  for (int r = 0; r < RPT; ++r) s[r] = sp[(int64_t)r * DV];
+  griddep_wait();
+  griddep_launch();
+
+  const float nexpA = -__expf(a.A_log[h]), dtb = a.dt_bias[h];
+  const float nw = a.norm_w[j];
+  bf16* ring = a.ring + (int64_t)slot * kRing * conv_dim;
+
+  for (int t = 0; t < a.ntok; ++t) {
+    const int pos = pos0 + t;
+    const bf16* prow = a.proj + ((int64_t)m * a.ntok + t) * a.ldp;
+    // ---- causal conv + SiLU on this head's q, k, v channels ---------------------------
+    if (tid < 2 * DK + DV) {
+      int c;
+      bool own;
+      if (tid < DK) { c = kh * DK + tid; own = (h % a.rep) == 0; }
+      else if (tid < 2 * DK) { c = kdim + kh * DK + (tid - DK); own = (h % a.rep) == 0; }
+      else { c = 2 * kdim + h * DV + (tid - 2 * DK); own = true; }
+      const float4 w = *reinterpret_cast<const float4*>(a.conv_w + (int64_t)c * 4);
+      const bf16 xn = prow[c];
+      // tokens of this launch older than t come from the projection rows, the rest from the ring
+      float x3 = 0.f, x2 = 0.f, x1 = 0.f;
+      if (t >= 1) x1 = __bfloat162float(prow[c - a.ldp]);
+      else if (pos >= 1) x1 = __bfloat162float(ring[(int64_t)((pos - 1) & (kRing - 1)) * conv_dim + c]);
+      if (t >= 2) x2 = __bfloat162float(prow[c - 2 * a.ldp]);
+      else if (pos >= 2) x2 = __bfloat162float(ring[(int64_t)((pos - 2) & (kRing - 1)) * conv_dim + c]);
+      if (t >= 3) x3 = __bfloat162float(prow[c - 3 * a.ldp]);
+      else if (pos >= 3) x3 = __bfloat162float(ring[(int64_t)((pos - 3) & (kRing - 1)) * conv_dim + c]);
+      const float v = silu_f(w.x * x3 + w.y * x2 + w.z * x1 + w.w * __bfloat162float(xn));
+      if (own) ring[(int64_t)(pos & (kRing - 1)) * conv_dim + c] = xn;
+      if (tid < DK) q_s[tid] = v;
+      else if (tid < 2 * DK) k_s[tid - DK] = v;
+      else v_s[tid - 2 * DK] = v;
+    }
+    __syncthreads();
+    // ---- head prep: sum q^2, sum k^2, k.q ------------------------------------------------
+    if (tid < 96) {
+      const int w = tid >> 5, lane = tid & 31;
+      float acc = 0.f;
+      for (int i = lane; i < DK; i += 32) {
+        const float qa = q_s[i], ka = k_s[i];
+        acc += (w == 0) ? qa * qa : (w == 1) ? ka * ka : qa * ka;
+      }
+      acc = warp_sum(acc);
+      if (lane == 0) scal[w] = acc;
+    }
+    __syncthreads();
+    const float rq = rsqrtf(scal[0] + 1e-6f) * rsqrtf((float)DK), rk = rsqrtf(scal[1] + 1e-6f);
+    const float kq = scal[2] * rq * rk;
+    const float bl = __bfloat162float(prow[conv_dim + a.nv * DV + h]);
+    const float al = __bfloat162float(prow[conv_dim + a.nv * DV + a.nv + h]);
+    const float beta = sigmoid_f(bl);
+    const float alpha = __expf(nexpA * softplus_f(al + dtb));
+    // ---- S^T k and S^T q over this thread's rows -----------------------------------------
+    float pk = 0.f, pq = 0.f;
+#pragma unroll
+    for (int r = 0; r < RPT; ++r) {
+      pk = fmaf(s[r], k_s[grp * RPT + r], pk);
+      pq = fmaf(s[r], q_s[grp * RPT + r], pq);
+    }
+    sk[grp][j] = pk;
+    sq[grp][j] = pq;
+    __syncthreads();
+    const float Sk = (sk[0][j] + sk[1][j] + sk[2][j] + sk[3][j]) * rk;
+    const float Sq = (sq[0][j] + sq[1][j] + sq[2][j] + sq[3][j]) * rq;
+    const float d = (v_s[j] - alpha * Sk) * beta;
+    const float o = alpha * Sq + kq * d;
+#pragma unroll
+    for (int r = 0; r < RPT; ++r) s[r] = fmaf(k_s[grp * RPT + r] * rk, d, alpha * s[r]);
+    if (a.record) {
+      float* rec = a.record + (((int64_t)m * a.rec_w + t) * a.nv + h) * (DK + DV + 1);
+      if (tid < DK) rec[tid] = k_s[tid] * rk;
+      if (grp == 0) rec[DK + j] = d;
+      if (tid == 0) rec[DK + DV] = alpha;
+    }
+    // ---- gated RMSNorm over the head ---------------------------------------------------
+    const float ms = block_sum(grp == 0 ? o * o : 0.f, red) / (float)DV;
+    if (grp == 0) {
+      const float z = __bfloat162float(prow[conv_dim + h * DV + j]);
+      a.out[((int64_t)m * a.ntok + t) * a.ldo + h * DV + j] =
+          __float2bfloat16(o * rsqrtf(ms + a.eps) * nw * silu_f(z));
+    }
+    __syncthreads();
+  }
+  if (a.write_state) {
+#pragma unroll
+    for (int r = 0; r < RPT; ++r) sp[(int64_t)r * DV] = s[r];
+  }
+  (void)NT;
+}
+
+// state[slot] = replay of the first steps[m] recorded updates on state[slot] (verify leaves the
+// state untouched, so the base is the state itself).
+template <int DK, int DV>
+__global__ void __launch_bounds__(4 * DV) gdn_commit_kernel(float* state, const float* record,
+                                                            const int* slots, const int* steps,
+                                                            int rec_w, int nv) {
+  constexpr int G = 4, RPT = DK / G;
+  const int h = blockIdx.x, m = blockIdx.y, j = threadIdx.x % DV, grp = threadIdx.x / DV;
+  griddep_wait();
+  griddep_launch();
+  const int slot = slots[m], n = steps[m];
+  if (slot < 0 || n <= 0) return;
+  float* sp = state + (((int64_t)slot * nv + h) * DK + grp * RPT) * DV + j;
+  float s[RPT];
+#pragma unroll
+  for (int r = 0; r < RPT; ++r) s[r] = sp[(int64_t)r * DV];
+  for (int t = 0; t < n && t < rec_w; ++t) {
+    const float* rec = record + (((int64_t)m * rec_w + t) * nv + h) * (DK + DV + 1);
+    const float alpha = rec[DK + DV], d = rec[DK + j];
+#pragma unroll
+    for (int r = 0; r < RPT; ++r) s[r] = fmaf(rec[grp * RPT + r], d, alpha * s[r]);
+  }
+#pragma unroll
+  for (int r = 0; r < RPT; ++r) sp[(int64_t)r * DV] = s[r];
+}
+
+// ---------------------------------------------------------------------------------------
+// Prefill prep: one CTA per token, one warp per head task.
+struct GdnPrepArgs {
+  const bf16* proj; int64_t ldp;
+  const float* conv_w; const float* A_log; const float* dt_bias;
+  const bf16* ring;        // this sequence's ring [16, conv_dim]
+  float* qn; float* kn;    // [nk, Tp, DK]
+  float* v;                // [nv, Tp, DV]
+  float* beta; float* g;   // [nv, Tp]
+  int T, Tp, pos0, nk, nv;
+};
+
+template <int DK, int DV>
+__global__ void __launch_bounds__(256) gdn_prep_kernel(const GdnPrepArgs a) {
+  griddep_wait();
+  griddep_launch();
+  const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int kdim = a.nk * DK, conv_dim = 2 * kdim + a.nv * DV;
+  const int ntask = 2 * a.nk + a.nv + 1;
+  for (int task = warp; task < ntask; task += 8) {
+    if (task == ntask - 1) {  // beta / g for every value head
+      for (int h = lane; h < a.nv; h += 32) {
+        float b = 0.f, gg = 0.f;
+        if (t < a.T) {
+          const bf16* prow = a.proj + (int64_t)t * a.ldp + conv_dim + a.nv * DV;
+          b = sigmoid_f(__bfloat162float(prow[h]));
+          gg = -__expf(a.A_log[h]) * softplus_f(__bfloat162float(prow[a.nv + h]) + a.dt_bias[h]);
+        }
+        a.beta[(int64_t)h * a.Tp + t] = b;
+        a.g[(int64_t)h * a.Tp + t] = gg;
+      }
+      continue;
+    }
+    int cbase, width, head, kind;  // kind 0 = q, 1 = k, 2 = v
+    if (task < a.nk) { kind = 0; head = task; cbase = head * DK; width = DK; }
+    else if (task < 2 * a.nk) { kind = 1; head = task - a.nk; cbase = kdim + head * DK; width = DK; }
+    else { kind = 2; head = task - 2 * a.nk; cbase = 2 * kdim + head * DV; width = DV; }
+    constexpr int CPL = (DK > DV ? DK : DV) / 32;
+    float val[CPL];
+    float ss = 0.f;
+#pragma unroll
+    for (int e = 0; e < CPL; ++e) {
+      const int i = lane + 32 * e;
+      val[e] = 0.f;
+      if (i < width && t < a.T) {
+        const int c = cbase + i;
+        const float4 w = *reinterpret_cast<const float4*>(a.conv_w + (int64_t)c * 4);
+        float x[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const int tt = t - 3 + k, pp = a.pos0 + tt;
+          if (tt >= 0) x[k] = __bfloat162float(a.proj[(int64_t)tt * a.ldp + c]);
+          else if (pp >= 0) x[k] = __bfloat162float(a.ring[(int64_t)(pp & (kRing - 1)) * conv_dim + c]);
+          else x[k] = 0.f;
+        }
+        val[e] = silu_f(w.x * x[0] + w.y * x[1] + w.z * x[2] + w.w * x[3]);
+        ss += val[e] * val[e];
+      }
+    }
+    float scale = 1.f;
+    if (kind < 2) {
+      ss = warp_sum(ss);
+      scale = rsqrtf(ss + 1e-6f) * (kind == 0 ? rsqrtf((float)DK) : 1.f);
+    }
+    float* dst = (kind == 0 ? a.qn : kind == 1 ? a.kn : a.v) + ((int64_t)head * a.Tp + t) * width;
+#pragma unroll
+    for (int e = 0; e < CPL; ++e) {
+      const int i = lane + 32 * e;
+      if (i < width) dst[i] = val[e] * scale;
+    }
+  }
+}
+
+// ring[(pos0 + t) & 15] = proj[t] for the last min(T, 16) tokens of the chunk
+__global__ void gdn_ring_update_kernel(const bf16* proj, int64_t ldp, bf16* ring, int T, int pos0, int conv_dim) {
+  griddep_wait();
+  griddep_launch();
+  const int first = max(0, T - kRing);
+  const int t = first + blockIdx.x;
+  if (t >= T) return;
+  const uint4* src = reinterpret_cast<const uint4*>(proj + (int64_t)t * ldp);
+  uint4* dst = reinterpret_cast<uint4*>(ring + (int64_t)((pos0 + t) & (kRing - 1)) * conv_dim);
+  for (int c = threadIdx.x; c < (conv_dim >> 3); c += blockDim.x) dst[c] = src[c];
+}
+
+// ---------------------------------------------------------------------------------------
+// Per-chunk triangular system. For chunk rows i (64) with cumulative log decay c_i:
+//   Tm_ij = beta_i e^{c_i-c_j} k_i.k_j (j<i);  W = (I+Tm)^-1
+//   nvv = W (beta V)  [64, DV];  kcd = W (beta e^c K) [64, DK];  ica_ij = q_i.k_j e^{c_i-c_j} (j<=i)
+// and the scaled copies the scan needs: qe = q e^c, ke = k e^{c_L - c}, ecl = e^{c_L}.
+struct GdnChunkArgs {
+  const float* qn; const float* kn; const float* v; const float* beta; const float* g;
+  float* nvv;   // [nv, nc, 64, DV]
+  float* kcd;   // [nv, nc, 64, DK]
+  float* ica;   // [nv, nc, 64, 64]
+  float* qe;    // [nv, nc, 64, DK]
+  float* ke;    // [nv, nc, 64, DK]
+  float* ecl;   // [nv, nc]
+  int Tp, nc, rep;
+};
+
+template <int DK, int DV>
+__global__ void __launch_bounds__(256) gdn_chunk_prepare_kernel(const GdnChunkArgs a) {
+  constexpr int L = kChunk, LDK = DK + 4, LDV = DV + 4, LDL = L + 1;
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  float* Ks = reinterpret_cast<float*>(smem_raw);   // [L][LDK]
+  float* Qs = Ks + L * LDK;                         // [L][LDK]  (later: beta e^c K)
+  float* Vs = Qs + L * LDK;                         // [L][LDV]  (beta V)
+  float* Tm = Vs + L * LDV;                         // [L][LDL]
+  float* Wi = Tm + L * LDL;                         // [L][LDL]
+  float* cs = Wi + L * LDL;                         // [L] cumulative log decay
+  float* bs = cs + L;                               // [L] beta
+  griddep_wait();
+  griddep_launch();
+  const int n = blockIdx.x, h = blockIdx.y, kh = h / a.rep, tid = threadIdx.x;
+  const int64_t t0 = (int64_t)n * L;
+  const float* kp = a.kn + ((int64_t)kh * a.Tp + t0) * DK;
+  const float* qp = a.qn + ((int64_t)kh * a.Tp + t0) * DK;
+  const float* vp = a.v + ((int64_t)h * a.Tp + t0) * DV;
+  for (int idx = tid; idx < L * DK / 4; idx += 256) {
+    const int i = idx / (DK / 4), c = (idx % (DK / 4)) * 4;
+    *reinterpret_cast<float4*>(Ks + i * LDK + c) = *reinterpret_cast<const float4*>(kp + (int64_t)i * DK + c);
+    *reinterpret_cast<float4*>(Qs + i * LDK + c) = *reinterpret_cast<const float4*>(qp + (int64_t)i * DK + c);
+  }
+  for (int idx = tid; idx < L * DV / 4; idx += 256) {
+    const int i = idx / (DV / 4), c = (idx % (DV / 4)) * 4;
+    *reinterpret_cast<float4*>(Vs + i * LDV + c) = *reinterpret_cast<const float4*>(vp + (int64_t)i * DV + c);
+  }
+  if (tid < 32) {  // inclusive scan of g over the 64 rows
+    const float g0 = a.g[(int64_t)h * a.Tp + t0 + tid], g1 = a.g[(int64_t)h * a.Tp + t0 + 32 + tid];
+    float x0 = g0, x1 = g1;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const float y0 = __shfl_up_sync(0xffffffffu, x0, o), y1 = __shfl_up_sync(0xffffffffu, x1, o);
+      if (tid >= o) { x0 += y0; x1 += y1; }
+    }
+    const float tot0 = __shfl_sync(0xffffffffu, x0, 31);
+    cs[tid] = x0;
+    cs[32 + tid] = x1 + tot0;
+    bs[tid] = a.beta[(int64_t)h * a.Tp + t0 + tid];
+    bs[32 + tid] = a.beta[(int64_t)h * a.Tp + t0 + 32 + tid];
+  }
+  __syncthreads();
+  // ---- K K^T and Q K^T: 4x4 register tiles ---------------------------------------------
+  {
+    const int ti = tid / 16, tj = tid % 16;
+    float kk[4][4] = {}, qk[4][4] = {};
+    for (int c = 0; c < DK; c += 4) {
+      float4 ki[4], qi[4], kj[4];
+#pragma unroll
+      for (int x = 0; x < 4; ++x) {
+        ki[x] = *reinterpret_cast<const float4*>(Ks + (ti * 4 + x) * LDK + c);
+        qi[x] = *reinterpret_cast<const float4*>(Qs + (ti * 4 + x) * LDK + c);
+        kj[x] = *reinterpret_cast<const float4*>(Ks + (tj * 4 + x) * LDK + c);
+      }
+#pragma unroll
+      for (int x = 0; x < 4; ++x)
+#pragma unroll
+        for (int y = 0; y < 4; ++y) {
+          kk[x][y] += ki[x].x * kj[y].x + ki[x].y * kj[y].y + ki[x].z * kj[y].z + ki[x].w * kj[y].w;
+          qk[x][y] += qi[x].x * kj[y].x + qi[x].y * kj[y].y + qi[x].z * kj[y].z + qi[x].w * kj[y].w;
+        }
+    }
+    float* icap = a.ica + ((int64_t)h * a.nc + n) * L * L;
+#pragma unroll
+    for (int x = 0; x < 4; ++x)
+#pragma unroll
+      for (int y = 0; y < 4; ++y) {
+        const int i = ti * 4 + x, jj = tj * 4 + y;
+        const float dec = (jj <= i) ? __expf(cs[i] - cs[jj]) : 0.f;
+        Tm[i * LDL + jj] = (jj < i) ? bs[i] * dec * kk[x][y] : 0.f;
+        icap[i * L + jj] = dec * qk[x][y];
+      }
+  }
+  __syncthreads();
+  // ---- scaled copies for the scan, then overwrite Qs <- beta e^c K, Vs <- beta V -------
+  {
+    float* qep = a.qe + ((int64_t)h * a.nc + n) * L * DK;
+    float* kep = a.ke + ((int64_t)h * a.nc + n) * L * DK;
+    const float cl = cs[L - 1];
+    for (int idx = tid; idx < L * DK; idx += 256) {
+      const int i = idx / DK, c = idx % DK;
+      const float ec = __expf(cs[i]);
+      const float kv = Ks[i * LDK + c];
+      qep[idx] = Qs[i * LDK + c] * ec;
+      kep[idx] = kv * __expf(cl - cs[i]);
+      Qs[i * LDK + c] = bs[i] * ec * kv;
+    }
+    for (int idx = tid; idx < L * DV; idx += 256) {
+      const int i = idx / DV, c = idx % DV;
+      Vs[i * LDV + c] *= bs[i];
+    }
+    if (tid == 0) a.ecl[(int64_t)h * a.nc + n] = __expf(cl);
+  }
+  // ---- W = (I + Tm)^-1 by forward substitution, one column per thread ------------------
+  if (tid < L) {
+    const int c = tid;
+    for (int i = 0; i < L; ++i) {
+      float acc = (i == c) ? 1.f : 0.f;
+      for (int jj = c; jj < i; ++jj) acc -= Tm[i * LDL + jj] * Wi[jj * LDL + c];
+      Wi[i * LDL + c] = (i >= c) ? acc : 0.f;
+    }
+  }
+  __syncthreads();
+  // ---- nvv = W (beta V), kcd = W (beta e^c K) ---------------------------------------------
+  {
+    float* nvp = a.nvv + ((int64_t)h * a.nc + n) * L * DV;
+    float* kcp = a.kcd + ((int64_t)h * a.nc + n) * L * DK;
+    // thread -> 4 rows x 4 cols tiles over [64 x (DV + DK)]
+    constexpr int NCOL = (DV + DK) / 4;
+    for (int tile = tid; tile < 16 * NCOL; tile += 256) {
+      const int ti = tile / NCOL, tc = tile % NCOL;
+      const bool isv = tc < DV / 4;
+      const float* B = isv ? (Vs + tc * 4) : (Qs + (tc - DV / 4) * 4);
+      const int ldb = isv ? LDV : LDK;
+      float acc[4][4] = {};
+      const int imax = ti * 4 + 3;
+      for (int l = 0; l <= imax; ++l) {
+        const float4 b = *reinterpret_cast<const float4*>(B + l * ldb);
+#pragma unroll
+        for (int x = 0; x < 4; ++x) {
+          const float w = Wi[(ti * 4 + x) * LDL + l];
+          acc[x][0] += w * b.x; acc[x][1] += w * b.y; acc[x][2] += w * b.z; acc[x][3] += w * b.w;
+        }
+      }
+#pragma unroll
+      for (int x = 0; x < 4; ++x) {
+        const float4 o = make_float4(acc[x][0], acc[x][1], acc[x][2], acc[x][3]);
+        if (isv) *reinterpret_cast<float4*>(nvp + (ti * 4 + x) * DV + tc * 4) = o;
+        else *reinterpret_cast<float4*>(kcp + (ti * 4 + x) * DK + (tc - DV / 4) * 4) = o;
+      }
+    }
+  }
+}
+
+// Sequential scan over chunks for one (value head, DVS-column slice) of the state.
+//   U = nvv - kcd S ;  O = qe S + ica U ;  S <- ecl S + ke^T U
+struct GdnScanArgs {
+  const float* nvv; const float* kcd; const float* ica; const float* qe; const float* ke; const float* ecl;
+  float* state;   // this sequence's state [nv, DK, DV] (read as S0, written as S_final)
+  float* out;     // [T, nv*DV] fp32
+  int T, nc, nv;
+};
+
+template <int DK, int DV, int DVS>
+__global__ void __launch_bounds__(256) gdn_chunk_scan_kernel(const GdnScanArgs a) {
+  constexpr int L = kChunk, LDK = DK + 4, LDS = DVS + 4, LDL = L + 4;
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  float* S = reinterpret_cast<float*>(smem_raw);  // [DK][LDS]
+  float* A1 = S + DK * LDS;                       // [L][LDK] kcd, then ke
+  float* A2 = A1 + L * LDK;                       // [L][LDK] qe
+  float* Ic = A2 + L * LDK;                       // [L][LDL]
+  float* U = Ic + L * LDL;                        // [L][LDS]
+  griddep_wait();
+  griddep_launch();
+  const int h = blockIdx.x, sl = blockIdx.y, tid = threadIdx.x;
+  const int col0 = sl * DVS;
+  float* sp = a.state + (int64_t)h * DK * DV + col0;
+  for (int idx = tid; idx < DK * DVS; idx += 256) S[(idx / DVS) * LDS + idx % DVS] = sp[(int64_t)(idx / DVS) * DV + idx % DVS];
+  // thread tiles: (64 x DVS) outputs -> rows ty*RT.., cols tx*4.. ; (DK x DVS) -> rows ty*RS..
+  constexpr int TX = DVS / 4, TY = 256 / TX, RT = L / TY, RS = DK / TY;
+  static_assert(L % TY == 0 && DK % TY == 0, "tile");
+  const int tx = tid % TX, ty = tid / TX;
+  for (int n = 0; n < a.nc; ++n) {
+    const int64_t base = (int64_t)h * a.nc + n;
+    __syncthreads();
+    for (int idx = tid; idx < L * DK / 4; idx += 256) {
+      const int i = idx / (DK / 4), c = (idx % (DK / 4)) * 4;
+      *reinterpret_cast<float4*>(A1 + i * LDK + c) = *reinterpret_cast<const float4*>(a.kcd + base * L * DK + (int64_t)i * DK + c);
+      *reinterpret_cast<float4*>(A2 + i * LDK + c) = *reinterpret_cast<const float4*>(a.qe + base * L * DK + (int64_t)i * DK + c);
+    }
+    for (int idx = tid; idx < L * L / 4; idx += 256) {
+      const int i = idx / (L / 4), c = (idx % (L / 4)) * 4;
+      *reinterpret_cast<float4*>(Ic + i * LDL + c) = *reinterpret_cast<const float4*>(a.ica + base * L * L + (int64_t)i * L + c);
+    }
+    __syncthreads();
+    // U = nvv - kcd S ; Oacc = qe S
+    float u[RT][4], o[RT][4];
+#pragma unroll
+    for (int r = 0; r < RT; ++r) {
+      const float4 nv4 = *reinterpret_cast<const float4*>(a.nvv + base * L * DV + (int64_t)(ty * RT + r) * DV + col0 + tx * 4);
+      u[r][0] = nv4.x; u[r][1] = nv4.y; u[r][2] = nv4.z; u[r][3] = nv4.w;
+      o[r][0] = o[r][1] = o[r][2] = o[r][3] = 0.f;
+    }
+    for (int k = 0; k < DK; ++k) {
+      const float4 sv = *reinterpret_cast<const float4*>(S + k * LDS + tx * 4);
+#pragma unroll
+      for (int r = 0; r < RT; ++r) {
+        const float ak = A1[(ty * RT + r) * LDK + k], aq = A2[(ty * RT + r) * LDK + k];
+        u[r][0] -= ak * sv.x; u[r][1] -= ak * sv.y; u[r][2] -= ak * sv.z; u[r][3] -= ak * sv.w;
+        o[r][0] += aq * sv.x; o[r][1] += aq * sv.y; o[r][2] += aq * sv.z; o[r][3] += aq * sv.w;
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < RT; ++r)
+      *reinterpret_cast<float4*>(U + (ty * RT + r) * LDS + tx * 4) = make_float4(u[r][0], u[r][1], u[r][2], u[r][3]);
+    __syncthreads();
+    // ke replaces kcd in A1 (kcd no longer needed)
+    for (int idx = tid; idx < L * DK / 4; idx += 256) {
+      const int i = idx / (DK / 4), c = (idx % (DK / 4)) * 4;
+      *reinterpret_cast<float4*>(A1 + i * LDK + c) = *reinterpret_cast<const float4*>(a.ke + base * L * DK + (int64_t)i * DK + c);
+    }
+    // O += ica U (lower triangular: l <= row)
+    for (int l = 0; l < L; ++l) {
+      const float4 uv = *reinterpret_cast<const float4*>(U + l * LDS + tx * 4);
+#pragma unroll
+      for (int r = 0; r < RT; ++r) {
+        const float c = Ic[(ty * RT + r) * LDL + l];
+        o[r][0] += c * uv.x; o[r][1] += c * uv.y; o[r][2] += c * uv.z; o[r][3] += c * uv.w;
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < RT; ++r) {
+      const int64_t t = (int64_t)n * L + ty * RT + r;
+      if (t < a.T)
+        *reinterpret_cast<float4*>(a.out + t * a.nv * DV + (int64_t)h * DV + col0 + tx * 4) =
+            make_float4(o[r][0], o[r][1], o[r][2], o[r][3]);
+    }
+    __syncthreads();
+    // S <- ecl S + ke^T U
+    const float el = a.ecl[base];
+    float sacc[RS][4];
+#pragma unroll
+    for (int r = 0; r < RS; ++r) {
+      const float4 sv = *reinterpret_cast<const float4*>(S + (ty * RS + r) * LDS + tx * 4);
+      sacc[r][0] = sv.x * el; sacc[r][1] = sv.y * el; sacc[r][2] = sv.z * el; sacc[r][3] = sv.w * el;
+    }
+    for (int l = 0; l < L; ++l) {
+      const float4 uv = *reinterpret_cast<const float4*>(U + l * LDS + tx * 4);
+#pragma unroll
+      for (int r = 0; r < RS; ++r) {
+        const float kv = A1[l * LDK + ty * RS + r];
+        sacc[r][0] += kv * uv.x; sacc[r][1] += kv * uv.y; sacc[r][2] += kv * uv.z; sacc[r][3] += kv * uv.w;
+      }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int r = 0; r < RS; ++r)
+      *reinterpret_cast<float4*>(S + (ty * RS + r) * LDS + tx * 4) = make_float4(sacc[r][0], sacc[r][1], sacc[r][2], sacc[r][3]);
+  }
+  __syncthreads();
+  for (int idx = tid; idx < DK * DVS; idx += 256) sp[(int64_t)(idx / DVS) * DV + idx % DVS] = S[(idx / DVS) * LDS + idx % DVS];
+}
+
+// out[t, h*DV + j] = bf16( o * rsqrt(mean_j o^2 + eps) * w[j] * silu(z) ), one warp per (t, h)
+template <int DV>
+__global__ void gdn_gated_norm_kernel(const float* o, const bf16* z, int64_t ldz, const float* w, bf16* out,
+                                      int64_t ldo, int T, int nv, float eps) {
+  griddep_wait();
+  griddep_launch();
+  const int lane = threadIdx.x & 31;
+  const int64_t task = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (task >= (int64_t)T * nv) return;
+  const int64_t t = task / nv;
+  const int h = task % nv;
+  constexpr int E = DV / 32;
+  float x[E], ss = 0.f;
+#pragma unroll
+  for (int e = 0; e < E; ++e) { x[e] = o[(t * nv + h) * DV + lane + 32 * e]; ss += x[e] * x[e]; }
+  const float r = rsqrtf(warp_sum(ss) / (float)DV + eps);
+#pragma unroll
+  for (int e = 0; e < E; ++e) {
+    const int jj = lane + 32 * e;
+    const float zz = __bfloat162float(z[t * ldz + h * DV + jj]);
+    out[t * ldo + h * DV + jj] = __float2bfloat16(x[e] * r * w[jj] * silu_f(zz));
+  }
+}
+
+template <int DK, int DV>
+size_t chunk_prepare_smem() {
+  return sizeof(float) * (size_t)(2 * kChunk * (DK + 4) + kChunk * (DV + 4) + 2 * kChunk * (kChunk + 1) + 2 * kChunk);
+}
+template <int DK, int DVS>
+size_t chunk_scan_smem() {
+  return sizeof(float) * (size_t)(DK * (DVS + 4) + 2 * kChunk * (DK + 4) + kChunk * (kChunk + 4) + kChunk * (DVS + 4));
+}
+
+template <typename K>
+int set_smem(K kern, size_t smem) {
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+  }
+  return 0;
+}
+
+}  // namespace
+
+CB_EXPORT int cb_gdn_decode(const void* proj, int64_t ldp, const void* conv_w, const void* A_log,
+                            const void* dt_bias, const void* norm_w, void* ring, void* state,
+                            const void* slots, const void* positions, void* out, int64_t ldo,
+                            void* record, int64_t rec_w, int64_t M, int64_t ntok, int64_t write_state,
+                            int64_t nk, int64_t nv, int64_t dk, int64_t dv, float eps, void* stream) {
+  if (nv % nk || M < 1 || ntok < 1 || ntok > 12) return CB_ERR_SHAPE;
+  GdnDecodeArgs a;
+  a.proj = (const bf16*)proj; a.ldp = ldp; a.conv_w = (const float*)conv_w; a.A_log = (const float*)A_log;
+  a.dt_bias = (const float*)dt_bias; a.norm_w = (const float*)norm_w; a.ring = (bf16*)ring;
+  a.state = (float*)state; a.slots = (const int*)slots; a.positions = (const int*)positions;
+  a.out = (bf16*)out; a.ldo = ldo; a.record = (float*)record; a.rec_w = (int)rec_w; a.ntok = (int)ntok;
+  a.write_state = (int)write_state; a.nk = (int)nk; a.nv = (int)nv; a.rep = (int)(nv / nk); a.eps = eps;
+  dim3 grid((unsigned)nv, (unsigned)M);
+  if (dk == 128 && dv == 128) return (int)cb_launch(gdn_decode_kernel<128, 128>, grid, dim3(512), 0, (cudaStream_t)stream, a);
+  if (dk == 64 && dv == 64) return (int)cb_launch(gdn_decode_kernel<64, 64>, grid, dim3(256), 0, (cudaStream_t)stream, a);
+  return CB_ERR_SHAPE;
+}
+
+CB_EXPORT int cb_gdn_commit(void* state, const void* record, const void* slots, const void* steps,
+                            int64_t rec_w, int64_t M, int64_t nv, int64_t dk, int64_t dv, void* stream) {
+  dim3 grid((unsigned)nv, (unsigned)M);
+  if (dk == 128 && dv == 128)
+    return (int)cb_launch(gdn_commit_kernel<128, 128>, grid, dim3(512), 0, (cudaStream_t)stream, (float*)state,
+                          (const float*)record, (const int*)slots, (const int*)steps, (int)rec_w, (int)nv);
+  if (dk == 64 && dv == 64)
+    return (int)cb_launch(gdn_commit_kernel<64, 64>, grid, dim3(256), 0, (cudaStream_t)stream, (float*)state,
+                          (const float*)record, (const int*)slots, (const int*)steps, (int)rec_w, (int)nv);
+  return CB_ERR_SHAPE;
+}
+
+// Whole prefill chain for one sequence chunk of T tokens starting at pos0.
+// scratch (fp32) must hold cb_gdn_prefill_scratch(T, ...) floats.
+CB_EXPORT int64_t cb_gdn_prefill_scratch(int64_t T, int64_t nk, int64_t nv, int64_t dk, int64_t dv) {
+  const int64_t nc = (T + kChunk - 1) / kChunk, Tp = nc * kChunk;
+  return 2 * nk * Tp * dk + nv * Tp * dv + 2 * nv * Tp       // qn kn v beta g
+         + nv * nc * kChunk * (dv + 3 * dk + kChunk) + ((nv * nc + 3) & ~(int64_t)3)  // nvv kcd qe ke ica ecl
+         + T * nv * dv;                                        // scan output
+}
+
+CB_EXPORT int cb_gdn_prefill(const void* proj, int64_t ldp, const void* conv_w, const void* A_log,
+                             const void* dt_bias, const void* norm_w, void* ring_seq, void* state_seq,
+                             void* scratch, void* out, int64_t ldo, int64_t T, int64_t pos0, int64_t nk,
+                             int64_t nv, int64_t dk, int64_t dv, float eps, void* stream) {
+  if (T < 1 || nv % nk) return CB_ERR_SHAPE;
+  // the ring update moves whole 16-byte vectors of a projection row
+  if (ldp % 8 || (2 * nk * dk + nv * dv) % 8 || ((uintptr_t)proj & 15) || ((uintptr_t)ring_seq & 15)) return CB_ERR_SHAPE;
+  cudaStream_t st = (cudaStream_t)stream;
+  const int64_t nc = (T + kChunk - 1) / kChunk, Tp = nc * kChunk;
+  const int conv_dim = (int)(2 * nk * dk + nv * dv);
+  float* p = (float*)scratch;
+  float* qn = p; p += nk * Tp * dk;
+  float* kn = p; p += nk * Tp * dk;
+  float* v = p; p += nv * Tp * dv;
+  float* beta = p; p += nv * Tp;
+  float* g = p; p += nv * Tp;
+  float* nvv = p; p += nv * nc * kChunk * dv;
+  float* kcd = p; p += nv * nc * kChunk * dk;
+  float* qe = p; p += nv * nc * kChunk * dk;
+  float* ke = p; p += nv * nc * kChunk * dk;
+  float* ica = p; p += nv * nc * kChunk * kChunk;
+  float* ecl = p; p += (nv * nc + 3) & ~(int64_t)3;
+  float* o = p;
+  GdnPrepArgs pa{(const bf16*)proj, ldp, (const float*)conv_w, (const float*)A_log, (const float*)dt_bias,
+                 (const bf16*)ring_seq, qn, kn, v, beta, g, (int)T, (int)Tp, (int)pos0, (int)nk, (int)nv};
+  GdnChunkArgs ca{qn, kn, v, beta, g, nvv, kcd, ica, qe, ke, ecl, (int)Tp, (int)nc, (int)(nv / nk)};
+  GdnScanArgs sa{nvv, kcd, ica, qe, ke, ecl, (float*)state_seq, o, (int)T, (int)nc, (int)nv};
+  cudaError_t e;
+  int rc;
+#define GDN_PREFILL(DK_, DV_, DVS_)                                                                      \
+  do {                                                                                                   \
+    e = cb_launch(gdn_prep_kernel<DK_, DV_>, dim3((unsigned)Tp), dim3(256), 0, st, pa);                  \
+    if (e != cudaSuccess) return (int)e;                                                                 \
+    e = cb_launch(gdn_ring_update_kernel, dim3((unsigned)(T < kRing ? T : kRing)), dim3(256), 0, st,     \
+                  (const bf16*)proj, ldp, (bf16*)ring_seq, (int)T, (int)pos0, conv_dim);                 \
+    if (e != cudaSuccess) return (int)e;                                                                 \
+    size_t s1 = chunk_prepare_smem<DK_, DV_>();                                                          \
+    if ((rc = set_smem(gdn_chunk_prepare_kernel<DK_, DV_>, s1))) return rc;                              \
+    e = cb_launch(gdn_chunk_prepare_kernel<DK_, DV_>, dim3((unsigned)nc, (unsigned)nv), dim3(256), s1, st, ca); \
+    if (e != cudaSuccess) return (int)e;                                                                 \
+    size_t s2 = chunk_scan_smem<DK_, DVS_>();                                                            \
+    if ((rc = set_smem(gdn_chunk_scan_kernel<DK_, DV_, DVS_>, s2))) return rc;                           \
+    e = cb_launch(gdn_chunk_scan_kernel<DK_, DV_, DVS_>, dim3((unsigned)nv, (unsigned)(DV_ / DVS_)),      \
+                  dim3(256), s2, st, sa);                                                                \
+    if (e != cudaSuccess) return (int)e;                                                                 \
+    const int64_t tasks = T * nv;                                                                        \
+    e = cb_launch(gdn_gated_norm_kernel<DV_>, dim3((unsigned)((tasks + 7) / 8)), dim3(256), 0, st,       \
+                  (const float*)o, (const bf16*)proj + conv_dim, ldp, (const float*)norm_w, (bf16*)out,  \
+                  ldo, (int)T, (int)nv, eps);                                                            \
+    return (int)e;                                                                                       \
+  } while (0)
+  if (dk == 128 && dv == 128) GDN_PREFILL(128, 128, 32);
+  if (dk == 64 && dv == 64) GDN_PREFILL(64, 64, 32);
+#undef GDN_PREFILL
+  return CB_ERR_SHAPE;
+}

@@ -1,0 +1,277 @@
+// Prefill GEMM on the 5th-generation tensor cores: C[M,N] = A[M,K] * W[N,K]^T (+ residual).
+//
+// Persistent, warp-specialised, one CTA per SM:
+//   warp 0   : TMA producer  - 128B-swizzled [128 x 64] A tiles and [BN x 64] W tiles into a
+//              STAGES-deep shared-memory ring, completion on per-stage "full" mbarriers;
+//   warp 1   : MMA issuer    - one elected thread issues tcgen05.mma (cta_group::1, 128 x BN x 16)
+//              straight from the swizzled tiles, accumulating in TMEM; tcgen05.commit releases
+//              each stage ("empty") and, after the last k-block, publishes the accumulator;
+//   warps 2-5: epilogue      - tcgen05.ld the fp32 accumulator (one TMEM lane quadrant per warp),
+//              add the optional residual, convert and store; the accumulator is double-buffered
+//              in TMEM so the next tile's MMAs overlap this tile's epilogue.
+// bf16 (kind::f16) and int8 (kind::i8, int32 accumulate, per-row x per-column scales) share the
+// pipeline.  Both operands are K-major, i.e. the checkpoint's [N, K] weight layout is used as is.
+// No cluster multicast anywhere: every CTA fetches its own tiles.
+// Replaces the reference's linear_prefill (torch matmul / cublasGemmEx + epilogue kernel,
+// backends/corex/__init__.py:1612-1701, kernels/w8a8.cu:196-366, w8a8_tcu.cu:327-776).
+#include "sm100.cuh"
+
+namespace {
+
+using namespace sm100;
+
+constexpr int BM = 128, BK_BYTES = 128;
+constexpr int kThreadsGemm = 192;
+
+struct GemmArgs {
+  void* C; int64_t ldc;            // bf16 [M, ldc]
+  const bf16* residual; int64_t ldr;  // optional, added before the store
+  const float* row_scale;          // int8: [M] activation scales
+  const float* col_scale;          // int8: [N] weight scales
+  int M, N, K;
+  int m_tiles, n_tiles, k_blocks;
+  int* status;                     // device status word: set to a non-zero code if a wait ran out
+};
+
+__device__ __forceinline__ uint64_t gtime_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+// wall-clock bounded wait (2 s)
+__device__ __forceinline__ bool wait_bar(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  if (mbar_try(bar, parity)) return true;
+  const uint64_t t0 = gtime_ns();
+  for (;;) {
+    for (int i = 0; i < 256; ++i)
+      if (mbar_try(bar, parity)) return true;
+    if (*abort_flag) return false;
+    if (gtime_ns() - t0 > 2000000000ull) return false;
+  }
+}
+
+template <int BN, int STAGES, bool I8>
+__global__ void __launch_bounds__(kThreadsGemm, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmArgs a) {
+  constexpr int A_BYTES = BM * BK_BYTES, B_BYTES = BN * BK_BYTES, STAGE_BYTES = A_BYTES + B_BYTES;
+  constexpr int ESIZE = I8 ? 1 : 2, BK = BK_BYTES / ESIZE, UK = 32 / ESIZE;  // elements per k-block / per MMA
+  constexpr uint32_t TMEM_COLS = 2 * BN;  // two accumulators (power of two >= 32)
+  constexpr uint32_t IDESC = umma_idesc(BM, BN, 1, I8 ? 2 : 1);
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  unsigned char* tiles = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  __shared__ uint64_t full_bar[STAGES], empty_bar[STAGES], acc_full[2], acc_empty[2];
+  __shared__ uint32_t tmem_base_s;
+  __shared__ int abort_s;
+  volatile int* abort_flag = &abort_s;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+    for (int i = 0; i < 2; ++i) { mbar_init(&acc_full[i], 1); mbar_init(&acc_empty[i], 4); }
+    abort_s = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc(&tmem_base_s, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_base_s;
+  griddep_wait();
+  griddep_launch();
+
+  const int total = a.m_tiles * a.n_tiles;
+  if (warp == 0) {
+    // ------------------------------- TMA producer -----------------------------------------
+    if (lane == 0) {
+      uint32_t it = 0;
+      for (int tile = blockIdx.x; tile < total && !*abort_flag; tile += gridDim.x) {
+        const int m0 = (tile % a.m_tiles) * BM, n0 = (tile / a.m_tiles) * BN;
+        for (int kb = 0; kb < a.k_blocks; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!wait_bar(&empty_bar[s], ph ^ 1, abort_flag)) { atomicExch(a.status, 1); abort_s = 1; break; }
+          mbar_expect_tx(&full_bar[s], STAGE_BYTES);
+          unsigned char* st = tiles + (size_t)s * STAGE_BYTES;
+          tma_load_2d(st, &tmA, &full_bar[s], kb * BK, m0);
+          tma_load_2d(st + A_BYTES, &tmB, &full_bar[s], kb * BK, n0);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------- MMA issuer -------------------------------------------
+    if (lane == 0) {
+      uint32_t it = 0, tcount = 0;
+      for (int tile = blockIdx.x; tile < total && !*abort_flag; tile += gridDim.x, ++tcount) {
+        const uint32_t acc = tcount & 1, aph = (tcount >> 1) & 1;
+        if (!wait_bar(&acc_empty[acc], aph ^ 1, abort_flag)) { atomicExch(a.status, 2); abort_s = 1; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        bool ok = true;
+        for (int kb = 0; kb < a.k_blocks; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!wait_bar(&full_bar[s], ph, abort_flag)) { atomicExch(a.status, 3); abort_s = 1; ok = false; break; }
+          tc_fence_after();
+          const unsigned char* st = tiles + (size_t)s * STAGE_BYTES;
+          const uint64_t ad = umma_desc_sw128(st), bd = umma_desc_sw128(st + A_BYTES);
+#pragma unroll
+          for (int k = 0; k < BK / UK; ++k) {
+            // advance 32 bytes along K inside the 128-byte swizzle atom: +2 in 16-byte units
+            if (I8) umma_i8(d_tmem, ad + 2 * k, bd + 2 * k, IDESC, (kb | k) != 0);
+            else umma_f16(d_tmem, ad + 2 * k, bd + 2 * k, IDESC, (kb | k) != 0);
+          }
+          umma_commit(&empty_bar[s]);
+        }
+        if (!ok) break;
+        umma_commit(&acc_full[acc]);
+      }
+    }
+  } else {
+    // ------------------------------- epilogue ---------------------------------------------
+    const int q = warp & 3;  // TMEM lane quadrant this warp may read
+    uint32_t tcount = 0;
+    for (int tile = blockIdx.x; tile < total && !*abort_flag; tile += gridDim.x, ++tcount) {
+      const int m0 = (tile % a.m_tiles) * BM, n0 = (tile / a.m_tiles) * BN;
+      const uint32_t acc = tcount & 1, aph = (tcount >> 1) & 1;
+      if (!wait_bar(&acc_full[acc], aph, abort_flag)) { if (lane == 0) { atomicExch(a.status, 4); abort_s = 1; } break; }
+      tc_fence_after();
+      const int row = m0 + q * 32 + lane;
+      const float rs = (I8 && row < a.M) ? a.row_scale[row] : 1.f;
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        uint32_t r[32];
+        tmem_ld32(tmem_base + acc * BN + ((uint32_t)(q * 32) << 16) + c0, r);
+        tmem_ld_wait();
+        const int col0 = n0 + c0;
+        if (row < a.M && col0 < a.N) {
+          bf16* cp = reinterpret_cast<bf16*>(a.C) + (int64_t)row * a.ldc + col0;
+          const bf16* rp = a.residual ? a.residual + (int64_t)row * a.ldr + col0 : nullptr;
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            if (col0 + v * 8 >= a.N) break;  // N is a multiple of 8
+            float f[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              if (I8) f[i] = (float)(int)r[v * 8 + i] * rs * a.col_scale[col0 + v * 8 + i];
+              else f[i] = __uint_as_float(r[v * 8 + i]);
+            }
+            if (rp) {
+              float g[8];
+              bf16x8_to_float(*reinterpret_cast<const uint4*>(rp + v * 8), g);
+#pragma unroll
+              for (int i = 0; i < 8; ++i) f[i] += g[i];
+            }
+            *reinterpret_cast<uint4*>(cp + v * 8) = float_to_bf16x8(f);
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[acc]);
+    }
+  }
+  // ------------------------------- teardown ---------------------------------------------------
+  tc_fence_before();
+  __syncthreads();
+  if (abort_s) {  // give copies still in flight time to land before the shared memory is released
+    const uint64_t t0 = gtime_ns();
+    while (gtime_ns() - t0 < 2000000ull) __nanosleep(1000);
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+template <int BN, int STAGES, bool I8>
+int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmArgs a, int sms, cudaStream_t st) {
+  a.n_tiles = (a.N + BN - 1) / BN;
+  const size_t smem = (size_t)STAGES * (BM + BN) * BK_BYTES + 1024;
+  auto kern = gemm_tc_kernel<BN, STAGES, I8>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return (int)e;
+  const int total = a.m_tiles * a.n_tiles;
+  const int grid = total < sms ? total : sms;
+  return (int)cb_launch(kern, dim3((unsigned)grid), dim3(kThreadsGemm), smem, st, tmA, tmB, a);
+}
+
+int g_sms = 0;
+int sm_count() {
+  if (!g_sms) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&g_sms, cudaDevAttrMultiProcessorCount, dev);
+    if (g_sms <= 0) g_sms = 148;
+  }
+  return g_sms;
+}
+
+// waves of `tiles` over `sms` SMs times the per-tile cost (proportional to BN)
+double tile_cost(int M, int N, int bn, int sms) {
+  const int tiles = ((M + BM - 1) / BM) * ((N + bn - 1) / bn);
+  const int waves = (tiles + sms - 1) / sms;
+  return (double)waves * bn;
+}
+
+}  // namespace
+
+// C[M,N] (bf16) = A[M,K] (bf16) x W[N,K]^T (bf16) (+ residual[M,N]).  K % 8 == 0, N % 8 == 0.
+// bn_hint: 0 = choose, else 64/128/256.
+CB_EXPORT int cb_gemm_bf16(const void* A, int64_t lda, const void* W, int64_t ldw, void* C, int64_t ldc,
+                           const void* residual, int64_t ldr, int64_t M, int64_t N, int64_t K,
+                           int64_t bn_hint, void* status, void* stream) {
+  if (M < 1 || N < 1 || K < 1) return CB_ERR_SHAPE;
+  if (K % 8 || N % 8 || ldc % 8 || (residual && ldr % 8) || !status) return CB_ERR_SHAPE;
+  const int sms = sm_count();
+  int bn = (int)bn_hint;
+  if (!bn) {
+    const double c256 = tile_cost((int)M, (int)N, 256, sms), c128 = tile_cost((int)M, (int)N, 128, sms) * 1.08;
+    const double c64 = tile_cost((int)M, (int)N, 64, sms) * 1.35;
+    bn = c256 <= c128 && c256 <= c64 ? 256 : (c128 <= c64 ? 128 : 64);
+  }
+  CUtensorMap tmA, tmB;
+  int rc = cb_make_tmap_2d(&tmA, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, BM, 64);
+  if (rc) return rc;
+  rc = cb_make_tmap_2d(&tmB, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, W, (uint64_t)N, (uint64_t)K, (uint64_t)ldw, (uint32_t)bn, 64);
+  if (rc) return rc;
+  GemmArgs a;
+  a.C = C; a.ldc = ldc; a.residual = (const bf16*)residual; a.ldr = ldr; a.row_scale = nullptr; a.col_scale = nullptr;
+  a.M = (int)M; a.N = (int)N; a.K = (int)K; a.m_tiles = (int)((M + BM - 1) / BM); a.n_tiles = 0;
+  a.k_blocks = (int)((K + 63) / 64); a.status = (int*)status;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (bn == 256) return launch_gemm<256, 4, false>(tmA, tmB, a, sms, st);
+  if (bn == 128) return launch_gemm<128, 6, false>(tmA, tmB, a, sms, st);
+  if (bn == 64) return launch_gemm<64, 8, false>(tmA, tmB, a, sms, st);
+  return CB_ERR_ARG;
+}
+
+// C[M,N] (bf16) = (A_q[M,K] int8 x W_q[N,K]^T int8) * row_scale[m] * col_scale[n] (+ residual). K % 16 == 0.
+CB_EXPORT int cb_gemm_i8(const void* A, int64_t lda, const void* W, int64_t ldw, void* C, int64_t ldc,
+                         const void* residual, int64_t ldr, const void* row_scale, const void* col_scale,
+                         int64_t M, int64_t N, int64_t K, int64_t bn_hint, void* status, void* stream) {
+  if (M < 1 || N < 1 || K < 1) return CB_ERR_SHAPE;
+  if (K % 16 || N % 8 || ldc % 8 || lda % 16 || ldw % 16 || (residual && ldr % 8) || !status || !row_scale || !col_scale)
+    return CB_ERR_SHAPE;
+  const int sms = sm_count();
+  int bn = (int)bn_hint;
+  if (!bn) bn = tile_cost((int)M, (int)N, 256, sms) <= tile_cost((int)M, (int)N, 128, sms) * 1.08 ? 256 : 128;
+  CUtensorMap tmA, tmB;
+  int rc = cb_make_tmap_2d(&tmA, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, BM, 128);
+  if (rc) return rc;
+  rc = cb_make_tmap_2d(&tmB, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, W, (uint64_t)N, (uint64_t)K, (uint64_t)ldw, (uint32_t)bn, 128);
+  if (rc) return rc;
+  GemmArgs a;
+  a.C = C; a.ldc = ldc; a.residual = (const bf16*)residual; a.ldr = ldr;
+  a.row_scale = (const float*)row_scale; a.col_scale = (const float*)col_scale;
+  a.M = (int)M; a.N = (int)N; a.K = (int)K; a.m_tiles = (int)((M + BM - 1) / BM); a.n_tiles = 0;
+  a.k_blocks = (int)((K + 127) / 128); a.status = (int*)status;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (bn == 256) return launch_gemm<256, 4, true>(tmA, tmB, a, sms, st);
+  if (bn == 128) return launch_gemm<128, 6, true>(tmA, tmB, a, sms, st);
+  return CB_ERR_ARG;
+}

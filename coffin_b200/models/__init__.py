@@ -1,0 +1,62 @@
+"""Model families. ``build_model`` maps a config to the sm_100a implementation.
+
+Counterpart of the reference's family registry (``engine_api.py:210-361``): the architecture
+string of ``config.json`` selects the class; here there is one backend, so the registry maps
+names to classes only.
+"""
+from __future__ import annotations
+
+from typing import Callable
+
+from ..config import ModelConfig
+
+_REGISTRY: dict[str, Callable] = {}
+
+
+def register(name: str, factory: Callable) -> None:
+    _REGISTRY[name] = factory
+
+
+def registered() -> list[str]:
+    _ensure_builtin()
+    return sorted(_REGISTRY)
+
+
+def _ensure_builtin() -> None:
+    if _REGISTRY:
+        return
+
+    def qwen35(cfg, sd, **kw):
+        from .qwen35.model import Qwen35Model
+        tp_world, tp_rank = kw.pop("tp_world", 1), kw.pop("tp_rank", 0)
+        if tp_world > 1:
+            from ..parallel.tp import TensorParallelQwen35
+            return TensorParallelQwen35(cfg, sd, tp_world=tp_world, tp_rank=tp_rank, **kw)
+        return Qwen35Model(cfg, sd, **kw)
+
+    for n in ("qwen3_5", "qwen35", "qwen3_5_moe", "qwen3_5_text", "qwen3_next"):
+        register(n, qwen35)
+
+    def qwen4(cfg, sd, **kw):
+        from .qwen4exp.model import Qwen4ExpModel
+        kw.pop("tp_world", None), kw.pop("tp_rank", None)
+        return Qwen4ExpModel(cfg, sd, **kw)
+
+    for n in ("qwen4_exp", "qwen4exp"):
+        register(n, qwen4)
+
+
+def detect_architecture(cfg: ModelConfig) -> str:
+    """Registry key for a config; unknown names fall back on geometry (a config that has
+    delta-net heads is a Qwen3.5-style hybrid), as ``engine_api.py:295-297`` does."""
+    _ensure_builtin()
+    if cfg.architecture in _REGISTRY:
+        return cfg.architecture
+    if cfg.linear_num_value_heads > 0:
+        return "qwen3_5"
+    raise RuntimeError(f"no registered model family for architecture {cfg.architecture!r}")
+
+
+def build_model(cfg: ModelConfig, sd: dict, **kw):
+    _ensure_builtin()
+    return _REGISTRY[detect_architecture(cfg)](cfg, sd, **kw)

@@ -1,0 +1,437 @@
+"""Qwen3.5-style hybrid model on one B200 (optionally one tensor-parallel shard).
+
+Execution model
+---------------
+* Weights are repacked once at load into the shapes the kernels read: per layer one fused
+  input projection (``q|k|v|z|b|a`` for a delta-net layer, ``q+gate|k|v`` for an attention
+  layer), one fused ``gate|up`` matrix, all ``[N, K]`` bf16 (the checkpoint layout is already
+  K-major, which is what both the GEMV and the tcgen05 GEMM want).
+* Decode is a CUDA graph per row bucket (1, 2, 4, 8): 5 launches per delta-net layer, 6 per
+  attention layer — residual add + RMSNorm are folded into the projections, SwiGLU into the
+  gate/up projection, conv + head prep + delta rule + gated norm into one kernel, q/k norm +
+  rotary + KV append into the attention kernel (the reference runs ~26 launches per layer,
+  ``docs/DECODE-LAUNCH-LEDGER.md:15-23``, and keeps graphs disabled,
+  ``backends/corex/__init__.py:2830-2896``).
+* Prefill runs one sequence chunk at a time through tcgen05 GEMMs (residual add fused in the
+  epilogue), the chunked delta-net scan and paged flash attention.
+* Sequence state lives in caller-assigned *slots* (delta-net recurrent state + conv ring) and
+  in a paged KV pool addressed through block tables, so the engine's block manager, radix
+  cache and scheduler own placement; this class owns no policy.
+
+Structure reference: ``models/qwen35/model.py:81-266`` (init), ``:515-604`` (decode forward),
+``:641-858`` (prefill), ``:1093-1349`` (graph capture, row buckets).
+"""
+from __future__ import annotations
+
+import dataclasses
+
+import torch
+
+from ...config import LINEAR, ModelConfig
+from ...ops import kernels as K
+from ...oracle import ops as O
+from ...weights.init import LM
+
+BUCKETS = (1, 2, 4, 8)
+
+
+def _pad8(n: int) -> int:
+    return (n + 7) // 8 * 8
+
+
+@dataclasses.dataclass
+class LayerWeights:
+    kind: str
+    in_gain: torch.Tensor
+    post_gain: torch.Tensor
+    w_in: torch.Tensor          # fused input projection [N_in, H]
+    w_out: torch.Tensor         # [H, mixer_width]
+    w_gu: torch.Tensor | None   # [2I, H]
+    w_down: torch.Tensor | None  # [H, I]
+    # delta net
+    conv_w: torch.Tensor | None = None
+    A_log: torch.Tensor | None = None
+    dt_bias: torch.Tensor | None = None
+    norm_w: torch.Tensor | None = None
+    # attention
+    qg: torch.Tensor | None = None
+    kg: torch.Tensor | None = None
+    moe: object | None = None
+
+
+class Qwen35Model:
+    """sm_100a execution of the hybrid model. ``sd`` uses the HF key layout."""
+
+    def __init__(self, cfg: ModelConfig, sd: dict[str, torch.Tensor], device: str | torch.device = "cuda",
+                 max_seq: int = 4096, num_slots: int = 2, num_blocks: int | None = None,
+                 max_chunk: int = 2048, pdl: bool = True, free_source: bool = False) -> None:
+        self.cfg = cfg
+        self.device = torch.device(device)
+        self.max_seq = int(max_seq)
+        self.num_slots = int(num_slots)
+        self.max_chunk = int(max_chunk)
+        self.max_blocks_per_seq = (self.max_seq + K.BLOCK - 1) // K.BLOCK
+        self.num_blocks = int(num_blocks) if num_blocks else self.max_blocks_per_seq * self.num_slots + 1
+        self.eps = cfg.rms_norm_eps
+        K.status_word(self.device)
+        K._lib.set_pdl(pdl)
+        dev, bf = self.device, torch.bfloat16
+        c = cfg
+
+        def w(key: str) -> torch.Tensor:
+            t = sd.pop(key) if free_source else sd[key]
+            return t.to(device=dev, dtype=bf)
+
+        def gain(key: str, centred: bool = True) -> torch.Tensor:
+            t = sd[key].to(device=dev, dtype=torch.float32)
+            return (1.0 + t).contiguous() if centred else t.contiguous()
+
+        self.embed = w(LM + "embed_tokens.weight").contiguous()
+        self.lm_head = w("lm_head.weight").contiguous() if "lm_head.weight" in sd else self.embed
+        self.final_gain = gain(LM + "norm.weight")
+        self.layers: list[LayerWeights] = []
+        for i, kind in enumerate(c.layer_types):
+            p = f"{LM}layers.{i}."
+            if kind == LINEAR:
+                q = p + "linear_attn."
+                parts = [w(q + "in_proj_qkv.weight"), w(q + "in_proj_z.weight"),
+                         w(q + "in_proj_b.weight"), w(q + "in_proj_a.weight")]
+                n = sum(t.shape[0] for t in parts)
+                if _pad8(n) != n:
+                    parts.append(torch.zeros(_pad8(n) - n, c.hidden_size, dtype=bf, device=dev))
+                lw = LayerWeights(
+                    kind=kind, in_gain=gain(p + "input_layernorm.weight"),
+                    post_gain=gain(p + "post_attention_layernorm.weight"),
+                    w_in=torch.cat(parts).contiguous(), w_out=w(q + "out_proj.weight").contiguous(),
+                    w_gu=None, w_down=None,
+                    conv_w=sd[q + "conv1d.weight"].to(dev, torch.float32).reshape(c.lin_conv_dim, -1).contiguous(),
+                    A_log=sd[q + "A_log"].to(dev, torch.float32).contiguous(),
+                    dt_bias=sd[q + "dt_bias"].to(dev, torch.float32).contiguous(),
+                    norm_w=gain(q + "norm.weight", centred=False))
+            else:
+                q = p + "self_attn."
+                lw = LayerWeights(
+                    kind=kind, in_gain=gain(p + "input_layernorm.weight"),
+                    post_gain=gain(p + "post_attention_layernorm.weight"),
+                    w_in=torch.cat([w(q + "q_proj.weight"), w(q + "k_proj.weight"), w(q + "v_proj.weight")]).contiguous(),
+                    w_out=w(q + "o_proj.weight").contiguous(), w_gu=None, w_down=None,
+                    qg=gain(q + "q_norm.weight"), kg=gain(q + "k_norm.weight"))
+            m = p + "mlp."
+            if c.is_moe:
+                from .moe import MoEWeights
+                lw.moe = MoEWeights.from_state_dict(c, sd, m, dev)
+            else:
+                lw.w_gu = torch.cat([w(m + "gate_proj.weight"), w(m + "up_proj.weight")]).contiguous()
+                lw.w_down = w(m + "down_proj.weight").contiguous()
+            self.layers.append(lw)
+        # ---- rotary tables -------------------------------------------------------------
+        cos, sin = O.rope_tables(c.rotary_dim, c.rope_theta, self.max_seq + 64)
+        self.cos, self.sin = cos.to(dev).contiguous(), sin.to(dev).contiguous()
+        # ---- sequence state ------------------------------------------------------------
+        self.lin_ids = {li: j for j, li in enumerate(c.linear_layers)}
+        self.full_ids = {li: j for j, li in enumerate(c.full_layers)}
+        nl, nf = len(self.lin_ids), len(self.full_ids)
+        self.state = torch.zeros(nl, self.num_slots, c.linear_num_value_heads, c.linear_key_head_dim,
+                                 c.linear_value_head_dim, dtype=torch.float32, device=dev)
+        self.ring = torch.zeros(nl, self.num_slots, K.RING, c.lin_conv_dim, dtype=bf, device=dev)
+        self.kpool = torch.zeros(nf, self.num_blocks * K.BLOCK, c.num_key_value_heads, c.head_dim, dtype=bf, device=dev)
+        self.vpool = torch.zeros_like(self.kpool)
+        # ---- prefill workspace (allocated lazily at the largest chunk seen) ----------------
+        self._pf: dict | None = None
+        self._pf_rows = 0
+        self._rows: dict[int, dict] = {}
+        self._graphs: dict[int, torch.cuda.CUDAGraph] = {}
+        self.graph_pool = None
+        self._step_launches: dict[int, int] = {}
+
+    def launches_per_step(self, M: int) -> int:
+        """Kernels launched by one decode step of bucket ``M`` (counted while capturing)."""
+        return self._step_launches.get(M, 0)
+
+    # ------------------------------------------------------------------ sizes
+    @property
+    def in_width(self) -> int:
+        return max(l.w_in.shape[0] for l in self.layers)
+
+    @property
+    def mix_width(self) -> int:
+        c = self.cfg
+        return max(c.lin_vdim, c.num_attention_heads * c.head_dim)
+
+    def weight_bytes(self) -> int:
+        seen, total = set(), 0
+        tensors = [self.embed, self.lm_head]
+        for l in self.layers:
+            tensors += [l.w_in, l.w_out] + ([l.w_gu, l.w_down] if l.w_gu is not None else [])
+            if l.moe is not None:
+                tensors += l.moe.tensors()
+        for t in tensors:
+            if t.data_ptr() not in seen:
+                seen.add(t.data_ptr())
+                total += t.numel() * t.element_size()
+        return total
+
+    # ------------------------------------------------------------------ sequence state
+    def zero_state(self, slot: int) -> None:
+        self.state[:, slot].zero_()
+        self.ring[:, slot].zero_()
+
+    def snapshot_state(self, slot: int) -> tuple[torch.Tensor, torch.Tensor]:
+        """Clone of the slot's delta-net state (recurrent matrices + conv ring)."""
+        return self.state[:, slot].clone(), self.ring[:, slot].clone()
+
+    def restore_state(self, slot: int, snap: tuple[torch.Tensor, torch.Tensor]) -> None:
+        self.state[:, slot].copy_(snap[0])
+        self.ring[:, slot].copy_(snap[1])
+
+    def copy_block(self, src: int, dst: int) -> None:
+        """Copy one KV block in every attention layer (copy-on-write of a shared tail block)."""
+        s, d = src * K.BLOCK, dst * K.BLOCK
+        self.kpool[:, d:d + K.BLOCK].copy_(self.kpool[:, s:s + K.BLOCK])
+        self.vpool[:, d:d + K.BLOCK].copy_(self.vpool[:, s:s + K.BLOCK])
+
+    # ------------------------------------------------------------------ prefill
+    def _prefill_ws(self, T: int) -> dict:
+        if self._pf is None or self._pf_rows < T:
+            c, dev, bf = self.cfg, self.device, torch.bfloat16
+            rows = max(T, min(self.max_chunk, 256))
+            H = c.hidden_size
+            ws = {
+                "res": torch.empty(rows, H, dtype=bf, device=dev),
+                "normed": torch.empty(rows, H, dtype=bf, device=dev),
+                "proj": torch.empty(rows, self.in_width, dtype=bf, device=dev),
+                "act": torch.empty(rows, self.mix_width, dtype=bf, device=dev),
+                "q": torch.empty(rows, c.num_attention_heads, c.head_dim, dtype=bf, device=dev),
+                "slots": torch.empty(rows, dtype=torch.int32, device=dev),
+                "ridx": torch.empty(rows, dtype=torch.int32, device=dev),
+            }
+            if not c.is_moe:
+                ws["gu"] = torch.empty(rows, 2 * c.intermediate_size, dtype=bf, device=dev)
+                ws["inter"] = torch.empty(rows, c.intermediate_size, dtype=bf, device=dev)
+            if self.lin_ids:
+                n = K.gdn_prefill_scratch_floats(rows, c.linear_num_key_heads, c.linear_num_value_heads,
+                                                 c.linear_key_head_dim, c.linear_value_head_dim)
+                ws["gdn"] = torch.empty(n, dtype=torch.float32, device=dev)
+            self._pf, self._pf_rows = ws, rows
+        return self._pf
+
+    @torch.no_grad()
+    def prefill(self, tokens: torch.Tensor, pos0: int, slot: int, block_table: torch.Tensor,
+                embeds: torch.Tensor | None = None, cos_sin: tuple[torch.Tensor, torch.Tensor] | None = None,
+                want_logits: bool = True, want_hidden: bool = False):
+        """Run ``tokens`` (int64 ``[T]`` on the device) of one sequence at positions
+        ``pos0..pos0+T-1``.
+
+        ``block_table`` (int32 on the device) lists the sequence's pool blocks from position 0.
+        ``embeds [T, H]`` overrides the token embeddings (image rows scattered in);
+        ``cos_sin`` gives per-token rotary rows ``[T, rot]`` (mRoPE) instead of the 1-D table.
+        Returns fp32 logits ``[vocab]`` of the last token (or ``None``).
+        """
+        c = self.cfg
+        T = int(tokens.numel())
+        assert 0 < T <= self.max_chunk, f"chunk of {T} tokens exceeds max_chunk {self.max_chunk}"
+        ws = self._prefill_ws(T)
+        res, normed = ws["res"][:T], ws["normed"][:T]
+        if embeds is None:
+            K.embed_gather(self.embed, tokens, res)
+        else:
+            res.copy_(embeds)
+        pos = torch.arange(pos0, pos0 + T, dtype=torch.int64, device=self.device)
+        slots = ws["slots"][:T]
+        slots.copy_(block_table.to(torch.int64)[pos // K.BLOCK] * K.BLOCK + pos % K.BLOCK)
+        if cos_sin is None:
+            cos, sin = self.cos, self.sin
+            ridx = ws["ridx"][:T]
+            ridx.copy_(pos)
+        else:
+            cos, sin = cos_sin[0].float().contiguous(), cos_sin[1].float().contiguous()
+            ridx = None
+        for li, lw in enumerate(self.layers):
+            K.rmsnorm(res, lw.in_gain, self.eps, out=normed)
+            n_in = lw.w_in.shape[0]
+            proj = ws["proj"][:T, :n_in]
+            K.gemm(normed, lw.w_in, out=proj)
+            if lw.kind == LINEAR:
+                j = self.lin_ids[li]
+                act = ws["act"][:T, :c.lin_vdim]
+                K.gdn_prefill(proj, lw.conv_w, lw.A_log, lw.dt_bias, lw.norm_w, self.ring[j, slot], self.state[j, slot],
+                              ws["gdn"], act, pos0=pos0, nk=c.linear_num_key_heads, nv=c.linear_num_value_heads,
+                              dk=c.linear_key_head_dim, dv=c.linear_value_head_dim, eps=self.eps)
+            else:
+                j = self.full_ids[li]
+                act = ws["act"][:T, :c.num_attention_heads * c.head_dim]
+                q = ws["q"][:T]
+                K.attn_prep(proj, lw.qg, lw.kg, cos, sin, ridx, slots, q, self.kpool[j], self.vpool[j],
+                            nh=c.num_attention_heads, nkv=c.num_key_value_heads, hd=c.head_dim,
+                            rot=c.rotary_dim, eps=self.eps)
+                K.attn_prefill(q, proj, self.kpool[j], self.vpool[j], block_table, act, q_pos0=pos0,
+                               nh=c.num_attention_heads, nkv=c.num_key_value_heads, hd=c.head_dim)
+            K.gemm(act, lw.w_out, out=res, residual=res)
+            K.rmsnorm(res, lw.post_gain, self.eps, out=normed)
+            if lw.moe is not None:
+                lw.moe.forward_prefill(normed, res, self)
+            else:
+                gu = ws["gu"][:T]
+                K.gemm(normed, lw.w_gu, out=gu)
+                inter = K.swiglu(gu, ws["inter"][:T])
+                K.gemm(inter, lw.w_down, out=res, residual=res)
+        out_logits = None
+        self.last_hidden = None
+        if want_hidden:
+            self.last_hidden = K.rmsnorm(res, self.final_gain, self.eps)
+        if want_logits:
+            out_logits = torch.empty(1, c.vocab_size, dtype=torch.float32, device=self.device)
+            K.gemv(self.lm_head, None, out_logits, norm=(res[T - 1:T].contiguous(), None, self.final_gain, None, self.eps))
+            out_logits = out_logits[0]
+        return out_logits
+
+    # ------------------------------------------------------------------ decode
+    def _row_buffers(self, M: int) -> dict:
+        b = self._rows.get(M)
+        if b is None:
+            c, dev, bf = self.cfg, self.device, torch.bfloat16
+            H = c.hidden_size
+            nsplit = K.decode_splits(c.num_key_value_heads, M)
+            b = {
+                "tokens": torch.zeros(M, dtype=torch.int64, device=dev),
+                "positions": torch.full((M,), -1, dtype=torch.int32, device=dev),
+                "rope_pos": torch.zeros(M, dtype=torch.int32, device=dev),
+                "slots": torch.full((M,), -1, dtype=torch.int32, device=dev),
+                "block_table": torch.zeros(M, self.max_blocks_per_seq, dtype=torch.int32, device=dev),
+                "res": [torch.zeros(M, H, dtype=bf, device=dev) for _ in range(2)],
+                "h": torch.zeros(M, H, dtype=bf, device=dev),
+                "h2": torch.zeros(M, H, dtype=bf, device=dev),
+                "proj": torch.zeros(M, self.in_width, dtype=bf, device=dev),
+                "act_lin": torch.zeros(M, c.lin_vdim, dtype=bf, device=dev),
+                "act_full": torch.zeros(M, c.num_attention_heads * c.head_dim, dtype=bf, device=dev),
+                "inter": torch.zeros(M, max(1, c.intermediate_size), dtype=bf, device=dev),
+                "logits": torch.zeros(M, c.vocab_size, dtype=torch.float32, device=dev),
+                "next": torch.zeros(M, dtype=torch.int64, device=dev),
+                "hidden": torch.zeros(M, H, dtype=bf, device=dev),
+                "nsplit": nsplit,
+                "part_o": torch.zeros(M, c.num_attention_heads, nsplit, c.head_dim, dtype=torch.float32, device=dev),
+                "part_ml": torch.zeros(M, c.num_attention_heads, nsplit, 2, dtype=torch.float32, device=dev),
+                # host staging (pinned) so that set_rows is one async copy per array
+                "h_tokens": torch.zeros(M, dtype=torch.int64).pin_memory(),
+                "h_meta": torch.zeros(3, M, dtype=torch.int32).pin_memory(),
+                "h_bt": torch.zeros(M, self.max_blocks_per_seq, dtype=torch.int32).pin_memory(),
+            }
+            self._rows[M] = b
+        return b
+
+    def _decode_body(self, M: int) -> None:
+        """One decode step for the ``M`` rows staged in the bucket's buffers (graph-capturable)."""
+        c, b = self.cfg, self._row_buffers(M)
+        cur, nxt = b["res"]
+        K.embed_gather(self.embed, b["tokens"], cur)
+        carry = None
+        for li, lw in enumerate(self.layers):
+            n_in = lw.w_in.shape[0]
+            proj = b["proj"][:, :n_in]
+            K.gemv(lw.w_in, None, proj, norm=(cur, carry, lw.in_gain, nxt if carry is not None else None, self.eps))
+            if carry is not None:
+                cur, nxt = nxt, cur
+            if lw.kind == LINEAR:
+                j = self.lin_ids[li]
+                act = b["act_lin"]
+                K.gdn_decode(proj, lw.conv_w, lw.A_log, lw.dt_bias, lw.norm_w, self.ring[j], self.state[j],
+                             b["slots"], b["positions"], act, nk=c.linear_num_key_heads,
+                             nv=c.linear_num_value_heads, dk=c.linear_key_head_dim, dv=c.linear_value_head_dim,
+                             eps=self.eps)
+            else:
+                j = self.full_ids[li]
+                act = b["act_full"]
+                K.attn_decode(proj, lw.qg, lw.kg, self.cos, self.sin, b["positions"], b["rope_pos"],
+                              b["block_table"], self.kpool[j], self.vpool[j], b["part_o"], b["part_ml"], act,
+                              nh=c.num_attention_heads, nkv=c.num_key_value_heads, hd=c.head_dim,
+                              rot=c.rotary_dim, nsplit=b["nsplit"], eps=self.eps)
+            K.gemv(lw.w_out, act, b["h"])
+            if lw.moe is not None:
+                lw.moe.forward_decode(cur, b["h"], nxt, lw.post_gain, b["h2"], self, M)
+                cur, nxt = nxt, cur
+            else:
+                K.gemv(lw.w_gu, None, b["inter"], swiglu=True, norm=(cur, b["h"], lw.post_gain, nxt, self.eps))
+                cur, nxt = nxt, cur
+                K.gemv(lw.w_down, b["inter"], b["h2"])
+            carry = b["h2"]
+        K.gemv(self.lm_head, None, b["logits"], norm=(cur, carry, self.final_gain, nxt, self.eps))
+        K.argmax(b["logits"], b["next"])
+        b["final_res"] = nxt
+
+    def set_rows(self, M: int, tokens, positions, slots, block_tables, rope_deltas=None) -> None:
+        """Stage up to ``M`` rows (lists of per-row values); missing rows are padding."""
+        b = self._row_buffers(M)
+        n = len(tokens)
+        ht, hm, hb = b["h_tokens"], b["h_meta"], b["h_bt"]
+        ht.zero_()
+        hm[0].fill_(-1)
+        hm[1].zero_()
+        hm[2].fill_(-1)
+        for r in range(n):
+            ht[r] = tokens[r]
+            hm[0, r] = positions[r]
+            hm[1, r] = positions[r] + (rope_deltas[r] if rope_deltas else 0)
+            hm[2, r] = slots[r]
+            bt = block_tables[r]
+            hb[r, :len(bt)] = torch.as_tensor(bt, dtype=torch.int32)
+        b["tokens"].copy_(ht, non_blocking=True)
+        b["positions"].copy_(hm[0], non_blocking=True)
+        b["rope_pos"].copy_(hm[1], non_blocking=True)
+        b["slots"].copy_(hm[2], non_blocking=True)
+        b["block_table"].copy_(hb, non_blocking=True)
+
+    def capture(self, M: int, warmup: int = 2) -> None:
+        """Capture the decode step of bucket ``M`` into a CUDA graph. Warm-up runs use padded
+        rows (slot -1 / position -1) so that no sequence state is touched."""
+        if M in self._graphs:
+            return
+        b = self._row_buffers(M)
+        saved = (b["positions"].clone(), b["slots"].clone())
+        b["positions"].fill_(-1)
+        b["slots"].fill_(-1)
+        s = torch.cuda.Stream(device=self.device)
+        s.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(s):
+            for _ in range(warmup):
+                self._decode_body(M)
+        torch.cuda.current_stream().wait_stream(s)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        if self.graph_pool is None:
+            self.graph_pool = torch.cuda.graph_pool_handle()
+        l0 = K.LAUNCHES
+        with torch.cuda.graph(g, pool=self.graph_pool):
+            self._decode_body(M)
+        self._step_launches[M] = K.LAUNCHES - l0
+        self._graphs[M] = g
+        b["positions"].copy_(saved[0])
+        b["slots"].copy_(saved[1])
+
+    @torch.no_grad()
+    def decode(self, M: int, graph: bool = True) -> tuple[torch.Tensor, torch.Tensor]:
+        """Run one decode step on the staged rows. Returns ``(next_tokens [M], logits [M, V])``
+        device tensors owned by the bucket (overwritten by the next step)."""
+        b = self._row_buffers(M)
+        if graph:
+            if M not in self._graphs:
+                self.capture(M)
+            self._graphs[M].replay()
+        else:
+            self._decode_body(M)
+        return b["next"], b["logits"]
+
+    def advance_rows(self, M: int) -> None:
+        """Feed the sampled tokens back and advance positions by one (device-side, no host sync):
+        lets a caller run many greedy steps back to back."""
+        b = self._row_buffers(M)
+        b["tokens"].copy_(b["next"])
+        live = b["positions"] >= 0
+        b["positions"].add_(live.to(torch.int32))
+        b["rope_pos"].add_(live.to(torch.int32))
+
+    @staticmethod
+    def bucket_for(n: int) -> int:
+        for m in BUCKETS:
+            if n <= m:
+                return m
+        raise ValueError(f"{n} rows exceed the largest decode bucket {BUCKETS[-1]}")

@@ -1,0 +1,230 @@
+"""Python entry points of the sm_100a kernels (thin shape-checking wrappers over ctypes).
+
+Every function launches on the current CUDA stream and writes into caller-owned buffers
+where one is passed, so a decode step can be captured in a CUDA graph with fixed addresses.
+The capability list mirrors the reference's op table (``backends/protocol.py:129-498``)
+at the granularity of the fused kernels, not op for op.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+
+from . import _lib
+from ._lib import call
+
+BLOCK = 64          # tokens per KV block (and key tile)
+RING = 16           # conv ring depth of the delta-net layers
+
+_status: dict[int, torch.Tensor] = {}
+LAUNCHES = 0        # kernels launched through this module (bench bookkeeping)
+
+
+def _count(n: int = 1) -> None:
+    global LAUNCHES
+    LAUNCHES += n
+
+
+def status_word(device=None) -> torch.Tensor:
+    """Per-device int32 status word the tensor-core kernels set when a bounded wait runs out."""
+    dev = torch.device(device if device is not None else torch.cuda.current_device())
+    idx = dev.index if dev.index is not None else torch.cuda.current_device()
+    t = _status.get(idx)
+    if t is None:
+        t = torch.zeros(4, dtype=torch.int32, device=f"cuda:{idx}")
+        _status[idx] = t
+    return t
+
+
+def check_status() -> None:
+    for idx, t in _status.items():
+        code = int(t[0].item())
+        if code:
+            t.zero_()
+            raise _lib.KernelError(f"device-side wait timed out on cuda:{idx} (role {code})")
+
+
+# ------------------------------------------------------------------ row-wise kernels
+def embed_gather(table: torch.Tensor, tokens: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    T, (V, H) = tokens.numel(), table.shape
+    if out is None:
+        out = torch.empty(T, H, dtype=table.dtype, device=table.device)
+    assert tokens.dtype == torch.int64 and table.dtype == torch.bfloat16
+    call("embed_gather", table, tokens, out, T, H, V)
+    _count()
+    return out
+
+
+def rmsnorm(x: torch.Tensor, gain: torch.Tensor, eps: float, out: torch.Tensor | None = None,
+            add: torch.Tensor | None = None, res_out: torch.Tensor | None = None) -> torch.Tensor:
+    """``out = rmsnorm(x [+ add]) * gain``; with ``add`` the sum is also written to ``res_out``
+    (which may be ``x`` itself)."""
+    M, N = x.shape
+    if out is None:
+        out = torch.empty_like(x)
+    assert gain.dtype == torch.float32 and x.stride(1) == 1 and out.stride(1) == 1
+    if add is not None:
+        assert add.stride(0) == x.stride(0)
+        if res_out is not None:
+            assert res_out.stride(0) == x.stride(0)
+    call("rmsnorm", x, add, gain, res_out, out, M, N, x.stride(0), out.stride(0), float(eps))
+    _count()
+    return out
+
+
+def swiglu(gu: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    M, two_i = gu.shape
+    I = two_i // 2
+    if out is None:
+        out = torch.empty(M, I, dtype=gu.dtype, device=gu.device)
+    call("swiglu", gu, out, M, I, gu.stride(0), out.stride(0))
+    _count()
+    return out
+
+
+def argmax(logits: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    M, V = logits.shape
+    assert logits.dtype == torch.float32
+    if out is None:
+        out = torch.empty(M, dtype=torch.int64, device=logits.device)
+    call("argmax", logits, out, M, V, logits.stride(0))
+    _count()
+    return out
+
+
+def sample(logits: torch.Tensor, temperature: torch.Tensor, u: torch.Tensor,
+           out: torch.Tensor | None = None) -> torch.Tensor:
+    """Per-row temperature sampling (``temperature[row] <= 0`` = greedy) with host-supplied
+    uniforms ``u``."""
+    M, V = logits.shape
+    if out is None:
+        out = torch.empty(M, dtype=torch.int64, device=logits.device)
+    call("sample", logits, temperature, u, out, M, V, logits.stride(0))
+    _count()
+    return out
+
+
+def block_copy(dst: torch.Tensor, src: torch.Tensor, dst_idx: torch.Tensor, src_idx: torch.Tensor) -> None:
+    """``dst[dst_idx[j]] = src[src_idx[j]]`` over the leading axis (KV block COW, state snapshots)."""
+    nbytes = dst[0].numel() * dst.element_size()
+    assert src[0].numel() * src.element_size() == nbytes and dst_idx.dtype == torch.int64
+    call("block_copy", dst, src, dst_idx, src_idx, dst_idx.numel(), nbytes)
+    _count()
+
+
+# ------------------------------------------------------------------ projections
+def gemv(W: torch.Tensor, x: torch.Tensor | None, out: torch.Tensor, *, swiglu: bool = False,
+         norm: tuple | None = None) -> torch.Tensor:
+    """Decode projection for 1, 2, 4 or 8 rows.
+
+    ``W [N, K]`` (``[2I, K]`` gate rows then up rows with ``swiglu``); ``out [M, N]`` bf16 or fp32.
+    ``norm = (res_in, add | None, gain, res_out | None, eps)`` replaces ``x`` by
+    ``rmsnorm(res_in + add) * gain`` computed inside the kernel; ``res_out`` receives the sum.
+    """
+    M = out.shape[0]
+    K = W.shape[1]
+    N = W.shape[0] // 2 if swiglu else W.shape[0]
+    mode = (1 if swiglu else 0) | (2 if out.dtype == torch.float32 else 0)
+    if norm is None:
+        assert x is not None and x.is_contiguous() and x.shape == (M, K)
+        call("gemv_bf16", W, x, out, M, N, K, out.stride(0), mode, N, None, None, None, None, 0.0)
+    else:
+        res_in, add, gain, res_out, eps = norm
+        assert res_in.is_contiguous() and res_in.shape == (M, K)
+        call("gemv_bf16", W, None, out, M, N, K, out.stride(0), mode, N, res_in, add, gain, res_out, float(eps))
+    _count()
+    return out
+
+
+def gemm(A: torch.Tensor, W: torch.Tensor, out: torch.Tensor | None = None,
+         residual: torch.Tensor | None = None, bn: int = 0) -> torch.Tensor:
+    """Prefill projection on tcgen05: ``out[M, N] = A[M, K] @ W[N, K]^T (+ residual)``, bf16."""
+    M, K = A.shape
+    N = W.shape[0]
+    if out is None:
+        out = torch.empty(M, N, dtype=torch.bfloat16, device=A.device)
+    assert A.stride(1) == 1 and W.stride(1) == 1 and out.stride(1) == 1
+    call("gemm_bf16", A, A.stride(0), W, W.stride(0), out, out.stride(0), residual,
+         residual.stride(0) if residual is not None else 0, M, N, K, bn, status_word(A.device))
+    _count()
+    return out
+
+
+def gemm_i8(Aq: torch.Tensor, a_scale: torch.Tensor, Wq: torch.Tensor, w_scale: torch.Tensor,
+            out: torch.Tensor | None = None, residual: torch.Tensor | None = None, bn: int = 0) -> torch.Tensor:
+    """W8A8 projection: int8 x int8 -> int32 on tcgen05 (kind::i8), ``* a_scale[m] * w_scale[n]``."""
+    M, K = Aq.shape
+    N = Wq.shape[0]
+    if out is None:
+        out = torch.empty(M, N, dtype=torch.bfloat16, device=Aq.device)
+    call("gemm_i8", Aq, Aq.stride(0), Wq, Wq.stride(0), out, out.stride(0), residual,
+         residual.stride(0) if residual is not None else 0, a_scale, w_scale, M, N, K, bn,
+         status_word(Aq.device))
+    _count()
+    return out
+
+
+# ------------------------------------------------------------------ gated delta net
+def gdn_decode(proj, conv_w, A_log, dt_bias, norm_w, ring, state, slots, positions, out, *, nk, nv, dk, dv,
+               eps, ntok: int = 1, record: torch.Tensor | None = None, write_state: bool = True) -> torch.Tensor:
+    M = slots.numel()
+    assert proj.shape[0] == M * ntok and slots.dtype == torch.int32 and positions.dtype == torch.int32
+    call("gdn_decode", proj, proj.stride(0), conv_w, A_log, dt_bias, norm_w, ring, state, slots, positions,
+         out, out.stride(0), record, record.shape[1] if record is not None else 0, M, ntok,
+         int(write_state), nk, nv, dk, dv, float(eps))
+    _count()
+    return out
+
+
+def gdn_commit(state, record, slots, steps, *, nv, dk, dv) -> None:
+    call("gdn_commit", state, record, slots, steps, record.shape[1], slots.numel(), nv, dk, dv)
+    _count()
+
+
+def gdn_prefill_scratch_floats(T: int, nk: int, nv: int, dk: int, dv: int) -> int:
+    fn = _lib.lib().cb_gdn_prefill_scratch
+    import ctypes
+    fn.restype = ctypes.c_int64
+    return int(fn(*[ctypes.c_int64(v) for v in (T, nk, nv, dk, dv)]))
+
+
+def gdn_prefill(proj, conv_w, A_log, dt_bias, norm_w, ring_seq, state_seq, scratch, out, *, pos0, nk, nv, dk, dv,
+                eps) -> torch.Tensor:
+    T = proj.shape[0]
+    assert scratch.dtype == torch.float32 and scratch.numel() >= gdn_prefill_scratch_floats(T, nk, nv, dk, dv)
+    call("gdn_prefill", proj, proj.stride(0), conv_w, A_log, dt_bias, norm_w, ring_seq, state_seq, scratch,
+         out, out.stride(0), T, pos0, nk, nv, dk, dv, float(eps))
+    _count(5)
+    return out
+
+
+# ------------------------------------------------------------------ attention
+def attn_prep(proj, qg, kg, cos, sin, rope_idx, kv_slot, q_out, kpool, vpool, *, nh, nkv, hd, rot, eps) -> None:
+    T = proj.shape[0]
+    call("attn_prep", proj, proj.stride(0), qg, kg, cos, sin, rope_idx, kv_slot, q_out, kpool, vpool,
+         T, nh, nkv, hd, rot, float(eps))
+    _count()
+
+
+def attn_prefill(q, proj, kpool, vpool, block_table, out, *, q_pos0, nh, nkv, hd) -> torch.Tensor:
+    T = q.shape[0]
+    call("attn_prefill", q, proj, proj.stride(0), kpool, vpool, block_table, out, out.stride(0), T, q_pos0,
+         nh, nkv, hd)
+    _count()
+    return out
+
+
+def attn_decode(proj, qg, kg, cos, sin, positions, rope_pos, block_table, kpool, vpool, part_o, part_ml, out, *,
+                nh, nkv, hd, rot, nsplit, eps) -> torch.Tensor:
+    M = positions.numel()
+    call("attn_decode", proj, proj.stride(0), qg, kg, cos, sin, positions, rope_pos, block_table,
+         block_table.stride(0), kpool, vpool, part_o, part_ml, out, out.stride(0), M, nh, nkv, hd, rot,
+         nsplit, float(eps))
+    _count(2)
+    return out
+
+
+def decode_splits(nkv: int, rows: int) -> int:
+    """Key-tile splits so that a decode attention launch covers about two waves of SMs."""
+    return max(1, min(32, 296 // max(1, nkv * rows)))

@@ -1,0 +1,272 @@
+"""Each sm_100a kernel against the fp32 PyTorch definition of the same op (small shapes,
+odd sizes, tails).  Tolerances: bf16 outputs 2e-2 relative to the row scale, fp32 1e-4."""
+import math
+
+import pytest
+import torch
+
+from coffin_b200.oracle import ops as O
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def K():
+    from coffin_b200.ops import kernels
+    return kernels
+
+
+def close(got, ref, tol=2e-2):
+    got, ref = got.float().cpu(), ref.float().cpu()
+    scale = ref.abs().max().clamp_min(1e-6)
+    err = (got - ref).abs().max() / scale
+    assert torch.isfinite(got).all()
+    assert err < tol, f"relative error {err:.4g} (scale {scale:.4g})"
+
+
+def bf(*shape, s=1.0, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(*shape, generator=g) * s).to(torch.bfloat16)
+
+
+def test_rowwise_kernels():
+    k = K()
+    x, add = bf(5, 520, seed=1), bf(5, 520, seed=2)
+    gain = (1 + 0.1 * torch.randn(520)).float()
+    out = k.rmsnorm(x.to(DEV), gain.to(DEV), 1e-6)
+    close(out, O.rms_norm(x, gain))
+    res = torch.empty_like(x, device=DEV)
+    out = k.rmsnorm(x.to(DEV), gain.to(DEV), 1e-6, add=add.to(DEV), res_out=res)
+    s, n = O.add_rms_norm(x, add, gain)
+    close(res, s)
+    close(out, n)
+    gu = bf(7, 2 * 264, seed=3)
+    close(k.swiglu(gu.to(DEV)), O.silu_mul(gu[:, :264], gu[:, 264:]))
+    logits = torch.randn(3, 4099)
+    logits[1, 77] = logits[1, 4000] = 50.0
+    assert k.argmax(logits.to(DEV)).cpu().tolist() == logits.argmax(-1).tolist()[:1] + [77] + logits.argmax(-1).tolist()[2:]
+    table = bf(100, 64, seed=4)
+    toks = torch.tensor([3, 99, 0, 3])
+    assert torch.equal(k.embed_gather(table.to(DEV), toks.to(DEV)).cpu(), table[toks])
+    temp = torch.tensor([0.0, 1.0, 0.5]).to(DEV)
+    u = torch.tensor([0.3, 0.0, 0.999999]).to(DEV)
+    got = k.sample(logits.to(DEV), temp, u).cpu()
+    assert got[0] == logits[0].argmax() and 0 <= got[1] < 4099 and 0 <= got[2] < 4099
+    # inverse-CDF check for row 2
+    p = torch.softmax(logits[2].double() / 0.5, -1).cumsum(0)
+    assert abs(int(got[2]) - int((p > 0.999999).nonzero()[0])) <= 2 or p[int(got[2])] > 0.9999
+    src = torch.arange(4 * 32, dtype=torch.float32).reshape(4, 32).to(DEV)
+    dst = torch.zeros(6, 32, device=DEV)
+    k.block_copy(dst, src, torch.tensor([5, 0]).to(DEV), torch.tensor([1, 3]).to(DEV))
+    assert torch.equal(dst[5], src[1]) and torch.equal(dst[0], src[3]) and dst[1].sum() == 0
+
+
+@pytest.mark.parametrize("M", [1, 2, 4, 8])
+@pytest.mark.parametrize("N,Kd", [(520, 512), (2560, 1032), (37, 264), (6000, 256)])
+def test_gemv(M, N, Kd):
+    k = K()
+    W, x = bf(N, Kd, s=0.05, seed=5), bf(M, Kd, seed=6)
+    out = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
+    k.gemv(W.to(DEV), x.to(DEV), out)
+    close(out, x.float() @ W.float().t())
+    out32 = torch.empty(M, N, dtype=torch.float32, device=DEV)
+    k.gemv(W.to(DEV), x.to(DEV), out32)
+    close(out32, x.float() @ W.float().t(), 1e-3)
+
+
+@pytest.mark.parametrize("M", [1, 4])
+def test_gemv_fused_norm_swiglu(M):
+    k = K()
+    H, I = 520, 264
+    Wgu, res, add = bf(2 * I, H, s=0.05, seed=7), bf(M, H, seed=8), bf(M, H, seed=9)
+    gain = (1 + 0.1 * torch.randn(H)).float()
+    out = torch.empty(M, I, dtype=torch.bfloat16, device=DEV)
+    res_out = torch.empty(M, H, dtype=torch.bfloat16, device=DEV)
+    k.gemv(Wgu.to(DEV), None, out, swiglu=True, norm=(res.to(DEV), add.to(DEV), gain.to(DEV), res_out, 1e-6))
+    s, n = O.add_rms_norm(res, add, gain)
+    n = n.to(torch.bfloat16).float()
+    gu = n @ Wgu.float().t()
+    close(res_out, s)
+    close(out, O.silu_mul(gu[:, :I], gu[:, I:]), 3e-2)
+    out2 = torch.empty(M, 2 * I, dtype=torch.bfloat16, device=DEV)
+    k.gemv(Wgu.to(DEV), None, out2, norm=(res.to(DEV), None, gain.to(DEV), None, 1e-6))
+    close(out2, O.rms_norm(res, gain).to(torch.bfloat16).float() @ Wgu.float().t())
+
+
+@pytest.mark.parametrize("M,N,Kd,bn", [(128, 256, 64, 256), (200, 264, 192, 128), (300, 520, 1032, 0),
+                                       (64, 64, 256, 64), (1000, 1536, 512, 256), (130, 136, 72, 128)])
+def test_gemm_tcgen05(M, N, Kd, bn):
+    k = K()
+    A, W = bf(M, Kd, seed=10), bf(N, Kd, s=0.05, seed=11)
+    out = k.gemm(A.to(DEV), W.to(DEV), bn=bn)
+    torch.cuda.synchronize()
+    k.check_status()
+    close(out, A.float() @ W.float().t())
+    res = bf(M, N, seed=12)
+    out = k.gemm(A.to(DEV), W.to(DEV), residual=res.to(DEV), bn=bn)
+    torch.cuda.synchronize()
+    k.check_status()
+    close(out, A.float() @ W.float().t() + res.float())
+
+
+@pytest.mark.parametrize("M,N,Kd,bn", [(128, 256, 128, 256), (200, 264, 400, 128), (77, 520, 1040, 0)])
+def test_gemm_i8_tcgen05(M, N, Kd, bn):
+    k = K()
+    g = torch.Generator().manual_seed(13)
+    Aq = torch.randint(-127, 128, (M, Kd), generator=g, dtype=torch.int8)
+    Wq = torch.randint(-127, 128, (N, Kd), generator=g, dtype=torch.int8)
+    sa, sw = torch.rand(M, generator=g) * 0.01 + 1e-3, torch.rand(N, generator=g) * 0.01 + 1e-3
+    out = k.gemm_i8(Aq.to(DEV), sa.to(DEV), Wq.to(DEV), sw.to(DEV), bn=bn)
+    torch.cuda.synchronize()
+    k.check_status()
+    ref = (Aq.double() @ Wq.double().t()) * sa.double()[:, None] * sw.double()[None, :]
+    close(out, ref.float(), 1e-2)
+
+
+def _gdn_inputs(T, nk, nv, dk, dv, seed):
+    conv_dim = 2 * nk * dk + nv * dv
+    ldp = (conv_dim + nv * dv + 2 * nv + 7) // 8 * 8     # rows are 16-byte aligned, as in the model
+    proj = bf(T, ldp, seed=seed)
+    g = torch.Generator().manual_seed(seed + 100)
+    conv_w = (torch.randn(conv_dim, 4, generator=g) * 0.3).float()
+    A_log = torch.log(1 + 15 * torch.rand(nv, generator=g))
+    dt_bias = torch.randn(nv, generator=g) * 0.5
+    norm_w = 1 + 0.1 * torch.randn(dv, generator=g)
+    return proj, conv_w, A_log, dt_bias, norm_w, conv_dim
+
+
+def _gdn_oracle(proj, conv_w, A_log, dt_bias, norm_w, nk, nv, dk, dv, conv_state, state):
+    """fp32 oracle over T rows: returns the normed outputs, updates states in place."""
+    T = proj.shape[0]
+    conv_dim = 2 * nk * dk + nv * dv
+    p = proj.float()
+    qkv, z = p[:, :conv_dim], p[:, conv_dim:conv_dim + nv * dv]
+    b, a = p[:, conv_dim + nv * dv:conv_dim + nv * dv + nv], p[:, conv_dim + nv * dv + nv:conv_dim + nv * dv + 2 * nv]
+    conv, new_conv = O.conv1d_silu_seq(conv_w, qkv, conv_state)
+    conv_state.copy_(new_conv)
+    q = conv[:, :nk * dk].reshape(T, nk, dk)
+    kk = conv[:, nk * dk:2 * nk * dk].reshape(T, nk, dk)
+    v = conv[:, 2 * nk * dk:].reshape(T, nv, dv)
+    qn, kn, beta, g = O.gdn_head_prep(q, kk, b, a, A_log, dt_bias, nv // nk)
+    o = O.delta_recurrent(qn, kn, v, beta, g, state)
+    return O.rms_norm_gated(o, norm_w, z.reshape(T, nv, dv)).reshape(T, nv * dv)
+
+
+@pytest.mark.parametrize("nk,nv,dk,dv", [(2, 4, 64, 64), (2, 4, 128, 128), (2, 6, 128, 128)])
+def test_gdn_decode_steps_and_verify(nk, nv, dk, dv):
+    k = K()
+    T = 9
+    proj, conv_w, A_log, dt_bias, norm_w, conv_dim = _gdn_inputs(T, nk, nv, dk, dv, 20)
+    conv_state, state = torch.zeros(conv_dim, 3), torch.zeros(nv, dk, dv)
+    ref = _gdn_oracle(proj, conv_w, A_log, dt_bias, norm_w, nk, nv, dk, dv, conv_state, state)
+    d = lambda t: t.to(DEV)
+    ring = torch.zeros(3, k.RING, conv_dim, dtype=torch.bfloat16, device=DEV)
+    st = torch.zeros(3, nv, dk, dv, device=DEV)
+    slots = torch.tensor([2], dtype=torch.int32, device=DEV)
+    out = torch.empty(T, nv * dv, dtype=torch.bfloat16, device=DEV)
+    cw, al, db, nw = d(conv_w), d(A_log), d(dt_bias), d(norm_w.float())
+    for t in range(5):      # five single-token steps
+        pos = torch.tensor([t], dtype=torch.int32, device=DEV)
+        k.gdn_decode(d(proj[t:t + 1]), cw, al, db, nw, ring, st, slots, pos, out[t:t + 1], nk=nk, nv=nv, dk=dk,
+                     dv=dv, eps=1e-6)
+    # then a 4-token verify chain that leaves the state untouched and records the updates
+    rec = torch.zeros(1, 4, nv, dk + dv + 1, device=DEV)
+    base = st.clone()
+    pos = torch.tensor([5], dtype=torch.int32, device=DEV)
+    k.gdn_decode(d(proj[5:9]), cw, al, db, nw, ring, st, slots, pos, out[5:9], nk=nk, nv=nv, dk=dk, dv=dv,
+                 eps=1e-6, ntok=4, record=rec, write_state=False)
+    assert torch.equal(st, base)
+    close(out, ref, 3e-2)
+    k.gdn_commit(st, rec, slots, torch.tensor([4], dtype=torch.int32, device=DEV), nv=nv, dk=dk, dv=dv)
+    close(st[2], state, 1e-3)
+    assert st[0].abs().sum() == 0
+
+
+@pytest.mark.parametrize("nk,nv,dk,dv,T1,T2", [(2, 4, 64, 64, 150, 37), (2, 4, 128, 128, 64, 70), (1, 2, 128, 128, 5, 3)])
+def test_gdn_prefill_chunked(nk, nv, dk, dv, T1, T2):
+    k = K()
+    T = T1 + T2
+    proj, conv_w, A_log, dt_bias, norm_w, conv_dim = _gdn_inputs(T, nk, nv, dk, dv, 30)
+    conv_state, state = torch.zeros(conv_dim, 3), torch.zeros(nv, dk, dv)
+    ref = _gdn_oracle(proj, conv_w, A_log, dt_bias, norm_w, nk, nv, dk, dv, conv_state, state)
+    d = lambda t: t.to(DEV)
+    ring = torch.zeros(k.RING, conv_dim, dtype=torch.bfloat16, device=DEV)
+    st = torch.zeros(nv, dk, dv, device=DEV)
+    out = torch.empty(T, nv * dv, dtype=torch.bfloat16, device=DEV)
+    scratch = torch.empty(k.gdn_prefill_scratch_floats(max(T1, T2), nk, nv, dk, dv), device=DEV)
+    args = (d(conv_w), d(A_log), d(dt_bias), d(norm_w.float()), ring, st, scratch)
+    pj = d(proj)
+    k.gdn_prefill(pj[:T1], *args, out[:T1], pos0=0, nk=nk, nv=nv, dk=dk, dv=dv, eps=1e-6)
+    k.gdn_prefill(pj[T1:], *args, out[T1:], pos0=T1, nk=nk, nv=nv, dk=dk, dv=dv, eps=1e-6)
+    close(out, ref, 3e-2)
+    close(st, state, 2e-3)
+    # a decode step after the chunked prefill continues from the ring + state
+    extra = bf(1, proj.shape[1], seed=31)
+    ref2 = _gdn_oracle(extra, conv_w, A_log, dt_bias, norm_w, nk, nv, dk, dv, conv_state, state)
+    out2 = torch.empty(1, nv * dv, dtype=torch.bfloat16, device=DEV)
+    k.gdn_decode(d(extra), d(conv_w), d(A_log), d(dt_bias), d(norm_w.float()), ring.unsqueeze(0), st.unsqueeze(0),
+                 torch.zeros(1, dtype=torch.int32, device=DEV), torch.tensor([T], dtype=torch.int32, device=DEV),
+                 out2, nk=nk, nv=nv, dk=dk, dv=dv, eps=1e-6)
+    close(out2, ref2, 3e-2)
+
+
+def _attn_setup(T, nh, nkv, hd, rot, seed):
+    ldp = nh * 2 * hd + 2 * nkv * hd
+    proj = bf(T, ldp, seed=seed)
+    g = torch.Generator().manual_seed(seed + 1)
+    qg, kg = 1 + 0.1 * torch.randn(hd, generator=g), 1 + 0.1 * torch.randn(hd, generator=g)
+    cos, sin = O.rope_tables(rot, 1e7, 4096)
+    return proj, qg.float(), kg.float(), cos, sin
+
+
+def _attn_oracle(proj, qg, kg, cos, sin, nh, nkv, hd, rot, pos):
+    T = proj.shape[0]
+    p = proj.float()
+    qgate = p[:, :nh * 2 * hd].reshape(T, nh, 2 * hd)
+    q, gate = qgate[..., :hd], qgate[..., hd:]
+    kk = p[:, nh * 2 * hd:nh * 2 * hd + nkv * hd].reshape(T, nkv, hd)
+    v = p[:, nh * 2 * hd + nkv * hd:].reshape(T, nkv, hd)
+    q = O.apply_rope(O.rms_norm(q, qg), cos[pos], sin[pos], rot)
+    kk = O.apply_rope(O.rms_norm(kk, kg), cos[pos], sin[pos], rot)
+    return O.gated_attention(q, gate, kk, v, pos, hd ** -0.5).reshape(T, nh * hd), kk, v
+
+
+@pytest.mark.parametrize("nh,nkv,hd,rot,T1,T2", [(4, 2, 64, 16, 100, 30), (4, 1, 256, 64, 70, 129), (2, 2, 256, 64, 3, 1)])
+def test_attention_prefill_and_decode(nh, nkv, hd, rot, T1, T2):
+    k = K()
+    T = T1 + T2 + 3
+    proj, qg, kg, cos, sin = _attn_setup(T, nh, nkv, hd, rot, 40)
+    pos = torch.arange(T)
+    ref, kref, vref = _attn_oracle(proj, qg, kg, cos, sin, nh, nkv, hd, rot, pos)
+    d = lambda t: t.to(DEV)
+    nblk = (T + 63) // 64
+    pool_blocks = nblk + 3
+    kpool = torch.zeros(pool_blocks * 64, nkv, hd, dtype=torch.bfloat16, device=DEV)
+    vpool = torch.zeros_like(kpool)
+    bt = torch.tensor(list(range(pool_blocks - 1, pool_blocks - 1 - nblk, -1)), dtype=torch.int32)  # reversed blocks
+    slot_of = lambda p: int(bt[p // 64]) * 64 + p % 64
+    out = torch.empty(T, nh * hd, dtype=torch.bfloat16, device=DEV)
+    pj, dc, ds = d(proj), d(cos), d(sin)
+    for s, e in ((0, T1), (T1, T1 + T2)):
+        n = e - s
+        q = torch.empty(n, nh, hd, dtype=torch.bfloat16, device=DEV)
+        slots = torch.tensor([slot_of(p) for p in range(s, e)], dtype=torch.int32, device=DEV)
+        ridx = torch.arange(s, e, dtype=torch.int32, device=DEV)
+        k.attn_prep(pj[s:e], d(qg), d(kg), dc, ds, ridx, slots, q, kpool, vpool, nh=nh, nkv=nkv, hd=hd, rot=rot, eps=1e-6)
+        k.attn_prefill(q, pj[s:e], kpool, vpool, d(bt), out[s:e], q_pos0=s, nh=nh, nkv=nkv, hd=hd)
+    # three decode steps (2 rows in the bucket: row 1 is padding)
+    nsplit = 3
+    part_o = torch.empty(2, nh, nsplit, hd, device=DEV)
+    part_ml = torch.empty(2, nh, nsplit, 2, device=DEV)
+    btab = torch.zeros(2, nblk, dtype=torch.int32)
+    btab[0] = bt
+    for p in range(T1 + T2, T):
+        posv = torch.tensor([p, -1], dtype=torch.int32, device=DEV)
+        o2 = torch.empty(2, nh * hd, dtype=torch.bfloat16, device=DEV)
+        pr = torch.cat([pj[p:p + 1], pj[p:p + 1]])
+        k.attn_decode(pr, d(qg), d(kg), dc, ds, posv, posv.clamp_min(0), d(btab), kpool, vpool, part_o, part_ml, o2,
+                      nh=nh, nkv=nkv, hd=hd, rot=rot, nsplit=nsplit, eps=1e-6)
+        out[p] = o2[0]
+    close(out, ref, 3e-2)
+    got_k = torch.stack([kpool[slot_of(p)] for p in range(T)]).cpu()
+    close(got_k, kref, 2e-2)
