@@ -101,6 +101,8 @@ def main() -> None:
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--no-pdl", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--gemv-ctas", type=int, default=0, help="tuning: GEMV CTAs per SM (0 = library default)")
+    ap.add_argument("--gemv-prefetch", type=int, default=-1, help="tuning: GEMV L2 prefetch-ahead (-1 = default)")
     args = ap.parse_args()
     sys.path.insert(0, str(ROOT))
     if args.impl == "reference":
@@ -121,6 +123,9 @@ def main() -> None:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     W = max(3, args.warmup)
+    if args.gemv_ctas or args.gemv_prefetch >= 0:
+        from coffin_b200.ops import _lib
+        _lib.call_nostream("set_gemv_opts", args.gemv_ctas or 2, 1 if args.gemv_prefetch != 0 else 0)
     cfg = preset(args.model)
     llm = LLM.from_random(cfg, seed=0, max_seq=args.prompt + args.new + 64, max_num_seqs=1,
                           tp_world=world, tp_rank=rank, graph=not args.no_graph, pdl=not args.no_pdl,
@@ -147,6 +152,7 @@ def main() -> None:
             if rank == 0:
                 sampler.start()
             l0 = K.LAUNCHES
+            r0 = llm.graph_launches_replayed
             t_wall = time.perf_counter()
         e0, e1, e2 = ev(), ev(), ev()
         dev_prompt = p.cuda(non_blocking=True)
@@ -162,7 +168,7 @@ def main() -> None:
     barrier()
     wall_s = time.perf_counter() - t_wall
     clocks = sampler.stop() if rank == 0 else {}
-    launches = (K.LAUNCHES - l0) + llm.graph_launches_replayed
+    launches = (K.LAUNCHES - l0) + (llm.graph_launches_replayed - r0)
     K.check_status()
     stats = torch.tensor([sum(pre_ms), sum(dec_ms)], dtype=torch.float64, device="cuda")
     if world > 1:

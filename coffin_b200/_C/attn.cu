@@ -59,8 +59,8 @@ __device__ __forceinline__ void norm_rope_lane(float* x, const float* gain, cons
 template <int HD>
 __global__ void __launch_bounds__(256) attn_prep_kernel(const PrepArgs a) {
   constexpr int EPL = HD / 32;
-  griddep_wait();
   griddep_launch();
+  griddep_wait();
   const int lane = threadIdx.x & 31;
   const int64_t task = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
   const int per = a.nh + 2 * a.nkv;
@@ -137,8 +137,8 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(const PrefillArgs a) 
   bf16* Qs = reinterpret_cast<bf16*>(smem_raw);  // [64][LD]
   bf16* Ks = Qs + 64 * LD;
   bf16* Vs = Ks + 64 * LD;
-  griddep_wait();
   griddep_launch();
+  griddep_wait();
   const int qt = blockIdx.x, h = blockIdx.y, kvh = h / (a.nh / a.nkv);
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, tq = lane & 3;
   constexpr int CPR = HD / 8;  // 16-byte chunks per row
@@ -284,8 +284,8 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const DecodeArgs a) {
   __shared__ float mml[4][REP][2];
   const int kvh = blockIdx.x, split = blockIdx.y, m = blockIdx.z;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  griddep_wait();
   griddep_launch();
+  griddep_wait();
   const int pos = a.positions[m];
   float* po = a.part_o + (((int64_t)m * a.nh + kvh * REP) * a.nsplit + split) * HD;
   float* pml = a.part_ml + (((int64_t)m * a.nh + kvh * REP) * a.nsplit + split) * 2;
@@ -412,8 +412,8 @@ template <int HD>
 __global__ void __launch_bounds__(HD) attn_combine_kernel(const float* part_o, const float* part_ml,
                                                           const bf16* proj, int64_t ldp, bf16* out, int64_t ldo,
                                                           int nh, int nsplit) {
-  griddep_wait();
   griddep_launch();
+  griddep_wait();
   const int h = blockIdx.x, m = blockIdx.y, d = threadIdx.x;
   const float* po = part_o + ((int64_t)m * nh + h) * nsplit * HD;
   const float* pml = part_ml + ((int64_t)m * nh + h) * nsplit * 2;

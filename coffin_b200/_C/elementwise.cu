@@ -13,8 +13,8 @@ namespace {
 
 __global__ void embed_gather_kernel(const bf16* __restrict__ table, const int64_t* __restrict__ tokens,
                                     bf16* __restrict__ out, int64_t H, int64_t V) {
-  griddep_wait();
   griddep_launch();
+  griddep_wait();
   int64_t tok = tokens[blockIdx.x];
   if (tok < 0 || tok >= V) tok = 0;
   const uint4* src = reinterpret_cast<const uint4*>(table + tok * H);
@@ -30,8 +30,8 @@ __global__ void rmsnorm_kernel(const bf16* __restrict__ x, const bf16* __restric
   extern __shared__ __align__(16) unsigned char smem_raw[];
   float* row = reinterpret_cast<float*>(smem_raw);  // [N]
   __shared__ float red[32];
-  griddep_wait();
   griddep_launch();
+  griddep_wait();
   const int64_t r = blockIdx.x;
   float ss = 0.f;
   for (int64_t c = threadIdx.x; c < (N >> 3); c += blockDim.x) {
@@ -58,8 +58,8 @@ __global__ void rmsnorm_kernel(const bf16* __restrict__ x, const bf16* __restric
 // out[m, i] = silu(gu[m, i]) * gu[m, I + i]
 __global__ void swiglu_kernel(const bf16* __restrict__ gu, bf16* __restrict__ out, int64_t I,
                               int64_t ldg, int64_t ldo, int64_t total_chunks) {
-  griddep_wait();
   griddep_launch();
+  griddep_wait();
   const int64_t cpr = I >> 3;
   for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total_chunks;
        idx += (int64_t)gridDim.x * blockDim.x) {
@@ -73,40 +73,85 @@ __global__ void swiglu_kernel(const bf16* __restrict__ gu, bf16* __restrict__ ou
   }
 }
 
-// argmax over a row of fp32 logits; ties resolve to the lowest index (torch.argmax order).
-__global__ void argmax_kernel(const float* __restrict__ logits, int64_t* __restrict__ out, int64_t V,
-                              int64_t ld) {
-  __shared__ float bv[32];
-  __shared__ int64_t bi[32];
-  griddep_wait();
-  griddep_launch();
-  const float* row = logits + (int64_t)blockIdx.x * ld;
-  float best = -INFINITY;
-  int64_t idx = 0x7fffffffffffffffLL;
-  for (int64_t i = threadIdx.x; i < V; i += blockDim.x) {
-    const float v = row[i];
-    if (v > best || (v == best && i < idx)) { best = v; idx = i; }
-  }
+// argmax over rows of fp32 logits; ties resolve to the lowest index (torch.argmax order).
+// Two stages in one launch: kArgmaxParts CTAs per row each reduce a slice into a (value, index)
+// partial in scratch memory, and the last CTA to arrive (atomic ticket) reduces the partials,
+// writes the token and re-arms the ticket, so the scratch can be reused by the next launch.
+constexpr int kArgmaxParts = 64;
+
+__device__ __forceinline__ void argmax_pair(float& best, int64_t& idx, float ov, int64_t oi) {
+  if (ov > best || (ov == best && oi < idx)) { best = ov; idx = oi; }
+}
+
+__device__ __forceinline__ void argmax_block(float& best, int64_t& idx, float* bv, int64_t* bi) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {
     const float ov = __shfl_xor_sync(0xffffffffu, best, o);
     const int64_t oi = __shfl_xor_sync(0xffffffffu, idx, o);
-    if (ov > best || (ov == best && oi < idx)) { best = ov; idx = oi; }
+    argmax_pair(best, idx, ov, oi);
   }
   const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  __syncthreads();
   if (lane == 0) { bv[w] = best; bi[w] = idx; }
   __syncthreads();
-  if (w == 0) {
-    best = lane < nw ? bv[lane] : -INFINITY;
-    idx = lane < nw ? bi[lane] : 0x7fffffffffffffffLL;
+  best = lane < nw ? bv[lane] : -INFINITY;
+  idx = lane < nw ? bi[lane] : 0x7fffffffffffffffLL;
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
-      const int64_t oi = __shfl_xor_sync(0xffffffffu, idx, o);
-      if (ov > best || (ov == best && oi < idx)) { best = ov; idx = oi; }
-    }
-    if (lane == 0) out[blockIdx.x] = idx;
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+    const int64_t oi = __shfl_xor_sync(0xffffffffu, idx, o);
+    argmax_pair(best, idx, ov, oi);
   }
+}
+
+// scratch layout per row: kArgmaxParts floats, kArgmaxParts int64, one unsigned ticket
+struct ArgmaxScratch {
+  float val[kArgmaxParts];
+  int64_t idx[kArgmaxParts];
+  unsigned int ticket;
+  unsigned int pad;
+};
+
+__device__ __forceinline__ void argmax_body(const float* __restrict__ logits, int64_t* __restrict__ out,
+                                            int64_t V, int64_t ld, ArgmaxScratch* scratch) {
+  __shared__ float bv[32];
+  __shared__ int64_t bi[32];
+  __shared__ bool last;
+  const int row = blockIdx.y, part = blockIdx.x;
+  const float* r = logits + (int64_t)row * ld;
+  const int64_t per = (V + kArgmaxParts - 1) / kArgmaxParts, b = part * per, e = min(V, b + per);
+  float best = -INFINITY;
+  int64_t idx = 0x7fffffffffffffffLL;
+  for (int64_t i = b + threadIdx.x; i < e; i += blockDim.x) argmax_pair(best, idx, r[i], i);
+  argmax_block(best, idx, bv, bi);
+  ArgmaxScratch* sc = scratch + row;
+  if (threadIdx.x == 0) {
+    sc->val[part] = best;
+    sc->idx[part] = idx;
+    __threadfence();
+    last = atomicAdd(&sc->ticket, 1u) == kArgmaxParts - 1;
+  }
+  __syncthreads();
+  if (!last) return;
+  __threadfence();
+  best = -INFINITY;
+  idx = 0x7fffffffffffffffLL;
+  if (threadIdx.x < kArgmaxParts) {
+    best = *((volatile float*)&sc->val[threadIdx.x]);
+    idx = *((volatile int64_t*)&sc->idx[threadIdx.x]);
+  }
+  argmax_block(best, idx, bv, bi);
+  if (threadIdx.x == 0) {
+    out[row] = idx;
+    sc->ticket = 0;
+  }
+}
+
+__global__ void __launch_bounds__(256) argmax_kernel(const float* __restrict__ logits, int64_t* __restrict__ out,
+                                                      int64_t V, int64_t ld, ArgmaxScratch* scratch) {
+  griddep_launch();
+  griddep_wait();
+  argmax_body(logits, out, V, ld, scratch);
 }
 
 // Temperature sampling by inverse CDF: p = softmax(logits / T); token = first i with cdf(i) > u.
@@ -116,8 +161,8 @@ __global__ void sample_kernel(const float* __restrict__ logits, const float* __r
                               const float* __restrict__ u, int64_t* __restrict__ out, int64_t V, int64_t ld) {
   __shared__ float red[32];
   __shared__ float chunk_sum[1024];
-  griddep_wait();
   griddep_launch();
+  griddep_wait();
   const float* row = logits + (int64_t)blockIdx.x * ld;
   const float T = temperature[blockIdx.x];
   const int tid = threadIdx.x, nt = blockDim.x;
@@ -162,8 +207,8 @@ __global__ void sample_kernel(const float* __restrict__ logits, const float* __r
 __global__ void block_copy_kernel(unsigned char* __restrict__ dst, const unsigned char* __restrict__ src,
                                   const int64_t* __restrict__ dst_idx, const int64_t* __restrict__ src_idx,
                                   int64_t block_bytes) {
-  griddep_wait();
   griddep_launch();
+  griddep_wait();
   const int64_t j = blockIdx.y;
   const uint4* s = reinterpret_cast<const uint4*>(src + src_idx[j] * block_bytes);
   uint4* d = reinterpret_cast<uint4*>(dst + dst_idx[j] * block_bytes);
@@ -207,10 +252,15 @@ CB_EXPORT int cb_swiglu(const void* gu, void* out, int64_t M, int64_t I, int64_t
                         (const bf16*)gu, (bf16*)out, I, ldg, ldo, total);
 }
 
-CB_EXPORT int cb_argmax(const void* logits, void* out, int64_t M, int64_t V, int64_t ld, void* stream) {
+// scratch: cb_argmax_scratch_bytes(M) bytes, zero-initialised once by the caller.
+CB_EXPORT int64_t cb_argmax_scratch_bytes(int64_t M) { return M * (int64_t)sizeof(ArgmaxScratch); }
+
+CB_EXPORT int cb_argmax(const void* logits, void* out, int64_t M, int64_t V, int64_t ld, void* scratch,
+                        void* stream) {
   if (M == 0) return 0;
-  return (int)cb_launch(argmax_kernel, dim3((unsigned)M), dim3(1024), 0, (cudaStream_t)stream,
-                        (const float*)logits, (int64_t*)out, V, ld);
+  if (!scratch) return CB_ERR_ARG;
+  return (int)cb_launch(argmax_kernel, dim3(kArgmaxParts, (unsigned)M), dim3(256), 0, (cudaStream_t)stream,
+                        (const float*)logits, (int64_t*)out, V, ld, (ArgmaxScratch*)scratch);
 }
 
 CB_EXPORT int cb_sample(const void* logits, const void* temperature, const void* u, void* out, int64_t M,

@@ -57,10 +57,10 @@ __global__ void __launch_bounds__(4 * DV) gdn_decode_kernel(const GdnDecodeArgs 
   // before waiting for the projection kernel.
   float* sp = a.state + (((int64_t)slot * a.nv + h) * DK + grp * RPT) * DV + j;
   float s[RPT];
+  griddep_launch();
 #pragma unroll
   for (int r = 0; r < RPT; ++r) s[r] = sp[(int64_t)r * DV];
   griddep_wait();
-  griddep_launch();
 
   const float nexpA = -__expf(a.A_log[h]), dtb = a.dt_bias[h];
   const float nw = a.norm_w[j];
@@ -157,8 +157,8 @@ __global__ void __launch_bounds__(4 * DV) gdn_commit_kernel(float* state, const 
                                                             int rec_w, int nv) {
   constexpr int G = 4, RPT = DK / G;
   const int h = blockIdx.x, m = blockIdx.y, j = threadIdx.x % DV, grp = threadIdx.x / DV;
-  griddep_wait();
   griddep_launch();
+  griddep_wait();
   const int slot = slots[m], n = steps[m];
   if (slot < 0 || n <= 0) return;
   float* sp = state + (((int64_t)slot * nv + h) * DK + grp * RPT) * DV + j;
@@ -189,8 +189,8 @@ struct GdnPrepArgs {
 
 template <int DK, int DV>
 __global__ void __launch_bounds__(256) gdn_prep_kernel(const GdnPrepArgs a) {
-  griddep_wait();
   griddep_launch();
+  griddep_wait();
   const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int kdim = a.nk * DK, conv_dim = 2 * kdim + a.nv * DV;
   const int ntask = 2 * a.nk + a.nv + 1;
@@ -250,8 +250,8 @@ __global__ void __launch_bounds__(256) gdn_prep_kernel(const GdnPrepArgs a) {
 
 // ring[(pos0 + t) & 15] = proj[t] for the last min(T, 16) tokens of the chunk
 __global__ void gdn_ring_update_kernel(const bf16* proj, int64_t ldp, bf16* ring, int T, int pos0, int conv_dim) {
-  griddep_wait();
   griddep_launch();
+  griddep_wait();
   const int first = max(0, T - kRing);
   const int t = first + blockIdx.x;
   if (t >= T) return;
@@ -287,8 +287,8 @@ __global__ void __launch_bounds__(256) gdn_chunk_prepare_kernel(const GdnChunkAr
   float* Wi = Tm + L * LDL;                         // [L][LDL]
   float* cs = Wi + L * LDL;                         // [L] cumulative log decay
   float* bs = cs + L;                               // [L] beta
-  griddep_wait();
   griddep_launch();
+  griddep_wait();
   const int n = blockIdx.x, h = blockIdx.y, kh = h / a.rep, tid = threadIdx.x;
   const int64_t t0 = (int64_t)n * L;
   const float* kp = a.kn + ((int64_t)kh * a.Tp + t0) * DK;
@@ -428,8 +428,8 @@ __global__ void __launch_bounds__(256) gdn_chunk_scan_kernel(const GdnScanArgs a
   float* A2 = A1 + L * LDK;                       // [L][LDK] qe
   float* Ic = A2 + L * LDK;                       // [L][LDL]
   float* U = Ic + L * LDL;                        // [L][LDS]
-  griddep_wait();
   griddep_launch();
+  griddep_wait();
   const int h = blockIdx.x, sl = blockIdx.y, tid = threadIdx.x;
   const int col0 = sl * DVS;
   float* sp = a.state + (int64_t)h * DK * DV + col0;
@@ -523,8 +523,8 @@ __global__ void __launch_bounds__(256) gdn_chunk_scan_kernel(const GdnScanArgs a
 template <int DV>
 __global__ void gdn_gated_norm_kernel(const float* o, const bf16* z, int64_t ldz, const float* w, bf16* out,
                                       int64_t ldo, int T, int nv, float eps) {
-  griddep_wait();
   griddep_launch();
+  griddep_wait();
   const int lane = threadIdx.x & 31;
   const int64_t task = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (task >= (int64_t)T * nv) return;

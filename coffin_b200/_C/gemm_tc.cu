@@ -81,8 +81,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = tmem_base_s;
-  griddep_wait();
   griddep_launch();
+  griddep_wait();
 
   const int total = a.m_tiles * a.n_tiles;
   if (warp == 0) {

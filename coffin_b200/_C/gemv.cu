@@ -32,11 +32,26 @@ struct GemvArgs {
   const float* gain;  // [K] fp32, already 1 + w
   bf16* res_out;      // may be null (no residual write-back); must not alias res_in/add
   float eps;
-  int nrg;            // row groups per CTA; KSPLIT = kWarps / nrg
+  int nrg;            // row groups per round; KSPLIT = kWarps / nrg
+  int rows_per_cta;   // logical rows owned by one CTA (a multiple of nrg * R)
+  int pf_rounds;      // rounds of weights kept in flight towards L2 ahead of the compute
 };
 
+// L2 prefetch of the weight rows [ra, rb) (contiguous bytes), one 128-byte line per thread-step.
+__device__ __forceinline__ void prefetch_rows(const bf16* W, int64_t K, int64_t ra, int64_t rb) {
+  if (rb <= ra) return;
+  const char* base = reinterpret_cast<const char*>(W + ra * K);
+  const int64_t bytes = (rb - ra) * K * (int64_t)sizeof(bf16);
+  for (int64_t off = (int64_t)threadIdx.x * 128; off < bytes; off += (int64_t)kThreads * 128)
+    asm volatile("prefetch.global.L2 [%0];" ::"l"(base + off));
+}
+
+// One CTA per SM owns a contiguous band of output rows and walks it in rounds of nrg * R rows.
+// The band's weights are pulled into L2 a few rounds ahead of the arithmetic, starting before the
+// wait on the previous kernel, so that under programmatic dependent launch the HBM stream never
+// stops at a kernel boundary; the compute phase then reads L2-resident lines.
 template <int M, int R, bool SWIGLU, bool NORM, bool OUT_F32>
-__global__ void __launch_bounds__(kThreads) gemv_kernel(const GemvArgs a) {
+__global__ void __launch_bounds__(kThreads, 2) gemv_kernel(const GemvArgs a) {
   constexpr int PHYS = R * (SWIGLU ? 2 : 1);
   extern __shared__ __align__(16) unsigned char smem_raw[];
   bf16* xs = reinterpret_cast<bf16*>(smem_raw);                       // [M][K]
@@ -47,30 +62,21 @@ __global__ void __launch_bounds__(kThreads) gemv_kernel(const GemvArgs a) {
   const int nrg = a.nrg, ksplit = kWarps / nrg;
   const int rg = warp % nrg, ks = warp / nrg;
   const int64_t K = a.K;
-  const int64_t row0 = ((int64_t)blockIdx.x * nrg + rg) * R;  // first logical row of this warp
-
-  // physical row pointers (clamped so out-of-range warps read valid memory and skip the store)
-  const bf16* wrow[PHYS];
-#pragma unroll
-  for (int p = 0; p < PHYS; ++p) {
-    int64_t r = row0 + (p % R);
-    if (r >= a.N) r = a.N - 1;
-    if (SWIGLU && p >= R) r += a.up_off;
-    wrow[p] = a.W + r * K;
-  }
+  const int round_rows = nrg * R;
+  const int64_t row_begin = (int64_t)blockIdx.x * a.rows_per_cta;
+  const int64_t row_end = min(a.N, row_begin + a.rows_per_cta);
+  const int nrounds = (int)((row_end - row_begin + round_rows - 1) / round_rows);
   const int64_t nchunk = K >> 3;                 // 16-byte chunks per row
   const int64_t cper = ((nchunk + ksplit - 1) / ksplit + 31) & ~(int64_t)31;
   const int64_t c0 = ks * cper, c1 = min(nchunk, c0 + cper);
 
-  // Weights do not depend on the previous kernel: pull the first lines of every row into L2/L1
-  // before waiting on the producer of x.
-#pragma unroll
-  for (int p = 0; p < PHYS; ++p) {
-    int64_t c = c0 + lane * 8;                   // one 128-byte line per lane
-    if (c < c1) asm volatile("prefetch.global.L2 [%0];" ::"l"(wrow[p] + c * 8));
+  griddep_launch();
+  if (a.pf_rounds > 0) {
+    const int64_t pe = min(row_end, row_begin + (int64_t)a.pf_rounds * round_rows);
+    prefetch_rows(a.W, K, row_begin, pe);
+    if (SWIGLU) prefetch_rows(a.W, K, a.up_off + row_begin, a.up_off + pe);
   }
   griddep_wait();
-  griddep_launch();
 
   // ---- prologue: activation rows into shared memory --------------------------------------
   if (NORM) {
@@ -107,82 +113,143 @@ __global__ void __launch_bounds__(kThreads) gemv_kernel(const GemvArgs a) {
   }
   __syncthreads();
 
-  // ---- main loop ---------------------------------------------------------------------------
-  float acc[PHYS][M];
-#pragma unroll
-  for (int p = 0; p < PHYS; ++p)
-#pragma unroll
-    for (int m = 0; m < M; ++m) acc[p][m] = 0.f;
-
-  for (int64_t c = c0 + lane; c < c1; c += 32 * kU) {
-    uint4 wv[kU][PHYS];
-#pragma unroll
-    for (int u = 0; u < kU; ++u) {
-      const int64_t cc = c + 32 * u;
-#pragma unroll
-      for (int p = 0; p < PHYS; ++p)
-        wv[u][p] = (cc < c1) ? ld_stream(wrow[p] + cc * 8) : make_uint4(0, 0, 0, 0);
+  for (int round = 0; round < nrounds; ++round) {
+    const int64_t round0 = row_begin + (int64_t)round * round_rows;
+    if (a.pf_rounds > 0) {  // keep the L2 stream pf_rounds ahead
+      const int64_t pa = round0 + (int64_t)a.pf_rounds * round_rows;
+      const int64_t pb = min(row_end, pa + round_rows);
+      prefetch_rows(a.W, K, pa, pb);
+      if (SWIGLU) prefetch_rows(a.W, K, a.up_off + pa, a.up_off + pb);
     }
+    const int64_t row0 = round0 + rg * R;  // first logical row of this warp in this round
+    // physical row pointers (clamped so out-of-range warps read valid memory and skip the store)
+    const bf16* wrow[PHYS];
 #pragma unroll
-    for (int u = 0; u < kU; ++u) {
-      const int64_t cc = c + 32 * u;
-      if (cc < c1) {
-        float wf[PHYS][8];
-#pragma unroll
-        for (int p = 0; p < PHYS; ++p) bf16x8_to_float(wv[u][p], wf[p]);
-#pragma unroll
-        for (int m = 0; m < M; ++m) {
-          float xf[8];
-          bf16x8_to_float(*reinterpret_cast<const uint4*>(xs + m * K + cc * 8), xf);
-#pragma unroll
-          for (int p = 0; p < PHYS; ++p)
-#pragma unroll
-            for (int i = 0; i < 8; ++i) acc[p][m] = fmaf(wf[p][i], xf[i], acc[p][m]);
-        }
-      }
+    for (int p = 0; p < PHYS; ++p) {
+      int64_t r = row0 + (p % R);
+      if (r >= a.N) r = a.N - 1;
+      if (SWIGLU && p >= R) r += a.up_off;
+      wrow[p] = a.W + r * K;
     }
-  }
-
-  // ---- reduce: lanes, then the K-split warps ---------------------------------------------
-#pragma unroll
-  for (int p = 0; p < PHYS; ++p)
-#pragma unroll
-    for (int m = 0; m < M; ++m) acc[p][m] = warp_sum(acc[p][m]);
-  if (lane == 0) {
+    float acc[PHYS][M];
 #pragma unroll
     for (int p = 0; p < PHYS; ++p)
 #pragma unroll
-      for (int m = 0; m < M; ++m) part[(warp * PHYS + p) * M + m] = acc[p][m];
-  }
-  __syncthreads();
-  // one thread per (row group, logical row, m)
-  for (int o = tid; o < nrg * R * M; o += kThreads) {
-    const int m = o % M, r = (o / M) % R, g = o / (M * R);
-    const int64_t row = ((int64_t)blockIdx.x * nrg + g) * R + r;
-    if (row >= a.N) continue;
-    float v = 0.f, v2 = 0.f;
-    for (int s = 0; s < ksplit; ++s) {
-      const int w = s * nrg + g;
-      v += part[(w * PHYS + r) * M + m];
-      if (SWIGLU) v2 += part[(w * PHYS + R + r) * M + m];
+      for (int m = 0; m < M; ++m) acc[p][m] = 0.f;
+
+    if (row0 < row_end) {
+      for (int64_t c = c0 + lane; c < c1; c += 32 * kU) {
+        uint4 wv[kU][PHYS];
+#pragma unroll
+        for (int u = 0; u < kU; ++u) {
+          const int64_t cc = c + 32 * u;
+#pragma unroll
+          for (int p = 0; p < PHYS; ++p)
+            wv[u][p] = (cc < c1) ? ld_stream(wrow[p] + cc * 8) : make_uint4(0, 0, 0, 0);
+        }
+#pragma unroll
+        for (int u = 0; u < kU; ++u) {
+          const int64_t cc = c + 32 * u;
+          if (cc < c1) {
+            float wf[PHYS][8];
+#pragma unroll
+            for (int p = 0; p < PHYS; ++p) bf16x8_to_float(wv[u][p], wf[p]);
+#pragma unroll
+            for (int m = 0; m < M; ++m) {
+              float xf[8];
+              bf16x8_to_float(*reinterpret_cast<const uint4*>(xs + m * K + cc * 8), xf);
+#pragma unroll
+              for (int p = 0; p < PHYS; ++p)
+#pragma unroll
+                for (int i = 0; i < 8; ++i) acc[p][m] = fmaf(wf[p][i], xf[i], acc[p][m]);
+            }
+          }
+        }
+      }
     }
-    if (SWIGLU) v = silu_f(v) * v2;
-    if (OUT_F32) reinterpret_cast<float*>(a.y)[m * a.ldy + row] = v;
-    else reinterpret_cast<bf16*>(a.y)[m * a.ldy + row] = __float2bfloat16(v);
+    // ---- reduce: lanes, then (if K is split) the warps ------------------------------------
+#pragma unroll
+    for (int p = 0; p < PHYS; ++p)
+#pragma unroll
+      for (int m = 0; m < M; ++m) acc[p][m] = warp_sum(acc[p][m]);
+    if (ksplit == 1) {
+      // every lane holds the sums; lane (r * M + m) stores logical row r of row m
+      if (lane < R * M) {
+        const int m = lane % M, r = lane / M;
+        const int64_t row = row0 + r;
+        float v = 0.f, v2 = 0.f;
+#pragma unroll
+        for (int p = 0; p < R; ++p)
+#pragma unroll
+          for (int mm = 0; mm < M; ++mm)
+            if (p == r && mm == m) { v = acc[p][mm]; if (SWIGLU) v2 = acc[R + p][mm]; }
+        if (row < row_end) {
+          if (SWIGLU) v = silu_f(v) * v2;
+          if (OUT_F32) reinterpret_cast<float*>(a.y)[m * a.ldy + row] = v;
+          else reinterpret_cast<bf16*>(a.y)[m * a.ldy + row] = __float2bfloat16(v);
+        }
+      }
+    } else {
+      __syncthreads();  // previous round's partials consumed
+      if (lane == 0) {
+#pragma unroll
+        for (int p = 0; p < PHYS; ++p)
+#pragma unroll
+          for (int m = 0; m < M; ++m) part[(warp * PHYS + p) * M + m] = acc[p][m];
+      }
+      __syncthreads();
+      for (int o = tid; o < nrg * R * M; o += kThreads) {
+        const int m = o % M, r = (o / M) % R, g = o / (M * R);
+        const int64_t row = round0 + g * R + r;
+        if (row >= row_end) continue;
+        float v = 0.f, v2 = 0.f;
+        for (int s = 0; s < ksplit; ++s) {
+          const int w = s * nrg + g;
+          v += part[(w * PHYS + r) * M + m];
+          if (SWIGLU) v2 += part[(w * PHYS + R + r) * M + m];
+        }
+        if (SWIGLU) v = silu_f(v) * v2;
+        if (OUT_F32) reinterpret_cast<float*>(a.y)[m * a.ldy + row] = v;
+        else reinterpret_cast<bf16*>(a.y)[m * a.ldy + row] = __float2bfloat16(v);
+      }
+    }
   }
 }
+
+int g_gemv_sms = 0;
+int g_gemv_ctas_per_sm = 2;   // CTAs per SM the band partition targets
+int g_gemv_prefetch = 1;      // L2 prefetch-ahead on/off
 
 template <int M, int R, bool SWIGLU, bool NORM, bool OUT_F32>
 int launch(const GemvArgs& a0, cudaStream_t st) {
   GemvArgs a = a0;
   constexpr int PHYS = R * (SWIGLU ? 2 : 1);
-  // largest row-group count that still gives >= 2 CTAs per SM; smaller N splits K instead
-  int nrg = kWarps;
-  while (nrg > 1 && (a.N + (int64_t)nrg * R - 1) / ((int64_t)nrg * R) < 296) nrg >>= 1;
-  a.nrg = nrg;
-  const int64_t grid = (a.N + (int64_t)nrg * R - 1) / ((int64_t)nrg * R);
+  if (!g_gemv_sms) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&g_gemv_sms, cudaDevAttrMultiProcessorCount, dev);
+    if (g_gemv_sms <= 0) g_gemv_sms = 148;
+  }
+  // One CTA per SM; pick the row-group count whose rounds cover the ideal band with least waste.
+  const int64_t slots = (int64_t)g_gemv_sms * g_gemv_ctas_per_sm;
+  const int64_t ideal = (a.N + slots - 1) / slots;
+  int best_nrg = 1;
+  int64_t best_rows = INT64_MAX;
+  for (int nrg = kWarps; nrg >= 1; nrg >>= 1) {
+    const int64_t rr = (int64_t)nrg * R;
+    const int64_t rows = (ideal + rr - 1) / rr * rr;
+    // splitting K below 64 chunks (2 per lane) per warp is not worth the shared-memory reduction
+    if (nrg < kWarps && (a.K >> 3) / (kWarps / nrg) < 64) continue;
+    if (rows < best_rows) { best_rows = rows; best_nrg = nrg; }
+  }
+  if (best_rows == INT64_MAX) { best_nrg = kWarps; best_rows = (ideal + kWarps * R - 1) / (kWarps * R) * (kWarps * R); }
+  a.nrg = best_nrg;
+  a.rows_per_cta = (int)best_rows;
+  const int64_t round_bytes = (int64_t)best_nrg * PHYS * a.K * 2;
+  a.pf_rounds = g_gemv_prefetch ? (int)max((int64_t)1, min((int64_t)64, (128 * 1024) / max((int64_t)1, round_bytes))) : 0;
+  const int64_t grid = (a.N + best_rows - 1) / best_rows;
   const size_t smem = (size_t)M * a.K * sizeof(bf16) + (size_t)kWarps * PHYS * M * sizeof(float);
-  if (smem > 200 * 1024) return CB_ERR_SHAPE;
+  if (smem > 100 * 1024) return CB_ERR_SHAPE;
   auto kern = gemv_kernel<M, R, SWIGLU, NORM, OUT_F32>;
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -198,11 +265,20 @@ int dispatch(const GemvArgs& a, bool swiglu, bool norm, bool f32, cudaStream_t s
     if (f32) return CB_ERR_ARG;
     return norm ? launch<M, 2, true, true, false>(a, st) : launch<M, 2, true, false, false>(a, st);
   }
+  // narrow outputs (N = hidden) balance better with two rows per warp
+  const bool narrow = a.N <= 8192;
   if (f32) return norm ? launch<M, 4, false, true, true>(a, st) : launch<M, 4, false, false, true>(a, st);
+  if (narrow) return norm ? launch<M, 2, false, true, false>(a, st) : launch<M, 2, false, false, false>(a, st);
   return norm ? launch<M, 4, false, true, false>(a, st) : launch<M, 4, false, false, false>(a, st);
 }
 
 }  // namespace
+
+CB_EXPORT int cb_set_gemv_opts(int64_t ctas_per_sm, int64_t prefetch) {
+  g_gemv_ctas_per_sm = ctas_per_sm < 1 ? 1 : (int)ctas_per_sm;
+  g_gemv_prefetch = prefetch ? 1 : 0;
+  return 0;
+}
 
 // mode bits: 1 = swiglu epilogue (W holds gate rows then up rows at `up_off`), 2 = fp32 output.
 // Norm prologue is enabled when res_in != null (then x is ignored).
@@ -215,7 +291,7 @@ CB_EXPORT int cb_gemv_bf16(const void* W, const void* x, void* y, int64_t M, int
   GemvArgs a;
   a.W = (const bf16*)W; a.x = (const bf16*)x; a.y = y; a.N = N; a.K = K; a.ldy = ldy;
   a.up_off = up_off; a.res_in = (const bf16*)res_in; a.add = (const bf16*)add;
-  a.gain = (const float*)gain; a.res_out = (bf16*)res_out; a.eps = eps; a.nrg = 1;
+  a.gain = (const float*)gain; a.res_out = (bf16*)res_out; a.eps = eps; a.nrg = 1; a.rows_per_cta = 0; a.pf_rounds = 1;
   const bool sw = mode & 1, f32 = mode & 2, norm = res_in != nullptr;
   cudaStream_t st = (cudaStream_t)stream;
   switch (M) {

@@ -1,0 +1,61 @@
+"""``EngineConfig``: the single source of truth for engine behaviour.
+
+CLI flags and server arguments are folded into this dataclass and everything below reads
+it (the reference's three-tier scheme: argparse -> ``EngineConfig`` -> environment switches,
+``engine/config.py:22-120``).  Defaults follow the reference where they are hardware
+neutral; ``max_num_seqs`` defaults to 8 (one full decode bucket) because a B200 has room.
+"""
+from __future__ import annotations
+
+import dataclasses
+import os
+
+
+@dataclasses.dataclass
+class EngineConfig:
+    max_seq: int = 262144              # context window (tokens) per sequence
+    quant: str = "none"                # none | int8 | w4a8 : weight storage of the text model
+    kv_dtype: str = "bf16"
+    prefix_cache: bool = True
+    block_size: int = 64
+    num_blocks: int = -1               # -1: size the pool from max_seq * max_num_seqs
+    snapshots: int = 8                 # delta-net state snapshots kept in the radix tree
+    snapshot_interval: int = 2048      # tokens between snapshots during a long prefill
+    spec_k: int = 0                    # speculative draft length (0 = off)
+    spec_batch: bool = False
+    spec_min_ctx: int = 0
+    chunk: int = 2048                  # largest prefill chunk handed to the model
+    prefill_quantum: int = 2048        # tokens of one sequence prefilled per engine step
+    max_num_seqs: int = 8              # concurrent sequences (= state slots = decode rows)
+    max_num_batched_tokens: int = 2048
+    max_seconds: float = 0.0           # default per-request deadline (0 = none)
+    graph: bool = True
+    vision: bool = True
+    image_max_pixels: int = 1024 * 1024
+    image_min_pixels: int = 32 * 32
+    max_images: int = 4
+    batch_window_ms: float = 0.0       # hold a lone decode this long for companions
+
+    @classmethod
+    def from_env(cls, **overrides) -> "EngineConfig":
+        """Apply ``COFFIN_*`` environment switches, then explicit overrides."""
+        cfg = cls()
+        env = os.environ
+        if "COFFIN_BATCH_WINDOW" in env:
+            cfg.batch_window_ms = float(env["COFFIN_BATCH_WINDOW"])
+        if "COFFIN_MAX_SEQ" in env:
+            cfg.max_seq = int(env["COFFIN_MAX_SEQ"])
+        if env.get("COFFIN_NO_GRAPH") == "1":
+            cfg.graph = False
+        for k, v in overrides.items():
+            if v is not None:
+                if not hasattr(cfg, k):
+                    raise TypeError(f"unknown engine option {k!r}")
+                setattr(cfg, k, v)
+        return cfg
+
+    def pool_blocks(self) -> int:
+        if self.num_blocks > 0:
+            return self.num_blocks
+        per_seq = (self.max_seq + self.block_size - 1) // self.block_size
+        return per_seq * self.max_num_seqs + 1

@@ -1,0 +1,214 @@
+"""``LLMEngine``: request lifecycle around the scheduler, the block manager and the runner.
+
+``add_request`` queues a sequence; every ``step()`` runs exactly one forward (a decode step of
+all running rows, or one prefill quantum) and returns the tokens it produced.  Capacity is
+claimed lazily: before a decode step every row reserves room for one more token, and when the
+pool (after evicting cached blocks) cannot provide it the latest-arrived sequence is preempted
+and recomputed later.  A run of steps that makes no progress raises instead of spinning.
+Reference: ``engine/llm_engine.py:113-657`` (``step`` l.206-240, ``_check_progress`` l.242,
+``_make_room_for_decode/_preempt`` l.388-473).
+"""
+from __future__ import annotations
+
+import dataclasses
+import time
+from typing import Any, Iterable, Iterator
+
+from .block_manager import BlockManager
+from .config import EngineConfig
+from .model_runner import ModelRunner
+from .scheduler import Scheduler
+from .sequence import SamplingParams, Sequence, SequenceStatus
+
+NO_PROGRESS_LIMIT = 200
+
+
+@dataclasses.dataclass
+class StepOutput:
+    seq: Sequence
+    token: int | None
+    finished: bool
+
+
+class LLMEngine:
+    def __init__(self, model, cfg: EngineConfig | None = None, bm: BlockManager | None = None) -> None:
+        self.cfg = cfg or EngineConfig()
+        self.model = model
+        slots = getattr(model, "num_slots", self.cfg.max_num_seqs)
+        if slots < self.cfg.max_num_seqs:
+            self.cfg = dataclasses.replace(self.cfg, max_num_seqs=slots)
+        self.bm = bm or BlockManager(model, getattr(model, "num_blocks", None), self.cfg.block_size,
+                                     self.cfg.snapshots, self.cfg.prefix_cache)
+        self.scheduler = Scheduler(self.cfg)
+        self.runner = ModelRunner(model, self.bm, self.cfg)
+        self.max_seq = min(self.cfg.max_seq, getattr(model, "max_seq", self.cfg.max_seq))
+        self._stall = 0
+        self.n_steps = 0
+        self.n_preempt = 0
+        self.n_finished = 0
+
+    @classmethod
+    def build(cls, model, cfg: EngineConfig | None = None) -> "LLMEngine":
+        eng = cls(model, cfg)
+        if eng.cfg.graph and hasattr(model, "capture"):
+            for m in (1,):
+                model.capture(m)
+        return eng
+
+    # ------------------------------------------------------------------ requests
+    def add_request(self, prompt: list[int], params: SamplingParams | None = None, mm: Any | None = None,
+                    request_id: str | None = None) -> Sequence:
+        params = params or SamplingParams()
+        if len(prompt) >= self.max_seq:
+            raise ValueError(f"prompt of {len(prompt)} tokens does not fit the {self.max_seq}-token window")
+        if params.deadline is None and self.cfg.max_seconds > 0:
+            params = dataclasses.replace(params, deadline=time.monotonic() + self.cfg.max_seconds)
+        seq = Sequence(prompt, params, mm, request_id)
+        self.scheduler.add(seq)
+        return seq
+
+    def abort(self, seq: Sequence, reason: str = "abort") -> None:
+        if not seq.finished:
+            self._release(seq, reason)
+
+    def has_work(self) -> bool:
+        return self.scheduler.has_work()
+
+    # ------------------------------------------------------------------ the step
+    def step(self) -> list[StepOutput]:
+        out: list[StepOutput] = []
+        self.n_steps += 1
+        for seq in self.scheduler.expire():
+            self._release(seq, "timeout")
+            out.append(StepOutput(seq, None, True))
+        batch = self.scheduler.schedule()
+        for seq in self.scheduler.admitted:
+            self.runner.begin_prefill(seq)
+        progressed = False
+        if batch.kind == "prefill":
+            progressed = self._run_prefill(batch, out)
+        elif batch.kind == "decode":
+            progressed = self._run_decode(batch.seqs, out)
+        self._check_progress(progressed or bool(out), batch.kind)
+        return out
+
+    def _check_progress(self, progressed: bool, kind: str) -> None:
+        if progressed or kind == "idle" and not self.scheduler.has_work():
+            self._stall = 0
+            return
+        self._stall += 1
+        if self._stall >= NO_PROGRESS_LIMIT:
+            raise RuntimeError(f"engine made no progress in {NO_PROGRESS_LIMIT} steps: "
+                               f"{self.scheduler.stats()} {self.bm.stats()}")
+
+    # ------------------------------------------------------------------ prefill
+    def _run_prefill(self, batch, out: list[StepOutput]) -> bool:
+        progressed = False
+        for seq, n in zip(batch.seqs, batch.chunks):
+            if seq.finished or seq.status is not SequenceStatus.PREFILLING:
+                continue
+            done = self.runner.prefill_chunk(seq, n)
+            if done == 0:
+                # no room even for one chunk: take blocks back from someone else
+                victim = self.scheduler.preempt_victim(exclude=seq)
+                if victim is not None:
+                    self._preempt(victim)
+                elif seq.blocks is not None and not seq.blocks.table and self.bm.pool.free_blocks == 0:
+                    pass
+                continue
+            progressed = True
+            if seq.remaining_prefill == 0:
+                self.runner.finish_prefill(seq)
+                self.scheduler.prefill_done(seq)
+                tok = self.runner.sample([seq], seq.pending_logits.reshape(1, -1))[0]
+                seq.pending_logits = None
+                if seq.first_token_time is None:
+                    seq.first_token_time = time.monotonic()
+                self._commit(seq, tok, out)
+        return progressed
+
+    # ------------------------------------------------------------------ decode
+    def _run_decode(self, seqs: list[Sequence], out: list[StepOutput]) -> bool:
+        ready = []
+        for seq in list(seqs):
+            if seq.finished or seq.status is not SequenceStatus.RUNNING:
+                continue
+            while not self.bm.ensure_blocks(seq.blocks, 1):
+                victim = self.scheduler.preempt_victim(exclude=None)
+                if victim is None:
+                    break
+                self._preempt(victim)
+                if victim is seq:
+                    break
+            if seq.status is SequenceStatus.RUNNING:
+                ready.append(seq)
+        ready = [s for s in ready if s.status is SequenceStatus.RUNNING]
+        if not ready:
+            return False
+        tokens = [s.output[-1] for s in ready]
+        logits = self.runner.decode(ready, tokens)
+        greedy = getattr(self.runner, "_last_next", None)
+        picked = self.runner.sample(ready, logits, greedy)
+        for seq, tok in zip(ready, picked):
+            self._commit(seq, tok, out)
+        return True
+
+    def _preempt(self, seq: Sequence) -> None:
+        self.n_preempt += 1
+        self.bm.release(seq.blocks)
+        self.scheduler.park(seq)
+
+    # ------------------------------------------------------------------ commit / release
+    def _commit(self, seq: Sequence, tok: int, out: list[StepOutput]) -> None:
+        p = seq.params
+        if not p.ignore_eos and tok in p.eos:
+            self._release(seq, "stop")
+            out.append(StepOutput(seq, None, True))
+            return
+        seq.output.append(tok)
+        reason = None
+        if len(seq.output) >= p.max_tokens:
+            reason = "length"
+        elif seq.num_tokens >= self.max_seq:
+            reason = "window"
+        if reason:
+            self._release(seq, reason)
+        out.append(StepOutput(seq, tok, reason is not None))
+
+    def _release(self, seq: Sequence, reason: str) -> None:
+        self.bm.release(seq.blocks)
+        seq.blocks = None
+        self.runner.forget(seq)
+        self.scheduler.finish(seq, reason)
+        self.n_finished += 1
+
+    # ------------------------------------------------------------------ conveniences
+    def generate(self, prompts: Iterable[list[int]], params: SamplingParams | None = None) -> list[Sequence]:
+        seqs = [self.add_request(p, params) for p in prompts]
+        while any(not s.finished for s in seqs):
+            self.step()
+        return seqs
+
+    def stream(self, seq: Sequence) -> Iterator[int]:
+        """Yield the tokens of ``seq`` as the engine produces them (drives ``step`` itself)."""
+        sent = 0
+        while True:
+            while sent < len(seq.output):
+                yield seq.output[sent]
+                sent += 1
+            if seq.finished:
+                return
+            self.step()
+
+    def reset(self) -> None:
+        """Drop every request and the prefix cache (the recovery path after a failed step)."""
+        for seq in list(self.scheduler.waiting) + self.scheduler.prefilling + self.scheduler.running:
+            self.bm.release(seq.blocks)
+            seq.blocks = None
+            self.scheduler.finish(seq, "reset")
+        self.bm.radix.clear()
+        self._stall = 0
+
+    def stats(self) -> dict:
+        return {"steps": self.n_steps, "finished": self.n_finished, "preempted": self.n_preempt,
+                "queue": self.scheduler.stats(), "blocks": self.bm.stats(), "runner": self.runner.stats()}

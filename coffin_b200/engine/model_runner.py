@@ -1,0 +1,168 @@
+"""``ModelRunner``: turns scheduler decisions into model calls.
+
+It owns nothing but staging: token tensors, block tables, sampling.  A model is anything with
+the slot/block-table interface of ``models.qwen35.model.Qwen35Model`` (``prefill``,
+``set_rows``/``decode``, ``zero_state``/``snapshot_state``/``restore_state``, ``copy_block``,
+``sample``); the CPU twin in ``oracle/engine_model.py`` and the fake models of the tests
+implement the same calls.  Reference: ``engine/model_runner.py:216-924`` (chunked prefill
+l.331-515, prefix insertion l.517-571, batched decode l.829-879, sampling l.900-924).
+"""
+from __future__ import annotations
+
+import random
+from typing import Any
+
+import torch
+
+from ..cache.paged_cache import OutOfBlocks
+from .block_manager import BlockManager
+from .config import EngineConfig
+from .sequence import Sequence
+
+BATCH_BUCKETS = (1, 2, 4, 8)
+
+
+class ModelRunner:
+    def __init__(self, model, bm: BlockManager, cfg: EngineConfig) -> None:
+        self.model = model
+        self.bm = bm
+        self.cfg = cfg
+        self.device = getattr(model, "device", torch.device("cpu"))
+        self.block_size = bm.pool.block_size
+        self._rng: dict[int, random.Random] = {}
+        self.n_prefill_tokens = 0
+        self.n_decode_steps = 0
+        self.n_cached_tokens = 0
+
+    # ------------------------------------------------------------------ admission
+    def begin_prefill(self, seq: Sequence) -> None:
+        """Give a freshly admitted sequence its block table; reuse a cached prefix if one
+        matches (KV blocks by reference, delta-net state restored from the snapshot)."""
+        seq.blocks = self.bm.new_table()
+        toks = seq.all_tokens
+        blocks, n, state = self.bm.match_prefix(toks, seq.mm)
+        if n:
+            seq.blocks.adopt(blocks, n)
+            self.model.restore_state(seq.slot, state)
+            seq.num_computed = n
+            seq.cached_tokens = n
+            self.n_cached_tokens += n
+        else:
+            self.model.zero_state(seq.slot)
+            seq.num_computed = 0
+            seq.cached_tokens = 0
+        seq.snap_marks = {}
+
+    # ------------------------------------------------------------------ prefill
+    def _chunk_end(self, seq: Sequence, n: int) -> int:
+        """End of the next chunk: at most ``n`` tokens, cut at the next snapshot boundary and at
+        the last block boundary before the sampling position (so that the longest reusable
+        prefix of this prompt gets a state snapshot)."""
+        start, total = seq.num_computed, seq.num_tokens
+        end = min(total, start + n, start + self.cfg.chunk)
+        if self.bm.prefix_cache:
+            iv = max(self.block_size, self.cfg.snapshot_interval // self.block_size * self.block_size)
+            nxt = (start // iv + 1) * iv
+            tail = (total - 1) // self.block_size * self.block_size
+            for cut in (nxt, tail):
+                if start < cut < end:
+                    end = cut
+        return end
+
+    def prefill_chunk(self, seq: Sequence, n: int) -> int:
+        """Run up to ``n`` more tokens of ``seq``.  Returns the tokens computed (0 = no room)."""
+        done = 0
+        while done < n and seq.remaining_prefill > 0:
+            start = seq.num_computed
+            end = self._chunk_end(seq, n - done)
+            T = end - start
+            if not self.bm.ensure_blocks(seq.blocks, T):
+                break
+            toks = seq.all_tokens[start:end]
+            last = end == seq.num_tokens
+            embeds = cos_sin = None
+            if seq.mm is not None:
+                embeds, cos_sin = self._mm_chunk(seq, toks, start, end)
+            logits = self.model.prefill(self._tokens(toks), start, seq.slot, self._table(seq),
+                                        embeds=embeds, cos_sin=cos_sin, want_logits=last)
+            seq.blocks.commit(T)
+            seq.num_computed = end
+            self.n_prefill_tokens += T
+            done += T
+            if last:
+                seq.pending_logits = logits
+            if self.bm.prefix_cache and end % self.block_size == 0 and not last:
+                iv = max(self.block_size, self.cfg.snapshot_interval // self.block_size * self.block_size)
+                tail = (seq.num_tokens - 1) // self.block_size * self.block_size
+                if end % iv == 0 or end == tail:
+                    seq.snap_marks[end] = self.model.snapshot_state(seq.slot)
+        return done
+
+    def finish_prefill(self, seq: Sequence) -> None:
+        """Publish the computed prompt blocks (and their snapshots) to the prefix cache."""
+        if self.bm.prefix_cache and seq.snap_marks:
+            self.bm.insert(seq.all_tokens[:seq.num_computed], seq.blocks.table, seq.snap_marks, seq.mm)
+        seq.snap_marks = {}
+
+    def _mm_chunk(self, seq: Sequence, toks, start: int, end: int):
+        mm = seq.mm
+        embeds = cos_sin = None
+        if getattr(mm, "embeds", None) is not None:
+            x = self.model.embed_tokens(self._tokens(toks))
+            embeds = mm.scatter_into(x, start, end)
+        if getattr(mm, "positions", None) is not None:
+            cos_sin = self.model.mrope_rows(mm.positions[:, start:end])
+            seq.rope_delta = int(mm.rope_delta)
+        return embeds, cos_sin
+
+    def _tokens(self, toks) -> torch.Tensor:
+        t = torch.tensor(toks, dtype=torch.int64)
+        if self.device.type == "cuda":
+            return t.pin_memory().to(self.device, non_blocking=True)
+        return t
+
+    def _table(self, seq: Sequence) -> torch.Tensor:
+        t = torch.tensor(seq.blocks.table, dtype=torch.int32)
+        return t.to(self.device) if self.device.type == "cuda" else t
+
+    # ------------------------------------------------------------------ decode
+    def decode(self, seqs: list[Sequence], tokens: list[int]) -> torch.Tensor:
+        """One decode step: ``tokens[i]`` is fed to ``seqs[i]`` at position ``num_computed``.
+        Blocks must already be reserved.  Returns logits ``[len(seqs), vocab]``."""
+        n = len(seqs)
+        M = self.model.bucket_for(n)
+        self.model.set_rows(M, tokens, [s.num_computed for s in seqs], [s.slot for s in seqs],
+                            [s.blocks.table for s in seqs], [s.rope_delta for s in seqs])
+        nxt, logits = self.model.decode(M, graph=self.cfg.graph)
+        for s in seqs:
+            s.blocks.commit(1)
+            s.num_computed += 1
+        self.n_decode_steps += 1
+        self._last_next = nxt
+        return logits[:n]
+
+    # ------------------------------------------------------------------ sampling
+    def sample(self, seqs: list[Sequence], logits: torch.Tensor, greedy_tokens: torch.Tensor | None = None) -> list[int]:
+        """Greedy rows take the argmax (already computed on the device by the decode step when
+        ``greedy_tokens`` is given); temperature rows are drawn by inverse CDF from a uniform
+        produced by the sequence's own seeded generator, so every tensor-parallel rank picks the
+        same token without a broadcast."""
+        temps = [s.params.temperature for s in seqs]
+        if all(t <= 0 for t in temps):
+            if greedy_tokens is not None:
+                return [int(v) for v in greedy_tokens[:len(seqs)].tolist()]
+            return [int(v) for v in self.model.sample(logits, None, None).tolist()]
+        us = []
+        for s in seqs:
+            rng = self._rng.get(s.seq_id)
+            if rng is None:
+                rng = self._rng[s.seq_id] = random.Random(s.params.seed if s.params.seed is not None else s.seq_id)
+            us.append(rng.random())
+        return [int(v) for v in self.model.sample(logits, temps, us).tolist()]
+
+    def forget(self, seq: Sequence) -> None:
+        self._rng.pop(seq.seq_id, None)
+
+    def stats(self) -> dict:
+        return {"prefill_tokens": self.n_prefill_tokens, "decode_steps": self.n_decode_steps,
+                "cached_tokens": self.n_cached_tokens}

@@ -429,6 +429,24 @@ class Qwen35Model:
         b["positions"].add_(live.to(torch.int32))
         b["rope_pos"].add_(live.to(torch.int32))
 
+    # ------------------------------------------------------------------ runner hooks
+    def embed_tokens(self, tokens: torch.Tensor) -> torch.Tensor:
+        return K.embed_gather(self.embed, tokens)
+
+    def mrope_rows(self, positions3: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+        """Per-token rotary rows ``[T, rot]`` for 3-axis (t, h, w) positions ``[3, T]``."""
+        c = self.cfg
+        cos, sin = O.mrope_cos_sin(positions3.cpu(), c.rotary_dim, c.rope_theta, c.mrope_section)
+        return cos.to(self.device), sin.to(self.device)
+
+    def sample(self, logits: torch.Tensor, temps, us) -> torch.Tensor:
+        """Greedy (``temps`` None) or per-row temperature sampling with host uniforms ``us``."""
+        if temps is None:
+            return K.argmax(logits.contiguous())
+        t = torch.tensor(temps, dtype=torch.float32, device=self.device)
+        u = torch.tensor(us, dtype=torch.float32, device=self.device)
+        return K.sample(logits.contiguous(), t, u)
+
     @staticmethod
     def bucket_for(n: int) -> int:
         for m in BUCKETS:

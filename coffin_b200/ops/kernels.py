@@ -83,12 +83,29 @@ def swiglu(gu: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
     return out
 
 
+_argmax_scratch: dict[int, torch.Tensor] = {}
+
+
+def _argmax_ws(device: torch.device, M: int) -> torch.Tensor:
+    """Zero-initialised per-device scratch of the two-stage argmax (partials + arrival tickets)."""
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    t = _argmax_scratch.get(idx)
+    import ctypes
+    fn = _lib.lib().cb_argmax_scratch_bytes
+    fn.restype = ctypes.c_int64
+    need = int(fn(ctypes.c_int64(max(M, 64))))
+    if t is None or t.numel() < need:
+        t = torch.zeros(need, dtype=torch.uint8, device=device)
+        _argmax_scratch[idx] = t
+    return t
+
+
 def argmax(logits: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
     M, V = logits.shape
-    assert logits.dtype == torch.float32
+    assert logits.dtype == torch.float32 and M <= 64
     if out is None:
         out = torch.empty(M, dtype=torch.int64, device=logits.device)
-    call("argmax", logits, out, M, V, logits.stride(0))
+    call("argmax", logits, out, M, V, logits.stride(0), _argmax_ws(logits.device, M))
     _count()
     return out
 

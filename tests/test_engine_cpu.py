@@ -1,0 +1,124 @@
+"""The engine (scheduler + block manager + radix cache + runner) driven end to end on the CPU
+twin of the device model (tiny hybrid config, real logits): batched continuous decoding equals
+solo greedy decoding, chunked prefill equals one-shot, prefix hits reuse blocks and snapshots,
+preemption recomputes to the same tokens, nothing leaks."""
+import pytest
+import torch
+
+from coffin_b200.config import preset
+from coffin_b200.engine.config import EngineConfig
+from coffin_b200.engine.llm_engine import LLMEngine, NO_PROGRESS_LIMIT
+from coffin_b200.engine.sequence import SamplingParams
+from coffin_b200.oracle.engine_model import OracleEngineModel
+from coffin_b200.oracle.model import OracleModel
+from coffin_b200.weights.init import random_state_dict
+
+CFG = preset("tiny")
+SD = random_state_dict(CFG, 0)
+
+
+def prompt(n, seed):
+    g = torch.Generator().manual_seed(seed)
+    return torch.randint(0, CFG.vocab_size, (n,), generator=g).tolist()
+
+
+def solo(p, n):
+    m = OracleModel(CFG, SD)
+    with torch.no_grad():
+        return m.generate(p, n)[0]
+
+
+def engine(**kw):
+    model_kw = {k: kw.pop(k) for k in ("num_slots", "num_blocks", "max_seq") if k in kw}
+    model = OracleEngineModel(CFG, SD, **{"max_seq": 512, "num_slots": 4, **model_kw})
+    cfg = EngineConfig(max_seq=512, max_num_seqs=model.num_slots, graph=False, **kw)
+    return LLMEngine(model, cfg)
+
+
+def test_batched_decode_equals_solo_and_no_leak():
+    eng = engine(chunk=48, prefill_quantum=48, max_num_batched_tokens=96)
+    prompts = [prompt(n, 100 + n) for n in (70, 33, 130)]
+    seqs = eng.generate(prompts, SamplingParams(max_tokens=6))
+    for p, s in zip(prompts, seqs):
+        assert s.output == solo(p, 6)
+        assert s.finish_reason == "length"
+    eng.bm.radix.clear()
+    eng.bm.pool.check()
+    assert eng.bm.pool.used_blocks == 0
+    assert len(eng.scheduler.free_slots) == 4
+
+
+def test_prefix_hit_reuses_blocks_and_state():
+    eng = engine(snapshot_interval=64)
+    shared = prompt(128, 7)
+    a = shared + prompt(20, 8)
+    b = shared + prompt(31, 9)
+    sa = eng.generate([a], SamplingParams(max_tokens=4))[0]
+    before = eng.model.n_prefill_calls
+    sb = eng.generate([b], SamplingParams(max_tokens=4))[0]
+    assert sa.cached_tokens == 0 and sb.cached_tokens == 128
+    assert sa.output == solo(a, 4) and sb.output == solo(b, 4)
+    assert eng.bm.radix.stats()["tokens_hit"] == 128
+    # the same prompt again hits its own tail boundary
+    sc = eng.generate([a], SamplingParams(max_tokens=4))[0]
+    assert sc.cached_tokens == 128 and sc.output == sa.output
+    assert eng.model.n_prefill_calls > before
+
+
+def test_preemption_recomputes_to_same_tokens():
+    # 8 allocatable blocks: three 126-token prompts hold 2 blocks each and each grows into a 3rd
+    eng = engine(num_blocks=9, prefix_cache=False, num_slots=3)
+    prompts = [prompt(126, 40 + i) for i in range(3)]
+    seqs = eng.generate(prompts, SamplingParams(max_tokens=8))
+    assert eng.n_preempt >= 1
+    for p, s in zip(prompts, seqs):
+        assert s.output == solo(p, 8)
+    eng.bm.pool.check()
+    assert eng.bm.pool.used_blocks == 0
+
+
+def test_unsatisfiable_pool_raises_instead_of_spinning():
+    eng = engine(num_blocks=3, prefix_cache=False, num_slots=2)
+    eng.add_request(prompt(200, 1), SamplingParams(max_tokens=2))
+    with pytest.raises(RuntimeError, match="no progress"):
+        for _ in range(NO_PROGRESS_LIMIT + 5):
+            eng.step()
+
+
+def test_eos_deadline_and_streaming():
+    eng = engine()
+    p = prompt(40, 3)
+    ref = solo(p, 12)
+    cut = next((i for i in range(1, 12) if ref[i] not in ref[:i]), None)   # first token not seen before
+    if cut is not None:
+        s = eng.add_request(p, SamplingParams(max_tokens=12, eos=(ref[cut],)))
+        assert list(eng.stream(s)) == ref[:cut] and s.finish_reason == "stop"
+    t = eng.add_request(p, SamplingParams(max_tokens=50, deadline=0.0))
+    while not t.finished:
+        eng.step()
+    assert t.finish_reason == "timeout"
+    u = eng.add_request(p, SamplingParams(max_tokens=3, temperature=0.8, seed=5))
+    v = eng.add_request(p, SamplingParams(max_tokens=3, temperature=0.8, seed=5))
+    while not (u.finished and v.finished):
+        eng.step()
+    assert u.output == v.output
+
+
+def test_no_head_of_line_blocking_and_reset():
+    eng = engine(chunk=32, prefill_quantum=32, max_num_batched_tokens=32)
+    long = eng.add_request(prompt(300, 11), SamplingParams(max_tokens=2))
+    short = eng.add_request(prompt(20, 12), SamplingParams(max_tokens=2))
+    first_done = None
+    for _ in range(400):
+        eng.step()
+        if first_done is None and (long.finished or short.finished):
+            first_done = "short" if short.finished else "long"
+        if long.finished and short.finished:
+            break
+    assert long.finished and short.finished
+    w = eng.add_request(prompt(50, 13), SamplingParams(max_tokens=100))
+    eng.step()
+    eng.reset()
+    assert w.finished and w.finish_reason == "reset" and not eng.has_work()
+    eng.bm.pool.check()
+    assert eng.bm.pool.used_blocks == 0
