@@ -101,6 +101,7 @@ def main() -> None:
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--no-pdl", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-stream-gemv", action="store_true", help="tuning: register-staged GEMV for batch 1")
     ap.add_argument("--gemv-ctas", type=int, default=0, help="tuning: GEMV CTAs per SM (0 = library default)")
     ap.add_argument("--gemv-prefetch", type=int, default=-1, help="tuning: GEMV L2 prefetch-ahead (-1 = default)")
     args = ap.parse_args()
@@ -123,6 +124,8 @@ def main() -> None:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     W = max(3, args.warmup)
+    if args.no_stream_gemv:
+        K.STREAM_GEMV = False
     if args.gemv_ctas or args.gemv_prefetch >= 0:
         from coffin_b200.ops import _lib
         _lib.call_nostream("set_gemv_opts", args.gemv_ctas or 2, 1 if args.gemv_prefetch != 0 else 0)

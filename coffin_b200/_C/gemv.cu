@@ -33,7 +33,7 @@ struct GemvArgs {
   bf16* res_out;      // may be null (no residual write-back); must not alias res_in/add
   float eps;
   int nrg;            // row groups per round; KSPLIT = kWarps / nrg
-  int rows_per_cta;   // logical rows owned by one CTA (a multiple of nrg * R)
+  int rounds;         // rounds of the grid-wide sweep (nrg * R rows per CTA per round)
   int pf_rounds;      // rounds of weights kept in flight towards L2 ahead of the compute
 };
 
@@ -63,18 +63,21 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_kernel(const GemvArgs a) {
   const int rg = warp % nrg, ks = warp / nrg;
   const int64_t K = a.K;
   const int round_rows = nrg * R;
-  const int64_t row_begin = (int64_t)blockIdx.x * a.rows_per_cta;
-  const int64_t row_end = min(a.N, row_begin + a.rows_per_cta);
-  const int nrounds = (int)((row_end - row_begin + round_rows - 1) / round_rows);
+  // Sweep order: in round r the grid covers one contiguous window of rows (CTA c takes the
+  // round_rows rows at (r * grid + c) * round_rows), so concurrently streamed rows are neighbours
+  // in memory and DRAM pages stay open.
+  const int nrounds = a.rounds;
+  const int64_t row_end = a.N;
+  auto round_start = [&](int r) { return ((int64_t)r * gridDim.x + blockIdx.x) * round_rows; };
   const int64_t nchunk = K >> 3;                 // 16-byte chunks per row
   const int64_t cper = ((nchunk + ksplit - 1) / ksplit + 31) & ~(int64_t)31;
   const int64_t c0 = ks * cper, c1 = min(nchunk, c0 + cper);
 
   griddep_launch();
-  if (a.pf_rounds > 0) {
-    const int64_t pe = min(row_end, row_begin + (int64_t)a.pf_rounds * round_rows);
-    prefetch_rows(a.W, K, row_begin, pe);
-    if (SWIGLU) prefetch_rows(a.W, K, a.up_off + row_begin, a.up_off + pe);
+  for (int r = 0; r < a.pf_rounds && r < nrounds; ++r) {
+    const int64_t pa = round_start(r), pb = min(row_end, pa + round_rows);
+    prefetch_rows(a.W, K, pa, pb);
+    if (SWIGLU) prefetch_rows(a.W, K, a.up_off + pa, a.up_off + pb);
   }
   griddep_wait();
 
@@ -114,9 +117,9 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_kernel(const GemvArgs a) {
   __syncthreads();
 
   for (int round = 0; round < nrounds; ++round) {
-    const int64_t round0 = row_begin + (int64_t)round * round_rows;
-    if (a.pf_rounds > 0) {  // keep the L2 stream pf_rounds ahead
-      const int64_t pa = round0 + (int64_t)a.pf_rounds * round_rows;
+    const int64_t round0 = round_start(round);
+    if (a.pf_rounds > 0 && round + a.pf_rounds < nrounds) {  // keep the L2 stream pf_rounds ahead
+      const int64_t pa = round_start(round + a.pf_rounds);
       const int64_t pb = min(row_end, pa + round_rows);
       prefetch_rows(a.W, K, pa, pb);
       if (SWIGLU) prefetch_rows(a.W, K, a.up_off + pa, a.up_off + pb);
@@ -230,24 +233,18 @@ int launch(const GemvArgs& a0, cudaStream_t st) {
     cudaDeviceGetAttribute(&g_gemv_sms, cudaDevAttrMultiProcessorCount, dev);
     if (g_gemv_sms <= 0) g_gemv_sms = 148;
   }
-  // One CTA per SM; pick the row-group count whose rounds cover the ideal band with least waste.
+  // Row groups per round: all eight warps on distinct rows when there are enough rows to fill the
+  // grid that way, else split K across warps so that narrow outputs still occupy every SM.
   const int64_t slots = (int64_t)g_gemv_sms * g_gemv_ctas_per_sm;
-  const int64_t ideal = (a.N + slots - 1) / slots;
-  int best_nrg = 1;
-  int64_t best_rows = INT64_MAX;
-  for (int nrg = kWarps; nrg >= 1; nrg >>= 1) {
-    const int64_t rr = (int64_t)nrg * R;
-    const int64_t rows = (ideal + rr - 1) / rr * rr;
-    // splitting K below 64 chunks (2 per lane) per warp is not worth the shared-memory reduction
-    if (nrg < kWarps && (a.K >> 3) / (kWarps / nrg) < 64) continue;
-    if (rows < best_rows) { best_rows = rows; best_nrg = nrg; }
-  }
-  if (best_rows == INT64_MAX) { best_nrg = kWarps; best_rows = (ideal + kWarps * R - 1) / (kWarps * R) * (kWarps * R); }
-  a.nrg = best_nrg;
-  a.rows_per_cta = (int)best_rows;
-  const int64_t round_bytes = (int64_t)best_nrg * PHYS * a.K * 2;
-  a.pf_rounds = g_gemv_prefetch ? (int)max((int64_t)1, min((int64_t)64, (128 * 1024) / max((int64_t)1, round_bytes))) : 0;
-  const int64_t grid = (a.N + best_rows - 1) / best_rows;
+  int nrg = kWarps;
+  while (nrg > 1 && (a.N + (int64_t)nrg * R - 1) / ((int64_t)nrg * R) < slots && (a.K >> 3) / (kWarps / (nrg / 2)) >= 64)
+    nrg >>= 1;
+  a.nrg = nrg;
+  const int64_t rr = (int64_t)nrg * R;
+  const int64_t grid = min(slots, (a.N + rr - 1) / rr);
+  a.rounds = (int)((a.N + grid * rr - 1) / (grid * rr));
+  const int64_t round_bytes = rr * (SWIGLU ? 2 : 1) * a.K * 2;
+  a.pf_rounds = g_gemv_prefetch ? (int)max((int64_t)1, min((int64_t)8, (64 * 1024) / max((int64_t)1, round_bytes))) : 0;
   const size_t smem = (size_t)M * a.K * sizeof(bf16) + (size_t)kWarps * PHYS * M * sizeof(float);
   if (smem > 100 * 1024) return CB_ERR_SHAPE;
   auto kern = gemv_kernel<M, R, SWIGLU, NORM, OUT_F32>;
@@ -291,7 +288,7 @@ CB_EXPORT int cb_gemv_bf16(const void* W, const void* x, void* y, int64_t M, int
   GemvArgs a;
   a.W = (const bf16*)W; a.x = (const bf16*)x; a.y = y; a.N = N; a.K = K; a.ldy = ldy;
   a.up_off = up_off; a.res_in = (const bf16*)res_in; a.add = (const bf16*)add;
-  a.gain = (const float*)gain; a.res_out = (bf16*)res_out; a.eps = eps; a.nrg = 1; a.rows_per_cta = 0; a.pf_rounds = 1;
+  a.gain = (const float*)gain; a.res_out = (bf16*)res_out; a.eps = eps; a.nrg = 1; a.rounds = 0; a.pf_rounds = 1;
   const bool sw = mode & 1, f32 = mode & 2, norm = res_in != nullptr;
   cudaStream_t st = (cudaStream_t)stream;
   switch (M) {

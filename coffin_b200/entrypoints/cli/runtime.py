@@ -1,0 +1,156 @@
+"""Engine CLI: ``--serve`` starts the resident process; the other commands are socket clients.
+
+    python -m coffin_b200.entrypoints.cli.runtime --serve --model /path/to/ckpt
+    python -m coffin_b200.entrypoints.cli.runtime --serve --preset qwen35-4b        # random weights
+    python -m coffin_b200.entrypoints.cli.runtime chat "hello"
+
+Commands: ``ping reload reset stop generate chat bench profile ops spec`` (reference:
+``entrypoints/cli/runtime.py:30-208``).  Multi-GPU: launch one process per GPU with
+``RANK/WORLD_SIZE/MASTER_ADDR/MASTER_PORT`` set and ``COFFIN_PARALLEL=tp|pp|ep``; rank 0 owns the
+socket.
+"""
+from __future__ import annotations
+
+import argparse
+import faulthandler
+import json
+import os
+import sys
+
+COMMANDS = ("ping", "reload", "reset", "stop", "generate", "chat", "bench", "profile", "ops", "spec", "tokenize")
+
+
+def parser() -> argparse.ArgumentParser:
+    ap = argparse.ArgumentParser(prog="coffin-b200", description=__doc__.split("\n")[0])
+    ap.add_argument("--serve", action="store_true", help="run the engine process")
+    ap.add_argument("cmd", nargs="?", choices=COMMANDS, default="ping")
+    ap.add_argument("text", nargs="?", default="", help="prompt for generate/chat/bench/profile/ops/spec")
+    ap.add_argument("--sock", default=os.environ.get("ENGINE_SOCK", "/tmp/coffin_b200.sock"))
+    ap.add_argument("--model", default=os.environ.get("ENGINE_MODEL", ""), help="checkpoint directory")
+    ap.add_argument("--preset", default="", help="serve a random-init model of a named shape")
+    ap.add_argument("--device", default="cuda", choices=["cuda", "cpu"])
+    ap.add_argument("--max-seq", type=int, default=None)
+    ap.add_argument("--quant", default=None, choices=["none", "int8", "w4a8"])
+    ap.add_argument("--no-prefix-cache", action="store_true")
+    ap.add_argument("--num-blocks", type=int, default=None)
+    ap.add_argument("--snapshots", type=int, default=None)
+    ap.add_argument("--snapshot-interval", type=int, default=None)
+    ap.add_argument("--spec-k", type=int, default=None)
+    ap.add_argument("--spec-batch", action="store_true")
+    ap.add_argument("--chunk", type=int, default=None)
+    ap.add_argument("--prefill-quantum", type=int, default=None)
+    ap.add_argument("--max-num-seqs", type=int, default=None)
+    ap.add_argument("--max-num-batched-tokens", type=int, default=None)
+    ap.add_argument("--max-seconds", type=float, default=None)
+    ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--no-vision", action="store_true")
+    ap.add_argument("-n", type=int, default=64, help="tokens for generate/chat/bench")
+    ap.add_argument("--temperature", type=float, default=0.0)
+    ap.add_argument("--system", default="")
+    ap.add_argument("--tools", default="", help="JSON file with an OpenAI tools array")
+    ap.add_argument("--no-thinking", action="store_true")
+    return ap
+
+
+def engine_config(args):
+    from ...engine.config import EngineConfig
+    return EngineConfig.from_env(
+        max_seq=args.max_seq, quant=args.quant, prefix_cache=False if args.no_prefix_cache else None,
+        num_blocks=args.num_blocks, snapshots=args.snapshots, snapshot_interval=args.snapshot_interval,
+        spec_k=args.spec_k, spec_batch=True if args.spec_batch else None, chunk=args.chunk,
+        prefill_quantum=args.prefill_quantum, max_num_seqs=args.max_num_seqs,
+        max_num_batched_tokens=args.max_num_batched_tokens, max_seconds=args.max_seconds,
+        graph=False if args.no_graph else None, vision=False if args.no_vision else None)
+
+
+def build_server(args):
+    """Load (or draw) the weights once and return a ``Server`` whose ``reload`` rebuilds the model
+    from the resident state dict."""
+    import torch
+    from ...config import ModelConfig, preset
+    from ...serving.runtime import Server
+    cfg_e = engine_config(args)
+    if cfg_e.max_seq > 32768 and args.max_seq is None:
+        cfg_e.max_seq = 32768
+    world, rank = int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("RANK", "0"))
+    mode = os.environ.get("COFFIN_PARALLEL", "tp")
+    if args.model:
+        from ...weights.loader import load_checkpoint
+        mcfg = ModelConfig.from_dir(args.model)
+        sd = load_checkpoint(args.model)
+    else:
+        from ...weights.init import random_state_dict
+        mcfg = preset(args.preset or "tiny")
+        dev = args.device if args.device == "cpu" else f"cuda:{int(os.environ.get('LOCAL_RANK', '0'))}"
+        sd = random_state_dict(mcfg, 0, dtype=torch.float32 if args.device == "cpu" else torch.bfloat16, device=dev)
+
+    def builder():
+        if args.device == "cpu":
+            from ...oracle.engine_model import OracleEngineModel
+            return OracleEngineModel(mcfg, sd, max_seq=min(cfg_e.max_seq, 4096), num_slots=cfg_e.max_num_seqs,
+                                     max_chunk=cfg_e.chunk)
+        from ...models import build_model
+        kw = dict(device=f"cuda:{int(os.environ.get('LOCAL_RANK', '0'))}", max_seq=cfg_e.max_seq,
+                  num_slots=cfg_e.max_num_seqs, max_chunk=cfg_e.chunk,
+                  num_blocks=cfg_e.num_blocks if cfg_e.num_blocks > 0 else None)
+        if world > 1 and mode == "tp":
+            kw.update(tp_world=world, tp_rank=rank)
+        return build_model(mcfg, sd, **kw)
+
+    return Server(builder(), cfg_e, model_path=args.model, model_name=args.preset or "", builder=builder)
+
+
+def main(argv=None) -> int:
+    args = parser().parse_args(argv)
+    dump = float(os.environ.get("COFFIN_FAULT_DUMP", "0") or 0)
+    if dump > 0:
+        faulthandler.dump_traceback_later(dump, repeat=True)
+    if args.serve:
+        from ...serving.transport import serve
+        world, rank = int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("RANK", "0"))
+        fanout = None
+        if world > 1:
+            from ...parallel.control import init_control_plane, make_fanout, worker_loop
+            init_control_plane()
+            srv = build_server(args)
+            if rank != 0:
+                worker_loop(srv)
+                return 0
+            fanout = make_fanout()
+        else:
+            srv = build_server(args)
+        serve(srv, args.sock, fanout=fanout)
+        return 0
+    from ...serving.transport import call
+    req: dict = {"op": args.cmd}
+    if args.cmd in ("generate", "bench", "profile", "ops", "spec", "tokenize"):
+        req.update({"prompt": args.text or "Hello", "n": args.n, "max_new": args.n, "temperature": args.temperature})
+        if args.spec_k:
+            req["spec_k"] = args.spec_k
+    elif args.cmd == "chat":
+        msgs = ([{"role": "system", "content": args.system}] if args.system else []) + \
+               [{"role": "user", "content": args.text or "Hello"}]
+        req.update({"messages": msgs, "max_new": args.n, "temperature": args.temperature,
+                    "enable_thinking": not args.no_thinking})
+        if args.tools:
+            req["tools"] = json.load(open(args.tools))
+    try:
+        rep = call(args.sock, req)
+    except OSError as exc:
+        print(f"engine not reachable on {args.sock}: {exc}", file=sys.stderr)
+        return 2
+    if args.cmd in ("generate", "chat") and rep.get("ok"):
+        if rep.get("thinking"):
+            print(f"[thinking] {rep['thinking']}")
+        print(rep.get("text", ""))
+        for c in rep.get("tool_calls") or []:
+            print(f"[tool_call] {json.dumps(c, ensure_ascii=False)}")
+        print(f"[{rep.get('n_prompt')} prompt, {rep.get('n_new')} new, cached {rep.get('cached_tokens')}, "
+              f"prefill {rep.get('prefill_ms')} ms, {rep.get('decode_tok_s')} tok/s]")
+    else:
+        print(json.dumps(rep, indent=1, ensure_ascii=False))
+    return 0 if rep.get("ok", True) else 1
+
+
+if __name__ == "__main__":
+    sys.exit(main())

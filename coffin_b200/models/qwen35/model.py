@@ -429,6 +429,98 @@ class Qwen35Model:
         b["positions"].add_(live.to(torch.int32))
         b["rope_pos"].add_(live.to(torch.int32))
 
+    # ------------------------------------------------------------------ speculative verification
+    def _verify_buffers(self, C: int) -> dict:
+        key = ("verify", C)
+        b = self._rows.get(key)
+        if b is None:
+            c, dev, bf = self.cfg, self.device, torch.bfloat16
+            H = c.hidden_size
+            b = {
+                "tokens": torch.zeros(C, dtype=torch.int64, device=dev),
+                "res": [torch.zeros(C, H, dtype=bf, device=dev) for _ in range(2)],
+                "h": torch.zeros(C, H, dtype=bf, device=dev), "h2": torch.zeros(C, H, dtype=bf, device=dev),
+                "proj": torch.zeros(C, self.in_width, dtype=bf, device=dev),
+                "act_lin": torch.zeros(C, c.lin_vdim, dtype=bf, device=dev),
+                "act_full": torch.zeros(C, c.num_attention_heads * c.head_dim, dtype=bf, device=dev),
+                "q": torch.zeros(C, c.num_attention_heads, c.head_dim, dtype=bf, device=dev),
+                "inter": torch.zeros(C, max(1, c.intermediate_size), dtype=bf, device=dev),
+                "logits": torch.zeros(C, c.vocab_size, dtype=torch.float32, device=dev),
+                "slot": torch.zeros(1, dtype=torch.int32, device=dev),
+                "pos": torch.zeros(1, dtype=torch.int32, device=dev),
+                "kv_slots": torch.zeros(C, dtype=torch.int32, device=dev),
+                "ridx": torch.zeros(C, dtype=torch.int32, device=dev),
+                "record": torch.zeros(len(self.lin_ids), 1, C, c.linear_num_value_heads,
+                                      c.linear_key_head_dim + c.linear_value_head_dim + 1,
+                                      dtype=torch.float32, device=dev),
+                "steps": torch.zeros(1, dtype=torch.int32, device=dev),
+            }
+            self._rows[key] = b
+        return b
+
+    @torch.no_grad()
+    def verify(self, tokens: list[int], pos0: int, slot: int, block_table: torch.Tensor, rope_delta: int = 0) -> torch.Tensor:
+        """Run ``C`` consecutive tokens (the last sampled token followed by drafts) of one sequence
+        in one pass and return their logits ``[C, vocab]``.  KV rows of all ``C`` positions are
+        written (rejected ones are overwritten later); the delta-net state is left untouched and
+        the per-token rank-one updates are recorded, so that ``commit`` can apply the accepted
+        prefix.  ``C`` must be 2, 4 or 8 (``models/qwen35/model.py:1761-1911`` in the reference)."""
+        c = self.cfg
+        C = len(tokens)
+        assert C in (2, 4, 8), "verify width must be 2, 4 or 8"
+        b = self._verify_buffers(C)
+        b["tokens"].copy_(torch.tensor(tokens, dtype=torch.int64))
+        b["slot"].fill_(slot)
+        b["pos"].fill_(pos0)
+        pos = torch.arange(pos0, pos0 + C, device=self.device)
+        b["kv_slots"].copy_(block_table.to(torch.int64)[pos // K.BLOCK] * K.BLOCK + pos % K.BLOCK)
+        b["ridx"].copy_(pos + rope_delta)
+        cur, nxt = b["res"]
+        K.embed_gather(self.embed, b["tokens"], cur)
+        carry = None
+        for li, lw in enumerate(self.layers):
+            proj = b["proj"][:, :lw.w_in.shape[0]]
+            K.gemv(lw.w_in, None, proj, norm=(cur, carry, lw.in_gain, nxt if carry is not None else None, self.eps))
+            if carry is not None:
+                cur, nxt = nxt, cur
+            if lw.kind == LINEAR:
+                j = self.lin_ids[li]
+                act = b["act_lin"]
+                K.gdn_decode(proj, lw.conv_w, lw.A_log, lw.dt_bias, lw.norm_w, self.ring[j], self.state[j], b["slot"],
+                             b["pos"], act, nk=c.linear_num_key_heads, nv=c.linear_num_value_heads,
+                             dk=c.linear_key_head_dim, dv=c.linear_value_head_dim, eps=self.eps, ntok=C,
+                             record=b["record"][j], write_state=False)
+            else:
+                j = self.full_ids[li]
+                act = b["act_full"]
+                K.attn_prep(proj, lw.qg, lw.kg, self.cos, self.sin, b["ridx"], b["kv_slots"], b["q"], self.kpool[j],
+                            self.vpool[j], nh=c.num_attention_heads, nkv=c.num_key_value_heads, hd=c.head_dim,
+                            rot=c.rotary_dim, eps=self.eps)
+                K.attn_prefill(b["q"], proj, self.kpool[j], self.vpool[j], block_table, act, q_pos0=pos0,
+                               nh=c.num_attention_heads, nkv=c.num_key_value_heads, hd=c.head_dim)
+            K.gemv(lw.w_out, act, b["h"])
+            if lw.moe is not None:
+                lw.moe.forward_decode(cur, b["h"], nxt, lw.post_gain, b["h2"], self, C)
+                cur, nxt = nxt, cur
+            else:
+                K.gemv(lw.w_gu, None, b["inter"], swiglu=True, norm=(cur, b["h"], lw.post_gain, nxt, self.eps))
+                cur, nxt = nxt, cur
+                K.gemv(lw.w_down, b["inter"], b["h2"])
+            carry = b["h2"]
+        K.gemv(self.lm_head, None, b["logits"], norm=(cur, carry, self.final_gain, nxt, self.eps))
+        self._verify_width = C
+        return b["logits"]
+
+    def commit(self, slot: int, n_accept: int) -> None:
+        """Apply the first ``n_accept`` recorded delta-net updates of the last ``verify`` call."""
+        c = self.cfg
+        b = self._verify_buffers(self._verify_width)
+        b["steps"].fill_(n_accept)
+        b["slot"].fill_(slot)
+        for li, j in self.lin_ids.items():
+            K.gdn_commit(self.state[j], b["record"][j], b["slot"], b["steps"], nv=c.linear_num_value_heads,
+                         dk=c.linear_key_head_dim, dv=c.linear_value_head_dim)
+
     # ------------------------------------------------------------------ runner hooks
     def embed_tokens(self, tokens: torch.Tensor) -> torch.Tensor:
         return K.embed_gather(self.embed, tokens)

@@ -19,6 +19,7 @@ RING = 16           # conv ring depth of the delta-net layers
 
 _status: dict[int, torch.Tensor] = {}
 LAUNCHES = 0        # kernels launched through this module (bench bookkeeping)
+STREAM_GEMV = True   # route single-row projections to the cp.async streaming kernel
 
 
 def _count(n: int = 1) -> None:
@@ -143,6 +144,17 @@ def gemv(W: torch.Tensor, x: torch.Tensor | None, out: torch.Tensor, *, swiglu: 
     K = W.shape[1]
     N = W.shape[0] // 2 if swiglu else W.shape[0]
     mode = (1 if swiglu else 0) | (2 if out.dtype == torch.float32 else 0)
+    if M == 1 and STREAM_GEMV and K * 2 <= 28 * 1024:
+        # batch-1 decode: weights streamed through per-warp cp.async rings
+        if norm is None:
+            assert x is not None and x.is_contiguous() and x.shape == (1, K)
+            call("gemv_stream_bf16", W, x, out, N, K, mode, N, None, None, None, None, 0.0)
+        else:
+            res_in, add, gain, res_out, eps = norm
+            assert res_in.is_contiguous() and res_in.shape == (1, K)
+            call("gemv_stream_bf16", W, None, out, N, K, mode, N, res_in, add, gain, res_out, float(eps))
+        _count()
+        return out
     if norm is None:
         assert x is not None and x.is_contiguous() and x.shape == (M, K)
         call("gemv_bf16", W, x, out, M, N, K, out.stride(0), mode, N, None, None, None, None, 0.0)

@@ -174,6 +174,29 @@ class OracleEngineModel:
             logits[i] = self._head(x)[0]
         return logits.argmax(-1), logits
 
+    @torch.no_grad()
+    def verify(self, tokens: list[int], pos0: int, slot: int, block_table: torch.Tensor, rope_delta: int = 0) -> torch.Tensor:
+        """Logits of ``C`` consecutive tokens; the delta-net state is restored afterwards and
+        ``commit`` replays the accepted prefix."""
+        c = self.cfg
+        self._verify = (list(tokens), pos0, block_table.clone(), rope_delta, self.snapshot_state(slot))
+        T = len(tokens)
+        pos = torch.arange(pos0, pos0 + T) + rope_delta
+        cos, sin = O.mrope_cos_sin(pos.reshape(1, -1).expand(3, -1), c.rotary_dim, c.rope_theta, c.mrope_section)
+        x = self._forward(self.embed_tokens(torch.tensor(tokens)), pos0, slot, block_table, cos, sin)
+        logits = self._head(x)
+        self.restore_state(slot, self._verify[4])
+        return logits
+
+    def commit(self, slot: int, n_accept: int) -> None:
+        tokens, pos0, table, delta, snap = self._verify
+        c = self.cfg
+        self.restore_state(slot, snap)
+        if n_accept > 0:
+            pos = torch.arange(pos0, pos0 + n_accept) + delta
+            cos, sin = O.mrope_cos_sin(pos.reshape(1, -1).expand(3, -1), c.rotary_dim, c.rope_theta, c.mrope_section)
+            self._forward(self.embed_tokens(torch.tensor(tokens[:n_accept])), pos0, slot, table, cos, sin)
+
     def sample(self, logits: torch.Tensor, temps, us) -> torch.Tensor:
         """Greedy when ``temps`` is None; else per-row inverse-CDF sampling with uniforms ``us``
         (rows with temperature <= 0 stay greedy)."""

@@ -1,0 +1,142 @@
+"""The resident engine process on a real unix socket, with the CPU twin as model: protocol ops,
+concurrent streams, failure recovery, diagnostic ops, PD hand-off, and the HTTP adapter on top."""
+import http.client
+import json
+import os
+import tempfile
+import threading
+import time
+
+import pytest
+import torch
+
+from coffin_b200.config import preset
+from coffin_b200.engine.config import EngineConfig
+from coffin_b200.oracle.engine_model import OracleEngineModel
+from coffin_b200.oracle.model import OracleModel
+from coffin_b200.serving.runtime import Server
+from coffin_b200.serving.transport import call, serve, stream
+from coffin_b200.weights.init import random_state_dict
+
+CFG = preset("tiny")
+SD = random_state_dict(CFG, 0)
+
+
+@pytest.fixture(scope="module")
+def engine():
+    builder = lambda: OracleEngineModel(CFG, SD, max_seq=512, num_slots=4)
+    srv = Server(builder(), EngineConfig(max_seq=512, max_num_seqs=4, graph=False), model_name="tiny", builder=builder)
+    sock = os.path.join(tempfile.mkdtemp(), "engine.sock")
+    ready = threading.Event()
+    t = threading.Thread(target=serve, args=(srv, sock), kwargs={"ready": ready}, daemon=True)
+    t.start()
+    assert ready.wait(10)
+    yield srv, sock
+    call(sock, {"op": "stop"})
+    t.join(timeout=10)
+
+
+def test_ping_tokenize_generate(engine):
+    srv, sock = engine
+    p = call(sock, {"op": "ping"})
+    assert p["ok"] and p["model"] == "tiny" and p["decode_capacity"] == 4 and "prefix" in p and "wall_ms" in p
+    toks = call(sock, {"op": "tokenize", "prompt": "héllo<|im_end|>"})["tokens"]
+    assert toks[-1] == srv.tok.special["<|im_end|>"] and len(toks) == 7
+    g = torch.Generator().manual_seed(0)
+    prompt = torch.randint(0, 256, (30,), generator=g).tolist()
+    rep = call(sock, {"op": "generate", "tokens": prompt, "max_new": 5, "ignore_eos": True})
+    with torch.no_grad():
+        ref = OracleModel(CFG, SD).generate(prompt, 5)[0]
+    assert rep["ok"] and rep["tokens"] == ref and rep["n_prompt"] == 30 and rep["n_new"] == 5
+    assert rep["stopped"] == "length" and rep["prefill_ms"] > 0
+    assert call(sock, {"op": "nope"})["ok"] is False
+
+
+def test_concurrent_chat_streams(engine):
+    srv, sock = engine
+    results = {}
+
+    def run(i):
+        evs = list(stream(sock, {"op": "chat_stream", "messages": [{"role": "user", "content": f"question {i}"}],
+                                 "max_new": 6, "ignore_eos": True}))
+        results[i] = evs
+
+    ts = [threading.Thread(target=run, args=(i,)) for i in range(5)]
+    [t.start() for t in ts]
+    [t.join(timeout=120) for t in ts]
+    for i in range(5):
+        evs = results[i]
+        assert evs[0]["type"] == "start" and evs[0]["prompt_opens_think"] is True
+        assert evs[-1]["type"] == "done" and evs[-1]["n_new"] == 6 and evs[-1]["ok"]
+    assert call(sock, {"op": "ping"})["queue"] == {"waiting": 0, "running": 0}
+
+
+def test_failure_recovery_keeps_service_up(engine):
+    srv, sock = engine
+    real = srv.model.decode
+    state = {"n": 0}
+
+    def flaky(M, graph=True):
+        state["n"] += 1
+        if state["n"] == 2:
+            raise RuntimeError("injected step failure")
+        return real(M, graph)
+
+    srv.model.decode = flaky
+    try:
+        rep = call(sock, {"op": "generate", "prompt": "abc", "max_new": 8, "ignore_eos": True})
+        assert rep["ok"] is False and "injected" in rep["error"]
+    finally:
+        srv.model.decode = real
+    rep = call(sock, {"op": "generate", "prompt": "abc", "max_new": 3, "ignore_eos": True})
+    assert rep["ok"] and rep["n_new"] == 3
+    assert "injected" in call(sock, {"op": "ping"})["last_error"]
+
+
+def test_diagnostic_ops_and_pd_handoff(engine):
+    srv, sock = engine
+    b = call(sock, {"op": "bench", "n": 4, "prompt": "hello world"})
+    assert b["ok"] and b["n"] == 4 and b["decode_tok_s"] > 0
+    s = call(sock, {"op": "spec", "n": 10, "prompt": "abcabcabcabcabcabc", "spec_k": 3})
+    assert s["ok"] and s["exact"] is True and "accept_rate" in s["accept"]
+    v = call(sock, {"op": "verify", "c": 2, "n": 2, "prompt": "hello"})
+    assert v["ok"] and v["verify_ms"] > 0
+    d = tempfile.mkdtemp()
+    pf = call(sock, {"op": "pd_prefill", "prompt": "the quick brown fox", "out_dir": d})
+    assert pf["ok"] and pf["bytes"] > 0
+    plain = call(sock, {"op": "generate", "prompt": "the quick brown fox", "max_new": 5, "ignore_eos": True})
+    dec = call(sock, {"op": "pd_decode", "out_dir": d, "max_new": 5})
+    assert dec["ok"] and dec["tokens"] == plain["tokens"]
+    batch = call(sock, {"op": "pd_decode_batch", "items": [{"dir": d}, {"dir": d}], "max_new": 4})
+    assert batch["ok"] and all(it["tokens"] == plain["tokens"][:4] for it in batch["items"])
+    r = call(sock, {"op": "reload"})
+    assert r["ok"] and r["n_reload"] == 1
+    assert call(sock, {"op": "reset"})["ok"]
+    assert call(sock, {"op": "generate", "prompt": "x", "max_new": 2, "ignore_eos": True})["ok"]
+
+
+def test_http_adapter_end_to_end(engine):
+    from coffin_b200.entrypoints.openai import app as oa
+    from coffin_b200.entrypoints.openai.client import EngineClient
+    srv, sock = engine
+    oa.configure(oa.ReplicaRouter([EngineClient(sock, 60), EngineClient(sock, 60)]), served_model_name="tiny",
+                 default_max_tokens=6)
+    http_srv = oa.make_server("127.0.0.1", 0)
+    threading.Thread(target=http_srv.serve_forever, daemon=True).start()
+    port = http_srv.server_address[1]
+    try:
+        c = http.client.HTTPConnection("127.0.0.1", port, timeout=60)
+        c.request("POST", "/v1/chat/completions", json.dumps({"messages": [{"role": "user", "content": "hi"}],
+                                                              "max_tokens": 5, "stream": True}))
+        data = c.getresponse().read().decode()
+        events = [l[6:] for l in data.split("\n") if l.startswith("data: ")]
+        assert events[-1] == "[DONE]"
+        last = json.loads(events[-2])
+        assert last["choices"][0]["finish_reason"] in ("length", "stop")
+        c.request("POST", "/v1/chat/completions", json.dumps({"messages": [{"role": "user", "content": "hi"}],
+                                                              "max_tokens": 5}))
+        out = json.loads(c.getresponse().read().decode())
+        assert out["object"] == "chat.completion" and out["usage"]["completion_tokens"] <= 5
+        c.close()
+    finally:
+        http_srv.shutdown()
