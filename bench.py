@@ -101,6 +101,8 @@ def main() -> None:
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--no-pdl", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--mma-ctas", type=int, default=0, help="tuning: tensor-core GEMV CTAs per SM")
+    ap.add_argument("--gemv-impl", default="", help="tuning: mma | scalar")
     ap.add_argument("--no-stream-gemv", action="store_true", help="tuning: register-staged GEMV for batch 1")
     ap.add_argument("--gemv-ctas", type=int, default=0, help="tuning: GEMV CTAs per SM (0 = library default)")
     ap.add_argument("--gemv-prefetch", type=int, default=-1, help="tuning: GEMV L2 prefetch-ahead (-1 = default)")
@@ -126,6 +128,11 @@ def main() -> None:
     W = max(3, args.warmup)
     if args.no_stream_gemv:
         K.STREAM_GEMV = False
+    if args.gemv_impl:
+        K.GEMV_IMPL = args.gemv_impl
+    if args.mma_ctas:
+        from coffin_b200.ops import _lib as _l
+        _l.call_nostream("set_mma_gemv_opts", args.mma_ctas)
     if args.gemv_ctas or args.gemv_prefetch >= 0:
         from coffin_b200.ops import _lib
         _lib.call_nostream("set_gemv_opts", args.gemv_ctas or 2, 1 if args.gemv_prefetch != 0 else 0)

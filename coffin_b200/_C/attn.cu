@@ -274,6 +274,8 @@ struct DecodeArgs {
   float* part_ml;                     // [M, nh, nsplit, 2]
   int nh, nkv, rot, nsplit;
   float scale_log2, eps;
+  unsigned* tickets;                  // [M, nkv] arrival counters (zero between launches)
+  bf16* out; int64_t ldo;             // [M, nh*hd] gated output, written by the last split to arrive
 };
 
 template <int HD, int REP>
@@ -406,6 +408,36 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const DecodeArgs a) {
       pml[(int64_t)r * a.nsplit * 2 + 1] = L;
     }
   }
+  // ---- the last split of this (row, kv head) to arrive merges all splits and applies the gate ----
+  __shared__ bool is_last;
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) {
+    unsigned* tk = a.tickets + (int64_t)m * a.nkv + kvh;
+    is_last = atomicAdd(tk, 1u) == (unsigned)a.nsplit - 1;
+    if (is_last) *tk = 0;
+  }
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  const float* bo = a.part_o + ((int64_t)m * a.nh + kvh * REP) * a.nsplit * HD;
+  const float* bml = a.part_ml + ((int64_t)m * a.nh + kvh * REP) * a.nsplit * 2;
+  for (int idx = tid; idx < REP * HD; idx += 128) {
+    const int r = idx / HD, d = idx % HD;
+    const float* pm = bml + (int64_t)r * a.nsplit * 2;
+    float Mx = -INFINITY;
+    for (int sp = 0; sp < a.nsplit; ++sp) Mx = fmaxf(Mx, __ldcg(pm + sp * 2));
+    float acc = 0.f, L = 0.f;
+    if (Mx > -INFINITY)
+      for (int sp = 0; sp < a.nsplit; ++sp) {
+        const float c = exp2f(__ldcg(pm + sp * 2) - Mx);
+        acc += __ldcg(bo + ((int64_t)r * a.nsplit + sp) * HD + d) * c;
+        L += __ldcg(pm + sp * 2 + 1) * c;
+      }
+    const int h = kvh * REP + r;
+    const float gt = sigmoid_f(__bfloat162float(prow[(int64_t)h * 2 * HD + HD + d]));
+    a.out[(int64_t)m * a.ldo + (int64_t)h * HD + d] = __float2bfloat16(L > 0.f ? acc / L * gt : 0.f);
+  }
 }
 
 template <int HD>
@@ -475,14 +507,14 @@ CB_EXPORT int cb_attn_prefill(const void* q, const void* gate, int64_t ldg, cons
 CB_EXPORT int cb_attn_decode(const void* proj, int64_t ldp, const void* qg, const void* kg, const void* cos,
                              const void* sin, const void* positions, const void* rope_pos,
                              const void* block_table, int64_t ldbt, void* kpool, void* vpool, void* part_o,
-                             void* part_ml, void* out, int64_t ldo, int64_t M, int64_t nh, int64_t nkv,
+                             void* part_ml, void* tickets, void* out, int64_t ldo, int64_t M, int64_t nh, int64_t nkv,
                              int64_t hd, int64_t rot, int64_t nsplit, float eps, void* stream) {
   if (M == 0) return 0;
-  if (nh % nkv || nsplit < 1) return CB_ERR_SHAPE;
+  if (nh % nkv || nsplit < 1 || !tickets) return CB_ERR_SHAPE;
   DecodeArgs a{(const bf16*)proj, ldp, (const float*)qg, (const float*)kg, (const float*)cos, (const float*)sin,
                (const int*)positions, (const int*)rope_pos, (const int*)block_table, ldbt, (bf16*)kpool,
                (bf16*)vpool, (float*)part_o, (float*)part_ml, (int)nh, (int)nkv, (int)rot, (int)nsplit,
-               1.4426950408889634f / sqrtf((float)hd), eps};
+               1.4426950408889634f / sqrtf((float)hd), eps, (unsigned*)tickets, (bf16*)out, ldo};
   cudaStream_t st = (cudaStream_t)stream;
   const int rep = (int)(nh / nkv);
   int rc = CB_ERR_SHAPE;
@@ -504,11 +536,5 @@ CB_EXPORT int cb_attn_decode(const void* proj, int64_t ldp, const void* qg, cons
       default: return CB_ERR_SHAPE;
     }
   }
-  if (rc) return rc;
-  dim3 grid((unsigned)nh, (unsigned)M);
-  if (hd == 256)
-    return (int)cb_launch(attn_combine_kernel<256>, grid, dim3(256), 0, st, (const float*)part_o,
-                          (const float*)part_ml, (const bf16*)proj, ldp, (bf16*)out, ldo, (int)nh, (int)nsplit);
-  return (int)cb_launch(attn_combine_kernel<64>, grid, dim3(64), 0, st, (const float*)part_o,
-                        (const float*)part_ml, (const bf16*)proj, ldp, (bf16*)out, ldo, (int)nh, (int)nsplit);
+  return rc;
 }

@@ -12,7 +12,8 @@
 //     flight, and the SwiGLU variant computes gate row i and up row i in the same warp.
 // Replaces the reference's gemv family (backends/corex/kernels/gemv.cu:76-947, one launch
 // each for add, norm, GEMV, silu_mul) with a single launch per projection.
-#include "common.cuh"
+#include <string.h>
+#include "tp.cuh"
 
 namespace {
 
@@ -35,6 +36,8 @@ struct GemvArgs {
   int nrg;            // row groups per round; KSPLIT = kWarps / nrg
   int rounds;         // rounds of the grid-wide sweep (nrg * R rows per CTA per round)
   int pf_rounds;      // rounds of weights kept in flight towards L2 ahead of the compute
+  int pull_site, push_site;   // tensor parallel: -1 = off
+  TpComm tp;
 };
 
 // L2 prefetch of the weight rows [ra, rb) (contiguous bytes), one 128-byte line per thread-step.
@@ -83,12 +86,17 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_kernel(const GemvArgs a) {
 
   // ---- prologue: activation rows into shared memory --------------------------------------
   if (NORM) {
+    if (a.pull_site >= 0) tp_pull_wait(a.tp, a.pull_site);
     for (int m = 0; m < M; ++m) {
       float ss = 0.f;
       for (int64_t c = tid; c < nchunk; c += kThreads) {
         float f[8], g[8];
         bf16x8_to_float(*reinterpret_cast<const uint4*>(a.res_in + m * K + c * 8), f);
-        if (a.add) {
+        if (a.pull_site >= 0) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i)
+            f[i] = __bfloat162float(__float2bfloat16(f[i] + tp_pull_value(a.tp, a.pull_site, m * K + c * 8 + i)));
+        } else if (a.add) {
           bf16x8_to_float(*reinterpret_cast<const uint4*>(a.add + m * K + c * 8), g);
 #pragma unroll
           for (int i = 0; i < 8; ++i) f[i] = __bfloat162float(__float2bfloat16(f[i] + g[i]));
@@ -188,7 +196,8 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_kernel(const GemvArgs a) {
             if (p == r && mm == m) { v = acc[p][mm]; if (SWIGLU) v2 = acc[R + p][mm]; }
         if (row < row_end) {
           if (SWIGLU) v = silu_f(v) * v2;
-          if (OUT_F32) reinterpret_cast<float*>(a.y)[m * a.ldy + row] = v;
+          if (a.push_site >= 0) tp_push_value(a.tp, a.push_site, m * a.N + row, v);
+          else if (OUT_F32) reinterpret_cast<float*>(a.y)[m * a.ldy + row] = v;
           else reinterpret_cast<bf16*>(a.y)[m * a.ldy + row] = __float2bfloat16(v);
         }
       }
@@ -212,11 +221,13 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_kernel(const GemvArgs a) {
           if (SWIGLU) v2 += part[(w * PHYS + R + r) * M + m];
         }
         if (SWIGLU) v = silu_f(v) * v2;
-        if (OUT_F32) reinterpret_cast<float*>(a.y)[m * a.ldy + row] = v;
+        if (a.push_site >= 0) tp_push_value(a.tp, a.push_site, m * a.N + row, v);
+        else if (OUT_F32) reinterpret_cast<float*>(a.y)[m * a.ldy + row] = v;
         else reinterpret_cast<bf16*>(a.y)[m * a.ldy + row] = __float2bfloat16(v);
       }
     }
   }
+  if (a.push_site >= 0) tp_push_done(a.tp, a.push_site, gridDim.x);
 }
 
 int g_gemv_sms = 0;
@@ -281,14 +292,19 @@ CB_EXPORT int cb_set_gemv_opts(int64_t ctas_per_sm, int64_t prefetch) {
 // Norm prologue is enabled when res_in != null (then x is ignored).
 CB_EXPORT int cb_gemv_bf16(const void* W, const void* x, void* y, int64_t M, int64_t N, int64_t K,
                            int64_t ldy, int64_t mode, int64_t up_off, const void* res_in,
-                           const void* add, const void* gain, void* res_out, float eps, void* stream) {
-  if (!W || !y || (!x && !res_in) || (res_in && !gain)) return CB_ERR_ARG;
+                           const void* add, const void* gain, void* res_out, float eps, const void* tp,
+                           int64_t pull_site, int64_t push_site, void* stream) {
+  if (!W || (!y && push_site < 0) || (!x && !res_in) || (res_in && !gain)) return CB_ERR_ARG;
+  if ((pull_site >= 0 || push_site >= 0) && !tp) return CB_ERR_ARG;
+  if (pull_site >= 0 && !res_in) return CB_ERR_ARG;
   if (K % 8 || M < 1 || M > 8 || N < 1) return CB_ERR_SHAPE;
   if (res_in && res_out && (res_out == res_in || res_out == add)) return CB_ERR_ARG;
   GemvArgs a;
   a.W = (const bf16*)W; a.x = (const bf16*)x; a.y = y; a.N = N; a.K = K; a.ldy = ldy;
   a.up_off = up_off; a.res_in = (const bf16*)res_in; a.add = (const bf16*)add;
   a.gain = (const float*)gain; a.res_out = (bf16*)res_out; a.eps = eps; a.nrg = 1; a.rounds = 0; a.pf_rounds = 1;
+  a.pull_site = (int)pull_site; a.push_site = (int)push_site;
+  if (tp) a.tp = *(const TpComm*)tp; else memset(&a.tp, 0, sizeof(a.tp));
   const bool sw = mode & 1, f32 = mode & 2, norm = res_in != nullptr;
   cudaStream_t st = (cudaStream_t)stream;
   switch (M) {

@@ -1,0 +1,276 @@
+// Decode projection (1..8 activation rows) with the dot products on the tensor cores.
+//
+// Profiling the scalar GEMVs showed them instruction-bound, not memory-bound: unpacking bf16 and
+// issuing one FMA per element costs ~4 instructions per weight element, and at 6.5 TB/s the SMs
+// cannot issue that many.  Here a warp owns 16 weight rows and feeds them to mma.m16n8k16 as the
+// A operand straight from its 16-byte global loads: lane (g, t) loads chunk 4j+t of rows g and g+8,
+// which are exactly its A fragments for two MMAs if the k index is permuted the same way for the
+// B operand - and B is the activation, read from shared memory with the same permutation.  The 8
+// columns of B are the (up to) 8 batch rows, so one kernel serves M = 1..8 at the same cost:
+// ~0.5 instructions per weight element.  The kernel keeps the fused prologue (residual add +
+// RMSNorm, or the tensor-parallel pull-sum) and epilogues (SwiGLU, fp32 logits, tensor-parallel
+// push) of gemv.cu, the K-split for narrow outputs and the grid-wide sweep order.
+#include <string.h>
+#include "tp.cuh"
+
+namespace {
+
+constexpr int kW = 8, kT = kW * 32;
+constexpr int kU = 4;   // k-step pairs (32 elements each) in flight per lane
+
+struct MmaArgs {
+  const bf16* W; const bf16* x; void* y;
+  int64_t N, K, ldy, up_off;
+  const bf16* res_in; const bf16* add; const float* gain; bf16* res_out;
+  float eps;
+  int M;              // activation rows (1..8)
+  int ksplit;         // k-slices per 16-row block (a power of two <= 8)
+  int rounds;         // rounds of the grid-wide sweep
+  int pull_site, push_site;
+  TpComm tp;
+};
+
+__device__ __forceinline__ void mma16816(float* c, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                         uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+template <bool SWIGLU, bool NORM, bool OUT_F32>
+__global__ void __launch_bounds__(kT, 3) gemv_mma_kernel(const MmaArgs a) {
+  constexpr int PB = SWIGLU ? 2 : 1;   // physical 16-row blocks per unit (gate, up)
+  constexpr int U = SWIGLU ? 2 : kU;   // same number of loads in flight either way
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const int64_t K = a.K, nchunk = K >> 3;
+  const int M = a.M;
+  bf16* xs = reinterpret_cast<bf16*>(smem_raw);                                  // [M][K]
+  float* part = reinterpret_cast<float*>(smem_raw + (((size_t)M * K * 2 + 15) & ~(size_t)15));  // [rounds][kW][PB][16][8]
+  __shared__ float red[32];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
+  const int ksplit = a.ksplit, rbr = kW / ksplit;          // row blocks per CTA round
+  const int ks = warp % ksplit, rb_in = warp / ksplit;
+  // k range of this warp in units of 4 chunks (one MMA pair)
+  const int64_t npair = (nchunk + 3) >> 2;
+  const int64_t pper = (npair + ksplit - 1) / ksplit;
+  const int64_t p0 = ks * pper, p1 = min(npair, p0 + pper);
+
+  // Weights do not depend on the previous kernel: request this warp's first batch of round 0 into
+  // registers before waiting on the producer of the activations, so that (under programmatic
+  // dependent launch) the HBM stream of this projection starts during the previous kernel's tail and
+  // runs through the norm prologue below.
+  auto row_ptrs = [&](int round, const bf16** wlo, const bf16** whi) -> bool {
+    const int64_t blk = ((int64_t)round * gridDim.x + blockIdx.x) * rbr + rb_in;
+    const int64_t r_lo = blk * 16 + g, r_hi = r_lo + 8;
+#pragma unroll
+    for (int b = 0; b < PB; ++b) {
+      const int64_t off = b ? a.up_off : 0;
+      wlo[b] = a.W + (off + min(r_lo, a.N - 1)) * K;
+      whi[b] = a.W + (off + min(r_hi, a.N - 1)) * K;
+    }
+    return blk * 16 < a.N;
+  };
+  auto load_batch = [&](int64_t p, const bf16* const* wlo, const bf16* const* whi, uint4 (*lo)[PB], uint4 (*hi)[PB]) {
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int64_t c = (p + u) * 4 + t;
+      const bool ok = (p + u) < p1 && c < nchunk;
+#pragma unroll
+      for (int b = 0; b < PB; ++b) {
+        lo[u][b] = ok ? ld_stream(wlo[b] + c * 8) : make_uint4(0, 0, 0, 0);
+        hi[u][b] = ok ? ld_stream(whi[b] + c * 8) : make_uint4(0, 0, 0, 0);
+      }
+    }
+  };
+  griddep_launch();
+  uint4 lo[U][PB], hi[U][PB];
+  {
+    const bf16* wlo[PB];
+    const bf16* whi[PB];
+    if (row_ptrs(0, wlo, whi) && p0 < p1) load_batch(p0, wlo, whi, lo, hi);
+  }
+  griddep_wait();
+
+  // ---- prologue: activation rows into shared memory ------------------------------------------
+  if (NORM) {
+    if (a.pull_site >= 0) tp_pull_wait(a.tp, a.pull_site);
+    for (int m = 0; m < M; ++m) {
+      float ss = 0.f;
+      for (int64_t c = tid; c < nchunk; c += kT) {
+        float f[8], q[8];
+        bf16x8_to_float(*reinterpret_cast<const uint4*>(a.res_in + m * K + c * 8), f);
+        if (a.pull_site >= 0) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i)
+            f[i] = __bfloat162float(__float2bfloat16(f[i] + tp_pull_value(a.tp, a.pull_site, m * K + c * 8 + i)));
+        } else if (a.add) {
+          bf16x8_to_float(*reinterpret_cast<const uint4*>(a.add + m * K + c * 8), q);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) f[i] = __bfloat162float(__float2bfloat16(f[i] + q[i]));
+        }
+        const uint4 packed = float_to_bf16x8(f);
+        *reinterpret_cast<uint4*>(xs + m * K + c * 8) = packed;
+        if (a.res_out && blockIdx.x == 0) *reinterpret_cast<uint4*>(a.res_out + m * K + c * 8) = packed;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) ss += f[i] * f[i];
+      }
+      const float rstd = rsqrtf(block_sum(ss, red) / (float)K + a.eps);
+      for (int64_t c = tid; c < nchunk; c += kT) {
+        float f[8];
+        bf16x8_to_float(*reinterpret_cast<const uint4*>(xs + m * K + c * 8), f);
+        const float4 g0 = *reinterpret_cast<const float4*>(a.gain + c * 8);
+        const float4 g1 = *reinterpret_cast<const float4*>(a.gain + c * 8 + 4);
+        f[0] *= rstd * g0.x; f[1] *= rstd * g0.y; f[2] *= rstd * g0.z; f[3] *= rstd * g0.w;
+        f[4] *= rstd * g1.x; f[5] *= rstd * g1.y; f[6] *= rstd * g1.z; f[7] *= rstd * g1.w;
+        *reinterpret_cast<uint4*>(xs + m * K + c * 8) = float_to_bf16x8(f);
+      }
+    }
+  } else {
+    for (int64_t c = tid; c < (int64_t)M * nchunk; c += kT)
+      *reinterpret_cast<uint4*>(xs + c * 8) = *reinterpret_cast<const uint4*>(a.x + c * 8);
+  }
+  __syncthreads();
+
+  const bf16* xrow = xs + (int64_t)g * K;      // batch row g supplies column g of the B operand
+  const bool has_x = g < M;
+
+  for (int round = 0; round < a.rounds; ++round) {
+    const int64_t blk = ((int64_t)round * gridDim.x + blockIdx.x) * rbr + rb_in;   // 16-row block index
+    const int64_t r_lo = blk * 16 + g, r_hi = r_lo + 8;
+    float acc[PB][4];
+#pragma unroll
+    for (int b = 0; b < PB; ++b) acc[b][0] = acc[b][1] = acc[b][2] = acc[b][3] = 0.f;
+    const bf16* wlo[PB];
+    const bf16* whi[PB];
+    const bool blk_ok = row_ptrs(round, wlo, whi);
+    if (blk_ok) {
+      for (int64_t p = p0; p < p1; p += U) {
+        if (round > 0 || p > p0) load_batch(p, wlo, whi, lo, hi);   // the first batch is already in flight
+        uint4 xv[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const int64_t c = (p + u) * 4 + t;
+          const bool ok = (p + u) < p1 && c < nchunk;
+          xv[u] = (ok && has_x) ? *reinterpret_cast<const uint4*>(xrow + c * 8) : make_uint4(0, 0, 0, 0);
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u)
+#pragma unroll
+          for (int b = 0; b < PB; ++b) {
+            mma16816(acc[b], lo[u][b].x, hi[u][b].x, lo[u][b].y, hi[u][b].y, xv[u].x, xv[u].y);
+            mma16816(acc[b], lo[u][b].z, hi[u][b].z, lo[u][b].w, hi[u][b].w, xv[u].z, xv[u].w);
+          }
+      }
+    }
+    // acc[b][0..1]: (row g, batch rows 2t, 2t+1); acc[b][2..3]: (row g+8, same batch rows)
+    if (ksplit == 1) {
+      if (blk_ok) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int m = 2 * t + (e & 1);
+          const int64_t row = (e & 2) ? r_hi : r_lo;
+          if (m < M && row < a.N) {
+            float v = acc[0][e];
+            if (SWIGLU) v = silu_f(v) * acc[PB - 1][e];
+            if (a.push_site >= 0) tp_push_value(a.tp, a.push_site, (int64_t)m * a.N + row, v);
+            else if (OUT_F32) reinterpret_cast<float*>(a.y)[(int64_t)m * a.ldy + row] = v;
+            else reinterpret_cast<bf16*>(a.y)[(int64_t)m * a.ldy + row] = __float2bfloat16(v);
+          }
+        }
+      }
+    } else {
+      float* pw = part + (((size_t)round * kW + warp) * PB) * 128;
+#pragma unroll
+      for (int b = 0; b < PB; ++b)
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+          pw[b * 128 + (g + ((e & 2) ? 8 : 0)) * 8 + 2 * t + (e & 1)] = acc[b][e];
+    }
+  }
+  if (ksplit > 1) {
+    __syncthreads();
+    // one thread per (round, row block of the round, row in block, batch row): fixed-order sum over k-slices
+    const int per_round = rbr * 16 * 8;
+    for (int idx = tid; idx < a.rounds * per_round; idx += kT) {
+      const int round = idx / per_round, rem = idx % per_round;
+      const int rb = rem / 128, r = (rem % 128) / 8, m = rem % 8;
+      const int64_t row = (((int64_t)round * gridDim.x + blockIdx.x) * rbr + rb) * 16 + r;
+      if (m >= M || row >= a.N) continue;
+      float v = 0.f, v2 = 0.f;
+      for (int s = 0; s < ksplit; ++s) {
+        const float* pw = part + (((size_t)round * kW + rb * ksplit + s) * PB) * 128;
+        v += pw[r * 8 + m];
+        if (SWIGLU) v2 += pw[128 + r * 8 + m];
+      }
+      if (SWIGLU) v = silu_f(v) * v2;
+      if (a.push_site >= 0) tp_push_value(a.tp, a.push_site, (int64_t)m * a.N + row, v);
+      else if (OUT_F32) reinterpret_cast<float*>(a.y)[(int64_t)m * a.ldy + row] = v;
+      else reinterpret_cast<bf16*>(a.y)[(int64_t)m * a.ldy + row] = __float2bfloat16(v);
+    }
+  }
+  if (a.push_site >= 0) tp_push_done(a.tp, a.push_site, gridDim.x);
+}
+
+int g_mma_sms = 0;
+int g_mma_ctas = 3;
+
+template <bool SWIGLU, bool NORM, bool OUT_F32>
+int launch_mma(MmaArgs a, cudaStream_t st) {
+  if (!g_mma_sms) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&g_mma_sms, cudaDevAttrMultiProcessorCount, dev);
+    if (g_mma_sms <= 0) g_mma_sms = 148;
+  }
+  constexpr int PB = SWIGLU ? 2 : 1;
+  const int64_t nblk = (a.N + 15) / 16;
+  const int64_t slots = (int64_t)g_mma_sms * g_mma_ctas;
+  const int64_t npair = ((a.K >> 3) + 3) >> 2;
+  // split K across warps until the grid fills the resident CTA slots (or slices get too short)
+  int ks = 1;
+  while (ks < kW && (nblk * ks + kW - 1) / kW < slots && npair / (ks * 2) >= 8) ks <<= 1;
+  a.ksplit = ks;
+  const int rbr = kW / ks;
+  const int64_t units = (nblk + rbr - 1) / rbr;
+  const int64_t grid = units < slots ? units : slots;
+  a.rounds = (int)((units + grid - 1) / grid);
+  size_t smem = (((size_t)a.M * a.K * 2 + 15) & ~(size_t)15);
+  if (ks > 1) smem += (size_t)a.rounds * kW * PB * 128 * sizeof(float);
+  if (smem > 72 * 1024) return CB_ERR_SHAPE;
+  auto kern = gemv_mma_kernel<SWIGLU, NORM, OUT_F32>;
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+  }
+  return (int)cb_launch(kern, dim3((unsigned)grid), dim3(kT), smem, st, a);
+}
+
+}  // namespace
+
+CB_EXPORT int cb_set_mma_gemv_opts(int64_t ctas_per_sm) { g_mma_ctas = ctas_per_sm < 1 ? 1 : (int)ctas_per_sm; return 0; }
+
+// Same contract as cb_gemv_bf16 (M = 1..8, any M in that range).
+CB_EXPORT int cb_gemv_mma_bf16(const void* W, const void* x, void* y, int64_t M, int64_t N, int64_t K,
+                               int64_t ldy, int64_t mode, int64_t up_off, const void* res_in, const void* add,
+                               const void* gain, void* res_out, float eps, const void* tp, int64_t pull_site,
+                               int64_t push_site, void* stream) {
+  if (!W || (!y && push_site < 0) || (!x && !res_in) || (res_in && !gain)) return CB_ERR_ARG;
+  if ((pull_site >= 0 || push_site >= 0) && !tp) return CB_ERR_ARG;
+  if (pull_site >= 0 && !res_in) return CB_ERR_ARG;
+  if (K % 8 || M < 1 || M > 8 || N < 1) return CB_ERR_SHAPE;
+  if (res_in && res_out && (res_out == res_in || res_out == add)) return CB_ERR_ARG;
+  MmaArgs a;
+  a.W = (const bf16*)W; a.x = (const bf16*)x; a.y = y; a.N = N; a.K = K; a.ldy = ldy; a.up_off = up_off;
+  a.res_in = (const bf16*)res_in; a.add = (const bf16*)add; a.gain = (const float*)gain;
+  a.res_out = (bf16*)res_out; a.eps = eps; a.M = (int)M; a.ksplit = 1; a.rounds = 1;
+  a.pull_site = (int)pull_site; a.push_site = (int)push_site;
+  if (tp) a.tp = *(const TpComm*)tp; else memset(&a.tp, 0, sizeof(a.tp));
+  const bool sw = mode & 1, f32 = mode & 2, norm = res_in != nullptr;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (sw) {
+    if (f32) return CB_ERR_ARG;
+    return norm ? launch_mma<true, true, false>(a, st) : launch_mma<true, false, false>(a, st);
+  }
+  if (f32) return norm ? launch_mma<false, true, true>(a, st) : launch_mma<false, false, true>(a, st);
+  return norm ? launch_mma<false, true, false>(a, st) : launch_mma<false, false, false>(a, st);
+}

@@ -10,7 +10,8 @@
 // order (deterministic).  The first slices are requested before the wait on the previous kernel,
 // so under programmatic dependent launch the weight stream crosses kernel boundaries.
 // Same fused prologue (residual add + RMSNorm) and epilogue (SwiGLU, fp32 logits) as gemv.cu.
-#include "common.cuh"
+#include <string.h>
+#include "tp.cuh"
 
 namespace {
 
@@ -26,6 +27,8 @@ struct StreamArgs {
   int ksplit;         // slices per row
   int slc;            // chunks (16 B) per slice, a multiple of 32
   int nst;            // ring stages per warp
+  int pull_site, push_site;   // tensor parallel: -1 = off
+  TpComm tp;
 };
 
 __device__ __forceinline__ void cp16(uint32_t saddr, const void* g) {
@@ -95,10 +98,15 @@ __global__ void __launch_bounds__(kT, 2) gemv_stream_kernel(const StreamArgs a) 
   // ---- prologue: the activation row into shared memory ------------------------------------
   if (NORM) {
     float ss = 0.f;
+    if (a.pull_site >= 0) tp_pull_wait(a.tp, a.pull_site);
     for (int64_t c = tid; c < nchunk; c += kT) {
       float f[8], g[8];
       bf16x8_to_float(*reinterpret_cast<const uint4*>(a.res_in + c * 8), f);
-      if (a.add) {
+      if (a.pull_site >= 0) {   // add = sum over ranks of the previous projection's partial outputs
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+          f[i] = __bfloat162float(__float2bfloat16(f[i] + tp_pull_value(a.tp, a.pull_site, c * 8 + i)));
+      } else if (a.add) {
         bf16x8_to_float(*reinterpret_cast<const uint4*>(a.add + c * 8), g);
 #pragma unroll
         for (int i = 0; i < 8; ++i) f[i] = __bfloat162float(__float2bfloat16(f[i] + g[i]));
@@ -161,9 +169,11 @@ __global__ void __launch_bounds__(kT, 2) gemv_stream_kernel(const StreamArgs a) 
       if (SWIGLU) v2 += part[r * kW + i * upr + a.ksplit + s];
     }
     if (SWIGLU) v = silu_f(v) * v2;
-    if (OUT_F32) reinterpret_cast<float*>(a.y)[lrow] = v;
+    if (a.push_site >= 0) tp_push_value(a.tp, a.push_site, lrow, v);
+    else if (OUT_F32) reinterpret_cast<float*>(a.y)[lrow] = v;
     else reinterpret_cast<bf16*>(a.y)[lrow] = __float2bfloat16(v);
   }
+  if (a.push_site >= 0) tp_push_done(a.tp, a.push_site, gridDim.x);
 }
 
 int g_stream_sms = 0;
@@ -206,14 +216,19 @@ CB_EXPORT int cb_set_stream_opts(int64_t ctas_per_sm) { g_stream_ctas = ctas_per
 // Single-row projection; same arguments as cb_gemv_bf16 with M fixed to 1.
 CB_EXPORT int cb_gemv_stream_bf16(const void* W, const void* x, void* y, int64_t N, int64_t K, int64_t mode,
                                   int64_t up_off, const void* res_in, const void* add, const void* gain,
-                                  void* res_out, float eps, void* stream) {
-  if (!W || !y || (!x && !res_in) || (res_in && !gain)) return CB_ERR_ARG;
+                                  void* res_out, float eps, const void* tp, int64_t pull_site, int64_t push_site,
+                                  void* stream) {
+  if (!W || (!y && push_site < 0) || (!x && !res_in) || (res_in && !gain)) return CB_ERR_ARG;
+  if ((pull_site >= 0 || push_site >= 0) && !tp) return CB_ERR_ARG;
+  if (pull_site >= 0 && !res_in) return CB_ERR_ARG;
   if (K % 8 || N < 1) return CB_ERR_SHAPE;
   if (res_in && res_out && (res_out == res_in || res_out == add)) return CB_ERR_ARG;
   StreamArgs a;
   a.W = (const bf16*)W; a.x = (const bf16*)x; a.y = y; a.N = N; a.K = K; a.up_off = up_off;
   a.res_in = (const bf16*)res_in; a.add = (const bf16*)add; a.gain = (const float*)gain;
   a.res_out = (bf16*)res_out; a.eps = eps; a.rounds = 0; a.ksplit = 1; a.slc = 32; a.nst = 2;
+  a.pull_site = (int)pull_site; a.push_site = (int)push_site;
+  if (tp) a.tp = *(const TpComm*)tp; else memset(&a.tp, 0, sizeof(a.tp));
   const bool sw = mode & 1, f32 = mode & 2, norm = res_in != nullptr;
   cudaStream_t st = (cudaStream_t)stream;
   if (sw) {

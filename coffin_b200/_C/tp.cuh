@@ -1,0 +1,95 @@
+// Tensor-parallel all-reduce folded into the projections, over peer memory (NVLink / NVSwitch).
+//
+// A row-parallel projection leaves every rank with a partial sum of the hidden vector.  Instead of
+// a collective call between kernels, the producing GEMV *pushes* its partial rows straight into an
+// inbox on every rank (plain peer stores through IPC-mapped pointers) and publishes a flag; the next
+// projection's prologue *pulls*: it waits (bounded) for the flags of all ranks and adds the inbox
+// slots in rank order while it stages its activation, so the reduction costs no launch and its
+// latency hides behind the consumer's weight prefetch.  The sum order is fixed, hence every rank
+// computes bit-identical activations.  Replaces the reference's per-projection gloo all-reduce of
+// RowParallelProjection (models/qwen35/parallel.py:1015-1061) and the idea of its p2p_combine kernel
+// (backends/corex/kernels/p2p_reduce.cu:55-173: write to all peers, publish flag, bounded spin).
+//
+// Flags carry the step epoch (a device-side counter every rank advances once per step), so buffers
+// are reused without resetting: a site's inbox can only be overwritten a full step later, and a rank
+// cannot get there before all peers consumed the previous contents because it needs their partial
+// sums of the sites in between.  Waits give up after kTpWaitNs, set the status word and continue
+// with whatever is in the inbox, so a dead peer costs an error, not a hung GPU.
+#pragma once
+#include "common.cuh"
+
+constexpr int kTpMaxWorld = 8;
+constexpr unsigned long long kTpWaitNs = 2000000000ull;   // 2 s
+
+struct TpComm {
+  int rank, world;
+  int64_t slot_floats;      // floats per (site, rank) inbox slot  (= max rows * hidden)
+  float* inbox[kTpMaxWorld];       // base of every rank's inbox: [sites][world][slot_floats]
+  unsigned* flags[kTpMaxWorld];    // base of every rank's flags: [sites][world]
+  unsigned* arrive;         // local: [sites] CTA arrival counters of the producer
+  const unsigned* epoch;    // local: current step number
+  int* status;              // local status word (set to 16 + rank on a wait that ran out)
+};
+
+__device__ __forceinline__ unsigned long long tp_now_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ unsigned tp_ld_acquire(const unsigned* p) {
+  unsigned v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void tp_st_release(unsigned* p, unsigned v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+// Producer: store `n` consecutive fp32 partial values starting at element `off` of this rank's slot
+// on every rank.  Called by the threads that own the values.
+__device__ __forceinline__ void tp_push_value(const TpComm& c, int site, int64_t off, float v) {
+  const int64_t base = ((int64_t)site * c.world + c.rank) * c.slot_floats + off;
+#pragma unroll
+  for (int p = 0; p < kTpMaxWorld; ++p)
+    if (p < c.world) c.inbox[p][base] = v;
+}
+// Producer: after a CTA pushed all its values. The last CTA of the grid publishes the flags.
+__device__ __forceinline__ void tp_push_done(const TpComm& c, int site, unsigned nblocks) {
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned prev = atomicAdd(c.arrive + site, 1u);
+    if (prev == nblocks - 1) {
+      c.arrive[site] = 0;
+      __threadfence_system();
+      const unsigned e = *c.epoch;
+      for (int p = 0; p < c.world; ++p) tp_st_release(c.flags[p] + (int64_t)site * c.world + c.rank, e);
+    }
+  }
+}
+// Consumer: wait until every rank published this step's flag for the site. Thread 0 waits, then
+// the block synchronises.
+__device__ __forceinline__ void tp_pull_wait(const TpComm& c, int site) {
+  if (threadIdx.x == 0) {
+    const unsigned e = *c.epoch;
+    const unsigned* f = c.flags[c.rank] + (int64_t)site * c.world;
+    const unsigned long long t0 = tp_now_ns();
+    for (int r = 0; r < c.world; ++r) {
+      unsigned spins = 0;
+      while ((int)(tp_ld_acquire(f + r) - e) < 0) {
+        if ((++spins & 1023u) == 0 && tp_now_ns() - t0 > kTpWaitNs) {
+          atomicExch(c.status, 16 + r);
+          break;
+        }
+      }
+    }
+  }
+  __syncthreads();
+}
+// Consumer: sum of the ranks' partial values at element `off` (fixed rank order).
+__device__ __forceinline__ float tp_pull_value(const TpComm& c, int site, int64_t off) {
+  const float* base = c.inbox[c.rank] + (int64_t)site * c.world * c.slot_floats + off;
+  float s = 0.f;
+  for (int r = 0; r < c.world; ++r) s += __ldcg(base + (int64_t)r * c.slot_floats);
+  return s;
+}

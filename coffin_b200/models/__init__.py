@@ -30,8 +30,13 @@ def _ensure_builtin() -> None:
         from .qwen35.model import Qwen35Model
         tp_world, tp_rank = kw.pop("tp_world", 1), kw.pop("tp_rank", 0)
         if tp_world > 1:
-            from ..parallel.tp import TensorParallelQwen35
-            return TensorParallelQwen35(cfg, sd, tp_world=tp_world, tp_rank=tp_rank, **kw)
+            from ..parallel.tp import TpComm, local_config, make_exchange, shard_state_dict
+            lcfg = local_config(cfg, tp_world)
+            lsd = shard_state_dict(cfg, sd, tp_rank, tp_world)
+            n_sites = 2 * cfg.num_hidden_layers
+            tp = TpComm(tp_rank, tp_world, cfg.hidden_size, 8, n_sites, exchange=make_exchange())
+            kw.pop("free_source", None)
+            return Qwen35Model(lcfg, lsd, tp=tp, full_cfg=cfg, **kw)
         return Qwen35Model(cfg, sd, **kw)
 
     for n in ("qwen3_5", "qwen35", "qwen3_5_moe", "qwen3_5_text", "qwen3_next"):

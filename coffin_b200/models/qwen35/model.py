@@ -64,8 +64,15 @@ class Qwen35Model:
 
     def __init__(self, cfg: ModelConfig, sd: dict[str, torch.Tensor], device: str | torch.device = "cuda",
                  max_seq: int = 4096, num_slots: int = 2, num_blocks: int | None = None,
-                 max_chunk: int = 2048, pdl: bool = True, free_source: bool = False) -> None:
+                 max_chunk: int = 2048, pdl: bool = True, free_source: bool = False, tp=None,
+                 full_cfg: ModelConfig | None = None) -> None:
+        """``cfg`` is the geometry this instance computes (a tensor-parallel shard gets its local
+        head / channel counts, ``full_cfg`` the unsharded model and ``tp`` the communicator)."""
         self.cfg = cfg
+        self.tp = tp
+        self.tp_world = tp.world if tp is not None else 1
+        self.tp_rank = tp.rank if tp is not None else 0
+        self.full_cfg = full_cfg or cfg
         self.device = torch.device(device)
         self.max_seq = int(max_seq)
         self.num_slots = int(num_slots)
@@ -88,6 +95,12 @@ class Qwen35Model:
 
         self.embed = w(LM + "embed_tokens.weight").contiguous()
         self.lm_head = w("lm_head.weight").contiguous() if "lm_head.weight" in sd else self.embed
+        self.vocab_local = c.vocab_size
+        if self.tp_world > 1:       # vocabulary-parallel head: this rank scores a contiguous slice
+            if c.vocab_size % self.tp_world:
+                raise ValueError("vocab_size must divide by the tensor-parallel world")
+            self.vocab_local = c.vocab_size // self.tp_world
+            self.lm_head = self.lm_head[self.tp_rank * self.vocab_local:(self.tp_rank + 1) * self.vocab_local]
         self.final_gain = gain(LM + "norm.weight")
         self.layers: list[LayerWeights] = []
         for i, kind in enumerate(c.layer_types):
@@ -142,6 +155,7 @@ class Qwen35Model:
         self._rows: dict[int, dict] = {}
         self._graphs: dict[int, torch.cuda.CUDAGraph] = {}
         self.graph_pool = None
+        self.tp_force = False      # run the push/pull path even with world == 1 (single-GPU test of the protocol)
         self._step_launches: dict[int, int] = {}
 
     def launches_per_step(self, M: int) -> int:
@@ -205,6 +219,8 @@ class Qwen35Model:
                 "slots": torch.empty(rows, dtype=torch.int32, device=dev),
                 "ridx": torch.empty(rows, dtype=torch.int32, device=dev),
             }
+            if self.tp_world > 1:
+                ws["part"] = torch.empty(rows, H, dtype=bf, device=dev)
             if not c.is_moe:
                 ws["gu"] = torch.empty(rows, 2 * c.intermediate_size, dtype=bf, device=dev)
                 ws["inter"] = torch.empty(rows, c.intermediate_size, dtype=bf, device=dev)
@@ -266,24 +282,53 @@ class Qwen35Model:
                             rot=c.rotary_dim, eps=self.eps)
                 K.attn_prefill(q, proj, self.kpool[j], self.vpool[j], block_table, act, q_pos0=pos0,
                                nh=c.num_attention_heads, nkv=c.num_key_value_heads, hd=c.head_dim)
-            K.gemm(act, lw.w_out, out=res, residual=res)
-            K.rmsnorm(res, lw.post_gain, self.eps, out=normed)
+            if self.tp_world > 1:
+                part = self._tp_reduce(K.gemm(act, lw.w_out, out=ws["part"][:T]))
+                K.rmsnorm(res, lw.post_gain, self.eps, out=normed, add=part, res_out=res)
+            else:
+                K.gemm(act, lw.w_out, out=res, residual=res)
+                K.rmsnorm(res, lw.post_gain, self.eps, out=normed)
             if lw.moe is not None:
                 lw.moe.forward_prefill(normed, res, self)
             else:
                 gu = ws["gu"][:T]
                 K.gemm(normed, lw.w_gu, out=gu)
                 inter = K.swiglu(gu, ws["inter"][:T])
-                K.gemm(inter, lw.w_down, out=res, residual=res)
+                if self.tp_world > 1:
+                    part = self._tp_reduce(K.gemm(inter, lw.w_down, out=ws["part"][:T]))
+                    res.add_(part)
+                else:
+                    K.gemm(inter, lw.w_down, out=res, residual=res)
         out_logits = None
         self.last_hidden = None
         if want_hidden:
             self.last_hidden = K.rmsnorm(res, self.final_gain, self.eps)
         if want_logits:
-            out_logits = torch.empty(1, c.vocab_size, dtype=torch.float32, device=self.device)
-            K.gemv(self.lm_head, None, out_logits, norm=(res[T - 1:T].contiguous(), None, self.final_gain, None, self.eps))
-            out_logits = out_logits[0]
+            local = torch.empty(1, self.vocab_local, dtype=torch.float32, device=self.device)
+            K.gemv(self.lm_head, None, local, norm=(res[T - 1:T].contiguous(), None, self.final_gain, None, self.eps))
+            out_logits = self._gather_logits(local, 1)[0]
         return out_logits
+
+    # ------------------------------------------------------------------ tensor-parallel helpers
+    def _tp_reduce(self, t: torch.Tensor) -> torch.Tensor:
+        """Prefill all-reduce of a row-parallel projection output (NCCL; the decode path reduces
+        inside the GEMV kernels instead)."""
+        import torch.distributed as dist
+        dist.all_reduce(t)
+        K._count()
+        return t
+
+    def _gather_logits(self, local: torch.Tensor, M: int) -> torch.Tensor:
+        """``[M, vocab/world]`` per rank -> ``[M, vocab]`` on every rank."""
+        if self.tp_world == 1:
+            return local
+        import torch.distributed as dist
+        buf = torch.empty(self.tp_world, M, self.vocab_local, dtype=local.dtype, device=self.device)
+        dist.all_gather_into_tensor(buf, local.contiguous())
+        K._count()
+        if M == 1:
+            return buf.reshape(1, -1)
+        return buf.permute(1, 0, 2).reshape(M, -1)
 
     # ------------------------------------------------------------------ decode
     def _row_buffers(self, M: int) -> dict:
@@ -306,30 +351,43 @@ class Qwen35Model:
                 "act_full": torch.zeros(M, c.num_attention_heads * c.head_dim, dtype=bf, device=dev),
                 "inter": torch.zeros(M, max(1, c.intermediate_size), dtype=bf, device=dev),
                 "logits": torch.zeros(M, c.vocab_size, dtype=torch.float32, device=dev),
+                "logits_local": None,
                 "next": torch.zeros(M, dtype=torch.int64, device=dev),
                 "hidden": torch.zeros(M, H, dtype=bf, device=dev),
                 "nsplit": nsplit,
                 "part_o": torch.zeros(M, c.num_attention_heads, nsplit, c.head_dim, dtype=torch.float32, device=dev),
                 "part_ml": torch.zeros(M, c.num_attention_heads, nsplit, 2, dtype=torch.float32, device=dev),
+                "tickets": torch.zeros(M, c.num_key_value_heads, dtype=torch.int32, device=dev),
                 # host staging (pinned) so that set_rows is one async copy per array
                 "h_tokens": torch.zeros(M, dtype=torch.int64).pin_memory(),
                 "h_meta": torch.zeros(3, M, dtype=torch.int32).pin_memory(),
                 "h_bt": torch.zeros(M, self.max_blocks_per_seq, dtype=torch.int32).pin_memory(),
             }
+            b["logits_local"] = (b["logits"] if self.tp_world == 1 else
+                                 torch.zeros(M, self.vocab_local, dtype=torch.float32, device=dev))
             self._rows[M] = b
         return b
 
     def _decode_body(self, M: int) -> None:
-        """One decode step for the ``M`` rows staged in the bucket's buffers (graph-capturable)."""
+        """One decode step for the ``M`` rows staged in the bucket's buffers (graph-capturable).
+
+        Tensor parallel: the two row-parallel projections of a layer push their partial sums to all
+        ranks (sites ``2*layer`` and ``2*layer + 1``) and the following projection pulls the sum in
+        its prologue, so the step has no separate all-reduce launches."""
         c, b = self.cfg, self._row_buffers(M)
+        tp = self.tp if self.tp_world > 1 or (self.tp is not None and self.tp_force) else None
         cur, nxt = b["res"]
+        if tp is not None:
+            tp.epoch_bump()
         K.embed_gather(self.embed, b["tokens"], cur)
-        carry = None
+        carry, pull = None, -1
         for li, lw in enumerate(self.layers):
             n_in = lw.w_in.shape[0]
             proj = b["proj"][:, :n_in]
-            K.gemv(lw.w_in, None, proj, norm=(cur, carry, lw.in_gain, nxt if carry is not None else None, self.eps))
-            if carry is not None:
+            have = carry is not None or pull >= 0
+            K.gemv(lw.w_in, None, proj, norm=(cur, carry, lw.in_gain, nxt if have else None, self.eps),
+                   tp=tp, pull_site=pull)
+            if have:
                 cur, nxt = nxt, cur
             if lw.kind == LINEAR:
                 j = self.lin_ids[li]
@@ -342,19 +400,32 @@ class Qwen35Model:
                 j = self.full_ids[li]
                 act = b["act_full"]
                 K.attn_decode(proj, lw.qg, lw.kg, self.cos, self.sin, b["positions"], b["rope_pos"],
-                              b["block_table"], self.kpool[j], self.vpool[j], b["part_o"], b["part_ml"], act,
+                              b["block_table"], self.kpool[j], self.vpool[j], b["part_o"], b["part_ml"], b["tickets"], act,
                               nh=c.num_attention_heads, nkv=c.num_key_value_heads, hd=c.head_dim,
                               rot=c.rotary_dim, nsplit=b["nsplit"], eps=self.eps)
-            K.gemv(lw.w_out, act, b["h"])
+            if tp is not None:
+                K.gemv(lw.w_out, act, None, tp=tp, push_site=2 * li, rows=M)
+            else:
+                K.gemv(lw.w_out, act, b["h"])
             if lw.moe is not None:
                 lw.moe.forward_decode(cur, b["h"], nxt, lw.post_gain, b["h2"], self, M)
                 cur, nxt = nxt, cur
+                carry, pull = b["h2"], -1
+                continue
+            K.gemv(lw.w_gu, None, b["inter"], swiglu=True,
+                   norm=(cur, None if tp is not None else b["h"], lw.post_gain, nxt, self.eps),
+                   tp=tp, pull_site=2 * li if tp is not None else -1)
+            cur, nxt = nxt, cur
+            if tp is not None:
+                K.gemv(lw.w_down, b["inter"], None, tp=tp, push_site=2 * li + 1, rows=M)
+                carry, pull = None, 2 * li + 1
             else:
-                K.gemv(lw.w_gu, None, b["inter"], swiglu=True, norm=(cur, b["h"], lw.post_gain, nxt, self.eps))
-                cur, nxt = nxt, cur
                 K.gemv(lw.w_down, b["inter"], b["h2"])
-            carry = b["h2"]
-        K.gemv(self.lm_head, None, b["logits"], norm=(cur, carry, self.final_gain, nxt, self.eps))
+                carry, pull = b["h2"], -1
+        K.gemv(self.lm_head, None, b["logits_local"], norm=(cur, carry, self.final_gain, nxt, self.eps),
+               tp=tp, pull_site=pull)
+        if self.tp_world > 1:
+            b["logits"].copy_(self._gather_logits(b["logits_local"], M))
         K.argmax(b["logits"], b["next"])
         b["final_res"] = nxt
 

@@ -54,7 +54,7 @@ def _conv(a):
         return ctypes.c_int64(a)
     if isinstance(a, float):
         return ctypes.c_float(a)
-    if isinstance(a, (ctypes.c_void_p, ctypes.c_int64, ctypes.c_float)):
+    if isinstance(a, (ctypes.c_void_p, ctypes.c_int64, ctypes.c_float)) or type(a).__name__ == "CArgObject":
         return a
     raise TypeError(f"cannot pass {type(a)} to a kernel")
 

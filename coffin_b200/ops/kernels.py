@@ -19,7 +19,8 @@ RING = 16           # conv ring depth of the delta-net layers
 
 _status: dict[int, torch.Tensor] = {}
 LAUNCHES = 0        # kernels launched through this module (bench bookkeeping)
-STREAM_GEMV = True   # route single-row projections to the cp.async streaming kernel
+STREAM_GEMV = True   # route single-row projections to the cp.async streaming kernel (when GEMV_IMPL == 'scalar')
+GEMV_IMPL = "mma"     # 'mma': tensor-core GEMV for every M <= 8; 'scalar': FMA kernels
 
 
 def _count(n: int = 1) -> None:
@@ -132,36 +133,42 @@ def block_copy(dst: torch.Tensor, src: torch.Tensor, dst_idx: torch.Tensor, src_
 
 
 # ------------------------------------------------------------------ projections
-def gemv(W: torch.Tensor, x: torch.Tensor | None, out: torch.Tensor, *, swiglu: bool = False,
-         norm: tuple | None = None) -> torch.Tensor:
+def gemv(W: torch.Tensor, x: torch.Tensor | None, out: torch.Tensor | None, *, swiglu: bool = False,
+         norm: tuple | None = None, tp=None, pull_site: int = -1, push_site: int = -1, rows: int | None = None) -> torch.Tensor | None:
     """Decode projection for 1, 2, 4 or 8 rows.
 
     ``W [N, K]`` (``[2I, K]`` gate rows then up rows with ``swiglu``); ``out [M, N]`` bf16 or fp32.
     ``norm = (res_in, add | None, gain, res_out | None, eps)`` replaces ``x`` by
     ``rmsnorm(res_in + add) * gain`` computed inside the kernel; ``res_out`` receives the sum.
+    Tensor parallel (``tp`` = ``parallel.tp.TpComm``): ``push_site >= 0`` sends the fp32 partial
+    outputs to every rank's inbox instead of writing ``out``; ``pull_site >= 0`` takes ``add`` as the
+    sum over ranks of that site's inbox.
     """
-    M = out.shape[0]
+    M = out.shape[0] if out is not None else rows
     K = W.shape[1]
     N = W.shape[0] // 2 if swiglu else W.shape[0]
-    mode = (1 if swiglu else 0) | (2 if out.dtype == torch.float32 else 0)
-    if M == 1 and STREAM_GEMV and K * 2 <= 28 * 1024:
-        # batch-1 decode: weights streamed through per-warp cp.async rings
-        if norm is None:
-            assert x is not None and x.is_contiguous() and x.shape == (1, K)
-            call("gemv_stream_bf16", W, x, out, N, K, mode, N, None, None, None, None, 0.0)
-        else:
-            res_in, add, gain, res_out, eps = norm
-            assert res_in.is_contiguous() and res_in.shape == (1, K)
-            call("gemv_stream_bf16", W, None, out, N, K, mode, N, res_in, add, gain, res_out, float(eps))
-        _count()
-        return out
+    f32 = out is not None and out.dtype == torch.float32
+    mode = (1 if swiglu else 0) | (2 if f32 else 0)
+    ldy = out.stride(0) if out is not None else N
+    tpp = tp.cstruct_ref() if tp is not None and (pull_site >= 0 or push_site >= 0) else None
     if norm is None:
         assert x is not None and x.is_contiguous() and x.shape == (M, K)
-        call("gemv_bf16", W, x, out, M, N, K, out.stride(0), mode, N, None, None, None, None, 0.0)
+        res_in = add = gain = res_out = None
+        eps = 0.0
     else:
         res_in, add, gain, res_out, eps = norm
         assert res_in.is_contiguous() and res_in.shape == (M, K)
-        call("gemv_bf16", W, None, out, M, N, K, out.stride(0), mode, N, res_in, add, gain, res_out, float(eps))
+        x = None
+    if GEMV_IMPL == "mma" and M * K * 2 <= 64 * 1024:
+        call("gemv_mma_bf16", W, x, out, M, N, K, ldy, mode, N, res_in, add, gain, res_out, float(eps), tpp,
+             pull_site, push_site)
+    elif M == 1 and STREAM_GEMV and K * 2 <= 28 * 1024:
+        # batch-1 decode: weights streamed through per-warp cp.async rings
+        call("gemv_stream_bf16", W, x, out, N, K, mode, N, res_in, add, gain, res_out, float(eps), tpp,
+             pull_site, push_site)
+    else:
+        call("gemv_bf16", W, x, out, M, N, K, ldy, mode, N, res_in, add, gain, res_out, float(eps), tpp,
+             pull_site, push_site)
     _count()
     return out
 
@@ -244,13 +251,14 @@ def attn_prefill(q, proj, kpool, vpool, block_table, out, *, q_pos0, nh, nkv, hd
     return out
 
 
-def attn_decode(proj, qg, kg, cos, sin, positions, rope_pos, block_table, kpool, vpool, part_o, part_ml, out, *,
-                nh, nkv, hd, rot, nsplit, eps) -> torch.Tensor:
+def attn_decode(proj, qg, kg, cos, sin, positions, rope_pos, block_table, kpool, vpool, part_o, part_ml, tickets,
+                out, *, nh, nkv, hd, rot, nsplit, eps) -> torch.Tensor:
+    """``tickets``: zero-initialised int32 ``[M, nkv]`` arrival counters (re-armed by the kernel)."""
     M = positions.numel()
     call("attn_decode", proj, proj.stride(0), qg, kg, cos, sin, positions, rope_pos, block_table,
-         block_table.stride(0), kpool, vpool, part_o, part_ml, out, out.stride(0), M, nh, nkv, hd, rot,
+         block_table.stride(0), kpool, vpool, part_o, part_ml, tickets, out, out.stride(0), M, nh, nkv, hd, rot,
          nsplit, float(eps))
-    _count(2)
+    _count()
     return out
 
 

@@ -1,0 +1,196 @@
+"""Tensor parallelism: weight sharding and the peer-memory communicator behind the fused
+GEMV + all-reduce kernels.
+
+Sharding follows the usual column/row split: the fused input projections, gate/up and the lm_head
+are split by output rows (heads, intermediate channels, vocabulary), ``o_proj`` / ``out_proj`` /
+``down_proj`` by input columns, so each layer needs two all-reduces of the hidden vector.  During
+decode those all-reduces are not calls: the row-parallel projection pushes its partial sums into
+every rank's inbox and the next projection's prologue adds them (``_C/tp.cuh``).  Prefill uses the
+tcgen05 GEMM followed by an NCCL all-reduce.  KV heads are replicated when there are fewer of them
+than ranks (reference ``local_config``, ``models/qwen35/parallel.py:670-718``; sharding by key
+suffix ``:734-846``; ``RowParallelProjection`` ``:1015-1061``).
+"""
+from __future__ import annotations
+
+import ctypes
+import dataclasses
+
+import torch
+
+from ..config import LINEAR, ModelConfig
+from ..weights.init import LM
+
+MAX_WORLD = 8
+
+
+# ---------------------------------------------------------------------------------------------
+# sharding
+def local_config(cfg: ModelConfig, world: int) -> ModelConfig:
+    """Per-rank geometry. Raises when a dimension does not divide."""
+    def div(n: int, what: str) -> int:
+        if n % world:
+            raise ValueError(f"{what}={n} is not divisible by tensor-parallel world {world}")
+        return n // world
+    nkv = cfg.num_key_value_heads
+    if nkv >= world:
+        nkv_local = div(nkv, "num_key_value_heads")
+    else:
+        if world % nkv:
+            raise ValueError(f"world {world} must be a multiple of num_key_value_heads {nkv}")
+        nkv_local = 1
+    return dataclasses.replace(
+        cfg, num_attention_heads=div(cfg.num_attention_heads, "num_attention_heads"),
+        num_key_value_heads=nkv_local,
+        linear_num_key_heads=div(cfg.linear_num_key_heads, "linear_num_key_heads"),
+        linear_num_value_heads=div(cfg.linear_num_value_heads, "linear_num_value_heads"),
+        intermediate_size=div(cfg.intermediate_size, "intermediate_size") if cfg.intermediate_size else 0,
+        name=f"{cfg.name}-tp{world}")
+
+
+def _rows(t: torch.Tensor, rank: int, world: int, unit: int = 1) -> torch.Tensor:
+    n = t.shape[0] // unit
+    per = n // world
+    return t[rank * per * unit:(rank + 1) * per * unit]
+
+
+def shard_state_dict(cfg: ModelConfig, sd: dict[str, torch.Tensor], rank: int, world: int) -> dict[str, torch.Tensor]:
+    """The slice of a full state dict that rank ``rank`` of ``world`` computes with.
+    Tensors that every rank needs whole (norms, embedding, router) are shared, not copied."""
+    lc = local_config(cfg, world)
+    out: dict[str, torch.Tensor] = {}
+    nk, nv, dk, dv = cfg.linear_num_key_heads, cfg.linear_num_value_heads, cfg.linear_key_head_dim, cfg.linear_value_head_dim
+    kdim = nk * dk
+    nh, nkv, hd = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
+    for key, t in sd.items():
+        if not key.startswith(LM + "layers."):
+            out[key] = t
+            continue
+        name = key.split(".", 4)[-1]            # e.g. linear_attn.in_proj_qkv.weight
+        if name in ("linear_attn.in_proj_qkv.weight", "linear_attn.conv1d.weight"):
+            q, k, v = t[:kdim], t[kdim:2 * kdim], t[2 * kdim:]
+            out[key] = torch.cat([_rows(q, rank, world, dk), _rows(k, rank, world, dk), _rows(v, rank, world, dv)])
+        elif name == "linear_attn.in_proj_z.weight":
+            out[key] = _rows(t, rank, world, dv)
+        elif name in ("linear_attn.in_proj_b.weight", "linear_attn.in_proj_a.weight", "linear_attn.A_log",
+                      "linear_attn.dt_bias"):
+            out[key] = _rows(t, rank, world)
+        elif name == "linear_attn.out_proj.weight":
+            out[key] = _rows(t.t(), rank, world, dv).t().contiguous()
+        elif name == "self_attn.q_proj.weight":
+            out[key] = _rows(t, rank, world, 2 * hd)
+        elif name in ("self_attn.k_proj.weight", "self_attn.v_proj.weight"):
+            if nkv >= world:
+                out[key] = _rows(t, rank, world, hd)
+            else:
+                h = rank * nkv // world          # the kv head this rank's query heads attend with
+                out[key] = t[h * hd:(h + 1) * hd]
+        elif name == "self_attn.o_proj.weight":
+            out[key] = _rows(t.t(), rank, world, hd).t().contiguous()
+        elif name in ("mlp.gate_proj.weight", "mlp.up_proj.weight"):
+            out[key] = _rows(t, rank, world)
+        elif name == "mlp.down_proj.weight":
+            out[key] = _rows(t.t(), rank, world).t().contiguous()
+        else:
+            out[key] = t
+    assert lc.hidden_size == cfg.hidden_size
+    return out
+
+
+# ---------------------------------------------------------------------------------------------
+# communicator
+class _TpCommStruct(ctypes.Structure):
+    _fields_ = [("rank", ctypes.c_int), ("world", ctypes.c_int), ("slot_floats", ctypes.c_int64),
+                ("inbox", ctypes.c_void_p * MAX_WORLD), ("flags", ctypes.c_void_p * MAX_WORLD),
+                ("arrive", ctypes.c_void_p), ("epoch", ctypes.c_void_p), ("status", ctypes.c_void_p)]
+
+
+class TpComm:
+    """Peer-mapped inbox/flag buffers of one tensor-parallel group on one node.
+
+    One device allocation per rank holds ``[sites][world][max_rows * hidden]`` fp32 inbox slots,
+    ``[sites][world]`` flags, ``[sites]`` producer arrival counters, the step epoch and a status
+    word.  ``exchange`` is a callable that all-gathers a bytes object over the control plane (CPU
+    process group); with ``world == 1`` nothing is exchanged, which is how the push/pull path is
+    tested on a single GPU.
+    """
+
+    def __init__(self, rank: int, world: int, hidden: int, max_rows: int, n_sites: int, exchange=None) -> None:
+        from ..ops import _lib
+        if world > MAX_WORLD:
+            raise ValueError(f"tensor-parallel world {world} > {MAX_WORLD}")
+        self.rank, self.world, self.n_sites = rank, world, n_sites
+        self.slot_floats = max_rows * hidden
+        inbox_b = n_sites * world * self.slot_floats * 4
+        flags_b = n_sites * world * 4
+        self._off_flags = (inbox_b + 255) // 256 * 256
+        self._off_arrive = self._off_flags + (flags_b + 255) // 256 * 256
+        self._off_epoch = self._off_arrive + (n_sites * 4 + 255) // 256 * 256
+        self._off_status = self._off_epoch + 256
+        self.nbytes = self._off_status + 256
+        self._lib = _lib.lib()
+        base = ctypes.c_void_p()
+        rc = self._lib.cb_peer_alloc(ctypes.c_int64(self.nbytes), ctypes.byref(base))
+        if rc:
+            raise _lib.KernelError(f"cb_peer_alloc failed ({rc})")
+        self.base = base.value
+        self.peers = [None] * world
+        self.peers[rank] = self.base
+        self._opened: list[int] = []
+        if world > 1:
+            handle = ctypes.create_string_buffer(64)
+            rc = self._lib.cb_ipc_get_handle(ctypes.c_void_p(self.base), handle)
+            if rc:
+                raise _lib.KernelError(f"cudaIpcGetMemHandle failed ({rc})")
+            handles = exchange(bytes(handle.raw))
+            for r, h in enumerate(handles):
+                if r == rank:
+                    continue
+                p = ctypes.c_void_p()
+                rc = self._lib.cb_ipc_open_handle(ctypes.create_string_buffer(h, 64), ctypes.byref(p))
+                if rc:
+                    raise _lib.KernelError(f"cudaIpcOpenMemHandle of rank {r} failed ({rc})")
+                self.peers[r] = p.value
+                self._opened.append(p.value)
+        s = _TpCommStruct()
+        s.rank, s.world, s.slot_floats = rank, world, self.slot_floats
+        for r in range(world):
+            s.inbox[r] = self.peers[r]
+            s.flags[r] = self.peers[r] + self._off_flags
+        s.arrive = self.base + self._off_arrive
+        s.epoch = self.base + self._off_epoch
+        s.status = self.base + self._off_status
+        self._struct = s
+
+    def cstruct_ref(self):
+        return ctypes.byref(self._struct)
+
+    def epoch_bump(self) -> None:
+        from ..ops import kernels as K
+        K.call("tp_epoch_bump", ctypes.c_void_p(self.base + self._off_epoch))
+        K._count()
+
+    def status(self) -> int:
+        """Non-zero when a device-side wait ran out (16 + the rank that never arrived)."""
+        v = ctypes.c_int(0)
+        self._lib.cb_peer_read_i32(ctypes.c_void_p(self.base + self._off_status), ctypes.byref(v))
+        return int(v.value)
+
+    def close(self) -> None:
+        for p in self._opened:
+            self._lib.cb_ipc_close_handle(ctypes.c_void_p(p))
+        self._opened = []
+        if self.base:
+            self._lib.cb_peer_free(ctypes.c_void_p(self.base))
+            self.base = 0
+
+
+def make_exchange(group=None):
+    """All-gather of a bytes object over ``torch.distributed`` (any backend with object
+    collectives; the control plane uses gloo)."""
+    import torch.distributed as dist
+
+    def exchange(blob: bytes) -> list[bytes]:
+        out = [None] * dist.get_world_size(group)
+        dist.all_gather_object(out, blob, group=group)
+        return out
+    return exchange

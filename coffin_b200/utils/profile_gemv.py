@@ -18,7 +18,7 @@ def main() -> None:
     ap.add_argument("--n", type=int, default=151936)
     ap.add_argument("--k", type=int, default=2560)
     ap.add_argument("--rows", type=int, default=1)
-    ap.add_argument("--variant", default="stream", choices=["stream", "reg"])
+    ap.add_argument("--variant", default="mma", choices=["mma", "stream", "reg"])
     ap.add_argument("--swiglu", action="store_true")
     ap.add_argument("--norm", action="store_true")
     ap.add_argument("--iters", type=int, default=5)
@@ -26,6 +26,7 @@ def main() -> None:
     ap.add_argument("--no-flush", action="store_true")
     args = ap.parse_args()
     from ..ops import kernels as K
+    K.GEMV_IMPL = "mma" if args.variant == "mma" else "scalar"
     K.STREAM_GEMV = args.variant == "stream"
     dev = "cuda"
     rows = args.n * (2 if args.swiglu else 1)

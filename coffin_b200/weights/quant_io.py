@@ -1,0 +1,184 @@
+"""Reader and writer of pre-quantised checkpoint directories (``quant_index.json``).
+
+Two formats, byte-compatible with the reference's tools:
+
+* ``coffin-int8-kn-v1``: tensor ``key`` int8 ``[K, N]`` + ``key#scale`` fp32 ``[N]``; routed
+  experts as stacks ``...experts.gate_up_stack`` / ``down_stack`` int8 ``[E, K, N]`` with
+  ``#scale [E, N]`` and an ``#nk`` copy ``[E, N, K]``; shards ``quant-%05d-of-%05d.safetensors``.
+* ``coffin-w4a8-kn-v1``: ``key`` uint8 ``[ceil(K/2), N]`` + ``key#scale`` fp32 ``[ceil(K/128), N]``
+  (kind ``q4``; experts ``q4-moe`` ``[E, ceil(K/2), N]``); shards ``quant-w4a8-...``.
+
+The index records per tensor its kind (``q8 | q8-moe | q4 | q4-moe | dense``), ``k``, ``n``, shape,
+``scale_key``, ``nk_key`` and shard, plus the sha256 of the source ``config.json`` which the reader
+checks.  Reference: ``quantized_load.py:46-51,190-454``, ``tools/quant_disk.py:147-177,229-383,533-554``,
+``tools/quant_disk_w4a8.py:45-89,241-281``.
+"""
+from __future__ import annotations
+
+import hashlib
+import json
+from pathlib import Path
+
+import torch
+
+from .quant import GROUP, QWeight, W4A8Weight, is_quantizable
+
+INDEX_NAME = "quant_index.json"
+FORMAT = "coffin-int8-kn-v1"
+W4A8_FORMAT = "coffin-w4a8-kn-v1"
+DENSE_SUFFIXES = ("mlp.gate.weight", "shared_expert_gate.weight")
+
+
+def is_quantized_dir(model_dir: str | Path) -> bool:
+    return (Path(model_dir) / INDEX_NAME).is_file()
+
+
+def read_index(model_dir: str | Path) -> dict:
+    idx = json.loads((Path(model_dir) / INDEX_NAME).read_text())
+    if idx.get("format") not in (FORMAT, W4A8_FORMAT):
+        raise ValueError(f"{model_dir}: unknown quantised format {idx.get('format')!r}")
+    return idx
+
+
+def config_digest(model_dir: str | Path) -> str:
+    return hashlib.sha256((Path(model_dir) / "config.json").read_bytes()).hexdigest()
+
+
+def _disk_key(key: str) -> str:
+    if key.endswith("experts.gate_up_proj"):
+        return key[:-len("gate_up_proj")] + "gate_up_stack"
+    if key.endswith("experts.down_proj"):
+        return key[:-len("down_proj")] + "down_stack"
+    return key
+
+
+def _mem_key(key: str) -> str:
+    if key.endswith("experts.gate_up_stack"):
+        return key[:-len("gate_up_stack")] + "gate_up_proj"
+    if key.endswith("experts.down_stack"):
+        return key[:-len("down_stack")] + "down_proj"
+    return key
+
+
+def write_quantized(model_dir: str | Path, sd: dict[str, torch.Tensor], out_dir: str | Path, scheme: str = "int8",
+                    shard_bytes: int = 4 << 30, weight_dtype: str = "bfloat16") -> dict:
+    """Quantise ``sd`` (dense, HF key layout) and write a pre-quantised directory next to a copy
+    of ``config.json`` from ``model_dir``."""
+    from safetensors.torch import save_file
+    src, out = Path(model_dir), Path(out_dir)
+    out.mkdir(parents=True, exist_ok=True)
+    (out / "config.json").write_bytes((src / "config.json").read_bytes())
+    w4 = scheme == "w4a8"
+    tensors: dict[str, dict] = {}
+    shards: list[dict[str, torch.Tensor]] = [{}]
+    size = 0
+
+    def put(name: str, t: torch.Tensor) -> int:
+        nonlocal size
+        nb = t.numel() * t.element_size()
+        if size and size + nb > shard_bytes:
+            shards.append({})
+            size = 0
+        shards[-1][name] = t.contiguous().cpu()
+        size += nb
+        return len(shards) - 1
+
+    kinds: dict[str, int] = {}
+    for key, t in sd.items():
+        dk = _disk_key(key)
+        moe = t.dim() == 3
+        if is_quantizable(key, t) and not key.endswith(DENSE_SUFFIXES):
+            if w4:
+                q = W4A8Weight.quantize(t)
+                kind = "q4-moe" if moe else "q4"
+                si = put(dk, q.packed)
+                put(dk + "#scale", q.scale)
+                meta = {"kind": kind, "k": q.k, "n": q.n, "shape": list(q.packed.shape), "scale_key": dk + "#scale",
+                        "group_size": GROUP, "shard": si}
+            else:
+                q = QWeight.quantize(t)
+                kn, sc = q.to_kn()
+                kind = "q8-moe" if moe else "q8"
+                si = put(dk, kn)
+                put(dk + "#scale", sc)
+                meta = {"kind": kind, "k": q.k, "n": q.n, "shape": list(kn.shape), "scale_key": dk + "#scale", "shard": si}
+                if moe:
+                    put(dk + "#nk", q.wq)
+                    meta["nk_key"] = dk + "#nk"
+        else:
+            kind = "dense"
+            si = put(dk, t)
+            meta = {"kind": "dense", "shape": list(t.shape), "shard": si}
+        kinds[kind] = kinds.get(kind, 0) + 1
+        tensors[dk] = meta
+    pat = "quant-w4a8-%05d-of-%05d.safetensors" if w4 else "quant-%05d-of-%05d.safetensors"
+    files = []
+    for i, shard in enumerate(shards):
+        name = pat % (i + 1, len(shards))
+        save_file(shard, str(out / name))
+        files.append(name)
+    for meta in tensors.values():
+        meta["shard"] = files[meta["shard"]]
+    index = {"format": W4A8_FORMAT if w4 else FORMAT, "generated_by": "coffin_b200/tools/quant_disk.py",
+             "source": str(src), "source_config_sha256": config_digest(src), "weight_dtype": weight_dtype,
+             "act_dtype": "bfloat16",
+             "scheme": ("group-128 symmetric int4: s = max|w|/7, round, clamp [-8, 7], code = q + 8, low nibble = even k"
+                        if w4 else "per-output-column symmetric absmax: s = max|w|/127, round, clamp [-127, 127]; s floored at 1e-8"),
+             "layout": "uint8 [ceil(K/2), N] + fp32 [ceil(K/128), N]" if w4 else "int8 [K, N] contiguous + fp32 [N]",
+             "prefixes": ["model.language_model.", "mtp.", "lm_head."], "vision": any(k.startswith("model.visual.") for k in sd),
+             "files": files, "kinds": dict(sorted(kinds.items())),
+             "totals": {"tensors": len(tensors), "bytes": sum((out / f).stat().st_size for f in files)},
+             "tensors": tensors}
+    (out / INDEX_NAME).write_text(json.dumps(index, indent=1))
+    return index
+
+
+def load_quantized(model_dir: str | Path, device: str = "cpu", quant: bool = True,
+                   dense_dtype: torch.dtype = torch.bfloat16, check_config: bool = True) -> dict:
+    """State dict (canonical keys) of a pre-quantised directory: projections as ``QWeight`` /
+    ``W4A8Weight`` (or dequantised when ``quant`` is false), the rest dense."""
+    from safetensors import safe_open
+    model_dir = Path(model_dir)
+    index = read_index(model_dir)
+    if check_config and (model_dir / "config.json").is_file():
+        if config_digest(model_dir) != index.get("source_config_sha256"):
+            raise ValueError(f"{model_dir}: config.json does not match the one the weights were quantised from")
+    entries = index["tensors"]
+    sd: dict = {}
+    handles: dict[str, object] = {}
+
+    def get(shard: str, name: str) -> torch.Tensor:
+        path = model_dir / shard
+        if not path.is_file():
+            raise FileNotFoundError(f"{model_dir}: index names {shard}, which is missing")
+        h = handles.get(shard)
+        if h is None:
+            h = handles[shard] = safe_open(str(path), framework="pt", device=device)
+        if name not in h.keys():
+            raise ValueError(f"{path}: index names {name}, shard does not hold it")
+        return h.get_tensor(name)
+
+    for dk, meta in entries.items():
+        key, kind, shard = _mem_key(dk), meta["kind"], meta["shard"]
+        if kind == "dense":
+            sd[key] = get(shard, dk)
+        elif kind in ("q8", "q8-moe"):
+            kn, sc = get(shard, dk), get(shard, meta["scale_key"])
+            if kn.dtype != torch.int8 or list(kn.shape[-2:]) != [meta["k"], meta["n"]] or sc.shape[-1] != meta["n"]:
+                raise ValueError(f"{dk}: tensor does not match its index entry")
+            q = QWeight(get(shard, meta["nk_key"]), sc) if meta.get("nk_key") else QWeight.from_kn(kn, sc)
+            sd[key] = q if quant else q.dequant(dense_dtype)
+        elif kind in ("q4", "q4-moe"):
+            pk, sc = get(shard, dk), get(shard, meta["scale_key"])
+            if pk.dtype != torch.uint8 or pk.shape[-1] != meta["n"] or pk.shape[-2] != (meta["k"] + 1) // 2:
+                raise ValueError(f"{dk}: tensor does not match its index entry")
+            q = W4A8Weight(pk, sc, meta["k"], meta.get("group_size", GROUP))
+            sd[key] = q if quant else q.dequant(dense_dtype)
+        else:
+            raise ValueError(f"{dk}: unknown kind {kind!r}")
+    return sd
+
+
+def summary(model_dir: str | Path) -> dict:
+    idx = read_index(model_dir)
+    return {"format": idx["format"], "kinds": idx["kinds"], "files": len(idx["files"]), "totals": idx["totals"]}

@@ -258,13 +258,14 @@ def test_attention_prefill_and_decode(nh, nkv, hd, rot, T1, T2):
     nsplit = 3
     part_o = torch.empty(2, nh, nsplit, hd, device=DEV)
     part_ml = torch.empty(2, nh, nsplit, 2, device=DEV)
+    tickets = torch.zeros(2, nkv, dtype=torch.int32, device=DEV)
     btab = torch.zeros(2, nblk, dtype=torch.int32)
     btab[0] = bt
     for p in range(T1 + T2, T):
         posv = torch.tensor([p, -1], dtype=torch.int32, device=DEV)
         o2 = torch.empty(2, nh * hd, dtype=torch.bfloat16, device=DEV)
         pr = torch.cat([pj[p:p + 1], pj[p:p + 1]])
-        k.attn_decode(pr, d(qg), d(kg), dc, ds, posv, posv.clamp_min(0), d(btab), kpool, vpool, part_o, part_ml, o2,
+        k.attn_decode(pr, d(qg), d(kg), dc, ds, posv, posv.clamp_min(0), d(btab), kpool, vpool, part_o, part_ml, tickets, o2,
                       nh=nh, nkv=nkv, hd=hd, rot=rot, nsplit=nsplit, eps=1e-6)
         out[p] = o2[0]
     close(out, ref, 3e-2)
