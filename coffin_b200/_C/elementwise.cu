@@ -154,6 +154,24 @@ __global__ void __launch_bounds__(256) argmax_kernel(const float* __restrict__ l
   argmax_body(logits, out, V, ld, scratch);
 }
 
+// ---- allocation-free argmax ---------------------------------------------------------------------
+// Same two-stage reduction, but the partials and tickets live in a file-scope device array that the
+// library carries itself, so the caller provides nothing but its logits and the output.  The array
+// is sized for kArgmaxStaticRows rows (about 50 KB per GPU that loads the library, held until the
+// process exits).  Device code names the array directly; host code must not pass the symbol itself
+// to a kernel (on the host it is only a stand-in), it asks the runtime for the device address once
+// per device (cb_argmax_static below).
+constexpr int kArgmaxStaticRows = 64;
+static __device__ __align__(256) ArgmaxScratch g_argmax_static[kArgmaxStaticRows];
+
+__global__ void __launch_bounds__(256) argmax_static_kernel(const float* __restrict__ logits,
+                                                             int64_t* __restrict__ out, int64_t V, int64_t ld,
+                                                             ArgmaxScratch* scratch) {
+  griddep_launch();
+  griddep_wait();
+  argmax_body(logits, out, V, ld, scratch);
+}
+
 // Temperature sampling by inverse CDF: p = softmax(logits / T); token = first i with cdf(i) > u.
 // One CTA per row; u[row] is a uniform random number supplied by the host (so that every
 // tensor-parallel rank draws the same token from the same logits).
@@ -262,6 +280,36 @@ CB_EXPORT int cb_argmax(const void* logits, void* out, int64_t M, int64_t V, int
   return (int)cb_launch(argmax_kernel, dim3(kArgmaxParts, (unsigned)M), dim3(256), 0, (cudaStream_t)stream,
                         (const float*)logits, (int64_t*)out, V, ld, (ArgmaxScratch*)scratch);
 }
+
+// See no_alloc.h. Allocation-free variant of cb_argmax: no cudaMalloc / cudaFree / library
+// allocation on any call.  The first call on a device looks up the device address of the static
+// scratch and clears its tickets (with that device current); make that first call outside any
+// stream capture.
+static ArgmaxScratch* g_argmax_static_ptr[64] = {};
+
+CB_EXPORT int cb_argmax_static(const void* logits, void* out, int64_t M, int64_t V, int64_t ld, void* stream) {
+  if (M == 0) return 0;
+  if (!logits || !out || V < 1) return CB_ERR_ARG;
+  if (M < 0 || M > kArgmaxStaticRows) return CB_ERR_SHAPE;   // beyond the built-in scratch: use cb_argmax
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= 64) return CB_ERR_ARG;
+  if (!g_argmax_static_ptr[dev]) {
+    ArgmaxScratch* p = nullptr;
+    e = cudaGetSymbolAddress((void**)&p, g_argmax_static);
+    if (e != cudaSuccess) return (int)e;
+    if (!p) return CB_ERR_DRIVER;
+    // tickets must start at zero; the kernel re-arms them itself after every launch
+    e = cudaMemsetAsync(p, 0, sizeof(ArgmaxScratch) * kArgmaxStaticRows, (cudaStream_t)stream);
+    if (e != cudaSuccess) return (int)e;
+    g_argmax_static_ptr[dev] = p;
+  }
+  return (int)cb_launch(argmax_static_kernel, dim3(kArgmaxParts, (unsigned)M), dim3(256), 0, (cudaStream_t)stream,
+                        (const float*)logits, (int64_t*)out, V, ld, g_argmax_static_ptr[dev]);
+}
+
+CB_EXPORT int64_t cb_argmax_static_max_rows() { return kArgmaxStaticRows; }
 
 CB_EXPORT int cb_sample(const void* logits, const void* temperature, const void* u, void* out, int64_t M,
                         int64_t V, int64_t ld, void* stream) {
