@@ -27,6 +27,9 @@ struct MmaArgs {
   int ksplit;         // k-slices per 16-row block (a power of two <= 8)
   int rounds;         // rounds of the grid-wide sweep
   int pull_site, push_site;
+  // grouped (mixture-of-experts) mode: blockIdx.y is a slot; slot s multiplies activation row
+  // slot_xrow[s] by the weights of expert slot_expert[s] and writes output row s.  M must be 1.
+  const int* slot_expert; const int* slot_xrow; int64_t expert_stride;
   TpComm tp;
 };
 
@@ -38,10 +41,21 @@ __device__ __forceinline__ void mma16816(float* c, uint32_t a0, uint32_t a1, uin
 }
 
 template <bool SWIGLU, bool NORM, bool OUT_F32>
-__global__ void __launch_bounds__(kT, 3) gemv_mma_kernel(const MmaArgs a) {
+__global__ void __launch_bounds__(kT, 3) gemv_mma_kernel(const MmaArgs a_in) {
   constexpr int PB = SWIGLU ? 2 : 1;   // physical 16-row blocks per unit (gate, up)
   constexpr int U = SWIGLU ? 2 : kU;   // same number of loads in flight either way
   extern __shared__ __align__(16) unsigned char smem_raw[];
+  MmaArgs a = a_in;
+  if (a.slot_expert) {
+    // the routing tables come from the kernels just before this one: wait before reading them
+    // (the second wait below is then a no-op)
+    griddep_wait();
+    const int slot = blockIdx.y;
+    a.W += (int64_t)a.slot_expert[slot] * a.expert_stride;
+    a.x += (int64_t)(a.slot_xrow ? a.slot_xrow[slot] : slot) * a.K;
+    a.y = OUT_F32 ? (void*)(reinterpret_cast<float*>(a.y) + (int64_t)slot * a.ldy)
+                  : (void*)(reinterpret_cast<bf16*>(a.y) + (int64_t)slot * a.ldy);
+  }
   const int64_t K = a.K, nchunk = K >> 3;
   const int M = a.M;
   bf16* xs = reinterpret_cast<bf16*>(smem_raw);                                  // [M][K]
@@ -215,7 +229,7 @@ int g_mma_sms = 0;
 int g_mma_ctas = 3;
 
 template <bool SWIGLU, bool NORM, bool OUT_F32>
-int launch_mma(MmaArgs a, cudaStream_t st) {
+int launch_mma(MmaArgs a, cudaStream_t st, int n_slots = 1) {
   if (!g_mma_sms) {
     int dev = 0;
     cudaGetDevice(&dev);
@@ -224,7 +238,7 @@ int launch_mma(MmaArgs a, cudaStream_t st) {
   }
   constexpr int PB = SWIGLU ? 2 : 1;
   const int64_t nblk = (a.N + 15) / 16;
-  const int64_t slots = (int64_t)g_mma_sms * g_mma_ctas;
+  const int64_t slots = max((int64_t)1, (int64_t)g_mma_sms * g_mma_ctas / n_slots);
   const int64_t npair = ((a.K >> 3) + 3) >> 2;
   // split K across warps until the grid fills the resident CTA slots (or slices get too short)
   int ks = 1;
@@ -242,7 +256,7 @@ int launch_mma(MmaArgs a, cudaStream_t st) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
   }
-  return (int)cb_launch(kern, dim3((unsigned)grid), dim3(kT), smem, st, a);
+  return (int)cb_launch(kern, dim3((unsigned)grid, (unsigned)n_slots), dim3(kT), smem, st, a);
 }
 
 }  // namespace
@@ -264,6 +278,7 @@ CB_EXPORT int cb_gemv_mma_bf16(const void* W, const void* x, void* y, int64_t M,
   a.res_in = (const bf16*)res_in; a.add = (const bf16*)add; a.gain = (const float*)gain;
   a.res_out = (bf16*)res_out; a.eps = eps; a.M = (int)M; a.ksplit = 1; a.rounds = 1;
   a.pull_site = (int)pull_site; a.push_site = (int)push_site;
+  a.slot_expert = nullptr; a.slot_xrow = nullptr; a.expert_stride = 0;
   if (tp) a.tp = *(const TpComm*)tp; else memset(&a.tp, 0, sizeof(a.tp));
   const bool sw = mode & 1, f32 = mode & 2, norm = res_in != nullptr;
   cudaStream_t st = (cudaStream_t)stream;
@@ -273,4 +288,23 @@ CB_EXPORT int cb_gemv_mma_bf16(const void* W, const void* x, void* y, int64_t M,
   }
   if (f32) return norm ? launch_mma<false, true, true>(a, st) : launch_mma<false, false, true>(a, st);
   return norm ? launch_mma<false, true, false>(a, st) : launch_mma<false, false, false>(a, st);
+}
+
+// Grouped expert projection for decode: for every slot s (a routed (token, expert) pair),
+// y[s, :] = W[slot_expert[s]] x[slot_xrow[s], :]   (W: [E, N(or 2N), K] stacked experts).
+// mode bit 1 = SwiGLU epilogue (gate rows then up rows inside each expert).
+CB_EXPORT int cb_moe_gemv(const void* W, const void* x, void* y, int64_t n_slots, int64_t N, int64_t K, int64_t ldy,
+                          int64_t mode, const void* slot_expert, const void* slot_xrow, int64_t expert_stride,
+                          void* stream) {
+  if (!W || !x || !y || !slot_expert) return CB_ERR_ARG;
+  if (K % 8 || N < 1 || n_slots < 1 || n_slots > 65535) return CB_ERR_SHAPE;
+  MmaArgs a;
+  a.W = (const bf16*)W; a.x = (const bf16*)x; a.y = y; a.N = N; a.K = K; a.ldy = ldy; a.up_off = N;
+  a.res_in = nullptr; a.add = nullptr; a.gain = nullptr; a.res_out = nullptr; a.eps = 0.f; a.M = 1; a.ksplit = 1;
+  a.rounds = 1; a.pull_site = -1; a.push_site = -1;
+  a.slot_expert = (const int*)slot_expert; a.slot_xrow = (const int*)slot_xrow; a.expert_stride = expert_stride;
+  memset(&a.tp, 0, sizeof(a.tp));
+  cudaStream_t st = (cudaStream_t)stream;
+  if (mode & 1) return launch_mma<true, false, false>(a, st, (int)n_slots);
+  return launch_mma<false, false, false>(a, st, (int)n_slots);
 }

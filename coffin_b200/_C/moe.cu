@@ -1,0 +1,111 @@
+// Routed mixture-of-experts glue kernels: router (fp32 softmax, top-k, renormalise) and the
+// weighted combine of expert outputs with the shared expert.  The expert projections themselves
+// run on the grouped tensor-core GEMV (decode, gemv_mma.cu slot mode) or the tcgen05 GEMM (prefill).
+// Reference: moe_router_t (backends/corex/kernels/moe_grouped.cu:725-879), the merge kernels
+// (moe_grouped_i8.cu:546-640) and shared_gate_scale (moe_epilogue.cu:35-95).
+#include "common.cuh"
+
+namespace {
+
+constexpr int kMaxTopK = 32;
+
+// One warp per token. logits [T, ldl] fp32 (first E columns are expert logits).
+__global__ void __launch_bounds__(256) moe_router_kernel(const float* __restrict__ logits, int64_t ldl, int E, int top_k,
+                                                          int normalize, int* __restrict__ out_idx,
+                                                          float* __restrict__ out_w, int T) {
+  griddep_launch();
+  griddep_wait();
+  const int lane = threadIdx.x & 31;
+  const int64_t tok = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (tok >= T) return;
+  const float* row = logits + tok * ldl;
+  constexpr int PER = 16;                       // up to 512 experts
+  float v[PER];
+  float mx = -INFINITY;
+#pragma unroll
+  for (int i = 0; i < PER; ++i) {
+    const int e = lane + 32 * i;
+    v[i] = e < E ? row[e] : -INFINITY;
+    mx = fmaxf(mx, v[i]);
+  }
+  mx = warp_max(mx);
+  float sum = 0.f;
+#pragma unroll
+  for (int i = 0; i < PER; ++i) {
+    v[i] = (lane + 32 * i) < E ? __expf(v[i] - mx) : -1.f;   // probabilities (unnormalised); -1 = taken/invalid
+    if (v[i] > 0.f) sum += v[i];
+  }
+  sum = warp_sum(sum);
+  float wsum = 0.f, myw = 0.f;
+  int myidx = 0;
+  for (int k = 0; k < top_k; ++k) {
+    float best = -1.f;
+    int bi = 0x7fffffff;
+#pragma unroll
+    for (int i = 0; i < PER; ++i) {
+      const int e = lane + 32 * i;
+      if (v[i] > best) { best = v[i]; bi = e; }          // ascending e per lane: ties keep the lowest index
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ob > best || (ob == best && oi < bi)) { best = ob; bi = oi; }
+    }
+    // the owner lane removes the winner (compare-select keeps v[] in registers)
+#pragma unroll
+    for (int i = 0; i < PER; ++i) if ((bi & 31) == lane && i == (bi >> 5)) v[i] = -1.f;
+    const float p = best / sum;
+    wsum += p;
+    if (lane == k) { myw = p; myidx = bi; }
+  }
+  if (lane < top_k) {
+    out_idx[tok * top_k + lane] = myidx;
+    out_w[tok * top_k + lane] = normalize ? myw / wsum : myw;
+  }
+}
+
+// out[t, :] = sum_j w[t, j] * y[t * top_k + j, :]  (+ sigmoid(gate_logit[t]) * shared[t, :])
+__global__ void __launch_bounds__(256) moe_combine_kernel(const bf16* __restrict__ y, const float* __restrict__ w,
+                                                           const bf16* __restrict__ shared, const float* __restrict__ gate_logit,
+                                                           int64_t ldg, bf16* __restrict__ out, int64_t H, int top_k) {
+  griddep_launch();
+  griddep_wait();
+  const int64_t t = blockIdx.x;
+  const float sg = shared ? sigmoid_f(gate_logit[t * ldg]) : 0.f;
+  for (int64_t c = threadIdx.x; c < (H >> 3); c += blockDim.x) {
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int j = 0; j < top_k; ++j) {
+      float f[8];
+      bf16x8_to_float(*reinterpret_cast<const uint4*>(y + ((t * top_k + j) * H) + c * 8), f);
+      const float wj = w[t * top_k + j];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[i] = fmaf(wj, f[i], acc[i]);
+    }
+    if (shared) {
+      float f[8];
+      bf16x8_to_float(*reinterpret_cast<const uint4*>(shared + t * H + c * 8), f);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[i] = fmaf(sg, f[i], acc[i]);
+    }
+    *reinterpret_cast<uint4*>(out + t * H + c * 8) = float_to_bf16x8(acc);
+  }
+}
+
+}  // namespace
+
+CB_EXPORT int cb_moe_router(const void* logits, int64_t ldl, int64_t T, int64_t E, int64_t top_k, int64_t normalize,
+                            void* out_idx, void* out_w, void* stream) {
+  if (T == 0) return 0;
+  if (E > 512 || top_k > kMaxTopK || top_k < 1 || top_k > E) return CB_ERR_SHAPE;
+  return (int)cb_launch(moe_router_kernel, dim3((unsigned)((T + 7) / 8)), dim3(256), 0, (cudaStream_t)stream,
+                        (const float*)logits, ldl, (int)E, (int)top_k, (int)normalize, (int*)out_idx, (float*)out_w, (int)T);
+}
+
+CB_EXPORT int cb_moe_combine(const void* y, const void* w, const void* shared, const void* gate_logit, int64_t ldg,
+                             void* out, int64_t T, int64_t H, int64_t top_k, void* stream) {
+  if (T == 0) return 0;
+  if (H % 8) return CB_ERR_SHAPE;
+  return (int)cb_launch(moe_combine_kernel, dim3((unsigned)T), dim3(256), 0, (cudaStream_t)stream, (const bf16*)y,
+                        (const float*)w, (const bf16*)shared, (const float*)gate_logit, ldg, (bf16*)out, H, (int)top_k);
+}

@@ -1,0 +1,163 @@
+"""Routed mixture-of-experts FFN (top-k softmax routing + one shared expert with a sigmoid gate).
+
+Decode: router logits (one GEMV whose last row is the shared-expert gate vector), a router kernel
+(fp32 softmax, top-k, renormalise), two grouped tensor-core GEMVs over the selected experts
+(gate/up with fused SwiGLU, then down), the shared expert's two GEMVs and one combine kernel -
+8 launches, all graph-capturable, no host round trip.  Prefill sorts the (token, expert) slots by
+expert and runs the experts' tcgen05 GEMMs over their row segments.
+Reference: ``models/qwen35/moe.py:508-559`` (route, shared expert), ``:561-730`` (dispatch,
+grouped projections, merge), kernels ``backends/corex/kernels/moe_grouped*.cu``, ``moe_dispatch.cu``.
+"""
+from __future__ import annotations
+
+import dataclasses
+
+import torch
+
+from ...config import ModelConfig
+from ...ops import kernels as K
+
+
+def _pad8(n: int) -> int:
+    return (n + 7) // 8 * 8
+
+
+@dataclasses.dataclass
+class MoEWeights:
+    cfg: ModelConfig
+    router: torch.Tensor          # [pad8(E + 1), H]: expert rows, then the shared-expert gate vector
+    gate_up: torch.Tensor         # [E, 2I, H]
+    down: torch.Tensor            # [E, H, I]
+    sh_gu: torch.Tensor | None    # [2S, H]
+    sh_down: torch.Tensor | None  # [H, S]
+    bufs: dict = dataclasses.field(default_factory=dict)
+
+    @classmethod
+    def from_state_dict(cls, cfg: ModelConfig, sd: dict, p: str, dev, expert_range: tuple[int, int] | None = None):
+        bf = torch.bfloat16
+        E = cfg.num_experts
+        rows = [sd[p + "gate.weight"].to(dev, bf)]
+        has_shared = (p + "shared_expert.gate_proj.weight") in sd
+        if has_shared:
+            rows.append(sd[p + "shared_expert_gate.weight"].to(dev, bf).reshape(1, -1))
+        n = sum(r.shape[0] for r in rows)
+        if _pad8(n) != n:
+            rows.append(torch.zeros(_pad8(n) - n, cfg.hidden_size, dtype=bf, device=dev))
+        gu, dn = sd[p + "experts.gate_up_proj"], sd[p + "experts.down_proj"]
+        sh_gu = sh_down = None
+        if has_shared:
+            sh_gu = torch.cat([sd[p + "shared_expert.gate_proj.weight"].to(dev, bf),
+                               sd[p + "shared_expert.up_proj.weight"].to(dev, bf)]).contiguous()
+            sh_down = sd[p + "shared_expert.down_proj.weight"].to(dev, bf).contiguous()
+        return cls(cfg, torch.cat(rows).contiguous(), gu.to(dev, bf).contiguous(), dn.to(dev, bf).contiguous(),
+                   sh_gu, sh_down)
+
+    def tensors(self) -> list[torch.Tensor]:
+        return [t for t in (self.router, self.gate_up, self.down, self.sh_gu, self.sh_down) if t is not None]
+
+    # ------------------------------------------------------------------ buffers
+    def _b(self, T: int, dev) -> dict:
+        b = self.bufs.get(T)
+        if b is None:
+            c, bf = self.cfg, torch.bfloat16
+            k, H, I = c.num_experts_per_tok, c.hidden_size, c.moe_intermediate_size
+            b = {"normed": torch.zeros(T, H, dtype=bf, device=dev),
+                 "logits": torch.zeros(T, self.router.shape[0], dtype=torch.float32, device=dev),
+                 "idx": torch.zeros(T, k, dtype=torch.int32, device=dev),
+                 "w": torch.zeros(T, k, dtype=torch.float32, device=dev),
+                 "xrow": torch.arange(T, dtype=torch.int32, device=dev).repeat_interleave(k).contiguous(),
+                 "inter": torch.zeros(T * k, I, dtype=bf, device=dev),
+                 "irow": torch.arange(T * k, dtype=torch.int32, device=dev),
+                 "y": torch.zeros(T * k, H, dtype=bf, device=dev)}
+            if self.sh_gu is not None:
+                S = self.sh_gu.shape[0] // 2
+                b["sh_inter"] = torch.zeros(T, S, dtype=bf, device=dev)
+                b["sh_out"] = torch.zeros(T, H, dtype=bf, device=dev)
+            self.bufs[T] = b
+        return b
+
+    # ------------------------------------------------------------------ decode (graph-capturable)
+    def forward_decode(self, cur, h, nxt, post_gain, out, model, M: int) -> None:
+        """``nxt = cur + h``; ``out = moe(rmsnorm(nxt))`` for ``M`` rows (the caller swaps
+        ``cur``/``nxt`` and carries ``out`` into the next layer's norm)."""
+        c = self.cfg
+        b = self._b(M, cur.device)
+        E, k = c.num_experts, c.num_experts_per_tok
+        K.rmsnorm(cur, post_gain, model.eps, out=b["normed"], add=h, res_out=nxt)
+        self._experts(b, M, out)
+
+    def _experts(self, b: dict, T: int, out: torch.Tensor) -> None:
+        c = self.cfg
+        E, k, H, I = c.num_experts, c.num_experts_per_tok, c.hidden_size, c.moe_intermediate_size
+        normed = b["normed"][:T]
+        # router logits: small row counts go through the GEMV (fp32 logits), 1, 2, 4 or 8 rows at a time
+        for s in range(0, T, 8):
+            e = min(T, s + 8)
+            K.gemv(self.router, normed[s:e], b["logits"][s:e])
+        K.call("moe_router", b["logits"], b["logits"].stride(0), T, E, k, int(c.norm_topk_prob), b["idx"], b["w"])
+        K._count()
+        K.call("moe_gemv", self.gate_up, normed, b["inter"], T * k, I, H, I, 1, b["idx"], b["xrow"],
+               self.gate_up.stride(0))
+        K.call("moe_gemv", self.down, b["inter"], b["y"], T * k, H, I, H, 0, b["idx"], b["irow"], self.down.stride(0))
+        K._count(2)
+        shared = gate = None
+        if self.sh_gu is not None:
+            for s in range(0, T, 8):
+                e = min(T, s + 8)
+                K.gemv(self.sh_gu, normed[s:e], b["sh_inter"][s:e], swiglu=True)
+                K.gemv(self.sh_down, b["sh_inter"][s:e], b["sh_out"][s:e])
+            shared, gate = b["sh_out"], b["logits"][:, E:]
+        K.call("moe_combine", b["y"], b["w"], shared, gate, b["logits"].stride(0), out, T, H, k)
+        K._count()
+
+    # ------------------------------------------------------------------ prefill
+    def forward_prefill(self, normed: torch.Tensor, res: torch.Tensor, model) -> None:
+        """``res += moe(normed)`` for a prefill chunk.  Small chunks reuse the decode kernels (every
+        slot streams its expert once); larger chunks sort the slots by expert and run one tcgen05
+        GEMM pair per expert that received tokens."""
+        c = self.cfg
+        T = normed.shape[0]
+        E, k, H, I = c.num_experts, c.num_experts_per_tok, c.hidden_size, c.moe_intermediate_size
+        if T <= 32:
+            b = self._b(T, normed.device)
+            b["normed"][:T].copy_(normed)
+            out = torch.empty(T, H, dtype=torch.bfloat16, device=normed.device)
+            self._experts(b, T, out)
+            res.add_(out)
+            return
+        logits = K.gemm(normed, self.router).float()                       # [T, pad8(E+1)]
+        idx = torch.empty(T, k, dtype=torch.int32, device=normed.device)
+        w = torch.empty(T, k, dtype=torch.float32, device=normed.device)
+        K.call("moe_router", logits, logits.stride(0), T, E, k, int(c.norm_topk_prob), idx, w)
+        K._count()
+        flat = idx.reshape(-1).long()
+        order = torch.argsort(flat, stable=True)                          # slots grouped by expert
+        counts = torch.bincount(flat, minlength=E).tolist()
+        tok_of = (order // k)
+        xs = normed[tok_of]                                               # gathered activations [T*k, H]
+        ys = torch.empty(T * k, H, dtype=torch.bfloat16, device=normed.device)
+        s = 0
+        for e, n in enumerate(counts):
+            if n == 0:
+                continue
+            seg = xs[s:s + n]
+            if n <= 8:
+                inter = torch.empty(n, I, dtype=torch.bfloat16, device=normed.device)
+                K.gemv(self.gate_up[e], seg.contiguous(), inter, swiglu=True)
+                K.gemv(self.down[e], inter, ys[s:s + n])
+            else:
+                gu = K.gemm(seg, self.gate_up[e])
+                inter = K.swiglu(gu)
+                K.gemm(inter, self.down[e], out=ys[s:s + n])
+            s += n
+        y = torch.empty_like(ys)
+        y[order] = ys                                                     # back to (token, slot) order
+        shared = gate = None
+        if self.sh_gu is not None:
+            sh = K.swiglu(K.gemm(normed, self.sh_gu))
+            shared = K.gemm(sh, self.sh_down)
+            gate = logits[:, E:].contiguous()
+        out = torch.empty(T, H, dtype=torch.bfloat16, device=normed.device)
+        K.call("moe_combine", y, w, shared, gate, gate.stride(0) if gate is not None else 0, out, T, H, k)
+        K._count()
+        res.add_(out)

@@ -118,3 +118,36 @@ def test_greedy_generation_matches_oracle_tokens():
         logits = lg[0]
         ref_logits = oracle.forward(torch.tensor([tok]), st)[-1]
     assert total == 0 or agree == total
+
+
+@torch.no_grad()
+def test_moe_model_prefill_and_decode_match_oracle():
+    """tiny-moe: 8 experts, top-2, one shared expert. Router near-ties can flip an expert under
+    bf16, so the comparison is on the logits with a looser tolerance."""
+    cfg, oracle, model = _setup("tiny-moe")
+    toks = _tokens(cfg, 80, seed=21)
+    st = oracle.new_state()
+    ref = oracle.forward(toks[:70], st)[-1]
+    bt = torch.arange(1, 9, dtype=torch.int32, device="cuda")
+    model.zero_state(0)
+    got = model.prefill(toks[:70].cuda(), 0, 0, bt)
+    assert _rel(got, ref) < 6e-2
+    for i in range(70, 80):
+        ref = oracle.forward(toks[i:i + 1], st)[-1]
+        model.set_rows(1, [int(toks[i])], [i], [0], [bt.tolist()])
+        _, logits = model.decode(1, graph=i >= 74)
+        assert _rel(logits[0], ref) < 8e-2, f"step {i}"
+
+
+def test_moe_router_kernel_matches_oracle():
+    from coffin_b200.ops import kernels as K
+    from coffin_b200.oracle import ops as O
+    g = torch.Generator().manual_seed(3)
+    logits = torch.randn(37, 264, generator=g)
+    idx = torch.zeros(37, 8, dtype=torch.int32, device="cuda")
+    w = torch.zeros(37, 8, device="cuda")
+    lg = logits.cuda()
+    K.call("moe_router", lg, lg.stride(0), 37, 256, 8, 1, idx, w)
+    ri, rw = O.moe_route(logits[:, :256], 8, True)
+    assert torch.equal(idx.cpu().long(), ri)
+    assert (w.cpu() - rw).abs().max() < 1e-5
