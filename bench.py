@@ -98,6 +98,7 @@ def main() -> None:
     ap.add_argument("--model", default=MODEL)
     ap.add_argument("--prompt", type=int, default=PROMPT)
     ap.add_argument("--new", type=int, default=NEW)
+    ap.add_argument("--quant", default="none", choices=["none", "int8"])
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--no-pdl", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
@@ -139,7 +140,7 @@ def main() -> None:
     cfg = preset(args.model)
     llm = LLM.from_random(cfg, seed=0, max_seq=args.prompt + args.new + 64, max_num_seqs=1,
                           tp_world=world, tp_rank=rank, graph=not args.no_graph, pdl=not args.no_pdl,
-                          max_chunk=args.prompt)
+                          max_chunk=args.prompt, quant=args.quant)
     model = llm.model
     g = torch.Generator().manual_seed(1234)
     prompts = [torch.randint(0, cfg.vocab_size, (args.prompt,), generator=g).pin_memory()
@@ -211,7 +212,7 @@ def main() -> None:
             "metric": "decode_tok_s", "value": decode_tok_s, "unit": "tok/s", "n_gpus": world,
             "steps": steps, "warmup": W, "ms_per_step": (pre_total + dec_total) / steps,
             "higher_is_better": True, "scaling": "strong",
-            "vs_baseline": decode_tok_s / BASELINE_DECODE_TOK_S, "dtype": "bf16", "data": "synthetic",
+            "vs_baseline": decode_tok_s / BASELINE_DECODE_TOK_S, "dtype": "bf16" if args.quant == "none" else "int8-w8a8", "data": "synthetic",
             "prefill_tok_s": prefill_tok_s, "prefill_vs_baseline": prefill_tok_s / BASELINE_PREFILL_TOK_S,
             "ttft_ms_p50": statistics.median(pre_ms), "tpot_ms_p50": statistics.median(dec_ms) / args.new,
             "config": {"model": args.model, "global_batch": 1, "seq_len": args.prompt, "decode_tokens": args.new,

@@ -128,6 +128,8 @@ struct PrefillArgs {
   bf16* out; int64_t ldo;   // [T, nh*hd]
   int T, q_pos0, nh, nkv;
   float scale_log2;         // hd^-0.5 * log2(e)
+  int causal;               // 1: key s visible to query position p when s <= p; 0: all kv_len keys (vision)
+  int kv_len;               // non-causal: number of valid keys
 };
 
 template <int HD>
@@ -155,7 +157,7 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(const PrefillArgs a) 
   float mrow[2] = {-INFINITY, -INFINITY}, lrow[2] = {0.f, 0.f};
   const int qpos_lo = a.q_pos0 + qt * 64 + warp * 16 + g;  // position of row g (row g+8: +8)
   const int last_q = min(a.T - 1, qt * 64 + 63);
-  const int kv_end = a.q_pos0 + last_q + 1;               // keys visible to this tile: [0, kv_end)
+  const int kv_end = a.causal ? a.q_pos0 + last_q + 1 : a.kv_len;   // keys visible to this tile: [0, kv_end)
   const int ntiles = (kv_end + kBlock - 1) / kBlock;
 
   for (int kt = 0; kt < ntiles; ++kt) {
@@ -193,7 +195,8 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(const PrefillArgs a) 
       for (int e = 0; e < 4; ++e) {
         const int key = kt * kBlock + n * 8 + tq * 2 + (e & 1);
         const int qp = qpos_lo + ((e >> 1) << 3);
-        const float v = (key <= qp) ? s[n][e] * a.scale_log2 : -INFINITY;
+        const bool vis = a.causal ? (key <= qp) : (key < a.kv_len);
+        const float v = vis ? s[n][e] * a.scale_log2 : -INFINITY;
         s[n][e] = v;
         mnew[e >> 1] = fmaxf(mnew[e >> 1], v);
       }
@@ -249,12 +252,12 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(const PrefillArgs a) 
     const int t = qt * 64 + warp * 16 + g + r * 8;
     if (t >= a.T) continue;
     const float inv = lrow[r] > 0.f ? 1.f / lrow[r] : 0.f;
-    const bf16* gp = a.gate + (int64_t)t * a.ldg + (int64_t)h * 2 * HD + HD;
+    const bf16* gp = a.gate ? a.gate + (int64_t)t * a.ldg + (int64_t)h * 2 * HD + HD : nullptr;
     bf16* op = a.out + (int64_t)t * a.ldo + (int64_t)h * HD;
 #pragma unroll
     for (int n = 0; n < HD / 8; ++n) {
       const int d = n * 8 + tq * 2;
-      const float g0 = sigmoid_f(__bfloat162float(gp[d])), g1 = sigmoid_f(__bfloat162float(gp[d + 1]));
+      const float g0 = gp ? sigmoid_f(__bfloat162float(gp[d])) : 1.f, g1 = gp ? sigmoid_f(__bfloat162float(gp[d + 1])) : 1.f;
       *reinterpret_cast<uint32_t*>(op + d) = pack_bf162(o[n][r * 2] * inv * g0, o[n][r * 2 + 1] * inv * g1);
     }
   }
@@ -487,11 +490,11 @@ CB_EXPORT int cb_attn_prep(const void* proj, int64_t ldp, const void* qg, const 
 
 CB_EXPORT int cb_attn_prefill(const void* q, const void* gate, int64_t ldg, const void* kpool, const void* vpool,
                               const void* block_table, void* out, int64_t ldo, int64_t T, int64_t q_pos0,
-                              int64_t nh, int64_t nkv, int64_t hd, void* stream) {
+                              int64_t nh, int64_t nkv, int64_t hd, int64_t causal, int64_t kv_len, void* stream) {
   if (T == 0) return 0;
   PrefillArgs a{(const bf16*)q, (const bf16*)gate, ldg, (const bf16*)kpool, (const bf16*)vpool,
                 (const int*)block_table, (bf16*)out, ldo, (int)T, (int)q_pos0, (int)nh, (int)nkv,
-                1.4426950408889634f / sqrtf((float)hd)};
+                1.4426950408889634f / sqrtf((float)hd), (int)causal, (int)kv_len};
   dim3 grid((unsigned)((T + 63) / 64), (unsigned)nh);
   const size_t smem = (size_t)3 * 64 * (hd + 8) * sizeof(bf16);
   cudaError_t e;

@@ -73,6 +73,35 @@ __global__ void swiglu_kernel(const bf16* __restrict__ gu, bf16* __restrict__ ou
   }
 }
 
+// LayerNorm with bias (vision tower): out = (x - mean) * rsqrt(var + eps) * w + b
+__global__ void layernorm_kernel(const bf16* __restrict__ x, const float* __restrict__ w, const float* __restrict__ b,
+                                 bf16* __restrict__ out, int64_t N, int64_t ldx, int64_t ldo, float eps) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  float* row = reinterpret_cast<float*>(smem_raw);
+  __shared__ float red[32];
+  griddep_launch();
+  griddep_wait();
+  const int64_t r = blockIdx.x;
+  float s = 0.f;
+  for (int64_t i = threadIdx.x; i < N; i += blockDim.x) { row[i] = __bfloat162float(x[r * ldx + i]); s += row[i]; }
+  const float mean = block_sum(s, red) / (float)N;
+  float v = 0.f;
+  for (int64_t i = threadIdx.x; i < N; i += blockDim.x) { const float d = row[i] - mean; v += d * d; }
+  const float rstd = rsqrtf(block_sum(v, red) / (float)N + eps);
+  for (int64_t i = threadIdx.x; i < N; i += blockDim.x)
+    out[r * ldo + i] = __float2bfloat16((row[i] - mean) * rstd * w[i] + b[i]);
+}
+
+// tanh-approximated GELU, in place capable
+__global__ void gelu_tanh_kernel(const bf16* __restrict__ x, bf16* __restrict__ out, int64_t n) {
+  griddep_launch();
+  griddep_wait();
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+    const float v = __bfloat162float(x[i]);
+    out[i] = __float2bfloat16(0.5f * v * (1.f + tanhf(0.7978845608028654f * (v + 0.044715f * v * v * v))));
+  }
+}
+
 // argmax over rows of fp32 logits; ties resolve to the lowest index (torch.argmax order).
 // Two stages in one launch: kArgmaxParts CTAs per row each reduce a slice into a (value, index)
 // partial in scratch memory, and the last CTA to arrive (atomic ticket) reduces the partials,
@@ -258,6 +287,26 @@ CB_EXPORT int cb_rmsnorm(const void* x, const void* add, const void* gain, void*
   return (int)cb_launch(rmsnorm_kernel, dim3((unsigned)M), dim3(threads), smem, (cudaStream_t)stream,
                         (const bf16*)x, (const bf16*)add, (const float*)gain, (bf16*)res_out, (bf16*)out,
                         N, ldx, ldo, eps);
+}
+
+CB_EXPORT int cb_layernorm(const void* x, const void* w, const void* b, void* out, int64_t M, int64_t N, int64_t ldx,
+                           int64_t ldo, float eps, void* stream) {
+  if (M == 0) return 0;
+  if (N * 4 > 200 * 1024) return CB_ERR_SHAPE;
+  const size_t smem = (size_t)N * 4;
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(layernorm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+  }
+  return (int)cb_launch(layernorm_kernel, dim3((unsigned)M), dim3(256), smem, (cudaStream_t)stream, (const bf16*)x,
+                        (const float*)w, (const float*)b, (bf16*)out, N, ldx, ldo, eps);
+}
+
+CB_EXPORT int cb_gelu_tanh(const void* x, void* out, int64_t n, void* stream) {
+  if (n == 0) return 0;
+  const int64_t blocks = min((n + 255) / 256, (int64_t)148 * 8);
+  return (int)cb_launch(gelu_tanh_kernel, dim3((unsigned)blocks), dim3(256), 0, (cudaStream_t)stream, (const bf16*)x,
+                        (bf16*)out, n);
 }
 
 CB_EXPORT int cb_swiglu(const void* gu, void* out, int64_t M, int64_t I, int64_t ldg, int64_t ldo,

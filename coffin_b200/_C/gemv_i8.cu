@@ -7,7 +7,8 @@
 // SwiGLU / fp32 epilogues, K-split for narrow outputs, grid-wide sweep order.  Halves the bytes
 // streamed per token relative to bf16.  Replaces the reference's int8 GEMV family
 // (backends/corex/kernels/gemv.cu:839-947 nk int8, w8a8.cu:76-242 activation quant).
-#include "common.cuh"
+#include <string.h>
+#include "tp.cuh"
 
 namespace {
 
@@ -19,6 +20,8 @@ struct I8Args {
   const bf16* res_in; const bf16* add; const float* gain; bf16* res_out;
   float eps;
   int M, ksplit, rounds;
+  int pull_site, push_site;   // tensor parallel: -1 = off
+  TpComm tp;
 };
 
 __device__ __forceinline__ void mma_s8(int* c, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
@@ -79,13 +82,18 @@ __global__ void __launch_bounds__(kT, 3) gemv_i8_kernel(const I8Args a) {
   griddep_wait();
 
   // ---- prologue: (residual add + norm,) per-row absmax, int8 quantisation into shared memory ----
+  if (NORM && a.pull_site >= 0) tp_pull_wait(a.tp, a.pull_site);
   for (int m = 0; m < M; ++m) {
     float ss = 0.f;
     for (int64_t c = tid; c < (K >> 3); c += kT) {
       float f[8], q[8];
       if (NORM) {
         bf16x8_to_float(*reinterpret_cast<const uint4*>(a.res_in + m * K + c * 8), f);
-        if (a.add) {
+        if (a.pull_site >= 0) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i)
+            f[i] = __bfloat162float(__float2bfloat16(f[i] + tp_pull_value(a.tp, a.pull_site, m * K + c * 8 + i)));
+        } else if (a.add) {
           bf16x8_to_float(*reinterpret_cast<const uint4*>(a.add + m * K + c * 8), q);
 #pragma unroll
           for (int i = 0; i < 8; ++i) f[i] = __bfloat162float(__float2bfloat16(f[i] + q[i]));
@@ -156,7 +164,8 @@ __global__ void __launch_bounds__(kT, 3) gemv_i8_kernel(const I8Args a) {
           if (m < M && row < a.N) {
             float v = (float)acc[0][e] * xscale[m] * a.wscale[row];
             if (SWIGLU) v = silu_f(v) * ((float)acc[PB - 1][e] * xscale[m] * a.wscale[a.up_off + row]);
-            if (OUT_F32) reinterpret_cast<float*>(a.y)[(int64_t)m * a.ldy + row] = v;
+            if (a.push_site >= 0) tp_push_value(a.tp, a.push_site, (int64_t)m * a.N + row, v);
+            else if (OUT_F32) reinterpret_cast<float*>(a.y)[(int64_t)m * a.ldy + row] = v;
             else reinterpret_cast<bf16*>(a.y)[(int64_t)m * a.ldy + row] = __float2bfloat16(v);
           }
         }
@@ -186,10 +195,12 @@ __global__ void __launch_bounds__(kT, 3) gemv_i8_kernel(const I8Args a) {
       }
       v *= xscale[m] * a.wscale[row];
       if (SWIGLU) v = silu_f(v) * (v2 * xscale[m] * a.wscale[a.up_off + row]);
-      if (OUT_F32) reinterpret_cast<float*>(a.y)[(int64_t)m * a.ldy + row] = v;
+      if (a.push_site >= 0) tp_push_value(a.tp, a.push_site, (int64_t)m * a.N + row, v);
+      else if (OUT_F32) reinterpret_cast<float*>(a.y)[(int64_t)m * a.ldy + row] = v;
       else reinterpret_cast<bf16*>(a.y)[(int64_t)m * a.ldy + row] = __float2bfloat16(v);
     }
   }
+  if (a.push_site >= 0) tp_push_done(a.tp, a.push_site, gridDim.x);
 }
 
 int g_i8_sms = 0;
@@ -252,12 +263,16 @@ __global__ void __launch_bounds__(256) quant_rows_kernel(const bf16* __restrict_
 // Same contract as cb_gemv_bf16 with int8 weights + per-row scales; K % 16 == 0.
 CB_EXPORT int cb_gemv_i8(const void* W, const void* wscale, const void* x, void* y, int64_t M, int64_t N, int64_t K,
                          int64_t ldy, int64_t mode, int64_t up_off, const void* res_in, const void* add,
-                         const void* gain, void* res_out, float eps, void* stream) {
-  if (!W || !wscale || !y || (!x && !res_in) || (res_in && !gain)) return CB_ERR_ARG;
+                         const void* gain, void* res_out, float eps, const void* tp, int64_t pull_site,
+                         int64_t push_site, void* stream) {
+  if (!W || !wscale || (!y && push_site < 0) || (!x && !res_in) || (res_in && !gain)) return CB_ERR_ARG;
+  if ((pull_site >= 0 || push_site >= 0) && !tp) return CB_ERR_ARG;
+  if (pull_site >= 0 && !res_in) return CB_ERR_ARG;
   if (K % 16 || M < 1 || M > 8 || N < 1) return CB_ERR_SHAPE;
   if (res_in && res_out && (res_out == res_in || res_out == add)) return CB_ERR_ARG;
   I8Args a{(const int8_t*)W, (const float*)wscale, (const bf16*)x, y, N, K, ldy, up_off, (const bf16*)res_in,
-           (const bf16*)add, (const float*)gain, (bf16*)res_out, eps, (int)M, 1, 1};
+           (const bf16*)add, (const float*)gain, (bf16*)res_out, eps, (int)M, 1, 1, (int)pull_site, (int)push_site};
+  if (tp) a.tp = *(const TpComm*)tp; else memset(&a.tp, 0, sizeof(a.tp));
   const bool sw = mode & 1, f32 = mode & 2, norm = res_in != nullptr;
   cudaStream_t st = (cudaStream_t)stream;
   if (sw) {

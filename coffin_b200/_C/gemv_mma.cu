@@ -51,6 +51,7 @@ __global__ void __launch_bounds__(kT, 3) gemv_mma_kernel(const MmaArgs a_in) {
     // (the second wait below is then a no-op)
     griddep_wait();
     const int slot = blockIdx.y;
+    if (a.slot_expert[slot] < 0) return;          // expert owned by another rank
     a.W += (int64_t)a.slot_expert[slot] * a.expert_stride;
     a.x += (int64_t)(a.slot_xrow ? a.slot_xrow[slot] : slot) * a.K;
     a.y = OUT_F32 ? (void*)(reinterpret_cast<float*>(a.y) + (int64_t)slot * a.ldy)

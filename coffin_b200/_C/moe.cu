@@ -3,7 +3,8 @@
 // run on the grouped tensor-core GEMV (decode, gemv_mma.cu slot mode) or the tcgen05 GEMM (prefill).
 // Reference: moe_router_t (backends/corex/kernels/moe_grouped.cu:725-879), the merge kernels
 // (moe_grouped_i8.cu:546-640) and shared_gate_scale (moe_epilogue.cu:35-95).
-#include "common.cuh"
+#include <string.h>
+#include "tp.cuh"
 
 namespace {
 
@@ -12,7 +13,7 @@ constexpr int kMaxTopK = 32;
 // One warp per token. logits [T, ldl] fp32 (first E columns are expert logits).
 __global__ void __launch_bounds__(256) moe_router_kernel(const float* __restrict__ logits, int64_t ldl, int E, int top_k,
                                                           int normalize, int* __restrict__ out_idx,
-                                                          float* __restrict__ out_w, int T) {
+                                                          float* __restrict__ out_w, int T, int e_lo, int e_hi) {
   griddep_launch();
   griddep_wait();
   const int lane = threadIdx.x & 31;
@@ -59,16 +60,18 @@ __global__ void __launch_bounds__(256) moe_router_kernel(const float* __restrict
     wsum += p;
     if (lane == k) { myw = p; myidx = bi; }
   }
+  // expert parallel: this rank owns experts [e_lo, e_hi); other slots get index -1 and weight 0
   if (lane < top_k) {
-    out_idx[tok * top_k + lane] = myidx;
-    out_w[tok * top_k + lane] = normalize ? myw / wsum : myw;
+    const bool local = myidx >= e_lo && myidx < e_hi;
+    out_idx[tok * top_k + lane] = local ? myidx - e_lo : -1;
+    out_w[tok * top_k + lane] = local ? (normalize ? myw / wsum : myw) : 0.f;
   }
 }
 
 // out[t, :] = sum_j w[t, j] * y[t * top_k + j, :]  (+ sigmoid(gate_logit[t]) * shared[t, :])
 __global__ void __launch_bounds__(256) moe_combine_kernel(const bf16* __restrict__ y, const float* __restrict__ w,
                                                            const bf16* __restrict__ shared, const float* __restrict__ gate_logit,
-                                                           int64_t ldg, bf16* __restrict__ out, int64_t H, int top_k) {
+                                                           int64_t ldg, bf16* __restrict__ out, int64_t H, int top_k, int push_site, const TpComm tp) {
   griddep_launch();
   griddep_wait();
   const int64_t t = blockIdx.x;
@@ -79,6 +82,7 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const bf16* __restrict
       float f[8];
       bf16x8_to_float(*reinterpret_cast<const uint4*>(y + ((t * top_k + j) * H) + c * 8), f);
       const float wj = w[t * top_k + j];
+      if (wj == 0.f) continue;                    // slot of another rank's expert (its row was never written)
 #pragma unroll
       for (int i = 0; i < 8; ++i) acc[i] = fmaf(wj, f[i], acc[i]);
     }
@@ -88,24 +92,34 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const bf16* __restrict
 #pragma unroll
       for (int i = 0; i < 8; ++i) acc[i] = fmaf(sg, f[i], acc[i]);
     }
-    *reinterpret_cast<uint4*>(out + t * H + c * 8) = float_to_bf16x8(acc);
+    if (push_site >= 0) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) tp_push_value(tp, push_site, t * H + c * 8 + i, acc[i]);
+    } else {
+      *reinterpret_cast<uint4*>(out + t * H + c * 8) = float_to_bf16x8(acc);
+    }
   }
+  if (push_site >= 0) tp_push_done(tp, push_site, gridDim.x);
 }
 
 }  // namespace
 
 CB_EXPORT int cb_moe_router(const void* logits, int64_t ldl, int64_t T, int64_t E, int64_t top_k, int64_t normalize,
-                            void* out_idx, void* out_w, void* stream) {
+                            void* out_idx, void* out_w, int64_t e_lo, int64_t e_hi, void* stream) {
   if (T == 0) return 0;
   if (E > 512 || top_k > kMaxTopK || top_k < 1 || top_k > E) return CB_ERR_SHAPE;
   return (int)cb_launch(moe_router_kernel, dim3((unsigned)((T + 7) / 8)), dim3(256), 0, (cudaStream_t)stream,
-                        (const float*)logits, ldl, (int)E, (int)top_k, (int)normalize, (int*)out_idx, (float*)out_w, (int)T);
+                        (const float*)logits, ldl, (int)E, (int)top_k, (int)normalize, (int*)out_idx, (float*)out_w, (int)T, (int)e_lo, (int)e_hi);
 }
 
 CB_EXPORT int cb_moe_combine(const void* y, const void* w, const void* shared, const void* gate_logit, int64_t ldg,
-                             void* out, int64_t T, int64_t H, int64_t top_k, void* stream) {
+                             void* out, int64_t T, int64_t H, int64_t top_k, const void* tp, int64_t push_site,
+                             void* stream) {
   if (T == 0) return 0;
-  if (H % 8) return CB_ERR_SHAPE;
+  if (H % 8 || (push_site >= 0 && !tp)) return CB_ERR_SHAPE;
+  TpComm c;
+  if (tp) c = *(const TpComm*)tp; else memset(&c, 0, sizeof(c));
   return (int)cb_launch(moe_combine_kernel, dim3((unsigned)T), dim3(256), 0, (cudaStream_t)stream, (const bf16*)y,
-                        (const float*)w, (const bf16*)shared, (const float*)gate_logit, ldg, (bf16*)out, H, (int)top_k);
+                        (const float*)w, (const bf16*)shared, (const float*)gate_logit, ldg, (bf16*)out, H, (int)top_k,
+                        (int)push_site, c);
 }

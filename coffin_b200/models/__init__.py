@@ -29,6 +29,12 @@ def _ensure_builtin() -> None:
     def qwen35(cfg, sd, **kw):
         from .qwen35.model import Qwen35Model
         tp_world, tp_rank = kw.pop("tp_world", 1), kw.pop("tp_rank", 0)
+        ep_world, ep_rank = kw.pop("ep_world", 1), kw.pop("ep_rank", 0)
+        if ep_world > 1:
+            # expert parallel: attention / delta-net / dense weights replicated, routed experts split
+            from ..parallel.tp import TpComm, make_exchange
+            comm = TpComm(ep_rank, ep_world, cfg.hidden_size, 8, 2 * cfg.num_hidden_layers, exchange=make_exchange())
+            return Qwen35Model(cfg, sd, tp=comm, ep_rank=ep_rank, ep_world=ep_world, **kw)
         if tp_world > 1:
             from ..parallel.tp import TpComm, local_config, make_exchange, shard_state_dict
             lcfg = local_config(cfg, tp_world)

@@ -35,6 +35,35 @@ from ...weights.init import LM
 BUCKETS = (1, 2, 4, 8)
 
 
+class QW:
+    """Device-resident int8 projection: ``wq [N, K]`` int8 + per-row ``scale [N]`` (W8A8)."""
+
+    def __init__(self, wq: torch.Tensor, scale: torch.Tensor) -> None:
+        self.wq, self.scale = wq.contiguous(), scale.float().contiguous()
+
+    @property
+    def shape(self):
+        return self.wq.shape
+
+    def __getitem__(self, sl):
+        return QW(self.wq[sl], self.scale[sl])
+
+    def numel(self) -> int:
+        return self.wq.numel()
+
+    def element_size(self) -> int:
+        return 1
+
+    def data_ptr(self) -> int:
+        return self.wq.data_ptr()
+
+    @classmethod
+    def quantize(cls, w: torch.Tensor) -> "QW":
+        from ...weights.quant import QWeight
+        q = QWeight.quantize(w)
+        return cls(q.wq, q.scale)
+
+
 def _pad8(n: int) -> int:
     return (n + 7) // 8 * 8
 
@@ -65,10 +94,12 @@ class Qwen35Model:
     def __init__(self, cfg: ModelConfig, sd: dict[str, torch.Tensor], device: str | torch.device = "cuda",
                  max_seq: int = 4096, num_slots: int = 2, num_blocks: int | None = None,
                  max_chunk: int = 2048, pdl: bool = True, free_source: bool = False, tp=None,
-                 full_cfg: ModelConfig | None = None) -> None:
+                 full_cfg: ModelConfig | None = None, quant: str = "none", ep_rank: int = 0, ep_world: int = 1) -> None:
         """``cfg`` is the geometry this instance computes (a tensor-parallel shard gets its local
         head / channel counts, ``full_cfg`` the unsharded model and ``tp`` the communicator)."""
         self.cfg = cfg
+        self.quant = quant
+        self.ep_rank, self.ep_world, self.ep_site = ep_rank, ep_world, -1
         self.tp = tp
         self.tp_world = tp.world if tp is not None else 1
         self.tp_rank = tp.rank if tp is not None else 0
@@ -85,16 +116,38 @@ class Qwen35Model:
         dev, bf = self.device, torch.bfloat16
         c = cfg
 
-        def w(key: str) -> torch.Tensor:
+        from ...weights.quant import QWeight, W4A8Weight
+
+        def w(key: str):
             t = sd.pop(key) if free_source else sd[key]
+            if isinstance(t, QWeight):                      # pre-quantised int8 checkpoint
+                return QW(t.wq.to(dev), t.scale.to(dev))
+            if isinstance(t, W4A8Weight):                   # int4 group-128 storage: computed as bf16
+                t = t.dequant(bf)
             return t.to(device=dev, dtype=bf)
+
+        def cat(parts):
+            """Row-concatenate projections; int8 parts keep their per-row scales."""
+            if any(isinstance(p_, QW) for p_ in parts):
+                parts = [p_ if isinstance(p_, QW) else QW.quantize(p_) for p_ in parts]
+                return QW(torch.cat([p_.wq for p_ in parts]), torch.cat([p_.scale for p_ in parts]))
+            t = torch.cat(parts).contiguous()
+            return QW.quantize(t) if quant == "int8" else t
+
+        def one(t):
+            if isinstance(t, QW):
+                return t
+            return QW.quantize(t) if quant == "int8" else t.contiguous()
 
         def gain(key: str, centred: bool = True) -> torch.Tensor:
             t = sd[key].to(device=dev, dtype=torch.float32)
             return (1.0 + t).contiguous() if centred else t.contiguous()
 
-        self.embed = w(LM + "embed_tokens.weight").contiguous()
-        self.lm_head = w("lm_head.weight").contiguous() if "lm_head.weight" in sd else self.embed
+        self.embed = w(LM + "embed_tokens.weight")
+        if isinstance(self.embed, QW):
+            self.embed = (self.embed.wq.float() * self.embed.scale[:, None]).to(bf)
+        self.embed = self.embed.contiguous()
+        self.lm_head = one(w("lm_head.weight")) if "lm_head.weight" in sd else one(self.embed)
         self.vocab_local = c.vocab_size
         if self.tp_world > 1:       # vocabulary-parallel head: this rank scores a contiguous slice
             if c.vocab_size % self.tp_world:
@@ -115,7 +168,7 @@ class Qwen35Model:
                 lw = LayerWeights(
                     kind=kind, in_gain=gain(p + "input_layernorm.weight"),
                     post_gain=gain(p + "post_attention_layernorm.weight"),
-                    w_in=torch.cat(parts).contiguous(), w_out=w(q + "out_proj.weight").contiguous(),
+                    w_in=cat(parts), w_out=one(w(q + "out_proj.weight")),
                     w_gu=None, w_down=None,
                     conv_w=sd[q + "conv1d.weight"].to(dev, torch.float32).reshape(c.lin_conv_dim, -1).contiguous(),
                     A_log=sd[q + "A_log"].to(dev, torch.float32).contiguous(),
@@ -126,16 +179,16 @@ class Qwen35Model:
                 lw = LayerWeights(
                     kind=kind, in_gain=gain(p + "input_layernorm.weight"),
                     post_gain=gain(p + "post_attention_layernorm.weight"),
-                    w_in=torch.cat([w(q + "q_proj.weight"), w(q + "k_proj.weight"), w(q + "v_proj.weight")]).contiguous(),
-                    w_out=w(q + "o_proj.weight").contiguous(), w_gu=None, w_down=None,
+                    w_in=cat([w(q + "q_proj.weight"), w(q + "k_proj.weight"), w(q + "v_proj.weight")]),
+                    w_out=one(w(q + "o_proj.weight")), w_gu=None, w_down=None,
                     qg=gain(q + "q_norm.weight"), kg=gain(q + "k_norm.weight"))
             m = p + "mlp."
             if c.is_moe:
                 from .moe import MoEWeights
-                lw.moe = MoEWeights.from_state_dict(c, sd, m, dev)
+                lw.moe = MoEWeights.from_state_dict(c, sd, m, dev, ep_rank, ep_world)
             else:
-                lw.w_gu = torch.cat([w(m + "gate_proj.weight"), w(m + "up_proj.weight")]).contiguous()
-                lw.w_down = w(m + "down_proj.weight").contiguous()
+                lw.w_gu = cat([w(m + "gate_proj.weight"), w(m + "up_proj.weight")])
+                lw.w_down = one(w(m + "down_proj.weight"))
             self.layers.append(lw)
         # ---- rotary tables -------------------------------------------------------------
         cos, sin = O.rope_tables(c.rotary_dim, c.rope_theta, self.max_seq + 64)
@@ -155,12 +208,30 @@ class Qwen35Model:
         self._rows: dict[int, dict] = {}
         self._graphs: dict[int, torch.cuda.CUDAGraph] = {}
         self.graph_pool = None
+        self.input_hidden = None   # when set, a decode step starts from this [M, H] input instead of the token embedding
         self.tp_force = False      # run the push/pull path even with world == 1 (single-GPU test of the protocol)
         self._step_launches: dict[int, int] = {}
 
     def launches_per_step(self, M: int) -> int:
         """Kernels launched by one decode step of bucket ``M`` (counted while capturing)."""
         return self._step_launches.get(M, 0)
+
+    # ------------------------------------------------------------------ projection dispatch
+    def _gemv(self, W, x, out, **kw):
+        """Decode projection on whichever storage the weight has (bf16 or int8 W8A8)."""
+        if isinstance(W, QW):
+            return K.gemv_i8(W.wq, W.scale, x, out, **kw)
+        return K.gemv(W, x, out, **kw)
+
+    def _gemm(self, A, W, out=None, residual=None, swiglu_in: bool = False):
+        """Prefill projection.  ``swiglu_in``: ``A`` is a ``[T, 2I]`` gate|up tensor whose SwiGLU
+        product is the real input (fused into the activation quantisation on the int8 path)."""
+        if isinstance(W, QW):
+            q, sc = K.quant_rows(A, swiglu=swiglu_in)
+            return K.gemm_i8(q, sc, W.wq, W.scale, out=out, residual=residual)
+        if swiglu_in:
+            A = K.swiglu(A)
+        return K.gemm(A, W, out=out, residual=residual)
 
     # ------------------------------------------------------------------ sizes
     @property
@@ -266,7 +337,7 @@ class Qwen35Model:
             K.rmsnorm(res, lw.in_gain, self.eps, out=normed)
             n_in = lw.w_in.shape[0]
             proj = ws["proj"][:T, :n_in]
-            K.gemm(normed, lw.w_in, out=proj)
+            self._gemm(normed, lw.w_in, out=proj)
             if lw.kind == LINEAR:
                 j = self.lin_ids[li]
                 act = ws["act"][:T, :c.lin_vdim]
@@ -283,29 +354,29 @@ class Qwen35Model:
                 K.attn_prefill(q, proj, self.kpool[j], self.vpool[j], block_table, act, q_pos0=pos0,
                                nh=c.num_attention_heads, nkv=c.num_key_value_heads, hd=c.head_dim)
             if self.tp_world > 1:
-                part = self._tp_reduce(K.gemm(act, lw.w_out, out=ws["part"][:T]))
+                part = self._tp_reduce(self._gemm(act, lw.w_out, out=ws["part"][:T]))
                 K.rmsnorm(res, lw.post_gain, self.eps, out=normed, add=part, res_out=res)
             else:
-                K.gemm(act, lw.w_out, out=res, residual=res)
+                self._gemm(act, lw.w_out, out=res, residual=res)
                 K.rmsnorm(res, lw.post_gain, self.eps, out=normed)
             if lw.moe is not None:
                 lw.moe.forward_prefill(normed, res, self)
             else:
                 gu = ws["gu"][:T]
-                K.gemm(normed, lw.w_gu, out=gu)
-                inter = K.swiglu(gu, ws["inter"][:T])
+                self._gemm(normed, lw.w_gu, out=gu)
                 if self.tp_world > 1:
-                    part = self._tp_reduce(K.gemm(inter, lw.w_down, out=ws["part"][:T]))
+                    part = self._tp_reduce(self._gemm(gu, lw.w_down, out=ws["part"][:T], swiglu_in=True))
                     res.add_(part)
                 else:
-                    K.gemm(inter, lw.w_down, out=res, residual=res)
+                    self._gemm(gu, lw.w_down, out=res, residual=res, swiglu_in=True)
         out_logits = None
         self.last_hidden = None
+        self.last_prenorm = res            # last-layer residual stream of the chunk (view of the workspace)
         if want_hidden:
             self.last_hidden = K.rmsnorm(res, self.final_gain, self.eps)
         if want_logits:
             local = torch.empty(1, self.vocab_local, dtype=torch.float32, device=self.device)
-            K.gemv(self.lm_head, None, local, norm=(res[T - 1:T].contiguous(), None, self.final_gain, None, self.eps))
+            self._gemv(self.lm_head, None, local, norm=(res[T - 1:T].contiguous(), None, self.final_gain, None, self.eps))
             out_logits = self._gather_logits(local, 1)[0]
         return out_logits
 
@@ -375,18 +446,22 @@ class Qwen35Model:
         ranks (sites ``2*layer`` and ``2*layer + 1``) and the following projection pulls the sum in
         its prologue, so the step has no separate all-reduce launches."""
         c, b = self.cfg, self._row_buffers(M)
-        tp = self.tp if self.tp_world > 1 or (self.tp is not None and self.tp_force) else None
+        comm = self.tp if (self.tp is not None and (self.tp_world > 1 or self.ep_world > 1 or self.tp_force)) else None
+        tp = comm if (self.ep_world == 1 and not self.cfg.is_moe) else None     # dense row-parallel push/pull
         cur, nxt = b["res"]
-        if tp is not None:
-            tp.epoch_bump()
-        K.embed_gather(self.embed, b["tokens"], cur)
+        if comm is not None:
+            comm.epoch_bump()
+        if self.input_hidden is not None:
+            cur.copy_(self.input_hidden)
+        else:
+            K.embed_gather(self.embed, b["tokens"], cur)
         carry, pull = None, -1
         for li, lw in enumerate(self.layers):
             n_in = lw.w_in.shape[0]
             proj = b["proj"][:, :n_in]
             have = carry is not None or pull >= 0
-            K.gemv(lw.w_in, None, proj, norm=(cur, carry, lw.in_gain, nxt if have else None, self.eps),
-                   tp=tp, pull_site=pull)
+            self._gemv(lw.w_in, None, proj, norm=(cur, carry, lw.in_gain, nxt if have else None, self.eps),
+                       tp=comm, pull_site=pull)
             if have:
                 cur, nxt = nxt, cur
             if lw.kind == LINEAR:
@@ -404,26 +479,30 @@ class Qwen35Model:
                               nh=c.num_attention_heads, nkv=c.num_key_value_heads, hd=c.head_dim,
                               rot=c.rotary_dim, nsplit=b["nsplit"], eps=self.eps)
             if tp is not None:
-                K.gemv(lw.w_out, act, None, tp=tp, push_site=2 * li, rows=M)
+                self._gemv(lw.w_out, act, None, tp=tp, push_site=2 * li, rows=M)
             else:
-                K.gemv(lw.w_out, act, b["h"])
+                self._gemv(lw.w_out, act, b["h"])
             if lw.moe is not None:
+                # expert parallel: the combine kernel pushes this rank's partial sum to every rank and
+                # the next projection pulls the total (site 2 * layer + 1)
+                ep = self.tp is not None and (self.ep_world > 1 or self.tp_force)
+                self.ep_site = 2 * li + 1
                 lw.moe.forward_decode(cur, b["h"], nxt, lw.post_gain, b["h2"], self, M)
                 cur, nxt = nxt, cur
-                carry, pull = b["h2"], -1
+                carry, pull = (None, 2 * li + 1) if ep else (b["h2"], -1)
                 continue
-            K.gemv(lw.w_gu, None, b["inter"], swiglu=True,
+            self._gemv(lw.w_gu, None, b["inter"], swiglu=True,
                    norm=(cur, None if tp is not None else b["h"], lw.post_gain, nxt, self.eps),
                    tp=tp, pull_site=2 * li if tp is not None else -1)
             cur, nxt = nxt, cur
             if tp is not None:
-                K.gemv(lw.w_down, b["inter"], None, tp=tp, push_site=2 * li + 1, rows=M)
+                self._gemv(lw.w_down, b["inter"], None, tp=tp, push_site=2 * li + 1, rows=M)
                 carry, pull = None, 2 * li + 1
             else:
-                K.gemv(lw.w_down, b["inter"], b["h2"])
+                self._gemv(lw.w_down, b["inter"], b["h2"])
                 carry, pull = b["h2"], -1
-        K.gemv(self.lm_head, None, b["logits_local"], norm=(cur, carry, self.final_gain, nxt, self.eps),
-               tp=tp, pull_site=pull)
+        self._gemv(self.lm_head, None, b["logits_local"], norm=(cur, carry, self.final_gain, nxt, self.eps),
+                   tp=comm, pull_site=pull)
         if self.tp_world > 1:
             b["logits"].copy_(self._gather_logits(b["logits_local"], M))
         K.argmax(b["logits"], b["next"])
@@ -491,6 +570,11 @@ class Qwen35Model:
             self._decode_body(M)
         return b["next"], b["logits"]
 
+    def final_hidden(self, M: int, normed: bool = True) -> torch.Tensor:
+        """Last-layer residual stream of the previous decode step (``normed``: after the final norm)."""
+        res = self._row_buffers(M)["final_res"]
+        return K.rmsnorm(res, self.final_gain, self.eps) if normed else res
+
     def advance_rows(self, M: int) -> None:
         """Feed the sampled tokens back and advance positions by one (device-side, no host sync):
         lets a caller run many greedy steps back to back."""
@@ -551,7 +635,7 @@ class Qwen35Model:
         carry = None
         for li, lw in enumerate(self.layers):
             proj = b["proj"][:, :lw.w_in.shape[0]]
-            K.gemv(lw.w_in, None, proj, norm=(cur, carry, lw.in_gain, nxt if carry is not None else None, self.eps))
+            self._gemv(lw.w_in, None, proj, norm=(cur, carry, lw.in_gain, nxt if carry is not None else None, self.eps))
             if carry is not None:
                 cur, nxt = nxt, cur
             if lw.kind == LINEAR:
@@ -569,16 +653,16 @@ class Qwen35Model:
                             rot=c.rotary_dim, eps=self.eps)
                 K.attn_prefill(b["q"], proj, self.kpool[j], self.vpool[j], block_table, act, q_pos0=pos0,
                                nh=c.num_attention_heads, nkv=c.num_key_value_heads, hd=c.head_dim)
-            K.gemv(lw.w_out, act, b["h"])
+            self._gemv(lw.w_out, act, b["h"])
             if lw.moe is not None:
                 lw.moe.forward_decode(cur, b["h"], nxt, lw.post_gain, b["h2"], self, C)
                 cur, nxt = nxt, cur
             else:
-                K.gemv(lw.w_gu, None, b["inter"], swiglu=True, norm=(cur, b["h"], lw.post_gain, nxt, self.eps))
+                self._gemv(lw.w_gu, None, b["inter"], swiglu=True, norm=(cur, b["h"], lw.post_gain, nxt, self.eps))
                 cur, nxt = nxt, cur
-                K.gemv(lw.w_down, b["inter"], b["h2"])
+                self._gemv(lw.w_down, b["inter"], b["h2"])
             carry = b["h2"]
-        K.gemv(self.lm_head, None, b["logits"], norm=(cur, carry, self.final_gain, nxt, self.eps))
+        self._gemv(self.lm_head, None, b["logits"], norm=(cur, carry, self.final_gain, nxt, self.eps))
         self._verify_width = C
         return b["logits"]
 

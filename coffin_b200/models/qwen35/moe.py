@@ -30,10 +30,16 @@ class MoEWeights:
     down: torch.Tensor            # [E, H, I]
     sh_gu: torch.Tensor | None    # [2S, H]
     sh_down: torch.Tensor | None  # [H, S]
+    e_lo: int = 0                 # expert parallel: this rank holds experts [e_lo, e_hi)
+    e_hi: int = 0
+    ep_world: int = 1
     bufs: dict = dataclasses.field(default_factory=dict)
 
     @classmethod
-    def from_state_dict(cls, cfg: ModelConfig, sd: dict, p: str, dev, expert_range: tuple[int, int] | None = None):
+    def from_state_dict(cls, cfg: ModelConfig, sd: dict, p: str, dev, ep_rank: int = 0, ep_world: int = 1):
+        """Expert parallel (``ep_world > 1``): the routed experts are split by contiguous range
+        (reference ``expert_range``, ``models/qwen35/parallel.py:238-259``) and the shared expert by
+        intermediate columns, so every rank's partial output sums to the full layer output."""
         bf = torch.bfloat16
         E = cfg.num_experts
         rows = [sd[p + "gate.weight"].to(dev, bf)]
@@ -44,13 +50,23 @@ class MoEWeights:
         if _pad8(n) != n:
             rows.append(torch.zeros(_pad8(n) - n, cfg.hidden_size, dtype=bf, device=dev))
         gu, dn = sd[p + "experts.gate_up_proj"], sd[p + "experts.down_proj"]
+        if E % ep_world:
+            raise ValueError(f"num_experts={E} is not divisible by expert-parallel world {ep_world}")
+        per = E // ep_world
+        e_lo, e_hi = ep_rank * per, (ep_rank + 1) * per
+        gu, dn = gu[e_lo:e_hi], dn[e_lo:e_hi]
         sh_gu = sh_down = None
         if has_shared:
-            sh_gu = torch.cat([sd[p + "shared_expert.gate_proj.weight"].to(dev, bf),
-                               sd[p + "shared_expert.up_proj.weight"].to(dev, bf)]).contiguous()
-            sh_down = sd[p + "shared_expert.down_proj.weight"].to(dev, bf).contiguous()
+            sg, su = sd[p + "shared_expert.gate_proj.weight"], sd[p + "shared_expert.up_proj.weight"]
+            sdn = sd[p + "shared_expert.down_proj.weight"]
+            S = sg.shape[0]
+            if S % ep_world:
+                raise ValueError("shared expert width must divide by the expert-parallel world")
+            c0, c1 = ep_rank * (S // ep_world), (ep_rank + 1) * (S // ep_world)
+            sh_gu = torch.cat([sg[c0:c1].to(dev, bf), su[c0:c1].to(dev, bf)]).contiguous()
+            sh_down = sdn[:, c0:c1].to(dev, bf).contiguous()
         return cls(cfg, torch.cat(rows).contiguous(), gu.to(dev, bf).contiguous(), dn.to(dev, bf).contiguous(),
-                   sh_gu, sh_down)
+                   sh_gu, sh_down, e_lo, e_hi, ep_world)
 
     def tensors(self) -> list[torch.Tensor]:
         return [t for t in (self.router, self.gate_up, self.down, self.sh_gu, self.sh_down) if t is not None]
@@ -84,9 +100,10 @@ class MoEWeights:
         b = self._b(M, cur.device)
         E, k = c.num_experts, c.num_experts_per_tok
         K.rmsnorm(cur, post_gain, model.eps, out=b["normed"], add=h, res_out=nxt)
-        self._experts(b, M, out)
+        tp = model.tp if self.ep_world > 1 or model.tp_force else None
+        self._experts(b, M, out, tp=tp, push_site=model.ep_site if tp is not None else -1)
 
-    def _experts(self, b: dict, T: int, out: torch.Tensor) -> None:
+    def _experts(self, b: dict, T: int, out: torch.Tensor, tp=None, push_site: int = -1) -> None:
         c = self.cfg
         E, k, H, I = c.num_experts, c.num_experts_per_tok, c.hidden_size, c.moe_intermediate_size
         normed = b["normed"][:T]
@@ -94,7 +111,8 @@ class MoEWeights:
         for s in range(0, T, 8):
             e = min(T, s + 8)
             K.gemv(self.router, normed[s:e], b["logits"][s:e])
-        K.call("moe_router", b["logits"], b["logits"].stride(0), T, E, k, int(c.norm_topk_prob), b["idx"], b["w"])
+        K.call("moe_router", b["logits"], b["logits"].stride(0), T, E, k, int(c.norm_topk_prob), b["idx"], b["w"],
+               self.e_lo, self.e_hi)
         K._count()
         K.call("moe_gemv", self.gate_up, normed, b["inter"], T * k, I, H, I, 1, b["idx"], b["xrow"],
                self.gate_up.stride(0))
@@ -107,7 +125,8 @@ class MoEWeights:
                 K.gemv(self.sh_gu, normed[s:e], b["sh_inter"][s:e], swiglu=True)
                 K.gemv(self.sh_down, b["sh_inter"][s:e], b["sh_out"][s:e])
             shared, gate = b["sh_out"], b["logits"][:, E:]
-        K.call("moe_combine", b["y"], b["w"], shared, gate, b["logits"].stride(0), out, T, H, k)
+        K.call("moe_combine", b["y"], b["w"], shared, gate, b["logits"].stride(0), out, T, H, k,
+               tp.cstruct_ref() if tp is not None and push_site >= 0 else None, push_site)
         K._count()
 
     # ------------------------------------------------------------------ prefill
@@ -123,19 +142,23 @@ class MoEWeights:
             b["normed"][:T].copy_(normed)
             out = torch.empty(T, H, dtype=torch.bfloat16, device=normed.device)
             self._experts(b, T, out)
+            if self.ep_world > 1:
+                model._tp_reduce(out)
             res.add_(out)
             return
         logits = K.gemm(normed, self.router).float()                       # [T, pad8(E+1)]
         idx = torch.empty(T, k, dtype=torch.int32, device=normed.device)
         w = torch.empty(T, k, dtype=torch.float32, device=normed.device)
-        K.call("moe_router", logits, logits.stride(0), T, E, k, int(c.norm_topk_prob), idx, w)
+        K.call("moe_router", logits, logits.stride(0), T, E, k, int(c.norm_topk_prob), idx, w, self.e_lo, self.e_hi)
         K._count()
+        n_local = self.e_hi - self.e_lo
         flat = idx.reshape(-1).long()
+        flat = torch.where(flat < 0, torch.full_like(flat, n_local), flat)    # other ranks' slots sort last
         order = torch.argsort(flat, stable=True)                          # slots grouped by expert
-        counts = torch.bincount(flat, minlength=E).tolist()
+        counts = torch.bincount(flat, minlength=n_local + 1).tolist()[:n_local]
         tok_of = (order // k)
         xs = normed[tok_of]                                               # gathered activations [T*k, H]
-        ys = torch.empty(T * k, H, dtype=torch.bfloat16, device=normed.device)
+        ys = torch.zeros(T * k, H, dtype=torch.bfloat16, device=normed.device)
         s = 0
         for e, n in enumerate(counts):
             if n == 0:
@@ -158,6 +181,8 @@ class MoEWeights:
             shared = K.gemm(sh, self.sh_down)
             gate = logits[:, E:].contiguous()
         out = torch.empty(T, H, dtype=torch.bfloat16, device=normed.device)
-        K.call("moe_combine", y, w, shared, gate, gate.stride(0) if gate is not None else 0, out, T, H, k)
+        K.call("moe_combine", y, w, shared, gate, gate.stride(0) if gate is not None else 0, out, T, H, k, None, -1)
         K._count()
+        if self.ep_world > 1:
+            model._tp_reduce(out)
         res.add_(out)

@@ -173,6 +173,42 @@ def gemv(W: torch.Tensor, x: torch.Tensor | None, out: torch.Tensor | None, *, s
     return out
 
 
+def gemv_i8(Wq: torch.Tensor, wscale: torch.Tensor, x: torch.Tensor | None, out: torch.Tensor | None, *,
+            swiglu: bool = False, norm: tuple | None = None, tp=None, pull_site: int = -1, push_site: int = -1,
+            rows: int | None = None) -> torch.Tensor | None:
+    """W8A8 decode projection: int8 weights ``[N, K]`` (``[2I, K]`` with ``swiglu``) + per-row scales;
+    the activation rows are quantised per token inside the kernel."""
+    M = out.shape[0] if out is not None else rows
+    K = Wq.shape[1]
+    N = Wq.shape[0] // 2 if swiglu else Wq.shape[0]
+    mode = (1 if swiglu else 0) | (2 if out is not None and out.dtype == torch.float32 else 0)
+    ldy = out.stride(0) if out is not None else N
+    tpp = tp.cstruct_ref() if tp is not None and (pull_site >= 0 or push_site >= 0) else None
+    if norm is None:
+        assert x is not None and x.is_contiguous() and x.shape == (M, K)
+        res_in = add = gain = res_out = None
+        eps = 0.0
+    else:
+        res_in, add, gain, res_out, eps = norm
+        x = None
+    call("gemv_i8", Wq, wscale, x, out, M, N, K, ldy, mode, N, res_in, add, gain, res_out, float(eps), tpp,
+         pull_site, push_site)
+    _count()
+    return out
+
+
+def quant_rows(x: torch.Tensor, swiglu: bool = False) -> tuple[torch.Tensor, torch.Tensor]:
+    """Per-row dynamic int8 quantisation of bf16 rows (optionally of ``silu(gate) * up`` of a
+    ``[M, 2I]`` input). Returns ``(q int8 [M, K], scale fp32 [M])``."""
+    M = x.shape[0]
+    K = x.shape[1] // 2 if swiglu else x.shape[1]
+    q = torch.empty(M, K, dtype=torch.int8, device=x.device)
+    s = torch.empty(M, dtype=torch.float32, device=x.device)
+    call("quant_rows", x, x.stride(0), q, s, M, K, int(swiglu))
+    _count()
+    return q, s
+
+
 def gemm(A: torch.Tensor, W: torch.Tensor, out: torch.Tensor | None = None,
          residual: torch.Tensor | None = None, bn: int = 0) -> torch.Tensor:
     """Prefill projection on tcgen05: ``out[M, N] = A[M, K] @ W[N, K]^T (+ residual)``, bf16."""
@@ -243,10 +279,13 @@ def attn_prep(proj, qg, kg, cos, sin, rope_idx, kv_slot, q_out, kpool, vpool, *,
     _count()
 
 
-def attn_prefill(q, proj, kpool, vpool, block_table, out, *, q_pos0, nh, nkv, hd) -> torch.Tensor:
+def attn_prefill(q, proj, kpool, vpool, block_table, out, *, q_pos0, nh, nkv, hd, causal: bool = True,
+                 kv_len: int = 0) -> torch.Tensor:
+    """``proj`` supplies the per-head output gate (``None``: no gate). ``causal=False`` attends to the
+    first ``kv_len`` keys of the block table (bidirectional, used by the vision tower)."""
     T = q.shape[0]
-    call("attn_prefill", q, proj, proj.stride(0), kpool, vpool, block_table, out, out.stride(0), T, q_pos0,
-         nh, nkv, hd)
+    call("attn_prefill", q, proj, proj.stride(0) if proj is not None else 0, kpool, vpool, block_table, out,
+         out.stride(0), T, q_pos0, nh, nkv, hd, int(causal), kv_len)
     _count()
     return out
 

@@ -271,3 +271,47 @@ def test_attention_prefill_and_decode(nh, nkv, hd, rot, T1, T2):
     close(out, ref, 3e-2)
     got_k = torch.stack([kpool[slot_of(p)] for p in range(T)]).cpu()
     close(got_k, kref, 2e-2)
+
+
+@pytest.mark.parametrize("M", [1, 3, 8])
+@pytest.mark.parametrize("N,Kd", [(520, 512), (2560, 1040), (37, 272)])
+def test_gemv_i8_w8a8(M, N, Kd):
+    k = K()
+    from coffin_b200.weights.quant import QWeight
+    W, x = bf(N, Kd, s=0.05, seed=50), bf(M, Kd, seed=51)
+    q = QWeight.quantize(W.float())
+    out = torch.empty(M, N, dtype=torch.float32, device=DEV)
+    k.gemv_i8(q.wq.to(DEV), q.scale.to(DEV), x.to(DEV), out)
+    close(out, O.w8a8_linear(x, q.wq, q.scale), 5e-3)
+    # fused norm + swiglu
+    I = N // 2
+    res, add = bf(M, Kd, seed=52), bf(M, Kd, seed=53)
+    gain = (1 + 0.1 * torch.randn(Kd)).float()
+    out2 = torch.empty(M, I, dtype=torch.bfloat16, device=DEV)
+    ro = torch.empty(M, Kd, dtype=torch.bfloat16, device=DEV)
+    k.gemv_i8(q.wq[:2 * I].to(DEV), q.scale[:2 * I].to(DEV), None, out2, swiglu=True,
+              norm=(res.to(DEV), add.to(DEV), gain.to(DEV), ro, 1e-6))
+    s_, n_ = O.add_rms_norm(res, add, gain)
+    gu = O.w8a8_linear(n_.to(torch.bfloat16), q.wq[:2 * I], q.scale[:2 * I])
+    close(ro, s_)
+    close(out2, O.silu_mul(gu[:, :I], gu[:, I:]), 3e-2)
+
+
+def test_quant_rows_and_i8_prefill_chain():
+    k = K()
+    from coffin_b200.weights.quant import QWeight
+    x = bf(70, 528, seed=60)
+    qx, sx = k.quant_rows(x.to(DEV))
+    rq, rs = O.quant_rows_int8(x, floor=1e-8)
+    assert (qx.cpu().int() - rq.int()).abs().max() <= 1 and torch.allclose(sx.cpu(), rs, rtol=1e-5)
+    W = bf(264, 528, s=0.05, seed=61)
+    q = QWeight.quantize(W.float())
+    out = k.gemm_i8(qx, sx, q.wq.to(DEV), q.scale.to(DEV))
+    torch.cuda.synchronize()
+    k.check_status()
+    close(out, O.w8a8_linear(x, q.wq, q.scale), 1e-2)
+    gu = bf(9, 2 * 264, seed=62)
+    qs, ss = k.quant_rows(gu.to(DEV), swiglu=True)
+    ref = O.silu_mul(gu[:, :264], gu[:, 264:]).to(torch.bfloat16)
+    rq2, rs2 = O.quant_rows_int8(ref, floor=1e-8)
+    assert (qs.cpu().int() - rq2.int()).abs().max() <= 1

@@ -147,7 +147,84 @@ def test_moe_router_kernel_matches_oracle():
     idx = torch.zeros(37, 8, dtype=torch.int32, device="cuda")
     w = torch.zeros(37, 8, device="cuda")
     lg = logits.cuda()
-    K.call("moe_router", lg, lg.stride(0), 37, 256, 8, 1, idx, w)
+    K.call("moe_router", lg, lg.stride(0), 37, 256, 8, 1, idx, w, 0, 256)
     ri, rw = O.moe_route(logits[:, :256], 8, True)
     assert torch.equal(idx.cpu().long(), ri)
     assert (w.cpu() - rw).abs().max() < 1e-5
+
+
+@torch.no_grad()
+def test_int8_w8a8_model_matches_oracle_with_quantised_weights():
+    """quant="int8": weights per-output-channel int8, activations per-token int8. The oracle runs
+    on the dequantised weights, so the remaining difference is the activation quantisation."""
+    from coffin_b200.models.qwen35.model import Qwen35Model
+    from coffin_b200.weights.quant import QWeight, is_quantizable
+    cfg = preset("tiny")
+    sd = random_state_dict(cfg, 0)
+    sd_q = {}
+    for k, v in sd.items():
+        vb = v.to(torch.bfloat16).float() if not k.endswith(("A_log", "dt_bias")) else v
+        sd_q[k] = QWeight.quantize(vb).dequant() if is_quantizable(k, v) else vb
+    sd_q["lm_head.weight"] = QWeight.quantize(sd_q["model.language_model.embed_tokens.weight"]).dequant()
+    oracle = OracleModel(cfg, sd_q)
+    model = Qwen35Model(cfg, sd, max_seq=512, num_slots=2, quant="int8")
+    toks = _tokens(cfg, 90, seed=31)
+    st = oracle.new_state()
+    ref = oracle.forward(toks[:80], st)[-1]
+    bt = torch.arange(1, 9, dtype=torch.int32, device="cuda")
+    model.zero_state(0)
+    got = model.prefill(toks[:80].cuda(), 0, 0, bt)
+    assert _rel(got, ref) < 8e-2
+    for i in range(80, 90):
+        ref = oracle.forward(toks[i:i + 1], st)[-1]
+        model.set_rows(1, [int(toks[i])], [i], [0], [bt.tolist()])
+        _, logits = model.decode(1, graph=i >= 84)
+        assert _rel(logits[0], ref) < 8e-2, f"step {i}"
+
+
+@torch.no_grad()
+def test_mtp_head_drafts_match_oracle():
+    from coffin_b200.models.qwen35.model import Qwen35Model
+    from coffin_b200.models.qwen35.mtp import MTPHead
+    cfg = preset("tiny")
+    sd = random_state_dict(cfg, 0, mtp=True)
+    sd_b = {k: (v.to(torch.bfloat16).float() if not k.endswith(("A_log", "dt_bias")) else v) for k, v in sd.items()}
+    oracle = OracleModel(cfg, sd_b)
+    model = Qwen35Model(cfg, sd, max_seq=256, num_slots=1)
+    head = MTPHead(model, sd)
+    toks = _tokens(cfg, 50, seed=41)
+    bt = torch.arange(1, 5, dtype=torch.int32, device="cuda")
+    # main prefill; the head's KV pairs token t+1 with the main hidden of position t
+    st = oracle.new_state()
+    oracle.forward(toks, st)
+    pre_ref = oracle._last_prenorm
+    model.zero_state(0)
+    model.prefill(toks.cuda(), 0, 0, bt, want_logits=False)
+    pre = model.last_prenorm[:50].clone()
+    assert _rel(pre, pre_ref) < 4e-2
+    head.prefill(toks[1:].cuda(), pre[:-1], 0, bt)
+    ref_logits, ref_h = oracle.mtp_forward(toks[1:], pre_ref[:-1], st, torch.arange(49))
+    # one more step: token 50 (say id 7) with the hidden of position 49 -> draft for position 51
+    nxt_tok = 7
+    lg, h = oracle.mtp_forward(torch.tensor([nxt_tok]), pre_ref[-1:], st, torch.tensor([49]))
+    got = head.draft(nxt_tok, pre[-1], 49, bt.tolist(), 1)
+    top2 = lg[0].topk(2).values
+    if top2[0] - top2[1] > 0.05:
+        assert got[0] == int(lg[0].argmax())
+    assert _rel(head.inner.final_hidden(1), h) < 6e-2
+
+
+@torch.no_grad()
+def test_vision_tower_matches_oracle():
+    from coffin_b200.models.qwen35.vision import (OracleVision, VisionTower, patchify, random_vision_state_dict,
+                                                  tiny_vision, VisionConfig)
+    for cfg in (tiny_vision(256), VisionConfig(depth=2, hidden_size=256, num_heads=2, intermediate_size=512,
+                                               out_hidden_size=256, num_position_embeddings=64)):
+        sd = random_vision_state_dict(cfg, std=0.05)
+        sd_b = {k: v.to(torch.bfloat16).float() for k, v in sd.items()}
+        img = torch.rand(3, 96, 160, generator=torch.Generator().manual_seed(1))
+        patches, grid = patchify(img, cfg)
+        ref = OracleVision(cfg, sd_b).forward(patches, grid)
+        got = VisionTower(cfg, sd).forward(patches, grid)
+        assert got.shape == ref.shape == (grid[1] * grid[2] // 4, 256)
+        assert _rel(got, ref) < 5e-2

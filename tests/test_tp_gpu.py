@@ -97,3 +97,76 @@ def test_two_rank_tensor_parallel_matches_oracle(tmp_path):
     ref = torch.stack(ref)
     rel = ((got["logits"] - ref).abs().amax(-1) / ref.abs().amax(-1)).max().item()
     assert rel < 4e-2, rel
+
+
+@torch.no_grad()
+def test_expert_parallel_push_path_on_one_gpu():
+    """MoE decode with the combine kernel pushing its output through the peer inbox (world 1)."""
+    from coffin_b200.models.qwen35.model import Qwen35Model
+    from coffin_b200.parallel.tp import TpComm
+    cfg = preset("tiny-moe")
+    sd = random_state_dict(cfg, 0)
+    plain = Qwen35Model(cfg, sd, max_seq=256, num_slots=2)
+    tp = TpComm(0, 1, cfg.hidden_size, 8, 2 * cfg.num_hidden_layers)
+    fused = Qwen35Model(cfg, sd, max_seq=256, num_slots=2, tp=tp)
+    fused.tp_force = True
+    g = torch.Generator().manual_seed(2)
+    toks = torch.randint(0, cfg.vocab_size, (40,), generator=g)
+    bt = torch.arange(1, 5, dtype=torch.int32, device="cuda")
+    for m in (plain, fused):
+        m.zero_state(0)
+        m.prefill(toks[:32].cuda(), 0, 0, bt, want_logits=False)
+    for i in range(32, 38):
+        outs = []
+        for m in (plain, fused):
+            m.set_rows(1, [int(toks[i])], [i], [0], [bt.tolist()])
+            outs.append(m.decode(1, graph=i >= 35)[1][0].clone())
+        rel = ((outs[0] - outs[1]).abs().max() / outs[0].abs().max()).item()
+        assert rel < 3e-2, f"step {i}: {rel}"
+    torch.cuda.synchronize()
+    assert tp.status() == 0
+    tp.close()
+
+
+def _ep_rank_main(rank, world, port, out):
+    import torch.distributed as dist
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    from coffin_b200.models import build_model
+    cfg = preset("tiny-moe")
+    sd = random_state_dict(cfg, 0)
+    model = build_model(cfg, sd, device=f"cuda:{rank}", max_seq=256, num_slots=2, ep_world=world, ep_rank=rank)
+    g = torch.Generator().manual_seed(2)
+    toks = torch.randint(0, cfg.vocab_size, (84,), generator=g)
+    bt = torch.arange(1, 5, dtype=torch.int32, device=f"cuda:{rank}")
+    model.zero_state(0)
+    logits = [model.prefill(toks[:72].cuda(), 0, 0, bt).float().cpu()]
+    for i in range(72, 84):
+        model.set_rows(1, [int(toks[i])], [i], [0], [bt.tolist()])
+        logits.append(model.decode(1, graph=i >= 76)[1][0].float().cpu())
+    torch.cuda.synchronize()
+    status = model.tp.status()
+    dist.barrier()
+    if rank == 0:
+        torch.save({"logits": torch.stack(logits), "status": status}, out)
+    dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_two_rank_expert_parallel_matches_oracle(tmp_path):
+    import torch.multiprocessing as mp
+    out = str(tmp_path / "ep.pt")
+    mp.spawn(_ep_rank_main, args=(2, _free_port(), out), nprocs=2, join=True)
+    got = torch.load(out)
+    assert got["status"] == 0
+    cfg = preset("tiny-moe")
+    sd = random_state_dict(cfg, 0)
+    sd_b = {k: (v.to(torch.bfloat16).float() if not k.endswith(("A_log", "dt_bias")) else v) for k, v in sd.items()}
+    oracle = OracleModel(cfg, sd_b)
+    g = torch.Generator().manual_seed(2)
+    toks = torch.randint(0, cfg.vocab_size, (84,), generator=g)
+    st = oracle.new_state()
+    ref = torch.stack([oracle.forward(toks[:72], st)[-1]] + [oracle.forward(toks[i:i + 1], st)[-1] for i in range(72, 84)])
+    rel = ((got["logits"] - ref).abs().amax(-1) / ref.abs().amax(-1)).max().item()
+    assert rel < 8e-2, rel
