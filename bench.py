@@ -103,6 +103,9 @@ def main() -> None:
     ap.add_argument("--no-pdl", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--mma-ctas", type=int, default=0, help="tuning: tensor-core GEMV CTAs per SM")
+    ap.add_argument("--mma-stage", type=int, default=-1, help="tuning: GEMV weight batches per warp staged in shared memory before the wait")
+    ap.add_argument("--mma-kcta", type=int, default=0, help="tuning: max CTAs sharing one 16-row GEMV block (1 = off)")
+    ap.add_argument("--mma-prefetch", type=int, default=-1, help="tuning: GEMV sweep rounds prefetched into L2 before the dependency wait")
     ap.add_argument("--gemv-impl", default="", help="tuning: mma | scalar")
     ap.add_argument("--no-stream-gemv", action="store_true", help="tuning: register-staged GEMV for batch 1")
     ap.add_argument("--gemv-ctas", type=int, default=0, help="tuning: GEMV CTAs per SM (0 = library default)")
@@ -131,6 +134,15 @@ def main() -> None:
         K.STREAM_GEMV = False
     if args.gemv_impl:
         K.GEMV_IMPL = args.gemv_impl
+    if args.mma_stage >= 0:
+        from coffin_b200.ops import _lib as _l4
+        _l4.call_nostream("set_mma_gemv_stage", args.mma_stage)
+    if args.mma_kcta:
+        from coffin_b200.ops import _lib as _l3
+        _l3.call_nostream("set_mma_gemv_kcta", args.mma_kcta)
+    if args.mma_prefetch >= 0:
+        from coffin_b200.ops import _lib as _l2
+        _l2.call_nostream("set_mma_gemv_prefetch", args.mma_prefetch)
     if args.mma_ctas:
         from coffin_b200.ops import _lib as _l
         _l.call_nostream("set_mma_gemv_opts", args.mma_ctas)

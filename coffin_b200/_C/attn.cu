@@ -7,7 +7,7 @@
 //  * attn_decode:  one query per row, split over key tiles; the CTA that owns the tile holding
 //                  the current position also norms/rotates/appends this token's K/V, so a decode
 //                  layer needs no separate rope / kv-store launches.
-//  * attn_combine: merges the split partials and applies the gate.
+//    (the last split of a group to arrive merges the partials and applies the gate).
 // The reference has decode kernels (backends/corex/kernels/attn.cu:370-566: slice + combine over
 // an int8 cache through pos2slot) but prefill attention is torch code
 // (models/qwen35/full_attn.py:658-789); rope, kv_quant and kv_pool_store are separate launches
@@ -130,6 +130,9 @@ struct PrefillArgs {
   float scale_log2;         // hd^-0.5 * log2(e)
   int causal;               // 1: key s visible to query position p when s <= p; 0: all kv_len keys (vision)
   int kv_len;               // non-causal: number of valid keys
+  // block-selected attention: bit b of keep[t] says whether query t reads the block of (1 << ratio_log2)
+  // tokens number b; tokens after a query's last complete block are always read.  null = dense.
+  const unsigned* keep; int keep_words, ratio_log2;
 };
 
 template <int HD>
@@ -189,13 +192,26 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(const PrefillArgs a) 
     }
     // ---- mask + online softmax (base-2) --------------------------------------------------
     float mnew[2] = {mrow[0], mrow[1]};
+    unsigned kbits[2] = {0xffffffffu, 0xffffffffu};
+    if (a.keep) {
+      const int fb = kt * (kBlock >> a.ratio_log2);          // first block of this tile
+#pragma unroll
+      for (int hh = 0; hh < 2; ++hh) {
+        const int t = qt * 64 + warp * 16 + g + hh * 8;
+        kbits[hh] = t < a.T ? a.keep[(int64_t)t * a.keep_words + (fb >> 5)] >> (fb & 31) : 0u;
+      }
+    }
 #pragma unroll
     for (int n = 0; n < 8; ++n)
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         const int key = kt * kBlock + n * 8 + tq * 2 + (e & 1);
         const int qp = qpos_lo + ((e >> 1) << 3);
-        const bool vis = a.causal ? (key <= qp) : (key < a.kv_len);
+        bool vis = a.causal ? (key <= qp) : (key < a.kv_len);
+        if (a.keep) {
+          const int tail0 = ((qp + 1) >> a.ratio_log2) << a.ratio_log2;
+          vis = vis && (key >= tail0 || ((kbits[e >> 1] >> ((n * 8 + tq * 2 + (e & 1)) >> a.ratio_log2)) & 1u));
+        }
         const float v = vis ? s[n][e] * a.scale_log2 : -INFINITY;
         s[n][e] = v;
         mnew[e >> 1] = fmaxf(mnew[e >> 1], v);
@@ -279,14 +295,45 @@ struct DecodeArgs {
   float scale_log2, eps;
   unsigned* tickets;                  // [M, nkv] arrival counters (zero between launches)
   bf16* out; int64_t ldo;             // [M, nh*hd] gated output, written by the last split to arrive
+  // sparse mode (block-selected attention): queries come normed and rotated from q_in, K/V of the
+  // current token are already in the pool, and row m attends to the blocks sel[m, 0..nsel[m]) of
+  // `ratio` tokens plus the tokens after its last complete block (nsel[m] < 0: every visible token)
+  const bf16* q_in; const int* sel; const int* nsel; int topk, ratio;
 };
 
-template <int HD, int REP>
-__global__ void __launch_bounds__(128) attn_decode_kernel(const DecodeArgs a) {
+constexpr int kDecWarps = 8;          // warps per decode CTA; each takes 4 keys per iteration
+constexpr int kDecKeys = 4;
+
+// EPL bf16 channels of one lane as packed 32-bit words (kept packed while in flight: half the registers)
+template <int EPL>
+__device__ __forceinline__ void dec_load(const bf16* p, uint32_t* w) {
+  if (EPL == 8) {
+    const uint4 v = ld_stream(p);
+    w[0] = v.x; w[1] = v.y; w[2] = v.z; w[3] = v.w;
+  } else {
+#pragma unroll
+    for (int e = 0; e < EPL / 2; ++e) w[e] = reinterpret_cast<const uint32_t*>(p)[e];
+  }
+}
+__device__ __forceinline__ float bf_lo(uint32_t w) { return __uint_as_float(w << 16); }
+__device__ __forceinline__ float bf_hi(uint32_t w) { return __uint_as_float(w & 0xffff0000u); }
+
+// Split-KV decode attention for one (kv head, split, batch row).  Eight warps walk the split's keys
+// four at a time each, with the next four keys' K and V rows already requested while the current
+// ones are scored, so that a CTA keeps ~16 KB in flight; lanes own HD/32 consecutive channels.  The
+// warps merge pairwise through shared memory, the CTA writes one partial (o, m, l) per query head,
+// and the last split of the (row, kv head) group to arrive merges all partials with every thread
+// owning four channels of one head (independent float4 loads, scales staged in shared memory),
+// applies the sigmoid gate and writes the bf16 output.
+template <int HD, int REP, bool SPARSE>
+__global__ void __launch_bounds__(kDecWarps * 32) attn_decode_kernel(const DecodeArgs a) {
   constexpr int EPL = HD / 32;
+  constexpr int NT = kDecWarps * 32;
   __shared__ float q_s[REP][HD];
-  __shared__ float mo[4][REP][HD];
-  __shared__ float mml[4][REP][2];
+  __shared__ __align__(16) float mo[kDecWarps / 2][REP][HD];
+  __shared__ float mml[kDecWarps / 2][REP][2];
+  __shared__ float sc_s[REP][64];                 // per-split scales of the final merge (nsplit <= 64)
+  __shared__ float linv_s[REP];
   const int kvh = blockIdx.x, split = blockIdx.y, m = blockIdx.z;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   griddep_launch();
@@ -295,44 +342,48 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const DecodeArgs a) {
   float* po = a.part_o + (((int64_t)m * a.nh + kvh * REP) * a.nsplit + split) * HD;
   float* pml = a.part_ml + (((int64_t)m * a.nh + kvh * REP) * a.nsplit + split) * 2;
   if (pos < 0) {  // padded row
-    for (int i = tid; i < REP * 2; i += 128) pml[(int64_t)(i >> 1) * a.nsplit * 2 + (i & 1)] = (i & 1) ? 0.f : -INFINITY;
+    for (int i = tid; i < REP * 2; i += NT) pml[(int64_t)(i >> 1) * a.nsplit * 2 + (i & 1)] = (i & 1) ? 0.f : -INFINITY;
     return;
   }
   const bf16* prow = a.proj + (int64_t)m * a.ldp;
-  const int rp = a.rope_pos[m];
+  const int rp = SPARSE ? 0 : a.rope_pos[m];
   const float* cs = a.cos + (int64_t)rp * a.rot;
   const float* sn = a.sin + (int64_t)rp * a.rot;
-  // q heads of this kv group: norm + rope -> shared (pre-scaled for base-2 softmax)
-  for (int r = warp; r < REP; r += 4) {
-    float x[EPL];
-    const bf16* src = prow + (int64_t)(kvh * REP + r) * 2 * HD + lane * EPL;
-#pragma unroll
-    for (int e = 0; e < EPL; ++e) x[e] = __bfloat162float(src[e]);
-    norm_rope_lane<HD>(x, a.qg, cs, sn, a.rot, a.eps, lane);
-#pragma unroll
-    for (int e = 0; e < EPL; ++e) q_s[r][lane * EPL + e] = x[e] * a.scale_log2;
-  }
-  const int ntiles = pos / kBlock + 1;
   const int* bt = a.block_table + (int64_t)m * a.ldbt;
-  // the split that owns the tile holding `pos` appends this token's K/V first
-  if ((pos / kBlock) % a.nsplit == split) {
-    const int64_t slot = (int64_t)bt[pos / kBlock] * kBlock + pos % kBlock;
-    if (warp == 0) {
+  if (SPARSE) {
+    for (int i = tid; i < REP * HD; i += NT)
+      q_s[i / HD][i % HD] = __bfloat162float(a.q_in[((int64_t)m * a.nh + kvh * REP) * HD + i]) * a.scale_log2;
+  } else {
+    // q heads of this kv group: norm + rope -> shared (pre-scaled for base-2 softmax)
+    for (int r = warp; r < REP; r += kDecWarps) {
       float x[EPL];
-      const bf16* src = prow + (int64_t)a.nh * 2 * HD + (int64_t)kvh * HD + lane * EPL;
+      const bf16* src = prow + (int64_t)(kvh * REP + r) * 2 * HD + lane * EPL;
 #pragma unroll
       for (int e = 0; e < EPL; ++e) x[e] = __bfloat162float(src[e]);
-      norm_rope_lane<HD>(x, a.kg, cs, sn, a.rot, a.eps, lane);
-      bf16* dst = a.kpool + (slot * a.nkv + kvh) * HD + lane * EPL;
+      norm_rope_lane<HD>(x, a.qg, cs, sn, a.rot, a.eps, lane);
 #pragma unroll
-      for (int e = 0; e < EPL; ++e) dst[e] = __float2bfloat16(x[e]);
-    } else if (warp == 1) {
-      const bf16* src = prow + (int64_t)a.nh * 2 * HD + (int64_t)(a.nkv + kvh) * HD + lane * EPL;
-      bf16* dst = a.vpool + (slot * a.nkv + kvh) * HD + lane * EPL;
-#pragma unroll
-      for (int e = 0; e < EPL; ++e) dst[e] = src[e];
+      for (int e = 0; e < EPL; ++e) q_s[r][lane * EPL + e] = x[e] * a.scale_log2;
     }
-    __threadfence_block();
+    // the split that owns the tile holding `pos` appends this token's K/V first
+    if ((pos / kBlock) % a.nsplit == split) {
+      const int64_t slot = (int64_t)bt[pos / kBlock] * kBlock + pos % kBlock;
+      if (warp == kDecWarps - 1) {
+        float x[EPL];
+        const bf16* src = prow + (int64_t)a.nh * 2 * HD + (int64_t)kvh * HD + lane * EPL;
+#pragma unroll
+        for (int e = 0; e < EPL; ++e) x[e] = __bfloat162float(src[e]);
+        norm_rope_lane<HD>(x, a.kg, cs, sn, a.rot, a.eps, lane);
+        bf16* dst = a.kpool + (slot * a.nkv + kvh) * HD + lane * EPL;
+#pragma unroll
+        for (int e = 0; e < EPL; ++e) dst[e] = __float2bfloat16(x[e]);
+      } else if (warp == kDecWarps - 2) {
+        const bf16* src = prow + (int64_t)a.nh * 2 * HD + (int64_t)(a.nkv + kvh) * HD + lane * EPL;
+        bf16* dst = a.vpool + (slot * a.nkv + kvh) * HD + lane * EPL;
+#pragma unroll
+        for (int e = 0; e < EPL; ++e) dst[e] = src[e];
+      }
+      __threadfence_block();
+    }
   }
   __syncthreads();
   float q[REP][EPL], o[REP][EPL], mx[REP], l[REP];
@@ -342,73 +393,143 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const DecodeArgs a) {
 #pragma unroll
     for (int e = 0; e < EPL; ++e) { q[r][e] = q_s[r][lane * EPL + e]; o[r][e] = 0.f; }
   }
-  for (int kt = split; kt < ntiles; kt += a.nsplit) {
-    const int64_t slot0 = (int64_t)bt[kt] * kBlock;
-    const int nkeys = min(kBlock, pos + 1 - kt * kBlock);
-    for (int i0 = warp; i0 < nkeys; i0 += 8) {
-      // two keys per iteration for memory-level parallelism
-      const int i1 = i0 + 4;
-      const bool has1 = i1 < nkeys;
-      float kf0[EPL], kf1[EPL], vf0[EPL], vf1[EPL];
-      const bf16* k0 = a.kpool + ((slot0 + i0) * a.nkv + kvh) * HD + lane * EPL;
-      const bf16* v0 = a.vpool + ((slot0 + i0) * a.nkv + kvh) * HD + lane * EPL;
-      const bf16* k1 = has1 ? a.kpool + ((slot0 + i1) * a.nkv + kvh) * HD + lane * EPL : k0;
-      const bf16* v1 = has1 ? a.vpool + ((slot0 + i1) * a.nkv + kvh) * HD + lane * EPL : v0;
-      if (EPL == 8) {
-        bf16x8_to_float(*reinterpret_cast<const uint4*>(k0), kf0);
-        bf16x8_to_float(*reinterpret_cast<const uint4*>(k1), kf1);
-        bf16x8_to_float(*reinterpret_cast<const uint4*>(v0), vf0);
-        bf16x8_to_float(*reinterpret_cast<const uint4*>(v1), vf1);
-      } else {
+  // keys of this split, numbered j.  Dense: j = local tile * 64 + offset, tiles strided over the
+  // splits.  Sparse: the row's kept tokens (selected blocks, then the ragged tail) form one virtual
+  // list that the splits cut into equal contiguous pieces.
+  const int ntiles = pos / kBlock + 1;
+  int nj, j_base = 0, n_sel = 0, tail0 = 0;
+  if (SPARSE) {
+    n_sel = a.nsel[m];
+    const int nb = (pos + 1) / a.ratio;
+    tail0 = nb * a.ratio;
+    const int total = n_sel < 0 ? pos + 1 : n_sel * a.ratio + (pos + 1 - tail0);
+    int chunk = (total + a.nsplit - 1) / a.nsplit;
+    chunk = (chunk + kDecWarps * kDecKeys - 1) / (kDecWarps * kDecKeys) * (kDecWarps * kDecKeys);
+    j_base = split * chunk;
+    nj = max(0, min(chunk, total - j_base));
+  } else {
+    const int nloc = split < ntiles ? (ntiles - 1 - split) / a.nsplit + 1 : 0;
+    nj = nloc * kBlock;
+  }
+  auto key_row = [&](int j, bool& ok) -> int64_t {
+    if (SPARSE) {
+      ok = j < nj;
+      if (!ok) return 0;
+      const int jj = j_base + j;
+      int tok;
+      if (n_sel < 0) tok = jj;
+      else if (jj < n_sel * a.ratio) tok = a.sel[(int64_t)m * a.topk + jj / a.ratio] * a.ratio + jj % a.ratio;
+      else tok = tail0 + (jj - n_sel * a.ratio);
+      return ((int64_t)bt[tok / kBlock] * kBlock + tok % kBlock) * a.nkv + kvh;
+    }
+    const int kt = split + (j / kBlock) * a.nsplit;
+    const int i = j % kBlock;
+    ok = j < nj && kt * kBlock + i <= pos;
+    return ok ? ((int64_t)bt[kt] * kBlock + i) * a.nkv + kvh : 0;
+  };
+  constexpr int WPL = EPL / 2;
+  uint32_t kfa[kDecKeys][WPL], vfa[kDecKeys][WPL], kfb[kDecKeys][WPL], vfb[kDecKeys][WPL];
+  bool oka[kDecKeys], okb[kDecKeys];
+  auto fetch = [&](int it, uint32_t (&kf)[kDecKeys][WPL], uint32_t (&vf)[kDecKeys][WPL], bool (&okk)[kDecKeys]) {
 #pragma unroll
-        for (int e = 0; e < EPL; ++e) {
-          kf0[e] = __bfloat162float(k0[e]); kf1[e] = __bfloat162float(k1[e]);
-          vf0[e] = __bfloat162float(v0[e]); vf1[e] = __bfloat162float(v1[e]);
-        }
+    for (int u = 0; u < kDecKeys; ++u) {
+      const int64_t row = key_row(it * (kDecWarps * kDecKeys) + warp * kDecKeys + u, okk[u]);
+      if (okk[u]) {
+        dec_load<EPL>(a.kpool + row * HD + lane * EPL, kf[u]);
+        dec_load<EPL>(a.vpool + row * HD + lane * EPL, vf[u]);
       }
+    }
+  };
+  auto score = [&](const uint32_t (&kf)[kDecKeys][WPL], const uint32_t (&vf)[kDecKeys][WPL], const bool (&okk)[kDecKeys]) {
+#pragma unroll
+    for (int r = 0; r < REP; ++r) {
+      float d[kDecKeys];
+#pragma unroll
+      for (int u = 0; u < kDecKeys; ++u) {
+        float sdot = 0.f;
+        if (okk[u]) {
+#pragma unroll
+          for (int e = 0; e < WPL; ++e) {
+            sdot = fmaf(q[r][2 * e], bf_lo(kf[u][e]), sdot);
+            sdot = fmaf(q[r][2 * e + 1], bf_hi(kf[u][e]), sdot);
+          }
+        }
+        d[u] = sdot;
+      }
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1) {
+#pragma unroll
+        for (int u = 0; u < kDecKeys; ++u) d[u] += __shfl_xor_sync(0xffffffffu, d[u], off);
+      }
+      float mn = mx[r];
+#pragma unroll
+      for (int u = 0; u < kDecKeys; ++u) {
+        if (!okk[u]) d[u] = -INFINITY;
+        mn = fmaxf(mn, d[u]);
+      }
+      if (mn == -INFINITY) continue;
+      const float c = exp2f(mx[r] - mn);
+      float p[kDecKeys], ps = 0.f;
+#pragma unroll
+      for (int u = 0; u < kDecKeys; ++u) { p[u] = exp2f(d[u] - mn); ps += p[u]; }
+      l[r] = l[r] * c + ps;
+      mx[r] = mn;
+#pragma unroll
+      for (int e = 0; e < WPL; ++e) {
+        float a0 = o[r][2 * e] * c, a1 = o[r][2 * e + 1] * c;
+#pragma unroll
+        for (int u = 0; u < kDecKeys; ++u)
+          if (okk[u]) { a0 = fmaf(p[u], bf_lo(vf[u][e]), a0); a1 = fmaf(p[u], bf_hi(vf[u][e]), a1); }
+        o[r][2 * e] = a0; o[r][2 * e + 1] = a1;
+      }
+    }
+  };
+  // two register buffers, named (not indexed) so that they stay in registers
+  const int niter = (nj + kDecWarps * kDecKeys - 1) / (kDecWarps * kDecKeys);
+  if (niter > 0) fetch(0, kfa, vfa, oka);
+  for (int it = 0; it < niter; it += 2) {
+    if (it + 1 < niter) fetch(it + 1, kfb, vfb, okb);
+    score(kfa, vfa, oka);
+    if (it + 1 >= niter) break;
+    if (it + 2 < niter) fetch(it + 2, kfa, vfa, oka);
+    score(kfb, vfb, okb);
+  }
+  // ---- merge the warps pairwise through shared memory -------------------------------------------
+#pragma unroll
+  for (int step = kDecWarps / 2; step > 0; step >>= 1) {
+    if (warp >= step && warp < 2 * step) {
 #pragma unroll
       for (int r = 0; r < REP; ++r) {
-        float d0 = 0.f, d1 = 0.f;
 #pragma unroll
-        for (int e = 0; e < EPL; ++e) { d0 = fmaf(q[r][e], kf0[e], d0); d1 = fmaf(q[r][e], kf1[e], d1); }
-        d0 = warp_sum(d0);
-        d1 = has1 ? warp_sum(d1) : -INFINITY;
-        if (!has1) d1 = -INFINITY;
-        const float mn = fmaxf(mx[r], fmaxf(d0, d1));
-        const float c = exp2f(mx[r] - mn), p0 = exp2f(d0 - mn), p1 = exp2f(d1 - mn);
-        l[r] = l[r] * c + p0 + p1;
+        for (int e = 0; e < EPL; ++e) mo[warp - step][r][lane * EPL + e] = o[r][e];
+        if (lane == 0) { mml[warp - step][r][0] = mx[r]; mml[warp - step][r][1] = l[r]; }
+      }
+    }
+    __syncthreads();
+    if (warp < step) {
+#pragma unroll
+      for (int r = 0; r < REP; ++r) {
+        const float m2 = mml[warp][r][0], l2 = mml[warp][r][1];
+        const float mn = fmaxf(mx[r], m2);
+        const float c1 = mn == -INFINITY ? 0.f : exp2f(mx[r] - mn);
+        const float c2 = mn == -INFINITY ? 0.f : exp2f(m2 - mn);
+#pragma unroll
+        for (int e = 0; e < EPL; ++e) o[r][e] = o[r][e] * c1 + mo[warp][r][lane * EPL + e] * c2;
+        l[r] = l[r] * c1 + l2 * c2;
         mx[r] = mn;
-#pragma unroll
-        for (int e = 0; e < EPL; ++e) o[r][e] = o[r][e] * c + p0 * vf0[e] + p1 * vf1[e];
       }
     }
+    __syncthreads();
   }
-  // ---- merge the 4 warps ------------------------------------------------------------------
+  if (warp == 0) {
 #pragma unroll
-  for (int r = 0; r < REP; ++r) {
+    for (int r = 0; r < REP; ++r) {
 #pragma unroll
-    for (int e = 0; e < EPL; ++e) mo[warp][r][lane * EPL + e] = o[r][e];
-    if (lane == 0) { mml[warp][r][0] = mx[r]; mml[warp][r][1] = l[r]; }
-  }
-  __syncthreads();
-  for (int idx = tid; idx < REP * HD; idx += 128) {
-    const int r = idx / HD, d = idx % HD;
-    float M4 = -INFINITY;
-#pragma unroll
-    for (int w = 0; w < 4; ++w) M4 = fmaxf(M4, mml[w][r][0]);
-    float acc = 0.f, L = 0.f;
-    if (M4 > -INFINITY) {
-#pragma unroll
-      for (int w = 0; w < 4; ++w) {
-        const float c = exp2f(mml[w][r][0] - M4);
-        acc += mo[w][r][d] * c;
-        L += mml[w][r][1] * c;
+      for (int e = 0; e < EPL; ++e) po[(int64_t)r * a.nsplit * HD + lane * EPL + e] = o[r][e];
+      if (lane == 0) {
+        pml[(int64_t)r * a.nsplit * 2] = mx[r];
+        pml[(int64_t)r * a.nsplit * 2 + 1] = l[r];
       }
-    }
-    po[(int64_t)r * a.nsplit * HD + d] = acc;
-    if (d == 0) {
-      pml[(int64_t)r * a.nsplit * 2] = M4;
-      pml[(int64_t)r * a.nsplit * 2 + 1] = L;
     }
   }
   // ---- the last split of this (row, kv head) to arrive merges all splits and applies the gate ----
@@ -425,99 +546,52 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const DecodeArgs a) {
   __threadfence();
   const float* bo = a.part_o + ((int64_t)m * a.nh + kvh * REP) * a.nsplit * HD;
   const float* bml = a.part_ml + ((int64_t)m * a.nh + kvh * REP) * a.nsplit * 2;
-  for (int idx = tid; idx < REP * HD; idx += 128) {
-    const int r = idx / HD, d = idx % HD;
-    const float* pm = bml + (int64_t)r * a.nsplit * 2;
+  const int ns = a.nsplit;
+  for (int i = tid; i < REP * ns; i += NT) sc_s[i / ns][i % ns] = __ldcg(bml + (int64_t)i * 2);       // m of (r, sp)
+  __syncthreads();
+  if (tid < REP) {
     float Mx = -INFINITY;
-    for (int sp = 0; sp < a.nsplit; ++sp) Mx = fmaxf(Mx, __ldcg(pm + sp * 2));
-    float acc = 0.f, L = 0.f;
-    if (Mx > -INFINITY)
-      for (int sp = 0; sp < a.nsplit; ++sp) {
-        const float c = exp2f(__ldcg(pm + sp * 2) - Mx);
-        acc += __ldcg(bo + ((int64_t)r * a.nsplit + sp) * HD + d) * c;
-        L += __ldcg(pm + sp * 2 + 1) * c;
-      }
-    const int h = kvh * REP + r;
-    const float gt = sigmoid_f(__bfloat162float(prow[(int64_t)h * 2 * HD + HD + d]));
-    a.out[(int64_t)m * a.ldo + (int64_t)h * HD + d] = __float2bfloat16(L > 0.f ? acc / L * gt : 0.f);
-  }
-}
-
-template <int HD>
-__global__ void __launch_bounds__(HD) attn_combine_kernel(const float* part_o, const float* part_ml,
-                                                          const bf16* proj, int64_t ldp, bf16* out, int64_t ldo,
-                                                          int nh, int nsplit) {
-  griddep_launch();
-  griddep_wait();
-  const int h = blockIdx.x, m = blockIdx.y, d = threadIdx.x;
-  const float* po = part_o + ((int64_t)m * nh + h) * nsplit * HD;
-  const float* pml = part_ml + ((int64_t)m * nh + h) * nsplit * 2;
-  float M = -INFINITY;
-  for (int s = 0; s < nsplit; ++s) M = fmaxf(M, pml[s * 2]);
-  float acc = 0.f, L = 0.f;
-  if (M > -INFINITY)
-    for (int s = 0; s < nsplit; ++s) {
-      const float c = exp2f(pml[s * 2] - M);
-      acc += po[(int64_t)s * HD + d] * c;
-      L += pml[s * 2 + 1] * c;
+    for (int sp = 0; sp < ns; ++sp) Mx = fmaxf(Mx, sc_s[tid][sp]);
+    float L = 0.f;
+    for (int sp = 0; sp < ns; ++sp) {
+      const float c = Mx == -INFINITY ? 0.f : exp2f(sc_s[tid][sp] - Mx);
+      sc_s[tid][sp] = c;
+      L += __ldcg(bml + ((int64_t)tid * ns + sp) * 2 + 1) * c;
     }
-  const float g = sigmoid_f(__bfloat162float(proj[(int64_t)m * ldp + (int64_t)h * 2 * HD + HD + d]));
-  out[(int64_t)m * ldo + (int64_t)h * HD + d] = __float2bfloat16(L > 0.f ? acc / L * g : 0.f);
+    linv_s[tid] = L > 0.f ? 1.f / L : 0.f;
+  }
+  __syncthreads();
+  for (int idx = tid; idx < REP * (HD / 4); idx += NT) {
+    const int r = idx / (HD / 4), d = (idx % (HD / 4)) * 4;
+    const float* src = bo + (int64_t)r * ns * HD + d;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 8
+    for (int sp = 0; sp < ns; ++sp) {
+      const float4 v = __ldcg(reinterpret_cast<const float4*>(src + (int64_t)sp * HD));
+      const float c = sc_s[r][sp];
+      acc.x = fmaf(v.x, c, acc.x); acc.y = fmaf(v.y, c, acc.y); acc.z = fmaf(v.z, c, acc.z); acc.w = fmaf(v.w, c, acc.w);
+    }
+    const int h = kvh * REP + r;
+    const bf16* gp = prow + (int64_t)h * 2 * HD + HD + d;
+    const float li = linv_s[r];
+    bf16* dst = a.out + (int64_t)m * a.ldo + (int64_t)h * HD + d;
+    dst[0] = __float2bfloat16(acc.x * li * sigmoid_f(__bfloat162float(gp[0])));
+    dst[1] = __float2bfloat16(acc.y * li * sigmoid_f(__bfloat162float(gp[1])));
+    dst[2] = __float2bfloat16(acc.z * li * sigmoid_f(__bfloat162float(gp[2])));
+    dst[3] = __float2bfloat16(acc.w * li * sigmoid_f(__bfloat162float(gp[3])));
+  }
 }
 
 template <int HD, int REP>
 int launch_decode(const DecodeArgs& a, int M, cudaStream_t st) {
-  return (int)cb_launch(attn_decode_kernel<HD, REP>, dim3((unsigned)a.nkv, (unsigned)a.nsplit, (unsigned)M),
-                        dim3(128), 0, st, a);
+  if (a.sel)
+    return (int)cb_launch(attn_decode_kernel<HD, REP, true>, dim3((unsigned)a.nkv, (unsigned)a.nsplit, (unsigned)M),
+                          dim3(kDecWarps * 32), 0, st, a);
+  return (int)cb_launch(attn_decode_kernel<HD, REP, false>, dim3((unsigned)a.nkv, (unsigned)a.nsplit, (unsigned)M),
+                        dim3(kDecWarps * 32), 0, st, a);
 }
 
-}  // namespace
-
-CB_EXPORT int cb_attn_prep(const void* proj, int64_t ldp, const void* qg, const void* kg, const void* cos,
-                           const void* sin, const void* rope_idx, const void* kv_slot, void* q_out,
-                           void* kpool, void* vpool, int64_t T, int64_t nh, int64_t nkv, int64_t hd,
-                           int64_t rot, float eps, void* stream) {
-  if (T == 0) return 0;
-  PrepArgs a{(const bf16*)proj, ldp, (const float*)qg, (const float*)kg, (const float*)cos, (const float*)sin,
-             (const int*)rope_idx, (const int*)kv_slot, (bf16*)q_out, (bf16*)kpool, (bf16*)vpool,
-             (int)T, (int)nh, (int)nkv, (int)rot, eps};
-  const int64_t tasks = T * (nh + 2 * nkv);
-  dim3 grid((unsigned)((tasks + 7) / 8));
-  if (hd == 256 && (rot / 2) % 8 == 0) return (int)cb_launch(attn_prep_kernel<256>, grid, dim3(256), 0, (cudaStream_t)stream, a);
-  if (hd == 64 && (rot / 2) % 2 == 0) return (int)cb_launch(attn_prep_kernel<64>, grid, dim3(256), 0, (cudaStream_t)stream, a);
-  return CB_ERR_SHAPE;
-}
-
-CB_EXPORT int cb_attn_prefill(const void* q, const void* gate, int64_t ldg, const void* kpool, const void* vpool,
-                              const void* block_table, void* out, int64_t ldo, int64_t T, int64_t q_pos0,
-                              int64_t nh, int64_t nkv, int64_t hd, int64_t causal, int64_t kv_len, void* stream) {
-  if (T == 0) return 0;
-  PrefillArgs a{(const bf16*)q, (const bf16*)gate, ldg, (const bf16*)kpool, (const bf16*)vpool,
-                (const int*)block_table, (bf16*)out, ldo, (int)T, (int)q_pos0, (int)nh, (int)nkv,
-                1.4426950408889634f / sqrtf((float)hd), (int)causal, (int)kv_len};
-  dim3 grid((unsigned)((T + 63) / 64), (unsigned)nh);
-  const size_t smem = (size_t)3 * 64 * (hd + 8) * sizeof(bf16);
-  cudaError_t e;
-  if (hd == 256) {
-    e = cudaFuncSetAttribute(attn_prefill_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return (int)e;
-    return (int)cb_launch(attn_prefill_kernel<256>, grid, dim3(128), smem, (cudaStream_t)stream, a);
-  }
-  if (hd == 64) return (int)cb_launch(attn_prefill_kernel<64>, grid, dim3(128), smem, (cudaStream_t)stream, a);
-  return CB_ERR_SHAPE;
-}
-
-CB_EXPORT int cb_attn_decode(const void* proj, int64_t ldp, const void* qg, const void* kg, const void* cos,
-                             const void* sin, const void* positions, const void* rope_pos,
-                             const void* block_table, int64_t ldbt, void* kpool, void* vpool, void* part_o,
-                             void* part_ml, void* tickets, void* out, int64_t ldo, int64_t M, int64_t nh, int64_t nkv,
-                             int64_t hd, int64_t rot, int64_t nsplit, float eps, void* stream) {
-  if (M == 0) return 0;
-  if (nh % nkv || nsplit < 1 || !tickets) return CB_ERR_SHAPE;
-  DecodeArgs a{(const bf16*)proj, ldp, (const float*)qg, (const float*)kg, (const float*)cos, (const float*)sin,
-               (const int*)positions, (const int*)rope_pos, (const int*)block_table, ldbt, (bf16*)kpool,
-               (bf16*)vpool, (float*)part_o, (float*)part_ml, (int)nh, (int)nkv, (int)rot, (int)nsplit,
-               1.4426950408889634f / sqrtf((float)hd), eps, (unsigned*)tickets, (bf16*)out, ldo};
+int decode_dispatch(const DecodeArgs& a, int64_t M, int64_t nh, int64_t nkv, int64_t hd, int64_t rot, void* stream) {
   cudaStream_t st = (cudaStream_t)stream;
   const int rep = (int)(nh / nkv);
   int rc = CB_ERR_SHAPE;
@@ -540,4 +614,78 @@ CB_EXPORT int cb_attn_decode(const void* proj, int64_t ldp, const void* qg, cons
     }
   }
   return rc;
+}
+
+}  // namespace
+
+CB_EXPORT int cb_attn_prep(const void* proj, int64_t ldp, const void* qg, const void* kg, const void* cos,
+                           const void* sin, const void* rope_idx, const void* kv_slot, void* q_out,
+                           void* kpool, void* vpool, int64_t T, int64_t nh, int64_t nkv, int64_t hd,
+                           int64_t rot, float eps, void* stream) {
+  if (T == 0) return 0;
+  PrepArgs a{(const bf16*)proj, ldp, (const float*)qg, (const float*)kg, (const float*)cos, (const float*)sin,
+             (const int*)rope_idx, (const int*)kv_slot, (bf16*)q_out, (bf16*)kpool, (bf16*)vpool,
+             (int)T, (int)nh, (int)nkv, (int)rot, eps};
+  const int64_t tasks = T * (nh + 2 * nkv);
+  dim3 grid((unsigned)((tasks + 7) / 8));
+  if (hd == 256 && (rot / 2) % 8 == 0) return (int)cb_launch(attn_prep_kernel<256>, grid, dim3(256), 0, (cudaStream_t)stream, a);
+  if (hd == 64 && (rot / 2) % 2 == 0) return (int)cb_launch(attn_prep_kernel<64>, grid, dim3(256), 0, (cudaStream_t)stream, a);
+  return CB_ERR_SHAPE;
+}
+
+CB_EXPORT int cb_attn_prefill(const void* q, const void* gate, int64_t ldg, const void* kpool, const void* vpool,
+                              const void* block_table, void* out, int64_t ldo, int64_t T, int64_t q_pos0,
+                              int64_t nh, int64_t nkv, int64_t hd, int64_t causal, int64_t kv_len,
+                              const void* keep, int64_t keep_words, int64_t ratio, void* stream) {
+  if (T == 0) return 0;
+  int rl = 0;
+  if (keep) {
+    while ((1 << rl) < ratio) ++rl;
+    if ((1 << rl) != ratio || ratio < 2 || ratio > kBlock) return CB_ERR_SHAPE;
+  }
+  PrefillArgs a{(const bf16*)q, (const bf16*)gate, ldg, (const bf16*)kpool, (const bf16*)vpool,
+                (const int*)block_table, (bf16*)out, ldo, (int)T, (int)q_pos0, (int)nh, (int)nkv,
+                1.4426950408889634f / sqrtf((float)hd), (int)causal, (int)kv_len,
+                (const unsigned*)keep, (int)keep_words, rl};
+  dim3 grid((unsigned)((T + 63) / 64), (unsigned)nh);
+  const size_t smem = (size_t)3 * 64 * (hd + 8) * sizeof(bf16);
+  cudaError_t e;
+  if (hd == 256) {
+    e = cudaFuncSetAttribute(attn_prefill_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    return (int)cb_launch(attn_prefill_kernel<256>, grid, dim3(128), smem, (cudaStream_t)stream, a);
+  }
+  if (hd == 64) return (int)cb_launch(attn_prefill_kernel<64>, grid, dim3(128), smem, (cudaStream_t)stream, a);
+  return CB_ERR_SHAPE;
+}
+
+CB_EXPORT int cb_attn_decode(const void* proj, int64_t ldp, const void* qg, const void* kg, const void* cos,
+                             const void* sin, const void* positions, const void* rope_pos,
+                             const void* block_table, int64_t ldbt, void* kpool, void* vpool, void* part_o,
+                             void* part_ml, void* tickets, void* out, int64_t ldo, int64_t M, int64_t nh, int64_t nkv,
+                             int64_t hd, int64_t rot, int64_t nsplit, float eps, void* stream) {
+  if (M == 0) return 0;
+  if (nh % nkv || nsplit < 1 || nsplit > 64 || !tickets) return CB_ERR_SHAPE;
+  DecodeArgs a{(const bf16*)proj, ldp, (const float*)qg, (const float*)kg, (const float*)cos, (const float*)sin,
+               (const int*)positions, (const int*)rope_pos, (const int*)block_table, ldbt, (bf16*)kpool,
+               (bf16*)vpool, (float*)part_o, (float*)part_ml, (int)nh, (int)nkv, (int)rot, (int)nsplit,
+               1.4426950408889634f / sqrtf((float)hd), eps, (unsigned*)tickets, (bf16*)out, ldo,
+               nullptr, nullptr, nullptr, 0, 1};
+  return decode_dispatch(a, M, nh, nkv, hd, rot, stream);
+}
+
+// Block-selected ("QSA") decode attention: q [M, nh, hd] is normed and rotated, this step's K/V are in
+// the pool already; row m reads blocks sel[m, :nsel[m]] of `ratio` tokens and its ragged tail.
+CB_EXPORT int cb_attn_sparse(const void* q, const void* proj, int64_t ldp, const void* positions,
+                             const void* block_table, int64_t ldbt, const void* kpool, const void* vpool,
+                             const void* sel, const void* nsel, int64_t topk, int64_t ratio, void* part_o,
+                             void* part_ml, void* tickets, void* out, int64_t ldo, int64_t M, int64_t nh,
+                             int64_t nkv, int64_t hd, int64_t nsplit, void* stream) {
+  if (M == 0) return 0;
+  if (nh % nkv || nsplit < 1 || nsplit > 64 || !tickets || !sel || !nsel || ratio < 1) return CB_ERR_SHAPE;
+  DecodeArgs a{(const bf16*)proj, ldp, nullptr, nullptr, nullptr, nullptr, (const int*)positions, nullptr,
+               (const int*)block_table, ldbt, (bf16*)kpool, (bf16*)vpool, (float*)part_o, (float*)part_ml, (int)nh,
+               (int)nkv, 0, (int)nsplit, 1.4426950408889634f / sqrtf((float)hd), 0.f, (unsigned*)tickets, (bf16*)out,
+               ldo, (const bf16*)q, (const int*)sel, (const int*)nsel, (int)topk, (int)ratio};
+  return decode_dispatch(a, M, nh, nkv, hd, 0, stream);
 }

@@ -33,8 +33,45 @@ typedef __nv_bfloat162 bf162;
 // A kernel launched with the programmatic-stream-serialization attribute may start while its
 // predecessor drains; it must execute griddep_wait() before touching anything the predecessor
 // wrote (or writing anything the predecessor reads).  Without the attribute both are no-ops.
-__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
-__device__ __forceinline__ void griddep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+//
+// Step trace (diagnostic): when a trace buffer is installed, thread 0 of block 0 of every kernel
+// stamps %globaltimer when it enters (griddep_launch) and when its dependency has resolved
+// (griddep_wait).  Kernels of one stream run in order, so the n-th entry stamp and the n-th ready
+// stamp belong to the n-th kernel, and the time between two consecutive ready stamps is the span a
+// kernel really occupies inside a CUDA graph with programmatic dependent launch - something a
+// serialising profiler cannot show.  Layout: [0] entry count, [1] ready count, then (entry, ready)
+// pairs.  Every translation unit holds its own pointer (no relocatable device code); the setters
+// register themselves at load time.
+namespace cbtrace {
+constexpr int kMaxEvents = 8192;
+static __device__ unsigned long long* buf = nullptr;
+__device__ __forceinline__ void stamp(int which) {
+  if ((threadIdx.x | threadIdx.y | blockIdx.x | blockIdx.y | blockIdx.z) != 0) return;
+  unsigned long long* b = buf;
+  if (!b) return;
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  const unsigned long long i = atomicAdd(b + which, 1ull);
+  if (i < (unsigned long long)kMaxEvents) b[2 + 2 * i + which] = t;
+}
+}  // namespace cbtrace
+extern "C" void cb_trace_register(void (*setter)(unsigned long long*));
+extern "C" void cb_trace_name(const void* kernel);
+extern int g_cb_trace_names;
+namespace cbtrace {
+static void set_tu(unsigned long long* p) { cudaMemcpyToSymbol(buf, &p, sizeof(p)); }
+struct Registrar { Registrar() { cb_trace_register(&set_tu); } };
+static Registrar registrar;
+}  // namespace cbtrace
+
+__device__ __forceinline__ void griddep_wait() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  cbtrace::stamp(1);
+}
+__device__ __forceinline__ void griddep_launch() {
+  cbtrace::stamp(0);
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
 
 // Global switch (set from Python): launch with the PDL attribute or as plain launches.
 extern int g_cb_use_pdl;
@@ -52,6 +89,7 @@ static inline cudaError_t cb_launch(void (*kernel)(KArgs...), dim3 grid, dim3 bl
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = g_cb_use_pdl ? 1 : 0;
+  if (g_cb_trace_names) cb_trace_name((const void*)kernel);
   return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
 }
 

@@ -7,6 +7,48 @@
 
 int g_cb_use_pdl = 0;
 CB_EXPORT int cb_set_pdl(int64_t on) { g_cb_use_pdl = on ? 1 : 0; return 0; }
+
+// ---- step trace (see common.cuh) -------------------------------------------------------------
+#include <string>
+#include <vector>
+int g_cb_trace_names = 0;
+namespace {
+std::vector<void (*)(unsigned long long*)>& trace_setters() {
+  static std::vector<void (*)(unsigned long long*)> v;
+  return v;
+}
+std::vector<std::string>& trace_names() {
+  static std::vector<std::string> v;
+  return v;
+}
+}  // namespace
+extern "C" void cb_trace_register(void (*setter)(unsigned long long*)) { trace_setters().push_back(setter); }
+extern "C" void cb_trace_name(const void* kernel) {
+  const char* n = nullptr;
+  if (cudaFuncGetName(&n, kernel) == cudaSuccess && n) trace_names().push_back(n);
+  else trace_names().push_back("?");
+}
+// Install (or with a null pointer remove) the trace buffer in every translation unit.  The buffer
+// holds 2 + 2 * 8192 unsigned 64-bit words and must be zeroed by the caller.
+CB_EXPORT int cb_trace_set(void* buf) {
+  for (auto f : trace_setters()) f((unsigned long long*)buf);
+  return (int)cudaDeviceSynchronize();
+}
+// Record the kernel name of every launch made through cb_launch (1) or stop and keep the list (0).
+CB_EXPORT int cb_trace_record_names(int64_t on) {
+  if (on) trace_names().clear();
+  g_cb_trace_names = on ? 1 : 0;
+  return 0;
+}
+CB_EXPORT int64_t cb_trace_name_count() { return (int64_t)trace_names().size(); }
+CB_EXPORT int cb_trace_get_name(int64_t i, char* out, int64_t cap) {
+  if (i < 0 || i >= (int64_t)trace_names().size() || cap < 1) return CB_ERR_ARG;
+  const std::string& s = trace_names()[(size_t)i];
+  const size_t n = s.size() < (size_t)cap - 1 ? s.size() : (size_t)cap - 1;
+  memcpy(out, s.data(), n);
+  out[n] = 0;
+  return 0;
+}
 CB_EXPORT int cb_version() { return 1; }
 
 namespace {

@@ -35,6 +35,7 @@ struct GdnDecodeArgs {
   int rec_w;
   int ntok;               // tokens per row (1 = decode, c = verify chain)
   int write_state;        // 0: leave the state untouched (verify; commit replays the record)
+  int gate_sigmoid;       // output gate: 0 = silu(z) (Qwen3.5), 1 = sigmoid(z) (Qwen4-exp option)
   int nk, nv, rep;
   float eps;
 };
@@ -138,7 +139,7 @@ __global__ void __launch_bounds__(4 * DV) gdn_decode_kernel(const GdnDecodeArgs 
     if (grp == 0) {
       const float z = __bfloat162float(prow[conv_dim + h * DV + j]);
       a.out[((int64_t)m * a.ntok + t) * a.ldo + h * DV + j] =
-          __float2bfloat16(o * rsqrtf(ms + a.eps) * nw * silu_f(z));
+          __float2bfloat16(o * rsqrtf(ms + a.eps) * nw * (a.gate_sigmoid ? sigmoid_f(z) : silu_f(z)));
     }
     __syncthreads();
   }
@@ -522,7 +523,7 @@ __global__ void __launch_bounds__(256) gdn_chunk_scan_kernel(const GdnScanArgs a
 // out[t, h*DV + j] = bf16( o * rsqrt(mean_j o^2 + eps) * w[j] * silu(z) ), one warp per (t, h)
 template <int DV>
 __global__ void gdn_gated_norm_kernel(const float* o, const bf16* z, int64_t ldz, const float* w, bf16* out,
-                                      int64_t ldo, int T, int nv, float eps) {
+                                      int64_t ldo, int T, int nv, float eps, int gate_sigmoid) {
   griddep_launch();
   griddep_wait();
   const int lane = threadIdx.x & 31;
@@ -539,7 +540,7 @@ __global__ void gdn_gated_norm_kernel(const float* o, const bf16* z, int64_t ldz
   for (int e = 0; e < E; ++e) {
     const int jj = lane + 32 * e;
     const float zz = __bfloat162float(z[t * ldz + h * DV + jj]);
-    out[t * ldo + h * DV + jj] = __float2bfloat16(x[e] * r * w[jj] * silu_f(zz));
+    out[t * ldo + h * DV + jj] = __float2bfloat16(x[e] * r * w[jj] * (gate_sigmoid ? sigmoid_f(zz) : silu_f(zz)));
   }
 }
 
@@ -567,9 +568,11 @@ CB_EXPORT int cb_gdn_decode(const void* proj, int64_t ldp, const void* conv_w, c
                             const void* dt_bias, const void* norm_w, void* ring, void* state,
                             const void* slots, const void* positions, void* out, int64_t ldo,
                             void* record, int64_t rec_w, int64_t M, int64_t ntok, int64_t write_state,
-                            int64_t nk, int64_t nv, int64_t dk, int64_t dv, float eps, void* stream) {
+                            int64_t nk, int64_t nv, int64_t dk, int64_t dv, float eps, int64_t gate_sigmoid,
+                            void* stream) {
   if (nv % nk || M < 1 || ntok < 1 || ntok > 12) return CB_ERR_SHAPE;
   GdnDecodeArgs a;
+  a.gate_sigmoid = (int)gate_sigmoid;
   a.proj = (const bf16*)proj; a.ldp = ldp; a.conv_w = (const float*)conv_w; a.A_log = (const float*)A_log;
   a.dt_bias = (const float*)dt_bias; a.norm_w = (const float*)norm_w; a.ring = (bf16*)ring;
   a.state = (float*)state; a.slots = (const int*)slots; a.positions = (const int*)positions;
@@ -605,7 +608,7 @@ CB_EXPORT int64_t cb_gdn_prefill_scratch(int64_t T, int64_t nk, int64_t nv, int6
 CB_EXPORT int cb_gdn_prefill(const void* proj, int64_t ldp, const void* conv_w, const void* A_log,
                              const void* dt_bias, const void* norm_w, void* ring_seq, void* state_seq,
                              void* scratch, void* out, int64_t ldo, int64_t T, int64_t pos0, int64_t nk,
-                             int64_t nv, int64_t dk, int64_t dv, float eps, void* stream) {
+                             int64_t nv, int64_t dk, int64_t dv, float eps, int64_t gate_sigmoid, void* stream) {
   if (T < 1 || nv % nk) return CB_ERR_SHAPE;
   // the ring update moves whole 16-byte vectors of a projection row
   if (ldp % 8 || (2 * nk * dk + nv * dv) % 8 || ((uintptr_t)proj & 15) || ((uintptr_t)ring_seq & 15)) return CB_ERR_SHAPE;
@@ -650,7 +653,7 @@ CB_EXPORT int cb_gdn_prefill(const void* proj, int64_t ldp, const void* conv_w, 
     const int64_t tasks = T * nv;                                                                        \
     e = cb_launch(gdn_gated_norm_kernel<DV_>, dim3((unsigned)((tasks + 7) / 8)), dim3(256), 0, st,       \
                   (const float*)o, (const bf16*)proj + conv_dim, ldp, (const float*)norm_w, (bf16*)out,  \
-                  ldo, (int)T, (int)nv, eps);                                                            \
+                  ldo, (int)T, (int)nv, eps, (int)gate_sigmoid);                                         \
     return (int)e;                                                                                       \
   } while (0)
   if (dk == 128 && dv == 128) GDN_PREFILL(128, 128, 32);

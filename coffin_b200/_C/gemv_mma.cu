@@ -27,6 +27,10 @@ struct MmaArgs {
   int ksplit;         // k-slices per 16-row block (a power of two <= 8)
   int rounds;         // rounds of the grid-wide sweep
   int pull_site, push_site;
+  int pf_rounds;      // sweep rounds whose weights are requested into L2 before the dependency wait
+  int stage_batches;  // weight batches per warp copied into shared memory ahead of the dependency wait
+  int kcta;           // CTAs that share one 16-row block, each with its own k range (1: none; then ksplit == 8)
+  float* ws; unsigned* tickets;   // cross-CTA partial sums [unit][kcta][2][128] and arrival counters [unit]
   // grouped (mixture-of-experts) mode: blockIdx.y is a slot; slot s multiplies activation row
   // slot_xrow[s] by the weights of expert slot_expert[s] and writes output row s.  M must be 1.
   const int* slot_expert; const int* slot_xrow; int64_t expert_stride;
@@ -40,6 +44,23 @@ __device__ __forceinline__ void mma16816(float* c, uint32_t a0, uint32_t a1, uin
                : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+// Scratch of the cross-CTA K split: a projection with few output rows (2560 x 9216, say) has too few
+// 16-row blocks to fill the SMs with one CTA per block, and a CTA alone keeps only ~32 KB in flight,
+// so its time is set by memory latency, not bandwidth.  Up to kMaxKcta CTAs then share a block, each
+// streaming a slice of K; they leave fp32 partial sums here and the last one to arrive (ticket)
+// adds them in slice order and runs the epilogue, so the result does not depend on arrival order.
+// One decode stream per process uses this scratch at a time (kernels of one stream are ordered).
+constexpr int kMaxKcta = 4, kMaxSplitUnits = 2048;
+__device__ float g_split_ws[(size_t)kMaxSplitUnits * kMaxKcta * 2 * 128];
+__device__ unsigned g_split_tickets[kMaxSplitUnits];
+
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
+  const uint32_t sa = (uint32_t)__cvta_generic_to_shared(smem);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(sa), "l"(gmem) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all_() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+
 template <bool SWIGLU, bool NORM, bool OUT_F32>
 __global__ void __launch_bounds__(kT, 3) gemv_mma_kernel(const MmaArgs a_in) {
   constexpr int PB = SWIGLU ? 2 : 1;   // physical 16-row blocks per unit (gate, up)
@@ -49,9 +70,13 @@ __global__ void __launch_bounds__(kT, 3) gemv_mma_kernel(const MmaArgs a_in) {
   if (a.slot_expert) {
     // the routing tables come from the kernels just before this one: wait before reading them
     // (the second wait below is then a no-op)
-    griddep_wait();
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const int slot = blockIdx.y;
-    if (a.slot_expert[slot] < 0) return;          // expert owned by another rank
+    if (a.slot_expert[slot] < 0) {                // expert owned by another rank
+      cbtrace::stamp(0);
+      cbtrace::stamp(1);
+      return;
+    }
     a.W += (int64_t)a.slot_expert[slot] * a.expert_stride;
     a.x += (int64_t)(a.slot_xrow ? a.slot_xrow[slot] : slot) * a.K;
     a.y = OUT_F32 ? (void*)(reinterpret_cast<float*>(a.y) + (int64_t)slot * a.ldy)
@@ -60,22 +85,33 @@ __global__ void __launch_bounds__(kT, 3) gemv_mma_kernel(const MmaArgs a_in) {
   const int64_t K = a.K, nchunk = K >> 3;
   const int M = a.M;
   bf16* xs = reinterpret_cast<bf16*>(smem_raw);                                  // [M][K]
-  float* part = reinterpret_cast<float*>(smem_raw + (((size_t)M * K * 2 + 15) & ~(size_t)15));  // [rounds][kW][PB][16][8]
+  float* part = reinterpret_cast<float*>(smem_raw + (((size_t)M * K * 2 + 15) & ~(size_t)15));  // [rounds][warps][PB][16][8]
+  const int nT = blockDim.x, nW = nT >> 5;                  // the CTA has ksplit * (row blocks per round) warps
+  // per-warp staging area behind the partial sums: [batch][u][b][lo|hi][lane] 16-byte vectors
+  constexpr int kBatchVecs = U * PB * 2;                     // vectors per lane per batch
+  uint4* stage = reinterpret_cast<uint4*>(
+      smem_raw + (((size_t)M * K * 2 + 15) & ~(size_t)15) +
+      (a_in.ksplit > 1 ? (size_t)a_in.rounds * nW * PB * 128 * sizeof(float) : 0)) +
+      (size_t)(threadIdx.x >> 5) * a_in.stage_batches * kBatchVecs * 32;
   __shared__ float red[32];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
-  const int ksplit = a.ksplit, rbr = kW / ksplit;          // row blocks per CTA round
+  const int ksplit = a.ksplit, rbr = nW / ksplit;          // row blocks per CTA round
   const int ks = warp % ksplit, rb_in = warp / ksplit;
+  const int kcta = a.kcta;
+  const int unit_id = kcta > 1 ? blockIdx.x / kcta : blockIdx.x;   // which row-block unit this CTA works on
+  const int kc = kcta > 1 ? blockIdx.x % kcta : 0;
+  const unsigned unit_stride = kcta > 1 ? gridDim.x / kcta : gridDim.x;
   // k range of this warp in units of 4 chunks (one MMA pair)
   const int64_t npair = (nchunk + 3) >> 2;
-  const int64_t pper = (npair + ksplit - 1) / ksplit;
-  const int64_t p0 = ks * pper, p1 = min(npair, p0 + pper);
+  const int64_t pper = (npair + (int64_t)ksplit * kcta - 1) / ((int64_t)ksplit * kcta);
+  const int64_t p0 = ((int64_t)kc * ksplit + ks) * pper, p1 = min(npair, p0 + pper);
 
   // Weights do not depend on the previous kernel: request this warp's first batch of round 0 into
   // registers before waiting on the producer of the activations, so that (under programmatic
   // dependent launch) the HBM stream of this projection starts during the previous kernel's tail and
   // runs through the norm prologue below.
   auto row_ptrs = [&](int round, const bf16** wlo, const bf16** whi) -> bool {
-    const int64_t blk = ((int64_t)round * gridDim.x + blockIdx.x) * rbr + rb_in;
+    const int64_t blk = ((int64_t)round * unit_stride + unit_id) * rbr + rb_in;
     const int64_t r_lo = blk * 16 + g, r_hi = r_lo + 8;
 #pragma unroll
     for (int b = 0; b < PB; ++b) {
@@ -97,12 +133,64 @@ __global__ void __launch_bounds__(kT, 3) gemv_mma_kernel(const MmaArgs a_in) {
       }
     }
   };
+  // The batches after the first go to this warp's staging area with cp.async (no registers held),
+  // each lane copying exactly the vectors it will read back, so no cross-lane synchronisation is
+  // needed - only the lane's own cp.async completion.
+  auto stage_batch = [&](int sb, int64_t p, const bf16* const* wlo, const bf16* const* whi) {
+    uint4* dst = stage + (size_t)sb * kBatchVecs * 32 + lane;
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int64_t c = (p + u) * 4 + t;
+      const bool ok = (p + u) < p1 && c < nchunk;
+#pragma unroll
+      for (int b = 0; b < PB; ++b) {
+        if (ok) {
+          cp_async16(dst + ((u * PB + b) * 2 + 0) * 32, wlo[b] + c * 8);
+          cp_async16(dst + ((u * PB + b) * 2 + 1) * 32, whi[b] + c * 8);
+        }
+      }
+    }
+  };
+  auto unstage_batch = [&](int sb, int64_t p, uint4 (*lo)[PB], uint4 (*hi)[PB]) {
+    const uint4* src = stage + (size_t)sb * kBatchVecs * 32 + lane;
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int64_t c = (p + u) * 4 + t;
+      const bool ok = (p + u) < p1 && c < nchunk;
+#pragma unroll
+      for (int b = 0; b < PB; ++b) {
+        lo[u][b] = ok ? src[((u * PB + b) * 2 + 0) * 32] : make_uint4(0, 0, 0, 0);
+        hi[u][b] = ok ? src[((u * PB + b) * 2 + 1) * 32] : make_uint4(0, 0, 0, 0);
+      }
+    }
+  };
   griddep_launch();
   uint4 lo[U][PB], hi[U][PB];
   {
     const bf16* wlo[PB];
     const bf16* whi[PB];
-    if (row_ptrs(0, wlo, whi) && p0 < p1) load_batch(p0, wlo, whi, lo, hi);
+    if (row_ptrs(0, wlo, whi) && p0 < p1) {
+      load_batch(p0, wlo, whi, lo, hi);
+      for (int sb = 0; sb < a.stage_batches; ++sb) {
+        const int64_t p = p0 + (int64_t)(sb + 1) * U;
+        if (p < p1) stage_batch(sb, p, wlo, whi);
+      }
+    }
+    cp_async_commit();
+  }
+  // The rows a CTA sweeps in one round are contiguous in memory: ask the L2 for them with one bulk
+  // prefetch per (round, gate/up half), still before the wait.  Under programmatic dependent launch
+  // this CTA is resident long before its activations exist, so the HBM stream of this projection
+  // fills the bubbles (prologue, tail, launch gap) of the projection running ahead of it.
+  if (tid < a.pf_rounds * PB) {
+    const int round = tid / PB, b = tid % PB;
+    const int64_t row0 = ((int64_t)round * unit_stride + unit_id) * rbr * 16;
+    if (row0 < a.N) {
+      const int64_t rows = min((int64_t)rbr * 16, a.N - row0);
+      const bf16* src = a.W + ((b ? a.up_off : 0) + row0) * K;
+      const uint32_t bytes = (uint32_t)(rows * K * 2);
+      asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(bytes) : "memory");
+    }
   }
   griddep_wait();
 
@@ -111,7 +199,7 @@ __global__ void __launch_bounds__(kT, 3) gemv_mma_kernel(const MmaArgs a_in) {
     if (a.pull_site >= 0) tp_pull_wait(a.tp, a.pull_site);
     for (int m = 0; m < M; ++m) {
       float ss = 0.f;
-      for (int64_t c = tid; c < nchunk; c += kT) {
+      for (int64_t c = tid; c < nchunk; c += nT) {
         float f[8], q[8];
         bf16x8_to_float(*reinterpret_cast<const uint4*>(a.res_in + m * K + c * 8), f);
         if (a.pull_site >= 0) {
@@ -130,7 +218,7 @@ __global__ void __launch_bounds__(kT, 3) gemv_mma_kernel(const MmaArgs a_in) {
         for (int i = 0; i < 8; ++i) ss += f[i] * f[i];
       }
       const float rstd = rsqrtf(block_sum(ss, red) / (float)K + a.eps);
-      for (int64_t c = tid; c < nchunk; c += kT) {
+      for (int64_t c = tid; c < nchunk; c += nT) {
         float f[8];
         bf16x8_to_float(*reinterpret_cast<const uint4*>(xs + m * K + c * 8), f);
         const float4 g0 = *reinterpret_cast<const float4*>(a.gain + c * 8);
@@ -141,7 +229,7 @@ __global__ void __launch_bounds__(kT, 3) gemv_mma_kernel(const MmaArgs a_in) {
       }
     }
   } else {
-    for (int64_t c = tid; c < (int64_t)M * nchunk; c += kT)
+    for (int64_t c = tid; c < (int64_t)M * nchunk; c += nT)
       *reinterpret_cast<uint4*>(xs + c * 8) = *reinterpret_cast<const uint4*>(a.x + c * 8);
   }
   __syncthreads();
@@ -150,7 +238,7 @@ __global__ void __launch_bounds__(kT, 3) gemv_mma_kernel(const MmaArgs a_in) {
   const bool has_x = g < M;
 
   for (int round = 0; round < a.rounds; ++round) {
-    const int64_t blk = ((int64_t)round * gridDim.x + blockIdx.x) * rbr + rb_in;   // 16-row block index
+    const int64_t blk = ((int64_t)round * unit_stride + unit_id) * rbr + rb_in;   // 16-row block index
     const int64_t r_lo = blk * 16 + g, r_hi = r_lo + 8;
     float acc[PB][4];
 #pragma unroll
@@ -160,7 +248,13 @@ __global__ void __launch_bounds__(kT, 3) gemv_mma_kernel(const MmaArgs a_in) {
     const bool blk_ok = row_ptrs(round, wlo, whi);
     if (blk_ok) {
       for (int64_t p = p0; p < p1; p += U) {
-        if (round > 0 || p > p0) load_batch(p, wlo, whi, lo, hi);   // the first batch is already in flight
+        const int64_t bi = (p - p0) / U;                            // batch number within this warp's slice
+        if (round == 0 && bi >= 1 && bi <= a.stage_batches) {
+          if (bi == 1) cp_async_wait_all_();
+          unstage_batch((int)bi - 1, p, lo, hi);
+        } else if (round > 0 || bi > 0) {
+          load_batch(p, wlo, whi, lo, hi);                          // batch 0 of round 0 is already in registers
+        }
         uint4 xv[U];
 #pragma unroll
         for (int u = 0; u < U; ++u) {
@@ -194,7 +288,7 @@ __global__ void __launch_bounds__(kT, 3) gemv_mma_kernel(const MmaArgs a_in) {
         }
       }
     } else {
-      float* pw = part + (((size_t)round * kW + warp) * PB) * 128;
+      float* pw = part + (((size_t)round * nW + warp) * PB) * 128;
 #pragma unroll
       for (int b = 0; b < PB; ++b)
 #pragma unroll
@@ -204,16 +298,53 @@ __global__ void __launch_bounds__(kT, 3) gemv_mma_kernel(const MmaArgs a_in) {
   }
   if (ksplit > 1) {
     __syncthreads();
+    if (kcta > 1) {
+      // cross-CTA split (one round, one row block per CTA): publish this CTA's slice sums, take a
+      // ticket; the last CTA of the block re-reads all slices in order
+      float* mine = a.ws + ((size_t)unit_id * kMaxKcta + kc) * 256;
+      for (int idx = tid; idx < PB * 128; idx += nT) {
+        float v = 0.f;
+        for (int s = 0; s < ksplit; ++s) v += part[((size_t)s * PB + idx / 128) * 128 + idx % 128];
+        __stcg(mine + idx, v);
+      }
+      __shared__ bool last;
+      __threadfence();
+      __syncthreads();
+      if (tid == 0) {
+        last = atomicAdd(a.tickets + unit_id, 1u) == (unsigned)kcta - 1;
+        if (last) a.tickets[unit_id] = 0;
+      }
+      __syncthreads();
+      if (!last) return;
+      __threadfence();
+      const float* all = a.ws + (size_t)unit_id * kMaxKcta * 256;
+      for (int idx = tid; idx < 128; idx += nT) {
+        const int r = idx / 8, m = idx % 8;
+        const int64_t row = (int64_t)unit_id * 16 + r;
+        if (m >= M || row >= a.N) continue;
+        float v = 0.f, v2 = 0.f;
+        for (int c = 0; c < kcta; ++c) {
+          v += __ldcg(all + c * 256 + idx);
+          if (SWIGLU) v2 += __ldcg(all + c * 256 + 128 + idx);
+        }
+        if (SWIGLU) v = silu_f(v) * v2;
+        if (a.push_site >= 0) tp_push_value(a.tp, a.push_site, (int64_t)m * a.N + row, v);
+        else if (OUT_F32) reinterpret_cast<float*>(a.y)[(int64_t)m * a.ldy + row] = v;
+        else reinterpret_cast<bf16*>(a.y)[(int64_t)m * a.ldy + row] = __float2bfloat16(v);
+      }
+      if (a.push_site >= 0) tp_push_done(a.tp, a.push_site, unit_stride);
+      return;
+    }
     // one thread per (round, row block of the round, row in block, batch row): fixed-order sum over k-slices
     const int per_round = rbr * 16 * 8;
-    for (int idx = tid; idx < a.rounds * per_round; idx += kT) {
+    for (int idx = tid; idx < a.rounds * per_round; idx += nT) {
       const int round = idx / per_round, rem = idx % per_round;
       const int rb = rem / 128, r = (rem % 128) / 8, m = rem % 8;
       const int64_t row = (((int64_t)round * gridDim.x + blockIdx.x) * rbr + rb) * 16 + r;
       if (m >= M || row >= a.N) continue;
       float v = 0.f, v2 = 0.f;
       for (int s = 0; s < ksplit; ++s) {
-        const float* pw = part + (((size_t)round * kW + rb * ksplit + s) * PB) * 128;
+        const float* pw = part + (((size_t)round * nW + rb * ksplit + s) * PB) * 128;
         v += pw[r * 8 + m];
         if (SWIGLU) v2 += pw[128 + r * 8 + m];
       }
@@ -228,6 +359,9 @@ __global__ void __launch_bounds__(kT, 3) gemv_mma_kernel(const MmaArgs a_in) {
 
 int g_mma_sms = 0;
 int g_mma_ctas = 3;
+int g_mma_pf_rounds = 0;
+int g_mma_kcta_max = 4;
+int g_mma_stage = 0;   // measured: staging through shared memory is slower than the register batches alone
 
 template <bool SWIGLU, bool NORM, bool OUT_F32>
 int launch_mma(MmaArgs a, cudaStream_t st, int n_slots = 1) {
@@ -239,30 +373,87 @@ int launch_mma(MmaArgs a, cudaStream_t st, int n_slots = 1) {
   }
   constexpr int PB = SWIGLU ? 2 : 1;
   const int64_t nblk = (a.N + 15) / 16;
-  const int64_t slots = max((int64_t)1, (int64_t)g_mma_sms * g_mma_ctas / n_slots);
   const int64_t npair = ((a.K >> 3) + 3) >> 2;
-  // split K across warps until the grid fills the resident CTA slots (or slices get too short)
-  int ks = 1;
-  while (ks < kW && (nblk * ks + kW - 1) / kW < slots && npair / (ks * 2) >= 8) ks <<= 1;
+  // Work is cut so that every resident warp gets the same amount and everything is resident at
+  // once (one wave): a warp task is one 16-row block times one K slice.
+  //  * few blocks: S = ks * kcta slices per block, ks warps of one CTA times kcta CTAs (cross-CTA sum);
+  //  * more blocks than that but fewer than warp slots: one CTA of ks warps per block;
+  //  * more blocks than warp slots (vocabulary head): 8-warp CTAs sweep whole blocks in rounds,
+  //    the grid sized so that every CTA runs the same number of rounds.
+  const int warps_sm = 25;                                      // 80 registers per thread
+  const size_t xs_bytes = (((size_t)a.M * a.K * 2 + 15) & ~(size_t)15);
+  int stage_b = g_mma_stage;                                     // staged batches per warp (4 KB each)
+  auto cta_slots = [&](int w) -> int64_t {                       // CTAs of w warps resident on the machine
+    int64_t per = warps_sm / w;
+    const size_t sm = xs_bytes + (w > 1 ? (size_t)w * PB * 512 : 0) + (size_t)w * stage_b * 4096 + 1024;
+    const int64_t by_smem = (int64_t)((size_t)227 * 1024 / sm);
+    if (per > by_smem) per = by_smem;
+    if (per > 32) per = 32;
+    return per * g_mma_sms / n_slots;
+  };
+  int ks = 1, kcta = 1, warps = kW;
+  int64_t grid_x = 0;
+  a.rounds = 1;
+  if (nblk <= cta_slots(1)) {
+    const int64_t smax = npair / 4 > 0 ? npair / 4 : 1;         // at least 4 k-step pairs per warp
+    const int kc_cap = (a.slot_expert || nblk > kMaxSplitUnits) ? 1 : g_mma_kcta_max;
+    // prefer deep staging; give it up (2 -> 1 -> 0 batches) when shared memory would cost residency
+    int64_t best = -1;
+    int best_ks = 1, best_kcta = 1, best_stage = 0;
+    for (int sb = g_mma_stage; sb >= 0; --sb) {
+      stage_b = sb;
+      int64_t S = (int64_t)kW * kc_cap;
+      if (S > smax) S = smax;
+      int k1 = 1, c1 = 1;
+      for (; S > 1; --S) {                                       // most slices per block that still fit one wave
+        c1 = (int)((S + kW - 1) / kW);
+        k1 = (int)(S / c1);
+        if (nblk * c1 <= cta_slots(k1)) break;
+      }
+      if (S <= 1) { k1 = 1; c1 = 1; }
+      const int64_t warps_total = nblk * c1 * k1;
+      if (warps_total > best) { best = warps_total; best_ks = k1; best_kcta = c1; best_stage = sb; }
+    }
+    ks = best_ks; kcta = best_kcta; stage_b = best_stage;
+    warps = ks;
+    grid_x = nblk * kcta;
+  } else {
+    const int64_t units = (nblk + kW - 1) / kW;                  // 8 blocks per CTA round
+    const int64_t cap = (int64_t)g_mma_sms * g_mma_ctas / n_slots;
+    a.rounds = (int)((units + cap - 1) / cap);
+    grid_x = (units + a.rounds - 1) / a.rounds;
+    while (stage_b > 0 && (int64_t)(227 * 1024 / (xs_bytes + (size_t)kW * stage_b * 4096 + 1024)) < g_mma_ctas) --stage_b;
+  }
+  a.stage_batches = stage_b;
   a.ksplit = ks;
-  const int rbr = kW / ks;
-  const int64_t units = (nblk + rbr - 1) / rbr;
-  const int64_t grid = units < slots ? units : slots;
-  a.rounds = (int)((units + grid - 1) / grid);
+  a.kcta = kcta;
+  a.ws = nullptr; a.tickets = nullptr;
+  if (kcta > 1) {
+    cudaGetSymbolAddress((void**)&a.ws, g_split_ws);
+    cudaGetSymbolAddress((void**)&a.tickets, g_split_tickets);
+  }
+  a.pf_rounds = a.slot_expert ? 0 : (a.rounds < g_mma_pf_rounds ? a.rounds : g_mma_pf_rounds);
   size_t smem = (((size_t)a.M * a.K * 2 + 15) & ~(size_t)15);
-  if (ks > 1) smem += (size_t)a.rounds * kW * PB * 128 * sizeof(float);
+  if (ks > 1) smem += (size_t)a.rounds * warps * PB * 128 * sizeof(float);
   if (smem > 72 * 1024) return CB_ERR_SHAPE;
+  smem += (size_t)warps * stage_b * 4096;
   auto kern = gemv_mma_kernel<SWIGLU, NORM, OUT_F32>;
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
   }
-  return (int)cb_launch(kern, dim3((unsigned)grid, (unsigned)n_slots), dim3(kT), smem, st, a);
+  return (int)cb_launch(kern, dim3((unsigned)grid_x, (unsigned)n_slots), dim3((unsigned)warps * 32), smem, st, a);
 }
 
 }  // namespace
 
 CB_EXPORT int cb_set_mma_gemv_opts(int64_t ctas_per_sm) { g_mma_ctas = ctas_per_sm < 1 ? 1 : (int)ctas_per_sm; return 0; }
+// Largest number of CTAs that may share one 16-row block (1 switches the cross-CTA K split off).
+CB_EXPORT int cb_set_mma_gemv_kcta(int64_t n) { g_mma_kcta_max = n < 1 ? 1 : (n > 4 ? 4 : (int)n); return 0; }
+// Weight batches (4 KB per warp each) staged in shared memory ahead of the dependency wait.
+CB_EXPORT int cb_set_mma_gemv_stage(int64_t n) { g_mma_stage = n < 0 ? 0 : (n > 4 ? 4 : (int)n); return 0; }
+// Sweep rounds prefetched into L2 ahead of the dependency wait (0 = none).
+CB_EXPORT int cb_set_mma_gemv_prefetch(int64_t rounds) { g_mma_pf_rounds = rounds < 0 ? 0 : (int)rounds; return 0; }
 
 // Same contract as cb_gemv_bf16 (M = 1..8, any M in that range).
 CB_EXPORT int cb_gemv_mma_bf16(const void* W, const void* x, void* y, int64_t M, int64_t N, int64_t K,

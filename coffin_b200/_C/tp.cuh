@@ -26,6 +26,9 @@ struct TpComm {
   int64_t slot_floats;      // floats per (site, rank) inbox slot  (= max rows * hidden)
   float* inbox[kTpMaxWorld];       // base of every rank's inbox: [sites][world][slot_floats]
   unsigned* flags[kTpMaxWorld];    // base of every rank's flags: [sites][world]
+  const float* my_inbox;    // == inbox[rank]; a separate field so that no kernel indexes the arrays
+  const unsigned* my_flags; // == flags[rank]  with a run-time value (that would copy the parameter
+                            //    block to local memory in every thread)
   unsigned* arrive;         // local: [sites] CTA arrival counters of the producer
   const unsigned* epoch;    // local: current step number
   int* status;              // local status word (set to 16 + rank on a wait that ran out)
@@ -63,7 +66,9 @@ __device__ __forceinline__ void tp_push_done(const TpComm& c, int site, unsigned
       c.arrive[site] = 0;
       __threadfence_system();
       const unsigned e = *c.epoch;
-      for (int p = 0; p < c.world; ++p) tp_st_release(c.flags[p] + (int64_t)site * c.world + c.rank, e);
+#pragma unroll
+      for (int p = 0; p < kTpMaxWorld; ++p)
+        if (p < c.world) tp_st_release(c.flags[p] + (int64_t)site * c.world + c.rank, e);
     }
   }
 }
@@ -72,7 +77,7 @@ __device__ __forceinline__ void tp_push_done(const TpComm& c, int site, unsigned
 __device__ __forceinline__ void tp_pull_wait(const TpComm& c, int site) {
   if (threadIdx.x == 0) {
     const unsigned e = *c.epoch;
-    const unsigned* f = c.flags[c.rank] + (int64_t)site * c.world;
+    const unsigned* f = c.my_flags + (int64_t)site * c.world;
     const unsigned long long t0 = tp_now_ns();
     for (int r = 0; r < c.world; ++r) {
       unsigned spins = 0;
@@ -88,7 +93,7 @@ __device__ __forceinline__ void tp_pull_wait(const TpComm& c, int site) {
 }
 // Consumer: sum of the ranks' partial values at element `off` (fixed rank order).
 __device__ __forceinline__ float tp_pull_value(const TpComm& c, int site, int64_t off) {
-  const float* base = c.inbox[c.rank] + (int64_t)site * c.world * c.slot_floats + off;
+  const float* base = c.my_inbox + (int64_t)site * c.world * c.slot_floats + off;
   float s = 0.f;
   for (int r = 0; r < c.world; ++r) s += __ldcg(base + (int64_t)r * c.slot_floats);
   return s;

@@ -93,8 +93,10 @@ def build_server(args):
         kw = dict(device=f"cuda:{int(os.environ.get('LOCAL_RANK', '0'))}", max_seq=cfg_e.max_seq,
                   num_slots=cfg_e.max_num_seqs, max_chunk=cfg_e.chunk,
                   num_blocks=cfg_e.num_blocks if cfg_e.num_blocks > 0 else None)
-        if world > 1 and mode == "tp":
-            kw.update(tp_world=world, tp_rank=rank)
+        if world > 1:
+            if mode not in ("tp", "pp", "ep"):
+                raise SystemExit(f"COFFIN_PARALLEL={mode!r}: expected tp, pp or ep")
+            kw.update({f"{mode}_world": world, f"{mode}_rank": rank})
         return build_model(mcfg, sd, **kw)
 
     return Server(builder(), cfg_e, model_path=args.model, model_name=args.preset or "", builder=builder)

@@ -30,6 +30,10 @@ def _ensure_builtin() -> None:
         from .qwen35.model import Qwen35Model
         tp_world, tp_rank = kw.pop("tp_world", 1), kw.pop("tp_rank", 0)
         ep_world, ep_rank = kw.pop("ep_world", 1), kw.pop("ep_rank", 0)
+        pp_world, pp_rank = kw.pop("pp_world", 1), kw.pop("pp_rank", 0)
+        if pp_world > 1:
+            from ..parallel.pp import build_stage
+            return build_stage(cfg, sd, pp_rank, pp_world, lanes=kw.pop("pp_lanes", 2), **kw)
         if ep_world > 1:
             # expert parallel: attention / delta-net / dense weights replicated, routed experts split
             from ..parallel.tp import TpComm, make_exchange

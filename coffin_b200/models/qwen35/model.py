@@ -94,11 +94,16 @@ class Qwen35Model:
     def __init__(self, cfg: ModelConfig, sd: dict[str, torch.Tensor], device: str | torch.device = "cuda",
                  max_seq: int = 4096, num_slots: int = 2, num_blocks: int | None = None,
                  max_chunk: int = 2048, pdl: bool = True, free_source: bool = False, tp=None,
-                 full_cfg: ModelConfig | None = None, quant: str = "none", ep_rank: int = 0, ep_world: int = 1) -> None:
+                 full_cfg: ModelConfig | None = None, quant: str = "none", ep_rank: int = 0, ep_world: int = 1,
+                 pp_first: bool = True, pp_last: bool = True) -> None:
         """``cfg`` is the geometry this instance computes (a tensor-parallel shard gets its local
         head / channel counts, ``full_cfg`` the unsharded model and ``tp`` the communicator)."""
         self.cfg = cfg
         self.quant = quant
+        # pipeline stage: a non-first stage starts from a received hidden state instead of the
+        # embedding, a non-last stage ends at the residual stream instead of the logits
+        self.pp_first, self.pp_last = pp_first, pp_last
+        self.lane = 0              # micro-batch lane: decode buffers and graphs are kept per (bucket, lane)
         self.ep_rank, self.ep_world, self.ep_site = ep_rank, ep_world, -1
         self.tp = tp
         self.tp_world = tp.world if tp is not None else 1
@@ -143,11 +148,14 @@ class Qwen35Model:
             t = sd[key].to(device=dev, dtype=torch.float32)
             return (1.0 + t).contiguous() if centred else t.contiguous()
 
-        self.embed = w(LM + "embed_tokens.weight")
+        self.embed = w(LM + "embed_tokens.weight") if LM + "embed_tokens.weight" in sd else None
         if isinstance(self.embed, QW):
             self.embed = (self.embed.wq.float() * self.embed.scale[:, None]).to(bf)
-        self.embed = self.embed.contiguous()
-        self.lm_head = one(w("lm_head.weight")) if "lm_head.weight" in sd else one(self.embed)
+        if self.embed is not None:
+            self.embed = self.embed.contiguous()
+        self.lm_head = None
+        if pp_last:
+            self.lm_head = one(w("lm_head.weight")) if "lm_head.weight" in sd else one(self.embed)
         self.vocab_local = c.vocab_size
         if self.tp_world > 1:       # vocabulary-parallel head: this rank scores a contiguous slice
             if c.vocab_size % self.tp_world:
@@ -245,7 +253,7 @@ class Qwen35Model:
 
     def weight_bytes(self) -> int:
         seen, total = set(), 0
-        tensors = [self.embed, self.lm_head]
+        tensors = [t for t in (self.embed, self.lm_head) if t is not None]
         for l in self.layers:
             tensors += [l.w_in, l.w_out] + ([l.w_gu, l.w_down] if l.w_gu is not None else [])
             if l.moe is not None:
@@ -372,6 +380,8 @@ class Qwen35Model:
         out_logits = None
         self.last_hidden = None
         self.last_prenorm = res            # last-layer residual stream of the chunk (view of the workspace)
+        if not self.pp_last:
+            return None
         if want_hidden:
             self.last_hidden = K.rmsnorm(res, self.final_gain, self.eps)
         if want_logits:
@@ -403,7 +413,8 @@ class Qwen35Model:
 
     # ------------------------------------------------------------------ decode
     def _row_buffers(self, M: int) -> dict:
-        b = self._rows.get(M)
+        key = M if self.lane == 0 else (M, self.lane)
+        b = self._rows.get(key)
         if b is None:
             c, dev, bf = self.cfg, self.device, torch.bfloat16
             H = c.hidden_size
@@ -436,7 +447,7 @@ class Qwen35Model:
             }
             b["logits_local"] = (b["logits"] if self.tp_world == 1 else
                                  torch.zeros(M, self.vocab_local, dtype=torch.float32, device=dev))
-            self._rows[M] = b
+            self._rows[key] = b
         return b
 
     def _decode_body(self, M: int) -> None:
@@ -501,6 +512,14 @@ class Qwen35Model:
             else:
                 self._gemv(lw.w_down, b["inter"], b["h2"])
                 carry, pull = b["h2"], -1
+        if not self.pp_last:
+            # pipeline hand-off: the residual stream that the next stage starts from
+            if carry is not None:
+                torch.add(cur, carry, out=b["hidden"])
+            else:
+                b["hidden"].copy_(cur)
+            K._count()
+            return
         self._gemv(self.lm_head, None, b["logits_local"], norm=(cur, carry, self.final_gain, nxt, self.eps),
                    tp=comm, pull_site=pull)
         if self.tp_world > 1:
@@ -533,7 +552,8 @@ class Qwen35Model:
     def capture(self, M: int, warmup: int = 2) -> None:
         """Capture the decode step of bucket ``M`` into a CUDA graph. Warm-up runs use padded
         rows (slot -1 / position -1) so that no sequence state is touched."""
-        if M in self._graphs:
+        gkey = (M, self.lane)
+        if gkey in self._graphs:
             return
         b = self._row_buffers(M)
         saved = (b["positions"].clone(), b["slots"].clone())
@@ -553,7 +573,7 @@ class Qwen35Model:
         with torch.cuda.graph(g, pool=self.graph_pool):
             self._decode_body(M)
         self._step_launches[M] = K.LAUNCHES - l0
-        self._graphs[M] = g
+        self._graphs[gkey] = g
         b["positions"].copy_(saved[0])
         b["slots"].copy_(saved[1])
 
@@ -563,12 +583,16 @@ class Qwen35Model:
         device tensors owned by the bucket (overwritten by the next step)."""
         b = self._row_buffers(M)
         if graph:
-            if M not in self._graphs:
+            if (M, self.lane) not in self._graphs:
                 self.capture(M)
-            self._graphs[M].replay()
+            self._graphs[(M, self.lane)].replay()
         else:
             self._decode_body(M)
         return b["next"], b["logits"]
+
+    def stage_hidden(self, M: int) -> torch.Tensor:
+        """Residual stream after this pipeline stage's layers for the rows of the last decode step."""
+        return self._row_buffers(M)["hidden"]
 
     def final_hidden(self, M: int, normed: bool = True) -> torch.Tensor:
         """Last-layer residual stream of the previous decode step (``normed``: after the final norm)."""

@@ -131,9 +131,14 @@ class MoEWeights:
 
     # ------------------------------------------------------------------ prefill
     def forward_prefill(self, normed: torch.Tensor, res: torch.Tensor, model) -> None:
-        """``res += moe(normed)`` for a prefill chunk.  Small chunks reuse the decode kernels (every
-        slot streams its expert once); larger chunks sort the slots by expert and run one tcgen05
-        GEMM pair per expert that received tokens."""
+        """``res += moe(normed)`` for a prefill chunk."""
+        res.add_(self.apply(normed, model))
+
+    def apply(self, normed: torch.Tensor, model=None) -> torch.Tensor:
+        """``moe(normed)`` for ``T`` rows (a new ``[T, H]`` tensor).  Small row counts reuse the decode
+        kernels (every slot streams its expert once); larger ones sort the slots by expert and run one
+        tcgen05 GEMM pair per expert that received tokens.  ``model`` supplies the all-reduce under
+        expert parallelism."""
         c = self.cfg
         T = normed.shape[0]
         E, k, H, I = c.num_experts, c.num_experts_per_tok, c.hidden_size, c.moe_intermediate_size
@@ -144,8 +149,7 @@ class MoEWeights:
             self._experts(b, T, out)
             if self.ep_world > 1:
                 model._tp_reduce(out)
-            res.add_(out)
-            return
+            return out
         logits = K.gemm(normed, self.router).float()                       # [T, pad8(E+1)]
         idx = torch.empty(T, k, dtype=torch.int32, device=normed.device)
         w = torch.empty(T, k, dtype=torch.float32, device=normed.device)
@@ -185,4 +189,4 @@ class MoEWeights:
         K._count()
         if self.ep_world > 1:
             model._tp_reduce(out)
-        res.add_(out)
+        return out

@@ -1,0 +1,530 @@
+"""Qwen4-exp on one B200: hyper-connected residual lanes, delta-net and block-sparse (QSA)
+attention mixers, a routed MoE in every layer, optional n-gram (PLE) injection.
+
+Execution model (eager; the family's reference runs eager too, ``models/qwen4exp/engine.py:12-24``):
+
+* The residual stream is ``[rows, hc * H]`` bf16.  A mixer's output is not written back when it is
+  produced: the next hyper-connection read applies ``stream += out (x) inject`` inside its norm
+  kernel (``hyper_norm``), so a layer touches the wide stream twice, not four times.
+* Hyper-connection read: ``hyper_norm`` -> low-rank down GEMV -> ``hyper_up`` (read gate, lane mix,
+  write gates) for up to 8 rows; prefill chunks run the same algebra on tcgen05 GEMMs.
+* Delta-net layers reuse the Qwen3.5 kernels (fused decode step, chunked prefill scan); the MoE is
+  the Qwen3.5 module (router kernel, grouped tensor-core GEMVs / per-expert GEMMs, combine).
+* QSA layers keep three paged pools per layer - K, V and the raw index keys - plus a pool of
+  *block keys*: the key of a block of ``ratio`` tokens never changes once the block is complete, so
+  it is computed once (``qsa_block_keys``) instead of for every query as in the reference
+  (``models/qwen4exp/qsa.py:496-528, 800-860``).  Decode scores the cached block keys, selects by
+  an exact radix top-k and runs split-KV attention over the kept tokens only; prefill passes a
+  per-query block mask to the flash kernel.
+* PLE (one layer in the real model) runs as torch ops on the device; its table lives in HBM when it
+  fits and in pinned host memory with an asynchronous gather otherwise (``ngram.NGramTable``).
+
+The class offers the model interface the engine drives (``prefill`` / ``set_rows`` / ``decode`` /
+state snapshots / ``copy_block``), so the block manager, radix cache and scheduler are shared with
+the Qwen3.5 family.  Speculative verification is not offered for this family.
+Structure reference: ``models/qwen4exp/blocks.py:52-238``, ``model.py:250-470``, ``engine.py:360-897``.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+
+from ...ops import kernels as K
+from ...oracle import ops as O
+from ..qwen35.moe import MoEWeights
+from .config import LINEAR, Qwen4Config
+from .ngram import NGramHasher, NGramTable
+
+LM = "model.language_model."
+BUCKETS = (1, 2, 4, 8)
+
+
+def _pad8(n: int) -> int:
+    return (n + 7) // 8 * 8
+
+
+class _Hyper:
+    """Weights of one hyper-connection."""
+
+    def __init__(self, sd, prefix: str, dev, write_gate: bool = True) -> None:
+        bf = torch.bfloat16
+        self.gain = (1.0 + sd[prefix + "hc_norm.weight"].float()).to(dev).contiguous()
+        self.Wd = sd[prefix + "input_mix_weight_down.weight"].to(dev, bf).contiguous()      # [R, hc*H]
+        self.Wu = sd[prefix + "input_mix_weight_up.weight"].to(dev, bf).contiguous()        # [hc*H, R]
+        self.Wi = self.Wi8 = None
+        if write_gate:
+            wi = sd[prefix + "block_inject_weight.weight"].to(dev, bf)
+            self.Wi = wi.contiguous()                                                       # [hc, hc*H]
+            self.Wi8 = torch.zeros(_pad8(max(wi.shape[0], 8)), wi.shape[1], dtype=bf, device=dev)
+            self.Wi8[:wi.shape[0]] = wi                                                     # GEMM needs >= 8 output rows
+
+    def tensors(self):
+        return [t for t in (self.Wd, self.Wu, self.Wi) if t is not None]
+
+
+class _Layer:
+    pass
+
+
+class Qwen4ExpModel:
+    def __init__(self, cfg: Qwen4Config, sd: dict[str, torch.Tensor], device: str | torch.device = "cuda",
+                 max_seq: int = 4096, num_slots: int = 2, num_blocks: int | None = None, max_chunk: int = 2048,
+                 pdl: bool = True, ngram_device_budget: int = 120 << 30, **_unused) -> None:
+        self.cfg = c = cfg
+        if 64 % c.indexer_compress_ratio or c.indexer_compress_ratio < 2:
+            raise ValueError("indexer_compress_ratio must be a power of two between 2 and 64")
+        if c.indexer_n_heads > 8 or c.indexer_head_dim > 256:
+            raise ValueError("indexer geometry outside the kernels' range (heads <= 8, head_dim <= 256)")
+        self.device = dev = torch.device(device)
+        self.max_seq, self.num_slots, self.max_chunk = int(max_seq), int(num_slots), int(max_chunk)
+        self.max_blocks_per_seq = (self.max_seq + K.BLOCK - 1) // K.BLOCK
+        self.num_blocks = int(num_blocks) if num_blocks else self.max_blocks_per_seq * self.num_slots + 1
+        self.eps = c.rms_norm_eps
+        self.gate_sigmoid = c.output_gate_type == "sigmoid"
+        K.status_word(dev)
+        K._lib.set_pdl(pdl)
+        bf = torch.bfloat16
+
+        def w(key):
+            return sd[key].to(dev, bf)
+
+        def gain(key):
+            return (1.0 + sd[key].float()).to(dev).contiguous()
+
+        self.embed = w(LM + "embed_tokens.weight").contiguous()
+        self.lm_head = w("lm_head.weight").contiguous() if "lm_head.weight" in sd else self.embed
+        self.final = _Hyper(sd, LM + "hyper_connection_mixer.", dev, write_gate=False)
+        self.layers: list[_Layer] = []
+        self.lin_ids = {li: j for j, li in enumerate(c.linear_layers)}
+        self.full_ids = {li: j for j, li in enumerate(c.full_layers)}
+        self.ple_ids: dict[int, int] = {}
+        for li, kind in enumerate(c.layer_types):
+            p = f"{LM}layers.{li}."
+            L = _Layer()
+            L.kind = kind
+            L.h_attn = _Hyper(sd, p + "attn_hyper_connection.", dev)
+            L.h_mlp = _Hyper(sd, p + "mlp_hyper_connection.", dev)
+            if kind == LINEAR:
+                q = p + "linear_attn."
+                parts = [w(q + "in_proj_qkv.weight"), w(q + "in_proj_z.weight"), w(q + "in_proj_b.weight"),
+                         w(q + "in_proj_a.weight")]
+                n = sum(t.shape[0] for t in parts)
+                if _pad8(n) != n:
+                    parts.append(torch.zeros(_pad8(n) - n, c.hidden_size, dtype=bf, device=dev))
+                L.w_in = torch.cat(parts).contiguous()
+                L.w_out = w(q + "out_proj.weight").contiguous()
+                L.conv_w = sd[q + "conv1d.weight"].to(dev, torch.float32).reshape(c.lin_conv_dim, -1).contiguous()
+                L.A_log = sd[q + "A_log"].to(dev, torch.float32).contiguous()
+                L.dt_bias = sd[q + "dt_bias"].to(dev, torch.float32).contiguous()
+                L.norm_w = sd[q + "norm.weight"].to(dev, torch.float32).contiguous()
+            else:
+                q = p + "self_attn."
+                parts = [w(q + "q_proj.weight"), w(q + "k_proj.weight"), w(q + "v_proj.weight"),
+                         w(q + "indexer.index_qk_proj.weight")]
+                n = sum(t.shape[0] for t in parts)
+                L.idx_col = n - parts[3].shape[0]
+                if _pad8(n) != n:
+                    parts.append(torch.zeros(_pad8(n) - n, c.hidden_size, dtype=bf, device=dev))
+                L.w_in = torch.cat(parts).contiguous()
+                L.w_out = w(q + "o_proj.weight").contiguous()
+                L.qg, L.kg = gain(q + "q_norm.weight"), gain(q + "k_norm.weight")
+                L.iqg, L.ikg = gain(q + "indexer.q_layernorm.weight"), gain(q + "indexer.k_layernorm.weight")
+            L.moe = MoEWeights.from_state_dict(c, sd, p + "mlp.", dev)
+            L.ple = None
+            j = c.ple_index(li)
+            if j is not None:
+                q = p + "ple."
+                P = _Layer()
+                P.hasher = NGramHasher(c, j)
+                P.table = NGramTable(sd[q + "ple_embedding.ngram_embedding.weight"].to(bf), dev, ngram_device_budget)
+                P.key_w = w(q + "key_proj.weight").float()
+                P.val_w = w(q + "value_proj.weight").float()
+                P.g_key, P.g_query, P.g_conv = gain(q + "norm_key.weight"), gain(q + "norm_query.weight"), gain(q + "norm_conv.weight")
+                P.conv_w = sd[q + "conv1d.weight"].to(dev, torch.float32).reshape(c.hc_hidden, -1).contiguous()
+                L.ple = P
+                self.ple_ids[li] = len(self.ple_ids)
+            self.layers.append(L)
+        cos, sin = O.rope_tables(c.rotary_dim, c.rope_theta, self.max_seq + 64)
+        self.cos, self.sin = cos.to(dev).contiguous(), sin.to(dev).contiguous()
+        # ---- sequence state --------------------------------------------------------------------
+        nl, nf, npl = len(self.lin_ids), len(self.full_ids), len(self.ple_ids)
+        self.state = torch.zeros(nl, self.num_slots, c.linear_num_value_heads, c.linear_key_head_dim,
+                                 c.linear_value_head_dim, dtype=torch.float32, device=dev)
+        self.ring = torch.zeros(nl, self.num_slots, K.RING, c.lin_conv_dim, dtype=bf, device=dev)
+        rows = self.num_blocks * K.BLOCK
+        self.kpool = torch.zeros(nf, rows, c.num_key_value_heads, c.head_dim, dtype=bf, device=dev)
+        self.vpool = torch.zeros_like(self.kpool)
+        self.ipool = torch.zeros(nf, rows, c.indexer_head_dim, dtype=bf, device=dev)
+        self.per_page = K.BLOCK // c.indexer_compress_ratio
+        self.bkpool = torch.zeros(nf, self.num_blocks * self.per_page, c.indexer_head_dim, dtype=torch.float32, device=dev)
+        self.ple_hist = torch.zeros(max(npl, 1), self.num_slots, c.ple_conv_state_len, c.hc_hidden, dtype=torch.float32, device=dev)
+        self.ple_ctx: list[list[list[int]]] = [[self._fresh_ctx() for _ in range(self.num_slots)] for _ in range(max(npl, 1))]
+        self.max_sel_blocks = (self.max_seq + c.indexer_compress_ratio - 1) // c.indexer_compress_ratio
+        self._ws: dict = {}
+        self._rows: dict = {}
+        self._staged: dict | None = None
+        self.last_prenorm = None
+        self.last_hidden = None
+
+    # ------------------------------------------------------------------ sizes / bookkeeping
+    def _fresh_ctx(self) -> list[int]:
+        return [self.cfg.eos_token_id] * self.cfg.ple_context_len
+
+    def weight_bytes(self) -> int:
+        tensors = [self.embed, self.lm_head] + self.final.tensors()
+        for L in self.layers:
+            tensors += [L.w_in, L.w_out] + L.h_attn.tensors() + L.h_mlp.tensors() + L.moe.tensors()
+        seen, total = set(), 0
+        for t in tensors:
+            if t.data_ptr() not in seen:
+                seen.add(t.data_ptr())
+                total += t.numel() * t.element_size()
+        return total
+
+    def launches_per_step(self, M: int) -> int:
+        return 0
+
+    @staticmethod
+    def bucket_for(n: int) -> int:
+        for m in BUCKETS:
+            if n <= m:
+                return m
+        raise ValueError(f"{n} rows exceed the largest decode bucket {BUCKETS[-1]}")
+
+    # ------------------------------------------------------------------ sequence state hooks
+    def zero_state(self, slot: int) -> None:
+        self.state[:, slot].zero_()
+        self.ring[:, slot].zero_()
+        self.ple_hist[:, slot].zero_()
+        for ctx in self.ple_ctx:
+            ctx[slot] = self._fresh_ctx()
+
+    def snapshot_state(self, slot: int):
+        return (self.state[:, slot].clone(), self.ring[:, slot].clone(), self.ple_hist[:, slot].clone(),
+                [list(ctx[slot]) for ctx in self.ple_ctx])
+
+    def restore_state(self, slot: int, snap) -> None:
+        self.state[:, slot].copy_(snap[0])
+        self.ring[:, slot].copy_(snap[1])
+        self.ple_hist[:, slot].copy_(snap[2])
+        for ctx, saved in zip(self.ple_ctx, snap[3]):
+            ctx[slot] = list(saved)
+
+    def copy_block(self, src: int, dst: int) -> None:
+        """Copy one page of every paged pool (K, V, raw index keys, block keys)."""
+        s, d = src * K.BLOCK, dst * K.BLOCK
+        for pool in (self.kpool, self.vpool, self.ipool):
+            pool[:, d:d + K.BLOCK].copy_(pool[:, s:s + K.BLOCK])
+        pp = self.per_page
+        self.bkpool[:, dst * pp:(dst + 1) * pp].copy_(self.bkpool[:, src * pp:(src + 1) * pp])
+
+    def embed_tokens(self, tokens: torch.Tensor) -> torch.Tensor:
+        return K.embed_gather(self.embed, tokens)
+
+    def sample(self, logits: torch.Tensor, temps, us) -> torch.Tensor:
+        if temps is None:
+            return K.argmax(logits.contiguous())
+        t = torch.tensor(temps, dtype=torch.float32, device=self.device)
+        u = torch.tensor(us, dtype=torch.float32, device=self.device)
+        return K.sample(logits.contiguous(), t, u)
+
+    # ------------------------------------------------------------------ workspaces
+    def _work(self, T: int) -> dict:
+        """Buffers for a pass over ``T`` rows (kept per size; a prefill chunk and a decode bucket
+        never share them)."""
+        ws = self._ws.get(T)
+        if ws is None:
+            c, dev, bf = self.cfg, self.device, torch.bfloat16
+            H, W = c.hidden_size, c.hc_hidden
+            in_w = max(L.w_in.shape[0] for L in self.layers)
+            mix_w = max(c.lin_vdim, c.num_attention_heads * c.head_dim)
+            nsplit = K.decode_splits(c.num_key_value_heads, T) if T <= 8 else 1
+            ws = {
+                "stream": torch.empty(T, W, dtype=bf, device=dev),
+                "normed": torch.empty(T, W, dtype=bf, device=dev),
+                "low": torch.empty(T, c.hc_lowrank, dtype=torch.float32, device=dev),
+                "mixed": torch.empty(T, H, dtype=bf, device=dev),
+                "inject": [torch.empty(T, c.hc_count, dtype=torch.float32, device=dev) for _ in range(2)],
+                "proj": torch.empty(T, in_w, dtype=bf, device=dev),
+                "act": torch.empty(T, mix_w, dtype=bf, device=dev),
+                "out": [torch.empty(T, H, dtype=bf, device=dev) for _ in range(2)],
+                "q": torch.empty(T, c.num_attention_heads, c.head_dim, dtype=bf, device=dev),
+                "iq": torch.empty(T, c.indexer_n_heads, c.indexer_head_dim, dtype=torch.float32, device=dev),
+                "kv_slot": torch.empty(T, dtype=torch.int32, device=dev),
+                "pos": torch.empty(T, dtype=torch.int32, device=dev),
+                "scores": torch.empty(T, self.max_sel_blocks, dtype=torch.float32, device=dev),
+                "sel": torch.zeros(T, c.block_topk, dtype=torch.int32, device=dev),
+                "nsel": torch.zeros(T, dtype=torch.int32, device=dev),
+                "mask": torch.zeros(T, (self.max_sel_blocks + 31) // 32, dtype=torch.int32, device=dev),
+                "nsplit": nsplit,
+            }
+            if T <= 8:
+                ws["part_o"] = torch.zeros(T, c.num_attention_heads, nsplit, c.head_dim, dtype=torch.float32, device=dev)
+                ws["part_ml"] = torch.zeros(T, c.num_attention_heads, nsplit, 2, dtype=torch.float32, device=dev)
+                ws["tickets"] = torch.zeros(T, c.num_key_value_heads, dtype=torch.int32, device=dev)
+            if self.lin_ids and T > 1:
+                n = K.gdn_prefill_scratch_floats(T, c.linear_num_key_heads, c.linear_num_value_heads,
+                                                 c.linear_key_head_dim, c.linear_value_head_dim)
+                ws["gdn"] = torch.empty(n, dtype=torch.float32, device=dev)
+            if T > 8:                   # keep at most two chunk-sized workspaces
+                big = [k for k in self._ws if k > 8]
+                for k in big[:-1]:
+                    del self._ws[k]
+            self._ws[T] = ws
+        return ws
+
+    def _linear(self, W: torch.Tensor, x: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+        """``out = x @ W^T`` through the GEMV (up to 8 rows whose activations fit its shared memory)
+        or the tcgen05 GEMM."""
+        T, Kd = x.shape
+        if T <= 8 and T * Kd * 2 <= 64 * 1024:
+            return K.gemv(W, x, out)
+        if out.dtype == torch.bfloat16:
+            return K.gemm(x, W, out=out)
+        out.copy_(K.gemm(x, W))
+        return out
+
+    # ------------------------------------------------------------------ hyper-connection
+    def _hyper_read(self, hw: _Hyper, ws: dict, T: int, pending, inject_buf: torch.Tensor | None):
+        """Apply the pending write-back, norm the lanes and return ``(mixed [T, H], inject | None)``."""
+        c = self.cfg
+        H, hc = c.hidden_size, c.hc_count
+        stream, normed = ws["stream"], ws["normed"]
+        bo, inj = pending if pending is not None else (None, None)
+        K.hyper_norm(stream, hw.gain, normed, H=H, hc=hc, eps=self.eps, block_out=bo, inject=inj)
+        if T <= 8:
+            self._linear(hw.Wd, normed, ws["low"])
+            K.hyper_up(normed, ws["low"], hw.Wu, hw.Wi, ws["mixed"], inject_buf if hw.Wi is not None else None, H=H, hc=hc)
+            return ws["mixed"], (inject_buf if hw.Wi is not None else None)
+        low = K.gemm(normed, hw.Wd)
+        act = torch.nn.functional.silu(low.float() / hc).to(torch.bfloat16)
+        gate = torch.sigmoid(K.gemm(act, hw.Wu).float())
+        torch.mul(gate, normed.float(), out=gate)
+        ws["mixed"].copy_(gate.view(T, hc, H).mean(1))
+        K._count(4)
+        inject = None
+        if hw.Wi8 is not None:
+            inject_buf.copy_(2.0 * torch.sigmoid(K.gemm(normed, hw.Wi8)[:, :hc].float() / hc))
+            inject = inject_buf
+            K._count(1)
+        return ws["mixed"], inject
+
+    # ------------------------------------------------------------------ PLE
+    def _ple(self, L, j: int, stream: torch.Tensor, tokens: list[int], slot: int) -> torch.Tensor:
+        """n-gram injection for consecutive tokens of one sequence: returns the fp32 term ``[T, hc*H]``
+        to add to the stream and advances the slot's n-gram context and conv history."""
+        c, P = self.cfg, L.ple
+        hc, H = c.hc_count, c.hidden_size
+        ctx = self.ple_ctx[j][slot]
+        ids = P.hasher.ids(tokens, ctx)
+        emb = P.table.gather(ids).float()                                   # [T, E]
+        T = emb.shape[0]
+
+        def gnorm(x, g):
+            xf = x.reshape(T, hc, H)
+            return (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + self.eps)).reshape(T, hc * H) * g
+
+        key = gnorm(emb @ P.key_w.t(), P.g_key)
+        val = emb @ P.val_w.t()
+        qry = gnorm(stream.float(), P.g_query)
+        g = (key.view(T, hc, H) * qry.view(T, hc, H)).sum(-1, keepdim=True) / math.sqrt(H)
+        g = g.abs().clamp_min(1e-6).sqrt() * g.sign()
+        gv = (torch.sigmoid(g) * val[:, None, :]).reshape(T, hc * H)
+        gvn = gnorm(gv, P.g_conv)
+        hist = self.ple_hist[j, slot]
+        seq = torch.cat([hist, gvn], 0)
+        k, dil, span = c.ple_conv_kernel_size, c.ple_conv_dilation, c.ple_conv_state_len
+        conv = torch.zeros_like(gvn)
+        for tap in range(k):
+            conv += seq[tap * dil:tap * dil + T] * P.conv_w[:, tap]
+        hist.copy_(seq[seq.shape[0] - span:])
+        self.ple_ctx[j][slot] = (ctx + [int(t) for t in tokens])[-c.ple_context_len:]
+        K._count(12)
+        return gv + torch.nn.functional.silu(conv)
+
+    # ------------------------------------------------------------------ mixers
+    def _gdn(self, L, li: int, ws: dict, T: int, mixed, out, *, slot=None, pos0=None, slots=None, positions=None):
+        c = self.cfg
+        j = self.lin_ids[li]
+        proj = ws["proj"][:, :L.w_in.shape[0]]
+        self._linear(L.w_in, mixed, proj)
+        act = ws["act"][:, :c.lin_vdim]
+        kw = dict(nk=c.linear_num_key_heads, nv=c.linear_num_value_heads, dk=c.linear_key_head_dim,
+                  dv=c.linear_value_head_dim, eps=self.eps, gate_sigmoid=self.gate_sigmoid)
+        if slots is not None:
+            K.gdn_decode(proj, L.conv_w, L.A_log, L.dt_bias, L.norm_w, self.ring[j], self.state[j], slots, positions, act, **kw)
+        else:
+            K.gdn_prefill(proj, L.conv_w, L.A_log, L.dt_bias, L.norm_w, self.ring[j, slot], self.state[j, slot],
+                          ws["gdn"], act, pos0=pos0, **kw)
+        self._linear(L.w_out, act, out)
+
+    def _qsa(self, L, li: int, ws: dict, T: int, mixed, out, *, block_tables, positions_host: list[int],
+             shared_table: bool):
+        """``positions_host[t]`` is the position of row ``t``; with ``shared_table`` all rows belong to
+        one sequence (a prefill chunk) whose pages are ``block_tables`` (1-D)."""
+        c = self.cfg
+        j = self.full_ids[li]
+        nh, nkv, hd, rot = c.num_attention_heads, c.num_key_value_heads, c.head_dim, c.rotary_dim
+        ni, di, ratio = c.indexer_n_heads, c.indexer_head_dim, c.indexer_compress_ratio
+        proj = ws["proj"][:, :L.w_in.shape[0]]
+        self._linear(L.w_in, mixed, proj)
+        pos, kv_slot = ws["pos"], ws["kv_slot"]
+        K.attn_prep(proj, L.qg, L.kg, self.cos, self.sin, pos, kv_slot, ws["q"], self.kpool[j], self.vpool[j],
+                    nh=nh, nkv=nkv, hd=hd, rot=rot, eps=self.eps)
+        K.qsa_index_prep(proj, L.idx_col, L.iqg, self.cos, self.sin, pos, kv_slot, ws["iq"], self.ipool[j],
+                         ni=ni, di=di, rot=rot, eps=self.eps)
+        # keys of the blocks that this pass completed
+        if shared_table:
+            b0, b1 = positions_host[0] // ratio, (positions_host[-1] + 1) // ratio
+            K.qsa_block_keys(self.ipool[j], self.bkpool[j], L.ikg, self.cos, self.sin, block_tables, b0, b1,
+                             ratio=ratio, di=di, rot=rot, eps=self.eps)
+        else:
+            for r, p in enumerate(positions_host):
+                if p >= 0 and (p + 1) % ratio == 0:
+                    K.qsa_block_keys(self.ipool[j], self.bkpool[j], L.ikg, self.cos, self.sin, block_tables[r],
+                                     p // ratio, p // ratio + 1, ratio=ratio, di=di, rot=rot, eps=self.eps)
+        act = ws["act"][:, :nh * hd]
+        if T <= 8 and not shared_table:
+            K.qsa_select(ws["iq"], self.bkpool[j], block_tables, pos, ws["scores"], ws["sel"], ws["nsel"],
+                         ni=ni, di=di, ratio=ratio, topk=c.block_topk, full_factor=c.full_select_factor)
+            K.attn_sparse(ws["q"], proj, pos, block_tables, self.kpool[j], self.vpool[j], ws["sel"], ws["nsel"],
+                          ws["part_o"], ws["part_ml"], ws["tickets"], act, nh=nh, nkv=nkv, hd=hd, ratio=ratio,
+                          nsplit=ws["nsplit"])
+        else:
+            nb_last = (positions_host[-1] + 1) // ratio
+            keep = None
+            if nb_last > c.block_topk and nb_last > c.block_topk * c.full_select_factor:
+                K.qsa_select(ws["iq"], self.bkpool[j], block_tables, pos, ws["scores"], ws["sel"], ws["nsel"],
+                             ni=ni, di=di, ratio=ratio, topk=c.block_topk, full_factor=c.full_select_factor,
+                             mask=ws["mask"], shared_table=True)
+                keep = ws["mask"]
+            K.attn_prefill(ws["q"], proj, self.kpool[j], self.vpool[j], block_tables, act, q_pos0=positions_host[0],
+                           nh=nh, nkv=nkv, hd=hd, keep=keep, ratio=ratio)
+        self._linear(L.w_out, act, out)
+
+    # ------------------------------------------------------------------ layer stack
+    def _run(self, ws: dict, T: int, *, tokens_host, slot=None, pos0=None, block_table=None, slots=None,
+             positions=None, positions_host=None, block_tables=None, row_slots=None) -> torch.Tensor:
+        """All layers over the ``T`` rows staged in ``ws['stream']``.  Prefill: one sequence
+        (``slot``, ``pos0``, ``block_table``).  Decode: one token of each of ``T`` sequences
+        (``slots`` / ``positions`` device tensors, ``block_tables [T, pages]``).  Returns the mixed
+        final hidden state ``[T, H]``."""
+        c = self.cfg
+        decode = slots is not None
+        pending = None
+        for li, L in enumerate(self.layers):
+            if L.ple is not None:
+                stream = ws["stream"]
+                if pending is not None:                      # PLE reads the stream with the last write-back applied
+                    stream.add_((pending[0].float()[:, None, :] * pending[1][:, :, None]).flatten(1).to(stream.dtype))
+                    pending = None
+                    K._count()
+                j = self.ple_ids[li]
+                if decode:
+                    for r in range(T):
+                        if row_slots[r] >= 0:
+                            stream[r:r + 1].add_(self._ple(L, j, stream[r:r + 1], [tokens_host[r]], row_slots[r]).to(stream.dtype))
+                else:
+                    stream.add_(self._ple(L, j, stream, tokens_host, slot).to(stream.dtype))
+            inj_a, inj_b = ws["inject"]
+            mixed, inject = self._hyper_read(L.h_attn, ws, T, pending, inj_a)
+            out = ws["out"][0]
+            if L.kind == LINEAR:
+                if decode:
+                    self._gdn(L, li, ws, T, mixed, out, slots=slots, positions=positions)
+                else:
+                    self._gdn(L, li, ws, T, mixed, out, slot=slot, pos0=pos0)
+            else:
+                if decode:
+                    self._qsa(L, li, ws, T, mixed, out, block_tables=block_tables, positions_host=positions_host,
+                              shared_table=False)
+                else:
+                    self._qsa(L, li, ws, T, mixed, out, block_tables=block_table,
+                              positions_host=list(range(pos0, pos0 + T)), shared_table=True)
+            mixed, inject2 = self._hyper_read(L.h_mlp, ws, T, (out, inject), inj_b)
+            out2 = ws["out"][1]
+            out2.copy_(L.moe.apply(mixed.contiguous(), self))
+            pending = (out2, inject2)
+        mixed, _ = self._hyper_read(self.final, ws, T, pending, None)
+        return mixed
+
+    # ------------------------------------------------------------------ engine interface
+    @torch.no_grad()
+    def prefill(self, tokens: torch.Tensor, pos0: int, slot: int, block_table: torch.Tensor, embeds=None,
+                cos_sin=None, want_logits: bool = True, want_hidden: bool = False):
+        """One chunk of one sequence at positions ``pos0 .. pos0 + T - 1``; returns the fp32 logits of
+        the last token (or ``None``)."""
+        if cos_sin is not None:
+            raise NotImplementedError("multi-axis rotary positions are not wired for this family")
+        c = self.cfg
+        T = int(tokens.numel())
+        assert 0 < T <= self.max_chunk
+        if T <= 8:                      # a short tail runs through the decode path (same kernels, fewer buffers)
+            rows = [int(t) for t in tokens.tolist()]
+            out = None
+            for i, tok in enumerate(rows):
+                self.set_rows(1, [tok], [pos0 + i], [slot], [block_table.tolist()])
+                _, logits = self.decode(1, want_logits=want_logits and i == T - 1)
+                out = logits[0] if logits is not None else None
+            return out
+        ws = self._work(T)
+        e = K.embed_gather(self.embed, tokens) if embeds is None else embeds.to(torch.bfloat16)
+        ws["stream"].copy_(e.repeat(1, c.hc_count))
+        pos = torch.arange(pos0, pos0 + T, dtype=torch.int64, device=self.device)
+        ws["pos"].copy_(pos)
+        ws["kv_slot"].copy_(block_table.to(torch.int64)[pos // K.BLOCK] * K.BLOCK + pos % K.BLOCK)
+        mixed = self._run(ws, T, tokens_host=[int(t) for t in tokens.tolist()] if self.ple_ids else None,
+                          slot=slot, pos0=pos0, block_table=block_table)
+        self.last_hidden = mixed if want_hidden else None
+        if not want_logits:
+            return None
+        logits = torch.empty(1, c.vocab_size, dtype=torch.float32, device=self.device)
+        K.gemv(self.lm_head, mixed[T - 1:T].contiguous(), logits)
+        return logits[0]
+
+    def set_rows(self, M: int, tokens, positions, slots, block_tables, rope_deltas=None) -> None:
+        n = len(tokens)
+        dev = self.device
+        bt = torch.zeros(n, self.max_blocks_per_seq, dtype=torch.int32)
+        for r, row in enumerate(block_tables):
+            bt[r, :len(row)] = torch.as_tensor(row, dtype=torch.int32)
+        self._staged = dict(n=n, M=M, tokens=[int(t) for t in tokens], positions=[int(p) for p in positions],
+                            slots=[int(s) for s in slots], bt=bt.to(dev),
+                            tok_dev=torch.tensor(list(tokens), dtype=torch.int64, device=dev),
+                            pos_dev=torch.tensor(list(positions), dtype=torch.int32, device=dev),
+                            slot_dev=torch.tensor(list(slots), dtype=torch.int32, device=dev))
+
+    @torch.no_grad()
+    def decode(self, M: int, graph: bool = True, want_logits: bool = True):
+        """One token for each staged row.  Returns ``(next_tokens [M], logits [M, vocab])``; rows beyond
+        the staged ones are zero."""
+        c, st = self.cfg, self._staged
+        n = st["n"]
+        ws = self._work(n)
+        ws["stream"].copy_(K.embed_gather(self.embed, st["tok_dev"]).repeat(1, c.hc_count))
+        ws["pos"].copy_(st["pos_dev"])
+        p64 = st["pos_dev"].to(torch.int64)
+        ws["kv_slot"].copy_(st["bt"].to(torch.int64).gather(1, (p64 // K.BLOCK)[:, None])[:, 0] * K.BLOCK + p64 % K.BLOCK)
+        mixed = self._run(ws, n, tokens_host=st["tokens"], slots=st["slot_dev"], positions=st["pos_dev"],
+                          positions_host=st["positions"], block_tables=st["bt"], row_slots=st["slots"])
+        b = self._rows.get(M)
+        if b is None:
+            b = self._rows[M] = {"logits": torch.zeros(M, c.vocab_size, dtype=torch.float32, device=self.device),
+                                 "next": torch.zeros(M, dtype=torch.int64, device=self.device)}
+        if not want_logits:
+            return b["next"], None
+        K.gemv(self.lm_head, mixed.contiguous(), b["logits"][:n])
+        K.argmax(b["logits"], b["next"])
+        return b["next"], b["logits"]
+
+    def advance_rows(self, M: int) -> None:
+        st = self._staged
+        nxt = self._rows[M]["next"][:st["n"]].tolist()
+        self.set_rows(M, nxt, [p + 1 for p in st["positions"]], st["slots"],
+                      [row.tolist() for row in st["bt"].cpu()])
+
+    def verify(self, *a, **k):
+        raise NotImplementedError("speculative verification is not offered for the Qwen4-exp family")
+
+    commit = verify

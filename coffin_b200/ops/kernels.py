@@ -239,12 +239,13 @@ def gemm_i8(Aq: torch.Tensor, a_scale: torch.Tensor, Wq: torch.Tensor, w_scale: 
 
 # ------------------------------------------------------------------ gated delta net
 def gdn_decode(proj, conv_w, A_log, dt_bias, norm_w, ring, state, slots, positions, out, *, nk, nv, dk, dv,
-               eps, ntok: int = 1, record: torch.Tensor | None = None, write_state: bool = True) -> torch.Tensor:
+               eps, ntok: int = 1, record: torch.Tensor | None = None, write_state: bool = True,
+               gate_sigmoid: bool = False) -> torch.Tensor:
     M = slots.numel()
     assert proj.shape[0] == M * ntok and slots.dtype == torch.int32 and positions.dtype == torch.int32
     call("gdn_decode", proj, proj.stride(0), conv_w, A_log, dt_bias, norm_w, ring, state, slots, positions,
          out, out.stride(0), record, record.shape[1] if record is not None else 0, M, ntok,
-         int(write_state), nk, nv, dk, dv, float(eps))
+         int(write_state), nk, nv, dk, dv, float(eps), int(gate_sigmoid))
     _count()
     return out
 
@@ -262,11 +263,11 @@ def gdn_prefill_scratch_floats(T: int, nk: int, nv: int, dk: int, dv: int) -> in
 
 
 def gdn_prefill(proj, conv_w, A_log, dt_bias, norm_w, ring_seq, state_seq, scratch, out, *, pos0, nk, nv, dk, dv,
-                eps) -> torch.Tensor:
+                eps, gate_sigmoid: bool = False) -> torch.Tensor:
     T = proj.shape[0]
     assert scratch.dtype == torch.float32 and scratch.numel() >= gdn_prefill_scratch_floats(T, nk, nv, dk, dv)
     call("gdn_prefill", proj, proj.stride(0), conv_w, A_log, dt_bias, norm_w, ring_seq, state_seq, scratch,
-         out, out.stride(0), T, pos0, nk, nv, dk, dv, float(eps))
+         out, out.stride(0), T, pos0, nk, nv, dk, dv, float(eps), int(gate_sigmoid))
     _count(5)
     return out
 
@@ -280,14 +281,70 @@ def attn_prep(proj, qg, kg, cos, sin, rope_idx, kv_slot, q_out, kpool, vpool, *,
 
 
 def attn_prefill(q, proj, kpool, vpool, block_table, out, *, q_pos0, nh, nkv, hd, causal: bool = True,
-                 kv_len: int = 0) -> torch.Tensor:
+                 kv_len: int = 0, keep: torch.Tensor | None = None, ratio: int = 0) -> torch.Tensor:
     """``proj`` supplies the per-head output gate (``None``: no gate). ``causal=False`` attends to the
-    first ``kv_len`` keys of the block table (bidirectional, used by the vision tower)."""
+    first ``kv_len`` keys of the block table (bidirectional, used by the vision tower).  ``keep``
+    (int32 ``[T, words]`` bit mask over blocks of ``ratio`` tokens) restricts query ``t`` to the kept
+    blocks plus the tokens after its last complete block."""
     T = q.shape[0]
     call("attn_prefill", q, proj, proj.stride(0) if proj is not None else 0, kpool, vpool, block_table, out,
-         out.stride(0), T, q_pos0, nh, nkv, hd, int(causal), kv_len)
+         out.stride(0), T, q_pos0, nh, nkv, hd, int(causal), kv_len, keep,
+         keep.stride(0) if keep is not None else 0, ratio)
     _count()
     return out
+
+
+def attn_sparse(q, proj, positions, block_table, kpool, vpool, sel, nsel, part_o, part_ml, tickets, out, *,
+                nh, nkv, hd, ratio, nsplit) -> torch.Tensor:
+    """Block-selected decode attention: ``q [M, nh, hd]`` normed and rotated, the step's K/V already in
+    the pool; row ``m`` reads blocks ``sel[m, :nsel[m]]`` (``nsel < 0``: everything visible) and its tail."""
+    M = positions.numel()
+    call("attn_sparse", q, proj, proj.stride(0), positions, block_table, block_table.stride(0), kpool, vpool, sel,
+         nsel, sel.shape[1], ratio, part_o, part_ml, tickets, out, out.stride(0), M, nh, nkv, hd, nsplit)
+    _count()
+    return out
+
+
+# ------------------------------------------------------------------ Qwen4-exp: hyper-connection, QSA indexer
+def hyper_norm(stream, gain, normed, *, H, hc, eps, block_out=None, inject=None, add=None) -> torch.Tensor:
+    """Grouped zero-centred RMSNorm of the ``hc`` lanes of ``stream [M, hc*H]`` into ``normed``; a
+    pending write-back (``stream += add``, then ``stream += block_out (x) inject``) is applied first, in place."""
+    M = stream.shape[0]
+    assert stream.is_contiguous() and normed.is_contiguous()
+    call("hyper_norm", stream, gain, block_out, inject, add, normed, M, H, hc, float(eps))
+    _count()
+    return normed
+
+
+def hyper_up(normed, low, Wu, Wi, mixed, inject, *, H, hc) -> None:
+    """Read gate + lane mix (``mixed [M, H]``) and write gates (``inject [M, hc]`` fp32) for M <= 8 rows."""
+    M, R = low.shape
+    call("hyper_up", normed, low, Wu, Wi, mixed, inject, M, H, hc, R)
+    _count()
+
+
+def qsa_index_prep(proj, col0, qgain, cos, sin, rope_idx, kv_slot, iq, ipool, *, ni, di, rot, eps) -> None:
+    T = proj.shape[0]
+    call("qsa_index_prep", proj, proj.stride(0), col0, qgain, cos, sin, rope_idx, kv_slot, iq, ipool, T, ni, di,
+         rot, float(eps))
+    _count()
+
+
+def qsa_block_keys(ipool, bkpool, kgain, cos, sin, block_table, b0, b1, *, ratio, di, rot, eps) -> None:
+    """Keys of the blocks ``[b0, b1)`` of the sequence behind ``block_table`` (all their tokens stored)."""
+    if b1 > b0:
+        call("qsa_block_keys", ipool, bkpool, kgain, cos, sin, block_table, b0, b1, ratio, di, rot, float(eps))
+        _count()
+
+
+def qsa_select(iq, bkpool, block_table, positions, scores, sel, nsel, *, ni, di, ratio, topk, full_factor,
+               mask=None, row_seq=None, shared_table: bool = False) -> None:
+    """Top-``topk`` blocks per query row (``sel`` ascending, ``nsel``; -1 = attend to everything)."""
+    rows = positions.numel()
+    ldbt = 0 if shared_table else block_table.stride(0)
+    call("qsa_select", iq, bkpool, block_table, ldbt, positions, row_seq, scores, sel, nsel, mask,
+         mask.stride(0) if mask is not None else 0, rows, ni, di, ratio, topk, full_factor, scores.shape[1])
+    _count()
 
 
 def attn_decode(proj, qg, kg, cos, sin, positions, rope_pos, block_table, kpool, vpool, part_o, part_ml, tickets,
@@ -302,5 +359,6 @@ def attn_decode(proj, qg, kg, cos, sin, positions, rope_pos, block_table, kpool,
 
 
 def decode_splits(nkv: int, rows: int) -> int:
-    """Key-tile splits so that a decode attention launch covers about two waves of SMs."""
-    return max(1, min(32, 296 // max(1, nkv * rows)))
+    """Key-tile splits so that a decode attention launch (one 8-warp CTA per kv head, split and
+    row) covers about one wave of SMs."""
+    return max(1, min(32, 148 // max(1, nkv * rows)))

@@ -23,8 +23,13 @@ BUCKETS = (1, 2, 4, 8)
 
 class OracleEngineModel:
     def __init__(self, cfg: ModelConfig, sd: dict[str, torch.Tensor], max_seq: int = 1024, num_slots: int = 4,
-                 num_blocks: int | None = None, max_chunk: int = 2048) -> None:
+                 num_blocks: int | None = None, max_chunk: int = 2048, pp_first: bool = True,
+                 pp_last: bool = True) -> None:
         self.cfg = cfg
+        self.pp_first, self.pp_last = pp_first, pp_last
+        self.lane = 0
+        self.input_hidden = None
+        self._lanes: dict = {}
         self.sd = {k: v.float() if v.is_floating_point() else v for k, v in sd.items()}
         self.device = torch.device("cpu")
         self.max_seq, self.num_slots, self.max_chunk = max_seq, num_slots, max_chunk
@@ -151,28 +156,52 @@ class OracleEngineModel:
         else:
             cos, sin = cos_sin
         x = self._forward(x, pos0, slot, block_table, cos, sin)
+        self.last_prenorm = x
+        if not self.pp_last:
+            return None
         self.last_hidden = self._norm(x, LM + "norm.weight") if want_hidden else None
         return self._head(x[-1:])[0] if want_logits else None
 
     def set_rows(self, M, tokens, positions, slots, block_tables, rope_deltas=None) -> None:
         self._rows = dict(tokens=list(tokens), positions=list(positions), slots=list(slots),
                           tables=[list(t) for t in block_tables],
-                          deltas=list(rope_deltas) if rope_deltas else [0] * len(tokens))
+                          deltas=list(rope_deltas) if rope_deltas else [0] * len(tokens),
+                          next=torch.zeros(M, dtype=torch.int64), hidden=torch.zeros(M, self.cfg.hidden_size))
+        self._lanes[(M, self.lane)] = self._rows
+
+    def _row_buffers(self, M: int) -> dict:
+        return self._lanes[(M, self.lane)]
+
+    def stage_hidden(self, M: int) -> torch.Tensor:
+        """Residual stream after this stage's layers for the rows of the last decode step."""
+        return self._row_buffers(M)["hidden"]
+
+    def advance_rows(self, M: int) -> None:
+        r = self._row_buffers(M)
+        n = len(r["tokens"])
+        r["tokens"] = [int(t) for t in r["next"][:n]]
+        r["positions"] = [p + 1 for p in r["positions"]]
 
     @torch.no_grad()
     def decode(self, M: int, graph: bool = True):
         self.n_decode_calls += 1
-        r, c = self._rows, self.cfg
+        r, c = self._lanes.get((M, self.lane), self._rows), self.cfg
         n = len(r["tokens"])
         logits = torch.zeros(M, c.vocab_size)
         for i in range(n):
             pos = r["positions"][i]
             rp = torch.tensor([pos + r["deltas"][i]])
             cos, sin = O.mrope_cos_sin(rp.reshape(1, -1).expand(3, -1), c.rotary_dim, c.rope_theta, c.mrope_section)
-            x = self.embed_tokens(torch.tensor([r["tokens"][i]]))
+            if self.input_hidden is not None:
+                x = self.input_hidden[i:i + 1].float()
+            else:
+                x = self.embed_tokens(torch.tensor([r["tokens"][i]]))
             x = self._forward(x, pos, r["slots"][i], torch.tensor(r["tables"][i], dtype=torch.int32), cos, sin)
-            logits[i] = self._head(x)[0]
-        return logits.argmax(-1), logits
+            r["hidden"][i] = x[0]
+            if self.pp_last:
+                logits[i] = self._head(x)[0]
+        r["next"] = logits.argmax(-1)
+        return r["next"], logits
 
     @torch.no_grad()
     def verify(self, tokens: list[int], pos0: int, slot: int, block_table: torch.Tensor, rope_delta: int = 0) -> torch.Tensor:

@@ -101,6 +101,7 @@ def shard_state_dict(cfg: ModelConfig, sd: dict[str, torch.Tensor], rank: int, w
 class _TpCommStruct(ctypes.Structure):
     _fields_ = [("rank", ctypes.c_int), ("world", ctypes.c_int), ("slot_floats", ctypes.c_int64),
                 ("inbox", ctypes.c_void_p * MAX_WORLD), ("flags", ctypes.c_void_p * MAX_WORLD),
+                ("my_inbox", ctypes.c_void_p), ("my_flags", ctypes.c_void_p),
                 ("arrive", ctypes.c_void_p), ("epoch", ctypes.c_void_p), ("status", ctypes.c_void_p)]
 
 
@@ -156,6 +157,7 @@ class TpComm:
         for r in range(world):
             s.inbox[r] = self.peers[r]
             s.flags[r] = self.peers[r] + self._off_flags
+        s.my_inbox, s.my_flags = self.peers[rank], self.peers[rank] + self._off_flags
         s.arrive = self.base + self._off_arrive
         s.epoch = self.base + self._off_epoch
         s.status = self.base + self._off_status

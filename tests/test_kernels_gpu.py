@@ -62,7 +62,7 @@ def test_rowwise_kernels():
 
 
 @pytest.mark.parametrize("M", [1, 2, 4, 8])
-@pytest.mark.parametrize("N,Kd", [(520, 512), (2560, 1032), (37, 264), (6000, 256)])
+@pytest.mark.parametrize("N,Kd", [(520, 512), (2560, 1032), (37, 264), (6000, 256), (256, 4096), (1000, 2304)])
 def test_gemv(M, N, Kd):
     k = K()
     W, x = bf(N, Kd, s=0.05, seed=5), bf(M, Kd, seed=6)
@@ -74,10 +74,11 @@ def test_gemv(M, N, Kd):
     close(out32, x.float() @ W.float().t(), 1e-3)
 
 
-@pytest.mark.parametrize("M", [1, 4])
-def test_gemv_fused_norm_swiglu(M):
+@pytest.mark.parametrize("M,H,I", [(1, 520, 264), (4, 520, 264), (1, 4096, 256), (4, 2048, 520)])
+def test_gemv_fused_norm_swiglu(M, H, I):
+    """The last two shapes have few output rows and a long K: several CTAs share a 16-row block and
+    the last one to arrive adds their partial sums (cross-CTA K split)."""
     k = K()
-    H, I = 520, 264
     Wgu, res, add = bf(2 * I, H, s=0.05, seed=7), bf(M, H, seed=8), bf(M, H, seed=9)
     gain = (1 + 0.1 * torch.randn(H)).float()
     out = torch.empty(M, I, dtype=torch.bfloat16, device=DEV)

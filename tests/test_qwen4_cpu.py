@@ -1,0 +1,80 @@
+"""Qwen4-exp family on the CPU: config round trip, n-gram hashing, oracle self-consistency."""
+import torch
+
+from coffin_b200.models.qwen4exp.config import Qwen4Config, tiny_qwen4
+from coffin_b200.models.qwen4exp.ngram import NGramHasher, NGramTable, is_prime, layer_multipliers, splitmix64
+from coffin_b200.models.qwen4exp.oracle import Qwen4Oracle, qsa_select
+from coffin_b200.models.qwen4exp.weights import param_count, random_state_dict, tensor_plan
+
+
+def test_config_round_trip_and_derived_fields():
+    cfg = tiny_qwen4()
+    assert cfg.layer_types.count("indexed_attention") == 2 and cfg.block_topk == 4
+    assert cfg.ple_index(1) == 0 and cfg.ple_index(0) is None
+    again = Qwen4Config.from_hf(cfg.to_hf(), name=cfg.name)
+    for f in ("layer_types", "hc_count", "indexer_budget", "ple_layer_ids", "mrope_section", "rotary_dim", "ngram_heads"):
+        assert getattr(again, f) == getattr(cfg, f), f
+    assert param_count(cfg) == sum(torch.Size(s).numel() for _, s, _ in tensor_plan(cfg))
+
+
+def test_ngram_hash_properties():
+    assert splitmix64(0) == 0xE220A8397B1DCDAF            # published test vector of the generator
+    m = layer_multipliers(1024, 3, 0, 1234)
+    assert all(v % 2 == 1 and v > 0 for v in m) and len(set(m)) == 3
+    cfg = tiny_qwen4()
+    h = NGramHasher(cfg, 0)
+    assert all(is_prime(s) and s >= cfg.ngram_vocab_size_base for s in h.sizes) and len(set(h.sizes)) == h.heads
+    ids = h.ids([5, 9, 9, 5, 1, 5, 9], None)
+    assert ids.shape == (7, h.heads)
+    for j in range(h.heads):
+        assert (ids[:, j] >= h.offsets[j]).all() and (ids[:, j] < h.offsets[j] + h.sizes[j]).all()
+    # same 3-gram -> same rows; history does not cross the end-of-sequence token (id 1)
+    a = h.ids([7, 5, 9], None)[2]
+    b = h.ids([3, 3, 7, 5, 9], None)[4]
+    assert torch.equal(a, b)
+    after_eos = h.ids([5, 9, 1, 9], None)[3]
+    fresh = h.ids([9], None)[0]
+    assert torch.equal(after_eos, fresh)
+    # incremental hashing with a carried context equals hashing the whole history
+    whole = h.ids([4, 8, 15, 16, 23], None)
+    step = h.ids([16, 23], [8, 15])
+    assert torch.equal(whole[3:], step)
+
+
+def test_ngram_table_gather_on_cpu():
+    w = torch.arange(40, dtype=torch.float32).reshape(10, 4)
+    t = NGramTable(w, "cpu")
+    ids = torch.tensor([[0, 9], [3, 3]])
+    assert torch.equal(t.gather(ids), torch.cat([w[0], w[9], w[3], w[3]]).reshape(2, 8))
+
+
+def test_block_selection_rule():
+    cfg = tiny_qwen4()                       # ratio 4, topk 4, full-select factor 2
+    g = torch.Generator().manual_seed(0)
+    iq = torch.randn(cfg.indexer_n_heads, cfg.indexer_head_dim, generator=g)
+    bk = torch.randn(30, cfg.indexer_head_dim, generator=g)
+    assert qsa_select(iq, bk, 35, cfg).all()                       # 8 blocks <= 2 * topk: everything
+    keep = qsa_select(iq, bk, 103, cfg)                            # 25 blocks + 3 tail tokens
+    assert keep[100:].all() and int(keep.sum()) == 4 * 4 + 3
+    s = torch.relu(iq @ bk[:25].t()).sum(0)
+    best = int(s.argmax())
+    assert keep[best * 4:(best + 1) * 4].all()
+
+
+def test_oracle_chunked_and_incremental_equal_one_shot():
+    cfg = tiny_qwen4()
+    sd = random_state_dict(cfg, 0)
+    o = Qwen4Oracle(cfg, sd)
+    g = torch.Generator().manual_seed(0)
+    toks = torch.randint(0, cfg.vocab_size, (80,), generator=g)
+    toks[30] = cfg.eos_token_id
+    full = o.forward(toks, o.new_state())
+    st = o.new_state()
+    parts = [o.forward(toks[:33], st), o.forward(toks[33:72], st)] + [o.forward(toks[i:i + 1], st) for i in range(72, 80)]
+    assert torch.allclose(torch.cat(parts), full, atol=2e-5)
+    assert o.last_selected[7].shape == (1, 80) and int(o.last_selected[7].sum()) == 16     # sparse at 80 tokens
+    # a cloned state continues identically
+    st2 = o.new_state()
+    o.forward(toks[:40], st2)
+    st3 = st2.clone()
+    assert torch.equal(o.forward(toks[40:50], st2), o.forward(toks[40:50], st3))

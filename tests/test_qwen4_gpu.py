@@ -1,0 +1,158 @@
+"""Qwen4-exp family on the GPU: hyper-connection and QSA kernels against the fp32 oracle functions,
+then the whole model (prefill + decode) against ``Qwen4Oracle``."""
+import math
+
+import pytest
+import torch
+
+from coffin_b200.models.qwen4exp.config import tiny_qwen4
+from coffin_b200.models.qwen4exp.oracle import (Qwen4Oracle, grouped_rms_norm, hyper_read, hyper_write,
+                                                qsa_block_keys, qsa_select)
+from coffin_b200.models.qwen4exp.weights import random_state_dict
+from coffin_b200.oracle import ops as O
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _rel(a, b):
+    return ((a.float().cpu() - b.float()).abs().max() / b.float().abs().max().clamp_min(1e-6)).item()
+
+
+@pytest.mark.parametrize("M", [1, 3, 8])
+def test_hyper_connection_kernels(M):
+    from coffin_b200.ops import kernels as K
+    cfg = tiny_qwen4(hidden_size=256, hc_lowrank=64)
+    H, hc, R = cfg.hidden_size, cfg.hc_count, cfg.hc_lowrank
+    g = torch.Generator().manual_seed(M)
+    bf = lambda *s, sc=1.0: (torch.randn(*s, generator=g) * sc).to(torch.bfloat16)
+    p = {"hc_norm.weight": torch.randn(hc * H, generator=g) * 0.1,
+         "input_mix_weight_down.weight": bf(R, hc * H, sc=0.05).float(),
+         "input_mix_weight_up.weight": bf(hc * H, R, sc=0.3).float(),
+         "block_inject_weight.weight": bf(hc, hc * H, sc=0.05).float()}
+    x, out, inj = bf(M, hc * H), bf(M, H), torch.rand(M, hc, generator=g) * 2
+    # oracle: write back the pending mixer output, then read
+    xw = hyper_write(x.float(), out.float(), inj, cfg).to(torch.bfloat16)
+    n_ref = grouped_rms_norm(xw, p["hc_norm.weight"], H, cfg.rms_norm_eps)
+    mixed_ref, inject_ref = hyper_read(xw.float(), p, "", cfg)
+    stream, normed = x.to(DEV).clone(), torch.empty(M, hc * H, dtype=torch.bfloat16, device=DEV)
+    K.hyper_norm(stream, (1 + p["hc_norm.weight"]).to(DEV), normed, H=H, hc=hc, eps=cfg.rms_norm_eps,
+                 block_out=out.to(DEV), inject=inj.to(DEV))
+    assert _rel(stream, xw) < 1e-2 and _rel(normed, n_ref) < 2e-2
+    low = torch.empty(M, R, dtype=torch.float32, device=DEV)
+    K.gemv(p["input_mix_weight_down.weight"].to(DEV, torch.bfloat16), normed, low)
+    mixed = torch.empty(M, H, dtype=torch.bfloat16, device=DEV)
+    inject = torch.empty(M, hc, dtype=torch.float32, device=DEV)
+    K.hyper_up(normed, low, p["input_mix_weight_up.weight"].to(DEV, torch.bfloat16),
+               p["block_inject_weight.weight"].to(DEV, torch.bfloat16), mixed, inject, H=H, hc=hc)
+    assert _rel(mixed, mixed_ref) < 3e-2
+    assert _rel(inject, inject_ref) < 2e-2
+
+
+def test_qsa_index_kernels_and_selection():
+    from coffin_b200.ops import kernels as K
+    cfg = tiny_qwen4()
+    ni, di, ratio, rot, topk = cfg.indexer_n_heads, cfg.indexer_head_dim, cfg.indexer_compress_ratio, cfg.rotary_dim, cfg.block_topk
+    T = 150
+    g = torch.Generator().manual_seed(3)
+    proj = torch.randn(T, (ni + 1) * di + 8, generator=g).to(torch.bfloat16)
+    qw, kw = torch.randn(di, generator=g) * 0.1, torch.randn(di, generator=g) * 0.1
+    cos, sin = O.rope_tables(rot, cfg.rope_theta, 256)
+    # oracle
+    iq_ref = O.apply_rope(O.rms_norm(proj[:, 8:8 + ni * di].float().reshape(T, ni, di), 1 + qw, cfg.rms_norm_eps), cos[:T], sin[:T], rot)
+    raw = proj[:, 8 + ni * di:].float()
+    bk_ref = qsa_block_keys(raw, kw, cos, sin, ratio, rot, cfg.rms_norm_eps)
+    # device: pages 3, 1, 2 hold tokens 0..63, 64..127, 128..191
+    pages = torch.tensor([3, 1, 2], dtype=torch.int32, device=DEV)
+    pos = torch.arange(T, dtype=torch.int32, device=DEV)
+    kv_slot = (pages.long()[pos.long() // 64] * 64 + pos.long() % 64).to(torch.int32)
+    iq = torch.empty(T, ni, di, dtype=torch.float32, device=DEV)
+    ipool = torch.zeros(4 * 64, di, dtype=torch.bfloat16, device=DEV)
+    K.qsa_index_prep(proj.to(DEV), 8, (1 + qw).to(DEV), cos.to(DEV), sin.to(DEV), pos, kv_slot, iq, ipool,
+                     ni=ni, di=di, rot=rot, eps=cfg.rms_norm_eps)
+    assert _rel(iq, iq_ref) < 1e-2
+    assert torch.equal(ipool[kv_slot.long()].cpu(), proj[:, 8 + ni * di:])
+    per_page = 64 // ratio
+    bkpool = torch.zeros(4 * per_page, di, dtype=torch.float32, device=DEV)
+    K.qsa_block_keys(ipool, bkpool, (1 + kw).to(DEV), cos.to(DEV), sin.to(DEV), pages, 0, T // ratio,
+                     ratio=ratio, di=di, rot=rot, eps=cfg.rms_norm_eps)
+    nb = T // ratio
+    blk_rows = torch.tensor([int(pages[b // per_page]) * per_page + b % per_page for b in range(nb)])
+    got_bk = bkpool[blk_rows.to(DEV)].cpu()
+    assert _rel(got_bk, bk_ref) < 2e-2
+    # selection on the device block keys (so that both sides rank identical numbers)
+    rows = torch.tensor([10, 40, 99, 149], dtype=torch.int32, device=DEV)
+    sel = torch.zeros(4, topk, dtype=torch.int32, device=DEV)
+    nsel = torch.zeros(4, dtype=torch.int32, device=DEV)
+    scores = torch.zeros(4, 64, dtype=torch.float32, device=DEV)
+    mask = torch.zeros(4, 2, dtype=torch.int32, device=DEV)
+    K.qsa_select(iq[rows.long()].contiguous(), bkpool, pages, rows, scores, sel, nsel, ni=ni, di=di, ratio=ratio,
+                 topk=topk, full_factor=cfg.full_select_factor, mask=mask, shared_table=True)
+    for i, p in enumerate(rows.tolist()):
+        keep = qsa_select(iq[p].cpu(), got_bk, p + 1, cfg)
+        nblk = (p + 1) // ratio
+        if nblk <= topk * cfg.full_select_factor:
+            assert int(nsel[i]) == -1 and int(mask[i, 0]) == -1
+            continue
+        want = [b for b in range(nblk) if keep[b * ratio]]
+        assert int(nsel[i]) == topk and sel[i].tolist() == want
+        bits = (int(mask[i, 0]) & 0xffffffff) | ((int(mask[i, 1]) & 0xffffffff) << 32)
+        assert [b for b in range(64) if bits >> b & 1] == want
+
+
+@torch.no_grad()
+def test_qwen4_model_prefill_and_decode_match_oracle():
+    from coffin_b200.models.qwen4exp.model import Qwen4ExpModel
+    cfg = tiny_qwen4()
+    sd = random_state_dict(cfg, 0)
+    sd_b = {k: (v.to(torch.bfloat16).float() if not k.endswith(("A_log", "dt_bias")) else v) for k, v in sd.items()}
+    oracle = Qwen4Oracle(cfg, sd_b)
+    model = Qwen4ExpModel(cfg, sd, max_seq=256, num_slots=2)
+    g = torch.Generator().manual_seed(0)
+    toks = torch.randint(0, cfg.vocab_size, (112,), generator=g)
+    toks[40] = cfg.eos_token_id
+    st = oracle.new_state()
+    bt = torch.arange(1, 5, dtype=torch.int32, device=DEV)
+    model.zero_state(0)
+    # two chunks: the second one crosses into the sparse regime (more than 8 blocks of 4 tokens)
+    model.prefill(toks[:30].to(DEV), 0, 0, bt, want_logits=False)
+    got = model.prefill(toks[30:100].to(DEV), 30, 0, bt)
+    ref = oracle.forward(toks[:100], st)[-1]
+    assert _rel(got, ref) < 8e-2
+    for i in range(100, 112):
+        ref = oracle.forward(toks[i:i + 1], st)[-1]
+        model.set_rows(1, [int(toks[i])], [i], [0], [bt.tolist()])
+        _, logits = model.decode(1)
+        assert _rel(logits[0], ref) < 8e-2, f"step {i}"
+    from coffin_b200.ops import kernels as K
+    torch.cuda.synchronize()
+    K.check_status()
+
+
+@torch.no_grad()
+def test_qwen4_batched_decode_and_state_snapshot():
+    from coffin_b200.models.qwen4exp.model import Qwen4ExpModel
+    cfg = tiny_qwen4()
+    sd = random_state_dict(cfg, 0)
+    model = Qwen4ExpModel(cfg, sd, max_seq=256, num_slots=3)
+    g = torch.Generator().manual_seed(5)
+    seqs = [torch.randint(2, cfg.vocab_size, (n,), generator=g) for n in (70, 45)]
+    tables = [list(range(1, 5)), list(range(5, 9))]
+    single = []
+    for r, s in enumerate(seqs):
+        model.zero_state(r)
+        bt = torch.tensor(tables[r], dtype=torch.int32, device=DEV)
+        model.prefill(s[:-1].to(DEV), 0, r, bt, want_logits=False)
+    snaps = [model.snapshot_state(r) for r in range(2)]
+    # both rows in one batched step
+    model.set_rows(2, [int(s[-1]) for s in seqs], [len(s) - 1 for s in seqs], [0, 1], tables)
+    _, lg = model.decode(2)
+    batched = lg[:2].clone()
+    # the same rows one at a time from the restored states
+    for r, s in enumerate(seqs):
+        model.restore_state(r, snaps[r])
+        model.set_rows(1, [int(s[-1])], [len(s) - 1], [r], [tables[r]])
+        _, lg1 = model.decode(1)
+        single.append(lg1[0].clone())
+    for r in range(2):
+        assert _rel(batched[r], single[r].cpu()) < 2e-2

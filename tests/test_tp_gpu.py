@@ -101,28 +101,32 @@ def test_two_rank_tensor_parallel_matches_oracle(tmp_path):
 
 @torch.no_grad()
 def test_expert_parallel_push_path_on_one_gpu():
-    """MoE decode with the combine kernel pushing its output through the peer inbox (world 1)."""
+    """MoE decode with the combine kernel pushing its output through the peer inbox (world 1).
+    The pushed partial sums stay fp32 until the consumer adds them, so the rounding differs from the
+    single-GPU path and a router near-tie may flip: the check is against the oracle, as for the
+    plain MoE model."""
     from coffin_b200.models.qwen35.model import Qwen35Model
     from coffin_b200.parallel.tp import TpComm
     cfg = preset("tiny-moe")
     sd = random_state_dict(cfg, 0)
-    plain = Qwen35Model(cfg, sd, max_seq=256, num_slots=2)
+    sd_b = {k: (v.to(torch.bfloat16).float() if not k.endswith(("A_log", "dt_bias")) else v) for k, v in sd.items()}
+    oracle = OracleModel(cfg, sd_b)
     tp = TpComm(0, 1, cfg.hidden_size, 8, 2 * cfg.num_hidden_layers)
     fused = Qwen35Model(cfg, sd, max_seq=256, num_slots=2, tp=tp)
     fused.tp_force = True
     g = torch.Generator().manual_seed(2)
-    toks = torch.randint(0, cfg.vocab_size, (40,), generator=g)
+    toks = torch.randint(0, cfg.vocab_size, (44,), generator=g)
     bt = torch.arange(1, 5, dtype=torch.int32, device="cuda")
-    for m in (plain, fused):
-        m.zero_state(0)
-        m.prefill(toks[:32].cuda(), 0, 0, bt, want_logits=False)
-    for i in range(32, 38):
-        outs = []
-        for m in (plain, fused):
-            m.set_rows(1, [int(toks[i])], [i], [0], [bt.tolist()])
-            outs.append(m.decode(1, graph=i >= 35)[1][0].clone())
-        rel = ((outs[0] - outs[1]).abs().max() / outs[0].abs().max()).item()
-        assert rel < 3e-2, f"step {i}: {rel}"
+    st = oracle.new_state()
+    oracle.forward(toks[:32], st)
+    fused.zero_state(0)
+    fused.prefill(toks[:32].cuda(), 0, 0, bt, want_logits=False)
+    for i in range(32, 44):
+        ref = oracle.forward(toks[i:i + 1], st)[-1]
+        fused.set_rows(1, [int(toks[i])], [i], [0], [bt.tolist()])
+        got = fused.decode(1, graph=i >= 36)[1][0].float().cpu()
+        rel = ((got - ref).abs().max() / ref.abs().max()).item()
+        assert rel < 8e-2, f"step {i}: {rel}"
     torch.cuda.synchronize()
     assert tp.status() == 0
     tp.close()
