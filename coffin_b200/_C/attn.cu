@@ -333,6 +333,7 @@ __global__ void __launch_bounds__(kDecWarps * 32) attn_decode_kernel(const Decod
   __shared__ __align__(16) float mo[kDecWarps / 2][REP][HD];
   __shared__ float mml[kDecWarps / 2][REP][2];
   __shared__ float sc_s[REP][64];                 // per-split scales of the final merge (nsplit <= 64)
+  __shared__ float l_s[REP][64];
   __shared__ float linv_s[REP];
   const int kvh = blockIdx.x, split = blockIdx.y, m = blockIdx.z;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -547,18 +548,24 @@ __global__ void __launch_bounds__(kDecWarps * 32) attn_decode_kernel(const Decod
   const float* bo = a.part_o + ((int64_t)m * a.nh + kvh * REP) * a.nsplit * HD;
   const float* bml = a.part_ml + ((int64_t)m * a.nh + kvh * REP) * a.nsplit * 2;
   const int ns = a.nsplit;
-  for (int i = tid; i < REP * ns; i += NT) sc_s[i / ns][i % ns] = __ldcg(bml + (int64_t)i * 2);       // m of (r, sp)
+  for (int i = tid; i < REP * ns; i += NT) {                       // (m, l) of every (head, split): one parallel pass
+    sc_s[i / ns][i % ns] = __ldcg(bml + (int64_t)i * 2);
+    l_s[i / ns][i % ns] = __ldcg(bml + (int64_t)i * 2 + 1);
+  }
   __syncthreads();
-  if (tid < REP) {
+  if (warp < REP) {                                               // one warp per head: max, scales, 1 / l
+    const int r = warp;
     float Mx = -INFINITY;
-    for (int sp = 0; sp < ns; ++sp) Mx = fmaxf(Mx, sc_s[tid][sp]);
+    for (int sp = lane; sp < ns; sp += 32) Mx = fmaxf(Mx, sc_s[r][sp]);
+    Mx = warp_max(Mx);
     float L = 0.f;
-    for (int sp = 0; sp < ns; ++sp) {
-      const float c = Mx == -INFINITY ? 0.f : exp2f(sc_s[tid][sp] - Mx);
-      sc_s[tid][sp] = c;
-      L += __ldcg(bml + ((int64_t)tid * ns + sp) * 2 + 1) * c;
+    for (int sp = lane; sp < ns; sp += 32) {
+      const float c = Mx == -INFINITY ? 0.f : exp2f(sc_s[r][sp] - Mx);
+      sc_s[r][sp] = c;
+      L += l_s[r][sp] * c;
     }
-    linv_s[tid] = L > 0.f ? 1.f / L : 0.f;
+    L = warp_sum(L);
+    if (lane == 0) linv_s[r] = L > 0.f ? 1.f / L : 0.f;
   }
   __syncthreads();
   for (int idx = tid; idx < REP * (HD / 4); idx += NT) {

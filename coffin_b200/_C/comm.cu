@@ -12,7 +12,89 @@ __global__ void epoch_bump_kernel(unsigned* epoch) {
   griddep_wait();
   if (threadIdx.x == 0) *epoch += 1;
 }
+
+// Scatter an existing [T, width] bf16 tensor into the owners' inboxes (producers that are not a GEMM,
+// e.g. the MoE combine under expert parallelism).
+__global__ void __launch_bounds__(256) tp_pf_scatter_kernel(const TpPfDev* d, const bf16* src, int64_t lds, int T,
+                                                            unsigned seq) {
+  griddep_launch();
+  griddep_wait();
+  const int rpr = d->rows_per_rank, W = d->width, vec = W >> 3;
+  for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < (int64_t)T * vec; i += (int64_t)gridDim.x * 256) {
+    const int row = (int)(i / vec), c = (int)(i % vec) * 8;
+    const int owner = row / rpr, lr = row % rpr;
+    bf16* dst = d->inbox[owner] + ((int64_t)d->rank * rpr + lr) * W + c;
+    *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(src + (int64_t)row * lds + c);
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) tp_pf_publish(d, 1, seq, gridDim.x);
+}
+
+// Sum the partial slices this rank received (rank order), add the residual rows, store the reduced
+// rows into every rank's result buffer.
+__global__ void __launch_bounds__(256) tp_pf_reduce_gather_kernel(const TpPfDev* d, const bf16* residual, int64_t ldr,
+                                                                  int T, unsigned seq) {
+  griddep_launch();
+  griddep_wait();
+  tp_pf_wait(d->flags1[d->rank], d->world, seq, d->status, d->wait_ns);
+  const int rpr = d->rows_per_rank, W = d->width, vec = W >> 3, world = d->world;
+  const int row0 = d->rank * rpr;
+  const int nrows = max(0, min(rpr, T - row0));
+  const bf16* in = d->inbox[d->rank];
+  for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < (int64_t)nrows * vec; i += (int64_t)gridDim.x * 256) {
+    const int lr = (int)(i / vec), c = (int)(i % vec) * 8;
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int r = 0; r < world; ++r) {
+      float f[8];
+      bf16x8_to_float(__ldcg(reinterpret_cast<const uint4*>(in + ((int64_t)r * rpr + lr) * W + c)), f);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[e] += f[e];
+    }
+    if (residual) {
+      float f[8];
+      bf16x8_to_float(*reinterpret_cast<const uint4*>(residual + (int64_t)(row0 + lr) * ldr + c), f);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[e] += f[e];
+    }
+    const uint4 v = float_to_bf16x8(acc);
+    for (int p = 0; p < world; ++p)
+      *reinterpret_cast<uint4*>(d->out[p] + (int64_t)(row0 + lr) * W + c) = v;
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) tp_pf_publish(d, 2, seq, gridDim.x);
+}
+
+__global__ void tp_pf_wait_kernel(const TpPfDev* d, unsigned seq) {
+  griddep_launch();
+  griddep_wait();
+  tp_pf_wait(d->flags2[d->rank], d->world, seq, d->status, d->wait_ns);
+}
 }  // namespace
+
+CB_EXPORT int cb_tp_pf_scatter(const void* desc, const void* src, int64_t lds, int64_t T, int64_t seq, void* stream) {
+  if (!desc || !src || T < 1 || lds % 8) return CB_ERR_ARG;
+  return (int)cb_launch(tp_pf_scatter_kernel, dim3(148), dim3(256), 0, (cudaStream_t)stream, (const TpPfDev*)desc,
+                        (const bf16*)src, lds, (int)T, (unsigned)seq);
+}
+// Second half of the prefill all-reduce; the result is in this rank's result buffer once
+// cb_tp_pf_wait (launched right after) has returned.
+CB_EXPORT int cb_tp_pf_reduce_gather(const void* desc, const void* residual, int64_t ldr, int64_t T, int64_t seq,
+                                     void* stream) {
+  if (!desc || T < 1 || (residual && ldr % 8)) return CB_ERR_ARG;
+  return (int)cb_launch(tp_pf_reduce_gather_kernel, dim3(148), dim3(256), 0, (cudaStream_t)stream,
+                        (const TpPfDev*)desc, (const bf16*)residual, ldr, (int)T, (unsigned)seq);
+}
+CB_EXPORT int cb_tp_pf_wait(const void* desc, int64_t seq, void* stream) {
+  if (!desc) return CB_ERR_ARG;
+  return (int)cb_launch(tp_pf_wait_kernel, dim3(1), dim3(32), 0, (cudaStream_t)stream, (const TpPfDev*)desc,
+                        (unsigned)seq);
+}
+CB_EXPORT int cb_tp_pf_desc_size() { return (int)sizeof(TpPfDev); }
+CB_EXPORT int cb_peer_write(void* dev, const void* host, int64_t bytes) {
+  return (int)cudaMemcpy(dev, host, (size_t)bytes, cudaMemcpyHostToDevice);
+}
 
 CB_EXPORT int cb_peer_alloc(int64_t bytes, void** out) {
   void* p = nullptr;

@@ -11,10 +11,11 @@
 //              in TMEM so the next tile's MMAs overlap this tile's epilogue.
 // bf16 (kind::f16) and int8 (kind::i8, int32 accumulate, per-row x per-column scales) share the
 // pipeline.  Both operands are K-major, i.e. the checkpoint's [N, K] weight layout is used as is.
-// No cluster multicast anywhere: every CTA fetches its own tiles.
+// Every CTA fetches its own tiles with plain (single-destination) TMA loads.
 // Replaces the reference's linear_prefill (torch matmul / cublasGemmEx + epilogue kernel,
 // backends/corex/__init__.py:1612-1701, kernels/w8a8.cu:196-366, w8a8_tcu.cu:327-776).
 #include "sm100.cuh"
+#include "tp.cuh"
 
 namespace {
 
@@ -31,6 +32,9 @@ struct GemmArgs {
   int M, N, K;
   int m_tiles, n_tiles, k_blocks;
   int* status;                     // device status word: set to a non-zero code if a wait ran out
+  // tensor-parallel prefill: instead of C, every output row goes (bf16) to the inbox of the rank
+  // that owns it, and the last CTA publishes the sequence number (see tp.cuh)
+  const TpPfDev* pf; unsigned pf_seq;
 };
 
 __device__ __forceinline__ uint64_t gtime_ns() {
@@ -149,8 +153,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         tmem_ld_wait();
         const int col0 = n0 + c0;
         if (row < a.M && col0 < a.N) {
-          bf16* cp = reinterpret_cast<bf16*>(a.C) + (int64_t)row * a.ldc + col0;
-          const bf16* rp = a.residual ? a.residual + (int64_t)row * a.ldr + col0 : nullptr;
+          bf16* cp;
+          if (a.pf) {
+            const int rpr = a.pf->rows_per_rank;
+            cp = a.pf->inbox[row / rpr] + ((int64_t)a.pf->rank * rpr + row % rpr) * a.pf->width + col0;
+          } else {
+            cp = reinterpret_cast<bf16*>(a.C) + (int64_t)row * a.ldc + col0;
+          }
+          const bf16* rp = (a.residual && !a.pf) ? a.residual + (int64_t)row * a.ldr + col0 : nullptr;
 #pragma unroll
           for (int v = 0; v < 4; ++v) {
             if (col0 + v * 8 >= a.N) break;  // N is a multiple of 8
@@ -173,6 +183,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&acc_empty[acc]);
+    }
+    if (a.pf) {
+      __threadfence_system();
+      asm volatile("bar.sync 1, 128;" ::: "memory");      // the four epilogue warps
+      if (warp == 2 && lane == 0) tp_pf_publish(a.pf, 1, a.pf_seq, gridDim.x);
     }
   }
   // ------------------------------- teardown ---------------------------------------------------
@@ -224,9 +239,9 @@ double tile_cost(int M, int N, int bn, int sms) {
 // bn_hint: 0 = choose, else 64/128/256.
 CB_EXPORT int cb_gemm_bf16(const void* A, int64_t lda, const void* W, int64_t ldw, void* C, int64_t ldc,
                            const void* residual, int64_t ldr, int64_t M, int64_t N, int64_t K,
-                           int64_t bn_hint, void* status, void* stream) {
+                           int64_t bn_hint, const void* pf, int64_t pf_seq, void* status, void* stream) {
   if (M < 1 || N < 1 || K < 1) return CB_ERR_SHAPE;
-  if (K % 8 || N % 8 || ldc % 8 || (residual && ldr % 8) || !status) return CB_ERR_SHAPE;
+  if (K % 8 || N % 8 || (!pf && ldc % 8) || (residual && ldr % 8) || !status) return CB_ERR_SHAPE;
   const int sms = sm_count();
   int bn = (int)bn_hint;
   if (!bn) {
@@ -243,6 +258,7 @@ CB_EXPORT int cb_gemm_bf16(const void* A, int64_t lda, const void* W, int64_t ld
   a.C = C; a.ldc = ldc; a.residual = (const bf16*)residual; a.ldr = ldr; a.row_scale = nullptr; a.col_scale = nullptr;
   a.M = (int)M; a.N = (int)N; a.K = (int)K; a.m_tiles = (int)((M + BM - 1) / BM); a.n_tiles = 0;
   a.k_blocks = (int)((K + 63) / 64); a.status = (int*)status;
+  a.pf = (const TpPfDev*)pf; a.pf_seq = (unsigned)pf_seq;
   cudaStream_t st = (cudaStream_t)stream;
   if (bn == 256) return launch_gemm<256, 4, false>(tmA, tmB, a, sms, st);
   if (bn == 128) return launch_gemm<128, 6, false>(tmA, tmB, a, sms, st);
@@ -253,9 +269,10 @@ CB_EXPORT int cb_gemm_bf16(const void* A, int64_t lda, const void* W, int64_t ld
 // C[M,N] (bf16) = (A_q[M,K] int8 x W_q[N,K]^T int8) * row_scale[m] * col_scale[n] (+ residual). K % 16 == 0.
 CB_EXPORT int cb_gemm_i8(const void* A, int64_t lda, const void* W, int64_t ldw, void* C, int64_t ldc,
                          const void* residual, int64_t ldr, const void* row_scale, const void* col_scale,
-                         int64_t M, int64_t N, int64_t K, int64_t bn_hint, void* status, void* stream) {
+                         int64_t M, int64_t N, int64_t K, int64_t bn_hint, const void* pf, int64_t pf_seq,
+                         void* status, void* stream) {
   if (M < 1 || N < 1 || K < 1) return CB_ERR_SHAPE;
-  if (K % 16 || N % 8 || ldc % 8 || lda % 16 || ldw % 16 || (residual && ldr % 8) || !status || !row_scale || !col_scale)
+  if (K % 16 || N % 8 || (!pf && ldc % 8) || lda % 16 || ldw % 16 || (residual && ldr % 8) || !status || !row_scale || !col_scale)
     return CB_ERR_SHAPE;
   const int sms = sm_count();
   int bn = (int)bn_hint;
@@ -270,6 +287,7 @@ CB_EXPORT int cb_gemm_i8(const void* A, int64_t lda, const void* W, int64_t ldw,
   a.row_scale = (const float*)row_scale; a.col_scale = (const float*)col_scale;
   a.M = (int)M; a.N = (int)N; a.K = (int)K; a.m_tiles = (int)((M + BM - 1) / BM); a.n_tiles = 0;
   a.k_blocks = (int)((K + 127) / 128); a.status = (int*)status;
+  a.pf = (const TpPfDev*)pf; a.pf_seq = (unsigned)pf_seq;
   cudaStream_t st = (cudaStream_t)stream;
   if (bn == 256) return launch_gemm<256, 4, true>(tmA, tmB, a, sms, st);
   if (bn == 128) return launch_gemm<128, 6, true>(tmA, tmB, a, sms, st);

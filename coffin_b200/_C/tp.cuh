@@ -19,7 +19,7 @@
 #include "common.cuh"
 
 constexpr int kTpMaxWorld = 8;
-constexpr unsigned long long kTpWaitNs = 2000000000ull;   // 2 s
+constexpr unsigned long long kTpWaitNs = 2000000000ull;   // default limit of a device-side wait: 2 s
 
 struct TpComm {
   int rank, world;
@@ -32,6 +32,7 @@ struct TpComm {
   unsigned* arrive;         // local: [sites] CTA arrival counters of the producer
   const unsigned* epoch;    // local: current step number
   int* status;              // local status word (set to 16 + rank on a wait that ran out)
+  unsigned long long wait_ns;   // limit of a device-side wait (0: kTpWaitNs)
 };
 
 __device__ __forceinline__ unsigned long long tp_now_ns() {
@@ -82,7 +83,7 @@ __device__ __forceinline__ void tp_pull_wait(const TpComm& c, int site) {
     for (int r = 0; r < c.world; ++r) {
       unsigned spins = 0;
       while ((int)(tp_ld_acquire(f + r) - e) < 0) {
-        if ((++spins & 1023u) == 0 && tp_now_ns() - t0 > kTpWaitNs) {
+        if ((++spins & 1023u) == 0 && tp_now_ns() - t0 > (c.wait_ns ? c.wait_ns : kTpWaitNs)) {
           atomicExch(c.status, 16 + r);
           break;
         }
@@ -97,4 +98,61 @@ __device__ __forceinline__ float tp_pull_value(const TpComm& c, int site, int64_
   float s = 0.f;
   for (int r = 0; r < c.world; ++r) s += __ldcg(base + (int64_t)r * c.slot_floats);
   return s;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Prefill: row-parallel GEMM -> all-reduce as reduce-scatter + all-gather over peer memory.
+//
+// The GEMM epilogue (gemm_tc.cu) stores every bf16 output row straight into the inbox of the rank
+// that owns the row (rows are cut into `world` equal slices), tile by tile while later tiles are
+// still being multiplied; a small kernel on each rank then adds the `world` partial slices it
+// received in rank order (+ an optional residual) and stores the reduced rows into every rank's
+// result buffer.  Two flag arrays carry a sequence number that the host advances once per use (all
+// ranks run the same sequence of calls), so nothing is reset between uses; waits are bounded and
+// set the status word.  This replaces the reference's per-projection gloo all-reduce in prefill
+// (models/qwen35/parallel.py:1015-1061) and is what NCCL all-reduce would otherwise do between
+// kernels.
+// The descriptor lives in device memory (kernels index its pointer tables with run-time ranks).
+struct TpPfDev {
+  int rank, world;
+  int rows_per_rank;          // rows of one slice = ceil(max chunk rows / world)
+  int width;                  // row width in elements (hidden size)
+  bf16* inbox[kTpMaxWorld];       // rank p's inbox:  [source rank][rows_per_rank][width]
+  bf16* out[kTpMaxWorld];         // rank p's result: [world * rows_per_rank][width]
+  unsigned* flags1[kTpMaxWorld];  // rank p's flags: [source rank] partial slices have landed
+  unsigned* flags2[kTpMaxWorld];  // rank p's flags: [source rank] reduced rows have landed
+  unsigned* arrive;               // local: [2] CTA arrival counters (scatter, gather)
+  int* status;
+  unsigned long long wait_ns;     // limit of a device-side wait (0: kTpWaitNs)
+};
+
+// Bounded wait for `flags[0..world)` (local) to reach `seq`. Thread 0 of the block waits.
+__device__ __forceinline__ void tp_pf_wait(const unsigned* flags, int world, unsigned seq, int* status,
+                                           unsigned long long wait_ns) {
+  if (threadIdx.x == 0) {
+    const unsigned long long t0 = tp_now_ns();
+    const unsigned long long limit = wait_ns ? wait_ns : kTpWaitNs;
+    for (int r = 0; r < world; ++r) {
+      unsigned spins = 0;
+      while ((int)(tp_ld_acquire(flags + r) - seq) < 0) {
+        if ((++spins & 1023u) == 0 && tp_now_ns() - t0 > limit) {
+          atomicExch(status, 32 + r);
+          break;
+        }
+      }
+    }
+  }
+  __syncthreads();
+}
+// After a CTA's peer stores: the last CTA of the grid publishes `seq` in slot [my rank] of every
+// rank's flag array `which` (1 or 2). `arrive_slot` is 0 for the scatter, 1 for the gather.
+__device__ __forceinline__ void tp_pf_publish(const TpPfDev* d, int which, unsigned seq, unsigned nblocks) {
+  // callers have done __threadfence_system() + a barrier over the storing threads
+  const unsigned prev = atomicAdd(d->arrive + (which - 1), 1u);
+  if (prev == nblocks - 1) {
+    d->arrive[which - 1] = 0;
+    __threadfence_system();
+    for (int p = 0; p < d->world; ++p)
+      tp_st_release((which == 1 ? d->flags1[p] : d->flags2[p]) + d->rank, seq);
+  }
 }

@@ -193,6 +193,9 @@ def preset(name: str) -> ModelConfig:
     """
     if name == "tiny":
         return ModelConfig()
+    if "qwen4" in name:
+        from .models.qwen4exp.config import preset_qwen4
+        return preset_qwen4(name)
     if name == "tiny-moe":
         return ModelConfig(name="tiny-moe", num_experts=8, num_experts_per_tok=2,
                            moe_intermediate_size=128, shared_expert_intermediate_size=128,
@@ -222,3 +225,13 @@ def preset(name: str) -> ModelConfig:
 
 
 PRESETS = ("tiny", "tiny-moe", "qwen35-4b", "qwen35-27b", "qwen35-35b-a3b")
+
+
+def load_config(model_dir: str | Path):
+    """Config object of a checkpoint directory, of whichever family its ``config.json`` names."""
+    raw = json.loads((Path(model_dir) / "config.json").read_text())
+    kind = str(raw.get("model_type", "")) + " " + " ".join(raw.get("architectures", []))
+    if "qwen4" in kind.lower():
+        from .models.qwen4exp.config import Qwen4Config
+        return Qwen4Config.from_hf(raw, name=Path(model_dir).name)
+    return ModelConfig.from_hf(raw, name=Path(model_dir).name)

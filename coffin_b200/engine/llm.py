@@ -15,7 +15,7 @@ from typing import Iterable, Sequence
 
 import torch
 
-from ..config import ModelConfig
+from ..config import ModelConfig, load_config
 from ..ops import kernels as K
 
 
@@ -66,7 +66,7 @@ class LLM:
                         graph: bool = True, device: str = "cuda", **kw) -> "LLM":
         from ..models import build_model
         from ..weights.loader import load_checkpoint
-        cfg = ModelConfig.from_dir(model_dir)
+        cfg = load_config(model_dir)
         sd = load_checkpoint(model_dir)
         model = build_model(cfg, sd, device=device, max_seq=max_seq, num_slots=max_num_seqs, **kw)
         return cls(model, graph=graph)

@@ -44,7 +44,8 @@ class SpeculativeDecoder:
     def step(self, table: list[int], tok: int, pos: int) -> list[int]:
         """Advance by at least one token. ``tok`` is the last sampled token (not yet run) at
         position ``pos``.  Returns the new tokens (the last one is the next ``tok``)."""
-        drafts = self.drafter.draft(self.k)
+        ctx = getattr(self.drafter, "draft_ctx", None)            # model-based drafters (MTP head) need the context
+        drafts = ctx(table, tok, pos, self.k) if ctx is not None else self.drafter.draft(self.k)
         room = getattr(self.model, "max_seq", 1 << 30) - pos - 1
         drafts = drafts[:max(0, min(len(drafts), room - 1))]
         self.n_steps += 1
@@ -54,6 +55,8 @@ class SpeculativeDecoder:
             nxt, _ = self.model.decode(1, graph=False)
             new = [int(nxt[0])]
             self.drafter.observe(new)
+            if hasattr(self.drafter, "after_decode"):
+                self.drafter.after_decode()
             return new
         W = self._width(len(drafts))
         drafts = drafts[:W - 1]
@@ -69,6 +72,8 @@ class SpeculativeDecoder:
         self.model.commit(self.slot, a + 1)          # the fed token plus the accepted drafts
         new = preds[:a + 1]
         self.drafter.observe(new)
+        if hasattr(self.drafter, "after_verify"):
+            self.drafter.after_verify(table, fed, a, pos)
         return new
 
     def generate(self, prompt: list[int], table: list[int], logits: torch.Tensor, n: int) -> list[int]:

@@ -44,6 +44,8 @@ def parser() -> argparse.ArgumentParser:
     ap.add_argument("--max-seconds", type=float, default=None)
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--no-vision", action="store_true")
+    ap.add_argument("--vision", choices=("tiny", "default"), default=None,
+                    help="attach a vision tower with random weights of this geometry (checkpoints with model.visual.* tensors get theirs)")
     ap.add_argument("-n", type=int, default=64, help="tokens for generate/chat/bench")
     ap.add_argument("--temperature", type=float, default=0.0)
     ap.add_argument("--system", default="")
@@ -67,7 +69,7 @@ def build_server(args):
     """Load (or draw) the weights once and return a ``Server`` whose ``reload`` rebuilds the model
     from the resident state dict."""
     import torch
-    from ...config import ModelConfig, preset
+    from ...config import ModelConfig, load_config, preset
     from ...serving.runtime import Server
     cfg_e = engine_config(args)
     if cfg_e.max_seq > 32768 and args.max_seq is None:
@@ -76,7 +78,7 @@ def build_server(args):
     mode = os.environ.get("COFFIN_PARALLEL", "tp")
     if args.model:
         from ...weights.loader import load_checkpoint
-        mcfg = ModelConfig.from_dir(args.model)
+        mcfg = load_config(args.model)
         sd = load_checkpoint(args.model)
     else:
         from ...weights.init import random_state_dict
@@ -87,12 +89,20 @@ def build_server(args):
     def builder():
         if args.device == "cpu":
             from ...oracle.engine_model import OracleEngineModel
-            return OracleEngineModel(mcfg, sd, max_seq=min(cfg_e.max_seq, 4096), num_slots=cfg_e.max_num_seqs,
+            twin = OracleEngineModel(mcfg, sd, max_seq=min(cfg_e.max_seq, 4096), num_slots=cfg_e.max_num_seqs,
                                      max_chunk=cfg_e.chunk)
+            if not args.no_vision and (args.vision or any(k.startswith("model.visual.") for k in sd)):
+                from ...models import attach_vision
+                attach_vision(twin, mcfg, {k: v for k, v in sd.items() if k.startswith("model.visual.")},
+                              args.vision, args.model or None)
+            return twin
         from ...models import build_model
-        kw = dict(device=f"cuda:{int(os.environ.get('LOCAL_RANK', '0'))}", max_seq=cfg_e.max_seq,
+        kw = dict(vision=False if args.no_vision else args.vision, model_dir=args.model or None,
+                  device=f"cuda:{int(os.environ.get('LOCAL_RANK', '0'))}", max_seq=cfg_e.max_seq,
                   num_slots=cfg_e.max_num_seqs, max_chunk=cfg_e.chunk,
                   num_blocks=cfg_e.num_blocks if cfg_e.num_blocks > 0 else None)
+        if getattr(cfg_e, "quant", None) not in (None, "", "none"):
+            kw["quant"] = cfg_e.quant
         if world > 1:
             if mode not in ("tp", "pp", "ep"):
                 raise SystemExit(f"COFFIN_PARALLEL={mode!r}: expected tp, pp or ep")

@@ -37,14 +37,16 @@ def _ensure_builtin() -> None:
         if ep_world > 1:
             # expert parallel: attention / delta-net / dense weights replicated, routed experts split
             from ..parallel.tp import TpComm, make_exchange
-            comm = TpComm(ep_rank, ep_world, cfg.hidden_size, 8, 2 * cfg.num_hidden_layers, exchange=make_exchange())
+            comm = TpComm(ep_rank, ep_world, cfg.hidden_size, 8, 2 * cfg.num_hidden_layers, exchange=make_exchange(),
+                          prefill_rows=kw.get("max_chunk", 2048))
             return Qwen35Model(cfg, sd, tp=comm, ep_rank=ep_rank, ep_world=ep_world, **kw)
         if tp_world > 1:
             from ..parallel.tp import TpComm, local_config, make_exchange, shard_state_dict
             lcfg = local_config(cfg, tp_world)
             lsd = shard_state_dict(cfg, sd, tp_rank, tp_world)
             n_sites = 2 * cfg.num_hidden_layers
-            tp = TpComm(tp_rank, tp_world, cfg.hidden_size, 8, n_sites, exchange=make_exchange())
+            tp = TpComm(tp_rank, tp_world, cfg.hidden_size, 8, n_sites, exchange=make_exchange(),
+                        prefill_rows=kw.get("max_chunk", 2048))
             kw.pop("free_source", None)
             return Qwen35Model(lcfg, lsd, tp=tp, full_cfg=cfg, **kw)
         return Qwen35Model(cfg, sd, **kw)
@@ -72,6 +74,41 @@ def detect_architecture(cfg: ModelConfig) -> str:
     raise RuntimeError(f"no registered model family for architecture {cfg.architecture!r}")
 
 
+def attach_vision(model, cfg, sd: dict, vision=None, model_dir=None) -> None:
+    """Give ``model`` a ``vision`` tower when the checkpoint carries ``model.visual.*`` tensors, or
+    when ``vision`` is a ``VisionConfig`` / the string ``"tiny"`` / ``"default"`` (random weights of
+    that geometry - for benchmarks and tests; reference: the tower is optional and loaded on demand,
+    ``models/qwen35/model.py:213-266``)."""
+    from .qwen35.vision import V, VisionConfig, VisionTower, random_vision_state_dict, tiny_vision
+    has = any(k.startswith(V) for k in sd)
+    if not has and not vision:
+        return
+    if isinstance(vision, VisionConfig):
+        vcfg = vision
+    elif vision == "tiny":
+        vcfg = tiny_vision(cfg.hidden_size)
+    elif model_dir is not None:
+        import json
+        from pathlib import Path
+        vcfg = VisionConfig.from_hf(json.loads((Path(model_dir) / "config.json").read_text()), cfg.hidden_size)
+    else:
+        vcfg = VisionConfig(out_hidden_size=cfg.hidden_size)
+    vsd = sd if has else random_vision_state_dict(vcfg)
+    if getattr(model, "device", None) is not None and str(model.device).startswith("cuda"):
+        model.vision = VisionTower(vcfg, vsd, device=model.device)
+    else:
+        from .qwen35.vision import OracleVision
+        model.vision = OracleVision(vcfg, {k: v.float() for k, v in vsd.items() if k.startswith(V)})
+
+
 def build_model(cfg: ModelConfig, sd: dict, **kw):
+    """``vision`` (``None`` / ``"tiny"`` / ``"default"`` / a ``VisionConfig``) and ``model_dir`` are
+    consumed here: the tower is attached after the text model is built."""
     _ensure_builtin()
-    return _REGISTRY[detect_architecture(cfg)](cfg, sd, **kw)
+    vision, model_dir = kw.pop("vision", None), kw.pop("model_dir", None)
+    has_visual = any(k.startswith("model.visual.") for k in sd)
+    vsd = {k: v for k, v in sd.items() if k.startswith("model.visual.")} if has_visual else {}
+    model = _REGISTRY[detect_architecture(cfg)](cfg, sd, **kw)
+    if (vision or has_visual) and vision is not False:
+        attach_vision(model, cfg, vsd, vision, model_dir)
+    return model

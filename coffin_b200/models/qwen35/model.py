@@ -64,6 +64,44 @@ class QW:
         return cls(q.wq, q.scale)
 
 
+class QW4:
+    """Device-resident W4A8 projection: codes ``[N, K/2]`` uint8 + group scales ``[N, K/128]`` fp32
+    (``weights.quant.W4A8Weight.to_nk``).  A leading expert axis is allowed."""
+
+    def __init__(self, wq: torch.Tensor, scale: torch.Tensor) -> None:
+        self.wq, self.scale = wq.contiguous(), scale.float().contiguous()
+
+    @property
+    def shape(self):
+        return (*self.wq.shape[:-1], self.wq.shape[-1] * 2)
+
+    def __getitem__(self, sl):
+        return QW4(self.wq[sl], self.scale[sl])
+
+    def numel(self) -> int:
+        return self.wq.numel()
+
+    def element_size(self) -> int:
+        return 1
+
+    def data_ptr(self) -> int:
+        return self.wq.data_ptr()
+
+    @classmethod
+    def quantize(cls, w: torch.Tensor) -> "QW4":
+        from ...weights.quant import W4A8Weight
+        return cls(*W4A8Weight.quantize(w).to_nk())
+
+    @classmethod
+    def zeros(cls, rows: int, K: int, device) -> "QW4":
+        return cls(torch.full((rows, K // 2), 0x88, dtype=torch.uint8, device=device),
+                   torch.full((rows, K // 128), 1e-8, dtype=torch.float32, device=device))
+
+    def dequant(self) -> torch.Tensor:
+        """bf16 ``[N, K]`` (2-D only)."""
+        return K.w4_dequant(self.wq, self.scale)
+
+
 def _pad8(n: int) -> int:
     return (n + 7) // 8 * 8
 
@@ -127,12 +165,23 @@ class Qwen35Model:
             t = sd.pop(key) if free_source else sd[key]
             if isinstance(t, QWeight):                      # pre-quantised int8 checkpoint
                 return QW(t.wq.to(dev), t.scale.to(dev))
-            if isinstance(t, W4A8Weight):                   # int4 group-128 storage: computed as bf16
-                t = t.dequant(bf)
+            if isinstance(t, W4A8Weight):                   # int4 group-128 storage
+                if t.k % t.group_size == 0 and t.group_size == 128:
+                    return QW4(*t.to(dev).to_nk())
+                t = t.dequant(bf)                           # odd K: computed as bf16
             return t.to(device=dev, dtype=bf)
 
         def cat(parts):
             """Row-concatenate projections; int8 parts keep their per-row scales."""
+            if any(isinstance(p_, QW4) for p_ in parts) or quant == "w4a8":
+                def w4(p_):
+                    if isinstance(p_, QW4):
+                        return p_
+                    if not bool(p_.any()):                  # zero padding rows
+                        return QW4.zeros(p_.shape[0], p_.shape[1], dev)
+                    return QW4.quantize(p_)
+                parts = [w4(p_) for p_ in parts]
+                return QW4(torch.cat([p_.wq for p_ in parts]), torch.cat([p_.scale for p_ in parts]))
             if any(isinstance(p_, QW) for p_ in parts):
                 parts = [p_ if isinstance(p_, QW) else QW.quantize(p_) for p_ in parts]
                 return QW(torch.cat([p_.wq for p_ in parts]), torch.cat([p_.scale for p_ in parts]))
@@ -140,8 +189,10 @@ class Qwen35Model:
             return QW.quantize(t) if quant == "int8" else t
 
         def one(t):
-            if isinstance(t, QW):
+            if isinstance(t, (QW, QW4)):
                 return t
+            if quant == "w4a8" and t.shape[1] % 128 == 0:
+                return QW4.quantize(t)
             return QW.quantize(t) if quant == "int8" else t.contiguous()
 
         def gain(key: str, centred: bool = True) -> torch.Tensor:
@@ -151,6 +202,8 @@ class Qwen35Model:
         self.embed = w(LM + "embed_tokens.weight") if LM + "embed_tokens.weight" in sd else None
         if isinstance(self.embed, QW):
             self.embed = (self.embed.wq.float() * self.embed.scale[:, None]).to(bf)
+        if isinstance(self.embed, QW4):
+            self.embed = self.embed.dequant()
         if self.embed is not None:
             self.embed = self.embed.contiguous()
         self.lm_head = None
@@ -193,7 +246,7 @@ class Qwen35Model:
             m = p + "mlp."
             if c.is_moe:
                 from .moe import MoEWeights
-                lw.moe = MoEWeights.from_state_dict(c, sd, m, dev, ep_rank, ep_world)
+                lw.moe = MoEWeights.from_state_dict(c, sd, m, dev, ep_rank, ep_world, quant=quant)
             else:
                 lw.w_gu = cat([w(m + "gate_proj.weight"), w(m + "up_proj.weight")])
                 lw.w_down = one(w(m + "down_proj.weight"))
@@ -229,17 +282,34 @@ class Qwen35Model:
         """Decode projection on whichever storage the weight has (bf16 or int8 W8A8)."""
         if isinstance(W, QW):
             return K.gemv_i8(W.wq, W.scale, x, out, **kw)
+        if isinstance(W, QW4):
+            if kw.get("tp") is not None and (kw.get("pull_site", -1) >= 0 or kw.get("push_site", -1) >= 0):
+                raise NotImplementedError("W4A8 projections do not take part in the tensor-parallel push/pull")
+            return K.gemv_w4(W.wq, W.scale, x, out, swiglu=kw.get("swiglu", False), norm=kw.get("norm"))
         return K.gemv(W, x, out, **kw)
 
-    def _gemm(self, A, W, out=None, residual=None, swiglu_in: bool = False):
+    def _gemm(self, A, W, out=None, residual=None, swiglu_in: bool = False, push=None):
         """Prefill projection.  ``swiglu_in``: ``A`` is a ``[T, 2I]`` gate|up tensor whose SwiGLU
-        product is the real input (fused into the activation quantisation on the int8 path)."""
+        product is the real input (fused into the activation quantisation on the int8 path).
+        ``push``: the tensor-parallel communicator; the epilogue then sends the partial rows to their
+        owners instead of writing ``out`` (``_tp_finish`` completes the all-reduce)."""
         if isinstance(W, QW):
             q, sc = K.quant_rows(A, swiglu=swiglu_in)
-            return K.gemm_i8(q, sc, W.wq, W.scale, out=out, residual=residual)
+            return K.gemm_i8(q, sc, W.wq, W.scale, out=out, residual=residual, push=push)
+        if isinstance(W, QW4):
+            W = W.dequant()                 # expanded to bf16 for the chunk; the tcgen05 GEMM does the rest
         if swiglu_in:
             A = K.swiglu(A)
-        return K.gemm(A, W, out=out, residual=residual)
+        return K.gemm(A, W, out=out, residual=residual, push=push)
+
+    def _row_parallel(self, A, W, scratch: torch.Tensor, swiglu_in: bool = False) -> torch.Tensor:
+        """Row-parallel prefill projection + all-reduce.  With a peer-memory prefill region the GEMM
+        epilogue scatters its rows to the owning ranks and a reduce/gather kernel finishes; otherwise
+        the partial result is all-reduced by NCCL."""
+        if self.tp is not None and self.tp.pf_rows:
+            self._gemm(A, W, swiglu_in=swiglu_in, push=self.tp)
+            return self.tp.finish_reduce()
+        return self._tp_reduce(self._gemm(A, W, out=scratch, swiglu_in=swiglu_in))
 
     # ------------------------------------------------------------------ sizes
     @property
@@ -298,7 +368,7 @@ class Qwen35Model:
                 "slots": torch.empty(rows, dtype=torch.int32, device=dev),
                 "ridx": torch.empty(rows, dtype=torch.int32, device=dev),
             }
-            if self.tp_world > 1:
+            if self.tp is not None:
                 ws["part"] = torch.empty(rows, H, dtype=bf, device=dev)
             if not c.is_moe:
                 ws["gu"] = torch.empty(rows, 2 * c.intermediate_size, dtype=bf, device=dev)
@@ -361,8 +431,8 @@ class Qwen35Model:
                             rot=c.rotary_dim, eps=self.eps)
                 K.attn_prefill(q, proj, self.kpool[j], self.vpool[j], block_table, act, q_pos0=pos0,
                                nh=c.num_attention_heads, nkv=c.num_key_value_heads, hd=c.head_dim)
-            if self.tp_world > 1:
-                part = self._tp_reduce(self._gemm(act, lw.w_out, out=ws["part"][:T]))
+            if self.tp_world > 1 or (self.tp_force and not c.is_moe):
+                part = self._row_parallel(act, lw.w_out, ws["part"][:T])
                 K.rmsnorm(res, lw.post_gain, self.eps, out=normed, add=part, res_out=res)
             else:
                 self._gemm(act, lw.w_out, out=res, residual=res)
@@ -372,9 +442,8 @@ class Qwen35Model:
             else:
                 gu = ws["gu"][:T]
                 self._gemm(normed, lw.w_gu, out=gu)
-                if self.tp_world > 1:
-                    part = self._tp_reduce(self._gemm(gu, lw.w_down, out=ws["part"][:T], swiglu_in=True))
-                    res.add_(part)
+                if self.tp_world > 1 or self.tp_force:
+                    res.add_(self._row_parallel(gu, lw.w_down, ws["part"][:T], swiglu_in=True))
                 else:
                     self._gemm(gu, lw.w_down, out=res, residual=res, swiglu_in=True)
         out_logits = None
@@ -392,8 +461,15 @@ class Qwen35Model:
 
     # ------------------------------------------------------------------ tensor-parallel helpers
     def _tp_reduce(self, t: torch.Tensor) -> torch.Tensor:
-        """Prefill all-reduce of a row-parallel projection output (NCCL; the decode path reduces
-        inside the GEMV kernels instead)."""
+        """All-reduce of a ``[T, hidden]`` prefill tensor whose producer is not a GEMM (the MoE
+        combine under expert parallelism): scatter + reduce/gather over peer memory when the
+        communicator has a prefill region, NCCL otherwise.  Returns the reduced rows (``t`` itself
+        with NCCL, a view of the communicator's result buffer otherwise)."""
+        if self.tp is not None and self.tp.pf_rows and t.shape[0] <= self.tp.pf_rows:
+            self.tp.scatter(t)
+            return self.tp.finish_reduce()
+        if self.tp_world == 1 and self.ep_world == 1:
+            return t
         import torch.distributed as dist
         dist.all_reduce(t)
         K._count()
@@ -688,7 +764,13 @@ class Qwen35Model:
             carry = b["h2"]
         self._gemv(self.lm_head, None, b["logits"], norm=(cur, carry, self.final_gain, nxt, self.eps))
         self._verify_width = C
+        b["final_res"] = nxt
         return b["logits"]
+
+    def verify_hidden(self) -> torch.Tensor:
+        """Last-layer residual stream ``[C, H]`` (before the final norm) of the rows of the last
+        ``verify`` call - what the MTP head pairs with the following token."""
+        return self._verify_buffers(self._verify_width)["final_res"]
 
     def commit(self, slot: int, n_accept: int) -> None:
         """Apply the first ``n_accept`` recorded delta-net updates of the last ``verify`` call."""

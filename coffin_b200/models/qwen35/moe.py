@@ -36,7 +36,8 @@ class MoEWeights:
     bufs: dict = dataclasses.field(default_factory=dict)
 
     @classmethod
-    def from_state_dict(cls, cfg: ModelConfig, sd: dict, p: str, dev, ep_rank: int = 0, ep_world: int = 1):
+    def from_state_dict(cls, cfg: ModelConfig, sd: dict, p: str, dev, ep_rank: int = 0, ep_world: int = 1,
+                        quant: str = "none"):
         """Expert parallel (``ep_world > 1``): the routed experts are split by contiguous range
         (reference ``expert_range``, ``models/qwen35/parallel.py:238-259``) and the shared expert by
         intermediate columns, so every rank's partial output sums to the full layer output."""
@@ -54,7 +55,20 @@ class MoEWeights:
             raise ValueError(f"num_experts={E} is not divisible by expert-parallel world {ep_world}")
         per = E // ep_world
         e_lo, e_hi = ep_rank * per, (ep_rank + 1) * per
-        gu, dn = gu[e_lo:e_hi], dn[e_lo:e_hi]
+        from ...weights.quant import W4A8Weight
+        from .model import QW4
+
+        def experts(t):
+            """bf16 stack, or W4A8 codes + scales when the checkpoint (or ``quant``) says so."""
+            if isinstance(t, W4A8Weight):
+                part = W4A8Weight(t.packed[e_lo:e_hi], t.scale[e_lo:e_hi], t.k, t.group_size)
+                return QW4(*part.to(dev).to_nk())
+            t = t[e_lo:e_hi].to(dev, bf)
+            if quant == "w4a8" and t.shape[-1] % 128 == 0:
+                return QW4.quantize(t)
+            return t.contiguous()
+
+        gu, dn = experts(gu), experts(dn)
         sh_gu = sh_down = None
         if has_shared:
             sg, su = sd[p + "shared_expert.gate_proj.weight"], sd[p + "shared_expert.up_proj.weight"]
@@ -65,11 +79,18 @@ class MoEWeights:
             c0, c1 = ep_rank * (S // ep_world), (ep_rank + 1) * (S // ep_world)
             sh_gu = torch.cat([sg[c0:c1].to(dev, bf), su[c0:c1].to(dev, bf)]).contiguous()
             sh_down = sdn[:, c0:c1].to(dev, bf).contiguous()
-        return cls(cfg, torch.cat(rows).contiguous(), gu.to(dev, bf).contiguous(), dn.to(dev, bf).contiguous(),
-                   sh_gu, sh_down, e_lo, e_hi, ep_world)
+        return cls(cfg, torch.cat(rows).contiguous(), gu, dn, sh_gu, sh_down, e_lo, e_hi, ep_world)
 
     def tensors(self) -> list[torch.Tensor]:
         return [t for t in (self.router, self.gate_up, self.down, self.sh_gu, self.sh_down) if t is not None]
+
+    @property
+    def w4(self) -> bool:
+        return not isinstance(self.gate_up, torch.Tensor)
+
+    def _expert(self, stack, e: int) -> torch.Tensor:
+        """bf16 ``[rows, K]`` weights of local expert ``e`` (expanded from W4 storage for a prefill GEMM)."""
+        return stack[e] if isinstance(stack, torch.Tensor) else K.w4_dequant(stack.wq[e], stack.scale[e])
 
     # ------------------------------------------------------------------ buffers
     def _b(self, T: int, dev) -> dict:
@@ -114,10 +135,14 @@ class MoEWeights:
         K.call("moe_router", b["logits"], b["logits"].stride(0), T, E, k, int(c.norm_topk_prob), b["idx"], b["w"],
                self.e_lo, self.e_hi)
         K._count()
-        K.call("moe_gemv", self.gate_up, normed, b["inter"], T * k, I, H, I, 1, b["idx"], b["xrow"],
-               self.gate_up.stride(0))
-        K.call("moe_gemv", self.down, b["inter"], b["y"], T * k, H, I, H, 0, b["idx"], b["irow"], self.down.stride(0))
-        K._count(2)
+        if self.w4:
+            K.moe_gemv_w4(self.gate_up.wq, self.gate_up.scale, normed, b["inter"], b["idx"], b["xrow"], swiglu=True)
+            K.moe_gemv_w4(self.down.wq, self.down.scale, b["inter"], b["y"], b["idx"], b["irow"])
+        else:
+            K.call("moe_gemv", self.gate_up, normed, b["inter"], T * k, I, H, I, 1, b["idx"], b["xrow"],
+                   self.gate_up.stride(0))
+            K.call("moe_gemv", self.down, b["inter"], b["y"], T * k, H, I, H, 0, b["idx"], b["irow"], self.down.stride(0))
+            K._count(2)
         shared = gate = None
         if self.sh_gu is not None:
             for s in range(0, T, 8):
@@ -148,7 +173,7 @@ class MoEWeights:
             out = torch.empty(T, H, dtype=torch.bfloat16, device=normed.device)
             self._experts(b, T, out)
             if self.ep_world > 1:
-                model._tp_reduce(out)
+                out = model._tp_reduce(out)
             return out
         logits = K.gemm(normed, self.router).float()                       # [T, pad8(E+1)]
         idx = torch.empty(T, k, dtype=torch.int32, device=normed.device)
@@ -168,14 +193,18 @@ class MoEWeights:
             if n == 0:
                 continue
             seg = xs[s:s + n]
-            if n <= 8:
+            if n <= 8 and self.w4:
+                inter = torch.empty(n, I, dtype=torch.bfloat16, device=normed.device)
+                K.gemv_w4(self.gate_up.wq[e], self.gate_up.scale[e], seg.contiguous(), inter, swiglu=True)
+                K.gemv_w4(self.down.wq[e], self.down.scale[e], inter, ys[s:s + n])
+            elif n <= 8:
                 inter = torch.empty(n, I, dtype=torch.bfloat16, device=normed.device)
                 K.gemv(self.gate_up[e], seg.contiguous(), inter, swiglu=True)
                 K.gemv(self.down[e], inter, ys[s:s + n])
             else:
-                gu = K.gemm(seg, self.gate_up[e])
+                gu = K.gemm(seg, self._expert(self.gate_up, e))
                 inter = K.swiglu(gu)
-                K.gemm(inter, self.down[e], out=ys[s:s + n])
+                K.gemm(inter, self._expert(self.down, e), out=ys[s:s + n])
             s += n
         y = torch.empty_like(ys)
         y[order] = ys                                                     # back to (token, slot) order
@@ -188,5 +217,5 @@ class MoEWeights:
         K.call("moe_combine", y, w, shared, gate, gate.stride(0) if gate is not None else 0, out, T, H, k, None, -1)
         K._count()
         if self.ep_world > 1:
-            model._tp_reduce(out)
+            out = model._tp_reduce(out)
         return out

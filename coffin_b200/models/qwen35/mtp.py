@@ -95,3 +95,55 @@ class MTPHead:
             out.append(int(nxt[0]))
         self.n_drafted += k
         return out
+
+
+class MTPDrafter:
+    """Adapter that lets ``engine.speculative.SpeculativeDecoder`` draft with the MTP head.
+
+    The head keeps its own KV: head position ``p`` pairs token ``p + 1`` with the main model's hidden
+    of position ``p``.  ``prime`` fills it from a prefilled prompt, ``draft_ctx`` chains ``k`` greedy
+    drafts from the last sampled token, ``after_verify`` rewrites the head rows of the accepted
+    tokens with the main model's hiddens (while drafting they were written with the head's own) and
+    ``after_decode`` picks up the hidden of a plain step.  Reference: ``models/qwen35/model.py:
+    1832-1950`` (``spec_step``), ``models/qwen35/mtp.py`` (head and its cache)."""
+
+    def __init__(self, head: MTPHead) -> None:
+        self.head = head
+        self.h: torch.Tensor | None = None
+
+    # the suffix-drafter protocol (history is not needed here)
+    def reset(self) -> None:
+        self.h = None
+
+    def observe(self, tokens) -> None:
+        pass
+
+    def draft(self, k: int) -> list[int]:
+        return []
+
+    def prime(self, prompt: torch.Tensor, pos0: int, table: torch.Tensor) -> None:
+        """After the main model prefilled ``prompt`` (the chunk starting at ``pos0`` whose residual
+        stream is still in ``main.last_prenorm``)."""
+        main = self.head.main
+        T = prompt.numel()
+        pre = main.last_prenorm[:T]
+        if T > 1:
+            self.head.prefill(prompt[1:], pre[:-1], pos0, table)
+        self.h = pre[T - 1].clone()
+
+    def draft_ctx(self, table: list[int], tok: int, pos: int, k: int) -> list[int]:
+        if self.h is None or pos < 1:
+            return []
+        return self.head.draft(tok, self.h, pos - 1, table, k)
+
+    def after_verify(self, table: list[int], fed: list[int], accepted: int, pos: int) -> None:
+        main = self.head.main
+        hid = main.verify_hidden()
+        if accepted > 0:
+            bt = torch.tensor(table, dtype=torch.int32, device=main.device)
+            toks = torch.tensor(fed[1:accepted + 1], dtype=torch.int64, device=main.device)
+            self.head.prefill(toks, hid[:accepted], pos, bt)
+        self.h = hid[accepted].clone()
+
+    def after_decode(self) -> None:
+        self.h = self.head.main.final_hidden(1, normed=False)[0].clone()

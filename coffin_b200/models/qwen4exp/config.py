@@ -227,3 +227,14 @@ def tiny_qwen4(**over) -> Qwen4Config:
               name="tiny-qwen4")
     kw.update(over)
     return Qwen4Config(**kw)
+
+
+def preset_qwen4(name: str) -> Qwen4Config:
+    """``tiny-qwen4``: the test geometry.  ``qwen4exp-a``: the family's default shape (48 layers,
+    hidden 2560, 512 experts top-10, four residual lanes) without the n-gram table."""
+    if name == "tiny-qwen4":
+        return tiny_qwen4()
+    if name == "qwen4exp-a":
+        return Qwen4Config(name=name, vocab_size=151936, head_dim=256, partial_rotary_factor=0.25,
+                           mrope_section=(11, 11, 10), rope_theta=1e7)
+    raise KeyError(f"unknown Qwen4-exp preset {name!r}")

@@ -197,6 +197,48 @@ def gemv_i8(Wq: torch.Tensor, wscale: torch.Tensor, x: torch.Tensor | None, out:
     return out
 
 
+def gemv_w4(Wq: torch.Tensor, wscale: torch.Tensor, x: torch.Tensor | None, out: torch.Tensor, *,
+            swiglu: bool = False, norm: tuple | None = None) -> torch.Tensor:
+    """W4A8 decode projection: codes ``[N, K/2]`` uint8 (``[2I, K/2]`` with ``swiglu``), scales
+    ``[N, K/128]`` fp32 (``weights.quant.W4A8Weight.to_nk``); activations quantised per token in the kernel."""
+    M = out.shape[0]
+    K = Wq.shape[1] * 2
+    N = Wq.shape[0] // 2 if swiglu else Wq.shape[0]
+    mode = (1 if swiglu else 0) | (2 if out.dtype == torch.float32 else 0)
+    if norm is None:
+        assert x is not None and x.is_contiguous() and x.shape == (M, K)
+        res_in = add = gain = res_out = None
+        eps = 0.0
+    else:
+        res_in, add, gain, res_out, eps = norm
+        x = None
+    call("gemv_w4", Wq, wscale, x, out, M, N, K, out.stride(0), mode, N, res_in, add, gain, res_out, float(eps))
+    _count()
+    return out
+
+
+def moe_gemv_w4(Wq, wscale, x, out, slot_expert, slot_xrow, *, swiglu: bool = False) -> torch.Tensor:
+    """Routed experts on W4A8 storage: ``Wq [E, rows, K/2]``, ``wscale [E, rows, K/128]``; slot ``s``
+    multiplies activation row ``slot_xrow[s]`` by expert ``slot_expert[s]`` (``< 0``: skipped)."""
+    n_slots = out.shape[0]
+    K = Wq.shape[2] * 2
+    N = Wq.shape[1] // 2 if swiglu else Wq.shape[1]
+    mode = (1 if swiglu else 0) | (2 if out.dtype == torch.float32 else 0)
+    call("moe_gemv_w4", Wq, wscale, x, out, n_slots, N, K, out.stride(0), mode, slot_expert, slot_xrow)
+    _count()
+    return out
+
+
+def w4_dequant(Wq: torch.Tensor, wscale: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """bf16 ``[N, K]`` from W4 codes + group scales (prefill: expanded once per projection call)."""
+    N, K = Wq.shape[0], Wq.shape[1] * 2
+    if out is None:
+        out = torch.empty(N, K, dtype=torch.bfloat16, device=Wq.device)
+    call("w4_dequant", Wq, wscale, out, N, K)
+    _count()
+    return out
+
+
 def quant_rows(x: torch.Tensor, swiglu: bool = False) -> tuple[torch.Tensor, torch.Tensor]:
     """Per-row dynamic int8 quantisation of bf16 rows (optionally of ``silu(gate) * up`` of a
     ``[M, 2I]`` input). Returns ``(q int8 [M, K], scale fp32 [M])``."""
@@ -210,28 +252,44 @@ def quant_rows(x: torch.Tensor, swiglu: bool = False) -> tuple[torch.Tensor, tor
 
 
 def gemm(A: torch.Tensor, W: torch.Tensor, out: torch.Tensor | None = None,
-         residual: torch.Tensor | None = None, bn: int = 0) -> torch.Tensor:
-    """Prefill projection on tcgen05: ``out[M, N] = A[M, K] @ W[N, K]^T (+ residual)``, bf16."""
+         residual: torch.Tensor | None = None, bn: int = 0, push=None) -> torch.Tensor | None:
+    """Prefill projection on tcgen05: ``out[M, N] = A[M, K] @ W[N, K]^T (+ residual)``, bf16.
+
+    ``push`` (a ``parallel.tp.TpComm`` with a prefill region): nothing is written locally; every
+    output row goes to the inbox of the tensor-parallel rank that owns it (first half of the fused
+    all-reduce; ``TpComm.finish_reduce`` is the second)."""
     M, K = A.shape
     N = W.shape[0]
+    assert A.stride(1) == 1 and W.stride(1) == 1
+    if push is not None:
+        call("gemm_bf16", A, A.stride(0), W, W.stride(0), None, 0, None, 0, M, N, K, bn, push.pf_desc_ptr(),
+             push.next_seq(M, N), status_word(A.device))
+        _count()
+        return None
     if out is None:
         out = torch.empty(M, N, dtype=torch.bfloat16, device=A.device)
-    assert A.stride(1) == 1 and W.stride(1) == 1 and out.stride(1) == 1
+    assert out.stride(1) == 1
     call("gemm_bf16", A, A.stride(0), W, W.stride(0), out, out.stride(0), residual,
-         residual.stride(0) if residual is not None else 0, M, N, K, bn, status_word(A.device))
+         residual.stride(0) if residual is not None else 0, M, N, K, bn, None, 0, status_word(A.device))
     _count()
     return out
 
 
 def gemm_i8(Aq: torch.Tensor, a_scale: torch.Tensor, Wq: torch.Tensor, w_scale: torch.Tensor,
-            out: torch.Tensor | None = None, residual: torch.Tensor | None = None, bn: int = 0) -> torch.Tensor:
+            out: torch.Tensor | None = None, residual: torch.Tensor | None = None, bn: int = 0,
+            push=None) -> torch.Tensor | None:
     """W8A8 projection: int8 x int8 -> int32 on tcgen05 (kind::i8), ``* a_scale[m] * w_scale[n]``."""
     M, K = Aq.shape
     N = Wq.shape[0]
+    if push is not None:
+        call("gemm_i8", Aq, Aq.stride(0), Wq, Wq.stride(0), None, 0, None, 0, a_scale, w_scale, M, N, K, bn,
+             push.pf_desc_ptr(), push.next_seq(M, N), status_word(Aq.device))
+        _count()
+        return None
     if out is None:
         out = torch.empty(M, N, dtype=torch.bfloat16, device=Aq.device)
     call("gemm_i8", Aq, Aq.stride(0), Wq, Wq.stride(0), out, out.stride(0), residual,
-         residual.stride(0) if residual is not None else 0, a_scale, w_scale, M, N, K, bn,
+         residual.stride(0) if residual is not None else 0, a_scale, w_scale, M, N, K, bn, None, 0,
          status_word(Aq.device))
     _count()
     return out

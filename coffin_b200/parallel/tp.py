@@ -14,6 +14,7 @@ from __future__ import annotations
 
 import ctypes
 import dataclasses
+import os
 
 import torch
 
@@ -98,11 +99,28 @@ def shard_state_dict(cfg: ModelConfig, sd: dict[str, torch.Tensor], rank: int, w
 
 # ---------------------------------------------------------------------------------------------
 # communicator
+class _TpPfStruct(ctypes.Structure):
+    """Mirror of ``TpPfDev`` (``_C/tp.cuh``): descriptor of the prefill reduce-scatter / all-gather."""
+    _fields_ = [("rank", ctypes.c_int), ("world", ctypes.c_int), ("rows_per_rank", ctypes.c_int),
+                ("width", ctypes.c_int),
+                ("inbox", ctypes.c_void_p * MAX_WORLD), ("out", ctypes.c_void_p * MAX_WORLD),
+                ("flags1", ctypes.c_void_p * MAX_WORLD), ("flags2", ctypes.c_void_p * MAX_WORLD),
+                ("arrive", ctypes.c_void_p), ("status", ctypes.c_void_p), ("wait_ns", ctypes.c_uint64)]
+
+
+class _DevView:
+    """Lets torch wrap a raw device pointer (``__cuda_array_interface__``) without copying."""
+
+    def __init__(self, ptr: int, nelem: int) -> None:
+        self.__cuda_array_interface__ = {"shape": (nelem,), "typestr": "<i2", "data": (ptr, False), "version": 2}
+
+
 class _TpCommStruct(ctypes.Structure):
     _fields_ = [("rank", ctypes.c_int), ("world", ctypes.c_int), ("slot_floats", ctypes.c_int64),
                 ("inbox", ctypes.c_void_p * MAX_WORLD), ("flags", ctypes.c_void_p * MAX_WORLD),
                 ("my_inbox", ctypes.c_void_p), ("my_flags", ctypes.c_void_p),
-                ("arrive", ctypes.c_void_p), ("epoch", ctypes.c_void_p), ("status", ctypes.c_void_p)]
+                ("arrive", ctypes.c_void_p), ("epoch", ctypes.c_void_p), ("status", ctypes.c_void_p),
+                ("wait_ns", ctypes.c_uint64)]
 
 
 class TpComm:
@@ -115,7 +133,10 @@ class TpComm:
     tested on a single GPU.
     """
 
-    def __init__(self, rank: int, world: int, hidden: int, max_rows: int, n_sites: int, exchange=None) -> None:
+    def __init__(self, rank: int, world: int, hidden: int, max_rows: int, n_sites: int, exchange=None,
+                 prefill_rows: int = 0) -> None:
+        """``prefill_rows`` > 0 adds the buffers of the prefill all-reduce (chunks of up to that many
+        rows): per rank an inbox of ``world`` partial slices and a result buffer, both bf16."""
         from ..ops import _lib
         if world > MAX_WORLD:
             raise ValueError(f"tensor-parallel world {world} > {MAX_WORLD}")
@@ -128,6 +149,20 @@ class TpComm:
         self._off_epoch = self._off_arrive + (n_sites * 4 + 255) // 256 * 256
         self._off_status = self._off_epoch + 256
         self.nbytes = self._off_status + 256
+        self.hidden = hidden
+        self.pf_rows = 0
+        if prefill_rows > 0:
+            self.pf_rpr = (prefill_rows + world - 1) // world
+            self.pf_rows = self.pf_rpr * world
+            slab = (self.pf_rows * hidden * 2 + 255) // 256 * 256
+            self._off_pf_inbox = self.nbytes
+            self._off_pf_out = self._off_pf_inbox + slab
+            self._off_pf_f1 = self._off_pf_out + slab
+            self._off_pf_f2 = self._off_pf_f1 + 256
+            self._off_pf_arrive = self._off_pf_f2 + 256
+            self._off_pf_desc = self._off_pf_arrive + 256
+            self.nbytes = self._off_pf_desc + 1024
+        self._pf_seq = 0
         self._lib = _lib.lib()
         base = ctypes.c_void_p()
         rc = self._lib.cb_peer_alloc(ctypes.c_int64(self.nbytes), ctypes.byref(base))
@@ -157,11 +192,63 @@ class TpComm:
         for r in range(world):
             s.inbox[r] = self.peers[r]
             s.flags[r] = self.peers[r] + self._off_flags
+        # limit of a device-side wait; COFFIN_TP_WAIT_MS shortens it (tests make a wait run out on purpose)
+        self.wait_ns = int(float(os.environ.get("COFFIN_TP_WAIT_MS", "2000")) * 1e6)
+        s.wait_ns = self.wait_ns
         s.my_inbox, s.my_flags = self.peers[rank], self.peers[rank] + self._off_flags
         s.arrive = self.base + self._off_arrive
         s.epoch = self.base + self._off_epoch
         s.status = self.base + self._off_status
         self._struct = s
+        if self.pf_rows:
+            d = _TpPfStruct()
+            d.rank, d.world, d.rows_per_rank, d.width = rank, world, self.pf_rpr, hidden
+            for r in range(world):
+                d.inbox[r] = self.peers[r] + self._off_pf_inbox
+                d.out[r] = self.peers[r] + self._off_pf_out
+                d.flags1[r] = self.peers[r] + self._off_pf_f1
+                d.flags2[r] = self.peers[r] + self._off_pf_f2
+            d.arrive = self.base + self._off_pf_arrive
+            d.status = self.base + self._off_status
+            d.wait_ns = self.wait_ns
+            assert ctypes.sizeof(d) == self._lib.cb_tp_pf_desc_size() <= 1024
+            rc = self._lib.cb_peer_write(ctypes.c_void_p(self.base + self._off_pf_desc), ctypes.byref(d),
+                                         ctypes.c_int64(ctypes.sizeof(d)))
+            if rc:
+                raise _lib.KernelError(f"descriptor upload failed ({rc})")
+            self._pf_struct = d
+            view = torch.as_tensor(_DevView(self.base + self._off_pf_out, self.pf_rows * hidden), device="cuda")
+            self.pf_out = view.view(torch.bfloat16).view(self.pf_rows, hidden)
+
+    # ---- prefill all-reduce (reduce-scatter in the producer, all-gather here) ------------------
+    def pf_desc_ptr(self):
+        return ctypes.c_void_p(self.base + self._off_pf_desc)
+
+    def next_seq(self, rows: int, width: int) -> int:
+        """Sequence number of the next scatter (every rank makes the same calls in the same order)."""
+        if not self.pf_rows or rows > self.pf_rows or width != self.hidden:
+            raise ValueError(f"prefill all-reduce of [{rows}, {width}] outside the region [{self.pf_rows}, {self.hidden}]")
+        self._pf_seq += 1
+        self._pf_T = rows
+        return self._pf_seq
+
+    def scatter(self, src: torch.Tensor) -> None:
+        """First half for a producer that is not a GEMM: send the rows of ``src [T, hidden]`` (bf16) to their owners."""
+        from ..ops import kernels as K
+        T = src.shape[0]
+        K.call("tp_pf_scatter", self.pf_desc_ptr(), src, src.stride(0), T, self.next_seq(T, src.shape[1]))
+        K._count()
+
+    def finish_reduce(self, residual: torch.Tensor | None = None) -> torch.Tensor:
+        """Second half: add the partial slices this rank owns (+ ``residual`` rows), send the sums to
+        every rank and wait for everyone's.  Returns the reduced ``[T, hidden]`` rows (a view of the
+        result buffer, valid until the next all-reduce)."""
+        from ..ops import kernels as K
+        T, seq = self._pf_T, self._pf_seq
+        K.call("tp_pf_reduce_gather", self.pf_desc_ptr(), residual, residual.stride(0) if residual is not None else 0, T, seq)
+        K.call("tp_pf_wait", self.pf_desc_ptr(), seq)
+        K._count(2)
+        return self.pf_out[:T]
 
     def cstruct_ref(self):
         return ctypes.byref(self._struct)

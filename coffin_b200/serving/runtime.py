@@ -77,6 +77,13 @@ class Server:
         self._thread: threading.Thread | None = None
         self._stopping = threading.Event()
         self.last_error: str | None = None
+        # multi-rank engines: an object with ``check() -> list[int]`` (``parallel.control.Heartbeat``);
+        # the loop asks it between steps, before the next kernels are launched
+        self.heartbeat = None
+        self.dead_ranks: list[int] = []
+
+    def attach_heartbeat(self, hb) -> None:
+        self.heartbeat = hb
 
     # ------------------------------------------------------------------ lifecycle
     def start(self) -> None:
@@ -109,6 +116,16 @@ class Server:
                     if self._inbox.empty() and self._running:
                         self._wake.wait(timeout=0.05)
                 continue
+            if self.heartbeat is not None:
+                dead = self.heartbeat.check()
+                if dead:
+                    # a peer is gone: nothing more is launched for this group; the requests in flight
+                    # fail on the host and the launcher restarts the ranks (no elastic re-ranking)
+                    self.dead_ranks = dead
+                    self._fail(RuntimeError(f"rank(s) {dead} stopped answering the heartbeat"))
+                    self._running = False
+                    self._stopping.set()
+                    break
             try:
                 outs = self.engine.step()
             except Exception as exc:            # noqa: BLE001 - the service must survive a bad step

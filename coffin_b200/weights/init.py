@@ -120,6 +120,9 @@ def random_state_dict(cfg: ModelConfig, seed: int = 0, dtype: torch.dtype = torc
     generator is seeded per tensor (seed + index) so that any subset (a pipeline stage,
     a tensor-parallel shard source) sees the same values as the whole.
     """
+    if getattr(cfg, "architecture", "") == "qwen4_exp":
+        from ..models.qwen4exp.weights import random_state_dict as qwen4_random
+        return qwen4_random(cfg, seed, dtype=dtype, device=device, std=std)
     sd: dict[str, torch.Tensor] = {}
     dev = torch.device(device)
     for idx, (key, shape, kind) in enumerate(tensor_plan(cfg, mtp)):

@@ -124,6 +124,18 @@ class W4A8Weight:
     def to(self, device) -> "W4A8Weight":
         return W4A8Weight(self.packed.to(device), self.scale.to(device), self.k, self.group_size)
 
+    def to_nk(self) -> tuple[torch.Tensor, torch.Tensor]:
+        """The layout the sm_100a kernels stream: codes ``[..., N, K/2]`` uint8 (byte ``j`` of a row =
+        ``code(2j) | code(2j+1) << 4``) and scales ``[..., N, K/group]`` fp32.  ``K`` must be a multiple
+        of the group size."""
+        if self.k % self.group_size:
+            raise ValueError(f"K={self.k} is not a multiple of the group size {self.group_size}")
+        lo, hi = self.packed & 0xF, self.packed >> 4                               # [..., K/2, N] each
+        kn = torch.stack([lo, hi], -2).reshape(*self.packed.shape[:-2], -1, self.packed.shape[-1])[..., :self.k, :]
+        nk = kn.transpose(-1, -2)                                                  # [..., N, K]
+        packed = (nk[..., 0::2] | (nk[..., 1::2] << 4)).to(torch.uint8).contiguous()
+        return packed, self.scale.transpose(-1, -2).float().contiguous()
+
 
 def quantize_state_dict(sd: dict[str, torch.Tensor], scheme: str = "int8") -> dict:
     """Replace every quantisable projection by its container (``int8`` or ``w4a8``)."""

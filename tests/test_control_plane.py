@@ -77,3 +77,49 @@ def test_heartbeat_detects_a_rank_that_left():
     got = dict(q.get(timeout=60) for _ in range(3))
     [p.join(timeout=60) for p in ps]
     assert got["early"] == [] and got["late"] == [1]
+
+
+def test_server_fails_requests_in_flight_when_a_peer_heartbeat_stops():
+    """The failure is made on the host: a fake heartbeat reports rank 1 dead after a few checks; the
+    serving loop must fail the running request, launch nothing more and mark itself stopping."""
+    import queue
+
+    import torch
+
+    from coffin_b200.config import preset
+    from coffin_b200.engine.config import EngineConfig
+    from coffin_b200.engine.sequence import SamplingParams
+    from coffin_b200.oracle.engine_model import OracleEngineModel
+    from coffin_b200.serving.runtime import Server
+    from coffin_b200.weights.init import random_state_dict
+
+    class FakeHeartbeat:
+        def __init__(self):
+            self.n = 0
+
+        def check(self):
+            self.n += 1
+            return [1] if self.n > 3 else []
+
+    cfg = preset("tiny")
+    srv = Server(OracleEngineModel(cfg, random_state_dict(cfg, 0), max_seq=256, num_slots=2),
+                 EngineConfig(max_seq=256, max_num_seqs=2, graph=False), model_name="tiny")
+    srv.attach_heartbeat(FakeHeartbeat())
+    srv.start()
+    seq, outq = srv._submit(list(range(5, 25)), SamplingParams(max_tokens=64, ignore_eos=True))
+    kinds = []
+    while True:
+        try:
+            kind, val = outq.get(timeout=20)
+        except queue.Empty:
+            break
+        kinds.append(kind)
+        if kind in ("error", "done"):
+            break
+    assert kinds[-1] == "error" and "heartbeat" in val
+    assert srv.dead_ranks == [1] and srv.stopping
+    steps = srv.model.n_decode_calls
+    import time
+    time.sleep(0.3)
+    assert srv.model.n_decode_calls == steps          # nothing launched after the peer was declared dead
+    srv.stop()

@@ -316,3 +316,52 @@ def test_quant_rows_and_i8_prefill_chain():
     ref = O.silu_mul(gu[:, :264], gu[:, 264:]).to(torch.bfloat16)
     rq2, rs2 = O.quant_rows_int8(ref, floor=1e-8)
     assert (qs.cpu().int() - rq2.int()).abs().max() <= 1
+
+
+@pytest.mark.parametrize("M,N,Kd", [(1, 520, 512), (4, 2560, 1024), (8, 264, 256), (2, 1000, 2304)])
+def test_gemv_w4a8(M, N, Kd):
+    """W4A8 GEMV against the integer oracle (group-128 int4 weights, per-token int8 activations)."""
+    k = K()
+    from coffin_b200.weights.quant import W4A8Weight
+    W, x = bf(N, Kd, s=0.05, seed=60), bf(M, Kd, seed=61)
+    q = W4A8Weight.quantize(W.float())
+    wq, sc = q.to_nk()
+    out = torch.empty(M, N, dtype=torch.float32, device=DEV)
+    k.gemv_w4(wq.to(DEV), sc.to(DEV), x.to(DEV), out)
+    close(out, O.w4a8_linear(x, q.packed, q.scale, Kd), 5e-3)
+    close(k.w4_dequant(wq.to(DEV), sc.to(DEV)), q.dequant(), 1e-2)
+    # fused norm + swiglu
+    I = N // 2 // 8 * 8
+    res, add = bf(M, Kd, seed=62), bf(M, Kd, seed=63)
+    gain = (1 + 0.1 * torch.randn(Kd)).float()
+    out2 = torch.empty(M, I, dtype=torch.bfloat16, device=DEV)
+    ro = torch.empty(M, Kd, dtype=torch.bfloat16, device=DEV)
+    q2 = W4A8Weight.quantize(W[:2 * I].float())
+    wq2, sc2 = q2.to_nk()
+    k.gemv_w4(wq2.to(DEV), sc2.to(DEV), None, out2, swiglu=True, norm=(res.to(DEV), add.to(DEV), gain.to(DEV), ro, 1e-6))
+    s_, n_ = O.add_rms_norm(res, add, gain)
+    gu = O.w4a8_linear(n_.to(torch.bfloat16), q2.packed, q2.scale, Kd)
+    close(ro, s_)
+    close(out2, O.silu_mul(gu[:, :I], gu[:, I:]), 3e-2)
+
+
+def test_moe_gemv_w4a8_slots():
+    k = K()
+    from coffin_b200.weights.quant import W4A8Weight
+    E, I, H = 6, 128, 256
+    g = torch.Generator().manual_seed(70)
+    Wgu = (torch.randn(E, 2 * I, H, generator=g) * 0.05).to(torch.bfloat16)
+    x = torch.randn(3, H, generator=g).to(torch.bfloat16)
+    q = W4A8Weight.quantize(Wgu.float())
+    wq, sc = q.to_nk()
+    slot_e = torch.tensor([4, 0, -1, 5, 1], dtype=torch.int32, device=DEV)
+    slot_x = torch.tensor([0, 0, 1, 2, 2], dtype=torch.int32, device=DEV)
+    out = torch.zeros(5, I, dtype=torch.bfloat16, device=DEV)
+    k.moe_gemv_w4(wq.to(DEV), sc.to(DEV), x.to(DEV), out, slot_e, slot_x, swiglu=True)
+    for s in range(5):
+        e, r = int(slot_e[s]), int(slot_x[s])
+        if e < 0:
+            assert float(out[s].abs().max()) == 0.0
+            continue
+        gu = O.w4a8_linear(x[r:r + 1], q.packed[e], q.scale[e], H)
+        close(out[s:s + 1], O.silu_mul(gu[:, :I], gu[:, I:]), 3e-2)

@@ -228,3 +228,68 @@ def test_vision_tower_matches_oracle():
         got = VisionTower(cfg, sd).forward(patches, grid)
         assert got.shape == ref.shape == (grid[1] * grid[2] // 4, 256)
         assert _rel(got, ref) < 5e-2
+
+
+@torch.no_grad()
+@pytest.mark.parametrize("name", ["tiny", "tiny-moe"])
+def test_w4a8_model_matches_oracle_with_quantised_weights(name):
+    """quant="w4a8": group-128 int4 weights, per-token int8 activations; the oracle runs on the
+    dequantised weights, the rest of the gap is activation quantisation (and router flips for MoE)."""
+    from coffin_b200.models.qwen35.model import Qwen35Model
+    from coffin_b200.weights.quant import W4A8Weight, is_quantizable
+    cfg = preset(name)
+    sd = random_state_dict(cfg, 0)
+    sd_q = {}
+    for k, v in sd.items():
+        vb = v.to(torch.bfloat16).float() if not k.endswith(("A_log", "dt_bias")) else v
+        sd_q[k] = W4A8Weight.quantize(vb).dequant() if is_quantizable(k, v) and v.shape[-1] % 128 == 0 else vb
+    sd_q["lm_head.weight"] = W4A8Weight.quantize(sd_q["model.language_model.embed_tokens.weight"]).dequant()
+    oracle = OracleModel(cfg, sd_q)
+    model = Qwen35Model(cfg, sd, max_seq=512, num_slots=2, quant="w4a8")
+    toks = _tokens(cfg, 90, seed=33)
+    st = oracle.new_state()
+    ref = oracle.forward(toks[:80], st)[-1]
+    bt = torch.arange(1, 9, dtype=torch.int32, device="cuda")
+    model.zero_state(0)
+    got = model.prefill(toks[:80].cuda(), 0, 0, bt)
+    tol = 8e-2 if name == "tiny" else 0.15
+    assert _rel(got, ref) < tol
+    for i in range(80, 90):
+        ref = oracle.forward(toks[i:i + 1], st)[-1]
+        model.set_rows(1, [int(toks[i])], [i], [0], [bt.tolist()])
+        _, logits = model.decode(1, graph=i >= 84)
+        assert _rel(logits[0], ref) < tol, f"step {i}"
+
+
+@torch.no_grad()
+def test_speculative_decoding_with_mtp_drafter_follows_plain_greedy():
+    """Drafts come from the MTP head; whatever their quality, verification keeps the output on the
+    model's own greedy path (up to near-ties between the verify and decode kernels)."""
+    from coffin_b200.engine.speculative import SpeculativeDecoder
+    from coffin_b200.models.qwen35.model import Qwen35Model
+    from coffin_b200.models.qwen35.mtp import MTPDrafter, MTPHead
+    cfg = preset("tiny")
+    sd = random_state_dict(cfg, 0, mtp=True)
+    model = Qwen35Model(cfg, sd, max_seq=256, num_slots=1)
+    drafter = MTPDrafter(MTPHead(model, sd))
+    spec = SpeculativeDecoder(model, k=3, drafter=drafter, slot=0)
+    prompt = _tokens(cfg, 40, seed=51)
+    bt = torch.arange(1, 5, dtype=torch.int32, device="cuda")
+    model.zero_state(0)
+    logits = model.prefill(prompt.cuda(), 0, 0, bt)
+    drafter.prime(prompt.cuda(), 0, bt)
+    got = spec.generate(prompt.tolist(), bt.tolist(), logits, 12)
+    st = spec.stats()
+    assert st["drafted"] > 0 and st["steps"] >= 1 and len(got) == 12
+    model.zero_state(0)
+    logits = model.prefill(prompt.cuda(), 0, 0, bt)
+    plain, tok = [], int(logits.argmax())
+    for i in range(12):
+        plain.append(tok)
+        model.set_rows(1, [tok], [40 + i], [0], [bt.tolist()])
+        nxt, _ = model.decode(1, graph=False)
+        tok = int(nxt[0])
+    agree = 0
+    while agree < 12 and got[agree] == plain[agree]:
+        agree += 1
+    assert agree >= 6, (got, plain, st)

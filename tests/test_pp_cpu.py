@@ -4,7 +4,11 @@ import os
 import socket
 
 import torch
-import torch.multiprocessing as mp
+
+from ranks import run_ranks
+
+RANK_TIMEOUT = 120
+RANK_ENV = {"COFFIN_TP_WAIT_MS": "250", "NCCL_NVLS_ENABLE": "0", "COFFIN_RANK_LOG_DIR": os.environ.get("COFFIN_RANK_LOG_DIR", "")}
 
 from coffin_b200.config import preset
 from coffin_b200.parallel.pp import layer_range, split_lanes, stage_config, stage_state_dict
@@ -87,7 +91,7 @@ def test_two_stage_pipeline_matches_single_process(tmp_path):
     cfg = preset("tiny")
     ref = _scenario(OracleEngineModel(cfg, random_state_dict(cfg, 0), max_seq=256, num_slots=2), cfg)
     path = str(tmp_path / "pp.pt")
-    mp.spawn(_pp_rank, args=(2, _free_port(), path), nprocs=2, join=True)
+    run_ranks(_pp_rank, 2, args=(_free_port(), path), timeout=RANK_TIMEOUT, env=RANK_ENV)
     got = torch.load(path)
     assert len(got["outs"]) == len(ref)
     for a, b in zip(got["outs"], ref):

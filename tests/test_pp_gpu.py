@@ -5,6 +5,11 @@ import socket
 import pytest
 import torch
 
+from ranks import run_ranks
+
+RANK_TIMEOUT = 150
+RANK_ENV = {"COFFIN_TP_WAIT_MS": "250", "NCCL_NVLS_ENABLE": "0", "COFFIN_RANK_LOG_DIR": os.environ.get("COFFIN_RANK_LOG_DIR", "")}
+
 from coffin_b200.config import preset
 from coffin_b200.oracle.model import OracleModel
 from coffin_b200.weights.init import random_state_dict
@@ -52,9 +57,8 @@ def _rank_main(rank, world, port, out):
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
 def test_two_stage_pipeline_matches_oracle(tmp_path):
-    import torch.multiprocessing as mp
     out = str(tmp_path / "pp.pt")
-    mp.spawn(_rank_main, args=(2, _free_port(), out), nprocs=2, join=True)
+    run_ranks(_rank_main, 2, args=(_free_port(), out), timeout=RANK_TIMEOUT, env=RANK_ENV)
     got = torch.load(out)
     cfg = preset("tiny")
     sd = random_state_dict(cfg, 0)

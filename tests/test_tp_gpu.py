@@ -7,6 +7,11 @@ import sys
 import pytest
 import torch
 
+from ranks import run_ranks
+
+RANK_TIMEOUT = 150
+RANK_ENV = {"COFFIN_TP_WAIT_MS": "250", "NCCL_NVLS_ENABLE": "0", "COFFIN_RANK_LOG_DIR": os.environ.get("COFFIN_RANK_LOG_DIR", "")}
+
 from coffin_b200.config import preset
 from coffin_b200.oracle.model import OracleModel
 from coffin_b200.weights.init import random_state_dict
@@ -54,6 +59,45 @@ def test_push_pull_path_on_one_gpu_matches_plain_decode():
     tp.close()
 
 
+@torch.no_grad()
+def test_prefill_all_reduce_protocol_on_one_gpu():
+    """World 1: the GEMM epilogue scatters into this rank's own inbox, the reduce/gather kernel adds
+    the single slice (+ residual) and the wait sees its own flags - the whole protocol, no peer."""
+    from coffin_b200.models.qwen35.model import Qwen35Model
+    from coffin_b200.ops import kernels as K
+    from coffin_b200.parallel.tp import TpComm
+    cfg = preset("tiny")
+    tp = TpComm(0, 1, cfg.hidden_size, 8, 2 * cfg.num_hidden_layers, prefill_rows=160)
+    g = torch.Generator().manual_seed(4)
+    A = (torch.randn(150, 512, generator=g)).to(torch.bfloat16).cuda()
+    W = (torch.randn(cfg.hidden_size, 512, generator=g) * 0.05).to(torch.bfloat16).cuda()
+    res = torch.randn(150, cfg.hidden_size, generator=g).to(torch.bfloat16).cuda()
+    for _ in range(3):                                   # the sequence number advances, buffers are reused
+        K.gemm(A, W, push=tp)
+        got = tp.finish_reduce(residual=res).float()
+        ref = (A.float() @ W.float().t()).to(torch.bfloat16).float() + res.float()
+        assert ((got - ref).abs().max() / ref.abs().max()).item() < 1e-2
+    tp.scatter(res)
+    assert torch.equal(tp.finish_reduce(), res)
+    # the model's prefill through the fused path equals the plain prefill
+    sd = random_state_dict(cfg, 0)
+    plain = Qwen35Model(cfg, sd, max_seq=256, num_slots=1)
+    fused = Qwen35Model(cfg, sd, max_seq=256, num_slots=1, tp=tp)
+    fused.tp_force = True
+    toks = torch.randint(0, cfg.vocab_size, (100,), generator=g).cuda()
+    bt = torch.arange(1, 5, dtype=torch.int32, device="cuda")
+    outs = []
+    for m in (plain, fused):
+        m.zero_state(0)
+        outs.append(m.prefill(toks, 0, 0, bt).clone())
+    rel = ((outs[0] - outs[1]).abs().max() / outs[0].abs().max()).item()
+    assert rel < 4e-2, rel        # the fused path rounds the projection to bf16 before the residual add
+    torch.cuda.synchronize()
+    assert tp.status() == 0
+    K.check_status()
+    tp.close()
+
+
 def _rank_main(rank, world, port, out):
     import torch.distributed as dist
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
@@ -81,9 +125,8 @@ def _rank_main(rank, world, port, out):
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
 def test_two_rank_tensor_parallel_matches_oracle(tmp_path):
-    import torch.multiprocessing as mp
     out = str(tmp_path / "tp.pt")
-    mp.spawn(_rank_main, args=(2, _free_port(), out), nprocs=2, join=True)
+    run_ranks(_rank_main, 2, args=(_free_port(), out), timeout=RANK_TIMEOUT, env=RANK_ENV)
     got = torch.load(out)
     assert got["status"] == 0
     cfg = preset("tiny")
@@ -159,9 +202,8 @@ def _ep_rank_main(rank, world, port, out):
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
 def test_two_rank_expert_parallel_matches_oracle(tmp_path):
-    import torch.multiprocessing as mp
     out = str(tmp_path / "ep.pt")
-    mp.spawn(_ep_rank_main, args=(2, _free_port(), out), nprocs=2, join=True)
+    run_ranks(_ep_rank_main, 2, args=(_free_port(), out), timeout=RANK_TIMEOUT, env=RANK_ENV)
     got = torch.load(out)
     assert got["status"] == 0
     cfg = preset("tiny-moe")
