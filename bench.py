@@ -98,7 +98,9 @@ def main() -> None:
     ap.add_argument("--model", default=MODEL)
     ap.add_argument("--prompt", type=int, default=PROMPT)
     ap.add_argument("--new", type=int, default=NEW)
-    ap.add_argument("--quant", default="none", choices=["none", "int8"])
+    ap.add_argument("--quant", default="none", choices=["none", "int8", "w4a8"])
+    ap.add_argument("--rows", type=int, default=1,
+                    help="concurrent sequences: > 1 measures batched decode throughput (not the headline config)")
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--no-pdl", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
@@ -150,6 +152,8 @@ def main() -> None:
         from coffin_b200.ops import _lib
         _lib.call_nostream("set_gemv_opts", args.gemv_ctas or 2, 1 if args.gemv_prefetch != 0 else 0)
     cfg = preset(args.model)
+    if args.rows > 1:
+        return bench_rows(args, cfg, W)
     llm = LLM.from_random(cfg, seed=0, max_seq=args.prompt + args.new + 64, max_num_seqs=1,
                           tp_world=world, tp_rank=rank, graph=not args.no_graph, pdl=not args.no_pdl,
                           max_chunk=args.prompt, quant=args.quant)
@@ -224,7 +228,7 @@ def main() -> None:
             "metric": "decode_tok_s", "value": decode_tok_s, "unit": "tok/s", "n_gpus": world,
             "steps": steps, "warmup": W, "ms_per_step": (pre_total + dec_total) / steps,
             "higher_is_better": True, "scaling": "strong",
-            "vs_baseline": decode_tok_s / BASELINE_DECODE_TOK_S, "dtype": "bf16" if args.quant == "none" else "int8-w8a8", "data": "synthetic",
+            "vs_baseline": decode_tok_s / BASELINE_DECODE_TOK_S, "dtype": {"none": "bf16", "int8": "int8-w8a8", "w4a8": "int4-w4a8"}.get(args.quant, args.quant), "data": "synthetic",
             "prefill_tok_s": prefill_tok_s, "prefill_vs_baseline": prefill_tok_s / BASELINE_PREFILL_TOK_S,
             "ttft_ms_p50": statistics.median(pre_ms), "tpot_ms_p50": statistics.median(dec_ms) / args.new,
             "config": {"model": args.model, "global_batch": 1, "seq_len": args.prompt, "decode_tokens": args.new,
@@ -235,7 +239,62 @@ def main() -> None:
         }
         print(json.dumps(line), flush=True)
     if world > 1:
-        dist.destroy_process_group()
+        from coffin_b200.parallel.control import shutdown
+        dist.barrier()
+        tp = getattr(llm.model, "tp", None)
+        llm.model._graphs.clear()
+        if tp is not None:
+            tp.close()
+        shutdown(timeout_s=10.0)
+
+
+def bench_rows(args, cfg, W: int) -> None:
+    """Batched decode throughput on one GPU: ``--rows`` sequences are prefilled one after the other and
+    then advance together, one CUDA-graph step per token (buckets above 8 rows run their projections
+    on the tcgen05 GEMM).  Prints one JSON line; ``value`` is the aggregate decode tok/s."""
+    import json
+    import statistics
+    import torch
+    from coffin_b200.engine.llm import LLM
+    from coffin_b200.ops import kernels as K
+    R = args.rows
+    llm = LLM.from_random(cfg, seed=0, max_seq=args.prompt + args.new + 64, max_num_seqs=R, max_chunk=args.prompt,
+                          quant=args.quant)
+    m = llm.model
+    M = m.bucket_for(R)
+    nblk = m.max_blocks_per_seq
+    tables = [list(range(r * nblk, (r + 1) * nblk)) for r in range(R)]
+    g = torch.Generator().manual_seed(1234)
+    ev = lambda: torch.cuda.Event(enable_timing=True)
+    pre_ms, dec_ms = [], []
+    for it in range(W + args.steps):
+        prompts = [torch.randint(0, cfg.vocab_size, (args.prompt,), generator=g).pin_memory() for _ in range(R)]
+        e0, e1, e2 = ev(), ev(), ev()
+        e0.record()
+        firsts = []
+        for r in range(R):
+            m.zero_state(r)
+            lg = m.prefill(prompts[r].cuda(non_blocking=True), 0, r, torch.tensor(tables[r], dtype=torch.int32, device="cuda"))
+            firsts.append(int(lg.argmax()))
+        e1.record()
+        m.set_rows(M, firsts, [args.prompt] * R, list(range(R)), tables)
+        for _ in range(args.new):
+            m.decode(M, graph=True)
+            m.advance_rows(M)
+        e2.record()
+        e2.synchronize()
+        if it >= W:
+            pre_ms.append(e0.elapsed_time(e1))
+            dec_ms.append(e1.elapsed_time(e2))
+    K.check_status()
+    dec_tok_s = R * args.new * len(dec_ms) / (sum(dec_ms) / 1e3)
+    print(json.dumps({"metric": "batched_decode_tok_s", "value": dec_tok_s, "unit": "tok/s", "n_gpus": 1,
+                      "steps": args.steps, "warmup": W, "higher_is_better": True,
+                      "prefill_tok_s": R * args.prompt * len(pre_ms) / (sum(pre_ms) / 1e3),
+                      "step_ms_p50": statistics.median(dec_ms) / args.new,
+                      "dtype": {"none": "bf16", "int8": "int8-w8a8", "w4a8": "int4-w4a8"}[args.quant], "data": "synthetic",
+                      "config": {"model": args.model, "global_batch": R, "seq_len": args.prompt,
+                                 "decode_tokens": args.new, "bucket": M, "cuda_graph": True}, "impl": "ours"}), flush=True)
 
 
 if __name__ == "__main__":

@@ -90,9 +90,10 @@ __global__ void __launch_bounds__(kT, 3) gemv_i8_kernel(const I8Args a) {
       if (NORM) {
         bf16x8_to_float(*reinterpret_cast<const uint4*>(a.res_in + m * K + c * 8), f);
         if (a.pull_site >= 0) {
+          float pulled[8];
+          tp_pull8(a.tp, a.pull_site, m * K + c * 8, pulled);
 #pragma unroll
-          for (int i = 0; i < 8; ++i)
-            f[i] = __bfloat162float(__float2bfloat16(f[i] + tp_pull_value(a.tp, a.pull_site, m * K + c * 8 + i)));
+          for (int i = 0; i < 8; ++i) f[i] = __bfloat162float(__float2bfloat16(f[i] + pulled[i]));
         } else if (a.add) {
           bf16x8_to_float(*reinterpret_cast<const uint4*>(a.add + m * K + c * 8), q);
 #pragma unroll

@@ -2,15 +2,15 @@
 //
 // A row-parallel projection leaves every rank with a partial sum of the hidden vector.  Instead of
 // a collective call between kernels, the producing GEMV *pushes* its partial rows straight into an
-// inbox on every rank (plain peer stores through IPC-mapped pointers) and publishes a flag; the next
-// projection's prologue *pulls*: it waits (bounded) for the flags of all ranks and adds the inbox
-// slots in rank order while it stages its activation, so the reduction costs no launch and its
-// latency hides behind the consumer's weight prefetch.  The sum order is fixed, hence every rank
+// inbox on every rank (plain peer stores through IPC-mapped pointers), each value paired with the
+// step's epoch; the next projection's prologue *pulls*: it polls (bounded) every rank's element
+// until it carries this step's epoch and adds them in rank order while it stages its activation,
+// so the reduction costs no launch and its latency hides behind the consumer's weight prefetch.  The sum order is fixed, hence every rank
 // computes bit-identical activations.  Replaces the reference's per-projection gloo all-reduce of
 // RowParallelProjection (models/qwen35/parallel.py:1015-1061) and the idea of its p2p_combine kernel
 // (backends/corex/kernels/p2p_reduce.cu:55-173: write to all peers, publish flag, bounded spin).
 //
-// Flags carry the step epoch (a device-side counter every rank advances once per step), so buffers
+// The epoch is a device-side counter every rank advances once per step, so buffers
 // are reused without resetting: a site's inbox can only be overwritten a full step later, and a rank
 // cannot get there before all peers consumed the previous contents because it needs their partial
 // sums of the sites in between.  Waits give up after kTpWaitNs, set the status word and continue
@@ -24,7 +24,7 @@ constexpr unsigned long long kTpWaitNs = 2000000000ull;   // default limit of a 
 struct TpComm {
   int rank, world;
   int64_t slot_floats;      // floats per (site, rank) inbox slot  (= max rows * hidden)
-  float* inbox[kTpMaxWorld];       // base of every rank's inbox: [sites][world][slot_floats]
+  float* inbox[kTpMaxWorld];       // base of every rank's inbox: [sites][world][slot_floats] {value, epoch} pairs
   unsigned* flags[kTpMaxWorld];    // base of every rank's flags: [sites][world]
   const float* my_inbox;    // == inbox[rank]; a separate field so that no kernel indexes the arrays
   const unsigned* my_flags; // == flags[rank]  with a run-time value (that would copy the parameter
@@ -49,55 +49,101 @@ __device__ __forceinline__ void tp_st_release(unsigned* p, unsigned v) {
   asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 
-// Producer: store `n` consecutive fp32 partial values starting at element `off` of this rank's slot
-// on every rank.  Called by the threads that own the values.
+// Data and flag travel together (the "low-latency" layout of collective libraries): an inbox element
+// is an aligned 8-byte pair {fp32 value, epoch}, written with one 64-bit store.  The consumer polls
+// the element itself until its epoch word equals the current step, so the producer needs no fence,
+// no arrival counter and no separate flag, and the consumer sees a value the moment it lands.
+__device__ __forceinline__ void tp_st_pair(float* slot_base, int64_t elem, float v, unsigned epoch) {
+  const unsigned long long packed = ((unsigned long long)epoch << 32) | (unsigned long long)__float_as_uint(v);
+  asm volatile("st.volatile.global.u64 [%0], %1;" ::"l"(reinterpret_cast<unsigned long long*>(slot_base) + elem),
+               "l"(packed) : "memory");
+}
+__device__ __forceinline__ unsigned long long tp_ld_pair(const float* slot_base, int64_t elem) {
+  unsigned long long v;
+  asm volatile("ld.volatile.global.u64 %0, [%1];" : "=l"(v)
+               : "l"(reinterpret_cast<const unsigned long long*>(slot_base) + elem) : "memory");
+  return v;
+}
+// Producer: store the fp32 partial value of element `off` of this rank's slot on every rank.
+// Called by the thread that owns the value.
 __device__ __forceinline__ void tp_push_value(const TpComm& c, int site, int64_t off, float v) {
-  const int64_t base = ((int64_t)site * c.world + c.rank) * c.slot_floats + off;
+  const int64_t elem = ((int64_t)site * c.world + c.rank) * c.slot_floats + off;
+  const unsigned e = *c.epoch;
 #pragma unroll
   for (int p = 0; p < kTpMaxWorld; ++p)
-    if (p < c.world) c.inbox[p][base] = v;
+    if (p < c.world) tp_st_pair(c.inbox[p], elem, v, e);
 }
-// Producer: after a CTA pushed all its values. The last CTA of the grid publishes the flags.
-__device__ __forceinline__ void tp_push_done(const TpComm& c, int site, unsigned nblocks) {
-  __threadfence_system();
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    const unsigned prev = atomicAdd(c.arrive + site, 1u);
-    if (prev == nblocks - 1) {
-      c.arrive[site] = 0;
-      __threadfence_system();
-      const unsigned e = *c.epoch;
-#pragma unroll
-      for (int p = 0; p < kTpMaxWorld; ++p)
-        if (p < c.world) tp_st_release(c.flags[p] + (int64_t)site * c.world + c.rank, e);
-    }
-  }
-}
-// Consumer: wait until every rank published this step's flag for the site. Thread 0 waits, then
-// the block synchronises.
-__device__ __forceinline__ void tp_pull_wait(const TpComm& c, int site) {
-  if (threadIdx.x == 0) {
-    const unsigned e = *c.epoch;
-    const unsigned* f = c.my_flags + (int64_t)site * c.world;
-    const unsigned long long t0 = tp_now_ns();
-    for (int r = 0; r < c.world; ++r) {
+// Kept for the call sites' symmetry: with data-carried flags nothing is left to publish.
+__device__ __forceinline__ void tp_push_done(const TpComm&, int, unsigned) {}
+__device__ __forceinline__ void tp_pull_wait(const TpComm&, int) {}
+// Consumer: sum of the ranks' partial values at element `off` (fixed rank order).  Polls every
+// rank's element until it carries this step's epoch; gives up after the wait limit, records
+// 16 + rank in the status word and uses what is there.
+__device__ __forceinline__ float tp_pull_value(const TpComm& c, int site, int64_t off) {
+  const unsigned e = *c.epoch;
+  float s = 0.f;
+  for (int r = 0; r < c.world; ++r) {
+    const int64_t elem = ((int64_t)site * c.world + r) * c.slot_floats + off;
+    unsigned long long v = tp_ld_pair(c.my_inbox, elem);
+    if ((unsigned)(v >> 32) != e) {
+      const unsigned long long t0 = tp_now_ns(), limit = c.wait_ns ? c.wait_ns : kTpWaitNs;
       unsigned spins = 0;
-      while ((int)(tp_ld_acquire(f + r) - e) < 0) {
-        if ((++spins & 1023u) == 0 && tp_now_ns() - t0 > (c.wait_ns ? c.wait_ns : kTpWaitNs)) {
+      while ((unsigned)(v >> 32) != e) {
+        if ((++spins & 255u) == 0 && tp_now_ns() - t0 > limit) {
           atomicExch(c.status, 16 + r);
           break;
         }
+        v = tp_ld_pair(c.my_inbox, elem);
       }
     }
+    s += __uint_as_float((unsigned)v);
   }
-  __syncthreads();
-}
-// Consumer: sum of the ranks' partial values at element `off` (fixed rank order).
-__device__ __forceinline__ float tp_pull_value(const TpComm& c, int site, int64_t off) {
-  const float* base = c.my_inbox + (int64_t)site * c.world * c.slot_floats + off;
-  float s = 0.f;
-  for (int r = 0; r < c.world; ++r) s += __ldcg(base + (int64_t)r * c.slot_floats);
   return s;
+}
+
+// Consumer, vector form: sums of 8 consecutive elements starting at `off` (a multiple of 8).  The 64
+// bytes of a rank's 8 pairs are fetched with four independent 16-byte loads before any flag is
+// looked at, so a thread pays one memory round trip per rank instead of eight; only pairs that have
+// not landed yet are polled again.
+__device__ __forceinline__ void tp_pull8(const TpComm& c, int site, int64_t off, float* out) {
+  const unsigned e = *c.epoch;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) out[i] = 0.f;
+  for (int r = 0; r < c.world; ++r) {
+    const unsigned long long* base = reinterpret_cast<const unsigned long long*>(c.my_inbox) +
+                                     ((int64_t)site * c.world + r) * c.slot_floats + off;
+    uint4 q[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];"
+                   : "=r"(q[j].x), "=r"(q[j].y), "=r"(q[j].z), "=r"(q[j].w) : "l"(base + 2 * j) : "memory");
+    bool ok = true;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) ok = ok && q[j].y == e && q[j].w == e;
+    if (!ok) {
+      const unsigned long long t0 = tp_now_ns(), limit = c.wait_ns ? c.wait_ns : kTpWaitNs;
+      unsigned spins = 0;
+      while (!ok) {
+        if ((++spins & 63u) == 0 && tp_now_ns() - t0 > limit) {
+          atomicExch(c.status, 16 + r);
+          break;
+        }
+        ok = true;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          if (q[j].y != e || q[j].w != e)
+            asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];"
+                         : "=r"(q[j].x), "=r"(q[j].y), "=r"(q[j].z), "=r"(q[j].w) : "l"(base + 2 * j) : "memory");
+          ok = ok && q[j].y == e && q[j].w == e;
+        }
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      out[2 * j] += __uint_as_float(q[j].x);
+      out[2 * j + 1] += __uint_as_float(q[j].z);
+    }
+  }
 }
 
 // ---------------------------------------------------------------------------------------------

@@ -19,7 +19,7 @@ from .block_manager import BlockManager
 from .config import EngineConfig
 from .sequence import Sequence
 
-BATCH_BUCKETS = (1, 2, 4, 8)
+BATCH_BUCKETS = (1, 2, 4, 8, 16, 32, 64)
 
 
 class ModelRunner:
@@ -130,10 +130,24 @@ class ModelRunner:
         """One decode step: ``tokens[i]`` is fed to ``seqs[i]`` at position ``num_computed``.
         Blocks must already be reserved.  Returns logits ``[len(seqs), vocab]``."""
         n = len(seqs)
-        M = self.model.bucket_for(n)
-        self.model.set_rows(M, tokens, [s.num_computed for s in seqs], [s.slot for s in seqs],
-                            [s.blocks.table for s in seqs], [s.rope_delta for s in seqs])
-        nxt, logits = self.model.decode(M, graph=self.cfg.graph)
+        cap = BATCH_BUCKETS[-1]
+        if n > cap:
+            # more rows than the widest bucket: run them in groups (each group is one model step)
+            parts, nxts = [], []
+            for g0 in range(0, n, cap):
+                grp = seqs[g0:g0 + cap]
+                M = self.model.bucket_for(len(grp))
+                self.model.set_rows(M, tokens[g0:g0 + cap], [s.num_computed for s in grp], [s.slot for s in grp],
+                                    [s.blocks.table for s in grp], [s.rope_delta for s in grp])
+                nx, lg = self.model.decode(M, graph=self.cfg.graph)
+                parts.append(lg[:len(grp)].clone())
+                nxts.append(nx[:len(grp)].clone())
+            nxt, logits = torch.cat(nxts), torch.cat(parts)
+        else:
+            M = self.model.bucket_for(n)
+            self.model.set_rows(M, tokens, [s.num_computed for s in seqs], [s.slot for s in seqs],
+                                [s.blocks.table for s in seqs], [s.rope_delta for s in seqs])
+            nxt, logits = self.model.decode(M, graph=self.cfg.graph)
         for s in seqs:
             s.blocks.commit(1)
             s.num_computed += 1

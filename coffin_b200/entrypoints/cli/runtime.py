@@ -112,6 +112,18 @@ def build_server(args):
     return Server(builder(), cfg_e, model_path=args.model, model_name=args.preset or "", builder=builder)
 
 
+def _leave_group(srv) -> None:
+    """End of a rank of a multi-rank engine: release the peer mappings, then a bounded teardown."""
+    from ...parallel.control import shutdown
+    comm = getattr(srv.model, "tp", None)
+    graphs = getattr(srv.model, "_graphs", None)
+    if graphs is not None:
+        graphs.clear()
+    if comm is not None:
+        comm.close()
+    shutdown(timeout_s=10.0)
+
+
 def main(argv=None) -> int:
     args = parser().parse_args(argv)
     dump = float(os.environ.get("COFFIN_FAULT_DUMP", "0") or 0)
@@ -127,11 +139,14 @@ def main(argv=None) -> int:
             srv = build_server(args)
             if rank != 0:
                 worker_loop(srv)
+                _leave_group(srv)
                 return 0
             fanout = make_fanout()
         else:
             srv = build_server(args)
         serve(srv, args.sock, fanout=fanout)
+        if world > 1:
+            _leave_group(srv)
         return 0
     from ...serving.transport import call
     req: dict = {"op": args.cmd}

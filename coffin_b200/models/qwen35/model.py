@@ -32,7 +32,8 @@ from ...ops import kernels as K
 from ...oracle import ops as O
 from ...weights.init import LM
 
-BUCKETS = (1, 2, 4, 8)
+BUCKETS = (1, 2, 4, 8, 16, 32, 64)
+WIDE = 8          # buckets above this run their projections on the tcgen05 GEMM instead of the GEMV
 
 
 class QW:
@@ -144,8 +145,10 @@ class Qwen35Model:
         self.lane = 0              # micro-batch lane: decode buffers and graphs are kept per (bucket, lane)
         self.ep_rank, self.ep_world, self.ep_site = ep_rank, ep_world, -1
         self.tp = tp
-        self.tp_world = tp.world if tp is not None else 1
-        self.tp_rank = tp.rank if tp is not None else 0
+        # under expert parallelism the communicator spans the ranks but the dense weights are
+        # replicated: the model is not tensor-parallel
+        self.tp_world = tp.world if (tp is not None and ep_world == 1) else 1
+        self.tp_rank = tp.rank if (tp is not None and ep_world == 1) else 0
         self.full_cfg = full_cfg or cfg
         self.device = torch.device(device)
         self.max_seq = int(max_seq)
@@ -523,6 +526,11 @@ class Qwen35Model:
             }
             b["logits_local"] = (b["logits"] if self.tp_world == 1 else
                                  torch.zeros(M, self.vocab_local, dtype=torch.float32, device=dev))
+            if M > WIDE:
+                b["normed"] = torch.zeros(M, H, dtype=bf, device=dev)
+                if not c.is_moe:
+                    b["gu"] = torch.zeros(M, 2 * c.intermediate_size, dtype=bf, device=dev)
+                b["logits_bf"] = torch.zeros(M, self.vocab_local, dtype=bf, device=dev)
             self._rows[key] = b
         return b
 
@@ -532,6 +540,8 @@ class Qwen35Model:
         Tensor parallel: the two row-parallel projections of a layer push their partial sums to all
         ranks (sites ``2*layer`` and ``2*layer + 1``) and the following projection pulls the sum in
         its prologue, so the step has no separate all-reduce launches."""
+        if M > WIDE:
+            return self._decode_body_wide(M)
         c, b = self.cfg, self._row_buffers(M)
         comm = self.tp if (self.tp is not None and (self.tp_world > 1 or self.ep_world > 1 or self.tp_force)) else None
         tp = comm if (self.ep_world == 1 and not self.cfg.is_moe) else None     # dense row-parallel push/pull
@@ -603,6 +613,57 @@ class Qwen35Model:
         K.argmax(b["logits"], b["next"])
         b["final_res"] = nxt
 
+    def _decode_body_wide(self, M: int) -> None:
+        """One decode step for a wide bucket (16..64 rows): every row still advances by one token
+        through the per-row state kernels (delta-net step, split-KV attention with the fused KV
+        append), but the projections run on the tcgen05 GEMM - at these row counts one 128-row tile
+        streams each weight once, which is what the GEMV would do eight rows at a time.  Single-GPU
+        only; the multi-rank paths stay within the narrow buckets."""
+        if self.tp is not None and (self.tp_world > 1 or self.ep_world > 1):
+            raise NotImplementedError("wide decode buckets are not tensor/expert parallel")
+        c, b = self.cfg, self._row_buffers(M)
+        res, normed = b["res"][0], b["normed"]
+        if self.input_hidden is not None:
+            res.copy_(self.input_hidden)
+        else:
+            K.embed_gather(self.embed, b["tokens"], res)
+        for li, lw in enumerate(self.layers):
+            K.rmsnorm(res, lw.in_gain, self.eps, out=normed)
+            proj = b["proj"][:, :lw.w_in.shape[0]]
+            self._gemm(normed, lw.w_in, out=proj)
+            if lw.kind == LINEAR:
+                j = self.lin_ids[li]
+                act = b["act_lin"]
+                K.gdn_decode(proj, lw.conv_w, lw.A_log, lw.dt_bias, lw.norm_w, self.ring[j], self.state[j],
+                             b["slots"], b["positions"], act, nk=c.linear_num_key_heads,
+                             nv=c.linear_num_value_heads, dk=c.linear_key_head_dim, dv=c.linear_value_head_dim,
+                             eps=self.eps)
+            else:
+                j = self.full_ids[li]
+                act = b["act_full"]
+                K.attn_decode(proj, lw.qg, lw.kg, self.cos, self.sin, b["positions"], b["rope_pos"],
+                              b["block_table"], self.kpool[j], self.vpool[j], b["part_o"], b["part_ml"], b["tickets"], act,
+                              nh=c.num_attention_heads, nkv=c.num_key_value_heads, hd=c.head_dim,
+                              rot=c.rotary_dim, nsplit=b["nsplit"], eps=self.eps)
+            self._gemm(act, lw.w_out, out=res, residual=res)
+            K.rmsnorm(res, lw.post_gain, self.eps, out=normed)
+            if lw.moe is not None:
+                res.add_(lw.moe.apply(normed, self))
+                K._count()
+            else:
+                self._gemm(normed, lw.w_gu, out=b["gu"])
+                self._gemm(b["gu"], lw.w_down, out=res, residual=res, swiglu_in=True)
+        if not self.pp_last:
+            b["hidden"].copy_(res)
+            K._count()
+            return
+        K.rmsnorm(res, self.final_gain, self.eps, out=normed)
+        self._gemm(normed, self.lm_head, out=b["logits_bf"])
+        b["logits"].copy_(b["logits_bf"])
+        K._count()
+        K.argmax(b["logits"], b["next"])
+        b["final_res"] = res
+
     def set_rows(self, M: int, tokens, positions, slots, block_tables, rope_deltas=None) -> None:
         """Stage up to ``M`` rows (lists of per-row values); missing rows are padding."""
         b = self._row_buffers(M)
@@ -658,6 +719,8 @@ class Qwen35Model:
         """Run one decode step on the staged rows. Returns ``(next_tokens [M], logits [M, V])``
         device tensors owned by the bucket (overwritten by the next step)."""
         b = self._row_buffers(M)
+        if graph and self.cfg.is_moe and M > 32:
+            graph = False          # the sorted expert path reads the per-expert counts on the host
         if graph:
             if (M, self.lane) not in self._graphs:
                 self.capture(M)

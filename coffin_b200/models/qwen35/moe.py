@@ -71,8 +71,13 @@ class MoEWeights:
         gu, dn = experts(gu), experts(dn)
         sh_gu = sh_down = None
         if has_shared:
-            sg, su = sd[p + "shared_expert.gate_proj.weight"], sd[p + "shared_expert.up_proj.weight"]
-            sdn = sd[p + "shared_expert.down_proj.weight"]
+            from ...weights.quant import QWeight
+
+            def dense(t):            # the shared expert is small: quantised storage is expanded to bf16
+                return t.dequant(bf) if isinstance(t, (W4A8Weight, QWeight)) else t
+
+            sg, su = dense(sd[p + "shared_expert.gate_proj.weight"]), dense(sd[p + "shared_expert.up_proj.weight"])
+            sdn = dense(sd[p + "shared_expert.down_proj.weight"])
             S = sg.shape[0]
             if S % ep_world:
                 raise ValueError("shared expert width must divide by the expert-parallel world")

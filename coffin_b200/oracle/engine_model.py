@@ -18,7 +18,7 @@ from ..weights.init import LM
 from . import ops as O
 
 BLOCK = 64
-BUCKETS = (1, 2, 4, 8)
+BUCKETS = (1, 2, 4, 8, 16, 32, 64)
 
 
 class OracleEngineModel:

@@ -139,3 +139,34 @@ class Heartbeat:
             elif now - last[1] > self.timeout_s:
                 dead.append(r)
         return dead
+
+
+def shutdown(timeout_s: float = 10.0, hard_exit: bool = True) -> bool:
+    """Leave the process group at the end of a rank process.
+
+    ``destroy_process_group`` has been seen to block for minutes when the ranks hold CUDA-IPC
+    mappings of each other's memory (the peer communicator), although every collective had
+    completed.  So the ranks synchronise, the teardown runs in a helper thread, and when it has not
+    returned after ``timeout_s`` the process ends itself with ``os._exit(0)`` (all results have been
+    written by then; the driver reaps the child).  Returns whether the teardown finished."""
+    import sys
+    done = threading.Event()
+
+    def run() -> None:
+        try:
+            dist.destroy_process_group()
+        finally:
+            done.set()
+
+    if not dist.is_initialized():
+        return True
+    if torch.cuda.is_available():
+        torch.cuda.synchronize()
+    t = threading.Thread(target=run, name="pg-teardown", daemon=True)
+    t.start()
+    ok = done.wait(timeout_s)
+    if not ok and hard_exit:
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
+    return ok

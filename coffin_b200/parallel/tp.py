@@ -142,7 +142,7 @@ class TpComm:
             raise ValueError(f"tensor-parallel world {world} > {MAX_WORLD}")
         self.rank, self.world, self.n_sites = rank, world, n_sites
         self.slot_floats = max_rows * hidden
-        inbox_b = n_sites * world * self.slot_floats * 4
+        inbox_b = n_sites * world * self.slot_floats * 8        # {fp32 value, epoch} pairs
         flags_b = n_sites * world * 4
         self._off_flags = (inbox_b + 255) // 256 * 256
         self._off_arrive = self._off_flags + (flags_b + 255) // 256 * 256

@@ -128,8 +128,17 @@ def main() -> None:
     cfg = preset(args.model)
     if args.layers and args.layers < cfg.num_hidden_layers:
         cfg = dataclasses.replace(cfg, num_hidden_layers=args.layers, layer_types=cfg.layer_types[:args.layers])
+    import os
+    world, rank = int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1:                       # tensor-parallel trace: run under torch.distributed.run
+        import torch.distributed as dist
+        torch.cuda.set_device(local)
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     llm = LLM.from_random(cfg, seed=0, max_seq=args.prompt + 64, max_num_seqs=max(1, args.rows),
-                          max_chunk=min(args.prompt, 2048), quant=args.quant)
+                          max_chunk=min(args.prompt, 2048), quant=args.quant, tp_world=world, tp_rank=rank,
+                          device=f"cuda:{local}")
     g = torch.Generator().manual_seed(0)
     prompt = torch.randint(0, cfg.vocab_size, (args.prompt,), generator=g).cuda()
     first = llm.device_prefill(prompt)
@@ -140,6 +149,19 @@ def main() -> None:
     for _ in range(3):
         m.decode(M, graph=True)
     rows, step_us, prev_us = trace_decode(m, M)
+    if world > 1:
+        from ..parallel.control import shutdown
+        import torch.distributed as dist
+        dist.barrier()
+    if rank == 0:
+        _report(rows, step_us, prev_us, args)
+    if world > 1:
+        m._graphs.clear()
+        m.tp.close()
+        shutdown(timeout_s=10.0)
+
+
+def _report(rows, step_us, prev_us, args) -> None:
     print(f"decode step (first ready -> last ready): {step_us:.1f} us; replay period {prev_us:.1f} us; {len(rows)} kernels")
     agg = collections.OrderedDict()
     for name, lead, span in rows:

@@ -52,7 +52,14 @@ def _rank_main(rank, world, port, out):
     dist.barrier()
     if rank == 0:
         torch.save(logits, out)
-    dist.destroy_process_group()
+    from coffin_b200.parallel.control import shutdown
+    comm = getattr(model, "tp", None)
+    if hasattr(model, "_graphs"):
+        model._graphs.clear()
+    if comm is not None:
+        comm.close()
+    print("teardown finished" if shutdown(timeout_s=10.0, hard_exit=False) else "teardown did not finish: leaving", flush=True)
+    os._exit(0)
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
