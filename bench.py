@@ -105,6 +105,7 @@ def main() -> None:
     ap.add_argument("--no-pdl", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--mma-ctas", type=int, default=0, help="tuning: tensor-core GEMV CTAs per SM")
+    ap.add_argument("--gdn-tc", type=int, default=-1, help="tuning: 0 = fp32 SIMT delta-net chunk kernels, 1 = tensor-core (default)")
     ap.add_argument("--mma-stage", type=int, default=-1, help="tuning: GEMV weight batches per warp staged in shared memory before the wait")
     ap.add_argument("--mma-kcta", type=int, default=0, help="tuning: max CTAs sharing one 16-row GEMV block (1 = off)")
     ap.add_argument("--mma-prefetch", type=int, default=-1, help="tuning: GEMV sweep rounds prefetched into L2 before the dependency wait")
@@ -136,6 +137,9 @@ def main() -> None:
         K.STREAM_GEMV = False
     if args.gemv_impl:
         K.GEMV_IMPL = args.gemv_impl
+    if args.gdn_tc >= 0:
+        from coffin_b200.ops import _lib as _l5
+        _l5.call_nostream("set_gdn_tc", args.gdn_tc)
     if args.mma_stage >= 0:
         from coffin_b200.ops import _lib as _l4
         _l4.call_nostream("set_mma_gemv_stage", args.mma_stage)

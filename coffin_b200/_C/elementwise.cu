@@ -321,7 +321,7 @@ CB_EXPORT int cb_rmsnorm(const void* x, const void* add, const void* gain, void*
   if (N % 8 || N * 4 > 200 * 1024) return CB_ERR_SHAPE;
   if (M == 0) return 0;
   const size_t smem = (size_t)N * 4;
-  if (smem > 48 * 1024) {
+  if (smem + 2048 > 48 * 1024) {   // the 48 KB default also has to hold the static shared memory
     cudaError_t e = cudaFuncSetAttribute(rmsnorm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
   }
@@ -336,7 +336,7 @@ CB_EXPORT int cb_layernorm(const void* x, const void* w, const void* b, void* ou
   if (M == 0) return 0;
   if (N * 4 > 200 * 1024) return CB_ERR_SHAPE;
   const size_t smem = (size_t)N * 4;
-  if (smem > 48 * 1024) {
+  if (smem + 2048 > 48 * 1024) {   // the 48 KB default also has to hold the static shared memory
     cudaError_t e = cudaFuncSetAttribute(layernorm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
   }

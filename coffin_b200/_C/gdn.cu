@@ -520,6 +520,369 @@ __global__ void __launch_bounds__(256) gdn_chunk_scan_kernel(const GdnScanArgs a
   for (int idx = tid; idx < DK * DVS; idx += 256) sp[(int64_t)(idx / DVS) * DV + idx % DVS] = S[(idx / DVS) * LDS + idx % DVS];
 }
 
+// ---------------------------------------------------------------------------------------------
+// Tensor-core versions of the two chunk kernels.  The products are small (64x64x128, 64x128x32)
+// but there are eight of them per (chunk, head); as fp32 SIMT loops they made the delta-net layers
+// the largest part of a prefill.  Operands stay fp32 in shared memory and go to the tensor cores as
+// TF32 (mma.m16n8k8, fp32 accumulate): no conversion pass, and the state itself is never rounded -
+// only its copy that enters a product.  Leading dimensions are chosen so that fragment loads are
+// bank-conflict free: an operand read "row = g, k = t" wants ld = 4 (mod 32), one read "k = t,
+// column = g" wants ld = 8 (mod 32).
+__device__ __forceinline__ void mma_tf32(float* c, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+// A fragment of rows r0+g / r0+g+8, columns k0+t / k0+t+4 of a row-major matrix
+__device__ __forceinline__ void frag_a(const float* M, int ld, int r0, int k0, int g, int t, uint32_t* a) {
+  const float* p = M + (r0 + g) * ld + k0 + t;
+  a[0] = __float_as_uint(p[0]);
+  a[1] = __float_as_uint(p[8 * ld]);
+  a[2] = __float_as_uint(p[4]);
+  a[3] = __float_as_uint(p[8 * ld + 4]);
+}
+// A fragment of the transpose: element (row, k) = M[k][row]
+__device__ __forceinline__ void frag_at(const float* M, int ld, int r0, int k0, int g, int t, uint32_t* a) {
+  const float* p = M + (k0 + t) * ld + r0 + g;
+  a[0] = __float_as_uint(p[0]);
+  a[1] = __float_as_uint(p[8]);
+  a[2] = __float_as_uint(p[4 * ld]);
+  a[3] = __float_as_uint(p[4 * ld + 8]);
+}
+// B fragment (k = k0+t / k0+t+4, column c0+g) of a row-major [K][N] matrix
+__device__ __forceinline__ void frag_b(const float* M, int ld, int k0, int c0, int g, int t, uint32_t* b) {
+  const float* p = M + (k0 + t) * ld + c0 + g;
+  b[0] = __float_as_uint(p[0]);
+  b[1] = __float_as_uint(p[4 * ld]);
+}
+// B fragment of the transpose: element (k, column) = M[column][k]
+__device__ __forceinline__ void frag_bt(const float* M, int ld, int k0, int c0, int g, int t, uint32_t* b) {
+  const float* p = M + (c0 + g) * ld + k0 + t;
+  b[0] = __float_as_uint(p[0]);
+  b[1] = __float_as_uint(p[4]);
+}
+
+template <int DK, int DV>
+struct PrepTcLayout {
+  static constexpr int L = kChunk, LDA = DK + 4, LDB = DK + 8, LDV = DV + 8, LDL = L + 4;
+  // Ks, Qs [L][LDA] (row operands), Kb [L][LDB] (beta e^c K as a k-major operand), Vs [L][LDV], Tm, Wi [L][LDL], cs, bs [L]
+  static constexpr size_t floats = (size_t)2 * L * LDA + (size_t)L * LDB + (size_t)L * LDV + (size_t)2 * L * LDL + 2 * L;
+};
+
+template <int DK, int DV>
+__global__ void __launch_bounds__(256) gdn_chunk_prepare_tc_kernel(const GdnChunkArgs a) {
+  using Lay = PrepTcLayout<DK, DV>;
+  constexpr int L = kChunk, LDA = Lay::LDA, LDB = Lay::LDB, LDV = Lay::LDV, LDL = Lay::LDL;
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  float* Ks = reinterpret_cast<float*>(smem_raw);
+  float* Qs = Ks + L * LDA;
+  float* Kb = Qs + L * LDA;
+  float* Vs = Kb + L * LDB;
+  float* Tm = Vs + L * LDV;
+  float* Wi = Tm + L * LDL;
+  float* cs = Wi + L * LDL;
+  float* bs = cs + L;
+  griddep_launch();
+  griddep_wait();
+  const int n = blockIdx.x, h = blockIdx.y, kh = h / a.rep, tid = threadIdx.x;
+  const int lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
+  const int64_t t0 = (int64_t)n * L;
+  const float* kp = a.kn + ((int64_t)kh * a.Tp + t0) * DK;
+  const float* qp = a.qn + ((int64_t)kh * a.Tp + t0) * DK;
+  const float* vp = a.v + ((int64_t)h * a.Tp + t0) * DV;
+  for (int idx = tid; idx < L * DK / 4; idx += 256) {
+    const int i = idx / (DK / 4), c = (idx % (DK / 4)) * 4;
+    *reinterpret_cast<float4*>(Ks + i * LDA + c) = *reinterpret_cast<const float4*>(kp + (int64_t)i * DK + c);
+    *reinterpret_cast<float4*>(Qs + i * LDA + c) = *reinterpret_cast<const float4*>(qp + (int64_t)i * DK + c);
+  }
+  for (int idx = tid; idx < L * DV / 4; idx += 256) {
+    const int i = idx / (DV / 4), c = (idx % (DV / 4)) * 4;
+    *reinterpret_cast<float4*>(Vs + i * LDV + c) = *reinterpret_cast<const float4*>(vp + (int64_t)i * DV + c);
+  }
+  if (tid < 32) {  // inclusive scan of g over the 64 rows
+    const float g0 = a.g[(int64_t)h * a.Tp + t0 + tid], g1 = a.g[(int64_t)h * a.Tp + t0 + 32 + tid];
+    float x0 = g0, x1 = g1;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const float y0 = __shfl_up_sync(0xffffffffu, x0, o), y1 = __shfl_up_sync(0xffffffffu, x1, o);
+      if (tid >= o) { x0 += y0; x1 += y1; }
+    }
+    const float tot0 = __shfl_sync(0xffffffffu, x0, 31);
+    cs[tid] = x0;
+    cs[32 + tid] = x1 + tot0;
+    bs[tid] = a.beta[(int64_t)h * a.Tp + t0 + tid];
+    bs[32 + tid] = a.beta[(int64_t)h * a.Tp + t0 + 32 + tid];
+  }
+  __syncthreads();
+  // ---- K K^T and Q K^T: warp (row tile of 16) x (column half of 32) ----------------------------
+  {
+    const int r0 = (warp & 3) * 16, c0 = (warp >> 2) * 32;
+    float kk[4][4] = {}, qk[4][4] = {};
+    for (int k0 = 0; k0 < DK; k0 += 8) {
+      uint32_t ak[4], aq[4];
+      frag_a(Ks, LDA, r0, k0, g, t, ak);
+      frag_a(Qs, LDA, r0, k0, g, t, aq);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        uint32_t b[2];
+        frag_bt(Ks, LDA, k0, c0 + j * 8, g, t, b);
+        mma_tf32(kk[j], ak[0], ak[1], ak[2], ak[3], b[0], b[1]);
+        mma_tf32(qk[j], aq[0], aq[1], aq[2], aq[3], b[0], b[1]);
+      }
+    }
+    float* icap = a.ica + ((int64_t)h * a.nc + n) * L * L;
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int i = r0 + g + ((e & 2) ? 8 : 0), jj = c0 + j * 8 + 2 * t + (e & 1);
+        const float dec = (jj <= i) ? __expf(cs[i] - cs[jj]) : 0.f;
+        Tm[i * LDL + jj] = (jj < i) ? bs[i] * dec * kk[j][e] : 0.f;
+        icap[i * L + jj] = dec * qk[j][e];
+      }
+  }
+  __syncthreads();
+  // ---- W = (I + Tm)^-1, blocked: the four 16x16 diagonal blocks are inverted by forward
+  // substitution (one warp each, one column per lane, 16 dependent rows instead of 64), then the
+  // blocks below the diagonal follow level by level from  W_ij = -W_ii (sum_{k=j..i-1} T_ik W_kj).
+  __syncthreads();                                   // Tm complete (written by its fragment owners)
+  for (int idx = tid; idx < L * L; idx += 256) Wi[(idx / L) * LDL + idx % L] = 0.f;
+  __syncthreads();
+  if (warp < 4 && lane < 16) {
+    const int b0 = warp * 16, c = lane;
+    for (int i = 0; i < 16; ++i) {
+      float acc = (i == c) ? 1.f : 0.f;
+      for (int jj = c; jj < i; ++jj) acc -= Tm[(b0 + i) * LDL + b0 + jj] * Wi[(b0 + jj) * LDL + b0 + c];
+      if (i >= c) Wi[(b0 + i) * LDL + b0 + c] = acc;
+    }
+  }
+  __syncthreads();
+  {
+    float* P = Kb;                                    // scratch for the block sums: Kb is filled later
+    for (int d = 1; d < 4; ++d) {
+      const int npairs = 4 - d;
+      // P_p = sum_{k=j}^{i-1} T_ik W_kj for the pairs (i = j + d, j)
+      for (int idx = tid; idx < npairs * 256; idx += 256) {
+        const int pr = idx >> 8, r = (idx >> 4) & 15, c = idx & 15;
+        const int j = pr, i = pr + d;
+        float acc = 0.f;
+        for (int kk = j * 16; kk < i * 16; ++kk) acc += Tm[(i * 16 + r) * LDL + kk] * Wi[kk * LDL + j * 16 + c];
+        P[idx] = acc;
+      }
+      __syncthreads();
+      for (int idx = tid; idx < npairs * 256; idx += 256) {
+        const int pr = idx >> 8, r = (idx >> 4) & 15, c = idx & 15;
+        const int j = pr, i = pr + d;
+        float acc = 0.f;
+        for (int kk = 0; kk <= r; ++kk) acc += Wi[(i * 16 + r) * LDL + i * 16 + kk] * P[(pr << 8) + kk * 16 + c];
+        Wi[(i * 16 + r) * LDL + j * 16 + c] = -acc;
+      }
+      __syncthreads();
+    }
+  }
+  // ---- scaled copies for the scan; Kb <- beta e^c K, Vs <- beta V ------------------------------
+  {
+    float* qep = a.qe + ((int64_t)h * a.nc + n) * L * DK;
+    float* kep = a.ke + ((int64_t)h * a.nc + n) * L * DK;
+    const float cl = cs[L - 1];
+    for (int idx = tid; idx < L * DK; idx += 256) {
+      const int i = idx / DK, c = idx % DK;
+      const float ec = __expf(cs[i]);
+      const float kv = Ks[i * LDA + c];
+      qep[idx] = Qs[i * LDA + c] * ec;
+      kep[idx] = kv * __expf(cl - cs[i]);
+      Kb[i * LDB + c] = bs[i] * ec * kv;
+    }
+    for (int idx = tid; idx < L * DV; idx += 256) {
+      const int i = idx / DV, c = idx % DV;
+      Vs[i * LDV + c] *= bs[i];
+    }
+    if (tid == 0) a.ecl[(int64_t)h * a.nc + n] = __expf(cl);
+  }
+  __syncthreads();
+  // ---- nvv = W (beta V), kcd = W (beta e^c K): warp (row tile) x (V or K half); W is lower triangular ----
+  {
+    const int r0 = (warp & 3) * 16;
+    const bool isv = (warp >> 2) == 0;
+    const float* B = isv ? Vs : Kb;
+    const int ldb = isv ? LDV : LDB;
+    constexpr int NT = (DV > DK ? DV : DK) / 8;
+    const int nt = (isv ? DV : DK) / 8;
+    float acc[NT][4];
+#pragma unroll
+    for (int j = 0; j < NT; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+    for (int k0 = 0; k0 < r0 + 16; k0 += 8) {
+      uint32_t aw[4];
+      frag_a(Wi, LDL, r0, k0, g, t, aw);
+#pragma unroll
+      for (int j = 0; j < NT; ++j) {
+        if (j < nt) {
+          uint32_t b[2];
+          frag_b(B, ldb, k0, j * 8, g, t, b);
+          mma_tf32(acc[j], aw[0], aw[1], aw[2], aw[3], b[0], b[1]);
+        }
+      }
+    }
+    float* dst = isv ? a.nvv + ((int64_t)h * a.nc + n) * L * DV : a.kcd + ((int64_t)h * a.nc + n) * L * DK;
+    const int ldd = isv ? DV : DK;
+#pragma unroll
+    for (int j = 0; j < NT; ++j) {
+      if (j < nt) {
+        *reinterpret_cast<float2*>(dst + (r0 + g) * ldd + j * 8 + 2 * t) = make_float2(acc[j][0], acc[j][1]);
+        *reinterpret_cast<float2*>(dst + (r0 + g + 8) * ldd + j * 8 + 2 * t) = make_float2(acc[j][2], acc[j][3]);
+      }
+    }
+  }
+}
+
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
+  const uint32_t sa = (uint32_t)__cvta_generic_to_shared(smem);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(sa), "l"(gmem) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+
+template <int DK, int DVS>
+struct ScanTcLayout {
+  static constexpr int L = kChunk, LDS = DVS + 8, LDA = DK + 4, LDT = DK + 8, LDL = L + 4;
+  // S [DK][LDS], A1 = kcd [L][LDA], A2 = qe [L][LDA], A3 = ke [L][LDT] (read transposed), Ic [L][LDL], U [L][LDS]
+  static constexpr size_t floats = (size_t)DK * LDS + (size_t)2 * L * LDA + (size_t)L * LDT + (size_t)L * LDL + (size_t)L * LDS;
+};
+
+template <int DK, int DV, int DVS>
+__global__ void __launch_bounds__(256) gdn_chunk_scan_tc_kernel(const GdnScanArgs a) {
+  using Lay = ScanTcLayout<DK, DVS>;
+  constexpr int L = kChunk, LDS = Lay::LDS, LDA = Lay::LDA, LDT = Lay::LDT, LDL = Lay::LDL;
+  constexpr int NRT = DK / 16;                 // row tiles of the state
+  constexpr int CG = 8 / NRT;                  // column groups the 8 warps split the state update into
+  constexpr int NTS = (DVS / 8) / CG;          // n-tiles per warp in the state update
+  static_assert(DVS == 32 && (DK == 64 || DK == 128), "tiling");
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  float* S = reinterpret_cast<float*>(smem_raw);
+  float* A1 = S + DK * LDS;
+  float* A2 = A1 + L * LDA;
+  float* A3 = A2 + L * LDA;
+  float* Ic = A3 + L * LDT;
+  float* U = Ic + L * LDL;
+  griddep_launch();
+  griddep_wait();
+  const int h = blockIdx.x, sl = blockIdx.y, tid = threadIdx.x;
+  const int lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
+  const int col0 = sl * DVS;
+  float* sp = a.state + (int64_t)h * DK * DV + col0;
+  for (int idx = tid; idx < DK * DVS; idx += 256) S[(idx / DVS) * LDS + idx % DVS] = sp[(int64_t)(idx / DVS) * DV + idx % DVS];
+  const int r0 = (warp & 3) * 16, ch = (warp >> 2) * 16;          // U / O tile of this warp: 16 rows x 16 columns
+  const int s0 = (warp % NRT) * 16, sc0 = (warp / NRT) * (DVS / CG);   // state tile: 16 rows x NTS*8 columns
+  // Operand loads are asynchronous copies in two groups, so that they overlap the products: kcd and
+  // qe of chunk n+1 are fetched while chunk n runs its second half (they are free once U exists), ke
+  // and ica of chunk n while it runs its first half (the previous chunk's state update was their
+  // last reader).  Two barriers per chunk.
+  auto load_a12 = [&](int n) {
+    const int64_t base = (int64_t)h * a.nc + n;
+    for (int idx = tid; idx < L * DK / 4; idx += 256) {
+      const int i = idx / (DK / 4), c = (idx % (DK / 4)) * 4;
+      const int64_t off = base * L * DK + (int64_t)i * DK + c;
+      cp_async16(A1 + i * LDA + c, a.kcd + off);
+      cp_async16(A2 + i * LDA + c, a.qe + off);
+    }
+    cp_async_commit();
+  };
+  auto load_a3i = [&](int n) {
+    const int64_t base = (int64_t)h * a.nc + n;
+    for (int idx = tid; idx < L * DK / 4; idx += 256) {
+      const int i = idx / (DK / 4), c = (idx % (DK / 4)) * 4;
+      cp_async16(A3 + i * LDT + c, a.ke + base * L * DK + (int64_t)i * DK + c);
+    }
+    for (int idx = tid; idx < L * L / 4; idx += 256) {
+      const int i = idx / (L / 4), c = (idx % (L / 4)) * 4;
+      cp_async16(Ic + i * LDL + c, a.ica + base * L * L + (int64_t)i * L + c);
+    }
+    cp_async_commit();
+  };
+  load_a12(0);
+  for (int n = 0; n < a.nc; ++n) {
+    const int64_t base = (int64_t)h * a.nc + n;
+    cp_async_wait_all();
+    __syncthreads();          // kcd, qe of this chunk visible; every warp has left the previous chunk
+    load_a3i(n);
+    const float el = a.ecl[base];
+    float2 nv0[2], nv1[2];
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      const float* nvp = a.nvv + base * L * DV + col0 + ch + j * 8 + 2 * t;
+      nv0[j] = *reinterpret_cast<const float2*>(nvp + (int64_t)(r0 + g) * DV);
+      nv1[j] = *reinterpret_cast<const float2*>(nvp + (int64_t)(r0 + g + 8) * DV);
+    }
+    // ---- accU = kcd S, accO = qe S ------------------------------------------------------------
+    float accU[2][4] = {}, accO[2][4] = {};
+    for (int k0 = 0; k0 < DK; k0 += 8) {
+      uint32_t ak[4], aq[4];
+      frag_a(A1, LDA, r0, k0, g, t, ak);
+      frag_a(A2, LDA, r0, k0, g, t, aq);
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        uint32_t b[2];
+        frag_b(S, LDS, k0, ch + j * 8, g, t, b);
+        mma_tf32(accU[j], ak[0], ak[1], ak[2], ak[3], b[0], b[1]);
+        mma_tf32(accO[j], aq[0], aq[1], aq[2], aq[3], b[0], b[1]);
+      }
+    }
+    // ---- U = nvv - accU -> shared ---------------------------------------------------------------
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      *reinterpret_cast<float2*>(U + (r0 + g) * LDS + ch + j * 8 + 2 * t) = make_float2(nv0[j].x - accU[j][0], nv0[j].y - accU[j][1]);
+      *reinterpret_cast<float2*>(U + (r0 + g + 8) * LDS + ch + j * 8 + 2 * t) = make_float2(nv1[j].x - accU[j][2], nv1[j].y - accU[j][3]);
+    }
+    cp_async_wait_all();
+    __syncthreads();          // U, ke and ica visible; kcd and qe are free
+    if (n + 1 < a.nc) load_a12(n + 1);
+    // ---- O += ica U (ica is lower triangular: k <= row) -----------------------------------------
+    for (int k0 = 0; k0 < r0 + 16; k0 += 8) {
+      uint32_t ai[4];
+      frag_a(Ic, LDL, r0, k0, g, t, ai);
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        uint32_t b[2];
+        frag_b(U, LDS, k0, ch + j * 8, g, t, b);
+        mma_tf32(accO[j], ai[0], ai[1], ai[2], ai[3], b[0], b[1]);
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      const int64_t ta = (int64_t)n * L + r0 + g, tb = ta + 8;
+      float* op = a.out + (int64_t)h * DV + col0 + ch + j * 8 + 2 * t;
+      if (ta < a.T) *reinterpret_cast<float2*>(op + ta * a.nv * DV) = make_float2(accO[j][0], accO[j][1]);
+      if (tb < a.T) *reinterpret_cast<float2*>(op + tb * a.nv * DV) = make_float2(accO[j][2], accO[j][3]);
+    }
+    // ---- S <- ecl S + ke^T U: warp owns a 16-row tile of the state --------------------------------
+    float accS[NTS][4];
+#pragma unroll
+    for (int j = 0; j < NTS; ++j) {
+      const float2 x0 = *reinterpret_cast<const float2*>(S + (s0 + g) * LDS + sc0 + j * 8 + 2 * t);
+      const float2 x1 = *reinterpret_cast<const float2*>(S + (s0 + g + 8) * LDS + sc0 + j * 8 + 2 * t);
+      accS[j][0] = x0.x * el; accS[j][1] = x0.y * el; accS[j][2] = x1.x * el; accS[j][3] = x1.y * el;
+    }
+    for (int k0 = 0; k0 < L; k0 += 8) {
+      uint32_t at[4];
+      frag_at(A3, LDT, s0, k0, g, t, at);
+#pragma unroll
+      for (int j = 0; j < NTS; ++j) {
+        uint32_t b[2];
+        frag_b(U, LDS, k0, sc0 + j * 8, g, t, b);
+        mma_tf32(accS[j], at[0], at[1], at[2], at[3], b[0], b[1]);
+      }
+    }
+    // every warp has finished reading S for this chunk (the barrier after U); the tile is this warp's own
+#pragma unroll
+    for (int j = 0; j < NTS; ++j) {
+      *reinterpret_cast<float2*>(S + (s0 + g) * LDS + sc0 + j * 8 + 2 * t) = make_float2(accS[j][0], accS[j][1]);
+      *reinterpret_cast<float2*>(S + (s0 + g + 8) * LDS + sc0 + j * 8 + 2 * t) = make_float2(accS[j][2], accS[j][3]);
+    }
+  }
+  __syncthreads();
+  for (int idx = tid; idx < DK * DVS; idx += 256) sp[(int64_t)(idx / DVS) * DV + idx % DVS] = S[(idx / DVS) * LDS + idx % DVS];
+}
+
 // out[t, h*DV + j] = bf16( o * rsqrt(mean_j o^2 + eps) * w[j] * silu(z) ), one warp per (t, h)
 template <int DV>
 __global__ void gdn_gated_norm_kernel(const float* o, const bf16* z, int64_t ldz, const float* w, bf16* out,
@@ -553,9 +916,11 @@ size_t chunk_scan_smem() {
   return sizeof(float) * (size_t)(DK * (DVS + 4) + 2 * kChunk * (DK + 4) + kChunk * (kChunk + 4) + kChunk * (DVS + 4));
 }
 
+int g_gdn_tc = 1;    // chunk kernels on the tensor cores (TF32); 0 selects the fp32 SIMT versions
+
 template <typename K>
 int set_smem(K kern, size_t smem) {
-  if (smem > 48 * 1024) {
+  if (smem + 2048 > 48 * 1024) {   // the 48 KB default also has to hold the static shared memory
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
   }
@@ -583,6 +948,9 @@ CB_EXPORT int cb_gdn_decode(const void* proj, int64_t ldp, const void* conv_w, c
   if (dk == 64 && dv == 64) return (int)cb_launch(gdn_decode_kernel<64, 64>, grid, dim3(256), 0, (cudaStream_t)stream, a);
   return CB_ERR_SHAPE;
 }
+
+// 1: tensor-core (TF32) chunk kernels for prefill (default); 0: the fp32 SIMT versions.
+CB_EXPORT int cb_set_gdn_tc(int64_t on) { g_gdn_tc = on ? 1 : 0; return 0; }
 
 CB_EXPORT int cb_gdn_commit(void* state, const void* record, const void* slots, const void* steps,
                             int64_t rec_w, int64_t M, int64_t nv, int64_t dk, int64_t dv, void* stream) {
@@ -641,15 +1009,27 @@ CB_EXPORT int cb_gdn_prefill(const void* proj, int64_t ldp, const void* conv_w, 
     e = cb_launch(gdn_ring_update_kernel, dim3((unsigned)(T < kRing ? T : kRing)), dim3(256), 0, st,     \
                   (const bf16*)proj, ldp, (bf16*)ring_seq, (int)T, (int)pos0, conv_dim);                 \
     if (e != cudaSuccess) return (int)e;                                                                 \
-    size_t s1 = chunk_prepare_smem<DK_, DV_>();                                                          \
-    if ((rc = set_smem(gdn_chunk_prepare_kernel<DK_, DV_>, s1))) return rc;                              \
-    e = cb_launch(gdn_chunk_prepare_kernel<DK_, DV_>, dim3((unsigned)nc, (unsigned)nv), dim3(256), s1, st, ca); \
-    if (e != cudaSuccess) return (int)e;                                                                 \
-    size_t s2 = chunk_scan_smem<DK_, DVS_>();                                                            \
-    if ((rc = set_smem(gdn_chunk_scan_kernel<DK_, DV_, DVS_>, s2))) return rc;                           \
-    e = cb_launch(gdn_chunk_scan_kernel<DK_, DV_, DVS_>, dim3((unsigned)nv, (unsigned)(DV_ / DVS_)),      \
-                  dim3(256), s2, st, sa);                                                                \
-    if (e != cudaSuccess) return (int)e;                                                                 \
+    if (g_gdn_tc) {                                                                                      \
+      size_t s1 = sizeof(float) * PrepTcLayout<DK_, DV_>::floats;                                        \
+      if ((rc = set_smem(gdn_chunk_prepare_tc_kernel<DK_, DV_>, s1))) return rc;                         \
+      e = cb_launch(gdn_chunk_prepare_tc_kernel<DK_, DV_>, dim3((unsigned)nc, (unsigned)nv), dim3(256), s1, st, ca); \
+      if (e != cudaSuccess) return (int)e;                                                               \
+      size_t s2 = sizeof(float) * ScanTcLayout<DK_, DVS_>::floats;                                       \
+      if ((rc = set_smem(gdn_chunk_scan_tc_kernel<DK_, DV_, DVS_>, s2))) return rc;                      \
+      e = cb_launch(gdn_chunk_scan_tc_kernel<DK_, DV_, DVS_>, dim3((unsigned)nv, (unsigned)(DV_ / DVS_)), \
+                    dim3(256), s2, st, sa);                                                              \
+      if (e != cudaSuccess) return (int)e;                                                               \
+    } else {                                                                                             \
+      size_t s1 = chunk_prepare_smem<DK_, DV_>();                                                        \
+      if ((rc = set_smem(gdn_chunk_prepare_kernel<DK_, DV_>, s1))) return rc;                            \
+      e = cb_launch(gdn_chunk_prepare_kernel<DK_, DV_>, dim3((unsigned)nc, (unsigned)nv), dim3(256), s1, st, ca); \
+      if (e != cudaSuccess) return (int)e;                                                               \
+      size_t s2 = chunk_scan_smem<DK_, DVS_>();                                                          \
+      if ((rc = set_smem(gdn_chunk_scan_kernel<DK_, DV_, DVS_>, s2))) return rc;                         \
+      e = cb_launch(gdn_chunk_scan_kernel<DK_, DV_, DVS_>, dim3((unsigned)nv, (unsigned)(DV_ / DVS_)),    \
+                    dim3(256), s2, st, sa);                                                              \
+      if (e != cudaSuccess) return (int)e;                                                               \
+    }                                                                                                    \
     const int64_t tasks = T * nv;                                                                        \
     e = cb_launch(gdn_gated_norm_kernel<DV_>, dim3((unsigned)((tasks + 7) / 8)), dim3(256), 0, st,       \
                   (const float*)o, (const bf16*)proj + conv_dim, ldp, (const float*)norm_w, (bf16*)out,  \

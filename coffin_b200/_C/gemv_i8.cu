@@ -228,7 +228,7 @@ int launch_i8(I8Args a, cudaStream_t st) {
   if (ks > 1) smem += (size_t)a.rounds * kW * PB * 128 * sizeof(float);
   if (smem > 72 * 1024) return CB_ERR_SHAPE;
   auto kern = gemv_i8_kernel<SWIGLU, NORM, OUT_F32>;
-  if (smem > 48 * 1024) {
+  if (smem + 2048 > 48 * 1024) {   // the 48 KB default also has to hold the static shared memory
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
   }
@@ -289,7 +289,7 @@ CB_EXPORT int cb_quant_rows(const void* x, int64_t ldx, void* q, void* scale, in
   if (M == 0) return 0;
   if (K * 4 > 200 * 1024) return CB_ERR_SHAPE;
   const size_t smem = (size_t)K * 4;
-  if (smem > 48 * 1024) {
+  if (smem + 2048 > 48 * 1024) {   // the 48 KB default also has to hold the static shared memory
     cudaError_t e = cudaFuncSetAttribute(quant_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
   }

@@ -419,11 +419,17 @@ int launch_mma(MmaArgs a, cudaStream_t st, int n_slots = 1) {
     warps = ks;
     grid_x = nblk * kcta;
   } else {
-    const int64_t units = (nblk + kW - 1) / kW;                  // 8 blocks per CTA round
-    const int64_t cap = (int64_t)g_mma_sms * g_mma_ctas / n_slots;
+    // more 16-row blocks than one wave holds: 8-warp CTAs sweep in rounds.  The K split inside a CTA
+    // (ks warps per block, 8 / ks blocks per round) grows until there are enough units to occupy
+    // the CTAs that fit (few fit when many activation rows x a long K fill the shared memory).
+    stage_b = 0;
+    const int64_t cap = cta_slots(kW) > 0 ? cta_slots(kW) : 1;
+    ks = 1;
+    while (ks < kW && (nblk * ks + kW - 1) / kW < cap && npair / (ks * 2) >= 4) ks <<= 1;
+    const int64_t units = (nblk * ks + kW - 1) / kW;
     a.rounds = (int)((units + cap - 1) / cap);
-    grid_x = (units + a.rounds - 1) / a.rounds;
-    while (stage_b > 0 && (int64_t)(227 * 1024 / (xs_bytes + (size_t)kW * stage_b * 4096 + 1024)) < g_mma_ctas) --stage_b;
+    grid_x = (units + a.rounds - 1) / a.rounds;             // every CTA the same number of rounds ...
+    if (grid_x * 5 < cap * 4) grid_x = units < cap ? units : cap;   // ... unless that idles a fifth of the machine
   }
   a.stage_batches = stage_b;
   a.ksplit = ks;
@@ -436,10 +442,10 @@ int launch_mma(MmaArgs a, cudaStream_t st, int n_slots = 1) {
   a.pf_rounds = a.slot_expert ? 0 : (a.rounds < g_mma_pf_rounds ? a.rounds : g_mma_pf_rounds);
   size_t smem = (((size_t)a.M * a.K * 2 + 15) & ~(size_t)15);
   if (ks > 1) smem += (size_t)a.rounds * warps * PB * 128 * sizeof(float);
-  if (smem > 72 * 1024) return CB_ERR_SHAPE;
+  if (smem > 200 * 1024) return CB_ERR_SHAPE;
   smem += (size_t)warps * stage_b * 4096;
   auto kern = gemv_mma_kernel<SWIGLU, NORM, OUT_F32>;
-  if (smem > 48 * 1024) {
+  if (smem + 2048 > 48 * 1024) {   // the 48 KB default also has to hold the static shared memory
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
   }

@@ -272,7 +272,7 @@ int launch_w4(W4Args a, cudaStream_t st, int n_slots) {
   if (ks > 1) smem += (size_t)a.rounds * kW * PB * 128 * sizeof(float);
   if (smem > 96 * 1024) return CB_ERR_SHAPE;
   auto kern = gemv_w4_kernel<SWIGLU, NORM, OUT_F32>;
-  if (smem > 48 * 1024) {
+  if (smem + 2048 > 48 * 1024) {   // the 48 KB default also has to hold the static shared memory
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
   }

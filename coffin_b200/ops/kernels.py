@@ -159,7 +159,7 @@ def gemv(W: torch.Tensor, x: torch.Tensor | None, out: torch.Tensor | None, *, s
         res_in, add, gain, res_out, eps = norm
         assert res_in.is_contiguous() and res_in.shape == (M, K)
         x = None
-    if GEMV_IMPL == "mma" and M * K * 2 <= 64 * 1024:
+    if GEMV_IMPL == "mma" and M * K * 2 <= 160 * 1024:
         call("gemv_mma_bf16", W, x, out, M, N, K, ldy, mode, N, res_in, add, gain, res_out, float(eps), tpp,
              pull_site, push_site)
     elif M == 1 and STREAM_GEMV and K * 2 <= 28 * 1024:
