@@ -59,7 +59,8 @@ __global__ void __launch_bounds__(kThreadsGemm, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmArgs a) {
   constexpr int A_BYTES = BM * BK_BYTES, B_BYTES = BN * BK_BYTES, STAGE_BYTES = A_BYTES + B_BYTES;
   constexpr int ESIZE = I8 ? 1 : 2, BK = BK_BYTES / ESIZE, UK = 32 / ESIZE;  // elements per k-block / per MMA
-  constexpr uint32_t TMEM_COLS = 2 * BN;  // two accumulators (power of two >= 32)
+  // two accumulators; an allocation is a power of two >= 32 columns
+  constexpr uint32_t TMEM_COLS = 2 * BN <= 128 ? 128 : (2 * BN <= 256 ? 256 : 512);
   constexpr uint32_t IDESC = umma_idesc(BM, BN, 1, I8 ? 2 : 1);
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   unsigned char* tiles = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -226,17 +227,31 @@ int sm_count() {
   return g_sms;
 }
 
-// waves of `tiles` over `sms` SMs times the per-tile cost (proportional to BN)
+// Relative time of an [M, N] product with BN-wide tiles: waves of tiles over the SMs times the cost
+// of one tile.  A tile's cost is its width times a factor measured on B200 for K = 2560..9216: a
+// narrow tile re-reads the A tile from L2 for fewer flops and the loads, not the tensor pipe, set
+// its pace (128 x 256 tiles ran at 1.3 PFLOP/s machine-wide, 128 x 128 at 0.79).
 double tile_cost(int M, int N, int bn, int sms) {
   const int tiles = ((M + BM - 1) / BM) * ((N + bn - 1) / bn);
   const int waves = (tiles + sms - 1) / sms;
-  return (double)waves * bn;
+  const double f = bn >= 256 ? 1.0 : (bn >= 160 ? 1.3 : (bn >= 128 ? 1.7 : 2.5));
+  return (double)waves * bn * f;
+}
+int pick_bn(int M, int N, int sms, bool allow64) {
+  const int cand[4] = {256, 160, 128, 64};
+  int best = 256;
+  double bc = 1e300;
+  for (int i = 0; i < (allow64 ? 4 : 3); ++i) {
+    const double c = tile_cost(M, N, cand[i], sms);
+    if (c < bc) { bc = c; best = cand[i]; }
+  }
+  return best;
 }
 
 }  // namespace
 
 // C[M,N] (bf16) = A[M,K] (bf16) x W[N,K]^T (bf16) (+ residual[M,N]).  K % 8 == 0, N % 8 == 0.
-// bn_hint: 0 = choose, else 64/128/256.
+// bn_hint: 0 = choose, else 64/128/160/256.
 CB_EXPORT int cb_gemm_bf16(const void* A, int64_t lda, const void* W, int64_t ldw, void* C, int64_t ldc,
                            const void* residual, int64_t ldr, int64_t M, int64_t N, int64_t K,
                            int64_t bn_hint, const void* pf, int64_t pf_seq, void* status, void* stream) {
@@ -244,11 +259,7 @@ CB_EXPORT int cb_gemm_bf16(const void* A, int64_t lda, const void* W, int64_t ld
   if (K % 8 || N % 8 || (!pf && ldc % 8) || (residual && ldr % 8) || !status) return CB_ERR_SHAPE;
   const int sms = sm_count();
   int bn = (int)bn_hint;
-  if (!bn) {
-    const double c256 = tile_cost((int)M, (int)N, 256, sms), c128 = tile_cost((int)M, (int)N, 128, sms) * 1.08;
-    const double c64 = tile_cost((int)M, (int)N, 64, sms) * 1.35;
-    bn = c256 <= c128 && c256 <= c64 ? 256 : (c128 <= c64 ? 128 : 64);
-  }
+  if (!bn) bn = pick_bn((int)M, (int)N, sms, true);
   CUtensorMap tmA, tmB;
   int rc = cb_make_tmap_2d(&tmA, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, BM, 64);
   if (rc) return rc;
@@ -261,6 +272,7 @@ CB_EXPORT int cb_gemm_bf16(const void* A, int64_t lda, const void* W, int64_t ld
   a.pf = (const TpPfDev*)pf; a.pf_seq = (unsigned)pf_seq;
   cudaStream_t st = (cudaStream_t)stream;
   if (bn == 256) return launch_gemm<256, 4, false>(tmA, tmB, a, sms, st);
+  if (bn == 160) return launch_gemm<160, 5, false>(tmA, tmB, a, sms, st);
   if (bn == 128) return launch_gemm<128, 6, false>(tmA, tmB, a, sms, st);
   if (bn == 64) return launch_gemm<64, 8, false>(tmA, tmB, a, sms, st);
   return CB_ERR_ARG;
@@ -276,7 +288,7 @@ CB_EXPORT int cb_gemm_i8(const void* A, int64_t lda, const void* W, int64_t ldw,
     return CB_ERR_SHAPE;
   const int sms = sm_count();
   int bn = (int)bn_hint;
-  if (!bn) bn = tile_cost((int)M, (int)N, 256, sms) <= tile_cost((int)M, (int)N, 128, sms) * 1.08 ? 256 : 128;
+  if (!bn) bn = pick_bn((int)M, (int)N, sms, false);
   CUtensorMap tmA, tmB;
   int rc = cb_make_tmap_2d(&tmA, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, BM, 128);
   if (rc) return rc;
@@ -290,6 +302,7 @@ CB_EXPORT int cb_gemm_i8(const void* A, int64_t lda, const void* W, int64_t ldw,
   a.pf = (const TpPfDev*)pf; a.pf_seq = (unsigned)pf_seq;
   cudaStream_t st = (cudaStream_t)stream;
   if (bn == 256) return launch_gemm<256, 4, true>(tmA, tmB, a, sms, st);
+  if (bn == 160) return launch_gemm<160, 5, true>(tmA, tmB, a, sms, st);
   if (bn == 128) return launch_gemm<128, 6, true>(tmA, tmB, a, sms, st);
   return CB_ERR_ARG;
 }

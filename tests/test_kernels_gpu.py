@@ -95,7 +95,8 @@ def test_gemv_fused_norm_swiglu(M, H, I):
 
 
 @pytest.mark.parametrize("M,N,Kd,bn", [(128, 256, 64, 256), (200, 264, 192, 128), (300, 520, 1032, 0),
-                                       (64, 64, 256, 64), (1000, 1536, 512, 256), (130, 136, 72, 128)])
+                                       (64, 64, 256, 64), (1000, 1536, 512, 256), (130, 136, 72, 128),
+                                       (300, 520, 1032, 160), (2048, 2560, 1024, 0)])
 def test_gemm_tcgen05(M, N, Kd, bn):
     k = K()
     A, W = bf(M, Kd, seed=10), bf(N, Kd, s=0.05, seed=11)
@@ -110,7 +111,8 @@ def test_gemm_tcgen05(M, N, Kd, bn):
     close(out, A.float() @ W.float().t() + res.float())
 
 
-@pytest.mark.parametrize("M,N,Kd,bn", [(128, 256, 128, 256), (200, 264, 400, 128), (77, 520, 1040, 0)])
+@pytest.mark.parametrize("M,N,Kd,bn", [(128, 256, 128, 256), (200, 264, 400, 128), (77, 520, 1040, 0),
+                                       (300, 488, 528, 160)])
 def test_gemm_i8_tcgen05(M, N, Kd, bn):
     k = K()
     g = torch.Generator().manual_seed(13)
