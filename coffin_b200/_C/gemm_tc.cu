@@ -35,7 +35,28 @@ struct GemmArgs {
   // tensor-parallel prefill: instead of C, every output row goes (bf16) to the inbox of the rank
   // that owns it, and the last CTA publishes the sequence number (see tp.cuh)
   const TpPfDev* pf; unsigned pf_seq;
+  // grouped (expert-major) mode: the m-tile list lives in device memory, written by the dispatch
+  // kernel of the same step.  Tile i covers rows [g_row0[i], g_row0[i] + g_rows[i]) of A and C and
+  // multiplies them by expert g_expert[i]'s [N, K] block of the weight stack.
+  const int* g_count; const int* g_row0; const int* g_rows; const int* g_expert;
 };
+struct TileCoord { int m0, row_end, n0, brow; };
+template <int BN>
+__device__ __forceinline__ TileCoord tile_coord(const GemmArgs& a, int tile, int m_tiles) {
+  const int mt = tile % m_tiles, nt = tile / m_tiles;
+  TileCoord c;
+  c.n0 = nt * BN;
+  if (a.g_count) {
+    c.m0 = a.g_row0[mt];
+    c.row_end = c.m0 + a.g_rows[mt];
+    c.brow = a.g_expert[mt] * a.N + c.n0;
+  } else {
+    c.m0 = mt * BM;
+    c.row_end = a.M;
+    c.brow = c.n0;
+  }
+  return c;
+}
 
 __device__ __forceinline__ uint64_t gtime_ns() {
   uint64_t t;
@@ -89,21 +110,23 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   griddep_launch();
   griddep_wait();
 
-  const int total = a.m_tiles * a.n_tiles;
+  int m_tiles = a.m_tiles;
+  if (a.g_count) { m_tiles = *a.g_count; if (m_tiles > a.m_tiles) m_tiles = a.m_tiles; }   // a.m_tiles: list capacity
+  const int total = m_tiles * a.n_tiles;
   if (warp == 0) {
     // ------------------------------- TMA producer -----------------------------------------
     if (lane == 0) {
       uint32_t it = 0;
       for (int tile = blockIdx.x; tile < total && !*abort_flag; tile += gridDim.x) {
-        const int m0 = (tile % a.m_tiles) * BM, n0 = (tile / a.m_tiles) * BN;
+        const TileCoord tc = tile_coord<BN>(a, tile, m_tiles);
         for (int kb = 0; kb < a.k_blocks; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
           if (!wait_bar(&empty_bar[s], ph ^ 1, abort_flag)) { atomicExch(a.status, 1); abort_s = 1; break; }
           mbar_expect_tx(&full_bar[s], STAGE_BYTES);
           unsigned char* st = tiles + (size_t)s * STAGE_BYTES;
-          tma_load_2d(st, &tmA, &full_bar[s], kb * BK, m0);
-          tma_load_2d(st + A_BYTES, &tmB, &full_bar[s], kb * BK, n0);
+          tma_load_2d(st, &tmA, &full_bar[s], kb * BK, tc.m0);
+          tma_load_2d(st + A_BYTES, &tmB, &full_bar[s], kb * BK, tc.brow);
         }
       }
     }
@@ -141,19 +164,20 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     const int q = warp & 3;  // TMEM lane quadrant this warp may read
     uint32_t tcount = 0;
     for (int tile = blockIdx.x; tile < total && !*abort_flag; tile += gridDim.x, ++tcount) {
-      const int m0 = (tile % a.m_tiles) * BM, n0 = (tile / a.m_tiles) * BN;
+      const TileCoord tc = tile_coord<BN>(a, tile, m_tiles);
+      const int m0 = tc.m0, n0 = tc.n0, row_end = tc.row_end;
       const uint32_t acc = tcount & 1, aph = (tcount >> 1) & 1;
       if (!wait_bar(&acc_full[acc], aph, abort_flag)) { if (lane == 0) { atomicExch(a.status, 4); abort_s = 1; } break; }
       tc_fence_after();
       const int row = m0 + q * 32 + lane;
-      const float rs = (I8 && row < a.M) ? a.row_scale[row] : 1.f;
+      const float rs = (I8 && row < row_end) ? a.row_scale[row] : 1.f;
 #pragma unroll 1
       for (int c0 = 0; c0 < BN; c0 += 32) {
         uint32_t r[32];
         tmem_ld32(tmem_base + acc * BN + ((uint32_t)(q * 32) << 16) + c0, r);
         tmem_ld_wait();
         const int col0 = n0 + c0;
-        if (row < a.M && col0 < a.N) {
+        if (row < row_end && col0 < a.N) {
           bf16* cp;
           if (a.pf) {
             const int rpr = a.pf->rows_per_rank;
@@ -270,6 +294,7 @@ CB_EXPORT int cb_gemm_bf16(const void* A, int64_t lda, const void* W, int64_t ld
   a.M = (int)M; a.N = (int)N; a.K = (int)K; a.m_tiles = (int)((M + BM - 1) / BM); a.n_tiles = 0;
   a.k_blocks = (int)((K + 63) / 64); a.status = (int*)status;
   a.pf = (const TpPfDev*)pf; a.pf_seq = (unsigned)pf_seq;
+  a.g_count = a.g_row0 = a.g_rows = a.g_expert = nullptr;
   cudaStream_t st = (cudaStream_t)stream;
   if (bn == 256) return launch_gemm<256, 4, false>(tmA, tmB, a, sms, st);
   if (bn == 160) return launch_gemm<160, 5, false>(tmA, tmB, a, sms, st);
@@ -300,9 +325,40 @@ CB_EXPORT int cb_gemm_i8(const void* A, int64_t lda, const void* W, int64_t ldw,
   a.M = (int)M; a.N = (int)N; a.K = (int)K; a.m_tiles = (int)((M + BM - 1) / BM); a.n_tiles = 0;
   a.k_blocks = (int)((K + 127) / 128); a.status = (int*)status;
   a.pf = (const TpPfDev*)pf; a.pf_seq = (unsigned)pf_seq;
+  a.g_count = a.g_row0 = a.g_rows = a.g_expert = nullptr;
   cudaStream_t st = (cudaStream_t)stream;
   if (bn == 256) return launch_gemm<256, 4, true>(tmA, tmB, a, sms, st);
   if (bn == 160) return launch_gemm<160, 5, true>(tmA, tmB, a, sms, st);
   if (bn == 128) return launch_gemm<128, 6, true>(tmA, tmB, a, sms, st);
   return CB_ERR_ARG;
+}
+
+// Grouped (expert-major) product for routed-MoE prefill: rows of A sorted by expert, W a stack
+// [E, N, K]; C[r, :] = A[r, :] x W[expert(r)]^T for the rows the tile list covers.  The list
+// (g_count m-tiles of at most 128 rows, never crossing an expert boundary) is produced on the device
+// by cb_moe_dispatch, so no count travels to the host; max_tiles bounds it and sizes the grid.
+// Replaces the reference's expert-major grouped GEMMs (kernels/w8a8_tcu.cu:962, moe_grouped_i8.cu:1283).
+CB_EXPORT int cb_gemm_bf16_grouped(const void* A, int64_t lda, const void* W, int64_t ldw, void* C, int64_t ldc,
+                                   int64_t rows, int64_t E, int64_t N, int64_t K, const void* g_count,
+                                   const void* g_row0, const void* g_rows, const void* g_expert, int64_t max_tiles,
+                                   void* status, void* stream) {
+  if (rows < 1 || N < 1 || K < 1 || E < 1 || max_tiles < 1) return CB_ERR_SHAPE;
+  if (K % 8 || N % 8 || ldc % 8 || !status || !g_count || !g_row0 || !g_rows || !g_expert) return CB_ERR_SHAPE;
+  const int sms = sm_count();
+  const int bn = N % 256 == 0 || N > 1024 ? 256 : (N % 160 == 0 ? 160 : 128);
+  CUtensorMap tmA, tmB;
+  int rc = cb_make_tmap_2d(&tmA, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, A, (uint64_t)rows, (uint64_t)K, (uint64_t)lda, BM, 64);
+  if (rc) return rc;
+  rc = cb_make_tmap_2d(&tmB, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, W, (uint64_t)(E * N), (uint64_t)K, (uint64_t)ldw, (uint32_t)bn, 64);
+  if (rc) return rc;
+  GemmArgs a;
+  a.C = C; a.ldc = ldc; a.residual = nullptr; a.ldr = 0; a.row_scale = nullptr; a.col_scale = nullptr;
+  a.M = (int)rows; a.N = (int)N; a.K = (int)K; a.m_tiles = (int)max_tiles; a.n_tiles = 0;
+  a.k_blocks = (int)((K + 63) / 64); a.status = (int*)status;
+  a.pf = nullptr; a.pf_seq = 0;
+  a.g_count = (const int*)g_count; a.g_row0 = (const int*)g_row0; a.g_rows = (const int*)g_rows; a.g_expert = (const int*)g_expert;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (bn == 256) return launch_gemm<256, 4, false>(tmA, tmB, a, sms, st);
+  if (bn == 160) return launch_gemm<160, 5, false>(tmA, tmB, a, sms, st);
+  return launch_gemm<128, 6, false>(tmA, tmB, a, sms, st);
 }

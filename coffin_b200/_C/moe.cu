@@ -71,7 +71,8 @@ __global__ void __launch_bounds__(256) moe_router_kernel(const float* __restrict
 // out[t, :] = sum_j w[t, j] * y[t * top_k + j, :]  (+ sigmoid(gate_logit[t]) * shared[t, :])
 __global__ void __launch_bounds__(256) moe_combine_kernel(const bf16* __restrict__ y, const float* __restrict__ w,
                                                            const bf16* __restrict__ shared, const float* __restrict__ gate_logit,
-                                                           int64_t ldg, bf16* __restrict__ out, int64_t H, int top_k, int push_site, const TpComm tp) {
+                                                           int64_t ldg, bf16* __restrict__ out, int64_t H, int top_k, int push_site, const TpComm tp,
+                                                           const int* __restrict__ pos) {
   griddep_launch();
   griddep_wait();
   const int64_t t = blockIdx.x;
@@ -79,10 +80,12 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const bf16* __restrict
   for (int64_t c = threadIdx.x; c < (H >> 3); c += blockDim.x) {
     float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
     for (int j = 0; j < top_k; ++j) {
-      float f[8];
-      bf16x8_to_float(*reinterpret_cast<const uint4*>(y + ((t * top_k + j) * H) + c * 8), f);
       const float wj = w[t * top_k + j];
       if (wj == 0.f) continue;                    // slot of another rank's expert (its row was never written)
+      const int64_t row = pos ? pos[t * top_k + j] : t * top_k + j;   // expert-sorted rows are found through pos
+      if (row < 0) continue;
+      float f[8];
+      bf16x8_to_float(*reinterpret_cast<const uint4*>(y + row * H + c * 8), f);
 #pragma unroll
       for (int i = 0; i < 8; ++i) acc[i] = fmaf(wj, f[i], acc[i]);
     }
@@ -100,6 +103,58 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const bf16* __restrict
     }
   }
   if (push_site >= 0) tp_push_done(tp, push_site, gridDim.x);
+}
+
+__global__ void __launch_bounds__(1024) moe_dispatch_kernel(const int* __restrict__ idx, int S, int top_k, int E,
+                                                            int* __restrict__ pos, int* __restrict__ src_tok,
+                                                            int* g_count, int* g_row0, int* g_rows, int* g_expert,
+                                                            int max_tiles) {
+  extern __shared__ int dsm[];
+  int* cnt = dsm;            // [E] slots per expert, then the running cursor of the scatter
+  int* off = dsm + E;        // [E + 1] first sorted row of every expert
+  int* total = dsm + 2 * E + 1;
+  griddep_launch();
+  griddep_wait();
+  const int tid = threadIdx.x;
+  for (int e = tid; e < E; e += 1024) cnt[e] = 0;
+  __syncthreads();
+  for (int s = tid; s < S; s += 1024) {
+    const int e = idx[s];
+    if (e >= 0 && e < E) atomicAdd(&cnt[e], 1);
+  }
+  __syncthreads();
+  if (tid == 0) {
+    int run = 0, nt = 0;
+    for (int e = 0; e < E; ++e) {
+      const int n = cnt[e];
+      off[e] = run;
+      for (int i = 0; i < n; i += 128, ++nt) {
+        if (nt < max_tiles) {
+          g_row0[nt] = run + i;
+          g_rows[nt] = min(128, n - i);
+          g_expert[nt] = e;
+        }
+      }
+      run += n;
+    }
+    off[E] = run;
+    *total = run;
+    *g_count = min(nt, max_tiles);
+  }
+  __syncthreads();
+  for (int e = tid; e < E; e += 1024) cnt[e] = off[e];
+  for (int r = *total + tid; r < S; r += 1024) src_tok[r] = 0;
+  __syncthreads();
+  for (int s = tid; s < S; s += 1024) {
+    const int e = idx[s];
+    if (e >= 0 && e < E) {
+      const int r = atomicAdd(&cnt[e], 1);
+      pos[s] = r;
+      src_tok[r] = s / top_k;
+    } else {
+      pos[s] = -1;
+    }
+  }
 }
 
 }  // namespace
@@ -121,5 +176,33 @@ CB_EXPORT int cb_moe_combine(const void* y, const void* w, const void* shared, c
   if (tp) c = *(const TpComm*)tp; else memset(&c, 0, sizeof(c));
   return (int)cb_launch(moe_combine_kernel, dim3((unsigned)T), dim3(256), 0, (cudaStream_t)stream, (const bf16*)y,
                         (const float*)w, (const bf16*)shared, (const float*)gate_logit, ldg, (bf16*)out, H, (int)top_k,
-                        (int)push_site, c);
+                        (int)push_site, c, (const int*)nullptr);
+}
+
+// The same merge for expert-sorted rows: slot (t, j)'s row of y is pos[t * top_k + j] (< 0: none).
+CB_EXPORT int cb_moe_combine_pos(const void* y, const void* w, const void* pos, const void* shared, const void* gate_logit,
+                                 int64_t ldg, void* out, int64_t T, int64_t H, int64_t top_k, void* stream) {
+  if (T == 0) return 0;
+  if (H % 8 || !pos) return CB_ERR_SHAPE;
+  TpComm c;
+  memset(&c, 0, sizeof(c));
+  return (int)cb_launch(moe_combine_kernel, dim3((unsigned)T), dim3(256), 0, (cudaStream_t)stream, (const bf16*)y,
+                        (const float*)w, (const bf16*)shared, (const float*)gate_logit, ldg, (bf16*)out, H, (int)top_k,
+                        -1, c, (const int*)pos);
+}
+
+// Expert-major dispatch of S = T * top_k routed slots, one CTA: count per expert, prefix, scatter.
+//   pos[s]      row of slot s in the expert-sorted order, -1 for a slot whose expert is not local
+//   src_tok[r]  token whose activation row goes to sorted row r (0 for the unused rows at the end)
+//   tile list   m-tiles of at most 128 rows that never cross an expert boundary (g_count of them)
+// Rows of one expert are adjacent but in no fixed order among themselves: every output row depends
+// on its own input row only, so the result does not depend on that order.
+// Replaces the reference's moe_dispatch (kernels/moe_dispatch.cu:101, count -> prefix -> scatter).
+CB_EXPORT int cb_moe_dispatch(const void* idx, int64_t S, int64_t top_k, int64_t E, void* pos, void* src_tok,
+                              void* g_count, void* g_row0, void* g_rows, void* g_expert, int64_t max_tiles,
+                              void* stream) {
+  if (S < 1 || E < 1 || E > 1024 || top_k < 1 || max_tiles < 1) return CB_ERR_SHAPE;
+  return (int)cb_launch(moe_dispatch_kernel, dim3(1), dim3(1024), (size_t)(2 * E + 2) * sizeof(int), (cudaStream_t)stream,
+                        (const int*)idx, (int)S, (int)top_k, (int)E, (int*)pos, (int*)src_tok, (int*)g_count,
+                        (int*)g_row0, (int*)g_rows, (int*)g_expert, (int)max_tiles);
 }

@@ -97,6 +97,13 @@ class MoEWeights:
         """bf16 ``[rows, K]`` weights of local expert ``e`` (expanded from W4 storage for a prefill GEMM)."""
         return stack[e] if isinstance(stack, torch.Tensor) else K.w4_dequant(stack.wq[e], stack.scale[e])
 
+    def _stack(self, stack) -> torch.Tensor:
+        """bf16 ``[E, rows, K]`` weights of all local experts (W4 storage is expanded for the call)."""
+        if isinstance(stack, torch.Tensor):
+            return stack
+        E, N, half = stack.wq.shape
+        return K.w4_dequant(stack.wq.reshape(E * N, half), stack.scale.reshape(E * N, -1)).reshape(E, N, half * 2)
+
     # ------------------------------------------------------------------ buffers
     def _b(self, T: int, dev) -> dict:
         b = self.bufs.get(T)
@@ -166,8 +173,8 @@ class MoEWeights:
 
     def apply(self, normed: torch.Tensor, model=None) -> torch.Tensor:
         """``moe(normed)`` for ``T`` rows (a new ``[T, H]`` tensor).  Small row counts reuse the decode
-        kernels (every slot streams its expert once); larger ones sort the slots by expert and run one
-        tcgen05 GEMM pair per expert that received tokens.  ``model`` supplies the all-reduce under
+        kernels (every slot streams its expert once); larger ones sort the slots by expert on the
+        device and run two grouped tcgen05 GEMMs over the sorted rows.  ``model`` supplies the all-reduce under
         expert parallelism."""
         c = self.cfg
         T = normed.shape[0]
@@ -186,40 +193,20 @@ class MoEWeights:
         K.call("moe_router", logits, logits.stride(0), T, E, k, int(c.norm_topk_prob), idx, w, self.e_lo, self.e_hi)
         K._count()
         n_local = self.e_hi - self.e_lo
-        flat = idx.reshape(-1).long()
-        flat = torch.where(flat < 0, torch.full_like(flat, n_local), flat)    # other ranks' slots sort last
-        order = torch.argsort(flat, stable=True)                          # slots grouped by expert
-        counts = torch.bincount(flat, minlength=n_local + 1).tolist()[:n_local]
-        tok_of = (order // k)
-        xs = normed[tok_of]                                               # gathered activations [T*k, H]
-        ys = torch.zeros(T * k, H, dtype=torch.bfloat16, device=normed.device)
-        s = 0
-        for e, n in enumerate(counts):
-            if n == 0:
-                continue
-            seg = xs[s:s + n]
-            if n <= 8 and self.w4:
-                inter = torch.empty(n, I, dtype=torch.bfloat16, device=normed.device)
-                K.gemv_w4(self.gate_up.wq[e], self.gate_up.scale[e], seg.contiguous(), inter, swiglu=True)
-                K.gemv_w4(self.down.wq[e], self.down.scale[e], inter, ys[s:s + n])
-            elif n <= 8:
-                inter = torch.empty(n, I, dtype=torch.bfloat16, device=normed.device)
-                K.gemv(self.gate_up[e], seg.contiguous(), inter, swiglu=True)
-                K.gemv(self.down[e], inter, ys[s:s + n])
-            else:
-                gu = K.gemm(seg, self._expert(self.gate_up, e))
-                inter = K.swiglu(gu)
-                K.gemm(inter, self._expert(self.down, e), out=ys[s:s + n])
-            s += n
-        y = torch.empty_like(ys)
-        y[order] = ys                                                     # back to (token, slot) order
+        # device-side dispatch (count -> prefix -> scatter), then one grouped tcgen05 GEMM per
+        # projection over the expert-sorted rows; nothing is read back to the host
+        disp = K.moe_dispatch(idx, n_local)
+        xs = normed.index_select(0, disp["src_tok"])                      # gathered activations [T*k, H]
+        gu = K.gemm_grouped(xs, self._stack(self.gate_up), disp)
+        inter = K.swiglu(gu)
+        y = K.gemm_grouped(inter, self._stack(self.down), disp)
         shared = gate = None
         if self.sh_gu is not None:
             sh = K.swiglu(K.gemm(normed, self.sh_gu))
             shared = K.gemm(sh, self.sh_down)
             gate = logits[:, E:].contiguous()
         out = torch.empty(T, H, dtype=torch.bfloat16, device=normed.device)
-        K.call("moe_combine", y, w, shared, gate, gate.stride(0) if gate is not None else 0, out, T, H, k, None, -1)
+        K.call("moe_combine_pos", y, w, disp["pos"], shared, gate, gate.stride(0) if gate is not None else 0, out, T, H, k)
         K._count()
         if self.ep_world > 1:
             out = model._tp_reduce(out)

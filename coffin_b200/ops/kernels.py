@@ -239,6 +239,40 @@ def w4_dequant(Wq: torch.Tensor, wscale: torch.Tensor, out: torch.Tensor | None 
     return out
 
 
+def moe_dispatch(idx: torch.Tensor, n_experts: int) -> dict:
+    """Expert-major order of the routed slots ``idx [T, k]`` (local expert id, or < 0 for a slot of
+    another rank), computed on the device: ``pos [T*k]`` (sorted row of a slot, -1 = none),
+    ``src_tok [T*k]`` (token feeding sorted row r) and the m-tile list consumed by
+    :func:`gemm_grouped`.  No count is read back to the host."""
+    T, k = idx.shape
+    S = T * k
+    dev = idx.device
+    max_tiles = (S + 127) // 128 + n_experts
+    meta = torch.empty(1 + 3 * max_tiles, dtype=torch.int32, device=dev)
+    d = {"pos": torch.empty(S, dtype=torch.int32, device=dev),
+         "src_tok": torch.empty(S, dtype=torch.int32, device=dev),
+         "count": meta[:1], "row0": meta[1:1 + max_tiles], "rows": meta[1 + max_tiles:1 + 2 * max_tiles],
+         "expert": meta[1 + 2 * max_tiles:], "max_tiles": max_tiles, "meta": meta}
+    call("moe_dispatch", idx, S, k, n_experts, d["pos"], d["src_tok"], d["count"], d["row0"], d["rows"], d["expert"],
+         max_tiles)
+    _count()
+    return d
+
+
+def gemm_grouped(A: torch.Tensor, W: torch.Tensor, disp: dict, out: torch.Tensor | None = None) -> torch.Tensor:
+    """``out[r] = A[r] @ W[expert(r)].T`` for expert-sorted rows ``A [S, K]`` and a weight stack
+    ``W [E, N, K]`` (bf16), tiles taken from ``disp`` (:func:`moe_dispatch`).  Rows outside the tile
+    list (slots of other ranks) are left untouched."""
+    S, Kd = A.shape
+    E, N, _ = W.shape
+    if out is None:
+        out = torch.empty(S, N, dtype=torch.bfloat16, device=A.device)
+    call("gemm_bf16_grouped", A, A.stride(0), W, W.stride(1), out, out.stride(0), S, E, N, Kd, disp["count"],
+         disp["row0"], disp["rows"], disp["expert"], disp["max_tiles"], status_word(A.device))
+    _count()
+    return out
+
+
 def quant_rows(x: torch.Tensor, swiglu: bool = False) -> tuple[torch.Tensor, torch.Tensor]:
     """Per-row dynamic int8 quantisation of bf16 rows (optionally of ``silu(gate) * up`` of a
     ``[M, 2I]`` input). Returns ``(q int8 [M, K], scale fp32 [M])``."""

@@ -367,3 +367,41 @@ def test_moe_gemv_w4a8_slots():
             continue
         gu = O.w4a8_linear(x[r:r + 1], q.packed[e], q.scale[e], H)
         close(out[s:s + 1], O.silu_mul(gu[:, :I], gu[:, I:]), 3e-2)
+
+
+@pytest.mark.parametrize("T,k,E,H,N", [(300, 4, 8, 256, 512), (64, 2, 16, 128, 264), (1000, 8, 32, 512, 256)])
+def test_moe_dispatch_and_grouped_gemm(T, k, E, H, N):
+    """Device-side expert-major dispatch + grouped tcgen05 GEMM against a per-expert fp32 matmul;
+    some slots belong to no local expert (-1) and must be left out."""
+    kk = K()
+    g = torch.Generator().manual_seed(T + E)
+    idx = torch.randint(-2, E, (T, k), generator=g, dtype=torch.int32)
+    x = (torch.randn(T, H, generator=g) * 0.5).bfloat16()
+    W = (torch.randn(E, N, H, generator=g) * 0.05).bfloat16()
+    d = kk.moe_dispatch(idx.to(DEV), E)
+    pos = d["pos"].cpu().reshape(T, k)
+    src = d["src_tok"].cpu()
+    n_local = int((idx >= 0).sum())
+    assert sorted(pos[idx >= 0].tolist()) == list(range(n_local))
+    assert (pos[idx < 0] == -1).all()
+    nt = int(d["count"].cpu())
+    row0, rows, ex = d["row0"].cpu()[:nt], d["rows"].cpu()[:nt], d["expert"].cpu()[:nt]
+    assert int(rows.sum()) == n_local and int(rows.max()) <= 128
+    for t in range(T):
+        for j in range(k):
+            if idx[t, j] >= 0:
+                assert src[pos[t, j]] == t
+    xs = x.to(DEV).index_select(0, d["src_tok"])
+    y = kk.gemm_grouped(xs, W.to(DEV), d).float().cpu()
+    for t in range(0, T, 7):
+        for j in range(k):
+            e = int(idx[t, j])
+            if e < 0:
+                continue
+            ref = x[t].float() @ W[e].float().T
+            got = y[pos[t, j]]
+            assert (got - ref).abs().max() <= 2e-2 * ref.abs().max() + 1e-3
+    # every tile stays inside one expert's row range
+    for i in range(nt):
+        sel = (pos >= int(row0[i])) & (pos < int(row0[i] + rows[i]))
+        assert (idx[sel] == int(ex[i])).all()
