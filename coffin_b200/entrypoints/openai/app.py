@@ -87,8 +87,11 @@ def finish_reason(out: dict) -> str:
 
 def usage(out: dict) -> dict:
     pt, ct = int(out.get("n_prompt") or 0), int(out.get("n_new") or 0)
-    return {"prompt_tokens": pt, "completion_tokens": ct, "total_tokens": pt + ct,
-            "prompt_tokens_details": {"cached_tokens": int(out.get("cached_tokens") or 0)}}
+    u = {"prompt_tokens": pt, "completion_tokens": ct, "total_tokens": pt + ct,
+         "prompt_tokens_details": {"cached_tokens": int(out.get("cached_tokens") or 0)}}
+    if "prefill_ms" in out:     # engine-side clock: submit -> first token, first -> last token (an extension field)
+        u["timing"] = {"ttft_ms": out.get("prefill_ms"), "decode_ms": out.get("decode_ms")}
+    return u
 
 
 class Handler(BaseHTTPRequestHandler):

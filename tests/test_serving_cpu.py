@@ -140,3 +140,19 @@ def test_http_adapter_end_to_end(engine):
         c.close()
     finally:
         http_srv.shutdown()
+
+
+def test_serving_load_generator_end_to_end(capsys):
+    """The open-loop load generator starts an engine process (tiny model, CPU oracle twin) and the
+    HTTP front, drives Poisson arrivals with a shared prefix over SSE and reports percentiles; the
+    shared prefix must show up as cached prompt tokens."""
+    import json
+    from coffin_b200.tools import bench_serving
+    rc = bench_serving.main(["--spawn", "--preset", "tiny", "--device", "cpu", "--requests", "6", "--rate", "30",
+                             "--prefix-tokens", "64", "--suffix-tokens", "8", "--max-tokens", "6", "--max-seq", "512",
+                             "--max-num-seqs", "4", "--startup-timeout", "120"])
+    rep = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert rc == 0 and rep["completed"] == 6 and rep["failed"] == 0
+    assert rep["output_tokens_total"] == 36
+    assert rep["ttft_ms"]["p50"] is not None and rep["tpot_ms"]["p50"] is not None
+    assert rep["cached_prompt_tokens_p50"] >= 32
