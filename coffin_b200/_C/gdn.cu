@@ -177,7 +177,8 @@ __global__ void __launch_bounds__(4 * DV) gdn_commit_kernel(float* state, const 
 }
 
 // ---------------------------------------------------------------------------------------
-// Prefill prep: one CTA per token, one warp per head task.
+// Prefill prep: conv + SiLU, q/k normalisation, beta and g for a chunk of tokens.
+constexpr int kPrepTok = 8;   // tokens per CTA of the prefill prep kernel
 struct GdnPrepArgs {
   const bf16* proj; int64_t ldp;
   const float* conv_w; const float* A_log; const float* dt_bias;
@@ -190,22 +191,29 @@ struct GdnPrepArgs {
 
 template <int DK, int DV>
 __global__ void __launch_bounds__(256) gdn_prep_kernel(const GdnPrepArgs a) {
+  // One CTA per tile of kPrepTok tokens, one warp per head task.  A lane owns four adjacent channels
+  // (8-byte loads of the projection rows, 16-byte stores) and slides the 4-tap window over the tile's
+  // tokens in registers, so a row is read once per tile instead of once per tap.
   griddep_launch();
   griddep_wait();
-  const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  constexpr int TT = kPrepTok;
+  const int t0 = blockIdx.x * TT, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int kdim = a.nk * DK, conv_dim = 2 * kdim + a.nv * DV;
   const int ntask = 2 * a.nk + a.nv + 1;
   for (int task = warp; task < ntask; task += 8) {
-    if (task == ntask - 1) {  // beta / g for every value head
-      for (int h = lane; h < a.nv; h += 32) {
+    if (task == ntask - 1) {  // beta / g for every (value head, token of the tile)
+      for (int idx = lane; idx < a.nv * TT; idx += 32) {
+        const int h = idx / TT, t = t0 + idx % TT;
         float b = 0.f, gg = 0.f;
         if (t < a.T) {
           const bf16* prow = a.proj + (int64_t)t * a.ldp + conv_dim + a.nv * DV;
           b = sigmoid_f(__bfloat162float(prow[h]));
           gg = -__expf(a.A_log[h]) * softplus_f(__bfloat162float(prow[a.nv + h]) + a.dt_bias[h]);
         }
-        a.beta[(int64_t)h * a.Tp + t] = b;
-        a.g[(int64_t)h * a.Tp + t] = gg;
+        if (t < a.Tp) {
+          a.beta[(int64_t)h * a.Tp + t] = b;
+          a.g[(int64_t)h * a.Tp + t] = gg;
+        }
       }
       continue;
     }
@@ -213,38 +221,50 @@ __global__ void __launch_bounds__(256) gdn_prep_kernel(const GdnPrepArgs a) {
     if (task < a.nk) { kind = 0; head = task; cbase = head * DK; width = DK; }
     else if (task < 2 * a.nk) { kind = 1; head = task - a.nk; cbase = kdim + head * DK; width = DK; }
     else { kind = 2; head = task - 2 * a.nk; cbase = 2 * kdim + head * DV; width = DV; }
-    constexpr int CPL = (DK > DV ? DK : DV) / 32;
-    float val[CPL];
-    float ss = 0.f;
+    const int i0 = lane * 4;
+    const bool act = i0 < width;
+    const int c = cbase + i0;
+    float w[4][4];                       // [channel][tap]
+    float win[3][4];                     // the three rows before the current token
 #pragma unroll
-    for (int e = 0; e < CPL; ++e) {
-      const int i = lane + 32 * e;
-      val[e] = 0.f;
-      if (i < width && t < a.T) {
-        const int c = cbase + i;
-        const float4 w = *reinterpret_cast<const float4*>(a.conv_w + (int64_t)c * 4);
-        float x[4];
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {
-          const int tt = t - 3 + k, pp = a.pos0 + tt;
-          if (tt >= 0) x[k] = __bfloat162float(a.proj[(int64_t)tt * a.ldp + c]);
-          else if (pp >= 0) x[k] = __bfloat162float(a.ring[(int64_t)(pp & (kRing - 1)) * conv_dim + c]);
-          else x[k] = 0.f;
-        }
-        val[e] = silu_f(w.x * x[0] + w.y * x[1] + w.z * x[2] + w.w * x[3]);
-        ss += val[e] * val[e];
+    for (int j = 0; j < 4; ++j) {
+      const float4 wj = act ? *reinterpret_cast<const float4*>(a.conv_w + (int64_t)(c + j) * 4) : make_float4(0.f, 0.f, 0.f, 0.f);
+      w[j][0] = wj.x; w[j][1] = wj.y; w[j][2] = wj.z; w[j][3] = wj.w;
+    }
+    auto load_row = [&](int tt, float* x) {          // conv input row of token tt (tile-relative rows may precede the chunk)
+      const int pp = a.pos0 + tt;
+      uint2 raw = make_uint2(0u, 0u);
+      if (act) {
+        if (tt >= 0) { if (tt < a.T) raw = *reinterpret_cast<const uint2*>(a.proj + (int64_t)tt * a.ldp + c); }
+        else if (pp >= 0) raw = *reinterpret_cast<const uint2*>(a.ring + (int64_t)(pp & (kRing - 1)) * conv_dim + c);
       }
-    }
-    float scale = 1.f;
-    if (kind < 2) {
-      ss = warp_sum(ss);
-      scale = rsqrtf(ss + 1e-6f) * (kind == 0 ? rsqrtf((float)DK) : 1.f);
-    }
-    float* dst = (kind == 0 ? a.qn : kind == 1 ? a.kn : a.v) + ((int64_t)head * a.Tp + t) * width;
+      // a bf16 is the upper half of the fp32 with the same value
+      x[0] = __uint_as_float(raw.x << 16); x[1] = __uint_as_float(raw.x & 0xffff0000u);
+      x[2] = __uint_as_float(raw.y << 16); x[3] = __uint_as_float(raw.y & 0xffff0000u);
+    };
+    load_row(t0 - 3, win[0]);
+    load_row(t0 - 2, win[1]);
+    load_row(t0 - 1, win[2]);
+    float* dbase = (kind == 0 ? a.qn : kind == 1 ? a.kn : a.v) + (int64_t)head * a.Tp * width;
 #pragma unroll
-    for (int e = 0; e < CPL; ++e) {
-      const int i = lane + 32 * e;
-      if (i < width) dst[i] = val[e] * scale;
+    for (int k = 0; k < TT; ++k) {
+      const int t = t0 + k;
+      float cur[4], val[4];
+      load_row(t, cur);
+      float ss = 0.f;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        val[j] = (act && t < a.T) ? silu_f(w[j][0] * win[0][j] + w[j][1] * win[1][j] + w[j][2] * win[2][j] + w[j][3] * cur[j]) : 0.f;
+        ss += val[j] * val[j];
+        win[0][j] = win[1][j]; win[1][j] = win[2][j]; win[2][j] = cur[j];
+      }
+      float scale = 1.f;
+      if (kind < 2) {
+        ss = warp_sum(ss);
+        scale = rsqrtf(ss + 1e-6f) * (kind == 0 ? rsqrtf((float)DK) : 1.f);
+      }
+      if (act && t < a.Tp)
+        *reinterpret_cast<float4*>(dbase + (int64_t)t * width + i0) = make_float4(val[0] * scale, val[1] * scale, val[2] * scale, val[3] * scale);
     }
   }
 }
@@ -565,23 +585,35 @@ __device__ __forceinline__ void frag_bt(const float* M, int ld, int k0, int c0, 
 template <int DK, int DV>
 struct PrepTcLayout {
   static constexpr int L = kChunk, LDA = DK + 4, LDB = DK + 8, LDV = DV + 8, LDL = L + 4;
-  // Ks, Qs [L][LDA] (row operands), Kb [L][LDB] (beta e^c K as a k-major operand), Vs [L][LDV], Tm, Wi [L][LDL], cs, bs [L]
-  static constexpr size_t floats = (size_t)2 * L * LDA + (size_t)L * LDB + (size_t)L * LDV + (size_t)2 * L * LDL + 2 * L;
+  // R1 [L][max(LDA, LDV)]: K as a row operand, later V (k-major operand of the last product)
+  // R2 [L][LDB]: Q as a row operand (leading dimension LDA), later e^c K as a k-major operand
+  // Tm, Wi [L][LDL]; cs, bs [L].  105 KB for 128-wide heads: two CTAs per SM.
+  static constexpr int LD1 = LDA > LDV ? LDA : LDV;
+  static constexpr size_t floats = (size_t)L * LD1 + (size_t)L * LDB + (size_t)2 * L * LDL + 2 * L;
 };
 
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
+  const uint32_t sa = (uint32_t)__cvta_generic_to_shared(smem);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(sa), "l"(gmem) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+
 template <int DK, int DV>
-__global__ void __launch_bounds__(256) gdn_chunk_prepare_tc_kernel(const GdnChunkArgs a) {
+__global__ void __launch_bounds__(256, 2) gdn_chunk_prepare_tc_kernel(const GdnChunkArgs a) {
   using Lay = PrepTcLayout<DK, DV>;
   constexpr int L = kChunk, LDA = Lay::LDA, LDB = Lay::LDB, LDV = Lay::LDV, LDL = Lay::LDL;
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  float* Ks = reinterpret_cast<float*>(smem_raw);
-  float* Qs = Ks + L * LDA;
-  float* Kb = Qs + L * LDA;
-  float* Vs = Kb + L * LDB;
-  float* Tm = Vs + L * LDV;
+  float* R1 = reinterpret_cast<float*>(smem_raw);
+  float* R2 = R1 + L * Lay::LD1;
+  float* Tm = R2 + L * LDB;
   float* Wi = Tm + L * LDL;
   float* cs = Wi + L * LDL;
   float* bs = cs + L;
+  float* Ks = R1;          // phase 1-3
+  float* Qs = R2;          // phase 1-2
+  float* Kb = R2;          // phase 4-5
+  float* Vs = R1;          // phase 5
   griddep_launch();
   griddep_wait();
   const int n = blockIdx.x, h = blockIdx.y, kh = h / a.rep, tid = threadIdx.x;
@@ -594,10 +626,6 @@ __global__ void __launch_bounds__(256) gdn_chunk_prepare_tc_kernel(const GdnChun
     const int i = idx / (DK / 4), c = (idx % (DK / 4)) * 4;
     *reinterpret_cast<float4*>(Ks + i * LDA + c) = *reinterpret_cast<const float4*>(kp + (int64_t)i * DK + c);
     *reinterpret_cast<float4*>(Qs + i * LDA + c) = *reinterpret_cast<const float4*>(qp + (int64_t)i * DK + c);
-  }
-  for (int idx = tid; idx < L * DV / 4; idx += 256) {
-    const int i = idx / (DV / 4), c = (idx % (DV / 4)) * 4;
-    *reinterpret_cast<float4*>(Vs + i * LDV + c) = *reinterpret_cast<const float4*>(vp + (int64_t)i * DV + c);
   }
   if (tid < 32) {  // inclusive scan of g over the 64 rows
     const float g0 = a.g[(int64_t)h * a.Tp + t0 + tid], g1 = a.g[(int64_t)h * a.Tp + t0 + 32 + tid];
@@ -641,13 +669,21 @@ __global__ void __launch_bounds__(256) gdn_chunk_prepare_tc_kernel(const GdnChun
         icap[i * L + jj] = dec * qk[j][e];
       }
   }
-  __syncthreads();
+  // ---- qe = e^c Q for the scan (Q's last use), zero the inverse ---------------------------------
+  {
+    float* qep = a.qe + ((int64_t)h * a.nc + n) * L * DK;
+    for (int idx = tid; idx < L * DK / 4; idx += 256) {
+      const int i = idx / (DK / 4), c = (idx % (DK / 4)) * 4;
+      const float ec = __expf(cs[i]);
+      const float4 q = *reinterpret_cast<const float4*>(Qs + i * LDA + c);
+      *reinterpret_cast<float4*>(qep + (int64_t)i * DK + c) = make_float4(q.x * ec, q.y * ec, q.z * ec, q.w * ec);
+    }
+    for (int idx = tid; idx < L * L; idx += 256) Wi[(idx / L) * LDL + idx % L] = 0.f;
+  }
+  __syncthreads();                                   // Tm complete, Q no longer needed
   // ---- W = (I + Tm)^-1, blocked: the four 16x16 diagonal blocks are inverted by forward
   // substitution (one warp each, one column per lane, 16 dependent rows instead of 64), then the
   // blocks below the diagonal follow level by level from  W_ij = -W_ii (sum_{k=j..i-1} T_ik W_kj).
-  __syncthreads();                                   // Tm complete (written by its fragment owners)
-  for (int idx = tid; idx < L * L; idx += 256) Wi[(idx / L) * LDL + idx % L] = 0.f;
-  __syncthreads();
   if (warp < 4 && lane < 16) {
     const int b0 = warp * 16, c = lane;
     for (int i = 0; i < 16; ++i) {
@@ -658,7 +694,7 @@ __global__ void __launch_bounds__(256) gdn_chunk_prepare_tc_kernel(const GdnChun
   }
   __syncthreads();
   {
-    float* P = Kb;                                    // scratch for the block sums: Kb is filled later
+    float* P = R2;                                    // scratch for the block sums (Q is gone, e^c K not yet there)
     for (int d = 1; d < 4; ++d) {
       const int npairs = 4 - d;
       // P_p = sum_{k=j}^{i-1} T_ik W_kj for the pairs (i = j + d, j)
@@ -680,30 +716,34 @@ __global__ void __launch_bounds__(256) gdn_chunk_prepare_tc_kernel(const GdnChun
       __syncthreads();
     }
   }
-  // ---- scaled copies for the scan; Kb <- beta e^c K, Vs <- beta V ------------------------------
+  // ---- W <- W diag(beta) (both products below carry beta); ke and e^c K from K -------------------
   {
-    float* qep = a.qe + ((int64_t)h * a.nc + n) * L * DK;
+    for (int idx = tid; idx < L * L; idx += 256) Wi[(idx / L) * LDL + idx % L] *= bs[idx % L];
     float* kep = a.ke + ((int64_t)h * a.nc + n) * L * DK;
     const float cl = cs[L - 1];
-    for (int idx = tid; idx < L * DK; idx += 256) {
-      const int i = idx / DK, c = idx % DK;
-      const float ec = __expf(cs[i]);
-      const float kv = Ks[i * LDA + c];
-      qep[idx] = Qs[i * LDA + c] * ec;
-      kep[idx] = kv * __expf(cl - cs[i]);
-      Kb[i * LDB + c] = bs[i] * ec * kv;
-    }
-    for (int idx = tid; idx < L * DV; idx += 256) {
-      const int i = idx / DV, c = idx % DV;
-      Vs[i * LDV + c] *= bs[i];
+    for (int idx = tid; idx < L * DK / 4; idx += 256) {
+      const int i = idx / (DK / 4), c = (idx % (DK / 4)) * 4;
+      const float ec = __expf(cs[i]), el = __expf(cl - cs[i]);
+      const float4 k = *reinterpret_cast<const float4*>(Ks + i * LDA + c);
+      *reinterpret_cast<float4*>(kep + (int64_t)i * DK + c) = make_float4(k.x * el, k.y * el, k.z * el, k.w * el);
+      *reinterpret_cast<float4*>(Kb + i * LDB + c) = make_float4(k.x * ec, k.y * ec, k.z * ec, k.w * ec);
     }
     if (tid == 0) a.ecl[(int64_t)h * a.nc + n] = __expf(cl);
   }
-  __syncthreads();
-  // ---- nvv = W (beta V), kcd = W (beta e^c K): warp (row tile) x (V or K half); W is lower triangular ----
+  __syncthreads();                                   // K is no longer needed: V takes its place
+  // ---- nvv = W' V, kcd = W' (e^c K): warp (row tile) x (V or K half); W' is lower triangular ------
   {
     const int r0 = (warp & 3) * 16;
     const bool isv = (warp >> 2) == 0;
+    if (isv) {                                       // the four V warps fetch V while the K warps multiply
+      for (int idx = tid; idx < L * DV / 4; idx += 128) {
+        const int i = idx / (DV / 4), c = (idx % (DV / 4)) * 4;
+        cp_async16(Vs + i * LDV + c, vp + (int64_t)i * DV + c);
+      }
+      cp_async_commit();
+      cp_async_wait_all();
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+    }
     const float* B = isv ? Vs : Kb;
     const int ldb = isv ? LDV : LDB;
     constexpr int NT = (DV > DK ? DV : DK) / 8;
@@ -734,13 +774,6 @@ __global__ void __launch_bounds__(256) gdn_chunk_prepare_tc_kernel(const GdnChun
     }
   }
 }
-
-__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
-  const uint32_t sa = (uint32_t)__cvta_generic_to_shared(smem);
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(sa), "l"(gmem) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
 
 template <int DK, int DVS>
 struct ScanTcLayout {
@@ -1004,7 +1037,7 @@ CB_EXPORT int cb_gdn_prefill(const void* proj, int64_t ldp, const void* conv_w, 
   int rc;
 #define GDN_PREFILL(DK_, DV_, DVS_)                                                                      \
   do {                                                                                                   \
-    e = cb_launch(gdn_prep_kernel<DK_, DV_>, dim3((unsigned)Tp), dim3(256), 0, st, pa);                  \
+    e = cb_launch(gdn_prep_kernel<DK_, DV_>, dim3((unsigned)((Tp + kPrepTok - 1) / kPrepTok)), dim3(256), 0, st, pa);                  \
     if (e != cudaSuccess) return (int)e;                                                                 \
     e = cb_launch(gdn_ring_update_kernel, dim3((unsigned)(T < kRing ? T : kRing)), dim3(256), 0, st,     \
                   (const bf16*)proj, ldp, (bf16*)ring_seq, (int)T, (int)pos0, conv_dim);                 \

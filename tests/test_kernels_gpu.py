@@ -202,7 +202,7 @@ def test_gdn_prefill_chunked(nk, nv, dk, dv, T1, T2):
     k.gdn_prefill(pj[:T1], *args, out[:T1], pos0=0, nk=nk, nv=nv, dk=dk, dv=dv, eps=1e-6)
     k.gdn_prefill(pj[T1:], *args, out[T1:], pos0=T1, nk=nk, nv=nv, dk=dk, dv=dv, eps=1e-6)
     close(out, ref, 3e-2)
-    close(st, state, 2e-3)
+    close(st, state, 4e-3)      # the chunk products run as TF32 (10-bit mantissa) on the tensor cores
     # a decode step after the chunked prefill continues from the ring + state
     extra = bf(1, proj.shape[1], seed=31)
     ref2 = _gdn_oracle(extra, conv_w, A_log, dt_bias, norm_w, nk, nv, dk, dv, conv_state, state)
