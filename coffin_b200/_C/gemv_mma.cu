@@ -28,6 +28,7 @@ struct MmaArgs {
   int rounds;         // rounds of the grid-wide sweep
   int pull_site, push_site;
   int pf_rounds;      // sweep rounds whose weights are requested into L2 before the dependency wait
+  int64_t xs_ld;      // activation elements staged per row (K, or this CTA's K slice)
   int stage_batches;  // weight batches per warp copied into shared memory ahead of the dependency wait
   int kcta;           // CTAs that share one 16-row block, each with its own k range (1: none; then ksplit == 8)
   float* ws; unsigned* tickets;   // cross-CTA partial sums [unit][kcta][2][128] and arrival counters [unit]
@@ -84,13 +85,18 @@ __global__ void __launch_bounds__(kT, 3) gemv_mma_kernel(const MmaArgs a_in) {
   }
   const int64_t K = a.K, nchunk = K >> 3;
   const int M = a.M;
-  bf16* xs = reinterpret_cast<bf16*>(smem_raw);                                  // [M][K]
-  float* part = reinterpret_cast<float*>(smem_raw + (((size_t)M * K * 2 + 15) & ~(size_t)15));  // [rounds][warps][PB][16][8]
+  // A CTA that shares its row block with other CTAs (cross-CTA K split) only ever multiplies its own
+  // K slice: without a norm prologue (which needs whole rows) it stages just that slice, xs_ld
+  // elements per row starting at chunk xs_c0.  Fewer bytes per CTA keep more CTAs resident when
+  // several activation rows times a long K would otherwise fill the shared memory.
+  const int64_t xs_ld = a.xs_ld, xs_c0 = a.xs_ld == K ? 0 : (int64_t)(blockIdx.x % a.kcta) * (a.xs_ld >> 3);
+  bf16* xs = reinterpret_cast<bf16*>(smem_raw);                                  // [M][xs_ld]
+  float* part = reinterpret_cast<float*>(smem_raw + (((size_t)M * xs_ld * 2 + 15) & ~(size_t)15));  // [rounds][warps][PB][16][8]
   const int nT = blockDim.x, nW = nT >> 5;                  // the CTA has ksplit * (row blocks per round) warps
   // per-warp staging area behind the partial sums: [batch][u][b][lo|hi][lane] 16-byte vectors
   constexpr int kBatchVecs = U * PB * 2;                     // vectors per lane per batch
   uint4* stage = reinterpret_cast<uint4*>(
-      smem_raw + (((size_t)M * K * 2 + 15) & ~(size_t)15) +
+      smem_raw + (((size_t)M * xs_ld * 2 + 15) & ~(size_t)15) +
       (a_in.ksplit > 1 ? (size_t)a_in.rounds * nW * PB * 128 * sizeof(float) : 0)) +
       (size_t)(threadIdx.x >> 5) * a_in.stage_batches * kBatchVecs * 32;
   __shared__ float red[32];
@@ -230,12 +236,15 @@ __global__ void __launch_bounds__(kT, 3) gemv_mma_kernel(const MmaArgs a_in) {
       }
     }
   } else {
-    for (int64_t c = tid; c < (int64_t)M * nchunk; c += nT)
-      *reinterpret_cast<uint4*>(xs + c * 8) = *reinterpret_cast<const uint4*>(a.x + c * 8);
+    const int64_t lc = xs_ld >> 3;                     // chunks staged per row
+    for (int64_t i = tid; i < (int64_t)M * lc; i += nT) {
+      const int64_t m = i / lc, c = xs_c0 + i % lc;
+      if (c < nchunk) *reinterpret_cast<uint4*>(xs + i * 8) = *reinterpret_cast<const uint4*>(a.x + (m * nchunk + c) * 8);
+    }
   }
   __syncthreads();
 
-  const bf16* xrow = xs + (int64_t)g * K;      // batch row g supplies column g of the B operand
+  const bf16* xrow = xs + (int64_t)g * xs_ld - xs_c0 * 8;   // batch row g supplies column g of the B operand; indexed by global chunk
   const bool has_x = g < M;
 
   for (int round = 0; round < a.rounds; ++round) {
@@ -382,10 +391,17 @@ int launch_mma(MmaArgs a, cudaStream_t st, int n_slots = 1) {
   //  * more blocks than warp slots (vocabulary head): 8-warp CTAs sweep whole blocks in rounds,
   //    the grid sized so that every CTA runs the same number of rounds.
   const int warps_sm = 25;                                      // 80 registers per thread
-  const size_t xs_bytes = (((size_t)a.M * a.K * 2 + 15) & ~(size_t)15);
+  // elements of a row that a CTA stages when kc CTAs share a block and each has w K-slice warps
+  auto slice_ld = [&](int w, int kc) -> int64_t {
+    if (NORM || kc <= 1) return a.K;
+    const int64_t pper = (npair + (int64_t)w * kc - 1) / ((int64_t)w * kc);
+    const int64_t ld = pper * w * 32;
+    return ld < a.K ? ld : a.K;
+  };
   int stage_b = g_mma_stage;                                     // staged batches per warp (4 KB each)
-  auto cta_slots = [&](int w) -> int64_t {                       // CTAs of w warps resident on the machine
+  auto cta_slots = [&](int w, int kc = 1) -> int64_t {           // CTAs of w warps resident on the machine
     int64_t per = warps_sm / w;
+    const size_t xs_bytes = (((size_t)a.M * slice_ld(w, kc) * 2 + 15) & ~(size_t)15);
     const size_t sm = xs_bytes + (w > 1 ? (size_t)w * PB * 512 : 0) + (size_t)w * stage_b * 4096 + 1024;
     const int64_t by_smem = (int64_t)((size_t)227 * 1024 / sm);
     if (per > by_smem) per = by_smem;
@@ -409,7 +425,7 @@ int launch_mma(MmaArgs a, cudaStream_t st, int n_slots = 1) {
       for (; S > 1; --S) {                                       // most slices per block that still fit one wave
         c1 = (int)((S + kW - 1) / kW);
         k1 = (int)(S / c1);
-        if (nblk * c1 <= cta_slots(k1)) break;
+        if (nblk * c1 <= cta_slots(k1, c1)) break;
       }
       if (S <= 1) { k1 = 1; c1 = 1; }
       const int64_t warps_total = nblk * c1 * k1;
@@ -440,7 +456,8 @@ int launch_mma(MmaArgs a, cudaStream_t st, int n_slots = 1) {
     cudaGetSymbolAddress((void**)&a.tickets, g_split_tickets);
   }
   a.pf_rounds = a.slot_expert ? 0 : (a.rounds < g_mma_pf_rounds ? a.rounds : g_mma_pf_rounds);
-  size_t smem = (((size_t)a.M * a.K * 2 + 15) & ~(size_t)15);
+  a.xs_ld = slice_ld(ks, kcta);
+  size_t smem = (((size_t)a.M * a.xs_ld * 2 + 15) & ~(size_t)15);
   if (ks > 1) smem += (size_t)a.rounds * warps * PB * 128 * sizeof(float);
   if (smem > 200 * 1024) return CB_ERR_SHAPE;
   smem += (size_t)warps * stage_b * 4096;

@@ -133,6 +133,28 @@ def block_copy(dst: torch.Tensor, src: torch.Tensor, dst_idx: torch.Tensor, src_
 
 
 # ------------------------------------------------------------------ projections
+# Batched decode rows: the fused add + RMSNorm prologue is repeated by every CTA of a projection
+# (hundreds of CTAs x M rows of conversions), which at M >= 2 costs more issue slots than the weight
+# stream leaves free.  From this many rows on, the rows are normalised once by a small kernel and the
+# projection copies them.
+NORM_SPLIT_ROWS = 2
+_norm_scratch: dict[tuple, torch.Tensor] = {}
+
+
+def _norm_rows(res_in: torch.Tensor, add, gain: torch.Tensor, res_out, eps: float) -> torch.Tensor:
+    """``rmsnorm(res_in + add) * gain`` into a per-shape scratch (stream-ordered reuse); ``res_out``
+    receives the sum, as the fused prologue would have written it."""
+    M, K = res_in.shape
+    key = (M, K, res_in.device.index)
+    buf = _norm_scratch.get(key)
+    if buf is None:
+        buf = _norm_scratch[key] = torch.empty(M, K, dtype=torch.bfloat16, device=res_in.device)
+    if add is None and res_out is not None and res_out.data_ptr() != res_in.data_ptr():
+        res_out.copy_(res_in)
+    rmsnorm(res_in, gain, eps, out=buf, add=add, res_out=res_out)
+    return buf
+
+
 def gemv(W: torch.Tensor, x: torch.Tensor | None, out: torch.Tensor | None, *, swiglu: bool = False,
          norm: tuple | None = None, tp=None, pull_site: int = -1, push_site: int = -1, rows: int | None = None) -> torch.Tensor | None:
     """Decode projection for 1, 2, 4 or 8 rows.
@@ -159,6 +181,8 @@ def gemv(W: torch.Tensor, x: torch.Tensor | None, out: torch.Tensor | None, *, s
         res_in, add, gain, res_out, eps = norm
         assert res_in.is_contiguous() and res_in.shape == (M, K)
         x = None
+    if norm is not None and M >= NORM_SPLIT_ROWS and pull_site < 0:
+        x, res_in, add, gain, res_out = _norm_rows(res_in, add, gain, res_out, eps), None, None, None, None
     if GEMV_IMPL == "mma" and M * K * 2 <= 160 * 1024:
         call("gemv_mma_bf16", W, x, out, M, N, K, ldy, mode, N, res_in, add, gain, res_out, float(eps), tpp,
              pull_site, push_site)
@@ -191,6 +215,8 @@ def gemv_i8(Wq: torch.Tensor, wscale: torch.Tensor, x: torch.Tensor | None, out:
     else:
         res_in, add, gain, res_out, eps = norm
         x = None
+        if M >= NORM_SPLIT_ROWS and pull_site < 0:
+            x, res_in, add, gain, res_out = _norm_rows(res_in, add, gain, res_out, eps), None, None, None, None
     call("gemv_i8", Wq, wscale, x, out, M, N, K, ldy, mode, N, res_in, add, gain, res_out, float(eps), tpp,
          pull_site, push_site)
     _count()
@@ -212,6 +238,8 @@ def gemv_w4(Wq: torch.Tensor, wscale: torch.Tensor, x: torch.Tensor | None, out:
     else:
         res_in, add, gain, res_out, eps = norm
         x = None
+        if M >= NORM_SPLIT_ROWS:
+            x, res_in, add, gain, res_out = _norm_rows(res_in, add, gain, res_out, eps), None, None, None, None
     call("gemv_w4", Wq, wscale, x, out, M, N, K, out.stride(0), mode, N, res_in, add, gain, res_out, float(eps))
     _count()
     return out

@@ -201,6 +201,8 @@ def spawn_stack(args):
         cmd += ["--model", args.model_dir] if args.model_dir else ["--preset", args.preset]
         if args.quant != "none":
             cmd += ["--quant", args.quant]
+        if args.snapshot_interval:
+            cmd += ["--snapshot-interval", str(args.snapshot_interval), "--snapshots", str(args.snapshots)]
         if args.image_frac > 0:
             cmd += ["--vision", args.vision]
         if args.device:
@@ -277,6 +279,9 @@ def main(argv=None) -> int:
     ap.add_argument("--device", default=None)
     ap.add_argument("--max-seq", type=int, default=4096)
     ap.add_argument("--max-num-seqs", type=int, default=64)
+    ap.add_argument("--snapshot-interval", type=int, default=0,
+                    help="tokens between delta-net state snapshots (a shared prefix is reusable up to the last snapshot inside it)")
+    ap.add_argument("--snapshots", type=int, default=32)
     ap.add_argument("--startup-timeout", type=float, default=600.0)
     args = ap.parse_args(argv)
     stop = None
@@ -289,7 +294,7 @@ def main(argv=None) -> int:
         if stop is not None:
             stop()
     rep["config"] = {k: getattr(args, k) for k in ("preset", "quant", "replicas", "prefix_tokens", "suffix_tokens",
-                                                   "max_tokens", "image_frac", "image_size", "max_num_seqs")}
+                                                   "max_tokens", "image_frac", "image_size", "max_num_seqs", "snapshot_interval")}
     print(json.dumps(rep))
     return 0 if rep["failed"] == 0 else 1
 
