@@ -215,18 +215,25 @@ int launch_i8(I8Args a, cudaStream_t st) {
     if (g_i8_sms <= 0) g_i8_sms = 148;
   }
   constexpr int PB = SWIGLU ? 2 : 1;
-  const int64_t nblk = (a.N + 15) / 16, slots = (int64_t)g_i8_sms * 3;
+  const int64_t nblk = (a.N + 15) / 16;
   const int64_t npair = ((a.K >> 4) + 3) >> 2;
-  int ks = 1;
-  while (ks < kW && (nblk * ks + kW - 1) / kW < slots && npair / (ks * 2) >= 4) ks <<= 1;
-  a.ksplit = ks;
-  const int rbr = kW / ks;
-  const int64_t units = (nblk + rbr - 1) / rbr;
-  const int64_t grid = units < slots ? units : slots;
-  a.rounds = (int)((units + grid - 1) / grid);
-  size_t smem = (size_t)a.K * 2 + (((size_t)a.M * a.K + 15) & ~(size_t)15) + 32;
-  if (ks > 1) smem += (size_t)a.rounds * kW * PB * 128 * sizeof(float);
-  if (smem > 72 * 1024) return CB_ERR_SHAPE;
+  // three CTAs per SM while their activations fit; several rows of a long K get fewer, larger shares
+  size_t smem = 0;
+  int64_t grid = 0;
+  for (int per_sm = 3; per_sm >= 1; --per_sm) {
+    const int64_t slots = (int64_t)g_i8_sms * per_sm;
+    int ks = 1;
+    while (ks < kW && (nblk * ks + kW - 1) / kW < slots && npair / (ks * 2) >= 4) ks <<= 1;
+    a.ksplit = ks;
+    const int rbr = kW / ks;
+    const int64_t units = (nblk + rbr - 1) / rbr;
+    grid = units < slots ? units : slots;
+    a.rounds = (int)((units + grid - 1) / grid);
+    smem = (size_t)a.K * 2 + (((size_t)a.M * a.K + 15) & ~(size_t)15) + 32;
+    if (ks > 1) smem += (size_t)a.rounds * kW * PB * 128 * sizeof(float);
+    if ((smem + 2048) * per_sm <= (size_t)227 * 1024) break;
+  }
+  if (smem > 200 * 1024) return CB_ERR_SHAPE;
   auto kern = gemv_i8_kernel<SWIGLU, NORM, OUT_F32>;
   if (smem + 2048 > 48 * 1024) {   // the 48 KB default also has to hold the static shared memory
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);

@@ -260,17 +260,24 @@ int launch_w4(W4Args a, cudaStream_t st, int n_slots) {
   }
   constexpr int PB = SWIGLU ? 2 : 1;
   const int G = (int)(a.K / kGroup);
-  const int64_t nblk = (a.N + 15) / 16, slots = std::max<int64_t>(1, (int64_t)g_w4_sms * 2 / n_slots);
-  int ks = 1;
-  while (ks < kW && (nblk * ks + kW - 1) / kW < slots && G / (ks * 2) >= 1) ks <<= 1;
-  a.ksplit = ks;
-  const int rbr = kW / ks;
-  const int64_t units = (nblk + rbr - 1) / rbr;
-  const int64_t grid = units < slots ? units : slots;
-  a.rounds = (int)((units + grid - 1) / grid);
-  size_t smem = (size_t)a.K * 2 + (size_t)a.M * a.K + (size_t)a.M * G * 4 + 32;
-  if (ks > 1) smem += (size_t)a.rounds * kW * PB * 128 * sizeof(float);
-  if (smem > 96 * 1024) return CB_ERR_SHAPE;
+  const int64_t nblk = (a.N + 15) / 16;
+  // two CTAs per SM while their activations fit; several rows of a long K get one
+  size_t smem = 0;
+  int64_t grid = 0;
+  for (int per_sm = 2; per_sm >= 1; --per_sm) {
+    const int64_t slots = std::max<int64_t>(1, (int64_t)g_w4_sms * per_sm / n_slots);
+    int ks = 1;
+    while (ks < kW && (nblk * ks + kW - 1) / kW < slots && G / (ks * 2) >= 1) ks <<= 1;
+    a.ksplit = ks;
+    const int rbr = kW / ks;
+    const int64_t units = (nblk + rbr - 1) / rbr;
+    grid = units < slots ? units : slots;
+    a.rounds = (int)((units + grid - 1) / grid);
+    smem = (size_t)a.K * 2 + (size_t)a.M * a.K + (size_t)a.M * G * 4 + 32;
+    if (ks > 1) smem += (size_t)a.rounds * kW * PB * 128 * sizeof(float);
+    if ((smem + 2048) * per_sm <= (size_t)227 * 1024) break;
+  }
+  if (smem > 200 * 1024) return CB_ERR_SHAPE;
   auto kern = gemv_w4_kernel<SWIGLU, NORM, OUT_F32>;
   if (smem + 2048 > 48 * 1024) {   // the 48 KB default also has to hold the static shared memory
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
