@@ -132,3 +132,61 @@ CB_EXPORT int cb_peer_read_i32(const void* dev, int* out) {
 CB_EXPORT int cb_tp_epoch_bump(void* epoch, void* stream) {
   return (int)cb_launch(epoch_bump_kernel, dim3(1), dim3(32), 0, (cudaStream_t)stream, (unsigned*)epoch);
 }
+
+// ---------------------------------------------------------------------------------------------
+// Decode all-reduce, consumer side, done once per row instead of once per CTA of the next
+// projection: pull the ranks' partial sums of `site` (bounded wait on the data-carried epochs), add
+// them to the residual in rank order, write the new residual and its RMSNorm.  One CTA per row.
+// A projection of several hundred CTAs that each pulled world x K pairs spent ~10 us per site in L2
+// traffic (world x 20 KB x CTAs); here a single CTA reads them and the projection copies 5 KB.
+// Arithmetic and rounding are those of the fused GEMV prologue (gemv_mma.cu), so every rank still
+// holds bit-identical activations.
+namespace {
+__global__ void __launch_bounds__(1024) tp_pull_norm_kernel(const TpComm tp, int site, const bf16* __restrict__ res_in,
+                                                            const float* __restrict__ gain, bf16* __restrict__ res_out,
+                                                            bf16* __restrict__ out, int64_t K, float eps) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  float* row = reinterpret_cast<float*>(smem_raw);  // [K]
+  __shared__ float red[32];
+  griddep_launch();
+  griddep_wait();
+  const int64_t m = blockIdx.x;
+  float ss = 0.f;
+  for (int64_t c = threadIdx.x; c < (K >> 3); c += blockDim.x) {
+    float f[8], pulled[8];
+    bf16x8_to_float(*reinterpret_cast<const uint4*>(res_in + m * K + c * 8), f);
+    tp_pull8(tp, site, m * K + c * 8, pulled);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) f[i] = __bfloat162float(__float2bfloat16(f[i] + pulled[i]));
+    if (res_out) *reinterpret_cast<uint4*>(res_out + m * K + c * 8) = float_to_bf16x8(f);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) { row[c * 8 + i] = f[i]; ss += f[i] * f[i]; }
+  }
+  const float rstd = rsqrtf(block_sum(ss, red) / (float)K + eps);
+  for (int64_t c = threadIdx.x; c < (K >> 3); c += blockDim.x) {
+    float f[8];
+    const float4 g0 = *reinterpret_cast<const float4*>(gain + c * 8);
+    const float4 g1 = *reinterpret_cast<const float4*>(gain + c * 8 + 4);
+    f[0] = row[c * 8 + 0] * (rstd * g0.x); f[1] = row[c * 8 + 1] * (rstd * g0.y);
+    f[2] = row[c * 8 + 2] * (rstd * g0.z); f[3] = row[c * 8 + 3] * (rstd * g0.w);
+    f[4] = row[c * 8 + 4] * (rstd * g1.x); f[5] = row[c * 8 + 5] * (rstd * g1.y);
+    f[6] = row[c * 8 + 6] * (rstd * g1.z); f[7] = row[c * 8 + 7] * (rstd * g1.w);
+    *reinterpret_cast<uint4*>(out + m * K + c * 8) = float_to_bf16x8(f);
+  }
+}
+}  // namespace
+
+CB_EXPORT int cb_tp_pull_norm(const void* tp, int64_t site, const void* res_in, const void* gain, void* res_out,
+                              void* out, int64_t M, int64_t K, float eps, void* stream) {
+  if (!tp || !res_in || !gain || !out || site < 0) return CB_ERR_ARG;
+  if (M < 1 || K % 8 || K * 4 > 200 * 1024) return CB_ERR_SHAPE;
+  const size_t smem = (size_t)K * 4;
+  if (smem + 2048 > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(tp_pull_norm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+  }
+  const int threads = K >= 8192 ? 1024 : (K >= 2048 ? 512 : 256);
+  return (int)cb_launch(tp_pull_norm_kernel, dim3((unsigned)M), dim3(threads), smem, (cudaStream_t)stream,
+                        *(const TpComm*)tp, (int)site, (const bf16*)res_in, (const float*)gain, (bf16*)res_out,
+                        (bf16*)out, K, eps);
+}

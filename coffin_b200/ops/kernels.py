@@ -141,6 +141,23 @@ NORM_SPLIT_ROWS = 2
 _norm_scratch: dict[tuple, torch.Tensor] = {}
 
 
+# Tensor-parallel decode: the partial sums of the previous row-parallel projection are pulled, added to
+# the residual and normalised once per row by a one-CTA kernel; the projection then copies the result.
+# (Pulling inside the projection made every one of its CTAs read world x K pairs.)
+TP_PULL_SPLIT = True
+
+
+def _pull_norm_rows(tp, site: int, res_in: torch.Tensor, gain: torch.Tensor, res_out, eps: float) -> torch.Tensor:
+    M, K = res_in.shape
+    key = (M, K, res_in.device.index)
+    buf = _norm_scratch.get(key)
+    if buf is None:
+        buf = _norm_scratch[key] = torch.empty(M, K, dtype=torch.bfloat16, device=res_in.device)
+    call("tp_pull_norm", tp.cstruct_ref(), site, res_in, gain, res_out, buf, M, K, float(eps))
+    _count()
+    return buf
+
+
 def _norm_rows(res_in: torch.Tensor, add, gain: torch.Tensor, res_out, eps: float) -> torch.Tensor:
     """``rmsnorm(res_in + add) * gain`` into a per-shape scratch (stream-ordered reuse); ``res_out``
     receives the sum, as the fused prologue would have written it."""
@@ -181,7 +198,11 @@ def gemv(W: torch.Tensor, x: torch.Tensor | None, out: torch.Tensor | None, *, s
         res_in, add, gain, res_out, eps = norm
         assert res_in.is_contiguous() and res_in.shape == (M, K)
         x = None
-    if norm is not None and M >= NORM_SPLIT_ROWS and pull_site < 0:
+    if norm is not None and pull_site >= 0 and TP_PULL_SPLIT:
+        x, res_in, add, gain, res_out = _pull_norm_rows(tp, pull_site, res_in, gain, res_out, eps), None, None, None, None
+        pull_site = -1
+        tpp = tp.cstruct_ref() if push_site >= 0 else None
+    elif norm is not None and M >= NORM_SPLIT_ROWS and pull_site < 0:
         x, res_in, add, gain, res_out = _norm_rows(res_in, add, gain, res_out, eps), None, None, None, None
     if GEMV_IMPL == "mma" and M * K * 2 <= 160 * 1024:
         call("gemv_mma_bf16", W, x, out, M, N, K, ldy, mode, N, res_in, add, gain, res_out, float(eps), tpp,
@@ -215,7 +236,11 @@ def gemv_i8(Wq: torch.Tensor, wscale: torch.Tensor, x: torch.Tensor | None, out:
     else:
         res_in, add, gain, res_out, eps = norm
         x = None
-        if M >= NORM_SPLIT_ROWS and pull_site < 0:
+        if pull_site >= 0 and TP_PULL_SPLIT:
+            x, res_in, add, gain, res_out = _pull_norm_rows(tp, pull_site, res_in, gain, res_out, eps), None, None, None, None
+            pull_site = -1
+            tpp = tp.cstruct_ref() if push_site >= 0 else None
+        elif M >= NORM_SPLIT_ROWS and pull_site < 0:
             x, res_in, add, gain, res_out = _norm_rows(res_in, add, gain, res_out, eps), None, None, None, None
     call("gemv_i8", Wq, wscale, x, out, M, N, K, ldy, mode, N, res_in, add, gain, res_out, float(eps), tpp,
          pull_site, push_site)
