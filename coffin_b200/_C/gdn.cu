@@ -178,7 +178,7 @@ __global__ void __launch_bounds__(4 * DV) gdn_commit_kernel(float* state, const 
 
 // ---------------------------------------------------------------------------------------
 // Prefill prep: conv + SiLU, q/k normalisation, beta and g for a chunk of tokens.
-constexpr int kPrepTok = 8;   // tokens per CTA of the prefill prep kernel
+constexpr int kPrepTok = 4;   // tokens per CTA of the prefill prep kernel (512 CTAs for a 2048-token chunk)
 struct GdnPrepArgs {
   const bf16* proj; int64_t ldp;
   const float* conv_w; const float* A_log; const float* dt_bias;
