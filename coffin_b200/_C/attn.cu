@@ -325,8 +325,10 @@ __device__ __forceinline__ float bf_hi(uint32_t w) { return __uint_as_float(w & 
 // and the last split of the (row, kv head) group to arrive merges all partials with every thread
 // owning four channels of one head (independent float4 loads, scales staged in shared memory),
 // applies the sigmoid gate and writes the bf16 output.
-template <int HD, int REP, bool SPARSE>
-__global__ void __launch_bounds__(kDecWarps * 32) attn_decode_kernel(const DecodeArgs a) {
+// MINB = 2 compiles the same kernel for two resident CTAs per SM (128 registers): a batch of rows
+// launches far more CTAs than SMs, and throughput then wants residency more than the last register.
+template <int HD, int REP, bool SPARSE, int MINB = 1>
+__global__ void __launch_bounds__(kDecWarps * 32, MINB) attn_decode_kernel(const DecodeArgs a) {
   constexpr int EPL = HD / 32;
   constexpr int NT = kDecWarps * 32;
   __shared__ float q_s[REP][HD];
@@ -593,6 +595,9 @@ template <int HD, int REP>
 int launch_decode(const DecodeArgs& a, int M, cudaStream_t st) {
   if (a.sel)
     return (int)cb_launch(attn_decode_kernel<HD, REP, true>, dim3((unsigned)a.nkv, (unsigned)a.nsplit, (unsigned)M),
+                          dim3(kDecWarps * 32), 0, st, a);
+  if ((int64_t)a.nkv * a.nsplit * M > 2 * 148)
+    return (int)cb_launch(attn_decode_kernel<HD, REP, false, 2>, dim3((unsigned)a.nkv, (unsigned)a.nsplit, (unsigned)M),
                           dim3(kDecWarps * 32), 0, st, a);
   return (int)cb_launch(attn_decode_kernel<HD, REP, false>, dim3((unsigned)a.nkv, (unsigned)a.nsplit, (unsigned)M),
                         dim3(kDecWarps * 32), 0, st, a);

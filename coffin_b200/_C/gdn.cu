@@ -40,8 +40,10 @@ struct GdnDecodeArgs {
   float eps;
 };
 
-template <int DK, int DV>
-__global__ void __launch_bounds__(4 * DV) gdn_decode_kernel(const GdnDecodeArgs a) {
+// MINB = 2: the same kernel compiled for two resident CTAs per SM, used when a batch of rows
+// launches many more CTAs than there are SMs.
+template <int DK, int DV, int MINB = 1>
+__global__ void __launch_bounds__(4 * DV, MINB) gdn_decode_kernel(const GdnDecodeArgs a) {
   constexpr int G = 4, RPT = DK / G, NT = 4 * DV;
   __shared__ float q_s[DK], k_s[DK], v_s[DV];
   __shared__ float sk[G][DV], sq[G][DV];
@@ -977,6 +979,8 @@ CB_EXPORT int cb_gdn_decode(const void* proj, int64_t ldp, const void* conv_w, c
   a.out = (bf16*)out; a.ldo = ldo; a.record = (float*)record; a.rec_w = (int)rec_w; a.ntok = (int)ntok;
   a.write_state = (int)write_state; a.nk = (int)nk; a.nv = (int)nv; a.rep = (int)(nv / nk); a.eps = eps;
   dim3 grid((unsigned)nv, (unsigned)M);
+  if (dk == 128 && dv == 128 && nv * M > 2 * 148)
+    return (int)cb_launch(gdn_decode_kernel<128, 128, 2>, grid, dim3(512), 0, (cudaStream_t)stream, a);
   if (dk == 128 && dv == 128) return (int)cb_launch(gdn_decode_kernel<128, 128>, grid, dim3(512), 0, (cudaStream_t)stream, a);
   if (dk == 64 && dv == 64) return (int)cb_launch(gdn_decode_kernel<64, 64>, grid, dim3(256), 0, (cudaStream_t)stream, a);
   return CB_ERR_SHAPE;

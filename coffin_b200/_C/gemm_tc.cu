@@ -39,6 +39,10 @@ struct GemmArgs {
   // kernel of the same step.  Tile i covers rows [g_row0[i], g_row0[i] + g_rows[i]) of A and C and
   // multiplies them by expert g_expert[i]'s [N, K] block of the weight stack.
   const int* g_count; const int* g_row0; const int* g_rows; const int* g_expert;
+  // split-K for products with few rows (batched decode): `splits` CTAs share one output tile, each
+  // multiplies a K slice and leaves an fp32 partial tile in `ws`; the last one to arrive (ticket)
+  // adds the partials in slice order and writes the result, so the sum does not depend on timing.
+  int splits; float* ws; unsigned* tickets;
 };
 struct TileCoord { int m0, row_end, n0, brow; };
 template <int BN>
@@ -88,6 +92,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   __shared__ uint64_t full_bar[STAGES], empty_bar[STAGES], acc_full[2], acc_empty[2];
   __shared__ uint32_t tmem_base_s;
   __shared__ int abort_s;
+  __shared__ bool split_last_s;
   volatile int* abort_flag = &abort_s;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -112,14 +117,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 
   int m_tiles = a.m_tiles;
   if (a.g_count) { m_tiles = *a.g_count; if (m_tiles > a.m_tiles) m_tiles = a.m_tiles; }   // a.m_tiles: list capacity
-  const int total = m_tiles * a.n_tiles;
+  const int splits = a.splits > 1 ? a.splits : 1;
+  const int kper = (a.k_blocks + splits - 1) / splits;            // k-blocks per slice
+  const int total = m_tiles * a.n_tiles * splits;                  // work item = (tile, K slice), slice fastest
   if (warp == 0) {
     // ------------------------------- TMA producer -----------------------------------------
     if (lane == 0) {
       uint32_t it = 0;
       for (int tile = blockIdx.x; tile < total && !*abort_flag; tile += gridDim.x) {
-        const TileCoord tc = tile_coord<BN>(a, tile, m_tiles);
-        for (int kb = 0; kb < a.k_blocks; ++kb, ++it) {
+        const TileCoord tc = tile_coord<BN>(a, tile / splits, m_tiles);
+        const int kb0 = (tile % splits) * kper, kb1 = min(a.k_blocks, kb0 + kper);
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
           if (!wait_bar(&empty_bar[s], ph ^ 1, abort_flag)) { atomicExch(a.status, 1); abort_s = 1; break; }
@@ -140,7 +148,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
         bool ok = true;
-        for (int kb = 0; kb < a.k_blocks; ++kb, ++it) {
+        const int kb0 = (tile % splits) * kper, kb1 = min(a.k_blocks, kb0 + kper);
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
           if (!wait_bar(&full_bar[s], ph, abort_flag)) { atomicExch(a.status, 3); abort_s = 1; ok = false; break; }
@@ -150,8 +159,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 #pragma unroll
           for (int k = 0; k < BK / UK; ++k) {
             // advance 32 bytes along K inside the 128-byte swizzle atom: +2 in 16-byte units
-            if (I8) umma_i8(d_tmem, ad + 2 * k, bd + 2 * k, IDESC, (kb | k) != 0);
-            else umma_f16(d_tmem, ad + 2 * k, bd + 2 * k, IDESC, (kb | k) != 0);
+            if (I8) umma_i8(d_tmem, ad + 2 * k, bd + 2 * k, IDESC, ((kb - kb0) | k) != 0);
+            else umma_f16(d_tmem, ad + 2 * k, bd + 2 * k, IDESC, ((kb - kb0) | k) != 0);
           }
           umma_commit(&empty_bar[s]);
         }
@@ -164,13 +173,79 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     const int q = warp & 3;  // TMEM lane quadrant this warp may read
     uint32_t tcount = 0;
     for (int tile = blockIdx.x; tile < total && !*abort_flag; tile += gridDim.x, ++tcount) {
-      const TileCoord tc = tile_coord<BN>(a, tile, m_tiles);
+      const int otile = tile / splits, ksl = tile % splits;
+      const TileCoord tc = tile_coord<BN>(a, otile, m_tiles);
       const int m0 = tc.m0, n0 = tc.n0, row_end = tc.row_end;
       const uint32_t acc = tcount & 1, aph = (tcount >> 1) & 1;
       if (!wait_bar(&acc_full[acc], aph, abort_flag)) { if (lane == 0) { atomicExch(a.status, 4); abort_s = 1; } break; }
       tc_fence_after();
       const int row = m0 + q * 32 + lane;
       const float rs = (I8 && row < row_end) ? a.row_scale[row] : 1.f;
+      if (splits > 1) {
+        // ---- K slice: park the fp32 partial tile, the last slice to arrive reduces all of them ----
+        float* mine = a.ws + ((size_t)tile * BM + q * 32 + lane) * BN;
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += 32) {
+          uint32_t r[32];
+          tmem_ld32(tmem_base + acc * BN + ((uint32_t)(q * 32) << 16) + c0, r);
+          tmem_ld_wait();
+          if (row < row_end && n0 + c0 < a.N) {
+#pragma unroll
+            for (int v = 0; v < 8; ++v) {
+              float4 f;
+              if (I8) f = make_float4((float)(int)r[4 * v], (float)(int)r[4 * v + 1], (float)(int)r[4 * v + 2], (float)(int)r[4 * v + 3]);
+              else f = make_float4(__uint_as_float(r[4 * v]), __uint_as_float(r[4 * v + 1]), __uint_as_float(r[4 * v + 2]), __uint_as_float(r[4 * v + 3]));
+              __stcg(reinterpret_cast<float4*>(mine + c0) + v, f);
+            }
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&acc_empty[acc]);
+        __threadfence();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (warp == 2 && lane == 0) {
+          const unsigned prev = atomicAdd(a.tickets + otile, 1u);
+          split_last_s = prev == (unsigned)splits - 1;
+          if (split_last_s) a.tickets[otile] = 0;
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (split_last_s) {
+          __threadfence();
+          // all 128 epilogue threads walk the tile's valid rows as float4 columns (coalesced), adding
+          // the slices in slice order
+          const int et = (warp - 2) * 32 + lane;
+          const int nrow = min(BM, row_end - m0), ncol4 = min(BN, a.N - n0) >> 2;
+          const float* base = a.ws + (size_t)otile * splits * BM * BN;
+#pragma unroll 2
+          for (int e = et; e < nrow * ncol4; e += 128) {
+            const int r = e / ncol4, c = (e % ncol4) * 4;
+            float4 f = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int sidx = 0; sidx < splits; ++sidx) {
+              const float4 x = __ldcg(reinterpret_cast<const float4*>(base + ((size_t)sidx * BM + r) * BN + c));
+              f.x += x.x; f.y += x.y; f.z += x.z; f.w += x.w;
+            }
+            const int grow = m0 + r, gcol = n0 + c;
+            if (I8) {
+              const float rsr = a.row_scale[grow];
+              f.x *= rsr * a.col_scale[gcol]; f.y *= rsr * a.col_scale[gcol + 1];
+              f.z *= rsr * a.col_scale[gcol + 2]; f.w *= rsr * a.col_scale[gcol + 3];
+            }
+            if (a.residual) {
+              const uint2 rr = *reinterpret_cast<const uint2*>(a.residual + (int64_t)grow * a.ldr + gcol);
+              f.x += __uint_as_float(rr.x << 16); f.y += __uint_as_float(rr.x & 0xffff0000u);
+              f.z += __uint_as_float(rr.y << 16); f.w += __uint_as_float(rr.y & 0xffff0000u);
+            }
+            const __nv_bfloat162 lo = __floats2bfloat162_rn(f.x, f.y), hi = __floats2bfloat162_rn(f.z, f.w);
+            uint2 o;
+            o.x = *reinterpret_cast<const uint32_t*>(&lo);
+            o.y = *reinterpret_cast<const uint32_t*>(&hi);
+            *reinterpret_cast<uint2*>(reinterpret_cast<bf16*>(a.C) + (int64_t)grow * a.ldc + gcol) = o;
+          }
+        }
+        (void)ksl;
+        continue;
+      }
 #pragma unroll 1
       for (int c0 = 0; c0 < BN; c0 += 32) {
         uint32_t r[32];
@@ -235,7 +310,7 @@ int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, GemmArgs a, int 
   auto kern = gemm_tc_kernel<BN, STAGES, I8>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return (int)e;
-  const int total = a.m_tiles * a.n_tiles;
+  const int total = a.m_tiles * a.n_tiles * (a.splits > 1 ? a.splits : 1);
   const int grid = total < sms ? total : sms;
   return (int)cb_launch(kern, dim3((unsigned)grid), dim3(kThreadsGemm), smem, st, tmA, tmB, a);
 }
@@ -295,6 +370,7 @@ CB_EXPORT int cb_gemm_bf16(const void* A, int64_t lda, const void* W, int64_t ld
   a.k_blocks = (int)((K + 63) / 64); a.status = (int*)status;
   a.pf = (const TpPfDev*)pf; a.pf_seq = (unsigned)pf_seq;
   a.g_count = a.g_row0 = a.g_rows = a.g_expert = nullptr;
+  a.splits = 1; a.ws = nullptr; a.tickets = nullptr;
   cudaStream_t st = (cudaStream_t)stream;
   if (bn == 256) return launch_gemm<256, 4, false>(tmA, tmB, a, sms, st);
   if (bn == 160) return launch_gemm<160, 5, false>(tmA, tmB, a, sms, st);
@@ -326,6 +402,7 @@ CB_EXPORT int cb_gemm_i8(const void* A, int64_t lda, const void* W, int64_t ldw,
   a.k_blocks = (int)((K + 127) / 128); a.status = (int*)status;
   a.pf = (const TpPfDev*)pf; a.pf_seq = (unsigned)pf_seq;
   a.g_count = a.g_row0 = a.g_rows = a.g_expert = nullptr;
+  a.splits = 1; a.ws = nullptr; a.tickets = nullptr;
   cudaStream_t st = (cudaStream_t)stream;
   if (bn == 256) return launch_gemm<256, 4, true>(tmA, tmB, a, sms, st);
   if (bn == 160) return launch_gemm<160, 5, true>(tmA, tmB, a, sms, st);
@@ -357,8 +434,87 @@ CB_EXPORT int cb_gemm_bf16_grouped(const void* A, int64_t lda, const void* W, in
   a.k_blocks = (int)((K + 63) / 64); a.status = (int*)status;
   a.pf = nullptr; a.pf_seq = 0;
   a.g_count = (const int*)g_count; a.g_row0 = (const int*)g_row0; a.g_rows = (const int*)g_rows; a.g_expert = (const int*)g_expert;
+  a.splits = 1; a.ws = nullptr; a.tickets = nullptr;
   cudaStream_t st = (cudaStream_t)stream;
   if (bn == 256) return launch_gemm<256, 4, false>(tmA, tmB, a, sms, st);
   if (bn == 160) return launch_gemm<160, 5, false>(tmA, tmB, a, sms, st);
   return launch_gemm<128, 6, false>(tmA, tmB, a, sms, st);
+}
+
+// Skinny product for batched decode (M <= 128 rows: one m-tile): C = A x W^T (+ residual) with the K
+// dimension split over CTAs so that the whole machine streams the weights even when N gives only a
+// few 256-wide tiles (N = 2560: 10 tiles x 14 slices).  ws holds the fp32 partial tiles
+// (cb_gemm_splitk_ws_bytes), tickets one zero-initialised counter per output tile; both may be
+// shared by all calls of a stream.  Falls back to the plain kernel when splitting does not pay.
+namespace {
+// Tile width and slice count for a product of at most 128 rows.  Every (tile, slice) gets its own CTA
+// in a single wave; the estimate is the bytes one CTA moves into shared memory (its slice of W and of
+// the valid rows of A) plus what the last slice re-reads to add the partial tiles.
+void plan_split(int64_t M, int64_t N, int64_t K, int* bn_out, int* s_out) {
+  const int sms = sm_count();
+  const int64_t kb = (K + 63) / 64;
+  const int cand[3] = {256, 128, 64};
+  double best = 1e300;
+  *bn_out = 256; *s_out = 1;
+  for (int i = 0; i < 3; ++i) {
+    const int bn = cand[i];
+    const int64_t tiles = (N + bn - 1) / bn;
+    int64_t s = sms / tiles;
+    if (s > kb / 4) s = kb / 4;          // at least four k-blocks per slice
+    if (s > 32) s = 32;
+    if (s < 1) s = 1;
+    for (;;) {                           // no slice may be empty: s = ceil(kb / ceil(kb / s))
+      const int64_t kper = (kb + s - 1) / s, s2 = (kb + kper - 1) / kper;
+      if (s2 == s) break;
+      s = s2;
+    }
+    const int64_t waves = (tiles * s + sms - 1) / sms;
+    const double stream = (double)waves * (bn + M) * ((double)K / s) * 2.0 / 130e3;        // us at ~130 GB/s per SM
+    const double reduce = s > 1 ? (double)s * M * bn * 4.0 / 100e3 + 2.0 : 0.0;
+    const double cost = stream + reduce;
+    if (cost < best) { best = cost; *bn_out = bn; *s_out = (int)s; }
+  }
+}
+}  // namespace
+
+// (slices, or 1 when the plain kernel is used) and the workspace a call needs
+CB_EXPORT int64_t cb_gemm_splitk_plan(int64_t M, int64_t N, int64_t K) {
+  if (M > BM) return 1;
+  int bn, s;
+  plan_split(M, N, K, &bn, &s);
+  return s;
+}
+CB_EXPORT int64_t cb_gemm_splitk_ws_bytes(int64_t M, int64_t N, int64_t K) {
+  if (M > BM) return 0;
+  int bn, s;
+  plan_split(M, N, K, &bn, &s);
+  return s < 2 ? 0 : ((N + bn - 1) / bn) * s * BM * bn * (int64_t)sizeof(float);
+}
+CB_EXPORT int cb_gemm_bf16_splitk(const void* A, int64_t lda, const void* W, int64_t ldw, void* C, int64_t ldc,
+                                  const void* residual, int64_t ldr, int64_t M, int64_t N, int64_t K, void* ws,
+                                  int64_t ws_bytes, void* tickets, int64_t n_tickets, void* status, void* stream) {
+  if (M < 1 || M > BM || N < 1 || K < 1) return CB_ERR_SHAPE;
+  if (K % 8 || N % 8 || ldc % 8 || (residual && ldr % 8) || !status) return CB_ERR_SHAPE;
+  int bn, splits;
+  plan_split(M, N, K, &bn, &splits);
+  if (splits < 2) return cb_gemm_bf16(A, lda, W, ldw, C, ldc, residual, ldr, M, N, K, bn, nullptr, 0, status, stream);
+  const int64_t tiles = (N + bn - 1) / bn;
+  if (!ws || !tickets || ws_bytes < cb_gemm_splitk_ws_bytes(M, N, K) || n_tickets < tiles) return CB_ERR_ARG;
+  const int sms = sm_count();
+  CUtensorMap tmA, tmB;
+  int rc = cb_make_tmap_2d(&tmA, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, BM, 64);
+  if (rc) return rc;
+  rc = cb_make_tmap_2d(&tmB, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, W, (uint64_t)N, (uint64_t)K, (uint64_t)ldw, (uint32_t)bn, 64);
+  if (rc) return rc;
+  GemmArgs a;
+  a.C = C; a.ldc = ldc; a.residual = (const bf16*)residual; a.ldr = ldr; a.row_scale = nullptr; a.col_scale = nullptr;
+  a.M = (int)M; a.N = (int)N; a.K = (int)K; a.m_tiles = 1; a.n_tiles = 0;
+  a.k_blocks = (int)((K + 63) / 64); a.status = (int*)status;
+  a.pf = nullptr; a.pf_seq = 0;
+  a.g_count = a.g_row0 = a.g_rows = a.g_expert = nullptr;
+  a.splits = splits; a.ws = (float*)ws; a.tickets = (unsigned*)tickets;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (bn == 256) return launch_gemm<256, 4, false>(tmA, tmB, a, sms, st);
+  if (bn == 128) return launch_gemm<128, 6, false>(tmA, tmB, a, sms, st);
+  return launch_gemm<64, 8, false>(tmA, tmB, a, sms, st);
 }

@@ -8,6 +8,7 @@ at the granularity of the fused kernels, not op for op.
 from __future__ import annotations
 
 import math
+import os
 
 import torch
 
@@ -356,10 +357,33 @@ def gemm(A: torch.Tensor, W: torch.Tensor, out: torch.Tensor | None = None,
     if out is None:
         out = torch.empty(M, N, dtype=torch.bfloat16, device=A.device)
     assert out.stride(1) == 1
+    if M <= 128 and bn == 0 and SPLITK_GEMM:
+        ws, tickets = _splitk_scratch(A.device)
+        call("gemm_bf16_splitk", A, A.stride(0), W, W.stride(0), out, out.stride(0), residual,
+             residual.stride(0) if residual is not None else 0, M, N, K, ws, ws.numel() * 4, tickets, tickets.numel(),
+             status_word(A.device))
+        _count()
+        return out
     call("gemm_bf16", A, A.stride(0), W, W.stride(0), out, out.stride(0), residual,
          residual.stride(0) if residual is not None else 0, M, N, K, bn, None, 0, status_word(A.device))
     _count()
     return out
+
+
+# Products with at most 128 rows (batched decode buckets of 16..64 rows, small prefill chunks) split K
+# over CTAs: fp32 partial tiles in a per-device workspace, reduced by the last slice to arrive.
+SPLITK_GEMM = os.environ.get("COFFIN_SPLITK_GEMM", "1") != "0"
+_splitk: dict[int, tuple[torch.Tensor, torch.Tensor]] = {}
+
+
+def _splitk_scratch(device) -> tuple[torch.Tensor, torch.Tensor]:
+    idx = torch.device(device).index or 0      # one compute stream per device: its launches are ordered
+    s = _splitk.get(idx)
+    if s is None:
+        # 148 slice-tiles of 128 x 256 fp32 is the most one launch parks (tiles * slices <= SMs)
+        s = _splitk[idx] = (torch.empty(160 * 128 * 256, dtype=torch.float32, device=device),
+                            torch.zeros(4096, dtype=torch.int32, device=device))
+    return s
 
 
 def gemm_i8(Aq: torch.Tensor, a_scale: torch.Tensor, Wq: torch.Tensor, w_scale: torch.Tensor,

@@ -96,7 +96,9 @@ def test_gemv_fused_norm_swiglu(M, H, I):
 
 @pytest.mark.parametrize("M,N,Kd,bn", [(128, 256, 64, 256), (200, 264, 192, 128), (300, 520, 1032, 0),
                                        (64, 64, 256, 64), (1000, 1536, 512, 256), (130, 136, 72, 128),
-                                       (300, 520, 1032, 160), (2048, 2560, 1024, 0)])
+                                       (300, 520, 1032, 160), (2048, 2560, 1024, 0),
+                                       # at most 128 rows: K split over CTAs, partial tiles reduced by the last slice
+                                       (64, 2560, 4096, 0), (16, 12352, 2560, 0), (128, 520, 9216, 0), (5, 264, 520, 0)])
 def test_gemm_tcgen05(M, N, Kd, bn):
     k = K()
     A, W = bf(M, Kd, seed=10), bf(N, Kd, s=0.05, seed=11)
