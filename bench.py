@@ -227,6 +227,7 @@ def main() -> None:
                "d2h_bytes_per_step": (args.new + 1) * 8,
                "timing": "host wall clock around LLM.generate phases, prompt from pinned memory, "
                          "every token read back"}
+    wbytes = llm.model.weight_bytes() if hasattr(llm.model, "weight_bytes") else 0
     if rank == 0:
         line = {
             "metric": "decode_tok_s", "value": decode_tok_s, "unit": "tok/s", "n_gpus": world,
@@ -237,7 +238,7 @@ def main() -> None:
             "ttft_ms_p50": statistics.median(pre_ms), "tpot_ms_p50": statistics.median(dec_ms) / args.new,
             "config": {"model": args.model, "global_batch": 1, "seq_len": args.prompt, "decode_tokens": args.new,
                        "parallelism": f"tp{world}" if world > 1 else "single", "cuda_graph": not args.no_graph,
-                       "cache": "weights (7.9 GB) far exceed the 126 MB L2, no flush needed",
+                       "cache": f"weights on this rank ({wbytes / 1e9:.1f} GB, streamed every decode step; a routed-MoE step reads its dense part plus the selected experts) far exceed the 126 MB L2, no flush needed",
                        "weights": "random-init N(0,0.02)"},
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "wall_s": wall_s, "impl": "ours",
         }

@@ -450,13 +450,14 @@ namespace {
 // Tile width and slice count for a product of at most 128 rows.  Every (tile, slice) gets its own CTA
 // in a single wave; the estimate is the bytes one CTA moves into shared memory (its slice of W and of
 // the valid rows of A) plus what the last slice re-reads to add the partial tiles.
-void plan_split(int64_t M, int64_t N, int64_t K, int* bn_out, int* s_out) {
+// K is counted in bytes of a row (a k-block is 128 bytes); n_cand = 2 leaves out the 64-wide tile.
+void plan_split(int64_t M, int64_t N, int64_t Kbytes, int* bn_out, int* s_out, int n_cand = 3) {
   const int sms = sm_count();
-  const int64_t kb = (K + 63) / 64;
+  const int64_t kb = (Kbytes + 127) / 128, K = Kbytes / 2;
   const int cand[3] = {256, 128, 64};
   double best = 1e300;
   *bn_out = 256; *s_out = 1;
-  for (int i = 0; i < 3; ++i) {
+  for (int i = 0; i < n_cand; ++i) {
     const int bn = cand[i];
     const int64_t tiles = (N + bn - 1) / bn;
     int64_t s = sms / tiles;
@@ -481,13 +482,13 @@ void plan_split(int64_t M, int64_t N, int64_t K, int* bn_out, int* s_out) {
 CB_EXPORT int64_t cb_gemm_splitk_plan(int64_t M, int64_t N, int64_t K) {
   if (M > BM) return 1;
   int bn, s;
-  plan_split(M, N, K, &bn, &s);
+  plan_split(M, N, K * 2, &bn, &s);
   return s;
 }
 CB_EXPORT int64_t cb_gemm_splitk_ws_bytes(int64_t M, int64_t N, int64_t K) {
   if (M > BM) return 0;
   int bn, s;
-  plan_split(M, N, K, &bn, &s);
+  plan_split(M, N, K * 2, &bn, &s);
   return s < 2 ? 0 : ((N + bn - 1) / bn) * s * BM * bn * (int64_t)sizeof(float);
 }
 CB_EXPORT int cb_gemm_bf16_splitk(const void* A, int64_t lda, const void* W, int64_t ldw, void* C, int64_t ldc,
@@ -496,7 +497,7 @@ CB_EXPORT int cb_gemm_bf16_splitk(const void* A, int64_t lda, const void* W, int
   if (M < 1 || M > BM || N < 1 || K < 1) return CB_ERR_SHAPE;
   if (K % 8 || N % 8 || ldc % 8 || (residual && ldr % 8) || !status) return CB_ERR_SHAPE;
   int bn, splits;
-  plan_split(M, N, K, &bn, &splits);
+  plan_split(M, N, K * 2, &bn, &splits);
   if (splits < 2) return cb_gemm_bf16(A, lda, W, ldw, C, ldc, residual, ldr, M, N, K, bn, nullptr, 0, status, stream);
   const int64_t tiles = (N + bn - 1) / bn;
   if (!ws || !tickets || ws_bytes < cb_gemm_splitk_ws_bytes(M, N, K) || n_tickets < tiles) return CB_ERR_ARG;
@@ -517,4 +518,38 @@ CB_EXPORT int cb_gemm_bf16_splitk(const void* A, int64_t lda, const void* W, int
   if (bn == 256) return launch_gemm<256, 4, false>(tmA, tmB, a, sms, st);
   if (bn == 128) return launch_gemm<128, 6, false>(tmA, tmB, a, sms, st);
   return launch_gemm<64, 8, false>(tmA, tmB, a, sms, st);
+}
+
+// int8 (W8A8) form of the split-K product: int32 partial sums are parked as fp32 (exact up to 2^24 per
+// slice, then rounded like any fp32 sum) and the row x column scales are applied by the reducing slice.
+CB_EXPORT int cb_gemm_i8_splitk(const void* A, int64_t lda, const void* W, int64_t ldw, void* C, int64_t ldc,
+                                const void* residual, int64_t ldr, const void* row_scale, const void* col_scale,
+                                int64_t M, int64_t N, int64_t K, void* ws, int64_t ws_bytes, void* tickets,
+                                int64_t n_tickets, void* status, void* stream) {
+  if (M < 1 || M > BM || N < 1 || K < 1) return CB_ERR_SHAPE;
+  if (K % 16 || N % 8 || ldc % 8 || lda % 16 || ldw % 16 || (residual && ldr % 8) || !status || !row_scale || !col_scale)
+    return CB_ERR_SHAPE;
+  int bn, splits;
+  plan_split(M, N, K, &bn, &splits, 2);
+  if (splits < 2)
+    return cb_gemm_i8(A, lda, W, ldw, C, ldc, residual, ldr, row_scale, col_scale, M, N, K, bn, nullptr, 0, status, stream);
+  const int64_t tiles = (N + bn - 1) / bn;
+  if (!ws || !tickets || ws_bytes < tiles * splits * BM * bn * (int64_t)sizeof(float) || n_tickets < tiles) return CB_ERR_ARG;
+  const int sms = sm_count();
+  CUtensorMap tmA, tmB;
+  int rc = cb_make_tmap_2d(&tmA, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, BM, 128);
+  if (rc) return rc;
+  rc = cb_make_tmap_2d(&tmB, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, W, (uint64_t)N, (uint64_t)K, (uint64_t)ldw, (uint32_t)bn, 128);
+  if (rc) return rc;
+  GemmArgs a;
+  a.C = C; a.ldc = ldc; a.residual = (const bf16*)residual; a.ldr = ldr;
+  a.row_scale = (const float*)row_scale; a.col_scale = (const float*)col_scale;
+  a.M = (int)M; a.N = (int)N; a.K = (int)K; a.m_tiles = 1; a.n_tiles = 0;
+  a.k_blocks = (int)((K + 127) / 128); a.status = (int*)status;
+  a.pf = nullptr; a.pf_seq = 0;
+  a.g_count = a.g_row0 = a.g_rows = a.g_expert = nullptr;
+  a.splits = splits; a.ws = (float*)ws; a.tickets = (unsigned*)tickets;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (bn == 256) return launch_gemm<256, 4, true>(tmA, tmB, a, sms, st);
+  return launch_gemm<128, 6, true>(tmA, tmB, a, sms, st);
 }

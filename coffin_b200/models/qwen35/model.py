@@ -719,8 +719,6 @@ class Qwen35Model:
         """Run one decode step on the staged rows. Returns ``(next_tokens [M], logits [M, V])``
         device tensors owned by the bucket (overwritten by the next step)."""
         b = self._row_buffers(M)
-        if graph and self.cfg.is_moe and M > 32:
-            graph = False          # the sorted expert path reads the per-expert counts on the host
         if graph:
             if (M, self.lane) not in self._graphs:
                 self.capture(M)

@@ -179,7 +179,7 @@ class MoEWeights:
         c = self.cfg
         T = normed.shape[0]
         E, k, H, I = c.num_experts, c.num_experts_per_tok, c.hidden_size, c.moe_intermediate_size
-        if T <= 32:
+        if T <= (64 if self.w4 else 32):      # W4 stacks would have to be expanded to bf16 for the grouped GEMM
             b = self._b(T, normed.device)
             b["normed"][:T].copy_(normed)
             out = torch.empty(T, H, dtype=torch.bfloat16, device=normed.device)

@@ -399,6 +399,13 @@ def gemm_i8(Aq: torch.Tensor, a_scale: torch.Tensor, Wq: torch.Tensor, w_scale: 
         return None
     if out is None:
         out = torch.empty(M, N, dtype=torch.bfloat16, device=Aq.device)
+    if M <= 128 and bn == 0 and SPLITK_GEMM:
+        ws, tickets = _splitk_scratch(Aq.device)
+        call("gemm_i8_splitk", Aq, Aq.stride(0), Wq, Wq.stride(0), out, out.stride(0), residual,
+             residual.stride(0) if residual is not None else 0, a_scale, w_scale, M, N, K, ws, ws.numel() * 4, tickets,
+             tickets.numel(), status_word(Aq.device))
+        _count()
+        return out
     call("gemm_i8", Aq, Aq.stride(0), Wq, Wq.stride(0), out, out.stride(0), residual,
          residual.stride(0) if residual is not None else 0, a_scale, w_scale, M, N, K, bn, None, 0,
          status_word(Aq.device))
