@@ -138,7 +138,7 @@ def block_copy(dst: torch.Tensor, src: torch.Tensor, dst_idx: torch.Tensor, src_
 # (hundreds of CTAs x M rows of conversions), which at M >= 2 costs more issue slots than the weight
 # stream leaves free.  From this many rows on, the rows are normalised once by a small kernel and the
 # projection copies them.
-NORM_SPLIT_ROWS = 2
+NORM_SPLIT_ROWS = int(os.environ.get("COFFIN_NORM_SPLIT_ROWS", "2"))
 _norm_scratch: dict[tuple, torch.Tensor] = {}
 
 
