@@ -99,6 +99,8 @@ def main() -> None:
     ap.add_argument("--prompt", type=int, default=PROMPT)
     ap.add_argument("--new", type=int, default=NEW)
     ap.add_argument("--quant", default="none", choices=["none", "int8", "w4a8"])
+    ap.add_argument("--parallel", default="tp", choices=["tp", "ep"],
+                    help="N > 1: tensor parallel (default) or expert parallel (routed-MoE models)")
     ap.add_argument("--rows", type=int, default=1,
                     help="concurrent sequences: > 1 measures batched decode throughput (not the headline config)")
     ap.add_argument("--no-graph", action="store_true")
@@ -159,8 +161,9 @@ def main() -> None:
     if args.rows > 1:
         return bench_rows(args, cfg, W)
     llm = LLM.from_random(cfg, seed=0, max_seq=args.prompt + args.new + 64, max_num_seqs=1,
-                          tp_world=world, tp_rank=rank, graph=not args.no_graph, pdl=not args.no_pdl,
-                          max_chunk=args.prompt, quant=args.quant)
+                          graph=not args.no_graph, pdl=not args.no_pdl, max_chunk=args.prompt, quant=args.quant,
+                          **({"ep_world": world, "ep_rank": rank} if args.parallel == "ep" and world > 1
+                             else {"tp_world": world, "tp_rank": rank}))
     model = llm.model
     g = torch.Generator().manual_seed(1234)
     prompts = [torch.randint(0, cfg.vocab_size, (args.prompt,), generator=g).pin_memory()
@@ -237,7 +240,7 @@ def main() -> None:
             "prefill_tok_s": prefill_tok_s, "prefill_vs_baseline": prefill_tok_s / BASELINE_PREFILL_TOK_S,
             "ttft_ms_p50": statistics.median(pre_ms), "tpot_ms_p50": statistics.median(dec_ms) / args.new,
             "config": {"model": args.model, "global_batch": 1, "seq_len": args.prompt, "decode_tokens": args.new,
-                       "parallelism": f"tp{world}" if world > 1 else "single", "cuda_graph": not args.no_graph,
+                       "parallelism": f"{args.parallel}{world}" if world > 1 else "single", "cuda_graph": not args.no_graph,
                        "cache": f"weights on this rank ({wbytes / 1e9:.1f} GB, streamed every decode step; a routed-MoE step reads its dense part plus the selected experts) far exceed the 126 MB L2, no flush needed",
                        "weights": "random-init N(0,0.02)"},
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "wall_s": wall_s, "impl": "ours",

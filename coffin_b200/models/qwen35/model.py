@@ -286,9 +286,15 @@ class Qwen35Model:
         if isinstance(W, QW):
             return K.gemv_i8(W.wq, W.scale, x, out, **kw)
         if isinstance(W, QW4):
-            if kw.get("tp") is not None and (kw.get("pull_site", -1) >= 0 or kw.get("push_site", -1) >= 0):
-                raise NotImplementedError("W4A8 projections do not take part in the tensor-parallel push/pull")
-            return K.gemv_w4(W.wq, W.scale, x, out, swiglu=kw.get("swiglu", False), norm=kw.get("norm"))
+            if kw.get("tp") is not None and kw.get("push_site", -1) >= 0:
+                raise NotImplementedError("W4A8 projections do not push tensor-parallel partial sums")
+            norm = kw.get("norm")
+            if kw.get("tp") is not None and kw.get("pull_site", -1) >= 0:
+                # expert parallel: the sum pushed by the MoE combine is pulled, added and normalised by
+                # the one-CTA kernel; the W4 projection then takes plain rows
+                res_in, _add, gain, res_out, eps = norm
+                x, norm = K._pull_norm_rows(kw["tp"], kw["pull_site"], res_in, gain, res_out, eps), None
+            return K.gemv_w4(W.wq, W.scale, x, out, swiglu=kw.get("swiglu", False), norm=norm)
         return K.gemv(W, x, out, **kw)
 
     def _gemm(self, A, W, out=None, residual=None, swiglu_in: bool = False, push=None):
