@@ -237,9 +237,20 @@ __global__ void __launch_bounds__(kT, 3) gemv_mma_kernel(const MmaArgs a_in) {
     }
   } else {
     const int64_t lc = xs_ld >> 3;                     // chunks staged per row
-    for (int64_t i = tid; i < (int64_t)M * lc; i += nT) {
-      const int64_t m = i / lc, c = xs_c0 + i % lc;
-      if (c < nchunk) *reinterpret_cast<uint4*>(xs + i * 8) = *reinterpret_cast<const uint4*>(a.x + (m * nchunk + c) * 8);
+    // asynchronous 16-byte copies: a thread's share (tens of chunks when several rows are staged) is
+    // in flight at once instead of one L2 round trip per chunk
+    if ((int64_t)M * lc > 4 * nT) {
+      for (int64_t i = tid; i < (int64_t)M * lc; i += nT) {
+        const int64_t m = i / lc, c = xs_c0 + i % lc;
+        if (c < nchunk) cp_async16(xs + i * 8, a.x + (m * nchunk + c) * 8);
+      }
+      cp_async_commit();
+      cp_async_wait_all_();
+    } else {
+      for (int64_t i = tid; i < (int64_t)M * lc; i += nT) {
+        const int64_t m = i / lc, c = xs_c0 + i % lc;
+        if (c < nchunk) *reinterpret_cast<uint4*>(xs + i * 8) = *reinterpret_cast<const uint4*>(a.x + (m * nchunk + c) * 8);
+      }
     }
   }
   __syncthreads();
