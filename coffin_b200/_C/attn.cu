@@ -591,6 +591,179 @@ __global__ void __launch_bounds__(kDecWarps * 32, MINB) attn_decode_kernel(const
   }
 }
 
+// ------------------------------------------------------------------------------------------
+// Decode attention for a batch of rows on the tensor cores.  The kernel above is built for the
+// latency of one sequence (many key splits, scalar dot products with warp shuffles) and becomes issue
+// bound when every row brings its own CTAs.  Here one CTA serves one (row, kv head): the REP query
+// heads of the kv head are rows 0..REP-1 of a 16-row mma tile (the rest zero), the four warps take 16
+// keys each of every 64-key tile (S = Q K^T and O += P V as bf16 mma.m16n8k16 from ldmatrix
+// fragments, tiles staged with cp.async), keep their own running maximum and sum, and merge once at
+// the end.  Query / key normalisation, rotary embedding, the KV append of the current token and the
+// sigmoid output gate are part of the kernel as in the single-sequence one.
+template <int HD>
+__global__ void __launch_bounds__(128, 2) attn_decode_batch_kernel(const DecodeArgs a) {
+  constexpr int LD = HD + 8, EPL = HD / 32, CPR = HD / 8;
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  bf16* Qs = reinterpret_cast<bf16*>(smem_raw);   // [16][LD]
+  bf16* Ks = Qs + 16 * LD;                        // [64][LD]
+  bf16* Vs = Ks + 64 * LD;                        // [64][LD]
+  bf16* kcur = Vs + 64 * LD;                      // [HD] this token's key (normed, rotated)
+  bf16* vcur = kcur + HD;                         // [HD]
+  float* mo = reinterpret_cast<float*>(Ks);       // after the loop: [4 warps][8 rows][HD] partial outputs
+  __shared__ float mm_s[4][8], ml_s[4][8];
+  const int kvh = blockIdx.x, m = blockIdx.y, rep = a.nh / a.nkv;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, tq = lane & 3;
+  griddep_launch();
+  griddep_wait();
+  const int pos = a.positions[m];
+  if (pos < 0) return;                            // padded row
+  const bf16* prow = a.proj + (int64_t)m * a.ldp;
+  const int rp = a.rope_pos[m];
+  const float* cs = a.cos + (int64_t)rp * a.rot;
+  const float* sn = a.sin + (int64_t)rp * a.rot;
+  const int* bt = a.block_table + (int64_t)m * a.ldbt;
+  // ---- prologue: q heads -> Qs (bf16), this token's K / V -> pool and shared copies ---------------
+  for (int idx = tid; idx < 16 * CPR; idx += 128)
+    *reinterpret_cast<uint4*>(Qs + (idx / CPR) * LD + (idx % CPR) * 8) = make_uint4(0, 0, 0, 0);
+  __syncthreads();
+  for (int r = warp; r < rep + 2; r += 4) {
+    float x[EPL];
+    if (r < rep) {
+      const bf16* src = prow + (int64_t)(kvh * rep + r) * 2 * HD + lane * EPL;
+#pragma unroll
+      for (int e = 0; e < EPL; ++e) x[e] = __bfloat162float(src[e]);
+      norm_rope_lane<HD>(x, a.qg, cs, sn, a.rot, a.eps, lane);
+#pragma unroll
+      for (int e = 0; e < EPL; ++e) Qs[r * LD + lane * EPL + e] = __float2bfloat16(x[e]);
+    } else {
+      const int64_t slot = (int64_t)bt[pos / kBlock] * kBlock + pos % kBlock;
+      if (r == rep) {
+        const bf16* src = prow + (int64_t)a.nh * 2 * HD + (int64_t)kvh * HD + lane * EPL;
+#pragma unroll
+        for (int e = 0; e < EPL; ++e) x[e] = __bfloat162float(src[e]);
+        norm_rope_lane<HD>(x, a.kg, cs, sn, a.rot, a.eps, lane);
+        bf16* dst = a.kpool + (slot * a.nkv + kvh) * HD + lane * EPL;
+#pragma unroll
+        for (int e = 0; e < EPL; ++e) { const bf16 v = __float2bfloat16(x[e]); dst[e] = v; kcur[lane * EPL + e] = v; }
+      } else {
+        const bf16* src = prow + (int64_t)a.nh * 2 * HD + (int64_t)(a.nkv + kvh) * HD + lane * EPL;
+        bf16* dst = a.vpool + (slot * a.nkv + kvh) * HD + lane * EPL;
+#pragma unroll
+        for (int e = 0; e < EPL; ++e) { dst[e] = src[e]; vcur[lane * EPL + e] = src[e]; }
+      }
+    }
+  }
+  float o[HD / 8][2];                             // rows g (< 8) only: rows 8..15 of the tile are padding
+#pragma unroll
+  for (int n = 0; n < HD / 8; ++n) o[n][0] = o[n][1] = 0.f;
+  float mrow = -INFINITY, lrow = 0.f;
+  const int ntiles = pos / kBlock + 1;
+  for (int kt = 0; kt < ntiles; ++kt) {
+    __syncthreads();                              // previous tile consumed; prologue stores visible
+    const int64_t slot0 = (int64_t)bt[kt] * kBlock;
+    for (int idx = tid; idx < 64 * CPR; idx += 128) {
+      const int r = idx / CPR, c = idx % CPR;
+      const int64_t off = ((slot0 + r) * a.nkv + kvh) * HD + c * 8;
+      cp_async16(Ks + r * LD + c * 8, a.kpool + off);
+      cp_async16(Vs + r * LD + c * 8, a.vpool + off);
+    }
+    cp_async_wait_all();
+    __syncthreads();
+    if (kt == ntiles - 1) {                       // the current token's row comes from this CTA, not from memory
+      for (int c = tid; c < 2 * CPR; c += 128) {
+        const bool isv = c >= CPR;
+        const int cc = isv ? c - CPR : c;
+        *reinterpret_cast<uint4*>((isv ? Vs : Ks) + (pos % kBlock) * LD + cc * 8) =
+            *reinterpret_cast<const uint4*>((isv ? vcur : kcur) + cc * 8);
+      }
+      __syncthreads();
+    }
+    // ---- S = Q K^T for this warp's 16 keys ---------------------------------------------------
+    float sc[2][4];
+#pragma unroll
+    for (int n = 0; n < 2; ++n) sc[n][0] = sc[n][1] = sc[n][2] = sc[n][3] = 0.f;
+#pragma unroll 4
+    for (int kk = 0; kk < HD / 16; ++kk) {
+      uint32_t af[4], b0, b1, b2, b3;
+      ldsm_x4(af[0], af[1], af[2], af[3], Qs + (lane & 15) * LD + kk * 16 + (lane >> 4) * 8);
+      ldsm_x4(b0, b1, b2, b3, Ks + (warp * 16 + (lane & 7) + ((lane >> 4) << 3)) * LD + kk * 16 + ((lane >> 3) & 1) * 8);
+      mma_bf16(sc[0], af, b0, b1);
+      mma_bf16(sc[1], af, b2, b3);
+    }
+    // ---- mask + online softmax (base 2), row g of the tile --------------------------------------
+    float mnew = mrow;
+#pragma unroll
+    for (int n = 0; n < 2; ++n)
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const int key = kt * kBlock + warp * 16 + n * 8 + tq * 2 + e;
+        const float v = key <= pos ? sc[n][e] * a.scale_log2 : -INFINITY;
+        sc[n][e] = v;
+        mnew = fmaxf(mnew, v);
+      }
+    mnew = fmaxf(mnew, __shfl_xor_sync(0xffffffffu, mnew, 1));
+    mnew = fmaxf(mnew, __shfl_xor_sync(0xffffffffu, mnew, 2));
+    const float msafe = (mnew == -INFINITY) ? 0.f : mnew;
+    const float corr = exp2f(mrow - msafe);
+    mrow = mnew;
+    const float p0 = exp2f(sc[0][0] - msafe), p1 = exp2f(sc[0][1] - msafe);
+    const float p2 = exp2f(sc[1][0] - msafe), p3 = exp2f(sc[1][1] - msafe);
+    lrow = lrow * corr + p0 + p1 + p2 + p3;
+    uint32_t pf[4];
+    pf[0] = pack_bf162(p0, p1);
+    pf[1] = 0u;                                   // rows 8..15
+    pf[2] = pack_bf162(p2, p3);
+    pf[3] = 0u;
+#pragma unroll
+    for (int n = 0; n < HD / 8; ++n) { o[n][0] *= corr; o[n][1] *= corr; }
+    // ---- O += P V for the same 16 keys -------------------------------------------------------------
+#pragma unroll
+    for (int np = 0; np < HD / 16; ++np) {
+      uint32_t b0, b1, b2, b3;
+      ldsm_x4_t(b0, b1, b2, b3, Vs + (warp * 16 + (lane & 15)) * LD + np * 16 + (lane >> 4) * 8);
+      float c0[4] = {o[2 * np][0], o[2 * np][1], 0.f, 0.f}, c1[4] = {o[2 * np + 1][0], o[2 * np + 1][1], 0.f, 0.f};
+      mma_bf16(c0, pf, b0, b1);
+      mma_bf16(c1, pf, b2, b3);
+      o[2 * np][0] = c0[0]; o[2 * np][1] = c0[1];
+      o[2 * np + 1][0] = c1[0]; o[2 * np + 1][1] = c1[1];
+    }
+  }
+  // ---- merge the four warps, normalise, gate, store -----------------------------------------------------
+  lrow += __shfl_xor_sync(0xffffffffu, lrow, 1);
+  lrow += __shfl_xor_sync(0xffffffffu, lrow, 2);
+  __syncthreads();                                // all warps are done with Ks / Vs
+  if (tq == 0) { mm_s[warp][g] = mrow; ml_s[warp][g] = lrow; }
+#pragma unroll
+  for (int n = 0; n < HD / 8; ++n)
+    *reinterpret_cast<float2*>(mo + ((warp * 8 + g) * HD) + n * 8 + tq * 2) = make_float2(o[n][0], o[n][1]);
+  __syncthreads();
+  for (int idx = tid; idx < rep * (HD / 4); idx += 128) {
+    const int r = idx / (HD / 4), d = (idx % (HD / 4)) * 4;
+    float M4 = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) M4 = fmaxf(M4, mm_s[w][r]);
+    float L = 0.f;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const float sw = mm_s[w][r] == -INFINITY ? 0.f : exp2f(mm_s[w][r] - M4);
+      L += ml_s[w][r] * sw;
+      const float4 x = *reinterpret_cast<const float4*>(mo + (w * 8 + r) * HD + d);
+      acc.x += x.x * sw; acc.y += x.y * sw; acc.z += x.z * sw; acc.w += x.w * sw;
+    }
+    const float li = L > 0.f ? 1.f / L : 0.f;
+    const int h = kvh * rep + r;
+    const bf16* gp = prow + (int64_t)h * 2 * HD + HD + d;
+    bf16* dst = a.out + (int64_t)m * a.ldo + (int64_t)h * HD + d;
+    dst[0] = __float2bfloat16(acc.x * li * sigmoid_f(__bfloat162float(gp[0])));
+    dst[1] = __float2bfloat16(acc.y * li * sigmoid_f(__bfloat162float(gp[1])));
+    dst[2] = __float2bfloat16(acc.z * li * sigmoid_f(__bfloat162float(gp[2])));
+    dst[3] = __float2bfloat16(acc.w * li * sigmoid_f(__bfloat162float(gp[3])));
+  }
+}
+
+int g_attn_batch_ctas = 64;
+
 template <int HD, int REP>
 int launch_decode(const DecodeArgs& a, int M, cudaStream_t st) {
   if (a.sel)
@@ -683,8 +856,20 @@ CB_EXPORT int cb_attn_decode(const void* proj, int64_t ldp, const void* qg, cons
                (bf16*)vpool, (float*)part_o, (float*)part_ml, (int)nh, (int)nkv, (int)rot, (int)nsplit,
                1.4426950408889634f / sqrtf((float)hd), eps, (unsigned*)tickets, (bf16*)out, ldo,
                nullptr, nullptr, nullptr, 0, 1};
+  if (hd == 256 && (rot / 2) % 8 == 0 && nh / nkv <= 8 && g_attn_batch_ctas > 0 && nkv * M >= g_attn_batch_ctas) {
+    // enough (row, kv head) pairs to fill the machine with one CTA each: tensor-core batch kernel
+    constexpr int HD = 256;
+    const size_t smem = (size_t)(16 + 64 + 64) * (HD + 8) * sizeof(bf16) + 2 * HD * sizeof(bf16);
+    cudaError_t e = cudaFuncSetAttribute(attn_decode_batch_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    return (int)cb_launch(attn_decode_batch_kernel<HD>, dim3((unsigned)nkv, (unsigned)M), dim3(128), smem,
+                          (cudaStream_t)stream, a);
+  }
   return decode_dispatch(a, M, nh, nkv, hd, rot, stream);
 }
+
+// Number of (row, kv head) pairs from which the dense decode uses the batch kernel (0: never).
+CB_EXPORT int cb_set_attn_batch_ctas(int64_t n) { g_attn_batch_ctas = (int)n; return 0; }
 
 // Block-selected ("QSA") decode attention: q [M, nh, hd] is normed and rotated, this step's K/V are in
 // the pool already; row m reads blocks sel[m, :nsel[m]] of `ratio` tokens and its ragged tail.

@@ -407,3 +407,59 @@ def test_moe_dispatch_and_grouped_gemm(T, k, E, H, N):
     for i in range(nt):
         sel = (pos >= int(row0[i])) & (pos < int(row0[i] + rows[i]))
         assert (idx[sel] == int(ex[i])).all()
+
+
+@pytest.mark.parametrize("nh,nkv,T1", [(16, 4, 150), (8, 4, 64), (6, 2, 257)])
+def test_attention_decode_batch_kernel(nh, nkv, T1):
+    """Tensor-core batch decode kernel (one CTA per row and kv head) against the fp32 oracle and the
+    split kernel: every row has its own blocks holding the same prefix, one row is padding."""
+    from coffin_b200.ops import _lib
+    k = K()
+    hd, rot, R = 256, 64, 33
+    T = T1 + 1
+    proj, qg, kg, cos, sin = _attn_setup(T, nh, nkv, hd, rot, 77)
+    ref, _, _ = _attn_oracle(proj, qg, kg, cos, sin, nh, nkv, hd, rot, torch.arange(T))
+    d = lambda t: t.to(DEV)
+    nblk = (T + 63) // 64
+    kpool = torch.zeros((R * nblk + 1) * 64, nkv, hd, dtype=torch.bfloat16, device=DEV)
+    vpool = torch.zeros_like(kpool)
+    pj, dc, ds = d(proj), d(cos), d(sin)
+    btab = torch.zeros(R, nblk, dtype=torch.int32)
+    for r in range(R):
+        btab[r] = torch.arange(1 + r * nblk, 1 + (r + 1) * nblk)
+    # prefix K/V through the prep kernel into row 0's blocks, then copied to every other row's blocks
+    q = torch.empty(T1, nh, hd, dtype=torch.bfloat16, device=DEV)
+    slots = torch.tensor([int(btab[0, p // 64]) * 64 + p % 64 for p in range(T1)], dtype=torch.int32, device=DEV)
+    k.attn_prep(pj[:T1], d(qg), d(kg), dc, ds, torch.arange(T1, dtype=torch.int32, device=DEV), slots, q, kpool, vpool,
+                nh=nh, nkv=nkv, hd=hd, rot=rot, eps=1e-6)
+    for r in range(1, R):
+        for b in range(nblk):
+            s0, s1 = int(btab[0, b]) * 64, int(btab[r, b]) * 64
+            kpool[s1:s1 + 64] = kpool[s0:s0 + 64]
+            vpool[s1:s1 + 64] = vpool[s0:s0 + 64]
+    posv = torch.full((R,), T1, dtype=torch.int32)
+    posv[5] = -1
+    posv = posv.to(DEV)
+    pr = pj[T1:T1 + 1].repeat(R, 1).contiguous()
+    nsplit = 2
+    outs = []
+    for thr in (1, 0):               # 1: batch kernel for any size; 0: split kernel
+        _lib.call_nostream("set_attn_batch_ctas", thr)
+        kp, vp = kpool.clone(), vpool.clone()
+        part_o = torch.empty(R, nh, nsplit, hd, device=DEV)
+        part_ml = torch.empty(R, nh, nsplit, 2, device=DEV)
+        tickets = torch.zeros(R, nkv, dtype=torch.int32, device=DEV)
+        o2 = torch.zeros(R, nh * hd, dtype=torch.bfloat16, device=DEV)
+        k.attn_decode(pr, d(qg), d(kg), dc, ds, posv, posv.clamp_min(0), d(btab), kp, vp, part_o, part_ml, tickets, o2,
+                      nh=nh, nkv=nkv, hd=hd, rot=rot, nsplit=nsplit, eps=1e-6)
+        outs.append(o2.float().cpu())
+        # the appended key landed in every live row's block
+        for r in (0, R - 1):
+            slot = int(btab[r, T1 // 64]) * 64 + T1 % 64
+            assert kp[slot].float().abs().sum() > 0
+    _lib.call_nostream("set_attn_batch_ctas", 64)
+    for r in range(R):
+        if r == 5:
+            continue
+        close(outs[0][r], ref[T1], 3e-2)
+        close(outs[0][r], outs[1][r], 2e-2)
