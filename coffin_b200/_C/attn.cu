@@ -611,7 +611,9 @@ __global__ void __launch_bounds__(128, 2) attn_decode_batch_kernel(const DecodeA
   bf16* vcur = kcur + HD;                         // [HD]
   float* mo = reinterpret_cast<float*>(Ks);       // after the loop: [4 warps][8 rows][HD] partial outputs
   __shared__ float mm_s[4][8], ml_s[4][8];
-  const int kvh = blockIdx.x, m = blockIdx.y, rep = a.nh / a.nkv;
+  __shared__ float sc_s[8][64], l_s[8][64], linv_s[8];
+  __shared__ bool is_last;
+  const int kvh = blockIdx.x, m = blockIdx.y, split = blockIdx.z, nsplit = gridDim.z, rep = a.nh / a.nkv;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, tq = lane & 3;
   griddep_launch();
   griddep_wait();
@@ -635,7 +637,7 @@ __global__ void __launch_bounds__(128, 2) attn_decode_batch_kernel(const DecodeA
       norm_rope_lane<HD>(x, a.qg, cs, sn, a.rot, a.eps, lane);
 #pragma unroll
       for (int e = 0; e < EPL; ++e) Qs[r * LD + lane * EPL + e] = __float2bfloat16(x[e]);
-    } else {
+    } else if ((pos / kBlock) % nsplit == split) {   // the split that owns the last tile appends this token
       const int64_t slot = (int64_t)bt[pos / kBlock] * kBlock + pos % kBlock;
       if (r == rep) {
         const bf16* src = prow + (int64_t)a.nh * 2 * HD + (int64_t)kvh * HD + lane * EPL;
@@ -658,8 +660,9 @@ __global__ void __launch_bounds__(128, 2) attn_decode_batch_kernel(const DecodeA
   for (int n = 0; n < HD / 8; ++n) o[n][0] = o[n][1] = 0.f;
   float mrow = -INFINITY, lrow = 0.f;
   const int ntiles = pos / kBlock + 1;
-  for (int kt = 0; kt < ntiles; ++kt) {
-    __syncthreads();                              // previous tile consumed; prologue stores visible
+  __syncthreads();                                // prologue stores visible (a split may have no tile at all)
+  for (int kt = split; kt < ntiles; kt += nsplit) {
+    __syncthreads();                              // previous tile consumed
     const int64_t slot0 = (int64_t)bt[kt] * kBlock;
     for (int idx = tid; idx < 64 * CPR; idx += 128) {
       const int r = idx / CPR, c = idx % CPR;
@@ -751,9 +754,69 @@ __global__ void __launch_bounds__(128, 2) attn_decode_batch_kernel(const DecodeA
       const float4 x = *reinterpret_cast<const float4*>(mo + (w * 8 + r) * HD + d);
       acc.x += x.x * sw; acc.y += x.y * sw; acc.z += x.z * sw; acc.w += x.w * sw;
     }
+    const int h = kvh * rep + r;
+    if (nsplit > 1) {                             // unnormalised partial of this split
+      *reinterpret_cast<float4*>(a.part_o + (((int64_t)m * a.nh + h) * nsplit + split) * HD + d) = acc;
+      if (d == 0) {
+        float* pml = a.part_ml + (((int64_t)m * a.nh + h) * nsplit + split) * 2;
+        pml[0] = M4;
+        pml[1] = L;
+      }
+      continue;
+    }
     const float li = L > 0.f ? 1.f / L : 0.f;
+    const bf16* gp = prow + (int64_t)h * 2 * HD + HD + d;
+    bf16* dst = a.out + (int64_t)m * a.ldo + (int64_t)h * HD + d;
+    dst[0] = __float2bfloat16(acc.x * li * sigmoid_f(__bfloat162float(gp[0])));
+    dst[1] = __float2bfloat16(acc.y * li * sigmoid_f(__bfloat162float(gp[1])));
+    dst[2] = __float2bfloat16(acc.z * li * sigmoid_f(__bfloat162float(gp[2])));
+    dst[3] = __float2bfloat16(acc.w * li * sigmoid_f(__bfloat162float(gp[3])));
+  }
+  if (nsplit == 1) return;
+  // ---- several splits per (row, kv head): the last one to arrive merges all partials and applies the gate ----
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) {
+    unsigned* tk = a.tickets + (int64_t)m * a.nkv + kvh;
+    is_last = atomicAdd(tk, 1u) == (unsigned)nsplit - 1;
+    if (is_last) *tk = 0;
+  }
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  const float* bo = a.part_o + ((int64_t)m * a.nh + kvh * rep) * nsplit * HD;
+  const float* bml = a.part_ml + ((int64_t)m * a.nh + kvh * rep) * nsplit * 2;
+  for (int i = tid; i < rep * nsplit; i += 128) {
+    sc_s[i / nsplit][i % nsplit] = __ldcg(bml + (int64_t)i * 2);
+    l_s[i / nsplit][i % nsplit] = __ldcg(bml + (int64_t)i * 2 + 1);
+  }
+  __syncthreads();
+  for (int r = warp; r < rep; r += 4) {           // one warp per head: max, scales, 1 / l
+    float Mx = -INFINITY;
+    for (int sp = lane; sp < nsplit; sp += 32) Mx = fmaxf(Mx, sc_s[r][sp]);
+    Mx = warp_max(Mx);
+    float L = 0.f;
+    for (int sp = lane; sp < nsplit; sp += 32) {
+      const float c = sc_s[r][sp] == -INFINITY ? 0.f : exp2f(sc_s[r][sp] - Mx);
+      sc_s[r][sp] = c;
+      L += l_s[r][sp] * c;
+    }
+    L = warp_sum(L);
+    if (lane == 0) linv_s[r] = L > 0.f ? 1.f / L : 0.f;
+  }
+  __syncthreads();
+  for (int idx = tid; idx < rep * (HD / 4); idx += 128) {
+    const int r = idx / (HD / 4), d = (idx % (HD / 4)) * 4;
+    const float* src = bo + (int64_t)r * nsplit * HD + d;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int sp = 0; sp < nsplit; ++sp) {
+      const float4 v = __ldcg(reinterpret_cast<const float4*>(src + (int64_t)sp * HD));
+      const float c = sc_s[r][sp];
+      acc.x = fmaf(v.x, c, acc.x); acc.y = fmaf(v.y, c, acc.y); acc.z = fmaf(v.z, c, acc.z); acc.w = fmaf(v.w, c, acc.w);
+    }
     const int h = kvh * rep + r;
     const bf16* gp = prow + (int64_t)h * 2 * HD + HD + d;
+    const float li = linv_s[r];
     bf16* dst = a.out + (int64_t)m * a.ldo + (int64_t)h * HD + d;
     dst[0] = __float2bfloat16(acc.x * li * sigmoid_f(__bfloat162float(gp[0])));
     dst[1] = __float2bfloat16(acc.y * li * sigmoid_f(__bfloat162float(gp[1])));
@@ -862,7 +925,7 @@ CB_EXPORT int cb_attn_decode(const void* proj, int64_t ldp, const void* qg, cons
     const size_t smem = (size_t)(16 + 64 + 64) * (HD + 8) * sizeof(bf16) + 2 * HD * sizeof(bf16);
     cudaError_t e = cudaFuncSetAttribute(attn_decode_batch_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
-    return (int)cb_launch(attn_decode_batch_kernel<HD>, dim3((unsigned)nkv, (unsigned)M), dim3(128), smem,
+    return (int)cb_launch(attn_decode_batch_kernel<HD>, dim3((unsigned)nkv, (unsigned)M, (unsigned)nsplit), dim3(128), smem,
                           (cudaStream_t)stream, a);
   }
   return decode_dispatch(a, M, nh, nkv, hd, rot, stream);

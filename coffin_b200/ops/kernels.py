@@ -537,4 +537,10 @@ def attn_decode(proj, qg, kg, cos, sin, positions, rope_pos, block_table, kpool,
 def decode_splits(nkv: int, rows: int) -> int:
     """Key-tile splits so that a decode attention launch (one 8-warp CTA per kv head, split and
     row) covers about one wave of SMs."""
-    return max(1, min(32, 148 // max(1, nkv * rows)))
+    pairs = max(1, nkv * rows)
+    if pairs >= ATTN_BATCH_PAIRS:       # tensor-core batch kernel: two 4-warp CTAs per SM
+        return max(1, min(8, 296 // pairs))
+    return max(1, min(32, 148 // pairs))
+
+
+ATTN_BATCH_PAIRS = 64     # (row, kv head) pairs from which cb_attn_decode runs the batch kernel
