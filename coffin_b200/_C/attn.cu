@@ -825,7 +825,7 @@ __global__ void __launch_bounds__(128, 2) attn_decode_batch_kernel(const DecodeA
   }
 }
 
-int g_attn_batch_ctas = 64;
+int g_attn_batch_ctas = 32;
 
 template <int HD, int REP>
 int launch_decode(const DecodeArgs& a, int M, cudaStream_t st) {

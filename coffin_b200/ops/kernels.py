@@ -539,8 +539,11 @@ def decode_splits(nkv: int, rows: int) -> int:
     row) covers about one wave of SMs."""
     pairs = max(1, nkv * rows)
     if pairs >= ATTN_BATCH_PAIRS:       # tensor-core batch kernel: two 4-warp CTAs per SM
-        return max(1, min(8, 296 // pairs))
+        return max(1, min(32, 296 // pairs))
     return max(1, min(32, 148 // pairs))
 
 
-ATTN_BATCH_PAIRS = 64     # (row, kv head) pairs from which cb_attn_decode runs the batch kernel
+# (row, kv head) pairs from which cb_attn_decode runs the tensor-core batch kernel
+ATTN_BATCH_PAIRS = int(os.environ.get("COFFIN_ATTN_BATCH_PAIRS", "32"))
+if ATTN_BATCH_PAIRS != 32:
+    _lib.call_nostream("set_attn_batch_ctas", ATTN_BATCH_PAIRS)
