@@ -86,7 +86,6 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_kernel(const GemvArgs a) {
 
   // ---- prologue: activation rows into shared memory --------------------------------------
   if (NORM) {
-    if (a.pull_site >= 0) tp_pull_wait(a.tp, a.pull_site);
     for (int m = 0; m < M; ++m) {
       float ss = 0.f;
       for (int64_t c = tid; c < nchunk; c += kThreads) {
@@ -227,7 +226,6 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_kernel(const GemvArgs a) {
       }
     }
   }
-  if (a.push_site >= 0) tp_push_done(a.tp, a.push_site, gridDim.x);
 }
 
 int g_gemv_sms = 0;

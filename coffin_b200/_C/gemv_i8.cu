@@ -82,7 +82,6 @@ __global__ void __launch_bounds__(kT, 3) gemv_i8_kernel(const I8Args a) {
   griddep_wait();
 
   // ---- prologue: (residual add + norm,) per-row absmax, int8 quantisation into shared memory ----
-  if (NORM && a.pull_site >= 0) tp_pull_wait(a.tp, a.pull_site);
   for (int m = 0; m < M; ++m) {
     float ss = 0.f;
     for (int64_t c = tid; c < (K >> 3); c += kT) {
@@ -201,7 +200,6 @@ __global__ void __launch_bounds__(kT, 3) gemv_i8_kernel(const I8Args a) {
       else reinterpret_cast<bf16*>(a.y)[(int64_t)m * a.ldy + row] = __float2bfloat16(v);
     }
   }
-  if (a.push_site >= 0) tp_push_done(a.tp, a.push_site, gridDim.x);
 }
 
 int g_i8_sms = 0;

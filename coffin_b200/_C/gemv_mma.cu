@@ -202,7 +202,6 @@ __global__ void __launch_bounds__(kT, 3) gemv_mma_kernel(const MmaArgs a_in) {
 
   // ---- prologue: activation rows into shared memory ------------------------------------------
   if (NORM) {
-    if (a.pull_site >= 0) tp_pull_wait(a.tp, a.pull_site);
     for (int m = 0; m < M; ++m) {
       float ss = 0.f;
       for (int64_t c = tid; c < nchunk; c += nT) {
@@ -353,7 +352,6 @@ __global__ void __launch_bounds__(kT, 3) gemv_mma_kernel(const MmaArgs a_in) {
         else if (OUT_F32) reinterpret_cast<float*>(a.y)[(int64_t)m * a.ldy + row] = v;
         else reinterpret_cast<bf16*>(a.y)[(int64_t)m * a.ldy + row] = __float2bfloat16(v);
       }
-      if (a.push_site >= 0) tp_push_done(a.tp, a.push_site, unit_stride);
       return;
     }
     // one thread per (round, row block of the round, row in block, batch row): fixed-order sum over k-slices
@@ -375,7 +373,6 @@ __global__ void __launch_bounds__(kT, 3) gemv_mma_kernel(const MmaArgs a_in) {
       else reinterpret_cast<bf16*>(a.y)[(int64_t)m * a.ldy + row] = __float2bfloat16(v);
     }
   }
-  if (a.push_site >= 0) tp_push_done(a.tp, a.push_site, gridDim.x);
 }
 
 int g_mma_sms = 0;

@@ -98,7 +98,6 @@ __global__ void __launch_bounds__(kT, 2) gemv_stream_kernel(const StreamArgs a) 
   // ---- prologue: the activation row into shared memory ------------------------------------
   if (NORM) {
     float ss = 0.f;
-    if (a.pull_site >= 0) tp_pull_wait(a.tp, a.pull_site);
     for (int64_t c = tid; c < nchunk; c += kT) {
       float f[8], g[8];
       bf16x8_to_float(*reinterpret_cast<const uint4*>(a.res_in + c * 8), f);
@@ -173,7 +172,6 @@ __global__ void __launch_bounds__(kT, 2) gemv_stream_kernel(const StreamArgs a) 
     else if (OUT_F32) reinterpret_cast<float*>(a.y)[lrow] = v;
     else reinterpret_cast<bf16*>(a.y)[lrow] = __float2bfloat16(v);
   }
-  if (a.push_site >= 0) tp_push_done(a.tp, a.push_site, gridDim.x);
 }
 
 int g_stream_sms = 0;

@@ -102,7 +102,6 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const bf16* __restrict
       *reinterpret_cast<uint4*>(out + t * H + c * 8) = float_to_bf16x8(acc);
     }
   }
-  if (push_site >= 0) tp_push_done(tp, push_site, gridDim.x);
 }
 
 __global__ void __launch_bounds__(1024) moe_dispatch_kernel(const int* __restrict__ idx, int S, int top_k, int E,

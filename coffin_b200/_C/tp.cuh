@@ -3,18 +3,20 @@
 // A row-parallel projection leaves every rank with a partial sum of the hidden vector.  Instead of
 // a collective call between kernels, the producing GEMV *pushes* its partial rows straight into an
 // inbox on every rank (plain peer stores through IPC-mapped pointers), each value paired with the
-// step's epoch; the next projection's prologue *pulls*: it polls (bounded) every rank's element
-// until it carries this step's epoch and adds them in rank order while it stages its activation,
-// so the reduction costs no launch and its latency hides behind the consumer's weight prefetch.  The sum order is fixed, hence every rank
-// computes bit-identical activations.  Replaces the reference's per-projection gloo all-reduce of
+// step's epoch; the consumer *pulls*: a one-CTA kernel per row (comm.cu) or the consumer phase of
+// the persistent decode kernel (decode_mega.cu) polls (bounded) every rank's element until it
+// carries this step's epoch and adds them in rank order to the residual.  The sum order is fixed,
+// hence every rank computes bit-identical activations.  Replaces the reference's per-projection gloo all-reduce of
 // RowParallelProjection (models/qwen35/parallel.py:1015-1061) and the idea of its p2p_combine kernel
 // (backends/corex/kernels/p2p_reduce.cu:55-173: write to all peers, publish flag, bounded spin).
 //
 // The epoch is a device-side counter every rank advances once per step, so buffers
 // are reused without resetting: a site's inbox can only be overwritten a full step later, and a rank
 // cannot get there before all peers consumed the previous contents because it needs their partial
-// sums of the sites in between.  Waits give up after kTpWaitNs, set the status word and continue
-// with whatever is in the inbox, so a dead peer costs an error, not a hung GPU.
+// sums of the sites in between.  Waits give up after the limit, set the status word and continue
+// with whatever is in the inbox, so a dead peer costs an error, not a hung GPU; once the status word
+// is set no later wait spins (the step finishes at once with garbage, and the host, which reads the
+// word after every step, raises).
 #pragma once
 #include "common.cuh"
 
@@ -73,9 +75,9 @@ __device__ __forceinline__ void tp_push_value(const TpComm& c, int site, int64_t
   for (int p = 0; p < kTpMaxWorld; ++p)
     if (p < c.world) tp_st_pair(c.inbox[p], elem, v, e);
 }
-// Kept for the call sites' symmetry: with data-carried flags nothing is left to publish.
-__device__ __forceinline__ void tp_push_done(const TpComm&, int, unsigned) {}
-__device__ __forceinline__ void tp_pull_wait(const TpComm&, int) {}
+__device__ __forceinline__ int tp_status_set(const int* status) {
+  return *reinterpret_cast<const volatile int*>(status);
+}
 // Consumer: sum of the ranks' partial values at element `off` (fixed rank order).  Polls every
 // rank's element until it carries this step's epoch; gives up after the wait limit, records
 // 16 + rank in the status word and uses what is there.
@@ -88,10 +90,14 @@ __device__ __forceinline__ float tp_pull_value(const TpComm& c, int site, int64_
     if ((unsigned)(v >> 32) != e) {
       const unsigned long long t0 = tp_now_ns(), limit = c.wait_ns ? c.wait_ns : kTpWaitNs;
       unsigned spins = 0;
-      while ((unsigned)(v >> 32) != e) {
-        if ((++spins & 255u) == 0 && tp_now_ns() - t0 > limit) {
-          atomicExch(c.status, 16 + r);
-          break;
+      if (tp_status_set(c.status)) spins = ~0u;   // an earlier wait already ran out: do not spin again
+      while ((unsigned)(v >> 32) != e && spins != ~0u) {
+        if ((++spins & 255u) == 0) {
+          if (tp_status_set(c.status)) break;
+          if (tp_now_ns() - t0 > limit) {
+            atomicCAS(c.status, 0, 16 + r);
+            break;
+          }
         }
         v = tp_ld_pair(c.my_inbox, elem);
       }
@@ -123,10 +129,14 @@ __device__ __forceinline__ void tp_pull8(const TpComm& c, int site, int64_t off,
     if (!ok) {
       const unsigned long long t0 = tp_now_ns(), limit = c.wait_ns ? c.wait_ns : kTpWaitNs;
       unsigned spins = 0;
+      if (tp_status_set(c.status)) ok = true;     // an earlier wait already ran out: do not spin again
       while (!ok) {
-        if ((++spins & 63u) == 0 && tp_now_ns() - t0 > limit) {
-          atomicExch(c.status, 16 + r);
-          break;
+        if ((++spins & 63u) == 0) {
+          if (tp_status_set(c.status)) break;
+          if (tp_now_ns() - t0 > limit) {
+            atomicCAS(c.status, 0, 16 + r);
+            break;
+          }
         }
         ok = true;
 #pragma unroll
@@ -180,10 +190,14 @@ __device__ __forceinline__ void tp_pf_wait(const unsigned* flags, int world, uns
     const unsigned long long limit = wait_ns ? wait_ns : kTpWaitNs;
     for (int r = 0; r < world; ++r) {
       unsigned spins = 0;
+      if (tp_status_set(status)) break;           // an earlier wait already ran out: do not spin again
       while ((int)(tp_ld_acquire(flags + r) - seq) < 0) {
-        if ((++spins & 1023u) == 0 && tp_now_ns() - t0 > limit) {
-          atomicExch(status, 32 + r);
-          break;
+        if ((++spins & 1023u) == 0) {
+          if (tp_status_set(status)) break;
+          if (tp_now_ns() - t0 > limit) {
+            atomicCAS(status, 0, 32 + r);
+            break;
+          }
         }
       }
     }

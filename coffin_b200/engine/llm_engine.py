@@ -35,8 +35,13 @@ class LLMEngine:
         self.cfg = cfg or EngineConfig()
         self.model = model
         slots = getattr(model, "num_slots", self.cfg.max_num_seqs)
-        if slots < self.cfg.max_num_seqs:
-            self.cfg = dataclasses.replace(self.cfg, max_num_seqs=slots)
+        # a model may carry fewer rows per step than the configuration asks for (state slots, or the
+        # bucket limit of a multi-rank model): clamp instead of failing in the middle of a step
+        rows = getattr(model, "max_decode_rows", None)
+        limit = min(slots, rows) if rows else slots
+        if limit < self.cfg.max_num_seqs:
+            print(f"[engine] max_num_seqs {self.cfg.max_num_seqs} -> {limit} (model limit)", flush=True)
+            self.cfg = dataclasses.replace(self.cfg, max_num_seqs=limit)
         self.bm = bm or BlockManager(model, getattr(model, "num_blocks", None), self.cfg.block_size,
                                      self.cfg.snapshots, self.cfg.prefix_cache)
         self.scheduler = Scheduler(self.cfg)

@@ -33,6 +33,10 @@ class ModelRunner:
         self.n_prefill_tokens = 0
         self.n_decode_steps = 0
         self.n_cached_tokens = 0
+        # device status words (bounded waits that ran out): queued after every model call, looked at
+        # after the next synchronisation (the token read-back in ``sample``)
+        self._poll = getattr(model, "poll_status", None)
+        self._check = getattr(model, "check_status", None)
 
     # ------------------------------------------------------------------ admission
     def begin_prefill(self, seq: Sequence) -> None:
@@ -85,6 +89,8 @@ class ModelRunner:
                 embeds, cos_sin = self._mm_chunk(seq, toks, start, end)
             logits = self.model.prefill(self._tokens(toks), start, seq.slot, self._table(seq),
                                         embeds=embeds, cos_sin=cos_sin, want_logits=last)
+            if self._poll is not None:
+                self._poll()
             seq.blocks.commit(T)
             seq.num_computed = end
             self.n_prefill_tokens += T
@@ -111,7 +117,14 @@ class ModelRunner:
             x = self.model.embed_tokens(self._tokens(toks))
             embeds = mm.scatter_into(x, start, end)
         if getattr(mm, "positions", None) is not None:
-            cos_sin = self.model.mrope_rows(mm.positions[:, start:end])
+            pos3 = mm.positions[:, start:end]
+            L = mm.positions.shape[1]
+            if end > L:
+                # a preempted sequence re-prefills prompt + generated tokens: positions were built for the
+                # prompt only, the text after it continues on all three axes at index + rope_delta
+                tail = torch.arange(max(start, L), end, dtype=pos3.dtype) + int(mm.rope_delta)
+                pos3 = torch.cat([pos3, tail.unsqueeze(0).expand(3, -1).to(pos3.device)], dim=1)
+            cos_sin = self.model.mrope_rows(pos3)
             seq.rope_delta = int(mm.rope_delta)
         return embeds, cos_sin
 
@@ -148,6 +161,8 @@ class ModelRunner:
             self.model.set_rows(M, tokens, [s.num_computed for s in seqs], [s.slot for s in seqs],
                                 [s.blocks.table for s in seqs], [s.rope_delta for s in seqs])
             nxt, logits = self.model.decode(M, graph=self.cfg.graph)
+        if self._poll is not None:
+            self._poll()
         for s in seqs:
             s.blocks.commit(1)
             s.num_computed += 1
@@ -161,6 +176,12 @@ class ModelRunner:
         ``greedy_tokens`` is given); temperature rows are drawn by inverse CDF from a uniform
         produced by the sequence's own seeded generator, so every tensor-parallel rank picks the
         same token without a broadcast."""
+        picked = self._sample(seqs, logits, greedy_tokens)     # the read-back synchronises with the step
+        if self._check is not None:
+            self._check()
+        return picked
+
+    def _sample(self, seqs: list[Sequence], logits: torch.Tensor, greedy_tokens: torch.Tensor | None) -> list[int]:
         temps = [s.params.temperature for s in seqs]
         if all(t <= 0 for t in temps):
             if greedy_tokens is not None:

@@ -276,6 +276,17 @@ class Qwen35Model:
         self.tp_force = False      # run the push/pull path even with world == 1 (single-GPU test of the protocol)
         self._step_launches: dict[int, int] = {}
 
+    @property
+    def max_decode_rows(self) -> int:
+        """Rows one decode step can carry: the widest bucket, or the narrow-bucket limit when the
+        multi-rank exchange of the wide path is not available for this model."""
+        multi = self.tp is not None and (self.tp_world > 1 or self.ep_world > 1)
+        return BUCKETS[-1] if (not multi or self.wide_parallel_ok()) else WIDE
+
+    def wide_parallel_ok(self) -> bool:
+        """Whether buckets above ``WIDE`` rows run under tensor / expert parallelism."""
+        return False
+
     def launches_per_step(self, M: int) -> int:
         """Kernels launched by one decode step of bucket ``M`` (counted while capturing)."""
         return self._step_launches.get(M, 0)
@@ -331,8 +342,10 @@ class Qwen35Model:
         return max(c.lin_vdim, c.num_attention_heads * c.head_dim)
 
     def weight_bytes(self) -> int:
+        """Bytes of weights one decode step streams on this rank: every projection and the (local
+        slice of the) lm_head.  The embedding table is not counted (a step gathers one row of it)."""
         seen, total = set(), 0
-        tensors = [t for t in (self.embed, self.lm_head) if t is not None]
+        tensors = [t for t in (self.lm_head,) if t is not None]
         for l in self.layers:
             tensors += [l.w_in, l.w_out] + ([l.w_gu, l.w_down] if l.w_gu is not None else [])
             if l.moe is not None:
@@ -404,6 +417,7 @@ class Qwen35Model:
         c = self.cfg
         T = int(tokens.numel())
         assert 0 < T <= self.max_chunk, f"chunk of {T} tokens exceeds max_chunk {self.max_chunk}"
+        self._check_row(pos0, T, int(block_table.numel()), 0, slot)
         ws = self._prefill_ws(T)
         res, normed = ws["res"][:T], ws["normed"][:T]
         if embeds is None:
@@ -544,8 +558,8 @@ class Qwen35Model:
         """One decode step for the ``M`` rows staged in the bucket's buffers (graph-capturable).
 
         Tensor parallel: the two row-parallel projections of a layer push their partial sums to all
-        ranks (sites ``2*layer`` and ``2*layer + 1``) and the following projection pulls the sum in
-        its prologue, so the step has no separate all-reduce launches."""
+        ranks (sites ``2*layer`` and ``2*layer + 1``); a one-CTA kernel per row pulls the sum, adds the
+        residual and normalises, and the following projection copies the result - no collective call."""
         if M > WIDE:
             return self._decode_body_wide(M)
         c, b = self.cfg, self._row_buffers(M)
@@ -674,6 +688,10 @@ class Qwen35Model:
         """Stage up to ``M`` rows (lists of per-row values); missing rows are padding."""
         b = self._row_buffers(M)
         n = len(tokens)
+        if n > M:
+            raise ValueError(f"{n} rows do not fit bucket {M}")
+        for r in range(n):
+            self._check_row(positions[r], 1, len(block_tables[r]), rope_deltas[r] if rope_deltas else 0, slots[r])
         ht, hm, hb = b["h_tokens"], b["h_meta"], b["h_bt"]
         ht.zero_()
         hm[0].fill_(-1)
@@ -691,6 +709,20 @@ class Qwen35Model:
         b["rope_pos"].copy_(hm[1], non_blocking=True)
         b["slots"].copy_(hm[2], non_blocking=True)
         b["block_table"].copy_(hb, non_blocking=True)
+
+    def _check_row(self, pos0: int, n: int, table_len: int, rope_delta: int = 0, slot: int = 0) -> None:
+        """Host-side guard of everything a kernel indexes with a position: ``n`` tokens from ``pos0``
+        must lie inside the row's block table, the rotary table and the window; the slot must exist.
+        The kernels trust these values (they index the block table, the cos/sin tables and the KV pool
+        with them), so a bad request must stop here, not on the device."""
+        end = pos0 + n
+        if pos0 < 0 or end > self.max_seq or end > table_len * K.BLOCK or table_len > self.max_blocks_per_seq:
+            raise ValueError(f"positions {pos0}..{end - 1} outside the block table ({table_len} blocks) "
+                             f"or the {self.max_seq}-token window")
+        if not (0 <= pos0 + rope_delta and end + rope_delta <= self.cos.shape[0]):
+            raise ValueError(f"rotary positions {pos0 + rope_delta}..{end + rope_delta - 1} outside the table")
+        if not (0 <= slot < self.num_slots):
+            raise ValueError(f"state slot {slot} outside 0..{self.num_slots - 1}")
 
     def capture(self, M: int, warmup: int = 2) -> None:
         """Capture the decode step of bucket ``M`` into a CUDA graph. Warm-up runs use padded
@@ -790,6 +822,7 @@ class Qwen35Model:
         c = self.cfg
         C = len(tokens)
         assert C in (2, 4, 8), "verify width must be 2, 4 or 8"
+        self._check_row(pos0, C, int(block_table.numel()), rope_delta, slot)
         b = self._verify_buffers(C)
         b["tokens"].copy_(torch.tensor(tokens, dtype=torch.int64))
         b["slot"].fill_(slot)
@@ -850,6 +883,15 @@ class Qwen35Model:
                          dk=c.linear_key_head_dim, dv=c.linear_value_head_dim)
 
     # ------------------------------------------------------------------ runner hooks
+    def poll_status(self) -> None:
+        """Queue the read-back of the device status words behind the kernels launched so far."""
+        K.poll_status()
+
+    def check_status(self) -> None:
+        """After a synchronisation that followed ``poll_status``: raise if a bounded device-side wait
+        ran out during the step (a stalled peer, a stuck pipeline), so that wrong tokens never leave."""
+        K.raise_on_status()
+
     def embed_tokens(self, tokens: torch.Tensor) -> torch.Tensor:
         return K.embed_gather(self.embed, tokens)
 

@@ -81,6 +81,24 @@ def call_nostream(name: str, *args) -> int:
     return fn(*[_conv(a) for a in args])
 
 
+_exports: list[str] | None = None
+
+
+def exported() -> list[str]:
+    """Names of the ``cb_*`` entry points that the loaded library resolves: every ``CB_EXPORT``
+    declaration found in the sources beside it is looked up in the shared object, so the count
+    reported by ``ping`` is what the binary really exports, not a constant."""
+    global _exports
+    if _exports is None:
+        import re
+        names: set[str] = set()
+        for src in sorted(_LIB_PATH.parent.glob("*.cu")):
+            names.update(re.findall(r"CB_EXPORT\s+[\w\s\*]+?\b(cb_\w+)\s*\(", src.read_text()))
+        handle = lib()
+        _exports = sorted(n for n in names if hasattr(handle, n))
+    return _exports
+
+
 def set_pdl(on: bool) -> None:
     """Launch kernels with programmatic dependent launch (the prologue of kernel n+1 overlaps
     the tail of kernel n)."""

@@ -37,6 +37,7 @@ def status_word(device=None) -> torch.Tensor:
     if t is None:
         t = torch.zeros(4, dtype=torch.int32, device=f"cuda:{idx}")
         _status[idx] = t
+        watch_status(t[:1], f"cuda:{idx}")
     return t
 
 
@@ -46,6 +47,39 @@ def check_status() -> None:
         if code:
             t.zero_()
             raise _lib.KernelError(f"device-side wait timed out on cuda:{idx} (role {code})")
+
+
+# Status words watched by the serving path.  A bounded device-side wait that runs out sets a word and
+# lets the kernel finish with whatever data it has, so the host has to look at the words after every
+# step or a stalled peer turns into wrong tokens.  ``poll_status`` queues one small asynchronous copy
+# per word into pinned host memory behind the step's kernels; ``raise_on_status`` reads the pinned
+# values after the caller's own synchronisation (the token read-back), so the check adds no sync.
+_watch: list[list] = []      # [device int32 view (1 element), pinned host int32 (1 element), label]
+
+
+def watch_status(word: torch.Tensor, label: str) -> None:
+    assert word.dtype == torch.int32 and word.numel() == 1 and word.is_cuda
+    _watch.append([word, torch.zeros(1, dtype=torch.int32).pin_memory(), label])
+
+
+def unwatch_status(label: str) -> None:
+    _watch[:] = [w for w in _watch if w[2] != label]
+
+
+def poll_status() -> None:
+    """Queue the read-back of every watched status word on the current stream."""
+    for word, host, _ in _watch:
+        host.copy_(word, non_blocking=True)
+
+
+def raise_on_status() -> None:
+    """After a synchronisation that followed ``poll_status``: raise if any word was set (and clear it)."""
+    bad = [(label, int(host[0])) for _, host, label in _watch if int(host[0])]
+    if bad:
+        for word, host, _ in _watch:
+            word.zero_()
+            host.zero_()
+        raise _lib.KernelError("device-side wait timed out: " + ", ".join(f"{l} (role {c})" for l, c in bad))
 
 
 # ------------------------------------------------------------------ row-wise kernels

@@ -5,8 +5,9 @@ Sharding follows the usual column/row split: the fused input projections, gate/u
 are split by output rows (heads, intermediate channels, vocabulary), ``o_proj`` / ``out_proj`` /
 ``down_proj`` by input columns, so each layer needs two all-reduces of the hidden vector.  During
 decode those all-reduces are not calls: the row-parallel projection pushes its partial sums into
-every rank's inbox and the next projection's prologue adds them (``_C/tp.cuh``).  Prefill uses the
-tcgen05 GEMM followed by an NCCL all-reduce.  KV heads are replicated when there are fewer of them
+every rank's inbox and a one-CTA kernel per row (or the consumer phase of the persistent decode
+kernel) adds them (``_C/tp.cuh``).  In prefill the tcgen05 GEMM epilogue scatters its rows to the
+owning ranks and a reduce/gather kernel finishes the all-reduce.  KV heads are replicated when there are fewer of them
 than ranks (reference ``local_config``, ``models/qwen35/parallel.py:670-718``; sharding by key
 suffix ``:734-846``; ``RowParallelProjection`` ``:1015-1061``).
 """
@@ -134,9 +135,11 @@ class TpComm:
     """
 
     def __init__(self, rank: int, world: int, hidden: int, max_rows: int, n_sites: int, exchange=None,
-                 prefill_rows: int = 0) -> None:
+                 prefill_rows: int = 0, loopback: bool = False) -> None:
         """``prefill_rows`` > 0 adds the buffers of the prefill all-reduce (chunks of up to that many
-        rows): per rank an inbox of ``world`` partial slices and a result buffer, both bf16."""
+        rows): per rank an inbox of ``world`` partial slices and a result buffer, both bf16.
+        ``loopback``: every peer pointer is this rank's own buffer (no IPC, one GPU).  The slots of the
+        other ranks are then never written, which is how a test makes a bounded wait run out."""
         from ..ops import _lib
         if world > MAX_WORLD:
             raise ValueError(f"tensor-parallel world {world} > {MAX_WORLD}")
@@ -172,7 +175,9 @@ class TpComm:
         self.peers = [None] * world
         self.peers[rank] = self.base
         self._opened: list[int] = []
-        if world > 1:
+        if world > 1 and loopback:
+            self.peers = [self.base] * world
+        elif world > 1:
             handle = ctypes.create_string_buffer(64)
             rc = self._lib.cb_ipc_get_handle(ctypes.c_void_p(self.base), handle)
             if rc:
@@ -200,6 +205,12 @@ class TpComm:
         s.epoch = self.base + self._off_epoch
         s.status = self.base + self._off_status
         self._struct = s
+        # the serving path watches the status word (ops.kernels.poll_status / raise_on_status)
+        from ..ops import kernels as K
+        sv = torch.as_tensor(_DevView(self.base + self._off_status, 2), device="cuda").view(torch.int32)
+        self._status_view = sv
+        self._watch_label = f"tp rank {rank} @{self.base:#x}"
+        K.watch_status(sv[:1], self._watch_label)
         if self.pf_rows:
             d = _TpPfStruct()
             d.rank, d.world, d.rows_per_rank, d.width = rank, world, self.pf_rpr, hidden
@@ -264,7 +275,12 @@ class TpComm:
         self._lib.cb_peer_read_i32(ctypes.c_void_p(self.base + self._off_status), ctypes.byref(v))
         return int(v.value)
 
+    def clear_status(self) -> None:
+        self._status_view.zero_()
+
     def close(self) -> None:
+        from ..ops import kernels as K
+        K.unwatch_status(self._watch_label)
         for p in self._opened:
             self._lib.cb_ipc_close_handle(ctypes.c_void_p(p))
         self._opened = []

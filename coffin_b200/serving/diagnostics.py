@@ -25,12 +25,36 @@ def _sync(srv) -> None:
         torch.cuda.synchronize(dev)
 
 
+class DiagError(ValueError):
+    """A diagnostic request the engine refuses (answered as ``{"ok": false, "error": ...}``)."""
+
+
+def _room(srv, n_prompt: int) -> int:
+    """Tokens that a solo run can decode after a prompt of ``n_prompt`` tokens: bounded by the private
+    block table of ``_solo`` and by the model's window, with a margin for a verify pass of 8."""
+    m = srv.model
+    nblk = min((n_prompt + 64 + 4096) // 64 + 1, m.num_blocks - 1, getattr(m, "max_blocks_per_seq", 1 << 30))
+    return min(nblk * 64, getattr(m, "max_seq", 1 << 30)) - n_prompt - 8
+
+
+def _bounded(srv, prompt: list[int], n: int, what: str = "n") -> int:
+    """Validate a client-supplied step count against the room of the solo table; the kernels index
+    block tables and rotary tables with these positions and do not check them."""
+    room = _room(srv, len(prompt))
+    if n < 1 or n > room:
+        raise DiagError(f"{what}={n} outside 1..{max(room, 0)} for a prompt of {len(prompt)} tokens "
+                        f"(block table / context window)")
+    return n
+
+
 def _solo(srv, prompt: list[int]):
     """Prefill ``prompt`` into slot 0 with a private block table; returns (table, logits)."""
     m = srv.model
     srv.engine.reset()
+    if _room(srv, len(prompt)) < 1:
+        raise DiagError(f"a prompt of {len(prompt)} tokens leaves no room to decode")
     nblk = (len(prompt) + 64 + 4096) // 64 + 1
-    nblk = min(nblk, m.num_blocks - 1)
+    nblk = min(nblk, m.num_blocks - 1, getattr(m, "max_blocks_per_seq", 1 << 30))
     table = list(range(1, 1 + nblk))
     m.zero_state(0)
     bt = torch.tensor(table, dtype=torch.int32, device=m.device)
@@ -55,8 +79,8 @@ def _decode_loop(srv, table, tok: int, pos: int, n: int, graph: bool) -> list[in
 
 def bench(srv, req: dict) -> dict:
     """Host-timed decode after three warm-up steps, device synchronised on both sides."""
-    n = int(req.get("n", 32))
     prompt = _tokens(srv, req)
+    n = _bounded(srv, prompt, int(req.get("n", 32)) + 3) - 3
     table, logits = _solo(srv, prompt)
     tok = int(logits.argmax())
     _decode_loop(srv, table, tok, len(prompt), 3, srv.cfg.graph)
@@ -70,8 +94,8 @@ def bench(srv, req: dict) -> dict:
 
 def _profile(srv, req: dict, by_op: bool) -> dict:
     from torch.profiler import ProfilerActivity, profile as tprofile
-    n = int(req.get("n", 8))
     prompt = _tokens(srv, req)
+    n = _bounded(srv, prompt, int(req.get("n", 8)) + 2) - 2
     table, logits = _solo(srv, prompt)
     tok = int(logits.argmax())
     _decode_loop(srv, table, tok, len(prompt), 2, False)
@@ -113,9 +137,9 @@ def ops(srv, req: dict) -> dict:
 def spec(srv, req: dict) -> dict:
     """Plain vs speculative greedy decode on the same prompt: speed-up, exactness, accept rate."""
     from ..engine.speculative import SpeculativeDecoder
-    n = int(req.get("n", 32))
     k = int(req.get("spec_k", 3))
     prompt = _tokens(srv, req)
+    n = _bounded(srv, prompt, int(req.get("n", 32)))
     table, logits = _solo(srv, prompt)
     tok = int(logits.argmax())
     _sync(srv)
@@ -138,8 +162,11 @@ def verify(srv, req: dict) -> dict:
     """A/B timing of c-token verification against c single steps (same tokens)."""
     from ..engine.speculative import SpeculativeDecoder
     c = int(req.get("c", 4))
-    n = int(req.get("n", 8))
+    if c not in (2, 4, 8):
+        raise DiagError("c must be 2, 4 or 8")
     prompt = _tokens(srv, req)
+    n = int(req.get("n", 8))
+    _bounded(srv, prompt, c * n, "c*n")
     table, logits = _solo(srv, prompt)
     tok = int(logits.argmax())
     seq = [tok] + _decode_loop(srv, table, tok, len(prompt), c * n, False)
@@ -181,6 +208,8 @@ def pd_decode(srv, req: dict) -> dict:
     srv.engine.reset()
     n = int(req.get("max_new", 32))
     table, prompt, logits = adopt_state(srv.model, 0, Path(req["out_dir"]), max_new=n)
+    if n < 1 or len(prompt) + n > min(len(table) * 64, getattr(srv.model, "max_seq", 1 << 30)):
+        raise DiagError(f"max_new={n} does not fit the adopted sequence's block table / window")
     tok = int(logits.argmax())
     _sync(srv)
     t0 = time.perf_counter()
@@ -203,6 +232,8 @@ def pd_decode_batch(srv, req: dict) -> dict:
     for slot, it in enumerate(items):
         mx = int(it.get("max_new", req.get("max_new", 32)))
         table, prompt, logits = adopt_state(m, slot, Path(it["dir"]), first_block=base, max_new=mx)
+        if mx < 1 or len(prompt) + mx > min(len(table) * 64, getattr(m, "max_seq", 1 << 30)):
+            raise DiagError(f"max_new={mx} does not fit the adopted sequence's block table / window")
         base += len(table)
         rows.append({"table": table, "pos": len(prompt), "tok": int(logits.argmax()), "out": [], "max_new": mx})
     _sync(srv)

@@ -201,7 +201,10 @@ class Server:
             self._wake.notify_all()
         kind, val = outq.get(timeout=timeout)
         if kind == "error":
-            return {"ok": False, "error": val}
+            rep = {"ok": False, "error": val}
+            if str(val).startswith(("DiagError", "ValueError")):
+                rep["status"] = 400
+            return rep
         return val
 
     def _sampling(self, req: dict) -> SamplingParams:
@@ -384,7 +387,8 @@ class Server:
                 "arch": self.model_cfg.architecture, "graph": self.cfg.graph, "max_seq": self.engine.max_seq,
                 "load_s": self.load_s, "build_s": self.build_s, "n_req": self.n_req, "n_reload": self.n_reload,
                 "backend": "sm_100a" if dev.type == "cuda" else "oracle-cpu", "device": str(dev),
-                "native_ops": 24 if dev.type == "cuda" and _lib.available() else 0, "total_ops": 24,
+                "native_ops": len(_lib.exported()) if dev.type == "cuda" and _lib.available() else 0,
+                "total_ops": len(_lib.exported()) if _lib.available() else 0,
                 "int8": self.cfg.quant != "none", "vram_gib": vram, "batch": self.cfg.max_num_seqs > 1,
                 "decode_capacity": self.cfg.max_num_seqs, "vision": self.vision is not None, "vision_int8": False,
                 "image_max_pixels": self.cfg.image_max_pixels, "image_min_pixels": self.cfg.image_min_pixels,

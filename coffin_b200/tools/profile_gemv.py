@@ -1,6 +1,6 @@
 """Stand-alone decode-projection workload for profiling and bandwidth measurement.
 
-    python -m coffin_b200.utils.profile_gemv --n 151936 --k 2560 --variant stream --iters 5
+    python -m coffin_b200.tools.profile_gemv --n 151936 --k 2560 --variant stream --iters 5
 
 Runs one single-row projection shape several times (a buffer larger than L2 is rewritten between
 iterations so that every run reads the weights from HBM) and prints the CUDA-event time and the

@@ -1,7 +1,7 @@
 """Small fixed workload for kernel profiling: a few layers of a named model shape, one prefill
 chunk and a few decode steps, no timing.
 
-    python -m coffin_b200.utils.profile_step --model qwen35-4b --layers 4 --prompt 2048 --decode 3
+    python -m coffin_b200.tools.profile_step --model qwen35-4b --layers 4 --prompt 2048 --decode 3
 
 Meant to be run under ``ncu`` (launch list or a per-kernel capture); with ``--layers 4`` the
 kernels have the full model's shapes while only ~2 GB is resident.

@@ -3,7 +3,7 @@
 In memory the device kernels want K-major ``[N, K]`` int8 (what tcgen05 ``kind::i8`` and the int8
 GEMV read) and, for W4A8, the packed nibbles as they are on disk.  On disk the reference's
 layouts are kept so checkpoints stay interchangeable: int8 ``[K, N]`` + fp32 ``[N]`` scale
-(``coffin-int8-kn-v1``), packed uint8 ``[ceil(K/2), N]`` (low nibble = even k, code = q + 8) + fp32
+(``coffin-int8-kn-v1``), packed uint8 ``[ceil(K/128)*64, N]`` (K padded to whole groups; low nibble = even k, code = q + 8) + fp32
 ``[ceil(K/128), N]`` scale (``coffin-w4a8-kn-v1``).  Reference: ``int8_weights.py:249-384``
 (``QWeight.quantize``: absmax/127, scale floor 1e-8, chunked rows), ``w4a8_weights.py:28-222``,
 ``tools/quant_disk_w4a8.py:45-128``.
@@ -77,8 +77,9 @@ class QWeight:
 class W4A8Weight:
     """Group-``GROUP`` symmetric int4: ``w[n, k] ~= (code - 8) * scale[k // GROUP, n]``.
 
-    ``packed`` uint8 ``[..., ceil(K/2), N]``: low nibble = even k, high nibble = odd k.
-    ``scale`` fp32 ``[..., ceil(K/GROUP), N]``.
+    ``packed`` uint8 ``[..., R, N]``: low nibble = even k, high nibble = odd k; ``R`` is
+    ``ceil(K/GROUP) * GROUP / 2`` as written by the quantisers (K padded to whole groups with zero
+    codes) — a tensor of ``ceil(K/2)`` rows is read as well.  ``scale`` fp32 ``[..., ceil(K/GROUP), N]``.
     """
     packed: torch.Tensor
     scale: torch.Tensor
@@ -101,10 +102,10 @@ class W4A8Weight:
         grp = wf.reshape(*lead, N, G, group)
         scale = (grp.abs().amax(-1) / 7.0).clamp_min(1e-8)                  # [..., N, G]
         q = (grp / scale.unsqueeze(-1)).round().clamp_(-8, 7).to(torch.int16) + 8
-        q = q.reshape(*lead, N, G * group)[..., :K]
-        if K % 2:
-            q = torch.nn.functional.pad(q, (0, 1), value=8)
-        q = q.transpose(-1, -2)                                            # [..., K', N]
+        # K is padded to a whole number of groups before packing (the padding quantises to code 8 =
+        # zero), which is what the reference's writer stores: ``ceil(K / group) * group / 2`` rows
+        q = q.reshape(*lead, N, G * group)
+        q = q.transpose(-1, -2)                                            # [..., G * group, N]
         packed = (q[..., 0::2, :] | (q[..., 1::2, :] << 4)).to(torch.uint8).contiguous()
         return cls(packed, scale.transpose(-1, -2).contiguous(), K, group)
 

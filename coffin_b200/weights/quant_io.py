@@ -170,7 +170,9 @@ def load_quantized(model_dir: str | Path, device: str = "cpu", quant: bool = Tru
             sd[key] = q if quant else q.dequant(dense_dtype)
         elif kind in ("q4", "q4-moe"):
             pk, sc = get(shard, dk), get(shard, meta["scale_key"])
-            if pk.dtype != torch.uint8 or pk.shape[-1] != meta["n"] or pk.shape[-2] != (meta["k"] + 1) // 2:
+            gs = meta.get("group_size", GROUP)
+            rows_ok = {(meta["k"] + 1) // 2, (meta["k"] + gs - 1) // gs * gs // 2}   # unpadded, or padded to whole groups
+            if pk.dtype != torch.uint8 or pk.shape[-1] != meta["n"] or pk.shape[-2] not in rows_ok:
                 raise ValueError(f"{dk}: tensor does not match its index entry")
             q = W4A8Weight(pk, sc, meta["k"], meta.get("group_size", GROUP))
             sd[key] = q if quant else q.dequant(dense_dtype)

@@ -86,6 +86,32 @@ def test_engine_with_image_embeddings_and_media_salted_cache():
     assert sc.output == ref_a and sc.cached_tokens >= 128
 
 
+@torch.no_grad()
+def test_preempted_image_request_recomputes_to_the_same_tokens():
+    """A preempted sequence re-prefills prompt + generated tokens; the rotary positions past the
+    prompt continue at index + rope_delta, so the output equals the run that was never preempted."""
+    g = torch.Generator().manual_seed(9)
+    emb = torch.randn(8, CFG.hidden_size, generator=g) * 0.05
+
+    def run(num_blocks):
+        model = OracleEngineModel(CFG, SD, max_seq=512, num_slots=3, num_blocks=num_blocks)
+        eng = LLMEngine(model, EngineConfig(max_seq=512, max_num_seqs=3, graph=False, prefix_cache=False,
+                                            chunk=64, prefill_quantum=64, max_num_batched_tokens=64))
+        seqs = []
+        for i in range(3):
+            text = torch.randint(0, 3000, (118,), generator=torch.Generator().manual_seed(20 + i)).tolist()
+            prompt = text[:60] + [IMG] * 8 + text[60:]
+            seqs.append(eng.add_request(prompt, SamplingParams(max_tokens=8), mm=_mm(prompt, emb, f"d{i}")))
+        while any(not s.finished for s in seqs):
+            eng.step()
+        return [s.output for s in seqs], eng.n_preempt
+
+    roomy, n0 = run(64)
+    tight, n1 = run(9)          # three 126-token prompts hold 2 blocks each and each grows into a 3rd
+    assert n0 == 0 and n1 >= 1
+    assert tight == roomy
+
+
 def test_decode_image_budget_and_errors():
     from PIL import Image
     from coffin_b200.serving.runtime import MMError

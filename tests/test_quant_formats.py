@@ -29,7 +29,8 @@ def test_int8_container():
 def test_w4a8_container_layout_and_oracle():
     w = torch.randn(24, 300)
     q = W4A8Weight.quantize(w)
-    assert q.packed.shape == (150, 24) and q.scale.shape == (3, 24) and q.k == 300
+    # K is padded to whole groups before packing (3 groups of 128 -> 192 rows), as the reference's writer does
+    assert q.packed.shape == (192, 24) and q.scale.shape == (3, 24) and q.k == 300
     codes = q.codes()
     assert codes.shape == (300, 24) and codes.min() >= -8 and codes.max() <= 7
     # low nibble holds even k
@@ -39,6 +40,20 @@ def test_w4a8_container_layout_and_oracle():
     got = O.w4a8_linear(x, q.packed, q.scale, q.k)
     ref = x @ q.dequant().t()
     assert (got - ref).abs().max() / ref.abs().max() < 0.03
+
+
+def test_w4a8_k_not_a_multiple_of_the_group():
+    """K = 192: the writer stores ceil(K/128)*64 = 128 packed rows; a tensor of ceil(K/2) = 96 rows
+    (the unpadded form) is read as the same weight."""
+    from coffin_b200.oracle import ops as O
+    w = torch.randn(16, 192)
+    q = W4A8Weight.quantize(w)
+    assert q.packed.shape == (128, 16) and q.scale.shape == (2, 16)
+    assert bool((q.packed[96:] == 0x88).all())                      # padding rows are zero codes
+    short = W4A8Weight(q.packed[:96].contiguous(), q.scale, 192)
+    assert torch.equal(short.dequant(), q.dequant())
+    x = torch.randn(3, 192)
+    assert torch.allclose(O.w4a8_linear(x, q.packed, q.scale, q.k), O.w4a8_linear(x, short.packed, short.scale, 192))
 
 
 @pytest.mark.parametrize("scheme,name", [("int8", "tiny"), ("w4a8", "tiny-moe"), ("int8", "tiny-moe")])

@@ -115,6 +115,18 @@ def test_diagnostic_ops_and_pd_handoff(engine):
     assert call(sock, {"op": "generate", "prompt": "x", "max_new": 2, "ignore_eos": True})["ok"]
 
 
+def test_diagnostic_ops_refuse_counts_beyond_the_block_table(engine):
+    """``n`` / ``c*n`` come from the client and become positions that kernels index tables with: a
+    count that does not fit the solo block table or the window is answered with status 400, and the
+    model's own guard refuses a position outside a row's block table."""
+    srv, sock = engine
+    for req in ({"op": "spec", "n": 100000, "prompt": "abc"}, {"op": "verify", "c": 8, "n": 100000, "prompt": "abc"},
+                {"op": "bench", "n": 10 ** 7, "prompt": "abc"}, {"op": "verify", "c": 3, "n": 1, "prompt": "abc"}):
+        rep = call(sock, req)
+        assert rep["ok"] is False and rep.get("status") == 400, rep
+    assert call(sock, {"op": "bench", "n": 2, "prompt": "abc"})["ok"]
+
+
 def test_http_adapter_end_to_end(engine):
     from coffin_b200.entrypoints.openai import app as oa
     from coffin_b200.entrypoints.openai.client import EngineClient

@@ -98,6 +98,64 @@ def test_prefill_all_reduce_protocol_on_one_gpu():
     tp.close()
 
 
+@torch.no_grad()
+def test_bounded_waits_run_out_and_report(monkeypatch):
+    """A peer that never arrives: world 2 on one GPU with both peer pointers on the local buffer, so
+    rank 1's slots are never written.  The pull kernel and the prefill wait must return within their
+    (shortened) limit, report 16 + rank / 32 + rank through the status word, not spin again while the
+    word is set, and work normally once it is cleared.  No fault, trap or endless loop is involved:
+    the waits are bounded by ``%globaltimer``."""
+    import time
+    from coffin_b200.ops import _lib, kernels as K
+    from coffin_b200.parallel.tp import TpComm
+    monkeypatch.setenv("COFFIN_TP_WAIT_MS", "20")
+    H, M = 256, 2
+    tp = TpComm(0, 2, H, 8, 4, loopback=True, prefill_rows=64)
+    assert tp.wait_ns == 20_000_000
+    res = torch.randn(M, H, device="cuda").to(torch.bfloat16)
+    gain = torch.ones(H, device="cuda")
+    res_out, out = torch.empty_like(res), torch.empty_like(res)
+    # decode side: rank 0 pushes site 0 (into its own inbox through both pointers), nobody pushes as rank 1
+    tp.epoch_bump()
+    W = (torch.randn(H, H, device="cuda") * 0.05).to(torch.bfloat16)
+    x = torch.randn(M, H, device="cuda").to(torch.bfloat16)
+    K.gemv(W, x, None, tp=tp, push_site=0, rows=M)
+    t0 = time.perf_counter()
+    K.call("tp_pull_norm", tp.cstruct_ref(), 0, res, gain, res_out, out, M, H, 1e-6)
+    torch.cuda.synchronize()
+    first = time.perf_counter() - t0
+    assert tp.status() == 17                       # 16 + the rank that never arrived
+    assert first < 2.0
+    # a second wait while the word is set returns at once (no second spin)
+    t0 = time.perf_counter()
+    K.call("tp_pull_norm", tp.cstruct_ref(), 1, res, gain, res_out, out, M, H, 1e-6)
+    torch.cuda.synchronize()
+    assert time.perf_counter() - t0 < max(0.01, first / 2)
+    # the serving path's monitor sees it and raises; the word is cleared by the raise
+    K.poll_status()
+    torch.cuda.synchronize()
+    with pytest.raises(_lib.KernelError, match="role 17"):
+        K.raise_on_status()
+    assert tp.status() == 0
+    # prefill side: the scatter publishes only rank 0's flag, the reduce waits for rank 1's
+    tp.scatter(torch.randn(32, H, device="cuda").to(torch.bfloat16))
+    tp.finish_reduce()
+    torch.cuda.synchronize()
+    assert tp.status() == 33                       # 32 + the rank whose slice never landed
+    tp.clear_status()
+    tp.close()
+    # a healthy communicator afterwards: the same kernels complete with status 0
+    tp1 = TpComm(0, 1, H, 8, 4)
+    tp1.epoch_bump()
+    K.gemv(W, x, None, tp=tp1, push_site=0, rows=M)
+    K.call("tp_pull_norm", tp1.cstruct_ref(), 0, res, gain, res_out, out, M, H, 1e-6)
+    torch.cuda.synchronize()
+    ref = res.float() + (x.float() @ W.float().t())
+    assert ((res_out.float() - ref).abs().max() / ref.abs().max()).item() < 2e-2
+    assert tp1.status() == 0
+    tp1.close()
+
+
 def _rank_main(rank, world, port, out):
     import torch.distributed as dist
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
