@@ -84,12 +84,14 @@ __global__ void __launch_bounds__(256) attn_prep_kernel(const PrepArgs a) {
     const bf16* src = prow + (int64_t)a.nh * 2 * HD + (int64_t)kh * HD + lane * EPL;
 #pragma unroll
     for (int e = 0; e < EPL; ++e) x[e] = __bfloat162float(src[e]);
+    if (a.kv_slot[t] < 0) return;       // padding row of a batched verify: nothing to append
     norm_rope_lane<HD>(x, a.kg, cs, sn, a.rot, a.eps, lane);
     bf16* dst = a.kpool + ((int64_t)a.kv_slot[t] * a.nkv + kh) * HD + lane * EPL;
 #pragma unroll
     for (int e = 0; e < EPL; ++e) dst[e] = __float2bfloat16(x[e]);
   } else {
     const int vh = hh - a.nh - a.nkv;
+    if (a.kv_slot[t] < 0) return;
     const bf16* src = prow + (int64_t)a.nh * 2 * HD + (int64_t)(a.nkv + vh) * HD + lane * EPL;
     bf16* dst = a.vpool + ((int64_t)a.kv_slot[t] * a.nkv + vh) * HD + lane * EPL;
 #pragma unroll

@@ -21,9 +21,9 @@ class EngineConfig:
     num_blocks: int = -1               # -1: size the pool from max_seq * max_num_seqs
     snapshots: int = 8                 # delta-net state snapshots kept in the radix tree
     snapshot_interval: int = 2048      # tokens between snapshots during a long prefill
-    spec_k: int = 0                    # speculative draft length (0 = off)
-    spec_batch: bool = False
-    spec_min_ctx: int = 0
+    spec_k: int = 0                    # default speculative draft length of greedy requests (0 = off; a request's own spec_k overrides)
+    spec_batch: bool = False           # speculate also when several rows decode together (one verify pass over all rows)
+    spec_min_ctx: int = 0              # rows shorter than this many tokens do not draft yet
     chunk: int = 2048                  # largest prefill chunk handed to the model
     prefill_quantum: int = 2048        # tokens of one sequence prefilled per engine step
     max_num_seqs: int = 8              # concurrent sequences (= state slots = decode rows)

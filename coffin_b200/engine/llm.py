@@ -40,6 +40,7 @@ class LLM:
         self.graph = graph
         self.graph_launches_replayed = 0
         self._graph_launches: dict[int, int] = {}
+        self._graph_seen: set = set()
         self._slot = 0
         nblk = model.max_blocks_per_seq
         self._bt_list = list(range(nblk))
@@ -100,21 +101,32 @@ class LLM:
         b["slots"].fill_(self._slot)
         b["block_table"][0].copy_(self._bt)
         out = torch.empty(n, dtype=torch.int64, device=m.device)
+        fused = hasattr(m, "_gkey")          # the step itself feeds the token back and advances the position
+        if hasattr(m, "full_logits"):
+            m.full_logits = False            # greedy: the arg-max is all a tensor-parallel step has to agree on
         if self.graph:
-            self._ensure_graph(1)
+            self._ensure_graph(1, advance=fused)
         for i in range(n):
-            nxt, _ = m.decode(1, graph=self.graph)
-            out[i:i + 1].copy_(nxt)
-            m.advance_rows(1)
+            if fused:
+                nxt, _ = m.decode(1, graph=self.graph, advance=True)
+                out[i:i + 1].copy_(nxt)
+            else:
+                nxt, _ = m.decode(1, graph=self.graph)
+                out[i:i + 1].copy_(nxt)
+                m.advance_rows(1)
             if self.graph:
                 self.graph_launches_replayed += self._graph_launches[1]
         self._n_ctx += n
         return out
 
-    def _ensure_graph(self, M: int) -> None:
-        if M not in self._graph_launches:
+    def _ensure_graph(self, M: int, advance: bool = False) -> None:
+        if (M, advance) not in self._graph_seen:
+            self._graph_seen.add((M, advance))
             before = K.LAUNCHES
-            self.model.capture(M)
+            if advance:
+                self.model.capture(M, advance=True)
+            else:
+                self.model.capture(M)
             # capture() ran the body (warm-up + capture); one body's worth of launches per replay
             self._graph_launches[M] = self.model.launches_per_step(M)
             K.LAUNCHES = before
@@ -129,6 +141,8 @@ class LLM:
         host = prompt if isinstance(prompt, torch.Tensor) else torch.tensor(list(prompt), dtype=torch.int64)
         eos_set = set() if ignore_eos else set(eos)
         rng = torch.Generator().manual_seed(seed if seed is not None else 0)
+        if hasattr(m, "full_logits"):
+            m.full_logits = temperature > 0
         torch.cuda.synchronize()
         t0 = time.perf_counter()
         dev = host.to(m.device, non_blocking=True)

@@ -151,11 +151,42 @@ class LLMEngine:
         if not ready:
             return False
         tokens = [s.output[-1] for s in ready]
+        if self._run_spec(ready, tokens, out):
+            return True
         logits = self.runner.decode(ready, tokens)
         greedy = getattr(self.runner, "_last_next", None)
         picked = self.runner.sample(ready, logits, greedy)
         for seq, tok in zip(ready, picked):
             self._commit(seq, tok, out)
+        return True
+
+    def _run_spec(self, ready: list[Sequence], tokens: list[int], out: list[StepOutput]) -> bool:
+        """Speculative step: when a greedy row has drafts (and the configuration allows it), verify all
+        rows' drafts in one pass and commit, per row, the model's own tokens for the accepted prefix
+        plus one.  Speculation only changes speed: a draft is accepted only if it equals the model's
+        arg-max, so the tokens are those of plain greedy decoding.  Returns False when a plain step
+        should run instead (no drafts, no room for the draft window)."""
+        if not (self.cfg.spec_k > 0 or any(s.params.spec_k > 0 for s in ready)):
+            return False
+        drafts = self.runner.draft(ready)
+        if drafts is None:
+            return False
+        C = self.runner.spec_width(drafts)
+        for seq in ready:
+            if seq.num_computed + C > self.max_seq or not self.bm.ensure_blocks(seq.blocks, C):
+                return False
+        new_tokens, first_logits = self.runner.spec_step(ready, tokens, drafts, C)
+        sampled = [s for s in ready if s.params.temperature > 0]
+        if sampled:
+            idx = [i for i, s in enumerate(ready) if s.params.temperature > 0]
+            picked = self.runner.sample(sampled, first_logits[idx])
+            for i, tok in zip(idx, picked):
+                new_tokens[i] = [tok]
+        for seq, toks in zip(ready, new_tokens):
+            for tok in toks:
+                self._commit(seq, tok, out)
+                if seq.finished:
+                    break
         return True
 
     def _preempt(self, seq: Sequence) -> None:

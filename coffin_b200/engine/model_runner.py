@@ -33,6 +33,7 @@ class ModelRunner:
         self.n_prefill_tokens = 0
         self.n_decode_steps = 0
         self.n_cached_tokens = 0
+        self.n_spec_steps = self.n_spec_drafted = self.n_spec_accepted = 0
         # device status words (bounded waits that ran out): queued after every model call, looked at
         # after the next synchronisation (the token read-back in ``sample``)
         self._poll = getattr(model, "poll_status", None)
@@ -144,6 +145,9 @@ class ModelRunner:
         Blocks must already be reserved.  Returns logits ``[len(seqs), vocab]``."""
         n = len(seqs)
         cap = BATCH_BUCKETS[-1]
+        if hasattr(self.model, "full_logits"):
+            # a tensor-parallel step gathers the full-vocabulary logits only when a row samples from them
+            self.model.full_logits = any(s.params.temperature > 0 for s in seqs)
         if n > cap:
             # more rows than the widest bucket: run them in groups (each group is one model step)
             parts, nxts = [], []
@@ -169,6 +173,93 @@ class ModelRunner:
         self.n_decode_steps += 1
         self._last_next = nxt
         return logits[:n]
+
+    # ------------------------------------------------------------------ speculative decoding
+    @property
+    def spec_capable(self) -> bool:
+        return hasattr(self.model, "verify_batch") and hasattr(self.model, "commit_batch")
+
+    def spec_k_of(self, seq: Sequence) -> int:
+        """Draft length of a row: the request's own ``spec_k`` or the engine default; rows that sample
+        with a temperature cannot be verified by arg-max and never draft."""
+        if seq.params.temperature > 0 or not self.spec_capable:
+            return 0
+        k = seq.params.spec_k if seq.params.spec_k >= 0 else self.cfg.spec_k
+        if seq.num_tokens < self.cfg.spec_min_ctx:
+            return 0
+        return max(0, min(7, int(k)))
+
+    def draft(self, seqs: list[Sequence]) -> list[list[int]] | None:
+        """Drafts per row from the rows' suffix drafters (``None`` when no row proposes anything, in
+        which case a plain decode step is the better step)."""
+        from ..utils.suffix import SuffixDrafter
+        if len(seqs) > self.SPEC_MAX_ROWS or not (self.cfg.spec_batch or len(seqs) == 1):
+            return None
+        drafts, any_draft = [], False
+        for s in seqs:
+            k = self.spec_k_of(s)
+            if k <= 0:
+                drafts.append([])
+                continue
+            if s.drafter is None:
+                s.drafter, s.drafter_seen = SuffixDrafter(), 0
+            toks = s.all_tokens
+            if s.drafter_seen < len(toks):
+                s.drafter.observe(toks[s.drafter_seen:])
+                s.drafter_seen = len(toks)
+            room = self.model.max_seq - s.num_tokens - 1 if hasattr(self.model, "max_seq") else k
+            d = s.drafter.draft(min(k, max(0, room)))
+            drafts.append(d)
+            any_draft = any_draft or bool(d)
+        return drafts if any_draft else None
+
+    SPEC_MAX_ROWS = 8
+
+    @staticmethod
+    def spec_width(drafts: list[list[int]]) -> int:
+        need = max(len(d) for d in drafts) + 1
+        for w in (2, 4, 8):
+            if need <= w:
+                return w
+        return 8
+
+    def spec_step(self, seqs: list[Sequence], tokens: list[int], drafts: list[list[int]], C: int):
+        """One verify pass over all rows: row ``i`` feeds its pending token and its drafts (padded to
+        ``C`` tokens).  Returns ``(new_tokens, first_logits)``: per row the model's own greedy tokens for
+        the accepted prefix plus one (``new_tokens[i]`` has ``accepted + 1`` entries), and the logits of
+        every row's first position (what a temperature row samples from).  The delta-net states
+        advance by exactly the accepted tokens; KV rows of rejected positions are overwritten later."""
+        rows, fed_all = [], []
+        for s, tok, d in zip(seqs, tokens, drafts):
+            fed = [tok] + list(d[:C - 1])
+            fed_all.append(fed)
+            rows.append((fed + [fed[-1]] * (C - len(fed)), s.num_computed, s.slot, s.blocks.table, s.rope_delta))
+        logits = self.model.verify_batch(rows)                     # [n, C, vocab]
+        if self._poll is not None:
+            self._poll()
+        preds = logits.argmax(-1).tolist()                         # the read-back synchronises with the pass
+        if self._check is not None:
+            self._check()
+        new_tokens, steps = [], []
+        for s, fed, p in zip(seqs, fed_all, preds):
+            a = 0
+            while a < len(fed) - 1 and fed[a + 1] == p[a]:
+                a += 1
+            new_tokens.append([int(t) for t in p[:a + 1]])
+            steps.append(a + 1)
+            if len(fed) > 1:
+                s.spec_steps += 1
+                s.spec_drafted += len(fed) - 1
+                s.spec_accepted += a
+                self.n_spec_drafted += len(fed) - 1
+                self.n_spec_accepted += a
+        self.model.commit_batch([s.slot for s in seqs], steps)
+        for s, n in zip(seqs, steps):
+            s.blocks.commit(n)
+            s.num_computed += n
+        self.n_decode_steps += 1
+        self.n_spec_steps += 1
+        return new_tokens, logits[:, 0]
 
     # ------------------------------------------------------------------ sampling
     def sample(self, seqs: list[Sequence], logits: torch.Tensor, greedy_tokens: torch.Tensor | None = None) -> list[int]:
@@ -200,4 +291,5 @@ class ModelRunner:
 
     def stats(self) -> dict:
         return {"prefill_tokens": self.n_prefill_tokens, "decode_steps": self.n_decode_steps,
-                "cached_tokens": self.n_cached_tokens}
+                "cached_tokens": self.n_cached_tokens,
+                "spec": {"steps": self.n_spec_steps, "drafted": self.n_spec_drafted, "accepted": self.n_spec_accepted}}

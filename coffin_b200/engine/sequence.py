@@ -31,6 +31,7 @@ class SamplingParams:
     eos: tuple[int, ...] = ()
     deadline: float | None = None       # absolute time.monotonic() limit
     seed: int | None = None
+    spec_k: int = -1                    # speculative draft length: -1 = the engine's default, 0 = off
 
     def __post_init__(self) -> None:
         if self.max_tokens < 1:
@@ -67,6 +68,12 @@ class Sequence:
         self.cooldown = 0                       # engine steps before it may be preempted again
         self.snap_marks: dict[int, Any] = {}    # token count -> delta-net snapshot (for the cache)
         self.rope_delta = 0
+        # speculative decoding (greedy rows): host-side drafter and its acceptance counters
+        self.drafter = None
+        self.drafter_seen = 0                   # tokens of all_tokens the drafter has observed
+        self.spec_drafted = 0
+        self.spec_accepted = 0
+        self.spec_steps = 0
 
     # tokens the model must have seen before the next sample: prompt + generated so far
     @property

@@ -79,7 +79,15 @@ def build_server(args):
     if args.model:
         from ...weights.loader import load_checkpoint
         mcfg = load_config(args.model)
-        sd = load_checkpoint(args.model)
+        # a rank of a multi-rank engine reads only what it computes with: its tensor-parallel slices
+        # (get_slice reads) or the layers of its pipeline stage
+        if world > 1 and mode == "tp":
+            sd = load_checkpoint(args.model, tp=(rank, world))
+        elif world > 1 and mode == "pp":
+            from ...parallel.pp import layer_range
+            sd = load_checkpoint(args.model, layers=layer_range(mcfg.num_hidden_layers, rank, world))
+        else:
+            sd = load_checkpoint(args.model)
     else:
         from ...weights.init import random_state_dict
         mcfg = preset(args.preset or "tiny")

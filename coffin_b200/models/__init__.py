@@ -44,7 +44,7 @@ def _ensure_builtin() -> None:
             from ..parallel.tp import TpComm, local_config, make_exchange, shard_state_dict
             lcfg = local_config(cfg, tp_world)
             lsd = shard_state_dict(cfg, sd, tp_rank, tp_world)
-            n_sites = 2 * cfg.num_hidden_layers
+            n_sites = 2 * cfg.num_hidden_layers + 2      # two per layer + the vocabulary-parallel arg-max
             tp = TpComm(tp_rank, tp_world, cfg.hidden_size, 8, n_sites, exchange=make_exchange(),
                         prefill_rows=kw.get("max_chunk", 2048))
             kw.pop("free_source", None)

@@ -275,6 +275,14 @@ class Qwen35Model:
         self.input_hidden = None   # when set, a decode step starts from this [M, H] input instead of the token embedding
         self.tp_force = False      # run the push/pull path even with world == 1 (single-GPU test of the protocol)
         self._step_launches: dict[int, int] = {}
+        # persistent decode kernel (one cooperative launch per step), planned on first use
+        self.mega = None
+        self._mega_planned = False
+        self.use_mega = True
+        # tensor parallel: whether a decode step must leave the full-vocabulary logits on every rank
+        # (sampling with a temperature needs them; greedy decoding only needs the arg-max, which the
+        # persistent kernel reduces across ranks itself)
+        self.full_logits = True
 
     @property
     def max_decode_rows(self) -> int:
@@ -563,6 +571,13 @@ class Qwen35Model:
         if M > WIDE:
             return self._decode_body_wide(M)
         c, b = self.cfg, self._row_buffers(M)
+        if self._mega_for(M) is not None:
+            # the whole step is one cooperative launch: projections, mixers, all-reduces and arg-max
+            self.mega.launch(M, advance=self._advance)
+            b["final_res"] = b["res"][1]
+            if self.tp_world > 1 and self.full_logits:
+                b["logits"].copy_(self._gather_logits(b["logits_local"], M))
+            return
         comm = self.tp if (self.tp is not None and (self.tp_world > 1 or self.ep_world > 1 or self.tp_force)) else None
         tp = comm if (self.ep_world == 1 and not self.cfg.is_moe) else None     # dense row-parallel push/pull
         cur, nxt = b["res"]
@@ -632,6 +647,18 @@ class Qwen35Model:
             b["logits"].copy_(self._gather_logits(b["logits_local"], M))
         K.argmax(b["logits"], b["next"])
         b["final_res"] = nxt
+        if self._advance:
+            self.advance_rows(M)
+
+    def _mega_for(self, M: int):
+        """The persistent-kernel launcher when bucket ``M`` of this model runs on it, else ``None``."""
+        if not self._mega_planned:
+            self._mega_planned = True
+            from .mega import MegaDecode
+            self.mega = MegaDecode.plan(self)
+        if self.mega is None or not self.use_mega or self.input_hidden is not None or not self.mega.rows_ok(M):
+            return None
+        return self.mega
 
     def _decode_body_wide(self, M: int) -> None:
         """One decode step for a wide bucket (16..64 rows): every row still advances by one token
@@ -683,6 +710,8 @@ class Qwen35Model:
         K._count()
         K.argmax(b["logits"], b["next"])
         b["final_res"] = res
+        if self._advance:
+            self.advance_rows(M)
 
     def set_rows(self, M: int, tokens, positions, slots, block_tables, rope_deltas=None) -> None:
         """Stage up to ``M`` rows (lists of per-row values); missing rows are padding."""
@@ -724,14 +753,21 @@ class Qwen35Model:
         if not (0 <= slot < self.num_slots):
             raise ValueError(f"state slot {slot} outside 0..{self.num_slots - 1}")
 
-    def capture(self, M: int, warmup: int = 2) -> None:
+    _advance = False
+
+    def _gkey(self, M: int, advance: bool):
+        return (M, self.lane, bool(advance), bool(self.full_logits) if self.tp_world > 1 else True, bool(self.use_mega))
+
+    def capture(self, M: int, warmup: int = 2, advance: bool = False) -> None:
         """Capture the decode step of bucket ``M`` into a CUDA graph. Warm-up runs use padded
-        rows (slot -1 / position -1) so that no sequence state is touched."""
-        gkey = (M, self.lane)
+        rows (slot -1 / position -1) so that no sequence state is touched.  ``advance``: the step
+        also feeds the sampled tokens back and advances the positions (a graph of its own)."""
+        gkey = self._gkey(M, advance)
         if gkey in self._graphs:
             return
+        self._advance = bool(advance)
         b = self._row_buffers(M)
-        saved = (b["positions"].clone(), b["slots"].clone())
+        saved = (b["positions"].clone(), b["slots"].clone(), b["tokens"].clone(), b["rope_pos"].clone())
         b["positions"].fill_(-1)
         b["slots"].fill_(-1)
         s = torch.cuda.Stream(device=self.device)
@@ -749,20 +785,31 @@ class Qwen35Model:
             self._decode_body(M)
         self._step_launches[M] = K.LAUNCHES - l0
         self._graphs[gkey] = g
+        self._advance = False
         b["positions"].copy_(saved[0])
         b["slots"].copy_(saved[1])
+        b["tokens"].copy_(saved[2])
+        b["rope_pos"].copy_(saved[3])
 
     @torch.no_grad()
-    def decode(self, M: int, graph: bool = True) -> tuple[torch.Tensor, torch.Tensor]:
+    def decode(self, M: int, graph: bool = True, advance: bool = False) -> tuple[torch.Tensor, torch.Tensor]:
         """Run one decode step on the staged rows. Returns ``(next_tokens [M], logits [M, V])``
-        device tensors owned by the bucket (overwritten by the next step)."""
+        device tensors owned by the bucket (overwritten by the next step).  ``advance``: the step
+        ends by feeding the sampled tokens back and advancing the positions, so that a caller can
+        run greedy steps back to back without touching the rows.  Under tensor parallelism the
+        logits hold the full vocabulary only while ``full_logits`` is set."""
         b = self._row_buffers(M)
         if graph:
-            if (M, self.lane) not in self._graphs:
-                self.capture(M)
-            self._graphs[(M, self.lane)].replay()
+            gkey = self._gkey(M, advance)
+            if gkey not in self._graphs:
+                self.capture(M, advance=advance)
+            self._graphs[gkey].replay()
         else:
-            self._decode_body(M)
+            self._advance = bool(advance)
+            try:
+                self._decode_body(M)
+            finally:
+                self._advance = False
         return b["next"], b["logits"]
 
     def stage_hidden(self, M: int) -> torch.Tensor:
@@ -784,60 +831,99 @@ class Qwen35Model:
         b["rope_pos"].add_(live.to(torch.int32))
 
     # ------------------------------------------------------------------ speculative verification
-    def _verify_buffers(self, C: int) -> dict:
-        key = ("verify", C)
+    VERIFY_WIDTHS = (2, 4, 8)
+
+    def _verify_buffers(self, R: int, C: int) -> dict:
+        """Buffers of a verify pass over ``R`` sequences x ``C`` tokens (``R`` a power of two)."""
+        key = ("verify", R, C)
         b = self._rows.get(key)
         if b is None:
             c, dev, bf = self.cfg, self.device, torch.bfloat16
-            H = c.hidden_size
+            H, N = c.hidden_size, R * C
             b = {
-                "tokens": torch.zeros(C, dtype=torch.int64, device=dev),
-                "res": [torch.zeros(C, H, dtype=bf, device=dev) for _ in range(2)],
-                "h": torch.zeros(C, H, dtype=bf, device=dev), "h2": torch.zeros(C, H, dtype=bf, device=dev),
-                "proj": torch.zeros(C, self.in_width, dtype=bf, device=dev),
-                "act_lin": torch.zeros(C, c.lin_vdim, dtype=bf, device=dev),
-                "act_full": torch.zeros(C, c.num_attention_heads * c.head_dim, dtype=bf, device=dev),
-                "q": torch.zeros(C, c.num_attention_heads, c.head_dim, dtype=bf, device=dev),
-                "inter": torch.zeros(C, max(1, c.intermediate_size), dtype=bf, device=dev),
-                "logits": torch.zeros(C, c.vocab_size, dtype=torch.float32, device=dev),
-                "slot": torch.zeros(1, dtype=torch.int32, device=dev),
-                "pos": torch.zeros(1, dtype=torch.int32, device=dev),
-                "kv_slots": torch.zeros(C, dtype=torch.int32, device=dev),
-                "ridx": torch.zeros(C, dtype=torch.int32, device=dev),
-                "record": torch.zeros(len(self.lin_ids), 1, C, c.linear_num_value_heads,
+                "tokens": torch.zeros(N, dtype=torch.int64, device=dev),
+                "res": [torch.zeros(N, H, dtype=bf, device=dev) for _ in range(2)],
+                "h": torch.zeros(N, H, dtype=bf, device=dev), "h2": torch.zeros(N, H, dtype=bf, device=dev),
+                "normed": torch.zeros(N, H, dtype=bf, device=dev),
+                "proj": torch.zeros(N, self.in_width, dtype=bf, device=dev),
+                "act_lin": torch.zeros(N, c.lin_vdim, dtype=bf, device=dev),
+                "act_full": torch.zeros(N, c.num_attention_heads * c.head_dim, dtype=bf, device=dev),
+                "q": torch.zeros(N, c.num_attention_heads, c.head_dim, dtype=bf, device=dev),
+                "inter": torch.zeros(N, max(1, c.intermediate_size), dtype=bf, device=dev),
+                "gu": torch.zeros(N, max(1, 2 * c.intermediate_size), dtype=bf, device=dev) if N > WIDE else None,
+                "logits": torch.zeros(N, c.vocab_size, dtype=torch.float32, device=dev),
+                "logits_bf": torch.zeros(N, self.vocab_local, dtype=bf, device=dev) if N > WIDE else None,
+                "slot": torch.full((R,), -1, dtype=torch.int32, device=dev),
+                "pos": torch.zeros(R, dtype=torch.int32, device=dev),
+                "kv_slots": torch.full((N,), -1, dtype=torch.int32, device=dev),
+                "ridx": torch.zeros(N, dtype=torch.int32, device=dev),
+                "record": torch.zeros(len(self.lin_ids), R, C, c.linear_num_value_heads,
                                       c.linear_key_head_dim + c.linear_value_head_dim + 1,
                                       dtype=torch.float32, device=dev),
-                "steps": torch.zeros(1, dtype=torch.int32, device=dev),
+                "steps": torch.zeros(R, dtype=torch.int32, device=dev),
             }
             self._rows[key] = b
         return b
 
     @torch.no_grad()
-    def verify(self, tokens: list[int], pos0: int, slot: int, block_table: torch.Tensor, rope_delta: int = 0) -> torch.Tensor:
-        """Run ``C`` consecutive tokens (the last sampled token followed by drafts) of one sequence
-        in one pass and return their logits ``[C, vocab]``.  KV rows of all ``C`` positions are
-        written (rejected ones are overwritten later); the delta-net state is left untouched and
-        the per-token rank-one updates are recorded, so that ``commit`` can apply the accepted
-        prefix.  ``C`` must be 2, 4 or 8 (``models/qwen35/model.py:1761-1911`` in the reference)."""
+    def verify_batch(self, rows: list[tuple]) -> torch.Tensor:
+        """Score ``C`` consecutive tokens (the last sampled token followed by drafts) of each of ``R``
+        sequences in one pass over the weights.  ``rows[i] = (tokens[C], pos0, slot, block_table,
+        rope_delta)`` with the same ``C`` in (2, 4, 8) for every row and ``R * C <= 64``; returns
+        logits ``[R, C, vocab]``.  KV rows of all positions are written (rejected ones are overwritten
+        later); the delta-net states are left untouched and the per-token rank-one updates are
+        recorded, so that ``commit_batch`` can apply each row's accepted prefix.  Up to 8 token rows
+        run on the decode projections, more on the tcgen05 GEMM (reference: batched speculative step,
+        ``models/qwen35/model.py:1351-1759``)."""
         c = self.cfg
-        C = len(tokens)
-        assert C in (2, 4, 8), "verify width must be 2, 4 or 8"
-        self._check_row(pos0, C, int(block_table.numel()), rope_delta, slot)
-        b = self._verify_buffers(C)
-        b["tokens"].copy_(torch.tensor(tokens, dtype=torch.int64))
-        b["slot"].fill_(slot)
-        b["pos"].fill_(pos0)
-        pos = torch.arange(pos0, pos0 + C, device=self.device)
-        b["kv_slots"].copy_(block_table.to(torch.int64)[pos // K.BLOCK] * K.BLOCK + pos % K.BLOCK)
-        b["ridx"].copy_(pos + rope_delta)
+        n = len(rows)
+        C = len(rows[0][0])
+        assert C in self.VERIFY_WIDTHS and all(len(r[0]) == C for r in rows), "verify width must be 2, 4 or 8 for every row"
+        R = 1
+        while R < n:
+            R *= 2
+        N = R * C
+        if N > BUCKETS[-1]:
+            raise ValueError(f"{n} rows x {C} tokens exceed the {BUCKETS[-1]} token rows of one verify pass")
+        if N > WIDE and self.tp is not None and (self.tp_world > 1 or self.ep_world > 1):
+            raise NotImplementedError("a verify pass of more than 8 token rows is single-GPU")
+        tables = []
+        for toks, pos0, slot, table, delta in rows:
+            tl = table.tolist() if isinstance(table, torch.Tensor) else list(table)
+            self._check_row(pos0, C, len(tl), delta, slot)
+            tables.append(tl)
+        b = self._verify_buffers(R, C)
+        h_tok = torch.zeros(N, dtype=torch.int64)
+        h_slot = torch.full((R,), -1, dtype=torch.int32)
+        h_pos = torch.zeros(R, dtype=torch.int32)
+        h_kv = torch.full((N,), -1, dtype=torch.int32)
+        h_ridx = torch.zeros(N, dtype=torch.int32)
+        for i, (toks, pos0, slot, _t, delta) in enumerate(rows):
+            h_tok[i * C:(i + 1) * C] = torch.as_tensor(list(toks), dtype=torch.int64)
+            h_slot[i], h_pos[i] = slot, pos0
+            for j in range(C):
+                p = pos0 + j
+                h_kv[i * C + j] = tables[i][p // K.BLOCK] * K.BLOCK + p % K.BLOCK
+                h_ridx[i * C + j] = p + delta
+        b["tokens"].copy_(h_tok)
+        b["slot"].copy_(h_slot)
+        b["pos"].copy_(h_pos)
+        b["kv_slots"].copy_(h_kv)
+        b["ridx"].copy_(h_ridx)
+        dev_tables = [torch.tensor(t, dtype=torch.int32, device=self.device) for t in tables]
+        wide = N > WIDE
         cur, nxt = b["res"]
         K.embed_gather(self.embed, b["tokens"], cur)
         carry = None
         for li, lw in enumerate(self.layers):
             proj = b["proj"][:, :lw.w_in.shape[0]]
-            self._gemv(lw.w_in, None, proj, norm=(cur, carry, lw.in_gain, nxt if carry is not None else None, self.eps))
-            if carry is not None:
-                cur, nxt = nxt, cur
+            if wide:
+                K.rmsnorm(cur, lw.in_gain, self.eps, out=b["normed"])
+                self._gemm(b["normed"], lw.w_in, out=proj)
+            else:
+                self._gemv(lw.w_in, None, proj, norm=(cur, carry, lw.in_gain, nxt if carry is not None else None, self.eps))
+                if carry is not None:
+                    cur, nxt = nxt, cur
             if lw.kind == LINEAR:
                 j = self.lin_ids[li]
                 act = b["act_lin"]
@@ -851,36 +937,72 @@ class Qwen35Model:
                 K.attn_prep(proj, lw.qg, lw.kg, self.cos, self.sin, b["ridx"], b["kv_slots"], b["q"], self.kpool[j],
                             self.vpool[j], nh=c.num_attention_heads, nkv=c.num_key_value_heads, hd=c.head_dim,
                             rot=c.rotary_dim, eps=self.eps)
-                K.attn_prefill(b["q"], proj, self.kpool[j], self.vpool[j], block_table, act, q_pos0=pos0,
-                               nh=c.num_attention_heads, nkv=c.num_key_value_heads, hd=c.head_dim)
+                for i, (_tk, pos0, _s, _t, _d) in enumerate(rows):
+                    sl = slice(i * C, (i + 1) * C)
+                    K.attn_prefill(b["q"][sl], proj[sl], self.kpool[j], self.vpool[j], dev_tables[i], act[sl], q_pos0=pos0,
+                                   nh=c.num_attention_heads, nkv=c.num_key_value_heads, hd=c.head_dim)
+            if wide:
+                self._gemm(act, lw.w_out, out=cur, residual=cur)
+                K.rmsnorm(cur, lw.post_gain, self.eps, out=b["normed"])
+                if lw.moe is not None:
+                    cur.add_(lw.moe.apply(b["normed"], self))
+                    K._count()
+                else:
+                    self._gemm(b["normed"], lw.w_gu, out=b["gu"])
+                    self._gemm(b["gu"], lw.w_down, out=cur, residual=cur, swiglu_in=True)
+                continue
             self._gemv(lw.w_out, act, b["h"])
             if lw.moe is not None:
-                lw.moe.forward_decode(cur, b["h"], nxt, lw.post_gain, b["h2"], self, C)
+                lw.moe.forward_decode(cur, b["h"], nxt, lw.post_gain, b["h2"], self, N)
                 cur, nxt = nxt, cur
             else:
                 self._gemv(lw.w_gu, None, b["inter"], swiglu=True, norm=(cur, b["h"], lw.post_gain, nxt, self.eps))
                 cur, nxt = nxt, cur
                 self._gemv(lw.w_down, b["inter"], b["h2"])
             carry = b["h2"]
-        self._gemv(self.lm_head, None, b["logits"], norm=(cur, carry, self.final_gain, nxt, self.eps))
-        self._verify_width = C
-        b["final_res"] = nxt
-        return b["logits"]
+        if wide:
+            K.rmsnorm(cur, self.final_gain, self.eps, out=b["normed"])
+            self._gemm(b["normed"], self.lm_head, out=b["logits_bf"])
+            b["logits"].copy_(b["logits_bf"])
+            K._count()
+            b["final_res"] = cur
+        else:
+            self._gemv(self.lm_head, None, b["logits"], norm=(cur, carry, self.final_gain, nxt, self.eps))
+            b["final_res"] = nxt
+        self._verify_shape = (R, C, n)
+        return b["logits"].view(R, C, -1)[:n]
 
-    def verify_hidden(self) -> torch.Tensor:
-        """Last-layer residual stream ``[C, H]`` (before the final norm) of the rows of the last
-        ``verify`` call - what the MTP head pairs with the following token."""
-        return self._verify_buffers(self._verify_width)["final_res"]
-
-    def commit(self, slot: int, n_accept: int) -> None:
-        """Apply the first ``n_accept`` recorded delta-net updates of the last ``verify`` call."""
+    def commit_batch(self, slots: list[int], steps: list[int]) -> None:
+        """Apply, for row ``i`` of the last ``verify_batch`` call, its first ``steps[i]`` recorded
+        delta-net updates to the state of ``slots[i]``."""
         c = self.cfg
-        b = self._verify_buffers(self._verify_width)
-        b["steps"].fill_(n_accept)
-        b["slot"].fill_(slot)
+        R, C, n = self._verify_shape
+        assert len(slots) == len(steps) == n
+        b = self._verify_buffers(R, C)
+        h_steps = torch.zeros(R, dtype=torch.int32)
+        h_slot = torch.full((R,), -1, dtype=torch.int32)
+        h_steps[:n] = torch.as_tensor(steps, dtype=torch.int32)
+        h_slot[:n] = torch.as_tensor(slots, dtype=torch.int32)
+        b["steps"].copy_(h_steps)
+        b["slot"].copy_(h_slot)
         for li, j in self.lin_ids.items():
             K.gdn_commit(self.state[j], b["record"][j], b["slot"], b["steps"], nv=c.linear_num_value_heads,
                          dk=c.linear_key_head_dim, dv=c.linear_value_head_dim)
+
+    def verify(self, tokens: list[int], pos0: int, slot: int, block_table: torch.Tensor, rope_delta: int = 0) -> torch.Tensor:
+        """One sequence: logits ``[C, vocab]`` of ``C`` (2, 4 or 8) consecutive tokens
+        (``models/qwen35/model.py:1761-1911`` in the reference)."""
+        return self.verify_batch([(tokens, pos0, slot, block_table, rope_delta)])[0]
+
+    def verify_hidden(self) -> torch.Tensor:
+        """Last-layer residual stream ``[rows * C, H]`` (before the final norm) of the token rows of the
+        last verify pass - what the MTP head pairs with the following token."""
+        R, C, _ = self._verify_shape
+        return self._verify_buffers(R, C)["final_res"]
+
+    def commit(self, slot: int, n_accept: int) -> None:
+        """Apply the first ``n_accept`` recorded delta-net updates of the last one-sequence ``verify``."""
+        self.commit_batch([slot], [n_accept])
 
     # ------------------------------------------------------------------ runner hooks
     def poll_status(self) -> None:

@@ -204,27 +204,40 @@ class OracleEngineModel:
         return r["next"], logits
 
     @torch.no_grad()
-    def verify(self, tokens: list[int], pos0: int, slot: int, block_table: torch.Tensor, rope_delta: int = 0) -> torch.Tensor:
-        """Logits of ``C`` consecutive tokens; the delta-net state is restored afterwards and
-        ``commit`` replays the accepted prefix."""
+    def verify_batch(self, rows: list[tuple]) -> torch.Tensor:
+        """Logits ``[R, C, vocab]`` of ``C`` consecutive tokens of each row ``(tokens, pos0, slot,
+        block_table, rope_delta)``; the delta-net states are restored afterwards and ``commit_batch``
+        replays each row's accepted prefix."""
         c = self.cfg
-        self._verify = (list(tokens), pos0, block_table.clone(), rope_delta, self.snapshot_state(slot))
-        T = len(tokens)
-        pos = torch.arange(pos0, pos0 + T) + rope_delta
-        cos, sin = O.mrope_cos_sin(pos.reshape(1, -1).expand(3, -1), c.rotary_dim, c.rope_theta, c.mrope_section)
-        x = self._forward(self.embed_tokens(torch.tensor(tokens)), pos0, slot, block_table, cos, sin)
-        logits = self._head(x)
-        self.restore_state(slot, self._verify[4])
-        return logits
+        self._verify = []
+        out = []
+        for tokens, pos0, slot, block_table, rope_delta in rows:
+            table = block_table.clone() if isinstance(block_table, torch.Tensor) else torch.tensor(list(block_table), dtype=torch.int32)
+            snap = self.snapshot_state(slot)
+            self._verify.append((list(tokens), pos0, table, rope_delta, snap, slot))
+            T = len(tokens)
+            pos = torch.arange(pos0, pos0 + T) + rope_delta
+            cos, sin = O.mrope_cos_sin(pos.reshape(1, -1).expand(3, -1), c.rotary_dim, c.rope_theta, c.mrope_section)
+            x = self._forward(self.embed_tokens(torch.tensor(list(tokens))), pos0, slot, table, cos, sin)
+            out.append(self._head(x))
+            self.restore_state(slot, snap)
+        return torch.stack(out)
+
+    def commit_batch(self, slots: list[int], steps: list[int]) -> None:
+        c = self.cfg
+        for (tokens, pos0, table, delta, snap, slot0), slot, n_accept in zip(self._verify, slots, steps):
+            assert slot == slot0
+            self.restore_state(slot, snap)
+            if n_accept > 0:
+                pos = torch.arange(pos0, pos0 + n_accept) + delta
+                cos, sin = O.mrope_cos_sin(pos.reshape(1, -1).expand(3, -1), c.rotary_dim, c.rope_theta, c.mrope_section)
+                self._forward(self.embed_tokens(torch.tensor(tokens[:n_accept])), pos0, slot, table, cos, sin)
+
+    def verify(self, tokens: list[int], pos0: int, slot: int, block_table: torch.Tensor, rope_delta: int = 0) -> torch.Tensor:
+        return self.verify_batch([(tokens, pos0, slot, block_table, rope_delta)])[0]
 
     def commit(self, slot: int, n_accept: int) -> None:
-        tokens, pos0, table, delta, snap = self._verify
-        c = self.cfg
-        self.restore_state(slot, snap)
-        if n_accept > 0:
-            pos = torch.arange(pos0, pos0 + n_accept) + delta
-            cos, sin = O.mrope_cos_sin(pos.reshape(1, -1).expand(3, -1), c.rotary_dim, c.rope_theta, c.mrope_section)
-            self._forward(self.embed_tokens(torch.tensor(tokens[:n_accept])), pos0, slot, table, cos, sin)
+        self.commit_batch([slot], [n_accept])
 
     def sample(self, logits: torch.Tensor, temps, us) -> torch.Tensor:
         """Greedy when ``temps`` is None; else per-row inverse-CDF sampling with uniforms ``us``

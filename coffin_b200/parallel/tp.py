@@ -49,51 +49,89 @@ def local_config(cfg: ModelConfig, world: int) -> ModelConfig:
         name=f"{cfg.name}-tp{world}")
 
 
-def _rows(t: torch.Tensor, rank: int, world: int, unit: int = 1) -> torch.Tensor:
-    n = t.shape[0] // unit
-    per = n // world
-    return t[rank * per * unit:(rank + 1) * per * unit]
+TP_MARK = "__tp_shard__"      # key a state dict carries when its tensors are already one rank's slices
 
 
-def shard_state_dict(cfg: ModelConfig, sd: dict[str, torch.Tensor], rank: int, world: int) -> dict[str, torch.Tensor]:
-    """The slice of a full state dict that rank ``rank`` of ``world`` computes with.
-    Tensors that every rank needs whole (norms, embedding, router) are shared, not copied."""
-    lc = local_config(cfg, world)
-    out: dict[str, torch.Tensor] = {}
+def _span(n: int, rank: int, world: int, unit: int = 1) -> tuple[int, int]:
+    per = (n // unit) // world
+    return rank * per * unit, (rank + 1) * per * unit
+
+
+def slice_plan(cfg: ModelConfig, key: str, rank: int, world: int):
+    """How rank ``rank`` of ``world`` cuts the tensor stored under ``key``: ``None`` (whole tensor),
+    ``("rows", [(a, b), ...])`` = concatenation of output-row ranges, or ``("cols", [(a, b)])`` = a range
+    of input columns.  One description serves dense tensors, int8 / int4 containers and sliced reads
+    from a safetensors file, so a rank never has to hold (or read) more than its part."""
+    if not key.startswith(LM + "layers."):
+        return None
     nk, nv, dk, dv = cfg.linear_num_key_heads, cfg.linear_num_value_heads, cfg.linear_key_head_dim, cfg.linear_value_head_dim
     kdim = nk * dk
     nh, nkv, hd = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
-    for key, t in sd.items():
-        if not key.startswith(LM + "layers."):
-            out[key] = t
-            continue
-        name = key.split(".", 4)[-1]            # e.g. linear_attn.in_proj_qkv.weight
-        if name in ("linear_attn.in_proj_qkv.weight", "linear_attn.conv1d.weight"):
-            q, k, v = t[:kdim], t[kdim:2 * kdim], t[2 * kdim:]
-            out[key] = torch.cat([_rows(q, rank, world, dk), _rows(k, rank, world, dk), _rows(v, rank, world, dv)])
-        elif name == "linear_attn.in_proj_z.weight":
-            out[key] = _rows(t, rank, world, dv)
-        elif name in ("linear_attn.in_proj_b.weight", "linear_attn.in_proj_a.weight", "linear_attn.A_log",
-                      "linear_attn.dt_bias"):
-            out[key] = _rows(t, rank, world)
-        elif name == "linear_attn.out_proj.weight":
-            out[key] = _rows(t.t(), rank, world, dv).t().contiguous()
-        elif name == "self_attn.q_proj.weight":
-            out[key] = _rows(t, rank, world, 2 * hd)
-        elif name in ("self_attn.k_proj.weight", "self_attn.v_proj.weight"):
-            if nkv >= world:
-                out[key] = _rows(t, rank, world, hd)
-            else:
-                h = rank * nkv // world          # the kv head this rank's query heads attend with
-                out[key] = t[h * hd:(h + 1) * hd]
-        elif name == "self_attn.o_proj.weight":
-            out[key] = _rows(t.t(), rank, world, hd).t().contiguous()
-        elif name in ("mlp.gate_proj.weight", "mlp.up_proj.weight"):
-            out[key] = _rows(t, rank, world)
-        elif name == "mlp.down_proj.weight":
-            out[key] = _rows(t.t(), rank, world).t().contiguous()
-        else:
-            out[key] = t
+    name = key.split(".", 4)[-1]            # e.g. linear_attn.in_proj_qkv.weight
+    if name in ("linear_attn.in_proj_qkv.weight", "linear_attn.conv1d.weight"):
+        q0, q1 = _span(kdim, rank, world, dk)
+        v0, v1 = _span(nv * dv, rank, world, dv)
+        return "rows", [(q0, q1), (kdim + q0, kdim + q1), (2 * kdim + v0, 2 * kdim + v1)]
+    if name == "linear_attn.in_proj_z.weight":
+        return "rows", [_span(nv * dv, rank, world, dv)]
+    if name in ("linear_attn.in_proj_b.weight", "linear_attn.in_proj_a.weight", "linear_attn.A_log", "linear_attn.dt_bias"):
+        return "rows", [_span(nv, rank, world)]
+    if name == "linear_attn.out_proj.weight":
+        return "cols", [_span(nv * dv, rank, world, dv)]
+    if name == "self_attn.q_proj.weight":
+        return "rows", [_span(nh * 2 * hd, rank, world, 2 * hd)]
+    if name in ("self_attn.k_proj.weight", "self_attn.v_proj.weight"):
+        if nkv >= world:
+            return "rows", [_span(nkv * hd, rank, world, hd)]
+        h = rank * nkv // world          # the kv head this rank's query heads attend with
+        return "rows", [(h * hd, (h + 1) * hd)]
+    if name == "self_attn.o_proj.weight":
+        return "cols", [_span(nh * hd, rank, world, hd)]
+    if name in ("mlp.gate_proj.weight", "mlp.up_proj.weight"):
+        return "rows", [_span(cfg.intermediate_size, rank, world)]
+    if name == "mlp.down_proj.weight":
+        return "cols", [_span(cfg.intermediate_size, rank, world)]
+    return None
+
+
+def apply_plan(t, plan):
+    """Cut a dense tensor, a ``QWeight`` or a ``W4A8Weight`` according to ``slice_plan``."""
+    from ..weights.quant import QWeight, W4A8Weight
+    if plan is None:
+        return t
+    kind, ranges = plan
+    if isinstance(t, QWeight):                      # wq [N, K] + scale [N]: a column cut keeps the row scales
+        if kind == "rows":
+            return QWeight(torch.cat([t.wq[a:b] for a, b in ranges]).contiguous(), torch.cat([t.scale[a:b] for a, b in ranges]))
+        (a, b), = ranges
+        return QWeight(t.wq[:, a:b].contiguous(), t.scale)
+    if isinstance(t, W4A8Weight):                   # packed [K/2, N] + scale [K/group, N]
+        if kind == "rows":
+            return W4A8Weight(torch.cat([t.packed[..., a:b] for a, b in ranges], -1).contiguous(),
+                              torch.cat([t.scale[..., a:b] for a, b in ranges], -1).contiguous(), t.k, t.group_size)
+        (a, b), = ranges
+        if a % t.group_size or b % t.group_size:
+            raise ValueError(f"int4 column cut [{a}, {b}) is not aligned to the group size {t.group_size}")
+        return W4A8Weight(t.packed[..., a // 2:b // 2, :].contiguous(),
+                          t.scale[..., a // t.group_size:b // t.group_size, :].contiguous(), b - a, t.group_size)
+    if kind == "rows":
+        return t[ranges[0][0]:ranges[0][1]] if len(ranges) == 1 else torch.cat([t[a:b] for a, b in ranges])
+    (a, b), = ranges
+    return t[:, a:b].contiguous()
+
+
+def shard_state_dict(cfg: ModelConfig, sd: dict, rank: int, world: int) -> dict:
+    """The slice of a full state dict that rank ``rank`` of ``world`` computes with (dense tensors and
+    quantised containers alike).  Tensors that every rank needs whole (norms, embedding, router) are
+    shared, not copied.  A dict that was read rank-sliced from disk (``weights.loader.load_checkpoint``
+    with ``tp=(rank, world)``) carries a mark and is returned as it is."""
+    mark = sd.get(TP_MARK)
+    if mark is not None:
+        if tuple(mark) != (rank, world):
+            raise ValueError(f"state dict holds the slices of rank {mark}, not of {(rank, world)}")
+        return {k: v for k, v in sd.items() if k != TP_MARK}
+    lc = local_config(cfg, world)
+    out = {key: apply_plan(t, slice_plan(cfg, key, rank, world)) for key, t in sd.items()}
     assert lc.hidden_size == cfg.hidden_size
     return out
 

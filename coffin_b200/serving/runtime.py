@@ -213,7 +213,8 @@ class Server:
         return SamplingParams(temperature=float(req.get("temperature", 0.0) or 0.0), max_tokens=max(1, max_new),
                               eos=self.eos, ignore_eos=bool(req.get("ignore_eos", False)),
                               deadline=time.monotonic() + secs if secs > 0 else None,
-                              seed=req.get("seed"))
+                              seed=req.get("seed"),
+                              spec_k=int(req["spec_k"]) if req.get("spec_k") is not None else -1)
 
     def _collect(self, seq: Sequence, outq: "queue.Queue", on_token=None) -> str:
         while True:
@@ -236,7 +237,11 @@ class Server:
                 "window_full": seq.finish_reason == "window", "cached_tokens": seq.cached_tokens,
                 "prefill_ms": round(prefill_ms, 2), "decode_ms": round(decode_ms, 2),
                 "decode_tok_s": round((n_new - 1) / (decode_ms / 1e3), 2) if decode_ms > 0 and n_new > 1 else 0.0,
-                "stopped": seq.finish_reason, "spec_k": 0, "spec": None}
+                "stopped": seq.finish_reason,
+                "spec_k": self.engine.runner.spec_k_of(seq) if seq.params.temperature <= 0 else 0,
+                "spec": ({"steps": seq.spec_steps, "drafted": seq.spec_drafted, "accepted": seq.spec_accepted,
+                          "accept_rate": round(seq.spec_accepted / seq.spec_drafted, 4) if seq.spec_drafted else 0.0}
+                         if seq.spec_steps else None)}
 
     # ------------------------------------------------------------------ chat rendering
     def _render(self, req: dict) -> tuple[list[int], bool, str | None]:

@@ -81,7 +81,7 @@ def short_name(mangled: str) -> str:
 def trace_decode(model, M: int, replays: int = 4):
     """Returns ``[(name, lead_us, span_us)]`` of one replay of bucket ``M``'s decode graph."""
     with StepTrace(model.device) as t:
-        model._graphs.pop((M, model.lane), None)
+        model._graphs.pop(model._gkey(M, False), None)
         t.record_names(True)
         model.capture(M, warmup=0)
         t.record_names(False)

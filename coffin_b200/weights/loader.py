@@ -50,19 +50,55 @@ def fuse_experts(sd: dict[str, torch.Tensor]) -> dict[str, torch.Tensor]:
     return sd
 
 
-def load_checkpoint(model_dir: str | Path, device: str = "cpu", vision: bool = True) -> dict[str, torch.Tensor]:
+def read_sliced(fh, key: str, plan) -> torch.Tensor:
+    """Read tensor ``key`` of an open safetensors file cut by a ``parallel.tp.slice_plan`` (only the
+    bytes of the slice are read: ``get_slice``)."""
+    if plan is None:
+        return fh.get_tensor(key)
+    kind, ranges = plan
+    sl = fh.get_slice(key)
+    if kind == "rows":
+        parts = [sl[a:b] for a, b in ranges]
+        return parts[0] if len(parts) == 1 else torch.cat(parts)
+    (a, b), = ranges
+    return sl[:, a:b].contiguous()
+
+
+def load_checkpoint(model_dir: str | Path, device: str = "cpu", vision: bool = True, tp: tuple[int, int] | None = None,
+                    layers: tuple[int, int] | None = None) -> dict[str, torch.Tensor]:
+    """``tp=(rank, world)``: read only that tensor-parallel rank's slice of every projection (the
+    returned dict is marked, ``shard_state_dict`` then passes it through).  ``layers=(l0, l1)``: read
+    only the decoder layers of a pipeline stage (the embedding, final norm and head are kept).
+    Reference: per-rank ``get_slice`` reads, ``models/qwen35/parallel.py:887-1012``."""
     from safetensors import safe_open
     model_dir = Path(model_dir)
     from .quant_io import is_quantized_dir, load_quantized
+    cfg = plan_of = None
+    if tp is not None and tp[1] > 1:
+        from ..config import load_config
+        from ..parallel.tp import TP_MARK, local_config, slice_plan
+        cfg = load_config(model_dir)
+        local_config(cfg, tp[1])                 # raises when a dimension does not divide
+        plan_of = lambda k: slice_plan(cfg, k, tp[0], tp[1])
+
+    def wanted(k: str) -> bool:
+        if not k.startswith(KEEP_PREFIXES) or (not vision and k.startswith("model.visual.")):
+            return False
+        if layers is not None and k.startswith("model.language_model.layers."):
+            li = int(k.split(".")[3])
+            return layers[0] <= li < layers[1]
+        return True
+
     if is_quantized_dir(model_dir):
-        return load_quantized(model_dir, device=device)
-    sd: dict[str, torch.Tensor] = {}
-    for f in shard_files(model_dir):
-        with safe_open(str(f), framework="pt", device=device) as fh:
-            for k in fh.keys():
-                if not k.startswith(KEEP_PREFIXES):
-                    continue
-                if not vision and k.startswith("model.visual."):
-                    continue
-                sd[k] = fh.get_tensor(k)
-    return fuse_experts(sd)
+        sd = load_quantized(model_dir, device=device, plan_of=plan_of, wanted=wanted)
+    else:
+        sd = {}
+        for f in shard_files(model_dir):
+            with safe_open(str(f), framework="pt", device=device) as fh:
+                for k in fh.keys():
+                    if wanted(k):
+                        sd[k] = read_sliced(fh, k, plan_of(k) if plan_of else None)
+        sd = fuse_experts(sd)
+    if plan_of is not None:
+        sd[TP_MARK] = (tp[0], tp[1])
+    return sd

@@ -134,9 +134,13 @@ def write_quantized(model_dir: str | Path, sd: dict[str, torch.Tensor], out_dir:
 
 
 def load_quantized(model_dir: str | Path, device: str = "cpu", quant: bool = True,
-                   dense_dtype: torch.dtype = torch.bfloat16, check_config: bool = True) -> dict:
+                   dense_dtype: torch.dtype = torch.bfloat16, check_config: bool = True, plan_of=None,
+                   wanted=None) -> dict:
     """State dict (canonical keys) of a pre-quantised directory: projections as ``QWeight`` /
-    ``W4A8Weight`` (or dequantised when ``quant`` is false), the rest dense."""
+    ``W4A8Weight`` (or dequantised when ``quant`` is false), the rest dense.  ``plan_of(key)`` (a
+    ``parallel.tp.slice_plan``) makes every tensor the slice of one tensor-parallel rank: the on-disk
+    ``[K, N]`` tensors are read with ``get_slice`` (output rows = file columns, input columns = file
+    rows), so a rank reads only its bytes.  ``wanted(key)`` filters keys (pipeline stages)."""
     from safetensors import safe_open
     model_dir = Path(model_dir)
     index = read_index(model_dir)
@@ -147,7 +151,38 @@ def load_quantized(model_dir: str | Path, device: str = "cpu", quant: bool = Tru
     sd: dict = {}
     handles: dict[str, object] = {}
 
-    def get(shard: str, name: str) -> torch.Tensor:
+    def cut(h, name: str, plan, layout: str):
+        """Slice tensor ``name`` of file handle ``h``.  ``layout``: "kn" = [K(/2 or /group), N] file
+        tensor of a projection, "n" = a per-output vector (scales), "nk" = [.., N, K], "dense"."""
+        if plan is None:
+            return h.get_tensor(name)
+        kind, ranges = plan
+        sl = h.get_slice(name)
+        nd = len(sl.get_shape())
+        lead = (slice(None),) * (nd - 2) if layout in ("kn", "nk", "kn_grp", "kn_half") and nd > 2 else ()
+        if layout == "dense":
+            if kind == "rows":
+                return torch.cat([sl[a:b] for a, b in ranges]) if len(ranges) > 1 else sl[ranges[0][0]:ranges[0][1]]
+            (a, b), = ranges
+            return sl[:, a:b].contiguous()
+        if layout == "n":                                   # per-output-row vector
+            if kind == "rows":
+                return torch.cat([sl[lead + (slice(a, b),)] if lead else sl[a:b] for a, b in ranges])
+            return h.get_tensor(name)
+        if layout == "nk":
+            if kind == "rows":
+                return torch.cat([sl[lead + (slice(a, b), slice(None))] for a, b in ranges], -2).contiguous()
+            (a, b), = ranges
+            return sl[lead + (slice(None), slice(a, b))].contiguous()
+        div = {"kn": 1, "kn_half": 2, "kn_grp": GROUP}[layout]
+        if kind == "rows":                                  # output rows are the file's last axis
+            return torch.cat([sl[lead + (slice(None), slice(a, b))] for a, b in ranges], -1).contiguous()
+        (a, b), = ranges
+        if a % div or b % div:
+            raise ValueError(f"{name}: column cut [{a}, {b}) is not aligned to {div}")
+        return sl[lead + (slice(a // div, b // div), slice(None))].contiguous()
+
+    def get(shard: str, name: str, plan=None, layout: str = "dense") -> torch.Tensor:
         path = model_dir / shard
         if not path.is_file():
             raise FileNotFoundError(f"{model_dir}: index names {shard}, which is missing")
@@ -156,25 +191,47 @@ def load_quantized(model_dir: str | Path, device: str = "cpu", quant: bool = Tru
             h = handles[shard] = safe_open(str(path), framework="pt", device=device)
         if name not in h.keys():
             raise ValueError(f"{path}: index names {name}, shard does not hold it")
-        return h.get_tensor(name)
+        return cut(h, name, plan, layout)
+
+    def span(plan, full: int, kind: str) -> int:
+        """Extent left of a dimension of ``full`` elements after ``plan`` cut it along ``kind``."""
+        if plan is None or plan[0] != kind:
+            return full
+        return sum(b - a for a, b in plan[1])
 
     for dk, meta in entries.items():
         key, kind, shard = _mem_key(dk), meta["kind"], meta["shard"]
+        if wanted is not None and not wanted(key):
+            continue
+        plan = plan_of(key) if plan_of is not None else None
         if kind == "dense":
-            sd[key] = get(shard, dk)
+            sd[key] = get(shard, dk, plan, "dense")
         elif kind in ("q8", "q8-moe"):
-            kn, sc = get(shard, dk), get(shard, meta["scale_key"])
-            if kn.dtype != torch.int8 or list(kn.shape[-2:]) != [meta["k"], meta["n"]] or sc.shape[-1] != meta["n"]:
+            k_loc, n_loc = span(plan, meta["k"], "cols"), span(plan, meta["n"], "rows")
+            sc = get(shard, meta["scale_key"], plan, "n")
+            if meta.get("nk_key"):
+                q = QWeight(get(shard, meta["nk_key"], plan, "nk"), sc)
+            else:
+                kn = get(shard, dk, plan, "kn")
+                if kn.dtype != torch.int8 or list(kn.shape[-2:]) != [k_loc, n_loc]:
+                    raise ValueError(f"{dk}: tensor does not match its index entry")
+                q = QWeight.from_kn(kn, sc)
+            if list(q.wq.shape[-2:]) != [n_loc, k_loc] or sc.shape[-1] != n_loc:
                 raise ValueError(f"{dk}: tensor does not match its index entry")
-            q = QWeight(get(shard, meta["nk_key"]), sc) if meta.get("nk_key") else QWeight.from_kn(kn, sc)
             sd[key] = q if quant else q.dequant(dense_dtype)
         elif kind in ("q4", "q4-moe"):
-            pk, sc = get(shard, dk), get(shard, meta["scale_key"])
             gs = meta.get("group_size", GROUP)
-            rows_ok = {(meta["k"] + 1) // 2, (meta["k"] + gs - 1) // gs * gs // 2}   # unpadded, or padded to whole groups
-            if pk.dtype != torch.uint8 or pk.shape[-1] != meta["n"] or pk.shape[-2] not in rows_ok:
+            if gs != GROUP and plan is not None:
+                raise ValueError(f"{dk}: sliced reads need group size {GROUP}")
+            pk = get(shard, dk, plan, "kn_half")
+            sc = get(shard, meta["scale_key"], plan, "kn_grp")
+            k_loc, n_loc = span(plan, meta["k"], "cols"), span(plan, meta["n"], "rows")
+            rows_ok = {(k_loc + 1) // 2, (k_loc + gs - 1) // gs * gs // 2}   # unpadded, or padded to whole groups
+            if plan is not None and plan[0] == "cols":
+                rows_ok = {k_loc // 2}
+            if pk.dtype != torch.uint8 or pk.shape[-1] != n_loc or pk.shape[-2] not in rows_ok:
                 raise ValueError(f"{dk}: tensor does not match its index entry")
-            q = W4A8Weight(pk, sc, meta["k"], meta.get("group_size", GROUP))
+            q = W4A8Weight(pk, sc, k_loc, gs)
             sd[key] = q if quant else q.dequant(dense_dtype)
         else:
             raise ValueError(f"{dk}: unknown kind {kind!r}")

@@ -66,3 +66,71 @@ def test_speculative_equals_plain_greedy():
     ref.prefill(torch.tensor(prompt + got[:-1]), 0, 0, torch.tensor(table, dtype=torch.int32), want_logits=False)
     # the speculative model has consumed prompt + all generated tokens but the last one
     assert (model.state - ref.state).abs().max() < 1e-4
+
+
+def _engine(**kw):
+    from coffin_b200.engine.config import EngineConfig
+    from coffin_b200.engine.llm_engine import LLMEngine
+    model = OracleEngineModel(CFG, SD, max_seq=512, num_slots=4)
+    return LLMEngine(model, EngineConfig(max_seq=512, max_num_seqs=4, graph=False, **kw))
+
+
+def _repetitive(seed: int, n: int = 60) -> list[int]:
+    g = torch.Generator().manual_seed(seed)
+    unit = torch.randint(0, CFG.vocab_size, (6,), generator=g).tolist()
+    return (unit * (n // 6 + 1))[:n]
+
+
+@torch.no_grad()
+def test_engine_speculation_equals_plain_greedy_single_and_batched():
+    """``spec_k`` in the engine: the tokens are those of plain greedy decoding, drafts are really
+    verified (some accepted), no block leaks, and the counters reach the sequence."""
+    from coffin_b200.engine.sequence import SamplingParams
+    prompts = [_repetitive(1), _repetitive(2, 45), _repetitive(3, 70)]
+    plain = _engine()
+    ref = [s.output for s in plain.generate(prompts, SamplingParams(max_tokens=24))]
+    # single stream
+    eng = _engine(spec_k=3)
+    for p, r in zip(prompts, ref):
+        s = eng.generate([p], SamplingParams(max_tokens=24))[0]
+        assert s.output == r
+    st = eng.runner.stats()["spec"]
+    assert st["steps"] > 0 and st["drafted"] > 0
+    eng.bm.pool.check()
+    assert eng.bm.pool.used_blocks == 0 or eng.bm.prefix_cache
+    # batched rows, one of them sampling with a temperature (it must not be disturbed by the others' drafts)
+    eng = _engine(spec_k=3, spec_batch=True)
+    seqs = [eng.add_request(p, SamplingParams(max_tokens=24)) for p in prompts]
+    hot = eng.add_request(prompts[0], SamplingParams(max_tokens=10, temperature=0.7, seed=3))
+    while any(not s.finished for s in seqs + [hot]):
+        eng.step()
+    assert [s.output for s in seqs] == ref
+    assert len(hot.output) == 10 and hot.spec_drafted == 0
+    assert sum(s.spec_accepted for s in seqs) > 0
+    assert eng.runner.n_decode_steps < sum(len(r) for r in ref)     # fewer forwards than tokens
+    plain_hot = _engine()
+    h2 = plain_hot.generate([prompts[0]], SamplingParams(max_tokens=10, temperature=0.7, seed=3))[0]
+    assert h2.output == hot.output
+    # a request can switch speculation on for itself, or off
+    eng = _engine()
+    s_on = eng.generate([prompts[0]], SamplingParams(max_tokens=24, spec_k=4))[0]
+    assert s_on.output == ref[0] and s_on.spec_steps > 0
+    eng = _engine(spec_k=3)
+    s_off = eng.generate([prompts[0]], SamplingParams(max_tokens=24, spec_k=0))[0]
+    assert s_off.output == ref[0] and s_off.spec_steps == 0
+
+
+@torch.no_grad()
+def test_engine_speculation_stops_at_eos_and_max_tokens():
+    from coffin_b200.engine.sequence import SamplingParams
+    p = _repetitive(5)
+    ref = _engine().generate([p], SamplingParams(max_tokens=30))[0].output
+    eos = ref[11]
+    cut = ref.index(eos)
+    eng = _engine(spec_k=4)
+    s = eng.generate([p], SamplingParams(max_tokens=30, eos=(eos,)))[0]
+    assert s.output == ref[:cut] and s.finish_reason == "stop"
+    s = eng.generate([p], SamplingParams(max_tokens=7))[0]
+    assert s.output == ref[:7] and s.finish_reason == "length"
+    eng.reset()
+    eng.bm.pool.check()

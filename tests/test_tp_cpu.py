@@ -40,3 +40,59 @@ def test_sharded_partials_sum_to_full(world):
 def test_indivisible_world_is_rejected():
     with pytest.raises(ValueError):
         local_config(preset("tiny"), 3)
+
+
+def _same(a, b) -> bool:
+    from coffin_b200.weights.quant import QWeight, W4A8Weight
+    if isinstance(a, QWeight):
+        return isinstance(b, QWeight) and torch.equal(a.wq, b.wq) and torch.equal(a.scale, b.scale)
+    if isinstance(a, W4A8Weight):
+        return isinstance(b, W4A8Weight) and a.k == b.k and torch.equal(a.codes(), b.codes()) and torch.equal(a.scale, b.scale)
+    return torch.equal(a, b)
+
+
+@pytest.mark.parametrize("scheme", ["none", "int8", "w4a8"])
+@torch.no_grad()
+def test_rank_sliced_reads_equal_slicing_the_full_checkpoint(tmp_path, scheme):
+    """Two ranks read a (pre-quantised) checkpoint directory with ``tp=(rank, 2)``: each gets exactly
+    the slices that ``shard_state_dict`` cuts from the whole state dict, for dense tensors, int8
+    containers (column cuts keep the row scales) and int4 containers (cuts on group boundaries); the
+    sliced int8 partial products still sum to the unsharded product; a pipeline stage reads only its layers."""
+    from coffin_b200.parallel.tp import TP_MARK
+    from coffin_b200.weights.init import save_checkpoint
+    from coffin_b200.weights.loader import load_checkpoint
+    from coffin_b200.weights.quant import QWeight, W4A8Weight
+    from coffin_b200.weights.quant_io import write_quantized
+    cfg = preset("tiny")
+    sd = random_state_dict(cfg, 0)
+    src = save_checkpoint(cfg, sd, tmp_path / "src")
+    path = src
+    if scheme != "none":
+        write_quantized(src, load_checkpoint(src), tmp_path / "q", scheme=scheme)
+        path = tmp_path / "q"
+    full = load_checkpoint(path)
+    world = 2
+    parts = []
+    for r in range(world):
+        got = load_checkpoint(path, tp=(r, world))
+        assert got[TP_MARK] == (r, world)
+        ref = shard_state_dict(cfg, full, r, world)
+        assert shard_state_dict(cfg, got, r, world).keys() == ref.keys()       # a marked dict passes through
+        with pytest.raises(ValueError):
+            shard_state_dict(cfg, got, 1 - r, world)
+        for k, v in ref.items():
+            assert _same(got[k], v), k
+        parts.append(got)
+    if scheme == "int8":
+        key = f"{LM}layers.0.mlp.down_proj.weight"
+        x = torch.randn(3, cfg.intermediate_size)
+        half = cfg.intermediate_size // 2
+        whole = x @ full[key].dequant().t()
+        summed = sum(x[:, r * half:(r + 1) * half] @ parts[r][key].dequant().t() for r in range(world))
+        assert (whole - summed).abs().max() < 1e-4
+        assert isinstance(parts[0][key], QWeight)
+    if scheme == "w4a8":
+        assert isinstance(parts[0][f"{LM}layers.0.mlp.down_proj.weight"], W4A8Weight)
+    stage = load_checkpoint(path, layers=(2, 4))
+    assert any(k.startswith(f"{LM}layers.2.") for k in stage) and not any(k.startswith(f"{LM}layers.0.") for k in stage)
+    assert f"{LM}embed_tokens.weight" in stage and f"{LM}norm.weight" in stage
