@@ -37,6 +37,7 @@ __global__ void __launch_bounds__(256) tp_pf_reduce_gather_kernel(const TpPfDev*
                                                                   int T, unsigned seq) {
   griddep_launch();
   griddep_wait();
+  seq = tp_pf_seq(d, seq);
   tp_pf_wait(d->flags1[d->rank], d->world, seq, d->status, d->wait_ns);
   const int rpr = d->rows_per_rank, W = d->width, vec = W >> 3, world = d->world;
   const int row0 = d->rank * rpr;
@@ -69,7 +70,10 @@ __global__ void __launch_bounds__(256) tp_pf_reduce_gather_kernel(const TpPfDev*
 __global__ void tp_pf_wait_kernel(const TpPfDev* d, unsigned seq) {
   griddep_launch();
   griddep_wait();
+  const bool counted = seq == 0;
+  seq = tp_pf_seq(d, seq);
   tp_pf_wait(d->flags2[d->rank], d->world, seq, d->status, d->wait_ns);
+  if (counted && threadIdx.x == 0) *d->seq_dev = seq;      // this all-reduce is complete on this rank
 }
 }  // namespace
 
@@ -175,6 +179,26 @@ __global__ void __launch_bounds__(1024) tp_pull_norm_kernel(const TpComm tp, int
   }
 }
 }  // namespace
+
+// Producer side for projections whose kernel has no push epilogue (the int4 decode projection): store
+// fp32 partial rows [M, N] into this rank's slot of `site` on every rank, paired with the step's epoch.
+namespace {
+__global__ void __launch_bounds__(256) tp_push_rows_kernel(const TpComm tp, int site, const float* __restrict__ src,
+                                                           int64_t lds, int M, int64_t N) {
+  griddep_launch();
+  griddep_wait();
+  for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < (int64_t)M * N; i += (int64_t)gridDim.x * 256) {
+    const int64_t m = i / N, n = i % N;
+    tp_push_value(tp, site, m * N + n, src[m * lds + n]);
+  }
+}
+}  // namespace
+CB_EXPORT int cb_tp_push_rows(const void* tp, int64_t site, const void* src, int64_t lds, int64_t M, int64_t N, void* stream) {
+  if (!tp || !src || site < 0 || M < 1 || N < 1) return CB_ERR_ARG;
+  const unsigned blocks = (unsigned)((M * N + 255) / 256);
+  return (int)cb_launch(tp_push_rows_kernel, dim3(blocks < 148u ? blocks : 148u), dim3(256), 0, (cudaStream_t)stream,
+                        *(const TpComm*)tp, (int)site, (const float*)src, lds, (int)M, N);
+}
 
 CB_EXPORT int cb_tp_pull_norm(const void* tp, int64_t site, const void* res_in, const void* gain, void* res_out,
                               void* out, int64_t M, int64_t K, float eps, void* stream) {

@@ -40,7 +40,7 @@ namespace {
 constexpr int kThreads = 512, kWarps = 16;
 constexpr int kBlock = 64;     // tokens per KV block
 constexpr int kRing = 16;      // conv ring depth
-constexpr int kU = 4;          // (group, k-step) items in flight per lane
+constexpr int kU = 8;          // (group, k-step) items in flight per lane (two 16-byte loads each)
 constexpr int kTileLd = 9;     // padded row length of a warp's 16 x 8 accumulator tile in shared memory
 constexpr int kMaxSplit = 64;
 constexpr unsigned long long kBarWaitNs = 2000000000ull;
@@ -75,6 +75,7 @@ struct MegaArgs {
   int64_t* next;                   // [M]
   unsigned* bar;                   // [0] arrival counter, [1] its value when the kernel starts
   int* status;
+  unsigned long long* trace;       // optional: %globaltimer of CTA 0 at every phase boundary (diagnostic)
   unsigned long long wait_ns;
   int n_layers, M, H, I, ld_proj, ld_logits, ldbt;
   int nk, nv, dk, dv, nh, nkv, rot, nsplit, vocab_local, vocab_total, vocab_off;
@@ -113,7 +114,11 @@ struct Ctx {
   unsigned bar_target;     // counter value that completes the next barrier
   unsigned epoch;          // tensor-parallel epoch of this step
   int n_bar;               // barriers passed (every CTA passes the same number)
+  int n_stamp;             // trace entries written
 };
+__device__ __forceinline__ void stamp(const MegaArgs& a, Ctx& c) {
+  if (a.trace && blockIdx.x == 0 && threadIdx.x == 0) a.trace[c.n_stamp++] = tp_now_ns();
+}
 
 // Grid barrier: every CTA adds one to a monotonic counter and waits until it has reached this
 // barrier's target.  Bounded: gives up after the limit (status 48) and never spins again once the
@@ -191,10 +196,12 @@ __device__ __noinline__ void proj_prefetch(const Proj& p, int cap_kb) {
 // The activation rows are in shared memory, cut into M * S segments (batch row m, k-slice s) of
 // K / S elements each, padded so that the eight segments a warp reads at once fall into distinct
 // bank groups.
-__device__ __noinline__ void proj_run(const MegaArgs& a, const Ctx& c, const Proj& p, const bf16* xs, float* part, float* tile_s,
-                         float* red) {
+// Streaming half of a projection: this CTA's run of groups through the tensor cores, partial sums of
+// every (warp, segment) left in shared memory.  Kept apart from the epilogue so that its registers
+// are allocated for the hot loop alone.
+__device__ __noinline__ void proj_stream(const int M, const Proj& p, const bf16* xs, float* part, float* tile_s) {
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
-  const int M = a.M, S = 8 / M, K = p.K, Ks = K / S, P = (Ks + 31) >> 5, MM2 = 2 * M * M;   // Ks: a multiple of 8
+  const int S = 8 / M, K = p.K, Ks = K / S, P = (Ks + 31) >> 5, MM2 = 2 * M * M;   // Ks: a multiple of 8
   const int seg_ld = Ks + xs_pad(Ks);
   int G0, G1;
   proj_range(p, G0, G1);
@@ -207,57 +214,70 @@ __device__ __noinline__ void proj_run(const MegaArgs& a, const Ctx& c, const Pro
   const bf16* xlane = xs + (int64_t)g * seg_ld + t * 8;
   float* tile = tile_s + warp * 16 * kTileLd;
   if (i0 < i1) {
-    int gl = i0 / P, pp = i0 - gl * P;
+    // The warp's items are a run of (group, k-step) pairs: a tail of its first group, whole groups, a
+    // head of its last one.  Row pointers are set once per segment; the inner loop issues kU pairs of
+    // 16-byte loads before the first multiply, so that a warp keeps 8 KB in flight.
+    int gl = i0 / P, pb = i0 - gl * P, it = i0;
     const int gl_first = gl;
-    float acc[4] = {0.f, 0.f, 0.f, 0.f};
-    for (int it = i0; it < i1; it += kU) {
-      uint4 lo[kU], hi[kU], xv[kU];
-      int gl2 = gl, p2 = pp;
+    const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+    while (it < i1) {
+      const int pe = min(P, pb + (i1 - it));
+      const int64_t rbase = (int64_t)(G0 + gl) * p.rg + wr_lo;
+      const bf16* wlo = p.W + min(rbase, (int64_t)p.rows_total - 1) * K + lane_koff;
+      const bf16* whi = p.W + min(rbase + p.hi_base, (int64_t)p.rows_total - 1) * K + lane_koff;
+      float acc[4] = {0.f, 0.f, 0.f, 0.f};
+      for (int pp = pb; pp < pe; pp += kU) {
+        uint4 lo[kU], hi[kU];
 #pragma unroll
-      for (int u = 0; u < kU; ++u) {
-        if (it + u < i1) {
-          const int64_t rbase = (int64_t)(G0 + gl2) * p.rg + wr_lo;
-          const int64_t r_lo = min(rbase, (int64_t)p.rows_total - 1);
-          const int64_t r_hi = min(rbase + p.hi_base, (int64_t)p.rows_total - 1);
-          // the last k-step of a slice may be ragged (Ks not a multiple of 32): missing chunks are zeros
-          const bool okc = p2 * 32 + t * 8 < Ks;
-          const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
-          lo[u] = okc ? ld_stream(p.W + r_lo * K + lane_koff + p2 * 32) : zero;
-          hi[u] = okc ? ld_stream(p.W + r_hi * K + lane_koff + p2 * 32) : zero;
-          xv[u] = okc ? *reinterpret_cast<const uint4*>(xlane + p2 * 32) : zero;
-          if (++p2 == P) { p2 = 0; ++gl2; }
+        for (int u = 0; u < kU; ++u) {
+          const int q = pp + u;
+          // past the segment, or in the ragged last k-step of a slice (Ks not a multiple of 32): zeros
+          const bool ok = q < pe && q * 32 + t * 8 < Ks;
+          lo[u] = ok ? ld_stream(wlo + q * 32) : zero;
+          hi[u] = ok ? ld_stream(whi + q * 32) : zero;
+        }
+#pragma unroll
+        for (int u = 0; u < kU; ++u) {
+          const int q = pp + u;
+          const bool ok = q < pe && q * 32 + t * 8 < Ks;
+          const uint4 xv = ok ? *reinterpret_cast<const uint4*>(xlane + q * 32) : zero;
+          mma16816(acc, lo[u].x, hi[u].x, lo[u].y, hi[u].y, xv.x, xv.y);
+          mma16816(acc, lo[u].z, hi[u].z, lo[u].w, hi[u].w, xv.z, xv.w);
         }
       }
-#pragma unroll
-      for (int u = 0; u < kU; ++u) {
-        if (it + u < i1) {
-          mma16816(acc, lo[u].x, hi[u].x, lo[u].y, hi[u].y, xv[u].x, xv[u].y);
-          mma16816(acc, lo[u].z, hi[u].z, lo[u].w, hi[u].w, xv[u].z, xv[u].w);
-          ++pp;
-          if (pp == P || it + u == i1 - 1) {
-            // flush: C[i][n] pairs weight-row slot / slice of A row i with batch row / slice of B column n;
-            // the products of equal slices are the k-slices of one output
-            tile[g * kTileLd + 2 * t] = acc[0];
-            tile[g * kTileLd + 2 * t + 1] = acc[1];
-            tile[(g + 8) * kTileLd + 2 * t] = acc[2];
-            tile[(g + 8) * kTileLd + 2 * t + 1] = acc[3];
-            __syncwarp();
-            float* dst = part + ((int64_t)warp * maxseg + (gl - gl_first)) * MM2;
-            for (int o = lane; o < MM2; o += 32) {
-              const int wr = o / M, m = o % M;
-              const int ib = wr < M ? wr * S : 8 + (wr - M) * S, nb = m * S;
-              float v = 0.f;
-              for (int s = 0; s < S; ++s) v += tile[(ib + s) * kTileLd + nb + s];
-              dst[o] = v;
-            }
-            __syncwarp();
-            acc[0] = acc[1] = acc[2] = acc[3] = 0.f;
-            if (pp == P) { pp = 0; ++gl; }
-          }
-        }
+      // flush: C[i][n] pairs weight-row slot / slice of A row i with batch row / slice of B column n;
+      // the products of equal slices are the k-slices of one output
+      tile[g * kTileLd + 2 * t] = acc[0];
+      tile[g * kTileLd + 2 * t + 1] = acc[1];
+      tile[(g + 8) * kTileLd + 2 * t] = acc[2];
+      tile[(g + 8) * kTileLd + 2 * t + 1] = acc[3];
+      __syncwarp();
+      float* dst = part + ((int64_t)warp * maxseg + (gl - gl_first)) * MM2;
+      for (int o = lane; o < MM2; o += 32) {
+        const int wr = o / M, m = o % M;
+        const int ib = wr < M ? wr * S : 8 + (wr - M) * S, nb = m * S;
+        float v = 0.f;
+        for (int sidx = 0; sidx < S; ++sidx) v += tile[(ib + sidx) * kTileLd + nb + sidx];
+        dst[o] = v;
       }
+      __syncwarp();
+      it += pe - pb;
+      pb = 0;
+      ++gl;
     }
   }
+}
+
+__device__ __noinline__ void proj_run(const MegaArgs& a, const Ctx& c, const Proj& p, const bf16* xs, float* part, float* tile_s,
+                         float* red) {
+  proj_stream(a.M, p, xs, part, tile_s);
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int M = a.M, S = 8 / M, Ks = p.K / S, P = (Ks + 31) >> 5, MM2 = 2 * M * M;
+  int G0, G1;
+  proj_range(p, G0, G1);
+  const int ng = G1 - G0, items = ng * P;
+  const int ipw = (items + kWarps - 1) / kWarps;
+  const int maxseg = ipw > 0 ? (ipw + P - 1) / P + 1 : 1;
   __syncthreads();
   // ---- finalise: fixed-order sum over the warps that touched a group, then the epilogue ----------
   auto group_sum = [&](int gl, int r) -> float {
@@ -815,6 +835,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mega_kernel(const MegaArgs
   Ctx c;
   c.bar_target = __ldcg(a.bar + 1);
   c.n_bar = 0;
+  c.n_stamp = 0;
   c.epoch = a.tp_on ? __ldcg(a.tp.epoch) + 1u : 0u;
 
   auto make_proj = [&](const bf16* W, int rows_total, int K, int n_out, int mode, void* out, int ldo, int site) {
@@ -827,6 +848,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mega_kernel(const MegaArgs
   bf16* res_cur = a.res0;
   bf16* res_nxt = a.res1;
   bool have_h = false;
+  stamp(a, c);
   for (int li = 0; li < a.n_layers; ++li) {
     const MegaLayer& L = a.layers[li];
     const bool lin = L.kind == 0;
@@ -838,10 +860,13 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mega_kernel(const MegaArgs
     const Proj pdown = make_proj(L.w_down, H, a.I, H, 1, a.h, H, 2 * li + 1);
     if (li == 0 && !a.use_res0) prologue_norm(a, nullptr, a.tokens_in, nullptr, L.in_gain, res_nxt, H, xs, red);
     else prologue_norm(a, res_cur, nullptr, have_h ? a.h : nullptr, L.in_gain, res_nxt, H, xs, red);
+    stamp(a, c);
     { bf16* t = res_cur; res_cur = res_nxt; res_nxt = t; }
     proj_run(a, c, pin, xs, part, tile_s, red);
+    stamp(a, c);
     if (a.prefetch && tid == 0) proj_prefetch(pout, a.prefetch);
     grid_barrier(a, c);
+    stamp(a, c);
     // ---- B: mixer ---------------------------------------------------------------------------------
     if (lin) {
       gdn_phase<DK>(a, L, phase_sm);
@@ -850,22 +875,32 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mega_kernel(const MegaArgs
       grid_barrier(a, c);
       attn_merge_phase<HD>(a, phase_sm);
     }
+    stamp(a, c);
     if (a.prefetch && tid == 0) proj_prefetch(pgu, a.prefetch);
     grid_barrier(a, c);
+    stamp(a, c);
     // ---- C: output projection (+ all-reduce) ---------------------------------------------------------
     if (lin) prologue_gdn_act(a, L, xs);
     else prologue_copy_f32(a, a.mix, mixw, xs);
+    stamp(a, c);
     proj_run(a, c, pout, xs, part, tile_s, red);
+    stamp(a, c);
     grid_barrier(a, c);
+    stamp(a, c);
     // ---- D: gate | up with SwiGLU ----------------------------------------------------------------
     prologue_norm(a, res_cur, nullptr, a.h, L.post_gain, res_nxt, H, xs, red);
+    stamp(a, c);
     { bf16* t = res_cur; res_cur = res_nxt; res_nxt = t; }
     proj_run(a, c, pgu, xs, part, tile_s, red);
+    stamp(a, c);
     if (a.prefetch && tid == 0) proj_prefetch(pdown, a.prefetch);
     grid_barrier(a, c);
+    stamp(a, c);
     // ---- E: down projection (+ all-reduce) ---------------------------------------------------------
     prologue_copy_bf16(a, a.inter, a.I, a.I, xs);
+    stamp(a, c);
     proj_run(a, c, pdown, xs, part, tile_s, red);
+    stamp(a, c);
     if (a.prefetch && tid == 0) {
       if (li + 1 < a.n_layers) {
         const MegaLayer& Ln = a.layers[li + 1];
@@ -875,13 +910,17 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mega_kernel(const MegaArgs
       }
     }
     grid_barrier(a, c);
+    stamp(a, c);
     have_h = true;
   }
   // ---- lm_head + arg-max -----------------------------------------------------------------------------
   const Proj phead = make_proj(a.lm_head, a.vocab_local, H, a.vocab_local, 3, a.logits, a.ld_logits, -1);
   prologue_norm(a, res_cur, nullptr, have_h ? a.h : nullptr, a.final_gain, res_nxt, H, xs, red);
+  stamp(a, c);
   proj_run(a, c, phead, xs, part, tile_s, red);
+  stamp(a, c);
   grid_barrier(a, c);
+  stamp(a, c);
   if (blockIdx.x == 0) {
     // reduce the CTAs' candidates (ties to the lowest index); one warp per batch row
     const int lane = tid & 31, warp = tid >> 5;

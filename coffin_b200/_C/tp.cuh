@@ -180,7 +180,15 @@ struct TpPfDev {
   unsigned* arrive;               // local: [2] CTA arrival counters (scatter, gather)
   int* status;
   unsigned long long wait_ns;     // limit of a device-side wait (0: kTpWaitNs)
+  unsigned* seq_dev;              // local: sequence number of the last completed all-reduce
 };
+
+// Sequence number of the all-reduce in progress.  The kernels are passed 0 and take "last completed
+// + 1" from device memory (the wait kernel, last of the three, stores it back), so a captured CUDA
+// graph advances the numbering on every replay; a non-zero argument is used as it is.
+__device__ __forceinline__ unsigned tp_pf_seq(const TpPfDev* d, unsigned seq_arg) {
+  return seq_arg ? seq_arg : *reinterpret_cast<const volatile unsigned*>(d->seq_dev) + 1u;
+}
 
 // Bounded wait for `flags[0..world)` (local) to reach `seq`. Thread 0 of the block waits.
 __device__ __forceinline__ void tp_pf_wait(const unsigned* flags, int world, unsigned seq, int* status,
@@ -210,6 +218,7 @@ __device__ __forceinline__ void tp_pf_publish(const TpPfDev* d, int which, unsig
   // callers have done __threadfence_system() + a barrier over the storing threads
   const unsigned prev = atomicAdd(d->arrive + (which - 1), 1u);
   if (prev == nblocks - 1) {
+    seq = tp_pf_seq(d, seq);
     d->arrive[which - 1] = 0;
     __threadfence_system();
     for (int p = 0; p < d->world; ++p)

@@ -109,18 +109,20 @@ class LLMEngine:
     # ------------------------------------------------------------------ prefill
     def _run_prefill(self, batch, out: list[StepOutput]) -> bool:
         progressed = False
-        for seq, n in zip(batch.seqs, batch.chunks):
-            if seq.finished or seq.status is not SequenceStatus.PREFILLING:
-                continue
-            done = self.runner.prefill_chunk(seq, n)
-            if done == 0:
+        todo = [(seq, n) for seq, n in zip(batch.seqs, batch.chunks)
+                if not seq.finished and seq.status is SequenceStatus.PREFILLING]
+        if not todo:
+            return False
+        done = self.runner.prefill_many([s for s, _ in todo], [n for _, n in todo])
+        for seq, _n in todo:
+            if done.get(seq.seq_id, 0) == 0:
                 # no room even for one chunk: take blocks back from someone else
                 victim = self.scheduler.preempt_victim(exclude=seq)
-                if victim is not None:
+                if victim is not None and victim.status is not SequenceStatus.FINISHED:
                     self._preempt(victim)
-                elif seq.blocks is not None and not seq.blocks.table and self.bm.pool.free_blocks == 0:
-                    pass
                 continue
+            if seq.finished or seq.status is not SequenceStatus.PREFILLING:
+                continue                                  # preempted by an earlier sequence of this batch
             progressed = True
             if seq.remaining_prefill == 0:
                 self.runner.finish_prefill(seq)

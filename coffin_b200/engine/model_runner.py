@@ -34,6 +34,7 @@ class ModelRunner:
         self.n_decode_steps = 0
         self.n_cached_tokens = 0
         self.n_spec_steps = self.n_spec_drafted = self.n_spec_accepted = 0
+        self.n_prefill_groups = 0
         # device status words (bounded waits that ran out): queued after every model call, looked at
         # after the next synchronisation (the token read-back in ``sample``)
         self._poll = getattr(model, "poll_status", None)
@@ -92,17 +93,70 @@ class ModelRunner:
                                         embeds=embeds, cos_sin=cos_sin, want_logits=last)
             if self._poll is not None:
                 self._poll()
-            seq.blocks.commit(T)
-            seq.num_computed = end
-            self.n_prefill_tokens += T
+            self._chunk_done(seq, end, logits)
             done += T
-            if last:
-                seq.pending_logits = logits
-            if self.bm.prefix_cache and end % self.block_size == 0 and not last:
-                iv = max(self.block_size, self.cfg.snapshot_interval // self.block_size * self.block_size)
-                tail = (seq.num_tokens - 1) // self.block_size * self.block_size
-                if end % iv == 0 or end == tail:
-                    seq.snap_marks[end] = self.model.snapshot_state(seq.slot)
+        return done
+
+    def _chunk_done(self, seq: Sequence, end: int, logits) -> None:
+        """Bookkeeping after the tokens ``[num_computed, end)`` of ``seq`` ran."""
+        T = end - seq.num_computed
+        last = end == seq.num_tokens
+        seq.blocks.commit(T)
+        seq.num_computed = end
+        self.n_prefill_tokens += T
+        if last:
+            seq.pending_logits = logits
+        if self.bm.prefix_cache and end % self.block_size == 0 and not last:
+            iv = max(self.block_size, self.cfg.snapshot_interval // self.block_size * self.block_size)
+            tail = (seq.num_tokens - 1) // self.block_size * self.block_size
+            if end % iv == 0 or end == tail:
+                seq.snap_marks[end] = self.model.snapshot_state(seq.slot)
+
+    def prefill_many(self, seqs: list[Sequence], budgets: list[int]) -> dict[int, int]:
+        """Run the scheduled prefill quanta of several sequences.  Chunks of text-only sequences share
+        forwards (``model.prefill_group``: one GEMM over the stacked rows per projection), so a burst of
+        short prompts costs about one pass over the weights instead of one per prompt.  Chunks are still
+        cut at snapshot boundaries, so a sequence may take part in several rounds of one call.
+        Returns ``{seq_id: tokens computed}`` (0 = no room for that sequence)."""
+        done = {s.seq_id: 0 for s in seqs}
+        group_fn = getattr(self.model, "prefill_group", None)
+        text = [s for s in seqs if s.mm is None]
+        if group_fn is None or len(text) < 2 or not self.cfg.group_prefill:
+            for s, n in zip(seqs, budgets):
+                done[s.seq_id] = self.prefill_chunk(s, n)
+            return done
+        budget = {s.seq_id: n for s, n in zip(seqs, budgets)}
+        for s in seqs:
+            if s.mm is not None:
+                done[s.seq_id] = self.prefill_chunk(s, budget[s.seq_id])
+        cap = getattr(self.model, "max_chunk", self.cfg.chunk)
+        stuck: set[int] = set()
+        while True:
+            group, total = [], 0
+            for s in text:
+                left = budget[s.seq_id] - done[s.seq_id]
+                if left <= 0 or s.remaining_prefill <= 0 or s.seq_id in stuck:
+                    continue
+                end = self._chunk_end(s, left)
+                T = end - s.num_computed
+                if total + T > cap:
+                    continue
+                if not self.bm.ensure_blocks(s.blocks, T):
+                    stuck.add(s.seq_id)
+                    continue
+                group.append((s, end))
+                total += T
+            if not group:
+                break
+            items = [(self._tokens(s.all_tokens[s.num_computed:end]), s.num_computed, s.slot, self._table(s)) for s, end in group]
+            want = [end == s.num_tokens for s, end in group]
+            outs = group_fn(items, want_logits=want)
+            if self._poll is not None:
+                self._poll()
+            self.n_prefill_groups += 1
+            for (s, end), lg in zip(group, outs):
+                done[s.seq_id] += end - s.num_computed
+                self._chunk_done(s, end, lg)
         return done
 
     def finish_prefill(self, seq: Sequence) -> None:
@@ -291,5 +345,5 @@ class ModelRunner:
 
     def stats(self) -> dict:
         return {"prefill_tokens": self.n_prefill_tokens, "decode_steps": self.n_decode_steps,
-                "cached_tokens": self.n_cached_tokens,
+                "cached_tokens": self.n_cached_tokens, "prefill_groups": self.n_prefill_groups,
                 "spec": {"steps": self.n_spec_steps, "drafted": self.n_spec_drafted, "accepted": self.n_spec_accepted}}

@@ -36,7 +36,7 @@ class _Layer(ctypes.Structure):
 
 _PTRS = ("layers", "embed", "tokens_in", "slots", "block_table", "cos", "sin", "final_gain", "lm_head", "tokens",
          "positions", "rope_pos", "res0", "res1", "h", "proj", "mix", "inter", "part_o", "part_ml", "logits", "cand",
-         "next", "bar", "status")
+         "next", "bar", "status", "trace")
 _INTS = ("n_layers", "M", "H", "I", "ld_proj", "ld_logits", "ldbt", "nk", "nv", "dk", "dv", "nh", "nkv", "rot", "nsplit",
          "vocab_local", "vocab_total", "vocab_off", "part_floats", "xs_elems", "advance", "use_res0", "prefetch", "tp_on")
 
@@ -79,6 +79,7 @@ class MegaDecode:
         self.bar = torch.zeros(4, dtype=torch.int32, device=dev)
         self._bufs: dict = {}
         self._args: dict = {}
+        self.trace: torch.Tensor | None = None        # %globaltimer stamps of CTA 0 (see ``phase_times``)
         self.mixw = max(c.lin_vdim if model.lin_ids else 0, c.num_attention_heads * c.head_dim if model.full_ids else 0)
 
     # ------------------------------------------------------------------ qualification
@@ -201,6 +202,7 @@ class MegaDecode:
         a.part_o, a.part_ml = _ptr(mb["part_o"]), _ptr(mb["part_ml"])
         a.logits, a.cand, a.next = _ptr(rb["logits_local"]), _ptr(mb["cand"]), _ptr(rb["next"])
         a.bar, a.status = self.bar.data_ptr(), K.status_word(m.device).data_ptr()
+        a.trace = _ptr(self.trace)
         a.wait_ns = int(float(os.environ.get("COFFIN_MEGA_WAIT_MS", "2000")) * 1e6)
         a.n_layers, a.M, a.H, a.I = len(m.layers), M, c.hidden_size, c.intermediate_size
         a.ld_proj, a.ld_logits, a.ldbt = rb["proj"].stride(0), rb["logits_local"].stride(0), rb["block_table"].stride(0)
@@ -234,6 +236,34 @@ class MegaDecode:
         if rc != 0:
             raise _lib.KernelError(f"cb_decode_mega failed ({rc})")
         K._count()
+
+    STAMPS_PER_LAYER = 14
+    PHASES = ("in: prologue", "in: projection", "barrier", "mixer", "barrier", "out: prologue", "out: projection",
+              "barrier", "gate|up: prologue", "gate|up: projection", "barrier", "down: prologue", "down: projection",
+              "barrier")
+
+    def enable_trace(self, on: bool = True) -> None:
+        """Make CTA 0 stamp ``%globaltimer`` at every phase boundary of the following launches."""
+        n = 4 + self.STAMPS_PER_LAYER * len(self.model.layers)
+        self.trace = torch.zeros(n, dtype=torch.int64, device=self.model.device) if on else None
+        self._args.clear()
+
+    def phase_times(self) -> dict:
+        """Microseconds per phase kind of the last traced launch: per-layer sums split by layer kind,
+        the head, and the whole step (first to last stamp)."""
+        t = self.trace.cpu().tolist()
+        L = len(self.model.layers)
+        out = {"step_us": (t[-1] - t[0]) / 1e3, "lin": {}, "full": {}, "head": {}}
+        for li, lw in enumerate(self.model.layers):
+            base = 1 + li * self.STAMPS_PER_LAYER
+            kind = "lin" if lw.kind == LINEAR else "full"
+            for j, name in enumerate(self.PHASES):
+                key = name if name != "barrier" else f"barrier {j}"
+                out[kind][key] = out[kind].get(key, 0.0) + (t[base + j] - t[base + j - 1]) / 1e3
+        base = 1 + L * self.STAMPS_PER_LAYER
+        for j, name in enumerate(("head: prologue", "head: projection", "barrier")):
+            out["head"][name] = (t[base + j] - t[base + j - 1]) / 1e3
+        return out
 
     def reset(self) -> None:
         """After a failed step: the barrier counter may have been left between two targets."""

@@ -275,6 +275,7 @@ class Qwen35Model:
         self.input_hidden = None   # when set, a decode step starts from this [M, H] input instead of the token embedding
         self.tp_force = False      # run the push/pull path even with world == 1 (single-GPU test of the protocol)
         self._step_launches: dict[int, int] = {}
+        self._w4_part: dict[int, torch.Tensor] = {}
         # persistent decode kernel (one cooperative launch per step), planned on first use
         self.mega = None
         self._mega_planned = False
@@ -292,8 +293,9 @@ class Qwen35Model:
         return BUCKETS[-1] if (not multi or self.wide_parallel_ok()) else WIDE
 
     def wide_parallel_ok(self) -> bool:
-        """Whether buckets above ``WIDE`` rows run under tensor / expert parallelism."""
-        return False
+        """Whether buckets above ``WIDE`` rows run under tensor / expert parallelism: the exchange of
+        the wide step is the communicator's peer-memory prefill region."""
+        return self.tp is not None and self.tp.pf_rows >= BUCKETS[-1]
 
     def launches_per_step(self, M: int) -> int:
         """Kernels launched by one decode step of bucket ``M`` (counted while capturing)."""
@@ -306,7 +308,16 @@ class Qwen35Model:
             return K.gemv_i8(W.wq, W.scale, x, out, **kw)
         if isinstance(W, QW4):
             if kw.get("tp") is not None and kw.get("push_site", -1) >= 0:
-                raise NotImplementedError("W4A8 projections do not push tensor-parallel partial sums")
+                # row-parallel int4 projection under tensor parallelism: fp32 partial rows, then a small
+                # kernel stores them into every rank's inbox (the int4 GEMV has no push epilogue)
+                M = kw.get("rows") or x.shape[0]
+                part = self._w4_part.get(M)
+                if part is None:
+                    part = self._w4_part[M] = torch.empty(M, self.cfg.hidden_size, dtype=torch.float32, device=self.device)
+                K.gemv_w4(W.wq, W.scale, x, part[:, :W.shape[0]])
+                K.call("tp_push_rows", kw["tp"].cstruct_ref(), kw["push_site"], part, part.stride(0), M, W.shape[0])
+                K._count()
+                return None
             norm = kw.get("norm")
             if kw.get("tp") is not None and kw.get("pull_site", -1) >= 0:
                 # expert parallel: the sum pushed by the MoE combine is pulled, added and normalised by
@@ -422,19 +433,44 @@ class Qwen35Model:
         ``cos_sin`` gives per-token rotary rows ``[T, rot]`` (mRoPE) instead of the 1-D table.
         Returns fp32 logits ``[vocab]`` of the last token (or ``None``).
         """
+        out = self.prefill_group([(tokens, pos0, slot, block_table)], embeds=embeds, cos_sin=cos_sin,
+                                 want_logits=[want_logits], want_hidden=want_hidden)
+        return out[0]
+
+    @torch.no_grad()
+    def prefill_group(self, items: list[tuple], embeds: torch.Tensor | None = None,
+                      cos_sin: tuple[torch.Tensor, torch.Tensor] | None = None, want_logits: list[bool] | None = None,
+                      want_hidden: bool = False) -> list:
+        """Chunks of several sequences in ONE forward: ``items[i] = (tokens [T_i], pos0, slot,
+        block_table)``.  The rows of all chunks are stacked, so every projection is one GEMM over
+        ``sum(T_i)`` rows (short prompts share weight tiles instead of each streaming the weights); the
+        delta-net scan and the attention, which are per sequence, run per chunk on its row range.
+        ``embeds`` / ``cos_sin`` cover the stacked rows (only used with a single item by the engine).
+        Returns, per item, the fp32 logits ``[vocab]`` of its last token or ``None``
+        (reference: ``models/qwen35/model.py:861`` ``prefill_group``)."""
         c = self.cfg
-        T = int(tokens.numel())
-        assert 0 < T <= self.max_chunk, f"chunk of {T} tokens exceeds max_chunk {self.max_chunk}"
-        self._check_row(pos0, T, int(block_table.numel()), 0, slot)
+        lens = [int(it[0].numel()) for it in items]
+        T = sum(lens)
+        assert all(n > 0 for n in lens) and T <= self.max_chunk, f"group of {T} tokens exceeds max_chunk {self.max_chunk}"
+        want_logits = list(want_logits) if want_logits is not None else [True] * len(items)
+        for (toks, pos0, slot, bt), n in zip(items, lens):
+            self._check_row(pos0, n, int(bt.numel()), 0, slot)
         ws = self._prefill_ws(T)
         res, normed = ws["res"][:T], ws["normed"][:T]
+        tokens = items[0][0] if len(items) == 1 else torch.cat([it[0] for it in items])
         if embeds is None:
             K.embed_gather(self.embed, tokens, res)
         else:
             res.copy_(embeds)
-        pos = torch.arange(pos0, pos0 + T, dtype=torch.int64, device=self.device)
+        offs = [0]
+        for n in lens:
+            offs.append(offs[-1] + n)
+        pos = torch.cat([torch.arange(it[1], it[1] + n, dtype=torch.int64, device=self.device) for it, n in zip(items, lens)]) \
+            if len(items) > 1 else torch.arange(items[0][1], items[0][1] + T, dtype=torch.int64, device=self.device)
         slots = ws["slots"][:T]
-        slots.copy_(block_table.to(torch.int64)[pos // K.BLOCK] * K.BLOCK + pos % K.BLOCK)
+        for i, (it, n) in enumerate(zip(items, lens)):
+            p = pos[offs[i]:offs[i + 1]]
+            slots[offs[i]:offs[i + 1]].copy_(it[3].to(torch.int64)[p // K.BLOCK] * K.BLOCK + p % K.BLOCK)
         if cos_sin is None:
             cos, sin = self.cos, self.sin
             ridx = ws["ridx"][:T]
@@ -450,9 +486,12 @@ class Qwen35Model:
             if lw.kind == LINEAR:
                 j = self.lin_ids[li]
                 act = ws["act"][:T, :c.lin_vdim]
-                K.gdn_prefill(proj, lw.conv_w, lw.A_log, lw.dt_bias, lw.norm_w, self.ring[j, slot], self.state[j, slot],
-                              ws["gdn"], act, pos0=pos0, nk=c.linear_num_key_heads, nv=c.linear_num_value_heads,
-                              dk=c.linear_key_head_dim, dv=c.linear_value_head_dim, eps=self.eps)
+                for i, (it, n) in enumerate(zip(items, lens)):
+                    sl = slice(offs[i], offs[i + 1])
+                    K.gdn_prefill(proj[sl], lw.conv_w, lw.A_log, lw.dt_bias, lw.norm_w, self.ring[j, it[2]],
+                                  self.state[j, it[2]], ws["gdn"], act[sl], pos0=it[1], nk=c.linear_num_key_heads,
+                                  nv=c.linear_num_value_heads, dk=c.linear_key_head_dim, dv=c.linear_value_head_dim,
+                                  eps=self.eps)
             else:
                 j = self.full_ids[li]
                 act = ws["act"][:T, :c.num_attention_heads * c.head_dim]
@@ -460,8 +499,10 @@ class Qwen35Model:
                 K.attn_prep(proj, lw.qg, lw.kg, cos, sin, ridx, slots, q, self.kpool[j], self.vpool[j],
                             nh=c.num_attention_heads, nkv=c.num_key_value_heads, hd=c.head_dim,
                             rot=c.rotary_dim, eps=self.eps)
-                K.attn_prefill(q, proj, self.kpool[j], self.vpool[j], block_table, act, q_pos0=pos0,
-                               nh=c.num_attention_heads, nkv=c.num_key_value_heads, hd=c.head_dim)
+                for i, (it, n) in enumerate(zip(items, lens)):
+                    sl = slice(offs[i], offs[i + 1])
+                    K.attn_prefill(q[sl], proj[sl], self.kpool[j], self.vpool[j], it[3], act[sl], q_pos0=it[1],
+                                   nh=c.num_attention_heads, nkv=c.num_key_value_heads, hd=c.head_dim)
             if self.tp_world > 1 or (self.tp_force and not c.is_moe):
                 part = self._row_parallel(act, lw.w_out, ws["part"][:T])
                 K.rmsnorm(res, lw.post_gain, self.eps, out=normed, add=part, res_out=res)
@@ -477,18 +518,20 @@ class Qwen35Model:
                     res.add_(self._row_parallel(gu, lw.w_down, ws["part"][:T], swiglu_in=True))
                 else:
                     self._gemm(gu, lw.w_down, out=res, residual=res, swiglu_in=True)
-        out_logits = None
         self.last_hidden = None
-        self.last_prenorm = res            # last-layer residual stream of the chunk (view of the workspace)
+        self.last_prenorm = res            # last-layer residual stream of the group (view of the workspace)
+        out: list = [None] * len(items)
         if not self.pp_last:
-            return None
+            return out
         if want_hidden:
             self.last_hidden = K.rmsnorm(res, self.final_gain, self.eps)
-        if want_logits:
-            local = torch.empty(1, self.vocab_local, dtype=torch.float32, device=self.device)
-            self._gemv(self.lm_head, None, local, norm=(res[T - 1:T].contiguous(), None, self.final_gain, None, self.eps))
-            out_logits = self._gather_logits(local, 1)[0]
-        return out_logits
+        for i in range(len(items)):
+            if want_logits[i]:
+                last = offs[i + 1] - 1
+                local = torch.empty(1, self.vocab_local, dtype=torch.float32, device=self.device)
+                self._gemv(self.lm_head, None, local, norm=(res[last:last + 1].contiguous(), None, self.final_gain, None, self.eps))
+                out[i] = self._gather_logits(local, 1)[0]
+        return out
 
     # ------------------------------------------------------------------ tensor-parallel helpers
     def _tp_reduce(self, t: torch.Tensor) -> torch.Tensor:
@@ -559,6 +602,8 @@ class Qwen35Model:
                 if not c.is_moe:
                     b["gu"] = torch.zeros(M, 2 * c.intermediate_size, dtype=bf, device=dev)
                 b["logits_bf"] = torch.zeros(M, self.vocab_local, dtype=bf, device=dev)
+                if self.tp is not None:
+                    b["part"] = torch.zeros(M, H, dtype=bf, device=dev)
             self._rows[key] = b
         return b
 
@@ -664,11 +709,17 @@ class Qwen35Model:
         """One decode step for a wide bucket (16..64 rows): every row still advances by one token
         through the per-row state kernels (delta-net step, split-KV attention with the fused KV
         append), but the projections run on the tcgen05 GEMM - at these row counts one 128-row tile
-        streams each weight once, which is what the GEMV would do eight rows at a time.  Single-GPU
-        only; the multi-rank paths stay within the narrow buckets."""
-        if self.tp is not None and (self.tp_world > 1 or self.ep_world > 1):
-            raise NotImplementedError("wide decode buckets are not tensor/expert parallel")
+        streams each weight once, which is what the GEMV would do eight rows at a time.
+
+        Tensor parallel: the row-parallel projections scatter their rows to the owning ranks from the
+        GEMM epilogue and a reduce/gather kernel completes the all-reduce (the prefill path's exchange;
+        its sequence numbers live on the device, so the step is captured in a CUDA graph like any
+        other).  Expert parallel: the routed-expert output goes through the same exchange."""
+        multi = self.tp is not None and (self.tp_world > 1 or self.ep_world > 1)
+        if multi and not self.wide_parallel_ok():
+            raise NotImplementedError("wide decode buckets need the peer-memory prefill region of the communicator")
         c, b = self.cfg, self._row_buffers(M)
+        tpw = self.tp_world > 1
         res, normed = b["res"][0], b["normed"]
         if self.input_hidden is not None:
             res.copy_(self.input_hidden)
@@ -692,21 +743,34 @@ class Qwen35Model:
                               b["block_table"], self.kpool[j], self.vpool[j], b["part_o"], b["part_ml"], b["tickets"], act,
                               nh=c.num_attention_heads, nkv=c.num_key_value_heads, hd=c.head_dim,
                               rot=c.rotary_dim, nsplit=b["nsplit"], eps=self.eps)
-            self._gemm(act, lw.w_out, out=res, residual=res)
-            K.rmsnorm(res, lw.post_gain, self.eps, out=normed)
+            if tpw:
+                part = self._row_parallel(act, lw.w_out, b["part"])
+                K.rmsnorm(res, lw.post_gain, self.eps, out=normed, add=part, res_out=res)
+            else:
+                self._gemm(act, lw.w_out, out=res, residual=res)
+                K.rmsnorm(res, lw.post_gain, self.eps, out=normed)
             if lw.moe is not None:
                 res.add_(lw.moe.apply(normed, self))
                 K._count()
             else:
                 self._gemm(normed, lw.w_gu, out=b["gu"])
-                self._gemm(b["gu"], lw.w_down, out=res, residual=res, swiglu_in=True)
+                if tpw:
+                    res.add_(self._row_parallel(b["gu"], lw.w_down, b["part"], swiglu_in=True))
+                    K._count()
+                else:
+                    self._gemm(b["gu"], lw.w_down, out=res, residual=res, swiglu_in=True)
         if not self.pp_last:
             b["hidden"].copy_(res)
             K._count()
             return
         K.rmsnorm(res, self.final_gain, self.eps, out=normed)
         self._gemm(normed, self.lm_head, out=b["logits_bf"])
-        b["logits"].copy_(b["logits_bf"])
+        if tpw:
+            # vocabulary-parallel head: every rank needs the arg-max over the whole vocabulary
+            b["logits_local"].copy_(b["logits_bf"])
+            b["logits"].copy_(self._gather_logits(b["logits_local"], M))
+        else:
+            b["logits"].copy_(b["logits_bf"])
         K._count()
         K.argmax(b["logits"], b["next"])
         b["final_res"] = res
@@ -722,6 +786,13 @@ class Qwen35Model:
         for r in range(n):
             self._check_row(positions[r], 1, len(block_tables[r]), rope_deltas[r] if rope_deltas else 0, slots[r])
         ht, hm, hb = b["h_tokens"], b["h_meta"], b["h_bt"]
+        # the pinned staging arrays are reused: wait until the copies of the previous call have left them
+        # (a caller that queues steps without synchronising would otherwise overwrite rows in flight)
+        ev = b.get("h_event")
+        if ev is None:
+            ev = b["h_event"] = torch.cuda.Event()
+        else:
+            ev.synchronize()
         ht.zero_()
         hm[0].fill_(-1)
         hm[1].zero_()
@@ -738,6 +809,7 @@ class Qwen35Model:
         b["rope_pos"].copy_(hm[1], non_blocking=True)
         b["slots"].copy_(hm[2], non_blocking=True)
         b["block_table"].copy_(hb, non_blocking=True)
+        ev.record()
 
     def _check_row(self, pos0: int, n: int, table_len: int, rope_delta: int = 0, slot: int = 0) -> None:
         """Host-side guard of everything a kernel indexes with a position: ``n`` tokens from ``pos0``

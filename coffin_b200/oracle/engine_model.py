@@ -162,6 +162,14 @@ class OracleEngineModel:
         self.last_hidden = self._norm(x, LM + "norm.weight") if want_hidden else None
         return self._head(x[-1:])[0] if want_logits else None
 
+    @torch.no_grad()
+    def prefill_group(self, items: list[tuple], want_logits: list[bool] | None = None, **kw) -> list:
+        """Chunks of several sequences (``(tokens, pos0, slot, block_table)`` each); the twin runs them one
+        after the other, which is what the stacked forward of the device model computes."""
+        self.n_group_calls = getattr(self, "n_group_calls", 0) + 1
+        want = want_logits if want_logits is not None else [True] * len(items)
+        return [self.prefill(t, p0, slot, bt, want_logits=w) for (t, p0, slot, bt), w in zip(items, want)]
+
     def set_rows(self, M, tokens, positions, slots, block_tables, rope_deltas=None) -> None:
         self._rows = dict(tokens=list(tokens), positions=list(positions), slots=list(slots),
                           tables=[list(t) for t in block_tables],

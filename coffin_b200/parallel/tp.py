@@ -144,7 +144,8 @@ class _TpPfStruct(ctypes.Structure):
                 ("width", ctypes.c_int),
                 ("inbox", ctypes.c_void_p * MAX_WORLD), ("out", ctypes.c_void_p * MAX_WORLD),
                 ("flags1", ctypes.c_void_p * MAX_WORLD), ("flags2", ctypes.c_void_p * MAX_WORLD),
-                ("arrive", ctypes.c_void_p), ("status", ctypes.c_void_p), ("wait_ns", ctypes.c_uint64)]
+                ("arrive", ctypes.c_void_p), ("status", ctypes.c_void_p), ("wait_ns", ctypes.c_uint64),
+                ("seq_dev", ctypes.c_void_p)]
 
 
 class _DevView:
@@ -201,6 +202,7 @@ class TpComm:
             self._off_pf_f1 = self._off_pf_out + slab
             self._off_pf_f2 = self._off_pf_f1 + 256
             self._off_pf_arrive = self._off_pf_f2 + 256
+            self._off_pf_seq = self._off_pf_arrive + 128        # same 256-byte cell as the arrival counters
             self._off_pf_desc = self._off_pf_arrive + 256
             self.nbytes = self._off_pf_desc + 1024
         self._pf_seq = 0
@@ -260,6 +262,7 @@ class TpComm:
             d.arrive = self.base + self._off_pf_arrive
             d.status = self.base + self._off_status
             d.wait_ns = self.wait_ns
+            d.seq_dev = self.base + self._off_pf_seq
             assert ctypes.sizeof(d) == self._lib.cb_tp_pf_desc_size() <= 1024
             rc = self._lib.cb_peer_write(ctypes.c_void_p(self.base + self._off_pf_desc), ctypes.byref(d),
                                          ctypes.c_int64(ctypes.sizeof(d)))
@@ -274,12 +277,13 @@ class TpComm:
         return ctypes.c_void_p(self.base + self._off_pf_desc)
 
     def next_seq(self, rows: int, width: int) -> int:
-        """Sequence number of the next scatter (every rank makes the same calls in the same order)."""
+        """Validates the next all-reduce (every rank makes the same calls in the same order) and returns
+        the sequence argument of its kernels: 0 = "take the number from device memory", which the
+        kernels advance themselves, so that a captured CUDA graph can be replayed."""
         if not self.pf_rows or rows > self.pf_rows or width != self.hidden:
             raise ValueError(f"prefill all-reduce of [{rows}, {width}] outside the region [{self.pf_rows}, {self.hidden}]")
-        self._pf_seq += 1
         self._pf_T = rows
-        return self._pf_seq
+        return 0
 
     def scatter(self, src: torch.Tensor) -> None:
         """First half for a producer that is not a GEMM: send the rows of ``src [T, hidden]`` (bf16) to their owners."""
@@ -293,7 +297,7 @@ class TpComm:
         every rank and wait for everyone's.  Returns the reduced ``[T, hidden]`` rows (a view of the
         result buffer, valid until the next all-reduce)."""
         from ..ops import kernels as K
-        T, seq = self._pf_T, self._pf_seq
+        T, seq = self._pf_T, 0
         K.call("tp_pf_reduce_gather", self.pf_desc_ptr(), residual, residual.stride(0) if residual is not None else 0, T, seq)
         K.call("tp_pf_wait", self.pf_desc_ptr(), seq)
         K._count(2)

@@ -122,3 +122,22 @@ def test_no_head_of_line_blocking_and_reset():
     assert w.finished and w.finish_reason == "reset" and not eng.has_work()
     eng.bm.pool.check()
     assert eng.bm.pool.used_blocks == 0
+
+
+def test_grouped_prefill_shares_forwards_and_matches_solo():
+    """A burst of short prompts: their chunks run as groups (one forward for several sequences), cut at
+    snapshot boundaries, and every sequence still produces its solo tokens; with grouping off the
+    same tokens come out of per-sequence forwards."""
+    prompts = [prompt(30 + 17 * i, 60 + i) for i in range(4)]
+    ref = [solo(p, 5) for p in prompts]
+    eng = engine(chunk=128, prefill_quantum=128, max_num_batched_tokens=256, snapshot_interval=64)
+    seqs = eng.generate(prompts, SamplingParams(max_tokens=5))
+    assert [s.output for s in seqs] == ref
+    assert eng.runner.stats()["prefill_groups"] > 0 and eng.model.n_group_calls > 0
+    eng.bm.pool.check()
+    off = engine(chunk=128, prefill_quantum=128, max_num_batched_tokens=256, snapshot_interval=64, group_prefill=False)
+    assert [s.output for s in off.generate(prompts, SamplingParams(max_tokens=5))] == ref
+    assert off.runner.stats()["prefill_groups"] == 0
+    # the prefix cache still serves a repeated prompt after a grouped prefill
+    again = eng.generate([prompts[3]], SamplingParams(max_tokens=5))[0]
+    assert again.output == ref[3] and again.cached_tokens > 0

@@ -326,3 +326,28 @@ def test_wide_decode_bucket_matches_single_rows(name):
         for r in range(12):
             assert _rel(lg[r], alone[r].cpu()) < tol, (graph, r)
             model.restore_state(r, snaps[r])
+
+
+@torch.no_grad()
+def test_grouped_prefill_equals_separate_prefills():
+    """Three chunks (one of them a continuation at a non-zero position) stacked into one forward give
+    the logits, KV and delta-net states of three separate prefills."""
+    cfg, oracle, model = _setup()
+    _, _, solo_m = _setup()
+    lens = [40, 75, 33]
+    seqs = [_tokens(cfg, n, seed=30 + n) for n in lens]
+    tables = [torch.arange(1 + 8 * r, 9 + 8 * r, dtype=torch.int32, device="cuda") for r in range(3)]
+    for m in (model, solo_m):
+        for r in range(3):
+            m.zero_state(r)
+        m.prefill(seqs[1][:20].cuda(), 0, 1, tables[1], want_logits=False)      # row 1 continues from position 20
+    items = [(seqs[0].cuda(), 0, 0, tables[0]), (seqs[1][20:].cuda(), 20, 1, tables[1]), (seqs[2].cuda(), 0, 2, tables[2])]
+    got = model.prefill_group(items, want_logits=[True, True, False])
+    assert got[2] is None
+    for r in range(3):
+        ref = solo_m.prefill(*items[r], want_logits=True)
+        ref_oracle = oracle.forward(seqs[r], oracle.new_state())[-1]
+        if got[r] is not None:
+            assert _rel(got[r], ref.cpu()) < 2e-2 and _rel(got[r], ref_oracle) < 3e-2
+        assert _rel(model.state[:, r], solo_m.state[:, r].cpu()) < 2e-2
+    assert _rel(model.kpool, solo_m.kpool.cpu()) < 2e-2
