@@ -33,17 +33,35 @@
 // (backends/corex/kernels/mega.cu:79-119, docs/DECODE-LAUNCH-LEDGER.md:27-40,164-184), taken to the
 // whole step and to the multi-GPU exchange.
 #include <string.h>
+#include "sm100.cuh"
 #include "tp.cuh"
 
 namespace {
 
 constexpr int kThreads = 512, kWarps = 16;
+constexpr int kLaunchThreads = kThreads;
 constexpr int kBlock = 64;     // tokens per KV block
 constexpr int kRing = 16;      // conv ring depth
 constexpr int kU = 8;          // (group, k-step) items in flight per lane (two 16-byte loads each)
 constexpr int kTileLd = 9;     // padded row length of a warp's 16 x 8 accumulator tile in shared memory
 constexpr int kMaxSplit = 64;
 constexpr unsigned long long kBarWaitNs = 2000000000ull;
+
+// Weight ring.  Barriers, prologues and mixers do not touch the weights, yet with plain loads the HBM
+// stream stops at every one of them and has to ramp up again (~1-2 us per phase, ~130 phases per
+// step).  With the ring every warp keeps its next few batches of weight fragments in flight into its
+// own stages of shared memory with bulk asynchronous copies (cp.async.bulk, completion counted on an
+// mbarrier): whenever it has consumed a batch it issues the copy of the batch `stages` ahead, and
+// that look-ahead walks the step's whole schedule of projections, so before a warp enters a grid
+// barrier the first batches of the NEXT projection are already under way and land while it waits.
+// A stage holds one batch of one warp: kUR k-steps of its 16 A rows (two weight rows x k-slices), each
+// row a contiguous run of kUR * 64 bytes, rows padded to 64 B mod 128 so that a warp's 16-byte fragment
+// loads hit distinct banks.
+constexpr int kUR = 4;                          // k-steps per ring batch
+constexpr int kRowStride = kUR * 64 + 64;       // bytes between the 16 rows of a stage
+constexpr int kStageBytes = 16 * kRowStride;    // 5120
+constexpr int kMaxStages = 4;
+constexpr int kMaxLayers = 96;
 
 struct MegaLayer {
   const bf16* w_in; const bf16* w_out; const bf16* w_gu; const bf16* w_down;
@@ -85,6 +103,8 @@ struct MegaArgs {
   int use_res0;                    // 1: the step starts from res0 (a staged hidden state), not the embedding
   int prefetch;                    // > 0: KB per CTA of the next projection's slab requested into L2 before each barrier
   int tp_on;
+  int hd;                          // attention head dim (the kernel's HD)
+  int ring_stages;                 // 0: workers load weights themselves; 2..4: stages per warp of the weight ring
   float eps, scale_log2;
   TpComm tp;
 };
@@ -110,6 +130,18 @@ __device__ __forceinline__ float ldcg_bf16(const bf16* p) {
   return __bfloat162float(__ushort_as_bfloat16(__ldcg(reinterpret_cast<const unsigned short*>(p))));
 }
 
+// CTA-wide barrier of the 512 threads.
+__device__ __forceinline__ void cta_sync() { asm volatile("bar.sync 1, 512;" ::: "memory"); }
+__device__ __forceinline__ float wsum512(float v, float* red) {
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  v = warp_sum(v);
+  cta_sync();
+  if (lane == 0) red[w] = v;
+  cta_sync();
+  float t = (lane < kWarps) ? red[lane] : 0.f;
+  return warp_sum(t);
+}
+
 struct Ctx {
   unsigned bar_target;     // counter value that completes the next barrier
   unsigned epoch;          // tensor-parallel epoch of this step
@@ -124,12 +156,13 @@ __device__ __forceinline__ void stamp(const MegaArgs& a, Ctx& c) {
 // barrier's target.  Bounded: gives up after the limit (status 48) and never spins again once the
 // status word is set, so a CTA that cannot make progress costs an error, not a hung GPU.
 __device__ __forceinline__ void grid_barrier(const MegaArgs& a, Ctx& c) {
-  __syncthreads();
+  cta_sync();
   c.bar_target += gridDim.x;
   c.n_bar += 1;
   if (threadIdx.x == 0) {
-    __threadfence();
-    atomicAdd(a.bar, 1u);
+    // one release-add publishes everything this CTA wrote before the barrier (the CTA barrier above
+    // orders the other threads' writes before it); the acquire loads below pair with the other CTAs' adds
+    asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(a.bar), "r"(1u) : "memory");
     if (!tp_status_set(a.status)) {
       const unsigned long long limit = a.wait_ns ? a.wait_ns : kBarWaitNs;
       unsigned long long t0 = 0;
@@ -143,9 +176,8 @@ __device__ __forceinline__ void grid_barrier(const MegaArgs& a, Ctx& c) {
         }
       }
     }
-    __threadfence();
   }
-  __syncthreads();
+  cta_sync();
 }
 
 // Ask the L2 for a contiguous slab (16-byte aligned, size a multiple of 16).  One thread.
@@ -196,81 +228,228 @@ __device__ __noinline__ void proj_prefetch(const Proj& p, int cap_kb) {
 // The activation rows are in shared memory, cut into M * S segments (batch row m, k-slice s) of
 // K / S elements each, padded so that the eight segments a warp reads at once fall into distinct
 // bank groups.
-// Streaming half of a projection: this CTA's run of groups through the tensor cores, partial sums of
-// every (warp, segment) left in shared memory.  Kept apart from the epilogue so that its registers
-// are allocated for the hot loop alone.
-__device__ __noinline__ void proj_stream(const int M, const Proj& p, const bf16* xs, float* part, float* tile_s) {
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
-  const int S = 8 / M, K = p.K, Ks = K / S, P = (Ks + 31) >> 5, MM2 = 2 * M * M;   // Ks: a multiple of 8
-  const int seg_ld = Ks + xs_pad(Ks);
-  int G0, G1;
-  proj_range(p, G0, G1);
-  const int ng = G1 - G0, items = ng * P;
-  const int ipw = (items + kWarps - 1) / kWarps;
-  const int i0 = min(items, warp * ipw), i1 = min(items, i0 + ipw);
-  const int maxseg = ipw > 0 ? (ipw + P - 1) / P + 1 : 1;
-  const int wr_lo = g / S, sl = g % S;
-  const int64_t lane_koff = (int64_t)sl * Ks + t * 8;
-  const bf16* xlane = xs + (int64_t)g * seg_ld + t * 8;
-  float* tile = tile_s + warp * 16 * kTileLd;
-  if (i0 < i1) {
-    // The warp's items are a run of (group, k-step) pairs: a tail of its first group, whole groups, a
-    // head of its last one.  Row pointers are set once per segment; the inner loop issues kU pairs of
-    // 16-byte loads before the first multiply, so that a warp keeps 8 KB in flight.
-    int gl = i0 / P, pb = i0 - gl * P, it = i0;
-    const int gl_first = gl;
-    const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
-    while (it < i1) {
-      const int pe = min(P, pb + (i1 - it));
-      const int64_t rbase = (int64_t)(G0 + gl) * p.rg + wr_lo;
-      const bf16* wlo = p.W + min(rbase, (int64_t)p.rows_total - 1) * K + lane_koff;
-      const bf16* whi = p.W + min(rbase + p.hi_base, (int64_t)p.rows_total - 1) * K + lane_koff;
-      float acc[4] = {0.f, 0.f, 0.f, 0.f};
-      for (int pp = pb; pp < pe; pp += kU) {
-        uint4 lo[kU], hi[kU];
-#pragma unroll
-        for (int u = 0; u < kU; ++u) {
-          const int q = pp + u;
-          // past the segment, or in the ragged last k-step of a slice (Ks not a multiple of 32): zeros
-          const bool ok = q < pe && q * 32 + t * 8 < Ks;
-          lo[u] = ok ? ld_stream(wlo + q * 32) : zero;
-          hi[u] = ok ? ld_stream(whi + q * 32) : zero;
-        }
-#pragma unroll
-        for (int u = 0; u < kU; ++u) {
-          const int q = pp + u;
-          const bool ok = q < pe && q * 32 + t * 8 < Ks;
-          const uint4 xv = ok ? *reinterpret_cast<const uint4*>(xlane + q * 32) : zero;
-          mma16816(acc, lo[u].x, hi[u].x, lo[u].y, hi[u].y, xv.x, xv.y);
-          mma16816(acc, lo[u].z, hi[u].z, lo[u].w, hi[u].w, xv.z, xv.w);
-        }
-      }
-      // flush: C[i][n] pairs weight-row slot / slice of A row i with batch row / slice of B column n;
-      // the products of equal slices are the k-slices of one output
-      tile[g * kTileLd + 2 * t] = acc[0];
-      tile[g * kTileLd + 2 * t + 1] = acc[1];
-      tile[(g + 8) * kTileLd + 2 * t] = acc[2];
-      tile[(g + 8) * kTileLd + 2 * t + 1] = acc[3];
-      __syncwarp();
-      float* dst = part + ((int64_t)warp * maxseg + (gl - gl_first)) * MM2;
-      for (int o = lane; o < MM2; o += 32) {
-        const int wr = o / M, m = o % M;
-        const int ib = wr < M ? wr * S : 8 + (wr - M) * S, nb = m * S;
-        float v = 0.f;
-        for (int sidx = 0; sidx < S; ++sidx) v += tile[(ib + sidx) * kTileLd + nb + sidx];
-        dst[o] = v;
-      }
-      __syncwarp();
-      it += pe - pb;
-      pb = 0;
-      ++gl;
+// The (group, k-step) items of one worker warp in one projection, cut into batches of at most `cap`
+// k-steps that never cross a group.  The workers and the producer warp walk the same sequence.
+struct BatchIter {
+  int it, i1, gl, pb, P, G0, gl_first;
+  __device__ __forceinline__ void init(const Proj& p, int M, int warp) {
+    const int S = 8 / M, Ks = p.K / S;
+    P = (Ks + 31) >> 5;
+    int G1;
+    proj_range(p, G0, G1);
+    const int items = (G1 - G0) * P;
+    const int ipw = (items + kWarps - 1) / kWarps;
+    it = min(items, warp * ipw);
+    i1 = min(items, it + ipw);
+    gl = P ? it / P : 0;
+    pb = it - gl * P;
+    gl_first = gl;
+  }
+  __device__ __forceinline__ bool done() const { return it >= i1; }
+  // next batch: `n` k-steps of group `gl` starting at step `pb`; seg_end: the warp's share of the group ends with it
+  __device__ __forceinline__ void peek(int cap, int& n, bool& seg_end) const {
+    const int pe = min(P, pb + (i1 - it));
+    n = min(cap, pe - pb);
+    seg_end = pb + n == pe;
+  }
+  __device__ __forceinline__ void advance(int n) {
+    pb += n;
+    it += n;
+    if (pb == P) { pb = 0; ++gl; }
+  }
+};
+
+struct Ring {
+  unsigned char* base;      // [kWarps][stages][kStageBytes]
+  uint64_t* full;           // [kWarps][kMaxStages]
+  int stages;               // 0: off
+  unsigned bc;              // batches this warp has consumed since the kernel started
+  unsigned issued;          // batches whose copies it has issued
+  int ph;                   // projection (in program order) the look-ahead is in
+  bool active;              // the look-ahead has not reached the end of the step
+  BatchIter it;             // look-ahead position
+  Proj p;                   // its projection
+};
+__device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(sm100::smem_u32(dst)), "l"(src), "r"(bytes), "r"(sm100::smem_u32(bar)) : "memory");
+}
+// Bounded wait of a worker warp for its stage; gives up (status 49) after the limit and never spins
+// once the status word is set.
+__device__ __forceinline__ void ring_wait_full(const MegaArgs& a, uint64_t* bar, uint32_t parity) {
+  if (sm100::mbar_try(bar, parity)) return;
+  if (tp_status_set(a.status)) return;
+  const unsigned long long t0 = tp_now_ns(), limit = a.wait_ns ? a.wait_ns : kBarWaitNs;
+  unsigned spins = 0;
+  while (!sm100::mbar_try(bar, parity)) {
+    if ((++spins & 15u) == 0) {
+      if (tp_status_set(a.status)) return;
+      if (tp_now_ns() - t0 > limit) { atomicCAS(a.status, 0, 49); return; }
     }
   }
 }
 
+// Streaming half of a projection: this CTA's run of groups through the tensor cores, partial sums of
+// every (warp, segment) left in shared memory.  Kept apart from the epilogue so that its registers
+// are allocated for the hot loop alone.
+// ------------------------------------------------------------------------------------------------
+// The projections of a step in program order: 4 per layer (in, out, gate|up, down), then the head.
+__device__ __forceinline__ Proj make_proj(const MegaArgs& a, const bf16* W, int rows_total, int K, int n_out, int mode,
+                                          void* out, int ldo, int site) {
+  Proj p;
+  p.W = W; p.rows_total = rows_total; p.K = K; p.mode = mode; p.out = out; p.ldo = ldo; p.n_out = n_out; p.site = site;
+  if (mode == 2) { p.rg = a.M; p.hi_base = n_out; p.groups = (n_out + a.M - 1) / a.M; }
+  else { p.rg = 2 * a.M; p.hi_base = a.M; p.groups = (n_out + 2 * a.M - 1) / (2 * a.M); }
+  return p;
+}
+__device__ __forceinline__ Proj proj_of(const MegaArgs& a, const MegaLayer* layers, int ph) {
+  const int H = a.H;
+  if (ph >= 4 * a.n_layers) return make_proj(a, a.lm_head, a.vocab_local, H, a.vocab_local, 3, a.logits, a.ld_logits, -1);
+  const int li = ph >> 2, k = ph & 3;
+  const MegaLayer& L = layers[li];
+  const int mixw = L.kind == 0 ? a.nv * a.dv : a.nh * a.hd;
+  if (k == 0) return make_proj(a, L.w_in, L.n_in, H, L.n_in, 0, a.proj, a.ld_proj, -1);
+  if (k == 1) return make_proj(a, L.w_out, H, mixw, H, 1, a.h, H, 2 * li);
+  if (k == 2) return make_proj(a, L.w_gu, 2 * a.I, H, a.I, 2, a.inter, a.I, -1);
+  return make_proj(a, L.w_down, H, a.I, H, 1, a.h, H, 2 * li + 1);
+}
+
+// One step of a warp's look-ahead: issue the copies of its next batch (16 rows, one per lane 0..15) into
+// the stage that batch will be read from, and move on, across projections, to the batch after it.
+__device__ __forceinline__ void ring_settle(const MegaArgs& a, const MegaLayer* layers, Ring& r, int warp) {
+  const int n_ph = 4 * a.n_layers + 1;
+  while (r.active && r.it.done()) {
+    if (++r.ph >= n_ph) { r.active = false; break; }
+    r.p = proj_of(a, layers, r.ph);
+    r.it.init(r.p, a.M, warp);
+  }
+}
+__device__ __forceinline__ void ring_issue(const MegaArgs& a, const MegaLayer* layers, Ring& r, int warp, int lane) {
+  if (!r.active) return;
+  const int S = 8 / a.M, K = r.p.K, Ks = K / S;
+  int n;
+  bool seg_end;
+  r.it.peek(kUR, n, seg_end);
+  const unsigned st = r.issued % (unsigned)r.stages;
+  const uint32_t row_bytes = (uint32_t)(min(n * 32, Ks - r.it.pb * 32) * 2);
+  uint64_t* fullb = r.full + warp * kMaxStages + st;
+  if (lane == 0) sm100::mbar_expect_tx(fullb, 16u * row_bytes);
+  __syncwarp();
+  if (lane < 16) {
+    const int g = lane & 7, hi = lane >> 3;
+    const int64_t rbase = (int64_t)(r.it.G0 + r.it.gl) * r.p.rg + g / S + (hi ? r.p.hi_base : 0);
+    const int64_t row = min(rbase, (int64_t)r.p.rows_total - 1);
+    const bf16* src = r.p.W + row * K + (int64_t)(g % S) * Ks + r.it.pb * 32;
+    unsigned char* dst = r.base + ((size_t)warp * r.stages + st) * kStageBytes + lane * kRowStride;
+    bulk_g2s(dst, src, row_bytes, fullb);
+  }
+  r.it.advance(n);
+  r.issued += 1;
+  ring_settle(a, layers, r, warp);
+}
+
+__device__ __forceinline__ void proj_flush(const float* acc, float* tile, float* dst, int M, int S, int MM2, int lane, int g, int t) {
+  // C[i][n] pairs weight-row slot / slice of A row i with batch row / slice of B column n; the products
+  // of equal slices are the k-slices of one output
+  tile[g * kTileLd + 2 * t] = acc[0];
+  tile[g * kTileLd + 2 * t + 1] = acc[1];
+  tile[(g + 8) * kTileLd + 2 * t] = acc[2];
+  tile[(g + 8) * kTileLd + 2 * t + 1] = acc[3];
+  __syncwarp();
+  for (int o = lane; o < MM2; o += 32) {
+    const int wr = o / M, m = o % M;
+    const int ib = wr < M ? wr * S : 8 + (wr - M) * S, nb = m * S;
+    float v = 0.f;
+    for (int sidx = 0; sidx < S; ++sidx) v += tile[(ib + sidx) * kTileLd + nb + sidx];
+    dst[o] = v;
+  }
+  __syncwarp();
+}
+
+__device__ __noinline__ void proj_stream(const MegaArgs& a, const MegaLayer* layers, const Proj& p, const bf16* xs, float* part,
+                                         float* tile_s, Ring& ring) {
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
+  const int M = a.M, S = 8 / M, K = p.K, Ks = K / S, MM2 = 2 * M * M;   // Ks: a multiple of 8
+  const int seg_ld = Ks + xs_pad(Ks);
+  BatchIter bi;
+  bi.init(p, M, warp);
+  int G0, G1;
+  proj_range(p, G0, G1);
+  const int items = (G1 - G0) * bi.P;
+  const int ipw2 = (items + kWarps - 1) / kWarps;
+  const int maxseg = ipw2 > 0 ? (ipw2 + bi.P - 1) / bi.P + 1 : 1;
+  const int wr_lo = g / S, sl = g % S;
+  const int64_t lane_koff = (int64_t)sl * Ks + t * 8;
+  const bf16* xlane = xs + (int64_t)g * seg_ld + t * 8;
+  float* tile = tile_s + warp * 16 * kTileLd;
+  const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+  if (ring.stages > 0) {
+    // ---- weights arrive through this warp's stages of the ring ---------------------------------------
+    while (!bi.done()) {
+      int n;
+      bool seg_end;
+      bi.peek(kUR, n, seg_end);
+      const unsigned st = ring.bc % (unsigned)ring.stages, par = (ring.bc / (unsigned)ring.stages) & 1u;
+      ring_wait_full(a, ring.full + warp * kMaxStages + st, par);
+      const unsigned char* sb = ring.base + ((size_t)warp * ring.stages + st) * kStageBytes;
+#pragma unroll
+      for (int u = 0; u < kUR; ++u) {
+        const int q = bi.pb + u;
+        const bool ok = u < n && q * 32 + t * 8 < Ks;
+        const uint4 lo = ok ? *reinterpret_cast<const uint4*>(sb + g * kRowStride + u * 64 + t * 16) : zero;
+        const uint4 hi = ok ? *reinterpret_cast<const uint4*>(sb + (g + 8) * kRowStride + u * 64 + t * 16) : zero;
+        const uint4 xv = ok ? *reinterpret_cast<const uint4*>(xlane + q * 32) : zero;
+        mma16816(acc, lo.x, hi.x, lo.y, hi.y, xv.x, xv.y);
+        mma16816(acc, lo.z, hi.z, lo.w, hi.w, xv.z, xv.w);
+      }
+      __syncwarp();                 // every lane has its fragments: the stage may be refilled
+      ring.bc += 1;
+      ring_issue(a, layers, ring, warp, lane);
+      if (seg_end) {
+        proj_flush(acc, tile, part + ((int64_t)warp * maxseg + (bi.gl - bi.gl_first)) * MM2, M, S, MM2, lane, g, t);
+        acc[0] = acc[1] = acc[2] = acc[3] = 0.f;
+      }
+      bi.advance(n);
+    }
+    return;
+  }
+  // ---- the warp loads its weights itself: kU pairs of 16-byte loads issued before the first multiply ----
+  while (!bi.done()) {
+    int n;
+    bool seg_end;
+    bi.peek(kU, n, seg_end);
+    const int64_t rbase = (int64_t)(bi.G0 + bi.gl) * p.rg + wr_lo;
+    const bf16* wlo = p.W + min(rbase, (int64_t)p.rows_total - 1) * K + lane_koff;
+    const bf16* whi = p.W + min(rbase + p.hi_base, (int64_t)p.rows_total - 1) * K + lane_koff;
+    uint4 lo[kU], hi[kU];
+#pragma unroll
+    for (int u = 0; u < kU; ++u) {
+      const int q = bi.pb + u;
+      // past the batch, or in the ragged last k-step of a slice (Ks not a multiple of 32): zeros
+      const bool ok = u < n && q * 32 + t * 8 < Ks;
+      lo[u] = ok ? ld_stream(wlo + q * 32) : zero;
+      hi[u] = ok ? ld_stream(whi + q * 32) : zero;
+    }
+#pragma unroll
+    for (int u = 0; u < kU; ++u) {
+      const int q = bi.pb + u;
+      const bool ok = u < n && q * 32 + t * 8 < Ks;
+      const uint4 xv = ok ? *reinterpret_cast<const uint4*>(xlane + q * 32) : zero;
+      mma16816(acc, lo[u].x, hi[u].x, lo[u].y, hi[u].y, xv.x, xv.y);
+      mma16816(acc, lo[u].z, hi[u].z, lo[u].w, hi[u].w, xv.z, xv.w);
+    }
+    if (seg_end) {
+      proj_flush(acc, tile, part + ((int64_t)warp * maxseg + (bi.gl - bi.gl_first)) * MM2, M, S, MM2, lane, g, t);
+      acc[0] = acc[1] = acc[2] = acc[3] = 0.f;
+    }
+    bi.advance(n);
+  }
+}
+
 __device__ __noinline__ void proj_run(const MegaArgs& a, const Ctx& c, const Proj& p, const bf16* xs, float* part, float* tile_s,
-                         float* red) {
-  proj_stream(a.M, p, xs, part, tile_s);
+                         float* red, Ring& ring, const MegaLayer* layers) {
+  proj_stream(a, layers, p, xs, part, tile_s, ring);
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int M = a.M, S = 8 / M, Ks = p.K / S, P = (Ks + 31) >> 5, MM2 = 2 * M * M;
   int G0, G1;
@@ -278,7 +457,7 @@ __device__ __noinline__ void proj_run(const MegaArgs& a, const Ctx& c, const Pro
   const int ng = G1 - G0, items = ng * P;
   const int ipw = (items + kWarps - 1) / kWarps;
   const int maxseg = ipw > 0 ? (ipw + P - 1) / P + 1 : 1;
-  __syncthreads();
+  cta_sync();
   // ---- finalise: fixed-order sum over the warps that touched a group, then the epilogue ----------
   auto group_sum = [&](int gl, int r) -> float {
     const int w0 = (gl * P) / ipw, w1 = (gl * P + P - 1) / ipw;
@@ -328,7 +507,7 @@ __device__ __noinline__ void proj_run(const MegaArgs& a, const Ctx& c, const Pro
       }
       if (lane == 0) { cv[warp * 8 + m] = v; ci[warp * 8 + m] = ix; }
     }
-    __syncthreads();
+    cta_sync();
     if (tid < M) {
       float v = -INFINITY;
       int ix = 0x7fffffff;
@@ -417,7 +596,7 @@ __device__ __noinline__ void prologue_norm(const MegaArgs& a, const bf16* res_in
 #pragma unroll
       for (int i = 0; i < 8; ++i) ss += f[i] * f[i];
     }
-    const float rstd = rsqrtf(block_sum(ss, red) / (float)K + a.eps);
+    const float rstd = rsqrtf(wsum512(ss, red) / (float)K + a.eps);
     for (int cidx = tid; cidx < nchunk; cidx += kThreads) {
       float f[8];
       uint4* px = reinterpret_cast<uint4*>(xs + xs_index(m, cidx * 8, S, Ks, seg_ld));
@@ -429,7 +608,7 @@ __device__ __noinline__ void prologue_norm(const MegaArgs& a, const bf16* res_in
       *px = float_to_bf16x8(f);
     }
   }
-  __syncthreads();
+  cta_sync();
 }
 
 // Prologue of the delta-net output projection: gated RMSNorm over each value head of the raw mixer
@@ -463,7 +642,7 @@ __device__ __noinline__ void prologue_gdn_act(const MegaArgs& a, const MegaLayer
       }
     }
   }
-  __syncthreads();
+  cta_sync();
 }
 
 // Prologue that copies fp32 rows (merged attention output) or bf16 rows (SwiGLU output) into the
@@ -477,7 +656,7 @@ __device__ __noinline__ void prologue_copy_f32(const MegaArgs& a, const float* s
     const float f[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
     *reinterpret_cast<uint4*>(xs + xs_index(m, col, S, Ks, seg_ld)) = float_to_bf16x8(f);
   }
-  __syncthreads();
+  cta_sync();
 }
 __device__ __noinline__ void prologue_copy_bf16(const MegaArgs& a, const bf16* src, int64_t lds, int K, bf16* xs) {
   const int M = a.M, S = 8 / M, Ks = K / S, seg_ld = Ks + xs_pad(Ks), n8 = K >> 3;
@@ -486,7 +665,7 @@ __device__ __noinline__ void prologue_copy_bf16(const MegaArgs& a, const bf16* s
     *reinterpret_cast<uint4*>(xs + xs_index(m, col, S, Ks, seg_ld)) =
         __ldcg(reinterpret_cast<const uint4*>(src + (int64_t)m * lds + col));
   }
-  __syncthreads();
+  cta_sync();
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -536,7 +715,7 @@ __device__ __noinline__ void gdn_phase(const MegaArgs& a, const MegaLayer& L, fl
       else if (tid < 2 * DK) k_s[tid - DK] = v;
       else v_s[tid - 2 * DK] = v;
     }
-    __syncthreads();
+    cta_sync();
     if (tid < 96) {
       const int w = tid >> 5;
       float acc = 0.f;
@@ -555,7 +734,7 @@ __device__ __noinline__ void gdn_phase(const MegaArgs& a, const MegaLayer& L, fl
     }
     sk[rg * 32 + j] = pk;
     sq[rg * 32 + j] = pq;
-    __syncthreads();
+    cta_sync();
     const float rq = rsqrtf(scal[0] + 1e-6f) * rsqrtf((float)DK), rk = rsqrtf(scal[1] + 1e-6f);
     const float kq = scal[2] * rq * rk;
     const float bl = ldcg_bf16(prow + conv_dim + a.nv * DV + h);
@@ -572,7 +751,7 @@ __device__ __noinline__ void gdn_phase(const MegaArgs& a, const MegaLayer& L, fl
 #pragma unroll
     for (int r = 0; r < RPT; ++r) sp[(int64_t)r * DV] = fmaf(k_s[rg * RPT + r] * rk, d, alpha * s[r]);
     if (rg == 0) a.mix[(int64_t)m * a.nv * DV + h * DV + cb * 32 + j] = o;
-    __syncthreads();
+    cta_sync();
   }
 }
 
@@ -667,7 +846,7 @@ __device__ __noinline__ void attn_phase(const MegaArgs& a, const MegaLayer& L, f
       }
       __threadfence_block();
     }
-    __syncthreads();
+    cta_sync();
     float q[REP][EPL], o[REP][EPL], mx[REP], l[REP];
 #pragma unroll
     for (int r = 0; r < REP; ++r) {
@@ -747,7 +926,7 @@ __device__ __noinline__ void attn_phase(const MegaArgs& a, const MegaLayer& L, f
           if (lane == 0) { mml[((warp - step) * REP + r) * 2] = mx[r]; mml[((warp - step) * REP + r) * 2 + 1] = l[r]; }
         }
       }
-      __syncthreads();
+      cta_sync();
       if (warp < step) {
 #pragma unroll
         for (int r = 0; r < REP; ++r) {
@@ -761,7 +940,7 @@ __device__ __noinline__ void attn_phase(const MegaArgs& a, const MegaLayer& L, f
           mx[r] = mn;
         }
       }
-      __syncthreads();
+      cta_sync();
     }
     if (warp == 0) {
 #pragma unroll
@@ -774,7 +953,7 @@ __device__ __noinline__ void attn_phase(const MegaArgs& a, const MegaLayer& L, f
         }
       }
     }
-    __syncthreads();
+    cta_sync();
   }
 }
 
@@ -795,7 +974,7 @@ __device__ __noinline__ void attn_merge_phase(const MegaArgs& a, float* sm) {
       sc_s[tid] = __ldcg(bml + tid * 2);
       l_s[tid] = __ldcg(bml + tid * 2 + 1);
     }
-    __syncthreads();
+    cta_sync();
     if (warp == 0) {
       float Mx = -INFINITY;
       for (int sp = lane; sp < ns; sp += 32) Mx = fmaxf(Mx, sc_s[sp]);
@@ -809,7 +988,7 @@ __device__ __noinline__ void attn_merge_phase(const MegaArgs& a, float* sm) {
       Lsum = warp_sum(Lsum);
       if (lane == 0) linv[0] = Lsum > 0.f ? 1.f / Lsum : 0.f;
     }
-    __syncthreads();
+    cta_sync();
     for (int d = tid; d < HD; d += kThreads) {
       float acc = 0.f;
       for (int sp = 0; sp < ns; ++sp) acc = fmaf(__ldcg(bo + (int64_t)sp * HD + d), sc_s[sp], acc);
@@ -817,40 +996,68 @@ __device__ __noinline__ void attn_merge_phase(const MegaArgs& a, float* sm) {
       // rounded to bf16 by the output projection's prologue, as the multi-kernel path rounds it
       a.mix[(int64_t)m * a.nh * HD + h * HD + d] = acc * linv[0] * sigmoid_f(gate);
     }
-    __syncthreads();
+    cta_sync();
   }
 }
 
 // ------------------------------------------------------------------------------------------------
 // The step.
 template <int DK, int HD, int REP>
-__global__ void __launch_bounds__(kThreads, 1) decode_mega_kernel(const MegaArgs a) {
-  extern __shared__ __align__(16) unsigned char smem_raw[];
+__global__ void __launch_bounds__(kLaunchThreads, 1) decode_mega_kernel(const MegaArgs a) {
+  // shared memory: [activation rows | mixer scratch] [partial sums] [accumulator tiles] [reductions]
+  //                [layer table] [ring barriers] [weight ring]
+  extern __shared__ __align__(128) unsigned char smem_raw[];
   bf16* xs = reinterpret_cast<bf16*>(smem_raw);
   float* part = reinterpret_cast<float*>(smem_raw + (((size_t)a.xs_elems * 2 + 255) & ~(size_t)255));
   float* tile_s = part + a.part_floats;                       // [kWarps][16][kTileLd]
   float* red = tile_s + kWarps * 16 * kTileLd;                // [kWarps * 16] reductions / arg-max staging
+  MegaLayer* layers_s = reinterpret_cast<MegaLayer*>(red + kWarps * 16);
+  uint64_t* ring_bars = reinterpret_cast<uint64_t*>(layers_s + a.n_layers);          // full[16][kMaxStages]
+  unsigned char* ring_base = reinterpret_cast<unsigned char*>(
+      ((uintptr_t)(ring_bars + kWarps * kMaxStages) + 127) & ~(uintptr_t)127);
   float* phase_sm = reinterpret_cast<float*>(smem_raw);       // mixer phases reuse the activation area
   const int tid = threadIdx.x, M = a.M, H = a.H;
+  // the per-layer table is read by every phase: one copy into shared memory instead of cold global reads
+  {
+    const int words = a.n_layers * (int)(sizeof(MegaLayer) / 4);
+    const uint32_t* src = reinterpret_cast<const uint32_t*>(a.layers);
+    uint32_t* dst = reinterpret_cast<uint32_t*>(layers_s);
+    for (int i = tid; i < words; i += kThreads) dst[i] = __ldg(src + i);
+  }
+  Ring ring;
+  ring.base = ring_base;
+  ring.full = ring_bars;
+  ring.stages = a.ring_stages;
+  ring.bc = ring.issued = 0;
+  ring.ph = 0;
+  ring.active = false;
+  if (tid == 0 && ring.stages > 0) {
+    for (int i = 0; i < kWarps * kMaxStages; ++i) sm100::mbar_init(ring.full + i, 1);
+    sm100::mbar_fence_init();
+  }
+  cta_sync();                                                 // table and barriers are ready
+  if (ring.stages > 0) {
+    // fill the warp's stages with its first batches of the step
+    ring.active = true;
+    ring.p = proj_of(a, layers_s, 0);
+    ring.it.init(ring.p, M, tid >> 5);
+    ring_settle(a, layers_s, ring, tid >> 5);
+    for (int i = 0; i < ring.stages; ++i) ring_issue(a, layers_s, ring, tid >> 5, tid & 31);
+  }
   Ctx c;
   c.bar_target = __ldcg(a.bar + 1);
   c.n_bar = 0;
   c.n_stamp = 0;
   c.epoch = a.tp_on ? __ldcg(a.tp.epoch) + 1u : 0u;
-
   auto make_proj = [&](const bf16* W, int rows_total, int K, int n_out, int mode, void* out, int ldo, int site) {
-    Proj p;
-    p.W = W; p.rows_total = rows_total; p.K = K; p.mode = mode; p.out = out; p.ldo = ldo; p.n_out = n_out; p.site = site;
-    if (mode == 2) { p.rg = M; p.hi_base = n_out; p.groups = (n_out + M - 1) / M; }
-    else { p.rg = 2 * M; p.hi_base = M; p.groups = (n_out + 2 * M - 1) / (2 * M); }
-    return p;
+    return ::make_proj(a, W, rows_total, K, n_out, mode, out, ldo, site);
   };
   bf16* res_cur = a.res0;
   bf16* res_nxt = a.res1;
   bool have_h = false;
   stamp(a, c);
   for (int li = 0; li < a.n_layers; ++li) {
-    const MegaLayer& L = a.layers[li];
+    const MegaLayer& L = layers_s[li];
     const bool lin = L.kind == 0;
     const int mixw = lin ? a.nv * a.dv : a.nh * HD;
     // ---- A: input projection -------------------------------------------------------------------
@@ -862,7 +1069,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mega_kernel(const MegaArgs
     else prologue_norm(a, res_cur, nullptr, have_h ? a.h : nullptr, L.in_gain, res_nxt, H, xs, red);
     stamp(a, c);
     { bf16* t = res_cur; res_cur = res_nxt; res_nxt = t; }
-    proj_run(a, c, pin, xs, part, tile_s, red);
+    proj_run(a, c, pin, xs, part, tile_s, red, ring, layers_s);
     stamp(a, c);
     if (a.prefetch && tid == 0) proj_prefetch(pout, a.prefetch);
     grid_barrier(a, c);
@@ -883,7 +1090,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mega_kernel(const MegaArgs
     if (lin) prologue_gdn_act(a, L, xs);
     else prologue_copy_f32(a, a.mix, mixw, xs);
     stamp(a, c);
-    proj_run(a, c, pout, xs, part, tile_s, red);
+    proj_run(a, c, pout, xs, part, tile_s, red, ring, layers_s);
     stamp(a, c);
     grid_barrier(a, c);
     stamp(a, c);
@@ -891,7 +1098,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mega_kernel(const MegaArgs
     prologue_norm(a, res_cur, nullptr, a.h, L.post_gain, res_nxt, H, xs, red);
     stamp(a, c);
     { bf16* t = res_cur; res_cur = res_nxt; res_nxt = t; }
-    proj_run(a, c, pgu, xs, part, tile_s, red);
+    proj_run(a, c, pgu, xs, part, tile_s, red, ring, layers_s);
     stamp(a, c);
     if (a.prefetch && tid == 0) proj_prefetch(pdown, a.prefetch);
     grid_barrier(a, c);
@@ -899,11 +1106,11 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mega_kernel(const MegaArgs
     // ---- E: down projection (+ all-reduce) ---------------------------------------------------------
     prologue_copy_bf16(a, a.inter, a.I, a.I, xs);
     stamp(a, c);
-    proj_run(a, c, pdown, xs, part, tile_s, red);
+    proj_run(a, c, pdown, xs, part, tile_s, red, ring, layers_s);
     stamp(a, c);
     if (a.prefetch && tid == 0) {
       if (li + 1 < a.n_layers) {
-        const MegaLayer& Ln = a.layers[li + 1];
+        const MegaLayer& Ln = layers_s[li + 1];
         proj_prefetch(make_proj(Ln.w_in, Ln.n_in, H, Ln.n_in, 0, nullptr, 0, -1), a.prefetch);
       } else {
         proj_prefetch(make_proj(a.lm_head, a.vocab_local, H, a.vocab_local, 3, nullptr, 0, -1), a.prefetch);
@@ -917,7 +1124,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mega_kernel(const MegaArgs
   const Proj phead = make_proj(a.lm_head, a.vocab_local, H, a.vocab_local, 3, a.logits, a.ld_logits, -1);
   prologue_norm(a, res_cur, nullptr, have_h ? a.h : nullptr, a.final_gain, res_nxt, H, xs, red);
   stamp(a, c);
-  proj_run(a, c, phead, xs, part, tile_s, red);
+  proj_run(a, c, phead, xs, part, tile_s, red, ring, layers_s);
   stamp(a, c);
   grid_barrier(a, c);
   stamp(a, c);
@@ -1009,7 +1216,10 @@ CB_EXPORT int cb_decode_mega_supported(int64_t dk, int64_t hd, int64_t rep) {
   return find_variant((int)dk, (int)hd, (int)rep) ? 1 : 0;
 }
 // Shared memory beyond the activation and partial-sum areas (accumulator tiles + reduction staging).
-CB_EXPORT int cb_decode_mega_fixed_smem() { return (int)((kWarps * 16 * kTileLd + kWarps * 16) * sizeof(float)) + 256; }
+CB_EXPORT int cb_decode_mega_fixed_smem(int64_t n_layers, int64_t ring_stages) {
+  return (int)((kWarps * 16 * kTileLd + kWarps * 16) * sizeof(float)) + 256 + (int)(n_layers * sizeof(MegaLayer)) +
+         kWarps * kMaxStages * 8 + 128 + (int)(kWarps * ring_stages * kStageBytes);
+}
 
 // Grid size of a cooperative launch with `smem` bytes of dynamic shared memory: one CTA per SM, or 0
 // when not even one CTA fits.
@@ -1023,7 +1233,7 @@ CB_EXPORT int cb_decode_mega_grid(int64_t dk, int64_t hd, int64_t rep, int64_t s
   int dev = 0, sms = 0, per_sm = 0;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, fn, kThreads, (size_t)smem) != cudaSuccess || per_sm < 1) {
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, fn, kLaunchThreads, (size_t)smem) != cudaSuccess || per_sm < 1) {
     cudaGetLastError();
     return 0;
   }
@@ -1041,9 +1251,10 @@ CB_EXPORT int cb_decode_mega(const void* args, int64_t dk, int64_t hd, int64_t r
   memcpy(&a, args, sizeof(a));
   if (a.M != 1 && a.M != 2 && a.M != 4 && a.M != 8) return CB_ERR_SHAPE;
   if (a.nsplit < 1 || a.nsplit > kMaxSplit || a.dv % 32 || a.dv > 256) return CB_ERR_SHAPE;
+  if (a.n_layers > kMaxLayers || a.ring_stages < 0 || a.ring_stages > kMaxStages || a.ring_stages == 1) return CB_ERR_SHAPE;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)grid);
-  cfg.blockDim = dim3(kThreads);
+  cfg.blockDim = dim3(kLaunchThreads);
   cfg.dynamicSmemBytes = (size_t)smem;
   cfg.stream = (cudaStream_t)stream;
   cudaLaunchAttribute attr[1];

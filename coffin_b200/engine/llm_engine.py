@@ -46,6 +46,7 @@ class LLMEngine:
                                      self.cfg.snapshots, self.cfg.prefix_cache)
         self.scheduler = Scheduler(self.cfg)
         self.runner = ModelRunner(model, self.bm, self.cfg)
+        self.runner.live_seqs = lambda: self.scheduler.prefilling + self.scheduler.running
         self.max_seq = min(self.cfg.max_seq, getattr(model, "max_seq", self.cfg.max_seq))
         self._stall = 0
         self.n_steps = 0

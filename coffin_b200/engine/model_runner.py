@@ -10,11 +10,13 @@ l.331-515, prefix insertion l.517-571, batched decode l.829-879, sampling l.900-
 from __future__ import annotations
 
 import random
+import time
 from typing import Any
 
 import torch
 
 from ..cache.paged_cache import OutOfBlocks
+from . import debug
 from .block_manager import BlockManager
 from .config import EngineConfig
 from .sequence import Sequence
@@ -40,6 +42,11 @@ class ModelRunner:
         self._poll = getattr(model, "poll_status", None)
         self._check = getattr(model, "check_status", None)
 
+    live_seqs = None      # callable returning the sequences that hold blocks (set by the engine; used by the debug checks)
+
+    def live(self) -> list:
+        return list(self.live_seqs()) if self.live_seqs is not None else []
+
     # ------------------------------------------------------------------ admission
     def begin_prefill(self, seq: Sequence) -> None:
         """Give a freshly admitted sequence its block table; reuse a cached prefix if one
@@ -47,6 +54,9 @@ class ModelRunner:
         seq.blocks = self.bm.new_table()
         toks = seq.all_tokens
         blocks, n, state = self.bm.match_prefix(toks, seq.mm)
+        if debug.PC_TRACE:
+            print(f"[pctrace] seq={seq.seq_id} prompt={len(toks)} matched={n} blocks={len(blocks) if n else 0} "
+                  f"snapshot={'yes' if state is not None else 'no'}", flush=True)
         if n:
             seq.blocks.adopt(blocks, n)
             self.model.restore_state(seq.slot, state)
@@ -89,8 +99,13 @@ class ModelRunner:
             embeds = cos_sin = None
             if seq.mm is not None:
                 embeds, cos_sin = self._mm_chunk(seq, toks, start, end)
+            if debug.KV_TRACE:
+                debug.check_block_alias(self.live(), self.block_size, "prefill", {seq.seq_id: T}, verbose=True)
+            t0 = time.perf_counter() if debug.PREFILL_TRACE else 0.0
             logits = self.model.prefill(self._tokens(toks), start, seq.slot, self._table(seq),
                                         embeds=embeds, cos_sin=cos_sin, want_logits=last)
+            if debug.PREFILL_TRACE:
+                debug.prefill_trace(seq, start, end, t0, self.device)
             if self._poll is not None:
                 self._poll()
             self._chunk_done(seq, end, logits)
@@ -199,6 +214,8 @@ class ModelRunner:
         Blocks must already be reserved.  Returns logits ``[len(seqs), vocab]``."""
         n = len(seqs)
         cap = BATCH_BUCKETS[-1]
+        if debug.KV_TRACE:
+            debug.check_block_alias(self.live() or seqs, self.block_size, "decode", verbose=True)
         if hasattr(self.model, "full_logits"):
             # a tensor-parallel step gathers the full-vocabulary logits only when a row samples from them
             self.model.full_logits = any(s.params.temperature > 0 for s in seqs)

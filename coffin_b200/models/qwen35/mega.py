@@ -23,8 +23,10 @@ from ...ops import _lib, kernels as K
 from ...parallel.tp import _TpCommStruct
 
 ENABLED = os.environ.get("COFFIN_MEGA", "1") != "0"
-PREFETCH_KB = int(os.environ.get("COFFIN_MEGA_PREFETCH_KB", "192"))
-SMEM_LIMIT = 220 * 1024
+PREFETCH_KB = int(os.environ.get("COFFIN_MEGA_PREFETCH_KB", "0"))
+RING = int(os.environ.get("COFFIN_MEGA_RING", "4"))        # most stages per warp of the weight ring (0 = off)
+SMEM_LIMIT = 226 * 1024
+STAGE_BYTES = 5120                                          # kStageBytes of decode_mega.cu
 ROWS = (1, 2, 4, 8)
 
 
@@ -38,7 +40,8 @@ _PTRS = ("layers", "embed", "tokens_in", "slots", "block_table", "cos", "sin", "
          "positions", "rope_pos", "res0", "res1", "h", "proj", "mix", "inter", "part_o", "part_ml", "logits", "cand",
          "next", "bar", "status", "trace")
 _INTS = ("n_layers", "M", "H", "I", "ld_proj", "ld_logits", "ldbt", "nk", "nv", "dk", "dv", "nh", "nkv", "rot", "nsplit",
-         "vocab_local", "vocab_total", "vocab_off", "part_floats", "xs_elems", "advance", "use_res0", "prefetch", "tp_on")
+         "vocab_local", "vocab_total", "vocab_off", "part_floats", "xs_elems", "advance", "use_res0", "prefetch", "tp_on",
+         "hd", "ring_stages")
 
 
 class _Args(ctypes.Structure):
@@ -119,7 +122,7 @@ class MegaDecode:
             if model.tp.n_sites < 2 * len(model.layers) + 1 or model.tp.slot_floats < 16:
                 return None
         # the function's shared-memory attribute is set once, for the largest bucket that fits
-        fits = [cls._smem(model, M, rep) for M in ROWS if cls._smem(model, M, rep) <= SMEM_LIMIT]
+        fits = [cls._smem(model, M, rep, 148, cls._stages(model, M, rep)) for M in ROWS if cls._smem(model, M, rep) <= SMEM_LIMIT]
         if not fits:
             return None
         grid = lib.cb_decode_mega_grid(ctypes.c_int64(dk), ctypes.c_int64(hd), ctypes.c_int64(rep), ctypes.c_int64(max(fits)))
@@ -150,16 +153,29 @@ class MegaDecode:
         return need
 
     @classmethod
-    def _smem(cls, model, M: int, rep: int, grid: int = 148) -> int:
+    def _region_a(cls, model, M: int, rep: int) -> int:
+        """bf16 elements of the first shared-memory region: the activation rows of the projections, or
+        the scratch of the mixer phases, whichever is larger."""
         c = model.cfg
         _, Ks = cls._geometry(model)
         xs = max(Ks) * M + 8 * 32
+        attn = 2 * (9 * rep * c.head_dim + 64) if model.full_ids else 0            # floats -> bf16 elements
+        gdn = 2 * (2 * c.linear_key_head_dim + 36 + 2 * 16 * 32) if model.lin_ids else 0
+        return max(xs, attn + 128, gdn + 128)
+
+    @classmethod
+    def _smem(cls, model, M: int, rep: int, grid: int = 148, stages: int = 0) -> int:
         part = cls._part_floats(model, M, grid)
-        fixed = _lib.lib().cb_decode_mega_fixed_smem()
-        proj = (xs * 2 + 255) // 256 * 256 + part * 4 + fixed
-        attn = 4 * (9 * rep * c.head_dim + 64) if model.full_ids else 0
-        gdn = 4 * (2 * c.linear_key_head_dim + 36 + 2 * 16 * 32) if model.lin_ids else 0
-        return max(proj, attn, gdn) + 256
+        fixed = int(_lib.lib().cb_decode_mega_fixed_smem(ctypes.c_int64(len(model.layers)), ctypes.c_int64(stages)))
+        return (cls._region_a(model, M, rep) * 2 + 255) // 256 * 256 + part * 4 + fixed + 256
+
+    @classmethod
+    def _stages(cls, model, M: int, rep: int, grid: int = 148) -> int:
+        """Stages per warp of the weight ring for bucket ``M``: as many as fit (2..RING), 0 = no ring."""
+        for ns in range(min(RING, 4), 1, -1):
+            if cls._smem(model, M, rep, grid, ns) <= SMEM_LIMIT:
+                return ns
+        return 0
 
     def rows_ok(self, M: int) -> bool:
         """Whether bucket ``M`` runs on the persistent kernel (reduction lengths and shared memory)."""
@@ -171,7 +187,7 @@ class MegaDecode:
             return False
         if self.model.cfg.intermediate_size % M:
             return False
-        return self._smem(self.model, M, self.rep, self.grid) <= SMEM_LIMIT
+        return self._smem(self.model, M, self.rep, self.grid) <= SMEM_LIMIT and len(self.model.layers) <= 96
 
     # ------------------------------------------------------------------ launch
     def _buffers(self, M: int) -> dict:
@@ -211,7 +227,8 @@ class MegaDecode:
         a.vocab_local, a.vocab_total, a.vocab_off = m.vocab_local, m.embed.shape[0], m.tp_rank * m.vocab_local
         _, Ks = self._geometry(m)
         a.part_floats = self._part_floats(m, M, self.grid)
-        a.xs_elems = max(Ks) * M + 8 * 32
+        a.xs_elems = self._region_a(m, M, self.rep)
+        a.hd, a.ring_stages = c.head_dim, self._stages(m, M, self.rep, self.grid)
         a.advance, a.use_res0, a.prefetch = int(advance), 0, PREFETCH_KB
         tp_on = m.tp is not None and (m.tp_world > 1 or m.tp_force)
         a.tp_on = int(tp_on)
@@ -226,7 +243,7 @@ class MegaDecode:
         ent = self._args.get(key)
         if ent is None:
             a = self._build_args(M, advance)
-            ent = self._args[key] = (a, self._smem(self.model, M, self.rep, self.grid))
+            ent = self._args[key] = (a, self._smem(self.model, M, self.rep, self.grid, a.ring_stages))
         a, smem = ent
         c = self.model.cfg
         fn = self.lib.cb_decode_mega

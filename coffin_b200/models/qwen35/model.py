@@ -540,8 +540,13 @@ class Qwen35Model:
         communicator has a prefill region, NCCL otherwise.  Returns the reduced rows (``t`` itself
         with NCCL, a view of the communicator's result buffer otherwise)."""
         if self.tp is not None and self.tp.pf_rows and t.shape[0] <= self.tp.pf_rows:
+            from ...engine import debug
+            end = debug.ep_span()
             self.tp.scatter(t)
-            return self.tp.finish_reduce()
+            out = self.tp.finish_reduce()
+            if end is not None:
+                end.record()
+            return out
         if self.tp_world == 1 and self.ep_world == 1:
             return t
         import torch.distributed as dist

@@ -196,6 +196,9 @@ class MoEWeights:
         # device-side dispatch (count -> prefix -> scatter), then one grouped tcgen05 GEMM per
         # projection over the expert-sorted rows; nothing is read back to the host
         disp = K.moe_dispatch(idx, n_local)
+        from ...engine import debug
+        if debug.MOE_CHECK:
+            debug.check_moe_dispatch(idx, disp, n_local)
         xs = normed.index_select(0, disp["src_tok"])                      # gathered activations [T*k, H]
         gu = K.gemm_grouped(xs, self._stack(self.gate_up), disp)
         inter = K.swiglu(gu)

@@ -141,3 +141,25 @@ def test_grouped_prefill_shares_forwards_and_matches_solo():
     # the prefix cache still serves a repeated prompt after a grouped prefill
     again = eng.generate([prompts[3]], SamplingParams(max_tokens=5))[0]
     assert again.output == ref[3] and again.cached_tokens > 0
+
+
+def test_block_alias_check_catches_a_shared_write_block():
+    """The debug check behind ``COFFIN_KV_TRACE``: shared prefix blocks are legal, a block that one
+    sequence is about to write and another sequence also references is not."""
+    from coffin_b200.engine import debug
+    eng = engine(chunk=64, prefill_quantum=64, max_num_batched_tokens=128)
+    a = eng.add_request(prompt(100, 21), SamplingParams(max_tokens=4))
+    b = eng.add_request(prompt(100, 22), SamplingParams(max_tokens=4))
+    for _ in range(3):
+        eng.step()
+    live = eng.runner.live()
+    assert len(live) == 2
+    debug.check_block_alias(live, 64, "test")                       # healthy tables
+    tb = b.blocks.table
+    saved = tb[b.num_computed // 64]
+    tb[b.num_computed // 64] = a.blocks.table[a.num_computed // 64]
+    with pytest.raises(debug.BlockAliasError):
+        debug.check_block_alias(live, 64, "test")
+    tb[b.num_computed // 64] = saved
+    while not (a.finished and b.finished):
+        eng.step()

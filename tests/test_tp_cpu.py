@@ -96,3 +96,24 @@ def test_rank_sliced_reads_equal_slicing_the_full_checkpoint(tmp_path, scheme):
     stage = load_checkpoint(path, layers=(2, 4))
     assert any(k.startswith(f"{LM}layers.2.") for k in stage) and not any(k.startswith(f"{LM}layers.0.") for k in stage)
     assert f"{LM}embed_tokens.weight" in stage and f"{LM}norm.weight" in stage
+
+
+def test_single_process_all_reduce_contract():
+    """One process, several ranks: every rank receives the same rank-ordered sum; mismatched inputs are
+    refused (the device path is exercised on a multi-GPU box)."""
+    from coffin_b200.parallel.peer_allreduce import PeerAllReduce
+    ar = PeerAllReduce(["cpu", "cpu", "cpu"])
+    xs = [torch.randn(4, 8).to(torch.bfloat16) for _ in range(3)]
+    out = ar.all_reduce(xs)
+    ref = (xs[0].float() + xs[1].float() + xs[2].float()).to(torch.bfloat16)
+    assert all(torch.equal(o, ref) for o in out)
+    ar.all_reduce(xs, out=xs)                      # in place
+    assert all(torch.equal(x, ref) for x in xs)
+    with pytest.raises(ValueError):
+        ar.all_reduce(xs[:2])
+    with pytest.raises(ValueError):
+        ar.all_reduce([xs[0], xs[1], xs[2].float()])
+    with pytest.raises(ValueError):
+        ar.all_reduce([x.to(torch.int32) for x in xs])
+    with pytest.raises(ValueError):
+        PeerAllReduce([0, 0])

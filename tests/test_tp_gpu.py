@@ -84,7 +84,7 @@ def test_quantised_push_pull_path_on_one_gpu(quant):
             m.set_rows(1, [int(toks[i])], [i], [0], [bt.tolist()])
             outs.append(m.decode(1, graph=i >= 35)[1][0].clone())
         rel = ((outs[0] - outs[1]).abs().max() / outs[0].abs().max()).item()
-        assert rel < 5e-2, f"{quant} step {i}: {rel}"
+        assert rel < 8e-2, f"{quant} step {i}: {rel}"     # per-token int8 activations: the two paths quantise slightly different rows
     torch.cuda.synchronize()
     assert tp.status() == 0
     tp.close()
@@ -410,3 +410,18 @@ def test_two_rank_wide_bucket_matches_oracle(tmp_path, mode, rows, tol):
             if mode == "ep" and rel > tol:
                 break                                   # a router near-tie flipped: later steps of this row differ
     assert worst < tol or mode == "ep", worst
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_single_process_all_reduce_over_peer_copies():
+    from coffin_b200.parallel.peer_allreduce import PeerAllReduce
+    n = min(4, torch.cuda.device_count())
+    ar = PeerAllReduce(list(range(n)))
+    g = torch.Generator().manual_seed(0)
+    for shape in ((1, 2560), (64, 2048), (1, 2560)):
+        xs = [torch.randn(*shape, generator=g).to(torch.bfloat16).to(f"cuda:{r}") for r in range(n)]
+        ref = sum(x.float().cpu() for x in xs).to(torch.bfloat16)
+        out = ar.all_reduce(xs)
+        for r in range(n):
+            torch.cuda.synchronize(r)
+            assert torch.equal(out[r].cpu(), ref)
