@@ -105,6 +105,8 @@ def main() -> None:
                     help="N > 1: tensor parallel (default) or expert parallel (routed-MoE models)")
     ap.add_argument("--rows", type=int, default=1,
                     help="concurrent sequences: > 1 measures batched decode throughput (not the headline config)")
+    ap.add_argument("--nccl", action="store_true", help="A/B baseline: all-reduces of prefill and wide decode buckets through NCCL between kernels")
+    ap.add_argument("--mega", action="store_true", help="A/B: the persistent one-launch decode step instead of the graph of kernels")
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--no-pdl", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
@@ -118,6 +120,10 @@ def main() -> None:
     ap.add_argument("--gemv-ctas", type=int, default=0, help="tuning: GEMV CTAs per SM (0 = library default)")
     ap.add_argument("--gemv-prefetch", type=int, default=-1, help="tuning: GEMV L2 prefetch-ahead (-1 = default)")
     args = ap.parse_args()
+    if args.nccl:
+        os.environ["COFFIN_TP_NCCL"] = "1"
+    if args.mega:
+        os.environ["COFFIN_MEGA"] = "1"
     sys.path.insert(0, str(ROOT))
     if args.impl == "reference":
         reference_arm(args)
@@ -270,52 +276,83 @@ def main() -> None:
 
 
 def bench_rows(args, cfg, W: int) -> None:
-    """Batched decode throughput on one GPU: ``--rows`` sequences are prefilled one after the other and
-    then advance together, one CUDA-graph step per token (buckets above 8 rows run their projections
-    on the tcgen05 GEMM).  Prints one JSON line; ``value`` is the aggregate decode tok/s."""
+    """Batched decode throughput: ``--rows`` sequences are prefilled one after the other and then
+    advance together, one CUDA-graph step per token (buckets above 8 rows run their projections on the
+    tcgen05 GEMM).  On N > 1 GPUs the model is tensor parallel (or expert parallel with ``--parallel
+    ep``); ``--nccl`` routes the all-reduces through NCCL between kernels instead of the exchange fused
+    into the GEMM epilogue (the A/B baseline).  Device-timed, max over ranks; ``value`` is the
+    aggregate decode tok/s."""
     import json
     import statistics
     import torch
+    import torch.distributed as dist
     from coffin_b200.engine.llm import LLM
     from coffin_b200.ops import kernels as K
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
     R = args.rows
-    llm = LLM.from_random(cfg, seed=0, max_seq=args.prompt + args.new + 64, max_num_seqs=R, max_chunk=args.prompt,
-                          quant=args.quant)
+    par = ({"ep_world": world, "ep_rank": rank} if args.parallel == "ep" and world > 1 else {"tp_world": world, "tp_rank": rank})
+    llm = LLM.from_random(cfg, seed=0, max_seq=args.prompt + args.new + 64, max_num_seqs=R, max_chunk=min(args.prompt, 2048),
+                          quant=args.quant, **par)
     m = llm.model
+    m.full_logits = False
     M = m.bucket_for(R)
     nblk = m.max_blocks_per_seq
     tables = [list(range(r * nblk, (r + 1) * nblk)) for r in range(R)]
     g = torch.Generator().manual_seed(1234)
     ev = lambda: torch.cuda.Event(enable_timing=True)
     pre_ms, dec_ms = [], []
+    chunk = m.max_chunk
     for it in range(W + args.steps):
         prompts = [torch.randint(0, cfg.vocab_size, (args.prompt,), generator=g).pin_memory() for _ in range(R)]
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
         e0, e1, e2 = ev(), ev(), ev()
         e0.record()
         firsts = []
         for r in range(R):
             m.zero_state(r)
-            lg = m.prefill(prompts[r].cuda(non_blocking=True), 0, r, torch.tensor(tables[r], dtype=torch.int32, device="cuda"))
+            dev = prompts[r].cuda(non_blocking=True)
+            bt = torch.tensor(tables[r], dtype=torch.int32, device="cuda")
+            lg = None
+            for s0 in range(0, args.prompt, chunk):
+                s1 = min(args.prompt, s0 + chunk)
+                lg = m.prefill(dev[s0:s1], s0, r, bt, want_logits=s1 == args.prompt)
             firsts.append(int(lg.argmax()))
         e1.record()
         m.set_rows(M, firsts, [args.prompt] * R, list(range(R)), tables)
         for _ in range(args.new):
-            m.decode(M, graph=True)
-            m.advance_rows(M)
+            m.decode(M, graph=True, advance=True)
         e2.record()
         e2.synchronize()
         if it >= W:
             pre_ms.append(e0.elapsed_time(e1))
             dec_ms.append(e1.elapsed_time(e2))
     K.check_status()
-    dec_tok_s = R * args.new * len(dec_ms) / (sum(dec_ms) / 1e3)
-    print(json.dumps({"metric": "batched_decode_tok_s", "value": dec_tok_s, "unit": "tok/s", "n_gpus": 1,
-                      "steps": args.steps, "warmup": W, "higher_is_better": True,
-                      "prefill_tok_s": R * args.prompt * len(pre_ms) / (sum(pre_ms) / 1e3),
-                      "step_ms_p50": statistics.median(dec_ms) / args.new,
-                      "dtype": {"none": "bf16", "int8": "int8-w8a8", "w4a8": "int4-w4a8"}[args.quant], "data": "synthetic",
-                      "config": {"model": args.model, "global_batch": R, "seq_len": args.prompt,
-                                 "decode_tokens": args.new, "bucket": M, "cuda_graph": True}, "impl": "ours"}), flush=True)
+    stats = torch.tensor([sum(pre_ms), sum(dec_ms)], dtype=torch.float64, device="cuda")
+    if world > 1:
+        dist.all_reduce(stats, op=dist.ReduceOp.MAX)
+    pre_total, dec_total = stats.tolist()
+    dec_tok_s = R * args.new * len(dec_ms) / (dec_total / 1e3)
+    if rank == 0:
+        print(json.dumps({"metric": "batched_decode_tok_s", "value": dec_tok_s, "unit": "tok/s", "n_gpus": world,
+                          "steps": args.steps, "warmup": W, "higher_is_better": True,
+                          "prefill_tok_s": R * args.prompt * len(pre_ms) / (pre_total / 1e3),
+                          "step_ms": dec_total / len(dec_ms) / args.new,
+                          "dtype": {"none": "bf16", "int8": "int8-w8a8", "w4a8": "int4-w4a8"}[args.quant], "data": "synthetic",
+                          "config": {"model": args.model, "global_batch": R, "seq_len": args.prompt, "decode_tokens": args.new,
+                                     "parallelism": f"{args.parallel}{world}" if world > 1 else "single"},
+                          "notes": {"bucket": M, "cuda_graph": True, "exchange": "nccl" if os.environ.get("COFFIN_TP_NCCL") == "1" else "fused peer-memory",
+                                    "launches_per_step": m.launches_per_step(M), "weight_gb_per_rank": round(m.weight_bytes() / 1e9, 2)},
+                          "impl": "ours"}), flush=True)
+    if world > 1:
+        from coffin_b200.parallel.control import shutdown
+        dist.barrier()
+        m._graphs.clear()
+        if getattr(m, "tp", None) is not None:
+            m.tp.close()
+        shutdown(timeout_s=10.0)
 
 
 if __name__ == "__main__":

@@ -19,6 +19,80 @@ namespace {
 
 constexpr int kBlock = 64;  // tokens per KV block == key tile
 
+// ---- int8 KV pool (optional) ------------------------------------------------------------------
+// With scale pointers set, the pools hold int8 [slots, nkv, hd] and one fp32 scale per (slot, kv head):
+// x ~= q * scale, scale = max|x| / 127 (floored at 1e-8), the reference's paged int8 cache
+// (cache/paged_cache.py:78-141, kv_quant / kv_pool_store in backends/corex/kernels/attn.cu:132,1200).
+// Every kernel converts on load into the bf16 form it already computes with, so the products and the
+// softmax are unchanged; only the bytes read per key halve.
+//
+// Quantise a head row held as EPL consecutive values per lane; returns the scale and leaves the
+// dequantised values in x (what later steps will read back).
+template <int EPL>
+__device__ __forceinline__ float quant_row_q8(float* x, int8_t* dst_row, int lane) {
+  float amax = 0.f;
+#pragma unroll
+  for (int e = 0; e < EPL; ++e) amax = fmaxf(amax, fabsf(x[e]));
+  amax = warp_max(amax);
+  const float sc = fmaxf(amax / 127.f, 1e-8f), inv = 1.f / sc;
+  int q[EPL];
+#pragma unroll
+  for (int e = 0; e < EPL; ++e) {
+    q[e] = max(-127, min(127, __float2int_rn(x[e] * inv)));
+    x[e] = (float)q[e] * sc;
+  }
+  if (EPL == 8) {
+    uint2 w;
+    w.x = (uint32_t)(q[0] & 0xff) | ((uint32_t)(q[1] & 0xff) << 8) | ((uint32_t)(q[2] & 0xff) << 16) | ((uint32_t)(q[3] & 0xff) << 24);
+    w.y = (uint32_t)(q[4] & 0xff) | ((uint32_t)(q[5] & 0xff) << 8) | ((uint32_t)(q[6] & 0xff) << 16) | ((uint32_t)(q[7] & 0xff) << 24);
+    *reinterpret_cast<uint2*>(dst_row + lane * EPL) = w;
+  } else {
+#pragma unroll
+    for (int e = 0; e < EPL; ++e) dst_row[lane * EPL + e] = (int8_t)q[e];
+  }
+  return sc;
+}
+// 8 int8 (one 8-byte vector) times a scale -> 8 bf16 (one 16-byte vector)
+__device__ __forceinline__ uint4 q8x8_to_bf16x8(uint2 w, float sc) {
+  float f[8];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    f[i] = (float)(int8_t)((w.x >> (8 * i)) & 0xff) * sc;
+    f[4 + i] = (float)(int8_t)((w.y >> (8 * i)) & 0xff) * sc;
+  }
+  return float_to_bf16x8(f);
+}
+// A 64-key tile of K and V of one kv head into shared memory as bf16 rows of LD elements: asynchronous
+// 16-byte copies from a bf16 pool, or 8-byte loads + conversion from an int8 pool.
+template <int HD, int NT>
+__device__ __forceinline__ void load_kv_tile(bf16* Ks, bf16* Vs, int LD, const bf16* kpool, const bf16* vpool,
+                                             const float* kscale, const float* vscale, int64_t slot0, int nkv, int kvh,
+                                             int tid) {
+  constexpr int CPR = HD / 8;
+  if (kscale) {
+    const int8_t* k8 = reinterpret_cast<const int8_t*>(kpool);
+    const int8_t* v8 = reinterpret_cast<const int8_t*>(vpool);
+    for (int idx = tid; idx < 64 * CPR; idx += NT) {
+      const int r = idx / CPR, c = idx % CPR;
+      const int64_t row = (slot0 + r) * nkv + kvh;
+      const uint2 kq = *reinterpret_cast<const uint2*>(k8 + row * HD + c * 8);
+      const uint2 vq = *reinterpret_cast<const uint2*>(v8 + row * HD + c * 8);
+      *reinterpret_cast<uint4*>(Ks + r * LD + c * 8) = q8x8_to_bf16x8(kq, kscale[row]);
+      *reinterpret_cast<uint4*>(Vs + r * LD + c * 8) = q8x8_to_bf16x8(vq, vscale[row]);
+    }
+    return;
+  }
+  for (int idx = tid; idx < 64 * CPR; idx += NT) {
+    const int r = idx / CPR, c = idx % CPR;
+    const int64_t off = ((slot0 + r) * nkv + kvh) * HD + c * 8;
+    const uint32_t ka = (uint32_t)__cvta_generic_to_shared(Ks + r * LD + c * 8);
+    const uint32_t va = (uint32_t)__cvta_generic_to_shared(Vs + r * LD + c * 8);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(ka), "l"(kpool + off));
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(va), "l"(vpool + off));
+  }
+  asm volatile("cp.async.wait_all;" ::: "memory");
+}
+
 // ------------------------------------------------------------------------------------------
 // q/k norm + rope (+ KV append) for prefill rows. One warp per (token, head).
 struct PrepArgs {
@@ -31,6 +105,7 @@ struct PrepArgs {
   bf16* kpool; bf16* vpool;          // [slots, nkv, hd]
   int T, nh, nkv, rot;
   float eps;
+  float* kscale; float* vscale;      // int8 pools: [slots, nkv] scales (null: bf16 pools)
 };
 
 template <int HD>
@@ -86,14 +161,28 @@ __global__ void __launch_bounds__(256) attn_prep_kernel(const PrepArgs a) {
     for (int e = 0; e < EPL; ++e) x[e] = __bfloat162float(src[e]);
     if (a.kv_slot[t] < 0) return;       // padding row of a batched verify: nothing to append
     norm_rope_lane<HD>(x, a.kg, cs, sn, a.rot, a.eps, lane);
-    bf16* dst = a.kpool + ((int64_t)a.kv_slot[t] * a.nkv + kh) * HD + lane * EPL;
+    const int64_t krow = (int64_t)a.kv_slot[t] * a.nkv + kh;
+    if (a.kscale) {
+      const float sc = quant_row_q8<EPL>(x, reinterpret_cast<int8_t*>(a.kpool) + krow * HD, lane);
+      if (lane == 0) a.kscale[krow] = sc;
+      return;
+    }
+    bf16* dst = a.kpool + krow * HD + lane * EPL;
 #pragma unroll
     for (int e = 0; e < EPL; ++e) dst[e] = __float2bfloat16(x[e]);
   } else {
     const int vh = hh - a.nh - a.nkv;
     if (a.kv_slot[t] < 0) return;
     const bf16* src = prow + (int64_t)a.nh * 2 * HD + (int64_t)(a.nkv + vh) * HD + lane * EPL;
-    bf16* dst = a.vpool + ((int64_t)a.kv_slot[t] * a.nkv + vh) * HD + lane * EPL;
+    const int64_t vrow = (int64_t)a.kv_slot[t] * a.nkv + vh;
+    if (a.vscale) {
+#pragma unroll
+      for (int e = 0; e < EPL; ++e) x[e] = __bfloat162float(src[e]);
+      const float sc = quant_row_q8<EPL>(x, reinterpret_cast<int8_t*>(a.vpool) + vrow * HD, lane);
+      if (lane == 0) a.vscale[vrow] = sc;
+      return;
+    }
+    bf16* dst = a.vpool + vrow * HD + lane * EPL;
 #pragma unroll
     for (int e = 0; e < EPL; ++e) dst[e] = src[e];
   }
@@ -135,6 +224,7 @@ struct PrefillArgs {
   // block-selected attention: bit b of keep[t] says whether query t reads the block of (1 << ratio_log2)
   // tokens number b; tokens after a query's last complete block are always read.  null = dense.
   const unsigned* keep; int keep_words, ratio_log2;
+  const float* kscale; const float* vscale;   // int8 pools: [slots, nkv] scales (null: bf16 pools)
 };
 
 template <int HD>
@@ -168,13 +258,7 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(const PrefillArgs a) 
   for (int kt = 0; kt < ntiles; ++kt) {
     __syncthreads();  // previous tile fully consumed (also orders the Q store before first use)
     const int64_t slot0 = (int64_t)a.block_table[kt] * kBlock;
-    for (int idx = tid; idx < 64 * CPR; idx += 128) {
-      const int r = idx / CPR, c = idx % CPR;
-      const int64_t off = ((slot0 + r) * a.nkv + kvh) * HD + c * 8;
-      cp_async16(Ks + r * LD + c * 8, a.kpool + off);
-      cp_async16(Vs + r * LD + c * 8, a.vpool + off);
-    }
-    cp_async_wait_all();
+    load_kv_tile<HD, 128>(Ks, Vs, LD, a.kpool, a.vpool, a.kscale, a.vscale, slot0, a.nkv, kvh, tid);
     __syncthreads();
     // ---- S = Q K^T (16 x 64 per warp) --------------------------------------------------
     float s[8][4];
@@ -301,6 +385,7 @@ struct DecodeArgs {
   // current token are already in the pool, and row m attends to the blocks sel[m, 0..nsel[m]) of
   // `ratio` tokens plus the tokens after its last complete block (nsel[m] < 0: every visible token)
   const bf16* q_in; const int* sel; const int* nsel; int topk, ratio;
+  float* kscale; float* vscale;       // int8 pools: [slots, nkv] scales (null: bf16 pools)
 };
 
 constexpr int kDecWarps = 8;          // warps per decode CTA; each takes 4 keys per iteration
@@ -315,6 +400,18 @@ __device__ __forceinline__ void dec_load(const bf16* p, uint32_t* w) {
   } else {
 #pragma unroll
     for (int e = 0; e < EPL / 2; ++e) w[e] = reinterpret_cast<const uint32_t*>(p)[e];
+  }
+}
+// EPL int8 channels of one lane times the key's scale, as the same packed bf16 words
+template <int EPL>
+__device__ __forceinline__ void dec_load_q8(const int8_t* p, float sc, uint32_t* w) {
+  if (EPL == 8) {
+    const uint2 v = *reinterpret_cast<const uint2*>(p);
+    const uint4 b = q8x8_to_bf16x8(v, sc);
+    w[0] = b.x; w[1] = b.y; w[2] = b.z; w[3] = b.w;
+  } else {
+#pragma unroll
+    for (int e = 0; e < EPL / 2; ++e) w[e] = pack_bf162((float)p[2 * e] * sc, (float)p[2 * e + 1] * sc);
   }
 }
 __device__ __forceinline__ float bf_lo(uint32_t w) { return __uint_as_float(w << 16); }
@@ -378,14 +475,27 @@ __global__ void __launch_bounds__(kDecWarps * 32, MINB) attn_decode_kernel(const
 #pragma unroll
         for (int e = 0; e < EPL; ++e) x[e] = __bfloat162float(src[e]);
         norm_rope_lane<HD>(x, a.kg, cs, sn, a.rot, a.eps, lane);
-        bf16* dst = a.kpool + (slot * a.nkv + kvh) * HD + lane * EPL;
+        if (a.kscale) {
+          const float sc = quant_row_q8<EPL>(x, reinterpret_cast<int8_t*>(a.kpool) + (slot * a.nkv + kvh) * HD, lane);
+          if (lane == 0) a.kscale[slot * a.nkv + kvh] = sc;
+        } else {
+          bf16* dst = a.kpool + (slot * a.nkv + kvh) * HD + lane * EPL;
 #pragma unroll
-        for (int e = 0; e < EPL; ++e) dst[e] = __float2bfloat16(x[e]);
+          for (int e = 0; e < EPL; ++e) dst[e] = __float2bfloat16(x[e]);
+        }
       } else if (warp == kDecWarps - 2) {
         const bf16* src = prow + (int64_t)a.nh * 2 * HD + (int64_t)(a.nkv + kvh) * HD + lane * EPL;
-        bf16* dst = a.vpool + (slot * a.nkv + kvh) * HD + lane * EPL;
+        if (a.vscale) {
+          float x[EPL];
 #pragma unroll
-        for (int e = 0; e < EPL; ++e) dst[e] = src[e];
+          for (int e = 0; e < EPL; ++e) x[e] = __bfloat162float(src[e]);
+          const float sc = quant_row_q8<EPL>(x, reinterpret_cast<int8_t*>(a.vpool) + (slot * a.nkv + kvh) * HD, lane);
+          if (lane == 0) a.vscale[slot * a.nkv + kvh] = sc;
+        } else {
+          bf16* dst = a.vpool + (slot * a.nkv + kvh) * HD + lane * EPL;
+#pragma unroll
+          for (int e = 0; e < EPL; ++e) dst[e] = src[e];
+        }
       }
       __threadfence_block();
     }
@@ -440,8 +550,13 @@ __global__ void __launch_bounds__(kDecWarps * 32, MINB) attn_decode_kernel(const
     for (int u = 0; u < kDecKeys; ++u) {
       const int64_t row = key_row(it * (kDecWarps * kDecKeys) + warp * kDecKeys + u, okk[u]);
       if (okk[u]) {
-        dec_load<EPL>(a.kpool + row * HD + lane * EPL, kf[u]);
-        dec_load<EPL>(a.vpool + row * HD + lane * EPL, vf[u]);
+        if (a.kscale) {
+          dec_load_q8<EPL>(reinterpret_cast<const int8_t*>(a.kpool) + row * HD + lane * EPL, a.kscale[row], kf[u]);
+          dec_load_q8<EPL>(reinterpret_cast<const int8_t*>(a.vpool) + row * HD + lane * EPL, a.vscale[row], vf[u]);
+        } else {
+          dec_load<EPL>(a.kpool + row * HD + lane * EPL, kf[u]);
+          dec_load<EPL>(a.vpool + row * HD + lane * EPL, vf[u]);
+        }
       }
     }
   };
@@ -646,14 +761,30 @@ __global__ void __launch_bounds__(128, 2) attn_decode_batch_kernel(const DecodeA
 #pragma unroll
         for (int e = 0; e < EPL; ++e) x[e] = __bfloat162float(src[e]);
         norm_rope_lane<HD>(x, a.kg, cs, sn, a.rot, a.eps, lane);
-        bf16* dst = a.kpool + (slot * a.nkv + kvh) * HD + lane * EPL;
+        if (a.kscale) {            // the shared copy holds the dequantised row, what later steps will read
+          const float sc = quant_row_q8<EPL>(x, reinterpret_cast<int8_t*>(a.kpool) + (slot * a.nkv + kvh) * HD, lane);
+          if (lane == 0) a.kscale[slot * a.nkv + kvh] = sc;
 #pragma unroll
-        for (int e = 0; e < EPL; ++e) { const bf16 v = __float2bfloat16(x[e]); dst[e] = v; kcur[lane * EPL + e] = v; }
+          for (int e = 0; e < EPL; ++e) kcur[lane * EPL + e] = __float2bfloat16(x[e]);
+        } else {
+          bf16* dst = a.kpool + (slot * a.nkv + kvh) * HD + lane * EPL;
+#pragma unroll
+          for (int e = 0; e < EPL; ++e) { const bf16 v = __float2bfloat16(x[e]); dst[e] = v; kcur[lane * EPL + e] = v; }
+        }
       } else {
         const bf16* src = prow + (int64_t)a.nh * 2 * HD + (int64_t)(a.nkv + kvh) * HD + lane * EPL;
-        bf16* dst = a.vpool + (slot * a.nkv + kvh) * HD + lane * EPL;
+        if (a.vscale) {
 #pragma unroll
-        for (int e = 0; e < EPL; ++e) { dst[e] = src[e]; vcur[lane * EPL + e] = src[e]; }
+          for (int e = 0; e < EPL; ++e) x[e] = __bfloat162float(src[e]);
+          const float sc = quant_row_q8<EPL>(x, reinterpret_cast<int8_t*>(a.vpool) + (slot * a.nkv + kvh) * HD, lane);
+          if (lane == 0) a.vscale[slot * a.nkv + kvh] = sc;
+#pragma unroll
+          for (int e = 0; e < EPL; ++e) vcur[lane * EPL + e] = __float2bfloat16(x[e]);
+        } else {
+          bf16* dst = a.vpool + (slot * a.nkv + kvh) * HD + lane * EPL;
+#pragma unroll
+          for (int e = 0; e < EPL; ++e) { dst[e] = src[e]; vcur[lane * EPL + e] = src[e]; }
+        }
       }
     }
   }
@@ -666,13 +797,7 @@ __global__ void __launch_bounds__(128, 2) attn_decode_batch_kernel(const DecodeA
   for (int kt = split; kt < ntiles; kt += nsplit) {
     __syncthreads();                              // previous tile consumed
     const int64_t slot0 = (int64_t)bt[kt] * kBlock;
-    for (int idx = tid; idx < 64 * CPR; idx += 128) {
-      const int r = idx / CPR, c = idx % CPR;
-      const int64_t off = ((slot0 + r) * a.nkv + kvh) * HD + c * 8;
-      cp_async16(Ks + r * LD + c * 8, a.kpool + off);
-      cp_async16(Vs + r * LD + c * 8, a.vpool + off);
-    }
-    cp_async_wait_all();
+    load_kv_tile<HD, 128>(Ks, Vs, LD, a.kpool, a.vpool, a.kscale, a.vscale, slot0, a.nkv, kvh, tid);
     __syncthreads();
     if (kt == ntiles - 1) {                       // the current token's row comes from this CTA, not from memory
       for (int c = tid; c < 2 * CPR; c += 128) {
@@ -871,11 +996,12 @@ int decode_dispatch(const DecodeArgs& a, int64_t M, int64_t nh, int64_t nkv, int
 CB_EXPORT int cb_attn_prep(const void* proj, int64_t ldp, const void* qg, const void* kg, const void* cos,
                            const void* sin, const void* rope_idx, const void* kv_slot, void* q_out,
                            void* kpool, void* vpool, int64_t T, int64_t nh, int64_t nkv, int64_t hd,
-                           int64_t rot, float eps, void* stream) {
+                           int64_t rot, float eps, void* kscale, void* vscale, void* stream) {
   if (T == 0) return 0;
+  if ((kscale == nullptr) != (vscale == nullptr)) return CB_ERR_ARG;
   PrepArgs a{(const bf16*)proj, ldp, (const float*)qg, (const float*)kg, (const float*)cos, (const float*)sin,
              (const int*)rope_idx, (const int*)kv_slot, (bf16*)q_out, (bf16*)kpool, (bf16*)vpool,
-             (int)T, (int)nh, (int)nkv, (int)rot, eps};
+             (int)T, (int)nh, (int)nkv, (int)rot, eps, (float*)kscale, (float*)vscale};
   const int64_t tasks = T * (nh + 2 * nkv);
   dim3 grid((unsigned)((tasks + 7) / 8));
   if (hd == 256 && (rot / 2) % 8 == 0) return (int)cb_launch(attn_prep_kernel<256>, grid, dim3(256), 0, (cudaStream_t)stream, a);
@@ -886,8 +1012,10 @@ CB_EXPORT int cb_attn_prep(const void* proj, int64_t ldp, const void* qg, const 
 CB_EXPORT int cb_attn_prefill(const void* q, const void* gate, int64_t ldg, const void* kpool, const void* vpool,
                               const void* block_table, void* out, int64_t ldo, int64_t T, int64_t q_pos0,
                               int64_t nh, int64_t nkv, int64_t hd, int64_t causal, int64_t kv_len,
-                              const void* keep, int64_t keep_words, int64_t ratio, void* stream) {
+                              const void* keep, int64_t keep_words, int64_t ratio, const void* kscale,
+                              const void* vscale, void* stream) {
   if (T == 0) return 0;
+  if ((kscale == nullptr) != (vscale == nullptr)) return CB_ERR_ARG;
   int rl = 0;
   if (keep) {
     while ((1 << rl) < ratio) ++rl;
@@ -896,7 +1024,7 @@ CB_EXPORT int cb_attn_prefill(const void* q, const void* gate, int64_t ldg, cons
   PrefillArgs a{(const bf16*)q, (const bf16*)gate, ldg, (const bf16*)kpool, (const bf16*)vpool,
                 (const int*)block_table, (bf16*)out, ldo, (int)T, (int)q_pos0, (int)nh, (int)nkv,
                 1.4426950408889634f / sqrtf((float)hd), (int)causal, (int)kv_len,
-                (const unsigned*)keep, (int)keep_words, rl};
+                (const unsigned*)keep, (int)keep_words, rl, (const float*)kscale, (const float*)vscale};
   dim3 grid((unsigned)((T + 63) / 64), (unsigned)nh);
   const size_t smem = (size_t)3 * 64 * (hd + 8) * sizeof(bf16);
   cudaError_t e;
@@ -913,14 +1041,16 @@ CB_EXPORT int cb_attn_decode(const void* proj, int64_t ldp, const void* qg, cons
                              const void* sin, const void* positions, const void* rope_pos,
                              const void* block_table, int64_t ldbt, void* kpool, void* vpool, void* part_o,
                              void* part_ml, void* tickets, void* out, int64_t ldo, int64_t M, int64_t nh, int64_t nkv,
-                             int64_t hd, int64_t rot, int64_t nsplit, float eps, void* stream) {
+                             int64_t hd, int64_t rot, int64_t nsplit, float eps, void* kscale, void* vscale,
+                             void* stream) {
   if (M == 0) return 0;
   if (nh % nkv || nsplit < 1 || nsplit > 64 || !tickets) return CB_ERR_SHAPE;
+  if ((kscale == nullptr) != (vscale == nullptr)) return CB_ERR_ARG;
   DecodeArgs a{(const bf16*)proj, ldp, (const float*)qg, (const float*)kg, (const float*)cos, (const float*)sin,
                (const int*)positions, (const int*)rope_pos, (const int*)block_table, ldbt, (bf16*)kpool,
                (bf16*)vpool, (float*)part_o, (float*)part_ml, (int)nh, (int)nkv, (int)rot, (int)nsplit,
                1.4426950408889634f / sqrtf((float)hd), eps, (unsigned*)tickets, (bf16*)out, ldo,
-               nullptr, nullptr, nullptr, 0, 1};
+               nullptr, nullptr, nullptr, 0, 1, (float*)kscale, (float*)vscale};
   if (hd == 256 && (rot / 2) % 8 == 0 && nh / nkv <= 8 && g_attn_batch_ctas > 0 && nkv * M >= g_attn_batch_ctas) {
     // enough (row, kv head) pairs to fill the machine with one CTA each: tensor-core batch kernel
     constexpr int HD = 256;
@@ -948,6 +1078,6 @@ CB_EXPORT int cb_attn_sparse(const void* q, const void* proj, int64_t ldp, const
   DecodeArgs a{(const bf16*)proj, ldp, nullptr, nullptr, nullptr, nullptr, (const int*)positions, nullptr,
                (const int*)block_table, ldbt, (bf16*)kpool, (bf16*)vpool, (float*)part_o, (float*)part_ml, (int)nh,
                (int)nkv, 0, (int)nsplit, 1.4426950408889634f / sqrtf((float)hd), 0.f, (unsigned*)tickets, (bf16*)out,
-               ldo, (const bf16*)q, (const int*)sel, (const int*)nsel, (int)topk, (int)ratio};
+               ldo, (const bf16*)q, (const int*)sel, (const int*)nsel, (int)topk, (int)ratio, nullptr, nullptr};
   return decode_dispatch(a, M, nh, nkv, hd, 0, stream);
 }

@@ -580,6 +580,39 @@ __device__ __noinline__ void prologue_norm(const MegaArgs& a, const bf16* res_in
       tk = tk < 0 ? 0 : (tk >= a.vocab_total ? a.vocab_total - 1 : tk);
       src = a.embed + tk * K;
     }
+    if (nchunk <= kThreads) {
+      // one 8-element chunk per thread: residual, addend and gain are requested together and the row
+      // stays in registers between the sum of squares and the scaling (one pass, one reduction)
+      const bool ok = tid < nchunk;
+      float f[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      float4 g0 = make_float4(0.f, 0.f, 0.f, 0.f), g1 = g0;
+      if (ok) {
+        const uint4 rv = __ldcg(reinterpret_cast<const uint4*>(src + tid * 8));
+        float4 q0 = make_float4(0.f, 0.f, 0.f, 0.f), q1 = q0;
+        if (add) {
+          q0 = __ldcg(reinterpret_cast<const float4*>(add + (int64_t)m * K + tid * 8));
+          q1 = __ldcg(reinterpret_cast<const float4*>(add + (int64_t)m * K + tid * 8 + 4));
+        }
+        g0 = *reinterpret_cast<const float4*>(gain + tid * 8);
+        g1 = *reinterpret_cast<const float4*>(gain + tid * 8 + 4);
+        bf16x8_to_float(rv, f);
+        if (add) {
+          f[0] = round_bf16(f[0] + q0.x); f[1] = round_bf16(f[1] + q0.y); f[2] = round_bf16(f[2] + q0.z); f[3] = round_bf16(f[3] + q0.w);
+          f[4] = round_bf16(f[4] + q1.x); f[5] = round_bf16(f[5] + q1.y); f[6] = round_bf16(f[6] + q1.z); f[7] = round_bf16(f[7] + q1.w);
+        }
+        if (res_out && blockIdx.x == 0) *reinterpret_cast<uint4*>(res_out + (int64_t)m * K + tid * 8) = float_to_bf16x8(f);
+      }
+      float ss = 0.f;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) ss += f[i] * f[i];
+      const float rstd = rsqrtf(wsum512(ss, red) / (float)K + a.eps);
+      if (ok) {
+        f[0] *= rstd * g0.x; f[1] *= rstd * g0.y; f[2] *= rstd * g0.z; f[3] *= rstd * g0.w;
+        f[4] *= rstd * g1.x; f[5] *= rstd * g1.y; f[6] *= rstd * g1.z; f[7] *= rstd * g1.w;
+        *reinterpret_cast<uint4*>(xs + xs_index(m, tid * 8, S, Ks, seg_ld)) = float_to_bf16x8(f);
+      }
+      continue;
+    }
     float ss = 0.f;
     for (int cidx = tid; cidx < nchunk; cidx += kThreads) {
       float f[8];
@@ -964,7 +997,8 @@ __device__ __noinline__ void attn_merge_phase(const MegaArgs& a, float* sm) {
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   float* sc_s = sm;                 // [kMaxSplit]
   float* l_s = sc_s + kMaxSplit;    // [kMaxSplit]
-  float* linv = l_s + kMaxSplit;    // [1]
+  float* linv = l_s + kMaxSplit;    // [1] (padded to 4)
+  float* pacc = linv + 4;           // [kThreads / HD][HD] = kThreads partial sums
   const int ns = a.nsplit, units = a.M * a.nh;
   for (int u = blockIdx.x; u < units; u += gridDim.x) {
     const int m = u / a.nh, h = u % a.nh;
@@ -989,12 +1023,21 @@ __device__ __noinline__ void attn_merge_phase(const MegaArgs& a, float* sm) {
       if (lane == 0) linv[0] = Lsum > 0.f ? 1.f / Lsum : 0.f;
     }
     cta_sync();
-    for (int d = tid; d < HD; d += kThreads) {
-      float acc = 0.f;
-      for (int sp = 0; sp < ns; ++sp) acc = fmaf(__ldcg(bo + (int64_t)sp * HD + d), sc_s[sp], acc);
-      const float gate = ldcg_bf16(a.proj + (int64_t)m * a.ld_proj + (int64_t)h * 2 * HD + HD + d);
+    // kThreads / HD thread groups share the sum over the splits (independent loads, a few per thread)
+    constexpr int NP = kThreads / HD;
+    const int d = tid % HD, pt = tid / HD;
+    float acc = 0.f;
+#pragma unroll 4
+    for (int sp = pt; sp < ns; sp += NP) acc = fmaf(__ldcg(bo + (int64_t)sp * HD + d), sc_s[sp], acc);
+    pacc[pt * HD + d] = acc;
+    cta_sync();
+    if (tid < HD) {
+      float tot = 0.f;
+#pragma unroll
+      for (int q = 0; q < NP; ++q) tot += pacc[q * HD + tid];
+      const float gate = ldcg_bf16(a.proj + (int64_t)m * a.ld_proj + (int64_t)h * 2 * HD + HD + tid);
       // rounded to bf16 by the output projection's prologue, as the multi-kernel path rounds it
-      a.mix[(int64_t)m * a.nh * HD + h * HD + d] = acc * linv[0] * sigmoid_f(gate);
+      a.mix[(int64_t)m * a.nh * HD + h * HD + tid] = tot * linv[0] * sigmoid_f(gate);
     }
     cta_sync();
   }

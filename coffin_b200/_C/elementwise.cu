@@ -418,3 +418,24 @@ CB_EXPORT int cb_block_copy(void* dst, const void* src, const void* dst_idx, con
                         (cudaStream_t)stream, (unsigned char*)dst, (const unsigned char*)src,
                         (const int64_t*)dst_idx, (const int64_t*)src_idx, block_bytes);
 }
+
+// Feed the sampled tokens back and advance the positions of the live rows (positions >= 0) by one:
+// lets greedy steps run back to back with no host round trip and no framework kernels in between.
+namespace {
+__global__ void advance_rows_kernel(int64_t* tokens, const int64_t* next, int* positions, int* rope_pos, int M) {
+  griddep_launch();
+  griddep_wait();
+  const int m = threadIdx.x;
+  if (m >= M) return;
+  tokens[m] = next[m];
+  if (positions[m] >= 0) {
+    positions[m] += 1;
+    rope_pos[m] += 1;
+  }
+}
+}  // namespace
+CB_EXPORT int cb_advance_rows(void* tokens, const void* next, void* positions, void* rope_pos, int64_t M, void* stream) {
+  if (!tokens || !next || !positions || !rope_pos || M < 1 || M > 1024) return CB_ERR_ARG;
+  return (int)cb_launch(advance_rows_kernel, dim3(1), dim3((unsigned)((M + 31) / 32 * 32)), 0, (cudaStream_t)stream,
+                        (int64_t*)tokens, (const int64_t*)next, (int*)positions, (int*)rope_pos, (int)M);
+}

@@ -22,6 +22,13 @@ def registered() -> list[str]:
     return sorted(_REGISTRY)
 
 
+def _nccl_only() -> bool:
+    """``COFFIN_TP_NCCL=1``: the prefill and wide-bucket all-reduces go through NCCL between kernels
+    instead of the peer-memory exchange fused into the GEMM epilogue (the A/B baseline of the fused path)."""
+    import os
+    return os.environ.get("COFFIN_TP_NCCL") == "1"
+
+
 def _ensure_builtin() -> None:
     if _REGISTRY:
         return
@@ -38,7 +45,7 @@ def _ensure_builtin() -> None:
             # expert parallel: attention / delta-net / dense weights replicated, routed experts split
             from ..parallel.tp import TpComm, make_exchange
             comm = TpComm(ep_rank, ep_world, cfg.hidden_size, 8, 2 * cfg.num_hidden_layers, exchange=make_exchange(),
-                          prefill_rows=kw.get("max_chunk", 2048))
+                          prefill_rows=0 if _nccl_only() else kw.get("max_chunk", 2048))
             return Qwen35Model(cfg, sd, tp=comm, ep_rank=ep_rank, ep_world=ep_world, **kw)
         if tp_world > 1:
             from ..parallel.tp import TpComm, local_config, make_exchange, shard_state_dict
@@ -46,7 +53,7 @@ def _ensure_builtin() -> None:
             lsd = shard_state_dict(cfg, sd, tp_rank, tp_world)
             n_sites = 2 * cfg.num_hidden_layers + 2      # two per layer + the vocabulary-parallel arg-max
             tp = TpComm(tp_rank, tp_world, cfg.hidden_size, 8, n_sites, exchange=make_exchange(),
-                        prefill_rows=kw.get("max_chunk", 2048))
+                        prefill_rows=0 if _nccl_only() else kw.get("max_chunk", 2048))
             kw.pop("free_source", None)
             return Qwen35Model(lcfg, lsd, tp=tp, full_cfg=cfg, **kw)
         return Qwen35Model(cfg, sd, **kw)

@@ -22,9 +22,15 @@ from ...config import LINEAR
 from ...ops import _lib, kernels as K
 from ...parallel.tp import _TpCommStruct
 
-ENABLED = os.environ.get("COFFIN_MEGA", "1") != "0"
+# Off by default: measured on B200 (qwen35-4b, batch 1) the persistent step takes 3.3 ms against 2.26 ms
+# of the graph of PDL-chained kernels - a grid-wide barrier costs 4-5 us here, as much as a kernel
+# boundary, and a kernel boundary under programmatic dependent launch overlaps the next projection's
+# weight prefetch with the previous kernel's drain, which a barrier cannot.  COFFIN_MEGA=1 switches it on.
+ENABLED = os.environ.get("COFFIN_MEGA", "0") == "1"
 PREFETCH_KB = int(os.environ.get("COFFIN_MEGA_PREFETCH_KB", "0"))
-RING = int(os.environ.get("COFFIN_MEGA_RING", "4"))        # most stages per warp of the weight ring (0 = off)
+# most stages per warp of the weight ring (0 = off, the default: the 256-byte bulk copies that the
+# fragment layout forces are slower than the warps' own 16-byte loads, 5.8 ms against 3.3 ms per step)
+RING = int(os.environ.get("COFFIN_MEGA_RING", "0"))
 SMEM_LIMIT = 226 * 1024
 STAGE_BYTES = 5120                                          # kStageBytes of decode_mega.cu
 ROWS = (1, 2, 4, 8)

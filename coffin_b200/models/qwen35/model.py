@@ -295,7 +295,10 @@ class Qwen35Model:
     def wide_parallel_ok(self) -> bool:
         """Whether buckets above ``WIDE`` rows run under tensor / expert parallelism: the exchange of
         the wide step is the communicator's peer-memory prefill region."""
-        return self.tp is not None and self.tp.pf_rows >= BUCKETS[-1]
+        if self.tp is None:
+            return False
+        import torch.distributed as dist
+        return self.tp.pf_rows >= BUCKETS[-1] or (dist.is_available() and dist.is_initialized())   # NCCL between kernels otherwise
 
     def launches_per_step(self, M: int) -> int:
         """Kernels launched by one decode step of bucket ``M`` (counted while capturing)."""
@@ -899,13 +902,11 @@ class Qwen35Model:
         return K.rmsnorm(res, self.final_gain, self.eps) if normed else res
 
     def advance_rows(self, M: int) -> None:
-        """Feed the sampled tokens back and advance positions by one (device-side, no host sync):
+        """Feed the sampled tokens back and advance positions by one (one small kernel, no host sync):
         lets a caller run many greedy steps back to back."""
         b = self._row_buffers(M)
-        b["tokens"].copy_(b["next"])
-        live = b["positions"] >= 0
-        b["positions"].add_(live.to(torch.int32))
-        b["rope_pos"].add_(live.to(torch.int32))
+        K.call("advance_rows", b["tokens"], b["next"], b["positions"], b["rope_pos"], M)
+        K._count()
 
     # ------------------------------------------------------------------ speculative verification
     VERIFY_WIDTHS = (2, 4, 8)

@@ -14,6 +14,20 @@ from coffin_b200.weights.init import random_state_dict
 pytestmark = pytest.mark.gpu
 
 
+@pytest.fixture(autouse=True)
+def _mega_on(monkeypatch):
+    """The persistent kernel is opt-in (``COFFIN_MEGA=1``); these tests switch it on."""
+    from coffin_b200.models.qwen35 import mega
+    monkeypatch.setattr(mega, "ENABLED", True)
+
+
+@pytest.fixture(params=[0, 2])
+def ring(request, monkeypatch):
+    from coffin_b200.models.qwen35 import mega
+    monkeypatch.setattr(mega, "RING", request.param)
+    return request.param
+
+
 def _models(cfg, sd, **kw):
     from coffin_b200.models.qwen35.model import Qwen35Model
     a = Qwen35Model(cfg, sd, max_seq=512, num_slots=8, **kw)
@@ -30,7 +44,7 @@ def _close(got, ref, atol, rtol):
 
 
 @torch.no_grad()
-def test_mega_step_matches_multi_kernel_step_every_bucket():
+def test_mega_step_matches_multi_kernel_step_every_bucket(ring):
     from coffin_b200.ops import kernels as K
     cfg = preset("tiny")
     sd = random_state_dict(cfg, 0)
