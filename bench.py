@@ -101,6 +101,7 @@ def main() -> None:
     ap.add_argument("--prompt", type=int, default=PROMPT)
     ap.add_argument("--new", type=int, default=NEW)
     ap.add_argument("--quant", default="none", choices=["none", "int8", "w4a8"])
+    ap.add_argument("--kv-dtype", default="bf16", choices=["bf16", "int8"], help="KV pool storage")
     ap.add_argument("--parallel", default="tp", choices=["tp", "ep"],
                     help="N > 1: tensor parallel (default) or expert parallel (routed-MoE models)")
     ap.add_argument("--rows", type=int, default=1,
@@ -169,7 +170,8 @@ def main() -> None:
     if args.rows > 1:
         return bench_rows(args, cfg, W)
     llm = LLM.from_random(cfg, seed=0, max_seq=args.prompt + args.new + 64, max_num_seqs=1,
-                          graph=not args.no_graph, pdl=not args.no_pdl, max_chunk=args.prompt, quant=args.quant,
+                          graph=not args.no_graph, pdl=not args.no_pdl, max_chunk=min(args.prompt, 2048), quant=args.quant,
+                          kv_dtype=args.kv_dtype,
                           **({"ep_world": world, "ep_rank": rank} if args.parallel == "ep" and world > 1
                              else {"tp_world": world, "tp_rank": rank}))
     model = llm.model
@@ -258,7 +260,7 @@ def main() -> None:
             "ttft_ms_p50": statistics.median(pre_ms), "tpot_ms_p50": statistics.median(dec_ms) / args.new,
             "config": {"model": args.model, "global_batch": 1, "seq_len": args.prompt, "decode_tokens": args.new,
                        "parallelism": f"{args.parallel}{world}" if world > 1 else "single"},
-            "notes": {"cuda_graph": not args.no_graph,
+            "notes": {"cuda_graph": not args.no_graph, "kv_dtype": args.kv_dtype,
                       "cache": f"weights streamed by this rank every decode step ({wbytes / 1e9:.2f} GB; a routed-MoE step reads its dense part plus the selected experts) far exceed the 126 MB L2, no flush needed",
                       "weights": "random-init N(0,0.02)"},
             "token_crc": token_crc,
@@ -293,7 +295,7 @@ def bench_rows(args, cfg, W: int) -> None:
     R = args.rows
     par = ({"ep_world": world, "ep_rank": rank} if args.parallel == "ep" and world > 1 else {"tp_world": world, "tp_rank": rank})
     llm = LLM.from_random(cfg, seed=0, max_seq=args.prompt + args.new + 64, max_num_seqs=R, max_chunk=min(args.prompt, 2048),
-                          quant=args.quant, **par)
+                          quant=args.quant, kv_dtype=args.kv_dtype, **par)
     m = llm.model
     m.full_logits = False
     M = m.bucket_for(R)
@@ -343,7 +345,7 @@ def bench_rows(args, cfg, W: int) -> None:
                           "dtype": {"none": "bf16", "int8": "int8-w8a8", "w4a8": "int4-w4a8"}[args.quant], "data": "synthetic",
                           "config": {"model": args.model, "global_batch": R, "seq_len": args.prompt, "decode_tokens": args.new,
                                      "parallelism": f"{args.parallel}{world}" if world > 1 else "single"},
-                          "notes": {"bucket": M, "cuda_graph": True, "exchange": "nccl" if os.environ.get("COFFIN_TP_NCCL") == "1" else "fused peer-memory",
+                          "notes": {"bucket": M, "cuda_graph": True, "kv_dtype": args.kv_dtype, "exchange": "nccl" if os.environ.get("COFFIN_TP_NCCL") == "1" else "fused peer-memory",
                                     "launches_per_step": m.launches_per_step(M), "weight_gb_per_rank": round(m.weight_bytes() / 1e9, 2)},
                           "impl": "ours"}), flush=True)
     if world > 1:

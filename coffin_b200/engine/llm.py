@@ -52,7 +52,7 @@ class LLM:
     def from_random(cls, cfg: ModelConfig, seed: int = 0, max_seq: int = 4096, max_num_seqs: int = 1,
                     tp_world: int = 1, tp_rank: int = 0, graph: bool = True, pdl: bool = True,
                     max_chunk: int = 2048, device: str = "cuda", quant: str = "none",
-                    ep_world: int = 1, ep_rank: int = 0) -> "LLM":
+                    ep_world: int = 1, ep_rank: int = 0, kv_dtype: str = "bf16") -> "LLM":
         """Random-init weights ~N(0, 0.02) of the given geometry, drawn on the device.  ``tp_world`` > 1
         shards every layer (tensor parallel); ``ep_world`` > 1 splits the routed experts by range instead
         (expert parallel, the dense part replicated)."""
@@ -61,7 +61,8 @@ class LLM:
         sd = random_state_dict(cfg, seed, dtype=torch.bfloat16, device=device)
         model = build_model(cfg, sd, device=device, max_seq=max_seq, num_slots=max_num_seqs,
                             max_chunk=max_chunk, pdl=pdl, tp_world=tp_world, tp_rank=tp_rank, free_source=True, quant=quant,
-                            **({"ep_world": ep_world, "ep_rank": ep_rank} if ep_world > 1 else {}))
+                            **({"ep_world": ep_world, "ep_rank": ep_rank} if ep_world > 1 else {}),
+                            **({"kv_dtype": kv_dtype} if kv_dtype != "bf16" else {}))
         del sd
         torch.cuda.empty_cache()
         return cls(model, graph=graph)

@@ -26,6 +26,8 @@ def export_state(model, slot: int, table: list[int], prompt: list[int], logits: 
     payload = {
         "prompt": list(prompt), "n": n,
         "k": model.kpool[:, slots].cpu(), "v": model.vpool[:, slots].cpu(),
+        "ks": model.kscale[:, slots].cpu() if getattr(model, "kscale", None) is not None else None,
+        "vs": model.vscale[:, slots].cpu() if getattr(model, "vscale", None) is not None else None,
         "state": [t.cpu() for t in model.snapshot_state(slot)],
         "logits": logits.float().cpu(),
     }
@@ -47,8 +49,13 @@ def adopt_state(model, slot: int, in_dir: Path, first_block: int = 1, rank: int 
     table = list(range(first_block, first_block + nblk))
     pos = torch.arange(n)
     slots = (torch.tensor(table, dtype=torch.long)[pos // BLOCK] * BLOCK + pos % BLOCK).to(model.kpool.device)
+    if payload["k"].dtype != model.kpool.dtype:
+        raise RuntimeError(f"exported KV is {payload['k'].dtype}, this engine's pool is {model.kpool.dtype}")
     model.kpool[:, slots] = payload["k"].to(model.kpool.device, model.kpool.dtype)
     model.vpool[:, slots] = payload["v"].to(model.vpool.device, model.vpool.dtype)
+    if payload.get("ks") is not None:
+        model.kscale[:, slots] = payload["ks"].to(model.kscale.device)
+        model.vscale[:, slots] = payload["vs"].to(model.vscale.device)
     snap = model.snapshot_state(slot)
     model.restore_state(slot, tuple(t.to(s.device, s.dtype) for t, s in zip(payload["state"], snap)))
     return table, payload["prompt"], payload["logits"].to(getattr(model, "device", "cpu"))

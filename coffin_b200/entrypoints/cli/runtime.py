@@ -31,6 +31,7 @@ def parser() -> argparse.ArgumentParser:
     ap.add_argument("--device", default="cuda", choices=["cuda", "cpu"])
     ap.add_argument("--max-seq", type=int, default=None)
     ap.add_argument("--quant", default=None, choices=["none", "int8", "w4a8"])
+    ap.add_argument("--kv-dtype", default=None, choices=["bf16", "int8"], help="KV pool storage (int8: per-(token, head) scales)")
     ap.add_argument("--no-prefix-cache", action="store_true")
     ap.add_argument("--num-blocks", type=int, default=None)
     ap.add_argument("--snapshots", type=int, default=None)
@@ -57,7 +58,7 @@ def parser() -> argparse.ArgumentParser:
 def engine_config(args):
     from ...engine.config import EngineConfig
     return EngineConfig.from_env(
-        max_seq=args.max_seq, quant=args.quant, prefix_cache=False if args.no_prefix_cache else None,
+        max_seq=args.max_seq, quant=args.quant, kv_dtype=args.kv_dtype, prefix_cache=False if args.no_prefix_cache else None,
         num_blocks=args.num_blocks, snapshots=args.snapshots, snapshot_interval=args.snapshot_interval,
         spec_k=args.spec_k, spec_batch=True if args.spec_batch else None, chunk=args.chunk,
         prefill_quantum=args.prefill_quantum, max_num_seqs=args.max_num_seqs,
@@ -109,6 +110,8 @@ def build_server(args):
                   device=f"cuda:{int(os.environ.get('LOCAL_RANK', '0'))}", max_seq=cfg_e.max_seq,
                   num_slots=cfg_e.max_num_seqs, max_chunk=cfg_e.chunk,
                   num_blocks=cfg_e.num_blocks if cfg_e.num_blocks > 0 else None)
+        if getattr(cfg_e, "kv_dtype", "bf16") != "bf16":
+            kw["kv_dtype"] = cfg_e.kv_dtype
         if getattr(cfg_e, "quant", None) not in (None, "", "none"):
             kw["quant"] = cfg_e.quant
         if world > 1:

@@ -109,7 +109,7 @@ class MegaDecode:
         c = model.cfg
         if not ENABLED or c.is_moe or model.quant != "none" or not (model.pp_first and model.pp_last):
             return None
-        if model.ep_world > 1 or model.embed is None or model.lm_head is None:
+        if model.ep_world > 1 or model.embed is None or model.lm_head is None or model.kv_dtype != "bf16":
             return None
         for lw in model.layers:
             if any(not isinstance(t, torch.Tensor) for t in (lw.w_in, lw.w_out, lw.w_gu, lw.w_down)):

@@ -134,11 +134,14 @@ class Qwen35Model:
                  max_seq: int = 4096, num_slots: int = 2, num_blocks: int | None = None,
                  max_chunk: int = 2048, pdl: bool = True, free_source: bool = False, tp=None,
                  full_cfg: ModelConfig | None = None, quant: str = "none", ep_rank: int = 0, ep_world: int = 1,
-                 pp_first: bool = True, pp_last: bool = True) -> None:
+                 pp_first: bool = True, pp_last: bool = True, kv_dtype: str = "bf16") -> None:
         """``cfg`` is the geometry this instance computes (a tensor-parallel shard gets its local
         head / channel counts, ``full_cfg`` the unsharded model and ``tp`` the communicator)."""
         self.cfg = cfg
         self.quant = quant
+        if kv_dtype not in ("bf16", "int8"):
+            raise ValueError(f"kv_dtype {kv_dtype!r}: expected bf16 or int8")
+        self.kv_dtype = kv_dtype
         # pipeline stage: a non-first stage starts from a received hidden state instead of the
         # embedding, a non-last stage ends at the residual stream instead of the logits
         self.pp_first, self.pp_last = pp_first, pp_last
@@ -264,8 +267,15 @@ class Qwen35Model:
         self.state = torch.zeros(nl, self.num_slots, c.linear_num_value_heads, c.linear_key_head_dim,
                                  c.linear_value_head_dim, dtype=torch.float32, device=dev)
         self.ring = torch.zeros(nl, self.num_slots, K.RING, c.lin_conv_dim, dtype=bf, device=dev)
-        self.kpool = torch.zeros(nf, self.num_blocks * K.BLOCK, c.num_key_value_heads, c.head_dim, dtype=bf, device=dev)
+        # KV pool: bf16, or int8 with one fp32 scale per (token, kv head) - half the bytes per key read
+        # (reference: int8 pools + scales, cache/paged_cache.py:78-141)
+        kvt = torch.int8 if kv_dtype == "int8" else bf
+        self.kpool = torch.zeros(nf, self.num_blocks * K.BLOCK, c.num_key_value_heads, c.head_dim, dtype=kvt, device=dev)
         self.vpool = torch.zeros_like(self.kpool)
+        self.kscale = self.vscale = None
+        if kv_dtype == "int8":
+            self.kscale = torch.zeros(nf, self.num_blocks * K.BLOCK, c.num_key_value_heads, dtype=torch.float32, device=dev)
+            self.vscale = torch.zeros_like(self.kscale)
         # ---- prefill workspace (allocated lazily at the largest chunk seen) ----------------
         self._pf: dict | None = None
         self._pf_rows = 0
@@ -299,6 +309,12 @@ class Qwen35Model:
             return False
         import torch.distributed as dist
         return self.tp.pf_rows >= BUCKETS[-1] or (dist.is_available() and dist.is_initialized())   # NCCL between kernels otherwise
+
+    def _kvs(self, j: int) -> dict:
+        """Scale tensors of attention layer ``j`` for the attention kernels (empty for a bf16 pool)."""
+        if self.kscale is None:
+            return {}
+        return {"kscale": self.kscale[j], "vscale": self.vscale[j]}
 
     def launches_per_step(self, M: int) -> int:
         """Kernels launched by one decode step of bucket ``M`` (counted while capturing)."""
@@ -345,11 +361,18 @@ class Qwen35Model:
         return K.gemm(A, W, out=out, residual=residual, push=push)
 
     def _row_parallel(self, A, W, scratch: torch.Tensor, swiglu_in: bool = False) -> torch.Tensor:
-        """Row-parallel prefill projection + all-reduce.  With a peer-memory prefill region the GEMM
-        epilogue scatters its rows to the owning ranks and a reduce/gather kernel finishes; otherwise
-        the partial result is all-reduced by NCCL."""
+        """Row-parallel projection + all-reduce.  With a peer-memory region the all-reduce is a
+        reduce-scatter + all-gather over NVLink peer stores: for a prefill chunk the tcgen05 GEMM epilogue
+        scatters its rows to the owning ranks while later tiles are still being multiplied; for the few
+        rows of a decode bucket the K-split GEMM (one wave of CTAs, which a 128-row tile per CTA would
+        not fill) writes the partial rows and a small kernel scatters them.  A reduce/gather kernel
+        finishes either way.  Without the region the partial result is all-reduced by NCCL."""
         if self.tp is not None and self.tp.pf_rows:
-            self._gemm(A, W, swiglu_in=swiglu_in, push=self.tp)
+            if A.shape[0] <= 128 and K.SPLITK_GEMM:
+                self._gemm(A, W, out=scratch, swiglu_in=swiglu_in)
+                self.tp.scatter(scratch)
+            else:
+                self._gemm(A, W, swiglu_in=swiglu_in, push=self.tp)
             return self.tp.finish_reduce()
         return self._tp_reduce(self._gemm(A, W, out=scratch, swiglu_in=swiglu_in))
 
@@ -396,6 +419,9 @@ class Qwen35Model:
         s, d = src * K.BLOCK, dst * K.BLOCK
         self.kpool[:, d:d + K.BLOCK].copy_(self.kpool[:, s:s + K.BLOCK])
         self.vpool[:, d:d + K.BLOCK].copy_(self.vpool[:, s:s + K.BLOCK])
+        if self.kscale is not None:
+            self.kscale[:, d:d + K.BLOCK].copy_(self.kscale[:, s:s + K.BLOCK])
+            self.vscale[:, d:d + K.BLOCK].copy_(self.vscale[:, s:s + K.BLOCK])
 
     # ------------------------------------------------------------------ prefill
     def _prefill_ws(self, T: int) -> dict:
@@ -501,11 +527,11 @@ class Qwen35Model:
                 q = ws["q"][:T]
                 K.attn_prep(proj, lw.qg, lw.kg, cos, sin, ridx, slots, q, self.kpool[j], self.vpool[j],
                             nh=c.num_attention_heads, nkv=c.num_key_value_heads, hd=c.head_dim,
-                            rot=c.rotary_dim, eps=self.eps)
+                            rot=c.rotary_dim, eps=self.eps, **self._kvs(j))
                 for i, (it, n) in enumerate(zip(items, lens)):
                     sl = slice(offs[i], offs[i + 1])
                     K.attn_prefill(q[sl], proj[sl], self.kpool[j], self.vpool[j], it[3], act[sl], q_pos0=it[1],
-                                   nh=c.num_attention_heads, nkv=c.num_key_value_heads, hd=c.head_dim)
+                                   nh=c.num_attention_heads, nkv=c.num_key_value_heads, hd=c.head_dim, **self._kvs(j))
             if self.tp_world > 1 or (self.tp_force and not c.is_moe):
                 part = self._row_parallel(act, lw.w_out, ws["part"][:T])
                 K.rmsnorm(res, lw.post_gain, self.eps, out=normed, add=part, res_out=res)
@@ -662,7 +688,7 @@ class Qwen35Model:
                 K.attn_decode(proj, lw.qg, lw.kg, self.cos, self.sin, b["positions"], b["rope_pos"],
                               b["block_table"], self.kpool[j], self.vpool[j], b["part_o"], b["part_ml"], b["tickets"], act,
                               nh=c.num_attention_heads, nkv=c.num_key_value_heads, hd=c.head_dim,
-                              rot=c.rotary_dim, nsplit=b["nsplit"], eps=self.eps)
+                              rot=c.rotary_dim, nsplit=b["nsplit"], eps=self.eps, **self._kvs(j))
             if tp is not None:
                 self._gemv(lw.w_out, act, None, tp=tp, push_site=2 * li, rows=M)
             else:
@@ -750,7 +776,7 @@ class Qwen35Model:
                 K.attn_decode(proj, lw.qg, lw.kg, self.cos, self.sin, b["positions"], b["rope_pos"],
                               b["block_table"], self.kpool[j], self.vpool[j], b["part_o"], b["part_ml"], b["tickets"], act,
                               nh=c.num_attention_heads, nkv=c.num_key_value_heads, hd=c.head_dim,
-                              rot=c.rotary_dim, nsplit=b["nsplit"], eps=self.eps)
+                              rot=c.rotary_dim, nsplit=b["nsplit"], eps=self.eps, **self._kvs(j))
             if tpw:
                 part = self._row_parallel(act, lw.w_out, b["part"])
                 K.rmsnorm(res, lw.post_gain, self.eps, out=normed, add=part, res_out=res)
@@ -1014,11 +1040,11 @@ class Qwen35Model:
                 act = b["act_full"]
                 K.attn_prep(proj, lw.qg, lw.kg, self.cos, self.sin, b["ridx"], b["kv_slots"], b["q"], self.kpool[j],
                             self.vpool[j], nh=c.num_attention_heads, nkv=c.num_key_value_heads, hd=c.head_dim,
-                            rot=c.rotary_dim, eps=self.eps)
+                            rot=c.rotary_dim, eps=self.eps, **self._kvs(j))
                 for i, (_tk, pos0, _s, _t, _d) in enumerate(rows):
                     sl = slice(i * C, (i + 1) * C)
                     K.attn_prefill(b["q"][sl], proj[sl], self.kpool[j], self.vpool[j], dev_tables[i], act[sl], q_pos0=pos0,
-                                   nh=c.num_attention_heads, nkv=c.num_key_value_heads, hd=c.head_dim)
+                                   nh=c.num_attention_heads, nkv=c.num_key_value_heads, hd=c.head_dim, **self._kvs(j))
             if wide:
                 self._gemm(act, lw.w_out, out=cur, residual=cur)
                 K.rmsnorm(cur, lw.post_gain, self.eps, out=b["normed"])

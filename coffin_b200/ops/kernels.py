@@ -483,15 +483,19 @@ def gdn_prefill(proj, conv_w, A_log, dt_bias, norm_w, ring_seq, state_seq, scrat
 
 
 # ------------------------------------------------------------------ attention
-def attn_prep(proj, qg, kg, cos, sin, rope_idx, kv_slot, q_out, kpool, vpool, *, nh, nkv, hd, rot, eps) -> None:
+def attn_prep(proj, qg, kg, cos, sin, rope_idx, kv_slot, q_out, kpool, vpool, *, nh, nkv, hd, rot, eps,
+              kscale=None, vscale=None) -> None:
+    """``kscale`` / ``vscale`` (fp32 ``[slots, nkv]``): the pools are int8 and the appended rows are
+    quantised per (token, kv head)."""
     T = proj.shape[0]
+    assert (kscale is None) == (vscale is None) and (kscale is None) == (kpool.dtype != torch.int8)
     call("attn_prep", proj, proj.stride(0), qg, kg, cos, sin, rope_idx, kv_slot, q_out, kpool, vpool,
-         T, nh, nkv, hd, rot, float(eps))
+         T, nh, nkv, hd, rot, float(eps), kscale, vscale)
     _count()
 
 
 def attn_prefill(q, proj, kpool, vpool, block_table, out, *, q_pos0, nh, nkv, hd, causal: bool = True,
-                 kv_len: int = 0, keep: torch.Tensor | None = None, ratio: int = 0) -> torch.Tensor:
+                 kv_len: int = 0, keep: torch.Tensor | None = None, ratio: int = 0, kscale=None, vscale=None) -> torch.Tensor:
     """``proj`` supplies the per-head output gate (``None``: no gate). ``causal=False`` attends to the
     first ``kv_len`` keys of the block table (bidirectional, used by the vision tower).  ``keep``
     (int32 ``[T, words]`` bit mask over blocks of ``ratio`` tokens) restricts query ``t`` to the kept
@@ -499,7 +503,7 @@ def attn_prefill(q, proj, kpool, vpool, block_table, out, *, q_pos0, nh, nkv, hd
     T = q.shape[0]
     call("attn_prefill", q, proj, proj.stride(0) if proj is not None else 0, kpool, vpool, block_table, out,
          out.stride(0), T, q_pos0, nh, nkv, hd, int(causal), kv_len, keep,
-         keep.stride(0) if keep is not None else 0, ratio)
+         keep.stride(0) if keep is not None else 0, ratio, kscale, vscale)
     _count()
     return out
 
@@ -558,12 +562,12 @@ def qsa_select(iq, bkpool, block_table, positions, scores, sel, nsel, *, ni, di,
 
 
 def attn_decode(proj, qg, kg, cos, sin, positions, rope_pos, block_table, kpool, vpool, part_o, part_ml, tickets,
-                out, *, nh, nkv, hd, rot, nsplit, eps) -> torch.Tensor:
+                out, *, nh, nkv, hd, rot, nsplit, eps, kscale=None, vscale=None) -> torch.Tensor:
     """``tickets``: zero-initialised int32 ``[M, nkv]`` arrival counters (re-armed by the kernel)."""
     M = positions.numel()
     call("attn_decode", proj, proj.stride(0), qg, kg, cos, sin, positions, rope_pos, block_table,
          block_table.stride(0), kpool, vpool, part_o, part_ml, tickets, out, out.stride(0), M, nh, nkv, hd, rot,
-         nsplit, float(eps))
+         nsplit, float(eps), kscale, vscale)
     _count()
     return out
 

@@ -21,17 +21,38 @@ def main() -> None:
     ap.add_argument("--prompt", type=int, default=2048)
     ap.add_argument("--decode", type=int, default=3)
     ap.add_argument("--rows", type=int, default=1)
+    ap.add_argument("--quant", default="none", choices=["none", "int8", "w4a8"])
+    ap.add_argument("--kv-dtype", default="bf16", choices=["bf16", "int8"])
+    ap.add_argument("--mega", action="store_true", help="decode through the persistent one-launch kernel")
+    ap.add_argument("--tp-force", action="store_true",
+                    help="one GPU, world 1, with the tensor-parallel exchange forced on (push epilogues, pull+norm kernel, prefill scatter/reduce)")
     ap.add_argument("--graph", action="store_true")
     ap.add_argument("--no-pdl", action="store_true")
     args = ap.parse_args()
+    import os
+    if args.mega:
+        os.environ["COFFIN_MEGA"] = "1"
     from ..config import preset
     from ..engine.llm import LLM
     from ..ops import kernels as K
     cfg = preset(args.model)
     if args.layers and args.layers < cfg.num_hidden_layers:
         cfg = dataclasses.replace(cfg, num_hidden_layers=args.layers, layer_types=cfg.layer_types[:args.layers])
-    llm = LLM.from_random(cfg, seed=0, max_seq=args.prompt + 64, max_num_seqs=max(1, args.rows),
-                          graph=args.graph, pdl=not args.no_pdl, max_chunk=args.prompt)
+    if args.tp_force or args.kv_dtype != "bf16":
+        from ..models.qwen35.model import Qwen35Model
+        from ..weights.init import random_state_dict
+        tp = None
+        if args.tp_force:
+            from ..parallel.tp import TpComm
+            tp = TpComm(0, 1, cfg.hidden_size, 8, 2 * cfg.num_hidden_layers + 2, prefill_rows=args.prompt)
+        sd = random_state_dict(cfg, 0, dtype=torch.bfloat16, device="cuda")
+        model = Qwen35Model(cfg, sd, max_seq=args.prompt + 64, num_slots=max(1, args.rows), max_chunk=args.prompt,
+                            pdl=not args.no_pdl, free_source=True, tp=tp, quant=args.quant, kv_dtype=args.kv_dtype)
+        model.tp_force = args.tp_force
+        llm = LLM(model, graph=args.graph)
+    else:
+        llm = LLM.from_random(cfg, seed=0, max_seq=args.prompt + 64, max_num_seqs=max(1, args.rows),
+                              graph=args.graph, pdl=not args.no_pdl, max_chunk=args.prompt, quant=args.quant)
     g = torch.Generator().manual_seed(0)
     prompt = torch.randint(0, cfg.vocab_size, (args.prompt,), generator=g).cuda()
     first = llm.device_prefill(prompt)

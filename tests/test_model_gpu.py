@@ -351,3 +351,46 @@ def test_grouped_prefill_equals_separate_prefills():
             assert _rel(got[r], ref.cpu()) < 2e-2 and _rel(got[r], ref_oracle) < 3e-2
         assert _rel(model.state[:, r], solo_m.state[:, r].cpu()) < 2e-2
     assert _rel(model.kpool, solo_m.kpool.cpu()) < 2e-2
+
+
+@torch.no_grad()
+@pytest.mark.parametrize("rows", [1, 3, 12, 40])
+def test_int8_kv_pool_matches_the_int8_kv_oracle(rows):
+    """``kv_dtype="int8"``: K/V rows are quantised per (token, kv head) when appended (prefill prep, decode
+    append) and dequantised on load by every attention kernel - prefill flash, single-row decode, the
+    tensor-core batch kernel (40 rows x 2 kv heads) and the wide bucket.  Against the fp32 oracle that
+    quantises its KV the same way; and the pool really is int8 with one scale per (token, head)."""
+    from coffin_b200.models.qwen35.model import Qwen35Model
+    cfg = preset("tiny")
+    sd = random_state_dict(cfg, 0)
+    sd_b = {k: (v.to(torch.bfloat16).float() if v.dtype == torch.float32 and not k.endswith(("A_log", "dt_bias")) else v)
+            for k, v in sd.items()}
+    oracle = OracleModel(cfg, sd_b, kv_int8=True)
+    model = Qwen35Model(cfg, sd, max_seq=256, num_slots=rows, kv_dtype="int8")
+    assert model.kpool.dtype == torch.int8 and model.kscale.shape == model.kpool.shape[:-1]
+    lens = [33 + (7 * r) % 60 for r in range(rows)]
+    seqs = [_tokens(cfg, n + 3, seed=200 + r) for r, n in enumerate(lens)]
+    tables = [list(range(1 + 4 * r, 5 + 4 * r)) for r in range(rows)]
+    states = []
+    check = sorted(set([0, rows // 2, rows - 1]))
+    for r in range(rows):
+        bt = torch.tensor(tables[r], dtype=torch.int32, device="cuda")
+        model.zero_state(r)
+        # two chunks: the second one attends to int8 keys written by the first
+        model.prefill(seqs[r][:20].cuda(), 0, r, bt, want_logits=False)
+        got = model.prefill(seqs[r][20:lens[r]].cuda(), 20, r, bt)
+        if r in check:
+            st = oracle.new_state()
+            ref = oracle.forward(seqs[r][:lens[r]], st)[-1]
+            states.append((r, st))
+            assert _rel(got, ref) < 4e-2, f"prefill row {r}"
+    M = model.bucket_for(rows)
+    for step in range(3):
+        model.set_rows(M, [int(seqs[r][lens[r] + step]) for r in range(rows)], [lens[r] + step for r in range(rows)],
+                       list(range(rows)), tables)
+        _, lg = model.decode(M, graph=step >= 1)
+        for r, st in states:
+            ref = oracle.forward(seqs[r][lens[r] + step:lens[r] + step + 1], st)[-1]
+            assert _rel(lg[r], ref) < 5e-2, f"decode step {step} row {r}"
+    used = model.kscale[0, tables[0][0] * 64: tables[0][0] * 64 + lens[0]]
+    assert bool((used > 0).all())
