@@ -63,7 +63,15 @@ def _ensure_builtin() -> None:
 
     def qwen4(cfg, sd, **kw):
         from .qwen4exp.model import Qwen4ExpModel
-        kw.pop("tp_world", None), kw.pop("tp_rank", None)
+        if kw.pop("tp_world", 1) > 1 or kw.pop("pp_world", 1) > 1:
+            raise NotImplementedError("the Qwen4-exp family runs on one GPU or expert parallel (ep_world), as its reference does")
+        kw.pop("tp_rank", None), kw.pop("pp_rank", None)
+        ep_world, ep_rank = kw.pop("ep_world", 1), kw.pop("ep_rank", 0)
+        if ep_world > 1:
+            from ..parallel.tp import TpComm, make_exchange
+            comm = TpComm(ep_rank, ep_world, cfg.hidden_size, 8, 2, exchange=make_exchange(),
+                          prefill_rows=0 if _nccl_only() else kw.get("max_chunk", 2048))
+            return Qwen4ExpModel(cfg, sd, tp=comm, ep_rank=ep_rank, ep_world=ep_world, **kw)
         return Qwen4ExpModel(cfg, sd, **kw)
 
     for n in ("qwen4_exp", "qwen4exp"):

@@ -57,13 +57,16 @@ class MoEWeights:
         e_lo, e_hi = ep_rank * per, (ep_rank + 1) * per
         from ...weights.quant import W4A8Weight
         from .model import QW4
+        # a state dict read with an expert-parallel filter already holds only this rank's experts
+        presliced = tuple(sd.get("__ep_shard__", ())) == (ep_rank, ep_world) and ep_world > 1
+        s_lo, s_hi = (0, per) if presliced else (e_lo, e_hi)
 
         def experts(t):
             """bf16 stack, or W4A8 codes + scales when the checkpoint (or ``quant``) says so."""
             if isinstance(t, W4A8Weight):
-                part = W4A8Weight(t.packed[e_lo:e_hi], t.scale[e_lo:e_hi], t.k, t.group_size)
+                part = W4A8Weight(t.packed[s_lo:s_hi], t.scale[s_lo:s_hi], t.k, t.group_size)
                 return QW4(*part.to(dev).to_nk())
-            t = t[e_lo:e_hi].to(dev, bf)
+            t = t[s_lo:s_hi].to(dev, bf)
             if quant == "w4a8" and t.shape[-1] % 128 == 0:
                 return QW4.quantize(t)
             return t.contiguous()

@@ -32,6 +32,7 @@ import torch
 
 from ...ops import kernels as K
 from ...oracle import ops as O
+from ..qwen35.model import QW, QW4
 from ..qwen35.moe import MoEWeights
 from .config import LINEAR, Qwen4Config
 from .ngram import NGramHasher, NGramTable
@@ -67,11 +68,44 @@ class _Layer:
     pass
 
 
+class QuantEmbedding:
+    """Embedding table stored as int8 rows + one fp32 scale per row (a quarter of the bf16 table once
+    the scales are counted): gathered rows are dequantised to bf16 on the device.  Reference:
+    ``models/qwen4exp/proj.py:724-841`` (``QuantizedEmbedding``)."""
+
+    def __init__(self, wq: torch.Tensor, scale: torch.Tensor) -> None:
+        self.wq, self.scale = wq.contiguous(), scale.float().contiguous()
+        self.shape = self.wq.shape
+
+    def gather(self, tokens: torch.Tensor) -> torch.Tensor:
+        rows = self.wq.index_select(0, tokens)
+        return (rows.float() * self.scale.index_select(0, tokens)[:, None]).to(torch.bfloat16)
+
+    def dequant(self) -> torch.Tensor:
+        return (self.wq.float() * self.scale[:, None]).to(torch.bfloat16)
+
+    def numel(self) -> int:
+        return self.wq.numel()
+
+    def element_size(self) -> int:
+        return 1
+
+    def data_ptr(self) -> int:
+        return self.wq.data_ptr()
+
+
 class Qwen4ExpModel:
     def __init__(self, cfg: Qwen4Config, sd: dict[str, torch.Tensor], device: str | torch.device = "cuda",
                  max_seq: int = 4096, num_slots: int = 2, num_blocks: int | None = None, max_chunk: int = 2048,
-                 pdl: bool = True, ngram_device_budget: int = 120 << 30, **_unused) -> None:
+                 pdl: bool = True, ngram_device_budget: int = 120 << 30, quant: str = "none", tp=None,
+                 ep_rank: int = 0, ep_world: int = 1, **_unused) -> None:
+        """``quant``: ``int8`` / ``w4a8`` storage of the mixer projections, the experts and the head (a
+        pre-quantised state dict brings its own containers).  ``ep_world`` > 1: the routed experts are split
+        by range over the ranks of the communicator ``tp``; everything else is replicated."""
         self.cfg = c = cfg
+        self.quant = quant
+        self.tp, self.ep_rank, self.ep_world = tp, ep_rank, ep_world
+        self.tp_world, self.tp_rank, self.tp_force = 1, 0, False
         if 64 % c.indexer_compress_ratio or c.indexer_compress_ratio < 2:
             raise ValueError("indexer_compress_ratio must be a power of two between 2 and 64")
         if c.indexer_n_heads > 8 or c.indexer_head_dim > 256:
@@ -86,14 +120,55 @@ class Qwen4ExpModel:
         K._lib.set_pdl(pdl)
         bf = torch.bfloat16
 
+        from ...weights.quant import QWeight, W4A8Weight
+
         def w(key):
-            return sd[key].to(dev, bf)
+            """A projection in the storage the checkpoint (or ``quant``) gives it: bf16, int8 rows with
+            per-row scales, or int4 codes with group scales (``Proj`` of the reference, ``proj.py:524-722``)."""
+            t = sd[key]
+            if isinstance(t, QWeight):
+                return QW(t.wq.to(dev), t.scale.to(dev))
+            if isinstance(t, W4A8Weight):
+                if t.k % t.group_size == 0 and t.group_size == 128:
+                    return QW4(*t.to(dev).to_nk())
+                t = t.dequant(bf)
+            return t.to(dev, bf)
+
+        def dense(key):
+            t = sd[key]
+            return (t.dequant(bf) if isinstance(t, (QWeight, W4A8Weight)) else t).to(dev, bf)
+
+        def quantise(t):
+            """Apply ``quant`` to a dense projection (containers pass through)."""
+            if isinstance(t, (QW, QW4)):
+                return t
+            if quant == "w4a8" and t.shape[1] % 128 == 0:
+                return QW4.quantize(t)
+            return QW.quantize(t) if quant == "int8" else t.contiguous()
+
+        def cat(parts):
+            """Row-concatenate projections that share an input; quantised parts keep their scales."""
+            if any(isinstance(p_, QW4) for p_ in parts) or quant == "w4a8":
+                conv = [p_ if isinstance(p_, QW4) else (QW4.zeros(p_.shape[0], p_.shape[1], dev) if not bool(p_.any())
+                                                         else QW4.quantize(p_)) for p_ in parts]
+                return QW4(torch.cat([p_.wq for p_ in conv]), torch.cat([p_.scale for p_ in conv]))
+            if any(isinstance(p_, QW) for p_ in parts) or quant == "int8":
+                conv = [p_ if isinstance(p_, QW) else QW.quantize(p_) for p_ in parts]
+                return QW(torch.cat([p_.wq for p_ in conv]), torch.cat([p_.scale for p_ in conv]))
+            return torch.cat(parts).contiguous()
 
         def gain(key):
             return (1.0 + sd[key].float()).to(dev).contiguous()
 
-        self.embed = w(LM + "embed_tokens.weight").contiguous()
-        self.lm_head = w("lm_head.weight").contiguous() if "lm_head.weight" in sd else self.embed
+        e = sd[LM + "embed_tokens.weight"]
+        if isinstance(e, QWeight):
+            self.embed = QuantEmbedding(e.wq.to(dev), e.scale.to(dev))
+        else:
+            self.embed = dense(LM + "embed_tokens.weight").contiguous()
+        if "lm_head.weight" in sd:
+            self.lm_head = quantise(w("lm_head.weight"))
+        else:
+            self.lm_head = quantise(self.embed.dequant() if isinstance(self.embed, QuantEmbedding) else self.embed)
         self.final = _Hyper(sd, LM + "hyper_connection_mixer.", dev, write_gate=False)
         self.layers: list[_Layer] = []
         self.lin_ids = {li: j for j, li in enumerate(c.linear_layers)}
@@ -112,8 +187,8 @@ class Qwen4ExpModel:
                 n = sum(t.shape[0] for t in parts)
                 if _pad8(n) != n:
                     parts.append(torch.zeros(_pad8(n) - n, c.hidden_size, dtype=bf, device=dev))
-                L.w_in = torch.cat(parts).contiguous()
-                L.w_out = w(q + "out_proj.weight").contiguous()
+                L.w_in = cat(parts)
+                L.w_out = quantise(w(q + "out_proj.weight"))
                 L.conv_w = sd[q + "conv1d.weight"].to(dev, torch.float32).reshape(c.lin_conv_dim, -1).contiguous()
                 L.A_log = sd[q + "A_log"].to(dev, torch.float32).contiguous()
                 L.dt_bias = sd[q + "dt_bias"].to(dev, torch.float32).contiguous()
@@ -126,11 +201,11 @@ class Qwen4ExpModel:
                 L.idx_col = n - parts[3].shape[0]
                 if _pad8(n) != n:
                     parts.append(torch.zeros(_pad8(n) - n, c.hidden_size, dtype=bf, device=dev))
-                L.w_in = torch.cat(parts).contiguous()
-                L.w_out = w(q + "o_proj.weight").contiguous()
+                L.w_in = cat(parts)
+                L.w_out = quantise(w(q + "o_proj.weight"))
                 L.qg, L.kg = gain(q + "q_norm.weight"), gain(q + "k_norm.weight")
                 L.iqg, L.ikg = gain(q + "indexer.q_layernorm.weight"), gain(q + "indexer.k_layernorm.weight")
-            L.moe = MoEWeights.from_state_dict(c, sd, p + "mlp.", dev)
+            L.moe = MoEWeights.from_state_dict(c, sd, p + "mlp.", dev, ep_rank, ep_world, quant=quant)
             L.ple = None
             j = c.ple_index(li)
             if j is not None:
@@ -170,6 +245,12 @@ class Qwen4ExpModel:
     # ------------------------------------------------------------------ sizes / bookkeeping
     def _fresh_ctx(self) -> list[int]:
         return [self.cfg.eos_token_id] * self.cfg.ple_context_len
+
+    def poll_status(self) -> None:
+        K.poll_status()
+
+    def check_status(self) -> None:
+        K.raise_on_status()
 
     def weight_bytes(self) -> int:
         tensors = [self.embed, self.lm_head] + self.final.tensors()
@@ -274,16 +355,49 @@ class Qwen4ExpModel:
             self._ws[T] = ws
         return ws
 
-    def _linear(self, W: torch.Tensor, x: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
-        """``out = x @ W^T`` through the GEMV (up to 8 rows whose activations fit its shared memory)
-        or the tcgen05 GEMM."""
+    def _linear(self, W, x: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+        """``out = x @ W^T`` on whichever storage ``W`` has: up to 8 rows through the decode projections
+        (bf16 tensor-core GEMV, int8 W8A8, int4 W4A8), more through the tcgen05 GEMM (bf16, int8
+        ``kind::i8``, int4 expanded to bf16 for the call)."""
         T, Kd = x.shape
-        if T <= 8 and T * Kd * 2 <= 64 * 1024:
+        small = T <= 8 and T * Kd * 2 <= 64 * 1024
+        if isinstance(W, QW):
+            if small:
+                return K.gemv_i8(W.wq, W.scale, x, out)
+            qx, sc = K.quant_rows(x)
+            if out.dtype == torch.bfloat16:
+                return K.gemm_i8(qx, sc, W.wq, W.scale, out=out)
+            out.copy_(K.gemm_i8(qx, sc, W.wq, W.scale))
+            return out
+        if isinstance(W, QW4):
+            if small:
+                return K.gemv_w4(W.wq, W.scale, x, out)
+            W = W.dequant()
+        if small:
             return K.gemv(W, x, out)
         if out.dtype == torch.bfloat16:
             return K.gemm(x, W, out=out)
         out.copy_(K.gemm(x, W))
         return out
+
+    def _embed(self, tokens: torch.Tensor) -> torch.Tensor:
+        if isinstance(self.embed, QuantEmbedding):
+            return self.embed.gather(tokens)
+        return K.embed_gather(self.embed, tokens)
+
+    def _tp_reduce(self, t: torch.Tensor) -> torch.Tensor:
+        """Sum of the ranks' routed-expert outputs ``[T, hidden]`` (expert parallel): scatter + reduce/gather
+        over peer memory when the communicator has the region, NCCL otherwise (the reference combines
+        through a shared-memory board, ``models/qwen4exp/parallel.py:245-565``)."""
+        if self.ep_world == 1:
+            return t
+        if self.tp is not None and self.tp.pf_rows and t.shape[0] <= self.tp.pf_rows:
+            self.tp.scatter(t.contiguous())
+            return self.tp.finish_reduce()
+        import torch.distributed as dist
+        dist.all_reduce(t)
+        K._count()
+        return t
 
     # ------------------------------------------------------------------ hyper-connection
     def _hyper_read(self, hw: _Hyper, ws: dict, T: int, pending, inject_buf: torch.Tensor | None):
@@ -469,7 +583,7 @@ class Qwen4ExpModel:
                 out = logits[0] if logits is not None else None
             return out
         ws = self._work(T)
-        e = K.embed_gather(self.embed, tokens) if embeds is None else embeds.to(torch.bfloat16)
+        e = self._embed(tokens) if embeds is None else embeds.to(torch.bfloat16)
         ws["stream"].copy_(e.repeat(1, c.hc_count))
         pos = torch.arange(pos0, pos0 + T, dtype=torch.int64, device=self.device)
         ws["pos"].copy_(pos)
@@ -480,7 +594,7 @@ class Qwen4ExpModel:
         if not want_logits:
             return None
         logits = torch.empty(1, c.vocab_size, dtype=torch.float32, device=self.device)
-        K.gemv(self.lm_head, mixed[T - 1:T].contiguous(), logits)
+        self._linear(self.lm_head, mixed[T - 1:T].contiguous(), logits)
         return logits[0]
 
     def set_rows(self, M: int, tokens, positions, slots, block_tables, rope_deltas=None) -> None:
@@ -502,7 +616,7 @@ class Qwen4ExpModel:
         c, st = self.cfg, self._staged
         n = st["n"]
         ws = self._work(n)
-        ws["stream"].copy_(K.embed_gather(self.embed, st["tok_dev"]).repeat(1, c.hc_count))
+        ws["stream"].copy_(self._embed(st["tok_dev"]).repeat(1, c.hc_count))
         ws["pos"].copy_(st["pos_dev"])
         p64 = st["pos_dev"].to(torch.int64)
         ws["kv_slot"].copy_(st["bt"].to(torch.int64).gather(1, (p64 // K.BLOCK)[:, None])[:, 0] * K.BLOCK + p64 % K.BLOCK)
@@ -514,7 +628,7 @@ class Qwen4ExpModel:
                                  "next": torch.zeros(M, dtype=torch.int64, device=self.device)}
         if not want_logits:
             return b["next"], None
-        K.gemv(self.lm_head, mixed.contiguous(), b["logits"][:n])
+        self._linear(self.lm_head, mixed.contiguous(), b["logits"][:n])
         K.argmax(b["logits"], b["next"])
         return b["next"], b["logits"]
 

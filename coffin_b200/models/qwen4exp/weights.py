@@ -104,3 +104,129 @@ def random_state_dict(cfg: Qwen4Config, seed: int = 0, dtype: torch.dtype = torc
 
 def param_count(cfg: Qwen4Config) -> int:
     return sum(math.prod(s) for _, s, _ in tensor_plan(cfg))
+
+
+# ---------------------------------------------------------------------------------------------------
+# Streaming loader: shard index, plan check, rank-filtered reads.
+#
+# A real checkpoint of this family is dominated by two things a rank must not read whole: the routed
+# expert stacks (512 experts per layer) and the n-gram table of the PLE layer (tens of GiB).  The
+# loader therefore works from the safetensors shard index, checks every planned tensor's presence and
+# shape BEFORE reading any data, then streams shard by shard; under expert parallelism it reads only
+# this rank's expert range of every stack (``get_slice``) and marks the dict so that the MoE module does
+# not cut again.  Reference: ``models/qwen4exp/checkpoint.py`` (shard index + mmap) and
+# ``models/qwen4exp/weights.py`` (``plan / verify / load_into / slice_experts``).
+def checkpoint_index(model_dir) -> dict[str, str]:
+    """``{tensor name: shard file}`` of a checkpoint directory (``model.safetensors.index.json`` when it
+    exists, else the names found by opening every shard's header)."""
+    import json
+    from pathlib import Path
+
+    from safetensors import safe_open
+    d = Path(model_dir)
+    idx = d / "model.safetensors.index.json"
+    if idx.exists():
+        return dict(json.loads(idx.read_text())["weight_map"])
+    out: dict[str, str] = {}
+    for f in sorted(d.glob("*.safetensors")):
+        if f.name.startswith("quant-"):
+            continue
+        with safe_open(str(f), framework="pt") as fh:
+            for k in fh.keys():
+                out[k] = f.name
+    if not out:
+        raise FileNotFoundError(f"no safetensors shards in {d}")
+    return out
+
+
+def verify_plan(cfg: Qwen4Config, model_dir, index: dict[str, str] | None = None) -> dict:
+    """Compare the checkpoint's headers with ``tensor_plan(cfg)`` without reading tensor data.  Returns
+    ``{"missing": [...], "unexpected": [...], "shape": [(key, found, wanted), ...]}``; per-expert spellings
+    (``experts.{e}.gate_proj.weight`` ...) count for their fused stack."""
+    import re
+    from pathlib import Path
+
+    from safetensors import safe_open
+    index = index or checkpoint_index(model_dir)
+    want = {k: tuple(s) for k, s, _ in tensor_plan(cfg)}
+    shapes: dict[str, tuple] = {}
+    for fname in sorted(set(index.values())):
+        with safe_open(str(Path(model_dir) / fname), framework="pt") as fh:
+            for k in fh.keys():
+                shapes[k] = tuple(fh.get_slice(k).get_shape())
+    per_expert = re.compile(r"^(.*\.mlp\.experts\.)(\d+)\.(gate_proj|up_proj|down_proj)\.weight$")
+    fused_seen: dict[str, set] = {}
+    for k in list(shapes):
+        m = per_expert.match(k)
+        if m:
+            fused_seen.setdefault(m.group(1), set()).add(int(m.group(2)))
+    missing, bad = [], []
+    for k, s in want.items():
+        if k in shapes:
+            if shapes[k] != s:
+                bad.append((k, shapes[k], s))
+        elif k.endswith(("experts.gate_up_proj", "experts.down_proj")) and \
+                len(fused_seen.get(k.rsplit(".", 1)[0] + ".", ())) == cfg.num_experts:
+            continue
+        else:
+            missing.append(k)
+    known = set(want) | {k for k in shapes if per_expert.match(k)}
+    unexpected = [k for k in shapes if k not in known and k.startswith((LM, "lm_head."))]
+    return {"missing": missing, "unexpected": unexpected, "shape": bad}
+
+
+def load_streaming(model_dir, cfg: Qwen4Config | None = None, device: str = "cpu", ep: tuple[int, int] | None = None,
+                   strict: bool = True) -> dict[str, torch.Tensor]:
+    """State dict of a Qwen4-exp checkpoint read shard by shard.  ``ep=(rank, world)``: only this rank's
+    contiguous expert range of every routed stack is read (and the dict is marked ``__ep_shard__``); all
+    other tensors are read whole.  ``strict``: refuse a checkpoint whose headers do not match the plan."""
+    from pathlib import Path
+
+    from safetensors import safe_open
+
+    from ...config import load_config
+    from ...weights.loader import fuse_experts
+    d = Path(model_dir)
+    cfg = cfg or load_config(d)
+    index = checkpoint_index(d)
+    if strict:
+        rep = verify_plan(cfg, d, index)
+        if rep["missing"] or rep["shape"]:
+            raise ValueError(f"{d}: checkpoint does not match the tensor plan: missing {rep['missing'][:4]} "
+                             f"shape {rep['shape'][:2]}")
+    E = cfg.num_experts
+    lo, hi = 0, E
+    if ep is not None and ep[1] > 1:
+        if E % ep[1]:
+            raise ValueError(f"num_experts={E} is not divisible by expert-parallel world {ep[1]}")
+        per = E // ep[1]
+        lo, hi = ep[0] * per, (ep[0] + 1) * per
+    sd: dict[str, torch.Tensor] = {}
+    by_file: dict[str, list[str]] = {}
+    for k, f in index.items():
+        by_file.setdefault(f, []).append(k)
+    import re
+    per_expert = re.compile(r"\.mlp\.experts\.(\d+)\.")
+    for fname in sorted(by_file):
+        with safe_open(str(d / fname), framework="pt", device=device) as fh:
+            for k in by_file[fname]:
+                if not k.startswith((LM, "lm_head.", "mtp.", "model.visual.")):
+                    continue
+                if k.endswith(("experts.gate_up_proj", "experts.down_proj")) and (lo, hi) != (0, E):
+                    sd[k] = fh.get_slice(k)[lo:hi]
+                    continue
+                m = per_expert.search(k)
+                if m and not (lo <= int(m.group(1)) < hi):
+                    continue                                   # another rank's expert
+                sd[k] = fh.get_tensor(k)
+    if (lo, hi) != (0, E):
+        # per-expert spellings: renumber the kept experts from 0 so that they fuse into a local stack
+        ren = {}
+        for k, v in sd.items():
+            m = per_expert.search(k)
+            ren[k[:m.start(1)] + str(int(m.group(1)) - lo) + k[m.end(1):] if m else k] = v
+        sd = ren
+    sd = fuse_experts(sd)
+    if (lo, hi) != (0, E):
+        sd["__ep_shard__"] = (ep[0], ep[1])
+    return sd

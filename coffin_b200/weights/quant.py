@@ -31,6 +31,23 @@ def is_quantizable(key: str, t: torch.Tensor) -> bool:
                          "experts.gate_up_proj", "experts.down_proj"))
 
 
+def is_quantizable_qwen4(key: str, t: torch.Tensor) -> bool:
+    """Qwen4-exp: the mixer projections (including the fused indexer projection), the routed and shared
+    experts and the lm_head are quantised; the router, gates, norms, conv taps, the hyper-connection
+    matrices (low rank, read in fp32 gates), the PLE projections and tables and the embedding stay dense
+    (reference: ``tools/quant_disk_qwen4.py`` quantises the same families, ``models/qwen4exp/proj.py:524-722``
+    loads them)."""
+    if t.dim() not in (2, 3) or not t.is_floating_point():
+        return False
+    if "hyper_connection" in key or ".ple." in key or key.endswith(("embed_tokens.weight", "mlp.gate.weight",
+                                                                      "shared_expert_gate.weight", "conv1d.weight")):
+        return False
+    return key.endswith(("q_proj.weight", "k_proj.weight", "v_proj.weight", "o_proj.weight", "index_qk_proj.weight",
+                         "in_proj_qkv.weight", "in_proj_z.weight", "out_proj.weight", "gate_proj.weight",
+                         "up_proj.weight", "down_proj.weight", "lm_head.weight", "experts.gate_up_proj",
+                         "experts.down_proj"))
+
+
 @dataclasses.dataclass
 class QWeight:
     """Symmetric per-output-row int8: ``w[n, k] ~= wq[n, k] * scale[n]``. ``wq`` may carry a

@@ -60,72 +60,91 @@ def _mem_key(key: str) -> str:
     return key
 
 
-def write_quantized(model_dir: str | Path, sd: dict[str, torch.Tensor], out_dir: str | Path, scheme: str = "int8",
-                    shard_bytes: int = 4 << 30, weight_dtype: str = "bfloat16") -> dict:
+def write_quantized(model_dir: str | Path, sd, out_dir: str | Path, scheme: str = "int8",
+                    shard_bytes: int = 4 << 30, weight_dtype: str = "bfloat16", is_q=None, generated_by: str | None = None) -> dict:
     """Quantise ``sd`` (dense, HF key layout) and write a pre-quantised directory next to a copy
-    of ``config.json`` from ``model_dir``."""
+    of ``config.json`` from ``model_dir``.  ``sd`` is a mapping or any iterable of ``(key, tensor)``
+    pairs, consumed once in order (a streaming source never has to hold the whole model); ``is_q(key,
+    tensor)`` replaces the default choice of which tensors are quantised."""
     from safetensors.torch import save_file
     src, out = Path(model_dir), Path(out_dir)
     out.mkdir(parents=True, exist_ok=True)
     (out / "config.json").write_bytes((src / "config.json").read_bytes())
     w4 = scheme == "w4a8"
     tensors: dict[str, dict] = {}
-    shards: list[dict[str, torch.Tensor]] = [{}]
+    cur: dict[str, torch.Tensor] = {}
+    tmp_files: list[Path] = []
     size = 0
 
-    def put(name: str, t: torch.Tensor) -> int:
+    def flush() -> None:
+        """Write the shard collected so far (under a temporary name: the final names carry the shard
+        count, known only at the end) and drop its tensors, so memory stays at one shard."""
+        nonlocal cur, size
+        if cur:
+            path = out / f"quant-part-{len(tmp_files) + 1:05d}.tmp"
+            save_file(cur, str(path))
+            tmp_files.append(path)
+        cur, size = {}, 0
+
+    def put(group: dict[str, torch.Tensor]) -> int:
+        """Add the tensors of one logical weight (codes, scales, ...) to the SAME shard (the index records
+        one shard per weight) and return its number."""
         nonlocal size
-        nb = t.numel() * t.element_size()
+        nb = sum(t.numel() * t.element_size() for t in group.values())
         if size and size + nb > shard_bytes:
-            shards.append({})
-            size = 0
-        shards[-1][name] = t.contiguous().cpu()
+            flush()
+        for name, t in group.items():
+            cur[name] = t.contiguous().cpu()
         size += nb
-        return len(shards) - 1
+        return len(tmp_files)
 
     kinds: dict[str, int] = {}
-    for key, t in sd.items():
+    has_visual = False
+    pick = is_q or is_quantizable
+    for key, t in (sd.items() if hasattr(sd, "items") else sd):
         dk = _disk_key(key)
         moe = t.dim() == 3
-        if is_quantizable(key, t) and not key.endswith(DENSE_SUFFIXES):
+        has_visual = has_visual or key.startswith("model.visual.")
+        if pick(key, t) and not key.endswith(DENSE_SUFFIXES):
             if w4:
                 q = W4A8Weight.quantize(t)
                 kind = "q4-moe" if moe else "q4"
-                si = put(dk, q.packed)
-                put(dk + "#scale", q.scale)
+                si = put({dk: q.packed, dk + "#scale": q.scale})
                 meta = {"kind": kind, "k": q.k, "n": q.n, "shape": list(q.packed.shape), "scale_key": dk + "#scale",
                         "group_size": GROUP, "shard": si}
             else:
                 q = QWeight.quantize(t)
                 kn, sc = q.to_kn()
                 kind = "q8-moe" if moe else "q8"
-                si = put(dk, kn)
-                put(dk + "#scale", sc)
+                group = {dk: kn, dk + "#scale": sc}
+                if moe:
+                    group[dk + "#nk"] = q.wq
+                si = put(group)
                 meta = {"kind": kind, "k": q.k, "n": q.n, "shape": list(kn.shape), "scale_key": dk + "#scale", "shard": si}
                 if moe:
-                    put(dk + "#nk", q.wq)
                     meta["nk_key"] = dk + "#nk"
         else:
             kind = "dense"
-            si = put(dk, t)
+            si = put({dk: t})
             meta = {"kind": "dense", "shape": list(t.shape), "shard": si}
         kinds[kind] = kinds.get(kind, 0) + 1
         tensors[dk] = meta
+    flush()
     pat = "quant-w4a8-%05d-of-%05d.safetensors" if w4 else "quant-%05d-of-%05d.safetensors"
     files = []
-    for i, shard in enumerate(shards):
-        name = pat % (i + 1, len(shards))
-        save_file(shard, str(out / name))
+    for i, path in enumerate(tmp_files):
+        name = pat % (i + 1, len(tmp_files))
+        path.replace(out / name)
         files.append(name)
     for meta in tensors.values():
         meta["shard"] = files[meta["shard"]]
-    index = {"format": W4A8_FORMAT if w4 else FORMAT, "generated_by": "coffin_b200/tools/quant_disk.py",
+    index = {"format": W4A8_FORMAT if w4 else FORMAT, "generated_by": generated_by or "coffin_b200/tools/quant_disk.py",
              "source": str(src), "source_config_sha256": config_digest(src), "weight_dtype": weight_dtype,
              "act_dtype": "bfloat16",
              "scheme": ("group-128 symmetric int4: s = max|w|/7, round, clamp [-8, 7], code = q + 8, low nibble = even k"
                         if w4 else "per-output-column symmetric absmax: s = max|w|/127, round, clamp [-127, 127]; s floored at 1e-8"),
              "layout": "uint8 [ceil(K/2), N] + fp32 [ceil(K/128), N]" if w4 else "int8 [K, N] contiguous + fp32 [N]",
-             "prefixes": ["model.language_model.", "mtp.", "lm_head."], "vision": any(k.startswith("model.visual.") for k in sd),
+             "prefixes": ["model.language_model.", "mtp.", "lm_head."], "vision": has_visual,
              "files": files, "kinds": dict(sorted(kinds.items())),
              "totals": {"tensors": len(tensors), "bytes": sum((out / f).stat().st_size for f in files)},
              "tensors": tensors}

@@ -78,3 +78,73 @@ def test_oracle_chunked_and_incremental_equal_one_shot():
     o.forward(toks[:40], st2)
     st3 = st2.clone()
     assert torch.equal(o.forward(toks[40:50], st2), o.forward(toks[40:50], st3))
+
+
+def test_streaming_loader_plan_check_and_expert_parallel_reads(tmp_path):
+    """Shard index -> plan check without reading data -> shard-by-shard reads; an expert-parallel rank
+    reads only its expert range (fused stacks through ``get_slice``, per-expert files by name) and the MoE
+    module takes the pre-cut stack as it is; a checkpoint that does not match the plan is refused."""
+    import torch
+    from coffin_b200.models.qwen4exp.config import tiny_qwen4
+    from coffin_b200.models.qwen4exp.weights import (checkpoint_index, load_streaming, random_state_dict, tensor_plan,
+                                                    verify_plan)
+    from coffin_b200.weights.init import save_checkpoint
+    cfg = tiny_qwen4()
+    sd = random_state_dict(cfg, 0)
+    E = cfg.num_experts
+    for split in (False, True):
+        d = save_checkpoint(cfg, sd, tmp_path / f"ck{int(split)}", split_experts=split, shard_bytes=1 << 20)
+        idx = checkpoint_index(d)
+        assert len(set(idx.values())) > 1                       # really sharded
+        rep = verify_plan(cfg, d, idx)
+        assert rep == {"missing": [], "unexpected": [], "shape": []}
+        full = load_streaming(d)
+        assert set(full) == {k for k, _, _ in tensor_plan(cfg)}
+        for r in range(2):
+            part = load_streaming(d, ep=(r, 2))
+            assert part["__ep_shard__"] == (r, 2)
+            for k, v in sd.items():
+                if k.endswith(("experts.gate_up_proj", "experts.down_proj")):
+                    assert torch.equal(part[k], v[r * E // 2:(r + 1) * E // 2]), k
+                else:
+                    assert torch.equal(part[k], v), k
+    # a checkpoint of another geometry is refused before any data is read
+    other = tiny_qwen4(hidden_size=256)
+    assert verify_plan(other, d)["shape"]
+    import pytest
+    with pytest.raises(ValueError, match="tensor plan"):
+        load_streaming(d, cfg=other)
+
+
+def test_qwen4_quantiser_streams_and_round_trips(tmp_path):
+    """``tools/quant_disk_qwen4``: per-expert source files are fused per layer while streaming, the chosen
+    families are quantised (hyper-connection, PLE, router and embedding stay dense), the index has the
+    shared formats and the loader hands back containers whose dequantised values track the source."""
+    import torch
+    from coffin_b200.models.qwen4exp.config import tiny_qwen4
+    from coffin_b200.models.qwen4exp.weights import random_state_dict
+    from coffin_b200.tools.quant_disk_qwen4 import main as quantise
+    from coffin_b200.weights.init import save_checkpoint
+    from coffin_b200.weights.loader import load_checkpoint
+    from coffin_b200.weights.quant import QWeight, W4A8Weight
+    from coffin_b200.weights.quant_io import read_index
+    cfg = tiny_qwen4()
+    sd = random_state_dict(cfg, 0)
+    src = save_checkpoint(cfg, sd, tmp_path / "src", split_experts=True, shard_bytes=1 << 20)
+    for scheme, cls, tol in (("int8", QWeight, 0.02), ("w4a8", W4A8Weight, 0.2)):
+        out = tmp_path / scheme
+        assert quantise(["--model", str(src), "--out", str(out), "--scheme", scheme, "--shard-gb", "0.001"]) == 0
+        idx = read_index(out)
+        assert len(idx["files"]) > 1 and idx["generated_by"].endswith("quant_disk_qwen4.py")
+        back = load_checkpoint(out)
+        assert set(back) == set(sd)
+        n_q = 0
+        for k, v in back.items():
+            if isinstance(v, (QWeight, W4A8Weight)):
+                n_q += 1
+                assert isinstance(v, cls) and "hyper_connection" not in k and ".ple." not in k
+                assert (v.dequant() - sd[k]).abs().max() <= tol * sd[k].abs().max() + 1e-6, k
+            else:
+                assert torch.equal(v, sd[k]), k
+        assert n_q > 3 * cfg.num_hidden_layers
+    assert not list((tmp_path / "w4a8").glob("*.tmp"))
