@@ -77,6 +77,148 @@ __global__ void tp_pf_wait_kernel(const TpPfDev* d, unsigned seq) {
 }
 }  // namespace
 
+// ---------------------------------------------------------------------------------------------
+// One-shot all-reduce for the few rows of a decode bucket ([M <= 64, hidden]) in ONE kernel.  The
+// reduce-scatter / all-gather above crosses NVLink twice and takes three launches, which at ~160 KB is
+// all latency.  Here CTA m of every rank stores row m of its partial sums into a slot of every PEER's
+// inbox as {two bf16, sequence number} 8-byte pairs (data and flag travel together, so no fence, no
+// arrival counter and no flag round trip), then polls (bounded) the pairs the peers stored into its own
+// inbox, adds the world's rows in rank order plus the residual, and can finish with the RMSNorm the next
+// projection needs: all-reduce, residual add and norm are one launch, and the wait is one NVLink
+// crossing.  Slots alternate between two halves of the inbox with the sequence number: a rank can only
+// be one all-reduce ahead of a peer (it needs the peer's rows of the one in between), so the half it
+// writes is never one a peer is still reading.  Every rank adds the same values in the same order, so
+// the ranks' results are bit-identical.
+namespace {
+constexpr int kOsRows = 64;          // rows per slot
+
+// 16 bytes = two pairs = four bf16 + the sequence number twice
+__device__ __forceinline__ void os_st2(uint2* dst, unsigned d0, unsigned d1, unsigned s) {
+  asm volatile("st.volatile.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(dst), "r"(d0), "r"(s), "r"(d1), "r"(s) : "memory");
+}
+__device__ __forceinline__ uint4 os_ld2(const uint2* src) {
+  uint4 q;
+  asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(q.x), "=r"(q.y), "=r"(q.z), "=r"(q.w) : "l"(src) : "memory");
+  return q;
+}
+
+__global__ void __launch_bounds__(512) tp_os_allreduce_kernel(const TpPfDev* d, const bf16* src, int64_t lds,
+                                                              const bf16* residual, int64_t ldr, const float* gain,
+                                                              bf16* res_out, int64_t ldo, bf16* normed, int64_t ldn,
+                                                              float eps, unsigned seq) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  float* row = reinterpret_cast<float*>(smem_raw);   // [width]
+  __shared__ float red[32];
+  griddep_launch();
+  griddep_wait();
+  const bool counted = seq == 0;
+  const unsigned s = tp_pf_seq(d, seq);
+  const int W = d->width, world = d->world, me = d->rank, m = blockIdx.x;
+  const int64_t pairs_row = W >> 1;
+  // pair index of (half, source rank, row m)
+  auto slot = [&](int r) { return (((int64_t)(s & 1u) * world + r) * kOsRows + m) * pairs_row; };
+  // ---- push this rank's row to every peer
+  for (int c = threadIdx.x; c < (W >> 3); c += blockDim.x) {
+    const uint4 v = *reinterpret_cast<const uint4*>(src + (int64_t)m * lds + c * 8);
+    for (int p = 0; p < world; ++p) {
+      if (p == me) continue;
+      uint2* dst = reinterpret_cast<uint2*>(d->os_inbox[p]) + slot(me) + c * 4;
+      os_st2(dst, v.x, v.y, s);
+      os_st2(dst + 2, v.z, v.w, s);
+    }
+  }
+  // ---- gather the peers' rows from the own inbox, add in rank order
+  const uint2* in = reinterpret_cast<const uint2*>(d->os_inbox[me]);
+  const unsigned long long limit = d->wait_ns ? d->wait_ns : kTpWaitNs;
+  float ss = 0.f;
+  for (int c = threadIdx.x; c < (W >> 3); c += blockDim.x) {
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int r = 0; r < world; ++r) {
+      uint4 v;
+      if (r == me) {
+        v = *reinterpret_cast<const uint4*>(src + (int64_t)m * lds + c * 8);
+      } else {
+        const uint2* p = in + slot(r) + c * 4;
+        uint4 a = os_ld2(p), b = os_ld2(p + 2);
+        if (a.y != s || a.w != s || b.y != s || b.w != s) {
+          const unsigned long long t0 = tp_now_ns();
+          unsigned spins = 0;
+          bool ok = tp_status_set(d->status) != 0;      // an earlier wait already ran out: do not spin again
+          while (!ok) {
+            if ((++spins & 63u) == 0) {
+              if (tp_status_set(d->status)) break;
+              if (tp_now_ns() - t0 > limit) {
+                atomicCAS(d->status, 0, 32 + r);
+                break;
+              }
+            }
+            if (a.y != s || a.w != s) a = os_ld2(p);
+            if (b.y != s || b.w != s) b = os_ld2(p + 2);
+            ok = a.y == s && a.w == s && b.y == s && b.w == s;
+          }
+        }
+        v = make_uint4(a.x, a.z, b.x, b.z);
+      }
+      float f[8];
+      bf16x8_to_float(v, f);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[e] += f[e];
+    }
+    if (residual) {
+      float f[8];
+      bf16x8_to_float(*reinterpret_cast<const uint4*>(residual + (int64_t)m * ldr + c * 8), f);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[e] = __bfloat162float(__float2bfloat16(acc[e])) + f[e];   // the partial sum is a bf16 tensor in the unfused path
+    }
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[e] = __bfloat162float(__float2bfloat16(acc[e]));
+    if (res_out) *reinterpret_cast<uint4*>(res_out + (int64_t)m * ldo + c * 8) = float_to_bf16x8(acc);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) { row[c * 8 + e] = acc[e]; ss += acc[e] * acc[e]; }
+  }
+  if (gain) {
+    const float rstd = rsqrtf(block_sum(ss, red) / (float)W + eps);
+    for (int c = threadIdx.x; c < (W >> 3); c += blockDim.x) {
+      float f[8];
+      const float4 g0 = *reinterpret_cast<const float4*>(gain + c * 8);
+      const float4 g1 = *reinterpret_cast<const float4*>(gain + c * 8 + 4);
+      f[0] = row[c * 8 + 0] * (rstd * g0.x); f[1] = row[c * 8 + 1] * (rstd * g0.y);
+      f[2] = row[c * 8 + 2] * (rstd * g0.z); f[3] = row[c * 8 + 3] * (rstd * g0.w);
+      f[4] = row[c * 8 + 4] * (rstd * g1.x); f[5] = row[c * 8 + 5] * (rstd * g1.y);
+      f[6] = row[c * 8 + 6] * (rstd * g1.z); f[7] = row[c * 8 + 7] * (rstd * g1.w);
+      *reinterpret_cast<uint4*>(normed + (int64_t)m * ldn + c * 8) = float_to_bf16x8(f);
+    }
+  }
+  // the last CTA to finish marks the all-reduce complete (the next one takes "last completed + 1")
+  __syncthreads();
+  if (counted && threadIdx.x == 0) {
+    const unsigned prev = atomicAdd(d->arrive + 1, 1u);
+    if (prev == gridDim.x - 1) {
+      d->arrive[1] = 0;
+      *d->seq_dev = s;
+    }
+  }
+}
+}  // namespace
+
+CB_EXPORT int cb_tp_os_rows() { return kOsRows; }
+CB_EXPORT int cb_tp_os_allreduce(const void* desc, const void* src, int64_t lds, const void* residual, int64_t ldr,
+                                 const void* gain, void* res_out, int64_t ldo, void* normed, int64_t ldn, int64_t M,
+                                 int64_t width, float eps, int64_t seq, void* stream) {
+  if (!desc || !src || M < 1 || M > kOsRows || lds % 8 || width % 8 || width * 4 > 200 * 1024) return CB_ERR_ARG;
+  if ((gain != nullptr) != (normed != nullptr) || (!res_out && !normed)) return CB_ERR_ARG;
+  const size_t smem = (size_t)width * 4;
+  if (smem + 1024 > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(tp_os_allreduce_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+  }
+  int threads = (int)((width / 8 + 31) / 32 * 32);
+  threads = threads > 512 ? 512 : threads;
+  return (int)cb_launch(tp_os_allreduce_kernel, dim3((unsigned)M), dim3(threads), smem, (cudaStream_t)stream,
+                        (const TpPfDev*)desc, (const bf16*)src, lds, (const bf16*)residual, ldr, (const float*)gain,
+                        (bf16*)res_out, ldo, (bf16*)normed, ldn, eps, (unsigned)seq);
+}
+
 CB_EXPORT int cb_tp_pf_scatter(const void* desc, const void* src, int64_t lds, int64_t T, int64_t seq, void* stream) {
   if (!desc || !src || T < 1 || lds % 8) return CB_ERR_ARG;
   return (int)cb_launch(tp_pf_scatter_kernel, dim3(148), dim3(256), 0, (cudaStream_t)stream, (const TpPfDev*)desc,

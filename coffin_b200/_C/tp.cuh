@@ -181,6 +181,7 @@ struct TpPfDev {
   int* status;
   unsigned long long wait_ns;     // limit of a device-side wait (0: kTpWaitNs)
   unsigned* seq_dev;              // local: sequence number of the last completed all-reduce
+  bf16* os_inbox[kTpMaxWorld];    // rank p's one-shot inbox: [2 halves][source rank][64 rows][width] (comm.cu)
 };
 
 // Sequence number of the all-reduce in progress.  The kernels are passed 0 and take "last completed

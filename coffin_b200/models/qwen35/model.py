@@ -570,9 +570,14 @@ class Qwen35Model:
         with NCCL, a view of the communicator's result buffer otherwise)."""
         if self.tp is not None and self.tp.pf_rows and t.shape[0] <= self.tp.pf_rows:
             from ...engine import debug
+            from ...parallel.tp import OS_ROWS
             end = debug.ep_span()
-            self.tp.scatter(t)
-            out = self.tp.finish_reduce()
+            if t.shape[0] <= OS_ROWS:           # a decode bucket: one NVLink crossing, two launches
+                out = torch.empty_like(t)
+                self.tp.oneshot(t, res_out=out)
+            else:
+                self.tp.scatter(t)
+                out = self.tp.finish_reduce()
             if end is not None:
                 end.record()
             return out
@@ -777,7 +782,12 @@ class Qwen35Model:
                               b["block_table"], self.kpool[j], self.vpool[j], b["part_o"], b["part_ml"], b["tickets"], act,
                               nh=c.num_attention_heads, nkv=c.num_key_value_heads, hd=c.head_dim,
                               rot=c.rotary_dim, nsplit=b["nsplit"], eps=self.eps, **self._kvs(j))
-            if tpw:
+            if tpw and self.tp.pf_rows:
+                # K-split GEMM, then the one-shot all-reduce whose second kernel also adds the residual and
+                # applies the post-attention norm
+                self._gemm(act, lw.w_out, out=b["part"])
+                self.tp.oneshot(b["part"], residual=res, gain=lw.post_gain, res_out=res, normed=normed, eps=self.eps)
+            elif tpw:
                 part = self._row_parallel(act, lw.w_out, b["part"])
                 K.rmsnorm(res, lw.post_gain, self.eps, out=normed, add=part, res_out=res)
             else:
@@ -788,7 +798,10 @@ class Qwen35Model:
                 K._count()
             else:
                 self._gemm(normed, lw.w_gu, out=b["gu"])
-                if tpw:
+                if tpw and self.tp.pf_rows:
+                    self._gemm(b["gu"], lw.w_down, out=b["part"], swiglu_in=True)
+                    self.tp.oneshot(b["part"], residual=res, res_out=res)
+                elif tpw:
                     res.add_(self._row_parallel(b["gu"], lw.w_down, b["part"], swiglu_in=True))
                     K._count()
                 else:

@@ -55,7 +55,7 @@ class MoEWeights:
             raise ValueError(f"num_experts={E} is not divisible by expert-parallel world {ep_world}")
         per = E // ep_world
         e_lo, e_hi = ep_rank * per, (ep_rank + 1) * per
-        from ...weights.quant import W4A8Weight
+        from ...weights.quant import QWeight, W4A8Weight
         from .model import QW4
         # a state dict read with an expert-parallel filter already holds only this rank's experts
         presliced = tuple(sd.get("__ep_shard__", ())) == (ep_rank, ep_world) and ep_world > 1
@@ -66,12 +66,27 @@ class MoEWeights:
             if isinstance(t, W4A8Weight):
                 part = W4A8Weight(t.packed[s_lo:s_hi], t.scale[s_lo:s_hi], t.k, t.group_size)
                 return QW4(*part.to(dev).to_nk())
-            t = t[s_lo:s_hi].to(dev, bf)
+            if isinstance(t, QWeight):
+                # int8 expert stacks are expanded once at load: the grouped expert kernels read bf16 or int4
+                t = (t.wq[s_lo:s_hi].to(dev).float() * t.scale[s_lo:s_hi].to(dev).float()[..., None]).to(bf)
+                s0, s1 = 0, t.shape[0]
+            else:
+                s0, s1 = s_lo, s_hi
+            t = t[s0:s1].to(dev, bf)
             if quant == "w4a8" and t.shape[-1] % 128 == 0:
                 return QW4.quantize(t)
             return t.contiguous()
 
         gu, dn = experts(gu), experts(dn)
+        if isinstance(gu, QW4) != isinstance(dn, QW4):
+            # one stack cannot be stored as int4 (its reduction length is not a whole number of groups):
+            # both stay bf16, the expert kernels take one storage for the pair
+            def expand(st):
+                if not isinstance(st, QW4):
+                    return st
+                E_, N_, half = st.wq.shape
+                return K.w4_dequant(st.wq.reshape(E_ * N_, half), st.scale.reshape(E_ * N_, -1)).reshape(E_, N_, half * 2)
+            gu, dn = expand(gu), expand(dn)
         sh_gu = sh_down = None
         if has_shared:
             from ...weights.quant import QWeight

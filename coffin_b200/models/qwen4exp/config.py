@@ -174,6 +174,9 @@ class Qwen4Config:
         for one in self.ple_layer_ids:
             if not 1 <= one <= self.num_hidden_layers or self.layer_types[one - 1] != LINEAR:
                 raise ValueError(f"PLE layer {one} must be an existing linear_attention layer")
+        if self.mtp_num_hidden_layers not in (0, 1):
+            # each draft step would use another layer; the head drives exactly one
+            raise ValueError(f"the draft head has exactly one layer, the config declares {self.mtp_num_hidden_layers}")
         if self.ple_layer_ids and self.ple_embed_dim % self.ngram_heads:
             raise ValueError("ple_embed_dim must divide by the number of n-gram heads")
 

@@ -21,7 +21,8 @@ Execution model (eager; the family's reference runs eager too, ``models/qwen4exp
 
 The class offers the model interface the engine drives (``prefill`` / ``set_rows`` / ``decode`` /
 state snapshots / ``copy_block``), so the block manager, radix cache and scheduler are shared with
-the Qwen3.5 family.  Speculative verification is not offered for this family.
+the Qwen3.5 family.  Speculative decoding: ``verify_batch`` / ``commit_batch`` (what the engine's drafter
+path drives) and the family's own draft head (``mtp_run``, ``spec_generate``).
 Structure reference: ``models/qwen4exp/blocks.py:52-238``, ``model.py:250-470``, ``engine.py:360-897``.
 """
 from __future__ import annotations
@@ -34,7 +35,7 @@ from ...ops import kernels as K
 from ...oracle import ops as O
 from ..qwen35.model import QW, QW4
 from ..qwen35.moe import MoEWeights
-from .config import LINEAR, Qwen4Config
+from .config import INDEXED, LINEAR, Qwen4Config
 from .ngram import NGramHasher, NGramTable
 
 LM = "model.language_model."
@@ -98,7 +99,7 @@ class Qwen4ExpModel:
     def __init__(self, cfg: Qwen4Config, sd: dict[str, torch.Tensor], device: str | torch.device = "cuda",
                  max_seq: int = 4096, num_slots: int = 2, num_blocks: int | None = None, max_chunk: int = 2048,
                  pdl: bool = True, ngram_device_budget: int = 120 << 30, quant: str = "none", tp=None,
-                 ep_rank: int = 0, ep_world: int = 1, **_unused) -> None:
+                 ep_rank: int = 0, ep_world: int = 1, with_mtp: bool = False, **_unused) -> None:
         """``quant``: ``int8`` / ``w4a8`` storage of the mixer projections, the experts and the head (a
         pre-quantised state dict brings its own containers).  ``ep_world`` > 1: the routed experts are split
         by range over the ranks of the communicator ``tp``; everything else is replicated."""
@@ -174,8 +175,7 @@ class Qwen4ExpModel:
         self.lin_ids = {li: j for j, li in enumerate(c.linear_layers)}
         self.full_ids = {li: j for j, li in enumerate(c.full_layers)}
         self.ple_ids: dict[int, int] = {}
-        for li, kind in enumerate(c.layer_types):
-            p = f"{LM}layers.{li}."
+        def make_layer(p: str, kind: str, ple_j):
             L = _Layer()
             L.kind = kind
             L.h_attn = _Hyper(sd, p + "attn_hyper_connection.", dev)
@@ -207,7 +207,7 @@ class Qwen4ExpModel:
                 L.iqg, L.ikg = gain(q + "indexer.q_layernorm.weight"), gain(q + "indexer.k_layernorm.weight")
             L.moe = MoEWeights.from_state_dict(c, sd, p + "mlp.", dev, ep_rank, ep_world, quant=quant)
             L.ple = None
-            j = c.ple_index(li)
+            j = ple_j
             if j is not None:
                 q = p + "ple."
                 P = _Layer()
@@ -218,8 +218,24 @@ class Qwen4ExpModel:
                 P.g_key, P.g_query, P.g_conv = gain(q + "norm_key.weight"), gain(q + "norm_query.weight"), gain(q + "norm_conv.weight")
                 P.conv_w = sd[q + "conv1d.weight"].to(dev, torch.float32).reshape(c.hc_hidden, -1).contiguous()
                 L.ple = P
+            return L
+
+        for li, kind in enumerate(c.layer_types):
+            L = make_layer(f"{LM}layers.{li}.", kind, c.ple_index(li))
+            if L.ple is not None:
                 self.ple_ids[li] = len(self.ple_ids)
             self.layers.append(L)
+        # ---- draft head (MTP): one QSA + MoE layer of its own, two [H, H] projections, a final mixer
+        self.mtp = None
+        if with_mtp:
+            if not c.mtp_num_hidden_layers or "mtp.fc_embedding.weight" not in sd:
+                raise ValueError("with_mtp needs a checkpoint that carries the draft head (mtp_num_hidden_layers = 1)")
+            D = _Layer()
+            D.layer = make_layer("mtp.layers.0.", INDEXED, None)
+            D.fc_e, D.fc_h = quantise(w("mtp.fc_embedding.weight")), quantise(w("mtp.fc_hidden.weight"))
+            D.g_e, D.g_h = gain("mtp.pre_fc_norm_embedding.weight"), gain("mtp.pre_fc_norm_hidden.weight")
+            D.final = _Hyper(sd, "mtp.hyper_connection_mixer.", dev, write_gate=False)
+            self.mtp = D
         cos, sin = O.rope_tables(c.rotary_dim, c.rope_theta, self.max_seq + 64)
         self.cos, self.sin = cos.to(dev).contiguous(), sin.to(dev).contiguous()
         # ---- sequence state --------------------------------------------------------------------
@@ -228,11 +244,13 @@ class Qwen4ExpModel:
                                  c.linear_value_head_dim, dtype=torch.float32, device=dev)
         self.ring = torch.zeros(nl, self.num_slots, K.RING, c.lin_conv_dim, dtype=bf, device=dev)
         rows = self.num_blocks * K.BLOCK
-        self.kpool = torch.zeros(nf, rows, c.num_key_value_heads, c.head_dim, dtype=bf, device=dev)
+        npool = nf + (1 if self.mtp is not None else 0)       # the draft head pages its own K / V / index keys (last pool)
+        self.mtp_pool = nf
+        self.kpool = torch.zeros(npool, rows, c.num_key_value_heads, c.head_dim, dtype=bf, device=dev)
         self.vpool = torch.zeros_like(self.kpool)
-        self.ipool = torch.zeros(nf, rows, c.indexer_head_dim, dtype=bf, device=dev)
+        self.ipool = torch.zeros(npool, rows, c.indexer_head_dim, dtype=bf, device=dev)
         self.per_page = K.BLOCK // c.indexer_compress_ratio
-        self.bkpool = torch.zeros(nf, self.num_blocks * self.per_page, c.indexer_head_dim, dtype=torch.float32, device=dev)
+        self.bkpool = torch.zeros(npool, self.num_blocks * self.per_page, c.indexer_head_dim, dtype=torch.float32, device=dev)
         self.ple_hist = torch.zeros(max(npl, 1), self.num_slots, c.ple_conv_state_len, c.hc_hidden, dtype=torch.float32, device=dev)
         self.ple_ctx: list[list[list[int]]] = [[self._fresh_ctx() for _ in range(self.num_slots)] for _ in range(max(npl, 1))]
         self.max_sel_blocks = (self.max_seq + c.indexer_compress_ratio - 1) // c.indexer_compress_ratio
@@ -241,6 +259,8 @@ class Qwen4ExpModel:
         self._staged: dict | None = None
         self.last_prenorm = None
         self.last_hidden = None
+        self.last_lanes = None
+        self._verify: dict | None = None
 
     # ------------------------------------------------------------------ sizes / bookkeeping
     def _fresh_ctx(self) -> list[int]:
@@ -311,10 +331,11 @@ class Qwen4ExpModel:
         return K.sample(logits.contiguous(), t, u)
 
     # ------------------------------------------------------------------ workspaces
-    def _work(self, T: int) -> dict:
+    def _work(self, T: int, tag: str = "") -> dict:
         """Buffers for a pass over ``T`` rows (kept per size; a prefill chunk and a decode bucket
-        never share them)."""
-        ws = self._ws.get(T)
+        never share them; ``tag`` separates the draft head's buffers from the main model's)."""
+        key = (T, tag)
+        ws = self._ws.get(key)
         if ws is None:
             c, dev, bf = self.cfg, self.device, torch.bfloat16
             H, W = c.hidden_size, c.hc_hidden
@@ -344,15 +365,23 @@ class Qwen4ExpModel:
                 ws["part_o"] = torch.zeros(T, c.num_attention_heads, nsplit, c.head_dim, dtype=torch.float32, device=dev)
                 ws["part_ml"] = torch.zeros(T, c.num_attention_heads, nsplit, 2, dtype=torch.float32, device=dev)
                 ws["tickets"] = torch.zeros(T, c.num_key_value_heads, dtype=torch.int32, device=dev)
-            if self.lin_ids and T > 1:
+            if self.lin_ids and T > 8:
                 n = K.gdn_prefill_scratch_floats(T, c.linear_num_key_heads, c.linear_num_value_heads,
                                                  c.linear_key_head_dim, c.linear_value_head_dim)
                 ws["gdn"] = torch.empty(n, dtype=torch.float32, device=dev)
-            if T > 8:                   # keep at most two chunk-sized workspaces
-                big = [k for k in self._ws if k > 8]
+            if T <= 8 and self.lin_ids and not tag:
+                # verify pass: per-token rank-one updates of every delta-net layer, n-gram conv windows
+                ws["record"] = torch.zeros(len(self.lin_ids), 1, T, c.linear_num_value_heads,
+                                           c.linear_key_head_dim + c.linear_value_head_dim + 1, dtype=torch.float32, device=dev)
+                ws["one_slot"] = torch.zeros(1, dtype=torch.int32, device=dev)
+                ws["one_pos"] = torch.zeros(1, dtype=torch.int32, device=dev)
+                ws["steps"] = torch.zeros(1, dtype=torch.int32, device=dev)
+            ws["ones"] = torch.ones(T, c.hc_count, dtype=torch.float32, device=dev)
+            if T > 8:                   # keep at most two chunk-sized workspaces per tag
+                big = [k for k in self._ws if k[0] > 8 and k[1] == tag]
                 for k in big[:-1]:
                     del self._ws[k]
-            self._ws[T] = ws
+            self._ws[key] = ws
         return ws
 
     def _linear(self, W, x: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
@@ -392,7 +421,13 @@ class Qwen4ExpModel:
         if self.ep_world == 1:
             return t
         if self.tp is not None and self.tp.pf_rows and t.shape[0] <= self.tp.pf_rows:
-            self.tp.scatter(t.contiguous())
+            from ...parallel.tp import OS_ROWS
+            t = t.contiguous()
+            if t.shape[0] <= OS_ROWS:
+                out = torch.empty_like(t)
+                self.tp.oneshot(t, res_out=out)
+                return out
+            self.tp.scatter(t)
             return self.tp.finish_reduce()
         import torch.distributed as dist
         dist.all_reduce(t)
@@ -425,9 +460,11 @@ class Qwen4ExpModel:
         return ws["mixed"], inject
 
     # ------------------------------------------------------------------ PLE
-    def _ple(self, L, j: int, stream: torch.Tensor, tokens: list[int], slot: int) -> torch.Tensor:
+    def _ple(self, L, j: int, stream: torch.Tensor, tokens: list[int], slot: int, record: dict | None = None) -> torch.Tensor:
         """n-gram injection for consecutive tokens of one sequence: returns the fp32 term ``[T, hc*H]``
-        to add to the stream and advances the slot's n-gram context and conv history."""
+        to add to the stream and advances the slot's n-gram context and conv history.  With ``record``
+        (a verify pass) the slot is left untouched and the window + context are kept so that ``commit``
+        can advance by the accepted prefix."""
         c, P = self.cfg, L.ple
         hc, H = c.hc_count, c.hidden_size
         ctx = self.ple_ctx[j][slot]
@@ -452,13 +489,19 @@ class Qwen4ExpModel:
         conv = torch.zeros_like(gvn)
         for tap in range(k):
             conv += seq[tap * dil:tap * dil + T] * P.conv_w[:, tap]
-        hist.copy_(seq[seq.shape[0] - span:])
-        self.ple_ctx[j][slot] = (ctx + [int(t) for t in tokens])[-c.ple_context_len:]
+        if record is not None:
+            record[j] = (seq, list(ctx), [int(t) for t in tokens])
+        else:
+            hist.copy_(seq[seq.shape[0] - span:])
+            self.ple_ctx[j][slot] = (ctx + [int(t) for t in tokens])[-c.ple_context_len:]
         K._count(12)
         return gv + torch.nn.functional.silu(conv)
 
     # ------------------------------------------------------------------ mixers
-    def _gdn(self, L, li: int, ws: dict, T: int, mixed, out, *, slot=None, pos0=None, slots=None, positions=None):
+    def _gdn(self, L, li: int, ws: dict, T: int, mixed, out, *, slot=None, pos0=None, slots=None, positions=None,
+             verify: bool = False):
+        """``verify``: the ``T`` rows are consecutive tokens of one sequence scored without touching its
+        state - the per-token updates are recorded for ``commit``."""
         c = self.cfg
         j = self.lin_ids[li]
         proj = ws["proj"][:, :L.w_in.shape[0]]
@@ -466,7 +509,10 @@ class Qwen4ExpModel:
         act = ws["act"][:, :c.lin_vdim]
         kw = dict(nk=c.linear_num_key_heads, nv=c.linear_num_value_heads, dk=c.linear_key_head_dim,
                   dv=c.linear_value_head_dim, eps=self.eps, gate_sigmoid=self.gate_sigmoid)
-        if slots is not None:
+        if verify:
+            K.gdn_decode(proj, L.conv_w, L.A_log, L.dt_bias, L.norm_w, self.ring[j], self.state[j], ws["one_slot"],
+                         ws["one_pos"], act, ntok=T, record=ws["record"][j], write_state=False, **kw)
+        elif slots is not None:
             K.gdn_decode(proj, L.conv_w, L.A_log, L.dt_bias, L.norm_w, self.ring[j], self.state[j], slots, positions, act, **kw)
         else:
             K.gdn_prefill(proj, L.conv_w, L.A_log, L.dt_bias, L.norm_w, self.ring[j, slot], self.state[j, slot],
@@ -474,11 +520,14 @@ class Qwen4ExpModel:
         self._linear(L.w_out, act, out)
 
     def _qsa(self, L, li: int, ws: dict, T: int, mixed, out, *, block_tables, positions_host: list[int],
-             shared_table: bool):
+             shared_table: bool, pool: int | None = None, keep_selection: bool = False):
         """``positions_host[t]`` is the position of row ``t``; with ``shared_table`` all rows belong to
-        one sequence (a prefill chunk) whose pages are ``block_tables`` (1-D)."""
+        one sequence (a prefill chunk) whose pages are ``block_tables`` (1-D).  ``pool``: which set of
+        paged pools the layer owns (default: the layer's own; the draft head has the last one).
+        ``keep_selection`` (decode rows): attend through the blocks selected by the previous call on
+        this workspace instead of selecting again."""
         c = self.cfg
-        j = self.full_ids[li]
+        j = self.full_ids[li] if pool is None else pool
         nh, nkv, hd, rot = c.num_attention_heads, c.num_key_value_heads, c.head_dim, c.rotary_dim
         ni, di, ratio = c.indexer_n_heads, c.indexer_head_dim, c.indexer_compress_ratio
         proj = ws["proj"][:, :L.w_in.shape[0]]
@@ -500,8 +549,9 @@ class Qwen4ExpModel:
                                      p // ratio, p // ratio + 1, ratio=ratio, di=di, rot=rot, eps=self.eps)
         act = ws["act"][:, :nh * hd]
         if T <= 8 and not shared_table:
-            K.qsa_select(ws["iq"], self.bkpool[j], block_tables, pos, ws["scores"], ws["sel"], ws["nsel"],
-                         ni=ni, di=di, ratio=ratio, topk=c.block_topk, full_factor=c.full_select_factor)
+            if not keep_selection:
+                K.qsa_select(ws["iq"], self.bkpool[j], block_tables, pos, ws["scores"], ws["sel"], ws["nsel"],
+                             ni=ni, di=di, ratio=ratio, topk=c.block_topk, full_factor=c.full_select_factor)
             K.attn_sparse(ws["q"], proj, pos, block_tables, self.kpool[j], self.vpool[j], ws["sel"], ws["nsel"],
                           ws["part_o"], ws["part_ml"], ws["tickets"], act, nh=nh, nkv=nkv, hd=hd, ratio=ratio,
                           nsplit=ws["nsplit"])
@@ -519,7 +569,7 @@ class Qwen4ExpModel:
 
     # ------------------------------------------------------------------ layer stack
     def _run(self, ws: dict, T: int, *, tokens_host, slot=None, pos0=None, block_table=None, slots=None,
-             positions=None, positions_host=None, block_tables=None, row_slots=None) -> torch.Tensor:
+             positions=None, positions_host=None, block_tables=None, row_slots=None, verify: dict | None = None) -> torch.Tensor:
         """All layers over the ``T`` rows staged in ``ws['stream']``.  Prefill: one sequence
         (``slot``, ``pos0``, ``block_table``).  Decode: one token of each of ``T`` sequences
         (``slots`` / ``positions`` device tensors, ``block_tables [T, pages]``).  Returns the mixed
@@ -540,7 +590,7 @@ class Qwen4ExpModel:
                         if row_slots[r] >= 0:
                             stream[r:r + 1].add_(self._ple(L, j, stream[r:r + 1], [tokens_host[r]], row_slots[r]).to(stream.dtype))
                 else:
-                    stream.add_(self._ple(L, j, stream, tokens_host, slot).to(stream.dtype))
+                    stream.add_(self._ple(L, j, stream, tokens_host, slot, record=verify).to(stream.dtype))
             inj_a, inj_b = ws["inject"]
             mixed, inject = self._hyper_read(L.h_attn, ws, T, pending, inj_a)
             out = ws["out"][0]
@@ -548,7 +598,7 @@ class Qwen4ExpModel:
                 if decode:
                     self._gdn(L, li, ws, T, mixed, out, slots=slots, positions=positions)
                 else:
-                    self._gdn(L, li, ws, T, mixed, out, slot=slot, pos0=pos0)
+                    self._gdn(L, li, ws, T, mixed, out, slot=slot, pos0=pos0, verify=verify is not None)
             else:
                 if decode:
                     self._qsa(L, li, ws, T, mixed, out, block_tables=block_tables, positions_host=positions_host,
@@ -561,14 +611,15 @@ class Qwen4ExpModel:
             out2.copy_(L.moe.apply(mixed.contiguous(), self))
             pending = (out2, inject2)
         mixed, _ = self._hyper_read(self.final, ws, T, pending, None)
-        return mixed
+        return mixed                      # ws["stream"] now holds the un-collapsed lanes (last write-back applied)
 
     # ------------------------------------------------------------------ engine interface
     @torch.no_grad()
     def prefill(self, tokens: torch.Tensor, pos0: int, slot: int, block_table: torch.Tensor, embeds=None,
-                cos_sin=None, want_logits: bool = True, want_hidden: bool = False):
+                cos_sin=None, want_logits: bool = True, want_hidden: bool = False, want_lanes: bool = False):
         """One chunk of one sequence at positions ``pos0 .. pos0 + T - 1``; returns the fp32 logits of
-        the last token (or ``None``)."""
+        the last token (or ``None``).  ``want_lanes``: keep the un-collapsed lanes of every row in
+        ``last_lanes`` (what the draft head pairs with the following token)."""
         if cos_sin is not None:
             raise NotImplementedError("multi-axis rotary positions are not wired for this family")
         c = self.cfg
@@ -577,10 +628,14 @@ class Qwen4ExpModel:
         if T <= 8:                      # a short tail runs through the decode path (same kernels, fewer buffers)
             rows = [int(t) for t in tokens.tolist()]
             out = None
+            kept = []
             for i, tok in enumerate(rows):
                 self.set_rows(1, [tok], [pos0 + i], [slot], [block_table.tolist()])
                 _, logits = self.decode(1, want_logits=want_logits and i == T - 1)
                 out = logits[0] if logits is not None else None
+                if want_lanes:
+                    kept.append(self._work(1)["stream"].clone())
+            self.last_lanes = torch.cat(kept) if want_lanes else None
             return out
         ws = self._work(T)
         e = self._embed(tokens) if embeds is None else embeds.to(torch.bfloat16)
@@ -591,6 +646,7 @@ class Qwen4ExpModel:
         mixed = self._run(ws, T, tokens_host=[int(t) for t in tokens.tolist()] if self.ple_ids else None,
                           slot=slot, pos0=pos0, block_table=block_table)
         self.last_hidden = mixed if want_hidden else None
+        self.last_lanes = ws["stream"].clone() if want_lanes else None
         if not want_logits:
             return None
         logits = torch.empty(1, c.vocab_size, dtype=torch.float32, device=self.device)
@@ -638,7 +694,200 @@ class Qwen4ExpModel:
         self.set_rows(M, nxt, [p + 1 for p in st["positions"]], st["slots"],
                       [row.tolist() for row in st["bt"].cpu()])
 
-    def verify(self, *a, **k):
-        raise NotImplementedError("speculative verification is not offered for the Qwen4-exp family")
+    # ------------------------------------------------------------------ speculative decoding
+    VERIFY_WIDTHS = (2, 4, 8)
 
-    commit = verify
+    def _stage_rows(self, ws: dict, T: int, tokens, pos0: int, block_table: torch.Tensor, embeds=None) -> None:
+        """Stage ``T`` consecutive rows of one sequence: embeddings into every lane, positions, KV slots."""
+        c = self.cfg
+        tok = torch.as_tensor(list(tokens), dtype=torch.int64).to(self.device) if not isinstance(tokens, torch.Tensor) else tokens
+        e = self._embed(tok) if embeds is None else embeds
+        ws["stream"].copy_(e.repeat(1, c.hc_count))
+        pos = torch.arange(pos0, pos0 + T, dtype=torch.int64, device=self.device)
+        ws["pos"].copy_(pos)
+        ws["kv_slot"].copy_(block_table.to(torch.int64)[pos // K.BLOCK] * K.BLOCK + pos % K.BLOCK)
+
+    @torch.no_grad()
+    def verify_batch(self, rows: list[tuple]) -> torch.Tensor:
+        """Score ``C`` (2..8) consecutive tokens - the last sampled token followed by drafts - of each
+        row ``(tokens[C], pos0, slot, block_table, rope_delta)``; returns logits ``[n, C, vocab]``.
+        K / V / index keys of all positions are written (rejected ones are overwritten later), the
+        delta-net states and the n-gram windows are left untouched: the per-token updates are recorded
+        and ``commit_batch`` applies each row's accepted prefix.  Each row is one pass (the rows of this
+        family do not share a forward); the un-collapsed lanes of every scored position are kept for the
+        draft head (``verify_lanes``)."""
+        c = self.cfg
+        C = len(rows[0][0])
+        if not 2 <= C <= 8 or any(len(r[0]) != C for r in rows):
+            raise ValueError("a verify pass scores 2..8 tokens, the same number for every row")
+        out = torch.empty(len(rows), C, c.vocab_size, dtype=torch.float32, device=self.device)
+        self._verify = {"C": C, "rows": []}
+        for i, (tokens, pos0, slot, table, _delta) in enumerate(rows):
+            if pos0 + C > self.max_seq:
+                raise ValueError(f"positions {pos0}..{pos0 + C - 1} exceed max_seq {self.max_seq}")
+            bt = table if isinstance(table, torch.Tensor) else torch.tensor(list(table), dtype=torch.int32, device=self.device)
+            ws = self._work(C, tag=f"verify{i}" if i else "")
+            if "record" not in ws:
+                first = self._work(C)
+                for k_ in ("record", "one_slot", "one_pos", "steps"):
+                    ws[k_] = torch.zeros_like(first[k_])
+            self._stage_rows(ws, C, tokens, pos0, bt)
+            ws["one_slot"].fill_(slot)
+            ws["one_pos"].fill_(pos0)
+            rec: dict = {}
+            mixed = self._run(ws, C, tokens_host=[int(t) for t in tokens], slot=slot, pos0=pos0, block_table=bt, verify=rec)
+            self._linear(self.lm_head, mixed.contiguous(), out[i])
+            self._verify["rows"].append({"ws": ws, "ple": rec, "slot": slot})
+        return out
+
+    def commit_batch(self, slots: list[int], steps: list[int]) -> None:
+        """Advance row ``i`` of the last ``verify_batch`` by its first ``steps[i]`` tokens."""
+        c, v = self.cfg, self._verify
+        assert v is not None and len(slots) == len(steps) == len(v["rows"])
+        span = c.ple_conv_state_len
+        for row, slot, n in zip(v["rows"], slots, steps):
+            assert slot == row["slot"] and 0 <= n <= v["C"]
+            ws = row["ws"]
+            ws["steps"].fill_(n)
+            for li, j in self.lin_ids.items():
+                K.gdn_commit(self.state[j], ws["record"][j], ws["one_slot"], ws["steps"], nv=c.linear_num_value_heads,
+                             dk=c.linear_key_head_dim, dv=c.linear_value_head_dim)
+            for j, (seq, ctx, toks) in row["ple"].items():
+                self.ple_hist[j, slot].copy_(seq[n:n + span])
+                self.ple_ctx[j][slot] = (ctx + toks[:n])[-c.ple_context_len:]
+
+    def verify(self, tokens: list[int], pos0: int, slot: int, block_table: torch.Tensor, rope_delta: int = 0) -> torch.Tensor:
+        return self.verify_batch([(tokens, pos0, slot, block_table, rope_delta)])[0]
+
+    def commit(self, slot: int, steps: int) -> None:
+        self.commit_batch([slot], [steps])
+
+    def verify_lanes(self, row: int = 0) -> torch.Tensor:
+        """Un-collapsed lanes ``[C, hc*H]`` of the positions scored by row ``row`` of the last verify pass."""
+        return self._verify["rows"][row]["ws"]["stream"]
+
+    # ------------------------------------------------------------------ draft head (MTP)
+    @torch.no_grad()
+    def mtp_run(self, next_tokens, lanes: torch.Tensor, pos0: int, block_table: torch.Tensor, add_embedding: bool = True,
+                keep_selection: bool = False):
+        """The draft head over ``T`` rows at positions ``pos0 ..`` of one sequence: row ``t`` pairs the
+        lanes of position ``pos0 + t`` (``lanes [T, hc*H]``: the main model's, or the head's own ``multi``
+        on a chained draft step) with the token that follows that position, and predicts the one after.
+        Returns ``(sample [T, H], multi [T, hc*H])`` - views of the head's workspace, valid until its next
+        call with the same ``T``.  The head's K / V / index keys live in its own paged pools under the
+        sequence's block table, so truncating or sharing the sequence's pages carries the head along.
+        A single row runs the decode kernels (block selection + split-KV sparse attention; with
+        ``keep_selection`` the previous call's blocks are reused, the reference's ``DraftIndexPlan``,
+        ``models/qwen4exp/mtp.py:63-128``); more rows run the prefill kernels.  Reference: ``mtp.py:146-330``."""
+        D, c = self.mtp, self.cfg
+        if D is None:
+            raise RuntimeError("this model was built without the draft head (with_mtp=True)")
+        H, hc = c.hidden_size, c.hc_count
+        T = lanes.shape[0]
+        ws = self._work(T, tag="mtp")
+        tok = torch.as_tensor(list(next_tokens), dtype=torch.int64).to(self.device) if not isinstance(next_tokens, torch.Tensor) else next_tokens
+        pos = torch.arange(pos0, pos0 + T, dtype=torch.int64, device=self.device)
+        ws["pos"].copy_(pos)
+        ws["kv_slot"].copy_(block_table.to(torch.int64)[pos // K.BLOCK] * K.BLOCK + pos % K.BLOCK)
+        if "bo" not in ws:
+            ws["bo"] = torch.empty(T, H, dtype=torch.bfloat16, device=self.device)
+            ws["en"] = torch.empty(T, H, dtype=torch.bfloat16, device=self.device)
+        K.rmsnorm(self._embed(tok), D.g_e, self.eps, out=ws["en"])
+        self._linear(D.fc_e, ws["en"], ws["bo"])
+        K.rmsnorm(lanes.contiguous(), D.g_h, self.eps, out=ws["normed"])              # ONE norm over all hc*H channels
+        self._linear(D.fc_h, ws["normed"].view(T * hc, H), ws["stream"].view(T * hc, H))
+        pending = (ws["bo"], ws["ones"]) if add_embedding else None       # unit write gate: the embedding enters every lane
+        L = D.layer
+        inj_a, inj_b = ws["inject"]
+        mixed, inject = self._hyper_read(L.h_attn, ws, T, pending, inj_a)
+        out = ws["out"][0]
+        single = T == 1
+        self._qsa(L, -1, ws, T, mixed, out, block_tables=block_table[None] if single else block_table,
+                  positions_host=list(range(pos0, pos0 + T)), shared_table=not single, pool=self.mtp_pool,
+                  keep_selection=keep_selection and single)
+        mixed, inject2 = self._hyper_read(L.h_mlp, ws, T, (out, inject), inj_b)
+        out2 = ws["out"][1]
+        out2.copy_(L.moe.apply(mixed.contiguous(), self))
+        sample, _ = self._hyper_read(D.final, ws, T, (out2, inject2), None)
+        return sample, ws["stream"]
+
+    def head_logits(self, hidden: torch.Tensor) -> torch.Tensor:
+        out = torch.empty(hidden.shape[0], self.cfg.vocab_size, dtype=torch.float32, device=self.device)
+        return self._linear(self.lm_head, hidden.contiguous(), out)
+
+    @torch.no_grad()
+    def spec_generate(self, prompt: list[int], max_new: int, k: int = 3, slot: int = 0, block_table: torch.Tensor | None = None,
+                      index_reuse: bool = True, draft_hook=None):
+        """Greedy speculative decoding of one request with the draft head: ``k`` chained drafts, one
+        verify pass of ``k + 1`` tokens, the longest agreeing prefix is kept - token for token the result of
+        plain greedy decoding.  Unlike the reference's validation path (``models/qwen4exp/model.py:681-818``,
+        which recomputes the whole context with both models every round) everything is incremental: the
+        head's pools follow the main model's pages, the head appends exactly the rows the verify pass
+        accepted (its last appended row IS the first draft), rejected delta-net updates are never applied.
+        ``draft_hook(position, drafts) -> drafts`` lets a caller replace the drafts (tests of the accept
+        paths).  Returns ``(tokens, stats)``."""
+        c = self.cfg
+        if self.mtp is None:
+            raise RuntimeError("spec_generate needs the draft head (with_mtp=True)")
+        if not prompt or k < 1 or k > 7:
+            raise ValueError("spec_generate needs a prompt and 1 <= k <= 7")
+        n = len(prompt)
+        if n + max_new + k + 1 > self.max_seq:
+            raise ValueError("prompt + generation + drafts exceed max_seq")
+        bt = block_table if block_table is not None else torch.arange(
+            1 + slot * self.max_blocks_per_seq, 1 + (slot + 1) * self.max_blocks_per_seq, dtype=torch.int32, device=self.device)
+        ratio = c.indexer_compress_ratio
+        self.zero_state(slot)
+        toks = torch.tensor(prompt, dtype=torch.int64, device=self.device)
+        lanes = []
+        logits = None
+        for p0 in range(0, n, self.max_chunk):
+            part = toks[p0:p0 + self.max_chunk]
+            logits = self.prefill(part, p0, slot, bt, want_logits=p0 + part.numel() >= n, want_lanes=True)
+            lanes.append(self.last_lanes)
+        lanes = torch.cat(lanes)
+        out = [int(logits.argmax())]
+        stats = {"rounds": 0, "drafted": 0, "accepted": 0, "index_reuse": 0}
+        done = 0                                   # positions appended to the head
+        for p0 in range(0, n - 1, self.max_chunk):
+            p1 = min(n - 1, p0 + self.max_chunk)
+            self.mtp_run(toks[p0 + 1:p1 + 1], lanes[p0:p1], p0, bt)
+            done = p1
+        pend_lanes, pend_next = lanes[n - 1:n].clone(), [out[-1]]
+        while len(out) < max_new:
+            stats["rounds"] += 1
+            T = len(pend_next)
+            sample, multi = self.mtp_run(pend_next, pend_lanes, done, bt)
+            done += T                              # == the main model's committed length
+            drafts = [int(self.head_logits(sample[T - 1:T])[0].argmax())]
+            multi = multi[T - 1:T].clone()
+            sel_blocks = done // ratio             # complete blocks seen by the selection of the first chained step
+            selected = False
+            for step in range(1, k):
+                pos = done + step - 1
+                reuse = index_reuse and selected and (pos + 1) // ratio == sel_blocks
+                sample, m2 = self.mtp_run(drafts[-1:], multi, pos, bt, add_embedding=False, keep_selection=reuse)
+                if reuse:
+                    stats["index_reuse"] += 1
+                else:
+                    selected, sel_blocks = True, (pos + 1) // ratio
+                multi = m2.clone()
+                drafts.append(int(self.head_logits(sample)[0].argmax()))
+            if draft_hook is not None:
+                drafts = list(draft_hook(n + len(out), drafts))[:k]
+            stats["drafted"] += len(drafts)
+            fed = [out[-1]] + drafts
+            C = next(w for w in self.VERIFY_WIDTHS if len(fed) <= w)
+            fed_p = fed + [fed[-1]] * (C - len(fed))
+            picked = self.verify(fed_p, done, slot, bt).argmax(-1).tolist()
+            a = 0
+            while a < len(drafts) and picked[a] == drafts[a]:
+                a += 1
+            stats["accepted"] += a
+            self.commit(slot, a + 1)
+            new = drafts[:a] + [picked[a]]
+            out.extend(new)
+            pend_lanes, pend_next = self.verify_lanes()[:a + 1].clone(), new
+        stats["acceptance"] = stats["accepted"] / max(stats["drafted"], 1)
+        return out[:max_new], stats
+

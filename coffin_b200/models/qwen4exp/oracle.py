@@ -99,6 +99,47 @@ def qsa_select(iq: torch.Tensor, bkeys: torch.Tensor, n_visible: int, cfg: Qwen4
 
 
 @dataclasses.dataclass
+class DraftIndexPlan:
+    """Block selection shared along one draft chain: the head selects on draft step 0 and later steps
+    attend to the same blocks (``models/qwen4exp/mtp.py:63-128`` of the reference; only block numbers are
+    reused, the ragged tail after the last complete block is always visible).  The reuse holds only
+    while no further block has completed since step 0 - a step that crosses a block boundary selects
+    again and records anew, so the visible set never silently loses a block.  ``used`` counts the steps
+    that attended through the recorded selection."""
+    enabled: bool = True
+    blocks: torch.Tensor | None = None          # bool [n_complete_blocks] kept at the recording step
+    n_blocks: int = -1
+    used: int = 0
+
+    def before_step(self, step: int):
+        if step < 0:
+            raise ValueError(f"draft step index must be >= 0, got {step}")
+        if not self.enabled or step == 0 or self.blocks is None:
+            return None
+        return self.blocks
+
+    def record(self, keep_row: torch.Tensor, position: int, cfg) -> None:
+        ratio = cfg.indexer_compress_ratio
+        nb = (position + 1) // ratio
+        self.n_blocks = nb
+        self.blocks = keep_row[:nb * ratio].reshape(nb, ratio).all(1) if nb else torch.zeros(0, dtype=torch.bool)
+
+    def keep_rows(self, blocks: torch.Tensor, pos: torch.Tensor, S: int, cfg):
+        """Keep-mask ``[T, S]`` from the recorded blocks, or ``None`` when a row's block count differs
+        from the recorded one (select again)."""
+        ratio = cfg.indexer_compress_ratio
+        keep = torch.zeros(pos.numel(), S, dtype=torch.bool)
+        for t, p_ in enumerate(pos.tolist()):
+            nb = (p_ + 1) // ratio
+            if nb != self.n_blocks:
+                return None
+            keep[t, :nb * ratio] = blocks.repeat_interleave(ratio)
+            keep[t, nb * ratio:p_ + 1] = True
+        self.used += 1
+        return keep
+
+
+@dataclasses.dataclass
 class Qwen4State:
     n: int = 0
     conv: dict = dataclasses.field(default_factory=dict)        # layer -> [C, k-1]
@@ -184,9 +225,12 @@ class Qwen4Oracle:
         o = O.rms_norm(o, p[q + "norm.weight"], c.rms_norm_eps) * gate
         return o.reshape(T, nv * dv) @ p[q + "out_proj.weight"].t()
 
-    def _qsa(self, li: int, h: torch.Tensor, st: Qwen4State, pos: torch.Tensor, cos, sin) -> torch.Tensor:
+    def _qsa(self, li, h: torch.Tensor, st: Qwen4State, pos: torch.Tensor, cos, sin, prefix: str | None = None,
+             reuse: torch.Tensor | None = None) -> torch.Tensor:
+        """``li`` keys the K / V / index-key history in ``st`` (the draft head uses the key ``"mtp"``);
+        ``reuse`` (bool ``[T, S]``) replaces the block selection by a given keep-mask."""
         c, p = self.cfg, self.p
-        q = f"{LM}layers.{li}.self_attn."
+        q = (prefix if prefix is not None else f"{LM}layers.{li}.") + "self_attn."
         T = h.shape[0]
         nh, nkv, hd, rot = c.num_attention_heads, c.num_key_value_heads, c.head_dim, c.rotary_dim
         ni, di = c.indexer_n_heads, c.indexer_head_dim
@@ -210,14 +254,14 @@ class Qwen4Oracle:
         keep = torch.zeros(T, S, dtype=torch.bool)
         for t in range(T):
             nvis = int(pos[t]) + 1
-            keep[t, :nvis] = qsa_select(iq[t], bkeys, nvis, c)
+            keep[t, :nvis] = qsa_select(iq[t], bkeys, nvis, c) if reuse is None else reuse[t, :nvis]
         self.last_selected[li] = keep
         o = O.gated_attention(qq, gate, st.k[li], st.v[li], pos, hd ** -0.5, keep=keep)
         return o.reshape(T, nh * hd) @ p[q + "o_proj.weight"].t()
 
-    def _moe(self, li: int, h: torch.Tensor) -> torch.Tensor:
+    def _moe(self, li, h: torch.Tensor, prefix: str | None = None) -> torch.Tensor:
         c, p = self.cfg, self.p
-        m = f"{LM}layers.{li}.mlp."
+        m = (prefix if prefix is not None else f"{LM}layers.{li}.") + "mlp."
         shared = (p[m + "shared_expert.gate_proj.weight"], p[m + "shared_expert.up_proj.weight"],
                   p[m + "shared_expert.down_proj.weight"], p[m + "shared_expert_gate.weight"])
         return O.moe_ffn(h, p[m + "gate.weight"], p[m + "experts.gate_up_proj"], p[m + "experts.down_proj"],
@@ -244,6 +288,103 @@ class Qwen4Oracle:
             x = hyper_write(x, self._moe(li, mixed), inject, c)
         st.n += T
         return x
+
+    # ------------------------------------------------------------------ draft head (MTP)
+    @property
+    def has_mtp(self) -> bool:
+        return "mtp.fc_embedding.weight" in self.p
+
+    @torch.no_grad()
+    def mtp_run(self, next_tokens: torch.Tensor, lanes: torch.Tensor, mst: Qwen4State, add_embedding: bool = True,
+                plan: "DraftIndexPlan | None" = None, step: int = 0):
+        """One pass of the draft head over ``T`` rows at positions ``mst.n ..``: row ``t`` sees the main
+        model's un-collapsed lanes at its position (``lanes [T, hc*H]``; on later draft steps the head's
+        own ``multi`` output) and the token that FOLLOWS that position (``next_tokens [T]``), and
+        predicts the token after it.  Returns ``(sample [T, H], multi [T, hc*H])``; ``mst`` holds the
+        head's own K / V / index keys (nothing is shared with a main layer) and advances by ``T``.
+
+        Structure (``models/qwen4exp/mtp.py:146-330`` of the reference): the embedding goes through a
+        zero-centred RMSNorm of width ``H`` and ``fc_embedding``; the lanes through ONE RMSNorm over the
+        whole ``hc*H`` width and ``fc_hidden`` applied to every lane; the projected embedding is added to
+        every lane with unit weight only when ``add_embedding`` (prefill / append rows and draft step 0
+        - adding it on the chained steps would stack it into the stream again); then one QSA + MoE
+        layer without n-gram injection and the head's own final mixer, which has no write gate."""
+        c, p = self.cfg, self.p
+        hc, H = c.hc_count, c.hidden_size
+        T = next_tokens.numel()
+        pos = torch.arange(mst.n, mst.n + T)
+        cos, sin = self._cos_sin(pos)
+        e = p[LM + "embed_tokens.weight"][next_tokens.long()]
+        e = O.rms_norm(e, 1.0 + p["mtp.pre_fc_norm_embedding.weight"], c.rms_norm_eps) @ p["mtp.fc_embedding.weight"].t()
+        n = O.rms_norm(lanes.float(), 1.0 + p["mtp.pre_fc_norm_hidden.weight"], c.rms_norm_eps)
+        x = (n.reshape(T, hc, H) @ p["mtp.fc_hidden.weight"].t()).flatten(1)
+        if add_embedding:
+            x = x + e.repeat(1, hc)
+        lp = "mtp.layers.0."
+        mixed, inject = hyper_read(x, p, lp + "attn_hyper_connection.", c)
+        reuse = plan.before_step(step) if plan is not None else None
+        keep = None
+        if reuse is not None:
+            keep = plan.keep_rows(reuse, pos, mst.k["mtp"].shape[0] + T if "mtp" in mst.k else T, c)
+        out = self._qsa("mtp", mixed, mst, pos, cos, sin, prefix=lp, reuse=keep)
+        if plan is not None and keep is None:
+            plan.record(self.last_selected["mtp"][-1], int(pos[-1]), c)
+        x = hyper_write(x, out, inject, c)
+        mixed, inject = hyper_read(x, p, lp + "mlp_hyper_connection.", c)
+        x = hyper_write(x, self._moe("mtp", mixed, prefix=lp), inject, c)
+        mst.n += T
+        return hyper_read(x, p, "mtp.hyper_connection_mixer.", c)[0], x
+
+    def head(self, hidden: torch.Tensor) -> torch.Tensor:
+        return hidden @ self.p.get("lm_head.weight", self.p[LM + "embed_tokens.weight"]).t()
+
+    @torch.no_grad()
+    def spec_generate(self, prompt: list[int], max_new: int, k: int = 3, index_reuse: bool = True):
+        """Greedy speculative decoding with the draft head, stated as plainly as possible: the head's
+        K/V follow the main model's position by position (row ``i`` pairs the lanes at position ``i``
+        with token ``i + 1``), ``k`` drafts are chained from the last committed position, the main
+        model scores ``[last, d1..dk]`` in one pass and the longest agreeing prefix is kept.  The
+        result equals plain greedy decoding token for token.  Returns ``(tokens, stats)``."""
+        st, mst = self.new_state(), self.new_state()
+        toks = torch.tensor(prompt)
+        lanes = self.lanes(toks, st)
+        logits = self.head(hyper_read(lanes, self.p, LM + "hyper_connection_mixer.", self.cfg)[0])
+        out = [int(logits[-1].argmax())]
+        stats = {"rounds": 0, "drafted": 0, "accepted": 0, "index_reuse": 0}
+        # rows 0..n-2 of the prompt build the head's history; the row of the last prompt position is
+        # appended together with the first draft below (its "next token" is out[-1])
+        if len(prompt) > 1:
+            self.mtp_run(toks[1:], lanes[:-1], mst)
+        pend_lanes, pend_next = lanes[-1:], [out[-1]]          # rows not yet appended to the head
+        while len(out) < max_new:
+            stats["rounds"] += 1
+            plan = DraftIndexPlan(enabled=index_reuse)
+            sample, multi = self.mtp_run(torch.tensor(pend_next), pend_lanes, mst, plan=plan, step=0)
+            base = mst.clone()                                  # the head's state at the committed length
+            drafts = [int(self.head(sample[-1:])[0].argmax())]
+            multi = multi[-1:]
+            for step in range(1, k):
+                sample, multi = self.mtp_run(torch.tensor(drafts[-1:]), multi, mst, add_embedding=False, plan=plan, step=step)
+                drafts.append(int(self.head(sample)[0].argmax()))
+            mst = base                                          # the chain's K/V rows are dropped
+            stats["drafted"] += k
+            stats["index_reuse"] += plan.used
+            snap = st.clone()
+            seq = torch.tensor([out[-1]] + drafts)
+            v_lanes = self.lanes(seq, st)
+            picked = self.head(hyper_read(v_lanes, self.p, LM + "hyper_connection_mixer.", self.cfg)[0]).argmax(-1).tolist()
+            a = 0
+            while a < k and picked[a] == drafts[a]:
+                a += 1
+            stats["accepted"] += a
+            if a < k:                                            # roll the main model back to the accepted prefix
+                st = snap
+                v_lanes = self.lanes(seq[:a + 1], st)
+            new = drafts[:a] + [picked[a]]
+            out.extend(new)
+            pend_lanes, pend_next = v_lanes[:a + 1], new
+        stats["acceptance"] = stats["accepted"] / max(stats["drafted"], 1)
+        return out[:max_new], stats
 
     def hidden(self, tokens: torch.Tensor, st: Qwen4State, **kw) -> torch.Tensor:
         x = self.lanes(tokens, st, **kw)

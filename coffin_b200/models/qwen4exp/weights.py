@@ -13,7 +13,7 @@ import math
 import torch
 
 from ...weights.init import _draw
-from .config import LINEAR, Qwen4Config
+from .config import INDEXED, LINEAR, Qwen4Config
 from .ngram import NGramHasher
 
 LM = "model.language_model."
@@ -28,60 +28,75 @@ def _hyper(prefix: str, cfg: Qwen4Config, add, write_gate: bool = True) -> None:
         add(prefix + "block_inject_weight.weight", (cfg.hc_count, W), "w")
 
 
+def _layer_plan(p: str, kind: str, cfg: Qwen4Config, add, ple: int | None) -> None:
+    """Tensors of one decoder layer under prefix ``p`` (``ple``: index of its n-gram table, or None)."""
+    H = cfg.hidden_size
+    if kind == LINEAR:
+        q = p + "linear_attn."
+        add(q + "in_proj_qkv.weight", (cfg.lin_conv_dim, H), "w")
+        add(q + "in_proj_z.weight", (cfg.lin_vdim, H), "w")
+        add(q + "in_proj_b.weight", (cfg.linear_num_value_heads, H), "w")
+        add(q + "in_proj_a.weight", (cfg.linear_num_value_heads, H), "w")
+        add(q + "conv1d.weight", (cfg.lin_conv_dim, 1, cfg.linear_conv_kernel_dim), "conv")
+        add(q + "A_log", (cfg.linear_num_value_heads,), "alog")
+        add(q + "dt_bias", (cfg.linear_num_value_heads,), "dt")
+        add(q + "norm.weight", (cfg.linear_value_head_dim,), "norm1")
+        add(q + "out_proj.weight", (H, cfg.lin_vdim), "w")
+    else:
+        q = p + "self_attn."
+        nh, nkv, hd = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
+        add(q + "q_proj.weight", (nh * 2 * hd, H), "w")
+        add(q + "k_proj.weight", (nkv * hd, H), "w")
+        add(q + "v_proj.weight", (nkv * hd, H), "w")
+        add(q + "o_proj.weight", (H, nh * hd), "w")
+        add(q + "q_norm.weight", (hd,), "norm0")
+        add(q + "k_norm.weight", (hd,), "norm0")
+        add(q + "indexer.index_qk_proj.weight", ((cfg.indexer_n_heads + 1) * cfg.indexer_head_dim, H), "w")
+        add(q + "indexer.q_layernorm.weight", (cfg.indexer_head_dim,), "norm0")
+        add(q + "indexer.k_layernorm.weight", (cfg.indexer_head_dim,), "norm0")
+    m = p + "mlp."
+    E, I, S = cfg.num_experts, cfg.moe_intermediate_size, cfg.shared_expert_intermediate_size
+    add(m + "gate.weight", (E, H), "wide")
+    add(m + "experts.gate_up_proj", (E, 2 * I, H), "w")
+    add(m + "experts.down_proj", (E, H, I), "w")
+    add(m + "shared_expert.gate_proj.weight", (S, H), "w")
+    add(m + "shared_expert.up_proj.weight", (S, H), "w")
+    add(m + "shared_expert.down_proj.weight", (H, S), "w")
+    add(m + "shared_expert_gate.weight", (1, H), "w")
+    _hyper(p + "attn_hyper_connection.", cfg, add)
+    _hyper(p + "mlp_hyper_connection.", cfg, add)
+    j = ple
+    if j is not None:
+        q = p + "ple."
+        rows = NGramHasher(cfg, j).rows
+        add(q + "ple_embedding.ngram_embedding.weight", (rows, cfg.ngram_head_dim), "wide")
+        add(q + "key_proj.weight", (cfg.hc_hidden, cfg.ple_embed_dim), "wide")
+        add(q + "value_proj.weight", (H, cfg.ple_embed_dim), "wide")
+        for n in ("norm_key", "norm_query", "norm_conv"):
+            add(q + n + ".weight", (cfg.hc_hidden,), "norm0")
+        add(q + "conv1d.weight", (cfg.hc_hidden, 1, cfg.ple_conv_kernel_size), "conv")
+
+
 def tensor_plan(cfg: Qwen4Config) -> list[tuple[str, tuple[int, ...], str]]:
     plan: list[tuple[str, tuple[int, ...], str]] = []
     add = lambda k, s, kind: plan.append((k, s, kind))
     H = cfg.hidden_size
     add(LM + "embed_tokens.weight", (cfg.vocab_size, H), "w")
     for i, kind in enumerate(cfg.layer_types):
-        p = f"{LM}layers.{i}."
-        if kind == LINEAR:
-            q = p + "linear_attn."
-            add(q + "in_proj_qkv.weight", (cfg.lin_conv_dim, H), "w")
-            add(q + "in_proj_z.weight", (cfg.lin_vdim, H), "w")
-            add(q + "in_proj_b.weight", (cfg.linear_num_value_heads, H), "w")
-            add(q + "in_proj_a.weight", (cfg.linear_num_value_heads, H), "w")
-            add(q + "conv1d.weight", (cfg.lin_conv_dim, 1, cfg.linear_conv_kernel_dim), "conv")
-            add(q + "A_log", (cfg.linear_num_value_heads,), "alog")
-            add(q + "dt_bias", (cfg.linear_num_value_heads,), "dt")
-            add(q + "norm.weight", (cfg.linear_value_head_dim,), "norm1")
-            add(q + "out_proj.weight", (H, cfg.lin_vdim), "w")
-        else:
-            q = p + "self_attn."
-            nh, nkv, hd = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
-            add(q + "q_proj.weight", (nh * 2 * hd, H), "w")
-            add(q + "k_proj.weight", (nkv * hd, H), "w")
-            add(q + "v_proj.weight", (nkv * hd, H), "w")
-            add(q + "o_proj.weight", (H, nh * hd), "w")
-            add(q + "q_norm.weight", (hd,), "norm0")
-            add(q + "k_norm.weight", (hd,), "norm0")
-            add(q + "indexer.index_qk_proj.weight", ((cfg.indexer_n_heads + 1) * cfg.indexer_head_dim, H), "w")
-            add(q + "indexer.q_layernorm.weight", (cfg.indexer_head_dim,), "norm0")
-            add(q + "indexer.k_layernorm.weight", (cfg.indexer_head_dim,), "norm0")
-        m = p + "mlp."
-        E, I, S = cfg.num_experts, cfg.moe_intermediate_size, cfg.shared_expert_intermediate_size
-        add(m + "gate.weight", (E, H), "wide")
-        add(m + "experts.gate_up_proj", (E, 2 * I, H), "w")
-        add(m + "experts.down_proj", (E, H, I), "w")
-        add(m + "shared_expert.gate_proj.weight", (S, H), "w")
-        add(m + "shared_expert.up_proj.weight", (S, H), "w")
-        add(m + "shared_expert.down_proj.weight", (H, S), "w")
-        add(m + "shared_expert_gate.weight", (1, H), "w")
-        _hyper(p + "attn_hyper_connection.", cfg, add)
-        _hyper(p + "mlp_hyper_connection.", cfg, add)
-        j = cfg.ple_index(i)
-        if j is not None:
-            q = p + "ple."
-            rows = NGramHasher(cfg, j).rows
-            add(q + "ple_embedding.ngram_embedding.weight", (rows, cfg.ngram_head_dim), "wide")
-            add(q + "key_proj.weight", (cfg.hc_hidden, cfg.ple_embed_dim), "wide")
-            add(q + "value_proj.weight", (H, cfg.ple_embed_dim), "wide")
-            for n in ("norm_key", "norm_query", "norm_conv"):
-                add(q + n + ".weight", (cfg.hc_hidden,), "norm0")
-            add(q + "conv1d.weight", (cfg.hc_hidden, 1, cfg.ple_conv_kernel_size), "conv")
+        _layer_plan(f"{LM}layers.{i}.", kind, cfg, add, cfg.ple_index(i))
     _hyper(LM + "hyper_connection_mixer.", cfg, add, write_gate=False)
     if not cfg.tie_word_embeddings:
         add("lm_head.weight", (cfg.vocab_size, H), "w")
+    if cfg.mtp_num_hidden_layers:
+        # the draft head: two [H, H] projections with their pre-norms (the hidden one spans all lanes),
+        # one QSA + MoE layer without n-gram injection, and a final mixer without write gate
+        # (``models/qwen4exp/mtp.py:146-200`` of the reference)
+        add("mtp.fc_embedding.weight", (H, H), "w")
+        add("mtp.fc_hidden.weight", (H, H), "w")
+        add("mtp.pre_fc_norm_embedding.weight", (H,), "norm0")
+        add("mtp.pre_fc_norm_hidden.weight", (cfg.hc_hidden,), "norm0")
+        _layer_plan("mtp.layers.0.", INDEXED, cfg, add, None)
+        _hyper("mtp.hyper_connection_mixer.", cfg, add, write_gate=False)
     return plan
 
 

@@ -23,6 +23,7 @@ from ..config import LINEAR, ModelConfig
 from ..weights.init import LM
 
 MAX_WORLD = 8
+OS_ROWS = 64          # rows of a one-shot all-reduce (a decode bucket); kOsRows of _C/comm.cu
 
 
 # ---------------------------------------------------------------------------------------------
@@ -145,7 +146,7 @@ class _TpPfStruct(ctypes.Structure):
                 ("inbox", ctypes.c_void_p * MAX_WORLD), ("out", ctypes.c_void_p * MAX_WORLD),
                 ("flags1", ctypes.c_void_p * MAX_WORLD), ("flags2", ctypes.c_void_p * MAX_WORLD),
                 ("arrive", ctypes.c_void_p), ("status", ctypes.c_void_p), ("wait_ns", ctypes.c_uint64),
-                ("seq_dev", ctypes.c_void_p)]
+                ("seq_dev", ctypes.c_void_p), ("os_inbox", ctypes.c_void_p * MAX_WORLD)]
 
 
 class _DevView:
@@ -204,7 +205,8 @@ class TpComm:
             self._off_pf_arrive = self._off_pf_f2 + 256
             self._off_pf_seq = self._off_pf_arrive + 128        # same 256-byte cell as the arrival counters
             self._off_pf_desc = self._off_pf_arrive + 256
-            self.nbytes = self._off_pf_desc + 1024
+            self._off_os = self._off_pf_desc + 1024
+            self.nbytes = self._off_os + (2 * world * OS_ROWS * hidden * 4 + 255) // 256 * 256   # {2 x bf16, seq} pairs
         self._pf_seq = 0
         self._lib = _lib.lib()
         base = ctypes.c_void_p()
@@ -263,6 +265,8 @@ class TpComm:
             d.status = self.base + self._off_status
             d.wait_ns = self.wait_ns
             d.seq_dev = self.base + self._off_pf_seq
+            for r in range(world):
+                d.os_inbox[r] = self.peers[r] + self._off_os
             assert ctypes.sizeof(d) == self._lib.cb_tp_pf_desc_size() <= 1024
             rc = self._lib.cb_peer_write(ctypes.c_void_p(self.base + self._off_pf_desc), ctypes.byref(d),
                                          ctypes.c_int64(ctypes.sizeof(d)))
@@ -302,6 +306,22 @@ class TpComm:
         K.call("tp_pf_wait", self.pf_desc_ptr(), seq)
         K._count(2)
         return self.pf_out[:T]
+
+    def oneshot(self, src: torch.Tensor, residual: torch.Tensor | None = None, gain: torch.Tensor | None = None,
+                res_out: torch.Tensor | None = None, normed: torch.Tensor | None = None, eps: float = 0.0) -> None:
+        """All-reduce of the few rows of a decode bucket (``src [M <= 64, hidden]`` bf16) in one launch and
+        one NVLink crossing: CTA m of every rank stores row m into every peer's one-shot inbox (data paired
+        with the sequence number), polls the peers' rows in its own inbox, adds the world's rows (rank order)
+        + ``residual`` into ``res_out`` and, with ``gain``, writes ``rmsnorm(res_out) * gain`` into ``normed``."""
+        from ..ops import kernels as K
+        M, W = src.shape
+        if not self.pf_rows or M > OS_ROWS or W != self.hidden:
+            raise ValueError(f"one-shot all-reduce of [{M}, {W}] outside [{OS_ROWS}, {self.hidden}]")
+        K.call("tp_os_allreduce", self.pf_desc_ptr(), src, src.stride(0), residual,
+               residual.stride(0) if residual is not None else 0, gain,
+               res_out, res_out.stride(0) if res_out is not None else 0, normed,
+               normed.stride(0) if normed is not None else 0, M, W, float(eps), 0)
+        K._count()
 
     def cstruct_ref(self):
         return ctypes.byref(self._struct)

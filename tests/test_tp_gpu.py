@@ -187,6 +187,52 @@ def test_bounded_waits_run_out_and_report(monkeypatch):
     tp1.close()
 
 
+@torch.no_grad()
+def test_one_shot_all_reduce_protocol_on_one_gpu():
+    """World 1: the push kernel stores this rank's rows into its own one-shot inbox, the reduce kernel waits
+    for the flag, adds the residual and applies the RMSNorm; interleaved with the reduce-scatter protocol on
+    the same communicator (shared sequence counter) and replayed from a CUDA graph (the sequence number
+    advances on the device)."""
+    from coffin_b200.ops import kernels as K
+    from coffin_b200.parallel.tp import TpComm
+    H = 512
+    tp = TpComm(0, 1, H, 8, 4, prefill_rows=256)
+    g = torch.Generator().manual_seed(9)
+    gain = (1 + 0.1 * torch.randn(H, generator=g)).cuda()
+    for M in (1, 16, 64, 33):
+        part = torch.randn(M, H, generator=g).to(torch.bfloat16).cuda()
+        res = torch.randn(M, H, generator=g).to(torch.bfloat16).cuda()
+        res_out, normed = torch.empty_like(res), torch.empty_like(res)
+        tp.oneshot(part, residual=res, gain=gain, res_out=res_out, normed=normed, eps=1e-6)
+        ref = (part.float() + res.float()).to(torch.bfloat16)
+        assert torch.equal(res_out, ref)
+        rn = ref.float() * torch.rsqrt(ref.float().pow(2).mean(-1, keepdim=True) + 1e-6) * gain
+        assert ((normed.float() - rn).abs().max() / rn.abs().max()).item() < 1e-2
+        tp.scatter(res)                                   # the other protocol in between
+        assert torch.equal(tp.finish_reduce(), res)
+        out = torch.empty_like(part)
+        tp.oneshot(part, res_out=out)                     # plain sum, no residual, no norm
+        assert torch.equal(out, part)
+    # graph replay: the same two launches, new data every replay
+    part = torch.zeros(8, H, dtype=torch.bfloat16, device="cuda")
+    out = torch.empty_like(part)
+    s = torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(s):
+        tp.oneshot(part, res_out=out)
+    torch.cuda.current_stream().wait_stream(s)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        tp.oneshot(part, res_out=out)
+    for i in range(5):
+        part.fill_(float(i + 1))
+        graph.replay()
+        assert torch.equal(out, part)
+    torch.cuda.synchronize()
+    assert tp.status() == 0
+    tp.close()
+
+
 def _rank_main(rank, world, port, out):
     import torch.distributed as dist
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
