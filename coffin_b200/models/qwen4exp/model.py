@@ -261,6 +261,7 @@ class Qwen4ExpModel:
         self.last_hidden = None
         self.last_lanes = None
         self._verify: dict | None = None
+        self.layer_hook = None            # debugging: called as hook(layer index, residual lanes) before every layer
 
     # ------------------------------------------------------------------ sizes / bookkeeping
     def _fresh_ctx(self) -> list[int]:
@@ -578,6 +579,8 @@ class Qwen4ExpModel:
         decode = slots is not None
         pending = None
         for li, L in enumerate(self.layers):
+            if self.layer_hook is not None:
+                self.layer_hook(li, ws["stream"])
             if L.ple is not None:
                 stream = ws["stream"]
                 if pending is not None:                      # PLE reads the stream with the last write-back applied

@@ -339,12 +339,14 @@ class Qwen4Oracle:
         return hidden @ self.p.get("lm_head.weight", self.p[LM + "embed_tokens.weight"]).t()
 
     @torch.no_grad()
-    def spec_generate(self, prompt: list[int], max_new: int, k: int = 3, index_reuse: bool = True):
+    def spec_generate(self, prompt: list[int], max_new: int, k: int = 3, index_reuse: bool = True, draft_hook=None):
         """Greedy speculative decoding with the draft head, stated as plainly as possible: the head's
         K/V follow the main model's position by position (row ``i`` pairs the lanes at position ``i``
         with token ``i + 1``), ``k`` drafts are chained from the last committed position, the main
         model scores ``[last, d1..dk]`` in one pass and the longest agreeing prefix is kept.  The
-        result equals plain greedy decoding token for token.  Returns ``(tokens, stats)``."""
+        result equals plain greedy decoding token for token.  ``draft_hook(position, drafts)`` may
+        replace the drafts of a round (``position``: where the first draft would land).
+        Returns ``(tokens, stats)``."""
         st, mst = self.new_state(), self.new_state()
         toks = torch.tensor(prompt)
         lanes = self.lanes(toks, st)
@@ -367,6 +369,8 @@ class Qwen4Oracle:
                 sample, multi = self.mtp_run(torch.tensor(drafts[-1:]), multi, mst, add_embedding=False, plan=plan, step=step)
                 drafts.append(int(self.head(sample)[0].argmax()))
             mst = base                                          # the chain's K/V rows are dropped
+            if draft_hook is not None:                          # a caller may replace the drafts (tests of the accept paths)
+                drafts = list(draft_hook(len(prompt) + len(out), drafts))[:k]
             stats["drafted"] += k
             stats["index_reuse"] += plan.used
             snap = st.clone()
@@ -374,10 +378,10 @@ class Qwen4Oracle:
             v_lanes = self.lanes(seq, st)
             picked = self.head(hyper_read(v_lanes, self.p, LM + "hyper_connection_mixer.", self.cfg)[0]).argmax(-1).tolist()
             a = 0
-            while a < k and picked[a] == drafts[a]:
+            while a < len(drafts) and picked[a] == drafts[a]:
                 a += 1
             stats["accepted"] += a
-            if a < k:                                            # roll the main model back to the accepted prefix
+            if a < len(drafts):                                            # roll the main model back to the accepted prefix
                 st = snap
                 v_lanes = self.lanes(seq[:a + 1], st)
             new = drafts[:a] + [picked[a]]

@@ -278,6 +278,53 @@ def test_attention_prefill_and_decode(nh, nkv, hd, rot, T1, T2):
     close(got_k, kref, 2e-2)
 
 
+@pytest.mark.parametrize("nh,nkv,hd,rot,chunks", [(4, 2, 64, 16, (200, 57, 300)), (4, 1, 256, 64, (130, 128, 333)),
+                                                  (2, 2, 256, 64, (64, 1000))])
+def test_attention_prefill_tcgen05_matches_oracle_and_the_mma_kernel(nh, nkv, hd, rot, chunks):
+    """Chunked causal prefill through the tcgen05 kernel (TMA pages, TMEM accumulators, lazy rescale)
+    against the fp32 oracle and the mma.sync kernel: chunk starts that are not page aligned, query
+    tiles with padded rows, scattered pages, the output gate; run twice for bit-equal results."""
+    k = K()
+    T = sum(chunks)
+    proj, qg, kg, cos, sin = _attn_setup(T, nh, nkv, hd, rot, 41)
+    qg = qg * 6.0                                  # scores ~ N(0, 6^2): the running maximum moves by more than 2^8, rescales happen
+    pos = torch.arange(T)
+    ref, _, _ = _attn_oracle(proj, qg, kg, cos, sin, nh, nkv, hd, rot, pos)
+    d = lambda t: t.to(DEV)
+    nblk = (T + 63) // 64
+    kpool = torch.zeros((nblk + 2) * 64, nkv, hd, dtype=torch.bfloat16, device=DEV)
+    vpool = torch.zeros_like(kpool)
+    perm = torch.randperm(nblk + 1, generator=torch.Generator().manual_seed(3))[:nblk] + 1
+    bt = perm.to(torch.int32)
+    pj, dc, ds = d(proj), d(cos), d(sin)
+    outs = {}
+    for tc in (True, False, True):
+        k.ATTN_TC = tc
+        out = torch.full((T + 1, nh * hd), 7.0, dtype=torch.bfloat16, device=DEV)      # last row: canary
+        s = 0
+        try:
+            for n in chunks:
+                e = s + n
+                q = torch.empty(n, nh, hd, dtype=torch.bfloat16, device=DEV)
+                slots = (bt.long()[torch.arange(s, e) // 64] * 64 + torch.arange(s, e) % 64).to(torch.int32).to(DEV)
+                ridx = torch.arange(s, e, dtype=torch.int32, device=DEV)
+                k.attn_prep(pj[s:e], d(qg), d(kg), dc, ds, ridx, slots, q, kpool, vpool, nh=nh, nkv=nkv, hd=hd, rot=rot, eps=1e-6)
+                k.attn_prefill(q, pj[s:e], kpool, vpool, d(bt), out[s:e], q_pos0=s, nh=nh, nkv=nkv, hd=hd)
+                s = e
+        finally:
+            k.ATTN_TC = True
+        torch.cuda.synchronize()
+        k.check_status()
+        assert bool((out[T] == 7.0).all()), "wrote past the last row"
+        outs.setdefault(tc, []).append(out[:T].clone())
+    close(outs[True][0], ref, 3e-2)
+    close(outs[False][0], ref, 3e-2)
+    assert torch.equal(outs[True][0], outs[True][1]), "the tcgen05 kernel must be deterministic"
+    # per element against the mma.sync kernel (both round P to bf16; accumulation order differs)
+    a, b = outs[True][0].float(), outs[False][0].float()
+    assert float((a - b).abs().max()) <= 0.03 * float(b.abs().max())
+
+
 @pytest.mark.parametrize("M", [1, 3, 8])
 @pytest.mark.parametrize("N,Kd", [(520, 512), (2560, 1040), (37, 272)])
 def test_gemv_i8_w8a8(M, N, Kd):

@@ -1,4 +1,5 @@
 """Qwen4-exp family on the CPU: config round trip, n-gram hashing, oracle self-consistency."""
+import pytest
 import torch
 
 from coffin_b200.models.qwen4exp.config import Qwen4Config, tiny_qwen4
@@ -148,3 +149,61 @@ def test_qwen4_quantiser_streams_and_round_trips(tmp_path):
                 assert torch.equal(v, sd[k]), k
         assert n_q > 3 * cfg.num_hidden_layers
     assert not list((tmp_path / "w4a8").glob("*.tmp"))
+
+
+def _greedy(o, prompt, n):
+    st = o.new_state()
+    out = [int(o.forward(torch.tensor(prompt), st)[-1].argmax())]
+    while len(out) < n:
+        out.append(int(o.forward(torch.tensor(out[-1:]), st)[-1].argmax()))
+    return out
+
+
+def test_draft_head_plan_has_the_checkpoint_tensor_count_and_config_guard():
+    cfg = tiny_qwen4(mtp_num_hidden_layers=1)
+    names = [k for k, _, _ in tensor_plan(cfg) if k.startswith("mtp.")]
+    # 2 projections + 2 pre-norms + 3 final-mixer tensors + one QSA/MoE layer (9 + 7 + 2 x 4): the 31
+    # ``mtp.*`` tensors of a checkpoint of the family
+    assert len(names) == 31
+    assert "mtp.layers.0.self_attn.indexer.index_qk_proj.weight" in names
+    assert not any("block_inject" in k for k in names if k.startswith("mtp.hyper_connection_mixer."))
+    shapes = {k: s for k, s, _ in tensor_plan(cfg)}
+    assert shapes["mtp.pre_fc_norm_hidden.weight"] == (cfg.hc_hidden,) and shapes["mtp.fc_hidden.weight"] == (cfg.hidden_size,) * 2
+    with pytest.raises(ValueError, match="exactly one layer"):
+        tiny_qwen4(mtp_num_hidden_layers=2)
+
+
+def test_oracle_speculative_decoding_with_the_draft_head_equals_greedy():
+    """Random weights accept nothing, so a hook feeds partly correct drafts: 0, 1, 2 and all accepted
+    drafts per round, with and without block-selection reuse along the chain."""
+    from coffin_b200.models.qwen4exp.oracle import DraftIndexPlan
+    cfg = tiny_qwen4(mtp_num_hidden_layers=1)
+    o = Qwen4Oracle(cfg, random_state_dict(cfg, 0))
+    assert o.has_mtp
+    g = torch.Generator().manual_seed(1)
+    prompt = torch.randint(0, cfg.vocab_size, (50,), generator=g).tolist()       # 50 tokens: 12 blocks > 2 x 4, selection is sparse
+    ref = _greedy(o, prompt, 24)
+    out, stats = o.spec_generate(prompt, 24, k=3)
+    assert out == ref and stats["drafted"] == 3 * stats["rounds"]
+    rounds = []
+
+    def hook(position, drafts):
+        i = position - len(prompt)                      # index in ``ref`` of the first draft
+        good = len(rounds) % 4                          # 0, 1, 2, 3 correct drafts in turn
+        rounds.append(good)
+        return [ref[i + j] if j < good and i + j < len(ref) else (drafts[j] + 1) % cfg.vocab_size for j in range(3)]
+
+    for reuse in (True, False):
+        rounds.clear()
+        out, stats = o.spec_generate(prompt, 24, k=3, index_reuse=reuse, draft_hook=hook)
+        assert out == ref, reuse
+        assert stats["accepted"] > 0 and (stats["index_reuse"] > 0) == reuse
+    # the plan refuses a negative step and re-selects after a block boundary
+    plan = DraftIndexPlan()
+    with pytest.raises(ValueError):
+        plan.before_step(-1)
+    keep = torch.ones(12, dtype=torch.bool)
+    plan.record(keep, 11, cfg)                          # 3 complete blocks at position 11 (ratio 4)
+    assert plan.before_step(1) is not None
+    assert plan.keep_rows(plan.blocks, torch.tensor([13]), 14, cfg) is not None
+    assert plan.keep_rows(plan.blocks, torch.tensor([15]), 16, cfg) is None      # a fourth block completed

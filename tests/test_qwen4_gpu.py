@@ -210,3 +210,111 @@ def test_qwen4_runs_from_a_prequantised_directory_with_int8_embedding(tmp_path):
     a = dense.prefill(toks.to(DEV), 0, 0, bt)
     b = qm.prefill(toks.to(DEV), 0, 0, bt)
     assert _rel(b, a.cpu()) < 0.15
+
+
+@torch.no_grad()
+def test_qwen4_verify_and_commit_follow_sequential_decode():
+    """A verify pass of 4 tokens gives the logits of four sequential decode steps; committing the first
+    ``n`` leaves the delta-net states and the n-gram window exactly where ``n`` decode steps leave them
+    (the next decode step agrees)."""
+    from coffin_b200.models.qwen4exp.model import Qwen4ExpModel
+    cfg = tiny_qwen4()
+    sd = random_state_dict(cfg, 0)
+    seq_model = Qwen4ExpModel(cfg, sd, max_seq=256, num_slots=1)
+    ver_model = Qwen4ExpModel(cfg, sd, max_seq=256, num_slots=1)
+    g = torch.Generator().manual_seed(4)
+    toks = torch.randint(2, cfg.vocab_size, (80,), generator=g)
+    bt = torch.arange(1, 5, dtype=torch.int32, device=DEV)
+    for m in (seq_model, ver_model):
+        m.zero_state(0)
+        m.prefill(toks[:60].to(DEV), 0, 0, bt, want_logits=False)
+    ref = []
+    for i in range(60, 64):
+        seq_model.set_rows(1, [int(toks[i])], [i], [0], [bt.tolist()])
+        ref.append(seq_model.decode(1)[1][0].clone())
+    got = ver_model.verify(toks[60:64].tolist(), 60, 0, bt)
+    for j in range(4):
+        assert _rel(got[j], ref[j].cpu()) < 3e-2, j
+    assert ver_model.verify_lanes().shape == (4, cfg.hc_hidden)
+    # accept two of the four; both models then decode position 62 again with another token
+    ver_model.commit(0, 2)
+    seq2 = Qwen4ExpModel(cfg, sd, max_seq=256, num_slots=1)
+    seq2.zero_state(0)
+    seq2.prefill(toks[:60].to(DEV), 0, 0, bt, want_logits=False)
+    for i in (60, 61):
+        seq2.set_rows(1, [int(toks[i])], [i], [0], [bt.tolist()])
+        seq2.decode(1)
+    outs = []
+    for m in (seq2, ver_model):
+        m.set_rows(1, [int(toks[70])], [62], [0], [bt.tolist()])
+        outs.append(m.decode(1)[1][0].clone())
+    assert _rel(outs[1], outs[0].cpu()) < 3e-2
+    from coffin_b200.ops import kernels as K
+    torch.cuda.synchronize()
+    K.check_status()
+
+
+@torch.no_grad()
+def test_qwen4_draft_head_matches_oracle_and_speculative_decoding_equals_greedy():
+    from coffin_b200.models.qwen4exp.model import Qwen4ExpModel
+    cfg = tiny_qwen4(mtp_num_hidden_layers=1)
+    sd = random_state_dict(cfg, 0)
+    sd_b = {k: (v.to(torch.bfloat16).float() if not k.endswith(("A_log", "dt_bias")) else v) for k, v in sd.items()}
+    oracle = Qwen4Oracle(cfg, sd_b)
+    model = Qwen4ExpModel(cfg, sd, max_seq=256, num_slots=1, with_mtp=True)
+    g = torch.Generator().manual_seed(6)
+    toks = torch.randint(2, cfg.vocab_size, (64,), generator=g)
+    bt = torch.arange(1, 5, dtype=torch.int32, device=DEV)
+    # ---- the head alone: prompt rows (prefill kernels), then chained single rows (decode kernels)
+    st, mst = oracle.new_state(), oracle.new_state()
+    lanes_ref = oracle.lanes(toks[:60], st)
+    s_ref, m_ref = oracle.mtp_run(toks[1:60], lanes_ref[:59], mst)
+    model.zero_state(0)
+    model.prefill(toks[:60].to(DEV), 0, 0, bt, want_logits=False, want_lanes=True)
+    lanes = model.last_lanes
+    assert _rel(lanes, lanes_ref) < 6e-2
+    s_got, m_got = model.mtp_run(toks[1:60].to(DEV), lanes[:59], 0, bt)
+    assert _rel(s_got, s_ref) < 8e-2 and _rel(m_got, m_ref) < 8e-2
+    s1_ref, m1_ref = oracle.mtp_run(toks[60:61], lanes_ref[59:60], mst)
+    s1, m1 = model.mtp_run(toks[60:61].to(DEV), lanes[59:60], 59, bt)
+    assert _rel(s1, s1_ref) < 8e-2
+    s2_ref, _ = oracle.mtp_run(toks[61:62], m1_ref, mst, add_embedding=False)
+    s2, _ = model.mtp_run(toks[61:62].to(DEV), m1.clone(), 60, bt, add_embedding=False)
+    assert _rel(s2, s2_ref) < 8e-2
+    # ---- speculative decoding == the model's own greedy decoding, with accepted drafts fed by a hook
+    prompt = toks[:50].tolist()
+    model.zero_state(0)
+    lg = model.prefill(toks[:50].to(DEV), 0, 0, bt)
+    ref, margin = [int(lg.argmax())], [float(lg.topk(2).values.diff().abs())]
+    for i in range(23):
+        model.set_rows(1, [ref[-1]], [50 + i], [0], [bt.tolist()])
+        nxt, lg = model.decode(1)
+        ref.append(int(nxt[0]))
+        margin.append(float(lg[0].topk(2).values.diff().abs()))
+
+    def agree(out):
+        """Equal up to the first position whose top-2 margin is within the kernels' rounding noise (the
+        verify pass scores with the prefill kernels, plain decoding with the decode kernels)."""
+        for i, (a, b) in enumerate(zip(out, ref)):
+            if a != b:
+                return margin[i] < 0.02
+        return len(out) == len(ref)
+
+    out, stats = model.spec_generate(prompt, 24, k=3, slot=0, block_table=bt)
+    assert agree(out) and stats["drafted"] == 3 * stats["rounds"]
+    rounds = []
+
+    def hook(position, drafts):
+        i = position - len(prompt)
+        good = len(rounds) % 4
+        rounds.append(good)
+        return [ref[i + j] if j < good and i + j < len(ref) else (drafts[j] + 1) % cfg.vocab_size for j in range(3)]
+
+    for reuse in (True, False):
+        rounds.clear()
+        out, stats = model.spec_generate(prompt, 24, k=3, slot=0, block_table=bt, index_reuse=reuse, draft_hook=hook)
+        assert agree(out), (reuse, out, ref)
+        assert stats["accepted"] > 0
+    from coffin_b200.ops import kernels as K
+    torch.cuda.synchronize()
+    K.check_status()
