@@ -43,24 +43,47 @@ __global__ void __launch_bounds__(256) tp_pf_reduce_gather_kernel(const TpPfDev*
   const int row0 = d->rank * rpr;
   const int nrows = max(0, min(rpr, T - row0));
   const bf16* in = d->inbox[d->rank];
-  for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < (int64_t)nrows * vec; i += (int64_t)gridDim.x * 256) {
-    const int lr = (int)(i / vec), c = (int)(i % vec) * 8;
-    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-    for (int r = 0; r < world; ++r) {
-      float f[8];
-      bf16x8_to_float(__ldcg(reinterpret_cast<const uint4*>(in + ((int64_t)r * rpr + lr) * W + c)), f);
+  // four 16-byte columns per thread and pass: all loads of a pass are issued before the first add, so a
+  // thread has up to 4 x (world + 1) loads in flight instead of one (the kernel is latency bound)
+  constexpr int U = 4;
+  const int64_t total = (int64_t)nrows * vec, stride = (int64_t)gridDim.x * 256;
+  for (int64_t i0 = (int64_t)blockIdx.x * 256 + threadIdx.x; i0 < total; i0 += stride * U) {
+    uint4 part[U][kTpMaxWorld], res[U];
 #pragma unroll
-      for (int e = 0; e < 8; ++e) acc[e] += f[e];
-    }
-    if (residual) {
-      float f[8];
-      bf16x8_to_float(*reinterpret_cast<const uint4*>(residual + (int64_t)(row0 + lr) * ldr + c), f);
+    for (int u = 0; u < U; ++u) {
+      const int64_t i = i0 + u * stride;
+      if (i >= total) break;
+      const int lr = (int)(i / vec), c = (int)(i % vec) * 8;
 #pragma unroll
-      for (int e = 0; e < 8; ++e) acc[e] += f[e];
+      for (int r = 0; r < kTpMaxWorld; ++r)
+        if (r < world) part[u][r] = __ldcg(reinterpret_cast<const uint4*>(in + ((int64_t)r * rpr + lr) * W + c));
+      if (residual) res[u] = *reinterpret_cast<const uint4*>(residual + (int64_t)(row0 + lr) * ldr + c);
     }
-    const uint4 v = float_to_bf16x8(acc);
-    for (int p = 0; p < world; ++p)
-      *reinterpret_cast<uint4*>(d->out[p] + (int64_t)(row0 + lr) * W + c) = v;
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int64_t i = i0 + u * stride;
+      if (i >= total) break;
+      const int lr = (int)(i / vec), c = (int)(i % vec) * 8;
+      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int r = 0; r < kTpMaxWorld; ++r) {
+        if (r < world) {
+          float f[8];
+          bf16x8_to_float(part[u][r], f);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) acc[e] += f[e];
+        }
+      }
+      if (residual) {
+        float f[8];
+        bf16x8_to_float(res[u], f);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[e] += f[e];
+      }
+      const uint4 v = float_to_bf16x8(acc);
+      for (int p = 0; p < world; ++p)
+        *reinterpret_cast<uint4*>(d->out[p] + (int64_t)(row0 + lr) * W + c) = v;
+    }
   }
   __threadfence_system();
   __syncthreads();
@@ -321,6 +344,63 @@ __global__ void __launch_bounds__(1024) tp_pull_norm_kernel(const TpComm tp, int
   }
 }
 }  // namespace
+
+// Vocabulary-parallel arg-max without gathering the logits: every rank holds the arg-max of its own
+// vocabulary slice (local index per row), sends {value, global index} of every row to every rank as two
+// {word, epoch} pairs of `site`, polls the peers' pairs (bounded) and keeps the best - ties go to the
+// lowest index, so all ranks agree.  One warp per row, one CTA.  Replaces an all-gather of
+// [rows, vocabulary] fp32 logits plus a full-width arg-max.
+namespace {
+__device__ __forceinline__ unsigned long long tp_wait_pair(const TpComm& c, int64_t elem, unsigned e, int r) {
+  unsigned long long v = tp_ld_pair(c.my_inbox, elem);
+  if ((unsigned)(v >> 32) != e && !tp_status_set(c.status)) {
+    const unsigned long long t0 = tp_now_ns(), limit = c.wait_ns ? c.wait_ns : kTpWaitNs;
+    unsigned spins = 0;
+    while ((unsigned)(v >> 32) != e) {
+      if ((++spins & 63u) == 0) {
+        if (tp_status_set(c.status)) break;
+        if (tp_now_ns() - t0 > limit) {
+          atomicCAS(c.status, 0, 16 + r);
+          break;
+        }
+      }
+      v = tp_ld_pair(c.my_inbox, elem);
+    }
+  }
+  return v;
+}
+
+__global__ void __launch_bounds__(256) tp_argmax_kernel(const TpComm tp, int site, const float* __restrict__ logits,
+                                                         int64_t ld, const int64_t* __restrict__ local_idx,
+                                                         int vocab_off, int64_t* __restrict__ next, int M) {
+  griddep_launch();
+  griddep_wait();
+  if ((threadIdx.x & 31) != 0) return;
+  const unsigned e = *tp.epoch;
+  for (int m = threadIdx.x >> 5; m < M; m += 8) {
+    const int64_t li = local_idx[m];
+    tp_push_value(tp, site, m * 2, logits[(int64_t)m * ld + li]);
+    tp_push_value(tp, site, m * 2 + 1, __int_as_float((int)li + vocab_off));
+  }
+  for (int m = threadIdx.x >> 5; m < M; m += 8) {
+    float v = -INFINITY;
+    int ix = 0x7fffffff;
+    for (int r = 0; r < tp.world; ++r) {
+      const int64_t elem = ((int64_t)site * tp.world + r) * tp.slot_floats + m * 2;
+      const float ov = __uint_as_float((unsigned)tp_wait_pair(tp, elem, e, r));
+      const int oi = (int)(unsigned)tp_wait_pair(tp, elem + 1, e, r);
+      if (ov > v || (ov == v && oi < ix)) { v = ov; ix = oi; }
+    }
+    next[m] = ix == 0x7fffffff ? 0 : ix;
+  }
+}
+}  // namespace
+CB_EXPORT int cb_tp_argmax(const void* tp, int64_t site, const void* logits, int64_t ld, const void* local_idx,
+                           int64_t vocab_off, void* next, int64_t M, void* stream) {
+  if (!tp || !logits || !local_idx || !next || site < 0 || M < 1 || M > 64) return CB_ERR_ARG;
+  return (int)cb_launch(tp_argmax_kernel, dim3(1), dim3(256), 0, (cudaStream_t)stream, *(const TpComm*)tp, (int)site,
+                        (const float*)logits, ld, (const int64_t*)local_idx, (int)vocab_off, (int64_t*)next, (int)M);
+}
 
 // Producer side for projections whose kernel has no push epilogue (the int4 decode projection): store
 // fp32 partial rows [M, N] into this rank's slot of `site` on every rank, paired with the step's epoch.

@@ -624,6 +624,7 @@ class Qwen35Model:
                 "logits": torch.zeros(M, c.vocab_size, dtype=torch.float32, device=dev),
                 "logits_local": None,
                 "next": torch.zeros(M, dtype=torch.int64, device=dev),
+                "next_local": torch.zeros(M, dtype=torch.int64, device=dev),
                 "hidden": torch.zeros(M, H, dtype=bf, device=dev),
                 "nsplit": nsplit,
                 "part_o": torch.zeros(M, c.num_attention_heads, nsplit, c.head_dim, dtype=torch.float32, device=dev),
@@ -727,9 +728,17 @@ class Qwen35Model:
             return
         self._gemv(self.lm_head, None, b["logits_local"], norm=(cur, carry, self.final_gain, nxt, self.eps),
                    tp=comm, pull_site=pull)
-        if self.tp_world > 1:
-            b["logits"].copy_(self._gather_logits(b["logits_local"], M))
-        K.argmax(b["logits"], b["next"])
+        if self.tp_world > 1 and not self.full_logits and self.tp.n_sites > 2 * len(self.layers):
+            # greedy rows only need the arg-max: each rank's best {value, index} goes through the inbox
+            # (site after the layers' sites) instead of an all-gather of the logits
+            K.argmax(b["logits_local"], b["next_local"])
+            K.call("tp_argmax", self.tp.cstruct_ref(), 2 * len(self.layers), b["logits_local"], b["logits_local"].stride(0),
+                   b["next_local"], self.tp_rank * self.vocab_local, b["next"], M)
+            K._count()
+        else:
+            if self.tp_world > 1:
+                b["logits"].copy_(self._gather_logits(b["logits_local"], M))
+            K.argmax(b["logits"], b["next"])
         b["final_res"] = nxt
         if self._advance:
             self.advance_rows(M)
@@ -815,11 +824,21 @@ class Qwen35Model:
         if tpw:
             # vocabulary-parallel head: every rank needs the arg-max over the whole vocabulary
             b["logits_local"].copy_(b["logits_bf"])
-            b["logits"].copy_(self._gather_logits(b["logits_local"], M))
+            K._count()
+            if not self.full_logits and self.tp.n_sites > 2 * len(self.layers):
+                # greedy rows: each rank's best {value, index} per row through the inbox, no logits gather
+                self.tp.epoch_bump()
+                K.argmax(b["logits_local"], b["next_local"])
+                K.call("tp_argmax", self.tp.cstruct_ref(), 2 * len(self.layers), b["logits_local"],
+                       b["logits_local"].stride(0), b["next_local"], self.tp_rank * self.vocab_local, b["next"], M)
+                K._count()
+            else:
+                b["logits"].copy_(self._gather_logits(b["logits_local"], M))
+                K.argmax(b["logits"], b["next"])
         else:
             b["logits"].copy_(b["logits_bf"])
-        K._count()
-        K.argmax(b["logits"], b["next"])
+            K._count()
+            K.argmax(b["logits"], b["next"])
         b["final_res"] = res
         if self._advance:
             self.advance_rows(M)

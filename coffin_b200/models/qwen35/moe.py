@@ -14,8 +14,13 @@ import dataclasses
 
 import torch
 
+import os
+
 from ...config import ModelConfig
 from ...ops import kernels as K
+
+PREFILL_CACHE_BYTES = int(float(os.environ.get("COFFIN_MOE_PREFILL_CACHE_GB", "64")) * (1 << 30))
+CACHE_HEADROOM = 16 << 30      # HBM that must stay free after an expansion is kept
 
 
 def _pad8(n: int) -> int:
@@ -34,6 +39,7 @@ class MoEWeights:
     e_hi: int = 0
     ep_world: int = 1
     bufs: dict = dataclasses.field(default_factory=dict)
+    _expanded: dict = dataclasses.field(default_factory=dict)   # id(W4 stack) -> kept bf16 expansion
 
     @classmethod
     def from_state_dict(cls, cfg: ModelConfig, sd: dict, p: str, dev, ep_rank: int = 0, ep_world: int = 1,
@@ -104,6 +110,8 @@ class MoEWeights:
             sh_down = sdn[:, c0:c1].to(dev, bf).contiguous()
         return cls(cfg, torch.cat(rows).contiguous(), gu, dn, sh_gu, sh_down, e_lo, e_hi, ep_world)
 
+    cache_used = 0          # bytes of bf16 expansions kept by all MoE layers of the process
+
     def tensors(self) -> list[torch.Tensor]:
         return [t for t in (self.router, self.gate_up, self.down, self.sh_gu, self.sh_down) if t is not None]
 
@@ -116,11 +124,23 @@ class MoEWeights:
         return stack[e] if isinstance(stack, torch.Tensor) else K.w4_dequant(stack.wq[e], stack.scale[e])
 
     def _stack(self, stack) -> torch.Tensor:
-        """bf16 ``[E, rows, K]`` weights of all local experts (W4 storage is expanded for the call)."""
+        """bf16 ``[E, rows, K]`` weights of all local experts.  W4 storage is expanded on the first prefill
+        and the expansion is kept while HBM allows (``COFFIN_MOE_PREFILL_CACHE_GB``, default 64, and at least
+        ``CACHE_HEADROOM`` bytes left free): decode streams the int4 codes (bandwidth), prefill multiplies
+        the bf16 copy on the tensor cores (compute) - expanding 1.6 GB per layer on every call cost three
+        times the expert GEMMs themselves.  Without room the expansion is redone per call."""
         if isinstance(stack, torch.Tensor):
             return stack
+        hit = self._expanded.get(id(stack))
+        if hit is not None:
+            return hit
         E, N, half = stack.wq.shape
-        return K.w4_dequant(stack.wq.reshape(E * N, half), stack.scale.reshape(E * N, -1)).reshape(E, N, half * 2)
+        out = K.w4_dequant(stack.wq.reshape(E * N, half), stack.scale.reshape(E * N, -1)).reshape(E, N, half * 2)
+        size = out.numel() * 2
+        if MoEWeights.cache_used + size <= PREFILL_CACHE_BYTES and torch.cuda.mem_get_info(out.device)[0] > CACHE_HEADROOM:
+            MoEWeights.cache_used += size
+            self._expanded[id(stack)] = out
+        return out
 
     # ------------------------------------------------------------------ buffers
     def _b(self, T: int, dev) -> dict:

@@ -23,6 +23,7 @@ LAUNCHES = 0        # kernels launched through this module (bench bookkeeping)
 STREAM_GEMV = True   # route single-row projections to the cp.async streaming kernel (when GEMV_IMPL == 'scalar')
 GEMV_IMPL = "mma"     # 'mma': tensor-core GEMV for every M <= 8; 'scalar': FMA kernels
 ATTN_TC = os.environ.get("COFFIN_ATTN_TC", "1") != "0"   # dense causal prefill attention on tcgen05 (else the mma.sync kernel)
+ATTN_TC_TRACE = None  # debugging: int64 device tensor [tiles, 8] that receives the stamps of one CTA of the tcgen05 attention kernel
 ATTN_TC_MIN_T = 32    # shorter query blocks (verify passes, tails) stay on the mma.sync kernel
 
 
@@ -507,7 +508,7 @@ def attn_prefill(q, proj, kpool, vpool, block_table, out, *, q_pos0, nh, nkv, hd
             and kpool.dtype == torch.bfloat16 and q.is_contiguous() and kpool.is_contiguous() and vpool.is_contiguous()):
         # dense causal attention over bf16 pages: the tcgen05 kernel (TMA pages, TMEM accumulators)
         call("attn_prefill_tc", q, proj, proj.stride(0) if proj is not None else 0, kpool, vpool, kpool.shape[0],
-             block_table, out, out.stride(0), T, q_pos0, nh, nkv, hd, status_word(q.device))
+             block_table, out, out.stride(0), T, q_pos0, nh, nkv, hd, status_word(q.device), ATTN_TC_TRACE)
         _count()
         return out
     call("attn_prefill", q, proj, proj.stride(0) if proj is not None else 0, kpool, vpool, block_table, out,

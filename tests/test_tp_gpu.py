@@ -250,11 +250,26 @@ def _rank_main(rank, world, port, out):
     for i in range(32, 44):
         model.set_rows(1, [int(toks[i])], [i], [0], [bt.tolist()])
         logits.append(model.decode(1, graph=i >= 36)[1][0].float().cpu())
+    # greedy rows skip the logits gather: every rank's best {value, index} goes through the inbox and all
+    # ranks must name the arg-max of the full vocabulary
+    snap = model.snapshot_state(0)
+    model.set_rows(1, [int(toks[43])], [44], [0], [bt.tolist()])
+    nxt_full, lg_full = model.decode(1, graph=False)
+    want = int(lg_full[0].argmax())
+    assert int(nxt_full[0]) == want
+    model.restore_state(0, snap)
+    model.full_logits = False
+    greedy = []
+    for rep in range(3):
+        model.restore_state(0, snap)
+        model.set_rows(1, [int(toks[43])], [44], [0], [bt.tolist()])
+        greedy.append(int(model.decode(1, graph=rep >= 1)[0][0]))
+    model.full_logits = True
     torch.cuda.synchronize()
     status = model.tp.status()
     dist.barrier()
     if rank == 0:
-        torch.save({"logits": torch.stack(logits), "status": status}, out)
+        torch.save({"logits": torch.stack(logits), "status": status, "greedy": greedy, "want": want}, out)
     from coffin_b200.parallel.control import shutdown
     comm = getattr(model, "tp", None)
     if hasattr(model, "_graphs"):
@@ -271,6 +286,7 @@ def test_two_rank_tensor_parallel_matches_oracle(tmp_path):
     run_ranks(_rank_main, 2, args=(_free_port(), out), timeout=RANK_TIMEOUT, env=RANK_ENV)
     got = torch.load(out)
     assert got["status"] == 0
+    assert got["greedy"] == [got["want"]] * 3, "the vocabulary-parallel arg-max must name the full arg-max"
     cfg = preset("tiny")
     sd = random_state_dict(cfg, 0)
     sd_b = {k: (v.to(torch.bfloat16).float() if not k.endswith(("A_log", "dt_bias")) else v) for k, v in sd.items()}
@@ -418,11 +434,27 @@ def _wide_rank_main(rank, world, port, out, mode="tp", rows=16):
         model.set_rows(M, [int(seqs[r][lens[r] + step]) for r in range(rows)], [lens[r] + step for r in range(rows)],
                        list(range(rows)), tables)
         logits.append(model.decode(M, graph=step >= 1)[1][:rows].float().cpu())
+    greedy_ok = True
+    if mode == "tp":
+        # the same step once more from the same states, greedy: the arg-max goes through the inbox
+        snaps = [model.snapshot_state(r) for r in range(rows)]
+        args = ([int(seqs[r][lens[r] + 3]) for r in range(rows)], [lens[r] + 4 for r in range(rows)], list(range(rows)), tables)
+        model.set_rows(M, *args)
+        nxt, lg = model.decode(M, graph=False)
+        want = lg[:rows].argmax(-1).tolist()
+        for r in range(rows):
+            model.restore_state(r, snaps[r])
+        model.full_logits = False
+        model.set_rows(M, *args)
+        got = model.decode(M, graph=False)[0][:rows].tolist()
+        model.full_logits = True
+        greedy_ok = got == want
     torch.cuda.synchronize()
     status = model.tp.status()
     dist.barrier()
     if rank == 0:
-        torch.save({"logits": torch.stack(logits), "status": status, "lens": lens, "seqs": [s.tolist() for s in seqs]}, out)
+        torch.save({"logits": torch.stack(logits), "status": status, "lens": lens, "seqs": [s.tolist() for s in seqs],
+                    "greedy_ok": greedy_ok}, out)
     from coffin_b200.parallel.control import shutdown
     model._graphs.clear()
     model.tp.close()
@@ -439,6 +471,7 @@ def test_two_rank_wide_bucket_matches_oracle(tmp_path, mode, rows, tol):
     run_ranks(_wide_rank_main, 2, args=(_free_port(), out, mode, rows), timeout=RANK_TIMEOUT, env=RANK_ENV)
     got = torch.load(out)
     assert got["status"] == 0
+    assert got["greedy_ok"], "the vocabulary-parallel arg-max of a wide bucket must name the full arg-max"
     cfg = preset("tiny" if mode == "tp" else "tiny-moe")
     sd = random_state_dict(cfg, 0)
     sd_b = {k: (v.to(torch.bfloat16).float() if not k.endswith(("A_log", "dt_bias")) else v) for k, v in sd.items()}
