@@ -26,8 +26,10 @@ __global__ void __launch_bounds__(256) tp_pf_scatter_kernel(const TpPfDev* d, co
     bf16* dst = d->inbox[owner] + ((int64_t)d->rank * rpr + lr) * W + c;
     *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(src + (int64_t)row * lds + c);
   }
-  __threadfence_system();
+  // one system-scope fence per CTA: the barrier orders every thread's stores before thread 0's fence,
+  // which is cumulative, so the flag it publishes afterwards covers them all
   __syncthreads();
+  if (threadIdx.x == 0) __threadfence_system();
   if (threadIdx.x == 0) tp_pf_publish(d, 1, seq, gridDim.x);
 }
 
@@ -85,8 +87,10 @@ __global__ void __launch_bounds__(256) tp_pf_reduce_gather_kernel(const TpPfDev*
         *reinterpret_cast<uint4*>(d->out[p] + (int64_t)(row0 + lr) * W + c) = v;
     }
   }
-  __threadfence_system();
+  // one system-scope fence per CTA: the barrier orders every thread's stores before thread 0's fence,
+  // which is cumulative, so the flag it publishes afterwards covers them all
   __syncthreads();
+  if (threadIdx.x == 0) __threadfence_system();
   if (threadIdx.x == 0) tp_pf_publish(d, 2, seq, gridDim.x);
 }
 

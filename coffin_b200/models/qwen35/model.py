@@ -102,6 +102,19 @@ class QW4:
         """bf16 ``[N, K]`` (2-D only)."""
         return K.w4_dequant(self.wq, self.scale)
 
+    def expanded(self) -> torch.Tensor:
+        """The bf16 expansion for a tensor-core GEMM, kept after the first call while HBM allows: decode
+        streams the int4 codes (bandwidth bound), prefill and wide decode buckets multiply the bf16 copy
+        (compute bound) instead of expanding the projection on every call."""
+        kept = getattr(self, "_kept", None)
+        if kept is not None:
+            return kept
+        out = self.dequant()
+        from .moe import keep_expansion
+        if keep_expansion(out):
+            self._kept = out
+        return out
+
 
 def _pad8(n: int) -> int:
     return (n + 7) // 8 * 8
@@ -355,7 +368,7 @@ class Qwen35Model:
             q, sc = K.quant_rows(A, swiglu=swiglu_in)
             return K.gemm_i8(q, sc, W.wq, W.scale, out=out, residual=residual, push=push)
         if isinstance(W, QW4):
-            W = W.dequant()                 # expanded to bf16 for the chunk; the tcgen05 GEMM does the rest
+            W = W.expanded()                # bf16 copy (kept while HBM allows); the tcgen05 GEMM does the rest
         if swiglu_in:
             A = K.swiglu(A)
         return K.gemm(A, W, out=out, residual=residual, push=push)
@@ -919,7 +932,7 @@ class Qwen35Model:
         if self.graph_pool is None:
             self.graph_pool = torch.cuda.graph_pool_handle()
         l0 = K.LAUNCHES
-        with torch.cuda.graph(g, pool=self.graph_pool):
+        with K.capture_graph(g, pool=self.graph_pool):
             self._decode_body(M)
         self._step_launches[M] = K.LAUNCHES - l0
         self._graphs[gkey] = g

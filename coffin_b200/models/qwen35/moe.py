@@ -21,6 +21,18 @@ from ...ops import kernels as K
 
 PREFILL_CACHE_BYTES = int(float(os.environ.get("COFFIN_MOE_PREFILL_CACHE_GB", "64")) * (1 << 30))
 CACHE_HEADROOM = 16 << 30      # HBM that must stay free after an expansion is kept
+_cache_used = 0                # bytes of bf16 expansions kept by the process
+
+
+def keep_expansion(t: torch.Tensor) -> bool:
+    """Account a bf16 expansion of int4 weights that its owner wants to keep for later prefill calls;
+    False when the budget or the free HBM says it has to be redone per call."""
+    global _cache_used
+    size = t.numel() * t.element_size()
+    if not t.is_cuda or _cache_used + size > PREFILL_CACHE_BYTES or torch.cuda.mem_get_info(t.device)[0] < CACHE_HEADROOM:
+        return False
+    _cache_used += size
+    return True
 
 
 def _pad8(n: int) -> int:
@@ -110,8 +122,6 @@ class MoEWeights:
             sh_down = sdn[:, c0:c1].to(dev, bf).contiguous()
         return cls(cfg, torch.cat(rows).contiguous(), gu, dn, sh_gu, sh_down, e_lo, e_hi, ep_world)
 
-    cache_used = 0          # bytes of bf16 expansions kept by all MoE layers of the process
-
     def tensors(self) -> list[torch.Tensor]:
         return [t for t in (self.router, self.gate_up, self.down, self.sh_gu, self.sh_down) if t is not None]
 
@@ -136,9 +146,7 @@ class MoEWeights:
             return hit
         E, N, half = stack.wq.shape
         out = K.w4_dequant(stack.wq.reshape(E * N, half), stack.scale.reshape(E * N, -1)).reshape(E, N, half * 2)
-        size = out.numel() * 2
-        if MoEWeights.cache_used + size <= PREFILL_CACHE_BYTES and torch.cuda.mem_get_info(out.device)[0] > CACHE_HEADROOM:
-            MoEWeights.cache_used += size
+        if keep_expansion(out):
             self._expanded[id(stack)] = out
         return out
 
@@ -178,10 +186,19 @@ class MoEWeights:
         c = self.cfg
         E, k, H, I = c.num_experts, c.num_experts_per_tok, c.hidden_size, c.moe_intermediate_size
         normed = b["normed"][:T]
-        # router logits: small row counts go through the GEMV (fp32 logits), 1, 2, 4 or 8 rows at a time
-        for s in range(0, T, 8):
-            e = min(T, s + 8)
-            K.gemv(self.router, normed[s:e], b["logits"][s:e])
+        # router logits: up to 8 rows go through the GEMV (fp32 logits); more rows are one tensor-core GEMM
+        # (eight 8-row GEMV launches per layer were a fifth of a 64-row step)
+        wide = T > 8
+        if wide:
+            if "logits_bf" not in b:
+                b["logits_bf"] = torch.zeros(T, self.router.shape[0], dtype=torch.bfloat16, device=normed.device)
+                if self.sh_gu is not None:
+                    b["sh_gu_out"] = torch.zeros(T, self.sh_gu.shape[0], dtype=torch.bfloat16, device=normed.device)
+            K.gemm(normed, self.router, out=b["logits_bf"])
+            b["logits"][:T].copy_(b["logits_bf"])
+            K._count()
+        else:
+            K.gemv(self.router, normed, b["logits"][:T])
         K.call("moe_router", b["logits"], b["logits"].stride(0), T, E, k, int(c.norm_topk_prob), b["idx"], b["w"],
                self.e_lo, self.e_hi)
         K._count()
@@ -195,10 +212,13 @@ class MoEWeights:
             K._count(2)
         shared = gate = None
         if self.sh_gu is not None:
-            for s in range(0, T, 8):
-                e = min(T, s + 8)
-                K.gemv(self.sh_gu, normed[s:e], b["sh_inter"][s:e], swiglu=True)
-                K.gemv(self.sh_down, b["sh_inter"][s:e], b["sh_out"][s:e])
+            if wide:
+                K.gemm(normed, self.sh_gu, out=b["sh_gu_out"])
+                K.swiglu(b["sh_gu_out"], out=b["sh_inter"][:T])
+                K.gemm(b["sh_inter"][:T], self.sh_down, out=b["sh_out"][:T])
+            else:
+                K.gemv(self.sh_gu, normed, b["sh_inter"][:T], swiglu=True)
+                K.gemv(self.sh_down, b["sh_inter"][:T], b["sh_out"][:T])
             shared, gate = b["sh_out"], b["logits"][:, E:]
         K.call("moe_combine", b["y"], b["w"], shared, gate, b["logits"].stride(0), out, T, H, k,
                tp.cstruct_ref() if tp is not None and push_site >= 0 else None, push_site)

@@ -402,7 +402,7 @@ class Qwen4ExpModel:
         if isinstance(W, QW4):
             if small:
                 return K.gemv_w4(W.wq, W.scale, x, out)
-            W = W.dequant()
+            W = W.expanded()
         if small:
             return K.gemv(W, x, out)
         if out.dtype == torch.bfloat16:

@@ -7,6 +7,7 @@ at the granularity of the fused kernels, not op for op.
 """
 from __future__ import annotations
 
+import contextlib
 import math
 import os
 
@@ -25,6 +26,25 @@ GEMV_IMPL = "mma"     # 'mma': tensor-core GEMV for every M <= 8; 'scalar': FMA 
 ATTN_TC = os.environ.get("COFFIN_ATTN_TC", "1") != "0"   # dense causal prefill attention on tcgen05 (else the mma.sync kernel)
 ATTN_TC_TRACE = None  # debugging: int64 device tensor [tiles, 8] that receives the stamps of one CTA of the tcgen05 attention kernel
 ATTN_TC_MIN_T = 32    # shorter query blocks (verify passes, tails) stay on the mma.sync kernel
+
+
+@contextlib.contextmanager
+def capture_graph(graph: "torch.cuda.CUDAGraph", pool=None):
+    """``torch.cuda.graph`` with the garbage collector held off.  A collection that runs while a
+    stream is capturing may finalise CUDA graphs of dead models; destroying a graph is not permitted
+    during a capture and invalidates it (the next launch fails with a stream-capture error).  Dead
+    objects are therefore collected before the capture starts and automatic collection is disabled
+    until it ends."""
+    import gc
+    gc.collect()
+    was_enabled = gc.isenabled()
+    gc.disable()
+    try:
+        with torch.cuda.graph(graph, pool=pool):
+            yield
+    finally:
+        if was_enabled:
+            gc.enable()
 
 
 def _count(n: int = 1) -> None:

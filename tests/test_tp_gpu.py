@@ -222,7 +222,7 @@ def test_one_shot_all_reduce_protocol_on_one_gpu():
         tp.oneshot(part, res_out=out)
     torch.cuda.current_stream().wait_stream(s)
     graph = torch.cuda.CUDAGraph()
-    with torch.cuda.graph(graph):
+    with K.capture_graph(graph):
         tp.oneshot(part, res_out=out)
     for i in range(5):
         part.fill_(float(i + 1))
