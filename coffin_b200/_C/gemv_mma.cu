@@ -35,6 +35,10 @@ struct MmaArgs {
   // grouped (mixture-of-experts) mode: blockIdx.y is a slot; slot s multiplies activation row
   // slot_xrow[s] by the weights of expert slot_expert[s] and writes output row s.  M must be 1.
   const int* slot_expert; const int* slot_xrow; int64_t expert_stride;
+  // fused consumer of a pushing projection (tensor parallel): the last CTA of the grid to finish pulls the
+  // ranks' sums of push_site for every row, adds tail_res_in, stores the new residual in tail_res_out and
+  // its RMSNorm (gain tail_gain) in tail_out - what a separate pull kernel would do one launch later
+  const bf16* tail_res_in; const float* tail_gain; bf16* tail_res_out; bf16* tail_out; float tail_eps;
   TpComm tp;
 };
 
@@ -335,25 +339,25 @@ __global__ void __launch_bounds__(kT, 3) gemv_mma_kernel(const MmaArgs a_in) {
         if (last) a.tickets[unit_id] = 0;
       }
       __syncthreads();
-      if (!last) return;
-      __threadfence();
-      const float* all = a.ws + (size_t)unit_id * kMaxKcta * 256;
-      for (int idx = tid; idx < 128; idx += nT) {
-        const int r = idx / 8, m = idx % 8;
-        const int64_t row = (int64_t)unit_id * 16 + r;
-        if (m >= M || row >= a.N) continue;
-        float v = 0.f, v2 = 0.f;
-        for (int c = 0; c < kcta; ++c) {
-          v += __ldcg(all + c * 256 + idx);
-          if (SWIGLU) v2 += __ldcg(all + c * 256 + 128 + idx);
+      if (last) {
+        __threadfence();
+        const float* all = a.ws + (size_t)unit_id * kMaxKcta * 256;
+        for (int idx = tid; idx < 128; idx += nT) {
+          const int r = idx / 8, m = idx % 8;
+          const int64_t row = (int64_t)unit_id * 16 + r;
+          if (m >= M || row >= a.N) continue;
+          float v = 0.f, v2 = 0.f;
+          for (int c = 0; c < kcta; ++c) {
+            v += __ldcg(all + c * 256 + idx);
+            if (SWIGLU) v2 += __ldcg(all + c * 256 + 128 + idx);
+          }
+          if (SWIGLU) v = silu_f(v) * v2;
+          if (a.push_site >= 0) tp_push_value(a.tp, a.push_site, (int64_t)m * a.N + row, v);
+          else if (OUT_F32) reinterpret_cast<float*>(a.y)[(int64_t)m * a.ldy + row] = v;
+          else reinterpret_cast<bf16*>(a.y)[(int64_t)m * a.ldy + row] = __float2bfloat16(v);
         }
-        if (SWIGLU) v = silu_f(v) * v2;
-        if (a.push_site >= 0) tp_push_value(a.tp, a.push_site, (int64_t)m * a.N + row, v);
-        else if (OUT_F32) reinterpret_cast<float*>(a.y)[(int64_t)m * a.ldy + row] = v;
-        else reinterpret_cast<bf16*>(a.y)[(int64_t)m * a.ldy + row] = __float2bfloat16(v);
       }
-      return;
-    }
+    } else {
     // one thread per (round, row block of the round, row in block, batch row): fixed-order sum over k-slices
     const int per_round = rbr * 16 * 8;
     for (int idx = tid; idx < a.rounds * per_round; idx += nT) {
@@ -371,6 +375,45 @@ __global__ void __launch_bounds__(kT, 3) gemv_mma_kernel(const MmaArgs a_in) {
       if (a.push_site >= 0) tp_push_value(a.tp, a.push_site, (int64_t)m * a.N + row, v);
       else if (OUT_F32) reinterpret_cast<float*>(a.y)[(int64_t)m * a.ldy + row] = v;
       else reinterpret_cast<bf16*>(a.y)[(int64_t)m * a.ldy + row] = __float2bfloat16(v);
+    }
+    }
+  }
+  // ---- fused consumer: the last CTA to finish does the pull + residual add + RMSNorm of the rows --------
+  // Every rank's partial sums travel as {value, epoch} pairs, this rank's own included, so the CTA needs
+  // no fence: it polls (bounded) until every pair of the site carries this step's epoch.  The arithmetic
+  // is the one of tp_pull_norm_kernel (comm.cu); two passes over the row instead of a row buffer.
+  if (a.tail_out != nullptr) {
+    __shared__ bool grid_last;
+    __syncthreads();
+    if (tid == 0) {
+      unsigned* ticket = a.tp.arrive + a.push_site;
+      grid_last = atomicAdd(ticket, 1u) == gridDim.x * gridDim.y - 1;
+      if (grid_last) *ticket = 0;
+    }
+    __syncthreads();
+    if (grid_last) {
+      const int64_t W = a.N, wch = W >> 3;
+      for (int m = 0; m < M; ++m) {
+        float ss = 0.f;
+        for (int64_t c = tid; c < wch; c += nT) {
+          float f[8], pulled[8];
+          bf16x8_to_float(*reinterpret_cast<const uint4*>(a.tail_res_in + m * W + c * 8), f);
+          tp_pull8(a.tp, a.push_site, m * W + c * 8, pulled);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) { f[i] = __bfloat162float(__float2bfloat16(f[i] + pulled[i])); ss += f[i] * f[i]; }
+          *reinterpret_cast<uint4*>(a.tail_res_out + m * W + c * 8) = float_to_bf16x8(f);
+        }
+        const float rstd = rsqrtf(block_sum(ss, red) / (float)W + a.tail_eps);
+        for (int64_t c = tid; c < wch; c += nT) {          // each thread re-reads the chunks it wrote
+          float f[8];
+          bf16x8_to_float(*reinterpret_cast<const uint4*>(a.tail_res_out + m * W + c * 8), f);
+          const float4 g0 = *reinterpret_cast<const float4*>(a.tail_gain + c * 8);
+          const float4 g1 = *reinterpret_cast<const float4*>(a.tail_gain + c * 8 + 4);
+          f[0] *= rstd * g0.x; f[1] *= rstd * g0.y; f[2] *= rstd * g0.z; f[3] *= rstd * g0.w;
+          f[4] *= rstd * g1.x; f[5] *= rstd * g1.y; f[6] *= rstd * g1.z; f[7] *= rstd * g1.w;
+          *reinterpret_cast<uint4*>(a.tail_out + m * W + c * 8) = float_to_bf16x8(f);
+        }
+      }
     }
   }
 }
@@ -487,11 +530,35 @@ CB_EXPORT int cb_set_mma_gemv_stage(int64_t n) { g_mma_stage = n < 0 ? 0 : (n > 
 // Sweep rounds prefetched into L2 ahead of the dependency wait (0 = none).
 CB_EXPORT int cb_set_mma_gemv_prefetch(int64_t rounds) { g_mma_pf_rounds = rounds < 0 ? 0 : (int)rounds; return 0; }
 
-// Same contract as cb_gemv_bf16 (M = 1..8, any M in that range).
+// Same contract as cb_gemv_bf16 (M = 1..8, any M in that range).  The `_tail` form adds the fused consumer
+// of a pushing projection: tail_out = rmsnorm(tail_res_in + sum over ranks of push_site) * tail_gain and the
+// sum itself in tail_res_out, done by the last CTA of the grid (the epoch of the step must not change
+// between the push and the next kernel, which holds inside one decode step).
+static int gemv_mma_impl(const void* W, const void* x, void* y, int64_t M, int64_t N, int64_t K,
+                         int64_t ldy, int64_t mode, int64_t up_off, const void* res_in, const void* add,
+                         const void* gain, void* res_out, float eps, const void* tp, int64_t pull_site,
+                         int64_t push_site, const void* tail_res_in, const void* tail_gain, void* tail_res_out,
+                         void* tail_out, float tail_eps, void* stream);
 CB_EXPORT int cb_gemv_mma_bf16(const void* W, const void* x, void* y, int64_t M, int64_t N, int64_t K,
                                int64_t ldy, int64_t mode, int64_t up_off, const void* res_in, const void* add,
                                const void* gain, void* res_out, float eps, const void* tp, int64_t pull_site,
                                int64_t push_site, void* stream) {
+  return gemv_mma_impl(W, x, y, M, N, K, ldy, mode, up_off, res_in, add, gain, res_out, eps, tp, pull_site, push_site,
+                       nullptr, nullptr, nullptr, nullptr, 0.f, stream);
+}
+CB_EXPORT int cb_gemv_mma_bf16_tail(const void* W, const void* x, int64_t M, int64_t N, int64_t K, const void* tp,
+                                    int64_t push_site, const void* tail_res_in, const void* tail_gain,
+                                    void* tail_res_out, void* tail_out, float tail_eps, void* stream) {
+  if (!tp || push_site < 0 || !tail_res_in || !tail_gain || !tail_res_out || !tail_out || N % 8) return CB_ERR_ARG;
+  if (tail_res_out == tail_res_in) return CB_ERR_ARG;
+  return gemv_mma_impl(W, x, nullptr, M, N, K, N, 0, N, nullptr, nullptr, nullptr, nullptr, 0.f, tp, -1, push_site,
+                       tail_res_in, tail_gain, tail_res_out, tail_out, tail_eps, stream);
+}
+static int gemv_mma_impl(const void* W, const void* x, void* y, int64_t M, int64_t N, int64_t K,
+                         int64_t ldy, int64_t mode, int64_t up_off, const void* res_in, const void* add,
+                         const void* gain, void* res_out, float eps, const void* tp, int64_t pull_site,
+                         int64_t push_site, const void* tail_res_in, const void* tail_gain, void* tail_res_out,
+                         void* tail_out, float tail_eps, void* stream) {
   if (!W || (!y && push_site < 0) || (!x && !res_in) || (res_in && !gain)) return CB_ERR_ARG;
   if ((pull_site >= 0 || push_site >= 0) && !tp) return CB_ERR_ARG;
   if (pull_site >= 0 && !res_in) return CB_ERR_ARG;
@@ -503,6 +570,8 @@ CB_EXPORT int cb_gemv_mma_bf16(const void* W, const void* x, void* y, int64_t M,
   a.res_out = (bf16*)res_out; a.eps = eps; a.M = (int)M; a.ksplit = 1; a.rounds = 1;
   a.pull_site = (int)pull_site; a.push_site = (int)push_site;
   a.slot_expert = nullptr; a.slot_xrow = nullptr; a.expert_stride = 0;
+  a.tail_res_in = (const bf16*)tail_res_in; a.tail_gain = (const float*)tail_gain; a.tail_res_out = (bf16*)tail_res_out;
+  a.tail_out = (bf16*)tail_out; a.tail_eps = tail_eps;
   if (tp) a.tp = *(const TpComm*)tp; else memset(&a.tp, 0, sizeof(a.tp));
   const bool sw = mode & 1, f32 = mode & 2, norm = res_in != nullptr;
   cudaStream_t st = (cudaStream_t)stream;
@@ -526,6 +595,7 @@ CB_EXPORT int cb_moe_gemv(const void* W, const void* x, void* y, int64_t n_slots
   a.W = (const bf16*)W; a.x = (const bf16*)x; a.y = y; a.N = N; a.K = K; a.ldy = ldy; a.up_off = N;
   a.res_in = nullptr; a.add = nullptr; a.gain = nullptr; a.res_out = nullptr; a.eps = 0.f; a.M = 1; a.ksplit = 1;
   a.rounds = 1; a.pull_site = -1; a.push_site = -1;
+  a.tail_res_in = nullptr; a.tail_gain = nullptr; a.tail_res_out = nullptr; a.tail_out = nullptr; a.tail_eps = 0.f;
   a.slot_expert = (const int*)slot_expert; a.slot_xrow = (const int*)slot_xrow; a.expert_stride = expert_stride;
   memset(&a.tp, 0, sizeof(a.tp));
   cudaStream_t st = (cudaStream_t)stream;

@@ -108,46 +108,78 @@ __global__ void __launch_bounds__(1024) moe_dispatch_kernel(const int* __restric
                                                             int* __restrict__ pos, int* __restrict__ src_tok,
                                                             int* g_count, int* g_row0, int* g_rows, int* g_expert,
                                                             int max_tiles) {
+  // Shared memory: per-warp histograms [32][E] (a warp's atomics only meet its own lanes), then the
+  // per-expert totals, row offsets and tile offsets.  One CTA: the whole dispatch of a 2048-token chunk
+  // (16384 slots) is ~10 us of shared-memory work; several CTAs would need a grid-wide prefix.
   extern __shared__ int dsm[];
-  int* cnt = dsm;            // [E] slots per expert, then the running cursor of the scatter
-  int* off = dsm + E;        // [E + 1] first sorted row of every expert
-  int* total = dsm + 2 * E + 1;
+  int* wh = dsm;                 // [32][E] slots of expert e seen by warp w; later the warp's running cursor
+  int* cnt = dsm + 32 * E;       // [E]
+  int* off = cnt + E;            // [E + 1] first sorted row of every expert
+  int* toff = off + E + 1;       // [E + 1] first tile of every expert
   griddep_launch();
   griddep_wait();
-  const int tid = threadIdx.x;
-  for (int e = tid; e < E; e += 1024) cnt[e] = 0;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  for (int i = tid; i < 32 * E; i += 1024) wh[i] = 0;
   __syncthreads();
-  for (int s = tid; s < S; s += 1024) {
+  // every warp owns a contiguous range of slots (so that the second pass sees the same slots)
+  const int per = (S + 31) / 32, s0 = warp * per, s1 = min(S, s0 + per);
+  for (int s = s0 + lane; s < s1; s += 32) {
     const int e = idx[s];
-    if (e >= 0 && e < E) atomicAdd(&cnt[e], 1);
+    if (e >= 0 && e < E) atomicAdd(&wh[warp * E + e], 1);
   }
   __syncthreads();
-  if (tid == 0) {
-    int run = 0, nt = 0;
-    for (int e = 0; e < E; ++e) {
-      const int n = cnt[e];
-      off[e] = run;
-      for (int i = 0; i < n; i += 128, ++nt) {
-        if (nt < max_tiles) {
-          g_row0[nt] = run + i;
-          g_rows[nt] = min(128, n - i);
-          g_expert[nt] = e;
-        }
-      }
+  // totals per expert and, in place, the exclusive prefix over warps (the warp's first row inside the expert)
+  for (int e = tid; e < E; e += 1024) {
+    int run = 0;
+    for (int w = 0; w < 32; ++w) {
+      const int n = wh[w * E + e];
+      wh[w * E + e] = run;
       run += n;
     }
-    off[E] = run;
-    *total = run;
-    *g_count = min(nt, max_tiles);
+    cnt[e] = run;
   }
   __syncthreads();
-  for (int e = tid; e < E; e += 1024) cnt[e] = off[e];
-  for (int r = *total + tid; r < S; r += 1024) src_tok[r] = 0;
+  // exclusive prefixes over experts: rows and 128-row tiles (one warp, E <= 1024)
+  if (warp == 0) {
+    int carry_r = 0, carry_t = 0;
+    for (int e0 = 0; e0 < E; e0 += 32) {
+      const int e = e0 + lane;
+      const int n = e < E ? cnt[e] : 0, nt = (n + 127) >> 7;
+      int pr = n, pt = nt;
+#pragma unroll
+      for (int d = 1; d < 32; d <<= 1) {
+        const int ur = __shfl_up_sync(0xffffffffu, pr, d), ut = __shfl_up_sync(0xffffffffu, pt, d);
+        if (lane >= d) { pr += ur; pt += ut; }
+      }
+      if (e < E) { off[e] = carry_r + pr - n; toff[e] = carry_t + pt - nt; }
+      carry_r += __shfl_sync(0xffffffffu, pr, 31);
+      carry_t += __shfl_sync(0xffffffffu, pt, 31);
+    }
+    if (lane == 0) {
+      off[E] = carry_r;
+      toff[E] = carry_t;
+      *g_count = min(carry_t, max_tiles);
+    }
+  }
   __syncthreads();
-  for (int s = tid; s < S; s += 1024) {
+  // tile list: expert e emits its tiles at toff[e]
+  for (int e = tid; e < E; e += 1024) {
+    const int n = cnt[e], r0 = off[e];
+    int nt = toff[e];
+    for (int i = 0; i < n; i += 128, ++nt) {
+      if (nt < max_tiles) {
+        g_row0[nt] = r0 + i;
+        g_rows[nt] = min(128, n - i);
+        g_expert[nt] = e;
+      }
+    }
+  }
+  for (int r = off[E] + tid; r < S; r += 1024) src_tok[r] = 0;
+  // scatter: slot -> sorted row = first row of the expert + rows of earlier warps + this warp's cursor
+  for (int s = s0 + lane; s < s1; s += 32) {
     const int e = idx[s];
     if (e >= 0 && e < E) {
-      const int r = atomicAdd(&cnt[e], 1);
+      const int r = off[e] + atomicAdd(&wh[warp * E + e], 1);
       pos[s] = r;
       src_tok[r] = s / top_k;
     } else {
@@ -190,7 +222,8 @@ CB_EXPORT int cb_moe_combine_pos(const void* y, const void* w, const void* pos, 
                         -1, c, (const int*)pos);
 }
 
-// Expert-major dispatch of S = T * top_k routed slots, one CTA: count per expert, prefix, scatter.
+// Expert-major dispatch of S = T * top_k routed slots, one CTA: per-warp histograms, prefixes over warps and
+// experts, scatter (53 us -> with one shared histogram and a serial prefix the CTA spent its time in barriers).
 //   pos[s]      row of slot s in the expert-sorted order, -1 for a slot whose expert is not local
 //   src_tok[r]  token whose activation row goes to sorted row r (0 for the unused rows at the end)
 //   tile list   m-tiles of at most 128 rows that never cross an expert boundary (g_count of them)
@@ -201,7 +234,12 @@ CB_EXPORT int cb_moe_dispatch(const void* idx, int64_t S, int64_t top_k, int64_t
                               void* g_count, void* g_row0, void* g_rows, void* g_expert, int64_t max_tiles,
                               void* stream) {
   if (S < 1 || E < 1 || E > 1024 || top_k < 1 || max_tiles < 1) return CB_ERR_SHAPE;
-  return (int)cb_launch(moe_dispatch_kernel, dim3(1), dim3(1024), (size_t)(2 * E + 2) * sizeof(int), (cudaStream_t)stream,
+  const size_t smem = (size_t)(32 * E + 3 * E + 2) * sizeof(int);
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(moe_dispatch_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+  }
+  return (int)cb_launch(moe_dispatch_kernel, dim3(1), dim3(1024), smem, (cudaStream_t)stream,
                         (const int*)idx, (int)S, (int)top_k, (int)E, (int*)pos, (int*)src_tok, (int*)g_count,
                         (int*)g_row0, (int*)g_rows, (int*)g_expert, (int)max_tiles);
 }

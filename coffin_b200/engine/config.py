@@ -36,6 +36,7 @@ class EngineConfig:
     image_min_pixels: int = 32 * 32
     max_images: int = 4
     batch_window_ms: float = 0.0       # hold a lone decode this long for companions
+    warmup: bool = True                # serving: run a prefill chunk and capture every decode bucket before the first request
 
     @classmethod
     def from_env(cls, **overrides) -> "EngineConfig":
@@ -48,6 +49,8 @@ class EngineConfig:
             cfg.max_seq = int(env["COFFIN_MAX_SEQ"])
         if env.get("COFFIN_NO_GRAPH") == "1":
             cfg.graph = False
+        if env.get("COFFIN_NO_WARMUP") == "1":
+            cfg.warmup = False
         for k, v in overrides.items():
             if v is not None:
                 if not hasattr(cfg, k):

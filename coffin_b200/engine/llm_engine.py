@@ -61,6 +61,46 @@ class LLMEngine:
                 model.capture(m)
         return eng
 
+    def warmup(self) -> float:
+        """Pay the one-time costs before the first request: a prefill chunk (workspaces, kernel attributes)
+        on a scratch slot and the CUDA graph of every decode bucket the configuration can reach.  Without
+        it the first few dozen requests of a busy server wait behind seven graph captures (their TTFT was
+        2-4 s in a 16 request/s run whose steady state is 20 ms).  Returns the seconds spent; a model
+        without graphs or on the CPU only runs the prefill."""
+        t0 = time.monotonic()
+        m = self.model
+        dev = getattr(m, "device", None)
+        if (not hasattr(m, "prefill") or not hasattr(m, "zero_state") or self.scheduler.has_work()
+                or getattr(dev, "type", "cpu") != "cuda"):
+            return 0.0
+        if max(getattr(m, "tp_world", 1), getattr(m, "ep_world", 1), getattr(m, "pp_world", 1)) > 1:
+            return 0.0          # multi-rank steps are collective: the ranks warm up with their first request
+        import torch
+        n = max(1, min(self.cfg.chunk, getattr(m, "max_chunk", self.cfg.chunk), self.max_seq - 1))
+        per = -(-n // self.cfg.block_size)
+        blocks = getattr(m, "max_blocks_per_seq", per)
+        if per > blocks or per + 1 > getattr(m, "num_blocks", per + 1):
+            return 0.0
+        table = torch.arange(1, per + 1, dtype=torch.int32, device=dev)      # pages nobody owns yet: their contents are never read
+        vocab = int(getattr(getattr(m, "cfg", None), "vocab_size", 2))
+        with torch.no_grad():
+            for size in sorted({n, min(n, 64)}, reverse=True):
+                m.zero_state(0)
+                m.prefill(torch.ones(size, dtype=torch.int64, device=dev) % vocab, 0, 0, table[:-(-size // self.cfg.block_size)],
+                          want_logits=False)
+            m.zero_state(0)
+            if self.cfg.graph and hasattr(m, "capture") and getattr(dev, "type", "cpu") == "cuda":
+                buckets = getattr(m, "BUCKETS_ALL", None) or (1, 2, 4, 8, 16, 32, 64)
+                for M in buckets:
+                    if M <= max(1, self.cfg.max_num_seqs) * 2 - 1 and M <= getattr(m, "max_decode_rows", M):
+                        try:
+                            m.capture(M)
+                        except (NotImplementedError, ValueError):
+                            break
+            if dev is not None and getattr(dev, "type", "cpu") == "cuda":
+                torch.cuda.synchronize(dev)
+        return time.monotonic() - t0
+
     # ------------------------------------------------------------------ requests
     def add_request(self, prompt: list[int], params: SamplingParams | None = None, mm: Any | None = None,
                     request_id: str | None = None) -> Sequence:

@@ -123,7 +123,11 @@ def build_model(cfg: ModelConfig, sd: dict, **kw):
     vision, model_dir = kw.pop("vision", None), kw.pop("model_dir", None)
     has_visual = any(k.startswith("model.visual.") for k in sd)
     vsd = {k: v for k, v in sd.items() if k.startswith("model.visual.")} if has_visual else {}
-    model = _REGISTRY[detect_architecture(cfg)](cfg, sd, **kw)
-    if (vision or has_visual) and vision is not False:
+    arch = detect_architecture(cfg)
+    want_vision = bool(vision or has_visual) and vision is not False
+    if want_vision and arch in ("qwen4_exp", "qwen4exp"):
+        kw.setdefault("mrope_cache", True)     # image tokens rotate with 3-axis positions: the family keeps the rows per slot
+    model = _REGISTRY[arch](cfg, sd, **kw)
+    if want_vision:
         attach_vision(model, cfg, vsd, vision, model_dir)
     return model

@@ -337,8 +337,10 @@ class Qwen35Model:
     def _gemv(self, W, x, out, **kw):
         """Decode projection on whichever storage the weight has (bf16 or int8 W8A8)."""
         if isinstance(W, QW):
+            kw.pop("tail", None)
             return K.gemv_i8(W.wq, W.scale, x, out, **kw)
         if isinstance(W, QW4):
+            kw.pop("tail", None)
             if kw.get("tp") is not None and kw.get("push_site", -1) >= 0:
                 # row-parallel int4 projection under tensor parallelism: fp32 partial rows, then a small
                 # kernel stores them into every rank's inbox (the int4 GEMV has no push epilogue)
@@ -709,7 +711,10 @@ class Qwen35Model:
                               nh=c.num_attention_heads, nkv=c.num_key_value_heads, hd=c.head_dim,
                               rot=c.rotary_dim, nsplit=b["nsplit"], eps=self.eps, **self._kvs(j))
             if tp is not None:
-                self._gemv(lw.w_out, act, None, tp=tp, push_site=2 * li, rows=M)
+                # the pushing kernel's last CTA also pulls the ranks' sums, adds the residual and applies the
+                # post-attention norm, so the gate|up projection below starts from finished rows
+                self._gemv(lw.w_out, act, None, tp=tp, push_site=2 * li, rows=M,
+                           tail=(cur, lw.post_gain if lw.moe is None else None, nxt, self.eps))
             else:
                 self._gemv(lw.w_out, act, b["h"])
             if lw.moe is not None:
@@ -726,7 +731,9 @@ class Qwen35Model:
                    tp=tp, pull_site=2 * li if tp is not None else -1)
             cur, nxt = nxt, cur
             if tp is not None:
-                self._gemv(lw.w_down, b["inter"], None, tp=tp, push_site=2 * li + 1, rows=M)
+                nxt_gain = self.layers[li + 1].in_gain if li + 1 < len(self.layers) else (self.final_gain if self.pp_last else None)
+                self._gemv(lw.w_down, b["inter"], None, tp=tp, push_site=2 * li + 1, rows=M,
+                           tail=(cur, nxt_gain, nxt, self.eps))
                 carry, pull = None, 2 * li + 1
             else:
                 self._gemv(lw.w_down, b["inter"], b["h2"])

@@ -99,7 +99,8 @@ class Qwen4ExpModel:
     def __init__(self, cfg: Qwen4Config, sd: dict[str, torch.Tensor], device: str | torch.device = "cuda",
                  max_seq: int = 4096, num_slots: int = 2, num_blocks: int | None = None, max_chunk: int = 2048,
                  pdl: bool = True, ngram_device_budget: int = 120 << 30, quant: str = "none", tp=None,
-                 ep_rank: int = 0, ep_world: int = 1, with_mtp: bool = False, **_unused) -> None:
+                 ep_rank: int = 0, ep_world: int = 1, with_mtp: bool = False, mrope_cache: bool = False,
+                 **_unused) -> None:
         """``quant``: ``int8`` / ``w4a8`` storage of the mixer projections, the experts and the head (a
         pre-quantised state dict brings its own containers).  ``ep_world`` > 1: the routed experts are split
         by range over the ranks of the communicator ``tp``; everything else is replicated."""
@@ -238,6 +239,16 @@ class Qwen4ExpModel:
             self.mtp = D
         cos, sin = O.rope_tables(c.rotary_dim, c.rope_theta, self.max_seq + 64)
         self.cos, self.sin = cos.to(dev).contiguous(), sin.to(dev).contiguous()
+        # Multimodal sequences rotate with 3-axis positions (image tokens) and a position offset after the
+        # image, so "the rotary row of position p" is a property of the sequence, not of p.  Query, key and
+        # index-query rows get it when they are computed; the key of a BLOCK is rotated with the row of the
+        # block's first token when the block completes, possibly in a later pass - that row is looked up in
+        # a per-slot cache of the rows every position was rotated with.  Text-only models skip the cache.
+        self.rc_cos = self.rc_sin = None
+        if mrope_cache:
+            self.rc_cos = torch.zeros(self.num_slots, self.max_seq + 64, c.rotary_dim, dtype=torch.float32, device=dev)
+            self.rc_sin = torch.zeros_like(self.rc_cos)
+        self.vision = None
         # ---- sequence state --------------------------------------------------------------------
         nl, nf, npl = len(self.lin_ids), len(self.full_ids), len(self.ple_ids)
         self.state = torch.zeros(nl, self.num_slots, c.linear_num_value_heads, c.linear_key_head_dim,
@@ -415,6 +426,38 @@ class Qwen4ExpModel:
             return self.embed.gather(tokens)
         return K.embed_gather(self.embed, tokens)
 
+    def mrope_rows(self, positions3: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+        """Per-token rotary rows ``[T, rot]`` for 3-axis (t, h, w) positions ``[3, T]``."""
+        c = self.cfg
+        if not c.mrope_section:
+            raise ValueError("this checkpoint has no multi-axis rotary sections")
+        cos, sin = O.mrope_cos_sin(positions3.cpu(), c.rotary_dim, c.rope_theta, c.mrope_section)
+        return cos.to(self.device), sin.to(self.device)
+
+    def _set_rope(self, ws: dict, *, rows=None, ridx=None, slots=None, positions=None) -> None:
+        """Rotary rows of the pass staged in ``ws``: explicit per-row tables ``rows = (cos, sin)`` or the
+        1-D table indexed by ``ridx`` (int32, on the device).  With the row cache, the rows are also
+        recorded at (``slots[r]``, ``positions[r]``) (host lists; padding rows have slot < 0)."""
+        if rows is not None:
+            cos, sin = rows[0].float().contiguous(), rows[1].float().contiguous()
+            ws["rope"] = (cos, sin, None)
+        else:
+            ws["rope"] = (self.cos, self.sin, ridx)
+        if self.rc_cos is not None:
+            keep = [r for r, s_ in enumerate(slots) if s_ >= 0]
+            if keep:
+                sl = torch.tensor([slots[r] for r in keep], dtype=torch.int64, device=self.device)
+                ps = torch.tensor([positions[r] for r in keep], dtype=torch.int64, device=self.device)
+                kr = torch.tensor(keep, dtype=torch.int64, device=self.device)
+                if rows is not None:
+                    rc, rs = ws["rope"][0][kr], ws["rope"][1][kr]
+                else:
+                    ix = ridx.to(torch.int64)[kr]
+                    rc, rs = self.cos[ix], self.sin[ix]
+                self.rc_cos[sl, ps] = rc
+                self.rc_sin[sl, ps] = rs
+                K._count(2)
+
     def _tp_reduce(self, t: torch.Tensor) -> torch.Tensor:
         """Sum of the ranks' routed-expert outputs ``[T, hidden]`` (expert parallel): scatter + reduce/gather
         over peer memory when the communicator has the region, NCCL otherwise (the reference combines
@@ -521,7 +564,7 @@ class Qwen4ExpModel:
         self._linear(L.w_out, act, out)
 
     def _qsa(self, L, li: int, ws: dict, T: int, mixed, out, *, block_tables, positions_host: list[int],
-             shared_table: bool, pool: int | None = None, keep_selection: bool = False):
+             shared_table: bool, pool: int | None = None, keep_selection: bool = False, slots_host=None):
         """``positions_host[t]`` is the position of row ``t``; with ``shared_table`` all rows belong to
         one sequence (a prefill chunk) whose pages are ``block_tables`` (1-D).  ``pool``: which set of
         paged pools the layer owns (default: the layer's own; the draft head has the last one).
@@ -534,19 +577,27 @@ class Qwen4ExpModel:
         proj = ws["proj"][:, :L.w_in.shape[0]]
         self._linear(L.w_in, mixed, proj)
         pos, kv_slot = ws["pos"], ws["kv_slot"]
-        K.attn_prep(proj, L.qg, L.kg, self.cos, self.sin, pos, kv_slot, ws["q"], self.kpool[j], self.vpool[j],
+        rcos, rsin, ridx = ws.get("rope") or (self.cos, self.sin, pos)
+        K.attn_prep(proj, L.qg, L.kg, rcos, rsin, ridx, kv_slot, ws["q"], self.kpool[j], self.vpool[j],
                     nh=nh, nkv=nkv, hd=hd, rot=rot, eps=self.eps)
-        K.qsa_index_prep(proj, L.idx_col, L.iqg, self.cos, self.sin, pos, kv_slot, ws["iq"], self.ipool[j],
+        K.qsa_index_prep(proj, L.idx_col, L.iqg, rcos, rsin, ridx, kv_slot, ws["iq"], self.ipool[j],
                          ni=ni, di=di, rot=rot, eps=self.eps)
+        # rotary rows of block starts: the sequence's recorded rows when the model keeps them
+        cached = self.rc_cos is not None and pool is None and slots_host is not None
+
+        def start_rows(slot):
+            return (self.rc_cos[slot], self.rc_sin[slot]) if cached and slot >= 0 else (self.cos, self.sin)
         # keys of the blocks that this pass completed
         if shared_table:
             b0, b1 = positions_host[0] // ratio, (positions_host[-1] + 1) // ratio
-            K.qsa_block_keys(self.ipool[j], self.bkpool[j], L.ikg, self.cos, self.sin, block_tables, b0, b1,
+            bc, bs = start_rows(slots_host[0] if slots_host else -1)
+            K.qsa_block_keys(self.ipool[j], self.bkpool[j], L.ikg, bc, bs, block_tables, b0, b1,
                              ratio=ratio, di=di, rot=rot, eps=self.eps)
         else:
             for r, p in enumerate(positions_host):
                 if p >= 0 and (p + 1) % ratio == 0:
-                    K.qsa_block_keys(self.ipool[j], self.bkpool[j], L.ikg, self.cos, self.sin, block_tables[r],
+                    bc, bs = start_rows(slots_host[r] if slots_host else -1)
+                    K.qsa_block_keys(self.ipool[j], self.bkpool[j], L.ikg, bc, bs, block_tables[r],
                                      p // ratio, p // ratio + 1, ratio=ratio, di=di, rot=rot, eps=self.eps)
         act = ws["act"][:, :nh * hd]
         if T <= 8 and not shared_table:
@@ -605,10 +656,10 @@ class Qwen4ExpModel:
             else:
                 if decode:
                     self._qsa(L, li, ws, T, mixed, out, block_tables=block_tables, positions_host=positions_host,
-                              shared_table=False)
+                              shared_table=False, slots_host=row_slots)
                 else:
                     self._qsa(L, li, ws, T, mixed, out, block_tables=block_table,
-                              positions_host=list(range(pos0, pos0 + T)), shared_table=True)
+                              positions_host=list(range(pos0, pos0 + T)), shared_table=True, slots_host=[slot])
             mixed, inject2 = self._hyper_read(L.h_mlp, ws, T, (out, inject), inj_b)
             out2 = ws["out"][1]
             out2.copy_(L.moe.apply(mixed.contiguous(), self))
@@ -623,8 +674,8 @@ class Qwen4ExpModel:
         """One chunk of one sequence at positions ``pos0 .. pos0 + T - 1``; returns the fp32 logits of
         the last token (or ``None``).  ``want_lanes``: keep the un-collapsed lanes of every row in
         ``last_lanes`` (what the draft head pairs with the following token)."""
-        if cos_sin is not None:
-            raise NotImplementedError("multi-axis rotary positions are not wired for this family")
+        if cos_sin is not None and self.rc_cos is None:
+            raise ValueError("per-token rotary rows need the rotary-row cache (build the model with mrope_cache=True)")
         c = self.cfg
         T = int(tokens.numel())
         assert 0 < T <= self.max_chunk
@@ -634,6 +685,10 @@ class Qwen4ExpModel:
             kept = []
             for i, tok in enumerate(rows):
                 self.set_rows(1, [tok], [pos0 + i], [slot], [block_table.tolist()])
+                if cos_sin is not None:
+                    self._staged["rope_rows"] = (cos_sin[0][i:i + 1], cos_sin[1][i:i + 1])
+                if embeds is not None:
+                    self._staged["embeds"] = embeds[i:i + 1]
                 _, logits = self.decode(1, want_logits=want_logits and i == T - 1)
                 out = logits[0] if logits is not None else None
                 if want_lanes:
@@ -646,6 +701,7 @@ class Qwen4ExpModel:
         pos = torch.arange(pos0, pos0 + T, dtype=torch.int64, device=self.device)
         ws["pos"].copy_(pos)
         ws["kv_slot"].copy_(block_table.to(torch.int64)[pos // K.BLOCK] * K.BLOCK + pos % K.BLOCK)
+        self._set_rope(ws, rows=cos_sin, ridx=ws["pos"], slots=[slot] * T, positions=list(range(pos0, pos0 + T)))
         mixed = self._run(ws, T, tokens_host=[int(t) for t in tokens.tolist()] if self.ple_ids else None,
                           slot=slot, pos0=pos0, block_table=block_table)
         self.last_hidden = mixed if want_hidden else None
@@ -662,8 +718,12 @@ class Qwen4ExpModel:
         bt = torch.zeros(n, self.max_blocks_per_seq, dtype=torch.int32)
         for r, row in enumerate(block_tables):
             bt[r, :len(row)] = torch.as_tensor(row, dtype=torch.int32)
+        deltas = [int(d) for d in rope_deltas] if rope_deltas else [0] * n
+        if any(deltas) and self.rc_cos is None:
+            raise ValueError("rotary position offsets need the rotary-row cache (build the model with mrope_cache=True)")
         self._staged = dict(n=n, M=M, tokens=[int(t) for t in tokens], positions=[int(p) for p in positions],
-                            slots=[int(s) for s in slots], bt=bt.to(dev),
+                            slots=[int(s) for s in slots], bt=bt.to(dev), deltas=deltas,
+                            ridx_dev=torch.tensor([max(0, int(p) + d) for p, d in zip(positions, deltas)], dtype=torch.int32, device=dev),
                             tok_dev=torch.tensor(list(tokens), dtype=torch.int64, device=dev),
                             pos_dev=torch.tensor(list(positions), dtype=torch.int32, device=dev),
                             slot_dev=torch.tensor(list(slots), dtype=torch.int32, device=dev))
@@ -675,10 +735,12 @@ class Qwen4ExpModel:
         c, st = self.cfg, self._staged
         n = st["n"]
         ws = self._work(n)
-        ws["stream"].copy_(self._embed(st["tok_dev"]).repeat(1, c.hc_count))
+        e = st["embeds"].to(torch.bfloat16) if st.get("embeds") is not None else self._embed(st["tok_dev"])
+        ws["stream"].copy_(e.repeat(1, c.hc_count))
         ws["pos"].copy_(st["pos_dev"])
         p64 = st["pos_dev"].to(torch.int64)
         ws["kv_slot"].copy_(st["bt"].to(torch.int64).gather(1, (p64 // K.BLOCK)[:, None])[:, 0] * K.BLOCK + p64 % K.BLOCK)
+        self._set_rope(ws, rows=st.get("rope_rows"), ridx=st["ridx_dev"], slots=st["slots"], positions=st["positions"])
         mixed = self._run(ws, n, tokens_host=st["tokens"], slots=st["slot_dev"], positions=st["pos_dev"],
                           positions_host=st["positions"], block_tables=st["bt"], row_slots=st["slots"])
         b = self._rows.get(M)
@@ -695,7 +757,7 @@ class Qwen4ExpModel:
         st = self._staged
         nxt = self._rows[M]["next"][:st["n"]].tolist()
         self.set_rows(M, nxt, [p + 1 for p in st["positions"]], st["slots"],
-                      [row.tolist() for row in st["bt"].cpu()])
+                      [row.tolist() for row in st["bt"].cpu()], st["deltas"])
 
     # ------------------------------------------------------------------ speculative decoding
     VERIFY_WIDTHS = (2, 4, 8)
@@ -735,6 +797,8 @@ class Qwen4ExpModel:
                 for k_ in ("record", "one_slot", "one_pos", "steps"):
                     ws[k_] = torch.zeros_like(first[k_])
             self._stage_rows(ws, C, tokens, pos0, bt)
+            ridx = (ws["pos"] + int(_delta)).to(torch.int32) if _delta else ws["pos"]
+            self._set_rope(ws, ridx=ridx, slots=[slot] * C, positions=list(range(pos0, pos0 + C)))
             ws["one_slot"].fill_(slot)
             ws["one_pos"].fill_(pos0)
             rec: dict = {}

@@ -149,12 +149,14 @@ class Qwen4State:
     ik: dict = dataclasses.field(default_factory=dict)          # layer -> raw index keys [S, d]
     ple_ctx: dict = dataclasses.field(default_factory=dict)     # layer -> list[int]
     ple_hist: dict = dataclasses.field(default_factory=dict)    # layer -> [span, hc*H]
+    pos3: torch.Tensor | None = None                            # [3, n] rotary positions (t, h, w) of every token so far
 
     def clone(self) -> "Qwen4State":
         c = Qwen4State(self.n)
         for name in ("conv", "rec", "k", "v", "ik", "ple_hist"):
             setattr(c, name, {i: t.clone() for i, t in getattr(self, name).items()})
         c.ple_ctx = {i: list(t) for i, t in self.ple_ctx.items()}
+        c.pos3 = None if self.pos3 is None else self.pos3.clone()
         return c
 
 
@@ -171,9 +173,13 @@ class Qwen4Oracle:
 
     # ------------------------------------------------------------------ pieces
     def _cos_sin(self, pos: torch.Tensor):
+        """``pos [L]`` (the same index on every axis) or ``[3, L]`` (t, h, w of image tokens)."""
         c = self.cfg
+        if pos.dim() == 2 and not c.mrope_section:
+            pos = pos[0]
         if c.mrope_section:
-            return O.mrope_cos_sin(pos.reshape(1, -1).expand(3, -1), c.rotary_dim, c.rope_theta, c.mrope_section)
+            p3 = pos if pos.dim() == 2 else pos.reshape(1, -1).expand(3, -1)
+            return O.mrope_cos_sin(p3, c.rotary_dim, c.rope_theta, c.mrope_section)
         inv = O.inv_freq(c.rotary_dim, c.rope_theta)
         f = pos.float()[:, None] * inv[None, :]
         return torch.cat([f.cos(), f.cos()], -1), torch.cat([f.sin(), f.sin()], -1)
@@ -248,7 +254,7 @@ class Qwen4Oracle:
         st.v[li] = torch.cat([st.v[li], vv]) if li in st.v else vv
         st.ik[li] = torch.cat([st.ik[li], raw]) if li in st.ik else raw
         S = st.k[li].shape[0]
-        allcos, allsin = self._cos_sin(torch.arange(S))
+        allcos, allsin = self._cos_sin(st.pos3[:, :S] if (st.pos3 is not None and li != "mtp") else torch.arange(S))
         bkeys = qsa_block_keys(st.ik[li], p[q + "indexer.k_layernorm.weight"], allcos, allsin, c.indexer_compress_ratio,
                                rot, c.rms_norm_eps)
         keep = torch.zeros(T, S, dtype=torch.bool)
@@ -269,12 +275,19 @@ class Qwen4Oracle:
 
     # ------------------------------------------------------------------ forward
     @torch.no_grad()
-    def lanes(self, tokens: torch.Tensor, st: Qwen4State, embeds: torch.Tensor | None = None) -> torch.Tensor:
-        """The ``hc`` residual lanes ``[T, hc*H]`` after the last layer; ``st`` advances by ``T``."""
+    def lanes(self, tokens: torch.Tensor, st: Qwen4State, embeds: torch.Tensor | None = None,
+              pos3: torch.Tensor | None = None) -> torch.Tensor:
+        """The ``hc`` residual lanes ``[T, hc*H]`` after the last layer; ``st`` advances by ``T``.
+        ``embeds`` replaces the token embeddings (image tokens carry the vision tower's output),
+        ``pos3 [3, T]`` the rotary positions (default: the token index on every axis).  Causality and
+        the block structure of the sparse attention always follow the token index."""
         c, p = self.cfg, self.p
         T = tokens.numel()
         pos = torch.arange(st.n, st.n + T)
-        cos, sin = self._cos_sin(pos)
+        if pos3 is None:
+            pos3 = pos.reshape(1, -1).expand(3, -1)
+        st.pos3 = pos3.clone() if st.pos3 is None else torch.cat([st.pos3, pos3], 1)
+        cos, sin = self._cos_sin(pos3)
         e = p[LM + "embed_tokens.weight"][tokens.long()] if embeds is None else embeds.float()
         x = e.repeat(1, c.hc_count)
         for li, kind in enumerate(c.layer_types):

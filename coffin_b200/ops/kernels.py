@@ -23,6 +23,7 @@ _status: dict[int, torch.Tensor] = {}
 LAUNCHES = 0        # kernels launched through this module (bench bookkeeping)
 STREAM_GEMV = True   # route single-row projections to the cp.async streaming kernel (when GEMV_IMPL == 'scalar')
 GEMV_IMPL = "mma"     # 'mma': tensor-core GEMV for every M <= 8; 'scalar': FMA kernels
+TP_FUSED_TAIL = os.environ.get("COFFIN_TP_FUSED_TAIL", "1") != "0"   # tensor parallel decode: pull + norm in the pushing kernel's last CTA
 ATTN_TC = os.environ.get("COFFIN_ATTN_TC", "1") != "0"   # dense causal prefill attention on tcgen05 (else the mma.sync kernel)
 ATTN_TC_TRACE = None  # debugging: int64 device tensor [tiles, 8] that receives the stamps of one CTA of the tcgen05 attention kernel
 ATTN_TC_MIN_T = 32    # shorter query blocks (verify passes, tails) stay on the mma.sync kernel
@@ -231,7 +232,8 @@ def _norm_rows(res_in: torch.Tensor, add, gain: torch.Tensor, res_out, eps: floa
 
 
 def gemv(W: torch.Tensor, x: torch.Tensor | None, out: torch.Tensor | None, *, swiglu: bool = False,
-         norm: tuple | None = None, tp=None, pull_site: int = -1, push_site: int = -1, rows: int | None = None) -> torch.Tensor | None:
+         norm: tuple | None = None, tp=None, pull_site: int = -1, push_site: int = -1, rows: int | None = None,
+         tail: tuple | None = None) -> torch.Tensor | None:
     """Decode projection for 1, 2, 4 or 8 rows.
 
     ``W [N, K]`` (``[2I, K]`` gate rows then up rows with ``swiglu``); ``out [M, N]`` bf16 or fp32.
@@ -239,11 +241,26 @@ def gemv(W: torch.Tensor, x: torch.Tensor | None, out: torch.Tensor | None, *, s
     ``rmsnorm(res_in + add) * gain`` computed inside the kernel; ``res_out`` receives the sum.
     Tensor parallel (``tp`` = ``parallel.tp.TpComm``): ``push_site >= 0`` sends the fp32 partial
     outputs to every rank's inbox instead of writing ``out``; ``pull_site >= 0`` takes ``add`` as the
-    sum over ranks of that site's inbox.
+    sum over ranks of that site's inbox.  ``tail = (res_in, gain, res_out, eps)`` with a push: the last CTA of
+    the pushing kernel also does the consumer's work (pull, residual add, RMSNorm); the projection that
+    later names this site as ``pull_site`` finds the normalised rows ready and launches no pull kernel.
     """
     M = out.shape[0] if out is not None else rows
     K = W.shape[1]
     N = W.shape[0] // 2 if swiglu else W.shape[0]
+    if (tail is not None and tail[1] is not None and push_site >= 0 and TP_FUSED_TAIL and TP_PULL_SPLIT and GEMV_IMPL == "mma"
+            and norm is None and not swiglu and M * K * 2 <= 160 * 1024 and N % 8 == 0):
+        t_res, t_gain, t_out, t_eps = tail
+        key = (M, N, x.device.index)
+        buf = _norm_scratch.get(key)
+        if buf is None:
+            buf = _norm_scratch[key] = torch.empty(M, N, dtype=torch.bfloat16, device=x.device)
+        call("gemv_mma_bf16_tail", W, x, M, N, K, tp.cstruct_ref(), push_site, t_res, t_gain, t_out, buf, float(t_eps))
+        if not hasattr(tp, "_fused"):
+            tp._fused = {}
+        tp._fused[push_site] = buf
+        _count()
+        return None
     f32 = out is not None and out.dtype == torch.float32
     mode = (1 if swiglu else 0) | (2 if f32 else 0)
     ldy = out.stride(0) if out is not None else N
@@ -257,7 +274,9 @@ def gemv(W: torch.Tensor, x: torch.Tensor | None, out: torch.Tensor | None, *, s
         assert res_in.is_contiguous() and res_in.shape == (M, K)
         x = None
     if norm is not None and pull_site >= 0 and TP_PULL_SPLIT:
-        x, res_in, add, gain, res_out = _pull_norm_rows(tp, pull_site, res_in, gain, res_out, eps), None, None, None, None
+        ready = getattr(tp, "_fused", {}).pop(pull_site, None)      # the pushing kernel's last CTA already pulled and normalised
+        x = ready if ready is not None else _pull_norm_rows(tp, pull_site, res_in, gain, res_out, eps)
+        res_in = add = gain = res_out = None
         pull_site = -1
         tpp = tp.cstruct_ref() if push_site >= 0 else None
     elif norm is not None and M >= NORM_SPLIT_ROWS and pull_site < 0:

@@ -65,6 +65,7 @@ class Server:
         self.builder = builder
         t0 = time.time()
         self.engine = LLMEngine(model, self.cfg)
+        self.warmup_s = round(self.engine.warmup(), 3) if self.cfg.warmup else 0.0
         self.build_s = round(time.time() - t0, 3)
         self.load_s = 0.0
         self.eos = tuple(i for i in self.tok.eos_ids if i < self.model_cfg.vocab_size)
@@ -377,6 +378,7 @@ class Server:
         self.engine.reset()
         self.model = self.builder()
         self.engine = LLMEngine(self.model, self.cfg)
+        self.warmup_s = round(self.engine.warmup(), 3) if self.cfg.warmup else 0.0
         self.n_reload += 1
         self.build_s = round(time.time() - t0, 3)
         return {"ok": True, "build_s": self.build_s, "n_reload": self.n_reload, "backend": "sm_100a", "reason": "reload"}
@@ -390,7 +392,7 @@ class Server:
         from ..ops import _lib
         return {"ok": True, "model": self.model_name, "model_path": self.model_path,
                 "arch": self.model_cfg.architecture, "graph": self.cfg.graph, "max_seq": self.engine.max_seq,
-                "load_s": self.load_s, "build_s": self.build_s, "n_req": self.n_req, "n_reload": self.n_reload,
+                "load_s": self.load_s, "build_s": self.build_s, "warmup_s": getattr(self, "warmup_s", 0.0), "n_req": self.n_req, "n_reload": self.n_reload,
                 "backend": "sm_100a" if dev.type == "cuda" else "oracle-cpu", "device": str(dev),
                 "native_ops": len(_lib.exported()) if dev.type == "cuda" and _lib.available() else 0,
                 "total_ops": len(_lib.exported()) if _lib.available() else 0,

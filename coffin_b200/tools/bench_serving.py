@@ -162,12 +162,15 @@ def run_load(host: str, port: int, args) -> dict:
         th.join(args.timeout)
     t1 = time.perf_counter()
     ok = [r for r in results if r.ok]
-    # client clock where text was streamed; a random-init model emits tokens that decode to no text,
-    # then the engine's own clock (submit -> first token -> last token) from the usage chunk is used
-    ttft = [(r.t_first - r.t_send) * 1e3 if r.t_first else float(r.srv_ttft_ms) for r in ok
-            if r.t_first or r.srv_ttft_ms is not None]
-    tpot = [((r.t_done - r.t_first) * 1e3 if r.t_first else float(r.srv_decode_ms)) / (r.n_out - 1) for r in ok
-            if (r.t_first or r.srv_decode_ms is not None) and r.n_out > 1]
+    # TTFT / TPOT come from the engine's own clock (submit -> first token -> last token, scheduling queue
+    # included) reported in the usage chunk: a random-init model emits tokens that often decode to no
+    # text, so "first text seen by the client" says when the detokeniser first had something to show,
+    # not when the first token existed.  The client's first-text clock is reported next to it.
+    srv = [r for r in ok if r.srv_ttft_ms is not None]
+    ttft = [float(r.srv_ttft_ms) for r in srv] or [(r.t_first - r.t_send) * 1e3 for r in ok if r.t_first]
+    tpot = [float(r.srv_decode_ms) / (r.n_out - 1) for r in srv if r.srv_decode_ms is not None and r.n_out > 1] or \
+           [(r.t_done - r.t_first) * 1e3 / (r.n_out - 1) for r in ok if r.t_first and r.n_out > 1]
+    first_text = [(r.t_first - r.t_send) * 1e3 for r in ok if r.t_first]
     lat = [(r.t_done - r.t_send) * 1e3 for r in ok]
     out_tokens = sum(r.n_out for r in ok)
     rnd = lambda v: None if v is None else round(v, 2)   # noqa: E731
@@ -177,7 +180,8 @@ def run_load(host: str, port: int, args) -> dict:
            "output_tok_s": round(out_tokens / (t1 - t0), 1),
            "prompt_tokens_p50": pct([float(r.prompt_tokens) for r in ok], 0.5),
            "cached_prompt_tokens_p50": pct([float(r.cached) for r in ok], 0.5),
-           "timing_source": "client" if any(r.t_first for r in ok) else "engine",
+           "timing_source": "engine" if srv else "client",
+           "client_first_text_ms": {"p50": rnd(pct(first_text, 0.5)), "p99": rnd(pct(first_text, 0.99)), "n": len(first_text)},
            "output_tokens_total": out_tokens, "image_requests": sum(1 for r in results if r.image),
            "ttft_ms": {"p50": rnd(pct(ttft, 0.5)), "p90": rnd(pct(ttft, 0.9)), "p99": rnd(pct(ttft, 0.99))},
            "tpot_ms": {"p50": rnd(pct(tpot, 0.5)), "p90": rnd(pct(tpot, 0.9)), "p99": rnd(pct(tpot, 0.99))},

@@ -318,3 +318,55 @@ def test_qwen4_draft_head_matches_oracle_and_speculative_decoding_equals_greedy(
     from coffin_b200.ops import kernels as K
     torch.cuda.synchronize()
     K.check_status()
+
+
+@torch.no_grad()
+def test_qwen4_image_tokens_with_three_axis_rotary_positions_match_oracle():
+    """A prompt with an image in the middle: the tower's embeddings replace the image tokens, their
+    rotary rows come from (t, h, w) positions, the text after the image continues at index + delta on
+    all axes, and block keys of blocks that complete later are rotated with the rows recorded for
+    their first token.  Chunked prefill (a chunk boundary inside the image), then decode steps."""
+    from coffin_b200.models import build_model
+    from coffin_b200.models.qwen35.vision import patchify
+    from coffin_b200.utils.mm_input import mrope_positions
+    cfg = tiny_qwen4()
+    sd = random_state_dict(cfg, 0)
+    sd_b = {k: (v.to(torch.bfloat16).float() if not k.endswith(("A_log", "dt_bias")) else v) for k, v in sd.items()}
+    oracle = Qwen4Oracle(cfg, sd_b)
+    model = build_model(cfg, sd, device=DEV, max_seq=256, num_slots=2, vision="tiny")
+    assert model.vision is not None and model.rc_cos is not None
+    g = torch.Generator().manual_seed(8)
+    image = torch.rand(3, 96, 64, generator=g)
+    patches, grid = patchify(image, model.vision.cfg)
+    feats = model.vision.forward(patches.to(DEV), grid)                     # [n_img, H]
+    n_img = feats.shape[0]
+    assert n_img == grid[0] * grid[1] * grid[2] // 4
+    n_txt0, n_txt1 = 21, 40
+    n = n_txt0 + n_img + n_txt1
+    toks = torch.randint(2, cfg.vocab_size, (n + 6,), generator=g)
+    pos3, delta = mrope_positions(n, [(n_txt0, n_txt0 + n_img)], [grid], 2)
+    assert delta != 0
+    emb = model.embed_tokens(toks[:n].to(DEV)).clone()
+    emb[n_txt0:n_txt0 + n_img] = feats.to(emb.dtype)
+    cos, sin = model.mrope_rows(pos3)
+    bt = torch.arange(1, 5, dtype=torch.int32, device=DEV)
+    model.zero_state(0)
+    cut = n_txt0 + n_img // 2                                               # chunk boundary inside the image
+    model.prefill(toks[:cut].to(DEV), 0, 0, bt, embeds=emb[:cut], cos_sin=(cos[:cut], sin[:cut]), want_logits=False)
+    got = model.prefill(toks[cut:n].to(DEV), cut, 0, bt, embeds=emb[cut:n], cos_sin=(cos[cut:n], sin[cut:n]))
+    st = oracle.new_state()
+    ref = oracle.forward(toks[:n], st, embeds=emb.float().cpu(), pos3=pos3)[-1]
+    assert _rel(got, ref) < 8e-2
+    for i in range(n, n + 6):
+        p3 = torch.full((3, 1), i + delta, dtype=pos3.dtype)
+        ref = oracle.forward(toks[i:i + 1], st, pos3=p3)[-1]
+        model.set_rows(1, [int(toks[i])], [i], [0], [bt.tolist()], [delta])
+        _, logits = model.decode(1)
+        assert _rel(logits[0], ref) < 8e-2, f"step {i}"
+    # a text-only model refuses offsets instead of rotating with the wrong rows
+    plain = build_model(cfg, sd, device=DEV, max_seq=256, num_slots=1)
+    with pytest.raises(ValueError, match="rotary"):
+        plain.set_rows(1, [1], [5], [0], [bt.tolist()], [3])
+    from coffin_b200.ops import kernels as K
+    torch.cuda.synchronize()
+    K.check_status()

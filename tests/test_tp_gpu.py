@@ -28,9 +28,14 @@ def _free_port():
 
 
 @torch.no_grad()
-def test_push_pull_path_on_one_gpu_matches_plain_decode():
+@pytest.mark.parametrize("tail", [True, False])
+def test_push_pull_path_on_one_gpu_matches_plain_decode(tail, monkeypatch):
+    """``tail``: the pushing projection's last CTA also pulls, adds the residual and normalises (no pull
+    kernel); otherwise the one-CTA pull kernel runs between the projections."""
     from coffin_b200.models.qwen35.model import Qwen35Model
+    from coffin_b200.ops import kernels as K
     from coffin_b200.parallel.tp import TpComm
+    monkeypatch.setattr(K, "TP_FUSED_TAIL", tail)
     cfg = preset("tiny")
     sd = random_state_dict(cfg, 0)
     plain = Qwen35Model(cfg, sd, max_seq=256, num_slots=2)
@@ -54,6 +59,8 @@ def test_push_pull_path_on_one_gpu_matches_plain_decode():
         for m in (plain, fused):      # rewind both models to the same state for the next bucket
             m.zero_state(0)
             m.prefill(toks[:32].cuda(), 0, 0, bt, want_logits=False)
+    # two launches fewer per layer with the fused consumer
+    assert fused.launches_per_step(1) == plain.launches_per_step(1) + (1 if tail else 1 + 2 * cfg.num_hidden_layers)
     torch.cuda.synchronize()
     assert tp.status() == 0
     tp.close()
