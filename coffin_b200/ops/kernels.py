@@ -23,7 +23,10 @@ _status: dict[int, torch.Tensor] = {}
 LAUNCHES = 0        # kernels launched through this module (bench bookkeeping)
 STREAM_GEMV = True   # route single-row projections to the cp.async streaming kernel (when GEMV_IMPL == 'scalar')
 GEMV_IMPL = "mma"     # 'mma': tensor-core GEMV for every M <= 8; 'scalar': FMA kernels
-TP_FUSED_TAIL = os.environ.get("COFFIN_TP_FUSED_TAIL", "1") != "0"   # tensor parallel decode: pull + norm in the pushing kernel's last CTA
+# tensor parallel decode: pull + residual + norm in the pushing kernel's last CTA instead of a pull kernel.  Opt-in:
+# measured at two ranks it is 2 % slower (1.843 vs 1.800 ms per token) - under programmatic dependent launch the
+# pull kernel is already resident when the projection ends, and its 1024-thread CTA beats a 256-thread tail
+TP_FUSED_TAIL = os.environ.get("COFFIN_TP_FUSED_TAIL", "0") == "1"
 ATTN_TC = os.environ.get("COFFIN_ATTN_TC", "1") != "0"   # dense causal prefill attention on tcgen05 (else the mma.sync kernel)
 ATTN_TC_TRACE = None  # debugging: int64 device tensor [tiles, 8] that receives the stamps of one CTA of the tcgen05 attention kernel
 ATTN_TC_MIN_T = 32    # shorter query blocks (verify passes, tails) stay on the mma.sync kernel

@@ -394,3 +394,32 @@ def test_int8_kv_pool_matches_the_int8_kv_oracle(rows):
             assert _rel(lg[r], ref) < 5e-2, f"decode step {step} row {r}"
     used = model.kscale[0, tables[0][0] * 64: tables[0][0] * 64 + lens[0]]
     assert bool((used > 0).all())
+
+
+@torch.no_grad()
+def test_engine_warmup_captures_the_decode_buckets_and_leaves_no_trace():
+    """``LLMEngine.warmup`` runs a prefill chunk on a scratch slot and captures every decode bucket the
+    configuration can reach; requests served afterwards give the tokens of an engine that never warmed up."""
+    from coffin_b200.engine.config import EngineConfig
+    from coffin_b200.engine.llm_engine import LLMEngine
+    from coffin_b200.engine.sequence import SamplingParams
+    from coffin_b200.models.qwen35.model import Qwen35Model
+    cfg = preset("tiny")
+    sd = random_state_dict(cfg, 0)
+    g = torch.Generator().manual_seed(3)
+    prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (40, 75, 33)]
+    outs = []
+    for warm in (True, False):
+        model = Qwen35Model(cfg, sd, max_seq=256, num_slots=4)
+        eng = LLMEngine(model, EngineConfig(max_seq=256, max_num_seqs=4, chunk=64, prefill_quantum=64, num_blocks=model.num_blocks))
+        if warm:
+            assert eng.warmup() > 0.0
+            assert {k[0] for k in model._graphs} >= {1, 2, 4}, sorted(model._graphs)
+        seqs = [eng.add_request(p, SamplingParams(max_tokens=12, temperature=0.0)) for p in prompts]
+        for _ in range(200):
+            if not eng.scheduler.has_work():
+                break
+            eng.step()
+        outs.append([list(s.output) for s in seqs])
+        assert all(len(o) == 12 for o in outs[-1])
+    assert outs[0] == outs[1]
