@@ -132,7 +132,7 @@ __device__ __forceinline__ uint4 os_ld2(const uint2* src) {
 __global__ void __launch_bounds__(512) tp_os_allreduce_kernel(const TpPfDev* d, const bf16* src, int64_t lds,
                                                               const bf16* residual, int64_t ldr, const float* gain,
                                                               bf16* res_out, int64_t ldo, bf16* normed, int64_t ldn,
-                                                              float eps, unsigned seq) {
+                                                              float eps, unsigned seq, int8_t* q, float* qscale) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   float* row = reinterpret_cast<float*>(smem_raw);   // [width]
   __shared__ float red[32];
@@ -205,6 +205,7 @@ __global__ void __launch_bounds__(512) tp_os_allreduce_kernel(const TpPfDev* d, 
   }
   if (gain) {
     const float rstd = rsqrtf(block_sum(ss, red) / (float)W + eps);
+    float amax = 0.f;
     for (int c = threadIdx.x; c < (W >> 3); c += blockDim.x) {
       float f[8];
       const float4 g0 = *reinterpret_cast<const float4*>(gain + c * 8);
@@ -213,7 +214,22 @@ __global__ void __launch_bounds__(512) tp_os_allreduce_kernel(const TpPfDev* d, 
       f[2] = row[c * 8 + 2] * (rstd * g0.z); f[3] = row[c * 8 + 3] * (rstd * g0.w);
       f[4] = row[c * 8 + 4] * (rstd * g1.x); f[5] = row[c * 8 + 5] * (rstd * g1.y);
       f[6] = row[c * 8 + 6] * (rstd * g1.z); f[7] = row[c * 8 + 7] * (rstd * g1.w);
-      *reinterpret_cast<uint4*>(normed + (int64_t)m * ldn + c * 8) = float_to_bf16x8(f);
+      if (normed) *reinterpret_cast<uint4*>(normed + (int64_t)m * ldn + c * 8) = float_to_bf16x8(f);
+      if (q) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          const float v = __bfloat162float(__float2bfloat16(f[e]));
+          row[c * 8 + e] = v;
+          amax = fmaxf(amax, fabsf(v));
+        }
+      }
+    }
+    if (q) {   // int8 rows + scales for an int8 projection that follows (the arithmetic of quant_rows)
+      amax = block_max(amax, red);
+      const float sc = fmaxf(amax, 1e-8f) / 127.f, inv = 1.f / sc;
+      if (threadIdx.x == 0) qscale[m] = sc;
+      for (int i = threadIdx.x; i < W; i += blockDim.x)
+        q[(int64_t)m * W + i] = (int8_t)max(-127, min(127, __float2int_rn(row[i] * inv)));
     }
   }
   // the last CTA to finish marks the all-reduce complete (the next one takes "last completed + 1")
@@ -231,9 +247,10 @@ __global__ void __launch_bounds__(512) tp_os_allreduce_kernel(const TpPfDev* d, 
 CB_EXPORT int cb_tp_os_rows() { return kOsRows; }
 CB_EXPORT int cb_tp_os_allreduce(const void* desc, const void* src, int64_t lds, const void* residual, int64_t ldr,
                                  const void* gain, void* res_out, int64_t ldo, void* normed, int64_t ldn, int64_t M,
-                                 int64_t width, float eps, int64_t seq, void* stream) {
+                                 int64_t width, float eps, int64_t seq, void* q, void* qscale, void* stream) {
   if (!desc || !src || M < 1 || M > kOsRows || lds % 8 || width % 8 || width * 4 > 200 * 1024) return CB_ERR_ARG;
-  if ((gain != nullptr) != (normed != nullptr) || (!res_out && !normed)) return CB_ERR_ARG;
+  if ((q == nullptr) != (qscale == nullptr) || ((normed || q) && !gain) || (gain && !normed && !q) || (!res_out && !normed && !q))
+    return CB_ERR_ARG;
   const size_t smem = (size_t)width * 4;
   if (smem + 1024 > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(tp_os_allreduce_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -243,7 +260,7 @@ CB_EXPORT int cb_tp_os_allreduce(const void* desc, const void* src, int64_t lds,
   threads = threads > 512 ? 512 : threads;
   return (int)cb_launch(tp_os_allreduce_kernel, dim3((unsigned)M), dim3(threads), smem, (cudaStream_t)stream,
                         (const TpPfDev*)desc, (const bf16*)src, lds, (const bf16*)residual, ldr, (const float*)gain,
-                        (bf16*)res_out, ldo, (bf16*)normed, ldn, eps, (unsigned)seq);
+                        (bf16*)res_out, ldo, (bf16*)normed, ldn, eps, (unsigned)seq, (int8_t*)q, (float*)qscale);
 }
 
 CB_EXPORT int cb_tp_pf_scatter(const void* desc, const void* src, int64_t lds, int64_t T, int64_t seq, void* stream) {

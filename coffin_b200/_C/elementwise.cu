@@ -66,9 +66,13 @@ __global__ void embed_gather_kernel(const bf16* __restrict__ table, const int64_
 
 // out = rmsnorm(x [+ add]) * gain ; optionally writes the sum back (res_out may alias x here:
 // one CTA owns the whole row).
+// q / qscale (optional): the normalised row is also quantised to int8 with one fp32 scale per row
+// (absmax / 127 of the bf16-rounded values, exactly what quant_rows would compute from `out`), so an
+// int8 projection that follows needs no quantisation launch of its own.  `out` may then be null.
 __global__ void rmsnorm_kernel(const bf16* __restrict__ x, const bf16* __restrict__ add,
                                const float* __restrict__ gain, bf16* __restrict__ res_out,
-                               bf16* __restrict__ out, int64_t N, int64_t ldx, int64_t ldo, float eps) {
+                               bf16* __restrict__ out, int64_t N, int64_t ldx, int64_t ldo, float eps,
+                               int8_t* __restrict__ q, float* __restrict__ qscale) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   float* row = reinterpret_cast<float*>(smem_raw);  // [N]
   __shared__ float red[32];
@@ -89,11 +93,27 @@ __global__ void rmsnorm_kernel(const bf16* __restrict__ x, const bf16* __restric
     for (int i = 0; i < 8; ++i) { row[c * 8 + i] = f[i]; ss += f[i] * f[i]; }
   }
   const float rstd = rsqrtf(block_sum(ss, red) / (float)N + eps);
+  float amax = 0.f;
   for (int64_t c = threadIdx.x; c < (N >> 3); c += blockDim.x) {
     float f[8];
 #pragma unroll
     for (int i = 0; i < 8; ++i) f[i] = row[c * 8 + i] * rstd * gain[c * 8 + i];
-    *reinterpret_cast<uint4*>(out + r * ldo + c * 8) = float_to_bf16x8(f);
+    if (out) *reinterpret_cast<uint4*>(out + r * ldo + c * 8) = float_to_bf16x8(f);
+    if (q) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float v = __bfloat162float(__float2bfloat16(f[i]));
+        row[c * 8 + i] = v;
+        amax = fmaxf(amax, fabsf(v));
+      }
+    }
+  }
+  if (q) {
+    amax = block_max(amax, red);
+    const float sc = fmaxf(amax, 1e-8f) / 127.f, inv = 1.f / sc;
+    if (threadIdx.x == 0) qscale[r] = sc;
+    for (int64_t i = threadIdx.x; i < N; i += blockDim.x)
+      q[r * N + i] = (int8_t)max(-127, min(127, __float2int_rn(row[i] * inv)));
   }
 }
 
@@ -316,9 +336,18 @@ CB_EXPORT int cb_embed_gather(const void* table, const void* tokens, void* out, 
                         (const bf16*)table, (const int64_t*)tokens, (bf16*)out, H, V);
 }
 
+CB_EXPORT int cb_rmsnorm_q(const void* x, const void* add, const void* gain, void* res_out, void* out,
+                           int64_t M, int64_t N, int64_t ldx, int64_t ldo, float eps, void* q, void* qscale, void* stream);
 CB_EXPORT int cb_rmsnorm(const void* x, const void* add, const void* gain, void* res_out, void* out,
                          int64_t M, int64_t N, int64_t ldx, int64_t ldo, float eps, void* stream) {
+  if (!out) return CB_ERR_ARG;
+  return cb_rmsnorm_q(x, add, gain, res_out, out, M, N, ldx, ldo, eps, nullptr, nullptr, stream);
+}
+// As cb_rmsnorm, plus the int8 rows q [M, N] and their scales qscale [M] (see the kernel); out may be null.
+CB_EXPORT int cb_rmsnorm_q(const void* x, const void* add, const void* gain, void* res_out, void* out,
+                           int64_t M, int64_t N, int64_t ldx, int64_t ldo, float eps, void* q, void* qscale, void* stream) {
   if (N % 8 || N * 4 > 200 * 1024) return CB_ERR_SHAPE;
+  if ((q == nullptr) != (qscale == nullptr) || (!out && !q)) return CB_ERR_ARG;
   if (M == 0) return 0;
   const size_t smem = (size_t)N * 4;
   if (smem + 2048 > 48 * 1024) {   // the 48 KB default also has to hold the static shared memory
@@ -328,7 +357,7 @@ CB_EXPORT int cb_rmsnorm(const void* x, const void* add, const void* gain, void*
   const int threads = N >= 2048 ? 256 : 128;
   return (int)cb_launch(rmsnorm_kernel, dim3((unsigned)M), dim3(threads), smem, (cudaStream_t)stream,
                         (const bf16*)x, (const bf16*)add, (const float*)gain, (bf16*)res_out, (bf16*)out,
-                        N, ldx, ldo, eps);
+                        N, ldx, ldo, eps, (int8_t*)q, (float*)qscale);
 }
 
 CB_EXPORT int cb_layernorm(const void* x, const void* w, const void* b, void* out, int64_t M, int64_t N, int64_t ldx,

@@ -233,26 +233,33 @@ __global__ void __launch_bounds__(256) gdn_prep_kernel(const GdnPrepArgs a) {
       const float4 wj = act ? *reinterpret_cast<const float4*>(a.conv_w + (int64_t)(c + j) * 4) : make_float4(0.f, 0.f, 0.f, 0.f);
       w[j][0] = wj.x; w[j][1] = wj.y; w[j][2] = wj.z; w[j][3] = wj.w;
     }
-    auto load_row = [&](int tt, float* x) {          // conv input row of token tt (tile-relative rows may precede the chunk)
-      const int pp = a.pos0 + tt;
-      uint2 raw = make_uint2(0u, 0u);
+    // all TT + 3 rows of the tile are requested before anything is computed or stored (the stores below
+    // may alias the loads as far as the compiler knows, so it would not hoist them itself): eleven
+    // independent 8-byte loads in flight per lane instead of one
+    uint2 raw[TT + 3];
+#pragma unroll
+    for (int r = 0; r < TT + 3; ++r) {
+      const int tt = t0 - 3 + r, pp = a.pos0 + tt;
+      raw[r] = make_uint2(0u, 0u);
       if (act) {
-        if (tt >= 0) { if (tt < a.T) raw = *reinterpret_cast<const uint2*>(a.proj + (int64_t)tt * a.ldp + c); }
-        else if (pp >= 0) raw = *reinterpret_cast<const uint2*>(a.ring + (int64_t)(pp & (kRing - 1)) * conv_dim + c);
+        if (tt >= 0) { if (tt < a.T) raw[r] = *reinterpret_cast<const uint2*>(a.proj + (int64_t)tt * a.ldp + c); }
+        else if (pp >= 0) raw[r] = *reinterpret_cast<const uint2*>(a.ring + (int64_t)(pp & (kRing - 1)) * conv_dim + c);
       }
+    }
+    auto load_row = [&](int r, float* x) {          // conv input row r of the tile window (row 0 = token t0 - 3)
       // a bf16 is the upper half of the fp32 with the same value
-      x[0] = __uint_as_float(raw.x << 16); x[1] = __uint_as_float(raw.x & 0xffff0000u);
-      x[2] = __uint_as_float(raw.y << 16); x[3] = __uint_as_float(raw.y & 0xffff0000u);
+      x[0] = __uint_as_float(raw[r].x << 16); x[1] = __uint_as_float(raw[r].x & 0xffff0000u);
+      x[2] = __uint_as_float(raw[r].y << 16); x[3] = __uint_as_float(raw[r].y & 0xffff0000u);
     };
-    load_row(t0 - 3, win[0]);
-    load_row(t0 - 2, win[1]);
-    load_row(t0 - 1, win[2]);
+    load_row(0, win[0]);
+    load_row(1, win[1]);
+    load_row(2, win[2]);
     float* dbase = (kind == 0 ? a.qn : kind == 1 ? a.kn : a.v) + (int64_t)head * a.Tp * width;
 #pragma unroll
     for (int k = 0; k < TT; ++k) {
       const int t = t0 + k;
       float cur[4], val[4];
-      load_row(t, cur);
+      load_row(k + 3, cur);
       float ss = 0.f;
 #pragma unroll
       for (int j = 0; j < 4; ++j) {

@@ -361,13 +361,13 @@ class Qwen35Model:
             return K.gemv_w4(W.wq, W.scale, x, out, swiglu=kw.get("swiglu", False), norm=norm)
         return K.gemv(W, x, out, **kw)
 
-    def _gemm(self, A, W, out=None, residual=None, swiglu_in: bool = False, push=None):
+    def _gemm(self, A, W, out=None, residual=None, swiglu_in: bool = False, push=None, aq=None):
         """Prefill projection.  ``swiglu_in``: ``A`` is a ``[T, 2I]`` gate|up tensor whose SwiGLU
         product is the real input (fused into the activation quantisation on the int8 path).
         ``push``: the tensor-parallel communicator; the epilogue then sends the partial rows to their
         owners instead of writing ``out`` (``_tp_finish`` completes the all-reduce)."""
         if isinstance(W, QW):
-            q, sc = K.quant_rows(A, swiglu=swiglu_in)
+            q, sc = aq if aq is not None else K.quant_rows(A, swiglu=swiglu_in)     # aq: rows quantised by the producing kernel
             return K.gemm_i8(q, sc, W.wq, W.scale, out=out, residual=residual, push=push)
         if isinstance(W, QW4):
             W = W.expanded()                # bf16 copy (kept while HBM allows); the tcgen05 GEMM does the rest
@@ -793,10 +793,20 @@ class Qwen35Model:
             res.copy_(self.input_hidden)
         else:
             K.embed_gather(self.embed, b["tokens"], res)
+        # int8 projections take their activation rows already quantised from the norm (or all-reduce + norm)
+        # kernel that produced them: no quantisation launch between the two
+        i8 = isinstance(self.layers[0].w_in, QW)
+        if i8 and "aq" not in b:
+            b["aq"] = (torch.empty(M, c.hidden_size, dtype=torch.int8, device=self.device),
+                       torch.empty(M, dtype=torch.float32, device=self.device))
+        aq = b["aq"] if i8 else None
         for li, lw in enumerate(self.layers):
-            K.rmsnorm(res, lw.in_gain, self.eps, out=normed)
+            if aq is not None and isinstance(lw.w_in, QW):
+                K.rmsnorm(res, lw.in_gain, self.eps, quant=aq)
+            else:
+                K.rmsnorm(res, lw.in_gain, self.eps, out=normed)
             proj = b["proj"][:, :lw.w_in.shape[0]]
-            self._gemm(normed, lw.w_in, out=proj)
+            self._gemm(normed, lw.w_in, out=proj, aq=aq if isinstance(lw.w_in, QW) else None)
             if lw.kind == LINEAR:
                 j = self.lin_ids[li]
                 act = b["act_lin"]
@@ -815,18 +825,25 @@ class Qwen35Model:
                 # K-split GEMM, then the one-shot all-reduce whose second kernel also adds the residual and
                 # applies the post-attention norm
                 self._gemm(act, lw.w_out, out=b["part"])
-                self.tp.oneshot(b["part"], residual=res, gain=lw.post_gain, res_out=res, normed=normed, eps=self.eps)
+                gq = aq if (lw.moe is None and isinstance(lw.w_gu, QW)) else None
+                self.tp.oneshot(b["part"], residual=res, gain=lw.post_gain, res_out=res, normed=None if gq else normed,
+                                eps=self.eps, quant=gq)
             elif tpw:
+                gq = None
                 part = self._row_parallel(act, lw.w_out, b["part"])
                 K.rmsnorm(res, lw.post_gain, self.eps, out=normed, add=part, res_out=res)
             else:
+                gq = aq if (lw.moe is None and isinstance(lw.w_gu, QW)) else None
                 self._gemm(act, lw.w_out, out=res, residual=res)
-                K.rmsnorm(res, lw.post_gain, self.eps, out=normed)
+                if gq is not None:
+                    K.rmsnorm(res, lw.post_gain, self.eps, quant=gq)
+                else:
+                    K.rmsnorm(res, lw.post_gain, self.eps, out=normed)
             if lw.moe is not None:
                 res.add_(lw.moe.apply(normed, self))
                 K._count()
             else:
-                self._gemm(normed, lw.w_gu, out=b["gu"])
+                self._gemm(normed, lw.w_gu, out=b["gu"], aq=gq)
                 if tpw and self.tp.pf_rows:
                     self._gemm(b["gu"], lw.w_down, out=b["part"], swiglu_in=True)
                     self.tp.oneshot(b["part"], residual=res, res_out=res)
@@ -839,8 +856,12 @@ class Qwen35Model:
             b["hidden"].copy_(res)
             K._count()
             return
-        K.rmsnorm(res, self.final_gain, self.eps, out=normed)
-        self._gemm(normed, self.lm_head, out=b["logits_bf"])
+        hq = aq if isinstance(self.lm_head, QW) else None
+        if hq is not None:
+            K.rmsnorm(res, self.final_gain, self.eps, quant=hq)
+        else:
+            K.rmsnorm(res, self.final_gain, self.eps, out=normed)
+        self._gemm(normed, self.lm_head, out=b["logits_bf"], aq=hq)
         if tpw:
             # vocabulary-parallel head: every rank needs the arg-max over the whole vocabulary
             b["logits_local"].copy_(b["logits_bf"])

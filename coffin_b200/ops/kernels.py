@@ -121,10 +121,18 @@ def embed_gather(table: torch.Tensor, tokens: torch.Tensor, out: torch.Tensor | 
 
 
 def rmsnorm(x: torch.Tensor, gain: torch.Tensor, eps: float, out: torch.Tensor | None = None,
-            add: torch.Tensor | None = None, res_out: torch.Tensor | None = None) -> torch.Tensor:
+            add: torch.Tensor | None = None, res_out: torch.Tensor | None = None, quant: tuple | None = None):
     """``out = rmsnorm(x [+ add]) * gain``; with ``add`` the sum is also written to ``res_out``
-    (which may be ``x`` itself)."""
+    (which may be ``x`` itself).  ``quant = (q int8 [M, N], scale fp32 [M])``: the normalised rows are
+    quantised in the same kernel (what ``quant_rows(out)`` would give) and no bf16 output is written
+    unless ``out`` is passed too."""
     M, N = x.shape
+    if quant is not None:
+        assert gain.dtype == torch.float32 and x.stride(1) == 1 and quant[0].is_contiguous()
+        call("rmsnorm_q", x, add, gain, res_out, out, M, N, x.stride(0), out.stride(0) if out is not None else 0,
+             float(eps), quant[0], quant[1])
+        _count()
+        return quant
     if out is None:
         out = torch.empty_like(x)
     assert gain.dtype == torch.float32 and x.stride(1) == 1 and out.stride(1) == 1

@@ -308,11 +308,13 @@ class TpComm:
         return self.pf_out[:T]
 
     def oneshot(self, src: torch.Tensor, residual: torch.Tensor | None = None, gain: torch.Tensor | None = None,
-                res_out: torch.Tensor | None = None, normed: torch.Tensor | None = None, eps: float = 0.0) -> None:
+                res_out: torch.Tensor | None = None, normed: torch.Tensor | None = None, eps: float = 0.0,
+                quant: tuple | None = None) -> None:
         """All-reduce of the few rows of a decode bucket (``src [M <= 64, hidden]`` bf16) in one launch and
         one NVLink crossing: CTA m of every rank stores row m into every peer's one-shot inbox (data paired
         with the sequence number), polls the peers' rows in its own inbox, adds the world's rows (rank order)
-        + ``residual`` into ``res_out`` and, with ``gain``, writes ``rmsnorm(res_out) * gain`` into ``normed``."""
+        + ``residual`` into ``res_out`` and, with ``gain``, writes ``rmsnorm(res_out) * gain`` into ``normed``
+        and / or its per-row int8 quantisation into ``quant = (q, scale)`` (for an int8 projection next)."""
         from ..ops import kernels as K
         M, W = src.shape
         if not self.pf_rows or M > OS_ROWS or W != self.hidden:
@@ -320,7 +322,8 @@ class TpComm:
         K.call("tp_os_allreduce", self.pf_desc_ptr(), src, src.stride(0), residual,
                residual.stride(0) if residual is not None else 0, gain,
                res_out, res_out.stride(0) if res_out is not None else 0, normed,
-               normed.stride(0) if normed is not None else 0, M, W, float(eps), 0)
+               normed.stride(0) if normed is not None else 0, M, W, float(eps), 0,
+               quant[0] if quant is not None else None, quant[1] if quant is not None else None)
         K._count()
 
     def cstruct_ref(self):

@@ -367,6 +367,17 @@ def test_quant_rows_and_i8_prefill_chain():
     ref = O.silu_mul(gu[:, :264], gu[:, 264:]).to(torch.bfloat16)
     rq2, rs2 = O.quant_rows_int8(ref, floor=1e-8)
     assert (qs.cpu().int() - rq2.int()).abs().max() <= 1
+    # the norm kernel's own int8 output: bit-equal to quantising its bf16 output, with and without the add
+    xr, add = bf(33, 528, seed=63).to(DEV), bf(33, 528, seed=64).to(DEV)
+    gain = (1 + 0.1 * torch.randn(528)).float().to(DEV)
+    for a in (None, add):
+        normed = k.rmsnorm(xr, gain, 1e-6, add=a, res_out=torch.empty_like(xr) if a is not None else None)
+        q_ref, s_ref = k.quant_rows(normed)
+        q8 = torch.empty(33, 528, dtype=torch.int8, device=DEV)
+        s8 = torch.empty(33, dtype=torch.float32, device=DEV)
+        ro = torch.empty_like(xr) if a is not None else None
+        k.rmsnorm(xr, gain, 1e-6, add=a, res_out=ro, quant=(q8, s8))
+        assert torch.equal(q8, q_ref) and torch.equal(s8, s_ref)
 
 
 @pytest.mark.parametrize("M,N,Kd", [(1, 520, 512), (4, 2560, 1024), (8, 264, 256), (2, 1000, 2304)])

@@ -215,6 +215,13 @@ def test_one_shot_all_reduce_protocol_on_one_gpu():
         assert torch.equal(res_out, ref)
         rn = ref.float() * torch.rsqrt(ref.float().pow(2).mean(-1, keepdim=True) + 1e-6) * gain
         assert ((normed.float() - rn).abs().max() / rn.abs().max()).item() < 1e-2
+        # int8 rows + scales straight from the all-reduce: what quant_rows gives on the normalised rows
+        q8 = torch.empty(M, H, dtype=torch.int8, device="cuda")
+        sc8 = torch.empty(M, dtype=torch.float32, device="cuda")
+        res2 = torch.empty_like(res)
+        tp.oneshot(part, residual=res, gain=gain, res_out=res2, eps=1e-6, quant=(q8, sc8))
+        q_ref, s_ref = K.quant_rows(normed)
+        assert torch.equal(res2, res_out) and torch.equal(q8, q_ref) and torch.equal(sc8, s_ref)
         tp.scatter(res)                                   # the other protocol in between
         assert torch.equal(tp.finish_reduce(), res)
         out = torch.empty_like(part)
