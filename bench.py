@@ -117,6 +117,7 @@ def main() -> None:
     ap.add_argument("--mma-kcta", type=int, default=0, help="tuning: max CTAs sharing one 16-row GEMV block (1 = off)")
     ap.add_argument("--mma-prefetch", type=int, default=-1, help="tuning: GEMV sweep rounds prefetched into L2 before the dependency wait")
     ap.add_argument("--gemv-impl", default="", help="tuning: mma | scalar")
+    ap.add_argument("--no-parity", action="store_true", help="multi-rank runs: skip the comparison with an unsharded copy on rank 0")
     ap.add_argument("--no-stream-gemv", action="store_true", help="tuning: register-staged GEMV for batch 1")
     ap.add_argument("--gemv-ctas", type=int, default=0, help="tuning: GEMV CTAs per SM (0 = library default)")
     ap.add_argument("--gemv-prefetch", type=int, default=-1, help="tuning: GEMV L2 prefetch-ahead (-1 = default)")
@@ -250,6 +251,7 @@ def main() -> None:
                "timing": "host wall clock around the phases of LLM.generate: prompt copied from pinned host memory, "
                          "every token read back to the host before the next step is staged"}
     wbytes = llm.model.weight_bytes() if hasattr(llm.model, "weight_bytes") else 0
+    parity = multi_rank_parity(args, cfg, llm, prompts[W], world, rank) if world > 1 and not args.no_parity else None
     if rank == 0:
         line = {
             "metric": "decode_tok_s", "value": decode_tok_s, "unit": "tok/s", "n_gpus": world,
@@ -263,7 +265,7 @@ def main() -> None:
             "notes": {"cuda_graph": not args.no_graph, "kv_dtype": args.kv_dtype,
                       "cache": f"weights streamed by this rank every decode step ({wbytes / 1e9:.2f} GB; a routed-MoE step reads its dense part plus the selected experts) far exceed the 126 MB L2, no flush needed",
                       "weights": "random-init N(0,0.02)"},
-            "token_crc": token_crc,
+            "token_crc": token_crc, "multi_rank_parity": parity,
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "wall_s": wall_s, "impl": "ours",
         }
         print(json.dumps(line), flush=True)
@@ -275,6 +277,63 @@ def main() -> None:
         if tp is not None:
             tp.close()
         shutdown(timeout_s=10.0)
+
+
+def multi_rank_parity(args, cfg, llm, prompt, world: int, rank: int):
+    """Outside the timed region: tie the sharded model's output to the single-GPU model's.  All ranks run
+    the prompt of the first timed step and 8 teacher-forced decode steps through the sharded model with
+    full logits; rank 0 then builds an UNSHARDED copy of the same random-init model on its own GPU, feeds it
+    the same tokens and compares logits (max relative difference on the scale of the largest logit, top-1
+    agreement where the single-GPU margin is clear).  Greedy token streams of random-init weights
+    diverge at the first near-tie, which is why a CRC of sampled tokens cannot serve as this proof."""
+    import torch
+    import torch.distributed as dist
+    from coffin_b200.engine.llm import LLM
+    n_steps = 8
+    toks = prompt.cuda()
+    g = torch.Generator().manual_seed(77)
+    forced = torch.randint(0, cfg.vocab_size, (n_steps,), generator=g).tolist()
+
+    def run(one: LLM):
+        m = one.model
+        if hasattr(m, "full_logits"):
+            m.full_logits = True
+        m.zero_state(one._slot)
+        T, lg = toks.numel(), None
+        for s0 in range(0, T, m.max_chunk):
+            s1 = min(T, s0 + m.max_chunk)
+            lg = m.prefill(toks[s0:s1], s0, one._slot, one._bt, want_logits=s1 == T)
+        out = [lg.float().clone()]
+        for i, t in enumerate(forced):
+            m.set_rows(1, [t], [T + i], [one._slot], [one._bt.tolist()])
+            out.append(m.decode(1, graph=False)[1][0].float().clone())
+        return torch.stack(out)
+
+    with torch.no_grad():
+        sharded = run(llm)
+        dist.barrier()
+        res = None
+        if rank == 0:
+            free = torch.cuda.mem_get_info()[0]
+            need = sum(v for v in [llm.model.weight_bytes() * world]) * 2.5
+            if free < need:
+                res = {"skipped": f"{free / 1e9:.0f} GB free on rank 0, the unsharded copy needs about {need / 1e9:.0f} GB"}
+            else:
+                single = LLM.from_random(cfg, seed=0, max_seq=args.prompt + args.new + 64, max_num_seqs=1, graph=False,
+                                         max_chunk=min(args.prompt, 2048), quant=args.quant, kv_dtype=args.kv_dtype)
+                ref = run(single)
+                scale = ref.abs().amax(-1, keepdim=True)
+                rel = float(((sharded - ref).abs() / scale).max())
+                top2 = ref.topk(2, dim=-1).values
+                clear = (top2[:, 0] - top2[:, 1]) > 0.02 * scale[:, 0]
+                same = bool((sharded.argmax(-1)[clear] == ref.argmax(-1)[clear]).all())
+                res = {"positions": int(ref.shape[0]), "max_rel_logit_diff": round(rel, 5),
+                       "clear_margin_positions": int(clear.sum()), "top1_equal_where_clear": same,
+                       "what": f"{args.parallel}{world} logits vs an unsharded copy on rank 0 (prompt + {n_steps} teacher-forced steps)"}
+                del single, ref
+                torch.cuda.empty_cache()
+        dist.barrier()
+    return res
 
 
 def bench_rows(args, cfg, W: int) -> None:

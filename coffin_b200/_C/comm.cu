@@ -314,6 +314,14 @@ CB_EXPORT int cb_ipc_open_handle(const void* handle64, void** out) {
 }
 CB_EXPORT int cb_ipc_close_handle(void* p) { return (int)cudaIpcCloseMemHandle(p); }
 
+// Device-to-device copy between two mappings of this process (a local buffer and, say, an IPC mapping of
+// another process's buffer on this or a peer GPU: the copy then crosses NVLink once, no host staging).
+CB_EXPORT int cb_copy_d2d(void* dst, const void* src, int64_t bytes, void* stream) {
+  if (!dst || !src || bytes < 0) return CB_ERR_ARG;
+  if (bytes == 0) return 0;
+  return (int)cudaMemcpyAsync(dst, src, (size_t)bytes, cudaMemcpyDefault, (cudaStream_t)stream);
+}
+
 CB_EXPORT int cb_peer_read_i32(const void* dev, int* out) {
   return (int)cudaMemcpy(out, dev, sizeof(int), cudaMemcpyDeviceToHost);
 }

@@ -192,22 +192,42 @@ def verify(srv, req: dict) -> dict:
 def pd_prefill(srv, req: dict) -> dict:
     """Prefill a prompt and export the sequence state (KV blocks + delta-net state + logits) to
     ``out_dir`` for a decode instance to adopt."""
-    from ..engine.pd import export_state
+    from ..engine.pd import export_state, export_state_device
     prompt = _tokens(srv, req)
     out_dir = Path(req["out_dir"])
+    transport = req.get("transport", "file")
+    if transport not in ("file", "device"):
+        raise DiagError("transport must be 'file' or 'device'")
+    if transport == "device" and getattr(getattr(srv.model, "device", None), "type", "cpu") != "cuda":
+        raise DiagError("the device transport needs a CUDA engine")
     t0 = time.perf_counter()
     table, logits = _solo(srv, prompt)
     _sync(srv)
     ms = (time.perf_counter() - t0) * 1e3
-    nbytes = export_state(srv.model, 0, table, prompt, logits, out_dir)
-    return {"ok": True, "n_prompt": len(prompt), "prefill_ms": round(ms, 2), "bytes": nbytes, "out_dir": str(out_dir)}
+    t1 = time.perf_counter()
+    if transport == "device":
+        # one device buffer + its CUDA IPC handle: the decode instance copies device to device
+        nbytes = export_state_device(srv.model, 0, table, prompt, logits, out_dir, token=str(req.get("token", "default")))
+    else:
+        stale = out_dir / "state.json"
+        if stale.exists():
+            stale.unlink()
+        nbytes = export_state(srv.model, 0, table, prompt, logits, out_dir)
+    return {"ok": True, "n_prompt": len(prompt), "prefill_ms": round(ms, 2), "bytes": nbytes, "out_dir": str(out_dir),
+            "transport": transport, "export_ms": round((time.perf_counter() - t1) * 1e3, 2)}
+
+
+def pd_release(srv, req: dict) -> dict:
+    """Free the device buffer a ``pd_prefill`` with the device transport published (after the adopter copied it)."""
+    from ..engine.pd import release_export
+    return {"ok": True, "released": release_export(str(req.get("token", "default")))}
 
 
 def pd_decode(srv, req: dict) -> dict:
-    from ..engine.pd import adopt_state
+    from ..engine.pd import adopt_any
     srv.engine.reset()
     n = int(req.get("max_new", 32))
-    table, prompt, logits = adopt_state(srv.model, 0, Path(req["out_dir"]), max_new=n)
+    table, prompt, logits = adopt_any(srv.model, 0, Path(req["out_dir"]), max_new=n)
     if n < 1 or len(prompt) + n > min(len(table) * 64, getattr(srv.model, "max_seq", 1 << 30)):
         raise DiagError(f"max_new={n} does not fit the adopted sequence's block table / window")
     tok = int(logits.argmax())
@@ -222,7 +242,7 @@ def pd_decode(srv, req: dict) -> dict:
 
 def pd_decode_batch(srv, req: dict) -> dict:
     """Adopt several exported sequences into batch rows and decode them together."""
-    from ..engine.pd import adopt_state
+    from ..engine.pd import adopt_any as adopt_state
     srv.engine.reset()
     items = req.get("items") or []
     m = srv.model

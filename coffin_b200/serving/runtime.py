@@ -8,7 +8,7 @@ A failing step fails the requests in flight, resets the engine and keeps the ser
 
 Wire protocol (one JSON object per line in, one or more lines out) and reply fields follow the
 reference: ops ``ping tokenize generate chat chat_stream bench profile ops spec verify
-pd_prefill pd_decode pd_decode_batch reload reset stop`` (``serving/runtime_parts.py:925-1133``),
+pd_prefill pd_decode pd_decode_batch pd_release reload reset stop`` (``serving/runtime_parts.py:925-1133``),
 stream events ``start / token / done / error`` (``:769-869``), engine loop and failure path
 (``:196-245``).
 """
@@ -33,7 +33,7 @@ from ..utils.tokenizer import IncrementalDecoder, load_tokenizer
 from ..utils.tool_call import TC_OPEN, parse_tool_calls, split_thinking
 
 DIAGNOSTIC_OPS = {"reload", "reset", "bench", "profile", "ops", "spec", "verify", "pd_prefill", "pd_decode",
-                  "pd_decode_batch"}
+                  "pd_decode_batch", "pd_release"}
 
 
 class MMError(Exception):
@@ -366,7 +366,7 @@ class Server:
             self.n_req += 1
             self._collect(seq, outq)
             return self._chat_reply(seq, t0, params.max_tokens, opens, forced, mm)
-        if op in ("bench", "profile", "ops", "spec", "verify", "pd_prefill", "pd_decode", "pd_decode_batch"):
+        if op in ("bench", "profile", "ops", "spec", "verify", "pd_prefill", "pd_decode", "pd_decode_batch", "pd_release"):
             from . import diagnostics
             return self._job(lambda: getattr(diagnostics, op)(self, req))
         return {"ok": False, "error": f"unknown op {op!r}", "status": 400}

@@ -109,6 +109,10 @@ def test_diagnostic_ops_and_pd_handoff(engine):
     assert dec["ok"] and dec["tokens"] == plain["tokens"]
     batch = call(sock, {"op": "pd_decode_batch", "items": [{"dir": d}, {"dir": d}], "max_new": 4})
     assert batch["ok"] and all(it["tokens"] == plain["tokens"][:4] for it in batch["items"])
+    # the device transport (one device buffer + CUDA IPC handle) is refused cleanly on the CPU twin
+    bad = call(sock, {"op": "pd_prefill", "prompt": "x", "out_dir": d, "transport": "device"})
+    assert not bad["ok"] and bad.get("status") == 400 and "CUDA" in bad["error"]
+    assert call(sock, {"op": "pd_release"}) == {"ok": True, "released": False} or call(sock, {"op": "pd_release"})["ok"]
     r = call(sock, {"op": "reload"})
     assert r["ok"] and r["n_reload"] == 1
     assert call(sock, {"op": "reset"})["ok"]
