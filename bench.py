@@ -117,6 +117,7 @@ def main() -> None:
     ap.add_argument("--mma-kcta", type=int, default=0, help="tuning: max CTAs sharing one 16-row GEMV block (1 = off)")
     ap.add_argument("--mma-prefetch", type=int, default=-1, help="tuning: GEMV sweep rounds prefetched into L2 before the dependency wait")
     ap.add_argument("--gemv-impl", default="", help="tuning: mma | scalar")
+    ap.add_argument("--layers", type=int, default=0, help="Qwen4-exp: cut the geometry to its first N layers")
     ap.add_argument("--no-parity", action="store_true", help="multi-rank runs: skip the comparison with an unsharded copy on rank 0")
     ap.add_argument("--no-stream-gemv", action="store_true", help="tuning: register-staged GEMV for batch 1")
     ap.add_argument("--gemv-ctas", type=int, default=0, help="tuning: GEMV CTAs per SM (0 = library default)")
@@ -168,6 +169,8 @@ def main() -> None:
         from coffin_b200.ops import _lib
         _lib.call_nostream("set_gemv_opts", args.gemv_ctas or 2, 1 if args.gemv_prefetch != 0 else 0)
     cfg = preset(args.model)
+    if "qwen4" in args.model:
+        return bench_qwen4(args, cfg, W)
     if args.rows > 1:
         return bench_rows(args, cfg, W)
     llm = LLM.from_random(cfg, seed=0, max_seq=args.prompt + args.new + 64, max_num_seqs=1,
@@ -334,6 +337,73 @@ def multi_rank_parity(args, cfg, llm, prompt, world: int, rank: int):
                 torch.cuda.empty_cache()
         dist.barrier()
     return res
+
+
+def bench_qwen4(args, cfg, W: int) -> None:
+    """Qwen4-exp family (hyper-connected lanes, QSA attention, 512-expert MoE): device-timed prefill of one
+    prompt and single-sequence decode on one GPU.  The step runs eagerly (no CUDA graph for this family);
+    weights are drawn and quantised tensor by tensor (`--quant w4a8` for the full 48-layer geometry, whose
+    experts would not fit in bf16); `--layers N` cuts the geometry to its first N layers."""
+    import dataclasses
+    import statistics
+    import torch
+    from coffin_b200.models.qwen4exp.model import Qwen4ExpModel
+    from coffin_b200.models.qwen4exp.weights import LazyRandomStateDict
+    from coffin_b200.ops import kernels as K
+    if args.layers and args.layers < cfg.num_hidden_layers:
+        cfg = dataclasses.replace(cfg, num_hidden_layers=args.layers, layer_types=cfg.layer_types[:args.layers],
+                                  ple_layer_ids=tuple(i for i in cfg.ple_layer_ids if i <= args.layers))
+    torch.cuda.set_device(0)
+    chunk = min(args.prompt, 2048)
+    model = Qwen4ExpModel(cfg, LazyRandomStateDict(cfg, 0), max_seq=args.prompt + args.new + 64, num_slots=1,
+                          max_chunk=chunk, quant=args.quant)
+    g = torch.Generator().manual_seed(1234)
+    prompts = [torch.randint(2, cfg.vocab_size, (args.prompt,), generator=g).pin_memory() for _ in range(W + args.steps)]
+    bt = torch.arange(1, model.max_blocks_per_seq + 1, dtype=torch.int32, device="cuda")
+    ev = lambda: torch.cuda.Event(enable_timing=True)
+    pre_ms, dec_ms = [], []
+    sampler = ClockSampler(0)
+    l0 = 0
+    with torch.no_grad():
+        for i, p in enumerate(prompts):
+            if i == W:
+                torch.cuda.synchronize()
+                sampler.start()
+                l0 = K.LAUNCHES
+            e0, e1, e2 = ev(), ev(), ev()
+            dev = p.cuda(non_blocking=True)
+            model.zero_state(0)
+            e0.record()
+            lg = None
+            for s0 in range(0, args.prompt, chunk):
+                s1 = min(args.prompt, s0 + chunk)
+                lg = model.prefill(dev[s0:s1], s0, 0, bt, want_logits=s1 == args.prompt)
+            tok = int(lg.argmax())
+            e1.record()
+            for j in range(args.new):
+                model.set_rows(1, [tok], [args.prompt + j], [0], [bt.tolist()])
+                tok = int(model.decode(1)[0][0])
+            e2.record()
+            e2.synchronize()
+            if i >= W:
+                pre_ms.append(e0.elapsed_time(e1))
+                dec_ms.append(e1.elapsed_time(e2))
+    clocks = sampler.stop()
+    launches = K.LAUNCHES - l0
+    K.check_status()
+    dec_tok_s = args.new * args.steps / (sum(dec_ms) / 1e3)
+    line = {"metric": "decode_tok_s", "value": dec_tok_s, "unit": "tok/s", "n_gpus": 1, "steps": args.steps, "warmup": W,
+            "ms_per_step": (sum(pre_ms) + sum(dec_ms)) / args.steps, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": {"none": "bf16", "int8": "int8-w8a8", "w4a8": "int4-w4a8"}.get(args.quant, args.quant),
+            "data": "synthetic", "prefill_tok_s": args.prompt * args.steps / (sum(pre_ms) / 1e3),
+            "ttft_ms_p50": statistics.median(pre_ms), "tpot_ms_p50": statistics.median(dec_ms) / args.new,
+            "config": {"model": args.model, "layers": cfg.num_hidden_layers, "global_batch": 1, "seq_len": args.prompt,
+                       "decode_tokens": args.new, "parallelism": "single"},
+            "notes": {"cuda_graph": False, "weights": "random-init, drawn and quantised per tensor",
+                      "weight_gb": round(model.weight_bytes() / 1e9, 2),
+                      "timing": "CUDA events; the decode loop reads every token back (eager step, host-staged rows)"},
+            "clocks": clocks, "gpu_launches": launches, "impl": "ours"}
+    print(json.dumps(line), flush=True)
 
 
 def bench_rows(args, cfg, W: int) -> None:

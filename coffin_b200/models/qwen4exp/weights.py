@@ -117,6 +117,38 @@ def random_state_dict(cfg: Qwen4Config, seed: int = 0, dtype: torch.dtype = torc
     return sd
 
 
+class LazyRandomStateDict:
+    """The tensors of ``random_state_dict`` drawn one at a time, on access: a model constructor that
+    quantises every projection as it reads it then never holds more than one bf16 tensor of the full-size
+    shape (the 48-layer geometry has 96 G expert parameters - 193 GB in bf16, 48 GB as int4).  The same
+    per-tensor seeds as ``random_state_dict``, so both give the same weights."""
+
+    def __init__(self, cfg: Qwen4Config, seed: int = 0, dtype: torch.dtype = torch.bfloat16,
+                 device: str | torch.device = "cuda", std: float = 0.02) -> None:
+        self.cfg, self.seed, self.dtype, self.device, self.std = cfg, seed, dtype, torch.device(device), std
+        self.plan = {key: (idx, shape, kind) for idx, (key, shape, kind) in enumerate(tensor_plan(cfg))}
+
+    def __contains__(self, key) -> bool:
+        return key in self.plan
+
+    def __iter__(self):
+        return iter(self.plan)
+
+    def keys(self):
+        return self.plan.keys()
+
+    def get(self, key, default=None):
+        return self[key] if key in self.plan else default
+
+    def __getitem__(self, key: str) -> torch.Tensor:
+        idx, shape, kind = self.plan[key]
+        gen = torch.Generator(device=self.device)
+        gen.manual_seed(self.seed * 1_000_003 + idx)
+        if kind == "wide":
+            return _draw(shape, "w", gen, self.device, self.dtype, self.std * 10)
+        return _draw(shape, kind, gen, self.device, self.dtype, self.std)
+
+
 def param_count(cfg: Qwen4Config) -> int:
     return sum(math.prod(s) for _, s, _ in tensor_plan(cfg))
 

@@ -12,7 +12,7 @@ import torch
 
 from coffin_b200.config import preset
 from coffin_b200.weights.init import random_state_dict
-from tests.ranks import run_ranks
+from ranks import run_ranks
 
 pytestmark = pytest.mark.gpu
 

@@ -207,3 +207,13 @@ def test_oracle_speculative_decoding_with_the_draft_head_equals_greedy():
     assert plan.before_step(1) is not None
     assert plan.keep_rows(plan.blocks, torch.tensor([13]), 14, cfg) is not None
     assert plan.keep_rows(plan.blocks, torch.tensor([15]), 16, cfg) is None      # a fourth block completed
+
+
+def test_lazy_random_state_dict_draws_the_same_tensors_one_at_a_time():
+    from coffin_b200.models.qwen4exp.weights import LazyRandomStateDict
+    cfg = tiny_qwen4(mtp_num_hidden_layers=1)
+    full = random_state_dict(cfg, 3, dtype=torch.bfloat16)
+    lazy = LazyRandomStateDict(cfg, 3, device="cpu")
+    assert set(lazy.keys()) == set(full) and "lm_head.weight" in lazy and "nope" not in lazy
+    assert lazy.get("nope", 7) == 7
+    assert all(torch.equal(full[k], lazy[k]) for k in full)
