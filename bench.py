@@ -341,7 +341,8 @@ def multi_rank_parity(args, cfg, llm, prompt, world: int, rank: int):
 
 def bench_qwen4(args, cfg, W: int) -> None:
     """Qwen4-exp family (hyper-connected lanes, QSA attention, 512-expert MoE): device-timed prefill of one
-    prompt and single-sequence decode on one GPU.  The step runs eagerly (no CUDA graph for this family);
+    prompt and single-sequence decode on one GPU.  The decode step replays as a CUDA graph when the model has no
+    n-gram layer (`COFFIN_QWEN4_GRAPH=0`: eager);
     weights are drawn and quantised tensor by tensor (`--quant w4a8` for the full 48-layer geometry, whose
     experts would not fit in bf16); `--layers N` cuts the geometry to its first N layers."""
     import dataclasses
@@ -399,7 +400,7 @@ def bench_qwen4(args, cfg, W: int) -> None:
             "ttft_ms_p50": statistics.median(pre_ms), "tpot_ms_p50": statistics.median(dec_ms) / args.new,
             "config": {"model": args.model, "layers": cfg.num_hidden_layers, "global_batch": 1, "seq_len": args.prompt,
                        "decode_tokens": args.new, "parallelism": "single"},
-            "notes": {"cuda_graph": False, "weights": "random-init, drawn and quantised per tensor",
+            "notes": {"cuda_graph": bool(model._graphs), "weights": "random-init, drawn and quantised per tensor",
                       "weight_gb": round(model.weight_bytes() / 1e9, 2),
                       "timing": "CUDA events; the decode loop reads every token back (eager step, host-staged rows)"},
             "clocks": clocks, "gpu_launches": launches, "impl": "ours"}

@@ -215,6 +215,10 @@ struct BlockKeysArgs {
   const int* block_table;                       // pages of the sequence
   int b0, b1, ratio, di, rot;
   float eps;
+  // row mode (decode rows inside a CUDA graph): warp w looks at row w of `positions`; if that row's
+  // token completes a block (position + 1 a multiple of ratio) it computes that block's key from the
+  // row's own block table (row w of block_table, ldbt apart), else it does nothing.  b1 = row count.
+  const int* positions; int64_t ldbt;
 };
 
 // One warp per block b in [b0, b1): tokens [b * ratio, (b + 1) * ratio) of the sequence.
@@ -222,10 +226,17 @@ __global__ void __launch_bounds__(256) qsa_block_keys_kernel(const BlockKeysArgs
   griddep_launch();
   griddep_wait();
   const int lane = threadIdx.x & 31;
-  const int b = a.b0 + blockIdx.x * 8 + (threadIdx.x >> 5);
+  int b = a.b0 + blockIdx.x * 8 + (threadIdx.x >> 5);
   if (b >= a.b1) return;
   const int per_page = kBlock / a.ratio;
-  const int page = a.block_table[b / per_page];
+  const int* table = a.block_table;
+  if (a.positions) {
+    const int p = a.positions[b];
+    if (p < 0 || (p + 1) % a.ratio) return;       // this row's token does not complete a block
+    table += (int64_t)b * a.ldbt;
+    b = p / a.ratio;
+  }
+  const int page = table[b / per_page];
   const int64_t tok0 = (int64_t)page * kBlock + (int64_t)(b % per_page) * a.ratio;
   // di <= 256: up to 8 channels per lane
   float m[8];
@@ -431,8 +442,19 @@ CB_EXPORT int cb_qsa_block_keys(const void* ipool, void* bkpool, const void* kga
   if (b1 <= b0) return 0;
   if (ratio < 1 || kBlock % ratio || di > 256 || rot % 2 || rot > di) return CB_ERR_SHAPE;
   BlockKeysArgs a{(const bf16*)ipool, (float*)bkpool, (const float*)kgain, (const float*)cos, (const float*)sin,
-                  (const int*)block_table, (int)b0, (int)b1, (int)ratio, (int)di, (int)rot, eps};
+                  (const int*)block_table, (int)b0, (int)b1, (int)ratio, (int)di, (int)rot, eps, nullptr, 0};
   return (int)cb_launch(qsa_block_keys_kernel, dim3((unsigned)((b1 - b0 + 7) / 8)), dim3(256), 0, (cudaStream_t)stream, a);
+}
+// Row mode: for each of `rows` decode rows, the key of the block that the row's token completes (if any).
+// Decided on the device from `positions`, so the call can sit in a CUDA graph.
+CB_EXPORT int cb_qsa_block_keys_rows(const void* ipool, void* bkpool, const void* kgain, const void* cos, const void* sin,
+                                     const void* block_tables, int64_t ldbt, const void* positions, int64_t rows,
+                                     int64_t ratio, int64_t di, int64_t rot, float eps, void* stream) {
+  if (rows < 1) return 0;
+  if (ratio < 1 || kBlock % ratio || di > 256 || rot % 2 || rot > di || !positions) return CB_ERR_SHAPE;
+  BlockKeysArgs a{(const bf16*)ipool, (float*)bkpool, (const float*)kgain, (const float*)cos, (const float*)sin,
+                  (const int*)block_tables, 0, (int)rows, (int)ratio, (int)di, (int)rot, eps, (const int*)positions, ldbt};
+  return (int)cb_launch(qsa_block_keys_kernel, dim3((unsigned)((rows + 7) / 8)), dim3(256), 0, (cudaStream_t)stream, a);
 }
 
 CB_EXPORT int cb_qsa_select(const void* iq, const void* bkpool, const void* block_table, int64_t ldbt,

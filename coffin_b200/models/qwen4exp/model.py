@@ -1,7 +1,9 @@
 """Qwen4-exp on one B200: hyper-connected residual lanes, delta-net and block-sparse (QSA)
 attention mixers, a routed MoE in every layer, optional n-gram (PLE) injection.
 
-Execution model (eager; the family's reference runs eager too, ``models/qwen4exp/engine.py:12-24``):
+Execution model (prefill eager; the decode step replays as a CUDA graph per row count when the model has no
+n-gram layer and no rotary-row cache - the family's reference runs everything eagerly,
+``models/qwen4exp/engine.py:12-24``):
 
 * The residual stream is ``[rows, hc * H]`` bf16.  A mixer's output is not written back when it is
   produced: the next hyper-connection read applies ``stream += out (x) inject`` inside its norm
@@ -40,6 +42,7 @@ from .ngram import NGramHasher, NGramTable
 
 LM = "model.language_model."
 BUCKETS = (1, 2, 4, 8)
+GRAPH_DECODE = __import__("os").environ.get("COFFIN_QWEN4_GRAPH", "1") != "0"   # decode steps as CUDA graphs where the model allows
 
 
 def _pad8(n: int) -> int:
@@ -268,6 +271,9 @@ class Qwen4ExpModel:
         self._ws: dict = {}
         self._rows: dict = {}
         self._staged: dict | None = None
+        self._rowbuf: dict = {}
+        self._graphs: dict = {}
+        self.graph_pool = None
         self.last_prenorm = None
         self.last_hidden = None
         self.last_lanes = None
@@ -593,6 +599,10 @@ class Qwen4ExpModel:
             bc, bs = start_rows(slots_host[0] if slots_host else -1)
             K.qsa_block_keys(self.ipool[j], self.bkpool[j], L.ikg, bc, bs, block_tables, b0, b1,
                              ratio=ratio, di=di, rot=rot, eps=self.eps)
+        elif positions_host is None:
+            # inside a CUDA graph: which rows complete a block is decided on the device
+            K.qsa_block_keys_rows(self.ipool[j], self.bkpool[j], L.ikg, self.cos, self.sin, block_tables, pos,
+                                  ratio=ratio, di=di, rot=rot, eps=self.eps)
         else:
             for r, p in enumerate(positions_host):
                 if p >= 0 and (p + 1) % ratio == 0:
@@ -721,28 +731,47 @@ class Qwen4ExpModel:
         deltas = [int(d) for d in rope_deltas] if rope_deltas else [0] * n
         if any(deltas) and self.rc_cos is None:
             raise ValueError("rotary position offsets need the rotary-row cache (build the model with mrope_cache=True)")
+        # the device copies live in buffers that persist per row count, so that a captured step finds its inputs
+        # at fixed addresses
+        rb = self._rowbuf.get(n)
+        if rb is None:
+            rb = self._rowbuf[n] = {"bt": torch.zeros(n, self.max_blocks_per_seq, dtype=torch.int32, device=dev),
+                                    "ridx": torch.zeros(n, dtype=torch.int32, device=dev),
+                                    "tok": torch.zeros(n, dtype=torch.int64, device=dev),
+                                    "pos": torch.zeros(n, dtype=torch.int32, device=dev),
+                                    "slot": torch.zeros(n, dtype=torch.int32, device=dev)}
+        rb["bt"].copy_(bt)
+        rb["ridx"].copy_(torch.tensor([max(0, int(p) + d) for p, d in zip(positions, deltas)], dtype=torch.int32))
+        rb["tok"].copy_(torch.tensor([int(t) for t in tokens], dtype=torch.int64))
+        rb["pos"].copy_(torch.tensor([int(p) for p in positions], dtype=torch.int32))
+        rb["slot"].copy_(torch.tensor([int(s) for s in slots], dtype=torch.int32))
         self._staged = dict(n=n, M=M, tokens=[int(t) for t in tokens], positions=[int(p) for p in positions],
-                            slots=[int(s) for s in slots], bt=bt.to(dev), deltas=deltas,
-                            ridx_dev=torch.tensor([max(0, int(p) + d) for p, d in zip(positions, deltas)], dtype=torch.int32, device=dev),
-                            tok_dev=torch.tensor(list(tokens), dtype=torch.int64, device=dev),
-                            pos_dev=torch.tensor(list(positions), dtype=torch.int32, device=dev),
-                            slot_dev=torch.tensor(list(slots), dtype=torch.int32, device=dev))
+                            slots=[int(s) for s in slots], bt=rb["bt"], deltas=deltas, ridx_dev=rb["ridx"],
+                            tok_dev=rb["tok"], pos_dev=rb["pos"], slot_dev=rb["slot"])
 
-    @torch.no_grad()
-    def decode(self, M: int, graph: bool = True, want_logits: bool = True):
-        """One token for each staged row.  Returns ``(next_tokens [M], logits [M, vocab])``; rows beyond
-        the staged ones are zero."""
+    def graph_ok(self) -> bool:
+        """Whether a decode step of this model can be captured: every decision of the step must be made on
+        the device.  The n-gram injection hashes token ids on the host and the rotary-row cache is indexed
+        with host lists, so models with either run the step eagerly."""
+        return not self.ple_ids and self.rc_cos is None and self.device.type == "cuda"
+
+    def _decode_body(self, n: int, M: int, want_logits: bool, host: bool):
+        """The step over the ``n`` staged rows.  ``host=False``: nothing depends on host copies of the rows
+        (block-key completion is decided by the kernel), which is what a CUDA graph needs."""
         c, st = self.cfg, self._staged
-        n = st["n"]
         ws = self._work(n)
         e = st["embeds"].to(torch.bfloat16) if st.get("embeds") is not None else self._embed(st["tok_dev"])
         ws["stream"].copy_(e.repeat(1, c.hc_count))
         ws["pos"].copy_(st["pos_dev"])
         p64 = st["pos_dev"].to(torch.int64)
         ws["kv_slot"].copy_(st["bt"].to(torch.int64).gather(1, (p64 // K.BLOCK)[:, None])[:, 0] * K.BLOCK + p64 % K.BLOCK)
-        self._set_rope(ws, rows=st.get("rope_rows"), ridx=st["ridx_dev"], slots=st["slots"], positions=st["positions"])
-        mixed = self._run(ws, n, tokens_host=st["tokens"], slots=st["slot_dev"], positions=st["pos_dev"],
-                          positions_host=st["positions"], block_tables=st["bt"], row_slots=st["slots"])
+        if host:
+            self._set_rope(ws, rows=st.get("rope_rows"), ridx=st["ridx_dev"], slots=st["slots"], positions=st["positions"])
+        else:
+            ws["rope"] = (self.cos, self.sin, st["ridx_dev"])
+        mixed = self._run(ws, n, tokens_host=st["tokens"] if host else None, slots=st["slot_dev"], positions=st["pos_dev"],
+                          positions_host=st["positions"] if host else None, block_tables=st["bt"],
+                          row_slots=st["slots"] if host else None)
         b = self._rows.get(M)
         if b is None:
             b = self._rows[M] = {"logits": torch.zeros(M, c.vocab_size, dtype=torch.float32, device=self.device),
@@ -751,6 +780,45 @@ class Qwen4ExpModel:
             return b["next"], None
         self._linear(self.lm_head, mixed.contiguous(), b["logits"][:n])
         K.argmax(b["logits"], b["next"])
+        return b["next"], b["logits"]
+
+    @torch.no_grad()
+    def decode(self, M: int, graph: bool = True, want_logits: bool = True):
+        """One token for each staged row.  Returns ``(next_tokens [M], logits [M, vocab])``; rows beyond
+        the staged ones are zero.  ``graph``: replay the step as a CUDA graph (captured per row count on
+        first use) when the model allows it (``graph_ok``) - the reference runs this family eagerly only
+        (``models/qwen4exp/engine.py:12-24``), which leaves a step bound by its ~50 launches per layer."""
+        st = self._staged
+        n = st["n"]
+        if (not graph or not GRAPH_DECODE or not self.graph_ok() or not want_logits or st.get("embeds") is not None
+                or st.get("rope_rows") is not None or any(st["deltas"])):
+            return self._decode_body(n, M, want_logits, host=True)
+        key = (n, M)
+        g = self._graphs.get(key)
+        if g is None:
+            # warm-up runs on a side stream (workspaces, kernel attributes), then the capture; the staged rows
+            # are real, so the warm-up steps are replays of the same step: state-changing kernels (delta-net
+            # update, KV append) rewrite the same values, and the state is put back before the graph runs
+            snaps = [self.snapshot_state(s_) for s_ in st["slots"]]
+            side = torch.cuda.Stream(device=self.device)
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                for _ in range(2):
+                    self._decode_body(n, M, True, host=False)
+                    for s_, sn in zip(st["slots"], snaps):
+                        self.restore_state(s_, sn)
+            torch.cuda.current_stream().wait_stream(side)
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            if self.graph_pool is None:
+                self.graph_pool = torch.cuda.graph_pool_handle()
+            with K.capture_graph(g, pool=self.graph_pool):
+                self._decode_body(n, M, True, host=False)
+            self._graphs[key] = g
+            for s_, sn in zip(st["slots"], snaps):      # the capture itself does not run the kernels; states are as staged
+                self.restore_state(s_, sn)
+        g.replay()
+        b = self._rows[M]
         return b["next"], b["logits"]
 
     def advance_rows(self, M: int) -> None:

@@ -611,6 +611,13 @@ def qsa_block_keys(ipool, bkpool, kgain, cos, sin, block_table, b0, b1, *, ratio
         _count()
 
 
+def qsa_block_keys_rows(ipool, bkpool, kgain, cos, sin, block_tables, positions, *, ratio, di, rot, eps) -> None:
+    """For every decode row whose token completes a block, that block's key (decided on the device)."""
+    call("qsa_block_keys_rows", ipool, bkpool, kgain, cos, sin, block_tables, block_tables.stride(0), positions,
+         positions.numel(), ratio, di, rot, float(eps))
+    _count()
+
+
 def qsa_select(iq, bkpool, block_table, positions, scores, sel, nsel, *, ni, di, ratio, topk, full_factor,
                mask=None, row_seq=None, shared_table: bool = False) -> None:
     """Top-``topk`` blocks per query row (``sel`` ascending, ``nsel``; -1 = attend to everything)."""

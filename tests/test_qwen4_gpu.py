@@ -370,3 +370,40 @@ def test_qwen4_image_tokens_with_three_axis_rotary_positions_match_oracle():
     from coffin_b200.ops import kernels as K
     torch.cuda.synchronize()
     K.check_status()
+
+
+@torch.no_grad()
+def test_qwen4_decode_as_cuda_graph_equals_the_eager_step():
+    """A model without n-gram injection replays its decode step as a CUDA graph (captured per row count):
+    twelve steps - block keys complete every fourth token, so the device-side completion test is hit
+    three times per row - give the eager step's logits bit for bit, for one row and for three."""
+    from coffin_b200.models.qwen4exp import model as qm
+    cfg = tiny_qwen4(ple_layer_ids=())
+    sd = random_state_dict(cfg, 0)
+    g = torch.Generator().manual_seed(9)
+    seqs = [torch.randint(2, cfg.vocab_size, (n + 12,), generator=g) for n in (61, 40, 52)]
+    tables = [list(range(1 + 4 * r, 5 + 4 * r)) for r in range(3)]
+    outs = {}
+    for use_graph in (True, False):
+        model = qm.Qwen4ExpModel(cfg, sd, max_seq=256, num_slots=3)
+        assert model.graph_ok()
+        for rows in (1, 3):
+            lens = [s.numel() - 12 for s in seqs[:rows]]
+            for r in range(rows):
+                model.zero_state(r)
+                model.prefill(seqs[r][:lens[r]].to(DEV), 0, r, torch.tensor(tables[r], dtype=torch.int32, device=DEV), want_logits=False)
+            M = model.bucket_for(rows)
+            for step in range(12):
+                model.set_rows(M, [int(seqs[r][lens[r] + step]) for r in range(rows)], [lens[r] + step for r in range(rows)],
+                               list(range(rows)), tables[:rows])
+                _, lg = model.decode(M, graph=use_graph)
+                outs.setdefault((use_graph, rows), []).append(lg[:rows].clone())
+        assert bool(model._graphs) == use_graph
+    for rows in (1, 3):
+        for a, b in zip(outs[(True, rows)], outs[(False, rows)]):
+            assert torch.equal(a, b), rows
+    # a model with the n-gram layer keeps the eager step
+    assert not qm.Qwen4ExpModel(tiny_qwen4(), random_state_dict(tiny_qwen4(), 0), max_seq=128, num_slots=1).graph_ok()
+    from coffin_b200.ops import kernels as K
+    torch.cuda.synchronize()
+    K.check_status()
