@@ -96,7 +96,10 @@ def test_gemv_fused_norm_swiglu(M, H, I):
 
 @pytest.mark.parametrize("M,N,Kd,bn", [(128, 256, 64, 256), (200, 264, 192, 128), (300, 520, 1032, 0),
                                        (64, 64, 256, 64), (1000, 1536, 512, 256), (130, 136, 72, 128),
-                                       (300, 520, 1032, 160), (2048, 2560, 1024, 0),
+                                       (300, 520, 1032, 160), (2048, 2560, 1024, 0), (2048, 2560, 1024, 160),
+                                       # CTA pairs (256-row tiles, 256 / 320 columns), edge tiles in both directions
+                                       (300, 520, 1032, 1256), (300, 520, 1032, 1320), (257, 264, 72, 1320),
+                                       (1000, 1536, 512, 1256), (2048, 2560, 4096, 1320), (2100, 1288, 2560, 1256),
                                        # at most 128 rows: K split over CTAs, partial tiles reduced by the last slice
                                        (64, 2560, 4096, 0), (16, 12352, 2560, 0), (128, 520, 9216, 0), (5, 264, 520, 0)])
 def test_gemm_tcgen05(M, N, Kd, bn):
