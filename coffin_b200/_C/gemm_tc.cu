@@ -352,8 +352,8 @@ int pick_bn(int M, int N, int sms, bool allow64) {
 // CTA-pair kernel (gemm_tc2.cu): tile width it would use for [M, N], or 0 for "not this product".
 int cb_gemm_pair_plan(int64_t M, int64_t N);
 int cb_gemm_pair_run(const void* A, int64_t lda, const void* W, int64_t ldw, void* C, int64_t ldc, const void* residual,
-                     int64_t ldr, int64_t M, int64_t N, int64_t K, int tile, const void* pf, int64_t pf_seq,
-                     void* status, void* stream);
+                     int64_t ldr, const void* row_scale, const void* col_scale, int64_t M, int64_t N, int64_t K, int tile,
+                     const void* pf, int64_t pf_seq, void* status, void* stream);
 
 // C[M,N] (bf16) = A[M,K] (bf16) x W[N,K]^T (bf16) (+ residual[M,N]).  K % 8 == 0, N % 8 == 0.
 // bn_hint: 0 = choose (CTA pairs for more than 256 rows), 64/128/160/256 = one-CTA kernel with that tile
@@ -367,7 +367,7 @@ CB_EXPORT int cb_gemm_bf16(const void* A, int64_t lda, const void* W, int64_t ld
   int bn = (int)bn_hint;
   if (bn == 0 || bn >= 1000) {
     const int tile = bn >= 1000 ? bn - 1000 : cb_gemm_pair_plan(M, N);
-    if (tile) return cb_gemm_pair_run(A, lda, W, ldw, C, ldc, residual, ldr, M, N, K, tile, pf, pf_seq, status, stream);
+    if (tile) return cb_gemm_pair_run(A, lda, W, ldw, C, ldc, residual, ldr, nullptr, nullptr, M, N, K, tile, pf, pf_seq, status, stream);
   }
   if (!bn) bn = pick_bn((int)M, (int)N, sms, true);
   CUtensorMap tmA, tmB;
@@ -400,6 +400,11 @@ CB_EXPORT int cb_gemm_i8(const void* A, int64_t lda, const void* W, int64_t ldw,
     return CB_ERR_SHAPE;
   const int sms = sm_count();
   int bn = (int)bn_hint;
+  if (bn == 0 || bn >= 1000) {
+    const int tile = bn >= 1000 ? bn - 1000 : cb_gemm_pair_plan(M, N);
+    if (tile)
+      return cb_gemm_pair_run(A, lda, W, ldw, C, ldc, residual, ldr, row_scale, col_scale, M, N, K, tile, pf, pf_seq, status, stream);
+  }
   if (!bn) bn = pick_bn((int)M, (int)N, sms, false);
   CUtensorMap tmA, tmB;
   int rc = cb_make_tmap_2d(&tmA, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, BM, 128);

@@ -1,4 +1,4 @@
-// Prefill GEMM on CTA pairs: C[M,N] = A[M,K] * W[N,K]^T (+ residual), bf16, 256-row tiles.
+// Prefill GEMM on CTA pairs: C[M,N] = A[M,K] * W[N,K]^T (+ residual), bf16 or int8 (W8A8), 256-row tiles.
 //
 // Two CTAs of a cluster (two SMs) work on one 256 x TILE_N output tile with tcgen05.mma
 // cta_group::2: each CTA stages only its own 128 rows of A and HALF of the tile's weight rows, the
@@ -29,6 +29,8 @@ constexpr int PM = 128;            // rows of A per CTA (256 per pair)
 struct PairArgs {
   bf16* C; int64_t ldc;
   const bf16* residual; int64_t ldr;
+  const float* row_scale;          // int8: [M] activation scales
+  const float* col_scale;          // int8: [N] weight scales
   int M, N, K;
   int m_tiles, n_tiles, k_blocks;  // m_tiles counts 256-row tiles
   int* status;
@@ -51,7 +53,7 @@ __device__ __forceinline__ bool wait_bar2(uint64_t* bar, uint32_t parity, volati
   }
 }
 
-template <int BNI, int NI, int STAGES>
+template <int BNI, int NI, int STAGES, bool I8>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreadsPair, 1)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const PairArgs a) {
   constexpr int TILE_N = BNI * NI;
@@ -59,7 +61,8 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   constexpr int A_BYTES = PM * 128, BJ_BYTES = BH * 128, STAGE_BYTES = A_BYTES + NI * BJ_BYTES;
   constexpr int ACC_BUFS = 2 * TILE_N <= 512 ? 2 : 1;
   constexpr uint32_t TMEM_COLS = ACC_BUFS * TILE_N <= 256 ? 256 : 512;
-  constexpr uint32_t IDESC = umma_idesc(256, BNI, 1, 1);
+  constexpr uint32_t IDESC = umma_idesc(256, BNI, 1, I8 ? 2 : 1);
+  constexpr int BK = I8 ? 128 : 64;                 // elements per 128-byte k-block
   static_assert(BNI % 16 == 0 && BNI <= 256 && BH % 8 == 0 && TILE_N % 32 == 0, "tile shape");
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   unsigned char* tiles = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -109,10 +112,10 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           if (leader) mbar_expect_tx(&full_bar[s], 2 * STAGE_BYTES);
           const uint32_t fb = map_to_cta(smem_u32(&full_bar[s]), 0);
           unsigned char* st = tiles + (size_t)s * STAGE_BYTES;
-          tma_load_2d_pair(st, &tmA, fb, kb * 64, m0);
+          tma_load_2d_pair(st, &tmA, fb, kb * BK, m0);
 #pragma unroll
           for (int j = 0; j < NI; ++j)
-            tma_load_2d_pair(st + A_BYTES + j * BJ_BYTES, &tmB, fb, kb * 64, n0 + j * BNI + (int)rank * BH);
+            tma_load_2d_pair(st + A_BYTES + j * BJ_BYTES, &tmB, fb, kb * BK, n0 + j * BNI + (int)rank * BH);
         }
       }
     }
@@ -142,7 +145,8 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 #pragma unroll
             for (int j = 0; j < NI; ++j) {
               const uint64_t bd = umma_desc_sw128(st + A_BYTES + j * BJ_BYTES);
-              umma_f16_pair(d_tmem + j * BNI, ad + 2 * k, bd + 2 * k, IDESC, (kb | k) != 0);
+              if (I8) umma_i8_pair(d_tmem + j * BNI, ad + 2 * k, bd + 2 * k, IDESC, (kb | k) != 0);
+              else umma_f16_pair(d_tmem + j * BNI, ad + 2 * k, bd + 2 * k, IDESC, (kb | k) != 0);
             }
           }
           umma_commit_pair(&empty_bar[s], 3);
@@ -165,6 +169,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       }
       tc_fence_after();
       const int row = m0 + q * 32 + lane;
+      const float rs = (I8 && row < a.M) ? a.row_scale[row] : 1.f;
 #pragma unroll 1
       for (int c0 = 0; c0 < TILE_N; c0 += 32) {
         uint32_t r[32];
@@ -185,7 +190,10 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             if (col0 + v * 8 >= a.N) break;  // N is a multiple of 8
             float f[8];
 #pragma unroll
-            for (int i = 0; i < 8; ++i) f[i] = __uint_as_float(r[v * 8 + i]);
+            for (int i = 0; i < 8; ++i) {
+              if (I8) f[i] = (float)(int)r[v * 8 + i] * rs * a.col_scale[col0 + v * 8 + i];
+              else f[i] = __uint_as_float(r[v * 8 + i]);
+            }
             if (rp) {
               float g[8];
               bf16x8_to_float(*reinterpret_cast<const uint4*>(rp + v * 8), g);
@@ -231,17 +239,20 @@ int pair_sm_count() {
   return g_pair_sms;
 }
 
-template <int BNI, int NI, int STAGES>
+template <int BNI, int NI, int STAGES, bool I8>
 int launch_pair(const void* A, int64_t lda, const void* W, int64_t ldw, PairArgs a, cudaStream_t st) {
   constexpr int TILE_N = BNI * NI;
+  const CUtensorMapDataType dt = I8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  constexpr int ES = I8 ? 1 : 2;
   CUtensorMap tmA, tmB;
-  int rc = cb_make_tmap_2d(&tmA, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, A, (uint64_t)a.M, (uint64_t)a.K, (uint64_t)lda, PM, 64);
+  int rc = cb_make_tmap_2d(&tmA, dt, ES, A, (uint64_t)a.M, (uint64_t)a.K, (uint64_t)lda, PM, 128 / ES);
   if (rc) return rc;
-  rc = cb_make_tmap_2d(&tmB, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, W, (uint64_t)a.N, (uint64_t)a.K, (uint64_t)ldw, BNI / 2, 64);
+  rc = cb_make_tmap_2d(&tmB, dt, ES, W, (uint64_t)a.N, (uint64_t)a.K, (uint64_t)ldw, BNI / 2, 128 / ES);
   if (rc) return rc;
+  a.k_blocks = (a.K * ES + 127) / 128;
   a.n_tiles = (a.N + TILE_N - 1) / TILE_N;
   const size_t smem = (size_t)STAGES * (PM * 128 + NI * (BNI / 2) * 128) + 1024;
-  auto kern = gemm_tc_pair_kernel<BNI, NI, STAGES>;
+  auto kern = gemm_tc_pair_kernel<BNI, NI, STAGES, I8>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return (int)e;
   const int total = a.m_tiles * a.n_tiles, pairs = pair_sm_count() / 2;
@@ -270,19 +281,26 @@ int cb_gemm_pair_plan(int64_t M, int64_t N) {
   return best;
 }
 
-// tile: 256 or 320 (0 = choose).  Same contract as cb_gemm_bf16 (K % 8 == 0, N % 8 == 0).
+// tile: 256 or 320 (0 = choose).  row_scale / col_scale given: int8 operands (contract of cb_gemm_i8), else
+// bf16 (contract of cb_gemm_bf16).
 int cb_gemm_pair_run(const void* A, int64_t lda, const void* W, int64_t ldw, void* C, int64_t ldc, const void* residual,
-                     int64_t ldr, int64_t M, int64_t N, int64_t K, int tile, const void* pf, int64_t pf_seq,
-                     void* status, void* stream) {
+                     int64_t ldr, const void* row_scale, const void* col_scale, int64_t M, int64_t N, int64_t K, int tile,
+                     const void* pf, int64_t pf_seq, void* status, void* stream) {
   PairArgs a;
   a.C = (bf16*)C; a.ldc = ldc; a.residual = (const bf16*)residual; a.ldr = ldr;
+  a.row_scale = (const float*)row_scale; a.col_scale = (const float*)col_scale;
   a.M = (int)M; a.N = (int)N; a.K = (int)K; a.m_tiles = (int)((M + 255) / 256); a.n_tiles = 0;
   a.k_blocks = (int)((K + 63) / 64); a.status = (int*)status;
   a.pf = (const TpPfDev*)pf; a.pf_seq = (unsigned)pf_seq;
   cudaStream_t st = (cudaStream_t)stream;
   if (!tile) tile = cb_gemm_pair_plan(M, N);
-  if (tile == 256) return launch_pair<256, 1, 6>(A, lda, W, ldw, a, st);
-  if (tile == 320) return launch_pair<160, 2, 6>(A, lda, W, ldw, a, st);
+  if (row_scale) {
+    if (tile == 256) return launch_pair<256, 1, 6, true>(A, lda, W, ldw, a, st);
+    if (tile == 320) return launch_pair<160, 2, 6, true>(A, lda, W, ldw, a, st);
+    return CB_ERR_ARG;
+  }
+  if (tile == 256) return launch_pair<256, 1, 6, false>(A, lda, W, ldw, a, st);
+  if (tile == 320) return launch_pair<160, 2, 6, false>(A, lda, W, ldw, a, st);
   return CB_ERR_ARG;
 }
 

@@ -117,7 +117,10 @@ def test_gemm_tcgen05(M, N, Kd, bn):
 
 
 @pytest.mark.parametrize("M,N,Kd,bn", [(128, 256, 128, 256), (200, 264, 400, 128), (77, 520, 1040, 0),
-                                       (300, 488, 528, 160), (64, 2560, 4096, 0), (16, 520, 9216, 0)])
+                                       (300, 488, 528, 160), (64, 2560, 4096, 0), (16, 520, 9216, 0),
+                                       # CTA pairs
+                                       (300, 488, 528, 1256), (300, 488, 528, 1320), (1000, 1536, 512, 0),
+                                       (2048, 2560, 4096, 1320)])
 def test_gemm_i8_tcgen05(M, N, Kd, bn):
     k = K()
     g = torch.Generator().manual_seed(13)
