@@ -35,6 +35,7 @@ struct PairArgs {
   int m_tiles, n_tiles, k_blocks;  // m_tiles counts 256-row tiles
   int* status;
   const TpPfDev* pf; unsigned pf_seq;   // tensor-parallel prefill: rows go to their owner's inbox (tp.cuh)
+  int up_off;                      // SwiGLU form: W is [gate rows | up rows], the up rows start here; N counts outputs
 };
 
 __device__ __forceinline__ uint64_t now_ns() {
@@ -53,7 +54,11 @@ __device__ __forceinline__ bool wait_bar2(uint64_t* bar, uint32_t parity, volati
   }
 }
 
-template <int BNI, int NI, int STAGES, bool I8>
+// SWIGLU (one MMA of N = 256, bf16): the even CTA stages 128 gate rows of W, the odd CTA the 128 up rows
+// of the same output columns, so accumulator columns [0, 128) hold the gate and [128, 256) the up
+// projection of one 128-column output tile; the epilogue writes silu(gate) * up and the [M, 2I]
+// intermediate never reaches memory.
+template <int BNI, int NI, int STAGES, bool I8, bool SWIGLU = false>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreadsPair, 1)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const PairArgs a) {
   constexpr int TILE_N = BNI * NI;
@@ -63,7 +68,9 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   constexpr uint32_t TMEM_COLS = ACC_BUFS * TILE_N <= 256 ? 256 : 512;
   constexpr uint32_t IDESC = umma_idesc(256, BNI, 1, I8 ? 2 : 1);
   constexpr int BK = I8 ? 128 : 64;                 // elements per 128-byte k-block
+  constexpr int OUT_N = SWIGLU ? TILE_N / 2 : TILE_N;   // output columns of a tile
   static_assert(BNI % 16 == 0 && BNI <= 256 && BH % 8 == 0 && TILE_N % 32 == 0, "tile shape");
+  static_assert(!SWIGLU || (NI == 1 && !I8), "the SwiGLU form is one bf16 MMA per k-step");
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   unsigned char* tiles = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   __shared__ uint64_t full_bar[STAGES], empty_bar[STAGES], acc_full[2], acc_empty[2];
@@ -102,7 +109,8 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     if (lane == 0) {
       uint32_t it = 0;
       for (int tile = pair; tile < total && !*abort_flag; tile += npairs) {
-        const int m0 = (tile % a.m_tiles) * 256 + (int)rank * PM, n0 = (tile / a.m_tiles) * TILE_N;
+        const int m0 = (tile % a.m_tiles) * 256 + (int)rank * PM, n0 = (tile / a.m_tiles) * OUT_N;
+        const int brow = SWIGLU ? n0 + (int)rank * a.up_off : n0 + (int)rank * BH;
         for (int kb = 0; kb < a.k_blocks; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
@@ -115,7 +123,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           tma_load_2d_pair(st, &tmA, fb, kb * BK, m0);
 #pragma unroll
           for (int j = 0; j < NI; ++j)
-            tma_load_2d_pair(st + A_BYTES + j * BJ_BYTES, &tmB, fb, kb * BK, n0 + j * BNI + (int)rank * BH);
+            tma_load_2d_pair(st + A_BYTES + j * BJ_BYTES, &tmB, fb, kb * BK, brow + j * BNI);
         }
       }
     }
@@ -161,7 +169,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     uint32_t tcount = 0;
     const uint32_t ae0 = map_to_cta(smem_u32(&acc_empty[0]), 0), ae1 = map_to_cta(smem_u32(&acc_empty[1]), 0);
     for (int tile = pair; tile < total && !*abort_flag; tile += npairs, ++tcount) {
-      const int m0 = (tile % a.m_tiles) * 256 + (int)rank * PM, n0 = (tile / a.m_tiles) * TILE_N;
+      const int m0 = (tile % a.m_tiles) * 256 + (int)rank * PM, n0 = (tile / a.m_tiles) * OUT_N;
       const uint32_t acc = tcount % ACC_BUFS, aph = (tcount / ACC_BUFS) & 1;
       if (!wait_bar2(&acc_full[acc], aph, abort_flag)) {
         if (lane == 0) { atomicExch(a.status, 84); abort_s = 1; st_cluster_u32(peer_abort, 1); }
@@ -170,6 +178,28 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       tc_fence_after();
       const int row = m0 + q * 32 + lane;
       const float rs = (I8 && row < a.M) ? a.row_scale[row] : 1.f;
+      if (SWIGLU) {
+#pragma unroll 1
+        for (int c0 = 0; c0 < OUT_N; c0 += 32) {
+          uint32_t rg[32], ru[32];
+          const uint32_t ta = tmem_base + acc * TILE_N + ((uint32_t)(q * 32) << 16) + c0;
+          tmem_ld32(ta, rg);
+          tmem_ld32(ta + OUT_N, ru);
+          tmem_ld_wait();
+          const int col0 = n0 + c0;
+          if (row < a.M && col0 < a.N) {
+            bf16* cp = a.C + (int64_t)row * a.ldc + col0;
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              if (col0 + v * 8 >= a.N) break;  // N is a multiple of 8
+              float f[8];
+#pragma unroll
+              for (int i = 0; i < 8; ++i) f[i] = silu_f(__uint_as_float(rg[v * 8 + i])) * __uint_as_float(ru[v * 8 + i]);
+              *reinterpret_cast<uint4*>(cp + v * 8) = float_to_bf16x8(f);
+            }
+          }
+        }
+      } else
 #pragma unroll 1
       for (int c0 = 0; c0 < TILE_N; c0 += 32) {
         uint32_t r[32];
@@ -239,7 +269,7 @@ int pair_sm_count() {
   return g_pair_sms;
 }
 
-template <int BNI, int NI, int STAGES, bool I8>
+template <int BNI, int NI, int STAGES, bool I8, bool SWIGLU = false>
 int launch_pair(const void* A, int64_t lda, const void* W, int64_t ldw, PairArgs a, cudaStream_t st) {
   constexpr int TILE_N = BNI * NI;
   const CUtensorMapDataType dt = I8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
@@ -247,12 +277,14 @@ int launch_pair(const void* A, int64_t lda, const void* W, int64_t ldw, PairArgs
   CUtensorMap tmA, tmB;
   int rc = cb_make_tmap_2d(&tmA, dt, ES, A, (uint64_t)a.M, (uint64_t)a.K, (uint64_t)lda, PM, 128 / ES);
   if (rc) return rc;
-  rc = cb_make_tmap_2d(&tmB, dt, ES, W, (uint64_t)a.N, (uint64_t)a.K, (uint64_t)ldw, BNI / 2, 128 / ES);
+  const uint64_t w_rows = SWIGLU ? (uint64_t)a.up_off + (uint64_t)a.N : (uint64_t)a.N;
+  rc = cb_make_tmap_2d(&tmB, dt, ES, W, w_rows, (uint64_t)a.K, (uint64_t)ldw, BNI / 2, 128 / ES);
   if (rc) return rc;
   a.k_blocks = (a.K * ES + 127) / 128;
-  a.n_tiles = (a.N + TILE_N - 1) / TILE_N;
+  constexpr int OUT_N = SWIGLU ? TILE_N / 2 : TILE_N;
+  a.n_tiles = (a.N + OUT_N - 1) / OUT_N;
   const size_t smem = (size_t)STAGES * (PM * 128 + NI * (BNI / 2) * 128) + 1024;
-  auto kern = gemm_tc_pair_kernel<BNI, NI, STAGES, I8>;
+  auto kern = gemm_tc_pair_kernel<BNI, NI, STAGES, I8, SWIGLU>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return (int)e;
   const int total = a.m_tiles * a.n_tiles, pairs = pair_sm_count() / 2;
@@ -291,7 +323,7 @@ int cb_gemm_pair_run(const void* A, int64_t lda, const void* W, int64_t ldw, voi
   a.row_scale = (const float*)row_scale; a.col_scale = (const float*)col_scale;
   a.M = (int)M; a.N = (int)N; a.K = (int)K; a.m_tiles = (int)((M + 255) / 256); a.n_tiles = 0;
   a.k_blocks = (int)((K + 63) / 64); a.status = (int*)status;
-  a.pf = (const TpPfDev*)pf; a.pf_seq = (unsigned)pf_seq;
+  a.pf = (const TpPfDev*)pf; a.pf_seq = (unsigned)pf_seq; a.up_off = 0;
   cudaStream_t st = (cudaStream_t)stream;
   if (!tile) tile = cb_gemm_pair_plan(M, N);
   if (row_scale) {
@@ -302,6 +334,19 @@ int cb_gemm_pair_run(const void* A, int64_t lda, const void* W, int64_t ldw, voi
   if (tile == 256) return launch_pair<256, 1, 6, false>(A, lda, W, ldw, a, st);
   if (tile == 320) return launch_pair<160, 2, 6, false>(A, lda, W, ldw, a, st);
   return CB_ERR_ARG;
+}
+
+// C[M, I] = silu(A W[0:I]^T) * (A W[up_off:up_off+I]^T), bf16: the gate|up projection with its SwiGLU product
+// in the epilogue.  More than 256 rows (smaller products: cb_gemm_bf16 + cb_swiglu).  K % 8 == 0, I % 8 == 0.
+CB_EXPORT int cb_gemm_bf16_swiglu(const void* A, int64_t lda, const void* W, int64_t ldw, void* C, int64_t ldc,
+                                  int64_t M, int64_t I, int64_t up_off, int64_t K, void* status, void* stream) {
+  if (M < 1 || I < 1 || K < 1 || up_off < I) return CB_ERR_SHAPE;
+  if (K % 8 || I % 8 || ldc % 8 || !status) return CB_ERR_SHAPE;
+  PairArgs a;
+  a.C = (bf16*)C; a.ldc = ldc; a.residual = nullptr; a.ldr = 0; a.row_scale = nullptr; a.col_scale = nullptr;
+  a.M = (int)M; a.N = (int)I; a.K = (int)K; a.m_tiles = (int)((M + 255) / 256); a.n_tiles = 0;
+  a.k_blocks = 0; a.status = (int*)status; a.pf = nullptr; a.pf_seq = 0; a.up_off = (int)up_off;
+  return launch_pair<256, 1, 6, false, true>(A, lda, W, ldw, a, (cudaStream_t)stream);
 }
 
 // 0: every bf16 product runs on the one-CTA kernel.

@@ -375,6 +375,17 @@ class Qwen35Model:
             A = K.swiglu(A)
         return K.gemm(A, W, out=out, residual=residual, push=push)
 
+    def _gemm_gu(self, A, W, gu: torch.Tensor):
+        """Gate|up projection of a prefill chunk into ``gu [T, 2I]``.  bf16 weights and more rows than one
+        CTA-pair tile: the SwiGLU product comes out of the GEMM epilogue and the ``[T, I]`` view holding it
+        is returned; otherwise ``gu`` is filled with both halves and None is returned."""
+        if isinstance(W, QW4):
+            W = W.expanded()
+        if not isinstance(W, QW) and K.PAIR_GEMM and A.shape[0] >= K.PAIR_MIN_ROWS and W.shape[0] >= 256:
+            return K.gemm_swiglu(A, W, out=gu[:, :W.shape[0] // 2])
+        self._gemm(A, W, out=gu)
+        return None
+
     def _row_parallel(self, A, W, scratch: torch.Tensor, swiglu_in: bool = False) -> torch.Tensor:
         """Row-parallel projection + all-reduce.  With a peer-memory region the all-reduce is a
         reduce-scatter + all-gather over NVLink peer stores: for a prefill chunk the tcgen05 GEMM epilogue
@@ -557,11 +568,13 @@ class Qwen35Model:
                 lw.moe.forward_prefill(normed, res, self)
             else:
                 gu = ws["gu"][:T]
-                self._gemm(normed, lw.w_gu, out=gu)
+                fused = self._gemm_gu(normed, lw.w_gu, gu)       # SwiGLU taken in the epilogue: gu[:, :I] is the product
+                if fused is not None:
+                    gu = fused
                 if self.tp_world > 1 or self.tp_force:
-                    res.add_(self._row_parallel(gu, lw.w_down, ws["part"][:T], swiglu_in=True))
+                    res.add_(self._row_parallel(gu, lw.w_down, ws["part"][:T], swiglu_in=fused is None))
                 else:
-                    self._gemm(gu, lw.w_down, out=res, residual=res, swiglu_in=True)
+                    self._gemm(gu, lw.w_down, out=res, residual=res, swiglu_in=fused is None)
         self.last_hidden = None
         self.last_prenorm = res            # last-layer residual stream of the group (view of the workspace)
         out: list = [None] * len(items)

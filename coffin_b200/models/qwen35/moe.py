@@ -263,7 +263,7 @@ class MoEWeights:
         y = K.gemm_grouped(inter, self._stack(self.down), disp)
         shared = gate = None
         if self.sh_gu is not None:
-            sh = K.swiglu(K.gemm(normed, self.sh_gu))
+            sh = K.gemm_swiglu(normed, self.sh_gu)
             shared = K.gemm(sh, self.sh_down)
             gate = logits[:, E:].contiguous()
         out = torch.empty(T, H, dtype=torch.bfloat16, device=normed.device)

@@ -457,6 +457,31 @@ def gemm(A: torch.Tensor, W: torch.Tensor, out: torch.Tensor | None = None,
     return out
 
 
+# CTA-pair kernel for products of more than 256 rows (COFFIN_GEMM_PAIR=0: one-CTA kernel everywhere).
+PAIR_GEMM = os.environ.get("COFFIN_GEMM_PAIR", "1") != "0"
+PAIR_MIN_ROWS = 257
+if not PAIR_GEMM:
+    _lib.call_nostream("set_gemm_pair", 0)
+
+
+def gemm_swiglu(A: torch.Tensor, Wgu: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """``out[M, I] = silu(A @ Wgu[:I]^T) * (A @ Wgu[I:]^T)``: the gate|up projection with the SwiGLU
+    product taken in the GEMM epilogue (CTA-pair kernel; the even CTA of a pair stages gate rows, the
+    odd one the matching up rows), so the ``[M, 2I]`` intermediate is never written.  Smaller products
+    run as projection + ``swiglu``."""
+    M, K = A.shape
+    I = Wgu.shape[0] // 2
+    assert A.stride(1) == 1 and Wgu.stride(1) == 1
+    if out is None:
+        out = torch.empty(M, I, dtype=torch.bfloat16, device=A.device)
+    assert out.stride(1) == 1
+    if not (PAIR_GEMM and M >= PAIR_MIN_ROWS and I >= 128):
+        return swiglu(gemm(A, Wgu), out=out)
+    call("gemm_bf16_swiglu", A, A.stride(0), Wgu, Wgu.stride(0), out, out.stride(0), M, I, I, K, status_word(A.device))
+    _count()
+    return out
+
+
 # Products with at most 128 rows (batched decode buckets of 16..64 rows, small prefill chunks) split K
 # over CTAs: fp32 partial tiles in a per-device workspace, reduced by the last slice to arrive.
 SPLITK_GEMM = os.environ.get("COFFIN_SPLITK_GEMM", "1") != "0"

@@ -1,6 +1,6 @@
-"""In-graph timeline of one decode step.
+"""In-graph timeline of one decode step (or, with ``--prefill``, of the prefill pass).
 
-    python -m coffin_b200.utils.trace_step --model qwen35-4b --prompt 2048 [--layers 8] [--rows 1]
+    python -m coffin_b200.utils.trace_step --model qwen35-4b --prompt 2048 [--layers 8] [--rows 1] [--prefill]
 
 Every kernel of the library stamps ``%globaltimer`` when its first block enters and when its
 programmatic dependency has resolved (``_C/common.cuh``).  This tool installs the trace buffer,
@@ -104,6 +104,25 @@ def trace_decode(model, M: int, replays: int = 4):
     return rows, step_us, prev_us
 
 
+def trace_prefill(llm, prompt: torch.Tensor):
+    """``[(name, lead_us, span_us)]`` of one prefill pass of ``prompt`` (eager launches, same stamps)."""
+    with StepTrace(llm.model.device) as t:
+        for _ in range(2):
+            llm.device_prefill(prompt)
+        t.reset()
+        t.record_names(True)
+        llm.device_prefill(prompt)
+        t.record_names(False)
+        names = t.names()
+        entry, ready = t.read()
+    n = min(len(names), len(ready))
+    rows = []
+    for i in range(n):
+        span = (ready[i + 1] - ready[i]) / 1e3 if i + 1 < n else float("nan")
+        rows.append((short_name(names[i]), (ready[i] - entry[i]) / 1e3, span))
+    return rows, (ready[n - 1] - ready[0]) / 1e3, float("nan")
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--model", default="qwen35-4b")
@@ -112,6 +131,7 @@ def main() -> None:
     ap.add_argument("--rows", type=int, default=1)
     ap.add_argument("--quant", default="none")
     ap.add_argument("--all", action="store_true", help="print every kernel, not only the first layers")
+    ap.add_argument("--prefill", action="store_true", help="trace the prefill pass of the prompt instead of a decode step")
     ap.add_argument("--mma-stage", type=int, default=-1, help="tuning: GEMV weight batches per warp staged in shared memory before the wait")
     ap.add_argument("--mma-kcta", type=int, default=0, help="max CTAs sharing one 16-row GEMV block (1 = off)")
     ap.add_argument("--mma-prefetch", type=int, default=-1, help="GEMV sweep rounds prefetched into L2 before the wait")
@@ -143,6 +163,17 @@ def main() -> None:
     prompt = torch.randint(0, cfg.vocab_size, (args.prompt,), generator=g).cuda()
     first = llm.device_prefill(prompt)
     m = llm.model
+    if args.prefill:
+        rows, step_us, prev_us = trace_prefill(llm, prompt)
+        if rank == 0:
+            _report(rows, step_us, prev_us, args, what="prefill")
+        if world > 1:
+            import torch.distributed as dist
+            from ..parallel.control import shutdown
+            dist.barrier()
+            m.tp.close()
+            shutdown(timeout_s=10.0)
+        return
     M = m.bucket_for(args.rows)
     bt = list(range(m.max_blocks_per_seq))
     m.set_rows(M, [int(first[0])] * args.rows, [args.prompt] * args.rows, list(range(args.rows)), [bt] * args.rows)
@@ -161,8 +192,8 @@ def main() -> None:
         shutdown(timeout_s=10.0)
 
 
-def _report(rows, step_us, prev_us, args) -> None:
-    print(f"decode step (first ready -> last ready): {step_us:.1f} us; replay period {prev_us:.1f} us; {len(rows)} kernels")
+def _report(rows, step_us, prev_us, args, what: str = "decode step") -> None:
+    print(f"{what} (first ready -> last ready): {step_us:.1f} us; replay period {prev_us:.1f} us; {len(rows)} kernels")
     agg = collections.OrderedDict()
     for name, lead, span in rows:
         a = agg.setdefault(name, [0, 0.0, 0.0])

@@ -116,6 +116,20 @@ def test_gemm_tcgen05(M, N, Kd, bn):
     close(out, A.float() @ W.float().t() + res.float())
 
 
+@pytest.mark.parametrize("M,I,Kd", [(300, 128, 72), (1000, 776, 512), (2048, 9216, 2560), (257, 200, 1032), (64, 256, 128)])
+def test_gemm_swiglu_epilogue(M, I, Kd):
+    """Gate|up projection with silu(gate) * up taken in the CTA-pair GEMM's epilogue (64 rows: two-kernel fallback)."""
+    k = K()
+    A, W = bf(M, Kd, seed=20), bf(2 * I, Kd, s=0.05, seed=21)
+    canary = torch.full((M + 1, I + 8), 7.0, dtype=torch.bfloat16, device=DEV)
+    out = k.gemm_swiglu(A.to(DEV), W.to(DEV), out=canary[:M, :I])
+    torch.cuda.synchronize()
+    k.check_status()
+    gu = A.float() @ W.float().t()
+    close(out, O.silu_mul(gu[:, :I], gu[:, I:]), 2e-2)
+    assert bool((canary[M] == 7.0).all()) and bool((canary[:, I:] == 7.0).all()), "wrote outside the output"
+
+
 @pytest.mark.parametrize("M,N,Kd,bn", [(128, 256, 128, 256), (200, 264, 400, 128), (77, 520, 1040, 0),
                                        (300, 488, 528, 160), (64, 2560, 4096, 0), (16, 520, 9216, 0),
                                        # CTA pairs
