@@ -608,7 +608,9 @@ __device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
 
-template <int DK, int DV>
+// BF: kcd, qe, ke and ica leave as bf16 (same element offsets in the same regions) for the bf16 scan below;
+// the triangular system itself is still solved from TF32 products in fp32.
+template <int DK, int DV, bool BF = false>
 __global__ void __launch_bounds__(256, 2) gdn_chunk_prepare_tc_kernel(const GdnChunkArgs a) {
   using Lay = PrepTcLayout<DK, DV>;
   constexpr int L = kChunk, LDA = Lay::LDA, LDB = Lay::LDB, LDV = Lay::LDV, LDL = Lay::LDL;
@@ -668,6 +670,7 @@ __global__ void __launch_bounds__(256, 2) gdn_chunk_prepare_tc_kernel(const GdnC
       }
     }
     float* icap = a.ica + ((int64_t)h * a.nc + n) * L * L;
+    bf16* icab = reinterpret_cast<bf16*>(a.ica) + ((int64_t)h * a.nc + n) * L * L;
 #pragma unroll
     for (int j = 0; j < 4; ++j)
 #pragma unroll
@@ -675,17 +678,20 @@ __global__ void __launch_bounds__(256, 2) gdn_chunk_prepare_tc_kernel(const GdnC
         const int i = r0 + g + ((e & 2) ? 8 : 0), jj = c0 + j * 8 + 2 * t + (e & 1);
         const float dec = (jj <= i) ? __expf(cs[i] - cs[jj]) : 0.f;
         Tm[i * LDL + jj] = (jj < i) ? bs[i] * dec * kk[j][e] : 0.f;
-        icap[i * L + jj] = dec * qk[j][e];
+        if (BF) icab[i * L + jj] = __float2bfloat16(dec * qk[j][e]);
+        else icap[i * L + jj] = dec * qk[j][e];
       }
   }
   // ---- qe = e^c Q for the scan (Q's last use), zero the inverse ---------------------------------
   {
     float* qep = a.qe + ((int64_t)h * a.nc + n) * L * DK;
+    bf16* qeb = reinterpret_cast<bf16*>(a.qe) + ((int64_t)h * a.nc + n) * L * DK;
     for (int idx = tid; idx < L * DK / 4; idx += 256) {
       const int i = idx / (DK / 4), c = (idx % (DK / 4)) * 4;
       const float ec = __expf(cs[i]);
       const float4 q = *reinterpret_cast<const float4*>(Qs + i * LDA + c);
-      *reinterpret_cast<float4*>(qep + (int64_t)i * DK + c) = make_float4(q.x * ec, q.y * ec, q.z * ec, q.w * ec);
+      if (BF) *reinterpret_cast<uint2*>(qeb + (int64_t)i * DK + c) = make_uint2(pack_bf162(q.x * ec, q.y * ec), pack_bf162(q.z * ec, q.w * ec));
+      else *reinterpret_cast<float4*>(qep + (int64_t)i * DK + c) = make_float4(q.x * ec, q.y * ec, q.z * ec, q.w * ec);
     }
     for (int idx = tid; idx < L * L; idx += 256) Wi[(idx / L) * LDL + idx % L] = 0.f;
   }
@@ -729,12 +735,14 @@ __global__ void __launch_bounds__(256, 2) gdn_chunk_prepare_tc_kernel(const GdnC
   {
     for (int idx = tid; idx < L * L; idx += 256) Wi[(idx / L) * LDL + idx % L] *= bs[idx % L];
     float* kep = a.ke + ((int64_t)h * a.nc + n) * L * DK;
+    bf16* keb = reinterpret_cast<bf16*>(a.ke) + ((int64_t)h * a.nc + n) * L * DK;
     const float cl = cs[L - 1];
     for (int idx = tid; idx < L * DK / 4; idx += 256) {
       const int i = idx / (DK / 4), c = (idx % (DK / 4)) * 4;
       const float ec = __expf(cs[i]), el = __expf(cl - cs[i]);
       const float4 k = *reinterpret_cast<const float4*>(Ks + i * LDA + c);
-      *reinterpret_cast<float4*>(kep + (int64_t)i * DK + c) = make_float4(k.x * el, k.y * el, k.z * el, k.w * el);
+      if (BF) *reinterpret_cast<uint2*>(keb + (int64_t)i * DK + c) = make_uint2(pack_bf162(k.x * el, k.y * el), pack_bf162(k.z * el, k.w * el));
+      else *reinterpret_cast<float4*>(kep + (int64_t)i * DK + c) = make_float4(k.x * el, k.y * el, k.z * el, k.w * el);
       *reinterpret_cast<float4*>(Kb + i * LDB + c) = make_float4(k.x * ec, k.y * ec, k.z * ec, k.w * ec);
     }
     if (tid == 0) a.ecl[(int64_t)h * a.nc + n] = __expf(cl);
@@ -773,12 +781,18 @@ __global__ void __launch_bounds__(256, 2) gdn_chunk_prepare_tc_kernel(const GdnC
       }
     }
     float* dst = isv ? a.nvv + ((int64_t)h * a.nc + n) * L * DV : a.kcd + ((int64_t)h * a.nc + n) * L * DK;
+    bf16* dstb = reinterpret_cast<bf16*>(a.kcd) + ((int64_t)h * a.nc + n) * L * DK;
     const int ldd = isv ? DV : DK;
 #pragma unroll
     for (int j = 0; j < NT; ++j) {
       if (j < nt) {
-        *reinterpret_cast<float2*>(dst + (r0 + g) * ldd + j * 8 + 2 * t) = make_float2(acc[j][0], acc[j][1]);
-        *reinterpret_cast<float2*>(dst + (r0 + g + 8) * ldd + j * 8 + 2 * t) = make_float2(acc[j][2], acc[j][3]);
+        if (BF && !isv) {
+          *reinterpret_cast<uint32_t*>(dstb + (r0 + g) * ldd + j * 8 + 2 * t) = pack_bf162(acc[j][0], acc[j][1]);
+          *reinterpret_cast<uint32_t*>(dstb + (r0 + g + 8) * ldd + j * 8 + 2 * t) = pack_bf162(acc[j][2], acc[j][3]);
+        } else {
+          *reinterpret_cast<float2*>(dst + (r0 + g) * ldd + j * 8 + 2 * t) = make_float2(acc[j][0], acc[j][1]);
+          *reinterpret_cast<float2*>(dst + (r0 + g + 8) * ldd + j * 8 + 2 * t) = make_float2(acc[j][2], acc[j][3]);
+        }
       }
     }
   }
@@ -925,6 +939,185 @@ __global__ void __launch_bounds__(256) gdn_chunk_scan_tc_kernel(const GdnScanArg
   for (int idx = tid; idx < DK * DVS; idx += 256) sp[(int64_t)(idx / DVS) * DV + idx % DVS] = S[(idx / DVS) * LDS + idx % DVS];
 }
 
+// ---------------------------------------------------------------------------------------------
+// bf16-operand scan.  The same recurrence with kcd, qe, ke, ica (written as bf16 by the prepare kernel)
+// and the copies of S and U that enter a product rounded to bf16 (mma.m16n8k16, fp32 accumulate); the
+// state itself stays fp32 in the registers of the warp that owns its tile, from the first chunk to the
+// last.  Half-size operands make room for a three-stage ring of whole-chunk operand sets, so the loads
+// of chunk n+2 are in flight while chunk n is multiplied: the TF32 scan could only look half a chunk
+// ahead and spent most of a chunk waiting for L2.  Fragments come from ldmatrix (.trans where the
+// stored layout has the reduction index in rows); row strides of 16 B (mod 128) keep them conflict free.
+__device__ __forceinline__ void mma_bf16(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t* r) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_t(uint32_t addr, uint32_t* r) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ uint32_t smem_u32addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void cp_async_wait_1() { asm volatile("cp.async.wait_group 1;" ::: "memory"); }
+
+template <int DK, int DVS>
+struct ScanBfLayout {
+  static constexpr int L = kChunk, LDA = DK + 8, LDL = L + 8, LDS = DVS + 8, STAGES = 3;
+  // stage: kcd [L][LDA], qe [L][LDA], ke [L][LDA], ica [L][LDL] (bf16); then S copy [DK][LDS], U [L][LDS] (bf16)
+  static constexpr size_t stage_bytes = 2 * ((size_t)3 * L * LDA + (size_t)L * LDL);
+  static constexpr size_t bytes = STAGES * stage_bytes + 2 * ((size_t)DK * LDS + (size_t)L * LDS);
+};
+
+template <int DK, int DV, int DVS>
+__global__ void __launch_bounds__(256) gdn_chunk_scan_bf_kernel(const GdnScanArgs a) {
+  using Lay = ScanBfLayout<DK, DVS>;
+  constexpr int L = kChunk, LDA = Lay::LDA, LDL = Lay::LDL, LDS = Lay::LDS, ST = Lay::STAGES;
+  constexpr int NRT = DK / 16;                 // row tiles of the state
+  constexpr int CG = 8 / NRT;                  // column groups the 8 warps split the state into
+  constexpr int NTS = (DVS / 8) / CG;          // n-tiles of a warp's state tile (2 or 4)
+  static_assert(DVS == 32 && (DK == 64 || DK == 128), "tiling");
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  bf16* Sb = reinterpret_cast<bf16*>(smem_raw + ST * Lay::stage_bytes);
+  bf16* Ub = Sb + DK * LDS;
+  griddep_launch();
+  griddep_wait();
+  const int h = blockIdx.x, sl = blockIdx.y, tid = threadIdx.x;
+  const int lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
+  const int col0 = sl * DVS;
+  const bf16* kcd = reinterpret_cast<const bf16*>(a.kcd);
+  const bf16* qe = reinterpret_cast<const bf16*>(a.qe);
+  const bf16* ke = reinterpret_cast<const bf16*>(a.ke);
+  const bf16* ica = reinterpret_cast<const bf16*>(a.ica);
+  auto load_chunk = [&](int n) {
+    if (n < a.nc) {
+      bf16* st = reinterpret_cast<bf16*>(smem_raw + (size_t)(n % ST) * Lay::stage_bytes);
+      const int64_t base = (int64_t)h * a.nc + n;
+      for (int idx = tid; idx < L * DK / 8; idx += 256) {
+        const int i = idx / (DK / 8), c = (idx % (DK / 8)) * 8;
+        const int64_t off = base * L * DK + (int64_t)i * DK + c;
+        cp_async16(st + i * LDA + c, kcd + off);
+        cp_async16(st + L * LDA + i * LDA + c, qe + off);
+        cp_async16(st + 2 * L * LDA + i * LDA + c, ke + off);
+      }
+      for (int idx = tid; idx < L * L / 8; idx += 256) {
+        const int i = idx / (L / 8), c = (idx % (L / 8)) * 8;
+        cp_async16(st + 3 * L * LDA + i * LDL + c, ica + base * L * L + (int64_t)i * L + c);
+      }
+    }
+    cp_async_commit();            // one group per chunk, empty past the end: the wait below counts groups
+  };
+  load_chunk(0);
+  load_chunk(1);
+  const int r0 = (warp & 3) * 16, ch = (warp >> 2) * 16;                // U / O tile of this warp: 16 rows x 16 columns
+  const int s0 = (warp % NRT) * 16, sc0 = (warp / NRT) * (NTS * 8);    // state tile: 16 rows x NTS*8 columns
+  // the warp's tile of the state: fp32 in registers for the whole scan, bf16 copy in shared memory
+  float* sp = a.state + (int64_t)h * DK * DV + col0;
+  float accS[NTS][4];
+#pragma unroll
+  for (int j = 0; j < NTS; ++j) {
+    const float2 x0 = *reinterpret_cast<const float2*>(sp + (int64_t)(s0 + g) * DV + sc0 + j * 8 + 2 * t);
+    const float2 x1 = *reinterpret_cast<const float2*>(sp + (int64_t)(s0 + g + 8) * DV + sc0 + j * 8 + 2 * t);
+    accS[j][0] = x0.x; accS[j][1] = x0.y; accS[j][2] = x1.x; accS[j][3] = x1.y;
+    *reinterpret_cast<uint32_t*>(Sb + (s0 + g) * LDS + sc0 + j * 8 + 2 * t) = pack_bf162(x0.x, x0.y);
+    *reinterpret_cast<uint32_t*>(Sb + (s0 + g + 8) * LDS + sc0 + j * 8 + 2 * t) = pack_bf162(x1.x, x1.y);
+  }
+  // per-lane fragment addresses (element offsets inside a tile)
+  const int a_row = (lane & 7) + ((lane >> 3) & 1) * 8, a_col = (lane >> 4) * 8;        // A, row-major
+  const int t_row = (lane & 7) + ((lane >> 4) & 1) * 8, t_col = ((lane >> 3) & 1) * 8;  // A from transposed storage
+  const int b_row = (lane & 7) + ((lane >> 3) & 1) * 8, b_col = (lane >> 4) * 8;        // B from [k][n] storage
+  const uint32_t sb_u = smem_u32addr(Sb), ub_u = smem_u32addr(Ub);
+  // nvv and e^{c_L} of the next chunk travel in registers, one chunk ahead
+  float2 nv0[2], nv1[2];
+  float el = 0.f;
+  auto load_nv = [&](int n) {
+    if (n < a.nc) {
+      const int64_t base = (int64_t)h * a.nc + n;
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        const float* nvp = a.nvv + base * L * DV + col0 + ch + j * 8 + 2 * t;
+        nv0[j] = *reinterpret_cast<const float2*>(nvp + (int64_t)(r0 + g) * DV);
+        nv1[j] = *reinterpret_cast<const float2*>(nvp + (int64_t)(r0 + g + 8) * DV);
+      }
+      el = a.ecl[base];
+    }
+  };
+  load_nv(0);
+  for (int n = 0; n < a.nc; ++n) {
+    cp_async_wait_1();
+    __syncthreads();          // chunk n's operands and the S copy are visible; every warp has left chunk n-1
+    load_chunk(n + 2);
+    const uint32_t st_u = smem_u32addr(smem_raw + (size_t)(n % ST) * Lay::stage_bytes);
+    const uint32_t a1_u = st_u, a2_u = st_u + 2 * L * LDA, a3_u = st_u + 4 * L * LDA, ic_u = st_u + 6 * L * LDA;
+    const float2 cnv0[2] = {nv0[0], nv0[1]}, cnv1[2] = {nv1[0], nv1[1]};
+    const float cel = el;
+    load_nv(n + 1);
+    // ---- accU = kcd S, accO = qe S ------------------------------------------------------------
+    float accU[2][4] = {}, accO[2][4] = {};
+#pragma unroll
+    for (int k0 = 0; k0 < DK; k0 += 16) {
+      uint32_t ak[4], aq[4], b[4];
+      ldsm_x4(a1_u + 2 * ((r0 + a_row) * LDA + k0 + a_col), ak);
+      ldsm_x4(a2_u + 2 * ((r0 + a_row) * LDA + k0 + a_col), aq);
+      ldsm_x4_t(sb_u + 2 * ((k0 + b_row) * LDS + ch + b_col), b);
+      mma_bf16(accU[0], ak, b[0], b[1]);
+      mma_bf16(accU[1], ak, b[2], b[3]);
+      mma_bf16(accO[0], aq, b[0], b[1]);
+      mma_bf16(accO[1], aq, b[2], b[3]);
+    }
+    // ---- U = nvv - accU -> shared (bf16) ----------------------------------------------------------
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      *reinterpret_cast<uint32_t*>(Ub + (r0 + g) * LDS + ch + j * 8 + 2 * t) = pack_bf162(cnv0[j].x - accU[j][0], cnv0[j].y - accU[j][1]);
+      *reinterpret_cast<uint32_t*>(Ub + (r0 + g + 8) * LDS + ch + j * 8 + 2 * t) = pack_bf162(cnv1[j].x - accU[j][2], cnv1[j].y - accU[j][3]);
+    }
+    __syncthreads();          // U visible; every warp is done reading the S copy
+    // ---- O += ica U (ica is lower triangular: k <= row) -----------------------------------------
+    for (int k0 = 0; k0 < r0 + 16; k0 += 16) {
+      uint32_t ai[4], b[4];
+      ldsm_x4(ic_u + 2 * ((r0 + a_row) * LDL + k0 + a_col), ai);
+      ldsm_x4_t(ub_u + 2 * ((k0 + b_row) * LDS + ch + b_col), b);
+      mma_bf16(accO[0], ai, b[0], b[1]);
+      mma_bf16(accO[1], ai, b[2], b[3]);
+    }
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      const int64_t ta = (int64_t)n * L + r0 + g, tb = ta + 8;
+      float* op = a.out + (int64_t)h * DV + col0 + ch + j * 8 + 2 * t;
+      if (ta < a.T) *reinterpret_cast<float2*>(op + ta * a.nv * DV) = make_float2(accO[j][0], accO[j][1]);
+      if (tb < a.T) *reinterpret_cast<float2*>(op + tb * a.nv * DV) = make_float2(accO[j][2], accO[j][3]);
+    }
+    // ---- S <- ecl S + ke^T U on the warp's own tile; refresh the bf16 copy -----------------------
+#pragma unroll
+    for (int j = 0; j < NTS; ++j) { accS[j][0] *= cel; accS[j][1] *= cel; accS[j][2] *= cel; accS[j][3] *= cel; }
+#pragma unroll
+    for (int k0 = 0; k0 < L; k0 += 16) {
+      uint32_t at[4];
+      ldsm_x4_t(a3_u + 2 * ((k0 + t_row) * LDA + s0 + t_col), at);
+#pragma unroll
+      for (int jj = 0; jj < NTS; jj += 2) {
+        uint32_t b[4];
+        ldsm_x4_t(ub_u + 2 * ((k0 + b_row) * LDS + sc0 + jj * 8 + b_col), b);
+        mma_bf16(accS[jj], at, b[0], b[1]);
+        mma_bf16(accS[jj + 1], at, b[2], b[3]);
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < NTS; ++j) {
+      *reinterpret_cast<uint32_t*>(Sb + (s0 + g) * LDS + sc0 + j * 8 + 2 * t) = pack_bf162(accS[j][0], accS[j][1]);
+      *reinterpret_cast<uint32_t*>(Sb + (s0 + g + 8) * LDS + sc0 + j * 8 + 2 * t) = pack_bf162(accS[j][2], accS[j][3]);
+    }
+  }
+  asm volatile("cp.async.wait_all;" ::: "memory");
+#pragma unroll
+  for (int j = 0; j < NTS; ++j) {
+    *reinterpret_cast<float2*>(sp + (int64_t)(s0 + g) * DV + sc0 + j * 8 + 2 * t) = make_float2(accS[j][0], accS[j][1]);
+    *reinterpret_cast<float2*>(sp + (int64_t)(s0 + g + 8) * DV + sc0 + j * 8 + 2 * t) = make_float2(accS[j][2], accS[j][3]);
+  }
+}
+
 // out[t, h*DV + j] = bf16( o * rsqrt(mean_j o^2 + eps) * w[j] * silu(z) ), one warp per (t, h)
 template <int DV>
 __global__ void gdn_gated_norm_kernel(const float* o, const bf16* z, int64_t ldz, const float* w, bf16* out,
@@ -936,17 +1129,29 @@ __global__ void gdn_gated_norm_kernel(const float* o, const bf16* z, int64_t ldz
   if (task >= (int64_t)T * nv) return;
   const int64_t t = task / nv;
   const int h = task % nv;
-  constexpr int E = DV / 32;
+  constexpr int E = DV / 32;                 // consecutive elements per lane (2 or 4): vector loads and stores
+  static_assert(E == 2 || E == 4, "head width");
+  const int j0 = lane * E;
   float x[E], ss = 0.f;
+  const float* op = o + (t * nv + h) * DV + j0;
+  if (E == 4) { const float4 v = *reinterpret_cast<const float4*>(op); x[0] = v.x; x[1] = v.y; x[E - 2] = v.z; x[E - 1] = v.w; }
+  else { const float2 v = *reinterpret_cast<const float2*>(op); x[0] = v.x; x[1] = v.y; }
 #pragma unroll
-  for (int e = 0; e < E; ++e) { x[e] = o[(t * nv + h) * DV + lane + 32 * e]; ss += x[e] * x[e]; }
+  for (int e = 0; e < E; ++e) ss += x[e] * x[e];
   const float r = rsqrtf(warp_sum(ss) / (float)DV + eps);
+  uint32_t zz[E / 2], oo[E / 2];
+  const bf16* zp = z + t * ldz + h * DV + j0;
+  if (E == 4) { const uint2 v = *reinterpret_cast<const uint2*>(zp); zz[0] = v.x; zz[E / 2 - 1] = v.y; }
+  else zz[0] = *reinterpret_cast<const uint32_t*>(zp);
 #pragma unroll
-  for (int e = 0; e < E; ++e) {
-    const int jj = lane + 32 * e;
-    const float zz = __bfloat162float(z[t * ldz + h * DV + jj]);
-    out[t * ldo + h * DV + jj] = __float2bfloat16(x[e] * r * w[jj] * (gate_sigmoid ? sigmoid_f(zz) : silu_f(zz)));
+  for (int e = 0; e < E; e += 2) {
+    const float z0 = __uint_as_float(zz[e / 2] << 16), z1 = __uint_as_float(zz[e / 2] & 0xffff0000u);
+    const float g0 = gate_sigmoid ? sigmoid_f(z0) : silu_f(z0), g1 = gate_sigmoid ? sigmoid_f(z1) : silu_f(z1);
+    oo[e / 2] = pack_bf162(x[e] * r * w[j0 + e] * g0, x[e + 1] * r * w[j0 + e + 1] * g1);
   }
+  bf16* dp = out + t * ldo + h * DV + j0;
+  if (E == 4) *reinterpret_cast<uint2*>(dp) = make_uint2(oo[0], oo[E / 2 - 1]);
+  else *reinterpret_cast<uint32_t*>(dp) = oo[0];
 }
 
 template <int DK, int DV>
@@ -958,7 +1163,7 @@ size_t chunk_scan_smem() {
   return sizeof(float) * (size_t)(DK * (DVS + 4) + 2 * kChunk * (DK + 4) + kChunk * (kChunk + 4) + kChunk * (DVS + 4));
 }
 
-int g_gdn_tc = 1;    // chunk kernels on the tensor cores (TF32); 0 selects the fp32 SIMT versions
+int g_gdn_tc = 2;    // chunk kernels: 2 = TF32 prepare + bf16-operand scan, 1 = TF32 for both, 0 = fp32 SIMT versions
 
 template <typename K>
 int set_smem(K kern, size_t smem) {
@@ -993,8 +1198,9 @@ CB_EXPORT int cb_gdn_decode(const void* proj, int64_t ldp, const void* conv_w, c
   return CB_ERR_SHAPE;
 }
 
-// 1: tensor-core (TF32) chunk kernels for prefill (default); 0: the fp32 SIMT versions.
-CB_EXPORT int cb_set_gdn_tc(int64_t on) { g_gdn_tc = on ? 1 : 0; return 0; }
+// 2: TF32 prepare + bf16-operand scan with a three-stage operand ring (default); 1: TF32 chunk kernels;
+// 0: the fp32 SIMT versions.
+CB_EXPORT int cb_set_gdn_tc(int64_t mode) { g_gdn_tc = mode < 0 ? 0 : (mode > 2 ? 2 : (int)mode); return 0; }
 
 CB_EXPORT int cb_gdn_commit(void* state, const void* record, const void* slots, const void* steps,
                             int64_t rec_w, int64_t M, int64_t nv, int64_t dk, int64_t dv, void* stream) {
@@ -1053,7 +1259,17 @@ CB_EXPORT int cb_gdn_prefill(const void* proj, int64_t ldp, const void* conv_w, 
     e = cb_launch(gdn_ring_update_kernel, dim3((unsigned)(T < kRing ? T : kRing)), dim3(256), 0, st,     \
                   (const bf16*)proj, ldp, (bf16*)ring_seq, (int)T, (int)pos0, conv_dim);                 \
     if (e != cudaSuccess) return (int)e;                                                                 \
-    if (g_gdn_tc) {                                                                                      \
+    if (g_gdn_tc == 2) {                                                                                 \
+      size_t s1 = sizeof(float) * PrepTcLayout<DK_, DV_>::floats;                                        \
+      if ((rc = set_smem(gdn_chunk_prepare_tc_kernel<DK_, DV_, true>, s1))) return rc;                   \
+      e = cb_launch(gdn_chunk_prepare_tc_kernel<DK_, DV_, true>, dim3((unsigned)nc, (unsigned)nv), dim3(256), s1, st, ca); \
+      if (e != cudaSuccess) return (int)e;                                                               \
+      size_t s2 = ScanBfLayout<DK_, DVS_>::bytes;                                                        \
+      if ((rc = set_smem(gdn_chunk_scan_bf_kernel<DK_, DV_, DVS_>, s2))) return rc;                      \
+      e = cb_launch(gdn_chunk_scan_bf_kernel<DK_, DV_, DVS_>, dim3((unsigned)nv, (unsigned)(DV_ / DVS_)), \
+                    dim3(256), s2, st, sa);                                                              \
+      if (e != cudaSuccess) return (int)e;                                                               \
+    } else if (g_gdn_tc) {                                                                               \
       size_t s1 = sizeof(float) * PrepTcLayout<DK_, DV_>::floats;                                        \
       if ((rc = set_smem(gdn_chunk_prepare_tc_kernel<DK_, DV_>, s1))) return rc;                         \
       e = cb_launch(gdn_chunk_prepare_tc_kernel<DK_, DV_>, dim3((unsigned)nc, (unsigned)nv), dim3(256), s1, st, ca); \

@@ -207,9 +207,20 @@ def test_gdn_decode_steps_and_verify(nk, nv, dk, dv):
     assert st[0].abs().sum() == 0
 
 
-@pytest.mark.parametrize("nk,nv,dk,dv,T1,T2", [(2, 4, 64, 64, 150, 37), (2, 4, 128, 128, 64, 70), (1, 2, 128, 128, 5, 3)])
-def test_gdn_prefill_chunked(nk, nv, dk, dv, T1, T2):
+@pytest.mark.parametrize("mode", [2, 1])
+@pytest.mark.parametrize("nk,nv,dk,dv,T1,T2", [(2, 4, 64, 64, 150, 37), (2, 4, 128, 128, 64, 70), (1, 2, 128, 128, 5, 3),
+                                               (2, 4, 128, 128, 700, 333)])
+def test_gdn_prefill_chunked(nk, nv, dk, dv, T1, T2, mode):
+    """mode 2: TF32 prepare + bf16-operand scan (three-stage operand ring); mode 1: TF32 for both."""
     k = K()
+    k.call("set_gdn_tc", mode)
+    try:
+        _gdn_prefill_case(k, nk, nv, dk, dv, T1, T2, mode)
+    finally:
+        k.call("set_gdn_tc", 2)
+
+
+def _gdn_prefill_case(k, nk, nv, dk, dv, T1, T2, mode):
     T = T1 + T2
     proj, conv_w, A_log, dt_bias, norm_w, conv_dim = _gdn_inputs(T, nk, nv, dk, dv, 30)
     conv_state, state = torch.zeros(conv_dim, 3), torch.zeros(nv, dk, dv)
@@ -224,7 +235,8 @@ def test_gdn_prefill_chunked(nk, nv, dk, dv, T1, T2):
     k.gdn_prefill(pj[:T1], *args, out[:T1], pos0=0, nk=nk, nv=nv, dk=dk, dv=dv, eps=1e-6)
     k.gdn_prefill(pj[T1:], *args, out[T1:], pos0=T1, nk=nk, nv=nv, dk=dk, dv=dv, eps=1e-6)
     close(out, ref, 3e-2)
-    close(st, state, 4e-3)      # the chunk products run as TF32 (10-bit mantissa) on the tensor cores
+    # the chunk products run as TF32 (10-bit mantissa) or, in the scan of mode 2, with bf16 operands
+    close(st, state, 4e-3 if mode == 1 else 2e-2)
     # a decode step after the chunked prefill continues from the ring + state
     extra = bf(1, proj.shape[1], seed=31)
     ref2 = _gdn_oracle(extra, conv_w, A_log, dt_bias, norm_w, nk, nv, dk, dv, conv_state, state)
