@@ -117,6 +117,66 @@ __global__ void rmsnorm_kernel(const bf16* __restrict__ x, const bf16* __restric
   }
 }
 
+// The same normalisation for many rows (a prefill chunk): one warp per row, the row held in registers
+// as packed bf16 (CPL 16-byte chunks per lane), no shared memory and no block barrier.  Reads x (+ add),
+// writes res_out (optional) and out.  Values and rounding as in rmsnorm_kernel.
+template <int CPL>
+__global__ void __launch_bounds__(256) rmsnorm_rows_kernel(const bf16* __restrict__ x, const bf16* __restrict__ add,
+                                                           const float* __restrict__ gain, bf16* __restrict__ res_out,
+                                                           bf16* __restrict__ out, int64_t M, int64_t N, int64_t ldx,
+                                                           int64_t ldo, float eps) {
+  griddep_launch();
+  griddep_wait();
+  const int lane = threadIdx.x & 31;
+  const int64_t r = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (r >= M) return;
+  const int nchunk = (int)(N >> 3);
+  uint4 v[CPL];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < CPL; ++i) {
+    const int c = lane + 32 * i;
+    if (c < nchunk) v[i] = *reinterpret_cast<const uint4*>(x + r * ldx + c * 8);
+  }
+  if (add) {
+#pragma unroll
+    for (int i = 0; i < CPL; ++i) {
+      const int c = lane + 32 * i;
+      if (c < nchunk) {
+        float f[8], g[8];
+        bf16x8_to_float(v[i], f);
+        bf16x8_to_float(*reinterpret_cast<const uint4*>(add + r * ldx + c * 8), g);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) f[e] += g[e];
+        v[i] = float_to_bf16x8(f);
+        if (res_out) *reinterpret_cast<uint4*>(res_out + r * ldx + c * 8) = v[i];
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < CPL; ++i) {
+    if (lane + 32 * i < nchunk) {
+      float f[8];
+      bf16x8_to_float(v[i], f);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) ss += f[e] * f[e];
+    }
+  }
+  const float rstd = rsqrtf(warp_sum(ss) / (float)N + eps);
+#pragma unroll
+  for (int i = 0; i < CPL; ++i) {
+    const int c = lane + 32 * i;
+    if (c < nchunk) {
+      float f[8];
+      bf16x8_to_float(v[i], f);
+      const float4 g0 = *reinterpret_cast<const float4*>(gain + c * 8), g1 = *reinterpret_cast<const float4*>(gain + c * 8 + 4);
+      f[0] *= rstd * g0.x; f[1] *= rstd * g0.y; f[2] *= rstd * g0.z; f[3] *= rstd * g0.w;
+      f[4] *= rstd * g1.x; f[5] *= rstd * g1.y; f[6] *= rstd * g1.z; f[7] *= rstd * g1.w;
+      *reinterpret_cast<uint4*>(out + r * ldo + c * 8) = float_to_bf16x8(f);
+    }
+  }
+}
+
 // out[m, i] = silu(gu[m, i]) * gu[m, I + i]
 __global__ void swiglu_kernel(const bf16* __restrict__ gu, bf16* __restrict__ out, int64_t I,
                               int64_t ldg, int64_t ldo, int64_t total_chunks) {
@@ -349,6 +409,17 @@ CB_EXPORT int cb_rmsnorm_q(const void* x, const void* add, const void* gain, voi
   if (N % 8 || N * 4 > 200 * 1024) return CB_ERR_SHAPE;
   if ((q == nullptr) != (qscale == nullptr) || (!out && !q)) return CB_ERR_ARG;
   if (M == 0) return 0;
+  if (M >= 256 && !q && out && ldx % 8 == 0 && ldo % 8 == 0 && ((uintptr_t)gain & 15) == 0) {   // a prefill chunk: one warp per row
+    const dim3 grid((unsigned)((M + 7) / 8));
+#define CB_RMS_ROWS(CPL_)                                                                                      \
+  return (int)cb_launch(rmsnorm_rows_kernel<CPL_>, grid, dim3(256), 0, (cudaStream_t)stream, (const bf16*)x,   \
+                        (const bf16*)add, (const float*)gain, (bf16*)res_out, (bf16*)out, M, N, ldx, ldo, eps)
+    if (N <= 8 * 32 * 4) CB_RMS_ROWS(4);
+    if (N <= 8 * 32 * 8) CB_RMS_ROWS(8);
+    if (N <= 8 * 32 * 12) CB_RMS_ROWS(12);
+    if (N <= 8 * 32 * 20) CB_RMS_ROWS(20);
+#undef CB_RMS_ROWS
+  }
   const size_t smem = (size_t)N * 4;
   if (smem + 2048 > 48 * 1024) {   // the 48 KB default also has to hold the static shared memory
     cudaError_t e = cudaFuncSetAttribute(rmsnorm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);

@@ -357,7 +357,7 @@ int cb_gemm_pair_run(const void* A, int64_t lda, const void* W, int64_t ldw, voi
 
 // C[M,N] (bf16) = A[M,K] (bf16) x W[N,K]^T (bf16) (+ residual[M,N]).  K % 8 == 0, N % 8 == 0.
 // bn_hint: 0 = choose (CTA pairs for more than 256 rows), 64/128/160/256 = one-CTA kernel with that tile
-// width, 1256/1320 = CTA-pair kernel with a 256 x 256 / 256 x 320 tile.
+// width, 1256/1288/1320 = CTA-pair kernel with a 256 x 256 / 256 x 288 / 256 x 320 tile.
 CB_EXPORT int cb_gemm_bf16(const void* A, int64_t lda, const void* W, int64_t ldw, void* C, int64_t ldc,
                            const void* residual, int64_t ldr, int64_t M, int64_t N, int64_t K,
                            int64_t bn_hint, const void* pf, int64_t pf_seq, void* status, void* stream) {

@@ -5,8 +5,8 @@
 // even CTA issues the MMAs and the tensor cores of both SMs read both halves.  Per k-block a CTA
 // therefore moves 16 KB + TILE_N/2 x 128 B into shared memory for 128 x TILE_N x 64 multiply-adds -
 // half the weight traffic of the one-CTA kernel, whose narrow tiles were paced by the L2 -> shared
-// memory loads, not by the tensor pipe.  TILE_N is one MMA of N = 256 or two MMAs of N = 160 that share
-// the A tile (a 256 x 320 tile gives N = 2560 eight n-tiles: 64 tiles for 74 pairs, one round).
+// memory loads, not by the tensor pipe.  TILE_N is one MMA of N = 256 or two MMAs of N = 144 / 160 that share
+// the A tile (256 x 288 tiles cut a 2048 x 2560 product into 72 tiles for the 74 SM pairs: one round).
 //
 // Roles per CTA (192 threads): warp 0 TMA producer (plain single-destination loads into its own
 // shared memory; the completion bytes of both CTAs are counted on the even CTA's barrier), warp 1
@@ -302,18 +302,21 @@ int cb_gemm_pair_plan(int64_t M, int64_t N) {
   if (!g_pair_enabled || M <= 256 || N < 256) return 0;
   const int pairs = pair_sm_count() / 2;
   const int64_t mt = (M + 255) / 256;
-  const int cand[2] = {256, 320};
+  const int cand[3] = {256, 288, 320};
   int best = 0;
   int64_t bc = INT64_MAX;
-  for (int i = 0; i < 2; ++i) {
+  for (int i = 0; i < 3; ++i) {
     const int64_t tiles = mt * ((N + cand[i] - 1) / cand[i]);
-    const int64_t cost = ((tiles + pairs - 1) / pairs) * cand[i];
+    const int64_t rounds = (tiles + pairs - 1) / pairs;
+    // tiles wider than 256 columns have one accumulator: from the second round on their epilogue is not
+    // hidden behind the next tile's products (measured: +25 % on a six-round product)
+    const int64_t cost = rounds * cand[i] * (cand[i] > 256 && rounds > 1 ? 5 : 4);
     if (cost < bc) { bc = cost; best = cand[i]; }
   }
   return best;
 }
 
-// tile: 256 or 320 (0 = choose).  row_scale / col_scale given: int8 operands (contract of cb_gemm_i8), else
+// tile: 256, 288 or 320 (0 = choose).  row_scale / col_scale given: int8 operands (contract of cb_gemm_i8), else
 // bf16 (contract of cb_gemm_bf16).
 int cb_gemm_pair_run(const void* A, int64_t lda, const void* W, int64_t ldw, void* C, int64_t ldc, const void* residual,
                      int64_t ldr, const void* row_scale, const void* col_scale, int64_t M, int64_t N, int64_t K, int tile,
@@ -328,10 +331,12 @@ int cb_gemm_pair_run(const void* A, int64_t lda, const void* W, int64_t ldw, voi
   if (!tile) tile = cb_gemm_pair_plan(M, N);
   if (row_scale) {
     if (tile == 256) return launch_pair<256, 1, 6, true>(A, lda, W, ldw, a, st);
+    if (tile == 288) return launch_pair<144, 2, 6, true>(A, lda, W, ldw, a, st);
     if (tile == 320) return launch_pair<160, 2, 6, true>(A, lda, W, ldw, a, st);
     return CB_ERR_ARG;
   }
   if (tile == 256) return launch_pair<256, 1, 6, false>(A, lda, W, ldw, a, st);
+  if (tile == 288) return launch_pair<144, 2, 6, false>(A, lda, W, ldw, a, st);
   if (tile == 320) return launch_pair<160, 2, 6, false>(A, lda, W, ldw, a, st);
   return CB_ERR_ARG;
 }

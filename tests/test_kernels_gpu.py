@@ -29,6 +29,23 @@ def bf(*shape, s=1.0, seed=0):
     return (torch.randn(*shape, generator=g) * s).to(torch.bfloat16)
 
 
+@pytest.mark.parametrize("M,N", [(300, 520), (257, 2560), (1000, 5120), (256, 1000), (2048, 3072)])
+def test_rmsnorm_many_rows(M, N):
+    """Prefill-sized calls run one warp per row with the row in registers (chunks per lane 4 / 8 / 12 / 20)."""
+    k = K()
+    x, add = bf(M, N, seed=5), bf(M, N, seed=6)
+    gain = (1 + 0.1 * torch.randn(N)).float()
+    canary = torch.full((M + 1, N), 3.0, dtype=torch.bfloat16, device=DEV)
+    out = k.rmsnorm(x.to(DEV), gain.to(DEV), 1e-6, out=canary[:M])
+    close(out, O.rms_norm(x, gain))
+    assert bool((canary[M] == 3.0).all())
+    res = x.to(DEV)
+    out = k.rmsnorm(res, gain.to(DEV), 1e-6, add=add.to(DEV), res_out=res)      # in place, as the model does
+    s, n = O.add_rms_norm(x, add, gain)
+    close(res, s)
+    close(out, n)
+
+
 def test_rowwise_kernels():
     k = K()
     x, add = bf(5, 520, seed=1), bf(5, 520, seed=2)
@@ -98,7 +115,7 @@ def test_gemv_fused_norm_swiglu(M, H, I):
                                        (64, 64, 256, 64), (1000, 1536, 512, 256), (130, 136, 72, 128),
                                        (300, 520, 1032, 160), (2048, 2560, 1024, 0), (2048, 2560, 1024, 160),
                                        # CTA pairs (256-row tiles, 256 / 320 columns), edge tiles in both directions
-                                       (300, 520, 1032, 1256), (300, 520, 1032, 1320), (257, 264, 72, 1320),
+                                       (300, 520, 1032, 1256), (300, 520, 1032, 1320), (257, 264, 72, 1320), (300, 520, 1032, 1288), (2048, 2560, 512, 1288),
                                        (1000, 1536, 512, 1256), (2048, 2560, 4096, 1320), (2100, 1288, 2560, 1256),
                                        # at most 128 rows: K split over CTAs, partial tiles reduced by the last slice
                                        (64, 2560, 4096, 0), (16, 12352, 2560, 0), (128, 520, 9216, 0), (5, 264, 520, 0)])
@@ -133,7 +150,7 @@ def test_gemm_swiglu_epilogue(M, I, Kd):
 @pytest.mark.parametrize("M,N,Kd,bn", [(128, 256, 128, 256), (200, 264, 400, 128), (77, 520, 1040, 0),
                                        (300, 488, 528, 160), (64, 2560, 4096, 0), (16, 520, 9216, 0),
                                        # CTA pairs
-                                       (300, 488, 528, 1256), (300, 488, 528, 1320), (1000, 1536, 512, 0),
+                                       (300, 488, 528, 1256), (300, 488, 528, 1320), (300, 488, 528, 1288), (1000, 1536, 512, 0),
                                        (2048, 2560, 4096, 1320)])
 def test_gemm_i8_tcgen05(M, N, Kd, bn):
     k = K()
