@@ -304,6 +304,10 @@ struct GdnChunkArgs {
   float* ke;    // [nv, nc, 64, DK]
   float* ecl;   // [nv, nc]
   int Tp, nc, rep;
+  // fused form (the prepare kernel takes conv + SiLU, the q/k normalisation, beta and g from the raw
+  // projection rows itself; qn / kn / v / beta / g above are then unused)
+  const bf16* proj; int64_t ldp; const float* conv_w; const float* A_log; const float* dt_bias; const bf16* ring;
+  int T, pos0, nk, nv;
 };
 
 template <int DK, int DV>
@@ -608,9 +612,48 @@ __device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
 
+// Causal 4-tap conv + SiLU of NT consecutive tokens (first token t_first of the chunk whose rows are proj,
+// earlier rows come from the ring) for the four channels c..c+3 of this lane.  All NT + 3 rows are
+// requested before anything is computed.  val[k][j]: token t_first + k, channel c + j; rows past T give 0.
+template <int NT>
+__device__ __forceinline__ void conv_tokens(const bf16* proj, int64_t ldp, const bf16* ring, int conv_dim, const float* conv_w,
+                                            int c, bool act, int t_first, int T, int pos0, float (*val)[4]) {
+  float w[4][4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float4 wj = act ? *reinterpret_cast<const float4*>(conv_w + (int64_t)(c + j) * 4) : make_float4(0.f, 0.f, 0.f, 0.f);
+    w[j][0] = wj.x; w[j][1] = wj.y; w[j][2] = wj.z; w[j][3] = wj.w;
+  }
+  uint2 raw[NT + 3];
+#pragma unroll
+  for (int r = 0; r < NT + 3; ++r) {
+    const int tt = t_first - 3 + r, pp = pos0 + tt;
+    raw[r] = make_uint2(0u, 0u);
+    if (act) {
+      if (tt >= 0) { if (tt < T) raw[r] = *reinterpret_cast<const uint2*>(proj + (int64_t)tt * ldp + c); }
+      else if (pp >= 0) raw[r] = *reinterpret_cast<const uint2*>(ring + (int64_t)(pp & (kRing - 1)) * conv_dim + c);
+    }
+  }
+#pragma unroll
+  for (int k = 0; k < NT; ++k) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float x[4];
+#pragma unroll
+      for (int tap = 0; tap < 4; ++tap) {
+        const uint32_t word = (j < 2) ? raw[k + tap].x : raw[k + tap].y;
+        x[tap] = (j & 1) ? __uint_as_float(word & 0xffff0000u) : __uint_as_float(word << 16);
+      }
+      val[k][j] = (act && t_first + k < T) ? silu_f(w[j][0] * x[0] + w[j][1] * x[1] + w[j][2] * x[2] + w[j][3] * x[3]) : 0.f;
+    }
+  }
+}
+
+// FUSE: the q / k / v rows, beta and g are computed here from the raw projection rows (what gdn_prep_kernel
+// does as a launch of its own, with an fp32 round trip through memory).
 // BF: kcd, qe, ke and ica leave as bf16 (same element offsets in the same regions) for the bf16 scan below;
 // the triangular system itself is still solved from TF32 products in fp32.
-template <int DK, int DV, bool BF = false>
+template <int DK, int DV, bool BF = false, bool FUSE = false>
 __global__ void __launch_bounds__(256, 2) gdn_chunk_prepare_tc_kernel(const GdnChunkArgs a) {
   using Lay = PrepTcLayout<DK, DV>;
   constexpr int L = kChunk, LDA = Lay::LDA, LDB = Lay::LDB, LDV = Lay::LDV, LDL = Lay::LDL;
@@ -633,13 +676,45 @@ __global__ void __launch_bounds__(256, 2) gdn_chunk_prepare_tc_kernel(const GdnC
   const float* kp = a.kn + ((int64_t)kh * a.Tp + t0) * DK;
   const float* qp = a.qn + ((int64_t)kh * a.Tp + t0) * DK;
   const float* vp = a.v + ((int64_t)h * a.Tp + t0) * DV;
-  for (int idx = tid; idx < L * DK / 4; idx += 256) {
-    const int i = idx / (DK / 4), c = (idx % (DK / 4)) * 4;
-    *reinterpret_cast<float4*>(Ks + i * LDA + c) = *reinterpret_cast<const float4*>(kp + (int64_t)i * DK + c);
-    *reinterpret_cast<float4*>(Qs + i * LDA + c) = *reinterpret_cast<const float4*>(qp + (int64_t)i * DK + c);
+  const int kdim = a.nk * DK, conv_dim = 2 * kdim + a.nv * DV;
+  if (FUSE) {
+    // warp w: tokens 8w .. 8w+7 of the chunk, a lane owns four adjacent channels of the key head
+    const int i0 = lane * 4;
+    const bool act = i0 < DK;
+    const int tf = (int)t0 + warp * 8;
+#pragma unroll
+    for (int kind = 0; kind < 2; ++kind) {              // 0: q, 1: k
+      float val[8][4];
+      conv_tokens<8>(a.proj, a.ldp, a.ring, conv_dim, a.conv_w, kind * kdim + kh * DK + i0, act, tf, a.T, a.pos0, val);
+      float* dstm = kind ? Ks : Qs;
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        const float ss = warp_sum(val[k][0] * val[k][0] + val[k][1] * val[k][1] + val[k][2] * val[k][2] + val[k][3] * val[k][3]);
+        const float sc = rsqrtf(ss + 1e-6f) * (kind == 0 ? rsqrtf((float)DK) : 1.f);
+        if (act) *reinterpret_cast<float4*>(dstm + (warp * 8 + k) * LDA + i0) = make_float4(val[k][0] * sc, val[k][1] * sc, val[k][2] * sc, val[k][3] * sc);
+      }
+    }
+  } else {
+    for (int idx = tid; idx < L * DK / 4; idx += 256) {
+      const int i = idx / (DK / 4), c = (idx % (DK / 4)) * 4;
+      *reinterpret_cast<float4*>(Ks + i * LDA + c) = *reinterpret_cast<const float4*>(kp + (int64_t)i * DK + c);
+      *reinterpret_cast<float4*>(Qs + i * LDA + c) = *reinterpret_cast<const float4*>(qp + (int64_t)i * DK + c);
+    }
   }
   if (tid < 32) {  // inclusive scan of g over the 64 rows
-    const float g0 = a.g[(int64_t)h * a.Tp + t0 + tid], g1 = a.g[(int64_t)h * a.Tp + t0 + 32 + tid];
+    float g0, g1, be0, be1;
+    if (FUSE) {
+      const float al = -__expf(a.A_log[h]), db = a.dt_bias[h];
+      const int64_t ta = t0 + tid, tb = ta + 32;
+      const bf16* pa = a.proj + ta * a.ldp + conv_dim + a.nv * DV;
+      const bf16* pb = a.proj + tb * a.ldp + conv_dim + a.nv * DV;
+      g0 = g1 = be0 = be1 = 0.f;
+      if (ta < a.T) { be0 = sigmoid_f(__bfloat162float(pa[h])); g0 = al * softplus_f(__bfloat162float(pa[a.nv + h]) + db); }
+      if (tb < a.T) { be1 = sigmoid_f(__bfloat162float(pb[h])); g1 = al * softplus_f(__bfloat162float(pb[a.nv + h]) + db); }
+    } else {
+      g0 = a.g[(int64_t)h * a.Tp + t0 + tid]; g1 = a.g[(int64_t)h * a.Tp + t0 + 32 + tid];
+      be0 = a.beta[(int64_t)h * a.Tp + t0 + tid]; be1 = a.beta[(int64_t)h * a.Tp + t0 + 32 + tid];
+    }
     float x0 = g0, x1 = g1;
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
@@ -649,8 +724,8 @@ __global__ void __launch_bounds__(256, 2) gdn_chunk_prepare_tc_kernel(const GdnC
     const float tot0 = __shfl_sync(0xffffffffu, x0, 31);
     cs[tid] = x0;
     cs[32 + tid] = x1 + tot0;
-    bs[tid] = a.beta[(int64_t)h * a.Tp + t0 + tid];
-    bs[32 + tid] = a.beta[(int64_t)h * a.Tp + t0 + 32 + tid];
+    bs[tid] = be0;
+    bs[32 + tid] = be1;
   }
   __syncthreads();
   // ---- K K^T and Q K^T: warp (row tile of 16) x (column half of 32) ----------------------------
@@ -753,12 +828,26 @@ __global__ void __launch_bounds__(256, 2) gdn_chunk_prepare_tc_kernel(const GdnC
     const int r0 = (warp & 3) * 16;
     const bool isv = (warp >> 2) == 0;
     if (isv) {                                       // the four V warps fetch V while the K warps multiply
-      for (int idx = tid; idx < L * DV / 4; idx += 128) {
-        const int i = idx / (DV / 4), c = (idx % (DV / 4)) * 4;
-        cp_async16(Vs + i * LDV + c, vp + (int64_t)i * DV + c);
+      if (FUSE) {                                    // conv + SiLU of the value channels: 16 tokens per warp, 8 at a time
+        const int i0 = lane * 4;
+        const bool act = i0 < DV;
+#pragma unroll 1
+        for (int half = 0; half < 2; ++half) {
+          const int tl = warp * 16 + half * 8;
+          float val[8][4];
+          conv_tokens<8>(a.proj, a.ldp, a.ring, conv_dim, a.conv_w, 2 * kdim + h * DV + i0, act, (int)t0 + tl, a.T, a.pos0, val);
+#pragma unroll
+          for (int k = 0; k < 8; ++k)
+            if (act) *reinterpret_cast<float4*>(Vs + (tl + k) * LDV + i0) = make_float4(val[k][0], val[k][1], val[k][2], val[k][3]);
+        }
+      } else {
+        for (int idx = tid; idx < L * DV / 4; idx += 128) {
+          const int i = idx / (DV / 4), c = (idx % (DV / 4)) * 4;
+          cp_async16(Vs + i * LDV + c, vp + (int64_t)i * DV + c);
+        }
+        cp_async_commit();
+        cp_async_wait_all();
       }
-      cp_async_commit();
-      cp_async_wait_all();
       asm volatile("bar.sync 1, 128;" ::: "memory");
     }
     const float* B = isv ? Vs : Kb;
@@ -1163,7 +1252,8 @@ size_t chunk_scan_smem() {
   return sizeof(float) * (size_t)(DK * (DVS + 4) + 2 * kChunk * (DK + 4) + kChunk * (kChunk + 4) + kChunk * (DVS + 4));
 }
 
-int g_gdn_tc = 2;    // chunk kernels: 2 = TF32 prepare + bf16-operand scan, 1 = TF32 for both, 0 = fp32 SIMT versions
+int g_gdn_tc = 3;    // chunk kernels: 3 = prep fused into the TF32 prepare + bf16-operand scan, 2 = the same with the
+                     // prep kernel as a launch of its own, 1 = TF32 for both, 0 = fp32 SIMT versions
 
 template <typename K>
 int set_smem(K kern, size_t smem) {
@@ -1198,9 +1288,9 @@ CB_EXPORT int cb_gdn_decode(const void* proj, int64_t ldp, const void* conv_w, c
   return CB_ERR_SHAPE;
 }
 
-// 2: TF32 prepare + bf16-operand scan with a three-stage operand ring (default); 1: TF32 chunk kernels;
-// 0: the fp32 SIMT versions.
-CB_EXPORT int cb_set_gdn_tc(int64_t mode) { g_gdn_tc = mode < 0 ? 0 : (mode > 2 ? 2 : (int)mode); return 0; }
+// 3: conv / norm / beta / g inside the TF32 prepare kernel + bf16-operand scan with a three-stage operand ring
+// (default); 2: the same with the prep kernel launched separately; 1: TF32 chunk kernels; 0: the fp32 SIMT versions.
+CB_EXPORT int cb_set_gdn_tc(int64_t mode) { g_gdn_tc = mode < 0 ? 0 : (mode > 3 ? 3 : (int)mode); return 0; }
 
 CB_EXPORT int cb_gdn_commit(void* state, const void* record, const void* slots, const void* steps,
                             int64_t rec_w, int64_t M, int64_t nv, int64_t dk, int64_t dv, void* stream) {
@@ -1248,21 +1338,31 @@ CB_EXPORT int cb_gdn_prefill(const void* proj, int64_t ldp, const void* conv_w, 
   float* o = p;
   GdnPrepArgs pa{(const bf16*)proj, ldp, (const float*)conv_w, (const float*)A_log, (const float*)dt_bias,
                  (const bf16*)ring_seq, qn, kn, v, beta, g, (int)T, (int)Tp, (int)pos0, (int)nk, (int)nv};
-  GdnChunkArgs ca{qn, kn, v, beta, g, nvv, kcd, ica, qe, ke, ecl, (int)Tp, (int)nc, (int)(nv / nk)};
+  GdnChunkArgs ca{qn, kn, v, beta, g, nvv, kcd, ica, qe, ke, ecl, (int)Tp, (int)nc, (int)(nv / nk),
+                  (const bf16*)proj, ldp, (const float*)conv_w, (const float*)A_log, (const float*)dt_bias,
+                  (const bf16*)ring_seq, (int)T, (int)pos0, (int)nk, (int)nv};
   GdnScanArgs sa{nvv, kcd, ica, qe, ke, ecl, (float*)state_seq, o, (int)T, (int)nc, (int)nv};
   cudaError_t e;
   int rc;
 #define GDN_PREFILL(DK_, DV_, DVS_)                                                                      \
   do {                                                                                                   \
-    e = cb_launch(gdn_prep_kernel<DK_, DV_>, dim3((unsigned)((Tp + kPrepTok - 1) / kPrepTok)), dim3(256), 0, st, pa);                  \
-    if (e != cudaSuccess) return (int)e;                                                                 \
-    e = cb_launch(gdn_ring_update_kernel, dim3((unsigned)(T < kRing ? T : kRing)), dim3(256), 0, st,     \
-                  (const bf16*)proj, ldp, (bf16*)ring_seq, (int)T, (int)pos0, conv_dim);                 \
-    if (e != cudaSuccess) return (int)e;                                                                 \
-    if (g_gdn_tc == 2) {                                                                                 \
+    if (g_gdn_tc != 3) {                                                                                 \
+      e = cb_launch(gdn_prep_kernel<DK_, DV_>, dim3((unsigned)((Tp + kPrepTok - 1) / kPrepTok)), dim3(256), 0, st, pa);                \
+      if (e != cudaSuccess) return (int)e;                                                               \
+    }                                                                                                    \
+    if (g_gdn_tc >= 2) {                                                                                 \
+      /* the fused prepare kernel reads the ring (rows before the chunk), so the ring moves on after it */ \
       size_t s1 = sizeof(float) * PrepTcLayout<DK_, DV_>::floats;                                        \
-      if ((rc = set_smem(gdn_chunk_prepare_tc_kernel<DK_, DV_, true>, s1))) return rc;                   \
-      e = cb_launch(gdn_chunk_prepare_tc_kernel<DK_, DV_, true>, dim3((unsigned)nc, (unsigned)nv), dim3(256), s1, st, ca); \
+      if (g_gdn_tc == 3) {                                                                               \
+        if ((rc = set_smem(gdn_chunk_prepare_tc_kernel<DK_, DV_, true, true>, s1))) return rc;           \
+        e = cb_launch(gdn_chunk_prepare_tc_kernel<DK_, DV_, true, true>, dim3((unsigned)nc, (unsigned)nv), dim3(256), s1, st, ca); \
+      } else {                                                                                           \
+        if ((rc = set_smem(gdn_chunk_prepare_tc_kernel<DK_, DV_, true>, s1))) return rc;                 \
+        e = cb_launch(gdn_chunk_prepare_tc_kernel<DK_, DV_, true>, dim3((unsigned)nc, (unsigned)nv), dim3(256), s1, st, ca); \
+      }                                                                                                  \
+      if (e != cudaSuccess) return (int)e;                                                               \
+      e = cb_launch(gdn_ring_update_kernel, dim3((unsigned)(T < kRing ? T : kRing)), dim3(256), 0, st,   \
+                    (const bf16*)proj, ldp, (bf16*)ring_seq, (int)T, (int)pos0, conv_dim);               \
       if (e != cudaSuccess) return (int)e;                                                               \
       size_t s2 = ScanBfLayout<DK_, DVS_>::bytes;                                                        \
       if ((rc = set_smem(gdn_chunk_scan_bf_kernel<DK_, DV_, DVS_>, s2))) return rc;                      \
@@ -1270,6 +1370,9 @@ CB_EXPORT int cb_gdn_prefill(const void* proj, int64_t ldp, const void* conv_w, 
                     dim3(256), s2, st, sa);                                                              \
       if (e != cudaSuccess) return (int)e;                                                               \
     } else if (g_gdn_tc) {                                                                               \
+      e = cb_launch(gdn_ring_update_kernel, dim3((unsigned)(T < kRing ? T : kRing)), dim3(256), 0, st,   \
+                    (const bf16*)proj, ldp, (bf16*)ring_seq, (int)T, (int)pos0, conv_dim);               \
+      if (e != cudaSuccess) return (int)e;                                                               \
       size_t s1 = sizeof(float) * PrepTcLayout<DK_, DV_>::floats;                                        \
       if ((rc = set_smem(gdn_chunk_prepare_tc_kernel<DK_, DV_>, s1))) return rc;                         \
       e = cb_launch(gdn_chunk_prepare_tc_kernel<DK_, DV_>, dim3((unsigned)nc, (unsigned)nv), dim3(256), s1, st, ca); \
@@ -1280,6 +1383,9 @@ CB_EXPORT int cb_gdn_prefill(const void* proj, int64_t ldp, const void* conv_w, 
                     dim3(256), s2, st, sa);                                                              \
       if (e != cudaSuccess) return (int)e;                                                               \
     } else {                                                                                             \
+      e = cb_launch(gdn_ring_update_kernel, dim3((unsigned)(T < kRing ? T : kRing)), dim3(256), 0, st,   \
+                    (const bf16*)proj, ldp, (bf16*)ring_seq, (int)T, (int)pos0, conv_dim);               \
+      if (e != cudaSuccess) return (int)e;                                                               \
       size_t s1 = chunk_prepare_smem<DK_, DV_>();                                                        \
       if ((rc = set_smem(gdn_chunk_prepare_kernel<DK_, DV_>, s1))) return rc;                            \
       e = cb_launch(gdn_chunk_prepare_kernel<DK_, DV_>, dim3((unsigned)nc, (unsigned)nv), dim3(256), s1, st, ca); \

@@ -224,17 +224,18 @@ def test_gdn_decode_steps_and_verify(nk, nv, dk, dv):
     assert st[0].abs().sum() == 0
 
 
-@pytest.mark.parametrize("mode", [2, 1])
+@pytest.mark.parametrize("mode", [3, 2, 1])
 @pytest.mark.parametrize("nk,nv,dk,dv,T1,T2", [(2, 4, 64, 64, 150, 37), (2, 4, 128, 128, 64, 70), (1, 2, 128, 128, 5, 3),
                                                (2, 4, 128, 128, 700, 333)])
 def test_gdn_prefill_chunked(nk, nv, dk, dv, T1, T2, mode):
-    """mode 2: TF32 prepare + bf16-operand scan (three-stage operand ring); mode 1: TF32 for both."""
+    """mode 3: prep fused into the TF32 prepare kernel + bf16-operand scan (three-stage operand ring); mode 2: the
+    same with the prep kernel as its own launch; mode 1: TF32 for both."""
     k = K()
     k.call("set_gdn_tc", mode)
     try:
         _gdn_prefill_case(k, nk, nv, dk, dv, T1, T2, mode)
     finally:
-        k.call("set_gdn_tc", 2)
+        k.call("set_gdn_tc", 3)
 
 
 def _gdn_prefill_case(k, nk, nv, dk, dv, T1, T2, mode):
