@@ -171,13 +171,29 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     for (int tile = pair; tile < total && !*abort_flag; tile += npairs, ++tcount) {
       const int m0 = (tile % a.m_tiles) * 256 + (int)rank * PM, n0 = (tile / a.m_tiles) * OUT_N;
       const uint32_t acc = tcount % ACC_BUFS, aph = (tcount / ACC_BUFS) & 1;
+      const int row = m0 + q * 32 + lane;
+      const bool rowok = row < a.M;
+      // The residual rows are requested while the tile is still being multiplied, RPF column chunks ahead of
+      // the accumulator reads: the latency of their 64-byte pieces would otherwise sit between two
+      // tcgen05.ld of a tile whose epilogue nothing hides (one round of 256 x 288 tiles).
+      constexpr int NCH = TILE_N / 32, RPF = 4;
+      const bf16* rbase = (!SWIGLU && a.residual && !a.pf && rowok) ? a.residual + (int64_t)row * a.ldr + n0 : nullptr;
+      uint4 rbuf[RPF][4];
+      auto fetch = [&](int ci, uint4* dst) {
+        if (rbase) {
+#pragma unroll
+          for (int v = 0; v < 4; ++v)
+            if (n0 + ci * 32 + v * 8 < a.N) dst[v] = *reinterpret_cast<const uint4*>(rbase + ci * 32 + v * 8);
+        }
+      };
+#pragma unroll
+      for (int ci = 0; ci < RPF && ci < NCH; ++ci) fetch(ci, rbuf[ci]);
       if (!wait_bar2(&acc_full[acc], aph, abort_flag)) {
         if (lane == 0) { atomicExch(a.status, 84); abort_s = 1; st_cluster_u32(peer_abort, 1); }
         break;
       }
       tc_fence_after();
-      const int row = m0 + q * 32 + lane;
-      const float rs = (I8 && row < a.M) ? a.row_scale[row] : 1.f;
+      const float rs = (I8 && rowok) ? a.row_scale[row] : 1.f;
       if (SWIGLU) {
 #pragma unroll 1
         for (int c0 = 0; c0 < OUT_N; c0 += 32) {
@@ -199,39 +215,41 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             }
           }
         }
-      } else
-#pragma unroll 1
-      for (int c0 = 0; c0 < TILE_N; c0 += 32) {
-        uint32_t r[32];
-        tmem_ld32(tmem_base + acc * TILE_N + ((uint32_t)(q * 32) << 16) + c0, r);
-        tmem_ld_wait();
-        const int col0 = n0 + c0;
-        if (row < a.M && col0 < a.N) {
-          bf16* cp;
-          if (a.pf) {
-            const int rpr = a.pf->rows_per_rank;
-            cp = a.pf->inbox[row / rpr] + ((int64_t)a.pf->rank * rpr + row % rpr) * a.pf->width + col0;
-          } else {
-            cp = a.C + (int64_t)row * a.ldc + col0;
-          }
-          const bf16* rp = (a.residual && !a.pf) ? a.residual + (int64_t)row * a.ldr + col0 : nullptr;
+      } else {
 #pragma unroll
-          for (int v = 0; v < 4; ++v) {
-            if (col0 + v * 8 >= a.N) break;  // N is a multiple of 8
-            float f[8];
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-              if (I8) f[i] = (float)(int)r[v * 8 + i] * rs * a.col_scale[col0 + v * 8 + i];
-              else f[i] = __uint_as_float(r[v * 8 + i]);
+        for (int ci = 0; ci < NCH; ++ci) {
+          const int c0 = ci * 32;
+          uint32_t r[32];
+          tmem_ld32(tmem_base + acc * TILE_N + ((uint32_t)(q * 32) << 16) + c0, r);
+          tmem_ld_wait();
+          const int col0 = n0 + c0;
+          if (rowok && col0 < a.N) {
+            bf16* cp;
+            if (a.pf) {
+              const int rpr = a.pf->rows_per_rank;
+              cp = a.pf->inbox[row / rpr] + ((int64_t)a.pf->rank * rpr + row % rpr) * a.pf->width + col0;
+            } else {
+              cp = a.C + (int64_t)row * a.ldc + col0;
             }
-            if (rp) {
-              float g[8];
-              bf16x8_to_float(*reinterpret_cast<const uint4*>(rp + v * 8), g);
 #pragma unroll
-              for (int i = 0; i < 8; ++i) f[i] += g[i];
+            for (int v = 0; v < 4; ++v) {
+              if (col0 + v * 8 >= a.N) break;  // N is a multiple of 8
+              float f[8];
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                if (I8) f[i] = (float)(int)r[v * 8 + i] * rs * a.col_scale[col0 + v * 8 + i];
+                else f[i] = __uint_as_float(r[v * 8 + i]);
+              }
+              if (rbase) {
+                float g[8];
+                bf16x8_to_float(rbuf[ci % RPF][v], g);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) f[i] += g[i];
+              }
+              *reinterpret_cast<uint4*>(cp + v * 8) = float_to_bf16x8(f);
             }
-            *reinterpret_cast<uint4*>(cp + v * 8) = float_to_bf16x8(f);
           }
+          if (ci + RPF < NCH) fetch(ci + RPF, rbuf[ci % RPF]);
         }
       }
       tc_fence_before();
