@@ -1,0 +1,335 @@
+// Grouped (expert-major) prefill GEMM straight from int4 weight codes on the tensor cores:
+//   C[r, :] = A[r, :] x dequant(Wq[expert(r)])^T     (optionally silu(gate) * up in the epilogue)
+// A bf16 [rows, K] sorted by expert; Wq [E, N, K/2] uint8 (two codes per byte, low nibble = even k),
+// scales [E, N, K/128] fp32: the layout the decode kernels stream, so a W4A8 checkpoint keeps ONE copy
+// of its expert stacks.  A routed-MoE prefill reads every expert's weights for ~64 rows each: with a
+// bf16 expansion of the stacks that is HBM-bound on 4x the bytes (and the expansion costs 4x the
+// memory); here the codes travel (TMA, 8 KB per k-block and tile) and are expanded inside the CTA.
+//
+// Roles (448 threads, one CTA per SM, persistent over the tile list of cb_moe_dispatch):
+//   warp 0     TMA producer: [128 x 64] bf16 A tile (128B swizzle) + [256 x 32 B] code tile per k-block
+//              into a ring of RS raw stages;
+//   warps 6-13 dequant: thread r owns weight row r of the tile, turns its 64 codes into a bf16 row of
+//              the K-major 128B-swizzled B tile (ring of BS stages): nibble -> 0x4300 | n (= 128 + n
+//              exactly in bf16), - 136, x scale; fence.proxy.async; arrive on b_ready;
+//   warp 1     MMA issuer: waits for the A tile (raw_full) and the expanded B tile (b_ready), issues
+//              tcgen05.mma (128 x 256 x 16, kind::f16) into one of two TMEM accumulators; tcgen05.commit
+//              frees the raw stage and the B stage;
+//   warps 2-5  epilogue: tcgen05.ld, optional SwiGLU, bf16 store.
+// Every wait is bounded (2 s) and reports through the status word.
+// Replaces the reference's W4A8 expert-major grouped path (models/qwen35/moe.py:561-730,
+// backends/corex/kernels/w8a8_tcu.cu:962).
+#include <cuda_bf16.h>
+
+#include "sm100.cuh"
+
+namespace {
+
+using namespace sm100;
+
+constexpr int WM = 128, WN = 256, WRS = 4, WBS = 3;
+constexpr int kThreadsW4 = 448;
+constexpr int kMaxG = 32;          // groups of 128 along K a row may have (K <= 4096)
+constexpr int A_BYTES_W = WM * 128, Q_BYTES_W = WN * 32, RAW_BYTES = A_BYTES_W + Q_BYTES_W, B_BYTES_W = WN * 128;
+
+struct W4Args {
+  bf16* C; int64_t ldc;
+  const float* scale;              // [E, Nw, G]
+  int rows, N, Nw, K, G;           // N: output columns; Nw: weight rows per expert (2N with SwiGLU)
+  int n_tiles, k_blocks, max_tiles;
+  int swiglu, up_off;              // SwiGLU: tile = 128 gate rows + the 128 up rows of the same outputs
+  const int* g_count; const int* g_row0; const int* g_rows; const int* g_expert;
+  int* status;
+};
+
+__device__ __forceinline__ uint64_t w4_now() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ bool w4_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  if (mbar_try(bar, parity)) return true;
+  const uint64_t t0 = w4_now();
+  for (;;) {
+    for (int i = 0; i < 256; ++i)
+      if (mbar_try(bar, parity)) return true;
+    if (*abort_flag) return false;
+    if (w4_now() - t0 > 2000000000ull) return false;
+  }
+}
+__device__ __forceinline__ void fence_async_smem_w4() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+// 8 codes (one 32-bit word: byte i = codes 2i, 2i+1) -> 8 bf16 (4 words), value (code - 8) * s
+__device__ __forceinline__ void w4_expand(uint32_t w, __nv_bfloat162 s2, uint32_t* out) {
+  const uint32_t lo = w & 0x0f0f0f0fu, hi = (w >> 4) & 0x0f0f0f0fu;
+  const __nv_bfloat162 off = __floats2bfloat162_rn(136.f, 136.f);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    // bytes (lo.b_i, 0x43, hi.b_i, 0x43): two bf16 equal to 128 + code
+    uint32_t p;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(p) : "r"(lo), "r"(hi), "r"((uint32_t)i | ((uint32_t)(4 + i) << 8)));
+    p = (p & 0x00ff00ffu) | 0x43004300u;
+    __nv_bfloat162 v = *reinterpret_cast<__nv_bfloat162*>(&p);
+    v = __hmul2(__hsub2(v, off), s2);
+    out[i] = *reinterpret_cast<uint32_t*>(&v);
+  }
+}
+
+__global__ void __launch_bounds__(kThreadsW4, 1)
+gemm_w4_grouped_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmQ, const W4Args a) {
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  unsigned char* raw = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  unsigned char* btiles = raw + WRS * RAW_BYTES;
+  bf16* sc_s = reinterpret_cast<bf16*>(btiles + WBS * B_BYTES_W);      // [2][G][256] group scales of the current / next tile
+  __shared__ uint64_t raw_full[WRS], raw_empty[WRS], b_ready[WBS], b_empty[WBS], acc_full[2], acc_empty[2];
+  __shared__ uint32_t tmem_base_s;
+  __shared__ int abort_s;
+  volatile int* abort_flag = &abort_s;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < WRS; ++s) { mbar_init(&raw_full[s], 1); mbar_init(&raw_empty[s], 1); }
+    for (int s = 0; s < WBS; ++s) { mbar_init(&b_ready[s], 8); mbar_init(&b_empty[s], 1); }
+    for (int i = 0; i < 2; ++i) { mbar_init(&acc_full[i], 1); mbar_init(&acc_empty[i], 4); }
+    abort_s = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmQ);
+  }
+  if (warp == 1) {
+    tmem_alloc(&tmem_base_s, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_base_s;
+  griddep_launch();
+  griddep_wait();
+
+  int m_tiles = *a.g_count;
+  if (m_tiles > a.max_tiles) m_tiles = a.max_tiles;
+  const int total = m_tiles * a.n_tiles;
+  const int out_n = a.swiglu ? WN / 2 : WN;          // output columns per tile
+  constexpr uint32_t IDESC = umma_idesc(WM, WN, 1, 1);
+
+  if (warp == 0) {
+    // ------------------------------- TMA producer -----------------------------------------
+    if (lane == 0) {
+      uint32_t it = 0;
+      for (int tile = blockIdx.x; tile < total && !*abort_flag; tile += gridDim.x) {
+        const int mt = tile % m_tiles, nt = tile / m_tiles;
+        const int m0 = a.g_row0[mt], wrow = a.g_expert[mt] * a.Nw + nt * out_n;
+        for (int kb = 0; kb < a.k_blocks; ++kb, ++it) {
+          const int s = it % WRS;
+          const uint32_t ph = (it / WRS) & 1;
+          if (!w4_wait(&raw_empty[s], ph ^ 1, abort_flag)) { atomicCAS(a.status, 0, 91); abort_s = 1; break; }
+          mbar_expect_tx(&raw_full[s], RAW_BYTES);
+          unsigned char* st = raw + (size_t)s * RAW_BYTES;
+          tma_load_2d(st, &tmA, &raw_full[s], kb * 64, m0);
+          if (a.swiglu) {
+            tma_load_2d(st + A_BYTES_W, &tmQ, &raw_full[s], kb * 32, wrow);
+            tma_load_2d(st + A_BYTES_W + Q_BYTES_W / 2, &tmQ, &raw_full[s], kb * 32, wrow + a.up_off);
+          } else {
+            tma_load_2d(st + A_BYTES_W, &tmQ, &raw_full[s], kb * 32, wrow);
+            tma_load_2d(st + A_BYTES_W + Q_BYTES_W / 2, &tmQ, &raw_full[s], kb * 32, wrow + WN / 2);
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------- MMA issuer -------------------------------------------
+    if (lane == 0) {
+      uint32_t it = 0, tcount = 0;
+      for (int tile = blockIdx.x; tile < total && !*abort_flag; tile += gridDim.x, ++tcount) {
+        const uint32_t acc = tcount & 1, aph = (tcount >> 1) & 1;
+        if (!w4_wait(&acc_empty[acc], aph ^ 1, abort_flag)) { atomicCAS(a.status, 0, 92); abort_s = 1; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * WN;
+        bool ok = true;
+        for (int kb = 0; kb < a.k_blocks; ++kb, ++it) {
+          const int s = it % WRS, bs = it % WBS;
+          if (!w4_wait(&raw_full[s], (it / WRS) & 1, abort_flag) || !w4_wait(&b_ready[bs], (it / WBS) & 1, abort_flag)) {
+            atomicCAS(a.status, 0, 93); abort_s = 1; ok = false; break;
+          }
+          tc_fence_after();
+          const uint64_t ad = umma_desc_sw128(raw + (size_t)s * RAW_BYTES), bd = umma_desc_sw128(btiles + (size_t)bs * B_BYTES_W);
+#pragma unroll
+          for (int k = 0; k < 4; ++k) umma_f16(d_tmem, ad + 2 * k, bd + 2 * k, IDESC, (kb | k) != 0);
+          umma_commit(&raw_empty[s]);
+          umma_commit(&b_empty[bs]);
+        }
+        if (!ok) break;
+        umma_commit(&acc_full[acc]);
+      }
+    }
+  } else if (warp >= 6) {
+    // ------------------------------- dequant: thread r expands weight row r of the tile ----------------
+    const int r = threadIdx.x - 6 * 32;                 // 0 .. 255
+    uint32_t it = 0;
+    float4 sreg[kMaxG / 4];
+    // weight row of thread r for n-tile nt inside its expert's block, or -1 past the last output column
+    auto row_of = [&](int nt) {
+      if (a.swiglu) return (nt * out_n + (r & (WN / 2 - 1)) < a.N) ? nt * out_n + (r < WN / 2 ? r : a.up_off + r - WN / 2) : -1;
+      return nt * WN + r < a.N ? nt * WN + r : -1;
+    };
+    auto fetch_scales = [&](int mt, int nt) {
+      const int wr = row_of(nt);
+      if (wr >= 0) {
+        const float4* sp = reinterpret_cast<const float4*>(a.scale + ((int64_t)a.g_expert[mt] * a.Nw + wr) * a.G);
+#pragma unroll
+        for (int i = 0; i < kMaxG / 4; ++i)
+          if (i * 4 < a.G) sreg[i] = sp[i];
+      }
+    };
+    auto store_scales = [&](int slot) {
+      bf16* dst = sc_s + (size_t)slot * WN * a.G + r;
+#pragma unroll
+      for (int i = 0; i < kMaxG / 4; ++i) {
+        if (i * 4 < a.G) {
+          dst[(size_t)(4 * i) * WN] = __float2bfloat16(sreg[i].x);
+          dst[(size_t)(4 * i + 1) * WN] = __float2bfloat16(sreg[i].y);
+          dst[(size_t)(4 * i + 2) * WN] = __float2bfloat16(sreg[i].z);
+          dst[(size_t)(4 * i + 3) * WN] = __float2bfloat16(sreg[i].w);
+        }
+      }
+    };
+    if ((int)blockIdx.x < total) { fetch_scales(blockIdx.x % m_tiles, blockIdx.x / m_tiles); store_scales(0); }
+    int tnum = 0;
+    for (int tile = blockIdx.x; tile < total && !*abort_flag; tile += gridDim.x, ++tnum) {
+      const int nt = tile / m_tiles;
+      const bool live = row_of(nt) >= 0;
+      // this row's group scales (bf16, [group][row] in shared memory) were staged one tile ahead
+      const bf16* scs = sc_s + (size_t)(tnum & 1) * WN * a.G + r;
+      bool ok = true;
+      for (int kb = 0; kb < a.k_blocks; ++kb, ++it) {
+        const int s = it % WRS, bs = it % WBS;
+        if (kb == 0 && tile + (int)gridDim.x < total) {          // request the next tile's scales; stored after this tile
+          const int t2 = tile + gridDim.x, mt2 = t2 % m_tiles, nt2 = t2 / m_tiles;
+          fetch_scales(mt2, nt2);
+        }
+        if (!w4_wait(&raw_full[s], (it / WRS) & 1, abort_flag) || !w4_wait(&b_empty[bs], ((it / WBS) & 1) ^ 1, abort_flag)) {
+          if (lane == 0) { atomicCAS(a.status, 0, 94); abort_s = 1; }
+          ok = false; break;
+        }
+        const uint4* q = reinterpret_cast<const uint4*>(raw + (size_t)s * RAW_BYTES + A_BYTES_W + r * 32);
+        const uint4 q0 = q[0], q1 = q[1];
+        const bf16 sc = live ? scs[(size_t)(kb >> 1) * WN] : __float2bfloat16(0.f);
+        const __nv_bfloat162 s2 = __halves2bfloat162(sc, sc);
+        unsigned char* brow = btiles + (size_t)bs * B_BYTES_W + r * 128;
+        const uint32_t words[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {                    // word c = codes 8c .. 8c+7 = 16-byte chunk c of the row
+          uint32_t o[4];
+          w4_expand(words[c], s2, o);
+          *reinterpret_cast<uint4*>(brow + ((c ^ (r & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+        }
+        fence_async_smem_w4();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&b_ready[bs]);
+      }
+      if (!ok) break;
+      store_scales((tnum + 1) & 1);
+    }
+  } else {
+    // ------------------------------- epilogue ---------------------------------------------
+    const int q = warp & 3;
+    uint32_t tcount = 0;
+    for (int tile = blockIdx.x; tile < total && !*abort_flag; tile += gridDim.x, ++tcount) {
+      const int mt = tile % m_tiles, nt = tile / m_tiles;
+      const int m0 = a.g_row0[mt], row_end = m0 + a.g_rows[mt], n0 = nt * out_n;
+      const uint32_t acc = tcount & 1, aph = (tcount >> 1) & 1;
+      if (!w4_wait(&acc_full[acc], aph, abort_flag)) { if (lane == 0) { atomicCAS(a.status, 0, 95); abort_s = 1; } break; }
+      tc_fence_after();
+      const int row = m0 + q * 32 + lane;
+#pragma unroll 1
+      for (int c0 = 0; c0 < out_n; c0 += 32) {
+        uint32_t rg[32], ru[32];
+        const uint32_t ta = tmem_base + acc * WN + ((uint32_t)(q * 32) << 16) + c0;
+        tmem_ld32(ta, rg);
+        if (a.swiglu) tmem_ld32(ta + WN / 2, ru);
+        tmem_ld_wait();
+        const int col0 = n0 + c0;
+        if (row < row_end && col0 < a.N) {
+          bf16* cp = a.C + (int64_t)row * a.ldc + col0;
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            if (col0 + v * 8 >= a.N) break;  // N is a multiple of 8
+            float f[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const float g = __uint_as_float(rg[v * 8 + i]);
+              f[i] = a.swiglu ? silu_f(g) * __uint_as_float(ru[v * 8 + i]) : g;
+            }
+            *reinterpret_cast<uint4*>(cp + v * 8) = float_to_bf16x8(f);
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[acc]);
+    }
+  }
+  // ------------------------------- teardown ---------------------------------------------------
+  tc_fence_before();
+  __syncthreads();
+  if (abort_s) {
+    const uint64_t t0 = w4_now();
+    while (w4_now() - t0 < 2000000ull) __nanosleep(1000);
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+// codes viewed as a 2-D byte tensor [rows, K/2]: box [128 rows, 32 bytes], no swizzle
+int make_code_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t row_bytes) {
+  cb_encode_tiled_fn enc = cb_get_encode();
+  if (!enc) return CB_ERR_DRIVER;
+  if (((uintptr_t)base & 15) || (row_bytes & 15)) return CB_ERR_SHAPE;
+  cuuint64_t dims[2] = {row_bytes, rows};
+  cuuint64_t strides[1] = {row_bytes};
+  cuuint32_t box[2] = {32, 128};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : CB_ERR_DRIVER;
+}
+
+}  // namespace
+
+// rows x K (bf16, sorted by expert) times the int4 stack Wq [E, Nw, K/2] with scales [E, Nw, K/128] (fp32).
+// swiglu = 0: C [rows, N] with N = Nw.  swiglu = 1: Nw = 2N (gate rows, then up rows) and
+// C [rows, N] = silu(gate) * up.  K % 128 == 0, N % 8 == 0.  The tile list comes from cb_moe_dispatch.
+CB_EXPORT int cb_gemm_w4_grouped(const void* A, int64_t lda, const void* Wq, const void* wscale, void* C, int64_t ldc,
+                                 int64_t rows, int64_t E, int64_t Nw, int64_t K, int64_t swiglu, const void* g_count,
+                                 const void* g_row0, const void* g_rows, const void* g_expert, int64_t max_tiles,
+                                 void* status, void* stream) {
+  if (rows < 1 || Nw < 1 || K < 1 || E < 1 || max_tiles < 1) return CB_ERR_SHAPE;
+  const int64_t N = swiglu ? Nw / 2 : Nw;
+  if (K / 128 > kMaxG || (K / 128) % 4) return CB_ERR_SHAPE;      // the scales of a row travel as float4
+  if (K % 128 || N % 8 || ldc % 8 || (swiglu && Nw % 2) || !status || !g_count || !g_row0 || !g_rows || !g_expert) return CB_ERR_SHAPE;
+  CUtensorMap tmA, tmQ;
+  int rc = cb_make_tmap_2d(&tmA, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, A, (uint64_t)rows, (uint64_t)K, (uint64_t)lda, WM, 64);
+  if (rc) return rc;
+  rc = make_code_map(&tmQ, Wq, (uint64_t)(E * Nw), (uint64_t)(K / 2));
+  if (rc) return rc;
+  W4Args a;
+  a.C = (bf16*)C; a.ldc = ldc; a.scale = (const float*)wscale;
+  a.rows = (int)rows; a.N = (int)N; a.Nw = (int)Nw; a.K = (int)K; a.G = (int)(K / 128);
+  const int out_n = swiglu ? WN / 2 : WN;
+  a.n_tiles = (int)((N + out_n - 1) / out_n); a.k_blocks = (int)(K / 64); a.max_tiles = (int)max_tiles;
+  a.swiglu = swiglu ? 1 : 0; a.up_off = (int)N;
+  a.g_count = (const int*)g_count; a.g_row0 = (const int*)g_row0; a.g_rows = (const int*)g_rows; a.g_expert = (const int*)g_expert;
+  a.status = (int*)status;
+  const size_t smem = (size_t)WRS * RAW_BYTES + (size_t)WBS * B_BYTES_W + (size_t)2 * WN * a.G * sizeof(bf16) + 1024;
+  cudaError_t e = cudaFuncSetAttribute(gemm_w4_grouped_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return (int)e;
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const int64_t total = max_tiles * a.n_tiles;
+  const int grid = (int)(total < sms ? total : sms);
+  return (int)cb_launch(gemm_w4_grouped_kernel, dim3((unsigned)grid), dim3(kThreadsW4), smem, (cudaStream_t)stream, tmA, tmQ, a);
+}

@@ -258,9 +258,14 @@ class MoEWeights:
         if debug.MOE_CHECK:
             debug.check_moe_dispatch(idx, disp, n_local)
         xs = normed.index_select(0, disp["src_tok"])                      # gathered activations [T*k, H]
-        gu = K.gemm_grouped(xs, self._stack(self.gate_up), disp)
-        inter = K.swiglu(gu)
-        y = K.gemm_grouped(inter, self._stack(self.down), disp)
+        if self.w4 and K.w4_grouped_ok(H) and K.w4_grouped_ok(I):
+            # int4 codes straight into the tensor-core GEMM (expanded inside the CTA), SwiGLU in its epilogue
+            inter = K.gemm_w4_grouped(xs, self.gate_up.wq, self.gate_up.scale, disp, swiglu=True)
+            y = K.gemm_w4_grouped(inter, self.down.wq, self.down.scale, disp)
+        else:
+            gu = K.gemm_grouped(xs, self._stack(self.gate_up), disp)
+            inter = K.swiglu(gu)
+            y = K.gemm_grouped(inter, self._stack(self.down), disp)
         shared = gate = None
         if self.sh_gu is not None:
             sh = K.gemm_swiglu(normed, self.sh_gu)

@@ -414,6 +414,33 @@ def gemm_grouped(A: torch.Tensor, W: torch.Tensor, disp: dict, out: torch.Tensor
     return out
 
 
+# Routed-MoE prefill straight from the int4 expert stacks (COFFIN_W4_GROUPED=0: expand to bf16 first).
+W4_GROUPED = os.environ.get("COFFIN_W4_GROUPED", "1") != "0"
+
+
+def gemm_w4_grouped(A: torch.Tensor, Wq: torch.Tensor, wscale: torch.Tensor, disp: dict, *, swiglu: bool = False,
+                    out: torch.Tensor | None = None) -> torch.Tensor:
+    """``out[r] = A[r] @ dequant(Wq[expert(r)]).T`` for expert-sorted rows ``A [S, K]`` and int4 stacks
+    ``Wq [E, Nw, K/2]`` uint8 + ``wscale [E, Nw, K/128]`` fp32 (the layout the decode kernels stream): the
+    codes are expanded to bf16 inside the CTA, next to the tensor core.  ``swiglu``: ``Nw = 2N`` (gate rows,
+    then up rows) and ``out [S, N] = silu(gate) * up``."""
+    S, Kd = A.shape
+    E, Nw, half = Wq.shape
+    assert half * 2 == Kd and A.stride(1) == 1 and Wq.is_contiguous() and wscale.is_contiguous() and wscale.dtype == torch.float32
+    N = Nw // 2 if swiglu else Nw
+    if out is None:
+        out = torch.empty(S, N, dtype=torch.bfloat16, device=A.device)
+    call("gemm_w4_grouped", A, A.stride(0), Wq, wscale, out, out.stride(0), S, E, Nw, Kd, int(swiglu), disp["count"],
+         disp["row0"], disp["rows"], disp["expert"], disp["max_tiles"], status_word(A.device))
+    _count()
+    return out
+
+
+def w4_grouped_ok(Kd: int) -> bool:
+    """The grouped int4 kernel takes rows of at most 32 scale groups, four at a time."""
+    return W4_GROUPED and Kd % 512 == 0 and Kd <= 4096
+
+
 def quant_rows(x: torch.Tensor, swiglu: bool = False) -> tuple[torch.Tensor, torch.Tensor]:
     """Per-row dynamic int8 quantisation of bf16 rows (optionally of ``silu(gate) * up`` of a
     ``[M, 2I]`` input). Returns ``(q int8 [M, K], scale fp32 [M])``."""

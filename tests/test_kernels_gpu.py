@@ -517,6 +517,52 @@ def test_moe_dispatch_and_grouped_gemm(T, k, E, H, N):
         assert (idx[sel] == int(ex[i])).all()
 
 
+@pytest.mark.parametrize("T,k,E,H,I", [(300, 4, 8, 512, 256), (700, 8, 32, 1024, 512), (64, 2, 16, 512, 264), (2048, 8, 64, 2048, 512)])
+def test_grouped_gemm_from_int4_codes(T, k, E, H, I):
+    """Routed-expert prefill from the int4 stacks: codes expanded inside the CTA, gate|up with the SwiGLU
+    epilogue, then the down projection; against the dequantised fp32 product per expert."""
+    from coffin_b200.weights.quant import W4A8Weight
+    kk = K()
+    g = torch.Generator().manual_seed(T + E)
+    idx = torch.randint(-1, E, (T, k), generator=g, dtype=torch.int32)
+    x = (torch.randn(T, H, generator=g) * 0.5).bfloat16()
+    qgu = W4A8Weight.quantize(torch.randn(E, 2 * I, H, generator=g) * 0.05)
+    down = I % 512 == 0                  # the kernel takes reduction lengths that are multiples of 512
+    Wgu = qgu.dequant().float()          # [E, 2I, H]
+    if down:
+        qdn = W4A8Weight.quantize(torch.randn(E, H, I, generator=g) * 0.05)
+        Wdn = qdn.dequant().float()      # [E, H, I]
+    d = kk.moe_dispatch(idx.to(DEV), E)
+    pos = d["pos"].cpu().reshape(T, k)
+    xs = x.to(DEV).index_select(0, d["src_tok"])
+    gq, gs = (t.to(DEV) for t in qgu.to_nk())
+    inter = kk.gemm_w4_grouped(xs, gq, gs, d, swiglu=True)
+    if down:
+        dq, ds = (t.to(DEV) for t in qdn.to_nk())
+        y = kk.gemm_w4_grouped(inter, dq, ds, d)
+    torch.cuda.synchronize()
+    kk.check_status()
+    # plain (no SwiGLU) form of the first projection as well
+    gu_plain = kk.gemm_w4_grouped(xs, gq, gs, d)
+    torch.cuda.synchronize()
+    kk.check_status()
+    inter_c, gu_c = inter.float().cpu(), gu_plain.float().cpu()
+    y_c = y.float().cpu() if down else None
+    for t in range(0, T, 5):
+        for j in range(k):
+            e = int(idx[t, j])
+            if e < 0:
+                continue
+            gu = x[t].float() @ Wgu[e].T
+            ref_i = O.silu_mul(gu[None, :I], gu[None, I:])[0]
+            got_i = inter_c[pos[t, j]]
+            assert (got_i - ref_i).abs().max() <= 2e-2 * ref_i.abs().max() + 1e-3, f"inter t={t} j={j}"
+            assert (gu_c[pos[t, j]] - gu).abs().max() <= 2e-2 * gu.abs().max() + 1e-3, f"gate|up t={t} j={j}"
+            if down:
+                ref_y = got_i.bfloat16().float() @ Wdn[e].T
+                assert (y_c[pos[t, j]] - ref_y).abs().max() <= 2e-2 * ref_y.abs().max() + 1e-3, f"down t={t} j={j}"
+
+
 @pytest.mark.parametrize("nh,nkv,T1", [(16, 4, 150), (8, 4, 64), (6, 2, 257)])
 def test_attention_decode_batch_kernel(nh, nkv, T1):
     """Tensor-core batch decode kernel (one CTA per row and kv head) against the fp32 oracle and the
