@@ -419,7 +419,7 @@ W4_GROUPED = os.environ.get("COFFIN_W4_GROUPED", "1") != "0"
 
 
 def gemm_w4_grouped(A: torch.Tensor, Wq: torch.Tensor, wscale: torch.Tensor, disp: dict, *, swiglu: bool = False,
-                    out: torch.Tensor | None = None) -> torch.Tensor:
+                    out: torch.Tensor | None = None, trace: torch.Tensor | None = None) -> torch.Tensor:
     """``out[r] = A[r] @ dequant(Wq[expert(r)]).T`` for expert-sorted rows ``A [S, K]`` and int4 stacks
     ``Wq [E, Nw, K/2]`` uint8 + ``wscale [E, Nw, K/128]`` fp32 (the layout the decode kernels stream): the
     codes are expanded to bf16 inside the CTA, next to the tensor core.  ``swiglu``: ``Nw = 2N`` (gate rows,
@@ -431,14 +431,14 @@ def gemm_w4_grouped(A: torch.Tensor, Wq: torch.Tensor, wscale: torch.Tensor, dis
     if out is None:
         out = torch.empty(S, N, dtype=torch.bfloat16, device=A.device)
     call("gemm_w4_grouped", A, A.stride(0), Wq, wscale, out, out.stride(0), S, E, Nw, Kd, int(swiglu), disp["count"],
-         disp["row0"], disp["rows"], disp["expert"], disp["max_tiles"], status_word(A.device))
+         disp["row0"], disp["rows"], disp["expert"], disp["max_tiles"], status_word(A.device), trace)
     _count()
     return out
 
 
 def w4_grouped_ok(Kd: int) -> bool:
-    """The grouped int4 kernel takes rows of at most 32 scale groups, four at a time."""
-    return W4_GROUPED and Kd % 512 == 0 and Kd <= 4096
+    """The grouped int4 kernel takes rows of at most 20 scale groups, four at a time."""
+    return W4_GROUPED and Kd % 512 == 0 and Kd <= 2560
 
 
 def quant_rows(x: torch.Tensor, swiglu: bool = False) -> tuple[torch.Tensor, torch.Tensor]:
