@@ -124,7 +124,8 @@ template <int CPL>
 __global__ void __launch_bounds__(256) rmsnorm_rows_kernel(const bf16* __restrict__ x, const bf16* __restrict__ add,
                                                            const float* __restrict__ gain, bf16* __restrict__ res_out,
                                                            bf16* __restrict__ out, int64_t M, int64_t N, int64_t ldx,
-                                                           int64_t ldo, float eps) {
+                                                           int64_t ldo, float eps, int8_t* __restrict__ q,
+                                                           float* __restrict__ qscale) {
   griddep_launch();
   griddep_wait();
   const int lane = threadIdx.x & 31;
@@ -163,6 +164,7 @@ __global__ void __launch_bounds__(256) rmsnorm_rows_kernel(const bf16* __restric
     }
   }
   const float rstd = rsqrtf(warp_sum(ss) / (float)N + eps);
+  float amax = 0.f;
 #pragma unroll
   for (int i = 0; i < CPL; ++i) {
     const int c = lane + 32 * i;
@@ -172,7 +174,33 @@ __global__ void __launch_bounds__(256) rmsnorm_rows_kernel(const bf16* __restric
       const float4 g0 = *reinterpret_cast<const float4*>(gain + c * 8), g1 = *reinterpret_cast<const float4*>(gain + c * 8 + 4);
       f[0] *= rstd * g0.x; f[1] *= rstd * g0.y; f[2] *= rstd * g0.z; f[3] *= rstd * g0.w;
       f[4] *= rstd * g1.x; f[5] *= rstd * g1.y; f[6] *= rstd * g1.z; f[7] *= rstd * g1.w;
-      *reinterpret_cast<uint4*>(out + r * ldo + c * 8) = float_to_bf16x8(f);
+      v[i] = float_to_bf16x8(f);                       // the normalised row replaces the input in the registers
+      if (out) *reinterpret_cast<uint4*>(out + r * ldo + c * 8) = v[i];
+      if (q) {
+        bf16x8_to_float(v[i], f);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) amax = fmaxf(amax, fabsf(f[e]));
+      }
+    }
+  }
+  if (q) {   // int8 rows + scale of the bf16-rounded values (what quant_rows would compute from `out`)
+    amax = warp_max(amax);
+    const float sc = fmaxf(amax, 1e-8f) / 127.f, inv = 1.f / sc;
+    if (lane == 0) qscale[r] = sc;
+#pragma unroll
+    for (int i = 0; i < CPL; ++i) {
+      const int c = lane + 32 * i;
+      if (c < nchunk) {
+        float f[8];
+        bf16x8_to_float(v[i], f);
+        uint32_t w[2] = {0u, 0u};
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          const int qi = max(-127, min(127, __float2int_rn(f[e] * inv)));
+          w[e >> 2] |= (uint32_t)(qi & 0xff) << (8 * (e & 3));
+        }
+        *reinterpret_cast<uint2*>(q + r * N + c * 8) = make_uint2(w[0], w[1]);
+      }
     }
   }
 }
@@ -409,11 +437,12 @@ CB_EXPORT int cb_rmsnorm_q(const void* x, const void* add, const void* gain, voi
   if (N % 8 || N * 4 > 200 * 1024) return CB_ERR_SHAPE;
   if ((q == nullptr) != (qscale == nullptr) || (!out && !q)) return CB_ERR_ARG;
   if (M == 0) return 0;
-  if (M >= 256 && !q && out && ldx % 8 == 0 && ldo % 8 == 0 && ((uintptr_t)gain & 15) == 0) {   // a prefill chunk: one warp per row
+  if (M >= 256 && ldx % 8 == 0 && (!out || ldo % 8 == 0) && ((uintptr_t)gain & 15) == 0 && ((uintptr_t)q & 7) == 0) {   // a prefill chunk: one warp per row
     const dim3 grid((unsigned)((M + 7) / 8));
 #define CB_RMS_ROWS(CPL_)                                                                                      \
   return (int)cb_launch(rmsnorm_rows_kernel<CPL_>, grid, dim3(256), 0, (cudaStream_t)stream, (const bf16*)x,   \
-                        (const bf16*)add, (const float*)gain, (bf16*)res_out, (bf16*)out, M, N, ldx, ldo, eps)
+                        (const bf16*)add, (const float*)gain, (bf16*)res_out, (bf16*)out, M, N, ldx, ldo, eps,  \
+                        (int8_t*)q, (float*)qscale)
     if (N <= 8 * 32 * 4) CB_RMS_ROWS(4);
     if (N <= 8 * 32 * 8) CB_RMS_ROWS(8);
     if (N <= 8 * 32 * 12) CB_RMS_ROWS(12);

@@ -264,6 +264,47 @@ __global__ void __launch_bounds__(256) quant_rows_kernel(const bf16* __restrict_
     q[r * K + i] = (int8_t)max(-127, min(127, __float2int_rn(row[i] * inv)));
 }
 
+// The same for rows whose length is a multiple of 8 and whose rows start on 16 bytes: 16-byte loads, 8-byte
+// stores, two passes over the (cache-resident) row instead of a shared-memory copy.
+__device__ __forceinline__ void quant_chunk(const bf16* xr, int64_t K, int64_t c, int swiglu, float* f) {
+  bf16x8_to_float(*reinterpret_cast<const uint4*>(xr + c * 8), f);
+  if (swiglu) {
+    float u[8];
+    bf16x8_to_float(*reinterpret_cast<const uint4*>(xr + K + c * 8), u);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) f[e] = __bfloat162float(__float2bfloat16(silu_f(f[e]) * u[e]));
+  }
+}
+__global__ void __launch_bounds__(256) quant_rows_vec_kernel(const bf16* __restrict__ x, int64_t ldx, int8_t* __restrict__ q,
+                                                              float* __restrict__ scale, int64_t K, int swiglu) {
+  __shared__ float red[32];
+  griddep_launch();
+  griddep_wait();
+  const int64_t r = blockIdx.x, nchunk = K >> 3;
+  const bf16* xr = x + r * ldx;
+  float amax = 0.f;
+  for (int64_t c = threadIdx.x; c < nchunk; c += blockDim.x) {
+    float f[8];
+    quant_chunk(xr, K, c, swiglu, f);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) amax = fmaxf(amax, fabsf(f[e]));
+  }
+  amax = block_max(amax, red);
+  const float sc = fmaxf(amax, 1e-8f) / 127.f, inv = 1.f / sc;
+  if (threadIdx.x == 0) scale[r] = sc;
+  for (int64_t c = threadIdx.x; c < nchunk; c += blockDim.x) {
+    float f[8];
+    quant_chunk(xr, K, c, swiglu, f);
+    uint32_t w[2] = {0u, 0u};
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const int qi = max(-127, min(127, __float2int_rn(f[e] * inv)));
+      w[e >> 2] |= (uint32_t)(qi & 0xff) << (8 * (e & 3));
+    }
+    *reinterpret_cast<uint2*>(q + r * K + c * 8) = make_uint2(w[0], w[1]);
+  }
+}
+
 }  // namespace
 
 // Same contract as cb_gemv_bf16 with int8 weights + per-row scales; K % 16 == 0.
@@ -292,6 +333,9 @@ CB_EXPORT int cb_gemv_i8(const void* W, const void* wscale, const void* x, void*
 CB_EXPORT int cb_quant_rows(const void* x, int64_t ldx, void* q, void* scale, int64_t M, int64_t K, int64_t swiglu,
                             void* stream) {
   if (M == 0) return 0;
+  if (K % 8 == 0 && ldx % 8 == 0 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)q & 7) == 0)
+    return (int)cb_launch(quant_rows_vec_kernel, dim3((unsigned)M), dim3(256), 0, (cudaStream_t)stream, (const bf16*)x, ldx,
+                          (int8_t*)q, (float*)scale, K, (int)swiglu);
   if (K * 4 > 200 * 1024) return CB_ERR_SHAPE;
   const size_t smem = (size_t)K * 4;
   if (smem + 2048 > 48 * 1024) {   // the 48 KB default also has to hold the static shared memory

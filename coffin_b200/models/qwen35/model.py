@@ -375,7 +375,7 @@ class Qwen35Model:
             A = K.swiglu(A)
         return K.gemm(A, W, out=out, residual=residual, push=push)
 
-    def _gemm_gu(self, A, W, gu: torch.Tensor):
+    def _gemm_gu(self, A, W, gu: torch.Tensor, aq=None):
         """Gate|up projection of a prefill chunk into ``gu [T, 2I]``.  bf16 weights and more rows than one
         CTA-pair tile: the SwiGLU product comes out of the GEMM epilogue and the ``[T, I]`` view holding it
         is returned; otherwise ``gu`` is filled with both halves and None is returned."""
@@ -383,7 +383,7 @@ class Qwen35Model:
             W = W.expanded()
         if not isinstance(W, QW) and K.PAIR_GEMM and A.shape[0] >= K.PAIR_MIN_ROWS and W.shape[0] >= 256:
             return K.gemm_swiglu(A, W, out=gu[:, :W.shape[0] // 2])
-        self._gemm(A, W, out=gu)
+        self._gemm(A, W, out=gu, aq=aq)
         return None
 
     def _row_parallel(self, A, W, scratch: torch.Tensor, swiglu_in: bool = False) -> torch.Tensor:
@@ -466,6 +466,9 @@ class Qwen35Model:
             }
             if self.tp is not None:
                 ws["part"] = torch.empty(rows, H, dtype=bf, device=dev)
+            if any(isinstance(lw.w_in, QW) for lw in self.layers):
+                ws["q8"] = torch.empty(rows, H, dtype=torch.int8, device=dev)
+                ws["s8"] = torch.empty(rows, dtype=torch.float32, device=dev)
             if not c.is_moe:
                 ws["gu"] = torch.empty(rows, 2 * c.intermediate_size, dtype=bf, device=dev)
                 ws["inter"] = torch.empty(rows, c.intermediate_size, dtype=bf, device=dev)
@@ -533,11 +536,14 @@ class Qwen35Model:
         else:
             cos, sin = cos_sin[0].float().contiguous(), cos_sin[1].float().contiguous()
             ridx = None
+        q8 = (ws["q8"][:T], ws["s8"][:T]) if "q8" in ws else None
         for li, lw in enumerate(self.layers):
-            K.rmsnorm(res, lw.in_gain, self.eps, out=normed)
+            # an int8 projection takes its int8 rows straight from the norm kernel (no bf16 copy, no quantise launch)
+            aq = q8 if isinstance(lw.w_in, QW) else None
+            K.rmsnorm(res, lw.in_gain, self.eps, out=None if aq else normed, quant=aq)
             n_in = lw.w_in.shape[0]
             proj = ws["proj"][:T, :n_in]
-            self._gemm(normed, lw.w_in, out=proj)
+            self._gemm(normed, lw.w_in, out=proj, aq=aq)
             if lw.kind == LINEAR:
                 j = self.lin_ids[li]
                 act = ws["act"][:T, :c.lin_vdim]
@@ -558,17 +564,18 @@ class Qwen35Model:
                     sl = slice(offs[i], offs[i + 1])
                     K.attn_prefill(q[sl], proj[sl], self.kpool[j], self.vpool[j], it[3], act[sl], q_pos0=it[1],
                                    nh=c.num_attention_heads, nkv=c.num_key_value_heads, hd=c.head_dim, **self._kvs(j))
+            aq = q8 if lw.moe is None and isinstance(lw.w_gu, QW) else None
             if self.tp_world > 1 or (self.tp_force and not c.is_moe):
                 part = self._row_parallel(act, lw.w_out, ws["part"][:T])
-                K.rmsnorm(res, lw.post_gain, self.eps, out=normed, add=part, res_out=res)
+                K.rmsnorm(res, lw.post_gain, self.eps, out=None if aq else normed, add=part, res_out=res, quant=aq)
             else:
                 self._gemm(act, lw.w_out, out=res, residual=res)
-                K.rmsnorm(res, lw.post_gain, self.eps, out=normed)
+                K.rmsnorm(res, lw.post_gain, self.eps, out=None if aq else normed, quant=aq)
             if lw.moe is not None:
                 lw.moe.forward_prefill(normed, res, self)
             else:
                 gu = ws["gu"][:T]
-                fused = self._gemm_gu(normed, lw.w_gu, gu)       # SwiGLU taken in the epilogue: gu[:, :I] is the product
+                fused = self._gemm_gu(normed, lw.w_gu, gu, aq=aq)       # SwiGLU taken in the epilogue: gu[:, :I] is the product
                 if fused is not None:
                     gu = fused
                 if self.tp_world > 1 or self.tp_force:

@@ -44,6 +44,21 @@ def test_rmsnorm_many_rows(M, N):
     s, n = O.add_rms_norm(x, add, gain)
     close(res, s)
     close(out, n)
+    # int8 rows + scales straight from the norm kernel == quantising its bf16 output afterwards
+    q8 = torch.empty(M, N, dtype=torch.int8, device=DEV)
+    s8 = torch.empty(M, dtype=torch.float32, device=DEV)
+    k.rmsnorm(x.to(DEV), gain.to(DEV), 1e-6, quant=(q8, s8))
+    qr, sr = k.quant_rows(k.rmsnorm(x.to(DEV), gain.to(DEV), 1e-6))
+    assert torch.equal(q8, qr) and torch.equal(s8, sr)
+    # the vectorised quantiser against its definition (SwiGLU form included)
+    gu = bf(M, 2 * N, seed=8)
+    for sw, src in ((False, x), (True, gu)):
+        qv, sv = k.quant_rows(src.to(DEV), swiglu=sw)
+        v = O.silu_mul(src[:, :N], src[:, N:]).to(torch.bfloat16).float() if sw else src.float()
+        sc = v.abs().amax(-1).clamp_min(1e-8) / 127
+        ref = torch.clamp(torch.round(v / sc[:, None]), -127, 127)
+        assert (sv.cpu() - sc).abs().max() <= 1e-6 * sc.max() + 1e-12
+        assert (qv.cpu().float() - ref).abs().max() <= 1      # a value on a rounding boundary may land either side
 
 
 def test_rowwise_kernels():
