@@ -70,7 +70,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   constexpr int BK = I8 ? 128 : 64;                 // elements per 128-byte k-block
   constexpr int OUT_N = SWIGLU ? TILE_N / 2 : TILE_N;   // output columns of a tile
   static_assert(BNI % 16 == 0 && BNI <= 256 && BH % 8 == 0 && TILE_N % 32 == 0, "tile shape");
-  static_assert(!SWIGLU || (NI == 1 && !I8), "the SwiGLU form is one bf16 MMA per k-step");
+  static_assert(!SWIGLU || NI == 1, "the SwiGLU form is one MMA per k-step");
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   unsigned char* tiles = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   __shared__ uint64_t full_bar[STAGES], empty_bar[STAGES], acc_full[2], acc_empty[2];
@@ -210,7 +210,15 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
               if (col0 + v * 8 >= a.N) break;  // N is a multiple of 8
               float f[8];
 #pragma unroll
-              for (int i = 0; i < 8; ++i) f[i] = silu_f(__uint_as_float(rg[v * 8 + i])) * __uint_as_float(ru[v * 8 + i]);
+              for (int i = 0; i < 8; ++i) {
+                if (I8) {
+                  const int cc = col0 + v * 8 + i;
+                  f[i] = silu_f((float)(int)rg[v * 8 + i] * rs * a.col_scale[cc]) *
+                         ((float)(int)ru[v * 8 + i] * rs * a.col_scale[a.up_off + cc]);
+                } else {
+                  f[i] = silu_f(__uint_as_float(rg[v * 8 + i])) * __uint_as_float(ru[v * 8 + i]);
+                }
+              }
               *reinterpret_cast<uint4*>(cp + v * 8) = float_to_bf16x8(f);
             }
           }
@@ -370,6 +378,20 @@ CB_EXPORT int cb_gemm_bf16_swiglu(const void* A, int64_t lda, const void* W, int
   a.M = (int)M; a.N = (int)I; a.K = (int)K; a.m_tiles = (int)((M + 255) / 256); a.n_tiles = 0;
   a.k_blocks = 0; a.status = (int*)status; a.pf = nullptr; a.pf_seq = 0; a.up_off = (int)up_off;
   return launch_pair<256, 1, 6, false, true>(A, lda, W, ldw, a, (cudaStream_t)stream);
+}
+
+// int8 form: A_q [M, K] int8 with row scales, W_q [up_off + I, K] int8 with column scales (gate rows, then up rows).
+CB_EXPORT int cb_gemm_i8_swiglu(const void* A, int64_t lda, const void* W, int64_t ldw, void* C, int64_t ldc,
+                                const void* row_scale, const void* col_scale, int64_t M, int64_t I, int64_t up_off,
+                                int64_t K, void* status, void* stream) {
+  if (M < 1 || I < 1 || K < 1 || up_off < I || !row_scale || !col_scale) return CB_ERR_SHAPE;
+  if (K % 16 || I % 8 || ldc % 8 || lda % 16 || ldw % 16 || !status) return CB_ERR_SHAPE;
+  PairArgs a;
+  a.C = (bf16*)C; a.ldc = ldc; a.residual = nullptr; a.ldr = 0;
+  a.row_scale = (const float*)row_scale; a.col_scale = (const float*)col_scale;
+  a.M = (int)M; a.N = (int)I; a.K = (int)K; a.m_tiles = (int)((M + 255) / 256); a.n_tiles = 0;
+  a.k_blocks = 0; a.status = (int*)status; a.pf = nullptr; a.pf_seq = 0; a.up_off = (int)up_off;
+  return launch_pair<256, 1, 6, true, true>(A, lda, W, ldw, a, (cudaStream_t)stream);
 }
 
 // 0: every bf16 product runs on the one-CTA kernel.

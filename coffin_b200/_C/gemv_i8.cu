@@ -277,6 +277,8 @@ __device__ __forceinline__ void quant_chunk(const bf16* xr, int64_t K, int64_t c
 }
 __global__ void __launch_bounds__(256) quant_rows_vec_kernel(const bf16* __restrict__ x, int64_t ldx, int8_t* __restrict__ q,
                                                               float* __restrict__ scale, int64_t K, int swiglu) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  uint4* rowv = reinterpret_cast<uint4*>(smem_raw);        // the (SwiGLU'd) row as bf16, read once from memory
   __shared__ float red[32];
   griddep_launch();
   griddep_wait();
@@ -286,15 +288,16 @@ __global__ void __launch_bounds__(256) quant_rows_vec_kernel(const bf16* __restr
   for (int64_t c = threadIdx.x; c < nchunk; c += blockDim.x) {
     float f[8];
     quant_chunk(xr, K, c, swiglu, f);
+    rowv[c] = float_to_bf16x8(f);                          // exact: the values are bf16 already
 #pragma unroll
     for (int e = 0; e < 8; ++e) amax = fmaxf(amax, fabsf(f[e]));
   }
   amax = block_max(amax, red);
   const float sc = fmaxf(amax, 1e-8f) / 127.f, inv = 1.f / sc;
   if (threadIdx.x == 0) scale[r] = sc;
-  for (int64_t c = threadIdx.x; c < nchunk; c += blockDim.x) {
+  for (int64_t c = threadIdx.x; c < nchunk; c += blockDim.x) {   // a thread reads back the chunks it wrote
     float f[8];
-    quant_chunk(xr, K, c, swiglu, f);
+    bf16x8_to_float(rowv[c], f);
     uint32_t w[2] = {0u, 0u};
 #pragma unroll
     for (int e = 0; e < 8; ++e) {
@@ -333,9 +336,15 @@ CB_EXPORT int cb_gemv_i8(const void* W, const void* wscale, const void* x, void*
 CB_EXPORT int cb_quant_rows(const void* x, int64_t ldx, void* q, void* scale, int64_t M, int64_t K, int64_t swiglu,
                             void* stream) {
   if (M == 0) return 0;
-  if (K % 8 == 0 && ldx % 8 == 0 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)q & 7) == 0)
-    return (int)cb_launch(quant_rows_vec_kernel, dim3((unsigned)M), dim3(256), 0, (cudaStream_t)stream, (const bf16*)x, ldx,
+  if (K % 8 == 0 && ldx % 8 == 0 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)q & 7) == 0 && K * 2 <= 200 * 1024) {
+    const size_t sv = (size_t)K * 2;
+    if (sv + 2048 > 48 * 1024) {
+      cudaError_t e = cudaFuncSetAttribute(quant_rows_vec_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sv);
+      if (e != cudaSuccess) return (int)e;
+    }
+    return (int)cb_launch(quant_rows_vec_kernel, dim3((unsigned)M), dim3(256), sv, (cudaStream_t)stream, (const bf16*)x, ldx,
                           (int8_t*)q, (float*)scale, K, (int)swiglu);
+  }
   if (K * 4 > 200 * 1024) return CB_ERR_SHAPE;
   const size_t smem = (size_t)K * 4;
   if (smem + 2048 > 48 * 1024) {   // the 48 KB default also has to hold the static shared memory

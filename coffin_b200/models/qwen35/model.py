@@ -381,7 +381,10 @@ class Qwen35Model:
         is returned; otherwise ``gu`` is filled with both halves and None is returned."""
         if isinstance(W, QW4):
             W = W.expanded()
-        if not isinstance(W, QW) and K.PAIR_GEMM and A.shape[0] >= K.PAIR_MIN_ROWS and W.shape[0] >= 256:
+        if K.PAIR_GEMM and gu.shape[0] >= K.PAIR_MIN_ROWS and W.shape[0] >= 256:
+            if isinstance(W, QW):
+                q, sc = aq if aq is not None else K.quant_rows(A)
+                return K.gemm_i8_swiglu(q, sc, W.wq, W.scale, out=gu[:, :W.shape[0] // 2])
             return K.gemm_swiglu(A, W, out=gu[:, :W.shape[0] // 2])
         self._gemm(A, W, out=gu, aq=aq)
         return None

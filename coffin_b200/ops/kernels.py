@@ -509,6 +509,21 @@ def gemm_swiglu(A: torch.Tensor, Wgu: torch.Tensor, out: torch.Tensor | None = N
     return out
 
 
+def gemm_i8_swiglu(Aq: torch.Tensor, a_scale: torch.Tensor, Wq: torch.Tensor, w_scale: torch.Tensor,
+                   out: torch.Tensor | None = None) -> torch.Tensor:
+    """W8A8 form of :func:`gemm_swiglu`: ``out[M, I] = silu(gate) * up`` of the int8 gate|up projection, scales
+    applied before the activation.  More than 256 rows only (callers fall back to projection + ``quant_rows(swiglu)``)."""
+    M, K = Aq.shape
+    I = Wq.shape[0] // 2
+    assert PAIR_GEMM and M >= PAIR_MIN_ROWS and I >= 128
+    if out is None:
+        out = torch.empty(M, I, dtype=torch.bfloat16, device=Aq.device)
+    call("gemm_i8_swiglu", Aq, Aq.stride(0), Wq, Wq.stride(0), out, out.stride(0), a_scale, w_scale, M, I, I, K,
+         status_word(Aq.device))
+    _count()
+    return out
+
+
 # Products with at most 128 rows (batched decode buckets of 16..64 rows, small prefill chunks) split K
 # over CTAs: fp32 partial tiles in a per-device workspace, reduced by the last slice to arrive.
 SPLITK_GEMM = os.environ.get("COFFIN_SPLITK_GEMM", "1") != "0"

@@ -162,6 +162,20 @@ def test_gemm_swiglu_epilogue(M, I, Kd):
     assert bool((canary[M] == 7.0).all()) and bool((canary[:, I:] == 7.0).all()), "wrote outside the output"
 
 
+@pytest.mark.parametrize("M,I,Kd", [(300, 128, 80), (1000, 776, 512), (2048, 2176, 1024)])
+def test_gemm_i8_swiglu_epilogue(M, I, Kd):
+    k = K()
+    g = torch.Generator().manual_seed(9)
+    Aq = torch.randint(-127, 128, (M, Kd), generator=g, dtype=torch.int8)
+    Wq = torch.randint(-127, 128, (2 * I, Kd), generator=g, dtype=torch.int8)
+    sa, sw = torch.rand(M, generator=g) * 0.01 + 1e-3, torch.rand(2 * I, generator=g) * 0.002 + 1e-4
+    out = k.gemm_i8_swiglu(Aq.to(DEV), sa.to(DEV), Wq.to(DEV), sw.to(DEV))
+    torch.cuda.synchronize()
+    k.check_status()
+    gu = ((Aq.double() @ Wq.double().t()) * sa.double()[:, None] * sw.double()[None, :]).float()
+    close(out, O.silu_mul(gu[:, :I], gu[:, I:]), 1e-2)
+
+
 @pytest.mark.parametrize("M,N,Kd,bn", [(128, 256, 128, 256), (200, 264, 400, 128), (77, 520, 1040, 0),
                                        (300, 488, 528, 160), (64, 2560, 4096, 0), (16, 520, 9216, 0),
                                        # CTA pairs
