@@ -423,3 +423,48 @@ def test_engine_warmup_captures_the_decode_buckets_and_leaves_no_trace():
         outs.append([list(s.output) for s in seqs])
         assert all(len(o) == 12 for o in outs[-1])
     assert outs[0] == outs[1]
+
+
+@torch.no_grad()
+def test_long_chunk_of_the_4b_shape_matches_the_oracle_on_both_prefill_paths():
+    """A 600-token chunk through four layers of the 4B geometry: long enough for the CTA-pair GEMM (256-row
+    tiles, SwiGLU epilogue), the warp-per-row norm, the fused delta-net prepare + bf16 scan and the tcgen05
+    attention kernel.  Last-token logits against the fp32 oracle per element, and against the same model run
+    with those paths switched off (one-CTA GEMM, TF32 scan with its own prep launch)."""
+    import dataclasses
+    from coffin_b200.models.qwen35.model import Qwen35Model
+    from coffin_b200.ops import kernels as K
+    full = preset("qwen35-4b")
+    cfg = dataclasses.replace(full, name="4b-4layers", num_hidden_layers=4, layer_types=full.layer_types[:4], vocab_size=4096)
+    sd = random_state_dict(cfg, 0)
+    sd_b = {k: (v.to(torch.bfloat16).float() if v.dtype == torch.float32 and not k.endswith(("A_log", "dt_bias")) else v)
+            for k, v in sd.items()}
+    toks = _tokens(cfg, 600, seed=5)
+    oracle = OracleModel(cfg, sd_b)
+    ref = oracle.forward(toks, oracle.new_state())[-1]
+    scale = float(ref.abs().max())
+    bt = torch.arange(0, 12, dtype=torch.int32, device="cuda")
+
+    def run():
+        model = Qwen35Model(cfg, sd, max_seq=768, num_slots=1, max_chunk=1024)
+        model.zero_state(0)
+        out = model.prefill(toks.cuda(), 0, 0, bt).float().cpu()
+        torch.cuda.synchronize()
+        K.check_status()
+        return out
+
+    new = run()
+    K.call("set_gemm_pair", 0)
+    K.call("set_gdn_tc", 1)
+    pair = K.PAIR_GEMM
+    K.PAIR_GEMM = False
+    try:
+        old = run()
+    finally:
+        K.call("set_gemm_pair", 1)
+        K.call("set_gdn_tc", 3)
+        K.PAIR_GEMM = pair
+    for name, got in (("pair GEMM / bf16 scan", new), ("one-CTA GEMM / TF32 scan", old)):
+        bad = (got - ref).abs() > 0.03 * scale + 0.05 * ref.abs()
+        assert not bool(bad.any()), f"{name}: {int(bad.sum())} of {bad.numel()} logits off, worst {float((got - ref).abs().max()):.4g} on a scale of {scale:.4g}"
+    assert float((new - old).abs().max()) <= 0.03 * scale
