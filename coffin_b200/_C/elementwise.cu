@@ -205,6 +205,20 @@ __global__ void __launch_bounds__(256) rmsnorm_rows_kernel(const bf16* __restric
   }
 }
 
+// Pool slots and rotary rows of a prefill chunk: token t of the chunk sits at position pos0 + t, in page
+// block_table[(pos0 + t) / block] at offset (pos0 + t) % block.  One launch instead of a string of small
+// index operations per chunk.
+__global__ void prefill_index_kernel(const int* __restrict__ block_table, int pos0, int T, int block,
+                                     int* __restrict__ slots, int* __restrict__ ridx) {
+  griddep_launch();
+  griddep_wait();
+  const int t = blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= T) return;
+  const int p = pos0 + t;
+  slots[t] = block_table[p / block] * block + p % block;
+  if (ridx) ridx[t] = p;
+}
+
 // out[m, i] = silu(gu[m, i]) * gu[m, I + i]
 __global__ void swiglu_kernel(const bf16* __restrict__ gu, bf16* __restrict__ out, int64_t I,
                               int64_t ldg, int64_t ldo, int64_t total_chunks) {
@@ -478,6 +492,14 @@ CB_EXPORT int cb_gelu_tanh(const void* x, void* out, int64_t n, void* stream) {
   const int64_t blocks = min((n + 255) / 256, (int64_t)148 * 8);
   return (int)cb_launch(gelu_tanh_kernel, dim3((unsigned)blocks), dim3(256), 0, (cudaStream_t)stream, (const bf16*)x,
                         (bf16*)out, n);
+}
+
+CB_EXPORT int cb_prefill_index(const void* block_table, int64_t pos0, int64_t T, int64_t block, void* slots, void* ridx,
+                               void* stream) {
+  if (T == 0) return 0;
+  if (T < 0 || pos0 < 0 || block < 1 || !block_table || !slots) return CB_ERR_ARG;
+  return (int)cb_launch(prefill_index_kernel, dim3((unsigned)((T + 255) / 256)), dim3(256), 0, (cudaStream_t)stream,
+                        (const int*)block_table, (int)pos0, (int)T, (int)block, (int*)slots, (int*)ridx);
 }
 
 CB_EXPORT int cb_swiglu(const void* gu, void* out, int64_t M, int64_t I, int64_t ldg, int64_t ldo,

@@ -526,16 +526,15 @@ class Qwen35Model:
         offs = [0]
         for n in lens:
             offs.append(offs[-1] + n)
-        pos = torch.cat([torch.arange(it[1], it[1] + n, dtype=torch.int64, device=self.device) for it, n in zip(items, lens)]) \
-            if len(items) > 1 else torch.arange(items[0][1], items[0][1] + T, dtype=torch.int64, device=self.device)
         slots = ws["slots"][:T]
-        for i, (it, n) in enumerate(zip(items, lens)):
-            p = pos[offs[i]:offs[i + 1]]
-            slots[offs[i]:offs[i + 1]].copy_(it[3].to(torch.int64)[p // K.BLOCK] * K.BLOCK + p % K.BLOCK)
+        ridx = ws["ridx"][:T] if cos_sin is None else None
+        for i, (it, n) in enumerate(zip(items, lens)):          # pool slots (and 1-D rotary rows): one small kernel per chunk
+            bt = it[3] if it[3].dtype == torch.int32 and it[3].is_contiguous() else it[3].to(torch.int32).contiguous()
+            K.call("prefill_index", bt, it[1], n, K.BLOCK, slots[offs[i]:offs[i + 1]],
+                   ridx[offs[i]:offs[i + 1]] if ridx is not None else None)
+            K._count()
         if cos_sin is None:
             cos, sin = self.cos, self.sin
-            ridx = ws["ridx"][:T]
-            ridx.copy_(pos)
         else:
             cos, sin = cos_sin[0].float().contiguous(), cos_sin[1].float().contiguous()
             ridx = None
