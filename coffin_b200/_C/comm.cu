@@ -13,17 +13,16 @@ __global__ void epoch_bump_kernel(unsigned* epoch) {
   if (threadIdx.x == 0) *epoch += 1;
 }
 
-// Scatter an existing [T, width] bf16 tensor into the owners' inboxes (producers that are not a GEMM,
-// e.g. the MoE combine under expert parallelism).
+// Copy an existing [T, width] bf16 tensor into this rank's peer-visible buffer and publish it (producers
+// that are not a GEMM, e.g. the MoE combine under expert parallelism); the owners of the rows pull them.
 __global__ void __launch_bounds__(256) tp_pf_scatter_kernel(const TpPfDev* d, const bf16* src, int64_t lds, int T,
                                                             unsigned seq) {
   griddep_launch();
   griddep_wait();
-  const int rpr = d->rows_per_rank, W = d->width, vec = W >> 3;
+  const int W = d->width, vec = W >> 3;
   for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < (int64_t)T * vec; i += (int64_t)gridDim.x * 256) {
     const int row = (int)(i / vec), c = (int)(i % vec) * 8;
-    const int owner = row / rpr, lr = row % rpr;
-    bf16* dst = d->inbox[owner] + ((int64_t)d->rank * rpr + lr) * W + c;
+    bf16* dst = d->inbox[d->rank] + (int64_t)row * W + c;          // local copy: the owner of the row pulls it
     *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(src + (int64_t)row * lds + c);
   }
   // one system-scope fence per CTA: the barrier orders every thread's stores before thread 0's fence,
@@ -33,8 +32,12 @@ __global__ void __launch_bounds__(256) tp_pf_scatter_kernel(const TpPfDev* d, co
   if (threadIdx.x == 0) tp_pf_publish(d, 1, seq, gridDim.x);
 }
 
-// Sum the partial slices this rank received (rank order), add the residual rows, store the reduced
-// rows into every rank's result buffer.
+// Pull the partial rows this rank owns from every rank's buffer (coalesced 16-byte peer loads, rank order),
+// add the residual rows, store the reduced rows into every rank's result buffer.
+// WORLD_MAX bounds the rank loop at compile time and U is the number of 16-byte columns a thread handles per
+// pass: with few ranks more columns fit in the registers, and every column's loads (one per rank, most of
+// them over NVLink) are in flight before the first add - the kernel is latency bound.
+template <int WORLD_MAX, int U>
 __global__ void __launch_bounds__(256) tp_pf_reduce_gather_kernel(const TpPfDev* d, const bf16* residual, int64_t ldr,
                                                                   int T, unsigned seq) {
   griddep_launch();
@@ -44,21 +47,17 @@ __global__ void __launch_bounds__(256) tp_pf_reduce_gather_kernel(const TpPfDev*
   const int rpr = d->rows_per_rank, W = d->width, vec = W >> 3, world = d->world;
   const int row0 = d->rank * rpr;
   const int nrows = max(0, min(rpr, T - row0));
-  const bf16* in = d->inbox[d->rank];
-  // four 16-byte columns per thread and pass: all loads of a pass are issued before the first add, so a
-  // thread has up to 4 x (world + 1) loads in flight instead of one (the kernel is latency bound)
-  constexpr int U = 4;
   const int64_t total = (int64_t)nrows * vec, stride = (int64_t)gridDim.x * 256;
   for (int64_t i0 = (int64_t)blockIdx.x * 256 + threadIdx.x; i0 < total; i0 += stride * U) {
-    uint4 part[U][kTpMaxWorld], res[U];
+    uint4 part[U][WORLD_MAX], res[U];
 #pragma unroll
     for (int u = 0; u < U; ++u) {
       const int64_t i = i0 + u * stride;
       if (i >= total) break;
       const int lr = (int)(i / vec), c = (int)(i % vec) * 8;
 #pragma unroll
-      for (int r = 0; r < kTpMaxWorld; ++r)
-        if (r < world) part[u][r] = __ldcg(reinterpret_cast<const uint4*>(in + ((int64_t)r * rpr + lr) * W + c));
+      for (int r = 0; r < WORLD_MAX; ++r)
+        if (r < world) part[u][r] = __ldcg(reinterpret_cast<const uint4*>(d->inbox[r] + (int64_t)(row0 + lr) * W + c));
       if (residual) res[u] = *reinterpret_cast<const uint4*>(residual + (int64_t)(row0 + lr) * ldr + c);
     }
 #pragma unroll
@@ -68,7 +67,7 @@ __global__ void __launch_bounds__(256) tp_pf_reduce_gather_kernel(const TpPfDev*
       const int lr = (int)(i / vec), c = (int)(i % vec) * 8;
       float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int r = 0; r < kTpMaxWorld; ++r) {
+      for (int r = 0; r < WORLD_MAX; ++r) {
         if (r < world) {
           float f[8];
           bf16x8_to_float(part[u][r], f);
@@ -271,9 +270,16 @@ CB_EXPORT int cb_tp_pf_scatter(const void* desc, const void* src, int64_t lds, i
 // Second half of the prefill all-reduce; the result is in this rank's result buffer once
 // cb_tp_pf_wait (launched right after) has returned.
 CB_EXPORT int cb_tp_pf_reduce_gather(const void* desc, const void* residual, int64_t ldr, int64_t T, int64_t seq,
-                                     void* stream) {
+                                     int64_t world, void* stream) {
   if (!desc || T < 1 || (residual && ldr % 8)) return CB_ERR_ARG;
-  return (int)cb_launch(tp_pf_reduce_gather_kernel, dim3(148), dim3(256), 0, (cudaStream_t)stream,
+  if (world < 1 || world > kTpMaxWorld) return CB_ERR_ARG;      // the descriptor itself lives in device memory
+  if (world <= 2)
+    return (int)cb_launch(tp_pf_reduce_gather_kernel<2, 8>, dim3(148), dim3(256), 0, (cudaStream_t)stream,
+                          (const TpPfDev*)desc, (const bf16*)residual, ldr, (int)T, (unsigned)seq);
+  if (world <= 4)
+    return (int)cb_launch(tp_pf_reduce_gather_kernel<4, 6>, dim3(148), dim3(256), 0, (cudaStream_t)stream,
+                          (const TpPfDev*)desc, (const bf16*)residual, ldr, (int)T, (unsigned)seq);
+  return (int)cb_launch(tp_pf_reduce_gather_kernel<kTpMaxWorld, 4>, dim3(148), dim3(256), 0, (cudaStream_t)stream,
                         (const TpPfDev*)desc, (const bf16*)residual, ldr, (int)T, (unsigned)seq);
 }
 CB_EXPORT int cb_tp_pf_wait(const void* desc, int64_t seq, void* stream) {

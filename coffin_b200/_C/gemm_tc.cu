@@ -32,8 +32,8 @@ struct GemmArgs {
   int M, N, K;
   int m_tiles, n_tiles, k_blocks;
   int* status;                     // device status word: set to a non-zero code if a wait ran out
-  // tensor-parallel prefill: instead of C, every output row goes (bf16) to the inbox of the rank
-  // that owns it, and the last CTA publishes the sequence number (see tp.cuh)
+  // tensor-parallel prefill: instead of C, every output row goes (bf16) into this rank's own peer-visible
+  // buffer, from which the rank that owns the row pulls it; the last CTA publishes the sequence number (tp.cuh)
   const TpPfDev* pf; unsigned pf_seq;
   // grouped (expert-major) mode: the m-tile list lives in device memory, written by the dispatch
   // kernel of the same step.  Tile i covers rows [g_row0[i], g_row0[i] + g_rows[i]) of A and C and
@@ -256,7 +256,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           bf16* cp;
           if (a.pf) {
             const int rpr = a.pf->rows_per_rank;
-            cp = a.pf->inbox[row / rpr] + ((int64_t)a.pf->rank * rpr + row % rpr) * a.pf->width + col0;
+            cp = a.pf->inbox[a.pf->rank] + (int64_t)row * a.pf->width + col0;      // stays at home: the owner pulls it
           } else {
             cp = reinterpret_cast<bf16*>(a.C) + (int64_t)row * a.ldc + col0;
           }

@@ -34,7 +34,7 @@ struct PairArgs {
   int M, N, K;
   int m_tiles, n_tiles, k_blocks;  // m_tiles counts 256-row tiles
   int* status;
-  const TpPfDev* pf; unsigned pf_seq;   // tensor-parallel prefill: rows go to their owner's inbox (tp.cuh)
+  const TpPfDev* pf; unsigned pf_seq;   // tensor-parallel prefill: rows go to this rank's peer-visible buffer (tp.cuh)
   int up_off;                      // SwiGLU form: W is [gate rows | up rows], the up rows start here; N counts outputs
 };
 
@@ -235,7 +235,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             bf16* cp;
             if (a.pf) {
               const int rpr = a.pf->rows_per_rank;
-              cp = a.pf->inbox[row / rpr] + ((int64_t)a.pf->rank * rpr + row % rpr) * a.pf->width + col0;
+              cp = a.pf->inbox[a.pf->rank] + (int64_t)row * a.pf->width + col0;      // stays at home: the owner pulls it
             } else {
               cp = a.C + (int64_t)row * a.ldc + col0;
             }

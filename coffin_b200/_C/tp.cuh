@@ -173,9 +173,10 @@ struct TpPfDev {
   int rank, world;
   int rows_per_rank;          // rows of one slice = ceil(max chunk rows / world)
   int width;                  // row width in elements (hidden size)
-  bf16* inbox[kTpMaxWorld];       // rank p's inbox:  [source rank][rows_per_rank][width]
+  bf16* inbox[kTpMaxWorld];       // rank p's partial rows, all of them: [world * rows_per_rank][width]; row r is
+                                  // pulled by its owner, rank r / rows_per_rank
   bf16* out[kTpMaxWorld];         // rank p's result: [world * rows_per_rank][width]
-  unsigned* flags1[kTpMaxWorld];  // rank p's flags: [source rank] partial slices have landed
+  unsigned* flags1[kTpMaxWorld];  // rank p's flags: [source rank] that rank's partial rows are complete
   unsigned* flags2[kTpMaxWorld];  // rank p's flags: [source rank] reduced rows have landed
   unsigned* arrive;               // local: [2] CTA arrival counters (scatter, gather)
   int* status;

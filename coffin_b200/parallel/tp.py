@@ -290,19 +290,21 @@ class TpComm:
         return 0
 
     def scatter(self, src: torch.Tensor) -> None:
-        """First half for a producer that is not a GEMM: send the rows of ``src [T, hidden]`` (bf16) to their owners."""
+        """First half for a producer that is not a GEMM: copy the rows of ``src [T, hidden]`` (bf16) into this
+        rank's peer-visible buffer and tell every rank that they are there (the owners pull them)."""
         from ..ops import kernels as K
         T = src.shape[0]
         K.call("tp_pf_scatter", self.pf_desc_ptr(), src, src.stride(0), T, self.next_seq(T, src.shape[1]))
         K._count()
 
     def finish_reduce(self, residual: torch.Tensor | None = None) -> torch.Tensor:
-        """Second half: add the partial slices this rank owns (+ ``residual`` rows), send the sums to
-        every rank and wait for everyone's.  Returns the reduced ``[T, hidden]`` rows (a view of the
+        """Second half: pull the partial rows this rank owns from every rank (coalesced peer loads), add them
+        (+ ``residual`` rows), send the sums to every rank and wait for everyone's.  Returns the reduced ``[T, hidden]`` rows (a view of the
         result buffer, valid until the next all-reduce)."""
         from ..ops import kernels as K
         T, seq = self._pf_T, 0
-        K.call("tp_pf_reduce_gather", self.pf_desc_ptr(), residual, residual.stride(0) if residual is not None else 0, T, seq)
+        K.call("tp_pf_reduce_gather", self.pf_desc_ptr(), residual, residual.stride(0) if residual is not None else 0, T, seq,
+               self.world)
         K.call("tp_pf_wait", self.pf_desc_ptr(), seq)
         K._count(2)
         return self.pf_out[:T]
