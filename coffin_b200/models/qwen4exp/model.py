@@ -38,7 +38,7 @@ from ...oracle import ops as O
 from ..qwen35.model import QW, QW4
 from ..qwen35.moe import MoEWeights
 from .config import INDEXED, LINEAR, Qwen4Config
-from .ngram import NGramHasher, NGramTable
+from .ngram import NGramHasher, NGramTable, ShardedNGramTable
 
 LM = "model.language_model."
 BUCKETS = (1, 2, 4, 8)
@@ -216,7 +216,11 @@ class Qwen4ExpModel:
                 q = p + "ple."
                 P = _Layer()
                 P.hasher = NGramHasher(c, j)
-                P.table = NGramTable(sd[q + "ple_embedding.ngram_embedding.weight"].to(bf), dev, ngram_device_budget)
+                tw = sd[q + "ple_embedding.ngram_embedding.weight"]
+                if isinstance(tw, list):                # the checkpoint's row shards as mapped host views
+                    P.table = ShardedNGramTable(list(tw), dev, ngram_device_budget, keep=getattr(tw, "keep", None))
+                else:
+                    P.table = NGramTable(tw.to(bf), dev, ngram_device_budget)
                 P.key_w = w(q + "key_proj.weight").float()
                 P.val_w = w(q + "value_proj.weight").float()
                 P.g_key, P.g_query, P.g_conv = gain(q + "norm_key.weight"), gain(q + "norm_query.weight"), gain(q + "norm_conv.weight")

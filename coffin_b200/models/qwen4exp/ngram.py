@@ -146,12 +146,16 @@ class NGramTable:
         if self._stage is None or self._stage.shape[0] < n:
             self._stage = torch.empty(max(n, 4096), self.width, dtype=self.weight.dtype).pin_memory()
         stage = self._stage[:n]
-        torch.index_select(self.weight, 0, flat, out=stage)
+        self._fill(flat, stage)
         with torch.cuda.stream(self._stream):
             dev = stage.to(self.device, non_blocking=True)
             ev = torch.cuda.Event()
             ev.record(self._stream)
         self._pending = (ids.clone(), dev, ev)
+
+    def _fill(self, flat: torch.Tensor, out: torch.Tensor) -> None:
+        """Rows ``flat`` (host int64) of the host table into ``out [n, width]`` (pinned)."""
+        torch.index_select(self.weight, 0, flat, out=out)
 
     def take(self, ids: torch.Tensor) -> torch.Tensor:
         if self._pending is None:
@@ -164,3 +168,82 @@ class NGramTable:
             return self.gather(ids)
         torch.cuda.current_stream().wait_event(ev)
         return dev.reshape(ids.shape[0], -1)
+
+
+class ShardedNGramTable(NGramTable):
+    """The table as the checkpoint stores it: equally sized shards ``...ngram_embedding.shard_{k}.weight``
+    (128 x [2500012, 160] bf16 = 102 GB for the published geometry), kept as the VIEWS the loader hands over
+    (file mappings of the safetensors shards) instead of one concatenated tensor - a copy would double the
+    host footprint and cost a 100 GB pass at start-up for a table of which a step reads a few dozen rows.
+    Row ``r`` lives in shard ``r // rows_per_shard`` at ``r % rows_per_shard``; a gather groups its ids by
+    shard (one ``index_select`` per touched shard) and puts the rows back in request order.  Shards of unequal
+    height would shift every later row and still look well-formed, so they are refused
+    (reference: ``models/qwen4exp/ngram.py:363-470``).  ``keep``: whatever keeps the mappings alive."""
+
+    def __init__(self, shards: list[torch.Tensor], device, device_budget_bytes: int = 120 << 30, keep=None) -> None:
+        if not shards:
+            raise ValueError("the sharded n-gram table needs at least one shard")
+        first = shards[0]
+        for k, t in enumerate(shards):
+            if t.dim() != 2 or t.shape != first.shape or t.dtype != first.dtype:
+                raise ValueError(f"n-gram shard {k} is {tuple(t.shape)}/{t.dtype}, shard 0 is {tuple(first.shape)}/{first.dtype}: "
+                                 "unequal shards would shift the row mapping")
+            if t.device.type != "cpu":
+                raise ValueError(f"n-gram shard {k} is on {t.device}; the sharded table is the host-resident form")
+        self.device = torch.device(device)
+        self.rows_per_shard, self.width = int(first.shape[0]), int(first.shape[1])
+        self.rows = self.rows_per_shard * len(shards)
+        self.keep = keep
+        nbytes = self.rows * self.width * first.element_size()
+        self.on_device = self.device.type == "cuda" and nbytes <= device_budget_bytes
+        if self.on_device:                      # small enough for HBM: one device tensor, filled shard by shard
+            self.weight = torch.empty(self.rows, self.width, dtype=first.dtype, device=self.device)
+            for k, t in enumerate(shards):
+                self.weight[k * self.rows_per_shard:(k + 1) * self.rows_per_shard].copy_(t)
+            self.shards = []
+        else:
+            self.shards = list(shards)
+            self.weight = first                 # dtype / width holder for the staging buffer
+            if self.device.type == "cuda":
+                self._stream = torch.cuda.Stream(device=self.device)
+            self._stage = None
+        self._pending = None
+
+    def gather(self, ids: torch.Tensor) -> torch.Tensor:
+        if self.on_device or self.device.type == "cuda":
+            return super().gather(ids)
+        if int(ids.min()) < 0 or int(ids.max()) >= self.rows:
+            raise ValueError(f"n-gram row ids outside [0, {self.rows})")
+        out = torch.empty(ids.numel(), self.width, dtype=self.weight.dtype)
+        self._fill(ids.reshape(-1), out)
+        return out.reshape(ids.shape[0], -1)
+
+    def prefetch(self, ids: torch.Tensor) -> None:
+        if self.device.type != "cuda":          # nothing to overlap with on the host: the gather happens in take()
+            self._pending = (ids.clone(), None, None)
+            return
+        super().prefetch(ids)
+
+    def _fill(self, flat: torch.Tensor, out: torch.Tensor) -> None:
+        if flat.numel() == 0:
+            return
+        flat = flat.to("cpu")
+        shard_of = torch.div(flat, self.rows_per_shard, rounding_mode="floor")
+        order = torch.argsort(shard_of, stable=True)
+        local = (flat - shard_of * self.rows_per_shard)[order]          # grouped by shard, request order inside a group
+        bounds = torch.cumsum(torch.bincount(shard_of, minlength=len(self.shards)), 0).tolist()
+        grouped = torch.empty_like(out)
+        start = 0
+        for k, stop in enumerate(bounds):
+            if stop > start:
+                torch.index_select(self.shards[k], 0, local[start:stop], out=grouped[start:stop])
+                start = stop
+        out.index_copy_(0, order, grouped)
+
+    def close(self) -> None:
+        """Drop the shard views and whatever kept their mappings alive; the table cannot be read afterwards."""
+        self.shards = []
+        closer = getattr(self.keep, "close", None)
+        if closer is not None:
+            closer()
+        self.keep = None

@@ -163,7 +163,7 @@ class Qwen4State:
 class Qwen4Oracle:
     def __init__(self, cfg: Qwen4Config, sd: dict[str, torch.Tensor]) -> None:
         self.cfg = cfg
-        self.p = {k: (v.float() if v.is_floating_point() else v) for k, v in sd.items()}
+        self.p = {k: (v.float() if isinstance(v, torch.Tensor) and v.is_floating_point() else v) for k, v in sd.items()}
         self.hashers = {li: NGramHasher(cfg, cfg.ple_index(li)) for li in range(cfg.num_hidden_layers)
                         if cfg.ple_index(li) is not None}
         self.last_selected: dict[int, torch.Tensor] = {}
@@ -190,7 +190,12 @@ class Qwen4Oracle:
         hc, H = c.hc_count, c.hidden_size
         ctx = st.ple_ctx.get(li) or [c.eos_token_id] * c.ple_context_len
         ids = self.hashers[li].ids(tokens.tolist(), ctx)                         # [T, heads]
-        emb = p[q + "ple_embedding.ngram_embedding.weight"][ids].flatten(1)      # [T, E]
+        tw = p[q + "ple_embedding.ngram_embedding.weight"]
+        if isinstance(tw, list):                 # row shards of a real checkpoint (mapped host views)
+            from .ngram import ShardedNGramTable
+            emb = ShardedNGramTable(list(tw), "cpu").gather(ids).float()
+        else:
+            emb = tw[ids].flatten(1)             # [T, E]
         key = grouped_rms_norm(emb @ p[q + "key_proj.weight"].t(), p[q + "norm_key.weight"], H, c.rms_norm_eps)
         val = emb @ p[q + "value_proj.weight"].t()                               # [T, H]
         qry = grouped_rms_norm(x, p[q + "norm_query.weight"], H, c.rms_norm_eps)

@@ -186,6 +186,41 @@ def checkpoint_index(model_dir) -> dict[str, str]:
     return out
 
 
+NGRAM_SHARD = __import__("re").compile(r"^(.*\.ngram_embedding)\.shard_(\d+)\.weight$")
+
+
+class ShardList(list):
+    """Equally sized row shards of one table, in order, as host views (see ``ngram.ShardedNGramTable``);
+    ``keep`` holds the file mappings behind them."""
+    keep = None
+
+    @property
+    def shape(self) -> tuple:
+        return (sum(int(t.shape[0]) for t in self), int(self[0].shape[1])) if self else (0, 0)
+
+
+def open_mapped(path, names: list[str]) -> tuple[list[torch.Tensor], object]:
+    """Tensors ``names`` of one safetensors file as VIEWS of a private file mapping (no copy into anonymous
+    memory: the pages come and go with the page cache).  Returns ``(views, mapping)``; the views are valid
+    while ``mapping`` is alive."""
+    import json
+    import os
+    import struct
+    dt = {"BF16": torch.bfloat16, "F16": torch.float16, "F32": torch.float32, "I8": torch.int8, "U8": torch.uint8,
+          "I32": torch.int32, "I64": torch.int64}
+    size = os.path.getsize(path)
+    with open(path, "rb") as f:
+        hlen = struct.unpack("<Q", f.read(8))[0]
+        header = json.loads(f.read(hlen))
+    buf = torch.from_file(str(path), shared=False, size=size, dtype=torch.uint8)
+    views = []
+    for n in names:
+        e = header[n]
+        a, b = e["data_offsets"]
+        views.append(buf[8 + hlen + a:8 + hlen + b].view(dt[e["dtype"]]).reshape(e["shape"]))
+    return views, buf
+
+
 def verify_plan(cfg: Qwen4Config, model_dir, index: dict[str, str] | None = None) -> dict:
     """Compare the checkpoint's headers with ``tensor_plan(cfg)`` without reading tensor data.  Returns
     ``{"missing": [...], "unexpected": [...], "shape": [(key, found, wanted), ...]}``; per-expert spellings
@@ -201,6 +236,18 @@ def verify_plan(cfg: Qwen4Config, model_dir, index: dict[str, str] | None = None
         with safe_open(str(Path(model_dir) / fname), framework="pt") as fh:
             for k in fh.keys():
                 shapes[k] = tuple(fh.get_slice(k).get_shape())
+    # a table stored as shard_0 .. shard_{n-1}: equal shards count as one [n * rows, width] tensor
+    tables: dict[str, dict[int, tuple]] = {}
+    for k in list(shapes):
+        m = NGRAM_SHARD.match(k)
+        if m:
+            tables.setdefault(m.group(1), {})[int(m.group(2))] = shapes.pop(k)
+    for prefix, parts in tables.items():
+        ks = sorted(parts)
+        if ks == list(range(len(ks))) and len(set(parts.values())) == 1 and len(parts[0]) == 2:
+            shapes[prefix + ".weight"] = (len(ks) * parts[0][0], parts[0][1])
+        else:
+            shapes[prefix + ".weight"] = ("shards", tuple(ks), tuple(sorted(set(parts.values()))))   # reported as a shape mismatch
     per_expert = re.compile(r"^(.*\.mlp\.experts\.)(\d+)\.(gate_proj|up_proj|down_proj)\.weight$")
     fused_seen: dict[str, set] = {}
     for k in list(shapes):
@@ -222,11 +269,23 @@ def verify_plan(cfg: Qwen4Config, model_dir, index: dict[str, str] | None = None
     return {"missing": missing, "unexpected": unexpected, "shape": bad}
 
 
+def first_layers(cfg: Qwen4Config, n: int) -> Qwen4Config:
+    """Geometry of the first ``n`` layers as a model of its own (PLE layers keep their rank, which the n-gram
+    hashing depends on)."""
+    import dataclasses
+    if n >= cfg.num_hidden_layers:
+        return cfg
+    return dataclasses.replace(cfg, num_hidden_layers=n, layer_types=cfg.layer_types[:n],
+                               ple_layer_ids=tuple(i for i in cfg.ple_layer_ids if i <= n))
+
+
 def load_streaming(model_dir, cfg: Qwen4Config | None = None, device: str = "cpu", ep: tuple[int, int] | None = None,
-                   strict: bool = True) -> dict[str, torch.Tensor]:
+                   strict: bool = True, layers: int | None = None) -> dict[str, torch.Tensor]:
     """State dict of a Qwen4-exp checkpoint read shard by shard.  ``ep=(rank, world)``: only this rank's
     contiguous expert range of every routed stack is read (and the dict is marked ``__ep_shard__``); all
-    other tensors are read whole.  ``strict``: refuse a checkpoint whose headers do not match the plan."""
+    other tensors are read whole.  ``strict``: refuse a checkpoint whose headers do not match the plan.
+    ``layers``: read only the first ``layers`` decoder layers (a staged check of a checkpoint too large to
+    load whole; pair it with ``first_layers(cfg, layers)``)."""
     from pathlib import Path
 
     from safetensors import safe_open
@@ -254,10 +313,20 @@ def load_streaming(model_dir, cfg: Qwen4Config | None = None, device: str = "cpu
         by_file.setdefault(f, []).append(k)
     import re
     per_expert = re.compile(r"\.mlp\.experts\.(\d+)\.")
+    table_shards: dict[str, dict[int, tuple[str, str]]] = {}
+    layer_no = re.compile(re.escape(LM) + r"layers\.(\d+)\.")
     for fname in sorted(by_file):
         with safe_open(str(d / fname), framework="pt", device=device) as fh:
             for k in by_file[fname]:
                 if not k.startswith((LM, "lm_head.", "mtp.", "model.visual.")):
+                    continue
+                if layers is not None:
+                    ml = layer_no.match(k)
+                    if (ml and int(ml.group(1)) >= layers) or k.startswith(("mtp.", "model.visual.")):
+                        continue
+                ms = NGRAM_SHARD.match(k)
+                if ms:                                          # mapped after the loop, never copied
+                    table_shards.setdefault(ms.group(1), {})[int(ms.group(2))] = (fname, k)
                     continue
                 if k.endswith(("experts.gate_up_proj", "experts.down_proj")) and (lo, hi) != (0, E):
                     sd[k] = fh.get_slice(k)[lo:hi]
@@ -274,6 +343,23 @@ def load_streaming(model_dir, cfg: Qwen4Config | None = None, device: str = "cpu
             ren[k[:m.start(1)] + str(int(m.group(1)) - lo) + k[m.end(1):] if m else k] = v
         sd = ren
     sd = fuse_experts(sd)
+    for prefix, parts in table_shards.items():
+        ks = sorted(parts)
+        if ks != list(range(len(ks))):
+            raise ValueError(f"{prefix}: shards {ks[:4]}.. are not 0..{len(ks) - 1}; a missing shard would shift every later row")
+        lst, keep = ShardList(), []
+        by_f: dict[str, list[tuple[int, str]]] = {}
+        for k in ks:
+            by_f.setdefault(parts[k][0], []).append((k, parts[k][1]))
+        got: dict[int, torch.Tensor] = {}
+        for fname, items in by_f.items():
+            views, mapping = open_mapped(d / fname, [name for _, name in items])
+            keep.append(mapping)
+            for (k, _), v in zip(items, views):
+                got[k] = v
+        lst.extend(got[k] for k in ks)
+        lst.keep = keep
+        sd[prefix + ".weight"] = lst
     if (lo, hi) != (0, E):
         sd["__ep_shard__"] = (ep[0], ep[1])
     return sd
