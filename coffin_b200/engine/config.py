@@ -24,6 +24,9 @@ class EngineConfig:
     spec_k: int = 0                    # default speculative draft length of greedy requests (0 = off; a request's own spec_k overrides)
     spec_batch: bool = False           # speculate also when several rows decode together (one verify pass over all rows)
     spec_min_ctx: int = 0              # rows shorter than this many tokens do not draft yet
+    spec_sparse_k: int = 0             # approximate batched verify over the k best history blocks per row: accepted
+                                       # as an option for parity with the reference, where it is also refused when
+                                       # > 0 (no masked multi-query verify kernel, models/qwen35/model.py:1390-1401)
     group_prefill: bool = True         # chunks of several sequences share one forward (stacked rows)
     chunk: int = 2048                  # largest prefill chunk handed to the model
     prefill_quantum: int = 2048        # tokens of one sequence prefilled per engine step

@@ -33,6 +33,9 @@ class StepOutput:
 class LLMEngine:
     def __init__(self, model, cfg: EngineConfig | None = None, bm: BlockManager | None = None) -> None:
         self.cfg = cfg or EngineConfig()
+        if self.cfg.spec_sparse_k > 0:
+            raise NotImplementedError("spec_sparse_k > 0 (batched verify over the k best history blocks of a row) needs a "
+                                      "masked multi-query verify kernel that does not exist; pass spec_sparse_k=0")
         self.model = model
         slots = getattr(model, "num_slots", self.cfg.max_num_seqs)
         # a model may carry fewer rows per step than the configuration asks for (state slots, or the

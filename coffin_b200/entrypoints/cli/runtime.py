@@ -38,6 +38,7 @@ def parser() -> argparse.ArgumentParser:
     ap.add_argument("--snapshot-interval", type=int, default=None)
     ap.add_argument("--spec-k", type=int, default=None)
     ap.add_argument("--spec-batch", action="store_true")
+    ap.add_argument("--spec-sparse-k", type=int, default=0, help="approximate batched verify over the k best history blocks (refused when > 0: not built)")
     ap.add_argument("--chunk", type=int, default=None)
     ap.add_argument("--prefill-quantum", type=int, default=None)
     ap.add_argument("--max-num-seqs", type=int, default=None)
@@ -60,7 +61,7 @@ def engine_config(args):
     return EngineConfig.from_env(
         max_seq=args.max_seq, quant=args.quant, kv_dtype=args.kv_dtype, prefix_cache=False if args.no_prefix_cache else None,
         num_blocks=args.num_blocks, snapshots=args.snapshots, snapshot_interval=args.snapshot_interval,
-        spec_k=args.spec_k, spec_batch=True if args.spec_batch else None, chunk=args.chunk,
+        spec_k=args.spec_k, spec_batch=True if args.spec_batch else None, spec_sparse_k=args.spec_sparse_k or None, chunk=args.chunk,
         prefill_quantum=args.prefill_quantum, max_num_seqs=args.max_num_seqs,
         max_num_batched_tokens=args.max_num_batched_tokens, max_seconds=args.max_seconds,
         graph=False if args.no_graph else None, vision=False if args.no_vision else None)

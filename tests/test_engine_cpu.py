@@ -163,3 +163,12 @@ def test_block_alias_check_catches_a_shared_write_block():
     tb[b.num_computed // 64] = saved
     while not (a.finished and b.finished):
         eng.step()
+
+
+def test_sparse_verify_option_is_refused_like_in_the_reference():
+    import pytest
+    from coffin_b200.engine.config import EngineConfig
+    from coffin_b200.engine.llm_engine import LLMEngine
+    assert EngineConfig().spec_sparse_k == 0
+    with pytest.raises(NotImplementedError, match="spec_sparse_k"):
+        LLMEngine(object(), EngineConfig(spec_sparse_k=4))
