@@ -51,6 +51,27 @@ class _Ticket:
     t_submit: float
 
 
+SPEC_BATCH_MIN_FREE = int(1.5 * 2 ** 30)
+
+
+def free_bytes(device) -> int:
+    """Free device memory in bytes, or -1 when the device has no such notion (the CPU twin)."""
+    dev = torch.device(device)
+    if dev.type != "cuda" or not torch.cuda.is_available():
+        return -1
+    return int(torch.cuda.mem_get_info(dev)[0])
+
+
+def guard_spec_batch(cfg: EngineConfig, free: int) -> EngineConfig:
+    """Batched speculation keeps roll-back snapshots and the drafter's rows next to the weights; with less
+    than 1.5 GiB free it is switched off (with a line on the log) rather than left to run out of memory in the
+    middle of a step (reference: ``serving/runtime_service.py:186-198``)."""
+    if cfg.spec_batch and 0 <= free < SPEC_BATCH_MIN_FREE:
+        print(f"[serve] spec_batch disabled: only {free / 2 ** 30:.2f} GiB free (batched speculation needs ~1.5 GiB)", flush=True)
+        return dataclasses.replace(cfg, spec_batch=False)
+    return cfg
+
+
 class Server:
     def __init__(self, model, cfg: EngineConfig | None = None, tokenizer=None, model_path: str = "",
                  model_name: str = "", builder: Callable[[], Any] | None = None) -> None:
@@ -64,6 +85,7 @@ class Server:
         self.model_name = model_name or Path(model_path or self.model_cfg.name).name
         self.builder = builder
         t0 = time.time()
+        self.cfg = guard_spec_batch(self.cfg, free_bytes(getattr(model, "device", "cpu")))
         self.engine = LLMEngine(model, self.cfg)
         self.warmup_s = round(self.engine.warmup(), 3) if self.cfg.warmup else 0.0
         self.build_s = round(time.time() - t0, 3)

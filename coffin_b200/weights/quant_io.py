@@ -26,6 +26,8 @@ from .quant import GROUP, QWeight, W4A8Weight, is_quantizable
 INDEX_NAME = "quant_index.json"
 FORMAT = "coffin-int8-kn-v1"
 W4A8_FORMAT = "coffin-w4a8-kn-v1"
+# top level of a tree of per-rank directories (tools/quant_disk_qwen4.py --layout): a manifest, not loadable weights
+MANIFEST_FORMAT = "coffin-qwen4-w4a8-manifest-v1"
 DENSE_SUFFIXES = ("mlp.gate.weight", "shared_expert_gate.weight")
 
 
@@ -35,6 +37,10 @@ def is_quantized_dir(model_dir: str | Path) -> bool:
 
 def read_index(model_dir: str | Path) -> dict:
     idx = json.loads((Path(model_dir) / INDEX_NAME).read_text())
+    if idx.get("format") == MANIFEST_FORMAT:
+        dirs = {lay: sorted(per.values()) for lay, per in idx.get("rank_dirs", {}).items()}
+        raise ValueError(f"{model_dir}: this is the manifest of a per-rank tree, not a loadable directory; "
+                         f"load one of its rank directories: {dirs}")
     if idx.get("format") not in (FORMAT, W4A8_FORMAT):
         raise ValueError(f"{model_dir}: unknown quantised format {idx.get('format')!r}")
     return idx
@@ -254,6 +260,8 @@ def load_quantized(model_dir: str | Path, device: str = "cpu", quant: bool = Tru
             sd[key] = q if quant else q.dequant(dense_dtype)
         else:
             raise ValueError(f"{dk}: unknown kind {kind!r}")
+    if index.get("ep_shard"):          # a per-rank directory: the routed stacks already hold this rank's experts only
+        sd["__ep_shard__"] = tuple(int(x) for x in index["ep_shard"])
     return sd
 
 

@@ -217,3 +217,53 @@ def test_lazy_random_state_dict_draws_the_same_tensors_one_at_a_time():
     assert set(lazy.keys()) == set(full) and "lm_head.weight" in lazy and "nope" not in lazy
     assert lazy.get("nope", 7) == 7
     assert all(torch.equal(full[k], lazy[k]) for k in full)
+
+
+def test_qwen4_quantiser_writes_per_rank_trees_with_manifest_and_resumes(tmp_path, capsys):
+    """``--layout ep2``: one loadable directory per expert-parallel rank holding only that rank's experts, a
+    manifest at the top (not loadable, says so), progress after every rank directory; a second run finds the
+    finished directories and writes nothing again, a run that lost one directory rewrites just that one."""
+    import json
+    import shutil
+
+    import pytest
+    from coffin_b200.models.qwen4exp.config import tiny_qwen4
+    from coffin_b200.models.qwen4exp.weights import random_state_dict
+    from coffin_b200.tools.quant_disk_qwen4 import PROGRESS_NAME, main as quantise
+    from coffin_b200.weights.init import save_checkpoint
+    from coffin_b200.weights.quant import W4A8Weight
+    from coffin_b200.weights.quant_io import MANIFEST_FORMAT, load_quantized, read_index
+    cfg = tiny_qwen4()
+    sd = random_state_dict(cfg, 0)
+    src = save_checkpoint(cfg, sd, tmp_path / "src", split_experts=True, shard_bytes=1 << 20)
+    out = tmp_path / "tree"
+    assert quantise(["--model", str(src), "--out", str(out), "--scheme", "w4a8", "--layout", "ep2", "--verify"]) == 0
+    rep = json.loads(capsys.readouterr().out)
+    assert rep["format"] == MANIFEST_FORMAT and rep["resumed_units"] == [] and rep["worst_relative_error"] < 0.2
+    man = json.loads((out / "quant_index.json").read_text())
+    assert man["complete"] and man["world"] == {"ep2": 2} and sorted(man["rank_dirs"]["ep2"]) == ["0", "1"]
+    with pytest.raises(ValueError, match="manifest of a per-rank tree"):
+        read_index(out)
+    E = cfg.num_experts
+    for r in range(2):
+        back = load_quantized(out / man["rank_dirs"]["ep2"][str(r)])
+        assert back["__ep_shard__"] == (r, 2)
+        stacks = [k for k in back if k.endswith(("experts.gate_up_proj", "experts.down_proj"))]
+        assert stacks and all(isinstance(back[k], W4A8Weight) and back[k].dequant().shape[0] == E // 2 for k in stacks)
+        k0 = stacks[0]
+        ref = sd[k0][r * (E // 2):(r + 1) * (E // 2)]
+        assert (back[k0].dequant() - ref).abs().max() <= 0.2 * ref.abs().max()
+    prog = json.loads((out / PROGRESS_NAME).read_text())
+    assert sorted(prog["done"]) == ["ep2/rank-0", "ep2/rank-1"]
+    # resume: nothing is rewritten
+    stamp = (out / "ep2" / "rank-0" / "quant_index.json").stat().st_mtime_ns
+    assert quantise(["--model", str(src), "--out", str(out), "--scheme", "w4a8", "--layout", "ep2"]) == 0
+    assert json.loads(capsys.readouterr().out)["resumed_units"] == ["ep2/rank-0", "ep2/rank-1"]
+    assert (out / "ep2" / "rank-0" / "quant_index.json").stat().st_mtime_ns == stamp
+    # a lost rank directory is rewritten, the other one is kept
+    shutil.rmtree(out / "ep2" / "rank-1")
+    assert quantise(["--model", str(src), "--out", str(out), "--scheme", "w4a8", "--layout", "ep2"]) == 0
+    assert json.loads(capsys.readouterr().out)["resumed_units"] == ["ep2/rank-0"]
+    assert load_quantized(out / "ep2" / "rank-1")["__ep_shard__"] == (1, 2)
+    with pytest.raises(ValueError, match="only expert-parallel trees"):
+        quantise(["--model", str(src), "--out", str(tmp_path / "t2"), "--layout", "tp4"])

@@ -172,3 +172,15 @@ def test_serving_load_generator_end_to_end(capsys):
     assert rep["output_tokens_total"] == 36
     assert rep["ttft_ms"]["p50"] is not None and rep["tpot_ms"]["p50"] is not None
     assert rep["cached_prompt_tokens_p50"] >= 32
+
+
+def test_batched_speculation_is_switched_off_when_memory_is_short(capsys):
+    from coffin_b200.engine.config import EngineConfig
+    from coffin_b200.serving.runtime import SPEC_BATCH_MIN_FREE, free_bytes, guard_spec_batch
+    on = EngineConfig(spec_k=4, spec_batch=True)
+    assert guard_spec_batch(on, SPEC_BATCH_MIN_FREE).spec_batch
+    assert guard_spec_batch(on, -1).spec_batch                      # no memory figure (CPU twin): left alone
+    off = guard_spec_batch(on, SPEC_BATCH_MIN_FREE - 1)
+    assert not off.spec_batch and off.spec_k == 4
+    assert "spec_batch disabled" in capsys.readouterr().out
+    assert free_bytes("cpu") == -1
