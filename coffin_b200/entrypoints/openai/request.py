@@ -47,40 +47,63 @@ def decode_data_url(url: str, max_bytes: int) -> dict:
 
 def split_messages(messages: list[dict], max_images: int, max_image_bytes: int, max_total_bytes: int
                    ) -> tuple[list[dict], list[dict]]:
-    """Pull images out of the content parts.  Returns the messages with image parts replaced by
-    ``{"type": "image"}`` placeholders, and the images in prompt order."""
+    """Pull images out of the content parts.  Returns the messages, and the images in prompt order.  A message
+    with at least one image keeps a parts array in which every image is the template's ``{"type": "image"}``
+    marker at its place (text and images stay interleaved as the client wrote them); a parts array of text
+    only is flattened to the plain string it spells, so a text request reaches the template exactly as it would
+    without vision.  User and tool messages may carry images (a screenshot returned by a tool is the common
+    case); a system message may not (the chat template rejects it) and an assistant turn may not (the template
+    never renders media there), each with a message that says where the image belongs
+    (reference: ``entrypoints/openai/request.py:99-229, 232-300``)."""
     out, images, total = [], [], 0
     for m in messages:
         content = m.get("content")
         if not isinstance(content, list):
             out.append(dict(m))
             continue
-        parts = []
+        role = str(m.get("role") or "user").lower()
+        parts, n_img = [], 0
         for p in content:
+            if isinstance(p, str):
+                parts.append({"type": "text", "text": p})
+                continue
             if not isinstance(p, dict):
-                raise RequestError("content parts must be objects", 400)
+                raise RequestError(f"content part must be an object, got {type(p).__name__}", 400)
             t = p.get("type")
-            if t == "text":
-                parts.append({"type": "text", "text": str(p.get("text", ""))})
-            elif t == "image_url":
-                if m.get("role") not in ("user", "system", "developer"):
-                    raise RequestError(f"images are not accepted in {m.get('role')!r} messages", 400)
+            if t in (None, "text"):
+                parts.append({"type": "text", "text": str(p.get("text") or "")})
+            elif t in ("image_url", "image"):
+                if role in ("system", "developer"):
+                    raise RequestError("a system message cannot contain images: the chat template rejects it; "
+                                       "put the image in a user turn", 400)
+                if role == "assistant":
+                    raise RequestError("an assistant message cannot carry images; put the image in a user or tool message", 400)
                 url = p.get("image_url")
                 url = url.get("url") if isinstance(url, dict) else url
-                img = decode_data_url(url, max_image_bytes)
-                total += img["bytes"]
+                if url is None and t == "image":
+                    url = p.get("image")
+                    url = url.get("url") if isinstance(url, dict) else url
+                if url is None:
+                    raise RequestError(f"`{t}` part has no `image_url.url`; send "
+                                       '{"type": "image_url", "image_url": {"url": "data:image/png;base64,..."}}', 400)
                 if len(images) + 1 > max_images:
                     raise RequestError(f"too many images (max {max_images})", 400, "too_many_images")
+                img = decode_data_url(url, max_image_bytes)
+                total += img["bytes"]
                 if total > max_total_bytes:
                     raise RequestError(f"images exceed {max_total_bytes} bytes in total", 413, "images_too_large")
                 images.append({"b64": img["b64"], "mime": img["mime"]})
                 parts.append({"type": "image"})
-            elif t in ("video_url", "video", "input_audio", "audio_url"):
-                raise RequestError(f"content part type {t!r} is not supported", 400, "unsupported_content")
+                n_img += 1
+            elif t in ("video_url", "video", "input_video"):
+                raise RequestError("video input is not supported: frame count -> token count is not bounded by this "
+                                   "build's image limits", 400, "unsupported_content")
+            elif t in ("input_audio", "audio_url"):
+                raise RequestError("audio input is not supported by this model", 400, "unsupported_content")
             else:
                 raise RequestError(f"unknown content part type {t!r}", 400)
         nm = dict(m)
-        nm["content"] = parts
+        nm["content"] = parts if n_img else "".join(x["text"] for x in parts)
         out.append(nm)
     return out, images
 

@@ -254,3 +254,72 @@ def test_images(server):
     # engine-side refusals keep their status on both paths
     assert post(port, {"messages": user("err")})[0] == 413
     assert post(port, {"messages": user("err"), "stream": True})[0] == 413
+
+
+def test_cut_off_reasoning_is_not_passed_off_as_the_answer(server):
+    """A reply that ends inside the thinking block (token limit) has reasoning but no answer: the text must not
+    move into ``content``, and the finish reason says the budget ran out."""
+    eng, port = server
+    eng_script = eng._script
+    eng._script = lambda req: ("", "still thinking about it and never closing", True)
+    try:
+        st, data = post(port, {"messages": user("hi"), "max_tokens": 7})
+        out = json.loads(data)
+        msg = out["choices"][0]["message"]
+        assert st == 200 and not (msg.get("content") or "").strip()
+        assert "still thinking" in (msg.get("reasoning_content") or "")
+        assert out["choices"][0]["finish_reason"] == "length"
+        chunks = sse(post(port, {"messages": user("hi"), "max_tokens": 7, "stream": True})[1])
+        content = "".join(c["choices"][0]["delta"].get("content") or "" for c in chunks if c["choices"])
+        reasoning = "".join(c["choices"][0]["delta"].get("reasoning_content") or "" for c in chunks if c["choices"])
+        assert not content.strip() and "still thinking" in reasoning
+    finally:
+        eng._script = eng_script
+
+
+def test_split_tool_marker_is_held_back_in_the_stream(server):
+    """Five-character engine tokens cut ``<tool_call>`` in two: no content delta may carry a piece of the marker
+    or of the call body, and the accumulated argument fragments parse to the non-stream arguments."""
+    eng, port = server
+    chunks = sse(post(port, {"messages": user("tool"), "tools": TOOLS, "stream": True})[1])
+    content = "".join(c["choices"][0]["delta"].get("content") or "" for c in chunks if c["choices"])
+    assert "<tool" not in content and "function=" not in content and "parameter" not in content
+    frags, name = "", None
+    for c in chunks:
+        for ch in c["choices"]:
+            for tc in ch["delta"].get("tool_calls") or []:
+                name = tc["function"].get("name") or name
+                frags += tc["function"].get("arguments") or ""
+    assert name == "get_weather"
+    whole = json.loads(post(port, {"messages": user("tool"), "tools": TOOLS})[1])["choices"][0]["message"]["tool_calls"][0]
+    assert json.loads(frags) == json.loads(whole["function"]["arguments"]) == {"city": "Beijing", "days": 3}
+
+
+def test_image_roles_order_and_plain_parts(server):
+    eng, port = server
+
+    def img(tag: bytes):
+        return {"type": "image_url", "image_url": {"url": "data:image/png;base64," + base64.b64encode(b"\x89PNG" + tag * 20).decode()}}
+
+    a, b = img(b"a"), img(b"b")
+    # a parts array of text only flattens to a string, as without vision
+    st, _ = post(port, {"messages": [{"role": "user", "content": [{"type": "text", "text": "hel"}, {"type": "text", "text": "lo"}]}]})
+    assert st == 200 and eng.requests[-1]["messages"][0]["content"] == "hello" and not eng.requests[-1].get("images")
+    # two images keep their order, the template sees one marker per image at its place
+    st, _ = post(port, {"messages": [{"role": "user", "content": [a, {"type": "text", "text": "vs"}, b]}]})
+    r = eng.requests[-1]
+    assert st == 200 and [p["type"] for p in r["messages"][0]["content"]] == ["image", "text", "image"]
+    assert [base64.b64decode(i["b64"])[4:5] for i in r["images"]] == [b"a", b"b"]
+    # roles: a tool result may carry an image, a system or assistant message may not
+    st, _ = post(port, {"messages": [{"role": "user", "content": "look"},
+                                     {"role": "assistant", "content": None, "tool_calls": [{"id": "c", "type": "function", "function": {"name": "multiply", "arguments": "{}"}}]},
+                                     {"role": "tool", "tool_call_id": "c", "content": [a]}]})
+    assert st == 200 and len(eng.requests[-1]["images"]) == 1
+    st, data = post(port, {"messages": [{"role": "system", "content": [a]}, {"role": "user", "content": "x"}]})
+    assert st == 400 and "user" in json.loads(data)["error"]["message"]
+    # malformed payloads are 400 with a readable message
+    bad64 = {"type": "image_url", "image_url": {"url": "data:image/png;base64,@@@not-base64@@@"}}
+    st, data = post(port, {"messages": [{"role": "user", "content": [bad64]}]})
+    assert st == 400 and json.loads(data)["error"]["message"]
+    tiff = {"type": "image_url", "image_url": {"url": "data:image/tiff;base64," + base64.b64encode(b"II*\x00").decode()}}
+    assert post(port, {"messages": [{"role": "user", "content": [tiff]}]})[0] == 400
