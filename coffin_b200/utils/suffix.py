@@ -31,7 +31,9 @@ class SuffixDrafter:
                     self._index[tuple(self.history[n - 1 - k:n - 1])] = n - 1
 
     def draft(self, k: int) -> list[int]:
-        """Up to ``k`` proposed next tokens (possibly none)."""
+        """Up to ``k`` proposed next tokens (possibly none; none for ``k <= 0``)."""
+        if k <= 0:
+            return []
         h = self.history
         for m in range(min(self.max_match, len(h)), self.min_match - 1, -1):
             end = self._index.get(tuple(h[-m:]))
