@@ -172,3 +172,37 @@ def test_sparse_verify_option_is_refused_like_in_the_reference():
     assert EngineConfig().spec_sparse_k == 0
     with pytest.raises(NotImplementedError, match="spec_sparse_k"):
         LLMEngine(object(), EngineConfig(spec_sparse_k=4))
+
+
+def test_token_budget_bounds_a_step_and_a_sequence_walks_through_its_states():
+    from coffin_b200.engine.sequence import SequenceStatus
+    eng = engine(chunk=32, prefill_quantum=32, max_num_batched_tokens=64, prefix_cache=False)
+    prompts = [prompt(100, 60 + i) for i in range(3)]
+    seqs = [eng.add_request(p, SamplingParams(max_tokens=3)) for p in prompts]
+    assert all(s.status == SequenceStatus.WAITING for s in seqs)
+    seen = {id(s): [s.status] for s in seqs}
+    for _ in range(200):
+        before = eng.runner.n_prefill_tokens
+        eng.step()
+        assert eng.runner.n_prefill_tokens - before <= 64           # one step never prefills more than the budget
+        for s in seqs:
+            if seen[id(s)][-1] != s.status:
+                seen[id(s)].append(s.status)
+        if all(s.finished for s in seqs):
+            break
+    for p, s in zip(prompts, seqs):
+        assert s.output == solo(p, 3)
+        order = [st for st in seen[id(s)] if st != SequenceStatus.PREEMPTED]
+        assert order[0] == SequenceStatus.WAITING and order[-1] == SequenceStatus.FINISHED
+        assert SequenceStatus.PREFILLING in order and order.index(SequenceStatus.PREFILLING) < len(order) - 1
+        if SequenceStatus.RUNNING in order:
+            assert order.index(SequenceStatus.PREFILLING) < order.index(SequenceStatus.RUNNING)
+
+
+def test_one_shot_engine_without_chunking_serves_a_request():
+    p = prompt(300, 77)
+    for cache, calls in ((False, 1), (True, 2)):      # with the prefix cache the prompt is cut at its last block boundary (a reusable node)
+        eng = engine(chunk=512, prefill_quantum=512, max_num_batched_tokens=512, prefix_cache=cache)
+        before = eng.model.n_prefill_calls
+        s = eng.generate([p], SamplingParams(max_tokens=4))[0]
+        assert s.output == solo(p, 4) and eng.model.n_prefill_calls - before == calls
