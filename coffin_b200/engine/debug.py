@@ -9,9 +9,18 @@ variables read once at import):
 * ``COFFIN_EP_TRACE=1``      accumulated device time of the expert-parallel / prefill all-reduce, printed at exit.
 * ``COFFIN_MOE_CHECK=1``     after every device-side expert dispatch, check on the host that the sorted
   order is a permutation of the routed slots and that the tile list covers exactly the local slots.
+* ``COFFIN_MOE_SHAPE=1``     print every distinct shape the grouped expert projections run at (rows, local
+  experts, output width, depth, storage), once per shape.
+* ``COFFIN_WQ_TRACE=1``      print the shape and the caller's stack whenever a whole int4 expert stack is
+  expanded to bf16 (1.6 GB per layer on the 35B model: the line tells who reached it).
+* ``COFFIN_DEBUG_STEP=1``    every 50th engine step, one line with the scheduler's queues and the free
+  blocks (read in ``engine/llm_engine.py``); the serving loop also prints one line per submitted request.
+* ``COFFIN_PD_TRACE`` / ``COFFIN_PD_VERIFY``  one line per adopted sequence / a read-back comparison of what
+  the adopt wrote (read in ``engine/pd.py``).
 
 Reference switches of the same names: ``engine/model_runner.py:312,438,634,777-827``,
-``engine/prefix_engine.py:131``, ``models/qwen35/ep.py:45-48``, ``models/qwen4exp/moe.py:57-60``.
+``engine/prefix_engine.py:131``, ``models/qwen35/ep.py:45-48``, ``models/qwen4exp/moe.py:57-69``,
+``int8_weights.py:172``, ``engine/llm_engine.py:27-32``, ``serving/runtime_parts.py:1341-1342``.
 """
 from __future__ import annotations
 
@@ -25,6 +34,26 @@ PREFILL_TRACE = _env.get("COFFIN_PREFILL_TRACE") == "1"
 PC_TRACE = bool(_env.get("COFFIN_PC_TRACE"))
 EP_TRACE = _env.get("COFFIN_EP_TRACE", "").strip() == "1"
 MOE_CHECK = bool(_env.get("COFFIN_MOE_CHECK"))
+MOE_SHAPE = bool(_env.get("COFFIN_MOE_SHAPE"))
+WQ_TRACE = _env.get("COFFIN_WQ_TRACE") == "1"
+_shapes_seen: set = set()
+
+
+def moe_shape(tag: str, rows: int, experts: int, n: int, k: int, storage: str) -> bool:
+    """Print a grouped-projection shape the first time it is seen; True when it printed."""
+    key = (tag, rows, experts, n, k, storage)
+    if key in _shapes_seen:
+        return False
+    _shapes_seen.add(key)
+    print(f"[moe-shape] {tag} rows={rows} experts={experts} n={n} k={k} weights={storage}", flush=True)
+    return True
+
+
+def wq_expand(shape: tuple, kept: bool) -> None:
+    """Report a whole-stack int4 -> bf16 expansion with the last frames of the caller's stack."""
+    import traceback
+    print(f"[wq-expand] {tuple(shape)} kept={kept}", flush=True)
+    print("".join(traceback.format_stack()[-6:-1]), flush=True)
 
 
 class BlockAliasError(RuntimeError):

@@ -11,6 +11,7 @@ Reference: ``engine/llm_engine.py:113-657`` (``step`` l.206-240, ``_check_progre
 from __future__ import annotations
 
 import dataclasses
+import os
 import time
 from typing import Any, Iterable, Iterator
 
@@ -21,6 +22,10 @@ from .scheduler import Scheduler
 from .sequence import SamplingParams, Sequence, SequenceStatus
 
 NO_PROGRESS_LIMIT = 200
+#: ``COFFIN_DEBUG_STEP=1``: every 50 steps print what the scheduler really holds (reference
+#: ``engine/llm_engine.py:27-32``).
+DEBUG_STEP = bool(os.environ.get("COFFIN_DEBUG_STEP"))
+DEBUG_STEP_EVERY = 50
 
 
 @dataclasses.dataclass
@@ -131,6 +136,8 @@ class LLMEngine:
             self._release(seq, "timeout")
             out.append(StepOutput(seq, None, True))
         batch = self.scheduler.schedule()
+        if DEBUG_STEP and self.n_steps % DEBUG_STEP_EVERY == 0:
+            print(self.debug_line(batch.kind), flush=True)
         for seq in self.scheduler.admitted:
             self.runner.begin_prefill(seq)
         progressed = False
@@ -140,6 +147,14 @@ class LLMEngine:
             progressed = self._run_decode(batch.seqs, out)
         self._check_progress(progressed or bool(out), batch.kind)
         return out
+
+    def debug_line(self, kind: str = "") -> str:
+        """One line with the scheduler's queues and the free blocks; printed every 50th step under
+        ``COFFIN_DEBUG_STEP``."""
+        sch = self.scheduler
+        return (f"[step] n={self.n_steps} kind={kind} running={len(sch.running)} prefilling={len(sch.prefilling)} "
+                f"waiting={len(sch.waiting)} max_seqs={self.cfg.max_num_seqs} free_slots={len(sch.free_slots)} "
+                f"free_blocks={self.bm.pool.free_blocks} stall={self._stall}")
 
     def _check_progress(self, progressed: bool, kind: str) -> None:
         if progressed or kind == "idle" and not self.scheduler.has_work():

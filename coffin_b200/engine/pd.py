@@ -191,7 +191,34 @@ def adopt_payload(model, slot: int, payload: dict, first_block: int = 1, max_new
     snap = model.snapshot_state(slot)
     model.restore_state(slot, tuple(t.to(s.device, s.dtype) for t, s in zip(payload["state"], snap)))
     logits = payload["logits"]
+    if os.environ.get("COFFIN_PD_TRACE"):
+        print(f"[pd] adopt slot={slot} pos={n} blocks={len(table)} first_block={first_block} "
+              f"kv_layers={payload['k'].shape[0]} state_tensors={len(payload['state'])}", flush=True)
+    if os.environ.get("COFFIN_PD_VERIFY"):
+        for line in verify_adopted(model, slot, table, payload):
+            print(line, flush=True)
     return table, payload["prompt"], logits.to(getattr(model, "device", "cpu")) if logits is not None else None
+
+
+def verify_adopted(model, slot: int, table: list[int], payload: dict) -> list[str]:
+    """Read back what ``adopt_payload`` just wrote and count the elements that differ, one line per
+    tensor.  Repeated output after an adopt can come from a bad write (rows never reached the pool) or a
+    bad read (the block table points elsewhere); the read-back tells the two apart.  Printed under
+    ``COFFIN_PD_VERIFY`` (reference ``serving/runtime_parts.py:1487-1511``)."""
+    n = payload["n"]
+    pos = torch.arange(n)
+    slots = (torch.tensor(table, dtype=torch.long)[pos // BLOCK] * BLOCK + pos % BLOCK).to(model.kpool.device)
+    lines = []
+    for name, pool in (("k", model.kpool), ("v", model.vpool)):
+        want = payload[name].to(pool.device, pool.dtype)
+        got = pool[:, slots]
+        for i in range(want.shape[0]):
+            bad = int((got[i] != want[i]).sum())
+            lines.append(f"[pdverify] {name} layer={i} slot={slot} pos={n} mismatch={bad}/{want[i].numel()}")
+    for i, (got, want) in enumerate(zip(model.snapshot_state(slot), payload["state"])):
+        bad = int((got.cpu() != want.to(got.dtype).cpu()).sum())
+        lines.append(f"[pdverify] state tensor={i} slot={slot} mismatch={bad}/{want.numel()}")
+    return lines
 
 
 def adopt_state(model, slot: int, in_dir: Path, first_block: int = 1, rank: int = 0, max_new: int = 4096):

@@ -146,8 +146,12 @@ class MoEWeights:
             return hit
         E, N, half = stack.wq.shape
         out = K.w4_dequant(stack.wq.reshape(E * N, half), stack.scale.reshape(E * N, -1)).reshape(E, N, half * 2)
-        if keep_expansion(out):
+        kept = keep_expansion(out)
+        if kept:
             self._expanded[id(stack)] = out
+        from ...engine import debug
+        if debug.WQ_TRACE:
+            debug.wq_expand(out.shape, kept)
         return out
 
     # ------------------------------------------------------------------ buffers
@@ -258,6 +262,10 @@ class MoEWeights:
         if debug.MOE_CHECK:
             debug.check_moe_dispatch(idx, disp, n_local)
         xs = normed.index_select(0, disp["src_tok"])                      # gathered activations [T*k, H]
+        if debug.MOE_SHAPE:
+            storage = "int4" if self.w4 else "bf16"
+            debug.moe_shape("gate_up", xs.shape[0], n_local, 2 * I, H, storage)
+            debug.moe_shape("down", xs.shape[0], n_local, H, I, storage)
         if self.w4 and K.w4_grouped_ok(H) and K.w4_grouped_ok(I):
             # int4 codes straight into the tensor-core GEMM (expanded inside the CTA), SwiGLU in its epilogue
             inter = K.gemm_w4_grouped(xs, self.gate_up.wq, self.gate_up.scale, disp, swiglu=True)

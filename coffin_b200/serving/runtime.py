@@ -15,6 +15,7 @@ stream events ``start / token / done / error`` (``:769-869``), engine loop and f
 from __future__ import annotations
 
 import dataclasses
+import os
 import json
 import queue
 import threading
@@ -176,6 +177,10 @@ class Server:
                 try:
                     seq = self.engine.add_request(prompt, params, mm)
                     self._tickets[seq.seq_id] = _Ticket(seq, outq, time.monotonic())
+                    if os.environ.get("COFFIN_DEBUG_STEP"):
+                        sch = self.engine.scheduler
+                        print(f"[req] t={time.time():.3f} seq={seq.seq_id} waiting={len(sch.waiting)} "
+                              f"running={len(sch.running)}", flush=True)
                     outq.put(("seq", seq))
                 except Exception as exc:        # noqa: BLE001
                     outq.put(("error", str(exc)))

@@ -206,3 +206,25 @@ def test_one_shot_engine_without_chunking_serves_a_request():
         before = eng.model.n_prefill_calls
         s = eng.generate([p], SamplingParams(max_tokens=4))[0]
         assert s.output == solo(p, 4) and eng.model.n_prefill_calls - before == calls
+
+
+def test_debug_line_reports_the_queues():
+    eng = engine(chunk=32, prefill_quantum=32, max_num_batched_tokens=32)
+    eng.add_request(prompt(100, 5), SamplingParams(max_tokens=2))
+    eng.add_request(prompt(40, 6), SamplingParams(max_tokens=2))
+    assert "waiting=2" in eng.debug_line()
+    eng.step()
+    line = eng.debug_line("prefill")
+    assert line.startswith("[step] n=1 kind=prefill") and "free_blocks=" in line and "waiting=2" not in line
+
+
+def test_shape_and_expansion_traces_print_once_per_shape(capsys):
+    from coffin_b200.engine import debug
+    debug._shapes_seen.clear()
+    assert debug.moe_shape("gate_up", 4096, 128, 1536, 2048, "int4")
+    assert not debug.moe_shape("gate_up", 4096, 128, 1536, 2048, "int4")          # seen
+    assert debug.moe_shape("down", 4096, 128, 2048, 768, "int4")
+    debug.wq_expand((128, 1536, 2048), kept=False)
+    said = capsys.readouterr().out
+    assert said.count("[moe-shape]") == 2 and "rows=4096 experts=128 n=1536 k=2048 weights=int4" in said
+    assert "[wq-expand] (128, 1536, 2048) kept=False" in said and "test_engine_cpu.py" in said

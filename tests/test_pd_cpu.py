@@ -119,3 +119,20 @@ def test_exports_of_two_pipeline_stages_merge_into_the_whole_model(tmp_path):
     other["prompt"][0] ^= 1
     with pytest.raises(ValueError, match="different prompts"):
         pd.merge_parts([part0, other])
+
+
+def test_read_back_after_adopt_reports_no_mismatch_and_sees_a_damaged_row(tmp_path, monkeypatch, capsys):
+    cfg, sd, src, prompt, table, logits = _prefilled(tmp_path)
+    dst = _twin(cfg, sd)
+    monkeypatch.setenv("COFFIN_PD_TRACE", "1")
+    monkeypatch.setenv("COFFIN_PD_VERIFY", "1")
+    t2, _, _ = pd.adopt_state(dst, 0, tmp_path / "whole", first_block=3)
+    said = capsys.readouterr().out
+    assert "[pd] adopt slot=0 pos=70" in said
+    lines = [ln for ln in said.splitlines() if ln.startswith("[pdverify]")]
+    assert lines and all("mismatch=0/" in ln for ln in lines)
+    payload = torch.load(tmp_path / "whole" / "state.pt", map_location="cpu", weights_only=False)
+    dst.kpool[0, t2[0] * pd.BLOCK + 5] += 1.0                       # one KV row of layer 0 damaged after the write
+    after = pd.verify_adopted(dst, 0, t2, payload)
+    bad = [ln for ln in after if "mismatch=0/" not in ln]
+    assert len(bad) == 1 and bad[0].startswith("[pdverify] k layer=0")
