@@ -38,11 +38,13 @@ def main(argv=None) -> int:
         socks.extend(x for x in s.split(",") if x)
     clients = [EngineClient(s, args.timeout) for s in socks]
     name = args.served_model_name or args.model
+    vision = True
     for c in clients:
         for attempt in range(3):
             try:
                 p = c.ping()
                 name = name or p.get("model")
+                vision = vision and bool(p.get("vision", True))      # one replica without a tower closes the image path
                 break
             except OSError as exc:
                 if attempt == 2:
@@ -52,7 +54,7 @@ def main(argv=None) -> int:
     configure(ReplicaRouter(clients), served_model_name=name or "coffin-b200",
               default_max_tokens=args.default_max_tokens, enable_thinking=args.enable_thinking,
               max_decode_seconds=args.max_decode_seconds, max_images=args.max_images,
-              max_image_bytes=args.max_image_bytes, max_image_total_bytes=args.max_image_total_bytes)
+              max_image_bytes=args.max_image_bytes, max_image_total_bytes=args.max_image_total_bytes, vision=vision)
     srv = make_server(args.host, args.port)
     print(f"[http] serving {name} on http://{args.host}:{args.port} -> {', '.join(socks)}", flush=True)
     try:

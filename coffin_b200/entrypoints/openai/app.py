@@ -66,6 +66,7 @@ class ReplicaRouter:
 STATE: dict[str, Any] = {
     "engine": None, "served_model_name": "coffin-b200", "default_max_tokens": 8192, "enable_thinking": True,
     "max_decode_seconds": 180.0, "max_images": 4, "max_image_bytes": 10 << 20, "max_image_total_bytes": 32 << 20,
+    "vision": True,      # False when the engine reported no vision tower (``--no-vision``): image requests answer 503 here
 }
 
 
@@ -168,6 +169,9 @@ class Handler(BaseHTTPRequestHandler):
                 stream=stream)
         except RequestError as exc:
             self._error(exc.status, str(exc), code=exc.code)
+            return
+        if req.get("images") and STATE.get("vision") is False:
+            self._error(503, "this server's engine was started with --no-vision: image inputs are disabled", "server_error")
             return
         cid = "chatcmpl-" + uuid.uuid4().hex[:24]
         created = int(time.time())

@@ -40,6 +40,8 @@ def decode_data_url(url: str, max_bytes: int) -> dict:
         raw = base64.b64decode(payload, validate=True)
     except (binascii.Error, ValueError):
         raise RequestError("image payload is not valid base64", 400, "invalid_image_url") from None
+    if not raw:
+        raise RequestError("image payload is empty", 400, "invalid_image_url")
     if len(raw) > max_bytes:
         raise RequestError(f"image larger than {max_bytes} bytes", 413, "image_too_large")
     return {"b64": payload, "mime": mime, "bytes": len(raw)}

@@ -269,14 +269,14 @@ MEAN = (0.5, 0.5, 0.5)
 STD = (0.5, 0.5, 0.5)
 
 
-def patchify(image: torch.Tensor, cfg: VisionConfig) -> tuple[torch.Tensor, tuple[int, int, int]]:
+def patchify(image: torch.Tensor, cfg: VisionConfig, mean=MEAN, std=STD) -> tuple[torch.Tensor, tuple[int, int, int]]:
     """``image [3, H, W]`` float in [0, 1], sides multiples of ``patch * merge`` ->
     ``(patches [N, patch_dim] in merge-block order, (t, h, w))``.  A still image is repeated over
-    the temporal patch."""
+    the temporal patch.  ``mean`` / ``std``: per-channel normalisation (a checkpoint's own when it states one)."""
     C, Hh, Ww = image.shape
     p, tp = cfg.patch_size, cfg.temporal_patch_size
-    mean = torch.tensor(MEAN).reshape(3, 1, 1)
-    std = torch.tensor(STD).reshape(3, 1, 1)
+    mean = torch.tensor(tuple(mean)).reshape(3, 1, 1)
+    std = torch.tensor(tuple(std)).reshape(3, 1, 1)
     img = ((image - mean) / std).unsqueeze(1).expand(C, tp, Hh, Ww)
     h, w = Hh // p, Ww // p
     x = img.reshape(C, tp, h, p, w, p).permute(2, 4, 0, 1, 3, 5).reshape(h * w, C * tp * p * p)

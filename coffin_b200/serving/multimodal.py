@@ -65,16 +65,17 @@ def expand_placeholders(prompt: list[int], image_token_id: int, counts: list[int
 def build_mm_input(srv, images: list[dict], prompt: list[int]):
     """Run the tower on every image and return ``(MMInput, expanded prompt)``."""
     from ..models.qwen35.vision import patchify
+    from .processor import ensure_recipe
     tower = srv.vision
     vc = tower.cfg
-    factor = vc.patch_size * vc.spatial_merge_size
+    recipe = ensure_recipe(srv)          # 503 (cached) when the checkpoint states an algorithm the engine does not implement
     image_token = getattr(srv.tok, "special", {}).get("<|image_pad|>") if hasattr(srv.tok, "special") else None
     if image_token is None:
         image_token = srv.tok.encode("<|image_pad|>")[0]
     embeds, grids, digests = [], [], []
     for im in images:
-        t, raw = decode_image(im["b64"], srv.cfg.image_min_pixels, srv.cfg.image_max_pixels, factor)
-        patches, grid = patchify(t, vc)
+        t, raw = decode_image(im["b64"], recipe.min_pixels, recipe.max_pixels, recipe.factor)
+        patches, grid = patchify(t, vc, recipe.mean, recipe.std)
         embeds.append(tower.forward(patches, grid))
         grids.append(grid)
         digests.append(image_digest(raw, f"{grid}"))

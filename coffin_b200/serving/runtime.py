@@ -94,6 +94,8 @@ class Server:
         self.eos = tuple(i for i in self.tok.eos_ids if i < self.model_cfg.vocab_size)
         self.n_req = self.n_reload = self.n_image_req = 0
         self.vision = getattr(model, "vision", None)
+        self.processor = None                    # image recipe, loaded by the first image request (serving/processor.py)
+        self._processor_failed: str | None = None
         self._inbox: "queue.Queue[Any]" = queue.Queue()
         self._tickets: dict[int, _Ticket] = {}
         self._wake = threading.Condition()
@@ -404,6 +406,8 @@ class Server:
         t0 = time.time()
         self.engine.reset()
         self.model = self.builder()
+        self.vision = getattr(self.model, "vision", None)       # the rebuilt model brings its own tower ...
+        self.processor, self._processor_failed = None, None    # ... and the image recipe is read again
         self.engine = LLMEngine(self.model, self.cfg)
         self.warmup_s = round(self.engine.warmup(), 3) if self.cfg.warmup else 0.0
         self.n_reload += 1
@@ -427,6 +431,7 @@ class Server:
                 "decode_capacity": self.cfg.max_num_seqs, "vision": self.vision is not None, "vision_int8": False,
                 "image_max_pixels": self.cfg.image_max_pixels, "image_min_pixels": self.cfg.image_min_pixels,
                 "max_images": self.cfg.max_images, "n_image_req": self.n_image_req,
-                "processor": "builtin" if self.vision is not None else None,
+                "processor": (None if self.vision is None else "failed: " + self._processor_failed if self._processor_failed
+                              else self.processor.source if self.processor is not None else "not loaded"),
                 "queue": {"waiting": st["queue"]["waiting"], "running": st["queue"]["running"] + st["queue"]["prefilling"]},
                 "prefix": st["blocks"]["prefix"], "last_error": self.last_error}

@@ -323,3 +323,25 @@ def test_image_roles_order_and_plain_parts(server):
     assert st == 400 and json.loads(data)["error"]["message"]
     tiff = {"type": "image_url", "image_url": {"url": "data:image/tiff;base64," + base64.b64encode(b"II*\x00").decode()}}
     assert post(port, {"messages": [{"role": "user", "content": [tiff]}]})[0] == 400
+
+
+def test_malformed_image_urls_are_400_and_a_front_without_vision_answers_503(server):
+    eng, port = server
+    png = base64.b64encode(b"\x89PNG" + b"0" * 100).decode()
+    cases = {"bad base64": "data:image/png;base64,!!!notbase64!!!", "no payload": "data:image/png;base64,",
+             "not a url": "not-a-url", "svg": "data:image/svg+xml;base64," + png}
+    n = len(eng.requests)
+    for label, url in cases.items():
+        st, body = post(port, {"messages": [{"role": "user", "content": [{"type": "image_url", "image_url": {"url": url}}]}]})
+        assert st == 400 and json.loads(body)["error"]["message"], label
+    assert len(eng.requests) == n                                  # nothing malformed reached the engine
+    img = {"type": "image_url", "image_url": {"url": f"data:image/png;base64,{png}"}}
+    oa.STATE["vision"] = False
+    try:
+        st, body = post(port, {"messages": [{"role": "user", "content": [img]}]})
+        assert st == 503 and "--no-vision" in json.loads(body)["error"]["message"] and len(eng.requests) == n
+        st, body = post(port, {"messages": user("hi"), "max_tokens": 3})    # the text path is untouched
+        assert st == 200
+    finally:
+        oa.STATE["vision"] = True
+    assert post(port, {"messages": [{"role": "user", "content": [img]}]})[0] == 200
