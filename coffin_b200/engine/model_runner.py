@@ -11,11 +11,9 @@ from __future__ import annotations
 
 import random
 import time
-from typing import Any
 
 import torch
 
-from ..cache.paged_cache import OutOfBlocks
 from . import debug
 from .block_manager import BlockManager
 from .config import EngineConfig

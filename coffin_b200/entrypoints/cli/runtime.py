@@ -71,7 +71,7 @@ def build_server(args):
     """Load (or draw) the weights once and return a ``Server`` whose ``reload`` rebuilds the model
     from the resident state dict."""
     import torch
-    from ...config import ModelConfig, load_config, preset
+    from ...config import load_config, preset
     from ...serving.runtime import Server
     cfg_e = engine_config(args)
     if cfg_e.max_seq > 32768 and args.max_seq is None:

@@ -27,7 +27,7 @@ import torch
 import torch.nn.functional as F
 
 from ...oracle import ops as O
-from .config import INDEXED, LINEAR, Qwen4Config
+from .config import LINEAR, Qwen4Config
 from .ngram import NGramHasher
 
 LM = "model.language_model."

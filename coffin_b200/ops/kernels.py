@@ -8,7 +8,6 @@ at the granularity of the fused kernels, not op for op.
 from __future__ import annotations
 
 import contextlib
-import math
 import os
 
 import torch

@@ -11,7 +11,6 @@ logits.)
 from __future__ import annotations
 
 import torch
-import torch.nn.functional as F
 
 from ..config import LINEAR, ModelConfig
 from ..weights.init import LM

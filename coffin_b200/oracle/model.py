@@ -13,7 +13,6 @@ from __future__ import annotations
 import dataclasses
 
 import torch
-import torch.nn.functional as F
 
 from ..config import LINEAR, ModelConfig
 from ..weights.init import LM

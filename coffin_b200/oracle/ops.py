@@ -10,7 +10,6 @@ returns fp32 unless noted.
 """
 from __future__ import annotations
 
-import math
 
 import torch
 import torch.nn.functional as F

@@ -19,7 +19,7 @@ import os
 
 import torch
 
-from ..config import LINEAR, ModelConfig
+from ..config import ModelConfig
 from ..weights.init import LM
 
 MAX_WORLD = 8

@@ -16,7 +16,6 @@ from __future__ import annotations
 
 import dataclasses
 import os
-import json
 import queue
 import threading
 import time
@@ -31,7 +30,7 @@ from ..engine.config import EngineConfig
 from ..engine.llm_engine import LLMEngine
 from ..engine.sequence import SamplingParams, Sequence
 from ..utils.tokenizer import IncrementalDecoder, load_tokenizer
-from ..utils.tool_call import TC_OPEN, parse_tool_calls, split_thinking
+from ..utils.tool_call import parse_tool_calls, split_thinking
 
 DIAGNOSTIC_OPS = {"reload", "reset", "bench", "profile", "ops", "spec", "verify", "pd_prefill", "pd_decode",
                   "pd_decode_batch", "pd_release"}
