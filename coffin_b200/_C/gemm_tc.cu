@@ -181,6 +181,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       tc_fence_after();
       const int row = m0 + q * 32 + lane;
       const float rs = (I8 && row < row_end) ? a.row_scale[row] : 1.f;
+      // weight scales of this tile's columns: the grouped form keeps one [N] vector per expert, back to back
+      const float* cscale = I8 ? a.col_scale + (tc.brow - n0) : nullptr;
       if (splits > 1) {
         // ---- K slice: park the fp32 partial tile, the last slice to arrive reduces all of them ----
         float* mine = a.ws + ((size_t)tile * BM + q * 32 + lane) * BN;
@@ -267,7 +269,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             float f[8];
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
-              if (I8) f[i] = (float)(int)r[v * 8 + i] * rs * a.col_scale[col0 + v * 8 + i];
+              if (I8) f[i] = (float)(int)r[v * 8 + i] * rs * cscale[col0 + v * 8 + i];
               else f[i] = __uint_as_float(r[v * 8 + i]);
             }
             if (rp) {
@@ -455,6 +457,37 @@ CB_EXPORT int cb_gemm_bf16_grouped(const void* A, int64_t lda, const void* W, in
   if (bn == 256) return launch_gemm<256, 4, false>(tmA, tmB, a, sms, st);
   if (bn == 160) return launch_gemm<160, 5, false>(tmA, tmB, a, sms, st);
   return launch_gemm<128, 6, false>(tmA, tmB, a, sms, st);
+}
+
+// The same grouped product from int8 stacks (W8A8 routed experts): A int8 [rows, K] with one scale per row
+// (the gathered activation rows, quantised per token), W int8 [E, N, K] with col_scale [E, N];
+// C = (A x W[expert]^T) * row_scale * col_scale[expert] on the kind::i8 path.  K % 16 == 0.
+CB_EXPORT int cb_gemm_i8_grouped(const void* A, int64_t lda, const void* W, int64_t ldw, void* C, int64_t ldc,
+                                 const void* row_scale, const void* col_scale, int64_t rows, int64_t E, int64_t N,
+                                 int64_t K, const void* g_count, const void* g_row0, const void* g_rows,
+                                 const void* g_expert, int64_t max_tiles, void* status, void* stream) {
+  if (rows < 1 || N < 1 || K < 1 || E < 1 || max_tiles < 1) return CB_ERR_SHAPE;
+  if (K % 16 || N % 8 || ldc % 8 || lda % 16 || ldw % 16) return CB_ERR_SHAPE;
+  if (!status || !row_scale || !col_scale || !g_count || !g_row0 || !g_rows || !g_expert) return CB_ERR_ARG;
+  const int sms = sm_count();
+  const int bn = N % 256 == 0 || N > 1024 ? 256 : (N % 160 == 0 ? 160 : 128);
+  CUtensorMap tmA, tmB;
+  int rc = cb_make_tmap_2d(&tmA, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, A, (uint64_t)rows, (uint64_t)K, (uint64_t)lda, BM, 128);
+  if (rc) return rc;
+  rc = cb_make_tmap_2d(&tmB, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, W, (uint64_t)(E * N), (uint64_t)K, (uint64_t)ldw, (uint32_t)bn, 128);
+  if (rc) return rc;
+  GemmArgs a;
+  a.C = C; a.ldc = ldc; a.residual = nullptr; a.ldr = 0;
+  a.row_scale = (const float*)row_scale; a.col_scale = (const float*)col_scale;
+  a.M = (int)rows; a.N = (int)N; a.K = (int)K; a.m_tiles = (int)max_tiles; a.n_tiles = 0;
+  a.k_blocks = (int)((K + 127) / 128); a.status = (int*)status;
+  a.pf = nullptr; a.pf_seq = 0;
+  a.g_count = (const int*)g_count; a.g_row0 = (const int*)g_row0; a.g_rows = (const int*)g_rows; a.g_expert = (const int*)g_expert;
+  a.splits = 1; a.ws = nullptr; a.tickets = nullptr;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (bn == 256) return launch_gemm<256, 4, true>(tmA, tmB, a, sms, st);
+  if (bn == 160) return launch_gemm<160, 5, true>(tmA, tmB, a, sms, st);
+  return launch_gemm<128, 6, true>(tmA, tmB, a, sms, st);
 }
 
 // Skinny product for batched decode (M <= 128 rows: one m-tile): C = A x W^T (+ residual) with the K

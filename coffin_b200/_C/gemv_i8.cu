@@ -8,6 +8,7 @@
 // streamed per token relative to bf16.  Replaces the reference's int8 GEMV family
 // (backends/corex/kernels/gemv.cu:839-947 nk int8, w8a8.cu:76-242 activation quant).
 #include <string.h>
+#include <algorithm>
 #include "tp.cuh"
 
 namespace {
@@ -22,6 +23,9 @@ struct I8Args {
   int M, ksplit, rounds;
   int pull_site, push_site;   // tensor parallel: -1 = off
   TpComm tp;
+  // routed experts (slot mode): blockIdx.y selects (expert, activation row); W is a stack [E, expert_rows, K]
+  // with wscale [E, expert_rows]
+  const int* slot_expert; const int* slot_xrow; int64_t expert_rows;
 };
 
 __device__ __forceinline__ void mma_s8(int* c, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
@@ -31,10 +35,21 @@ __device__ __forceinline__ void mma_s8(int* c, uint32_t a0, uint32_t a1, uint32_
 }
 
 template <bool SWIGLU, bool NORM, bool OUT_F32>
-__global__ void __launch_bounds__(kT, 3) gemv_i8_kernel(const I8Args a) {
+__global__ void __launch_bounds__(kT, 3) gemv_i8_kernel(const I8Args a_in) {
   constexpr int PB = SWIGLU ? 2 : 1;
   constexpr int U = SWIGLU ? 2 : 4;
   extern __shared__ __align__(16) unsigned char smem_raw[];
+  I8Args a = a_in;
+  if (a.slot_expert) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");      // the routing tables come from the kernel just before
+    const int slot = blockIdx.y, e = a.slot_expert[slot];
+    if (e < 0) { cbtrace::stamp(0); cbtrace::stamp(1); return; }      // a slot routed to another rank's expert
+    a.W += (int64_t)e * a.expert_rows * a.K;
+    a.wscale += (int64_t)e * a.expert_rows;
+    a.x += (int64_t)(a.slot_xrow ? a.slot_xrow[slot] : slot) * a.K;
+    a.y = OUT_F32 ? (void*)(reinterpret_cast<float*>(a.y) + (int64_t)slot * a.ldy)
+                  : (void*)(reinterpret_cast<bf16*>(a.y) + (int64_t)slot * a.ldy);
+  }
   const int64_t K = a.K, nchunk = K >> 4;          // 16 int8 per chunk
   const int M = a.M;
   bf16* stage = reinterpret_cast<bf16*>(smem_raw);                         // [K] staging row (values are bf16-exact)
@@ -205,7 +220,7 @@ __global__ void __launch_bounds__(kT, 3) gemv_i8_kernel(const I8Args a) {
 int g_i8_sms = 0;
 
 template <bool SWIGLU, bool NORM, bool OUT_F32>
-int launch_i8(I8Args a, cudaStream_t st) {
+int launch_i8(I8Args a, cudaStream_t st, int n_slots = 1) {
   if (!g_i8_sms) {
     int dev = 0;
     cudaGetDevice(&dev);
@@ -219,7 +234,7 @@ int launch_i8(I8Args a, cudaStream_t st) {
   size_t smem = 0;
   int64_t grid = 0;
   for (int per_sm = 3; per_sm >= 1; --per_sm) {
-    const int64_t slots = (int64_t)g_i8_sms * per_sm;
+    const int64_t slots = std::max<int64_t>(1, (int64_t)g_i8_sms * per_sm / n_slots);
     int ks = 1;
     while (ks < kW && (nblk * ks + kW - 1) / kW < slots && npair / (ks * 2) >= 4) ks <<= 1;
     a.ksplit = ks;
@@ -237,7 +252,7 @@ int launch_i8(I8Args a, cudaStream_t st) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
   }
-  return (int)cb_launch(kern, dim3((unsigned)grid), dim3(kT), smem, st, a);
+  return (int)cb_launch(kern, dim3((unsigned)grid, (unsigned)n_slots), dim3(kT), smem, st, a);
 }
 
 // Per-row dynamic int8 quantisation of bf16 activations (prefill side of W8A8):
@@ -323,6 +338,7 @@ CB_EXPORT int cb_gemv_i8(const void* W, const void* wscale, const void* x, void*
   I8Args a{(const int8_t*)W, (const float*)wscale, (const bf16*)x, y, N, K, ldy, up_off, (const bf16*)res_in,
            (const bf16*)add, (const float*)gain, (bf16*)res_out, eps, (int)M, 1, 1, (int)pull_site, (int)push_site};
   if (tp) a.tp = *(const TpComm*)tp; else memset(&a.tp, 0, sizeof(a.tp));
+  a.slot_expert = nullptr; a.slot_xrow = nullptr; a.expert_rows = 0;
   const bool sw = mode & 1, f32 = mode & 2, norm = res_in != nullptr;
   cudaStream_t st = (cudaStream_t)stream;
   if (sw) {
@@ -331,6 +347,24 @@ CB_EXPORT int cb_gemv_i8(const void* W, const void* wscale, const void* x, void*
   }
   if (f32) return norm ? launch_i8<false, true, true>(a, st) : launch_i8<false, false, true>(a, st);
   return norm ? launch_i8<false, true, false>(a, st) : launch_i8<false, false, false>(a, st);
+}
+
+// Routed experts from int8 stacks: slot s computes y[s, :] = (W[slot_expert[s]] x[slot_xrow[s], :]) with the
+// activation row quantised in the prologue; W [E, rows, K] and wscale [E, rows] with rows = N (plain) or 2N
+// (mode bit 0, SwiGLU: gate rows then up rows).  A negative expert index leaves the slot's output untouched.
+CB_EXPORT int cb_moe_gemv_i8(const void* W, const void* wscale, const void* x, void* y, int64_t n_slots, int64_t N,
+                             int64_t K, int64_t ldy, int64_t mode, const void* slot_expert, const void* slot_xrow,
+                             void* stream) {
+  if (!W || !wscale || !x || !y || !slot_expert) return CB_ERR_ARG;
+  if (K % 16 || N < 1 || n_slots < 1 || n_slots > 65535) return CB_ERR_SHAPE;
+  I8Args a{(const int8_t*)W, (const float*)wscale, (const bf16*)x, y, N, K, ldy, N, nullptr, nullptr, nullptr, nullptr,
+           0.f, 1, 1, 1, -1, -1};
+  memset(&a.tp, 0, sizeof(a.tp));
+  a.slot_expert = (const int*)slot_expert; a.slot_xrow = (const int*)slot_xrow;
+  a.expert_rows = (mode & 1) ? 2 * N : N;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (mode & 1) return (mode & 2) ? CB_ERR_ARG : launch_i8<true, false, false>(a, st, (int)n_slots);
+  return (mode & 2) ? launch_i8<false, false, true>(a, st, (int)n_slots) : launch_i8<false, false, false>(a, st, (int)n_slots);
 }
 
 CB_EXPORT int cb_quant_rows(const void* x, int64_t ldx, void* q, void* scale, int64_t M, int64_t K, int64_t swiglu,

@@ -19,6 +19,9 @@ import os
 from ...config import ModelConfig
 from ...ops import kernels as K
 
+# Routed experts of an int8 checkpoint stay int8 (slot GEMV with in-kernel activation quantisation in decode,
+# grouped kind::i8 tcgen05 GEMM in prefill).  COFFIN_MOE_I8_GROUPED=0: expand the stacks to bf16 at load.
+I8_GROUPED = os.environ.get("COFFIN_MOE_I8_GROUPED", "1") != "0"
 PREFILL_CACHE_BYTES = int(float(os.environ.get("COFFIN_MOE_PREFILL_CACHE_GB", "64")) * (1 << 30))
 CACHE_HEADROOM = 16 << 30      # HBM that must stay free after an expansion is kept
 _cache_used = 0                # bytes of bf16 expansions kept by the process
@@ -74,7 +77,7 @@ class MoEWeights:
         per = E // ep_world
         e_lo, e_hi = ep_rank * per, (ep_rank + 1) * per
         from ...weights.quant import QWeight, W4A8Weight
-        from .model import QW4
+        from .model import QW, QW4
         # a state dict read with an expert-parallel filter already holds only this rank's experts
         presliced = tuple(sd.get("__ep_shard__", ())) == (ep_rank, ep_world) and ep_world > 1
         s_lo, s_hi = (0, per) if presliced else (e_lo, e_hi)
@@ -85,7 +88,9 @@ class MoEWeights:
                 part = W4A8Weight(t.packed[s_lo:s_hi], t.scale[s_lo:s_hi], t.k, t.group_size)
                 return QW4(*part.to(dev).to_nk())
             if isinstance(t, QWeight):
-                # int8 expert stacks are expanded once at load: the grouped expert kernels read bf16 or int4
+                if I8_GROUPED and t.k % 16 == 0 and t.n % 8 == 0:
+                    return QW(t.wq[s_lo:s_hi].to(dev), t.scale[s_lo:s_hi].to(dev))
+                # a depth the int8 kernels cannot take (or the switch): expanded once at load
                 t = (t.wq[s_lo:s_hi].to(dev).float() * t.scale[s_lo:s_hi].to(dev).float()[..., None]).to(bf)
                 s0, s1 = 0, t.shape[0]
             else:
@@ -96,6 +101,11 @@ class MoEWeights:
             return t.contiguous()
 
         gu, dn = experts(gu), experts(dn)
+        if isinstance(gu, QW) != isinstance(dn, QW):
+            # the expert kernels take one storage for the pair: the int8 one is expanded
+            def widen(st):
+                return (st.wq.float() * st.scale[..., None]).to(bf).contiguous() if isinstance(st, QW) else st
+            gu, dn = widen(gu), widen(dn)
         if isinstance(gu, QW4) != isinstance(dn, QW4):
             # one stack cannot be stored as int4 (its reduction length is not a whole number of groups):
             # both stay bf16, the expert kernels take one storage for the pair
@@ -127,11 +137,19 @@ class MoEWeights:
 
     @property
     def w4(self) -> bool:
-        return not isinstance(self.gate_up, torch.Tensor)
+        return hasattr(self.gate_up, "wq") and self.gate_up.wq.dtype == torch.uint8
+
+    @property
+    def i8(self) -> bool:
+        return hasattr(self.gate_up, "wq") and self.gate_up.wq.dtype == torch.int8
 
     def _expert(self, stack, e: int) -> torch.Tensor:
         """bf16 ``[rows, K]`` weights of local expert ``e`` (expanded from W4 storage for a prefill GEMM)."""
-        return stack[e] if isinstance(stack, torch.Tensor) else K.w4_dequant(stack.wq[e], stack.scale[e])
+        if isinstance(stack, torch.Tensor):
+            return stack[e]
+        if stack.wq.dtype == torch.int8:
+            return (stack.wq[e].float() * stack.scale[e][:, None]).to(torch.bfloat16)
+        return K.w4_dequant(stack.wq[e], stack.scale[e])
 
     def _stack(self, stack) -> torch.Tensor:
         """bf16 ``[E, rows, K]`` weights of all local experts.  W4 storage is expanded on the first prefill
@@ -209,6 +227,9 @@ class MoEWeights:
         if self.w4:
             K.moe_gemv_w4(self.gate_up.wq, self.gate_up.scale, normed, b["inter"], b["idx"], b["xrow"], swiglu=True)
             K.moe_gemv_w4(self.down.wq, self.down.scale, b["inter"], b["y"], b["idx"], b["irow"])
+        elif self.i8:
+            K.moe_gemv_i8(self.gate_up.wq, self.gate_up.scale, normed, b["inter"], b["idx"], b["xrow"], swiglu=True)
+            K.moe_gemv_i8(self.down.wq, self.down.scale, b["inter"], b["y"], b["idx"], b["irow"])
         else:
             K.call("moe_gemv", self.gate_up, normed, b["inter"], T * k, I, H, I, 1, b["idx"], b["xrow"],
                    self.gate_up.stride(0))
@@ -241,7 +262,7 @@ class MoEWeights:
         c = self.cfg
         T = normed.shape[0]
         E, k, H, I = c.num_experts, c.num_experts_per_tok, c.hidden_size, c.moe_intermediate_size
-        if T <= (64 if self.w4 else 32):      # W4 stacks would have to be expanded to bf16 for the grouped GEMM
+        if T <= (64 if self.w4 else 32):      # few rows: every slot streams its expert once
             b = self._b(T, normed.device)
             b["normed"][:T].copy_(normed)
             out = torch.empty(T, H, dtype=torch.bfloat16, device=normed.device)
@@ -261,15 +282,23 @@ class MoEWeights:
         from ...engine import debug
         if debug.MOE_CHECK:
             debug.check_moe_dispatch(idx, disp, n_local)
-        xs = normed.index_select(0, disp["src_tok"])                      # gathered activations [T*k, H]
         if debug.MOE_SHAPE:
-            storage = "int4" if self.w4 else "bf16"
-            debug.moe_shape("gate_up", xs.shape[0], n_local, 2 * I, H, storage)
-            debug.moe_shape("down", xs.shape[0], n_local, H, I, storage)
+            storage = "int4" if self.w4 else "int8" if self.i8 else "bf16"
+            debug.moe_shape("gate_up", T * k, n_local, 2 * I, H, storage)
+            debug.moe_shape("down", T * k, n_local, H, I, storage)
+        if not self.i8:
+            xs = normed.index_select(0, disp["src_tok"])                  # gathered activations [T*k, H]
         if self.w4 and K.w4_grouped_ok(H) and K.w4_grouped_ok(I):
             # int4 codes straight into the tensor-core GEMM (expanded inside the CTA), SwiGLU in its epilogue
             inter = K.gemm_w4_grouped(xs, self.gate_up.wq, self.gate_up.scale, disp, swiglu=True)
             y = K.gemm_w4_grouped(inter, self.down.wq, self.down.scale, disp)
+        elif self.i8:
+            # W8A8: the chunk's rows are quantised once per token and gathered as int8; kind::i8 grouped GEMMs
+            q, qs = K.quant_rows(normed)
+            src = disp["src_tok"]
+            gu = K.gemm_i8_grouped(q.index_select(0, src), qs.index_select(0, src), self.gate_up.wq, self.gate_up.scale, disp)
+            iq, iscale = K.quant_rows(gu, swiglu=True)
+            y = K.gemm_i8_grouped(iq, iscale, self.down.wq, self.down.scale, disp)
         else:
             gu = K.gemm_grouped(xs, self._stack(self.gate_up), disp)
             inter = K.swiglu(gu)

@@ -369,6 +369,20 @@ def moe_gemv_w4(Wq, wscale, x, out, slot_expert, slot_xrow, *, swiglu: bool = Fa
     return out
 
 
+def moe_gemv_i8(W, wscale, x, out, slot_expert, slot_xrow, *, swiglu: bool = False) -> torch.Tensor:
+    """Routed experts on int8 storage: ``W [E, rows, K]`` int8, ``wscale [E, rows]`` fp32; slot ``s`` multiplies
+    activation row ``slot_xrow[s]`` (bf16, quantised per row inside the kernel) by expert ``slot_expert[s]``
+    (``< 0``: skipped).  ``swiglu``: ``rows = 2N`` (gate rows, then up rows)."""
+    n_slots = out.shape[0]
+    Kd = W.shape[2]
+    N = W.shape[1] // 2 if swiglu else W.shape[1]
+    assert W.dtype == torch.int8 and W.is_contiguous() and wscale.dtype == torch.float32 and wscale.is_contiguous()
+    mode = (1 if swiglu else 0) | (2 if out.dtype == torch.float32 else 0)
+    call("moe_gemv_i8", W, wscale, x, out, n_slots, N, Kd, out.stride(0), mode, slot_expert, slot_xrow)
+    _count()
+    return out
+
+
 def w4_dequant(Wq: torch.Tensor, wscale: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
     """bf16 ``[N, K]`` from W4 codes + group scales (prefill: expanded once per projection call)."""
     N, K = Wq.shape[0], Wq.shape[1] * 2
@@ -409,6 +423,23 @@ def gemm_grouped(A: torch.Tensor, W: torch.Tensor, disp: dict, out: torch.Tensor
         out = torch.empty(S, N, dtype=torch.bfloat16, device=A.device)
     call("gemm_bf16_grouped", A, A.stride(0), W, W.stride(1), out, out.stride(0), S, E, N, Kd, disp["count"],
          disp["row0"], disp["rows"], disp["expert"], disp["max_tiles"], status_word(A.device))
+    _count()
+    return out
+
+
+def gemm_i8_grouped(Aq: torch.Tensor, a_scale: torch.Tensor, W: torch.Tensor, wscale: torch.Tensor, disp: dict,
+                    out: torch.Tensor | None = None) -> torch.Tensor:
+    """``out[r] = (Aq[r] @ W[expert(r)].T) * a_scale[r] * wscale[expert(r)]`` for expert-sorted int8 rows
+    ``Aq [S, K]`` (one scale per row) and an int8 stack ``W [E, N, K]`` with ``wscale [E, N]``, on the
+    ``kind::i8`` tensor-core path; tiles from ``disp`` (:func:`moe_dispatch`).  Output bf16 ``[S, N]``."""
+    S, Kd = Aq.shape
+    E, N, _ = W.shape
+    assert Aq.dtype == torch.int8 and W.dtype == torch.int8 and Aq.stride(1) == 1 and W.is_contiguous()
+    assert a_scale.dtype == torch.float32 and wscale.dtype == torch.float32 and wscale.is_contiguous()
+    if out is None:
+        out = torch.empty(S, N, dtype=torch.bfloat16, device=Aq.device)
+    call("gemm_i8_grouped", Aq, Aq.stride(0), W, W.stride(1), out, out.stride(0), a_scale, wscale, S, E, N, Kd,
+         disp["count"], disp["row0"], disp["rows"], disp["expert"], disp["max_tiles"], status_word(Aq.device))
     _count()
     return out
 

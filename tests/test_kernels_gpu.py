@@ -508,6 +508,72 @@ def test_moe_gemv_w4a8_slots():
         close(out[s:s + 1], O.silu_mul(gu[:, :I], gu[:, I:]), 3e-2)
 
 
+def test_moe_gemv_i8_slots():
+    """Routed experts from int8 stacks, one slot per (expert, activation row): the kernel quantises the row
+    itself; against the dequantised weights times the quantised row in fp32."""
+    k = K()
+    from coffin_b200.weights.quant import QWeight
+    E, I, H = 6, 128, 256
+    g = torch.Generator().manual_seed(71)
+    q = QWeight.quantize(torch.randn(E, 2 * I, H, generator=g) * 0.05)
+    qd = QWeight.quantize(torch.randn(E, H, I, generator=g) * 0.05)
+    x = torch.randn(3, H, generator=g).to(torch.bfloat16)
+    slot_e = torch.tensor([4, 0, -1, 5, 1], dtype=torch.int32, device=DEV)
+    slot_x = torch.tensor([0, 0, 1, 2, 2], dtype=torch.int32, device=DEV)
+    out = torch.zeros(5, I, dtype=torch.bfloat16, device=DEV)
+    k.moe_gemv_i8(q.wq.to(DEV), q.scale.to(DEV), x.to(DEV), out, slot_e, slot_x, swiglu=True)
+    y = torch.zeros(5, H, dtype=torch.float32, device=DEV)
+    k.moe_gemv_i8(qd.wq.to(DEV), qd.scale.to(DEV), out, y, slot_e, None)
+
+    def qrow(v):                                   # the per-row activation quantisation of the kernel
+        sc = v.float().abs().amax().clamp_min(1e-8) / 127.0
+        return (v.float() / sc).round().clamp(-127, 127) * sc
+
+    for s in range(5):
+        e, r = int(slot_e[s]), int(slot_x[s])
+        if e < 0:
+            assert float(out[s].abs().max()) == 0.0 and float(y[s].abs().max()) == 0.0
+            continue
+        gu = qrow(x[r]) @ q.dequant()[e].T
+        close(out[s:s + 1], O.silu_mul(gu[None, :I], gu[None, I:]), 2e-2)
+        close(y[s:s + 1], (qrow(out[s].cpu()) @ qd.dequant()[e].T)[None], 2e-2)
+
+
+@pytest.mark.parametrize("T,k,E,H,N", [(300, 4, 8, 256, 512), (64, 2, 16, 128, 264), (1000, 8, 32, 512, 256), (513, 2, 4, 2048, 160)])
+def test_grouped_gemm_from_int8_stacks(T, k, E, H, N):
+    """Grouped kind::i8 tcgen05 GEMM over expert-sorted int8 rows: per-row activation scales times the
+    expert's per-column weight scales in the epilogue; against the dequantised fp32 product per expert.
+    Slots of no local expert (-1) are left out; rows behind the tile list stay untouched (canary)."""
+    from coffin_b200.weights.quant import QWeight
+    kk = K()
+    g = torch.Generator().manual_seed(T + E + 1)
+    idx = torch.randint(-2, E, (T, k), generator=g, dtype=torch.int32)
+    x = (torch.randn(T, H, generator=g) * 0.5).bfloat16()
+    qw = QWeight.quantize(torch.randn(E, N, H, generator=g) * 0.05)
+    d = kk.moe_dispatch(idx.to(DEV), E)
+    pos = d["pos"].cpu().reshape(T, k)
+    xq, xs = kk.quant_rows(x.to(DEV))
+    out = torch.full((T * k, N), 7.0, dtype=torch.bfloat16, device=DEV)
+    y = kk.gemm_i8_grouped(xq.index_select(0, d["src_tok"]), xs.index_select(0, d["src_tok"]), qw.wq.to(DEV),
+                           qw.scale.to(DEV), d, out=out).float().cpu()
+    kk.check_status()
+    xdq = xq.float().cpu() * xs.cpu()[:, None]
+    Wd = qw.dequant()
+    for t in range(0, T, 5):
+        for j in range(k):
+            e = int(idx[t, j])
+            if e < 0:
+                continue
+            ref = xdq[t] @ Wd[e].T
+            got = y[pos[t, j]]
+            assert (got - ref).abs().max() <= 1e-2 * ref.abs().max() + 1e-3
+    n_local = int((idx >= 0).sum())
+    assert bool((y[n_local:] == 7.0).all())
+    y2 = kk.gemm_i8_grouped(xq.index_select(0, d["src_tok"]), xs.index_select(0, d["src_tok"]), qw.wq.to(DEV),
+                            qw.scale.to(DEV), d).float().cpu()
+    assert torch.equal(y2[:n_local], y[:n_local])
+
+
 @pytest.mark.parametrize("T,k,E,H,N", [(300, 4, 8, 256, 512), (64, 2, 16, 128, 264), (1000, 8, 32, 512, 256)])
 def test_moe_dispatch_and_grouped_gemm(T, k, E, H, N):
     """Device-side expert-major dispatch + grouped tcgen05 GEMM against a per-expert fp32 matmul;

@@ -265,6 +265,35 @@ def test_w4a8_model_matches_oracle_with_quantised_weights(name):
 
 
 @torch.no_grad()
+def test_int8_checkpoint_keeps_routed_experts_int8_and_matches_oracle():
+    """A W8A8 state dict (every projection and the expert stacks as ``QWeight``): the routed experts stay int8
+    on the device (slot GEMV in decode, grouped kind::i8 GEMM for the 80-row chunk); the oracle runs on the
+    dequantised weights, the gap is the per-token activation quantisation (and router near-ties)."""
+    from coffin_b200.models.qwen35.model import Qwen35Model
+    from coffin_b200.weights.quant import QWeight, quantize_state_dict
+    cfg = preset("tiny-moe")
+    sd = random_state_dict(cfg, 0)
+    sd_b = {k: (v.to(torch.bfloat16).float() if not k.endswith(("A_log", "dt_bias")) else v) for k, v in sd.items()}
+    sd_q8 = quantize_state_dict(sd_b, "int8")
+    oracle = OracleModel(cfg, {k: (v.dequant() if isinstance(v, QWeight) else v) for k, v in sd_q8.items()})
+    model = Qwen35Model(cfg, sd_q8, max_seq=512, num_slots=2)
+    moe = next(l.moe for l in model.layers if l.moe is not None)
+    assert moe.i8 and moe.gate_up.wq.dtype == torch.int8 and moe.down.wq.dtype == torch.int8
+    toks = _tokens(cfg, 90, seed=33)
+    st = oracle.new_state()
+    ref = oracle.forward(toks[:80], st)[-1]
+    bt = torch.arange(1, 9, dtype=torch.int32, device="cuda")
+    model.zero_state(0)
+    got = model.prefill(toks[:80].cuda(), 0, 0, bt)
+    assert _rel(got, ref) < 0.12
+    for i in range(80, 86):
+        ref = oracle.forward(toks[i:i + 1], st)[-1]
+        model.set_rows(1, [int(toks[i])], [i], [0], [bt.tolist()])
+        _, logits = model.decode(1, graph=i >= 83)
+        assert _rel(logits[0], ref) < 0.25, f"step {i}"
+
+
+@torch.no_grad()
 def test_speculative_decoding_with_mtp_drafter_follows_plain_greedy():
     """Drafts come from the MTP head; whatever their quality, verification keeps the output on the
     model's own greedy path (up to near-ties between the verify and decode kernels)."""
