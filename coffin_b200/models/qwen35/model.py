@@ -391,11 +391,11 @@ class Qwen35Model:
 
     def _row_parallel(self, A, W, scratch: torch.Tensor, swiglu_in: bool = False) -> torch.Tensor:
         """Row-parallel projection + all-reduce.  With a peer-memory region the all-reduce is a
-        reduce-scatter + all-gather over NVLink peer stores: for a prefill chunk the tcgen05 GEMM epilogue
-        scatters its rows to the owning ranks while later tiles are still being multiplied; for the few
+        reduce-scatter + all-gather over NVLink: for a prefill chunk the tcgen05 GEMM epilogue leaves its
+        partial rows in this rank's peer-visible buffer and publishes a sequence number; for the few
         rows of a decode bucket the K-split GEMM (one wave of CTAs, which a 128-row tile per CTA would
-        not fill) writes the partial rows and a small kernel scatters them.  A reduce/gather kernel
-        finishes either way.  Without the region the partial result is all-reduced by NCCL."""
+        not fill) writes the partial rows and a small kernel copies them there.  A reduce/gather kernel
+        on every rank then pulls the rows it owns from all ranks, adds them and stores the sums to every rank.  Without the region the partial result is all-reduced by NCCL."""
         if self.tp is not None and self.tp.pf_rows:
             if A.shape[0] <= 128 and K.SPLITK_GEMM:
                 self._gemm(A, W, out=scratch, swiglu_in=swiglu_in)
@@ -801,8 +801,9 @@ class Qwen35Model:
         append), but the projections run on the tcgen05 GEMM - at these row counts one 128-row tile
         streams each weight once, which is what the GEMV would do eight rows at a time.
 
-        Tensor parallel: the row-parallel projections scatter their rows to the owning ranks from the
-        GEMM epilogue and a reduce/gather kernel completes the all-reduce (the prefill path's exchange;
+        Tensor parallel: the row-parallel projections all-reduce in one kernel per site (peer stores paired
+        with sequence numbers), or through the prefill path's reduce/gather exchange (partial rows left in a
+        peer-visible buffer, owners pull them;
         its sequence numbers live on the device, so the step is captured in a CUDA graph like any
         other).  Expert parallel: the routed-expert output goes through the same exchange."""
         multi = self.tp is not None and (self.tp_world > 1 or self.ep_world > 1)

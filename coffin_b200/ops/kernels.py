@@ -487,8 +487,8 @@ def gemm(A: torch.Tensor, W: torch.Tensor, out: torch.Tensor | None = None,
          residual: torch.Tensor | None = None, bn: int = 0, push=None) -> torch.Tensor | None:
     """Prefill projection on tcgen05: ``out[M, N] = A[M, K] @ W[N, K]^T (+ residual)``, bf16.
 
-    ``push`` (a ``parallel.tp.TpComm`` with a prefill region): nothing is written locally; every
-    output row goes to the inbox of the tensor-parallel rank that owns it (first half of the fused
+    ``push`` (a ``parallel.tp.TpComm`` with a prefill region): nothing is written to ``out``; every
+    output row stays in this rank's peer-visible buffer, from which the rank that owns it pulls it (first half of the fused
     all-reduce; ``TpComm.finish_reduce`` is the second)."""
     M, K = A.shape
     N = W.shape[0]

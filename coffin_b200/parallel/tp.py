@@ -6,8 +6,9 @@ are split by output rows (heads, intermediate channels, vocabulary), ``o_proj`` 
 ``down_proj`` by input columns, so each layer needs two all-reduces of the hidden vector.  During
 decode those all-reduces are not calls: the row-parallel projection pushes its partial sums into
 every rank's inbox and a one-CTA kernel per row (or the consumer phase of the persistent decode
-kernel) adds them (``_C/tp.cuh``).  In prefill the tcgen05 GEMM epilogue scatters its rows to the
-owning ranks and a reduce/gather kernel finishes the all-reduce.  KV heads are replicated when there are fewer of them
+kernel) adds them (``_C/tp.cuh``).  In prefill the tcgen05 GEMM epilogue leaves its partial
+rows in this rank's peer-visible buffer and a reduce/gather kernel on every rank pulls the rows it owns from all
+ranks, adds them and stores the sums to every rank.  KV heads are replicated when there are fewer of them
 than ranks (reference ``local_config``, ``models/qwen35/parallel.py:670-718``; sharding by key
 suffix ``:734-846``; ``RowParallelProjection`` ``:1015-1061``).
 """
