@@ -184,3 +184,29 @@ def test_batched_speculation_is_switched_off_when_memory_is_short(capsys):
     assert not off.spec_batch and off.spec_k == 4
     assert "spec_batch disabled" in capsys.readouterr().out
     assert free_bytes("cpu") == -1
+
+
+def test_replies_carry_every_key_of_the_wire_contract(engine):
+    """The reply keys of the reference's socket protocol (``serving/runtime_parts.py:925-1133``): clients and the
+    HTTP front read them by name."""
+    srv, sock = engine
+    want = {
+        "ping": "ok model model_path arch graph max_seq load_s build_s n_req n_reload backend device native_ops total_ops "
+                "int8 vram_gib batch decode_capacity vision vision_int8 image_max_pixels image_min_pixels max_images "
+                "n_image_req processor queue prefix wall_ms",
+        "generate": "tokens text n_prompt n_new max_new window_full cached_tokens prefill_ms decode_ms decode_tok_s stopped "
+                    "spec_k spec wall_ms",
+        "chat": "text thinking raw tool_calls forced_tool n_prompt n_new max_new window_full cached_tokens prefill_ms "
+                "decode_tok_s stopped spec_k spec n_images image_tokens wall_ms",
+    }
+    replies = {"ping": call(sock, {"op": "ping"}),
+               "generate": call(sock, {"op": "generate", "prompt": "hi", "max_new": 3}),
+               "chat": call(sock, {"op": "chat", "messages": [{"role": "user", "content": "hi"}], "max_new": 3})}
+    for op, keys in want.items():
+        assert replies[op].get("ok", True), replies[op]
+        assert [k for k in keys.split() if k not in replies[op]] == [], op
+    assert set(replies["ping"]["queue"]) >= {"waiting", "running"}
+    lines = list(stream(sock, {"op": "chat_stream", "messages": [{"role": "user", "content": "hi"}], "max_new": 3}))
+    assert lines[0]["type"] == "start" and {"n_prompt", "prompt_opens_think", "forced_tool"} <= set(lines[0])
+    assert lines[-1]["type"] == "done" and {"text", "n_new", "cached_tokens", "prefill_ms"} <= set(lines[-1])
+    assert all(ln["type"] == "token" and "text" in ln for ln in lines[1:-1])
