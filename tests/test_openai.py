@@ -345,3 +345,32 @@ def test_malformed_image_urls_are_400_and_a_front_without_vision_answers_503(ser
     finally:
         oa.STATE["vision"] = True
     assert post(port, {"messages": [{"role": "user", "content": [img]}]})[0] == 200
+
+
+def test_request_field_spellings():
+    """Every accepted spelling of the token limit, the thinking switch and the legacy function fields
+    (reference ``entrypoints/openai/request.py:369-508``)."""
+    from coffin_b200.entrypoints.openai.request import RequestError, include_usage, max_tokens, thinking_flag, tool_plan
+    assert max_tokens({"max_completion_tokens": 5, "max_tokens": 9}, 64) == 5
+    assert max_tokens({"max_tokens": 9, "max_new_tokens": 3}, 64) == 9
+    assert max_tokens({"max_new_tokens": "3"}, 64) == 3 and max_tokens({}, 64) == 64
+    for bad in ({"max_tokens": "x"}, {"max_tokens": 0}, {"max_new_tokens": -1}):
+        with pytest.raises(RequestError):
+            max_tokens(bad, 64)
+    assert thinking_flag({}, True) is True and thinking_flag({}, False) is False
+    assert thinking_flag({"enable_thinking": False}, True) is False
+    assert thinking_flag({"thinking": {"type": "disabled"}}, True) is False
+    assert thinking_flag({"thinking": {"type": "enabled"}}, False) is True
+    assert thinking_flag({"reasoning_effort": "none"}, True) is False and thinking_flag({"reasoning_effort": "high"}, False) is True
+    # the template argument wins over the top-level switch
+    assert thinking_flag({"chat_template_kwargs": {"enable_thinking": False}, "enable_thinking": True}, True) is False
+    fn = {"name": "get_weather", "parameters": {}}
+    tools, forced, single = tool_plan({"functions": [fn], "function_call": {"name": "get_weather"}})
+    assert tools == [{"type": "function", "function": fn}] and forced == "<tool_call>\n<function=get_weather>\n" and not single
+    assert tool_plan({"functions": [fn], "function_call": "none"})[0] is None
+    assert tool_plan({"tools": TOOLS, "tool_choice": "required", "parallel_tool_calls": False})[1:] == ("<tool_call>\n", True)
+    for bad in ({"tool_choice": "required"}, {"tools": TOOLS, "tool_choice": {"type": "function", "function": {"name": "nope"}}},
+                {"tools": [{"type": "function", "function": {}}]}, {"tools": TOOLS, "tool_choice": "sometimes"}):
+        with pytest.raises(RequestError):
+            tool_plan(bad)
+    assert include_usage({"stream_options": {"include_usage": True}}) and not include_usage({"stream_options": None})
