@@ -159,11 +159,11 @@ __device__ __forceinline__ void tp_pull8(const TpComm& c, int site, int64_t off,
 // ---------------------------------------------------------------------------------------------
 // Prefill: row-parallel GEMM -> all-reduce as reduce-scatter + all-gather over peer memory.
 //
-// The GEMM epilogue (gemm_tc.cu) stores every bf16 output row straight into the inbox of the rank
-// that owns the row (rows are cut into `world` equal slices), tile by tile while later tiles are
-// still being multiplied; a small kernel on each rank then adds the `world` partial slices it
-// received in rank order (+ an optional residual) and stores the reduced rows into every rank's
-// result buffer.  Two flag arrays carry a sequence number that the host advances once per use (all
+// The GEMM epilogue (gemm_tc.cu, gemm_tc2.cu) leaves every bf16 partial row in this rank's own
+// peer-visible buffer ("inbox") at its row index and the last CTA publishes the sequence number to
+// every rank; rows are cut into `world` equal slices, and a small kernel on each rank then PULLS the
+// slice it owns from every rank's buffer (coalesced 16-byte peer loads), adds the partial rows in rank
+// order (+ an optional residual) and stores the reduced rows into every rank's result buffer.  Two flag arrays carry a sequence number that the host advances once per use (all
 // ranks run the same sequence of calls), so nothing is reset between uses; waits are bounded and
 // set the status word.  This replaces the reference's per-projection gloo all-reduce in prefill
 // (models/qwen35/parallel.py:1015-1061) and is what NCCL all-reduce would otherwise do between
