@@ -4,8 +4,11 @@
 // the gated delta-rule update of the fp32 recurrent state, and the gated RMSNorm of the output.
 // The reference runs these as 4-5 launches with fp32 scratch between them
 // (models/qwen35/linear_attn.py:358-396; kernels backends/corex/kernels/linear_attn.cu:172-744,
-// delta.cu:86-194).  Prefill: the chunked (UT-transform) form of ops/delta.py:57-178 as three
-// kernels: per-token prep, per-chunk triangular system, sequential inter-chunk scan.
+// delta.cu:86-194).  Prefill: the chunked (UT-transform) form of ops/delta.py:57-178 as two
+// kernels: the per-chunk triangular system, which also computes conv + SiLU, the q/k norms, beta and
+// the log decay from the raw projection rows, and the sequential inter-chunk scan (bf16 operands on
+// mma.m16n8k16, fp32 state in registers, a three-stage ring of whole-chunk operand sets); the
+// earlier forms (a prep kernel of its own, TF32 products, SIMT) stay selectable for A/B runs.
 //
 // Conv memory is a ring of the last 16 raw projection rows per sequence slot, indexed by
 // position & 15: a step writes only slot pos&15 and reads the three before it, so the CTAs of
