@@ -57,10 +57,16 @@ def engine_argv(args, extra: list[str]) -> list[str]:
     return argv + extra
 
 
-def wait_ping(sock: str, timeout: float) -> bool:
+def wait_ping(sock: str, timeout: float, procs: list | None = None) -> bool:
+    """Poll ``ping`` until rank 0 answers.  Gives up early when a rank process has already exited: the
+    others would wait in their first collective until the start limit runs out."""
     from ..serving.transport import call
     deadline = time.monotonic() + timeout
     while time.monotonic() < deadline:
+        dead = [i for i, p in enumerate(procs or []) if p.poll() is not None]
+        if dead:
+            print(f"rank(s) {dead} exited during start-up (codes {[procs[i].returncode for i in dead]})", file=sys.stderr)
+            return False
         try:
             if call(sock, {"op": "ping"}, timeout=5).get("ok"):
                 return True
@@ -104,7 +110,7 @@ def main(argv=None) -> int:
     procs = [subprocess.Popen(engine_argv(args, extra), env=rank_env(r, args.gpus, port, args.parallel))
              for r in range(args.gpus)]
     try:
-        if not wait_ping(args.sock, args.start_timeout):
+        if not wait_ping(args.sock, args.start_timeout, procs):
             print("engine did not answer ping", file=sys.stderr)
             return 3
         print(f"engine up: {args.gpus} ranks, {args.parallel}, socket {args.sock}", flush=True)

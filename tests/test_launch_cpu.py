@@ -1,0 +1,45 @@
+"""Host logic of the multi-rank launcher: per-rank environment, engine command line, early give-up when a
+rank dies during start-up, teardown by the ranks' own PIDs (reference: tools/launch_occamy_ep.sh:51-131)."""
+import subprocess
+import sys
+import time
+from types import SimpleNamespace
+
+from coffin_b200.tools import launch
+
+
+def test_rank_env_and_engine_command_line():
+    env = launch.rank_env(2, 4, 29511, "ep", base={"PATH": "/bin", "RANK": "9"})
+    assert env["RANK"] == "2" and env["LOCAL_RANK"] == "2" and env["WORLD_SIZE"] == "4"
+    assert env["MASTER_ADDR"] == "127.0.0.1" and env["MASTER_PORT"] == "29511" and env["COFFIN_PARALLEL"] == "ep"
+    assert env["PATH"] == "/bin" and "CUDA_VISIBLE_DEVICES" not in env     # every rank sees every GPU (peer memory)
+    argv = launch.engine_argv(SimpleNamespace(sock="/tmp/x.sock", model="/ckpt", preset=None), ["--max-seq", "4096"])
+    assert argv[:4] == [sys.executable, "-m", "coffin_b200.entrypoints.cli.runtime", "--serve"]
+    assert argv[4:] == ["--sock", "/tmp/x.sock", "--model", "/ckpt", "--max-seq", "4096"]
+    assert 1024 < launch.free_port() < 65536
+
+
+def test_start_up_gives_up_when_a_rank_has_exited(tmp_path, capsys):
+    alive = subprocess.Popen([sys.executable, "-c", "import time; time.sleep(30)"])
+    dead = subprocess.Popen([sys.executable, "-c", "import sys; sys.exit(7)"])
+    dead.wait(10)
+    t0 = time.monotonic()
+    try:
+        assert launch.wait_ping(str(tmp_path / "none.sock"), 20.0, [alive, dead]) is False
+        assert time.monotonic() - t0 < 5.0 and "rank(s) [1] exited" in capsys.readouterr().err
+        # nobody listens and nobody died: the limit itself ends the wait
+        assert launch.wait_ping(str(tmp_path / "none.sock"), 1.0, [alive]) is False
+    finally:
+        launch.stop([alive, dead], grace=5.0)
+    assert alive.poll() is not None
+
+
+def test_stop_kills_a_rank_that_ignores_sigterm():
+    stubborn = subprocess.Popen([sys.executable, "-c",
+                                 "import signal, time; signal.signal(signal.SIGTERM, signal.SIG_IGN); print('up', flush=True); time.sleep(60)"],
+                                stdout=subprocess.PIPE, text=True)
+    assert stubborn.stdout.readline().strip() == "up"
+    t0 = time.monotonic()
+    launch.stop([stubborn], grace=1.0)
+    stubborn.wait(5)
+    assert stubborn.returncode is not None and time.monotonic() - t0 < 6.0
