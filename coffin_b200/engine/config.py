@@ -38,6 +38,7 @@ class EngineConfig:
     image_max_pixels: int = 1024 * 1024
     image_min_pixels: int = 32 * 32
     max_images: int = 4
+    max_image_bytes: int = 8 << 20     # decoded bytes allowed per image on the engine side
     batch_window_ms: float = 0.0       # hold a lone decode this long for companions
     warmup: bool = True                # serving: run a prefill chunk and capture every decode bucket before the first request
 

@@ -29,8 +29,12 @@ def parser() -> argparse.ArgumentParser:
     ap.add_argument("--model", default=os.environ.get("ENGINE_MODEL", ""), help="checkpoint directory")
     ap.add_argument("--preset", default="", help="serve a random-init model of a named shape")
     ap.add_argument("--device", default="cuda", choices=["cuda", "cpu"])
+    ap.add_argument("--backend", default="", help="accepted for command-line compatibility: this engine has one backend "
+                                                  "(sm_100a; `--device cpu` selects the fp32 oracle twin)")
     ap.add_argument("--max-seq", type=int, default=None)
     ap.add_argument("--quant", default=None, choices=["none", "int8", "w4a8"])
+    ap.add_argument("--fp16", action="store_true", help="keep 16-bit weights (the default here; same as --quant none)")
+    ap.add_argument("--block-size", type=int, default=64, help="KV block size in tokens (the kernels are built for 64)")
     ap.add_argument("--kv-dtype", default=None, choices=["bf16", "int8"], help="KV pool storage (int8: per-(token, head) scales)")
     ap.add_argument("--no-prefix-cache", action="store_true")
     ap.add_argument("--num-blocks", type=int, default=None)
@@ -38,6 +42,8 @@ def parser() -> argparse.ArgumentParser:
     ap.add_argument("--snapshot-interval", type=int, default=None)
     ap.add_argument("--spec-k", type=int, default=None)
     ap.add_argument("--spec-batch", action="store_true")
+    ap.add_argument("--spec-min-ctx", type=int, default=None,
+                    help="rows with fewer cached tokens than this do not draft yet (0 = always)")
     ap.add_argument("--spec-sparse-k", type=int, default=0, help="approximate batched verify over the k best history blocks (refused when > 0: not built)")
     ap.add_argument("--chunk", type=int, default=None)
     ap.add_argument("--prefill-quantum", type=int, default=None)
@@ -46,9 +52,20 @@ def parser() -> argparse.ArgumentParser:
     ap.add_argument("--max-seconds", type=float, default=None)
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--no-vision", action="store_true")
+    ap.add_argument("--vision-int8", action="store_true",
+                    help="accepted for compatibility: the tower stays bf16 here (0.6 GiB of 180)")
+    ap.add_argument("--image-max-pixels", type=int, default=None, help="largest image served, in pixels (bigger ones are downsampled)")
+    ap.add_argument("--image-min-pixels", type=int, default=None, help="smallest image after the upscale, in pixels")
+    ap.add_argument("--max-images", type=int, default=None, help="images accepted in one request")
+    ap.add_argument("--max-image-bytes", type=int, default=None, help="decoded bytes allowed per image")
+    ap.add_argument("--no-bench", action="store_true", help="accepted for compatibility: the engine runs no benchmark at start")
     ap.add_argument("--vision", choices=("tiny", "default"), default=None,
                     help="attach a vision tower with random weights of this geometry (checkpoints with model.visual.* tensors get theirs)")
-    ap.add_argument("-n", type=int, default=64, help="tokens for generate/chat/bench")
+    ap.add_argument("-n", "--max-new", dest="n", type=int, default=64, help="tokens for generate/chat/bench")
+    ap.add_argument("--prompt", default="", help="prompt for generate (same as the positional text)")
+    ap.add_argument("--user", default="", help="user message for chat (same as the positional text)")
+    ap.add_argument("--think", action="store_true", help="enable thinking mode (the default; --no-thinking turns it off)")
+    ap.add_argument("--print-ids", action="store_true", help="print the generated token ids (accept rates are compared by id)")
     ap.add_argument("--temperature", type=float, default=0.0)
     ap.add_argument("--system", default="")
     ap.add_argument("--tools", default="", help="JSON file with an OpenAI tools array")
@@ -58,10 +75,20 @@ def parser() -> argparse.ArgumentParser:
 
 def engine_config(args):
     from ...engine.config import EngineConfig
+    if args.block_size != 64:
+        raise SystemExit(f"--block-size {args.block_size}: the attention and cache kernels are built for blocks of 64 tokens")
+    if args.backend and args.backend not in ("auto", "sm_100a", "cuda", "b200"):
+        raise SystemExit(f"--backend {args.backend!r}: this engine has one backend (sm_100a); use --device cpu for the oracle twin")
+    if args.fp16 and args.quant not in (None, "none"):
+        raise SystemExit("--fp16 contradicts --quant " + args.quant)
+    if args.vision_int8:
+        print("[serve] --vision-int8 ignored: the vision tower stays bf16", flush=True)
     return EngineConfig.from_env(
         max_seq=args.max_seq, quant=args.quant, kv_dtype=args.kv_dtype, prefix_cache=False if args.no_prefix_cache else None,
         num_blocks=args.num_blocks, snapshots=args.snapshots, snapshot_interval=args.snapshot_interval,
-        spec_k=args.spec_k, spec_batch=True if args.spec_batch else None, spec_sparse_k=args.spec_sparse_k or None, chunk=args.chunk,
+        spec_k=args.spec_k, spec_batch=True if args.spec_batch else None, spec_sparse_k=args.spec_sparse_k or None,
+        spec_min_ctx=args.spec_min_ctx, image_max_pixels=args.image_max_pixels, image_min_pixels=args.image_min_pixels,
+        max_images=args.max_images, max_image_bytes=args.max_image_bytes, chunk=args.chunk,
         prefill_quantum=args.prefill_quantum, max_num_seqs=args.max_num_seqs,
         max_num_batched_tokens=args.max_num_batched_tokens, max_seconds=args.max_seconds,
         graph=False if args.no_graph else None, vision=False if args.no_vision else None)
@@ -163,12 +190,12 @@ def main(argv=None) -> int:
     from ...serving.transport import call
     req: dict = {"op": args.cmd}
     if args.cmd in ("generate", "bench", "profile", "ops", "spec", "tokenize"):
-        req.update({"prompt": args.text or "Hello", "n": args.n, "max_new": args.n, "temperature": args.temperature})
+        req.update({"prompt": args.text or args.prompt or "Hello", "n": args.n, "max_new": args.n, "temperature": args.temperature})
         if args.spec_k:
             req["spec_k"] = args.spec_k
     elif args.cmd == "chat":
         msgs = ([{"role": "system", "content": args.system}] if args.system else []) + \
-               [{"role": "user", "content": args.text or "Hello"}]
+               [{"role": "user", "content": args.text or args.user or "Hello"}]
         req.update({"messages": msgs, "max_new": args.n, "temperature": args.temperature,
                     "enable_thinking": not args.no_thinking})
         if args.tools:
@@ -182,6 +209,8 @@ def main(argv=None) -> int:
         if rep.get("thinking"):
             print(f"[thinking] {rep['thinking']}")
         print(rep.get("text", ""))
+        if args.print_ids:
+            print(f"[ids] {rep.get('tokens')}")
         for c in rep.get("tool_calls") or []:
             print(f"[tool_call] {json.dumps(c, ensure_ascii=False)}")
         print(f"[{rep.get('n_prompt')} prompt, {rep.get('n_new')} new, cached {rep.get('cached_tokens')}, "

@@ -20,14 +20,20 @@ from ..utils.mm_input import MMInput, find_image_spans, image_digest, mrope_posi
 MAX_DECODE_PIXELS = 64 * 1024 * 1024
 
 
-def decode_image(b64: str, min_pixels: int, max_pixels: int, factor: int) -> tuple[torch.Tensor, bytes]:
-    """base64 -> ``[3, H, W]`` float tensor in [0, 1] (sides multiples of ``factor``) and the raw bytes."""
+def decode_image(b64: str, min_pixels: int, max_pixels: int, factor: int, max_bytes: int = 0) -> tuple[torch.Tensor, bytes]:
+    """base64 -> ``[3, H, W]`` float tensor in [0, 1] (sides multiples of ``factor``) and the raw bytes.
+    ``max_bytes`` > 0: decoded payloads above it are refused with 413 (the socket can be reached without the
+    HTTP front, so the engine keeps its own limit)."""
     from .runtime import MMError
     from ..models.qwen35.vision import smart_resize
+    if max_bytes > 0 and len(b64) * 3 // 4 - 2 > max_bytes:
+        raise MMError(f"image larger than {max_bytes} bytes", 413)
     try:
         raw = base64.b64decode(b64, validate=True)
     except (binascii.Error, ValueError):
         raise MMError("image payload is not valid base64", 400) from None
+    if max_bytes > 0 and len(raw) > max_bytes:
+        raise MMError(f"image larger than {max_bytes} bytes", 413)
     try:
         from PIL import Image, ImageOps
         Image.MAX_IMAGE_PIXELS = MAX_DECODE_PIXELS
@@ -74,7 +80,8 @@ def build_mm_input(srv, images: list[dict], prompt: list[int]):
         image_token = srv.tok.encode("<|image_pad|>")[0]
     embeds, grids, digests = [], [], []
     for im in images:
-        t, raw = decode_image(im["b64"], recipe.min_pixels, recipe.max_pixels, recipe.factor)
+        t, raw = decode_image(im["b64"], recipe.min_pixels, recipe.max_pixels, recipe.factor,
+                              getattr(srv.cfg, "max_image_bytes", 0))
         patches, grid = patchify(t, vc, recipe.mean, recipe.std)
         embeds.append(tower.forward(patches, grid))
         grids.append(grid)

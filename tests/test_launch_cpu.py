@@ -43,3 +43,22 @@ def test_stop_kills_a_rank_that_ignores_sigterm():
     launch.stop([stubborn], grace=1.0)
     stubborn.wait(5)
     assert stubborn.returncode is not None and time.monotonic() - t0 < 6.0
+
+
+def test_runtime_cli_accepts_the_reference_flag_names():
+    """Flags of the reference's command line that map onto this engine's options (or are accepted and ignored)."""
+    import pytest
+    from coffin_b200.entrypoints.cli.runtime import engine_config, parser
+    args = parser().parse_args(["--serve", "--spec-min-ctx", "512", "--image-max-pixels", "500000", "--image-min-pixels", "4096",
+                                "--max-images", "2", "--max-image-bytes", "1000", "--block-size", "64", "--fp16", "--no-bench",
+                                "--backend", "auto", "--vision-int8"])
+    cfg = engine_config(args)
+    assert (cfg.spec_min_ctx, cfg.image_max_pixels, cfg.image_min_pixels, cfg.max_images, cfg.max_image_bytes) == \
+        (512, 500000, 4096, 2, 1000)
+    a = parser().parse_args(["generate", "--prompt", "hello", "--max-new", "7", "--print-ids"])
+    assert a.cmd == "generate" and a.prompt == "hello" and a.n == 7 and a.print_ids
+    a = parser().parse_args(["chat", "--user", "hi", "--think"])
+    assert a.user == "hi" and a.think and not a.no_thinking
+    for bad in (["--block-size", "32"], ["--backend", "corex"], ["--fp16", "--quant", "int8"]):
+        with pytest.raises(SystemExit):
+            engine_config(parser().parse_args(["--serve", *bad]))

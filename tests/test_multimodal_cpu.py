@@ -124,3 +124,16 @@ def test_decode_image_budget_and_errors():
         decode_image("!!!notbase64", 1024, 4096, 32)
     with pytest.raises(MMError):
         decode_image(base64.b64encode(b"not an image").decode(), 1024, 4096, 32)
+
+
+def test_engine_side_image_byte_limit():
+    from PIL import Image
+    from coffin_b200.serving.runtime import MMError
+    buf = io.BytesIO()
+    Image.new("RGB", (64, 64), (0, 255, 0)).save(buf, format="PNG")
+    b64 = base64.b64encode(buf.getvalue()).decode()
+    n = len(buf.getvalue())
+    decode_image(b64, 32 * 32, 64 * 64, 32, max_bytes=n)                 # exactly at the limit
+    with pytest.raises(MMError) as e:
+        decode_image(b64, 32 * 32, 64 * 64, 32, max_bytes=n - 1)
+    assert e.value.status == 413
