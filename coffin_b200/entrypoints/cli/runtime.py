@@ -68,7 +68,7 @@ def parser() -> argparse.ArgumentParser:
     ap.add_argument("--print-ids", action="store_true", help="print the generated token ids (accept rates are compared by id)")
     ap.add_argument("--temperature", type=float, default=0.0)
     ap.add_argument("--system", default="")
-    ap.add_argument("--tools", default="", help="JSON file with an OpenAI tools array")
+    ap.add_argument("--tools", default="", help="JSON file with an OpenAI tools array, or `demo` for the built-in demo tools")
     ap.add_argument("--no-thinking", action="store_true")
     return ap
 
@@ -198,7 +198,10 @@ def main(argv=None) -> int:
                [{"role": "user", "content": args.text or args.user or "Hello"}]
         req.update({"messages": msgs, "max_new": args.n, "temperature": args.temperature,
                     "enable_thinking": not args.no_thinking})
-        if args.tools:
+        if args.tools == "demo":            # the two demo tools of the agent loop (get_weather, multiply)
+            from ..agent import DEMO_TOOLS
+            req["tools"] = DEMO_TOOLS
+        elif args.tools:
             req["tools"] = json.load(open(args.tools))
     try:
         rep = call(args.sock, req)
