@@ -228,3 +228,33 @@ def test_shape_and_expansion_traces_print_once_per_shape(capsys):
     said = capsys.readouterr().out
     assert said.count("[moe-shape]") == 2 and "rows=4096 experts=128 n=1536 k=2048 weights=int4" in said
     assert "[wq-expand] (128, 1536, 2048) kept=False" in said and "test_engine_cpu.py" in said
+
+
+@pytest.mark.parametrize("seed", [0, 1, 2])
+def test_random_arrivals_on_a_tight_pool_match_solo_and_leak_nothing(seed):
+    """Requests with random lengths, shared prefixes and token limits arrive at random steps on a pool that forces
+    evictions and preemptions; every sequence still produces its solo tokens and every block comes back."""
+    import random
+    rng = random.Random(seed)
+    eng = engine(num_blocks=14, num_slots=3, chunk=64, prefill_quantum=64, max_num_batched_tokens=128, snapshot_interval=64)
+    shared = prompt(64 * rng.randint(1, 2), 900 + seed)
+    plan = []
+    for i in range(7):
+        own = prompt(rng.randint(5, 150), 1000 * seed + i)
+        p = (shared + own) if rng.random() < 0.5 else own
+        plan.append((rng.randint(0, 25), p, rng.randint(1, 6)))
+    plan.sort(key=lambda t: t[0])
+    live, step = [], 0
+    while plan or any(not s.finished for _, s, _ in live):
+        while plan and plan[0][0] <= step:
+            _, p, n = plan.pop(0)
+            live.append((p, eng.add_request(p, SamplingParams(max_tokens=n)), n))
+        eng.step()
+        eng.bm.pool.check()
+        step += 1
+        assert step < 3000
+    for p, s, n in live:
+        assert s.output == solo(p, n), (len(p), n)
+    eng.bm.radix.clear()
+    eng.bm.pool.check()
+    assert eng.bm.pool.used_blocks == 0 and len(eng.scheduler.free_slots) == 3
