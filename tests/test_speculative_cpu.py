@@ -134,3 +134,35 @@ def test_engine_speculation_stops_at_eos_and_max_tokens():
     assert s.output == ref[:7] and s.finish_reason == "length"
     eng.reset()
     eng.bm.pool.check()
+
+
+@torch.no_grad()
+def test_speculation_survives_preemption_on_a_tight_pool():
+    """Three rows that each grow into a third block on a pool of 8: rows are preempted and recomputed while
+    the others keep drafting; the tokens stay those of plain greedy decoding and every block comes back."""
+    import random
+    from coffin_b200.engine.config import EngineConfig
+    from coffin_b200.engine.llm_engine import LLMEngine
+    from coffin_b200.engine.sequence import SamplingParams
+    preempted = 0
+    for seed in (0, 4, 9):
+        rng = random.Random(seed)
+        model = OracleEngineModel(CFG, SD, max_seq=512, num_slots=3, num_blocks=9)
+        eng = LLMEngine(model, EngineConfig(max_seq=512, max_num_seqs=3, graph=False, prefix_cache=False, spec_k=3, spec_batch=True))
+        prompts = []
+        for _ in range(3):
+            n = rng.randint(118, 127)
+            unit = [rng.randrange(CFG.vocab_size) for _ in range(rng.randint(3, 9))]
+            prompts.append((unit * (n // len(unit) + 1))[:n])
+        limits = [rng.randint(8, 14) for _ in range(3)]
+        seqs = [eng.add_request(p, SamplingParams(max_tokens=n)) for p, n in zip(prompts, limits)]
+        for _ in range(3000):
+            if all(s.finished for s in seqs):
+                break
+            eng.step()
+            eng.bm.pool.check()
+        for p, s, n in zip(prompts, seqs, limits):
+            assert s.output == OracleModel(CFG, SD).generate(p, n)[0]
+        assert eng.bm.pool.used_blocks == 0 and eng.runner.stats()["spec"]["accepted"] > 0
+        preempted += eng.n_preempt
+    assert preempted > 0
