@@ -317,13 +317,24 @@ class Server:
         self.n_req += 1
         yield {"type": "start", "n_prompt": len(prompt), "prompt_opens_think": opens, "forced_tool": forced}
         dec = IncrementalDecoder(self.tok)
+        waited = 0.0
         try:
             while True:
-                kind, val = outq.get(timeout=3600)
+                # {"type": "tick"} lines are not part of the protocol: they hand control to the transport while
+                # nothing printable is produced (a long prefill, tokens that complete no character), so that it can
+                # notice a client that went away and close this generator, which aborts the sequence
+                try:
+                    kind, val = outq.get(timeout=0.5)
+                except queue.Empty:
+                    waited += 0.5
+                    if waited > 3600:
+                        raise
+                    yield {"type": "tick"}
+                    continue
+                waited = 0.0
                 if kind == "token":
                     piece = dec.push(val)
-                    if piece:
-                        yield {"type": "token", "text": piece}
+                    yield {"type": "token", "text": piece} if piece else {"type": "tick"}
                 elif kind == "done":
                     break
                 elif kind == "error":

@@ -11,6 +11,7 @@ from __future__ import annotations
 
 import json
 import os
+import select
 import socket
 import threading
 import time
@@ -36,6 +37,17 @@ def _recv_line(conn: socket.socket) -> bytes:
     return buf
 
 
+def _peer_closed(conn: socket.socket) -> bool:
+    """True when the other end of a stream connection has closed it (an orderly shutdown reads as b"")."""
+    try:
+        readable, _, _ = select.select([conn], [], [], 0)
+        return bool(readable) and conn.recv(1, socket.MSG_PEEK | socket.MSG_DONTWAIT) == b""
+    except (BlockingIOError, InterruptedError):
+        return False
+    except OSError:
+        return True
+
+
 def _serve_connection(srv, conn: socket.socket, fanout=None) -> None:
     try:
         req = json.loads(_recv_line(conn).decode() or "{}")
@@ -43,8 +55,25 @@ def _serve_connection(srv, conn: socket.socket, fanout=None) -> None:
         if fanout is not None:
             fanout(req)
         if req.get("op") == "chat_stream":
-            for line in srv.stream_chat(req):
-                conn.sendall((json.dumps(line, ensure_ascii=False) + "\n").encode())
+            lines = srv.stream_chat(req)
+            try:
+                gone = False
+                for line in lines:
+                    if line.get("type") == "tick":       # nothing to send: see whether the client is still there
+                        if fanout is None and _peer_closed(conn):
+                            print("[serve] chat_stream: client went away, sequence aborted", flush=True)
+                            return
+                        continue
+                    if gone:
+                        continue
+                    try:
+                        conn.sendall((json.dumps(line, ensure_ascii=False) + "\n").encode())
+                    except (BrokenPipeError, ConnectionResetError):
+                        if fanout is None:
+                            raise
+                        gone = True      # the other ranks replay this request step for step: finish it, send nothing
+            finally:
+                lines.close()        # a client that went away mid-stream: the generator aborts its sequence
             print(f"[serve] chat_stream -> {round((time.time() - t0) * 1000, 1)}ms", flush=True)
             return
         rep = srv.handle(req)

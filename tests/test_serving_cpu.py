@@ -210,3 +210,30 @@ def test_replies_carry_every_key_of_the_wire_contract(engine):
     assert lines[0]["type"] == "start" and {"n_prompt", "prompt_opens_think", "forced_tool"} <= set(lines[0])
     assert lines[-1]["type"] == "done" and {"text", "n_new", "cached_tokens", "prefill_ms"} <= set(lines[-1])
     assert all(ln["type"] == "token" and "text" in ln for ln in lines[1:-1])
+
+
+def test_client_that_disconnects_mid_stream_frees_its_sequence(engine):
+    """A stream client reads the first lines and closes the socket: the engine aborts the sequence (slot and
+    blocks come back) and keeps serving."""
+    import socket
+    srv, sock = engine
+    c = socket.socket(socket.AF_UNIX, socket.SOCK_STREAM)
+    c.connect(sock)
+    c.sendall((json.dumps({"op": "chat_stream", "messages": [{"role": "user", "content": "count slowly"}],
+                           "max_new": 400}) + "\n").encode())
+    f = c.makefile("r")
+    assert json.loads(f.readline())["type"] == "start"
+    before = srv.engine.runner.n_decode_steps
+    f.close()
+    c.close()
+    deadline = time.time() + 20
+    while time.time() < deadline:
+        q = call(sock, {"op": "ping"})["queue"]
+        if q["running"] == 0 and q["waiting"] == 0:
+            break
+        time.sleep(0.05)
+    assert q["running"] == 0 and q["waiting"] == 0
+    assert len(srv.engine.scheduler.free_slots) == 4
+    assert srv.engine.runner.n_decode_steps - before < 300          # cut short, not decoded to the limit
+    rep = call(sock, {"op": "generate", "prompt": "still there?", "max_new": 3})
+    assert rep["ok"] and rep["n_new"] == 3
