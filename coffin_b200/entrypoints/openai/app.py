@@ -219,6 +219,12 @@ class Handler(BaseHTTPRequestHandler):
 
     def _chat_stream(self, req: dict, cid: str, created: int, model: str, single: bool, want_usage: bool) -> None:
         lines = STATE["engine"].stream(req)
+        try:
+            self._relay_stream(lines, cid, created, model, single, want_usage)
+        finally:
+            lines.close()      # closes the engine connection: an HTTP client that went away ends its sequence there
+
+    def _relay_stream(self, lines, cid: str, created: int, model: str, single: bool, want_usage: bool) -> None:
         first = next(lines, None)
         if first is None:
             self._error(503, "engine closed the stream", "server_error")
