@@ -44,7 +44,7 @@ def _peer_closed(conn: socket.socket) -> bool:
         return bool(readable) and conn.recv(1, socket.MSG_PEEK | socket.MSG_DONTWAIT) == b""
     except (BlockingIOError, InterruptedError):
         return False
-    except OSError:
+    except (OSError, ValueError):       # ValueError: the descriptor is already closed on this side
         return True
 
 

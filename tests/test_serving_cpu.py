@@ -237,3 +237,19 @@ def test_client_that_disconnects_mid_stream_frees_its_sequence(engine):
     assert srv.engine.runner.n_decode_steps - before < 300          # cut short, not decoded to the limit
     rep = call(sock, {"op": "generate", "prompt": "still there?", "max_new": 3})
     assert rep["ok"] and rep["n_new"] == 3
+
+
+def test_peer_closed_probe_tells_silence_from_a_closed_connection():
+    import socket
+    from coffin_b200.serving.transport import _peer_closed
+    a, b = socket.socketpair(socket.AF_UNIX, socket.SOCK_STREAM)
+    try:
+        assert _peer_closed(a) is False                 # open and silent
+        b.sendall(b"x")
+        assert _peer_closed(a) is False                 # data waiting is not a close (and is not consumed)
+        assert a.recv(1) == b"x"
+        b.close()
+        assert _peer_closed(a) is True
+    finally:
+        a.close()
+    assert _peer_closed(a) is True                      # a dead descriptor reads as gone, not as an exception
